@@ -86,7 +86,7 @@ def test_strip_equals_dense_columns():
     svh = rng.uniform(0.01, 0.05, 384).astype(np.float16)
     w = exl3.decode_weight(tr, "3inst", suh, svh)
     for s in range(3):
-        assert np.array_equal(exl3.decode_strip(tr, s, "3inst", suh, svh), w[:, 128 * s:128 * s + 128])
+        np.testing.assert_allclose(exl3.decode_strip(tr, s, "3inst", suh, svh), w[:, 128 * s:128 * s + 128], rtol=1e-12, atol=1e-15)
 
 
 def test_unpack_signs():
