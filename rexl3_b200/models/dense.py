@@ -1,0 +1,390 @@
+"""Dense GQA decoder (Llama / Qwen3-style): config, EXL3 weight sets, fp32 reference executor, sm_100a executor.
+
+Layer: RMSNorm -> fused qkv EXL3 linear -> (q/k norm) RoPE -> paged GQA attention -> o_proj -> residual ->
+RMSNorm -> fused gate|up EXL3 linear -> SwiGLU -> down_proj -> residual; final RMSNorm -> EXL3 lm_head.
+The reference engine's Qwen executor plays the same role (crates/model/src/forward.rs:986-1301); the launch
+schedule here is different: every elementwise stage is fused into the finish kernel of the GEMM before it, so a
+layer is 9 launches (4 GEMMs, 4 finishes, attention + merge).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field, asdict
+
+import numpy as np
+import torch
+
+from ..format import exl3
+
+PAGE = 64
+
+
+@dataclass
+class DenseConfig:
+    n_layers: int
+    d_model: int
+    n_q: int
+    n_kv: int
+    head_dim: int
+    ffn: int                 # true FFN width (may be padded up to a multiple of 128 in storage)
+    vocab: int
+    eps: float = 1e-6
+    rope_theta: float = 1e4
+    qk_norm: bool = False
+    bits: float = 4.0
+    head_bits: float | None = None
+    codebook: str = "3inst"
+    name: str = "dense-gqa"
+
+    @property
+    def ffn_padded(self) -> int:
+        return (self.ffn + 127) // 128 * 128
+
+    @property
+    def vocab_padded(self) -> int:
+        return (self.vocab + 127) // 128 * 128
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.n_q + 2 * self.n_kv) * self.head_dim
+
+    def to_json(self) -> dict:
+        return asdict(self)
+
+    def weight_params(self) -> int:
+        per = self.d_model * self.qkv_width + self.n_q * self.head_dim * self.d_model + 3 * self.d_model * self.ffn_padded
+        return per * self.n_layers + self.vocab_padded * self.d_model
+
+    def kv_bytes_per_token(self, elem_bytes: int = 2) -> int:
+        return 2 * self.n_kv * self.head_dim * elem_bytes * self.n_layers
+
+
+CONFIGS = {
+    # BASELINE config 1: CPU plumbing model
+    "tiny-llama": DenseConfig(n_layers=2, d_model=256, n_q=4, n_kv=2, head_dim=64, ffn=688, vocab=2048, eps=1e-6, rope_theta=1e4,
+                              bits=4.0, name="tiny-llama"),
+    # BASELINE config 2: 27B-class dense GQA decoder
+    "dense-27b": DenseConfig(n_layers=64, d_model=5120, n_q=40, n_kv=8, head_dim=128, ffn=17408, vocab=151936, eps=1e-6, rope_theta=1e6,
+                             bits=4.0, name="dense-27b"),
+    # small GPU test model with the production head geometry
+    "test-hd128": DenseConfig(n_layers=2, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hd128"),
+}
+
+
+@dataclass
+class HostLinear:
+    trellis: np.ndarray
+    suh: np.ndarray
+    svh: np.ndarray
+    bias: np.ndarray | None = None
+    codebook: str = "3inst"
+
+    def dense(self) -> np.ndarray:
+        """Effective [K, N] float32 weight."""
+        return exl3.decode_weight(self.trellis, self.codebook, self.suh.astype(np.float64), self.svh.astype(np.float64)).astype(np.float32)
+
+
+@dataclass
+class HostLayer:
+    attn_norm: np.ndarray
+    qkv: HostLinear
+    o: HostLinear
+    ffn_norm: np.ndarray
+    gate_up: HostLinear
+    down: HostLinear
+    q_norm: np.ndarray | None = None
+    k_norm: np.ndarray | None = None
+
+
+@dataclass
+class HostWeights:
+    cfg: DenseConfig
+    embed: np.ndarray            # float32 [vocab, d] (stored bf16 on device)
+    layers: list = field(default_factory=list)
+    final_norm: np.ndarray = None
+    lm_head: HostLinear = None
+
+
+def _bf16_round(a: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+def random_linear(K: int, N: int, bits: float, rng: np.random.Generator, codebook: str = "3inst", out_scale: float = 0.02,
+                  zero_cols_from: int | None = None, zero_rows_from: int | None = None) -> HostLinear:
+    """Random-init EXL3 layer: any random bit ring is a valid trellis; suh = +-1 signs, svh = +-out_scale."""
+    b = exl3.Bits.of(bits)
+    if not b.is_integer and codebook != "mul1":
+        codebook = "mul1"
+    trellis = rng.integers(-32768, 32768, size=(K // 16, N // 16, b.tile_words), dtype=np.int16)
+    suh = np.where(rng.random(K) < 0.5, -1.0, 1.0).astype(np.float16)
+    svh = (np.where(rng.random(N) < 0.5, -1.0, 1.0) * out_scale).astype(np.float16)
+    if zero_cols_from is not None:
+        svh[zero_cols_from:] = 0
+    if zero_rows_from is not None:
+        suh[zero_rows_from:] = 0
+    return HostLinear(trellis, suh, svh, None, codebook)
+
+
+def random_weights(cfg: DenseConfig, seed: int = 0) -> HostWeights:
+    """Random-init weights of the architecture with valid random EXL3 tensors (benchmarks and kernel tests)."""
+    rng = np.random.default_rng(seed)
+    d, F = cfg.d_model, cfg.ffn_padded
+    s_in = 1.0 / math.sqrt(d)
+    w = HostWeights(cfg, _bf16_round(rng.normal(0, 1.0, size=(cfg.vocab, d)).astype(np.float32)))
+    for _ in range(cfg.n_layers):
+        qkv = random_linear(d, cfg.qkv_width, cfg.bits, rng, cfg.codebook, s_in)
+        o = random_linear(cfg.n_q * cfg.head_dim, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(cfg.n_q * cfg.head_dim))
+        gu = random_linear(d, 2 * F, cfg.bits, rng, cfg.codebook, s_in)
+        if F != cfg.ffn:  # padded FFN columns contribute exactly zero
+            gu.svh[cfg.ffn:F] = 0
+            gu.svh[F + cfg.ffn:] = 0
+        down = random_linear(F, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(F), zero_rows_from=cfg.ffn if F != cfg.ffn else None)
+        lay = HostLayer(_bf16_round(1.0 + 0.1 * rng.normal(size=d)), qkv, o, _bf16_round(1.0 + 0.1 * rng.normal(size=d)), gu, down)
+        if cfg.qk_norm:
+            lay.q_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=cfg.head_dim))
+            lay.k_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=cfg.head_dim))
+        w.layers.append(lay)
+    w.final_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=d))
+    hb = cfg.head_bits or cfg.bits
+    w.lm_head = random_linear(d, cfg.vocab_padded, hb, rng, cfg.codebook, s_in, zero_cols_from=cfg.vocab if cfg.vocab_padded != cfg.vocab else None)
+    return w
+
+
+def rope_inv_freq(cfg: DenseConfig) -> np.ndarray:
+    i = np.arange(0, cfg.head_dim, 2, dtype=np.float32)
+    return (1.0 / (np.float32(cfg.rope_theta) ** (i / np.float32(cfg.head_dim)))).astype(np.float32)
+
+
+# ====================================================================================================== reference
+class ReferenceDense:
+    """fp32 PyTorch executor over the dequantized weights: the numerics oracle (CPU or any device).
+
+    Keeps one contiguous KV list per sequence id; rows are (seq, position, token).
+    """
+
+    def __init__(self, w: HostWeights, device="cpu", dtype=torch.float32):
+        self.cfg = cfg = w.cfg
+        self.device, self.dtype = device, dtype
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dtype)  # noqa: E731
+        self.embed = t(w.embed)
+        self.layers = []
+        for lay in w.layers:
+            self.layers.append(dict(attn_norm=t(lay.attn_norm), qkv=t(lay.qkv.dense()), o=t(lay.o.dense()), ffn_norm=t(lay.ffn_norm),
+                                    gate_up=t(lay.gate_up.dense()), down=t(lay.down.dense()),
+                                    q_norm=None if lay.q_norm is None else t(lay.q_norm), k_norm=None if lay.k_norm is None else t(lay.k_norm)))
+        self.final_norm = t(w.final_norm)
+        self.lm_head = t(w.lm_head.dense())[:, :cfg.vocab]
+        self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
+        self.kv = {}  # seq -> list over layers of (k [T, n_kv, hd], v)
+
+    def reset(self, seq=None):
+        if seq is None:
+            self.kv.clear()
+        else:
+            self.kv.pop(seq, None)
+
+    def truncate(self, seq, length: int):
+        if seq in self.kv:
+            self.kv[seq] = [(k[:length], v[:length]) for k, v in self.kv[seq]]
+
+    @staticmethod
+    def _rms(x, w, eps):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    def _rope(self, x, pos):
+        # x [T, H, hd]; rotate-half
+        ang = pos.to(torch.float32)[:, None] * self.inv_freq[None, :]
+        cos, sin = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
+        h = x.shape[-1] // 2
+        x1, x2 = x[..., :h], x[..., h:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+    @torch.no_grad()
+    def forward_seq(self, seq, tokens, start: int) -> torch.Tensor:
+        """Append `tokens` to sequence `seq` at positions start.. ; returns logits [T, vocab] (fp32)."""
+        cfg = self.cfg
+        ids = torch.as_tensor(tokens, dtype=torch.long, device=self.device)
+        T = ids.shape[0]
+        pos = torch.arange(start, start + T, device=self.device)
+        h = self.embed[ids]
+        if seq not in self.kv:
+            self.kv[seq] = [(torch.zeros(0, cfg.n_kv, cfg.head_dim, device=self.device, dtype=self.dtype),) * 2 for _ in self.layers]
+        for li, L in enumerate(self.layers):
+            x = self._rms(h, L["attn_norm"], cfg.eps)
+            qkv = x @ L["qkv"]
+            q = qkv[:, :cfg.n_q * cfg.head_dim].view(T, cfg.n_q, cfg.head_dim)
+            k = qkv[:, cfg.n_q * cfg.head_dim:(cfg.n_q + cfg.n_kv) * cfg.head_dim].view(T, cfg.n_kv, cfg.head_dim)
+            v = qkv[:, (cfg.n_q + cfg.n_kv) * cfg.head_dim:].view(T, cfg.n_kv, cfg.head_dim)
+            if L["q_norm"] is not None:
+                q, k = self._rms(q, L["q_norm"], cfg.eps), self._rms(k, L["k_norm"], cfg.eps)
+            q, k = self._rope(q, pos), self._rope(k, pos)
+            pk, pv = self.kv[seq][li]
+            kk, vv = torch.cat([pk[:start], k]), torch.cat([pv[:start], v])
+            self.kv[seq][li] = (kk, vv)
+            g = cfg.n_q // cfg.n_kv
+            kq, vq = kk.repeat_interleave(g, dim=1), vv.repeat_interleave(g, dim=1)
+            s = torch.einsum("thd,shd->hts", q, kq) / math.sqrt(cfg.head_dim)
+            kpos = torch.arange(kk.shape[0], device=self.device)
+            mask = kpos[None, :] > pos[:, None]
+            s = s.masked_fill(mask[None], float("-inf"))
+            a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), vq).reshape(T, -1)
+            h = h + a @ L["o"]
+            x = self._rms(h, L["ffn_norm"], cfg.eps)
+            gu = x @ L["gate_up"]
+            F = cfg.ffn_padded
+            h = h + (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
+        return (self._rms(h, self.final_norm, cfg.eps) @ self.lm_head).float()
+
+
+# ====================================================================================================== sm_100a executor
+class DenseGPU:
+    """The model on one B200: EXL3 weights as stored, paged bf16 KV cache, hand-written kernels only.
+
+    ``rows`` API (what the engine backend drives): every call passes per-row token ids, absolute positions,
+    the sequence slot of each row and the block table; rows may mix sequences freely (decode / verify windows) or be
+    one or more prompt chunks (prefill).
+    """
+
+    def __init__(self, w: HostWeights, num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256, device="cuda",
+                 max_prefill_rows: int = 8192):
+        from ..ops import kernels as K
+        self.K = K
+        self.cfg = cfg = w.cfg
+        self.device = device
+        self.num_pages, self.max_seqs, self.max_blocks = num_pages, max_seqs, max_blocks_per_seq
+        self.max_rows = max(max_rows, max_prefill_rows)
+        dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
+        up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731
+        self.embed = dev(w.embed, torch.bfloat16)
+        self.layers = []
+        for lay in w.layers:
+            self.layers.append(dict(attn_norm=dev(lay.attn_norm, torch.bfloat16), qkv=up(lay.qkv), o=up(lay.o), ffn_norm=dev(lay.ffn_norm, torch.bfloat16),
+                                    gate_up=up(lay.gate_up), down=up(lay.down),
+                                    q_norm=None if lay.q_norm is None else dev(lay.q_norm, torch.bfloat16),
+                                    k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16)))
+        self.final_norm = dev(w.final_norm, torch.bfloat16)
+        self.lm_head = up(w.lm_head)
+        self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
+        # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16, plus their TMA descriptors
+        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        self.tk = [K.KvTensorMap(c) for c in self.k_cache]
+        self.tv = [K.KvTensorMap(c) for c in self.v_cache]
+        self.status = K.new_status(device)
+        self._alloc_scratch(self.max_rows)
+        self.graphs = {}
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_scratch(self, R: int):
+        cfg, K, dev = self.cfg, self.K, self.device
+        widths = [cfg.qkv_width, cfg.d_model, 2 * cfg.ffn_padded]
+        self.splits = {}
+        part_elems = 0
+        for cls, rows in (("decode", min(R, 256)), ("prefill", R)):
+            for name, (k, n) in dict(qkv=(cfg.d_model, cfg.qkv_width), o=(cfg.n_q * cfg.head_dim, cfg.d_model),
+                                     gate_up=(cfg.d_model, 2 * cfg.ffn_padded), down=(cfg.ffn_padded, cfg.d_model),
+                                     lm_head=(cfg.d_model, cfg.vocab_padded)).items():
+                s = K.plan_splits(k, n, cls == "decode")
+                self.splits[(cls, name)] = s
+                r = rows if name != "lm_head" else min(rows, 256)
+                part_elems = max(part_elems, s * r * n)
+        self.part = torch.empty(part_elems, dtype=torch.float32, device=dev)
+        kmax = max(cfg.d_model, cfg.n_q * cfg.head_dim, cfg.ffn_padded)
+        self.xr = torch.empty(R * kmax, dtype=torch.float16, device=dev)
+        self.xr2 = torch.empty(R * cfg.ffn_padded, dtype=torch.float16, device=dev)
+        self.h = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
+        self.q = torch.empty(R, cfg.n_q * cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        self.attn_out = torch.empty(R, cfg.n_q * cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        self.logits = torch.empty(min(R, 256), cfg.vocab_padded, dtype=torch.float32, device=dev)
+        self.max_ctx_alloc = self.max_blocks * PAGE
+        self.attn_scratch = K.attn_decode_scratch(min(R, 256), cfg.n_q, cfg.head_dim, self.max_ctx_alloc, dev)
+        self.topk_scratch = K.topk_scratch(min(R, 256), cfg.vocab_padded, 64, dev)
+        self.cand_ids = torch.empty(min(R, 256), 64, dtype=torch.int32, device=dev)
+        self.cand_vals = torch.empty(min(R, 256), 64, dtype=torch.float32, device=dev)
+        del widths
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * 2 + self.lm_head.nbytes
+        for L in self.layers:
+            n += sum(L[k].nbytes for k in ("qkv", "o", "gate_up", "down"))
+        return n
+
+    # ------------------------------------------------------------------ forward
+    def _linear(self, xr, w, rows, cls, name):
+        s = self.splits[(cls, name)]
+        self.K.exl3_gemm(xr, w, self.part, s, self.status)
+        return s
+
+    def forward_rows(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None):
+        """Run all layers over M rows.
+
+        ids, positions, slots, row_seq, ctx_len: int32 device tensors [M] (slot = physical KV slot page*64+offset of the row's
+        own token; ctx_len = number of keys the row attends to = position + 1).  block_table int32 [max_seqs, max_blocks].
+        prefill: None for the decode/verify path, else dict(seq_ids, q_start, q_len, pos0, nseq, max_qlen) device tensors
+        describing which rows form which prompt chunk.  logit_rows: index tensor of the rows whose logits are wanted
+        (default: all rows).  Returns fp32 logits [len(logit_rows), vocab_padded] (a view of a reused buffer).
+        """
+        cfg, K = self.cfg, self.K
+        M = ids.shape[0]
+        cls = "decode" if prefill is None else "prefill"
+        assert M <= self.max_rows and (prefill is not None or M <= 256)
+        h = self.h[:M]
+        d, F, HQ = cfg.d_model, cfg.ffn_padded, cfg.n_q * cfg.head_dim
+        xr_d = self.xr[:M * d].view(M, d)
+        xr_a = self.xr[:M * HQ].view(M, HQ)
+        xr_f = self.xr2[:M * F].view(M, F)
+        q = self.q[:M]
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        K.embed(ids, self.embed, h)
+        L0 = self.layers[0]
+        K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)
+        for li, L in enumerate(self.layers):
+            s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
+            K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
+                              self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li])
+            if prefill is None:
+                K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
+                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status)
+            else:
+                ao = self.attn_out[:M]
+                K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
+                               ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status)
+                K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
+            s = self._linear(xr_a, L["o"], M, cls, "o")
+            K.finish_add_norm_rot(self.part, s, M, L["o"], h, L["ffn_norm"], cfg.eps, L["gate_up"].suh, xr_d)
+            s = self._linear(xr_d, L["gate_up"], M, cls, "gate_up")
+            K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
+            s = self._linear(xr_f, L["down"], M, cls, "down")
+            if li + 1 < len(self.layers):
+                nxt = self.layers[li + 1]
+                K.finish_add_norm_rot(self.part, s, M, L["down"], h, nxt["attn_norm"], cfg.eps, nxt["qkv"].suh, xr_d)
+            else:
+                K.finish_add_norm_rot(self.part, s, M, L["down"], h, self.final_norm, cfg.eps, self.lm_head.suh, xr_d)
+        if logit_rows is not None:
+            xl = xr_d.index_select(0, logit_rows).contiguous()
+        else:
+            xl = xr_d
+        R = xl.shape[0]
+        assert R <= self.logits.shape[0]
+        s = self._linear(xl, self.lm_head, R, "decode", "lm_head")
+        logits = self.logits[:R]
+        K.finish_store(self.part, s, R, self.lm_head, logits)
+        return logits
+
+    def candidates(self, logits: torch.Tensor, count: int):
+        """Top `count` (value desc, id asc) of each row, padded vocabulary columns excluded by construction (their logit is 0 * svh = 0
+        only when vocab is not a multiple of 128; callers mask them with `vocab`)."""
+        R = logits.shape[0]
+        if self.cfg.vocab_padded != self.cfg.vocab:
+            logits[:, self.cfg.vocab:] = float("-inf")
+        self.K.topk(logits, count, self.topk_scratch, self._ids_view(R, count), self._vals_view(R, count))
+        return self._ids_view(R, count), self._vals_view(R, count)
+
+    def _ids_view(self, R, count):
+        return self.cand_ids.view(-1)[:R * count].view(R, count)
+
+    def _vals_view(self, R, count):
+        return self.cand_vals.view(-1)[:R * count].view(R, count)
+
+    def check(self, what="forward"):
+        self.K.check_status(self.status, what)

@@ -1,0 +1,500 @@
+// Paged GQA attention for sm_100a: split-KV decode (+ merge fused with o_proj's input rotation) and causal flash
+// prefill, bf16 KV in 64-token pages.
+//
+// Cache layout (chosen so that one page of one KV head is ONE contiguous 64 x head_dim tile, i.e. one TMA box):
+//     k_cache, v_cache : bf16 [num_pages][n_kv_heads][64][head_dim]
+//     block_table      : int32 [num_seqs][max_blocks]   (page index of each 64-token block of a sequence)
+// K/V tiles are brought in by TMA (2-D tiled, SWIZZLE_128B, no multicast) through a small ring of stages; the
+// matrix math is bf16 mma.sync with fp32 online softmax, which is enough for a kernel whose roofline is HBM.
+//
+// Decode: one CTA per (row, kv head, 256-key chunk); chunks are ABSOLUTE key ranges and partials are merged in chunk
+// order, so a row's bits never depend on the batch (same idea as the reference's 512-key chunks,
+// crates/cuda/csrc/attention.cu:16-21; geometry, page size, KV layout and schedule are new).  The 4 warps of a CTA
+// each take 16 keys of every page and are merged in warp order.
+// Prefill: one CTA per (64 query rows, q head, sequence); warps own 16 query rows each and walk the pages causally.
+#include <cuda.h>
+#include "common.cuh"
+
+namespace rx {
+
+constexpr int PAGE = 64;
+constexpr int DEC_CHUNK = 256;              // keys per decode CTA (4 pages)
+constexpr int ATT_THREADS = 128;
+constexpr int KV_STAGES = 3;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A K or V page tile in shared memory: HD/64 boxes of [64 keys x 64 d] (128-byte rows, 128B swizzle), box b at b*8192.
+// Byte address of the 16-byte chunk `dchunk` (8 bf16) of key `key`.
+template <int HD>
+__device__ __forceinline__ uint32_t kv_chunk_addr(uint32_t base, int key, int dchunk) {
+  return base + (dchunk >> 3) * 8192 + key * 128 + (((dchunk & 7) ^ (key & 7)) << 4);
+}
+
+template <int HD>
+__device__ __forceinline__ void load_kv_page(uint8_t* kdst, uint8_t* vdst, const CUtensorMap* tk, const CUtensorMap* tv, int page, int kvh,
+                                             int n_kv, uint64_t* bar) {
+  constexpr int BYTES = PAGE * HD * 2;
+  mbar_arrive_expect_tx(bar, 2 * BYTES);
+  const int y = (page * n_kv + kvh) * PAGE;
+#pragma unroll
+  for (int b = 0; b < HD / 64; ++b) {
+    tma_load_2d(kdst + b * 8192, tk, b * 64, y, bar);
+    tma_load_2d(vdst + b * 8192, tv, b * 64, y, bar);
+  }
+}
+
+// One 16-row x NK-key step of flash attention for a warp.  qa: Q fragments [HD/16][4]; keys [key0, key0 + NK) of the
+// page tile at (ksm, vsm).  valid = number of unmasked keys counted from key0 for rows (r_lo) and (r_hi) (causal/ctx).
+template <int HD, int NK>
+__device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint32_t ksm, uint32_t vsm, int key0, int valid_lo, int valid_hi,
+                                          float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HD / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  constexpr int NT = NK / 8;
+  float s[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      uint32_t b0, b1, b2, b3;
+      const int mi = lane >> 3;
+      const int key = key0 + jp * 16 + (mi >> 1) * 8 + (lane & 7);
+      ldsm_x4(kv_chunk_addr<HD>(ksm, key, ks * 2 + (mi & 1)), b0, b1, b2, b3);
+      mma_bf16(s[2 * jp], qa[ks], b0, b1);
+      mma_bf16(s[2 * jp + 1], qa[ks], b2, b3);
+    }
+  }
+  // mask + row max
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int kk = j * 8 + 2 * (lane & 3) + (e & 1);
+      const int lim = (e < 2) ? valid_lo : valid_hi;
+      const float v = (kk < lim) ? s[j][e] * scale_log2 : -INFINITY;
+      s[j][e] = v;
+      mx[e >> 1] = fmaxf(mx[e >> 1], v);
+    }
+  }
+  float corr[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float mn = fmaxf(m[r], mx[r]);
+    corr[r] = (mn == -INFINITY) ? 1.f : exp2f(m[r] - mn);
+    m[r] = mn;
+  }
+  float rs[2] = {0.f, 0.f};
+  uint32_t pa[NT / 2][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float mm = m[e >> 1];
+      p[e] = (mm == -INFINITY) ? 0.f : exp2f(s[j][e] - mm);
+      rs[e >> 1] += p[e];
+    }
+    pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+    pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) l[r] = l[r] * corr[r] + rs[r];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) {
+    o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1];
+  }
+#pragma unroll
+  for (int kp = 0; kp < NT / 2; ++kp) {
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b0, b1, b2, b3;
+      const int mi = lane >> 3;
+      const int key = key0 + kp * 16 + (mi & 1) * 8 + (lane & 7);
+      ldsm_x4_t(kv_chunk_addr<HD>(vsm, key, dp * 2 + (mi >> 1)), b0, b1, b2, b3);
+      mma_bf16(o[2 * dp], pa[kp], b0, b1);
+      mma_bf16(o[2 * dp + 1], pa[kp], b2, b3);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ decode (split-KV)
+// part_o  : f32 [rows][n_q][max_chunks][HD]   unnormalised partial outputs
+// part_ml : f32 [rows][n_q][max_chunks][2]    (running max in log2 units, sum)
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
+                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE = PAGE * HD * 2;
+  uint64_t* bars = (uint64_t*)(smem + 2 * KV_STAGES * TILE);
+  volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
+  const int row = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = n_q / n_kv;
+  const int ctx = ctx_len[row];
+  const int k_begin = chunk * DEC_CHUNK;
+  if (k_begin >= ctx) return;  // uniform for the CTA; the merge kernel only reads chunks below ctx
+  const int k_end = min(ctx, k_begin + DEC_CHUNK);
+  const int npages = (k_end - k_begin + PAGE - 1) / PAGE;
+  const int* bt = block_table + (size_t)row_seq[row] * max_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < KV_STAGES; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p)
+      load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
+  }
+  // Q fragments straight from global: rows of the MMA tile are the G query heads of this KV head
+  uint32_t qa[HD / 16][4];
+  {
+    const int h0 = lane >> 2, h1 = h0 + 8;
+    const uint16_t* qrow = q + ((size_t)row * n_q + (size_t)kvh * G) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int c = ks * 16 + 2 * (lane & 3);
+      qa[ks][0] = h0 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h0 * HD + c) : 0u;
+      qa[ks][1] = h1 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h1 * HD + c) : 0u;
+      qa[ks][2] = h0 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h0 * HD + c + 8) : 0u;
+      qa[ks][3] = h1 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h1 * HD + c + 8) : 0u;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+  bool ok = true;
+  for (int p = 0; p < npages; ++p) {
+    const int s = p % KV_STAGES;
+    if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
+      const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;  // stage sn was consumed in iteration p-1 (barrier below)
+      load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+    }
+    ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 50);
+    if (!ok) break;
+    const int key0 = warp * 16;
+    const int valid = k_end - (k_begin + p * PAGE + key0);
+    if (valid > 0)
+      attn_step<HD, 16>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid, valid, scale_log2, m, l, o);
+    __syncthreads();
+  }
+  if (!ok || *abort_flag != 0) return;
+  // merge the 4 warps in warp order through shared memory (stages are free now: last iteration ended with a barrier)
+  float* sm_o = (float*)smem;                       // [4][16][HD]
+  float* sm_ml = sm_o + 4 * 16 * HD;                // [4][16][2]
+  {
+    const int r0 = lane >> 2, c0 = 2 * (lane & 3);
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      float* base = sm_o + ((size_t)warp * 16) * HD + d * 8 + c0;
+      base[(size_t)r0 * HD] = o[d][0]; base[(size_t)r0 * HD + 1] = o[d][1];
+      base[(size_t)(r0 + 8) * HD] = o[d][2]; base[(size_t)(r0 + 8) * HD + 1] = o[d][3];
+    }
+    // row sums: quad-reduce so every lane of a quad holds the full sum of its rows
+    float ls[2] = {l[0], l[1]};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      ls[r] += __shfl_xor_sync(0xffffffffu, ls[r], 1);
+      ls[r] += __shfl_xor_sync(0xffffffffu, ls[r], 2);
+    }
+    if ((lane & 3) == 0) {
+      sm_ml[(warp * 16 + r0) * 2] = m[0]; sm_ml[(warp * 16 + r0) * 2 + 1] = ls[0];
+      sm_ml[(warp * 16 + r0 + 8) * 2] = m[1]; sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = ls[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += ATT_THREADS) {
+    const int hq = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + hq) * 2]);
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_ml[(w * 16 + hq) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+      acc += f * sm_o[((size_t)w * 16 + hq) * HD + d];
+      lsum += f * sm_ml[(w * 16 + hq) * 2 + 1];
+    }
+    const size_t pidx = ((size_t)row * n_q + (size_t)kvh * G + hq) * max_chunks + chunk;
+    part_o[pidx * HD + d] = acc;
+    if (d == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = lsum; }
+  }
+}
+
+// Merge chunk partials in chunk order -> attention output; then (suh != nullptr) xr = fp16(H(out * suh)) per 128-block
+// (the o_proj input rotation), else plain bf16 output.  One warp per 128 output elements.
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ ctx_len, int n_q,
+                                  int max_chunks, const __half* __restrict__ suh, __half* __restrict__ xr, uint16_t* __restrict__ out_bf16) {
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int nch = (ctx_len[row] + DEC_CHUNK - 1) / DEC_CHUNK;
+  const int width = n_q * HD;
+  for (int b = blockIdx.y * nw + warp; b < width / 128; b += gridDim.y * nw) {
+    const int e0 = b * 128 + lane * 4;
+    const int hq = e0 / HD, d0 = e0 % HD;
+    const size_t base = ((size_t)row * n_q + hq) * max_chunks;
+    float mm = -INFINITY;
+    for (int c = 0; c < nch; ++c) mm = fmaxf(mm, part_ml[(base + c) * 2]);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, lsum = 0.f;
+    for (int c = 0; c < nch; ++c) {
+      const float mc = part_ml[(base + c) * 2];
+      const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - mm);
+      const float4 p = *reinterpret_cast<const float4*>(part_o + (base + c) * HD + d0);
+      acc[0] += f * p.x; acc[1] += f * p.y; acc[2] += f * p.z; acc[3] += f * p.w;
+      lsum += f * part_ml[(base + c) * 2 + 1];
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat16 t = __float2bfloat16_rn(acc[i] * inv);
+      v[i] = __bfloat162float(t);
+    }
+    if (out_bf16 != nullptr) {
+      uint2 u;
+      u.x = pack_bf16(v[0], v[1]); u.y = pack_bf16(v[2], v[3]);
+      *reinterpret_cast<uint2*>(out_bf16 + (size_t)row * width + e0) = u;
+    }
+    if (suh != nullptr) {
+      const uint2 su = *reinterpret_cast<const uint2*>(suh + e0);
+      const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+      v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
+      fwht128_warp(v);
+      const __half2 a = __floats2half2_rn(v[0], v[1]), c2 = __floats2half2_rn(v[2], v[3]);
+      uint2 u;
+      u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&c2);
+      *reinterpret_cast<uint2*>(xr + (size_t)row * width + e0) = u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ prefill (causal flash)
+// Queries: rows [q_start[s], q_start[s] + q_len[s]) of `q` belong to sequence s at positions pos0[s].. ; keys are the
+// sequence's cached tokens [0, pos0 + local row] (the chunk's own K/V are already in the cache).  out: bf16 [rows][n_q*HD].
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
+                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_ids, const int* __restrict__ q_start,
+                    const int* __restrict__ q_len, const int* __restrict__ pos0, uint16_t* __restrict__ out, int n_q, int n_kv, float scale_log2,
+                    int* status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE = PAGE * HD * 2;
+  uint64_t* bars = (uint64_t*)(smem + 2 * KV_STAGES * TILE);
+  volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
+  const int s_idx = blockIdx.z, hq = blockIdx.y;
+  const int qlen = q_len[s_idx];
+  // heaviest (latest) query tiles first
+  const int ntiles = (qlen + 63) / 64;
+  const int qt = ntiles - 1 - (int)blockIdx.x;
+  if (qt < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = n_q / n_kv, kvh = hq / G;
+  const int p0 = pos0[s_idx], r_base = q_start[s_idx];
+  const int* bt = block_table + (size_t)seq_ids[s_idx] * max_blocks;
+  const int q_lo = qt * 64;
+  const int last_q = min(qlen, q_lo + 64) - 1;
+  const int npages = (p0 + last_q) / PAGE + 1;  // keys 0 .. p0 + last_q
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < KV_STAGES; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p)
+      load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
+  }
+  uint32_t qa[HD / 16][4];
+  const int lr0 = q_lo + warp * 16 + (lane >> 2), lr1 = lr0 + 8;  // local query rows of this lane
+  {
+    const uint16_t* q0 = q + ((size_t)(r_base + lr0) * n_q + hq) * HD;
+    const uint16_t* q1 = q + ((size_t)(r_base + lr1) * n_q + hq) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int c = ks * 16 + 2 * (lane & 3);
+      qa[ks][0] = lr0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+      qa[ks][1] = lr1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+      qa[ks][2] = lr0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+      qa[ks][3] = lr1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+  const int warp_last_key = p0 + min(qlen - 1, q_lo + warp * 16 + 15);  // last key any row of this warp may see
+
+  bool ok = true;
+  for (int p = 0; p < npages; ++p) {
+    const int s = p % KV_STAGES;
+    if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
+      const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;
+      load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
+    }
+    ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 60);
+    if (!ok) break;
+    const int kbase = p * PAGE;
+    if (kbase <= warp_last_key && q_lo + warp * 16 < qlen) {
+      const int v0 = lr0 < qlen ? (p0 + lr0 + 1 - kbase) : 0, v1 = lr1 < qlen ? (p0 + lr1 + 1 - kbase) : 0;
+      attn_step<HD, 64>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), 0, v0, v1, scale_log2, m, l, o);
+    }
+    __syncthreads();
+  }
+  if (!ok || *abort_flag != 0) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  const float i0 = l[0] > 0.f ? 1.f / l[0] : 0.f, i1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) {
+    const int c = d * 8 + 2 * (lane & 3);
+    if (lr0 < qlen) *reinterpret_cast<uint32_t*>(out + ((size_t)(r_base + lr0) * n_q + hq) * HD + c) = pack_bf16(o[d][0] * i0, o[d][1] * i0);
+    if (lr1 < qlen) *reinterpret_cast<uint32_t*>(out + ((size_t)(r_base + lr1) * n_q + hq) * HD + c) = pack_bf16(o[d][2] * i1, o[d][3] * i1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn att_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+static int att_smem_bytes(int hd) { return 2 * KV_STAGES * PAGE * hd * 2 + 64 + 1024; }
+
+}  // namespace rx
+
+using namespace rx;
+
+// Writes a 128-byte tensor map for a bf16 cache [num_pages][n_kv][64][hd] viewed as 2-D [num_pages*n_kv*64, hd].
+RX_API int rx_make_kv_tmap(void* out128, const void* base, long long total_rows, int hd) {
+  EncodeTiledFn enc = att_encode_tiled();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  if (hd % 64 != 0 || (((uintptr_t)base) & 127) != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)total_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+  cuuint32_t box[2] = {64, PAGE};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc((CUtensorMap*)out128, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+RX_API int rx_attn_decode_chunk() { return DEC_CHUNK; }
+
+// scratch sizes (floats) for `rows` rows and contexts up to max_ctx
+RX_API long long rx_attn_decode_scratch_floats(int rows, int n_q, int hd, int max_ctx) {
+  const long long mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
+  return (long long)rows * n_q * mc * (hd + 2);
+}
+
+template <int HD>
+static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
+                         const int* ctx_len, float* scratch, int rows, int n_q, int n_kv, int max_ctx, float scale, const void* suh, void* xr,
+                         void* out_bf16, int* status, cudaStream_t st) {
+  const int mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)rows * n_q * mc * HD;
+  const int smem = att_smem_bytes(HD);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(rows, n_kv, mc);
+  attn_decode_kernel<HD><<<grid, ATT_THREADS, smem, st>>>(*tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, n_q,
+                                                         n_kv, mc, scale * 1.4426950408889634f, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  const int blocks128 = n_q * HD / 128;
+  int gy = (296 + rows - 1) / rows;
+  if (gy > (blocks128 + 3) / 4) gy = (blocks128 + 3) / 4;
+  if (gy < 1) gy = 1;
+  attn_merge_kernel<HD><<<dim3(rows, gy), 128, 0, st>>>(part_o, part_ml, ctx_len, n_q, mc, (const __half*)suh, (__half*)xr, (uint16_t*)out_bf16);
+  return (int)cudaGetLastError();
+}
+
+// q: bf16 [rows][n_q*hd] (already rotated by RoPE).  Either/both outputs: xr = fp16(H(out*suh)) [rows][n_q*hd], out_bf16.
+RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* row_seq,
+                          const void* ctx_len, void* scratch, int rows, int n_q, int n_kv, int hd, int max_ctx, float scale, const void* suh,
+                          void* xr, void* out_bf16, int* status, void* stream) {
+  if (n_q % n_kv != 0 || n_q / n_kv > 16 || (n_q * hd) % 128 != 0 || rows <= 0 || max_ctx <= 0) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (hd == 128)
+    return launch_decode<128>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)row_seq,
+                              (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st);
+  if (hd == 64)
+    return launch_decode<64>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)row_seq,
+                             (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st);
+  return (int)cudaErrorInvalidValue;
+}
+
+template <int HD>
+static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* seq_ids,
+                          const int* q_start, const int* q_len, const int* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, float scale,
+                          int* status, cudaStream_t st) {
+  const int smem = att_smem_bytes(HD);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_qlen + 63) / 64, n_q, nseq);
+  attn_prefill_kernel<HD><<<grid, ATT_THREADS, smem, st>>>(*tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
+                                                          (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status);
+  return (int)cudaGetLastError();
+}
+
+RX_API int rx_attn_prefill(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
+                           const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
+                           float scale, int* status, void* stream) {
+  if (n_q % n_kv != 0 || nseq <= 0 || max_qlen <= 0) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (hd == 128)
+    return launch_prefill<128>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)seq_ids,
+                               (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st);
+  if (hd == 64)
+    return launch_prefill<64>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)seq_ids,
+                              (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st);
+  return (int)cudaErrorInvalidValue;
+}

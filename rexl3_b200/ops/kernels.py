@@ -1,0 +1,178 @@
+"""Torch-facing wrappers of the sm_100a launchers.  Every function enqueues on the current CUDA stream, allocates
+nothing (callers pass outputs and scratch) and raises :class:`KernelError` on a launch error."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+
+CB_ID = {"3inst": 0, "mcg": 1, "mul1": 2}
+
+
+@dataclass
+class Exl3Weight:
+    """One EXL3 linear layer on the device."""
+
+    trellis: torch.Tensor          # int16 [K/16, N/16, 16*bits]
+    suh: torch.Tensor              # float16 [K]
+    svh: torch.Tensor              # float16 [N]
+    bias: torch.Tensor | None      # float32 [N]
+    codebook: str = "3inst"
+
+    @property
+    def K(self) -> int:
+        return self.trellis.shape[0] * 16
+
+    @property
+    def N(self) -> int:
+        return self.trellis.shape[1] * 16
+
+    @property
+    def twice(self) -> int:
+        return self.trellis.shape[2] // 8
+
+    @property
+    def nbytes(self) -> int:
+        return self.trellis.numel() * 2 + self.suh.numel() * 2 + self.svh.numel() * 2
+
+    @staticmethod
+    def from_numpy(trellis, suh, svh, bias=None, codebook="3inst", device="cuda") -> "Exl3Weight":
+        return Exl3Weight(torch.from_numpy(np.ascontiguousarray(trellis)).to(device),
+                          torch.from_numpy(np.ascontiguousarray(suh, dtype=np.float16)).to(device),
+                          torch.from_numpy(np.ascontiguousarray(svh, dtype=np.float16)).to(device),
+                          None if bias is None else torch.from_numpy(np.ascontiguousarray(bias, dtype=np.float32)).to(device), codebook)
+
+
+def new_status(device="cuda") -> torch.Tensor:
+    """Four int32 status words kernels write on a bounded-wait timeout: [code, site, block, aux]."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor, what: str = "kernel") -> None:
+    s = status.tolist()
+    if s[0] != 0:
+        raise _lib.KernelError(f"{what}: device status code {s[0]} at site {s[1]} (block {s[2]}, aux {s[3]})")
+
+
+def plan_splits(K: int, N: int, decode_class: bool) -> int:
+    return _lib.load().rx_exl3_plan_splits(K, N, 1 if decode_class else 0)
+
+
+def exl3_gemm(xr: torch.Tensor, w: Exl3Weight, part: torch.Tensor, splits: int, status: torch.Tensor) -> None:
+    """part[s, row, n] = partial sums of xr @ W_q over split s.  xr: fp16 [rows, K] contiguous; part: fp32 >= splits*rows*N."""
+    rows, K = xr.shape
+    assert xr.dtype == torch.float16 and xr.is_contiguous() and K == w.K
+    assert part.dtype == torch.float32 and part.numel() >= splits * rows * w.N
+    L = _lib.load()
+    _lib.check(L.rx_exl3_gemm(xr.data_ptr(), rows, K, w.trellis.data_ptr(), w.N, w.twice, CB_ID[w.codebook], part.data_ptr(), splits,
+                              status.data_ptr(), _lib.stream_ptr()), "rx_exl3_gemm")
+    _lib.count()
+
+
+def exl3_unpack(w: Exl3Weight) -> torch.Tensor:
+    out = torch.empty(w.K, w.N, dtype=torch.float16, device=w.trellis.device)
+    L = _lib.load()
+    _lib.check(L.rx_exl3_unpack(w.trellis.data_ptr(), w.K, w.N, w.twice, CB_ID[w.codebook], out.data_ptr(), _lib.stream_ptr()), "rx_exl3_unpack")
+    _lib.count()
+    return out
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, h: torch.Tensor) -> None:
+    L = _lib.load()
+    _lib.check(L.rx_embed(ids.data_ptr(), table.data_ptr(), h.data_ptr(), ids.numel(), table.shape[1], table.shape[0], _lib.stream_ptr()), "rx_embed")
+    _lib.count()
+
+
+def norm_rot_in(x: torch.Tensor, norm_w, eps: float, suh: torch.Tensor, xr: torch.Tensor) -> None:
+    rows, K = x.shape
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    L = _lib.load()
+    _lib.check(L.rx_norm_rot_in(x.data_ptr(), _lib.ptr(norm_w), eps, suh.data_ptr(), xr.data_ptr(), rows, K, _lib.stream_ptr()), "rx_norm_rot_in")
+    _lib.count()
+
+
+def finish_store(part, S, M, w: Exl3Weight, out: torch.Tensor) -> None:
+    L = _lib.load()
+    f32 = 1 if out.dtype == torch.float32 else 0
+    assert out.dtype in (torch.float32, torch.bfloat16)
+    _lib.check(L.rx_finish_store(part.data_ptr(), S, M, w.N, w.svh.data_ptr(), _lib.ptr(w.bias), out.data_ptr(), f32, _lib.stream_ptr()),
+               "rx_finish_store")
+    _lib.count()
+
+
+def finish_add_norm_rot(part, S, M, w: Exl3Weight, h: torch.Tensor, norm_w, eps: float, suh_next, xr) -> None:
+    L = _lib.load()
+    _lib.check(L.rx_finish_add_norm_rot(part.data_ptr(), S, M, w.N, w.svh.data_ptr(), _lib.ptr(w.bias), h.data_ptr(), _lib.ptr(norm_w), eps,
+                                        _lib.ptr(suh_next), _lib.ptr(xr), _lib.stream_ptr()), "rx_finish_add_norm_rot")
+    _lib.count()
+
+
+def finish_swiglu_rot(part, S, M, w: Exl3Weight, suh_down: torch.Tensor, xr: torch.Tensor) -> None:
+    L = _lib.load()
+    _lib.check(L.rx_finish_swiglu_rot(part.data_ptr(), S, M, w.N // 2, w.svh.data_ptr(), _lib.ptr(w.bias), suh_down.data_ptr(), xr.data_ptr(),
+                                      _lib.stream_ptr()), "rx_finish_swiglu_rot")
+    _lib.count()
+
+
+def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, eps, positions, inv_freq, slot, q_out, k_cache, v_cache) -> None:
+    L = _lib.load()
+    _lib.check(L.rx_finish_qkv_rope(part.data_ptr(), S, M, n_q, n_kv, hd, w.svh.data_ptr(), _lib.ptr(w.bias), _lib.ptr(q_norm), _lib.ptr(k_norm),
+                                    eps, positions.data_ptr(), inv_freq.data_ptr(), slot.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
+                                    v_cache.data_ptr(), _lib.stream_ptr()), "rx_finish_qkv_rope")
+    _lib.count()
+
+
+def topk_scratch(rows: int, vocab: int, count: int, device="cuda") -> torch.Tensor:
+    n = _lib.load().rx_topk_scratch_bytes(rows, vocab, count)
+    return torch.empty(n // 8 + 1, dtype=torch.int64, device=device)
+
+
+def topk(logits: torch.Tensor, count: int, scratch, ids: torch.Tensor, vals: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    L = _lib.load()
+    _lib.check(L.rx_topk(logits.data_ptr(), rows, vocab, count, scratch.data_ptr(), ids.data_ptr(), vals.data_ptr(), _lib.stream_ptr()), "rx_topk")
+    _lib.count(2)
+
+
+class KvTensorMap:
+    """Host-side TMA descriptor of one layer's K or V cache (bf16 [pages, n_kv, 64, hd])."""
+
+    def __init__(self, cache: torch.Tensor):
+        pages, n_kv, page, hd = cache.shape
+        assert page == 64 and cache.dtype == torch.bfloat16 and cache.is_contiguous()
+        self.buf = np.zeros(128, dtype=np.uint8)
+        self._keep = cache
+        L = _lib.load()
+        _lib.check(L.rx_make_kv_tmap(self.buf.ctypes.data, cache.data_ptr(), pages * n_kv * page, hd), "rx_make_kv_tmap")
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.ctypes.data
+
+
+def attn_decode_scratch(rows: int, n_q: int, hd: int, max_ctx: int, device="cuda") -> torch.Tensor:
+    n = _lib.load().rx_attn_decode_scratch_floats(rows, n_q, hd, max_ctx)
+    return torch.empty(n, dtype=torch.float32, device=device)
+
+
+def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_len, scratch, n_q, n_kv, hd, max_ctx, scale, suh, xr, out,
+                status) -> None:
+    rows = q.shape[0]
+    L = _lib.load()
+    _lib.check(L.rx_attn_decode(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
+                                scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out),
+                                status.data_ptr(), _lib.stream_ptr()), "rx_attn_decode")
+    _lib.count(2)
+
+
+def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,
+                 status) -> None:
+    L = _lib.load()
+    _lib.check(L.rx_attn_prefill(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], seq_ids.data_ptr(), q_start.data_ptr(),
+                                 q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
+                                 _lib.stream_ptr()), "rx_attn_prefill")
+    _lib.count()

@@ -1,0 +1,235 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op (small cases)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from rexl3_b200.format import exl3
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.ops import kernels
+    return kernels
+
+
+def _mk(K, k, n, bits, cb="3inst", seed=0, out_scale=0.05):
+    rng = np.random.default_rng(seed)
+    b = exl3.Bits.of(bits)
+    tr = exl3.random_trellis(k // 16, n // 16, b, seed)
+    suh = rng.uniform(0.5, 1.5, k).astype(np.float16) * np.where(rng.random(k) < 0.5, -1, 1).astype(np.float16)
+    svh = rng.uniform(0.5, 1.5, n).astype(np.float16) * np.float16(out_scale)
+    return K.Exl3Weight.from_numpy(tr, suh, svh, None, cb), tr, suh, svh
+
+
+def test_unpack_bit_exact_every_width_and_codebook(K):
+    for cb in exl3.CODEBOOKS:
+        for t in exl3.ALL_TWICE:
+            if t % 2 and cb != "mul1":
+                continue
+            tr = exl3.random_trellis(8, 8, exl3.Bits(t), seed=t)
+            w = K.Exl3Weight.from_numpy(tr, np.ones(128, np.float16), np.ones(128, np.float16), None, cb)
+            got = K.exl3_unpack(w).cpu().numpy().view(np.uint16)
+            assert np.array_equal(got, exl3.unpack(tr, cb)), (cb, t)
+
+
+@pytest.mark.parametrize("bits,cb", [(4, "3inst"), (3, "3inst"), (2, "mcg"), (2.5, "mul1"), (6, "mul1"), (8, "3inst"), (1, "3inst"), (3.5, "mul1")])
+@pytest.mark.parametrize("rows", [1, 7, 64, 200, 300])
+def test_exl3_gemm_matches_fp32_reference(K, bits, cb, rows):
+    k, n = 512, 384
+    w, tr, _, _ = _mk(K, k, n, bits, cb, seed=int(bits * 2) + rows)
+    wq = torch.from_numpy(exl3.unpack_f32(tr, cb)).cuda()
+    g = torch.Generator(device="cpu").manual_seed(rows)
+    xr = (torch.randn(rows, k, generator=g) * 0.5).to(torch.float16).cuda()
+    ref = xr.float() @ wq
+    status = K.new_status()
+    for splits in (1, 3):
+        part = torch.full((splits * rows * n,), float("nan"), device="cuda")
+        K.exl3_gemm(xr, w, part, splits, status)
+        torch.cuda.synchronize()
+        K.check_status(status)
+        got = part.view(splits, rows, n).sum(0)
+        err = (got - ref).abs().max().item()
+        assert err <= 2e-3 * ref.abs().max().item() + 1e-3, (bits, cb, rows, splits, err)
+
+
+def test_exl3_gemm_row_invariance(K):
+    """A row's bits do not depend on the other rows or their count (decode class)."""
+    k, n = 1024, 256
+    w, _, _, _ = _mk(K, k, n, 4, seed=3)
+    xr = (torch.randn(64, k) * 0.5).to(torch.float16).cuda()
+    status = K.new_status()
+    outs = []
+    for rows in (1, 5, 16, 33, 64):
+        part = torch.zeros(2 * rows * n, device="cuda")
+        K.exl3_gemm(xr[:rows].contiguous(), w, part, 2, status)
+        outs.append(part.view(2, rows, n)[:, 0].clone())
+    torch.cuda.synchronize()
+    K.check_status(status)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+
+
+def _hadamard(x):
+    h = torch.from_numpy(exl3.hadamard128(np.float32)).to(x.device)
+    return (x.reshape(*x.shape[:-1], -1, 128) @ h).reshape(x.shape)
+
+
+def _rms(x, w, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+
+def test_norm_rot_in_and_finish_kernels(K):
+    torch.manual_seed(0)
+    M, d, F, S, eps = 5, 512, 256, 3, 1e-6
+    x = torch.randn(M, d).to(torch.bfloat16).cuda()
+    nw = (1 + 0.1 * torch.randn(d)).to(torch.bfloat16).cuda()
+    suh = (torch.rand(d) + 0.5).to(torch.float16).cuda()
+    xr = torch.empty(M, d, dtype=torch.float16, device="cuda")
+    K.norm_rot_in(x, nw, eps, suh, xr)
+    ref = _hadamard(_rms(x.float(), 1.0, eps).to(torch.bfloat16).float() * nw.float() * suh.float())
+    assert (xr.float() - ref).abs().max() < 2e-2
+    K.norm_rot_in(x, None, eps, suh, xr)
+    assert (xr.float() - _hadamard(x.float() * suh.float())).abs().max() < 2e-2
+    # finish_store
+    w, _, _, svh = _mk(K, 128, d, 4)
+    part = torch.randn(S, M, d, device="cuda")
+    y_ref = _hadamard(part.sum(0)) * w.svh.float()
+    out = torch.empty(M, d, dtype=torch.float32, device="cuda")
+    K.finish_store(part, S, M, w, out)
+    assert (out - y_ref).abs().max() < 1e-4 * y_ref.abs().max() + 1e-5
+    outb = torch.empty(M, d, dtype=torch.bfloat16, device="cuda")
+    K.finish_store(part, S, M, w, outb)
+    assert (outb.float() - y_ref).abs().max() < 1e-2 * y_ref.abs().max()
+    # finish_add_norm_rot
+    h = torch.randn(M, d).to(torch.bfloat16).cuda()
+    h0 = h.clone()
+    K.finish_add_norm_rot(part, S, M, w, h, nw, eps, suh, xr)
+    h_ref = (h0.float() + y_ref).to(torch.bfloat16)
+    assert (h.float() - h_ref.float()).abs().max() <= 0.04
+    ref = _hadamard(_rms(h.float(), 1.0, eps).to(torch.bfloat16).float() * nw.float() * suh.float())
+    assert (xr.float() - ref).abs().max() < 3e-2
+    # finish_swiglu_rot
+    wgu, _, _, _ = _mk(K, 128, 2 * F, 4, out_scale=0.5)
+    partg = torch.randn(S, M, 2 * F, device="cuda")
+    yg = _hadamard(partg.sum(0)) * wgu.svh.float()
+    act = (torch.nn.functional.silu(yg[:, :F]) * yg[:, F:]).to(torch.bfloat16).float()
+    sd = (torch.rand(F) + 0.5).to(torch.float16).cuda()
+    xf = torch.empty(M, F, dtype=torch.float16, device="cuda")
+    K.finish_swiglu_rot(partg, S, M, wgu, sd, xf)
+    ref = _hadamard(act * sd.float())
+    assert (xf.float() - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_topk_exact_order(K):
+    torch.manual_seed(1)
+    rows, vocab, count = 3, 151936, 28
+    logits = torch.randn(rows, vocab, device="cuda")
+    logits[0, 5] = logits[0, 77777] = 9.0  # tie -> lower id first
+    scratch = K.topk_scratch(rows, vocab, count)
+    ids = torch.empty(rows, count, dtype=torch.int32, device="cuda")
+    vals = torch.empty(rows, count, dtype=torch.float32, device="cuda")
+    K.topk(logits, count, scratch, ids, vals)
+    v, i = torch.sort(logits, dim=1, descending=True, stable=True)
+    assert torch.equal(vals, v[:, :count])
+    assert ids[0, 0].item() == 5 and ids[0, 1].item() == 77777
+    assert torch.equal(ids[1:].long(), i[1:, :count])
+
+
+def _ref_attn(q, kc, vc, ctx, n_q, n_kv, hd):
+    # q [n_q, hd]; kc, vc [T, n_kv, hd]
+    g = n_q // n_kv
+    k = kc[:ctx].float().repeat_interleave(g, dim=1)
+    v = vc[:ctx].float().repeat_interleave(g, dim=1)
+    s = torch.einsum("hd,thd->ht", q.float(), k) / math.sqrt(hd)
+    return torch.einsum("ht,thd->hd", torch.softmax(s, -1), v).reshape(-1)
+
+
+@pytest.mark.parametrize("hd,n_q,n_kv", [(128, 10, 2), (64, 4, 2)])
+def test_paged_attention_decode_and_prefill(K, hd, n_q, n_kv):
+    torch.manual_seed(2)
+    pages, nseq, max_blocks = 40, 3, 12
+    kc = torch.zeros(pages, n_kv, 64, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    lens = [700, 65, 1]
+    perm = torch.randperm(pages).tolist()
+    bt = torch.zeros(nseq, max_blocks, dtype=torch.int32)
+    seq_k, seq_v = [], []
+    for s, T in enumerate(lens):
+        k = torch.randn(T, n_kv, hd).to(torch.bfloat16)
+        v = torch.randn(T, n_kv, hd).to(torch.bfloat16)
+        seq_k.append(k.cuda()); seq_v.append(v.cuda())
+        for b in range((T + 63) // 64):
+            pg = perm.pop()
+            bt[s, b] = pg
+            n = min(64, T - b * 64)
+            kc[pg, :, :n] = k[b * 64:b * 64 + n].transpose(0, 1).cuda()
+            vc[pg, :, :n] = v[b * 64:b * 64 + n].transpose(0, 1).cuda()
+    bt = bt.cuda()
+    tk, tv = K.KvTensorMap(kc), K.KvTensorMap(vc)
+    status = K.new_status()
+    # decode: rows = last token of each sequence + one mid-sequence row (verify-window style)
+    row_seq = torch.tensor([0, 1, 2, 0], dtype=torch.int32, device="cuda")
+    ctx = torch.tensor([700, 65, 1, 300], dtype=torch.int32, device="cuda")
+    q = torch.randn(4, n_q * hd).to(torch.bfloat16).cuda()
+    scratch = K.attn_decode_scratch(4, n_q, hd, max_blocks * 64)
+    out = torch.empty(4, n_q * hd, dtype=torch.bfloat16, device="cuda")
+    suh = (torch.rand(n_q * hd) + 0.5).to(torch.float16).cuda()
+    xr = torch.empty(4, n_q * hd, dtype=torch.float16, device="cuda")
+    K.attn_decode(tk, tv, q, bt, row_seq, ctx, scratch, n_q, n_kv, hd, max_blocks * 64, 1 / math.sqrt(hd), suh, xr, out, status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    for r in range(4):
+        s = int(row_seq[r])
+        ref = _ref_attn(q[r].view(n_q, hd), seq_k[s], seq_v[s], int(ctx[r]), n_q, n_kv, hd)
+        assert (out[r].float() - ref).abs().max() < 2e-2, r
+        assert (xr[r].float() - _hadamard(out[r].float() * suh.float())).abs().max() < 2e-2
+    # prefill: sequence 0 rows 500..699 (chunk of 200) and sequence 1 whole (65 rows)
+    q_start = torch.tensor([0, 200], dtype=torch.int32, device="cuda")
+    q_len = torch.tensor([200, 65], dtype=torch.int32, device="cuda")
+    pos0 = torch.tensor([500, 0], dtype=torch.int32, device="cuda")
+    seq_ids = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    qp = torch.randn(265, n_q * hd).to(torch.bfloat16).cuda()
+    outp = torch.zeros(265, n_q * hd, dtype=torch.bfloat16, device="cuda")
+    K.attn_prefill(tk, tv, qp, bt, seq_ids, q_start, q_len, pos0, outp, 2, 200, n_q, n_kv, hd, 1 / math.sqrt(hd), status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    for r in list(range(0, 200, 37)) + [199, 200, 230, 264]:
+        s, p = (0, 500 + r) if r < 200 else (1, r - 200)
+        ref = _ref_attn(qp[r].view(n_q, hd), seq_k[s], seq_v[s], p + 1, n_q, n_kv, hd)
+        assert (outp[r].float() - ref).abs().max() < 2e-2, r
+
+
+def test_qkv_finish_rope_and_cache_write(K):
+    torch.manual_seed(3)
+    M, n_q, n_kv, hd, S = 3, 4, 2, 128, 2
+    N = (n_q + 2 * n_kv) * hd
+    w, _, _, _ = _mk(K, 128, N, 4, out_scale=1.0)
+    part = torch.randn(S, M, N, device="cuda")
+    y = _hadamard(part.sum(0)) * w.svh.float()
+    pos = torch.tensor([0, 17, 4099], dtype=torch.int32, device="cuda")
+    slot = torch.tensor([64 * 3 + 0, 64 * 1 + 17, -1], dtype=torch.int32, device="cuda")
+    inv = torch.from_numpy((1.0 / (1e4 ** (np.arange(0, hd, 2, dtype=np.float32) / hd))).astype(np.float32)).cuda()
+    kc = torch.zeros(5, n_kv, 64, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    qo = torch.empty(M, n_q * hd, dtype=torch.bfloat16, device="cuda")
+    K.finish_qkv_rope(part, S, M, n_q, n_kv, hd, w, None, None, 1e-6, pos, inv, slot, qo, kc, vc)
+
+    def rope(x, p):
+        ang = p.float()[:, None] * inv[None]
+        c, s = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+        x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+    qr = rope(y[:, :n_q * hd].view(M, n_q, hd), pos).reshape(M, -1)
+    kr = rope(y[:, n_q * hd:(n_q + n_kv) * hd].view(M, n_kv, hd), pos)
+    v = y[:, (n_q + n_kv) * hd:].view(M, n_kv, hd)
+    assert (qo.float() - qr).abs().max() < 3e-2 * qr.abs().max()
+    assert (kc[3, :, 0].float() - kr[0]).abs().max() < 3e-2 * kr.abs().max()
+    assert (kc[1, :, 17].float() - kr[1]).abs().max() < 3e-2 * kr.abs().max()
+    assert (vc[1, :, 17].float() - v[1]).abs().max() < 3e-2 * v.abs().max()
+    assert kc[0].abs().max() == 0 and kc[2].abs().max() == 0 and kc[4].abs().max() == 0
