@@ -1,0 +1,120 @@
+"""The contract between the engine's step loop and a model runtime.
+
+A backend serves fixed sequence *slots*.  Every state-changing call is one of: ``prefill_slice`` (append prompt tokens
+to a slot), ``step`` (a window of rows over several slots: each slot feeds ``[last, d1..dk]`` at consecutive positions),
+``commit`` (keep the first ``keep`` rows of the slot's last window; the rest never become visible) and ``release``.
+Rows come back as the top candidates (value desc, id asc) - the engine never sees full logits except on the score path.
+
+Contract sentence: every row's output is bit-identical to what the same backend returns for that row in a one-row step.
+Behaviour parity: reference crates/engine/src/lib.rs:212-432 (trait Backend and its optional methods).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+
+@dataclass
+class RowRequest:
+    slot: int
+    tokens: list           # [last, d1 .. dk]
+    first_position: int    # absolute position of tokens[0]
+
+
+@dataclass
+class RowOutput:
+    ids: np.ndarray        # uint32 [count], ordered (value desc, id asc)
+    values: np.ndarray     # float32 [count]
+
+
+class BackendError(Exception):
+    def __init__(self, message: str, fatal: bool = False):
+        super().__init__(message)
+        self.fatal = fatal
+
+
+@dataclass
+class DraftAsk:
+    slot: int
+    context: list          # committed tokens of the sequence
+    max_drafts: int
+    sampling: object = None
+
+
+@dataclass
+class DraftOffer:
+    tokens: list = field(default_factory=list)
+    conf: list = field(default_factory=list)       # optional per-draft confidence (probability it is accepted given the ones before)
+
+
+class Backend:
+    """Base class; a runtime overrides what it supports."""
+
+    vocab_size: int = 0
+    max_rows: int = 64            # rows one window may hold
+    max_slots: int = 8
+    name: str = "backend"
+
+    # ---- required
+    def prefill_slice(self, slot: int, start: int, tokens: list, candidates: int, last: bool):
+        """Append `tokens` at positions start.. of `slot`.  Returns the last row's RowOutput when `last`, else None."""
+        raise NotImplementedError
+
+    def step(self, reqs: list, candidates: int) -> list:
+        """One window.  Returns, per request, a list of RowOutput (one per fed token)."""
+        raise NotImplementedError
+
+    def commit(self, slot: int, keep: int) -> None:
+        raise NotImplementedError
+
+    def release(self, slot: int) -> None:
+        raise NotImplementedError
+
+    # ---- optional
+    def prefill_slices(self, items: list, candidates: int) -> list:
+        """Batched short prompts: items = [(slot, start, tokens, last)].  Default: one after another."""
+        return [self.prefill_slice(s, st, t, candidates, last) for s, st, t, last in items]
+
+    def step_verified(self, reqs: list, candidates: int, greedy: list) -> list:
+        """`greedy[i]` says request i samples at T == 0 (a backend may return a single candidate per row for those)."""
+        return self.step(reqs, candidates)
+
+    def propose_batch(self, asks: list) -> dict:
+        """Native drafter: slot -> DraftOffer.  Default: no native drafter."""
+        return {}
+
+    def supports_native_draft(self) -> bool:
+        return False
+
+    def take_error(self):
+        """A BackendError raised asynchronously by the last call (device status words), or None."""
+        return None
+
+    def score_rows(self, slot: int, start: int, tokens: list) -> np.ndarray:
+        """Full-vocabulary logits of every fed row (prompt scoring / logprobs).  Optional."""
+        raise NotImplementedError
+
+    # prefix cache (optional): handles are opaque to the engine
+    def prefix_block_tokens(self) -> int:
+        return 0                   # 0 = no prefix cache support
+
+    def prefix_restore(self, slot: int, handles: list) -> int:
+        """Make `slot` start with the cached blocks `handles`; returns the number of tokens restored."""
+        return 0
+
+    def prefix_commit(self, slot: int, blocks: int) -> list:
+        """Handles of the slot's first `blocks` full blocks (the backend retains them for the cache)."""
+        return []
+
+    def prefix_release(self, handles: list) -> None:
+        pass
+
+    def prefix_bytes_per_block(self) -> int:
+        return 0
+
+    def quiesce(self) -> None:
+        """Wait for all device work (used before measuring and at shutdown)."""
+
+    def stats(self) -> dict:
+        return {}

@@ -1,0 +1,423 @@
+"""The engine step loop: deferred submit -> prefill slices (serial / burst) -> decode / verify rounds -> commit or
+rollback -> events.
+
+One ``step()`` is one scheduling iteration: a decode round over every active sequence (one window whose rows are, per
+sequence, its last token plus its drafts), then prefill work for sequences still reading their prompt.  Sampling is the
+keyed sampler on the CPU over the backend's top candidates; a draft is accepted iff it equals the keyed sample at its
+position, so drafted == serial by construction.  Behaviour parity: reference crates/engine/src/lib.rs:1715-2200
+(step / step_inner / decode_round), :1169-1626 (submit, prefill slices, prefix planning), :548-637 (Request / Event /
+FinishReason), :724-803 (BudgetPolicy, PrefillPolicy).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..sampling import Sampling, SamplingError, choose, seed_for
+from ..sched import AdmitError, Admission, CostModel, Demand, PrefixIndex, chain_hashes, choose_budget
+from ..spec import AcceptStats, CopyDrafter, SpecMode, accept
+from .backend import Backend, BackendError, DraftAsk, RowRequest
+
+PREFILL_STEP_ROWS = 4096
+
+
+@dataclass
+class Request:
+    id: str
+    prompt: list
+    max_new_tokens: int = 256
+    sampling: Sampling = None
+    stop_ids: tuple = ()
+    draft: bool = True
+    prefix_cache: bool = True
+    deadline: float | None = None       # absolute time.monotonic() after which the request is cancelled
+
+
+@dataclass
+class Event:
+    kind: str                 # "tokens" | "done" | "error"
+    id: str
+    tokens: list = field(default_factory=list)
+    reason: str = ""          # stop | length | cancelled | error | deadline
+    usage: dict = field(default_factory=dict)
+    message: str = ""
+
+
+@dataclass
+class _Seq:
+    req: Request
+    slot: int
+    tokens: list
+    prompt_len: int
+    prefilled: int = 0
+    cached: int = 0
+    generated: int = 0
+    drafter: CopyDrafter = None
+    stats: AcceptStats = None
+    drafted: int = 0
+    accepted: int = 0
+    rounds: int = 0
+    t_submit: float = 0.0
+    t_first: float | None = None
+    committed_blocks: int = 0
+    hashes: list = None
+
+
+class StepError(Exception):
+    def __init__(self, kind: str, message: str, fatal: bool):
+        super().__init__(f"{kind}: {message}")
+        self.kind, self.fatal = kind, fatal
+
+
+class Engine:
+    def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
+                 spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
+                 prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b""):
+        self.backend = backend
+        self.admission = admission
+        self.window_rows = min(window_rows, backend.max_rows)
+        self.prefill_chunk = prefill_chunk
+        self.spec = spec if isinstance(spec, SpecMode) else SpecMode(spec)
+        self.max_drafts = max_drafts
+        self.cost = cost
+        self.prefix = prefix if (prefix is not None and backend.prefix_block_tokens() > 0) else None
+        self.prefill_policy = prefill_policy
+        self.burst_tokens = burst_tokens
+        self.cache_namespace = cache_namespace
+        self.waiting: deque = deque()
+        self.seqs: dict = {}           # id -> _Seq (admitted)
+        self.order: list = []          # admitted ids in arrival order
+        self.free_slots = list(range(backend.max_slots - 1, -1, -1)) if admission is None else None
+        self.events: list = []
+        self.counters = dict(rounds=0, rows=0, prefill_tokens=0, decode_tokens=0, drafted=0, accepted=0, cached_tokens=0, requests=0,
+                             finished=0, errors=0)
+        self.phase_ns = dict(draft=0, verify=0, commit=0, prefill=0)
+
+    # ------------------------------------------------------------------ submit / cancel
+    def check(self, req: Request) -> None:
+        """Refuse what can never run (fail closed), before queueing."""
+        if not req.prompt:
+            raise ValueError("empty prompt")
+        if any((not isinstance(t, int)) or t < 0 or t >= self.backend.vocab_size for t in req.prompt):
+            raise ValueError("prompt token outside the vocabulary")
+        if req.max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be at least 1")
+        (req.sampling or Sampling()).validate()
+        if self.admission is not None:
+            self.admission.check(len(req.prompt) + req.max_new_tokens)
+
+    def submit(self, req: Request) -> None:
+        """Deferred submit: validated now, admitted in arrival order when memory and a slot allow."""
+        self.check(req)
+        if req.sampling is None:
+            req.sampling = Sampling()
+        if req.sampling.seed == 0 and req.sampling.temperature > 0:
+            req.sampling = req.sampling.with_seed(seed_for(req.prompt, 0))
+        self.waiting.append((req, time.monotonic()))
+        self.counters["requests"] += 1
+
+    def cancel(self, rid: str, reason: str = "cancelled") -> bool:
+        for i, (r, _) in enumerate(self.waiting):
+            if r.id == rid:
+                del self.waiting[i]
+                self.events.append(Event("done", rid, reason=reason, usage=self._usage(None, r)))
+                return True
+        s = self.seqs.get(rid)
+        if s is None:
+            return False
+        self._finish(s, reason)
+        return True
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.seqs)
+
+    def active_count(self) -> int:
+        return len(self.seqs)
+
+    def take_events(self) -> list:
+        ev, self.events = self.events, []
+        return ev
+
+    # ------------------------------------------------------------------ admission
+    def _admit(self) -> None:
+        while self.waiting:
+            req, t0 = self.waiting[0]
+            need = len(req.prompt) + req.max_new_tokens
+            try:
+                if self.admission is not None:
+                    slot = self.admission.admit(need)
+                else:
+                    if not self.free_slots:
+                        return
+                    slot = self.free_slots.pop()
+            except AdmitError as e:
+                if e.kind in ("NoMemory", "NoSlot"):
+                    if self.prefix is not None and e.kind == "NoMemory" and len(self.prefix):
+                        freed = self.prefix.evict_bytes(e.info.get("needed", 0) - e.info.get("available", 0))
+                        if freed:
+                            self.backend.prefix_release(freed)
+                            continue
+                    return  # strictly in arrival order: the head waits, nobody overtakes
+                self.waiting.popleft()
+                self.events.append(Event("error", req.id, reason="error", message=str(e)))
+                continue
+            self.waiting.popleft()
+            s = _Seq(req, slot, list(req.prompt), len(req.prompt), drafter=CopyDrafter(), stats=AcceptStats(), t_submit=t0)
+            self.seqs[req.id] = s
+            self.order.append(req.id)
+            self._plan_prefix(s)
+
+    def _plan_prefix(self, s: _Seq) -> None:
+        if self.prefix is None or not s.req.prefix_cache:
+            return
+        bt = self.backend.prefix_block_tokens()
+        s.hashes = chain_hashes(s.tokens[:s.prompt_len], bt, self.cache_namespace)
+        chain = self.prefix.lookup(s.hashes, s.prompt_len)
+        if chain:
+            n = self.backend.prefix_restore(s.slot, [e.handle for e in chain])
+            s.prefilled = s.cached = n
+            s.committed_blocks = n // bt
+            self.counters["cached_tokens"] += n
+
+    # ------------------------------------------------------------------ the step
+    def step(self) -> list:
+        """One scheduling iteration; returns the events it produced."""
+        self._expire()
+        self._admit()
+        try:
+            self._decode_round()
+            self._prefill()
+        except BackendError as e:
+            self.counters["errors"] += 1
+            if e.fatal:
+                raise StepError("Fatal", str(e), True)
+            for rid in list(self.seqs):
+                self._finish(self.seqs[rid], "error", message=str(e))
+            raise StepError("Backend", str(e), False)
+        return self.take_events()
+
+    def run_until_idle(self, max_steps: int = 1 << 30) -> list:
+        out = []
+        for _ in range(max_steps):
+            if not self.has_work():
+                break
+            out.extend(self.step())
+        return out
+
+    def _expire(self) -> None:
+        now = time.monotonic()
+        for req, _ in list(self.waiting):
+            if req.deadline is not None and now > req.deadline:
+                self.cancel(req.id, "deadline")
+        for s in list(self.seqs.values()):
+            if s.req.deadline is not None and now > s.req.deadline:
+                self._finish(s, "deadline")
+
+    def _check_backend(self) -> None:
+        err = self.backend.take_error()
+        if err is not None:
+            raise err
+
+    # ------------------------------------------------------------------ decode round
+    def _decode_round(self) -> None:
+        active = [self.seqs[i] for i in self.order if self.seqs[i].prefilled >= self.seqs[i].prompt_len and self.seqs[i].generated > 0]
+        if not active:
+            return
+        active = active[:self.window_rows]
+        t0 = time.perf_counter_ns()
+        # 1. how many drafts each stream may use
+        maxes = []
+        for s in active:
+            room = s.req.max_new_tokens - s.generated
+            m = min(self.max_drafts, max(0, room - 1)) if (self.spec.enabled and s.req.draft) else 0
+            maxes.append(m)
+        # 2. proposals: native drafter first, copy drafter otherwise
+        proposals = [[] for _ in active]
+        if any(maxes):
+            if self.spec.native and self.backend.supports_native_draft():
+                asks = [DraftAsk(s.slot, s.tokens, m, s.req.sampling) for s, m in zip(active, maxes) if m > 0]
+                offers = self.backend.propose_batch(asks)
+                for i, s in enumerate(active):
+                    off = offers.get(s.slot)
+                    if off is not None and maxes[i] > 0:
+                        proposals[i] = list(off.tokens[:maxes[i]])
+            if self.spec.copy:
+                for i, s in enumerate(active):
+                    if not proposals[i] and maxes[i] > 0:
+                        proposals[i] = s.drafter.propose(s.tokens, maxes[i])
+        # 3. budget: share the window's rows by expected value
+        budget = self.window_rows
+        demands = [Demand.geometric(s.stats.accept_rate(), len(p)) for s, p in zip(active, proposals)]
+        if self.cost is not None:
+            _, alloc = choose_budget(self.cost, demands, budget)
+        else:
+            from ..sched import allocate
+            alloc = allocate(demands, budget)
+        for i in range(len(active)):
+            proposals[i] = proposals[i][:alloc[i]]
+        t1 = time.perf_counter_ns()
+        # 4. the window
+        reqs = [RowRequest(s.slot, [s.tokens[-1]] + p, len(s.tokens) - 1) for s, p in zip(active, proposals)]
+        cand = max(s.req.sampling.candidate_count(self.backend.vocab_size) for s in active)
+        cand = min(cand, 64)
+        greedy = [s.req.sampling.temperature == 0.0 for s in active]
+        rows = self.backend.step_verified(reqs, cand, greedy)
+        self._check_backend()
+        t2 = time.perf_counter_ns()
+        if len(rows) != len(reqs) or any(len(r) != len(q.tokens) for r, q in zip(rows, reqs)):
+            raise BackendError("backend returned a window of the wrong shape", fatal=False)
+        self.counters["rounds"] += 1
+        self.counters["rows"] += sum(len(q.tokens) for q in reqs)
+        # 5. sample every row at its own position, accept the matching prefix, commit or finish
+        for s, p, out in zip(active, proposals, rows):
+            base = len(s.tokens)
+            try:
+                samples = [choose(o.values, o.ids, base + j, s.req.sampling) for j, o in enumerate(out)]
+            except SamplingError as e:
+                self._finish(s, "error", message=f"sampling failed: {e}")  # a NaN row fails only its sequence
+                continue
+            a = accept(p, samples)
+            s.rounds += 1
+            if p:
+                s.stats.update(len(p), a)
+                s.drafted += len(p)
+                s.accepted += a
+                self.counters["drafted"] += len(p)
+                self.counters["accepted"] += a
+            else:
+                s.stats.relax()
+            new = samples[:a + 1]
+            emitted, reason = [], None
+            for t in new:
+                emitted.append(t)
+                s.tokens.append(t)
+                s.generated += 1
+                if t in s.req.stop_ids:
+                    reason = "stop"
+                    break
+                if s.generated >= s.req.max_new_tokens:
+                    reason = "length"
+                    break
+            self.counters["decode_tokens"] += len(emitted)
+            self.events.append(Event("tokens", s.req.id, tokens=emitted))
+            if reason is not None:
+                self._finish(s, reason)
+            else:
+                self.backend.commit(s.slot, len(emitted))
+        self.phase_ns["draft"] += t1 - t0
+        self.phase_ns["verify"] += t2 - t1
+        self.phase_ns["commit"] += time.perf_counter_ns() - t2
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill(self) -> None:
+        pending = [self.seqs[i] for i in self.order if i in self.seqs and (self.seqs[i].prefilled < self.seqs[i].prompt_len or self.seqs[i].generated == 0)]
+        if not pending:
+            return
+        t0 = time.perf_counter_ns()
+        if self.prefill_policy == "burst":
+            # short prompts that fit one slice each are batched into one backend call
+            short = [s for s in pending if s.prompt_len - s.prefilled <= self.burst_tokens]
+            batch, used = [], 0
+            for s in short:
+                n = s.prompt_len - s.prefilled
+                if batch and used + n > self.prefill_chunk:
+                    break
+                batch.append(s)
+                used += n
+            if len(batch) > 1:
+                items = [(s.slot, s.prefilled, s.tokens[s.prefilled:s.prompt_len], True) for s in batch]
+                cand = min(64, max(s.req.sampling.candidate_count(self.backend.vocab_size) for s in batch))
+                outs = self.backend.prefill_slices(items, cand)
+                self._check_backend()
+                for s, o in zip(batch, outs):
+                    self.counters["prefill_tokens"] += s.prompt_len - s.prefilled
+                    s.prefilled = s.prompt_len
+                    self._complete_prefill(s, o)
+                self.phase_ns["prefill"] += time.perf_counter_ns() - t0
+                return
+        s = pending[0]
+        n = min(self.prefill_chunk, s.prompt_len - s.prefilled)
+        last = s.prefilled + n >= s.prompt_len
+        cand = min(64, s.req.sampling.candidate_count(self.backend.vocab_size))
+        out = self.backend.prefill_slice(s.slot, s.prefilled, s.tokens[s.prefilled:s.prefilled + n], cand, last)
+        self._check_backend()
+        s.prefilled += n
+        self.counters["prefill_tokens"] += n
+        self._commit_prefix(s)   # progressive checkpoints: a cancelled long prompt resumes from its last full block
+        if last:
+            self._complete_prefill(s, out)
+        self.phase_ns["prefill"] += time.perf_counter_ns() - t0
+
+    def _commit_prefix(self, s: _Seq) -> None:
+        if self.prefix is None or not s.req.prefix_cache or s.hashes is None:
+            return
+        bt = self.backend.prefix_block_tokens()
+        full = min(s.prefilled, s.prompt_len) // bt
+        if full <= s.committed_blocks:
+            return
+        handles = self.backend.prefix_commit(s.slot, full)
+        if not handles:
+            return
+        dup, evicted = self.prefix.insert(s.hashes[:full], handles, self.backend.prefix_bytes_per_block())
+        drop = list(dup) + list(evicted)
+        if drop:
+            self.backend.prefix_release(drop)
+        s.committed_blocks = full
+
+    def _complete_prefill(self, s: _Seq, out) -> None:
+        self._commit_prefix(s)
+        if out is None:
+            raise BackendError("backend returned no candidates for the last prompt row", fatal=False)
+        try:
+            t = choose(out.values, out.ids, s.prompt_len, s.req.sampling)
+        except SamplingError as e:
+            self._finish(s, "error", message=f"sampling failed: {e}")
+            return
+        s.tokens.append(t)
+        s.generated = 1
+        s.t_first = time.monotonic()
+        self.counters["decode_tokens"] += 1
+        self.events.append(Event("tokens", s.req.id, tokens=[t]))
+        if t in s.req.stop_ids:
+            self._finish(s, "stop")
+        elif s.generated >= s.req.max_new_tokens:
+            self._finish(s, "length")
+
+    # ------------------------------------------------------------------ finish
+    def _usage(self, s, req=None) -> dict:
+        if s is None:
+            return dict(prompt_tokens=len(req.prompt), completion_tokens=0, total_tokens=len(req.prompt), cached_tokens=0,
+                        spec=dict(drafted=0, accepted=0, rounds=0))
+        u = dict(prompt_tokens=s.prompt_len, completion_tokens=s.generated, total_tokens=s.prompt_len + s.generated, cached_tokens=s.cached,
+                 spec=dict(drafted=s.drafted, accepted=s.accepted, rounds=s.rounds))
+        if s.t_first is not None:
+            u["ttft_s"] = s.t_first - s.t_submit
+        return u
+
+    def _finish(self, s: _Seq, reason: str, message: str = "") -> None:
+        self.backend.release(s.slot)
+        if self.admission is not None:
+            self.admission.release(s.slot)
+        else:
+            self.free_slots.append(s.slot)
+        del self.seqs[s.req.id]
+        self.order.remove(s.req.id)
+        self.counters["finished"] += 1
+        kind = "error" if reason == "error" else "done"
+        self.events.append(Event(kind, s.req.id, reason=reason, usage=self._usage(s), message=message))
+
+
+def generate(engine: Engine, prompts: list, max_new_tokens: int = 32, sampling: Sampling | None = None, stop_ids=()) -> list:
+    """Offline generation: run `prompts` (token-id lists) to completion and return the generated ids of each."""
+    out = {}
+    for i, p in enumerate(prompts):
+        engine.submit(Request(str(i), list(p), max_new_tokens, sampling, tuple(stop_ids)))
+        out[str(i)] = []
+    while engine.has_work():
+        for ev in engine.step():
+            if ev.kind == "tokens":
+                out[ev.id].extend(ev.tokens)
+            elif ev.kind == "error":
+                raise RuntimeError(f"request {ev.id}: {ev.message}")
+    return [out[str(i)] for i in range(len(prompts))]

@@ -1,0 +1,214 @@
+"""CPU mock model: logits depend only on the context, state is deep (paged KV with refcounts, per-slot committed
+tokens, pending windows), and it can be told to violate each exactness property so the harness is proven to catch it.
+
+Behaviour parity: reference crates/engine/src/mock.rs:1-120 (MockBackend, MockOptions from ``key=value`` strings),
+:24-36 (Fault::{WindowDependent, ChunkDependent, RollbackLeak}), :38-83 (Faults: panic / fatal / retryable at a
+step, poisoned first token).
+"""
+from __future__ import annotations
+
+import hashlib
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from ..sched import BlockPool
+from .backend import Backend, BackendError, DraftOffer, RowOutput
+
+
+@dataclass
+class MockOptions:
+    vocab: int = 512
+    slots: int = 8
+    max_rows: int = 64
+    order: int = 0                 # 0: the next token depends on the WHOLE context (deep state); n > 0: on the last n tokens only (text repeats)
+    blocks: int = 4096
+    block_tokens: int = 64
+    fault: str = ""                # "" | window_dependent | chunk_dependent | rollback_leak | prefix_stale
+    native_draft: bool = False
+    draft_error: float = 0.25      # probability a native draft token is wrong
+    panic_at_step: int = -1
+    fatal_at_step: int = -1
+    retryable_from_step: int = -1
+    nan_at_step: int = -1
+    eos: int = -1                  # token the model emits after `eos_after` generated tokens (-1: never)
+    eos_after: int = 0
+    latency_ms: float = 0.0
+
+    @staticmethod
+    def parse(text: str) -> "MockOptions":
+        """``key=value,key=value`` as accepted by ``--mock`` on the server command line; unknown keys are refused by name."""
+        o = MockOptions()
+        for item in filter(None, (t.strip() for t in text.split(","))):
+            k, _, v = item.partition("=")
+            if not hasattr(o, k):
+                raise ValueError(f"unknown mock option {k!r}")
+            cur = getattr(o, k)
+            setattr(o, k, (v.lower() in ("1", "true", "yes", "on")) if isinstance(cur, bool) else type(cur)(v))
+        return o
+
+
+def _h(data: bytes) -> int:
+    return int.from_bytes(hashlib.blake2b(data, digest_size=8).digest(), "little")
+
+
+class MockBackend(Backend):
+    name = "mock"
+
+    def __init__(self, opts: MockOptions | None = None):
+        self.o = opts or MockOptions()
+        self.vocab_size = self.o.vocab
+        self.max_rows = self.o.max_rows
+        self.max_slots = self.o.slots
+        self.pool = BlockPool(self.o.blocks, self.o.block_tokens)
+        self.ctx = {}          # slot -> committed tokens
+        self.blocks = {}       # slot -> block ids
+        self.pending = {}      # slot -> tokens fed by the last window (beyond the committed ones)
+        self.leak = {}         # slot -> junk leaked by a faulty rollback
+        self.steps = 0
+        self.error = None
+        self.generated = {}
+
+    # ---------------------------------------------------------------- the "model"
+    def _row(self, context, count: int, salt: int = 0) -> RowOutput:
+        o = self.o
+        tail = context[-o.order:] if o.order > 0 else context
+        key = struct.pack(f"<{len(tail)}I", *[t & 0xFFFFFFFF for t in tail]) + struct.pack("<q", salt)
+        rng = np.random.default_rng(_h(key))
+        full = min(64, o.vocab)   # the row does not depend on how many candidates are asked for
+        ids = rng.choice(o.vocab, size=full, replace=False).astype(np.uint32)
+        vals = np.sort(rng.normal(0, 2.0, size=full).astype(np.float32))[::-1].copy()
+        vals[0] += 1.5  # a clear favourite most of the time
+        order = np.lexsort((ids, -vals.astype(np.float64)))
+        n = min(count, full)
+        return RowOutput(ids[order][:n].copy(), vals[order][:n].copy())
+
+    def _ensure_blocks(self, slot: int, tokens: int) -> None:
+        have = self.blocks.setdefault(slot, [])
+        need = self.pool.blocks_for(tokens) - len(have)
+        if need > 0:
+            got = self.pool.alloc(need)
+            if got is None:
+                raise BackendError("mock KV pool exhausted", fatal=False)
+            have.extend(got)
+
+    def _tick(self) -> None:
+        self.steps += 1
+        o = self.o
+        if self.steps == o.panic_at_step:
+            raise RuntimeError("mock panic")
+        if self.steps == o.fatal_at_step:
+            raise BackendError("mock fatal device error", fatal=True)
+        if o.retryable_from_step >= 0 and self.steps >= o.retryable_from_step:
+            self.error = BackendError("mock retryable error", fatal=False)
+
+    # ---------------------------------------------------------------- Backend
+    def prefill_slice(self, slot, start, tokens, candidates, last):
+        self._tick()
+        ctx = self.ctx.setdefault(slot, [])
+        if start != len(ctx):
+            raise BackendError(f"prefill at {start} but slot {slot} holds {len(ctx)} tokens", fatal=False)
+        ctx.extend(tokens)
+        self.pending.pop(slot, None)
+        self._ensure_blocks(slot, len(ctx))
+        if not last:
+            return None
+        salt = len(tokens) if self.o.fault == "chunk_dependent" else 0
+        return self._row(ctx + self.leak.get(slot, []), candidates, salt)
+
+    def step(self, reqs, candidates):
+        self._tick()
+        out = []
+        total_rows = sum(len(r.tokens) for r in reqs)
+        for r in reqs:
+            ctx = self.ctx.setdefault(r.slot, [])
+            if r.first_position != len(ctx):
+                raise BackendError(f"window at {r.first_position} but slot {r.slot} holds {len(ctx)} tokens", fatal=False)
+            self._ensure_blocks(r.slot, len(ctx) + len(r.tokens))
+            self.pending[r.slot] = list(r.tokens)
+            rows = []
+            for j in range(len(r.tokens)):
+                c = ctx + list(r.tokens[:j + 1]) + self.leak.get(r.slot, [])
+                salt = total_rows if self.o.fault == "window_dependent" else 0
+                row = self._row(c, candidates, salt)
+                if self.steps == self.o.nan_at_step:
+                    row.values[0] = np.nan
+                if self.o.eos >= 0 and self.generated.get(r.slot, 0) + j >= self.o.eos_after:
+                    row.ids[0] = self.o.eos
+                rows.append(row)
+            out.append(rows)
+        return out
+
+    def commit(self, slot, keep):
+        ctx = self.ctx[slot]
+        pend = self.pending.pop(slot, [])
+        # the window fed [last, d1..dk]; the first `keep` of those rows become part of the context, the rest never happened
+        kept = pend[:keep]
+        if self.o.fault == "rollback_leak" and len(pend) > len(kept):
+            self.leak[slot] = [pend[len(kept)]]
+        self.generated[slot] = self.generated.get(slot, 0) + keep
+        ctx.extend(kept)
+
+    def release(self, slot):
+        self.ctx.pop(slot, None)
+        self.pending.pop(slot, None)
+        self.leak.pop(slot, None)
+        self.generated.pop(slot, None)
+        b = self.blocks.pop(slot, None)
+        if b:
+            self.pool.release(b)
+
+    def take_error(self):
+        e, self.error = self.error, None
+        return e
+
+    def supports_native_draft(self):
+        return self.o.native_draft
+
+    def propose_batch(self, asks):
+        out = {}
+        for a in asks:
+            ctx, toks = list(a.context), []
+            for j in range(a.max_drafts):
+                row = self._row(ctx, 4)
+                t = int(row.ids[0])
+                if (_h(struct.pack("<qq", len(ctx), t)) % 1000) / 1000.0 < self.o.draft_error:
+                    t = (t + 1) % self.o.vocab
+                toks.append(t)
+                ctx.append(t)
+            out[a.slot] = DraftOffer(toks, [0.7] * len(toks))
+        return out
+
+    # prefix cache: blocks are shared by refcount
+    def prefix_block_tokens(self):
+        return self.o.block_tokens
+
+    def prefix_bytes_per_block(self):
+        return self.o.block_tokens * 1024
+
+    def prefix_commit(self, slot, blocks):
+        ids = self.blocks.get(slot, [])[:blocks]
+        ctx = self.ctx[slot]
+        handles = []
+        for i, b in enumerate(ids):
+            self.pool.retain([b])
+            handles.append(("blk", b, tuple(ctx[i * self.o.block_tokens:(i + 1) * self.o.block_tokens])))
+        return handles
+
+    def prefix_restore(self, slot, handles):
+        ctx = self.ctx.setdefault(slot, [])
+        assert not ctx
+        ids = []
+        for _, b, toks in handles:
+            self.pool.retain([b])
+            ids.append(b)
+            ctx.extend(toks)
+        if self.o.fault == "prefix_stale" and ctx:
+            ctx[-1] = (ctx[-1] + 1) % self.o.vocab
+        self.blocks[slot] = ids
+        return len(ctx)
+
+    def prefix_release(self, handles):
+        for _, b, _ in handles:
+            self.pool.release([b])
