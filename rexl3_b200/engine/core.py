@@ -93,6 +93,7 @@ class Engine:
         self.counters = dict(rounds=0, rows=0, prefill_tokens=0, decode_tokens=0, drafted=0, accepted=0, cached_tokens=0, requests=0,
                              finished=0, errors=0)
         self.phase_ns = dict(draft=0, verify=0, commit=0, prefill=0)
+        self.pause_decode = False      # hold decode rounds (used while a benchmark fills the batch with prompts)
 
     # ------------------------------------------------------------------ submit / cancel
     def check(self, req: Request) -> None:
@@ -221,6 +222,8 @@ class Engine:
 
     # ------------------------------------------------------------------ decode round
     def _decode_round(self) -> None:
+        if self.pause_decode:
+            return
         active = [self.seqs[i] for i in self.order if self.seqs[i].prefilled >= self.seqs[i].prompt_len and self.seqs[i].generated > 0]
         if not active:
             return

@@ -1,0 +1,66 @@
+"""CPU reference backend: the fp32 PyTorch executor over dequantized EXL3 weights behind the engine's Backend contract.
+
+Runs the CPU plumbing configuration (tiny Llama-style decoder) without a GPU and serves as the oracle for the device
+backend.  Each sequence is computed on its own, so row invariance holds by construction.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..models.dense import HostWeights, ReferenceDense
+from ..sampling import top_candidates
+from .backend import Backend, BackendError, RowOutput
+
+
+class CpuDenseBackend(Backend):
+    name = "cpu-reference"
+
+    def __init__(self, weights: HostWeights, max_slots: int = 8, max_rows: int = 64, dtype=torch.float32):
+        self.model = ReferenceDense(weights, device="cpu", dtype=dtype)
+        self.cfg = weights.cfg
+        self.vocab_size = weights.cfg.vocab
+        self.max_slots, self.max_rows = max_slots, max_rows
+        self.len = {}
+        self.pending = {}
+        self.last_logits = None
+
+    def _rows(self, logits: torch.Tensor, candidates: int):
+        out = []
+        for r in logits.numpy():
+            ids, vals = top_candidates(r, candidates)
+            out.append(RowOutput(ids, vals))
+        return out
+
+    def prefill_slice(self, slot, start, tokens, candidates, last):
+        if start != self.len.get(slot, 0):
+            raise BackendError(f"prefill at {start} but slot {slot} holds {self.len.get(slot, 0)} tokens")
+        logits = self.model.forward_seq(slot, tokens, start)
+        self.len[slot] = start + len(tokens)
+        self.last_logits = logits[-1:].clone()
+        return self._rows(logits[-1:], candidates)[0] if last else None
+
+    def step(self, reqs, candidates):
+        out = []
+        for r in reqs:
+            if r.first_position != self.len.get(r.slot, 0):
+                raise BackendError(f"window at {r.first_position} but slot {r.slot} holds {self.len.get(r.slot, 0)} tokens")
+            logits = self.model.forward_seq(r.slot, r.tokens, r.first_position)
+            self.pending[r.slot] = len(r.tokens)
+            out.append(self._rows(logits, candidates))
+        return out
+
+    def commit(self, slot, keep):
+        keep = min(keep, self.pending.pop(slot, 0))
+        self.len[slot] = self.len.get(slot, 0) + keep
+        self.model.truncate(slot, self.len[slot])
+
+    def release(self, slot):
+        self.len.pop(slot, None)
+        self.pending.pop(slot, None)
+        self.model.reset(slot)
+
+    def score_rows(self, slot, start, tokens):
+        logits = self.model.forward_seq(slot, tokens, start)
+        self.model.truncate(slot, start)
+        return logits.numpy()

@@ -1,0 +1,270 @@
+"""Backend over the sm_100a dense executor: slots, paged KV bookkeeping, pinned-host staging of the per-step row
+arrays, CUDA-graph replay of decode windows, device top-k with a small device->host read per step.
+
+Only this module touches the GPU on behalf of the engine (one engine thread owns the CUDA context, as in the
+reference's runtime, crates/server/src/runtime.rs:603).  Per step the host uploads five small int32 arrays
+(ids, positions, KV slots, row->sequence, context lengths) from pinned memory and reads back rows x count candidate
+(id, value) pairs; the full logits never leave the device (reference crates/model/src/forward.rs:1519-1552).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..models.dense import PAGE, DenseGPU
+from ..sched import BlockPool
+from .backend import Backend, BackendError, RowOutput
+
+CTX_BUCKET = 2048   # decode graphs are captured per (rows, candidate count, context bucket)
+
+
+class DenseGpuBackend(Backend):
+    name = "cuda"
+
+    def __init__(self, model: DenseGPU, max_slots: int | None = None, use_graphs: bool = True):
+        self.m = model
+        self.cfg = model.cfg
+        self.vocab_size = model.cfg.vocab
+        self.max_slots = max_slots or model.max_seqs
+        self.max_rows = min(256, model.max_rows)
+        self.use_graphs = use_graphs
+        self.pool = BlockPool(model.num_pages, PAGE)
+        self.len = [0] * self.max_slots            # committed tokens per slot
+        self.pages = [[] for _ in range(self.max_slots)]
+        self.pending = [0] * self.max_slots        # rows of the last window
+        dev = model.device
+        R = model.max_rows
+        self.h_rows = torch.zeros(5, R, dtype=torch.int32).pin_memory()
+        self.d_rows = torch.zeros(5, R, dtype=torch.int32, device=dev)
+        self.h_bt = torch.zeros(self.max_slots, model.max_blocks, dtype=torch.int32).pin_memory()
+        self.d_bt = torch.zeros(self.max_slots, model.max_blocks, dtype=torch.int32, device=dev)
+        self.bt_dirty = True
+        self.h_pf = torch.zeros(4, self.max_slots, dtype=torch.int32).pin_memory()
+        self.d_pf = torch.zeros(4, self.max_slots, dtype=torch.int32, device=dev)
+        self.h_cand_ids = torch.zeros(256, 64, dtype=torch.int32).pin_memory()
+        self.h_cand_vals = torch.zeros(256, 64, dtype=torch.float32).pin_memory()
+        self.h_status = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.graphs = {}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.graph_replays = 0
+        self.graph_captures = 0
+        self.graph_kernels = {}     # graph key -> kernels launched per replay
+        self.replayed_kernels = 0
+        self._err = None
+
+    # ------------------------------------------------------------------ pages
+    def _ensure(self, slot: int, tokens: int) -> None:
+        need = self.pool.blocks_for(tokens) - len(self.pages[slot])
+        if need <= 0:
+            return
+        if len(self.pages[slot]) + need > self.m.max_blocks:
+            raise BackendError(f"slot {slot}: {tokens} tokens exceed the {self.m.max_blocks * PAGE}-token window", fatal=False)
+        got = self.pool.alloc(need)
+        if got is None:
+            raise BackendError("KV page pool exhausted", fatal=False)
+        base = len(self.pages[slot])
+        self.pages[slot].extend(got)
+        self.h_bt[slot, base:base + need] = torch.tensor(got, dtype=torch.int32)
+        self.bt_dirty = True
+
+    def _sync_bt(self) -> None:
+        if self.bt_dirty:
+            self.d_bt.copy_(self.h_bt, non_blocking=True)
+            self.h2d_bytes += self.h_bt.numel() * 4
+            self.bt_dirty = False
+
+    def _fill_rows(self, specs) -> int:
+        """specs: list of (slot, first_position, tokens).  Fills the pinned staging rows; returns M."""
+        h = self.h_rows.numpy()
+        r = 0
+        for slot, p0, toks in specs:
+            n = len(toks)
+            pos = np.arange(p0, p0 + n, dtype=np.int64)
+            pg = np.asarray(self.pages[slot], dtype=np.int64)[pos // PAGE]
+            h[0, r:r + n] = toks
+            h[1, r:r + n] = pos
+            h[2, r:r + n] = pg * PAGE + pos % PAGE
+            h[3, r:r + n] = slot
+            h[4, r:r + n] = pos + 1
+            r += n
+        return r
+
+    def _upload_rows(self, M: int) -> None:
+        self.d_rows[:, :M].copy_(self.h_rows[:, :M], non_blocking=True)
+        self.h2d_bytes += 5 * M * 4
+
+    # ------------------------------------------------------------------ prefill
+    def prefill_slice(self, slot, start, tokens, candidates, last):
+        return self.prefill_slices([(slot, start, tokens, last)], candidates)[0]
+
+    def prefill_slices(self, items, candidates):
+        m = self.m
+        for slot, start, toks, _ in items:
+            if start != self.len[slot]:
+                raise BackendError(f"prefill at {start} but slot {slot} holds {self.len[slot]} tokens", fatal=False)
+            self._ensure(slot, start + len(toks))
+        M = self._fill_rows([(s, st, t) for s, st, t, _ in items])
+        if M > m.max_rows:
+            raise BackendError(f"prefill slice of {M} rows exceeds the {m.max_rows}-row scratch", fatal=False)
+        n = len(items)
+        hp = self.h_pf.numpy()
+        q0 = 0
+        last_rows = []
+        for i, (slot, start, toks, last) in enumerate(items):
+            hp[0, i], hp[1, i], hp[2, i], hp[3, i] = slot, q0, len(toks), start
+            q0 += len(toks)
+            if last:
+                last_rows.append(q0 - 1)
+        self._upload_rows(M)
+        self._sync_bt()
+        self.d_pf[:, :n].copy_(self.h_pf[:, :n], non_blocking=True)
+        self.h2d_bytes += 4 * n * 4
+        d = self.d_rows
+        pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=n,
+                  max_qlen=max(len(t) for _, _, t, _ in items))
+        lr = torch.tensor(last_rows, dtype=torch.long, device=m.device) if last_rows else None
+        logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr,
+                                want_logits=bool(last_rows))
+        for slot, start, toks, _ in items:
+            self.len[slot] = start + len(toks)
+            self.pending[slot] = 0
+        outs = [None] * n
+        if last_rows:
+            rows = self._read_candidates(logits, candidates)
+            k = 0
+            for i, (_, _, _, last) in enumerate(items):
+                if last:
+                    outs[i] = rows[k]
+                    k += 1
+        self._check()
+        return outs
+
+    # ------------------------------------------------------------------ decode / verify window
+    def step(self, reqs, candidates):
+        m = self.m
+        specs = []
+        for r in reqs:
+            if r.first_position != self.len[r.slot]:
+                raise BackendError(f"window at {r.first_position} but slot {r.slot} holds {self.len[r.slot]} tokens", fatal=False)
+            self._ensure(r.slot, r.first_position + len(r.tokens))
+            self.pending[r.slot] = len(r.tokens)
+            specs.append((r.slot, r.first_position, r.tokens))
+        M = self._fill_rows(specs)
+        if M > self.max_rows:
+            raise BackendError(f"window of {M} rows exceeds {self.max_rows}", fatal=False)
+        max_ctx = max(r.first_position + len(r.tokens) for r in reqs)
+        bucket = min(m.max_ctx_alloc, (max_ctx + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
+        self._upload_rows(M)
+        self._sync_bt()
+        count = max(1, min(64, candidates))
+        if self.use_graphs:
+            key = (M, count, bucket)
+            g = self.graphs.get(key)
+            if g is None:
+                g = self._capture(M, count, bucket)
+                self.graphs[key] = g
+            g.replay()
+            self.graph_replays += 1
+            self.replayed_kernels += self.graph_kernels[key]
+        else:
+            self._window(M, count, bucket)
+        rows = self._download(M, count)
+        self._check()
+        out, k = [], 0
+        for r in reqs:
+            out.append(rows[k:k + len(r.tokens)])
+            k += len(r.tokens)
+        return out
+
+    def _window(self, M: int, count: int, bucket: int) -> None:
+        d = self.d_rows
+        logits = self.m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, max_ctx=bucket)
+        self.m.candidates(logits, count)
+
+    def _capture(self, M: int, count: int, bucket: int):
+        # one eager run first: sets function attributes, resolves driver entry points, warms the allocator
+        self._window(M, count, bucket)
+        torch.cuda.synchronize()
+        from ..ops import lib as _oplib
+        g = torch.cuda.CUDAGraph()
+        n0 = _oplib.launch_count
+        with torch.cuda.graph(g):
+            self._window(M, count, bucket)
+        self.graph_kernels[(M, count, bucket)] = _oplib.launch_count - n0
+        self.graph_captures += 1
+        return g
+
+    def _download(self, M: int, count: int):
+        ids, vals = self.m._ids_view(M, count), self.m._vals_view(M, count)
+        hi, hv = self.h_cand_ids.view(-1)[:M * count].view(M, count), self.h_cand_vals.view(-1)[:M * count].view(M, count)
+        hi.copy_(ids, non_blocking=True)
+        hv.copy_(vals, non_blocking=True)
+        self.h_status.copy_(self.m.status, non_blocking=True)   # bounded-wait status words ride along with the candidates
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += M * count * 8 + 16
+        a, b = hi.numpy().astype(np.uint32), hv.numpy().copy()
+        return [RowOutput(a[i], b[i]) for i in range(M)]
+
+    def _read_candidates(self, logits, candidates):
+        count = max(1, min(64, candidates))
+        R = logits.shape[0]
+        self.m.candidates(logits, count)
+        return self._download(R, count)
+
+    def _check(self) -> None:
+        s = self.h_status.tolist()
+        if s[0] != 0:
+            self.m.status.zero_()
+            self.h_status.zero_()
+            self._err = BackendError(f"device status code {s[0]} at site {s[1]} (block {s[2]})", fatal=True)
+
+    def take_error(self):
+        e, self._err = self._err, None
+        return e
+
+    def commit(self, slot, keep):
+        keep = min(keep, self.pending[slot])
+        self.len[slot] += keep
+        self.pending[slot] = 0
+
+    def release(self, slot):
+        if self.pages[slot]:
+            self.pool.release(self.pages[slot])
+        self.pages[slot] = []
+        self.len[slot] = 0
+        self.pending[slot] = 0
+        self.h_bt[slot].zero_()
+        self.bt_dirty = True
+
+    # ------------------------------------------------------------------ prefix cache: pages are shared by refcount
+    def prefix_block_tokens(self):
+        return PAGE
+
+    def prefix_bytes_per_block(self):
+        return self.cfg.kv_bytes_per_token() * PAGE
+
+    def prefix_commit(self, slot, blocks):
+        ids = self.pages[slot][:blocks]
+        self.pool.retain(ids)
+        return [("page", p) for p in ids]
+
+    def prefix_restore(self, slot, handles):
+        assert self.len[slot] == 0 and not self.pages[slot]
+        ids = [p for _, p in handles]
+        self.pool.retain(ids)
+        self.pages[slot] = list(ids)
+        self.h_bt[slot, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        self.bt_dirty = True
+        self.len[slot] = len(ids) * PAGE
+        return self.len[slot]
+
+    def prefix_release(self, handles):
+        self.pool.release([p for _, p in handles])
+
+    def quiesce(self):
+        torch.cuda.synchronize()
+
+    def stats(self):
+        return dict(graph_replays=self.graph_replays, graph_captures=self.graph_captures, replayed_kernels=self.replayed_kernels, h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes,
+                    free_pages=self.pool.free_blocks())

@@ -245,14 +245,32 @@ class DenseGPU:
     one or more prompt chunks (prefill).
     """
 
-    def __init__(self, w: HostWeights, num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256, device="cuda",
-                 max_prefill_rows: int = 8192):
+    def __init__(self, w: "HostWeights | DenseConfig", num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256,
+                 device="cuda", max_prefill_rows: int = 8192, seed: int = 0):
+        """`w` is either host weights (uploaded as stored) or a bare config (random-init EXL3 weights are then generated on the
+        device: any random bit ring is a valid trellis, which is how benchmark models of tens of GB are made in seconds)."""
         from ..ops import kernels as K
         self.K = K
-        self.cfg = cfg = w.cfg
         self.device = device
+        if isinstance(w, DenseConfig):
+            self.cfg = cfg = w
+            self._load_random(seed)
+        else:
+            self.cfg = cfg = w.cfg
+            self._load_host(w)
         self.num_pages, self.max_seqs, self.max_blocks = num_pages, max_seqs, max_blocks_per_seq
         self.max_rows = max(max_rows, max_prefill_rows)
+        self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
+        # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16, plus their TMA descriptors
+        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        self.tk = [K.KvTensorMap(c) for c in self.k_cache]
+        self.tv = [K.KvTensorMap(c) for c in self.v_cache]
+        self.status = K.new_status(device)
+        self._alloc_scratch(self.max_rows)
+
+    def _load_host(self, w: HostWeights) -> None:
+        K, device = self.K, self.device
         dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
         up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731
         self.embed = dev(w.embed, torch.bfloat16)
@@ -264,15 +282,36 @@ class DenseGPU:
                                     k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16)))
         self.final_norm = dev(w.final_norm, torch.bfloat16)
         self.lm_head = up(w.lm_head)
-        self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
-        # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16, plus their TMA descriptors
-        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
-        self.tk = [K.KvTensorMap(c) for c in self.k_cache]
-        self.tv = [K.KvTensorMap(c) for c in self.v_cache]
-        self.status = K.new_status(device)
-        self._alloc_scratch(self.max_rows)
-        self.graphs = {}
+
+    def _load_random(self, seed: int) -> None:
+        cfg, K, device = self.cfg, self.K, self.device
+        g = torch.Generator(device=device).manual_seed(seed)
+        tw = exl3.Bits.of(cfg.bits).tile_words
+        cb = cfg.codebook if exl3.Bits.of(cfg.bits).is_integer else "mul1"
+
+        def lin(k, n, scale, words=tw):
+            tr = torch.randint(-32768, 32768, (k // 16, n // 16, words), dtype=torch.int16, device=device, generator=g)
+            sg = lambda m: (torch.randint(0, 2, (m,), device=device, generator=g) * 2 - 1)  # noqa: E731
+            return K.Exl3Weight(tr, sg(k).to(torch.float16), (sg(n) * scale).to(torch.float16), None, cb)
+
+        norm = lambda: (1.0 + 0.1 * torch.randn(cfg.d_model, device=device, generator=g)).to(torch.bfloat16)  # noqa: E731
+        d, F, HQ = cfg.d_model, cfg.ffn_padded, cfg.n_q * cfg.head_dim
+        self.embed = torch.randn(cfg.vocab, d, device=device, generator=g).to(torch.bfloat16)
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            gu = lin(d, 2 * F, 1.0 / math.sqrt(d))
+            dn = lin(F, d, 0.5 / math.sqrt(F))
+            if F != cfg.ffn:
+                gu.svh[cfg.ffn:F] = 0
+                gu.svh[F + cfg.ffn:] = 0
+                dn.suh[cfg.ffn:] = 0
+            self.layers.append(dict(attn_norm=norm(), qkv=lin(d, cfg.qkv_width, 1.0 / math.sqrt(d)), o=lin(HQ, d, 0.5 / math.sqrt(HQ)),
+                                    ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
+        self.final_norm = norm()
+        hw = exl3.Bits.of(cfg.head_bits or cfg.bits).tile_words
+        self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d), hw)
+        if cfg.vocab_padded != cfg.vocab:
+            self.lm_head.svh[cfg.vocab:] = 0
 
     # ------------------------------------------------------------------ buffers
     def _alloc_scratch(self, R: int):
@@ -315,7 +354,7 @@ class DenseGPU:
         self.K.exl3_gemm(xr, w, self.part, s, self.status)
         return s
 
-    def forward_rows(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None):
+    def forward_rows(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True):
         """Run all layers over M rows.
 
         ids, positions, slots, row_seq, ctx_len: int32 device tensors [M] (slot = physical KV slot page*64+offset of the row's
@@ -360,6 +399,8 @@ class DenseGPU:
                 K.finish_add_norm_rot(self.part, s, M, L["down"], h, nxt["attn_norm"], cfg.eps, nxt["qkv"].suh, xr_d)
             else:
                 K.finish_add_norm_rot(self.part, s, M, L["down"], h, self.final_norm, cfg.eps, self.lm_head.suh, xr_d)
+        if not want_logits:
+            return None
         if logit_rows is not None:
             xl = xr_d.index_select(0, logit_rows).contiguous()
         else:
