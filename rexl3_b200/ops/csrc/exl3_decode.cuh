@@ -55,9 +55,38 @@ __device__ __forceinline__ uint32_t pair_to_half2(uint32_t sa, uint32_t sb) {
     }
     xa = (xa & 0x8FFF8FFFu) ^ 0x3B603B60u;
     xb = (xb & 0x8FFF8FFFu) ^ 0x3B603B60u;
-    const uint32_t lo = __byte_perm(xa, xb, 0x5410), hi = __byte_perm(xa, xb, 0x7632);
-    const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&lo), *reinterpret_cast<const __half2*>(&hi));
-    return *reinterpret_cast<const uint32_t*>(&r);
+    // lo + hi of each word as a half2 add with swizzled operands (fp16 pipe), then ONE byte permute packs the pair:
+    // the integer ALU pipe issues at half rate and is the bottleneck of the decode, so work is moved off it
+    const __half2 a = *reinterpret_cast<const __half2*>(&xa), b = *reinterpret_cast<const __half2*>(&xb);
+    const __half2 ra = __hadd2(__low2half2(a), __high2half2(a)), rb = __hadd2(__low2half2(b), __high2half2(b));
+    return __byte_perm(*reinterpret_cast<const uint32_t*>(&ra), *reinterpret_cast<const uint32_t*>(&rb), 0x7610);
+  }
+}
+
+// 4 sixteen-bit fields of X at MSB-first bit offsets 4, 8, 12, 16 in 5 integer operations
+__device__ __forceinline__ void extract4(uint32_t X, uint32_t& s0, uint32_t& s1, uint32_t& s2, uint32_t& s3) {
+  const uint32_t X4 = X >> 4;
+  s0 = __byte_perm(X4, 0, 0x4421);
+  s1 = __byte_perm(X, 0, 0x4421);
+  s2 = X4 & 0xFFFFu;
+  s3 = X & 0xFFFFu;
+}
+
+// 4.0 bpw fast path: 32 consecutive values from their 4 words (w[1..4]) and the word before them (w[0]).
+// Value q's window starts at bit 20 + 4q of w[]: per word pair the windows sit at offsets 4, 8, 12, 16 of
+// A = bits 16..47 of the pair and at the same offsets of the second word.
+template <int CB>
+__device__ __forceinline__ void decode32_b4(const uint32_t (&w)[5], uint32_t (&h2)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t A = __funnelshift_l(w[i + 1], w[i], 16), B = w[i + 1];
+    uint32_t s0, s1, s2, s3, s4, s5, s6, s7;
+    extract4(A, s0, s1, s2, s3);
+    extract4(B, s4, s5, s6, s7);
+    h2[4 * i + 0] = pair_to_half2<CB>(s0, s1);
+    h2[4 * i + 1] = pair_to_half2<CB>(s2, s3);
+    h2[4 * i + 2] = pair_to_half2<CB>(s4, s5);
+    h2[4 * i + 3] = pair_to_half2<CB>(s6, s7);
   }
 }
 

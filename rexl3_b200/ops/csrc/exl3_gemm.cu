@@ -29,7 +29,8 @@ constexpr int NDEC_GROUPS = 2;
 constexpr int NDEC_WARPS = 8;
 constexpr int GEMM_THREADS = 64 + NDEC_WARPS * 32;
 constexpr int RAW_STAGES = 8;      // compressed-trellis ring depth
-constexpr int OP_STAGES = 3;       // operand (A + B) ring depth
+constexpr int OP_STAGES = 3;       // operand (A + B) ring depth; must be >= NDEC_GROUPS (a group may not run two barrier phases ahead)
+static_assert(OP_STAGES >= NDEC_GROUPS, "operand ring shallower than the number of decode groups");
 
 struct GemmSmemLayout {
   int a_off, b_off, raw_off, bar_off, total;
@@ -157,6 +158,53 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
     const int t = (dw % (NDEC_WARPS / NDEC_GROUPS)) * 32 + lane;  // 0..127 inside the group
     const int h = t & 3, ktl = (t >> 2) & 3, nt = t >> 4;
     bool ok = true;
+    if constexpr (TWICE == 8) {
+      // ---- 4.0 bpw fast path.  A thread owns the two eighths 2h and 2h+1 of its tile (two 16-byte loads, conflict free
+      // because odd k-tiles take them in the other order), gets the one word before each from its own other eighth or from
+      // the neighbouring lane, and releases the raw stage as soon as everything is in registers.
+      const int x = ktl & 1;
+      const int g1 = 2 * h + x, g2 = 2 * h + 1 - x;
+      const int n1 = 16 * nt + g1, n2 = 16 * nt + g2;
+      const int o1 = (n1 >> 3) * 1024 + (n1 & 7) * 128 + (((2 * ktl) ^ (g1 & 7)) << 4);
+      const int o2 = (n2 >> 3) * 1024 + (n2 & 7) * 128 + (((2 * ktl) ^ (g2 & 7)) << 4);
+      const int src = (lane & ~3) | ((h + 3) & 3);
+      for (int c = grp; c < nchunks && ok; c += NDEC_GROUPS) {
+        const int rs = c % RAW_STAGES, os = c % OP_STAGES;
+        ok = mbar_wait(&raw_full[rs], (c / RAW_STAGES) & 1, abort_flag, status, 30);
+        if (!ok) break;
+        const uint4* tile4 = reinterpret_cast<const uint4*>(smem + L.raw_off + rs * RAW_STAGE) + (ktl * 8 + nt) * 8;
+        const uint4 first = tile4[g1], second = tile4[g2];
+        const uint32_t sh_second = __shfl_sync(0xffffffffu, second.w, src), sh_first = __shfl_sync(0xffffffffu, first.w, src);
+        const uint32_t w1[5] = {x ? second.w : sh_second, first.x, first.y, first.z, first.w};
+        const uint32_t w2[5] = {x ? sh_first : first.w, second.x, second.y, second.z, second.w};
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        if (c >= OP_STAGES) ok = mbar_wait(&op_empty[os], ((c / OP_STAGES) - 1) & 1, abort_flag, status, 31);
+        if (!ok) break;
+        uint8_t* a_tile = smem + L.a_off + os * A_STAGE;
+        {
+          uint32_t h2[16];
+          decode32_b4<CB>(w1, h2);
+          uint8_t* p = a_tile + o1;
+          *reinterpret_cast<uint4*>(p) = eighth_chunk(h2, 0, 0);
+          *reinterpret_cast<uint4*>((uint8_t*)((uintptr_t)p ^ 16)) = eighth_chunk(h2, 0, 1);
+          *reinterpret_cast<uint4*>(p + 1024) = eighth_chunk(h2, 1, 0);
+          *reinterpret_cast<uint4*>((uint8_t*)((uintptr_t)(p + 1024) ^ 16)) = eighth_chunk(h2, 1, 1);
+        }
+        {
+          uint32_t h2[16];
+          decode32_b4<CB>(w2, h2);
+          uint8_t* p = a_tile + o2;
+          *reinterpret_cast<uint4*>(p) = eighth_chunk(h2, 0, 0);
+          *reinterpret_cast<uint4*>((uint8_t*)((uintptr_t)p ^ 16)) = eighth_chunk(h2, 0, 1);
+          *reinterpret_cast<uint4*>(p + 1024) = eighth_chunk(h2, 1, 0);
+          *reinterpret_cast<uint4*>((uint8_t*)((uintptr_t)(p + 1024) ^ 16)) = eighth_chunk(h2, 1, 1);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&op_full[os]);
+      }
+    } else
     for (int c = grp; c < nchunks && ok; c += NDEC_GROUPS) {
       const int rs = c % RAW_STAGES, os = c % OP_STAGES;
       ok = mbar_wait(&raw_full[rs], (c / RAW_STAGES) & 1, abort_flag, status, 30);
@@ -261,6 +309,19 @@ int make_tmap_f16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+// Trellis viewed as uint32 [K/16 rows, row_words]: a box is `box_rows` k-tile rows x `box_words` words, unswizzled.
+int make_tmap_trellis(CUtensorMap* out, const void* base, uint64_t kt_rows, uint64_t row_words, uint32_t box_words, uint32_t box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {row_words, kt_rows};
+  cuuint64_t strides[1] = {row_words * 4};
+  cuuint32_t box[2] = {box_words, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 

@@ -61,14 +61,19 @@ def plan_splits(K: int, N: int, decode_class: bool) -> int:
     return _lib.load().rx_exl3_plan_splits(K, N, 1 if decode_class else 0)
 
 
-def exl3_gemm(xr: torch.Tensor, w: Exl3Weight, part: torch.Tensor, splits: int, status: torch.Tensor) -> None:
+def exl3_gemm(xr: torch.Tensor, w: Exl3Weight, part: torch.Tensor, splits: int, status: torch.Tensor, force_generic: bool = False) -> None:
     """part[s, row, n] = partial sums of xr @ W_q over split s.  xr: fp16 [rows, K] contiguous; part: fp32 >= splits*rows*N."""
     rows, K = xr.shape
     assert xr.dtype == torch.float16 and xr.is_contiguous() and K == w.K
     assert part.dtype == torch.float32 and part.numel() >= splits * rows * w.N
     L = _lib.load()
-    _lib.check(L.rx_exl3_gemm(xr.data_ptr(), rows, K, w.trellis.data_ptr(), w.N, w.twice, CB_ID[w.codebook], part.data_ptr(), splits,
-                              status.data_ptr(), _lib.stream_ptr()), "rx_exl3_gemm")
+    if w.twice == 8 and not force_generic:
+        # 4.0 bpw: decoded weights go straight to tensor memory
+        _lib.check(L.rx_exl3_gemm_b4(xr.data_ptr(), rows, K, w.trellis.data_ptr(), w.N, CB_ID[w.codebook], part.data_ptr(), splits,
+                                     status.data_ptr(), _lib.stream_ptr()), "rx_exl3_gemm_b4")
+    else:
+        _lib.check(L.rx_exl3_gemm(xr.data_ptr(), rows, K, w.trellis.data_ptr(), w.N, w.twice, CB_ID[w.codebook], part.data_ptr(), splits,
+                                  status.data_ptr(), _lib.stream_ptr()), "rx_exl3_gemm")
     _lib.count()
 
 

@@ -58,6 +58,27 @@ def test_exl3_gemm_matches_fp32_reference(K, bits, cb, rows):
         assert err <= 2e-3 * ref.abs().max().item() + 1e-3, (bits, cb, rows, splits, err)
 
 
+@pytest.mark.parametrize("cb", ["3inst", "mcg", "mul1"])
+def test_exl3_gemm_4bpw_tensor_memory_path_equals_shared_memory_path(K, cb):
+    """The 4.0 bpw kernel keeps decoded weights in tensor memory; same products, same K order -> same bits as the generic kernel."""
+    k, n = 2048, 512     # 16 chunks per CTA at one split: every ring wraps several times
+    w, tr, _, _ = _mk(K, k, n, 4, cb, seed=11)
+    status = K.new_status()
+    for rows in (1, 40, 64, 130, 520):
+        xr = (torch.randn(rows, k) * 0.5).to(torch.float16).cuda()
+        a = torch.zeros(2 * rows * n, device="cuda")
+        b = torch.zeros(2 * rows * n, device="cuda")
+        ref = xr.float() @ torch.from_numpy(exl3.unpack_f32(tr, cb)).cuda()
+        for splits in (2, 1):
+            a.zero_(); b.zero_()
+            K.exl3_gemm(xr, w, a, splits, status)
+            K.exl3_gemm(xr, w, b, splits, status, force_generic=True)
+            torch.cuda.synchronize()
+            K.check_status(status)
+            assert (a.view(2, rows, n)[:splits].sum(0) - ref).abs().max() <= 2e-3 * ref.abs().max() + 1e-3
+            assert torch.equal(a, b), (rows, splits)
+
+
 def test_exl3_gemm_row_invariance(K):
     """A row's bits do not depend on the other rows or their count (decode class)."""
     k, n = 1024, 256
