@@ -144,6 +144,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2, int* status) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int TILE = PAGE * HD * 2;
@@ -252,6 +254,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ ctx_len, int n_q,
                                   int max_chunks, const __half* __restrict__ suh, __half* __restrict__ xr, uint16_t* __restrict__ out_bf16) {
+  pdl_launch();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int nch = (ctx_len[row] + DEC_CHUNK - 1) / DEC_CHUNK;
   const int width = n_q * HD;
@@ -259,15 +263,40 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     const int e0 = b * 128 + lane * 4;
     const int hq = e0 / HD, d0 = e0 % HD;
     const size_t base = ((size_t)row * n_q + hq) * max_chunks;
+    // GL chunks at a time (GL = lanes that share this head): lane c of the group fetches chunk c's (max, sum), the group reduces
+    // the max, then every lane walks the chunks in order with the factors broadcast by shuffle and the partial-output loads
+    // issued four at a time
+    constexpr int GL = HD / 4 < 32 ? HD / 4 : 32;
+    const int gl = lane % GL, gbase = lane - gl;
     float mm = -INFINITY;
-    for (int c = 0; c < nch; ++c) mm = fmaxf(mm, part_ml[(base + c) * 2]);
+    for (int c0 = 0; c0 < nch; c0 += GL) {
+      float m_l = (c0 + gl < nch) ? part_ml[(base + c0 + gl) * 2] : -INFINITY;
+#pragma unroll
+      for (int o = GL / 2; o > 0; o >>= 1) m_l = fmaxf(m_l, __shfl_xor_sync(0xffffffffu, m_l, o));
+      mm = fmaxf(mm, m_l);
+    }
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, lsum = 0.f;
-    for (int c = 0; c < nch; ++c) {
-      const float mc = part_ml[(base + c) * 2];
-      const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - mm);
-      const float4 p = *reinterpret_cast<const float4*>(part_o + (base + c) * HD + d0);
-      acc[0] += f * p.x; acc[1] += f * p.y; acc[2] += f * p.z; acc[3] += f * p.w;
-      lsum += f * part_ml[(base + c) * 2 + 1];
+    for (int c0 = 0; c0 < nch; c0 += GL) {
+      const bool in = c0 + gl < nch;
+      const float m_l = in ? part_ml[(base + c0 + gl) * 2] : -INFINITY;
+      const float l_l = in ? part_ml[(base + c0 + gl) * 2 + 1] : 0.f;
+      const float f_l = (m_l == -INFINITY) ? 0.f : exp2f(m_l - mm);
+      const int cnt = min(GL, nch - c0);
+      for (int j0 = 0; j0 < cnt; j0 += 4) {
+        float4 p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j0 + j < cnt) p[j] = *reinterpret_cast<const float4*>(part_o + (base + c0 + j0 + j) * HD + d0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int src = gbase + ((j0 + j) % GL);
+          const float f = __shfl_sync(0xffffffffu, f_l, src), ll = __shfl_sync(0xffffffffu, l_l, src);
+          if (j0 + j < cnt) {
+            acc[0] += f * p[j].x; acc[1] += f * p[j].y; acc[2] += f * p[j].z; acc[3] += f * p[j].w;
+            lsum += f * ll;
+          }
+        }
+      }
     }
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
     float v[4];
@@ -303,6 +332,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_ids, const int* __restrict__ q_start,
                     const int* __restrict__ q_len, const int* __restrict__ pos0, uint16_t* __restrict__ out, int n_q, int n_kv, float scale_log2,
                     int* status) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int TILE = PAGE * HD * 2;
@@ -441,7 +472,7 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
     configured = true;
   }
   dim3 grid(rows, n_kv, mc);
-  attn_decode_kernel<HD><<<grid, ATT_THREADS, smem, st>>>(*tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, n_q,
+  rx::launch(attn_decode_kernel<HD>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, n_q,
                                                          n_kv, mc, scale * 1.4426950408889634f, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
@@ -449,7 +480,7 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
   int gy = (296 + rows - 1) / rows;
   if (gy > (blocks128 + 3) / 4) gy = (blocks128 + 3) / 4;
   if (gy < 1) gy = 1;
-  attn_merge_kernel<HD><<<dim3(rows, gy), 128, 0, st>>>(part_o, part_ml, ctx_len, n_q, mc, (const __half*)suh, (__half*)xr, (uint16_t*)out_bf16);
+  rx::launch(attn_merge_kernel<HD>, dim3(dim3(rows, gy)), dim3(128), 0, st, part_o, part_ml, ctx_len, n_q, mc, (const __half*)suh, (__half*)xr, (uint16_t*)out_bf16);
   return (int)cudaGetLastError();
 }
 
@@ -480,7 +511,7 @@ static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const vo
     configured = true;
   }
   dim3 grid((max_qlen + 63) / 64, n_q, nseq);
-  attn_prefill_kernel<HD><<<grid, ATT_THREADS, smem, st>>>(*tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
+  rx::launch(attn_prefill_kernel<HD>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
                                                           (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status);
   return (int)cudaGetLastError();
 }

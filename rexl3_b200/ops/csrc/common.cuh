@@ -178,6 +178,27 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, int a_fmt, i
   return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of this library is launched with programmatic stream serialization allowed: a kernel calls pdl_launch() at its
+// start (the next kernel in the stream may begin its prologue, e.g. stream its weights) and pdl_wait() before it touches
+// anything the previous kernel wrote.  pdl_wait() returns once the previous kernel has fully completed and flushed.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& pdl_enabled() { static int on = 1; return on; }
+
+template <typename... P, typename... A>
+inline cudaError_t launch(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 // ---------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -54,6 +54,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ------------------------------------------------------------------------------------------------ unpack
 template <int TWICE, int CB>
 __global__ void unpack_kernel(const uint32_t* __restrict__ trellis, __half* __restrict__ w, int kt, int nt) {
+  pdl_launch();
+  pdl_wait();
   const int tile = blockIdx.x * (blockDim.x / 4) + threadIdx.x / 4;
   if (tile >= kt * nt) return;
   const int h = threadIdx.x & 3;
@@ -72,6 +74,8 @@ __global__ void unpack_kernel(const uint32_t* __restrict__ trellis, __half* __re
 
 // ------------------------------------------------------------------------------------------------ embed
 __global__ void embed_kernel(const int* __restrict__ ids, const uint16_t* __restrict__ table, uint16_t* __restrict__ h, int d, int vocab) {
+  pdl_launch();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   if (id < 0 || id >= vocab) id = 0;
@@ -82,20 +86,25 @@ __global__ void embed_kernel(const int* __restrict__ ids, const uint16_t* __rest
 
 // ------------------------------------------------------------------------------------------------ norm + rot_in
 // xr[row] = fp16( H( rmsnorm(x[row]) * w * suh ) ), one block per row.  norm_w == nullptr: no norm (plain rotation).
-__global__ void norm_rot_in_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ norm_w, float eps,
+__global__ void __launch_bounds__(1024) norm_rot_in_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ norm_w, float eps,
                                    const __half* __restrict__ suh, __half* __restrict__ xr, int K) {
-  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  __shared__ float blk_ss[512];   // one partial per 128-block (K <= 65536), added in block order: independent of the block size
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const uint16_t* xrow = x + (size_t)row * K;
   float rinv = 1.f;
   if (norm_w != nullptr) {
-    float ss = 0.f;
-    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
+    for (int b = warp; b < K / 128; b += nw) {
       float v[4];
-      load4_bf16(xrow + i, v);
-      ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+      load4_bf16(xrow + b * 128 + lane * 4, v);
+      const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+      if (lane == 0) blk_ss[b] = ss;
     }
-    rinv = rsqrtf(block_sum(ss, red) / (float)K + eps);
+    __syncthreads();
+    float tot = 0.f;
+    for (int b = 0; b < K / 128; ++b) tot += blk_ss[b];
+    rinv = rsqrtf(tot / (float)K + eps);
   }
   for (int b = warp; b < K / 128; b += nw) {
     const int i = b * 128 + lane * 4;
@@ -119,10 +128,21 @@ __global__ void norm_rot_in_kernel(const uint16_t* __restrict__ x, const uint16_
 // y[row][n] = H_N( sum_s part[s][row][:] )[n] * svh[n] + bias[n] for one 128-block, lane holds 4 consecutive n.
 __device__ __forceinline__ void finish_block(const float* __restrict__ part, int S, size_t split_stride, size_t off, const __half* svh,
                                              const float* bias, int n0, float (&y)[4]) {
-  float4 acc = *reinterpret_cast<const float4*>(part + off);
-  for (int s = 1; s < S; ++s) {
-    const float4 p = *reinterpret_cast<const float4*>(part + s * split_stride + off);
-    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+  // loads are issued eight at a time (independent, so their latencies overlap) and added in split order
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (S == 1) acc = __ldg(reinterpret_cast<const float4*>(part + off));
+  else
+  for (int s0 = 0; s0 < S; s0 += 8) {
+    float4 p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (s0 + j < S) p[j] = __ldg(reinterpret_cast<const float4*>(part + (size_t)(s0 + j) * split_stride + off));
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (s0 + j < S) {
+        if (s0 + j == 0) acc = p[j];
+        else { acc.x += p[j].x; acc.y += p[j].y; acc.z += p[j].z; acc.w += p[j].w; }
+      }
   }
   y[0] = acc.x; y[1] = acc.y; y[2] = acc.z; y[3] = acc.w;
   fwht128_warp(y);
@@ -139,6 +159,8 @@ __device__ __forceinline__ void finish_block(const float* __restrict__ part, int
 // mode 0: out bf16 [M, N];  mode 1: out f32 [M, N]
 __global__ void finish_store_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
                                     const float* __restrict__ bias, void* __restrict__ out, int f32_out) {
+  pdl_launch();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int b = blockIdx.y * nw + warp; b < N / 128; b += gridDim.y * nw) {
     const int n0 = b * 128 + lane * 4;
@@ -151,14 +173,16 @@ __global__ void finish_store_kernel(const float* __restrict__ part, int S, int M
 
 // h[row] += y (bf16 residual stream, updated in place); then xr = fp16(H(rmsnorm(h) * w * suh_next)).
 // norm_w == nullptr skips the norm, suh_next == nullptr skips the rotation output entirely (residual update only).
-__global__ void finish_add_norm_rot_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
+__global__ void __launch_bounds__(1024) finish_add_norm_rot_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
                                            const float* __restrict__ bias, uint16_t* __restrict__ h, const uint16_t* __restrict__ norm_w,
                                            float eps, const __half* __restrict__ suh_next, __half* __restrict__ xr) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ float rowbuf[];  // N floats: the updated residual row (as stored, bf16-rounded)
-  __shared__ float red[32];
+  __shared__ float blk_ss[512];      // per-128-block sums of squares, added in block order (independent of the block size)
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  float ss = 0.f;
   for (int b = warp; b < N / 128; b += nw) {
+    float ss = 0.f;
     const int n0 = b * 128 + lane * 4;
     float y[4], r[4];
     finish_block(part, S, (size_t)M * N, (size_t)row * N + n0, svh, bias, n0, y);
@@ -170,11 +194,17 @@ __global__ void finish_add_norm_rot_kernel(const float* __restrict__ part, int S
       rowbuf[n0 + i] = r[i];
     }
     store4_bf16(h + (size_t)row * N + n0, r);
+    ss = warp_sum(ss);
+    if (lane == 0) blk_ss[b] = ss;
   }
   if (suh_next == nullptr) return;
   float rinv = 1.f;
-  const float tot = block_sum(ss, red);  // also orders the rowbuf writes before the reads below
-  if (norm_w != nullptr) rinv = rsqrtf(tot / (float)N + eps);
+  __syncthreads();  // orders the rowbuf / blk_ss writes before the reads below
+  if (norm_w != nullptr) {
+    float tot = 0.f;
+    for (int b = 0; b < N / 128; ++b) tot += blk_ss[b];
+    rinv = rsqrtf(tot / (float)N + eps);
+  }
   for (int b = warp; b < N / 128; b += nw) {
     const int n0 = b * 128 + lane * 4;
     float v[4], s[4];
@@ -198,6 +228,8 @@ __global__ void finish_add_norm_rot_kernel(const float* __restrict__ part, int S
 // xr[row][F] = fp16(H(act * suh_down)).
 __global__ void finish_swiglu_rot_kernel(const float* __restrict__ part, int S, int M, int F, const __half* __restrict__ svh,
                                          const float* __restrict__ bias, const __half* __restrict__ suh_down, __half* __restrict__ xr) {
+  pdl_launch();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int N = 2 * F;
   for (int b = blockIdx.y * nw + warp; b < F / 128; b += gridDim.y * nw) {
@@ -225,7 +257,7 @@ RX_API int rx_exl3_unpack(const void* trellis, int K, int N, int twice, int code
   const int kt = K / 16, nt = N / 16, tiles = kt * nt;
   cudaStream_t st = (cudaStream_t)stream;
   const dim3 grid((tiles + 31) / 32), block(128);
-#define RX_GO(CBV) RX_DISPATCH_TWICE(twice, unpack_kernel<T_, CBV><<<grid, block, 0, st>>>((const uint32_t*)trellis, (__half*)w_f16, kt, nt))
+#define RX_GO(CBV) RX_DISPATCH_TWICE(twice, rx::launch(unpack_kernel<T_, CBV>, dim3(grid), dim3(block), 0, st, (const uint32_t*)trellis, (__half*)w_f16, kt, nt))
   switch (codebook) {
     case CB_3INST: RX_GO(CB_3INST); break;
     case CB_MCG: RX_GO(CB_MCG); break;
@@ -238,42 +270,42 @@ RX_API int rx_exl3_unpack(const void* trellis, int K, int N, int twice, int code
 
 RX_API int rx_embed(const void* ids, const void* table, void* h, int rows, int d, int vocab, void* stream) {
   if (d % 8) return (int)cudaErrorInvalidValue;
-  embed_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>((const int*)ids, (const uint16_t*)table, (uint16_t*)h, d, vocab);
+  rx::launch(embed_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, (const int*)ids, (const uint16_t*)table, (uint16_t*)h, d, vocab);
   return (int)cudaGetLastError();
 }
 
 RX_API int rx_norm_rot_in(const void* x_bf16, const void* norm_w_bf16, float eps, const void* suh, void* xr, int rows, int K, void* stream) {
-  if (K % 128) return (int)cudaErrorInvalidValue;
-  norm_rot_in_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)x_bf16, (const uint16_t*)norm_w_bf16, eps, (const __half*)suh,
+  if (K % 128 || K / 128 > 512) return (int)cudaErrorInvalidValue;
+  rx::launch(norm_rot_in_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, (const uint16_t*)x_bf16, (const uint16_t*)norm_w_bf16, eps, (const __half*)suh,
                                                             (__half*)xr, K);
   return (int)cudaGetLastError();
 }
 
 static int blocks_y(int rows, int nblocks128) {
-  // enough CTAs to fill the machine when there are few rows; 8 warps per CTA
-  int per_row = (nblocks128 + 7) / 8;
-  int want = (296 + rows - 1) / rows;
-  int y = want < per_row ? want : per_row;
-  return y < 1 ? 1 : y;
+  // one warp per 128-block (8 warps per CTA): the kernels without a row-wide reduction get their memory-level parallelism
+  // from many resident warps with one or two loads each, for one row as for thousands
+  (void)rows;
+  const int per_row = (nblocks128 + 7) / 8;
+  return per_row < 1 ? 1 : per_row;
 }
 
 RX_API int rx_finish_store(const void* part, int S, int M, int N, const void* svh, const void* bias, void* out, int f32_out, void* stream) {
   if (N % 128) return (int)cudaErrorInvalidValue;
   dim3 grid(M, blocks_y(M, N / 128));
-  finish_store_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)part, S, M, N, (const __half*)svh, (const float*)bias, out, f32_out);
+  rx::launch(finish_store_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh, (const float*)bias, out, f32_out);
   return (int)cudaGetLastError();
 }
 
 RX_API int rx_finish_add_norm_rot(const void* part, int S, int M, int N, const void* svh, const void* bias, void* h_bf16, const void* norm_w,
                                   float eps, const void* suh_next, void* xr, void* stream) {
-  if (N % 128 || N * 4 > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (N % 128 || N * 4 > 200 * 1024 || N / 128 > 512) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(finish_add_norm_rot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  finish_add_norm_rot_kernel<<<M, 256, N * 4, (cudaStream_t)stream>>>((const float*)part, S, M, N, (const __half*)svh, (const float*)bias,
+  rx::launch(finish_add_norm_rot_kernel, dim3(M), dim3(1024), (size_t)N * 4, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh, (const float*)bias,
                                                                      (uint16_t*)h_bf16, (const uint16_t*)norm_w, eps, (const __half*)suh_next,
                                                                      (__half*)xr);
   return (int)cudaGetLastError();
@@ -283,7 +315,13 @@ RX_API int rx_finish_swiglu_rot(const void* part, int S, int M, int F, const voi
                                 void* stream) {
   if (F % 128) return (int)cudaErrorInvalidValue;
   dim3 grid(M, blocks_y(M, F / 128));
-  finish_swiglu_rot_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)part, S, M, F, (const __half*)svh, (const float*)bias,
+  rx::launch(finish_swiglu_rot_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const float*)part, S, M, F, (const __half*)svh, (const float*)bias,
                                                                   (const __half*)suh_down, (__half*)xr);
   return (int)cudaGetLastError();
+}
+
+// Turn programmatic dependent launch on (1, default) or off (0) for every later launch of this library.
+RX_API int rx_set_pdl(int on) {
+  rx::pdl_enabled() = on ? 1 : 0;
+  return 0;
 }

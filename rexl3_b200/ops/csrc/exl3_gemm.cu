@@ -53,6 +53,7 @@ template <int TWICE, int CB>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
 exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __restrict__ trellis, float* __restrict__ part,
                  int rows, int K, int N, int splits, int brows, int row_tiles, int* status) {
+  pdl_launch();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled operand tiles
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -99,6 +100,7 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // the weights were not written by the previous kernel, everything else may have been
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
@@ -339,7 +341,7 @@ static int launch_gemm(const CUtensorMap& tm, const uint32_t* trellis, float* pa
   }
   if (smem > 232448) return (int)cudaErrorInvalidValue;
   dim3 grid(N / STRIP, splits, row_tiles);
-  kern<<<grid, GEMM_THREADS, smem, st>>>(tm, trellis, part, rows, K, N, splits, brows, row_tiles, status);
+  rx::launch(kern, dim3(grid), dim3(GEMM_THREADS), smem, st, tm, trellis, part, rows, K, N, splits, brows, row_tiles, status);
   return (int)cudaGetLastError();
 }
 
@@ -348,11 +350,14 @@ static int launch_gemm(const CUtensorMap& tm, const uint32_t* trellis, float* pa
 using namespace rx;
 
 // Split plan: a function of (K, N) and the row class only, never of the row count inside a class.
+// Decode class: as many K splits as keep strips * splits within ONE wave of the machine (148 SMs x 2 resident CTAs), so no
+// second, mostly empty wave is paid; every split keeps at least two 128-wide K chunks.
 RX_API int rx_exl3_plan_splits(int K, int N, int decode_class) {
   if (!decode_class) return 1;
-  const int strips = N / STRIP, chunks = K / KCH;
-  int s = (2 * 148 + strips - 1) / strips;
-  if (s > chunks / 4) s = chunks / 4;
+  const int strips = N / STRIP, chunks = K / 128;
+  const int slots = 2 * 148;
+  int s = slots / strips;
+  if (s > chunks / 2) s = chunks / 2;
   if (s < 1) s = 1;
   if (s > 32) s = 32;
   return s;

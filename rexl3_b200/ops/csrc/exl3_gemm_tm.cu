@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(128 + NG * 128, (NG == 2 ? 2 : 1))
 exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, float* __restrict__ part, int rows,
                     int K, int N, int splits, int brows, int* status) {
   constexpr int TM_RAW_STAGES = tm_raw_stages(NG);
+  pdl_launch();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int b_half = brows * 128;                    // one [brows x 64] swizzled sub-tile
@@ -77,6 +78,11 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     fence_barrier_init();
     prefetch_tmap(&tmap_x);
     prefetch_tmap(&tmap_w);
+    // the weight stream does not wait for the rest of the prologue (TMEM allocation, CTA barrier)
+    for (int c = 0; c < nchunks && c < TM_RAW_STAGES; ++c) {
+      mbar_arrive_expect_tx(&raw_full[c], TM_RAW_STAGE_BYTES);
+      tma_load_2d(raw_base + c * TM_RAW_STAGE_BYTES, &tmap_w, strip * 256, (c_begin + c) * 8, &raw_full[c]);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, ncols);
@@ -85,17 +91,18 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // the weights were not written by the previous kernel, everything else may have been
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t a_tmem0 = tmem_base + acc_cols;
 
   if (warp == 0) {
     // ---- weight producer: ONE 2-D tiled copy per chunk (8 k-tile rows x 1 KB of this strip)
     if (lane == 0) {
-      int y = c_begin * 8;
+      int y = (c_begin + TM_RAW_STAGES) * 8;
       const int x = strip * 256;
-      for (int c = 0; c < nchunks; ++c, y += 8) {
+      for (int c = TM_RAW_STAGES; c < nchunks; ++c, y += 8) {   // the first ring's worth was issued in the prologue
         const int s = c % TM_RAW_STAGES;
-        if (c >= TM_RAW_STAGES && !mbar_wait(&raw_empty[s], ((c / TM_RAW_STAGES) - 1) & 1, abort_flag, status, 110)) break;
+        if (!mbar_wait(&raw_empty[s], ((c / TM_RAW_STAGES) - 1) & 1, abort_flag, status, 110)) break;
         mbar_arrive_expect_tx(&raw_full[s], TM_RAW_STAGE_BYTES);
         tma_load_2d(raw_base + s * TM_RAW_STAGE_BYTES, &tmap_w, x, y, &raw_full[s]);
       }
@@ -236,7 +243,7 @@ static int launch_tm(const CUtensorMap& tm, const CUtensorMap& tw, float* part, 
     configured = true;
   }
   dim3 grid(N / TM_STRIP, splits, row_tiles);
-  kern<<<grid, 128 + NG * 128, smem, st>>>(tm, tw, part, rows, K, N, splits, brows, status);
+  rx::launch(kern, dim3(grid), dim3(128 + NG * 128), smem, st, tm, tw, part, rows, K, N, splits, brows, status);
   return (int)cudaGetLastError();
 }
 

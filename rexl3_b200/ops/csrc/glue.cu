@@ -22,6 +22,8 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
                                        float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                        const int* __restrict__ slot, uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
                                        uint16_t* __restrict__ v_cache) {
+  pdl_launch();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int N = (n_q + 2 * n_kv) * HD;
   const size_t sstride = (size_t)M * N;
@@ -31,10 +33,20 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
   for (int b = blockIdx.y * nw + warp; b < N / 128; b += gridDim.y * nw) {
     const int n0 = b * 128 + lane * 4;
     const size_t off = (size_t)row * N + n0;
-    float4 acc = *reinterpret_cast<const float4*>(part + off);
-    for (int s = 1; s < S; ++s) {
-      const float4 p = *reinterpret_cast<const float4*>(part + s * sstride + off);
-      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (S == 1) acc = __ldg(reinterpret_cast<const float4*>(part + off));
+    else
+    for (int s0 = 0; s0 < S; s0 += 8) {   // eight independent loads in flight, added in split order
+      float4 p[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) p[j] = __ldg(reinterpret_cast<const float4*>(part + (size_t)(s0 + j) * sstride + off));
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) {
+          if (s0 + j == 0) acc = p[j];
+          else { acc.x += p[j].x; acc.y += p[j].y; acc.z += p[j].z; acc.w += p[j].w; }
+        }
     }
     float y[4] = {acc.x, acc.y, acc.z, acc.w};
     fwht128_warp(y);
@@ -124,6 +136,8 @@ __device__ __forceinline__ void block_select(uint64_t (&k)[TOPK_PER_THREAD], int
 }
 
 __global__ void topk_stage1_kernel(const float* __restrict__ logits, int vocab, int count, uint64_t* __restrict__ cand, int nchunks) {
+  pdl_launch();
+  pdl_wait();
   __shared__ uint64_t red[TOPK_THREADS / 32];
   const int row = blockIdx.y, chunk = blockIdx.x;
   const float* lr = logits + (size_t)row * vocab;
@@ -137,6 +151,8 @@ __global__ void topk_stage1_kernel(const float* __restrict__ logits, int vocab, 
 }
 
 __global__ void topk_stage2_kernel(const uint64_t* __restrict__ cand, int total, int count, int* __restrict__ ids, float* __restrict__ vals) {
+  pdl_launch();
+  pdl_wait();
   __shared__ uint64_t red[TOPK_THREADS / 32];
   __shared__ uint64_t outk[64];
   const int row = blockIdx.x;
@@ -168,16 +184,13 @@ RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv,
                               void* k_cache, void* v_cache, void* stream) {
   const int N = (n_q + 2 * n_kv) * hd;
   if (N % 128) return (int)cudaErrorInvalidValue;
-  int gy = (296 + M - 1) / M;
-  const int per_row = (N / 128 + 7) / 8;
-  if (gy > per_row) gy = per_row;
-  if (gy < 1) gy = 1;
-  dim3 grid(M, gy);
+  const int per_row = (N / 128 + 7) / 8;   // one warp per 128-block
+  dim3 grid(M, per_row < 1 ? 1 : per_row);
   cudaStream_t st = (cudaStream_t)stream;
 #define RX_ARGS (const float*)part, S, M, n_q, n_kv, (const __half*)svh, (const float*)bias, (const uint16_t*)q_norm, (const uint16_t*)k_norm, eps, \
                 (const int*)positions, (const float*)inv_freq, (const int*)slot, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache
-  if (hd == 128) finish_qkv_rope_kernel<128><<<grid, 256, 0, st>>>(RX_ARGS);
-  else if (hd == 64) finish_qkv_rope_kernel<64><<<grid, 256, 0, st>>>(RX_ARGS);
+  if (hd == 128) rx::launch(finish_qkv_rope_kernel<128>, dim3(grid), dim3(256), 0, st, RX_ARGS);
+  else if (hd == 64) rx::launch(finish_qkv_rope_kernel<64>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else return (int)cudaErrorInvalidValue;
 #undef RX_ARGS
   return (int)cudaGetLastError();
@@ -193,9 +206,9 @@ RX_API int rx_topk(const void* logits, int rows, int vocab, int count, void* scr
   const int nchunks = (vocab + TOPK_CHUNK - 1) / TOPK_CHUNK;
   if (nchunks * count > TOPK_CHUNK) return (int)cudaErrorInvalidValue;  // vocab up to 65536 * 2048 / count: never hit in practice
   cudaStream_t st = (cudaStream_t)stream;
-  topk_stage1_kernel<<<dim3(nchunks, rows), TOPK_THREADS, 0, st>>>((const float*)logits, vocab, count, (uint64_t*)scratch, nchunks);
+  rx::launch(topk_stage1_kernel, dim3(dim3(nchunks, rows)), dim3(TOPK_THREADS), 0, st, (const float*)logits, vocab, count, (uint64_t*)scratch, nchunks);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  topk_stage2_kernel<<<rows, TOPK_THREADS, 0, st>>>((const uint64_t*)scratch, nchunks * count, count, (int*)ids, (float*)vals);
+  rx::launch(topk_stage2_kernel, dim3(rows), dim3(TOPK_THREADS), 0, st, (const uint64_t*)scratch, nchunks * count, count, (int*)ids, (float*)vals);
   return (int)cudaGetLastError();
 }

@@ -44,6 +44,7 @@ def _declare(lib):
         "rx_exl3_gemm": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_int, c_void, c_int, c_void, c_void]),
         "rx_exl3_gemm_b4": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_void, c_int, c_void, c_void]),
         "rx_exl3_unpack": (c_int, [c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
+        "rx_set_pdl": (c_int, [c_int]),
         "rx_embed": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void]),
         "rx_norm_rot_in": (c_int, [c_void, c_void, c_f, c_void, c_void, c_int, c_int, c_void]),
         "rx_finish_store": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_int, c_void]),
