@@ -220,11 +220,11 @@ __device__ __forceinline__ void fwht128_warp(float (&v)[4]) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
-    const bool hi = (lane & o) != 0;
+    const float sgn = (lane & o) ? -1.f : 1.f;   // upper half of the butterfly: other - v, lower half: other + v
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      float other = __shfl_xor_sync(0xffffffffu, v[r], o);
-      v[r] = hi ? (other - v[r]) : (v[r] + other);
+      const float other = __shfl_xor_sync(0xffffffffu, v[r], o);
+      v[r] = fmaf(sgn, v[r], other);
     }
   }
   const float s = 0.08838834764831845f;  // 1/sqrt(128)
