@@ -212,3 +212,51 @@ RX_API int rx_topk(const void* logits, int rows, int vocab, int count, void* scr
   rx::launch(topk_stage2_kernel, dim3(rows), dim3(TOPK_THREADS), 0, st, (const uint64_t*)scratch, nchunks * count, count, (int*)ids, (float*)vals);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------ allocation-free top-k
+// Scratch for rx_topk_static: the stage-1 candidate keys of up to TOPK_STATIC_ROWS rows.  It lives in the library image, so
+// every GPU that loads the library holds these 2 MiB until the process exits.
+namespace rx {
+constexpr int TOPK_STATIC_ROWS = 64;
+constexpr int TOPK_STATIC_CHUNKS = 64;      // vocabularies up to 64 * 4096 = 262,144 entries
+constexpr int TOPK_STATIC_COUNT = 64;
+static __device__ __align__(256) unsigned long long g_topk_static_scratch[(size_t)TOPK_STATIC_ROWS * TOPK_STATIC_CHUNKS * TOPK_STATIC_COUNT];
+constexpr int TOPK_STATIC_MAX_DEVICES = 64;
+static void* g_topk_static_ptr[TOPK_STATIC_MAX_DEVICES];   // per device: the array's DEVICE address (the symbol itself is a host stand-in)
+}  // namespace rx
+
+// Exact top-`count` candidates of every row, like rx_topk, for callers that cannot allocate device memory: a serving
+// loop whose memory plan is sealed after start-up, a plugin called from someone else's stream callback, code running
+// while a pool allocator is locked.  The caller passes only inputs and outputs; the intermediate candidate list goes to
+// a fixed array inside this library.
+//   limits : rows <= 64, vocab <= 262,144, 1 <= count <= 64 (anything larger is refused with cudaErrorInvalidValue)
+//   set-up : the first call on each device looks up the array's device address (cudaGetSymbolAddress with that device
+//            current).  Make that first call outside any stream capture.
+//   sharing: all calls use the same array, which keeps whatever the last call left in it; this routine overwrites every
+//            slot it later reads, so no clearing is needed, but two calls that overlap on the GPU (different streams)
+//            race on it.  Serialise them.
+// No cudaMalloc / cudaFree / allocating library call is made, here or in the kernels.
+RX_API int rx_topk_static(const void* logits, int rows, int vocab, int count, void* ids, void* vals, void* stream) {
+  if (logits == nullptr || ids == nullptr || vals == nullptr) return (int)cudaErrorInvalidValue;
+  if (rows < 1 || rows > TOPK_STATIC_ROWS || count < 1 || count > TOPK_STATIC_COUNT || vocab < 1) return (int)cudaErrorInvalidValue;
+  const int nchunks = (vocab + TOPK_CHUNK - 1) / TOPK_CHUNK;
+  if (nchunks > TOPK_STATIC_CHUNKS || nchunks * count > TOPK_CHUNK) return (int)cudaErrorInvalidValue;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= TOPK_STATIC_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+  if (g_topk_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_topk_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_topk_static_ptr[dev] = p;
+  }
+  uint64_t* scratch = (uint64_t*)g_topk_static_ptr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  e = rx::launch(topk_stage1_kernel, dim3(nchunks, rows), dim3(TOPK_THREADS), 0, st, (const float*)logits, vocab, count, scratch, nchunks);
+  if (e != cudaSuccess) return (int)e;
+  e = rx::launch(topk_stage2_kernel, dim3(rows), dim3(TOPK_THREADS), 0, st, (const uint64_t*)scratch, nchunks * count, count, (int*)ids,
+                 (float*)vals);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
