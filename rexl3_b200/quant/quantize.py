@@ -1,0 +1,203 @@
+"""EXL3 quantizer: sign flips + 128-block Hadamard rotation on both sides, global scale, trellis (Viterbi) coding, and
+the pack writer / loader.
+
+Stages (behaviour parity with the reference's quantizer outline, crates/quant/src/lib.rs:1-30, without the Hessian /
+LDLQ error feedback, which random-init benchmark weights do not need): W~ = H_K (su * W * sv) H_N / scale is coded tile by
+tile to the nearest trellis path, so that suh * (H W_q H) * svh reproduces W.  A pure "nearest trellis path" quantizer
+writes valid EXL3.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+
+from ..format import checkpoint, exl3, safetensors_io
+from ..models.dense import DenseConfig, HostLayer, HostLinear, HostWeights
+from .trellis import encode_tiles
+
+CODEBOOK_STD = {}
+
+
+def _cb_std(cb: str) -> float:
+    if cb not in CODEBOOK_STD:
+        CODEBOOK_STD[cb] = float(exl3.codebook_f32(cb).astype(np.float64).std())
+    return CODEBOOK_STD[cb]
+
+
+def to_stream_tiles(w: np.ndarray) -> np.ndarray:
+    """[K, N] -> [K/16 * N/16, 256] with each tile's values in trellis stream order."""
+    k, n = w.shape
+    r, c = exl3.tile_positions()
+    t = w.reshape(k // 16, 16, n // 16, 16).transpose(0, 2, 1, 3)      # [kt, nt, 16, 16]
+    return np.ascontiguousarray(t[:, :, r, c]).reshape(-1, 256)
+
+
+def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: int = 0, bias=None, threads: int = 0) -> HostLinear:
+    """w: float [K, N] with y = x @ w.  K and N must be multiples of 128 (pad first)."""
+    w = np.asarray(w, dtype=np.float64)
+    k, n = w.shape
+    if k % 128 or n % 128:
+        raise ValueError(f"K={k} and N={n} must be multiples of 128")
+    b = exl3.Bits.of(bits)
+    if not b.is_integer:
+        codebook = "mul1"
+    rng = np.random.default_rng(seed)
+    su = np.where(rng.random(k) < 0.5, -1.0, 1.0)
+    sv = np.where(rng.random(n) < 0.5, -1.0, 1.0)
+    rot = exl3.rotate(exl3.rotate((w * su[:, None] * sv[None, :]).T.copy()).T.copy())     # H_K (.) H_N, H symmetric and orthonormal
+    std = float(rot.std())
+    scale = std / _cb_std(codebook) if std > 0 else 1.0
+    tiles = to_stream_tiles(rot / scale)
+    packed, err = encode_tiles(tiles, b, codebook, threads)
+    trellis = packed.reshape(k // 16, n // 16, b.tile_words)
+    suh = su.astype(np.float16)
+    svh = (sv * scale).astype(np.float16)
+    return HostLinear(trellis, suh, svh, None if bias is None else np.asarray(bias, dtype=np.float32), codebook)
+
+
+def pad_to(w: np.ndarray, k: int, n: int) -> np.ndarray:
+    out = np.zeros((k, n), dtype=w.dtype)
+    out[:w.shape[0], :w.shape[1]] = w
+    return out
+
+
+def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0) -> HostWeights:
+    """fp: float weights of a dense GQA decoder, [in, out] matrices: embed [V, d], final_norm [d], lm_head [d, V] and per layer
+    attn_norm, q, k, v, o, ffn_norm, gate, up, down (optionally q_norm, k_norm)."""
+    d, F, V = cfg.d_model, cfg.ffn_padded, cfg.vocab_padded
+    w = HostWeights(cfg, np.asarray(fp["embed"], dtype=np.float32))
+    for i, L in enumerate(fp["layers"]):
+        qkv = np.concatenate([L["q"], L["k"], L["v"]], axis=1)
+        gu = np.concatenate([pad_to(L["gate"], d, F), pad_to(L["up"], d, F)], axis=1)
+        lay = HostLayer(np.asarray(L["attn_norm"], np.float32), quantize_linear(qkv, cfg.bits, cfg.codebook, seed + 10 * i + 1, threads=threads),
+                        quantize_linear(L["o"], cfg.bits, cfg.codebook, seed + 10 * i + 2, threads=threads), np.asarray(L["ffn_norm"], np.float32),
+                        quantize_linear(gu, cfg.bits, cfg.codebook, seed + 10 * i + 3, threads=threads),
+                        quantize_linear(pad_to(L["down"], F, d), cfg.bits, cfg.codebook, seed + 10 * i + 4, threads=threads),
+                        None if "q_norm" not in L else np.asarray(L["q_norm"], np.float32), None if "k_norm" not in L else np.asarray(L["k_norm"], np.float32))
+        w.layers.append(lay)
+    w.final_norm = np.asarray(fp["final_norm"], np.float32)
+    w.lm_head = quantize_linear(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, cfg.codebook, seed + 7777, threads=threads)
+    return w
+
+
+def random_fp_weights(cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> dict:
+    """N(0, std) matrices from a seed (norm weights 1), the shape BASELINE config 1 names."""
+    rng = np.random.default_rng(seed)
+    d, hd = cfg.d_model, cfg.head_dim
+    g = lambda *s: rng.normal(0, std, size=s).astype(np.float32)  # noqa: E731
+    layers = [dict(attn_norm=np.ones(d, np.float32), q=g(d, cfg.n_q * hd), k=g(d, cfg.n_kv * hd), v=g(d, cfg.n_kv * hd), o=g(cfg.n_q * hd, d),
+                   ffn_norm=np.ones(d, np.float32), gate=g(d, cfg.ffn), up=g(d, cfg.ffn), down=g(cfg.ffn, d)) for _ in range(cfg.n_layers)]
+    return dict(embed=g(cfg.vocab, d), layers=layers, final_norm=np.ones(d, np.float32), lm_head=g(d, cfg.vocab))
+
+
+# ----------------------------------------------------------------------------------------------------- pack I/O
+def _f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) -> None:
+    """A pack directory: config.json (+quantization_config), model.safetensors, model.safetensors.index.json, generation_config.json."""
+    os.makedirs(folder, exist_ok=True)
+    cfg = w.cfg
+    tensors, dtypes = {}, {}
+
+    def put_plain(name, a):
+        tensors[name] = _f32_to_bf16_bits(a)
+        dtypes[name] = "BF16"
+
+    def put_lin(prefix, l: HostLinear):
+        tensors[prefix + ".trellis"] = l.trellis
+        tensors[prefix + ".suh"] = l.suh.astype(np.float16)
+        tensors[prefix + ".svh"] = l.svh.astype(np.float16)
+        if l.codebook == "mcg":
+            tensors[prefix + ".mcg"] = np.array([exl3.MARKER_MCG], dtype=np.uint32).view(np.int32)
+        elif l.codebook == "mul1":
+            tensors[prefix + ".mul1"] = np.array([exl3.MARKER_MUL1], dtype=np.uint32).view(np.int32)
+        if l.bias is not None:
+            tensors[prefix + ".bias"] = l.bias.astype(np.float32)
+
+    put_plain("model.embed_tokens.weight", w.embed)
+    for i, L in enumerate(w.layers):
+        p = f"model.layers.{i}."
+        put_plain(p + "input_layernorm.weight", L.attn_norm)
+        put_plain(p + "post_attention_layernorm.weight", L.ffn_norm)
+        put_lin(p + "self_attn.qkv_proj", L.qkv)
+        put_lin(p + "self_attn.o_proj", L.o)
+        put_lin(p + "mlp.gate_up_proj", L.gate_up)
+        put_lin(p + "mlp.down_proj", L.down)
+        if L.q_norm is not None:
+            put_plain(p + "self_attn.q_norm.weight", L.q_norm)
+            put_plain(p + "self_attn.k_norm.weight", L.k_norm)
+    put_plain("model.norm.weight", w.final_norm)
+    put_lin("lm_head", w.lm_head)
+    safetensors_io.write_file(os.path.join(folder, "model.safetensors"), tensors, {"format": "pt"}, dtypes)
+    json.dump({"metadata": {}, "weight_map": {k: "model.safetensors" for k in sorted(tensors)}},
+              open(os.path.join(folder, "model.safetensors.index.json"), "w"), indent=1)
+    conf = {"architectures": ["Rexl3DenseForCausalLM"], "model_type": "rexl3_dense", "hidden_size": cfg.d_model, "num_hidden_layers": cfg.n_layers,
+            "num_attention_heads": cfg.n_q, "num_key_value_heads": cfg.n_kv, "head_dim": cfg.head_dim, "intermediate_size": cfg.ffn,
+            "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps, "rope_theta": cfg.rope_theta, "qk_norm": cfg.qk_norm, "name": cfg.name,
+            "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": cfg.bits, "head_bits": cfg.head_bits or cfg.bits,
+                                    "codebook": cfg.codebook, "fused_projections": True}}
+    conf.update(extra_config or {})
+    json.dump(conf, open(os.path.join(folder, "config.json"), "w"), indent=1)
+    json.dump({"eos_token_id": conf.get("eos_token_id", cfg.vocab - 1)}, open(os.path.join(folder, "generation_config.json"), "w"))
+
+
+def config_from_pack(folder: str) -> DenseConfig:
+    c = json.load(open(os.path.join(folder, "config.json")))
+    q = c.get("quantization_config") or (c.get("text_config") or {}).get("quantization_config")
+    if not q or q.get("quant_method") != "exl3":
+        raise ValueError("config.json has no quantization_config with quant_method exl3")
+    return DenseConfig(n_layers=c["num_hidden_layers"], d_model=c["hidden_size"], n_q=c["num_attention_heads"], n_kv=c["num_key_value_heads"],
+                       head_dim=c.get("head_dim", c["hidden_size"] // c["num_attention_heads"]), ffn=c["intermediate_size"], vocab=c["vocab_size"],
+                       eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), qk_norm=bool(c.get("qk_norm", False)),
+                       bits=float(q.get("bits", 4.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "dense"))
+
+
+def load_pack(folder: str) -> HostWeights:
+    """Scan (headers only), refuse bad groups by name, then read the tensors."""
+    cfg = config_from_pack(folder)
+    ck = checkpoint.scan(folder)
+    if ck.bad:
+        name, why = sorted(ck.bad.items())[0]
+        raise ValueError(f"pack refused: {name}: {why}")
+    if ck.issues:
+        raise ValueError(f"pack refused: {ck.issues[0]}")
+
+    def lin(prefix):
+        g = ck.groups.get(prefix)
+        if g is None:
+            raise ValueError(f"pack refused: no EXL3 group {prefix}")
+        lg = checkpoint.load_group(folder, g)
+        return HostLinear(lg.trellis, lg.suh, lg.svh, lg.bias, g.codebook)
+
+    def fused(prefix, fused_name, parts):
+        if prefix + fused_name in ck.groups:
+            return lin(prefix + fused_name)
+        ls = [lin(prefix + p) for p in parts]
+        if any(not np.array_equal(l.suh, ls[0].suh) or l.codebook != ls[0].codebook or l.trellis.shape[2] != ls[0].trellis.shape[2] for l in ls[1:]):
+            raise ValueError(f"pack refused: {prefix}{'/'.join(parts)} have different input scales or widths; the fused projection kernels "
+                             f"need one shared input rotation")
+        bias = None if ls[0].bias is None else np.concatenate([l.bias for l in ls])
+        return HostLinear(np.concatenate([l.trellis for l in ls], axis=1), ls[0].suh, np.concatenate([l.svh for l in ls]), bias, ls[0].codebook)
+
+    def plain(name):
+        e = ck.plain.get(name)
+        if e is None:
+            raise ValueError(f"pack refused: no tensor {name}")
+        return checkpoint.load_plain(folder, e).astype(np.float32)
+
+    w = HostWeights(cfg, plain("model.embed_tokens.weight"))
+    for i in range(cfg.n_layers):
+        p = f"model.layers.{i}."
+        lay = HostLayer(plain(p + "input_layernorm.weight"), fused(p + "self_attn.", "qkv_proj", ["q_proj", "k_proj", "v_proj"]), lin(p + "self_attn.o_proj"),
+                        plain(p + "post_attention_layernorm.weight"), fused(p + "mlp.", "gate_up_proj", ["gate_proj", "up_proj"]), lin(p + "mlp.down_proj"))
+        if cfg.qk_norm:
+            lay.q_norm, lay.k_norm = plain(p + "self_attn.q_norm.weight"), plain(p + "self_attn.k_norm.weight")
+        w.layers.append(lay)
+    w.final_norm = plain("model.norm.weight")
+    w.lm_head = lin("lm_head")
+    return w

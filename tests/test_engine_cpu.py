@@ -1,0 +1,123 @@
+"""Engine step loop on the CPU mock: exactness harness (and that it catches each injected fault), admission, errors,
+deadlines, stop tokens, prefix cache."""
+import time
+
+import numpy as np
+import pytest
+
+from rexl3_b200 import sched
+from rexl3_b200.engine import BackendError, Engine, MockBackend, MockOptions, Request, StepError, generate, harness
+from rexl3_b200.sampling import GREEDY, Sampling
+
+
+def mk(**kw):
+    return lambda: MockBackend(MockOptions(**kw))
+
+
+@pytest.mark.parametrize("check", [f.__name__ for f in harness.ALL])
+def test_exactness_checks_pass_on_the_honest_mock(check):
+    assert getattr(harness, check)(mk(), 512) is None
+
+
+@pytest.mark.parametrize("fault,caught_by", [("window_dependent", "row_invariance"), ("chunk_dependent", "chunked_prefill_equals_whole"),
+                                             ("rollback_leak", "rollback_equals_replay"), ("prefix_stale", "cached_equals_cold")])
+def test_each_fault_is_caught_by_its_check(fault, caught_by):
+    assert getattr(harness, caught_by)(mk(fault=fault), 512) is not None
+
+
+def test_native_draft_speeds_up_without_changing_output():
+    p = harness.default_prompts(512)
+    base = Engine(MockBackend(MockOptions()), spec="none")
+    a = generate(base, p, 64, harness.SAMPLING)
+    fast = Engine(MockBackend(MockOptions(native_draft=True)), spec="auto", max_drafts=4)
+    b = generate(fast, p, 64, harness.SAMPLING)
+    assert a == b and fast.counters["rounds"] < base.counters["rounds"] and fast.counters["accepted"] > 0
+
+
+def test_admission_queues_in_arrival_order_and_refuses_what_never_fits():
+    model = sched.ModelMemory(0, 10)
+    adm = sched.Admission(10 * 300, 0, model, 2)
+    eng = Engine(MockBackend(MockOptions(slots=2)), adm, spec="none")
+    with pytest.raises(sched.AdmitError):
+        eng.submit(Request("big", [1] * 400, 10, GREEDY))
+    for i in range(3):
+        eng.submit(Request(f"r{i}", [1 + i] * 100, 20, GREEDY))
+    eng.step()
+    assert eng.active_count() == 2 and len(eng.waiting) == 1
+    done = [e.id for e in eng.run_until_idle() if e.kind == "done"]
+    assert done.index("r0") < done.index("r2") and set(done) == {"r0", "r1", "r2"}
+    assert adm.available() == adm.capacity
+
+
+def test_stop_token_length_and_usage():
+    be = MockBackend(MockOptions(eos=7, eos_after=5))
+    eng = Engine(be, spec="none")
+    eng.submit(Request("a", [1, 2, 3], 50, GREEDY, stop_ids=(7,)))
+    eng.submit(Request("b", [4, 5], 4, GREEDY))
+    ev = eng.run_until_idle()
+    fin = {e.id: e for e in ev if e.kind == "done"}
+    assert fin["a"].reason == "stop" and fin["b"].reason == "length"
+    assert fin["b"].usage["completion_tokens"] == 4 and fin["b"].usage["prompt_tokens"] == 2 and "ttft_s" in fin["b"].usage
+    toks = [t for e in ev if e.kind == "tokens" and e.id == "a" for t in e.tokens]
+    assert toks[-1] == 7 and len(toks) == fin["a"].usage["completion_tokens"]
+
+
+def test_validation_cancel_and_deadline():
+    eng = Engine(MockBackend(MockOptions()), spec="none")
+    with pytest.raises(ValueError):
+        eng.submit(Request("x", [], 5, GREEDY))
+    with pytest.raises(ValueError):
+        eng.submit(Request("x", [99999], 5, GREEDY))
+    with pytest.raises(ValueError):
+        eng.submit(Request("x", [1], 5, Sampling(top_p=2.0)))
+    eng.submit(Request("c", [1, 2], 100, GREEDY))
+    eng.step()
+    assert eng.cancel("c") and not eng.has_work()
+    assert [e.reason for e in eng.take_events() if e.kind == "done"] == ["cancelled"]
+    eng.submit(Request("d", [1, 2], 10 ** 6, GREEDY, deadline=time.monotonic() + 0.05))
+    t0 = time.monotonic()
+    reasons = []
+    while eng.has_work() and time.monotonic() - t0 < 5:
+        reasons += [e.reason for e in eng.step() if e.kind == "done"]
+    assert reasons == ["deadline"]
+
+
+def test_backend_errors_retryable_fail_the_batch_fatal_raise():
+    eng = Engine(MockBackend(MockOptions(retryable_from_step=3)), spec="none")
+    eng.submit(Request("a", [1, 2, 3], 50, GREEDY))
+    with pytest.raises(StepError) as e:
+        eng.run_until_idle()
+    assert not e.value.fatal and not eng.has_work()
+    assert any(ev.kind == "error" for ev in eng.take_events())
+    eng = Engine(MockBackend(MockOptions(fatal_at_step=2)), spec="none")
+    eng.submit(Request("a", [1, 2, 3], 50, GREEDY))
+    with pytest.raises(StepError) as e:
+        eng.run_until_idle()
+    assert e.value.fatal
+
+
+def test_nan_row_fails_only_its_sequence():
+    be = MockBackend(MockOptions(nan_at_step=3))
+    eng = Engine(be, spec="none", prefill_policy="serial")
+    eng.submit(Request("a", [1, 2, 3], 6, Sampling(temperature=0.7)))
+    ev = eng.run_until_idle()
+    assert any(e.kind == "error" and "NaN" in e.message for e in ev)
+    eng.submit(Request("b", [1, 2, 3], 3, GREEDY))
+    assert any(e.kind == "done" and e.reason == "length" for e in eng.run_until_idle())
+
+
+def test_prefix_cache_hits_share_blocks_and_evict():
+    be = MockBackend(MockOptions(blocks=64))
+    idx = sched.PrefixIndex(sched.CacheBudget(max_bytes=3 * be.prefix_bytes_per_block()), block_tokens=64)
+    eng = Engine(be, spec="none", prefix=idx)
+    shared = np.random.default_rng(0).integers(0, 512, size=200).tolist()
+    generate(eng, [shared + [1]], 4, GREEDY)
+    assert len(idx) == 3 and be.pool.free_blocks() == 64 - 3          # the cache holds the three full blocks
+    generate(eng, [shared + [2, 3]], 4, GREEDY)
+    assert eng.counters["cached_tokens"] == 192
+    other = np.random.default_rng(1).integers(0, 512, size=200).tolist()
+    generate(eng, [other], 4, GREEDY)
+    assert len(idx) == 3 and idx.stats["evictions"] == 3 and be.pool.free_blocks() == 64 - 3
+    assert MockOptions.parse("vocab=100,native_draft=true,fault=rollback_leak").native_draft
+    with pytest.raises(ValueError):
+        MockOptions.parse("nope=1")
