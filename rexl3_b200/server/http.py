@@ -1,0 +1,289 @@
+"""OpenAI-compatible HTTP surface (ASGI / Starlette).
+
+Routes (reference crates/server/src/http.rs:229-243): GET /health/live, /health, /health/ready, /v1/health, /v1/models,
+/metrics; POST /v1/chat/completions (SSE when ``stream``), /v1/completions, /v1/chat/completions/render, /tokenize.
+Errors are OpenAI-shaped; 429 / 503 carry Retry-After.  The default seed is sha256 of the prompt tokens: same conversation,
+same reply.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+
+from starlette.applications import Starlette
+from starlette.requests import Request as HttpRequest
+from starlette.responses import JSONResponse, PlainTextResponse, StreamingResponse
+from starlette.routing import Route
+
+from ..engine import Request
+from ..sampling import seed_for
+from . import api
+from .runtime import EngineHandle
+from .text import ChatFormat, ReasoningSplitter, StopMatcher, TemplateRefused, extract_tool_calls
+from .tokenizer import Tok
+
+
+class AppState:
+    def __init__(self, handle: EngineHandle, tok: Tok, fmt: ChatFormat, model_name: str, max_model_len: int, aliases=(), defaults=None,
+                 default_max_tokens: int = 512, fingerprint: str = "rexl3-b200", max_body_bytes: int = 64 << 20, info: dict | None = None):
+        self.handle, self.tok, self.fmt = handle, tok, fmt
+        self.model_name, self.aliases = model_name, set(aliases)
+        self.max_model_len, self.default_max_tokens = max_model_len, default_max_tokens
+        self.defaults = defaults or api.GenDefaults()
+        self.fingerprint, self.max_body_bytes = fingerprint, max_body_bytes
+        self.info = info or {}
+
+
+def _err(e: api.ApiError) -> JSONResponse:
+    h = {"Retry-After": str(e.retry_after)} if e.retry_after else None
+    return JSONResponse(e.body(), status_code=e.status, headers=h)
+
+
+async def _json_body(request: HttpRequest, st: AppState) -> dict:
+    raw = await request.body()
+    if len(raw) > st.max_body_bytes:
+        raise api.ApiError(413, "request body too large", code="body_too_large")
+    try:
+        return json.loads(raw)
+    except (json.JSONDecodeError, UnicodeDecodeError, RecursionError):
+        raise api.bad("the request body is not valid JSON")
+
+
+def _check_model(st: AppState, p: api.Params) -> None:
+    if p.model and p.model != st.model_name and p.model not in st.aliases:
+        raise api.ApiError(404, f"model '{p.model}' is not served here", code="model_not_found", param="model")
+
+
+def _ready_or_503(st: AppState) -> None:
+    s = st.handle.state
+    if s not in ("ready", "degraded"):
+        raise api.ApiError(503, f"engine is {s}", "service_unavailable", s, retry_after=5)
+
+
+def _make_request(st: AppState, ids: list, p: api.Params, rid: str) -> Request:
+    if not ids:
+        raise api.bad("the prompt is empty")
+    limit = st.max_model_len
+    if len(ids) >= limit:
+        raise api.ApiError(400, f"the prompt has {len(ids)} tokens, the context window holds {limit}", code="context_length_exceeded", param="messages")
+    room = limit - len(ids)
+    max_new = min(room, p.max_tokens if p.max_tokens is not None else st.default_max_tokens)
+    samp = p.sampling
+    if p.seed is None and samp.temperature > 0:
+        samp = samp.with_seed(seed_for(ids, 0))
+    stop_ids = tuple(st.tok.eos_ids)
+    return Request(rid, ids, max_new, samp, stop_ids, draft=p.draft, prefix_cache=p.prefix_cache)
+
+
+class _Reply:
+    """Token ids -> text deltas through the decoder, the reasoning split and the stop matcher."""
+
+    def __init__(self, st: AppState, p: api.Params, chat: bool, prompt_text: str = ""):
+        self.dec = st.tok.stream(p.skip_special)
+        self.stop = StopMatcher(p.stop)
+        self.reason = ReasoningSplitter(st.fmt.think_open, st.fmt.think_close, started_inside=prompt_text.rstrip().endswith(st.fmt.think_open)) if chat else None
+        self.ids, self.text, self.reasoning = [], "", ""
+        self.stopped = False
+        self.eos = set(st.tok.eos_ids)
+
+    def push(self, ids):
+        """-> (content delta, reasoning delta)"""
+        if self.stopped:
+            return "", ""
+        self.ids.extend(ids)
+        piece = self.dec.push([i for i in ids if i not in self.eos])
+        return self._route(piece)
+
+    def _route(self, piece):
+        content, reasoning = (piece, "") if self.reason is None else self.reason.push(piece)
+        if content:
+            content, hit = self.stop.push(content)
+            self.stopped = hit
+        self.text += content
+        self.reasoning += reasoning
+        return content, reasoning
+
+    def finish(self):
+        if self.stopped:
+            return "", ""
+        c, r = self._route(self.dec.flush())
+        if self.reason is not None:
+            c2, r2 = self.reason.flush()
+            c2, hit = self.stop.push(c2) if c2 else ("", False)
+            c, r = c + c2, r + r2
+            self.text += c2
+            self.reasoning += r2
+        tail = "" if self.stopped else self.stop.flush()
+        self.text += tail
+        return c + tail, r
+
+
+async def _collect(st: AppState, ticket, reply: _Reply):
+    """Drive one request to its end (non-streaming).  Returns (reason, usage)."""
+    while True:
+        msg = await ticket.out.get()
+        if msg[0] == "tokens":
+            reply.push(msg[1])
+            if reply.stopped:
+                st.handle.cancel(ticket.id)
+        elif msg[0] == "done":
+            reply.finish()
+            return ("stop" if reply.stopped else msg[1]), msg[2]
+        elif msg[0] == "refused":
+            code = msg[1]
+            raise api.ApiError(400, msg[2], code="context_length_exceeded" if code == "context_length_exceeded" else None)
+        else:
+            raise api.ApiError(500, str(msg[1]), "server_error", "engine_error")
+
+
+def _sse(obj) -> bytes:
+    return b"data: " + json.dumps(obj, ensure_ascii=False).encode() + b"\n\n"
+
+
+def build_app(st: AppState) -> Starlette:
+    async def live(request):
+        return JSONResponse({"status": "ok"})
+
+    async def health(request):
+        s = st.handle.state
+        ok = s in ("ready",)
+        body = {"status": s}
+        if st.handle.error:
+            body["error"] = st.handle.error
+        return JSONResponse(body, status_code=200 if ok else 503)
+
+    async def models(request):
+        m = {"id": st.model_name, "object": "model", "owned_by": "rexl3-b200", "max_model_len": st.max_model_len,
+             "configured_max_model_len": st.max_model_len, "aliases": sorted(st.aliases)}
+        m.update(st.info)
+        return JSONResponse({"object": "list", "data": [m]})
+
+    async def metrics(request):
+        return PlainTextResponse(st.handle.metrics.render(), media_type="text/plain; version=0.0.4")
+
+    async def tokenize(request):
+        try:
+            body = await _json_body(request, st)
+            text = body.get("prompt", body.get("text"))
+            if not isinstance(text, str):
+                raise api.bad("'prompt' must be a string", "prompt")
+            ids = st.tok.encode(text)
+            return JSONResponse({"tokens": ids, "count": len(ids), "max_model_len": st.max_model_len})
+        except api.ApiError as e:
+            return _err(e)
+
+    def render_chat(body, p):
+        msgs = api.parse_messages(body)
+        try:
+            text = st.fmt.render(msgs, tools=p.tools, add_generation_prompt=True, **p.template_kwargs)
+        except TemplateRefused as e:
+            raise api.bad(str(e), "messages", "template_error")
+        return text, st.tok.encode(text)
+
+    async def render(request):
+        try:
+            body = await _json_body(request, st)
+            p = api.parse_params(body, api.CHAT_FIELDS, st.defaults)
+            text, ids = render_chat(body, p)
+            return JSONResponse({"prompt": text, "token_ids": ids, "count": len(ids)})
+        except api.ApiError as e:
+            return _err(e)
+
+    async def run(request, chat: bool):
+        try:
+            body = await _json_body(request, st)
+            p = api.parse_params(body, api.CHAT_FIELDS if chat else api.COMPLETION_FIELDS, st.defaults)
+            _check_model(st, p)
+            _ready_or_503(st)
+            if chat:
+                prompt_text, ids = render_chat(body, p)
+            else:
+                pr = body.get("prompt")
+                if isinstance(pr, list) and pr and all(isinstance(t, int) and not isinstance(t, bool) for t in pr):
+                    prompt_text, ids = "", list(pr)
+                elif isinstance(pr, str):
+                    prompt_text, ids = pr, st.tok.encode(pr)
+                else:
+                    raise api.bad("'prompt' must be a string or a list of token ids", "prompt")
+            rid = api.new_id("chatcmpl" if chat else "cmpl")
+            req = _make_request(st, ids, p, rid)
+            try:
+                ticket = st.handle.submit(req, asyncio.get_running_loop())
+            except OverflowError:
+                raise api.ApiError(429, "the request queue is full", "rate_limit_error", "queue_full", retry_after=1)
+            except RuntimeError as e:
+                raise api.ApiError(503, f"engine is {e}", "service_unavailable", str(e), retry_after=5)
+            reply = _Reply(st, p, chat, prompt_text)
+            model = p.model or st.model_name
+            if not p.stream:
+                reason, usage = await _collect(st, ticket, reply)
+                u = api.usage_object(usage, len(st.tok.encode(reply.reasoning)) if reply.reasoning else 0)
+                if chat:
+                    text, calls = extract_tool_calls(reply.text, st.fmt.tool_open, st.fmt.tool_close) if p.tools else (reply.text, [])
+                    return JSONResponse(api.chat_completion(rid, model, text, reply.reasoning, calls, reason, u, st.fingerprint,
+                                                            reply.ids if p.return_token_ids else None))
+                return JSONResponse(api.text_completion(rid, model, reply.text, reason, u, st.fingerprint))
+
+            async def gen():
+                try:
+                    if chat:
+                        yield _sse(api.chat_chunk(rid, model, {"role": "assistant", "content": ""}, None, st.fingerprint))
+                    while True:
+                        try:
+                            msg = await asyncio.wait_for(ticket.out.get(), timeout=15.0)
+                        except asyncio.TimeoutError:
+                            yield b": keep-alive\n\n"
+                            continue
+                        if msg[0] == "tokens":
+                            c, r = reply.push(msg[1])
+                            if chat:
+                                if r:
+                                    yield _sse(api.chat_chunk(rid, model, {"reasoning_content": r}, None, st.fingerprint))
+                                if c:
+                                    yield _sse(api.chat_chunk(rid, model, {"content": c}, None, st.fingerprint))
+                            elif c:
+                                yield _sse(api.text_completion(rid, model, c, None, None, st.fingerprint, stream_chunk=True))
+                            if reply.stopped:
+                                st.handle.cancel(ticket.id)
+                        elif msg[0] == "done":
+                            c, r = reply.finish()
+                            reason = "stop" if reply.stopped else msg[1]
+                            if chat:
+                                if r:
+                                    yield _sse(api.chat_chunk(rid, model, {"reasoning_content": r}, None, st.fingerprint))
+                                if c:
+                                    yield _sse(api.chat_chunk(rid, model, {"content": c}, None, st.fingerprint))
+                                yield _sse(api.chat_chunk(rid, model, {}, api.finish_reason(reason), st.fingerprint))
+                                if p.include_usage:
+                                    yield _sse(api.chat_chunk(rid, model, {}, None, st.fingerprint, usage=api.usage_object(msg[2])))
+                            else:
+                                yield _sse(api.text_completion(rid, model, c, reason, api.usage_object(msg[2]) if p.include_usage else None,
+                                                               st.fingerprint, stream_chunk=True))
+                            break
+                        else:
+                            text = msg[2] if msg[0] == "refused" else str(msg[1])
+                            yield _sse({"error": {"message": text, "type": "server_error", "code": msg[1] if msg[0] == "refused" else "engine_error",
+                                                  "param": None}})
+                            break
+                    yield b"data: [DONE]\n\n"
+                finally:
+                    ticket.closed = True
+                    st.handle.cancel(ticket.id)    # client gone (or done): free the slot
+
+            return StreamingResponse(gen(), media_type="text/event-stream", headers={"Cache-Control": "no-cache", "X-Accel-Buffering": "no"})
+        except api.ApiError as e:
+            return _err(e)
+
+    async def chat(request):
+        return await run(request, True)
+
+    async def completions(request):
+        return await run(request, False)
+
+    routes = [Route("/health/live", live), Route("/health", health), Route("/health/ready", health), Route("/v1/health", health),
+              Route("/v1/models", models), Route("/metrics", metrics), Route("/tokenize", tokenize, methods=["POST"]),
+              Route("/v1/chat/completions", chat, methods=["POST"]), Route("/v1/completions", completions, methods=["POST"]),
+              Route("/v1/chat/completions/render", render, methods=["POST"])]
+    app = Starlette(routes=routes)
+    app.state.rexl3 = st
+    return app

@@ -1,0 +1,163 @@
+"""``python -m rexl3_b200.server`` — the serving binary (the reference's ``rexl3-serve``, crates/server/src/main.rs:3-13,
+176-240): strict flags (an unknown flag is a usage error), everything CPU-side (tokenizer, template, listener) is set up
+before CUDA starts, the engine runs on its own thread, a watchdog aborts a wedged process, SIGTERM drains.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import signal
+import sys
+import threading
+import time
+
+from ..engine import Engine, MockBackend, MockOptions
+from ..sched import Admission, CacheBudget, ModelMemory, PrefixIndex
+from . import api
+from .http import AppState, build_app
+from .runtime import EngineHandle, Metrics, RuntimeConfig
+from .text import ChatFormat
+from .tokenizer import load_tokenizer
+
+
+def parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="rexl3-serve", allow_abbrev=False)
+    p.add_argument("--model", help="pack directory (config.json, model*.safetensors, tokenizer.json ...)")
+    p.add_argument("--backend", choices=["cuda", "cpu", "mock"], default="cuda")
+    p.add_argument("--mock", default="", help="key=value,... options of the mock backend")
+    p.add_argument("--random-init", default="", help="serve a random-init model of this built-in config instead of a pack (benchmarks)")
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8000)
+    p.add_argument("--served-model-name", default="")
+    p.add_argument("--model-alias", action="append", default=[])
+    p.add_argument("--slots", type=int, default=8)
+    p.add_argument("--max-model-len", type=int, default=8192)
+    p.add_argument("--kv-tokens", type=int, default=0, help="tokens of KV cache to reserve (0: slots * max-model-len)")
+    p.add_argument("--prefill-chunk", type=int, default=4096)
+    p.add_argument("--window-rows", type=int, default=64)
+    p.add_argument("--kv-dtype", choices=["bf16"], default="bf16")
+    p.add_argument("--spec", choices=["auto", "mtp", "copy", "self", "none"], default="auto")
+    p.add_argument("--no-drafts", action="store_true")
+    p.add_argument("--max-drafts", type=int, default=4)
+    p.add_argument("--prefix-cache", choices=["on", "off"], default="on")
+    p.add_argument("--prefix-cache-mib", type=int, default=4096)
+    p.add_argument("--default-max-tokens", type=int, default=512)
+    p.add_argument("--queue-depth", type=int, default=64)
+    p.add_argument("--queue-timeout", type=float, default=300)
+    p.add_argument("--request-timeout", type=float, default=1800)
+    p.add_argument("--shutdown-grace", type=float, default=8)
+    p.add_argument("--unready-after", type=int, default=3)
+    p.add_argument("--exit-after", type=int, default=10)
+    p.add_argument("--heartbeat-stale-secs", type=float, default=60)
+    p.add_argument("--max-body-mib", type=int, default=64)
+    p.add_argument("--no-graphs", action="store_true")
+    p.add_argument("--version", action="store_true")
+    return p
+
+
+def build(args):
+    """-> (make_engine callable for the engine thread, tokenizer, chat format, model name, info dict).  No CUDA call happens here."""
+    folder = args.model if args.model and os.path.isdir(args.model) else None
+    if args.backend == "mock":
+        opts = MockOptions.parse(args.mock)
+        opts.slots = args.slots
+        vocab, name = opts.vocab, args.served_model_name or "mock"
+
+        def make():
+            be = MockBackend(opts)
+            prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=be.prefix_block_tokens()) if args.prefix_cache == "on" else None
+            return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
+                          max_drafts=args.max_drafts, prefix=prefix)
+        info = {"backend": "mock"}
+    else:
+        from ..models import dense
+        if args.random_init:
+            cfg = dense.CONFIGS[args.random_init]
+            weights = None
+        else:
+            if folder is None:
+                raise SystemExit("rexl3-serve: --model DIR (or --random-init CONFIG) is required")
+            from ..quant import quantize
+            cfg = quantize.config_from_pack(folder)
+            weights = quantize.load_pack(folder)          # header scan + refusals by name happen before CUDA starts
+        vocab, name = cfg.vocab, args.served_model_name or cfg.name
+        kv_tokens = args.kv_tokens or args.slots * args.max_model_len
+        info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None}
+
+        def make():
+            if args.backend == "cpu":
+                from ..engine.cpu_backend import CpuDenseBackend
+                be = CpuDenseBackend(weights if weights is not None else dense.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
+                adm, prefix = None, None
+            else:
+                import torch
+                from ..engine.gpu_backend import DenseGpuBackend
+                pages = -(-kv_tokens // dense.PAGE) + args.slots
+                free, _ = torch.cuda.mem_get_info()
+                mm = ModelMemory(int(cfg.weight_params() * cfg.bits / 8), cfg.kv_bytes_per_token(), activation_reserve=2 << 30)
+                adm = Admission(free, 1 << 30, mm, args.slots).with_max_context(args.max_model_len).with_kv_tokens(kv_tokens)
+                adm.check(min(args.max_model_len, 1))     # fail closed: a plan that can never hold one token is refused at boot
+                if pages * cfg.kv_bytes_per_token() * dense.PAGE > adm.capacity:
+                    raise RuntimeError(f"memory plan refused: {kv_tokens} KV tokens need {pages * cfg.kv_bytes_per_token() * dense.PAGE >> 20} MiB, "
+                                       f"{adm.capacity >> 20} MiB are available after weights and reserve")
+                model = dense.DenseGPU(weights if weights is not None else cfg, num_pages=pages, max_rows=min(256, args.window_rows),
+                                       max_seqs=args.slots, max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1,
+                                       max_prefill_rows=args.prefill_chunk)
+                be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs)
+                prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
+            return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode())
+    tok = load_tokenizer(folder, vocab)
+    fmt = ChatFormat.from_dir(folder)
+    return make, tok, fmt, name, info
+
+
+def make_app(args, metrics: Metrics | None = None):
+    make, tok, fmt, name, info = build(args)
+    rc = RuntimeConfig(queue_depth=args.queue_depth, queue_timeout_s=args.queue_timeout, request_timeout_s=args.request_timeout,
+                       unready_after=args.unready_after, exit_after=args.exit_after, shutdown_grace_s=args.shutdown_grace)
+    handle = EngineHandle(make, rc, metrics)
+    defaults = api.GenDefaults()
+    if args.model and os.path.exists(os.path.join(args.model, "generation_config.json")):
+        defaults = api.GenDefaults.from_dict(json.load(open(os.path.join(args.model, "generation_config.json"))))
+    st = AppState(handle, tok, fmt, name, args.max_model_len, args.model_alias, defaults, args.default_max_tokens,
+                  fingerprint=f"rexl3-b200-{name}", max_body_bytes=args.max_body_mib << 20, info=info)
+    return build_app(st), handle
+
+
+def main(argv=None) -> int:
+    args = parser().parse_args(argv)
+    if args.version:
+        from .. import __version__
+        print(f"rexl3-serve (rexl3_b200) {__version__}")
+        return 0
+    import uvicorn
+    print(f"rexl3 event=start backend={args.backend} host={args.host} port={args.port}", file=sys.stderr, flush=True)
+    app, handle = make_app(args)
+
+    def watchdog():
+        while True:
+            time.sleep(0.25)
+            if handle.wedged(args.heartbeat_stale_secs):
+                print("rexl3 level=error event=wedged action=abort", file=sys.stderr, flush=True)
+                os.abort()
+            if handle.state == "failed":
+                print(f"rexl3 level=error event=engine_failed error={handle.error!r}", file=sys.stderr, flush=True)
+                os._exit(70)
+    threading.Thread(target=watchdog, daemon=True).start()
+    server = uvicorn.Server(uvicorn.Config(app, host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=int(args.shutdown_grace)))
+
+    def on_signal(signum, frame):
+        print("rexl3 event=drain", file=sys.stderr, flush=True)
+        handle.drain()
+        server.should_exit = True
+    signal.signal(signal.SIGTERM, on_signal)
+    signal.signal(signal.SIGINT, on_signal)
+    server.run()
+    handle.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

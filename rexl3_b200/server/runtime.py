@@ -1,0 +1,253 @@
+"""The engine thread: the only thread that touches the model.  HTTP handlers talk to it through a command queue and get
+tokens back over per-request asyncio queues.
+
+FIFO admission with a bounded queue, queue / request deadlines, consecutive-error counters (degraded after
+``unready_after``, exit after ``exit_after``), a progress heartbeat a watchdog can check, graceful drain.  "Never a zombie":
+a fatal backend error ends the loop and fails every request.  Behaviour parity: reference crates/server/src/runtime.rs:1-11,
+:603 (spawn_with), :772-900 (run loop), :1001-1252 (enqueue / admit / route), main.rs:978-990 (watchdog).
+"""
+from __future__ import annotations
+
+import asyncio
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+
+from ..engine import Engine, Request, StepError
+from ..sched import AdmitError
+
+
+@dataclass
+class RuntimeConfig:
+    queue_depth: int = 64
+    queue_timeout_s: float = 300.0
+    request_timeout_s: float = 1800.0
+    unready_after: int = 3
+    exit_after: int = 10
+    idle_sleep_s: float = 0.002
+    shutdown_grace_s: float = 8.0
+
+
+@dataclass
+class Ticket:
+    id: str
+    loop: asyncio.AbstractEventLoop
+    out: asyncio.Queue
+    t_submit: float = field(default_factory=time.monotonic)
+    t_first: float | None = None
+    closed: bool = False
+
+    def post(self, msg) -> None:
+        if not self.closed:
+            self.loop.call_soon_threadsafe(self.out.put_nowait, msg)
+
+
+class Metrics:
+    """Process-wide counters and 1 ms * 2^k latency histograms, rendered as Prometheus text."""
+
+    BUCKETS = [0.001 * 2 ** k for k in range(18)]
+
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.counters = {}
+        self.gauges = {}
+        self.hist = {}
+        self.t_boot = time.time()
+
+    def inc(self, name, v=1.0, **labels):
+        with self.lock:
+            k = (name, tuple(sorted(labels.items())))
+            self.counters[k] = self.counters.get(k, 0.0) + v
+
+    def set(self, name, v, **labels):
+        with self.lock:
+            self.gauges[(name, tuple(sorted(labels.items())))] = float(v)
+
+    def observe(self, name, v):
+        with self.lock:
+            h = self.hist.setdefault(name, [[0] * (len(self.BUCKETS) + 1), 0.0, 0])
+            i = next((j for j, b in enumerate(self.BUCKETS) if v <= b), len(self.BUCKETS))
+            h[0][i] += 1
+            h[1] += v
+            h[2] += 1
+
+    @staticmethod
+    def _lab(labels):
+        return "{" + ",".join(f'{k}="{v}"' for k, v in labels) + "}" if labels else ""
+
+    def render(self) -> str:
+        with self.lock:
+            lines = []
+            for (n, l), v in sorted(self.counters.items()):
+                lines.append(f"rexl3_{n}{self._lab(l)} {v:g}")
+            for (n, l), v in sorted(self.gauges.items()):
+                lines.append(f"rexl3_{n}{self._lab(l)} {v:g}")
+            for n, (counts, total, cnt) in sorted(self.hist.items()):
+                acc = 0
+                for b, c in zip(self.BUCKETS, counts):
+                    acc += c
+                    lines.append(f'rexl3_{n}_bucket{{le="{b:g}"}} {acc}')
+                lines.append(f'rexl3_{n}_bucket{{le="+Inf"}} {cnt}')
+                lines.append(f"rexl3_{n}_sum {total:g}")
+                lines.append(f"rexl3_{n}_count {cnt}")
+            lines.append(f"rexl3_uptime_seconds {time.time() - self.t_boot:g}")
+            return "\n".join(lines) + "\n"
+
+
+class EngineHandle:
+    """Owns the engine thread.  States: loading -> ready -> (degraded) -> draining -> stopped | failed."""
+
+    def __init__(self, make_engine, cfg: RuntimeConfig | None = None, metrics: Metrics | None = None):
+        self.cfg = cfg or RuntimeConfig()
+        self.metrics = metrics or Metrics()
+        self.cmd: "queue.Queue" = queue.Queue()
+        self.state = "loading"
+        self.error = ""
+        self.tickets = {}
+        self.pending = 0                 # queued + running requests
+        self.heartbeat = time.monotonic()
+        self.engine: Engine | None = None
+        self.consecutive_errors = 0
+        self._make = make_engine
+        self._ready = threading.Event()
+        self.thread = threading.Thread(target=self._run, name="rexl3-engine", daemon=True)
+        self.thread.start()
+
+    # ------------------------------------------------------------------ called from HTTP handlers
+    def wait_ready(self, timeout: float | None = None) -> bool:
+        self._ready.wait(timeout)
+        return self.state in ("ready", "degraded")
+
+    def submit(self, req: Request, loop: asyncio.AbstractEventLoop) -> Ticket:
+        if self.state not in ("ready", "degraded"):
+            raise RuntimeError(self.state)
+        if self.pending >= self.cfg.queue_depth:
+            raise OverflowError("queue full")
+        t = Ticket(req.id, loop, asyncio.Queue())
+        if req.deadline is None:
+            req.deadline = time.monotonic() + self.cfg.request_timeout_s
+        self.pending += 1
+        self.cmd.put(("submit", req, t))
+        return t
+
+    def cancel(self, rid: str) -> None:
+        self.cmd.put(("cancel", rid, None))
+
+    def drain(self) -> None:
+        self.cmd.put(("drain", None, None))
+
+    def wedged(self, stale_s: float = 60.0) -> bool:
+        """True when there is work but the loop has made no progress for `stale_s` (a watchdog aborts the process on this)."""
+        return self.state in ("ready", "degraded") and self.pending > 0 and time.monotonic() - self.heartbeat > stale_s
+
+    # ------------------------------------------------------------------ the engine thread
+    def _fail_all(self, message: str) -> None:
+        for t in list(self.tickets.values()):
+            t.post(("error", message))
+        self.tickets.clear()
+        self.pending = 0
+
+    def _run(self) -> None:
+        try:
+            self.engine = self._make()
+            self.state = "ready"
+        except Exception as e:  # boot failure: report, never serve
+            self.state, self.error = "failed", f"{e.__class__.__name__}: {e}"
+            self._ready.set()
+            return
+        self._ready.set()
+        eng, m = self.engine, self.metrics
+        draining, t_drain = False, 0.0
+        while True:
+            try:
+                while True:
+                    kind, a, b = self.cmd.get_nowait() if (eng.has_work() or draining) else self.cmd.get(timeout=0.05)
+                    if kind == "submit":
+                        if draining:
+                            b.post(("error", "draining"))
+                            self.pending -= 1
+                            continue
+                        try:
+                            eng.submit(a)
+                            self.tickets[a.id] = b
+                            m.inc("requests_total")
+                        except (ValueError, AdmitError) as e:
+                            code = "context_length_exceeded" if isinstance(e, AdmitError) and e.kind in ("ContextTooLong", "NeverFits") else "invalid"
+                            b.post(("refused", code, str(e)))
+                            self.pending -= 1
+                    elif kind == "cancel":
+                        eng.cancel(a)
+                    elif kind == "drain":
+                        draining, t_drain = True, time.monotonic()
+                        self.state = "draining"
+                    elif kind == "stop":
+                        self._fail_all("stopped")
+                        self.state = "stopped"
+                        return
+            except queue.Empty:
+                pass
+            if eng.events:                      # a cancel finishes a request outside step(): deliver it now
+                self._route(eng.take_events())
+            if draining and (not eng.has_work() or time.monotonic() - t_drain > self.cfg.shutdown_grace_s):
+                self._fail_all("draining")
+                self.state = "stopped"
+                return
+            if not eng.has_work():
+                self.heartbeat = time.monotonic()
+                continue
+            try:
+                t0 = time.perf_counter()
+                events = eng.step()
+                m.observe("step_seconds", time.perf_counter() - t0)
+                self.consecutive_errors = 0
+                if self.state == "degraded":
+                    self.state = "ready"
+            except StepError as e:
+                events = eng.take_events()
+                m.inc("step_errors_total", kind=e.kind)
+                self.consecutive_errors += 1
+                if e.fatal or self.consecutive_errors >= self.cfg.exit_after:
+                    self._route(events)
+                    self._fail_all(str(e))
+                    self.state, self.error = "failed", str(e)
+                    return
+                if self.consecutive_errors >= self.cfg.unready_after:
+                    self.state = "degraded"
+            except Exception as e:  # a bug in the loop must not leave a zombie that accepts requests
+                self._fail_all(f"internal error: {e.__class__.__name__}: {e}")
+                self.state, self.error = "failed", f"{e.__class__.__name__}: {e}"
+                return
+            self.heartbeat = time.monotonic()
+            self._route(events)
+            c = eng.counters
+            m.set("active_sequences", eng.active_count())
+            m.set("queued_requests", len(eng.waiting))
+            for k in ("decode_tokens", "prefill_tokens", "drafted", "accepted", "rounds", "cached_tokens"):
+                m.set(f"engine_{k}_total", c[k])
+
+    def _route(self, events) -> None:
+        for ev in events:
+            t = self.tickets.get(ev.id)
+            if t is None:
+                continue
+            if ev.kind == "tokens":
+                if t.t_first is None:
+                    t.t_first = time.monotonic()
+                    self.metrics.observe("ttft_seconds", t.t_first - t.t_submit)
+                self.metrics.inc("generated_tokens_total", len(ev.tokens))
+                t.post(("tokens", ev.tokens))
+            else:
+                if ev.kind == "done":
+                    t.post(("done", ev.reason, ev.usage))
+                    self.metrics.observe("e2e_seconds", time.monotonic() - t.t_submit)
+                    self.metrics.inc("finished_total", reason=ev.reason)
+                else:
+                    t.post(("error", ev.message or ev.reason))
+                    self.metrics.inc("finished_total", reason="error")
+                self.tickets.pop(ev.id, None)
+                self.pending = max(0, self.pending - 1)
+
+    def stop(self) -> None:
+        self.cmd.put(("stop", None, None))
+        self.thread.join(timeout=10)
