@@ -1,0 +1,230 @@
+// Tensor-parallel collectives fused with the EXL3 finish stages (sm_100a, NVLink peer memory).
+//
+//   GEMM (row-parallel o_proj / down_proj)  --tiles pushed to the owner by the GEMM epilogue (exl3_gemm_tm.cu)-->
+//   finish_rs_kernel    : owner sums the R x S partial planes in (rank, split) order, output Hadamard, svh, bias, residual add on
+//                         its d/R columns, and pushes the row's partial sum of squares to every rank            (reduce-scatter end)
+//   norm_rot_push_kernel: every rank normalises its columns with the all-rank sum of squares, applies the next layer's
+//                         input rotation and pushes the fp16 slice into every rank's gathered activation buffer (all-gather start)
+//   GEMM (column-parallel qkv / gate_up / lm_head) waits per source rank for the slices to land and consumes them chunk by chunk.
+//
+// Each kernel's CTAs wait only for kernels launched EARLIER on the other ranks' streams, so nothing here needs co-scheduling.
+// Every wait is bounded (2 s) and reports through the status words.  Semantics matched: the reference's TP arms sum disjoint
+// or partial buffers in a fixed rank order (crates/cuda/csrc/tp_oneshot.cu:1-83; nemotron_h_omni/tp_arm.rs:556-584); the
+// schedule (push + flags instead of ncclAllReduce) is new.
+#include "tp.cuh"
+
+namespace rx {
+
+__device__ __forceinline__ float c_bf16_to_f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+__device__ __forceinline__ uint16_t c_f_to_bf16(float f) {
+  __nv_bfloat16 b = __float2bfloat16_rn(f);
+  return *reinterpret_cast<uint16_t*>(&b);
+}
+
+struct FinishTp {
+  int ranks, rank;
+  const unsigned* in_flag;        // local flags [ranks]: partial tiles of source rank r have landed
+  float* ss[TP_MAX];              // per destination rank: sum-of-squares buffer f32 [ranks][rows_cap]
+  unsigned* ss_flag[TP_MAX];      // per destination rank: flags [ranks]
+  unsigned* local_count;
+  const unsigned* epoch;
+  unsigned use_index;
+  int rows_cap;
+};
+
+struct PushTp {
+  int ranks, rank;
+  const float* ss;                // local sum-of-squares buffer f32 [ranks][rows_cap]
+  const unsigned* ss_flag;        // local flags [ranks]
+  __half* xr[TP_MAX];             // per destination rank: gathered activation buffer fp16 [rows][d]
+  unsigned* xr_flag[TP_MAX];      // per destination rank: flags [ranks]
+  unsigned* local_count;
+  const unsigned* epoch;
+  unsigned use_index;
+  int rows_cap;
+};
+
+__global__ void tp_bump_epoch_kernel(unsigned* epoch) {
+  pdl_launch();
+  pdl_wait();
+  *epoch += 1;
+}
+
+// part: f32 [ranks][S][M][n_own].  h: bf16 [M][d], this rank owns columns [col0, col0 + n_own).
+__global__ void __launch_bounds__(1024) finish_rs_kernel(const float* __restrict__ part, int S, int M, int n_own, int d, int col0,
+                                                         const __half* __restrict__ svh_own, const float* __restrict__ bias_own,
+                                                         uint16_t* __restrict__ h, int* status, const __grid_constant__ FinishTp tp) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float blk_ss[64];
+  __shared__ int ok_sh;
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const unsigned ticket = tp_ticket(tp.epoch, tp.use_index);
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < tp.ranks && ok; ++r) ok = tp_wait_flag(tp.in_flag + r, ticket, status, 160) ? 1 : 0;
+    ok_sh = ok;
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  const size_t plane = (size_t)M * n_own;   // the GEMM epilogue laid the planes out for exactly M rows
+  for (int b = warp; b < n_own / 128; b += nw) {
+    const int n0 = b * 128 + lane * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int total = tp.ranks * S;      // planes in (rank, split) order: the reduction order is fixed by the layout
+    for (int s0 = 0; s0 < total; s0 += 8) {
+      float4 p[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < total) p[j] = *reinterpret_cast<const float4*>(part + (size_t)(s0 + j) * plane + (size_t)row * n_own + n0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < total) {
+          if (s0 + j == 0) acc = p[j];
+          else { acc.x += p[j].x; acc.y += p[j].y; acc.z += p[j].z; acc.w += p[j].w; }
+        }
+    }
+    float y[4] = {acc.x, acc.y, acc.z, acc.w};
+    fwht128_warp(y);
+    const uint2 su = *reinterpret_cast<const uint2*>(svh_own + n0);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+    y[0] *= a.x; y[1] *= a.y; y[2] *= c.x; y[3] *= c.y;
+    if (bias_own != nullptr) {
+      const float4 bb = *reinterpret_cast<const float4*>(bias_own + n0);
+      y[0] += bb.x; y[1] += bb.y; y[2] += bb.z; y[3] += bb.w;
+    }
+    uint16_t* hp = h + (size_t)row * d + col0 + n0;
+    const uint2 hu = *reinterpret_cast<const uint2*>(hp);
+    float r[4] = {__uint_as_float(hu.x << 16), __uint_as_float(hu.x & 0xFFFF0000u), __uint_as_float(hu.y << 16), __uint_as_float(hu.y & 0xFFFF0000u)};
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r[i] = c_bf16_to_f(c_f_to_bf16(r[i] + y[i]));
+      ss += r[i] * r[i];
+    }
+    uint2 o;
+    o.x = (uint32_t)c_f_to_bf16(r[0]) | ((uint32_t)c_f_to_bf16(r[1]) << 16);
+    o.y = (uint32_t)c_f_to_bf16(r[2]) | ((uint32_t)c_f_to_bf16(r[3]) << 16);
+    *reinterpret_cast<uint2*>(hp) = o;
+    ss = warp_sum(ss);
+    if (lane == 0) blk_ss[b] = ss;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int b = 0; b < n_own / 128; ++b) tot += blk_ss[b];
+    for (int r = 0; r < tp.ranks; ++r) tp.ss[r][(size_t)tp.rank * tp.rows_cap + row] = tot;     // push to every rank (self included)
+    tp_publish_last(tp.local_count, gridDim.x, tp.ss_flag, tp.ranks, tp.rank, ticket);
+  }
+}
+
+// h: bf16 [M][d]; this rank normalises and rotates its columns [col0, col0 + n_own) and pushes them into every rank's xr [M][d].
+// norm_w, suh_next: full-width vectors (the next layer's input rotation spans the whole hidden size).
+__global__ void __launch_bounds__(1024) norm_rot_push_kernel(const uint16_t* __restrict__ h, int M, int n_own, int d, int col0,
+                                                             const uint16_t* __restrict__ norm_w, float eps, const __half* __restrict__ suh_next,
+                                                             int* status, const __grid_constant__ PushTp tp) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float rinv_sh;
+  __shared__ int ok_sh;
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const unsigned ticket = tp_ticket(tp.epoch, tp.use_index);
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < tp.ranks && ok; ++r) ok = tp_wait_flag(tp.ss_flag + r, ticket, status, 170) ? 1 : 0;
+    float tot = 0.f;
+    if (ok)
+      for (int r = 0; r < tp.ranks; ++r) tot += __ldcg(tp.ss + (size_t)r * tp.rows_cap + row);   // rank order
+    rinv_sh = rsqrtf(tot / (float)d + eps);
+    ok_sh = ok;
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  const float rinv = norm_w != nullptr ? rinv_sh : 1.f;
+  for (int b = warp; b < n_own / 128; b += nw) {
+    const int c = col0 + b * 128 + lane * 4;
+    const uint2 hu = *reinterpret_cast<const uint2*>(h + (size_t)row * d + c);
+    float v[4] = {__uint_as_float(hu.x << 16), __uint_as_float(hu.x & 0xFFFF0000u), __uint_as_float(hu.y << 16), __uint_as_float(hu.y & 0xFFFF0000u)};
+    if (norm_w != nullptr) {
+      const uint2 wu = *reinterpret_cast<const uint2*>(norm_w + c);
+      const float w[4] = {__uint_as_float(wu.x << 16), __uint_as_float(wu.x & 0xFFFF0000u), __uint_as_float(wu.y << 16), __uint_as_float(wu.y & 0xFFFF0000u)};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = c_bf16_to_f(c_f_to_bf16(v[i] * rinv)) * w[i];
+    }
+    const uint2 su = *reinterpret_cast<const uint2*>(suh_next + c);
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+    v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
+    fwht128_warp(v);
+    const __half2 a = __floats2half2_rn(v[0], v[1]), bb = __floats2half2_rn(v[2], v[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
+    for (int r = 0; r < tp.ranks; ++r) *reinterpret_cast<uint2*>(tp.xr[r] + (size_t)row * d + c) = o;   // all-gather by push
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tp_publish_last(tp.local_count, gridDim.x, tp.xr_flag, tp.ranks, tp.rank, ticket);
+}
+
+// Blocks the stream until every flag in flags[0..ranks) has reached the ticket (for host-launched library ops, e.g. a row
+// gather, that read a buffer peers push into).
+__global__ void tp_wait_flags_kernel(const unsigned* flags, int ranks, const unsigned* epoch, unsigned use_index, int* status) {
+  pdl_launch();
+  pdl_wait();
+  const unsigned ticket = tp_ticket(epoch, use_index);
+  for (int r = 0; r < ranks; ++r)
+    if (!tp_wait_flag(flags + r, ticket, status, 180)) return;
+}
+
+}  // namespace rx
+
+using namespace rx;
+
+RX_API int rx_tp_wait_flags(const void* flags, int ranks, const void* epoch, unsigned use_index, int* status, void* stream) {
+  return (int)rx::launch(tp_wait_flags_kernel, dim3(1), dim3(1), 0, (cudaStream_t)stream, (const unsigned*)flags, ranks, (const unsigned*)epoch,
+                         use_index, status);
+}
+
+RX_API int rx_tp_desc_sizes(int* gemm, int* finish, int* push) {
+  *gemm = (int)sizeof(GemmTp); *finish = (int)sizeof(FinishTp); *push = (int)sizeof(PushTp);
+  return 0;
+}
+
+RX_API int rx_tp_bump_epoch(void* epoch, void* stream) {
+  return (int)rx::launch(tp_bump_epoch_kernel, dim3(1), dim3(1), 0, (cudaStream_t)stream, (unsigned*)epoch);
+}
+
+RX_API int rx_tp_finish_rs(const void* part, int S, int M, int n_own, int d, int col0, const void* svh_own, const void* bias_own, void* h,
+                           int* status, const void* desc, void* stream) {
+  if (desc == nullptr || n_own % 128 || n_own / 128 > 64 || M < 1) return (int)cudaErrorInvalidValue;
+  const FinishTp tp = *(const FinishTp*)desc;
+  if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
+  int threads = 32 * (n_own / 128);
+  if (threads > 1024) threads = 1024;
+  return (int)rx::launch(finish_rs_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)stream, (const float*)part, S, M, n_own, d, col0,
+                         (const __half*)svh_own, (const float*)bias_own, (uint16_t*)h, status, tp);
+}
+
+RX_API int rx_tp_norm_rot_push(const void* h, int M, int n_own, int d, int col0, const void* norm_w, float eps, const void* suh_next, int* status,
+                               const void* desc, void* stream) {
+  if (desc == nullptr || n_own % 128 || M < 1) return (int)cudaErrorInvalidValue;
+  const PushTp tp = *(const PushTp*)desc;
+  if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
+  int threads = 32 * (n_own / 128);
+  if (threads > 1024) threads = 1024;
+  return (int)rx::launch(norm_rot_push_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)stream, (const uint16_t*)h, M, n_own, d, col0,
+                         (const uint16_t*)norm_w, eps, (const __half*)suh_next, status, tp);
+}
+
+// ---- CUDA IPC helpers for the symmetric arena (one process per GPU)
+RX_API int rx_ipc_get_handle(void* dev_ptr, void* out64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, dev_ptr);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(out64, &h, sizeof(h));
+  return 0;
+}
+RX_API int rx_ipc_open(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+RX_API int rx_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }

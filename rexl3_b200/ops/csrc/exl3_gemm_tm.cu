@@ -17,6 +17,7 @@
 // the first group also runs the epilogue.  Bounded waits everywhere; no cluster multicast.
 #include <cuda.h>
 #include "exl3_decode.cuh"
+#include "tp.cuh"
 
 namespace rx {
 
@@ -38,7 +39,7 @@ __host__ __device__ inline int tm_smem_bytes(int brows, int ng) { return TM_OP_S
 template <int CB, int NG>
 __global__ void __launch_bounds__(128 + NG * 128, (NG == 2 ? 2 : 1))
 exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, float* __restrict__ part, int rows,
-                    int K, int N, int splits, int brows, int* status) {
+                    int K, int N, int splits, int brows, int* status, const __grid_constant__ GemmTp tp) {
   constexpr int TM_RAW_STAGES = tm_raw_stages(NG);
   pdl_launch();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -112,8 +113,18 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     if (lane == 0) {
       int x = c_begin * TM_KCH;
       const int y = row_tile * brows;
+      int waited_src = -1;
+      const unsigned ticket = (tp.ranks > 1 && tp.in_flag != nullptr) ? tp_ticket(tp.epoch, tp.use_index) : 0u;
       for (int c = 0; c < nchunks; ++c, x += TM_KCH) {
         const int s = c % TM_OP_STAGES;
+        if (tp.ranks > 1 && tp.in_flag != nullptr) {
+          // all-gather -> GEMM: this K chunk was pushed into the local buffer by rank `src`; consume it as soon as it has landed
+          const int src = x / tp.in_cols_per_src;
+          if (src != waited_src) {
+            if (!tp_wait_flag(tp.in_flag + src, ticket, status, 150)) { *abort_flag = 1; break; }
+            waited_src = src;
+          }
+        }
         if (c >= TM_OP_STAGES && !mbar_wait(&b_empty[s], ((c / TM_OP_STAGES) - 1) & 1, abort_flag, status, 111)) break;
         mbar_arrive_expect_tx(&b_full[s], (uint32_t)b_stage);
         tma_load_2d(b_base + s * b_stage, &tmap_x, x, y, &b_full[s]);
@@ -200,7 +211,17 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const bool done = mbar_wait(acc_full, 0, abort_flag, status, 140);
       tc_fence_after();
       if (done && *abort_flag == 0) {
-        float* out = part + ((size_t)split * rows) * N + strip * TM_STRIP + n;
+        float* out;
+        size_t ld;
+        if (tp.ranks > 1 && tp.strips_per_rank > 0) {
+          // GEMM -> reduce-scatter: the tile goes straight into the owning rank's buffer over NVLink (plane [src = this rank][split])
+          const int dest = strip / tp.strips_per_rank;
+          ld = (size_t)tp.out_ld;
+          out = tp.out[dest] + ((size_t)(tp.rank * splits + split) * tp.rows_cap) * ld + (strip % tp.strips_per_rank) * TM_STRIP + n;
+        } else {
+          ld = (size_t)N;
+          out = part + ((size_t)split * rows) * N + strip * TM_STRIP + n;
+        }
         const int row0 = row_tile * brows;
         for (int cb = 0; cb < brows; cb += 16) {
           if (row0 + cb >= rows) break;
@@ -210,9 +231,15 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int row = row0 + cb + i;
-            if (row < rows) out[(size_t)row * N] = __uint_as_float(r[i]);
+            if (row < rows) out[(size_t)row * ld] = __uint_as_float(r[i]);
           }
         }
+      }
+      if (tp.ranks > 1 && tp.strips_per_rank > 0) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        if (dw == 0 && lane == 0 && *abort_flag == 0)
+          tp_publish_last(tp.local_count, gridDim.x * gridDim.y * gridDim.z, tp.out_flag, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
       }
     }
   }
@@ -231,7 +258,7 @@ int make_tmap_trellis(CUtensorMap* out, const void* base, uint64_t kt_rows, uint
 
 template <int CB, int NG>
 static int launch_tm(const CUtensorMap& tm, const CUtensorMap& tw, float* part, int rows, int K, int N, int splits, int brows, int row_tiles,
-                     int* status, cudaStream_t st) {
+                     int* status, cudaStream_t st, const GemmTp& tp) {
   int smem = tm_smem_bytes(brows, NG) + 1024;
   if (NG == 2 && smem < 80 * 1024) smem = 80 * 1024;   // at most two CTAs per SM: each allocates 256 TMEM columns
   if (smem > 232448) return (int)cudaErrorInvalidValue;
@@ -243,7 +270,7 @@ static int launch_tm(const CUtensorMap& tm, const CUtensorMap& tw, float* part, 
     configured = true;
   }
   dim3 grid(N / TM_STRIP, splits, row_tiles);
-  rx::launch(kern, dim3(grid), dim3(128 + NG * 128), smem, st, tm, tw, part, rows, K, N, splits, brows, status);
+  rx::launch(kern, dim3(grid), dim3(128 + NG * 128), smem, st, tm, tw, part, rows, K, N, splits, brows, status, tp);
   return (int)cudaGetLastError();
 }
 
@@ -253,9 +280,8 @@ using namespace rx;
 
 extern "C" int rx_exl3_tile_rows(int rows);
 
-// 4.0 bpw only (twice == 8), codebooks 3inst / mcg / mul1.  Same arguments as rx_exl3_gemm.
-RX_API int rx_exl3_gemm_b4(const void* xr, int rows, int K, const void* trellis, int N, int codebook, void* part, int splits, int* status,
-                           void* stream) {
+static int gemm_b4(const void* xr, int rows, int K, const void* trellis, int N, int codebook, void* part, int splits, int* status, void* stream,
+                   const GemmTp& tp) {
   if (rows <= 0 || K % 128 != 0 || N % 128 != 0 || splits < 1 || splits > K / TM_KCH) return (int)cudaErrorInvalidValue;
   if ((((uintptr_t)xr) & 15) != 0 || (((uintptr_t)trellis) & 15) != 0) return (int)cudaErrorMisalignedAddress;
   const int brows = rx_exl3_tile_rows(rows);
@@ -269,8 +295,8 @@ RX_API int rx_exl3_gemm_b4(const void* xr, int rows, int K, const void* trellis,
   cudaStream_t st = (cudaStream_t)stream;
   float* p = (float*)part;
   const bool big = brows > 64;   // one CTA per SM with 16 decode warps, else two CTAs per SM with 8 each
-#define RX_TM(CBV) (big ? launch_tm<CBV, 4>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st) \
-                        : launch_tm<CBV, 2>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st))
+#define RX_TM(CBV) (big ? launch_tm<CBV, 4>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st, tp) \
+                        : launch_tm<CBV, 2>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st, tp))
   switch (codebook) {
     case CB_3INST: return RX_TM(CB_3INST);
     case CB_MCG: return RX_TM(CB_MCG);
@@ -278,4 +304,25 @@ RX_API int rx_exl3_gemm_b4(const void* xr, int rows, int K, const void* trellis,
     default: return (int)cudaErrorInvalidValue;
   }
 #undef RX_TM
+}
+
+// 4.0 bpw only (twice == 8), codebooks 3inst / mcg / mul1.  Same arguments as rx_exl3_gemm.
+RX_API int rx_exl3_gemm_b4(const void* xr, int rows, int K, const void* trellis, int N, int codebook, void* part, int splits, int* status,
+                           void* stream) {
+  GemmTp tp = {};
+  tp.ranks = 1;
+  return gemm_b4(xr, rows, K, trellis, N, codebook, part, splits, status, stream, tp);
+}
+
+// Tensor-parallel form.  `tp_desc` points at a HOST copy of GemmTp (filled by the comm layer: peer buffers, flags, ticket source).
+// strips_per_rank > 0 makes the epilogue a reduce-scatter (tiles pushed to their owner); in_flag != nullptr makes the activation
+// loads wait for the all-gathered input to land, source rank by source rank.
+RX_API int rx_exl3_gemm_b4_tp(const void* xr, int rows, int K, const void* trellis, int N, int codebook, void* part, int splits, int* status,
+                              void* stream, const void* tp_desc) {
+  if (tp_desc == nullptr) return (int)cudaErrorInvalidValue;
+  const GemmTp tp = *(const GemmTp*)tp_desc;
+  if (tp.ranks < 1 || tp.ranks > TP_MAX) return (int)cudaErrorInvalidValue;
+  if (tp.ranks > 1 && tp.strips_per_rank > 0 && (N / TM_STRIP) != tp.strips_per_rank * tp.ranks) return (int)cudaErrorInvalidValue;
+  if (tp.ranks > 1 && tp.in_flag != nullptr && (tp.in_cols_per_src % TM_KCH != 0 || tp.in_cols_per_src * tp.ranks != K)) return (int)cudaErrorInvalidValue;
+  return gemm_b4(xr, rows, K, trellis, N, codebook, part, splits, status, stream, tp);
 }

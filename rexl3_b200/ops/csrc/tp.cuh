@@ -1,0 +1,72 @@
+// Tensor-parallel plumbing shared by the fused compute+collective kernels: peer tables, tickets, bounded peer waits and
+// the "last CTA publishes" signal.
+//
+// Every rank owns one symmetric arena (same layout on every GPU, mapped into every peer through CUDA IPC).  Data moves by
+// plain vectorised stores into the CONSUMER's arena (push model), so every TMA / tensor-core read is from local memory.
+// A producer kernel finishes with: each CTA fences to system scope and bumps a local counter; the CTA that sees the last
+// count writes ticket = epoch * 4096 + use_index into flag[src] on every destination.  A consumer spins (bounded, 2 s)
+// on its LOCAL flag word until it reaches the ticket.  The epoch lives in device memory and is bumped by a one-thread
+// kernel at the start of every forward, so captured CUDA graphs replay with fresh tickets.
+// Counterpart in the reference: the flag/sequence protocol of its RDMA transport (crates/cuda/csrc/roce_dev.cuh:118-260);
+// NVLink peer stores replace the proxy thread and the RDMA writes.
+#pragma once
+#include "common.cuh"
+
+namespace rx {
+
+constexpr int TP_MAX = 8;
+
+struct GemmTp {
+  int ranks;                    // 1 = single GPU, nothing below is read
+  int rank;
+  int strips_per_rank;          // > 0: reduce-scatter epilogue, strip s goes to rank s / strips_per_rank
+  int out_ld;                   // leading dimension of the destination buffers (owned columns)
+  int rows_cap;                 // rows each [src][split] plane of a destination buffer can hold
+  float* out[TP_MAX];           // destination buffers, one per rank: f32 [ranks][splits][rows_cap][out_ld]
+  unsigned* out_flag[TP_MAX];   // per destination: flags [ranks] of this site; flag[src] = ticket when src's tiles have landed
+  unsigned* local_count;        // this rank's CTA counter for the site
+  const unsigned* in_flag;      // local flags [ranks] of the all-gathered input (nullptr: input is local)
+  int in_cols_per_src;          // K columns each source rank contributes to the gathered input
+  const unsigned* epoch;
+  unsigned use_index;
+};
+
+__device__ __forceinline__ unsigned tp_ticket(const unsigned* epoch, unsigned use_index) { return *epoch * 4096u + use_index; }
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait for a local flag word to reach `ticket` (tickets only grow).  Returns false and records the site on timeout.
+__device__ __forceinline__ bool tp_wait_flag(const unsigned* flag, unsigned ticket, int* status, int site) {
+  if ((int)(ld_acquire_sys(flag) - ticket) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if ((int)(ld_acquire_sys(flag) - ticket) >= 0) return true;
+    if (globaltimer_ns() - t0 > RX_WAIT_LIMIT_NS) {
+      set_status(status, ST_PEER_TIMEOUT, site, (int)ticket);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+// Called by ONE thread of every CTA after the CTA's peer stores are complete and fenced: the last CTA of the grid resets the
+// counter and publishes the ticket to flag[src = rank] on every destination rank.
+__device__ __forceinline__ void tp_publish_last(unsigned* local_count, unsigned total_ctas, unsigned* const* flags, int ranks, int rank,
+                                                unsigned ticket) {
+  __threadfence_system();
+  const unsigned old = atomicAdd(local_count, 1u);
+  if (old == total_ctas - 1) {
+    atomicExch(local_count, 0u);
+    __threadfence_system();
+    for (int r = 0; r < ranks; ++r) st_release_sys(flags[r] + rank, ticket);
+  }
+}
+
+}  // namespace rx

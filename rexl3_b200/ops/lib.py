@@ -43,6 +43,14 @@ def _declare(lib):
         "rx_exl3_tile_rows": (c_int, [c_int]),
         "rx_exl3_gemm": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_int, c_void, c_int, c_void, c_void]),
         "rx_exl3_gemm_b4": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_void, c_int, c_void, c_void]),
+        "rx_exl3_gemm_b4_tp": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_void, c_int, c_void, c_void, c_void]),
+        "rx_tp_bump_epoch": (c_int, [c_void, c_void]),
+        "rx_tp_finish_rs": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
+        "rx_tp_norm_rot_push": (c_int, [c_void, c_int, c_int, c_int, c_int, c_void, c_f, c_void, c_void, c_void, c_void]),
+        "rx_tp_wait_flags": (c_int, [c_void, c_int, c_void, ctypes.c_uint, c_void, c_void]),
+        "rx_ipc_get_handle": (c_int, [c_void, c_void]),
+        "rx_ipc_open": (c_int, [c_void, c_void]),
+        "rx_ipc_close": (c_int, [c_void]),
         "rx_exl3_unpack": (c_int, [c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
         "rx_set_pdl": (c_int, [c_int]),
         "rx_embed": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void]),

@@ -1,0 +1,210 @@
+"""Symmetric peer memory for tensor parallelism: one arena per rank with the same layout everywhere, mapped into every
+peer (CUDA IPC between processes, plain pointers between shards of one process), plus the descriptor structs the fused
+kernels take.
+
+Two groups implement the same interface:
+  * ``IpcGroup``      - one process per GPU (torchrun); arenas exchanged as cudaIpcMemHandles over torch.distributed.
+  * ``LoopbackGroup`` - R shards in ONE process on ONE GPU.  Kernels that wait on peers cannot run concurrently on one GPU,
+    so the caller steps the shards phase by phase; every flag a kernel waits for has then already been written.  This is
+    how the multi-rank protocol and numerics are tested without R GPUs (the reference's LoopbackComm plays the same role,
+    crates/model/src/families/nemotron_h_omni/tp_comm.rs:433-830).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import lib as _lib
+
+TP_MAX = 8
+c_u32p = ctypes.c_void_p
+
+
+class GemmTp(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("strips_per_rank", ctypes.c_int), ("out_ld", ctypes.c_int),
+                ("rows_cap", ctypes.c_int), ("out", ctypes.c_void_p * TP_MAX), ("out_flag", ctypes.c_void_p * TP_MAX),
+                ("local_count", ctypes.c_void_p), ("in_flag", ctypes.c_void_p), ("in_cols_per_src", ctypes.c_int),
+                ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint)]
+
+
+class FinishTp(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("in_flag", ctypes.c_void_p), ("ss", ctypes.c_void_p * TP_MAX),
+                ("ss_flag", ctypes.c_void_p * TP_MAX), ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p),
+                ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
+
+
+class PushTp(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("ss", ctypes.c_void_p), ("ss_flag", ctypes.c_void_p),
+                ("xr", ctypes.c_void_p * TP_MAX), ("xr_flag", ctypes.c_void_p * TP_MAX), ("local_count", ctypes.c_void_p),
+                ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
+
+
+def check_abi() -> None:
+    L = _lib.load()
+    a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    L.rx_tp_desc_sizes(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+    got = (ctypes.sizeof(GemmTp), ctypes.sizeof(FinishTp), ctypes.sizeof(PushTp))
+    if got != (a.value, b.value, c.value):
+        raise _lib.KernelError(f"TP descriptor layout mismatch: python {got}, library {(a.value, b.value, c.value)}")
+
+
+@dataclass
+class ArenaLayout:
+    """Byte offsets inside a rank's arena (identical on every rank)."""
+    ranks: int
+    rows_cap: int          # rows of the widest forward (prefill chunk)
+    plane_elems: int       # max over row classes of splits * rows * n_own  (one source rank's planes of one site)
+    d: int
+    n_own: int
+
+    def __post_init__(self):
+        R = self.ranks
+        off = 0
+
+        def take(nbytes):
+            nonlocal off
+            o = off
+            off = (off + nbytes + 255) // 256 * 256
+            return o
+        self.epoch = take(4)
+        self.count = take(4 * 8)                       # local CTA counters: [0,1] part sites, [2,3] ss parities, [4,5] xr parities
+        self.part_flag = take(4 * 2 * R)               # [site][src]
+        self.ss_flag = take(4 * 2 * R)                 # [parity][src]
+        self.xr_flag = take(4 * 2 * R)                 # [parity][src]
+        self.ss = take(4 * 2 * R * self.rows_cap)      # [parity][src][row]
+        self.part = take(4 * 2 * R * self.plane_elems)  # [site][src][plane]
+        self.xr = take(2 * 2 * self.rows_cap * self.d)  # [parity][row][d] fp16
+        self.total = off
+
+
+class _GroupBase:
+    ranks: int
+    layout: ArenaLayout
+
+    def base(self, viewer: int, owner: int) -> int:
+        """Device address of `owner`'s arena as seen from rank `viewer`."""
+        raise NotImplementedError
+
+    def local(self, rank: int) -> torch.Tensor:
+        raise NotImplementedError
+
+    # ---- descriptor builders (rank = the rank that will launch the kernel)
+    def gemm_rs(self, rank: int, site: int, use_index: int, splits: int, rows: int) -> GemmTp:
+        L, R = self.layout, self.ranks
+        t = GemmTp()
+        t.ranks, t.rank = R, rank
+        t.strips_per_rank = L.n_own // 128
+        t.out_ld, t.rows_cap = L.n_own, rows
+        assert splits * rows * L.n_own <= L.plane_elems, "reduce-scatter planes exceed the arena"
+        for r in range(R):
+            b = self.base(rank, r)
+            t.out[r] = b + L.part + 4 * site * R * L.plane_elems
+            t.out_flag[r] = b + L.part_flag + 4 * site * R
+        me = self.base(rank, rank)
+        t.local_count = me + L.count + 4 * site
+        t.in_flag, t.in_cols_per_src = None, 0
+        t.epoch, t.use_index = me + L.epoch, use_index
+        return t
+
+    def gemm_ag(self, rank: int, parity: int, use_index: int, k: int) -> GemmTp:
+        L, R = self.layout, self.ranks
+        t = GemmTp()
+        t.ranks, t.rank, t.strips_per_rank = R, rank, 0
+        me = self.base(rank, rank)
+        t.in_flag, t.in_cols_per_src = me + L.xr_flag + 4 * parity * R, k // R
+        t.epoch, t.use_index = me + L.epoch, use_index
+        return t
+
+    def finish(self, rank: int, site: int, parity: int, use_index: int) -> FinishTp:
+        L, R = self.layout, self.ranks
+        t = FinishTp()
+        t.ranks, t.rank, t.rows_cap = R, rank, L.rows_cap
+        me = self.base(rank, rank)
+        t.in_flag = me + L.part_flag + 4 * site * R
+        for r in range(R):
+            b = self.base(rank, r)
+            t.ss[r] = b + L.ss + 4 * parity * R * L.rows_cap
+            t.ss_flag[r] = b + L.ss_flag + 4 * parity * R
+        t.local_count = me + L.count + 4 * (2 + parity)
+        t.epoch, t.use_index = me + L.epoch, use_index
+        return t
+
+    def push(self, rank: int, parity: int, use_index: int) -> PushTp:
+        L, R = self.layout, self.ranks
+        t = PushTp()
+        t.ranks, t.rank, t.rows_cap = R, rank, L.rows_cap
+        me = self.base(rank, rank)
+        t.ss = me + L.ss + 4 * parity * R * L.rows_cap
+        t.ss_flag = me + L.ss_flag + 4 * parity * R
+        for r in range(R):
+            b = self.base(rank, r)
+            t.xr[r] = b + L.xr + 2 * parity * L.rows_cap * L.d
+            t.xr_flag[r] = b + L.xr_flag + 4 * parity * R
+        t.local_count = me + L.count + 4 * (4 + parity)
+        t.epoch, t.use_index = me + L.epoch, use_index
+        return t
+
+    def part_ptr(self, rank: int, site: int) -> int:
+        return self.base(rank, rank) + self.layout.part + 4 * site * self.ranks * self.layout.plane_elems
+
+    def xr_view(self, rank: int, parity: int, rows: int) -> torch.Tensor:
+        L = self.layout
+        a = self.local(rank)
+        off = L.xr + 2 * parity * L.rows_cap * L.d
+        return a[off:off + 2 * rows * L.d].view(torch.float16).view(rows, L.d)
+
+    def epoch_ptr(self, rank: int) -> int:
+        return self.base(rank, rank) + self.layout.epoch
+
+
+class LoopbackGroup(_GroupBase):
+    def __init__(self, layout: ArenaLayout, device="cuda"):
+        self.layout, self.ranks = layout, layout.ranks
+        self.arenas = [torch.zeros(layout.total, dtype=torch.uint8, device=device) for _ in range(self.ranks)]
+
+    def base(self, viewer, owner):
+        return self.arenas[owner].data_ptr()
+
+    def local(self, rank):
+        return self.arenas[rank]
+
+
+class IpcGroup(_GroupBase):
+    """One process per GPU.  Needs torch.distributed initialised (any backend) for the handle exchange."""
+
+    def __init__(self, layout: ArenaLayout, rank: int, device):
+        import torch.distributed as dist
+        self.layout, self.ranks, self.rank = layout, layout.ranks, rank
+        L = _lib.load()
+        self.arena = torch.zeros(layout.total, dtype=torch.uint8, device=device)
+        torch.cuda.synchronize()
+        h = (ctypes.c_ubyte * 64)()
+        _lib.check(L.rx_ipc_get_handle(ctypes.c_void_p(self.arena.data_ptr()), h), "rx_ipc_get_handle")
+        handles = [None] * self.ranks
+        dist.all_gather_object(handles, bytes(h))
+        self.bases = []
+        for r, hb in enumerate(handles):
+            if r == rank:
+                self.bases.append(self.arena.data_ptr())
+                continue
+            out = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(hb)
+            _lib.check(L.rx_ipc_open(buf, ctypes.byref(out)), "rx_ipc_open")
+            self.bases.append(out.value)
+        dist.barrier()
+
+    def base(self, viewer, owner):
+        assert viewer == self.rank
+        return self.bases[owner]
+
+    def local(self, rank):
+        assert rank == self.rank
+        return self.arena
+
+    def close(self):
+        L = _lib.load()
+        for r, b in enumerate(self.bases):
+            if r != self.rank:
+                L.rx_ipc_close(ctypes.c_void_p(b))
