@@ -103,6 +103,11 @@ class DenseTPShard:
         self.xr0 = torch.empty(max_rows * cfg.d_model, dtype=torch.float16, device=device)      # layer-0 input (computed locally)
         self.attn_out = torch.empty(max_rows, self.nq * hd, dtype=torch.bfloat16, device=device)
         self.logits = torch.empty(min(max_rows, 256), self.lm_head.N, dtype=torch.float32, device=device)
+        self.topk_scratch = K.topk_scratch(min(max_rows, 256), self.lm_head.N, 64, device)
+        self.loc_ids = torch.empty(256 * 64, dtype=torch.int32, device=device)
+        self.loc_vals = torch.empty(256 * 64, dtype=torch.float32, device=device)
+        self.cand_ids = torch.empty(256 * 64, dtype=torch.int32, device=device)      # merged result (leader)
+        self.cand_vals = torch.empty(256 * 64, dtype=torch.float32, device=device)
         self.attn_scratch = K.attn_decode_scratch(min(max_rows, 256), self.nq, hd, max_blocks_per_seq * PAGE, device)
         self.max_ctx_alloc = max_blocks_per_seq * PAGE
 
@@ -169,7 +174,8 @@ class DenseTPShard:
                                         self.status.data_ptr(), _lib.stream_ptr(), ctypes.byref(desc)), "rx_exl3_gemm_b4_tp")
         _lib.count()
 
-    def phases(self, ids, positions, slots, row_seq, ctx_len, block_table, prefill=None, max_ctx=None, want_logits=True, logit_rows=None):
+    def phases(self, ids, positions, slots, row_seq, ctx_len, block_table, prefill=None, max_ctx=None, want_logits=True, logit_rows=None,
+               cand_count=None, leader=0):
         """Generator of closures, one per phase; calling them in order runs this rank's forward.  Between two phases every
         cross-rank dependency points backwards, so a loopback group may interleave the ranks phase by phase."""
         cfg, g, r, R = self.cfg, self.g, self.rank, self.R
@@ -274,6 +280,33 @@ class DenseTPShard:
             self.last_logits = out
             return out
         yield p_head
+
+        if want_logits and cand_count is not None:
+            Rw = M if logit_rows is None else int(logit_rows.shape[0])
+            u_c = 2 * nl + 1
+
+            def p_cand_push():
+                out = self.last_logits
+                if self.vocab_hi > cfg.vocab:                      # padded vocabulary columns never become candidates
+                    out[:, max(0, cfg.vocab - self.vocab_lo):] = float("-inf")
+                K.topk(out, cand_count, self.topk_scratch, self.loc_ids[:Rw * cand_count].view(Rw, cand_count),
+                       self.loc_vals[:Rw * cand_count].view(Rw, cand_count))
+                _lib.check(Lib.rx_tp_cand_push(self.loc_ids.data_ptr(), self.loc_vals.data_ptr(), Rw, cand_count,
+                                               ctypes.byref(g.cand(r, leader, u_c, self.vocab_lo)), _lib.stream_ptr()), "rx_tp_cand_push")
+                _lib.count()
+            yield p_cand_push
+
+            def p_cand_merge():
+                if r != leader:
+                    return None
+                from ..parallel.symm import CAND_ROWS
+                La, b = g.layout, g.base(r, r)
+                _lib.check(Lib.rx_tp_cand_merge(b + La.cand_ids, b + La.cand_vals, b + La.cand_flag, R, Rw, cand_count, CAND_ROWS, g.epoch_ptr(r), u_c,
+                                                self.cand_ids.data_ptr(), self.cand_vals.data_ptr(), self.status.data_ptr(), _lib.stream_ptr()),
+                           "rx_tp_cand_merge")
+                _lib.count()
+                return self.cand_ids[:Rw * cand_count].view(Rw, cand_count), self.cand_vals[:Rw * cand_count].view(Rw, cand_count)
+            yield p_cand_merge
 
     def forward(self, *a, **kw):
         out = None

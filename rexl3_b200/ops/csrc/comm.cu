@@ -174,6 +174,76 @@ __global__ void tp_wait_flags_kernel(const unsigned* flags, int ranks, const uns
     if (!tp_wait_flag(flags + r, ticket, status, 180)) return;
 }
 
+
+// ---- candidate gather: every rank pushes its local top-`count` (ids offset to global vocabulary ids) to the leader, which merges the
+// R sorted lists into the global top-`count` in (value desc, id asc) order.  Full logits never cross NVLink.
+struct CandTp {
+  int ranks, rank;
+  unsigned* dst_ids;             // leader's buffer u32 [ranks][rows_cap * 64], as mapped into this rank
+  float* dst_vals;               // leader's buffer f32 [ranks][rows_cap * 64]
+  unsigned* dst_flag;            // leader's flags [ranks]
+  const unsigned* epoch;
+  unsigned use_index;
+  int rows_cap;
+  int id_offset;                 // first vocabulary id of this rank's lm_head shard
+};
+
+__global__ void __launch_bounds__(1024) cand_push_kernel(const int* __restrict__ ids, const float* __restrict__ vals, int n,
+                                                         const __grid_constant__ CandTp tp) {
+  pdl_launch();
+  pdl_wait();
+  const size_t base = (size_t)tp.rank * tp.rows_cap * 64;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    tp.dst_ids[base + i] = (unsigned)(ids[i] + tp.id_offset);
+    tp.dst_vals[base + i] = vals[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_sys(tp.dst_flag + tp.rank, tp_ticket(tp.epoch, tp.use_index));
+}
+
+// One CTA per row, one thread per candidate (ranks * count <= 512).  The output slot of a candidate is the number of candidates
+// that precede it; ids are distinct, so the order is total.
+__global__ void __launch_bounds__(512) cand_merge_kernel(const unsigned* __restrict__ in_ids, const float* __restrict__ in_vals,
+                                                         const unsigned* __restrict__ flags, int ranks, int count, int rows_cap,
+                                                         const unsigned* epoch, unsigned use_index, int* __restrict__ out_ids,
+                                                         float* __restrict__ out_vals, int* status) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sv[512];
+  __shared__ unsigned si[512];
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) {
+    const unsigned ticket = tp_ticket(epoch, use_index);
+    int ok = 1;
+    for (int r = 0; r < ranks && ok; ++r) ok = tp_wait_flag(flags + r, ticket, status, 190) ? 1 : 0;
+    ok_sh = ok;
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  const int row = blockIdx.x, n = ranks * count, t = threadIdx.x;
+  float v = 0.f;
+  unsigned id = 0;
+  if (t < n) {
+    const size_t at = (size_t)(t / count) * rows_cap * 64 + (size_t)row * count + (t % count);
+    v = in_vals[at];
+    id = in_ids[at];
+    sv[t] = v;
+    si[t] = id;
+  }
+  __syncthreads();
+  if (t >= n) return;
+  int before = 0;
+  for (int j = 0; j < n; ++j) {
+    const float w = sv[j];
+    before += (w > v || (w == v && si[j] < id)) ? 1 : 0;
+  }
+  if (before < count) {
+    out_ids[(size_t)row * count + before] = (int)id;
+    out_vals[(size_t)row * count + before] = v;
+  }
+}
+
 }  // namespace rx
 
 using namespace rx;
@@ -213,6 +283,30 @@ RX_API int rx_tp_norm_rot_push(const void* h, int M, int n_own, int d, int col0,
   return (int)rx::launch(norm_rot_push_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)stream, (const uint16_t*)h, M, n_own, d, col0,
                          (const uint16_t*)norm_w, eps, (const __half*)suh_next, status, tp);
 }
+
+RX_API int rx_tp_cand_desc_size() { return (int)sizeof(CandTp); }
+
+RX_API int rx_tp_cand_push(const void* ids, const void* vals, int rows, int count, const void* desc, void* stream) {
+  if (desc == nullptr || rows < 1 || count < 1 || count > 64) return (int)cudaErrorInvalidValue;
+  const CandTp tp = *(const CandTp*)desc;
+  if (tp.ranks < 1 || tp.ranks > TP_MAX || rows > tp.rows_cap) return (int)cudaErrorInvalidValue;
+  return (int)rx::launch(cand_push_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, (const int*)ids, (const float*)vals, rows * count, tp);
+}
+
+RX_API int rx_tp_cand_merge(const void* in_ids, const void* in_vals, const void* flags, int ranks, int rows, int count, int rows_cap,
+                            const void* epoch, unsigned use_index, void* out_ids, void* out_vals, int* status, void* stream) {
+  if (ranks < 1 || ranks > TP_MAX || rows < 1 || rows > rows_cap || count < 1 || count > 64) return (int)cudaErrorInvalidValue;
+  return (int)rx::launch(cand_merge_kernel, dim3(rows), dim3(512), 0, (cudaStream_t)stream, (const unsigned*)in_ids, (const float*)in_vals,
+                         (const unsigned*)flags, ranks, count, rows_cap, (const unsigned*)epoch, use_index, (int*)out_ids, (float*)out_vals, status);
+}
+
+// ---- device memory owned by the library: an arena that is its own allocation, so that its IPC handle maps exactly it
+RX_API int rx_dev_alloc(long long bytes, void** out) {
+  cudaError_t e = cudaMalloc(out, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemset(*out, 0, (size_t)bytes);
+}
+RX_API int rx_dev_free(void* p) { return (int)cudaFree(p); }
 
 // ---- CUDA IPC helpers for the symmetric arena (one process per GPU)
 RX_API int rx_ipc_get_handle(void* dev_ptr, void* out64) {

@@ -51,6 +51,11 @@ def _declare(lib):
         "rx_ipc_get_handle": (c_int, [c_void, c_void]),
         "rx_ipc_open": (c_int, [c_void, c_void]),
         "rx_ipc_close": (c_int, [c_void]),
+        "rx_tp_cand_desc_size": (c_int, []),
+        "rx_tp_cand_push": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void]),
+        "rx_tp_cand_merge": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, ctypes.c_uint, c_void, c_void, c_void, c_void]),
+        "rx_dev_alloc": (c_int, [c_ll, ctypes.POINTER(ctypes.c_void_p)]),
+        "rx_dev_free": (c_int, [c_void]),
         "rx_exl3_unpack": (c_int, [c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
         "rx_set_pdl": (c_int, [c_int]),
         "rx_embed": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void]),

@@ -41,6 +41,15 @@ class PushTp(ctypes.Structure):
                 ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
 
 
+class CandTp(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("dst_ids", ctypes.c_void_p), ("dst_vals", ctypes.c_void_p),
+                ("dst_flag", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int),
+                ("id_offset", ctypes.c_int)]
+
+
+CAND_ROWS = 256      # rows of candidates one forward can return (the logits rows of a window)
+
+
 def check_abi() -> None:
     L = _lib.load()
     a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
@@ -48,6 +57,8 @@ def check_abi() -> None:
     got = (ctypes.sizeof(GemmTp), ctypes.sizeof(FinishTp), ctypes.sizeof(PushTp))
     if got != (a.value, b.value, c.value):
         raise _lib.KernelError(f"TP descriptor layout mismatch: python {got}, library {(a.value, b.value, c.value)}")
+    if ctypes.sizeof(CandTp) != L.rx_tp_cand_desc_size():
+        raise _lib.KernelError("TP candidate descriptor layout mismatch")
 
 
 @dataclass
@@ -76,6 +87,9 @@ class ArenaLayout:
         self.ss = take(4 * 2 * R * self.rows_cap)      # [parity][src][row]
         self.part = take(4 * 2 * R * self.plane_elems)  # [site][src][plane]
         self.xr = take(2 * 2 * self.rows_cap * self.d)  # [parity][row][d] fp16
+        self.cand_flag = take(4 * R)                   # [src]                      (read on the leader only)
+        self.cand_ids = take(4 * R * CAND_ROWS * 64)   # [src][row * count + j] u32
+        self.cand_vals = take(4 * R * CAND_ROWS * 64)
         self.total = off
 
 
@@ -146,6 +160,15 @@ class _GroupBase:
         t.epoch, t.use_index = me + L.epoch, use_index
         return t
 
+    def cand(self, rank: int, leader: int, use_index: int, id_offset: int) -> CandTp:
+        L = self.layout
+        t = CandTp()
+        t.ranks, t.rank, t.rows_cap, t.id_offset = self.ranks, rank, CAND_ROWS, id_offset
+        b = self.base(rank, leader)
+        t.dst_ids, t.dst_vals, t.dst_flag = b + L.cand_ids, b + L.cand_vals, b + L.cand_flag
+        t.epoch, t.use_index = self.base(rank, rank) + L.epoch, use_index
+        return t
+
     def part_ptr(self, rank: int, site: int) -> int:
         return self.base(rank, rank) + self.layout.part + 4 * site * self.ranks * self.layout.plane_elems
 
@@ -171,19 +194,33 @@ class LoopbackGroup(_GroupBase):
         return self.arenas[rank]
 
 
-class IpcGroup(_GroupBase):
-    """One process per GPU.  Needs torch.distributed initialised (any backend) for the handle exchange."""
+class _RawDeviceBuffer:
+    """A cudaMalloc'ed range exposed to torch through the CUDA array interface (zero copy)."""
 
-    def __init__(self, layout: ArenaLayout, rank: int, device):
+    def __init__(self, ptr: int, nbytes: int):
+        self.ptr = ptr
+        self.__cuda_array_interface__ = dict(shape=(nbytes,), typestr="|u1", data=(ptr, False), version=2)
+
+
+class IpcGroup(_GroupBase):
+    """One process per GPU.  Needs torch.distributed initialised (any backend) for the handle exchange.  The arena is its own
+    cudaMalloc allocation (not a slice of torch's caching allocator), so the IPC handle maps exactly the arena."""
+
+    def __init__(self, layout: ArenaLayout, rank: int, device, group=None):
         import torch.distributed as dist
         self.layout, self.ranks, self.rank = layout, layout.ranks, rank
         L = _lib.load()
-        self.arena = torch.zeros(layout.total, dtype=torch.uint8, device=device)
-        torch.cuda.synchronize()
+        with torch.cuda.device(device):
+            p = ctypes.c_void_p()
+            _lib.check(L.rx_dev_alloc(layout.total, ctypes.byref(p)), "rx_dev_alloc")
+            self._raw = _RawDeviceBuffer(p.value, layout.total)
+            self.arena = torch.as_tensor(self._raw, device=device)
+            assert self.arena.data_ptr() == p.value and self.arena.numel() == layout.total
+            torch.cuda.synchronize()
         h = (ctypes.c_ubyte * 64)()
         _lib.check(L.rx_ipc_get_handle(ctypes.c_void_p(self.arena.data_ptr()), h), "rx_ipc_get_handle")
         handles = [None] * self.ranks
-        dist.all_gather_object(handles, bytes(h))
+        dist.all_gather_object(handles, bytes(h), group=group)
         self.bases = []
         for r, hb in enumerate(handles):
             if r == rank:
@@ -193,7 +230,7 @@ class IpcGroup(_GroupBase):
             buf = (ctypes.c_ubyte * 64).from_buffer_copy(hb)
             _lib.check(L.rx_ipc_open(buf, ctypes.byref(out)), "rx_ipc_open")
             self.bases.append(out.value)
-        dist.barrier()
+        dist.barrier(group=group)
 
     def base(self, viewer, owner):
         assert viewer == self.rank
@@ -208,3 +245,6 @@ class IpcGroup(_GroupBase):
         for r, b in enumerate(self.bases):
             if r != self.rank:
                 L.rx_ipc_close(ctypes.c_void_p(b))
+        self.bases = []
+        self.arena = None
+        L.rx_dev_free(ctypes.c_void_p(self._raw.ptr))

@@ -46,6 +46,13 @@ def test_tp_loopback_matches_single_gpu_and_reference(ranks):
         for s in shards:
             K = s.status.tolist()
             assert K[0] == 0, K
+        if "cand_count" in kw:        # the last phase returned the merged candidates on the leader; logits are kept per shard
+            full = torch.cat([s.last_logits for s in shards], dim=1)[:, :cfg.vocab]
+            ids, vals = outs[0]
+            tv, ti = torch.sort(full, dim=1, descending=True, stable=True)
+            n = kw["cand_count"]
+            assert torch.equal(vals, tv[:, :n]) and torch.equal(ids.long(), ti[:, :n])
+            return full
         return torch.cat([o[:, :] for o in outs], dim=1)[:, :cfg.vocab]
 
     got = run_tp(args, prefill=pf, logit_rows=lr)
@@ -59,7 +66,7 @@ def test_tp_loopback_matches_single_gpu_and_reference(ranks):
     for step in range(2):
         p = T + step
         a2 = (_i32([t0]), _i32([p]), _i32([int(bt[0, p // 64]) * 64 + p % 64]), _i32([0]), _i32([p + 1]), bt)
-        got = run_tp(a2, max_ctx=256)
+        got = run_tp(a2, max_ctx=256, cand_count=8 if step == 0 else 64)
         w0 = ref.forward_seq(0, [t0], p)[0]
         assert (got[0] - w0).abs().max().item() < 0.05 * scale
         t0 = int(w0.argmax())
