@@ -39,6 +39,7 @@ class DenseGpuBackend(Backend):
         self.h_bt = torch.zeros(self.max_slots, model.max_blocks, dtype=torch.int32).pin_memory()
         self.d_bt = torch.zeros(self.max_slots, model.max_blocks, dtype=torch.int32, device=dev)
         self.bt_dirty = True
+        self.bt_dirty_slots = set(range(self.max_slots))
         self.h_pf = torch.zeros(4, self.max_slots, dtype=torch.int32).pin_memory()
         self.d_pf = torch.zeros(4, self.max_slots, dtype=torch.int32, device=dev)
         self.h_cand_ids = torch.zeros(256, 64, dtype=torch.int32).pin_memory()
@@ -67,12 +68,14 @@ class DenseGpuBackend(Backend):
         self.pages[slot].extend(got)
         self.h_bt[slot, base:base + need] = torch.tensor(got, dtype=torch.int32)
         self.bt_dirty = True
+        self.bt_dirty_slots.add(slot)
 
     def _sync_bt(self) -> None:
         if self.bt_dirty:
             self.d_bt.copy_(self.h_bt, non_blocking=True)
             self.h2d_bytes += self.h_bt.numel() * 4
             self.bt_dirty = False
+            self.bt_dirty_slots.clear()
 
     def _fill_rows(self, specs) -> int:
         """specs: list of (slot, first_position, tokens).  Fills the pinned staging rows; returns M."""
@@ -116,22 +119,12 @@ class DenseGpuBackend(Backend):
             q0 += len(toks)
             if last:
                 last_rows.append(q0 - 1)
-        self._upload_rows(M)
-        self._sync_bt()
-        self.d_pf[:, :n].copy_(self.h_pf[:, :n], non_blocking=True)
-        self.h2d_bytes += 4 * n * 4
-        d = self.d_rows
-        pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=n,
-                  max_qlen=max(len(t) for _, _, t, _ in items))
-        lr = torch.tensor(last_rows, dtype=torch.long, device=m.device) if last_rows else None
-        logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr,
-                                want_logits=bool(last_rows))
+        rows = self._run_prefill(M, n, max(len(t) for _, _, t, _ in items), last_rows, candidates)
         for slot, start, toks, _ in items:
             self.len[slot] = start + len(toks)
             self.pending[slot] = 0
         outs = [None] * n
         if last_rows:
-            rows = self._read_candidates(logits, candidates)
             k = 0
             for i, (_, _, _, last) in enumerate(items):
                 if last:
@@ -139,6 +132,20 @@ class DenseGpuBackend(Backend):
                     k += 1
         self._check()
         return outs
+
+    def _run_prefill(self, M, n, max_qlen, last_rows, candidates):
+        """Uploads the staged rows and runs one prefill forward; returns the candidate rows of `last_rows` (or None)."""
+        m = self.m
+        self._upload_rows(M)
+        self._sync_bt()
+        self.d_pf[:, :n].copy_(self.h_pf[:, :n], non_blocking=True)
+        self.h2d_bytes += 4 * n * 4
+        d = self.d_rows
+        pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=n, max_qlen=max_qlen)
+        lr = torch.tensor(last_rows, dtype=torch.long, device=m.device) if last_rows else None
+        logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr,
+                                want_logits=bool(last_rows))
+        return self._read_candidates(logits, candidates) if last_rows else None
 
     # ------------------------------------------------------------------ decode / verify window
     def step(self, reqs, candidates):
@@ -155,9 +162,10 @@ class DenseGpuBackend(Backend):
             raise BackendError(f"window of {M} rows exceeds {self.max_rows}", fatal=False)
         max_ctx = max(r.first_position + len(r.tokens) for r in reqs)
         bucket = min(m.max_ctx_alloc, (max_ctx + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
+        count = max(1, min(64, candidates))
+        self._announce_window(M, count, bucket)
         self._upload_rows(M)
         self._sync_bt()
-        count = max(1, min(64, candidates))
         if self.use_graphs:
             key = (M, count, bucket)
             g = self.graphs.get(key)
@@ -176,6 +184,9 @@ class DenseGpuBackend(Backend):
             out.append(rows[k:k + len(r.tokens)])
             k += len(r.tokens)
         return out
+
+    def _announce_window(self, M: int, count: int, bucket: int) -> None:
+        """Hook for multi-rank backends: tell the other ranks what is about to run (before the block-table dirty set is cleared)."""
 
     def _window(self, M: int, count: int, bucket: int) -> None:
         d = self.d_rows
@@ -236,6 +247,7 @@ class DenseGpuBackend(Backend):
         self.pending[slot] = 0
         self.h_bt[slot].zero_()
         self.bt_dirty = True
+        self.bt_dirty_slots.add(slot)
 
     # ------------------------------------------------------------------ prefix cache: pages are shared by refcount
     def prefix_block_tokens(self):
@@ -256,6 +268,7 @@ class DenseGpuBackend(Backend):
         self.pages[slot] = list(ids)
         self.h_bt[slot, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
         self.bt_dirty = True
+        self.bt_dirty_slots.add(slot)
         self.len[slot] = len(ids) * PAGE
         return self.len[slot]
 

@@ -114,10 +114,10 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       int x = c_begin * TM_KCH;
       const int y = row_tile * brows;
       int waited_src = -1;
-      const unsigned ticket = (tp.ranks > 1 && tp.in_flag != nullptr) ? tp_ticket(tp.epoch, tp.use_index) : 0u;
+      const unsigned ticket = (tp.in_flag != nullptr) ? tp_ticket(tp.epoch, tp.use_index) : 0u;
       for (int c = 0; c < nchunks; ++c, x += TM_KCH) {
         const int s = c % TM_OP_STAGES;
-        if (tp.ranks > 1 && tp.in_flag != nullptr) {
+        if (tp.in_flag != nullptr) {
           // all-gather -> GEMM: this K chunk was pushed into the local buffer by rank `src`; consume it as soon as it has landed
           const int src = x / tp.in_cols_per_src;
           if (src != waited_src) {
@@ -213,7 +213,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (done && *abort_flag == 0) {
         float* out;
         size_t ld;
-        if (tp.ranks > 1 && tp.strips_per_rank > 0) {
+        if (tp.strips_per_rank > 0) {
           // GEMM -> reduce-scatter: the tile goes straight into the owning rank's buffer over NVLink (plane [src = this rank][split])
           const int dest = strip / tp.strips_per_rank;
           ld = (size_t)tp.out_ld;
@@ -235,7 +235,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           }
         }
       }
-      if (tp.ranks > 1 && tp.strips_per_rank > 0) {
+      if (tp.strips_per_rank > 0) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
         if (dw == 0 && lane == 0 && *abort_flag == 0)
@@ -322,7 +322,7 @@ RX_API int rx_exl3_gemm_b4_tp(const void* xr, int rows, int K, const void* trell
   if (tp_desc == nullptr) return (int)cudaErrorInvalidValue;
   const GemmTp tp = *(const GemmTp*)tp_desc;
   if (tp.ranks < 1 || tp.ranks > TP_MAX) return (int)cudaErrorInvalidValue;
-  if (tp.ranks > 1 && tp.strips_per_rank > 0 && (N / TM_STRIP) != tp.strips_per_rank * tp.ranks) return (int)cudaErrorInvalidValue;
-  if (tp.ranks > 1 && tp.in_flag != nullptr && (tp.in_cols_per_src % TM_KCH != 0 || tp.in_cols_per_src * tp.ranks != K)) return (int)cudaErrorInvalidValue;
+  if (tp.strips_per_rank > 0 && (N / TM_STRIP) != tp.strips_per_rank * tp.ranks) return (int)cudaErrorInvalidValue;
+  if (tp.in_flag != nullptr && (tp.in_cols_per_src % TM_KCH != 0 || tp.in_cols_per_src * tp.ranks != K)) return (int)cudaErrorInvalidValue;
   return gemm_b4(xr, rows, K, trellis, N, codebook, part, splits, status, stream, tp);
 }

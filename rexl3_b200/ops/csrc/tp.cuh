@@ -17,7 +17,7 @@ namespace rx {
 constexpr int TP_MAX = 8;
 
 struct GemmTp {
-  int ranks;                    // 1 = single GPU, nothing below is read
+  int ranks;                    // all-zero struct = single GPU: strips_per_rank == 0 and in_flag == nullptr switch both hooks off
   int rank;
   int strips_per_rank;          // > 0: reduce-scatter epilogue, strip s goes to rank s / strips_per_rank
   int out_ld;                   // leading dimension of the destination buffers (owned columns)

@@ -1,0 +1,22 @@
+"""Tensor parallelism across real GPUs (one process per GPU, fused peer-memory kernels, lockstep followers).  Needs at
+least two GPUs (the one-rank case runs the same kernels and leader code on one GPU); NVLS is switched off for the children (only the CPU control group and plain peer stores are used)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("ranks", [1, 2, 4])
+def test_tp_selftest_over_gpus(ranks):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29540 + ranks), "-m", "rexl3_b200.parallel.selftest"]
+    r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
+    assert r.returncode == 0 and f"TP_SELFTEST_OK ranks={ranks}" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
