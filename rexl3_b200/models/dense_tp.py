@@ -4,10 +4,13 @@ Sharding (Megatron layout; the reference slices output columns at 128-column til
 crates/exl3/src/tp.rs:39-123 - here heads and FFN columns are split, o_proj / down_proj are split along K):
   qkv, gate_up, lm_head : column-parallel (input = all-gathered activations, output local)
   o_proj, down_proj     : row-parallel (input local, output reduce-scattered: every rank owns d/R columns of the residual)
-Per layer and rank:  GEMM qkv [waits for the gathered input rank by rank] -> finish+RoPE+KV write -> attention (local heads)
--> GEMM o [epilogue pushes tiles to their owner] -> finish_rs (sum, Hadamard, residual, sum of squares push) ->
-norm_rot_push (RMSNorm with the all-rank sum, next rotation, all-gather by push) -> GEMM gate_up -> SwiGLU -> GEMM down -> ...
-No NCCL call is on this path.  `run_phases` exposes the kernels phase by phase so that R shards can be stepped on ONE GPU
+Prefill slices, per layer and rank:  GEMM qkv [waits for the gathered input rank by rank] -> finish+RoPE+KV write ->
+attention (local heads) -> GEMM o [epilogue pushes tiles to their owner] -> finish_rs (sum, Hadamard, residual, sum of squares
+push) -> norm_rot_push (RMSNorm with the all-rank sum, next rotation, all-gather by push) -> GEMM gate_up -> SwiGLU -> GEMM down -> ...
+Decode / verify windows (<= 256 rows) are latency-bound, so they use a one-shot all-reduce instead: every rank finishes its own
+partial rows (split sum, Hadamard, svh) and pushes them to all ranks, one kernel later each rank adds the R rows in rank order
+into a replicated residual stream and normalises / rotates the full row (one NVLink hop per projection instead of three).
+No NCCL call is on either path.  `run_phases` exposes the kernels phase by phase so that R shards can be stepped on ONE GPU
 (LoopbackGroup) to test the protocol and the numerics.
 """
 from __future__ import annotations
@@ -93,7 +96,7 @@ class DenseTPShard:
             for name, (k, n) in shapes.items():
                 s = K.plan_splits(k, n, cls == "decode")
                 self.splits[(cls, name)] = s
-                if name in ("qkv", "gate_up", "lm_head"):
+                if name in ("qkv", "gate_up", "lm_head") or cls == "decode":      # decode windows keep o / down partials local too
                     part = max(part, s * (rows if name != "lm_head" else min(rows, 256)) * n)
         self.part = torch.empty(part, dtype=torch.float32, device=device)
         self.h = torch.empty(max_rows, cfg.d_model, dtype=torch.bfloat16, device=device)
@@ -101,6 +104,7 @@ class DenseTPShard:
         self.xr_a = torch.empty(max_rows * self.nq * hd, dtype=torch.float16, device=device)
         self.xr_f = torch.empty(max_rows * self.F, dtype=torch.float16, device=device)
         self.xr0 = torch.empty(max_rows * cfg.d_model, dtype=torch.float16, device=device)      # layer-0 input (computed locally)
+        self.xr_d = torch.empty(min(max_rows, 256) * cfg.d_model, dtype=torch.float16, device=device)   # decode windows: full-width rotated input
         self.attn_out = torch.empty(max_rows, self.nq * hd, dtype=torch.bfloat16, device=device)
         self.logits = torch.empty(min(max_rows, 256), self.lm_head.N, dtype=torch.float32, device=device)
         self.topk_scratch = K.topk_scratch(min(max_rows, 256), self.lm_head.N, 64, device)
@@ -200,6 +204,77 @@ class DenseTPShard:
             K.norm_rot_in(h, self.layers[0]["attn_norm"], cfg.eps, self.layers[0]["qkv"].suh, xr0)
         yield p_start
 
+        if prefill is None:
+            yield from self._window_phases(M, positions, slots, row_seq, ctx_len, block_table, max_ctx, h, q, xr_a, xr_f, xr0)
+        else:
+            yield from self._prefill_phases(M, positions, slots, block_table, prefill, h, q, xr_a, xr_f, xr0)
+        yield from self._head_phases(M, want_logits, logit_rows, cand_count, leader, prefill is None)
+
+    def _window_phases(self, M, positions, slots, row_seq, ctx_len, block_table, max_ctx, h, q, xr_a, xr_f, xr0):
+        """Decode / verify windows (rows <= 256): one-shot all-reduce after o_proj and down_proj, residual stream replicated."""
+        cfg, g, r, R = self.cfg, self.g, self.rank, self.R
+        from ..parallel.symm import AR_ROWS
+        hd, d = cfg.head_dim, self.d
+        scale = 1.0 / math.sqrt(hd)
+        Lib = _lib.load()
+        sp = self.splits
+        nl = len(self.layers)
+        if M > AR_ROWS:
+            raise ValueError(f"a window of {M} rows exceeds the {AR_ROWS}-row all-reduce slots")
+        xr_d = self.xr_d[:M * d].view(M, d)
+        none = ctypes.c_void_p(0)
+
+        def chain(x_part, s, w, parity, use, norm_w, suh_next):
+            """Two phases: push this rank's finished partial rows to every rank; sum all ranks' rows into the residual, norm, rotate."""
+            def p_push():
+                _lib.check(Lib.rx_tp_finish_bcast(x_part.data_ptr(), s, M, d, w.svh.data_ptr(), None if (w.bias is None or r != 0) else w.bias.data_ptr(),
+                                                  ctypes.byref(g.bcast(r, parity, use)), _lib.stream_ptr()), "rx_tp_finish_bcast")
+                _lib.count()
+
+            def p_sum():
+                _lib.check(Lib.rx_tp_allsum_add_norm_rot(g.ar_ptr(r, parity), g.ar_flag_ptr(r, parity), R, AR_ROWS, g.epoch_ptr(r), use, M, d, h.data_ptr(),
+                                                         norm_w.data_ptr(), cfg.eps, suh_next.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(),
+                                                         _lib.stream_ptr()), "rx_tp_allsum_add_norm_rot")
+                _lib.count()
+            return p_push, p_sum
+
+        for li, L in enumerate(self.layers):
+            u_o, u_d = 2 * li + 1, 2 * li + 2
+
+            def p_attn(li=li, L=L):
+                x_in = xr0 if li == 0 else xr_d
+                s = sp[("decode", "qkv")]
+                K.exl3_gemm(x_in, L["qkv"], self.part, s, self.status)
+                K.finish_qkv_rope(self.part, s, M, self.nq, self.nkv, hd, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions, self.inv_freq,
+                                  slots, q, self.k_cache[li], self.v_cache[li])
+                K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, self.nq, self.nkv, hd,
+                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status)
+                K.exl3_gemm(xr_a, L["o"], self.part, sp[("decode", "o")], self.status)
+            yield p_attn
+            a, b = chain(self.part, sp[("decode", "o")], L["o"], 0, u_o, L["ffn_norm"], L["gate_up"].suh)
+            yield a
+            yield b
+
+            def p_mlp(L=L):
+                s = sp[("decode", "gate_up")]
+                K.exl3_gemm(xr_d, L["gate_up"], self.part, s, self.status)
+                K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
+                K.exl3_gemm(xr_f, L["down"], self.part, sp[("decode", "down")], self.status)
+            yield p_mlp
+            nw, su = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
+            a, b = chain(self.part, sp[("decode", "down")], L["down"], 1, u_d, nw, su)
+            yield a
+            yield b
+
+    def _prefill_phases(self, M, positions, slots, block_table, prefill, h, q, xr_a, xr_f, xr0):
+        """Prefill slices (many rows): reduce-scatter in the GEMM epilogue, all-gather feeding the next GEMM, residual stream sharded."""
+        cfg, g, r, R = self.cfg, self.g, self.rank, self.R
+        cls = "prefill"
+        hd, d = cfg.head_dim, self.d
+        scale = 1.0 / math.sqrt(hd)
+        Lib = _lib.load()
+        sp = self.splits
+        nl = len(self.layers)
         for li, L in enumerate(self.layers):
             u_o, u_d = 2 * li + 1, 2 * li + 2
 
@@ -212,14 +287,10 @@ class DenseTPShard:
                 self._gemm(x_in, L["qkv"], self.part.data_ptr(), s, desc)
                 K.finish_qkv_rope(self.part, s, M, self.nq, self.nkv, hd, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions, self.inv_freq,
                                   slots, q, self.k_cache[li], self.v_cache[li])
-                if prefill is None:
-                    K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, self.nq, self.nkv, hd,
-                                  max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status)
-                else:
-                    ao = self.attn_out[:M]
-                    K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"],
-                                   prefill["pos0"], ao, prefill["nseq"], prefill["max_qlen"], self.nq, self.nkv, hd, scale, self.status)
-                    K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
+                ao = self.attn_out[:M]
+                K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"],
+                               prefill["pos0"], ao, prefill["nseq"], prefill["max_qlen"], self.nq, self.nkv, hd, scale, self.status)
+                K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
                 so = sp[(cls, "o")]
                 self._gemm(xr_a, L["o"], g.part_ptr(r, 0), so, g.gemm_rs(r, 0, u_o, so, M))
             yield p_attn
@@ -262,12 +333,23 @@ class DenseTPShard:
                 _lib.count()
             yield p_push_d
 
+    def _head_phases(self, M, want_logits, logit_rows, cand_count, leader, window):
+        cfg, g, r, R = self.cfg, self.g, self.rank, self.R
+        d = self.d
+        Lib = _lib.load()
+        sp = self.splits
+        nl = len(self.layers)
+
         def p_head():
             if not want_logits:
                 return None
-            x = g.xr_view(r, 1, M)
+            x = g.xr_view(r, 1, M) if not window else self.xr_d[:M * d].view(M, d)
             desc = g.gemm_ag(r, 1, 2 * nl, d)
-            if logit_rows is not None:
+            if window:
+                desc.in_flag = None
+                if logit_rows is not None:
+                    x = x.index_select(0, logit_rows).contiguous()
+            elif logit_rows is not None:
                 # a library gather reads the pushed buffer: hold the stream until every rank's slice has landed
                 _lib.check(Lib.rx_tp_wait_flags(desc.in_flag, R, g.epoch_ptr(r), 2 * nl, self.status.data_ptr(), _lib.stream_ptr()), "rx_tp_wait_flags")
                 x = x.index_select(0, logit_rows).contiguous()

@@ -175,6 +175,139 @@ __global__ void tp_wait_flags_kernel(const unsigned* flags, int ranks, const uns
 }
 
 
+// ---- one-shot all-reduce for decode windows (rows <= 256): latency matters more than bytes, so every rank finishes its OWN
+// partial product (split sum, output Hadamard, svh - all linear, so they commute with the sum over ranks) and pushes the
+// f32 row to every rank; one kernel later each rank adds the R rows in rank order, the residual, and goes on to the norm
+// and the next rotation for the whole hidden size.  One NVLink hop per projection instead of three; the residual stream is
+// replicated.  Bias (if any) rides on rank 0's contribution.
+struct BcastTp {
+  int ranks, rank;
+  float* dst[TP_MAX];            // per destination rank: f32 [ranks][rows_cap][N] of this parity
+  unsigned* dst_flag[TP_MAX];    // per destination rank: flags [ranks]
+  unsigned* local_count;
+  const unsigned* epoch;
+  unsigned use_index;
+  int rows_cap;
+};
+
+__global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
+                                    const float* __restrict__ bias, const __grid_constant__ BcastTp tp) {
+  pdl_launch();
+  pdl_wait();
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const size_t plane = (size_t)M * N;
+  for (int b = blockIdx.y * nw + warp; b < N / 128; b += gridDim.y * nw) {
+    const int n0 = b * 128 + lane * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < S; s0 += 8) {
+      float4 p[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) p[j] = __ldg(reinterpret_cast<const float4*>(part + (size_t)(s0 + j) * plane + (size_t)row * N + n0));
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) {
+          if (s0 + j == 0) acc = p[j];
+          else { acc.x += p[j].x; acc.y += p[j].y; acc.z += p[j].z; acc.w += p[j].w; }
+        }
+    }
+    float y[4] = {acc.x, acc.y, acc.z, acc.w};
+    fwht128_warp(y);
+    const uint2 su = *reinterpret_cast<const uint2*>(svh + n0);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+    y[0] *= a.x; y[1] *= a.y; y[2] *= c.x; y[3] *= c.y;
+    if (bias != nullptr) {
+      const float4 bb = *reinterpret_cast<const float4*>(bias + n0);
+      y[0] += bb.x; y[1] += bb.y; y[2] += bb.z; y[3] += bb.w;
+    }
+    const float4 o = make_float4(y[0], y[1], y[2], y[3]);
+    const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * N + n0;
+    for (int r = 0; r < tp.ranks; ++r) *reinterpret_cast<float4*>(tp.dst[r] + at) = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    tp_publish_last(tp.local_count, gridDim.x * gridDim.y, tp.dst_flag, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
+}
+
+// ar: local f32 [ranks][rows_cap][N] filled by every rank's finish_bcast_kernel.  h[row] += sum_r ar[r][row] (rank order), then
+// xr = fp16(H(rmsnorm(h) * w * suh_next)) for the full row - the multi-rank form of the single-GPU residual/norm/rotate kernel.
+__global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* __restrict__ ar, const unsigned* __restrict__ flags, int ranks,
+                                                                   int rows_cap, const unsigned* epoch, unsigned use_index, int M, int N,
+                                                                   uint16_t* __restrict__ h, const uint16_t* __restrict__ norm_w, float eps,
+                                                                   const __half* __restrict__ suh_next, __half* __restrict__ xr, int* status) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float rowbuf[];
+  __shared__ float blk_ss[512];
+  __shared__ int ok_sh;
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (threadIdx.x == 0) {
+    const unsigned ticket = tp_ticket(epoch, use_index);
+    int ok = 1;
+    for (int r = 0; r < ranks && ok; ++r) ok = tp_wait_flag(flags + r, ticket, status, 200) ? 1 : 0;
+    ok_sh = ok;
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  const size_t plane = (size_t)rows_cap * N;
+  for (int b = warp; b < N / 128; b += nw) {
+    const int n0 = b * 128 + lane * 4;
+    float4 p[TP_MAX];
+#pragma unroll
+    for (int r = 0; r < TP_MAX; ++r)
+      if (r < ranks) p[r] = __ldcg(reinterpret_cast<const float4*>(ar + (size_t)r * plane + (size_t)row * N + n0));
+    float4 acc = p[0];
+#pragma unroll
+    for (int r = 1; r < TP_MAX; ++r)
+      if (r < ranks) { acc.x += p[r].x; acc.y += p[r].y; acc.z += p[r].z; acc.w += p[r].w; }
+    const float y[4] = {acc.x, acc.y, acc.z, acc.w};
+    uint16_t* hp = h + (size_t)row * N + n0;
+    const uint2 hu = *reinterpret_cast<const uint2*>(hp);
+    float rr[4] = {__uint_as_float(hu.x << 16), __uint_as_float(hu.x & 0xFFFF0000u), __uint_as_float(hu.y << 16), __uint_as_float(hu.y & 0xFFFF0000u)};
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      rr[i] = c_bf16_to_f(c_f_to_bf16(rr[i] + y[i]));
+      ss += rr[i] * rr[i];
+      rowbuf[n0 + i] = rr[i];
+    }
+    uint2 o;
+    o.x = (uint32_t)c_f_to_bf16(rr[0]) | ((uint32_t)c_f_to_bf16(rr[1]) << 16);
+    o.y = (uint32_t)c_f_to_bf16(rr[2]) | ((uint32_t)c_f_to_bf16(rr[3]) << 16);
+    *reinterpret_cast<uint2*>(hp) = o;
+    ss = warp_sum(ss);
+    if (lane == 0) blk_ss[b] = ss;
+  }
+  if (suh_next == nullptr) return;
+  __syncthreads();
+  float rinv = 1.f;
+  if (norm_w != nullptr) {
+    float tot = 0.f;
+    for (int b = 0; b < N / 128; ++b) tot += blk_ss[b];
+    rinv = rsqrtf(tot / (float)N + eps);
+  }
+  for (int b = warp; b < N / 128; b += nw) {
+    const int n0 = b * 128 + lane * 4;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = rowbuf[n0 + i];
+    if (norm_w != nullptr) {
+      const uint2 wu = *reinterpret_cast<const uint2*>(norm_w + n0);
+      const float w[4] = {__uint_as_float(wu.x << 16), __uint_as_float(wu.x & 0xFFFF0000u), __uint_as_float(wu.y << 16), __uint_as_float(wu.y & 0xFFFF0000u)};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = c_bf16_to_f(c_f_to_bf16(v[i] * rinv)) * w[i];
+    }
+    const uint2 su = *reinterpret_cast<const uint2*>(suh_next + n0);
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+    v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
+    fwht128_warp(v);
+    const __half2 a = __floats2half2_rn(v[0], v[1]), bb = __floats2half2_rn(v[2], v[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
+    *reinterpret_cast<uint2*>(xr + (size_t)row * N + n0) = o;
+  }
+}
+
 // ---- candidate gather: every rank pushes its local top-`count` (ids offset to global vocabulary ids) to the leader, which merges the
 // R sorted lists into the global top-`count` in (value desc, id asc) order.  Full logits never cross NVLink.
 struct CandTp {
@@ -282,6 +415,39 @@ RX_API int rx_tp_norm_rot_push(const void* h, int M, int n_own, int d, int col0,
   if (threads > 1024) threads = 1024;
   return (int)rx::launch(norm_rot_push_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)stream, (const uint16_t*)h, M, n_own, d, col0,
                          (const uint16_t*)norm_w, eps, (const __half*)suh_next, status, tp);
+}
+
+RX_API int rx_tp_bcast_desc_size() { return (int)sizeof(BcastTp); }
+
+RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void* svh, const void* bias, const void* desc, void* stream) {
+  if (desc == nullptr || N % 128 || M < 1 || S < 1) return (int)cudaErrorInvalidValue;
+  const BcastTp tp = *(const BcastTp*)desc;
+  if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
+  // one warp per 128-block; few rows -> spread the blocks of a row over several CTAs
+  const int blocks = N / 128;
+  int gy = 1;
+  if (M < 64) { gy = (blocks + 3) / 4; if (gy > 32) gy = 32; }
+  int warps = (blocks + gy - 1) / gy;
+  if (warps > 8) warps = 8;
+  return (int)rx::launch(finish_bcast_kernel, dim3(M, gy), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh,
+                         (const float*)bias, tp);
+}
+
+RX_API int rx_tp_allsum_add_norm_rot(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,
+                                     void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream) {
+  if (N % 128 || N / 128 > 512 || M < 1 || M > rows_cap || ranks < 1 || ranks > TP_MAX) return (int)cudaErrorInvalidValue;
+  int threads = 32 * (N / 128);
+  if (threads > 1024) threads = 1024;
+  const size_t smem = (size_t)N * sizeof(float);
+  static bool attr_set = false;
+  if (smem > 48 * 1024 && !attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(allsum_add_norm_rot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  return (int)rx::launch(allsum_add_norm_rot_kernel, dim3(M), dim3(threads), smem, (cudaStream_t)stream, (const float*)ar, (const unsigned*)flags, ranks,
+                         rows_cap, (const unsigned*)epoch, use_index, M, N, (uint16_t*)h, (const uint16_t*)norm_w, eps, (const __half*)suh_next,
+                         (__half*)xr, status);
 }
 
 RX_API int rx_tp_cand_desc_size() { return (int)sizeof(CandTp); }

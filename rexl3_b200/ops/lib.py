@@ -52,6 +52,10 @@ def _declare(lib):
         "rx_ipc_open": (c_int, [c_void, c_void]),
         "rx_ipc_close": (c_int, [c_void]),
         "rx_tp_cand_desc_size": (c_int, []),
+        "rx_tp_bcast_desc_size": (c_int, []),
+        "rx_tp_finish_bcast": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
+        "rx_tp_allsum_add_norm_rot": (c_int, [c_void, c_void, c_int, c_int, c_void, ctypes.c_uint, c_int, c_int, c_void, c_void, c_f, c_void, c_void,
+                                              c_void, c_void]),
         "rx_tp_cand_push": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void]),
         "rx_tp_cand_merge": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, ctypes.c_uint, c_void, c_void, c_void, c_void]),
         "rx_dev_alloc": (c_int, [c_ll, ctypes.POINTER(ctypes.c_void_p)]),

@@ -47,6 +47,12 @@ class CandTp(ctypes.Structure):
                 ("id_offset", ctypes.c_int)]
 
 
+class BcastTp(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("dst", ctypes.c_void_p * TP_MAX), ("dst_flag", ctypes.c_void_p * TP_MAX),
+                ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
+
+
+AR_ROWS = 256        # rows of a decode / verify window (the one-shot all-reduce path)
 CAND_ROWS = 256      # rows of candidates one forward can return (the logits rows of a window)
 
 
@@ -59,6 +65,8 @@ def check_abi() -> None:
         raise _lib.KernelError(f"TP descriptor layout mismatch: python {got}, library {(a.value, b.value, c.value)}")
     if ctypes.sizeof(CandTp) != L.rx_tp_cand_desc_size():
         raise _lib.KernelError("TP candidate descriptor layout mismatch")
+    if ctypes.sizeof(BcastTp) != L.rx_tp_bcast_desc_size():
+        raise _lib.KernelError("TP broadcast descriptor layout mismatch")
 
 
 @dataclass
@@ -80,13 +88,15 @@ class ArenaLayout:
             off = (off + nbytes + 255) // 256 * 256
             return o
         self.epoch = take(4)
-        self.count = take(4 * 8)                       # local CTA counters: [0,1] part sites, [2,3] ss parities, [4,5] xr parities
+        self.count = take(4 * 16)                      # local CTA counters: [0,1] part sites, [2,3] ss parities, [4,5] xr parities, [6,7] ar parities
         self.part_flag = take(4 * 2 * R)               # [site][src]
         self.ss_flag = take(4 * 2 * R)                 # [parity][src]
         self.xr_flag = take(4 * 2 * R)                 # [parity][src]
         self.ss = take(4 * 2 * R * self.rows_cap)      # [parity][src][row]
         self.part = take(4 * 2 * R * self.plane_elems)  # [site][src][plane]
         self.xr = take(2 * 2 * self.rows_cap * self.d)  # [parity][row][d] fp16
+        self.ar_flag = take(4 * 2 * R)                 # [parity][src]
+        self.ar = take(4 * 2 * R * AR_ROWS * self.d)   # [parity][src][row][d] f32: one-shot all-reduce slots
         self.cand_flag = take(4 * R)                   # [src]                      (read on the leader only)
         self.cand_ids = take(4 * R * CAND_ROWS * 64)   # [src][row * count + j] u32
         self.cand_vals = take(4 * R * CAND_ROWS * 64)
@@ -159,6 +169,25 @@ class _GroupBase:
         t.local_count = me + L.count + 4 * (4 + parity)
         t.epoch, t.use_index = me + L.epoch, use_index
         return t
+
+    def bcast(self, rank: int, parity: int, use_index: int) -> BcastTp:
+        L, R = self.layout, self.ranks
+        t = BcastTp()
+        t.ranks, t.rank, t.rows_cap = R, rank, AR_ROWS
+        for r in range(R):
+            b = self.base(rank, r)
+            t.dst[r] = b + L.ar + 4 * parity * R * AR_ROWS * L.d
+            t.dst_flag[r] = b + L.ar_flag + 4 * parity * R
+        me = self.base(rank, rank)
+        t.local_count = me + L.count + 4 * (6 + parity)
+        t.epoch, t.use_index = me + L.epoch, use_index
+        return t
+
+    def ar_ptr(self, rank: int, parity: int) -> int:
+        return self.base(rank, rank) + self.layout.ar + 4 * parity * self.ranks * AR_ROWS * self.layout.d
+
+    def ar_flag_ptr(self, rank: int, parity: int) -> int:
+        return self.base(rank, rank) + self.layout.ar_flag + 4 * parity * self.ranks
 
     def cand(self, rank: int, leader: int, use_index: int, id_offset: int) -> CandTp:
         L = self.layout
