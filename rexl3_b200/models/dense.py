@@ -200,8 +200,17 @@ class ReferenceDense:
         return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
 
     @torch.no_grad()
-    def forward_seq(self, seq, tokens, start: int) -> torch.Tensor:
-        """Append `tokens` to sequence `seq` at positions start.. ; returns logits [T, vocab] (fp32)."""
+    def _ffn(self, li, L, h):
+        cfg = self.cfg
+        x = self._rms(h, L["ffn_norm"], cfg.eps)
+        gu = x @ L["gate_up"]
+        F = cfg.ffn_padded
+        return h + (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
+
+    @torch.no_grad()
+    def forward_seq(self, seq, tokens, start: int, n_layers: int | None = None) -> torch.Tensor:
+        """Append `tokens` to sequence `seq` at positions start.. ; returns logits [T, vocab] (fp32).  `n_layers` runs only the
+        first layers and applies the final norm and head to their output (the self-speculative draft)."""
         cfg = self.cfg
         ids = torch.as_tensor(tokens, dtype=torch.long, device=self.device)
         T = ids.shape[0]
@@ -209,7 +218,7 @@ class ReferenceDense:
         h = self.embed[ids]
         if seq not in self.kv:
             self.kv[seq] = [(torch.zeros(0, cfg.n_kv, cfg.head_dim, device=self.device, dtype=self.dtype),) * 2 for _ in self.layers]
-        for li, L in enumerate(self.layers):
+        for li, L in enumerate(self.layers[:n_layers or len(self.layers)]):
             x = self._rms(h, L["attn_norm"], cfg.eps)
             qkv = x @ L["qkv"]
             q = qkv[:, :cfg.n_q * cfg.head_dim].view(T, cfg.n_q, cfg.head_dim)
@@ -228,11 +237,7 @@ class ReferenceDense:
             mask = kpos[None, :] > pos[:, None]
             s = s.masked_fill(mask[None], float("-inf"))
             a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), vq).reshape(T, -1)
-            h = h + a @ L["o"]
-            x = self._rms(h, L["ffn_norm"], cfg.eps)
-            gu = x @ L["gate_up"]
-            F = cfg.ffn_padded
-            h = h + (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
+            h = self._ffn(li, L, h + a @ L["o"])
         return (self._rms(h, self.final_norm, cfg.eps) @ self.lm_head).float()
 
 
@@ -354,7 +359,17 @@ class DenseGPU:
         self.K.exl3_gemm(xr, w, self.part, s, self.status)
         return s
 
-    def forward_rows(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True):
+    def _ffn(self, li, L, M, cls, s_o, h, xr_d, xr_f, next_norm, next_suh):
+        """Everything between the o_proj GEMM (its partials are in self.part, `s_o` splits) and the next layer's rotated input."""
+        cfg, K = self.cfg, self.K
+        K.finish_add_norm_rot(self.part, s_o, M, L["o"], h, L["ffn_norm"], cfg.eps, L["gate_up"].suh, xr_d)
+        s = self._linear(xr_d, L["gate_up"], M, cls, "gate_up")
+        K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
+        s = self._linear(xr_f, L["down"], M, cls, "down")
+        K.finish_add_norm_rot(self.part, s, M, L["down"], h, next_norm, cfg.eps, next_suh, xr_d)
+
+    def forward_rows(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True,
+                     n_layers=None):
         """Run all layers over M rows.
 
         ids, positions, slots, row_seq, ctx_len: int32 device tensors [M] (slot = physical KV slot page*64+offset of the row's
@@ -377,7 +392,9 @@ class DenseGPU:
         K.embed(ids, self.embed, h)
         L0 = self.layers[0]
         K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)
-        for li, L in enumerate(self.layers):
+        nl = n_layers or len(self.layers)      # n_layers < all: the self-speculative draft (first layers + shared final norm and head)
+        for li in range(nl):
+            L = self.layers[li]
             s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
             K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
                               self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li])
@@ -390,15 +407,8 @@ class DenseGPU:
                                ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status)
                 K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
             s = self._linear(xr_a, L["o"], M, cls, "o")
-            K.finish_add_norm_rot(self.part, s, M, L["o"], h, L["ffn_norm"], cfg.eps, L["gate_up"].suh, xr_d)
-            s = self._linear(xr_d, L["gate_up"], M, cls, "gate_up")
-            K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
-            s = self._linear(xr_f, L["down"], M, cls, "down")
-            if li + 1 < len(self.layers):
-                nxt = self.layers[li + 1]
-                K.finish_add_norm_rot(self.part, s, M, L["down"], h, nxt["attn_norm"], cfg.eps, nxt["qkv"].suh, xr_d)
-            else:
-                K.finish_add_norm_rot(self.part, s, M, L["down"], h, self.final_norm, cfg.eps, self.lm_head.suh, xr_d)
+            nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
+            self._ffn(li, L, M, cls, s, h, xr_d, xr_f, nn_, ns_)
         if not want_logits:
             return None
         if logit_rows is not None:

@@ -234,7 +234,7 @@ class DenseTPShard:
             def p_sum():
                 _lib.check(Lib.rx_tp_allsum_add_norm_rot(g.ar_ptr(r, parity), g.ar_flag_ptr(r, parity), R, AR_ROWS, g.epoch_ptr(r), use, M, d, h.data_ptr(),
                                                          norm_w.data_ptr(), cfg.eps, suh_next.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(),
-                                                         _lib.stream_ptr()), "rx_tp_allsum_add_norm_rot")
+                                                         _lib.stream_ptr(), None), "rx_tp_allsum_add_norm_rot")
                 _lib.count()
             return p_push, p_sum
 

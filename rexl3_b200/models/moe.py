@@ -1,0 +1,305 @@
+"""Mixture-of-experts GQA decoder (the Qwen3-MoE-shaped target of the speculative-decode benchmark: 48 layers, d_model 2048,
+32q/4kv x 128, 128 experts of FFN 768, top-8, EXL3 3.0 bpw) on the dense executor's attention path.
+
+FFN of a layer: router (f16/bf16 gate, fp32 scores, exact top-k) -> on-device plan (pairs sorted by expert) -> per-expert input
+rotation -> grouped EXL3 GEMM gate|up -> SwiGLU + rotation -> grouped EXL3 GEMM down -> top-k weighted sum in slot order ->
+residual / norm / next rotation.  Under expert parallelism every rank holds the experts [e_lo, e_hi); activations are replicated,
+so dispatch moves no bytes and the combine is a one-shot all-reduce of each rank's weighted partial rows (summed in rank order).
+Semantics: reference crates/cuda/csrc/fmoe.cu:11-13 (softmax top-k, renormalised), moe_router.cu:3-13 (sigmoid + bias),
+moe_experts.cu:379 (combine), crates/cuda/src/moe_owned.rs:1-30 (expert ownership).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..format import exl3
+from ..ops import lib as _lib
+from .dense import CONFIGS, DenseConfig, DenseGPU, HostLayer, HostLinear, HostWeights, ReferenceDense, _bf16_round, random_linear
+
+TP_MAX = 8
+
+
+@dataclass
+class MoEConfig(DenseConfig):
+    n_experts: int = 8
+    top_k: int = 2
+    expert_ffn: int = 128
+    router_mode: str = "softmax"       # "softmax" (renormalised top-k) | "sigmoid_bias" (DeepSeek-V3: rank by score + bias)
+    routed_scale: float = 1.0
+    draft_layers: int = 4              # self-speculative draft depth
+
+    def weight_params(self) -> int:
+        attn = self.d_model * self.qkv_width + self.n_q * self.head_dim * self.d_model
+        ffn = self.n_experts * 3 * self.d_model * self.expert_ffn
+        return (attn + ffn) * self.n_layers + self.vocab_padded * self.d_model
+
+
+CONFIGS["moe-spec-30b"] = MoEConfig(n_layers=48, d_model=2048, n_q=32, n_kv=4, head_dim=128, ffn=128, vocab=151936, eps=1e-6, rope_theta=1e6,
+                                    bits=3.0, name="moe-spec-30b", n_experts=128, top_k=8, expert_ffn=768)
+CONFIGS["test-moe"] = MoEConfig(n_layers=3, d_model=256, n_q=4, n_kv=2, head_dim=128, ffn=128, vocab=1024, bits=3.0, name="test-moe",
+                                n_experts=8, top_k=2, expert_ffn=128, draft_layers=1)
+
+
+@dataclass
+class HostMoELayer(HostLayer):
+    router: np.ndarray = None            # f32 [E, d] (bf16-rounded)
+    router_bias: np.ndarray | None = None
+    experts_gu: list = field(default_factory=list)
+    experts_down: list = field(default_factory=list)
+
+
+def random_moe_weights(cfg: MoEConfig, seed: int = 0) -> HostWeights:
+    rng = np.random.default_rng(seed)
+    d, F = cfg.d_model, cfg.expert_ffn
+    s_in = 1.0 / math.sqrt(d)
+    w = HostWeights(cfg, _bf16_round(rng.normal(0, 1.0, size=(cfg.vocab, d)).astype(np.float32)))
+    for _ in range(cfg.n_layers):
+        qkv = random_linear(d, cfg.qkv_width, cfg.bits, rng, cfg.codebook, s_in)
+        o = random_linear(cfg.n_q * cfg.head_dim, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(cfg.n_q * cfg.head_dim))
+        lay = HostMoELayer(_bf16_round(1.0 + 0.1 * rng.normal(size=d)), qkv, o, _bf16_round(1.0 + 0.1 * rng.normal(size=d)), None, None)
+        lay.router = _bf16_round(rng.normal(0, 1.0 / math.sqrt(d), size=(cfg.n_experts, d)))
+        if cfg.router_mode == "sigmoid_bias":
+            lay.router_bias = rng.normal(0, 0.1, size=cfg.n_experts).astype(np.float32)
+        lay.experts_gu = [random_linear(d, 2 * F, cfg.bits, rng, cfg.codebook, s_in) for _ in range(cfg.n_experts)]
+        lay.experts_down = [random_linear(F, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(F)) for _ in range(cfg.n_experts)]
+        w.layers.append(lay)
+    w.final_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=d))
+    w.lm_head = random_linear(d, cfg.vocab_padded, cfg.head_bits or cfg.bits, rng, cfg.codebook, s_in,
+                              zero_cols_from=cfg.vocab if cfg.vocab_padded != cfg.vocab else None)
+    return w
+
+
+def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | None):
+    """fp32 router: (ids [T, k], weights [T, k]) with ties to the lowest expert id."""
+    if cfg.router_mode == "softmax":
+        p = torch.softmax(logits.float(), dim=-1)
+        key = p
+    else:
+        p = torch.sigmoid(logits.float())
+        key = p + (bias if bias is not None else 0)
+    _, ids = torch.sort(key, dim=-1, descending=True, stable=True)
+    ids = ids[:, :cfg.top_k]
+    wts = torch.gather(p, 1, ids)
+    return ids, wts / wts.sum(-1, keepdim=True) * cfg.routed_scale
+
+
+class ReferenceMoE(ReferenceDense):
+    """fp32 oracle: the dense reference with the FFN replaced by routed experts."""
+
+    def __init__(self, w: HostWeights, device="cpu", dtype=torch.float32):
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dtype)  # noqa: E731
+        self.cfg = cfg = w.cfg
+        self.device, self.dtype = device, dtype
+        self.embed = t(w.embed)
+        self.layers = []
+        for lay in w.layers:
+            self.layers.append(dict(attn_norm=t(lay.attn_norm), qkv=t(lay.qkv.dense()), o=t(lay.o.dense()), ffn_norm=t(lay.ffn_norm),
+                                    q_norm=None if lay.q_norm is None else t(lay.q_norm), k_norm=None if lay.k_norm is None else t(lay.k_norm),
+                                    router=t(lay.router), router_bias=None if lay.router_bias is None else t(lay.router_bias),
+                                    gu=[t(e.dense()) for e in lay.experts_gu], down=[t(e.dense()) for e in lay.experts_down]))
+        self.final_norm = t(w.final_norm)
+        self.lm_head = t(w.lm_head.dense())[:, :cfg.vocab]
+        from .dense import rope_inv_freq
+        self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
+        self.kv = {}
+
+    def _ffn(self, li, L, h):
+        cfg = self.cfg
+        x = self._rms(h, L["ffn_norm"], cfg.eps)
+        ids, wts = route_reference(x @ L["router"].T, cfg, L["router_bias"])
+        F = cfg.expert_ffn
+        out = torch.zeros_like(h)
+        for t in range(x.shape[0]):
+            for j in range(cfg.top_k):
+                e = int(ids[t, j])
+                gu = x[t] @ L["gu"][e]
+                out[t] += wts[t, j] * ((torch.nn.functional.silu(gu[:F]) * gu[F:]) @ L["down"][e])
+        return h + out
+
+
+class _ExpertStack:
+    """E EXL3 tensors of one shape stacked for the grouped GEMM: trellis [E, K/16, N/16, words], suh [E, K], svh [E, N]."""
+
+    def __init__(self, trellis, suh, svh, codebook):
+        self.trellis, self.suh, self.svh, self.codebook = trellis, suh, svh, codebook
+        self.E, kt, nt, words = trellis.shape
+        self.K, self.N = kt * 16, nt * 16
+        self.twice = words * 2 // 16
+        self.expert_elems = kt * nt * words          # int16 elements per expert
+
+    @property
+    def nbytes(self):
+        return self.trellis.numel() * 2 + self.suh.numel() * 2 + self.svh.numel() * 2
+
+    @staticmethod
+    def from_host(lins: list, device):
+        tr = torch.from_numpy(np.stack([l.trellis for l in lins])).to(device)
+        suh = torch.from_numpy(np.stack([l.suh for l in lins]).astype(np.float16)).to(device)
+        svh = torch.from_numpy(np.stack([l.svh for l in lins]).astype(np.float16)).to(device)
+        return _ExpertStack(tr, suh, svh, lins[0].codebook)
+
+
+class CombineDst(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("dst", ctypes.c_void_p * TP_MAX), ("dst_flag", ctypes.c_void_p * TP_MAX),
+                ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
+
+
+class MoEGPU(DenseGPU):
+    """sm_100a executor.  `experts=(lo, hi)` keeps only those experts on this GPU (expert parallelism); `ep` is then the object
+    that supplies the all-reduce slots (see parallel/ep.py); with all experts local the combine writes a local slot."""
+
+    def __init__(self, w, num_pages, max_rows=256, max_seqs=64, max_blocks_per_seq=256, device="cuda", max_prefill_rows=4096, seed=0,
+                 experts=None, ep=None):
+        cfg = w if isinstance(w, DenseConfig) else w.cfg
+        self.e_lo, self.e_hi = experts or (0, cfg.n_experts)
+        self.ep = ep
+        if ctypes.sizeof(CombineDst) != _lib.load().rx_moe_combine_desc_size():
+            raise _lib.KernelError("MoE combine descriptor layout mismatch")
+        super().__init__(w, num_pages, max_rows, max_seqs, max_blocks_per_seq, device, max_prefill_rows, seed)
+
+    # ------------------------------------------------------------------ weights
+    def _load_host(self, w: HostWeights) -> None:
+        K, device = self.K, self.device
+        dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
+        up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731
+        self.embed = dev(w.embed, torch.bfloat16)
+        self.layers = []
+        lo, hi = self.e_lo, self.e_hi
+        for lay in w.layers:
+            self.layers.append(dict(attn_norm=dev(lay.attn_norm, torch.bfloat16), qkv=up(lay.qkv), o=up(lay.o), ffn_norm=dev(lay.ffn_norm, torch.bfloat16),
+                                    q_norm=None if lay.q_norm is None else dev(lay.q_norm, torch.bfloat16),
+                                    k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16),
+                                    router=dev(lay.router, torch.bfloat16),
+                                    router_bias=None if lay.router_bias is None else dev(lay.router_bias, torch.float32),
+                                    gu=_ExpertStack.from_host(lay.experts_gu[lo:hi], device), down=_ExpertStack.from_host(lay.experts_down[lo:hi], device)))
+        self.final_norm = dev(w.final_norm, torch.bfloat16)
+        self.lm_head = up(w.lm_head)
+
+    def _load_random(self, seed: int) -> None:
+        """Random-init model on the device.  Shared tensors (attention, router, norms, head) come from the seed alone so that every
+        expert-parallel rank holds the same ones; the expert stacks are drawn per expert range."""
+        cfg, K, device = self.cfg, self.K, self.device
+        g = torch.Generator(device=device).manual_seed(seed)
+        ge = torch.Generator(device=device).manual_seed(seed * 7919 + 13 + self.e_lo)
+        b = exl3.Bits.of(cfg.bits)
+        tw = b.tile_words
+        cb = cfg.codebook if b.is_integer else "mul1"
+        sg = lambda shape, gen: (torch.randint(0, 2, shape, device=device, generator=gen) * 2 - 1)  # noqa: E731
+
+        def lin(k, n, scale):
+            tr = torch.randint(-32768, 32768, (k // 16, n // 16, tw), dtype=torch.int16, device=device, generator=g)
+            return K.Exl3Weight(tr, sg((k,), g).to(torch.float16), (sg((n,), g) * scale).to(torch.float16), None, cb)
+
+        def stack(e, k, n, scale):
+            tr = torch.randint(-32768, 32768, (e, k // 16, n // 16, tw), dtype=torch.int16, device=device, generator=ge)
+            return _ExpertStack(tr, sg((e, k), ge).to(torch.float16), (sg((e, n), ge) * scale).to(torch.float16), cb)
+
+        norm = lambda: (1.0 + 0.1 * torch.randn(cfg.d_model, device=device, generator=g)).to(torch.bfloat16)  # noqa: E731
+        d, F, HQ, E = cfg.d_model, cfg.expert_ffn, cfg.n_q * cfg.head_dim, self.e_hi - self.e_lo
+        self.embed = torch.randn(cfg.vocab, d, device=device, generator=g).to(torch.bfloat16)
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            self.layers.append(dict(attn_norm=norm(), qkv=lin(d, cfg.qkv_width, 1.0 / math.sqrt(d)), o=lin(HQ, d, 0.5 / math.sqrt(HQ)), ffn_norm=norm(),
+                                    q_norm=None, k_norm=None,
+                                    router=(torch.randn(cfg.n_experts, d, device=device, generator=g) / math.sqrt(d)).to(torch.bfloat16),
+                                    router_bias=None if cfg.router_mode == "softmax" else 0.1 * torch.randn(cfg.n_experts, device=device, generator=g),
+                                    gu=stack(E, d, 2 * F, 1.0 / math.sqrt(d)), down=stack(E, F, d, 0.5 / math.sqrt(F))))
+        self.final_norm = norm()
+        self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d))
+        if cfg.vocab_padded != cfg.vocab:
+            self.lm_head.svh[cfg.vocab:] = 0
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * 2 + self.lm_head.nbytes
+        for L in self.layers:
+            n += L["qkv"].nbytes + L["o"].nbytes + L["gu"].nbytes + L["down"].nbytes + L["router"].numel() * 2
+        return n
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_scratch(self, R: int):
+        cfg, K, dev = self.cfg, self.K, self.device
+        super()._alloc_scratch(R)       # the dense scratch sizes its (unused) FFN buffers from cfg.ffn; the expert buffers follow
+        k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
+        self.pairs_cap = R * k
+        self.moe_splits = {}
+        part = 0
+        for cls, rows in (("decode", min(R, 256)), ("prefill", R)):
+            decode = cls == "decode"
+            # the grouped launch already spreads over experts: K splits only where a window has few pairs
+            s_gu = K.plan_splits(d, 2 * F, decode) if decode else 1
+            s_dn = K.plan_splits(F, d, decode) if decode else 1
+            s_gu, s_dn = max(1, min(s_gu, 4)), max(1, min(s_dn, 4))
+            self.moe_splits[cls] = (s_gu, s_dn)
+            part = max(part, s_gu * rows * k * 2 * F, s_dn * rows * k * d)
+        if part > self.part.numel():
+            self.part = torch.empty(part, dtype=torch.float32, device=dev)
+        i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)  # noqa: E731
+        self.xn = torch.empty(R, d, dtype=torch.bfloat16, device=dev)
+        self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
+        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
+        self.max_tiles_decode = min(E, 256 * k)
+        self.max_tiles_prefill = E + (R * k + 127) // 128
+        self.tile_tab = i32(3 * max(self.max_tiles_decode, self.max_tiles_prefill))
+        self.xs = torch.zeros(R * k, d, dtype=torch.float16, device=dev)
+        self.xs2 = torch.zeros(R * k, F, dtype=torch.float16, device=dev)
+        self.slot = torch.zeros(R, d, dtype=torch.float32, device=dev)        # one-rank all-reduce slot
+        self._dst = CombineDst()
+        self._dst.ranks, self._dst.rank, self._dst.rows_cap = 1, 0, R
+        self._dst.dst[0] = self.slot.data_ptr()
+
+    # ------------------------------------------------------------------ the routed FFN
+    def _ffn(self, li, L, M, cls, s_o, h, xr_d, xr_f, next_norm, next_suh):
+        cfg, K = self.cfg, self.K
+        Lib = _lib.load()
+        st = _lib.stream_ptr()
+        k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
+        pairs = M * k
+        xn = self.xn[:M]
+        K.finish_add_norm_rot(self.part, s_o, M, L["o"], h, L["ffn_norm"], cfg.eps, None, None, xn_out=xn)
+        _lib.check(Lib.rx_moe_router(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
+                                     0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st),
+                   "rx_moe_router")
+        if cls == "decode":
+            tile_rows, max_tiles = K.tile_rows(M), self.max_tiles_decode
+        else:
+            tile_rows, max_tiles = 128, self.max_tiles_prefill
+        _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, max_tiles, self.offs.data_ptr(),
+                                   self.pos_of_pair.data_ptr(), self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(),
+                                   self.total.data_ptr(), st), "rx_moe_plan")
+        # local expert index = global - e_lo: the stacks hold only the owned experts, so shift the pointers instead of the ids
+        gu, dn = L["gu"], L["down"]
+        suh_gu = gu.suh.data_ptr() - 2 * self.e_lo * gu.K
+        _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), self.pick_ids.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, ctypes.c_void_p(suh_gu),
+                                         self.xs.data_ptr(), st), "rx_moe_gather_rot")
+        s_gu, s_dn = self.moe_splits[cls]
+        self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows)
+        _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), s_gu, self.pairs_cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
+                                         ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
+                                         self.xs2.data_ptr(), st), "rx_moe_swiglu_rot")
+        self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows)
+        dst, ar, flags, ranks, rows_cap, epoch, use = self._combine_target(li, M)
+        _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), s_dn, self.pairs_cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(),
+                                      self.pos_of_pair.data_ptr(), ctypes.c_void_p(dn.svh.data_ptr() - 2 * self.e_lo * dn.N), None, ctypes.byref(dst), st),
+                   "rx_moe_combine")
+        _lib.check(Lib.rx_tp_allsum_add_norm_rot(ar, flags, ranks, rows_cap, epoch, use, M, d, h.data_ptr(), next_norm.data_ptr(), cfg.eps,
+                                                 next_suh.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(), st, None), "rx_tp_allsum_add_norm_rot")
+        _lib.count(7)
+
+    def _grouped_shifted(self, xs, st: _ExpertStack, splits, max_tiles, tile_rows):
+        """The tile table names GLOBAL expert ids; the stack starts at expert e_lo."""
+        L = _lib.load()
+        base = st.trellis.data_ptr() - 2 * self.e_lo * st.expert_elems
+        _lib.check(L.rx_exl3_gemm_grouped(xs.data_ptr(), self.pairs_cap, st.K, ctypes.c_void_p(base), st.expert_elems, st.N, st.twice,
+                                          self.K.CB_ID[st.codebook], self.part.data_ptr(), splits, self.tile_tab.data_ptr(), max_tiles, tile_rows,
+                                          self.status.data_ptr(), _lib.stream_ptr()), "rx_exl3_gemm_grouped")
+
+    def _combine_target(self, li, M):
+        """-> (CombineDst, all-reduce slots pointer, flags pointer or None, ranks, rows_cap, epoch pointer, use index)."""
+        if self.ep is None:
+            return self._dst, self.slot.data_ptr(), None, 1, self._dst.rows_cap, None, 0
+        return self.ep.combine_target(li, M)

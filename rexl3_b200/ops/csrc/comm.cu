@@ -234,7 +234,8 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
 __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* __restrict__ ar, const unsigned* __restrict__ flags, int ranks,
                                                                    int rows_cap, const unsigned* epoch, unsigned use_index, int M, int N,
                                                                    uint16_t* __restrict__ h, const uint16_t* __restrict__ norm_w, float eps,
-                                                                   const __half* __restrict__ suh_next, __half* __restrict__ xr, int* status) {
+                                                                   const __half* __restrict__ suh_next, __half* __restrict__ xr, int* status,
+                                                                   uint16_t* __restrict__ xn_out) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float rowbuf[];
@@ -242,9 +243,11 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
   __shared__ int ok_sh;
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   if (threadIdx.x == 0) {
-    const unsigned ticket = tp_ticket(epoch, use_index);
     int ok = 1;
-    for (int r = 0; r < ranks && ok; ++r) ok = tp_wait_flag(flags + r, ticket, status, 200) ? 1 : 0;
+    if (flags != nullptr) {          // nullptr: the slots were filled by an earlier kernel of this stream (one rank)
+      const unsigned ticket = tp_ticket(epoch, use_index);
+      for (int r = 0; r < ranks && ok; ++r) ok = tp_wait_flag(flags + r, ticket, status, 200) ? 1 : 0;
+    }
     ok_sh = ok;
   }
   __syncthreads();
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
     ss = warp_sum(ss);
     if (lane == 0) blk_ss[b] = ss;
   }
-  if (suh_next == nullptr) return;
+  if (suh_next == nullptr && xn_out == nullptr) return;
   __syncthreads();
   float rinv = 1.f;
   if (norm_w != nullptr) {
@@ -297,6 +300,13 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
 #pragma unroll
       for (int i = 0; i < 4; ++i) v[i] = c_bf16_to_f(c_f_to_bf16(v[i] * rinv)) * w[i];
     }
+    if (xn_out != nullptr) {       // the normalised row itself (router input, per-expert rotations)
+      uint2 o;
+      o.x = (uint32_t)c_f_to_bf16(v[0]) | ((uint32_t)c_f_to_bf16(v[1]) << 16);
+      o.y = (uint32_t)c_f_to_bf16(v[2]) | ((uint32_t)c_f_to_bf16(v[3]) << 16);
+      *reinterpret_cast<uint2*>(xn_out + (size_t)row * N + n0) = o;
+    }
+    if (suh_next == nullptr) continue;
     const uint2 su = *reinterpret_cast<const uint2*>(suh_next + n0);
     const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
     v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
@@ -434,7 +444,7 @@ RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void*
 }
 
 RX_API int rx_tp_allsum_add_norm_rot(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,
-                                     void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream) {
+                                     void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream, void* xn_out) {
   if (N % 128 || N / 128 > 512 || M < 1 || M > rows_cap || ranks < 1 || ranks > TP_MAX) return (int)cudaErrorInvalidValue;
   int threads = 32 * (N / 128);
   if (threads > 1024) threads = 1024;
@@ -447,7 +457,7 @@ RX_API int rx_tp_allsum_add_norm_rot(const void* ar, const void* flags, int rank
   }
   return (int)rx::launch(allsum_add_norm_rot_kernel, dim3(M), dim3(threads), smem, (cudaStream_t)stream, (const float*)ar, (const unsigned*)flags, ranks,
                          rows_cap, (const unsigned*)epoch, use_index, M, N, (uint16_t*)h, (const uint16_t*)norm_w, eps, (const __half*)suh_next,
-                         (__half*)xr, status);
+                         (__half*)xr, status, (uint16_t*)xn_out);
 }
 
 RX_API int rx_tp_cand_desc_size() { return (int)sizeof(CandTp); }

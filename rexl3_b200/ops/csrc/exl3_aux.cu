@@ -175,7 +175,8 @@ __global__ void finish_store_kernel(const float* __restrict__ part, int S, int M
 // norm_w == nullptr skips the norm, suh_next == nullptr skips the rotation output entirely (residual update only).
 __global__ void __launch_bounds__(1024) finish_add_norm_rot_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
                                            const float* __restrict__ bias, uint16_t* __restrict__ h, const uint16_t* __restrict__ norm_w,
-                                           float eps, const __half* __restrict__ suh_next, __half* __restrict__ xr) {
+                                           float eps, const __half* __restrict__ suh_next, __half* __restrict__ xr,
+                                           uint16_t* __restrict__ xn_out) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float rowbuf[];  // N floats: the updated residual row (as stored, bf16-rounded)
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(1024) finish_add_norm_rot_kernel(const float* 
     ss = warp_sum(ss);
     if (lane == 0) blk_ss[b] = ss;
   }
-  if (suh_next == nullptr) return;
+  if (suh_next == nullptr && xn_out == nullptr) return;
   float rinv = 1.f;
   __syncthreads();  // orders the rowbuf / blk_ss writes before the reads below
   if (norm_w != nullptr) {
@@ -210,13 +211,15 @@ __global__ void __launch_bounds__(1024) finish_add_norm_rot_kernel(const float* 
     float v[4], s[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = rowbuf[n0 + i];
-    load4_f16(suh_next + n0, s);
+    if (suh_next != nullptr) load4_f16(suh_next + n0, s);
     if (norm_w != nullptr) {
       float w[4];
       load4_bf16(norm_w + n0, w);
 #pragma unroll
       for (int i = 0; i < 4; ++i) v[i] = bf16_to_f(f_to_bf16(v[i] * rinv)) * w[i];
     }
+    if (xn_out != nullptr) store4_bf16(xn_out + (size_t)row * N + n0, v);   // the normalised row itself (router input, per-expert rotations)
+    if (suh_next == nullptr) continue;
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] *= s[i];
     fwht128_warp(v);
@@ -297,7 +300,7 @@ RX_API int rx_finish_store(const void* part, int S, int M, int N, const void* sv
 }
 
 RX_API int rx_finish_add_norm_rot(const void* part, int S, int M, int N, const void* svh, const void* bias, void* h_bf16, const void* norm_w,
-                                  float eps, const void* suh_next, void* xr, void* stream) {
+                                  float eps, const void* suh_next, void* xr, void* stream, void* xn_out) {
   if (N % 128 || N * 4 > 200 * 1024 || N / 128 > 512) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
@@ -307,7 +310,7 @@ RX_API int rx_finish_add_norm_rot(const void* part, int S, int M, int N, const v
   }
   rx::launch(finish_add_norm_rot_kernel, dim3(M), dim3(1024), (size_t)N * 4, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh, (const float*)bias,
                                                                      (uint16_t*)h_bf16, (const uint16_t*)norm_w, eps, (const __half*)suh_next,
-                                                                     (__half*)xr);
+                                                                     (__half*)xr, (uint16_t*)xn_out);
   return (int)cudaGetLastError();
 }
 

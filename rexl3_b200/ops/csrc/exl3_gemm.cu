@@ -52,8 +52,22 @@ __host__ __device__ inline GemmSmemLayout gemm_layout(int twice, int brows) {
 template <int TWICE, int CB>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
 exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __restrict__ trellis, float* __restrict__ part,
-                 int rows, int K, int N, int splits, int brows, int row_tiles, int* status) {
+                 int rows, int K, int N, int splits, int brows, int row_tiles, int* status, const int* __restrict__ tile_tab,
+                 size_t expert_words) {
   pdl_launch();
+  // Row window of this CTA.  Plain GEMM: tile z of the row dimension.  Grouped (mixture-of-experts) form: tile_tab[z] =
+  // {expert, first row, row count} written by the planning kernel; rows are pairs sorted by expert, every expert has its own
+  // trellis (expert_words apart); a tile with no rows exits before it allocates anything.
+  int g_row0 = blockIdx.z * brows;
+  int g_nrows = rows - g_row0 < brows ? rows - g_row0 : brows;
+  if (tile_tab != nullptr) {
+    pdl_wait();
+    const int e = tile_tab[3 * blockIdx.z];
+    g_row0 = tile_tab[3 * blockIdx.z + 1];
+    g_nrows = tile_tab[3 * blockIdx.z + 2];
+    if (g_nrows <= 0) return;
+    trellis += (size_t)e * expert_words;
+  }
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled operand tiles
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -76,7 +90,6 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int strip = blockIdx.x;
   const int split = blockIdx.y;
-  const int row_tile = blockIdx.z;
   const int nchunks_total = K / KCH;
   const int c_begin = (int)((long long)nchunks_total * split / splits);
   const int c_end = (int)((long long)nchunks_total * (split + 1) / splits);
@@ -129,7 +142,7 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
           if (c >= OP_STAGES) ok = mbar_wait(&op_empty[s], ((c / OP_STAGES) - 1) & 1, abort_flag, status, 11);
           if (!ok) break;
           mbar_arrive_expect_tx(&op_full[s], (uint32_t)b_stage);
-          tma_load_2d(smem + L.b_off + s * b_stage, &tmap_x, (c_begin + c) * KCH, row_tile * brows, &op_full[s]);
+          tma_load_2d(smem + L.b_off + s * b_stage, &tmap_x, (c_begin + c) * KCH, g_row0, &op_full[s]);
         }
       }
     }
@@ -257,16 +270,15 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
         const int q = warp & 3;
         const int n = strip * STRIP + q * 32 + lane;
         float* out = part + ((size_t)split * rows) * N + n;
-        const int row0 = row_tile * brows;
+        const int row0 = g_row0;
         for (int cb = 0; cb < brows; cb += 16) {
-          if (row0 + cb >= rows) break;  // warp-uniform
+          if (cb >= g_nrows) break;  // warp-uniform
           uint32_t r[16];
           tc_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + cb, r);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int row = row0 + cb + i;
-            if (row < rows) out[(size_t)row * N] = __uint_as_float(r[i]);
+            if (cb + i < g_nrows) out[(size_t)(row0 + cb + i) * N] = __uint_as_float(r[i]);
           }
         }
       }
@@ -329,7 +341,7 @@ int make_tmap_trellis(CUtensorMap* out, const void* base, uint64_t kt_rows, uint
 
 template <int TWICE, int CB>
 static int launch_gemm(const CUtensorMap& tm, const uint32_t* trellis, float* part, int rows, int K, int N, int splits, int brows,
-                       int row_tiles, int* status, cudaStream_t st) {
+                       int row_tiles, int* status, cudaStream_t st, const int* tile_tab = nullptr, size_t expert_words = 0) {
   const GemmSmemLayout L = gemm_layout(TWICE, brows);
   const int smem = L.total + 1024;
   auto kern = exl3_gemm_kernel<TWICE, CB>;
@@ -341,7 +353,7 @@ static int launch_gemm(const CUtensorMap& tm, const uint32_t* trellis, float* pa
   }
   if (smem > 232448) return (int)cudaErrorInvalidValue;
   dim3 grid(N / STRIP, splits, row_tiles);
-  rx::launch(kern, dim3(grid), dim3(GEMM_THREADS), smem, st, tm, trellis, part, rows, K, N, splits, brows, row_tiles, status);
+  rx::launch(kern, dim3(grid), dim3(GEMM_THREADS), smem, st, tm, trellis, part, rows, K, N, splits, brows, row_tiles, status, tile_tab, expert_words);
   return (int)cudaGetLastError();
 }
 
@@ -384,6 +396,32 @@ RX_API int rx_exl3_gemm(const void* xr, int rows, int K, const void* trellis, in
   const uint32_t* tr = (const uint32_t*)trellis;
   float* p = (float*)part;
 #define RX_GO(CBV) RX_DISPATCH_TWICE(twice, return launch_gemm<T_, CBV>(tm, tr, p, rows, K, N, splits, brows, row_tiles, status, st))
+  switch (codebook) {
+    case CB_3INST: RX_GO(CB_3INST); break;
+    case CB_MCG: RX_GO(CB_MCG); break;
+    case CB_MUL1: RX_GO(CB_MUL1); break;
+    default: return (int)cudaErrorInvalidValue;
+  }
+#undef RX_GO
+  return (int)cudaErrorInvalidValue;
+}
+
+// Grouped (mixture-of-experts) form.  xs: fp16 [pairs_cap, K], rows sorted by expert (each row already rotated with its expert's
+// suh).  trellis: int16 [E][K/16, N/16, 16*bits].  tile_tab: device int32 [max_tiles][3] = {expert, first row, rows} (rows == 0: idle
+// tile).  part: fp32 [splits, pairs_cap, N].  `tile_rows` is the MMA N of every tile (16..256, fixed for the launch).
+RX_API int rx_exl3_gemm_grouped(const void* xs, int pairs_cap, int K, const void* trellis, long long expert_elems, int N, int twice, int codebook,
+                                void* part, int splits, const void* tile_tab, int max_tiles, int tile_rows, int* status, void* stream) {
+  if (pairs_cap <= 0 || K % 128 != 0 || N % 128 != 0 || splits < 1 || splits > K / KCH || max_tiles < 1 || max_tiles > 65535) return (int)cudaErrorInvalidValue;
+  if (tile_rows != rx_exl3_tile_rows(tile_rows) || (expert_elems % 2) != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)xs) & 15) != 0 || (((uintptr_t)trellis) & 15) != 0) return (int)cudaErrorMisalignedAddress;
+  CUtensorMap tm;
+  int e = make_tmap_f16_2d(&tm, xs, (uint64_t)pairs_cap, (uint64_t)K, (uint32_t)tile_rows);
+  if (e != 0) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint32_t* tr = (const uint32_t*)trellis;
+  float* p = (float*)part;
+  const size_t ew = (size_t)expert_elems / 2;
+#define RX_GO(CBV) RX_DISPATCH_TWICE(twice, return launch_gemm<T_, CBV>(tm, tr, p, pairs_cap, K, N, splits, tile_rows, max_tiles, status, st, (const int*)tile_tab, ew))
   switch (codebook) {
     case CB_3INST: RX_GO(CB_3INST); break;
     case CB_MCG: RX_GO(CB_MCG); break;

@@ -1,0 +1,339 @@
+// Mixture-of-experts glue around the grouped EXL3 GEMM (sm_100a):
+//
+//   moe_router_kernel       gate logits (f16/bf16 gate matrix, fp32 accumulate) + scoring + exact top-k per row
+//                           mode 0: softmax over all experts, top-k, renormalised over the picks   (Qwen-MoE style)
+//                           mode 1: sigmoid scores, picks ranked by score + bias, weights = score / sum(picked) * scale (DeepSeek-V3 style)
+//   moe_plan_kernel         counting sort of the (row, slot) pairs by expert in (expert, row, slot) order -> positions, per-expert
+//                           offsets, the tile table of the grouped GEMM.  Only experts in [e_lo, e_hi) are planned (expert parallelism:
+//                           a rank plans its own experts; activations are replicated, so "dispatch" moves no bytes).
+//   moe_gather_rot_kernel   xs[pos] = fp16(H(x[row] * suh[expert]))   - the expert's own input rotation
+//   moe_swiglu_rot_kernel   finish of the gate|up GEMM per pair: split sum, Hadamard, svh, SwiGLU, the down projection's rotation
+//   moe_combine_kernel      finish of the down GEMM per pair and the top-k weighted sum in slot order (+ an optional shared-expert
+//                           row) -> f32 row, written to every rank's all-reduce slot (one rank: a local buffer)
+//
+// Semantics matched: reference crates/cuda/csrc/moe_router.cu:3-13 (sigmoid+bias router), coopmk.cu:66 / fmoe.cu:11-13 (softmax
+// top-k), moe_experts.cu:379 and moe_prefill.cu:444 (combine order: slot order, fp32), moe_prefill.cu:6-12 (on-device planning),
+// moe_owned.cu:1-25 (owned experts only; the others contribute nothing).  All reductions have a fixed order.
+#include "tp.cuh"
+
+namespace rx {
+
+__device__ __forceinline__ float m_bf16_to_f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+__device__ __forceinline__ uint16_t m_f_to_bf16(float f) {
+  __nv_bfloat16 b = __float2bfloat16_rn(f);
+  return *reinterpret_cast<uint16_t*>(&b);
+}
+
+// x: bf16 [M, d] (normalised hidden rows).  gate: bf16 [E, d].  bias: f32 [E] or nullptr (mode 1).
+// out_ids: int32 [M, topk], out_w: f32 [M, topk].  One CTA per row; warp w scores experts w, w + nw, ...
+__global__ void __launch_bounds__(256) moe_router_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const float* __restrict__ bias,
+                                                         int M, int d, int E, int topk, int mode, float scale, int* __restrict__ out_ids,
+                                                         float* __restrict__ out_w) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float score[512];     // selection key
+  __shared__ float prob[512];      // weight source
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const uint16_t* xr = x + (size_t)row * d;
+  for (int e = warp; e < E; e += nw) {
+    const uint16_t* g = gate + (size_t)e * d;
+    float acc = 0.f;
+    for (int k = lane * 8; k < d; k += 256) {
+      const uint4 a = *reinterpret_cast<const uint4*>(xr + k), b = __ldg(reinterpret_cast<const uint4*>(g + k));
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), acc);
+        acc = fmaf(__uint_as_float(aw[i] & 0xFFFF0000u), __uint_as_float(bw[i] & 0xFFFF0000u), acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) prob[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  // scoring (warp 0; every lane walks experts lane, lane + 32, ... so each reduction has a fixed order)
+  if (mode == 0) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = __expf(prob[e] - mx);
+      prob[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) {
+      prob[e] /= sum;
+      score[e] = prob[e];
+    }
+  } else {
+    for (int e = lane; e < E; e += 32) {
+      const float s = 1.f / (1.f + __expf(-prob[e]));
+      prob[e] = s;
+      score[e] = s + (bias != nullptr ? bias[e] : 0.f);
+    }
+  }
+  __syncwarp();
+  // exact top-k: k rounds of arg-max, ties to the lowest expert id
+  float picked_sum = 0.f;
+  for (int j = 0; j < topk; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float s = score[e];
+      if (s > best || (s == best && e < bi)) { best = s; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    const float p = prob[bi];
+    picked_sum += p;
+    if (lane == 0) {
+      out_ids[(size_t)row * topk + j] = bi;
+      out_w[(size_t)row * topk + j] = p;
+      score[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  // renormalise over the picks (slot order sum, identical on every lane)
+  if (lane < topk) out_w[(size_t)row * topk + lane] = out_w[(size_t)row * topk + lane] / picked_sum * scale;
+}
+
+// Single CTA.  ids: int32 [pairs].  Outputs: offs int32 [E + 1] (positions of expert e are offs[e] .. offs[e+1]; experts outside
+// [e_lo, e_hi) get empty ranges), pos_of_pair int32 [pairs] (-1: not owned), pair_of_pos / expert_of_pos int32 [pairs],
+// tile_tab int32 [max_tiles][3], total int32 [1].
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles,
+                                                        int* __restrict__ offs, int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos,
+                                                        int* __restrict__ expert_of_pos, int* __restrict__ tile_tab, int* __restrict__ total) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int cnt[513];
+  __shared__ int start[513];
+  const int t = threadIdx.x;
+  for (int e = t; e <= E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  // thread e counts its pairs in pair order (every thread reads the same id at the same time: broadcast)
+  if (t < E && t >= e_lo && t < e_hi) {
+    int c = 0;
+    for (int p = 0; p < pairs; ++p) c += (ids[p] == t) ? 1 : 0;
+    cnt[t] = c;
+  }
+  __syncthreads();
+  if (t == 0) {
+    int run = 0, tile = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = run;
+      offs[e] = run;
+      for (int r0 = 0; r0 < cnt[e] && tile < max_tiles; r0 += tile_rows, ++tile) {
+        tile_tab[3 * tile] = e;
+        tile_tab[3 * tile + 1] = run + r0;
+        tile_tab[3 * tile + 2] = min(tile_rows, cnt[e] - r0);
+      }
+      run += cnt[e];
+    }
+    offs[E] = run;
+    *total = run;
+    for (; tile < max_tiles; ++tile) { tile_tab[3 * tile] = 0; tile_tab[3 * tile + 1] = 0; tile_tab[3 * tile + 2] = 0; }
+  }
+  __syncthreads();
+  if (t < E && t >= e_lo && t < e_hi) {
+    int at = start[t];
+    for (int p = 0; p < pairs; ++p)
+      if (ids[p] == t) {
+        pos_of_pair[p] = at;
+        pair_of_pos[at] = p;
+        expert_of_pos[at] = t;
+        ++at;
+      }
+  }
+  for (int p = t; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e < e_lo || e >= e_hi) pos_of_pair[p] = -1;
+  }
+}
+
+// grid = pairs.  x: bf16 [M, d]; suh: f16 [E, d]; xs: f16 [pairs_cap, d].
+__global__ void moe_gather_rot_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids, const int* __restrict__ pos_of_pair, int topk, int d,
+                                      const __half* __restrict__ suh, __half* __restrict__ xs) {
+  pdl_launch();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const int pos = pos_of_pair[pair];
+  if (pos < 0) return;
+  const int row = pair / topk, e = ids[pair];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int b = warp; b < d / 128; b += nw) {
+    const int n0 = b * 128 + lane * 4;
+    const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * d + n0);
+    float v[4] = {__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u)};
+    const uint2 su = *reinterpret_cast<const uint2*>(suh + (size_t)e * d + n0);
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+    v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
+    fwht128_warp(v);
+    const __half2 a = __floats2half2_rn(v[0], v[1]), bb = __floats2half2_rn(v[2], v[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
+    *reinterpret_cast<uint2*>(xs + (size_t)pos * d + n0) = o;
+  }
+}
+
+// Sum of S split planes of one 128-block, output Hadamard, svh.  part: f32 [S][pairs_cap][N].
+__device__ __forceinline__ void moe_finish_block(const float* __restrict__ part, int S, size_t plane, size_t off, const __half* svh_n0, float (&y)[4]) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = 0; s0 < S; s0 += 8) {
+    float4 p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (s0 + j < S) p[j] = __ldg(reinterpret_cast<const float4*>(part + (size_t)(s0 + j) * plane + off));
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (s0 + j < S) {
+        if (s0 + j == 0) acc = p[j];
+        else { acc.x += p[j].x; acc.y += p[j].y; acc.z += p[j].z; acc.w += p[j].w; }
+      }
+  }
+  y[0] = acc.x; y[1] = acc.y; y[2] = acc.z; y[3] = acc.w;
+  fwht128_warp(y);
+  const uint2 su = *reinterpret_cast<const uint2*>(svh_n0);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+  y[0] *= a.x; y[1] *= a.y; y[2] *= c.x; y[3] *= c.y;
+}
+
+// grid = (pairs_cap, gy).  part: f32 [S][pairs_cap][2F] (gate | up).  xs2: f16 [pairs_cap, F] = H(silu(gate) * up * suh_down[e]).
+__global__ void moe_swiglu_rot_kernel(const float* __restrict__ part, int S, int pairs_cap, int F, const int* __restrict__ expert_of_pos,
+                                      const int* __restrict__ total, const __half* __restrict__ svh_gu, const __half* __restrict__ suh_down,
+                                      __half* __restrict__ xs2) {
+  pdl_launch();
+  pdl_wait();
+  const int pos = blockIdx.x;
+  if (pos >= *total) return;
+  const int e = expert_of_pos[pos];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int N = 2 * F;
+  const size_t plane = (size_t)pairs_cap * N;
+  for (int b = blockIdx.y * nw + warp; b < F / 128; b += gridDim.y * nw) {
+    const int n0 = b * 128 + lane * 4;
+    float g[4], u[4];
+    moe_finish_block(part, S, plane, (size_t)pos * N + n0, svh_gu + (size_t)e * N + n0, g);
+    moe_finish_block(part, S, plane, (size_t)pos * N + F + n0, svh_gu + (size_t)e * N + F + n0, u);
+    const uint2 su = *reinterpret_cast<const uint2*>(suh_down + (size_t)e * F + n0);
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+    const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = g[i] / (1.f + __expf(-g[i])) * u[i];
+      g[i] = m_bf16_to_f(m_f_to_bf16(a)) * s[i];
+    }
+    fwht128_warp(g);
+    const __half2 a = __floats2half2_rn(g[0], g[1]), bb = __floats2half2_rn(g[2], g[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
+    *reinterpret_cast<uint2*>(xs2 + (size_t)pos * F + n0) = o;
+  }
+}
+
+struct CombineDst {
+  int ranks, rank;
+  float* dst[TP_MAX];            // f32 [ranks][rows_cap][d] on every rank (one rank: a local buffer)
+  unsigned* dst_flag[TP_MAX];    // nullptr on one rank
+  unsigned* local_count;
+  const unsigned* epoch;
+  unsigned use_index;
+  int rows_cap;
+};
+
+// grid = (M, gy).  part: f32 [S][pairs_cap][d] (down GEMM).  y[row] = sum_slot w[row][slot] * finish(part[pos(row, slot)]) in slot order,
+// skipping pairs this rank does not own; + shared[row] (f32 [M, d] or nullptr; only one rank passes it).  The row goes to slot `rank`
+// of every rank's all-reduce buffer, then the last CTA publishes the flags.
+__global__ void moe_combine_kernel(const float* __restrict__ part, int S, int pairs_cap, int M, int d, int topk, const int* __restrict__ ids,
+                                   const float* __restrict__ w, const int* __restrict__ pos_of_pair, const __half* __restrict__ svh_down,
+                                   const float* __restrict__ shared, const __grid_constant__ CombineDst tp) {
+  pdl_launch();
+  pdl_wait();
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const size_t plane = (size_t)pairs_cap * d;
+  for (int b = blockIdx.y * nw + warp; b < d / 128; b += gridDim.y * nw) {
+    const int n0 = b * 128 + lane * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+      const int pair = row * topk + j;
+      const int pos = pos_of_pair[pair];
+      if (pos < 0) continue;     // warp-uniform
+      const int e = ids[pair];
+      float y[4];
+      moe_finish_block(part, S, plane, (size_t)pos * d + n0, svh_down + (size_t)e * d + n0, y);
+      const float wj = w[pair];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(wj, y[i], acc[i]);
+    }
+    if (shared != nullptr) {
+      const float4 sh = *reinterpret_cast<const float4*>(shared + (size_t)row * d + n0);
+      acc[0] += sh.x; acc[1] += sh.y; acc[2] += sh.z; acc[3] += sh.w;
+    }
+    const float4 o = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * d + n0;
+    for (int r = 0; r < tp.ranks; ++r) *reinterpret_cast<float4*>(tp.dst[r] + at) = o;
+  }
+  if (tp.dst_flag[0] == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    tp_publish_last(tp.local_count, gridDim.x * gridDim.y, tp.dst_flag, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
+}
+
+}  // namespace rx
+
+using namespace rx;
+
+RX_API int rx_moe_router(const void* x, const void* gate, const void* bias, int M, int d, int E, int topk, int mode, float scale, void* out_ids,
+                         void* out_w, void* stream) {
+  if (M < 1 || d % 256 != 0 || E < 1 || E > 512 || topk < 1 || topk > 32 || topk > E || (mode != 0 && mode != 1)) return (int)cudaErrorInvalidValue;
+  return (int)rx::launch(moe_router_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x, (const uint16_t*)gate, (const float*)bias, M,
+                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w);
+}
+
+RX_API int rx_moe_plan(const void* ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles, void* offs, void* pos_of_pair,
+                       void* pair_of_pos, void* expert_of_pos, void* tile_tab, void* total, void* stream) {
+  if (pairs < 1 || E < 1 || E > 512 || e_lo < 0 || e_hi > E || e_lo >= e_hi || tile_rows < 16 || max_tiles < 1) return (int)cudaErrorInvalidValue;
+  int threads = 32 * ((E + 31) / 32);
+  if (threads < 256) threads = 256;
+  return (int)rx::launch(moe_plan_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream, (const int*)ids, pairs, E, e_lo, e_hi, tile_rows, max_tiles,
+                         (int*)offs, (int*)pos_of_pair, (int*)pair_of_pos, (int*)expert_of_pos, (int*)tile_tab, (int*)total);
+}
+
+RX_API int rx_moe_gather_rot(const void* x, const void* ids, const void* pos_of_pair, int pairs, int topk, int d, const void* suh, void* xs, void* stream) {
+  if (pairs < 1 || d % 128 != 0) return (int)cudaErrorInvalidValue;
+  int warps = d / 128;
+  if (warps > 8) warps = 8;
+  return (int)rx::launch(moe_gather_rot_kernel, dim3(pairs), dim3(32 * warps), 0, (cudaStream_t)stream, (const uint16_t*)x, (const int*)ids,
+                         (const int*)pos_of_pair, topk, d, (const __half*)suh, (__half*)xs);
+}
+
+RX_API int rx_moe_swiglu_rot(const void* part, int S, int pairs_cap, int F, const void* expert_of_pos, const void* total, const void* svh_gu,
+                             const void* suh_down, void* xs2, void* stream) {
+  if (pairs_cap < 1 || F % 128 != 0 || S < 1) return (int)cudaErrorInvalidValue;
+  int warps = F / 128;
+  if (warps > 8) warps = 8;
+  return (int)rx::launch(moe_swiglu_rot_kernel, dim3(pairs_cap, 1), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, pairs_cap, F,
+                         (const int*)expert_of_pos, (const int*)total, (const __half*)svh_gu, (const __half*)suh_down, (__half*)xs2);
+}
+
+RX_API int rx_moe_combine_desc_size() { return (int)sizeof(CombineDst); }
+
+RX_API int rx_moe_combine(const void* part, int S, int pairs_cap, int M, int d, int topk, const void* ids, const void* w, const void* pos_of_pair,
+                          const void* svh_down, const void* shared, const void* desc, void* stream) {
+  if (desc == nullptr || M < 1 || d % 128 != 0 || S < 1) return (int)cudaErrorInvalidValue;
+  const CombineDst tp = *(const CombineDst*)desc;
+  if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
+  const int blocks = d / 128;
+  int gy = 1;
+  if (M < 64) { gy = (blocks + 3) / 4; if (gy > 16) gy = 16; }
+  int warps = (blocks + gy - 1) / gy;
+  if (warps > 8) warps = 8;
+  return (int)rx::launch(moe_combine_kernel, dim3(M, gy), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, pairs_cap, M, d, topk,
+                         (const int*)ids, (const float*)w, (const int*)pos_of_pair, (const __half*)svh_down, (const float*)shared, tp);
+}

@@ -61,6 +61,11 @@ def plan_splits(K: int, N: int, decode_class: bool) -> int:
     return _lib.load().rx_exl3_plan_splits(K, N, 1 if decode_class else 0)
 
 
+def tile_rows(rows: int) -> int:
+    """MMA N (rows per tile) the GEMM uses for a window of `rows` rows: 16..256."""
+    return _lib.load().rx_exl3_tile_rows(rows)
+
+
 def exl3_gemm(xr: torch.Tensor, w: Exl3Weight, part: torch.Tensor, splits: int, status: torch.Tensor, force_generic: bool = False) -> None:
     """part[s, row, n] = partial sums of xr @ W_q over split s.  xr: fp16 [rows, K] contiguous; part: fp32 >= splits*rows*N."""
     rows, K = xr.shape
@@ -108,10 +113,10 @@ def finish_store(part, S, M, w: Exl3Weight, out: torch.Tensor) -> None:
     _lib.count()
 
 
-def finish_add_norm_rot(part, S, M, w: Exl3Weight, h: torch.Tensor, norm_w, eps: float, suh_next, xr) -> None:
+def finish_add_norm_rot(part, S, M, w: Exl3Weight, h: torch.Tensor, norm_w, eps: float, suh_next, xr, xn_out=None) -> None:
     L = _lib.load()
     _lib.check(L.rx_finish_add_norm_rot(part.data_ptr(), S, M, w.N, w.svh.data_ptr(), _lib.ptr(w.bias), h.data_ptr(), _lib.ptr(norm_w), eps,
-                                        _lib.ptr(suh_next), _lib.ptr(xr), _lib.stream_ptr()), "rx_finish_add_norm_rot")
+                                        _lib.ptr(suh_next), _lib.ptr(xr), _lib.stream_ptr(), _lib.ptr(xn_out)), "rx_finish_add_norm_rot")
     _lib.count()
 
 

@@ -55,7 +55,14 @@ def _declare(lib):
         "rx_tp_bcast_desc_size": (c_int, []),
         "rx_tp_finish_bcast": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
         "rx_tp_allsum_add_norm_rot": (c_int, [c_void, c_void, c_int, c_int, c_void, ctypes.c_uint, c_int, c_int, c_void, c_void, c_f, c_void, c_void,
-                                              c_void, c_void]),
+                                              c_void, c_void, c_void]),
+        "rx_exl3_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_ll, c_int, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),
+        "rx_moe_router": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f, c_void, c_void, c_void]),
+        "rx_moe_plan": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
+        "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
+        "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
+        "rx_moe_combine_desc_size": (c_int, []),
+        "rx_moe_combine": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_tp_cand_push": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void]),
         "rx_tp_cand_merge": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, ctypes.c_uint, c_void, c_void, c_void, c_void]),
         "rx_dev_alloc": (c_int, [c_ll, ctypes.POINTER(ctypes.c_void_p)]),
@@ -65,7 +72,7 @@ def _declare(lib):
         "rx_embed": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void]),
         "rx_norm_rot_in": (c_int, [c_void, c_void, c_f, c_void, c_void, c_int, c_int, c_void]),
         "rx_finish_store": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_int, c_void]),
-        "rx_finish_add_norm_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void, c_void]),
+        "rx_finish_add_norm_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void]),
         "rx_finish_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_finish_qkv_rope": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void,
                                        c_void, c_void, c_void, c_void, c_void]),

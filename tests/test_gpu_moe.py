@@ -1,0 +1,95 @@
+"""Mixture-of-experts executor on the GPU against the fp32 reference: router picks, grouped EXL3 GEMM, combine, the whole model."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _i32(x):
+    return torch.tensor(x, dtype=torch.int32, device="cuda")
+
+
+def _setup(seed=3, **over):
+    import dataclasses
+    from rexl3_b200.models import moe
+    cfg = dataclasses.replace(moe.CONFIGS["test-moe"], **over)
+    w = moe.random_moe_weights(cfg, seed=seed)
+    return cfg, w, moe
+
+
+@pytest.mark.parametrize("mode", ["softmax", "sigmoid_bias"])
+def test_router_matches_reference(mode):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.models import moe
+    from rexl3_b200.ops import lib as L
+    import dataclasses
+    cfg = dataclasses.replace(moe.CONFIGS["test-moe"], n_experts=64, top_k=6, router_mode=mode, routed_scale=2.5 if mode != "softmax" else 1.0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    M, d = 37, 256
+    x = torch.randn(M, d, device="cuda", generator=g).to(torch.bfloat16)
+    gate = (torch.randn(cfg.n_experts, d, device="cuda", generator=g) / 16).to(torch.bfloat16)
+    bias = 0.1 * torch.randn(cfg.n_experts, device="cuda", generator=g) if mode != "softmax" else None
+    ids = torch.zeros(M, cfg.top_k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(M, cfg.top_k, dtype=torch.float32, device="cuda")
+    lib = L.load()
+    L.check(lib.rx_moe_router(x.data_ptr(), gate.data_ptr(), L.ptr(bias), M, d, cfg.n_experts, cfg.top_k, 0 if mode == "softmax" else 1,
+                              cfg.routed_scale, ids.data_ptr(), wts.data_ptr(), L.stream_ptr()), "router")
+    torch.cuda.synchronize()
+    ri, rw = moe.route_reference(x.float() @ gate.float().T, cfg, bias)
+    assert torch.equal(ids.long(), ri)
+    torch.testing.assert_close(wts, rw, rtol=2e-3, atol=1e-5)
+
+
+def test_moe_model_matches_reference_prefill_and_decode():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    cfg, w, moe = _setup()
+    ref = moe.ReferenceMoE(w, device="cuda")
+    m = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, size=90).tolist()
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[0, :2] = _i32([3, 7])
+    T = len(prompt)
+    pos = list(range(T))
+    slots = [int(bt[0, p // 64]) * 64 + p % 64 for p in pos]
+    pf = dict(seq_ids=_i32([0]), q_start=_i32([0]), q_len=_i32([T]), pos0=_i32([0]), nseq=1, max_qlen=T)
+    args = (_i32(prompt), _i32(pos), _i32(slots), _i32([0] * T), _i32([p + 1 for p in pos]), bt)
+    got = m.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+    m.check()
+    want = ref.forward_seq(0, prompt, 0)
+    scale = want.abs().max().item()
+    # a token whose router scores are nearly tied may pick another expert than the fp32 reference: allow a few rows to differ
+    err = (got - want).abs().amax(dim=1) / scale
+    assert (err < 0.05).float().mean().item() > 0.9, err
+    assert err[-1].item() < 0.05
+    t0 = int(want[-1].argmax())
+    for step in range(3):
+        p = T + step
+        a2 = (_i32([t0]), _i32([p]), _i32([int(bt[0, p // 64]) * 64 + p % 64]), _i32([0]), _i32([p + 1]), bt)
+        g1 = m.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+        m.check()
+        w0 = ref.forward_seq(0, [t0], p)[0]
+        assert (g1[0] - w0).abs().max().item() < 0.05 * scale
+        t0 = int(w0.argmax())
+
+
+def test_moe_draft_layers_match_reference():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    cfg, w, moe = _setup(seed=5)
+    ref = moe.ReferenceMoE(w, device="cuda")
+    m = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    prompt = np.random.default_rng(1).integers(0, cfg.vocab, size=40).tolist()
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[0, :1] = _i32([2])
+    T = len(prompt)
+    pos = list(range(T))
+    pf = dict(seq_ids=_i32([0]), q_start=_i32([0]), q_len=_i32([T]), pos0=_i32([0]), nseq=1, max_qlen=T)
+    args = (_i32(prompt), _i32(pos), _i32([2 * 64 + p for p in pos]), _i32([0] * T), _i32([p + 1 for p in pos]), bt)
+    got = m.forward_rows(*args, prefill=pf, n_layers=cfg.draft_layers, logit_rows=torch.tensor([T - 1], device="cuda"))[:, :cfg.vocab].clone()
+    m.check()
+    want = ref.forward_seq(0, prompt, 0, n_layers=cfg.draft_layers)[-1]
+    assert (got[0] - want).abs().max().item() < 0.05 * want.abs().max().item()
