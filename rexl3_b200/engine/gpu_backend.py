@@ -21,8 +21,11 @@ CTX_BUCKET = 2048   # decode graphs are captured per (rows, candidate count, con
 class DenseGpuBackend(Backend):
     name = "cuda"
 
-    def __init__(self, model: DenseGPU, max_slots: int | None = None, use_graphs: bool = True):
+    def __init__(self, model: DenseGPU, max_slots: int | None = None, use_graphs: bool = True, self_draft: bool = False):
+        """`self_draft`: offer drafts from the model's first `cfg.draft_layers` layers plus the shared final norm and head (the draft
+        shares the target's KV cache for those layers, so it needs no state of its own)."""
         self.m = model
+        self.self_draft = bool(self_draft and getattr(model.cfg, "draft_layers", 0) > 0)
         self.cfg = model.cfg
         self.vocab_size = model.cfg.vocab
         self.max_slots = max_slots or model.max_seqs
@@ -46,6 +49,15 @@ class DenseGpuBackend(Backend):
         self.h_cand_vals = torch.zeros(256, 64, dtype=torch.float32).pin_memory()
         self.h_status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.graphs = {}
+        self.draft_graphs = {}
+        self.draft_steps = 0
+        self.DK = 8                                            # most chained drafts one ask may get
+        if self.self_draft:
+            self.h_draft = torch.zeros(self.DK, 5, self.max_slots, dtype=torch.int32).pin_memory()
+            self.d_draft = torch.zeros(self.DK, 5, self.max_slots, dtype=torch.int32, device=dev)
+            self.d_draft_ids = torch.zeros(self.DK, self.max_slots, dtype=torch.int32, device=dev)
+            self.d_draft_vals = torch.zeros(self.DK, self.max_slots, dtype=torch.float32, device=dev)
+            self.h_draft_ids = torch.zeros(self.DK, self.max_slots, dtype=torch.int32).pin_memory()
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.graph_replays = 0
@@ -248,6 +260,66 @@ class DenseGpuBackend(Backend):
         self.h_bt[slot].zero_()
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
+
+    # ------------------------------------------------------------------ self-speculative drafter
+    def supports_native_draft(self) -> bool:
+        return self.self_draft
+
+    def _draft_chain(self, n: int, k: int, bucket: int) -> None:
+        """k chained greedy draft steps over n sequences, ids handed from step to step on the device."""
+        m, d = self.m, self.d_draft
+        D = m.cfg.draft_layers
+        for j in range(k):
+            ids = d[0, 0, :n] if j == 0 else self.d_draft_ids[j - 1, :n]
+            logits = m.forward_rows(ids, d[j, 1, :n], d[j, 2, :n], d[j, 3, :n], d[j, 4, :n], self.d_bt, max_ctx=bucket, n_layers=D)
+            if m.cfg.vocab_padded != m.cfg.vocab:
+                logits[:, m.cfg.vocab:] = float("-inf")
+            m.K.topk(logits, 1, m.topk_scratch, self.d_draft_ids[j, :n].view(n, 1), self.d_draft_vals[j, :n].view(n, 1))
+
+    def propose_batch(self, asks):
+        if not self.self_draft or not asks:
+            return {}
+        from .backend import DraftOffer
+        n = len(asks)
+        k = min(self.DK, max(a.max_drafts for a in asks))
+        if k <= 0:
+            return {}
+        h = self.h_draft.numpy()
+        top = 0
+        for i, a in enumerate(asks):
+            slot, p0 = a.slot, self.len[a.slot]
+            if p0 != len(a.context) - 1:
+                raise BackendError(f"draft for slot {slot} at {len(a.context) - 1} but the slot holds {p0} tokens", fatal=False)
+            self._ensure(slot, p0 + k + 1)
+            pg = self.pages[slot]
+            for j in range(k):
+                pos = p0 + j
+                h[j, 0, i] = a.context[-1] if j == 0 else 0
+                h[j, 1, i], h[j, 2, i], h[j, 3, i], h[j, 4, i] = pos, pg[pos // PAGE] * PAGE + pos % PAGE, slot, pos + 1
+            top = max(top, p0 + k)
+        bucket = min(self.m.max_ctx_alloc, (top + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
+        self.d_draft[:k, :, :n].copy_(self.h_draft[:k, :, :n], non_blocking=True)
+        self.h2d_bytes += k * 5 * n * 4
+        self._sync_bt()
+        if self.use_graphs:
+            key = (n, k, bucket)
+            g = self.draft_graphs.get(key)
+            if g is None:
+                self._draft_chain(n, k, bucket)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._draft_chain(n, k, bucket)
+                self.draft_graphs[key] = g
+            g.replay()
+        else:
+            self._draft_chain(n, k, bucket)
+        self.h_draft_ids[:k, :n].copy_(self.d_draft_ids[:k, :n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += k * n * 4
+        self.draft_steps += k
+        out = self.h_draft_ids.numpy()
+        return {a.slot: DraftOffer([int(out[j, i]) for j in range(min(k, a.max_drafts))]) for i, a in enumerate(asks)}
 
     # ------------------------------------------------------------------ prefix cache: pages are shared by refcount
     def prefix_block_tokens(self):

@@ -93,3 +93,34 @@ def test_moe_draft_layers_match_reference():
     m.check()
     want = ref.forward_seq(0, prompt, 0, n_layers=cfg.draft_layers)[-1]
     assert (got[0] - want).abs().max().item() < 0.05 * want.abs().max().item()
+
+
+def test_self_speculative_draft_is_exact():
+    """Engine over the MoE backend: drafts from the first layers change the schedule, never the tokens."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    from rexl3_b200.sampling import GREEDY
+    cfg, w, moe = _setup(seed=9)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (50, 21)]
+    outs = {}
+    for mode in ("none", "self"):
+        m = moe.MoEGPU(w, num_pages=24, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+        be = DenseGpuBackend(m, max_slots=4, self_draft=(mode == "self"))
+        eng = Engine(be, None, window_rows=32, prefill_chunk=256, spec=mode, max_drafts=3)
+        for i, p in enumerate(prompts):
+            eng.submit(Request(f"r{i}", p, 10, GREEDY))
+        got = {f"r{i}": [] for i in range(len(prompts))}
+        for _ in range(200):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                if ev.kind == "tokens":
+                    got[ev.id].extend(ev.tokens)
+                assert ev.kind != "error", ev.message
+        outs[mode] = got
+        if mode == "self":
+            assert eng.counters["drafted"] > 0 and be.draft_steps > 0
+    assert outs["none"] == outs["self"]
