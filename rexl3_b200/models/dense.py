@@ -359,6 +359,9 @@ class DenseGPU:
         self.K.exl3_gemm(xr, w, self.part, s, self.status)
         return s
 
+    def _begin_forward(self) -> None:
+        """Hook run once per forward before the first kernel (multi-rank executors bump their ticket epoch here)."""
+
     def _ffn(self, li, L, M, cls, s_o, h, xr_d, xr_f, next_norm, next_suh):
         """Everything between the o_proj GEMM (its partials are in self.part, `s_o` splits) and the next layer's rotated input."""
         cfg, K = self.cfg, self.K
@@ -368,8 +371,23 @@ class DenseGPU:
         s = self._linear(xr_f, L["down"], M, cls, "down")
         K.finish_add_norm_rot(self.part, s, M, L["down"], h, next_norm, cfg.eps, next_suh, xr_d)
 
-    def forward_rows(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True,
-                     n_layers=None):
+    def _ffn_phases(self, *a):
+        """Generator form of `_ffn`: yields wherever the ranks of a multi-rank executor must all have launched the previous kernels
+        before one of them may launch the next (a one-GPU loopback group steps its ranks there).  One rank: no such point."""
+        self._ffn(*a)
+        return
+        yield
+
+    def forward_rows(self, *a, **kw):
+        g = self.forward_phases(*a, **kw)
+        try:
+            while True:
+                next(g)
+        except StopIteration as e:
+            return e.value
+
+    def forward_phases(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True,
+                       n_layers=None):
         """Run all layers over M rows.
 
         ids, positions, slots, row_seq, ctx_len: int32 device tensors [M] (slot = physical KV slot page*64+offset of the row's
@@ -389,6 +407,7 @@ class DenseGPU:
         xr_f = self.xr2[:M * F].view(M, F)
         q = self.q[:M]
         scale = 1.0 / math.sqrt(cfg.head_dim)
+        self._begin_forward()
         K.embed(ids, self.embed, h)
         L0 = self.layers[0]
         K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)
@@ -408,7 +427,7 @@ class DenseGPU:
                 K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
             s = self._linear(xr_a, L["o"], M, cls, "o")
             nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
-            self._ffn(li, L, M, cls, s, h, xr_d, xr_f, nn_, ns_)
+            yield from self._ffn_phases(li, L, M, cls, s, h, xr_d, xr_f, nn_, ns_)
         if not want_logits:
             return None
         if logit_rows is not None:

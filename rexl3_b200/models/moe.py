@@ -225,7 +225,7 @@ class MoEGPU(DenseGPU):
         cfg, K, dev = self.cfg, self.K, self.device
         super()._alloc_scratch(R)       # the dense scratch sizes its (unused) FFN buffers from cfg.ffn; the expert buffers follow
         k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
-        self.pairs_cap = R * k
+        self.pairs_cap = {"decode": min(R, 256) * k, "prefill": R * k}   # rows of the sorted-pair buffers a launch of the class addresses
         self.moe_splits = {}
         part = 0
         for cls, rows in (("decode", min(R, 256)), ("prefill", R)):
@@ -242,7 +242,7 @@ class MoEGPU(DenseGPU):
         self.xn = torch.empty(R, d, dtype=torch.bfloat16, device=dev)
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
         self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
-        self.max_tiles_decode = min(E, 256 * k)
+        self.max_tiles_decode = E + (min(R, 256) * k + 31) // 32      # windows use 16- or 32-row tiles: small tiles keep two CTAs per SM
         self.max_tiles_prefill = E + (R * k + 127) // 128
         self.tile_tab = i32(3 * max(self.max_tiles_decode, self.max_tiles_prefill))
         self.xs = torch.zeros(R * k, d, dtype=torch.float16, device=dev)
@@ -252,20 +252,29 @@ class MoEGPU(DenseGPU):
         self._dst.ranks, self._dst.rank, self._dst.rows_cap = 1, 0, R
         self._dst.dst[0] = self.slot.data_ptr()
 
+    def _begin_forward(self) -> None:
+        if self.ep is not None:
+            self.ep.begin()
+
     # ------------------------------------------------------------------ the routed FFN
-    def _ffn(self, li, L, M, cls, s_o, h, xr_d, xr_f, next_norm, next_suh):
+    def _ffn(self, *a):
+        for _ in self._ffn_phases(*a):
+            pass
+
+    def _ffn_phases(self, li, L, M, cls, s_o, h, xr_d, xr_f, next_norm, next_suh):
         cfg, K = self.cfg, self.K
         Lib = _lib.load()
         st = _lib.stream_ptr()
         k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
         pairs = M * k
+        cap = self.pairs_cap[cls]
         xn = self.xn[:M]
         K.finish_add_norm_rot(self.part, s_o, M, L["o"], h, L["ffn_norm"], cfg.eps, None, None, xn_out=xn)
         _lib.check(Lib.rx_moe_router(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
                                      0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st),
                    "rx_moe_router")
         if cls == "decode":
-            tile_rows, max_tiles = K.tile_rows(M), self.max_tiles_decode
+            tile_rows, max_tiles = (16 if M <= 16 else 32), self.max_tiles_decode
         else:
             tile_rows, max_tiles = 128, self.max_tiles_prefill
         _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, max_tiles, self.offs.data_ptr(),
@@ -277,24 +286,28 @@ class MoEGPU(DenseGPU):
         _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), self.pick_ids.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, ctypes.c_void_p(suh_gu),
                                          self.xs.data_ptr(), st), "rx_moe_gather_rot")
         s_gu, s_dn = self.moe_splits[cls]
-        self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows)
-        _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), s_gu, self.pairs_cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
+        self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows, cap)
+        _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), s_gu, cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
                                          ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
                                          self.xs2.data_ptr(), st), "rx_moe_swiglu_rot")
-        self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows)
+        self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows, cap)
         dst, ar, flags, ranks, rows_cap, epoch, use = self._combine_target(li, M)
-        _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), s_dn, self.pairs_cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(),
+        _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), s_dn, cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(),
                                       self.pos_of_pair.data_ptr(), ctypes.c_void_p(dn.svh.data_ptr() - 2 * self.e_lo * dn.N), None, ctypes.byref(dst), st),
                    "rx_moe_combine")
+        if self.ep is not None:
+            yield          # every rank's combine must be in flight before any rank's sum may wait for it
         _lib.check(Lib.rx_tp_allsum_add_norm_rot(ar, flags, ranks, rows_cap, epoch, use, M, d, h.data_ptr(), next_norm.data_ptr(), cfg.eps,
                                                  next_suh.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(), st, None), "rx_tp_allsum_add_norm_rot")
         _lib.count(7)
 
-    def _grouped_shifted(self, xs, st: _ExpertStack, splits, max_tiles, tile_rows):
+    def _grouped_shifted(self, xs, st: _ExpertStack, splits, max_tiles, tile_rows, cap):
         """The tile table names GLOBAL expert ids; the stack starts at expert e_lo."""
         L = _lib.load()
         base = st.trellis.data_ptr() - 2 * self.e_lo * st.expert_elems
-        _lib.check(L.rx_exl3_gemm_grouped(xs.data_ptr(), self.pairs_cap, st.K, ctypes.c_void_p(base), st.expert_elems, st.N, st.twice,
+        if splits * cap * st.N > self.part.numel():
+            raise _lib.KernelError(f"grouped GEMM partials ({splits} x {cap} x {st.N}) exceed the scratch buffer")
+        _lib.check(L.rx_exl3_gemm_grouped(xs.data_ptr(), cap, st.K, ctypes.c_void_p(base), st.expert_elems, st.N, st.twice,
                                           self.K.CB_ID[st.codebook], self.part.data_ptr(), splits, self.tile_tab.data_ptr(), max_tiles, tile_rows,
                                           self.status.data_ptr(), _lib.stream_ptr()), "rx_exl3_gemm_grouped")
 

@@ -47,7 +47,8 @@ def test_moe_model_matches_reference_prefill_and_decode():
         pytest.skip("needs a CUDA device")
     cfg, w, moe = _setup()
     ref = moe.ReferenceMoE(w, device="cuda")
-    m = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    # prefill scratch larger than the decode class: the two classes address the sorted-pair buffers with different strides
+    m = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=1024)
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, cfg.vocab, size=90).tolist()
     bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
@@ -124,3 +125,53 @@ def test_self_speculative_draft_is_exact():
         if mode == "self":
             assert eng.counters["drafted"] > 0 and be.draft_steps > 0
     assert outs["none"] == outs["self"]
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_expert_parallel_loopback_matches_single(ranks):
+    """R expert-parallel ranks stepped phase by phase on one GPU: bit-identical logits on every rank, equal to the one-GPU
+    executor up to the order of the expert sum."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.parallel import ep
+    cfg, w, moe = _setup(seed=4)
+    single = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    comms = ep.make_loopback(cfg, ranks, 256)
+    shards = [moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256,
+                         experts=ep.expert_range(cfg.n_experts, r, ranks), ep=comms[r]) for r in range(ranks)]
+    prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=70).tolist()
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[0, :2] = _i32([3, 7])
+    T = len(prompt)
+    pos = list(range(T))
+    slots = [int(bt[0, p // 64]) * 64 + p % 64 for p in pos]
+    pf = dict(seq_ids=_i32([0]), q_start=_i32([0]), q_len=_i32([T]), pos0=_i32([0]), nseq=1, max_qlen=T)
+    args = (_i32(prompt), _i32(pos), _i32(slots), _i32([0] * T), _i32([p + 1 for p in pos]), bt)
+
+    def run(a, **kw):
+        gens = [s.forward_phases(*a, **kw) for s in shards]
+        outs = [None] * ranks
+        live = True
+        while live:
+            for r, g in enumerate(gens):
+                try:
+                    next(g)
+                except StopIteration as e:
+                    outs[r] = e.value[:, :cfg.vocab].clone()
+                    live = False
+        torch.cuda.synchronize()
+        for s in shards:
+            s.check()
+        return outs
+
+    outs = run(args, prefill=pf)
+    want = single.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    scale = want.abs().max().item()
+    assert (outs[0] - want).abs().max().item() < 0.02 * scale
+    p = T
+    a2 = (_i32([5]), _i32([p]), _i32([int(bt[0, p // 64]) * 64 + p % 64]), _i32([0]), _i32([p + 1]), bt)
+    o2 = run(a2, max_ctx=256)
+    w2 = single.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+    assert torch.equal(o2[0], o2[-1]) and (o2[0] - w2).abs().max().item() < 0.02 * scale
