@@ -1,0 +1,525 @@
+"""MLA + MoE decoder (DeepSeek-V3 shape: 61 layers, d_model 7168, 128 heads, q_lora 1536, kv_lora 512, rope 64, nope 128, v 128;
+3 dense layers of FFN 18432, then 256 routed experts of FFN 2048 top-8 with a sigmoid+bias router and one shared expert).
+Attention and shared weights are EXL3 (2.25 bpw = a mix of 2.0 and 2.5 bit tensors), routed experts MXFP4.
+
+Per layer on the GPU:
+  fused q_a | kv_a EXL3 GEMM (the 576-wide kv_a is padded to 640 columns with zero scales; EXL3 needs multiples of 128) ->
+  row kernel (q_a RMSNorm + q_b's rotation; latent RMSNorm + RoPE into the paged latent cache) -> q_b EXL3 GEMM -> RoPE of the
+  rope part, per-head absorb GEMM (q_nope @ W_uk) -> split-KV latent attention -> per-head expand GEMM (@ W_uv) -> o_proj
+  rotation -> o_proj EXL3 GEMM -> residual / norm -> dense SwiGLU FFN, or: router -> plan -> MXFP4 grouped gate|up -> SwiGLU ->
+  MXFP4 grouped down -> weighted sum + shared expert -> residual / norm.
+Parallel form: heads [h_lo, h_hi) and experts [e_lo, e_hi) live on this rank; the o_proj partial rows and the MoE partial rows
+are exchanged with the one-shot all-reduce (replicated residual stream, replicated latent cache).
+Semantics: reference crates/cuda/csrc/mla_gated.cu, ling_mla_attn.cu, glm_p2_mla.cu (MLA), moe_router.cu:3-13, fp4_linear.cu:5-18.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..format import exl3, mxfp4
+from ..ops import kernels as K
+from ..ops import lib as _lib
+from .dense import PAGE, HostLinear, _bf16_round, random_linear
+from .moe import CombineDst, route_reference
+
+
+@dataclass
+class MlaConfig:
+    n_layers: int = 61
+    n_dense: int = 3
+    d_model: int = 7168
+    n_heads: int = 128
+    q_lora: int = 1536
+    kv_lora: int = 512
+    rope_dim: int = 64
+    nope_dim: int = 128
+    v_dim: int = 128
+    dense_ffn: int = 18432
+    n_experts: int = 256
+    top_k: int = 8
+    expert_ffn: int = 2048
+    shared_ffn: int = 2048
+    routed_scale: float = 2.5
+    vocab: int = 129280
+    eps: float = 1e-6
+    rope_theta: float = 1e4
+    bits_a: float = 2.0        # 2.25 bpw overall: the big projections at 2.0 ...
+    bits_b: float = 2.5        # ... and the small / sensitive ones at 2.5 (half widths use the mul1 codebook)
+    name: str = "mla-moe-671b"
+
+    @property
+    def vocab_padded(self):
+        return (self.vocab + 127) // 128 * 128
+
+    def kv_bytes_per_token(self):
+        return 9 * 64 * 2 * self.n_layers
+
+
+CONFIGS = {
+    "mla-moe-671b": MlaConfig(),
+    "test-mla": MlaConfig(n_layers=3, n_dense=1, d_model=256, n_heads=16, dense_ffn=256, n_experts=8, top_k=2, expert_ffn=128, shared_ffn=128,
+                          vocab=1024, name="test-mla"),
+}
+assert MlaConfig().q_lora == 1536 and MlaConfig().kv_lora == 512 and MlaConfig().rope_dim == 64      # the row kernel is written for these
+
+
+@dataclass
+class HostMlaLayer:
+    attn_norm: np.ndarray
+    qkv_a: HostLinear            # d -> 1536 | 512 | 64 | pad 64
+    q_norm: np.ndarray
+    kv_norm: np.ndarray
+    q_b: HostLinear              # 1536 -> H * 192
+    w_uk: np.ndarray             # f32 [H, 128, 512] (bf16-rounded)
+    w_uv: np.ndarray             # f32 [H, 512, 128]
+    o: HostLinear                # H * 128 -> d
+    ffn_norm: np.ndarray
+    gate_up: HostLinear = None   # dense layers, or the shared expert of a routed layer
+    down: HostLinear = None
+    router: np.ndarray = None
+    router_bias: np.ndarray = None
+    ex_gu: list = field(default_factory=list)     # per expert (packed uint8 [2F, d/2], scales uint8 [2F, d/32])
+    ex_down: list = field(default_factory=list)   # per expert (packed uint8 [d, F/2], scales uint8 [d, F/32])
+
+
+@dataclass
+class HostMla:
+    cfg: MlaConfig
+    embed: np.ndarray
+    layers: list
+    final_norm: np.ndarray
+    lm_head: HostLinear
+
+
+def random_mla_weights(cfg: MlaConfig, seed: int = 0) -> HostMla:
+    rng = np.random.default_rng(seed)
+    d, H = cfg.d_model, cfg.n_heads
+    nrm = lambda n: _bf16_round(1.0 + 0.1 * rng.normal(size=n))  # noqa: E731
+    layers = []
+    for li in range(cfg.n_layers):
+        qkv_a = random_linear(d, 2176, cfg.bits_b, rng, "mul1", 1.0 / math.sqrt(d), zero_cols_from=2112)
+        q_b = random_linear(1536, H * 192, cfg.bits_a, rng, "3inst", 1.0 / math.sqrt(1536))
+        o = random_linear(H * 128, d, cfg.bits_a, rng, "3inst", 0.5 / math.sqrt(H * 128))
+        lay = HostMlaLayer(nrm(d), qkv_a, nrm(1536), nrm(512), q_b, _bf16_round(rng.normal(0, 1 / math.sqrt(128), size=(H, 128, 512))),
+                           _bf16_round(rng.normal(0, 1 / math.sqrt(512), size=(H, 512, 128))), o, nrm(d))
+        if li < cfg.n_dense:
+            F = cfg.dense_ffn
+            lay.gate_up = random_linear(d, 2 * F, cfg.bits_a, rng, "3inst", 1.0 / math.sqrt(d))
+            lay.down = random_linear(F, d, cfg.bits_b, rng, "mul1", 0.5 / math.sqrt(F))
+        else:
+            F, Fs = cfg.expert_ffn, cfg.shared_ffn
+            lay.gate_up = random_linear(d, 2 * Fs, cfg.bits_a, rng, "3inst", 1.0 / math.sqrt(d))
+            lay.down = random_linear(Fs, d, cfg.bits_b, rng, "mul1", 0.5 / math.sqrt(Fs))
+            lay.router = _bf16_round(rng.normal(0, 1.0 / math.sqrt(d), size=(cfg.n_experts, d)))
+            lay.router_bias = rng.normal(0, 0.1, size=cfg.n_experts).astype(np.float32)
+            for _ in range(cfg.n_experts):
+                lay.ex_gu.append(mxfp4.quantize(rng.normal(0, 1.0 / math.sqrt(d), size=(2 * F, d)).astype(np.float32)))
+                lay.ex_down.append(mxfp4.quantize(rng.normal(0, 0.5 / math.sqrt(F), size=(d, F)).astype(np.float32)))
+        layers.append(lay)
+    head = random_linear(d, cfg.vocab_padded, cfg.bits_b, rng, "mul1", 1.0 / math.sqrt(d), zero_cols_from=cfg.vocab if cfg.vocab_padded != cfg.vocab else None)
+    return HostMla(cfg, _bf16_round(rng.normal(0, 1.0, size=(cfg.vocab, d)).astype(np.float32)), layers, nrm(d), head)
+
+
+def mla_inv_freq(cfg: MlaConfig) -> np.ndarray:
+    i = np.arange(0, cfg.rope_dim, 2, dtype=np.float32)
+    return (1.0 / (np.float32(cfg.rope_theta) ** (i / np.float32(cfg.rope_dim)))).astype(np.float32)
+
+
+class ReferenceMla:
+    """fp32 oracle (non-absorbed arithmetic order is not required: the absorbed form is algebraically the same and is what runs)."""
+
+    def __init__(self, w: HostMla, device="cpu"):
+        self.cfg, self.device = w.cfg, device
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device)  # noqa: E731
+        self.embed = t(w.embed)
+        self.layers = []
+        for lay in w.layers:
+            L = dict(attn_norm=t(lay.attn_norm), qkv_a=t(lay.qkv_a.dense()), q_norm=t(lay.q_norm), kv_norm=t(lay.kv_norm), q_b=t(lay.q_b.dense()),
+                     w_uk=t(lay.w_uk), w_uv=t(lay.w_uv), o=t(lay.o.dense()), ffn_norm=t(lay.ffn_norm), gate_up=t(lay.gate_up.dense()),
+                     down=t(lay.down.dense()), router=None)
+            if lay.router is not None:
+                L.update(router=t(lay.router), router_bias=t(lay.router_bias), gu=[t(mxfp4.dequant(*e)) for e in lay.ex_gu],
+                         dn=[t(mxfp4.dequant(*e)) for e in lay.ex_down])
+            self.layers.append(L)
+        self.final_norm = t(w.final_norm)
+        self.lm_head = t(w.lm_head.dense())[:, :w.cfg.vocab]
+        self.inv_freq = torch.from_numpy(mla_inv_freq(w.cfg)).to(device)
+        self.kv = {}
+
+    @staticmethod
+    def _rms(x, w, eps):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    def _rope(self, x, pos):
+        ang = pos.to(torch.float32)[:, None] * self.inv_freq[None, :]
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        while cos.dim() < x.dim():
+            cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+        x1, x2 = x[..., :32], x[..., 32:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+    @torch.no_grad()
+    def forward_seq(self, seq, tokens, start: int) -> torch.Tensor:
+        cfg = self.cfg
+        ids = torch.as_tensor(tokens, dtype=torch.long, device=self.device)
+        T, H = ids.shape[0], cfg.n_heads
+        pos = torch.arange(start, start + T, device=self.device)
+        h = self.embed[ids]
+        if seq not in self.kv:
+            self.kv[seq] = [(torch.zeros(0, 512, device=self.device), torch.zeros(0, 64, device=self.device)) for _ in self.layers]
+        for li, L in enumerate(self.layers):
+            x = self._rms(h, L["attn_norm"], cfg.eps)
+            a = x @ L["qkv_a"]
+            q = (self._rms(a[:, :1536], L["q_norm"], cfg.eps) @ L["q_b"]).view(T, H, 192)
+            c = self._rms(a[:, 1536:2048], L["kv_norm"], cfg.eps)
+            kr = self._rope(a[:, 2048:2112], pos)
+            pc, pr = self.kv[seq][li]
+            cc, rr = torch.cat([pc[:start], c]), torch.cat([pr[:start], kr])
+            self.kv[seq][li] = (cc, rr)
+            q_lat = torch.einsum("thk,hkc->thc", q[..., :128], L["w_uk"])
+            q_rope = self._rope(q[..., 128:], pos)
+            s = (torch.einsum("thc,sc->hts", q_lat, cc) + torch.einsum("thr,sr->hts", q_rope, rr)) / math.sqrt(192)
+            kpos = torch.arange(cc.shape[0], device=self.device)
+            s = s.masked_fill((kpos[None, :] > pos[:, None])[None], float("-inf"))
+            o_lat = torch.einsum("hts,sc->thc", torch.softmax(s, dim=-1), cc)
+            o = torch.einsum("thc,hcv->thv", o_lat, L["w_uv"]).reshape(T, H * 128)
+            h = h + o @ L["o"]
+            x = self._rms(h, L["ffn_norm"], cfg.eps)
+            gu = x @ L["gate_up"]
+            F = gu.shape[1] // 2
+            y = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
+            if L["router"] is not None:
+                mc = _RouteCfg(cfg)
+                ids_e, wts = route_reference(x @ L["router"].T, mc, L["router_bias"])
+                Fe = cfg.expert_ffn
+                for t in range(T):
+                    for j in range(cfg.top_k):
+                        e = int(ids_e[t, j])
+                        g = L["gu"][e] @ x[t]
+                        y[t] += wts[t, j] * (L["dn"][e] @ (torch.nn.functional.silu(g[:Fe]) * g[Fe:]))
+            h = h + y
+        return (self._rms(h, self.final_norm, cfg.eps) @ self.lm_head).float()
+
+
+class _RouteCfg:
+    def __init__(self, cfg):
+        self.router_mode, self.top_k, self.routed_scale = "sigmoid_bias", cfg.top_k, cfg.routed_scale
+
+
+class _Local:
+    """One-rank stand-in for the exchange object: both collectives write a local slot."""
+
+    def __init__(self, rows_cap, d, device):
+        self.slot = torch.zeros(rows_cap, d, dtype=torch.float32, device=device)
+        self.dst = CombineDst()
+        self.dst.ranks, self.dst.rank, self.dst.rows_cap = 1, 0, rows_cap
+        self.dst.dst[0] = self.slot.data_ptr()
+        self.rows_cap = rows_cap
+
+    def begin(self):
+        pass
+
+    def target(self, use, M):
+        return self.dst, self.slot.data_ptr(), None, 1, self.rows_cap, None, 0
+
+
+class MlaMoEGPU:
+    def __init__(self, w: "HostMla | MlaConfig", num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256, device="cuda",
+                 max_prefill_rows: int = 4096, seed: int = 0, heads=None, experts=None, comm=None, rank: int = 0):
+        self.K = K
+        self.device = device
+        self.cfg = cfg = w if isinstance(w, MlaConfig) else w.cfg
+        self.h_lo, self.h_hi = heads or (0, cfg.n_heads)
+        self.e_lo, self.e_hi = experts or (0, cfg.n_experts)
+        self.Hl = self.h_hi - self.h_lo
+        self.rank = rank
+        if self.Hl % 16:
+            raise ValueError("a rank must own a multiple of 16 heads")
+        self.num_pages, self.max_seqs, self.max_blocks = num_pages, max_seqs, max_blocks_per_seq
+        self.max_rows = R = max(max_rows, max_prefill_rows)
+        self.max_ctx_alloc = max_blocks_per_seq * PAGE
+        if isinstance(w, MlaConfig):
+            self._load_random(seed)
+        else:
+            self._load_host(w)
+        self.inv_freq = torch.from_numpy(mla_inv_freq(cfg)).to(device)
+        self.cache = [torch.zeros(num_pages, 9, PAGE, 64, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        self.tc = [K.KvTensorMap(c) for c in self.cache]
+        self.status = K.new_status(device)
+        self.local = _Local(R, cfg.d_model, device)       # dense FFN layers are computed on every rank: their sum needs no exchange
+        self.comm = comm or self.local
+        self._alloc(R)
+
+    # ------------------------------------------------------------------ weights
+    def _load_host(self, w: HostMla):
+        dev = self.device
+        t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=dev, dtype=dt)  # noqa: E731
+        up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, dev)  # noqa: E731
+        hl, hh, el, eh = self.h_lo, self.h_hi, self.e_lo, self.e_hi
+        self.embed = t(w.embed, torch.bfloat16)
+        self.layers = []
+        for lay in w.layers:
+            qb = lay.q_b
+            qb_l = HostLinear(np.ascontiguousarray(qb.trellis[:, hl * 12:hh * 12]), qb.suh, np.ascontiguousarray(qb.svh[hl * 192:hh * 192]), None, qb.codebook)
+            o = lay.o
+            o_l = HostLinear(np.ascontiguousarray(o.trellis[hl * 8:hh * 8]), np.ascontiguousarray(o.suh[hl * 128:hh * 128]), o.svh, None, o.codebook)
+            L = dict(attn_norm=t(lay.attn_norm, torch.bfloat16), qkv_a=up(lay.qkv_a), q_norm=t(lay.q_norm, torch.bfloat16), kv_norm=t(lay.kv_norm, torch.bfloat16),
+                     q_b=up(qb_l), w_uk=t(lay.w_uk[hl:hh], torch.bfloat16), w_uv=t(lay.w_uv[hl:hh], torch.bfloat16), o=up(o_l),
+                     ffn_norm=t(lay.ffn_norm, torch.bfloat16), gate_up=up(lay.gate_up), down=up(lay.down), router=None)
+            if lay.router is not None:
+                L.update(router=t(lay.router, torch.bfloat16), router_bias=t(lay.router_bias, torch.float32),
+                         gu_w=torch.from_numpy(np.stack([e[0].view(np.uint8) for e in lay.ex_gu[el:eh]])).to(dev),
+                         gu_s=torch.from_numpy(np.stack([e[1] for e in lay.ex_gu[el:eh]])).to(dev),
+                         dn_w=torch.from_numpy(np.stack([e[0].view(np.uint8) for e in lay.ex_down[el:eh]])).to(dev),
+                         dn_s=torch.from_numpy(np.stack([e[1] for e in lay.ex_down[el:eh]])).to(dev))
+            self.layers.append(L)
+        self.final_norm = t(w.final_norm, torch.bfloat16)
+        self.lm_head = up(w.lm_head)
+
+    def _load_random(self, seed: int):
+        """Random-init model on the device: shared tensors from `seed` (identical on every rank), this rank's heads and experts from
+        rank-specific streams.  Random nibbles and scale bytes in a trained model's range are valid MXFP4."""
+        cfg, dev = self.cfg, self.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        gl = torch.Generator(device=dev).manual_seed(seed * 7919 + 101 + self.h_lo * 131 + self.e_lo)
+        d, Hl = cfg.d_model, self.Hl
+        sg = lambda n, gen: (torch.randint(0, 2, (n,), device=dev, generator=gen) * 2 - 1)  # noqa: E731
+
+        def lin(k, n, scale, bits, gen, suh=None):
+            b = exl3.Bits.of(bits)
+            tr = torch.randint(-32768, 32768, (k // 16, n // 16, b.tile_words), dtype=torch.int16, device=dev, generator=gen)
+            su = sg(k, gen).to(torch.float16) if suh is None else suh
+            return K.Exl3Weight(tr, su, (sg(n, gen) * scale).to(torch.float16), None, "3inst" if b.is_integer else "mul1")
+        nrm = lambda n: (1.0 + 0.1 * torch.randn(n, device=dev, generator=g)).to(torch.bfloat16)  # noqa: E731
+
+        def mx(e, n, k, amp):
+            wq = torch.randint(0, 256, (e, n, k // 2), dtype=torch.uint8, device=dev, generator=gl)
+            sc = torch.randint(0, 3, (e, n, k // 32), dtype=torch.uint8, device=dev, generator=gl) + int(127 + math.log2(amp)) - 3
+            return wq, sc.to(torch.uint8)
+        self.embed = torch.randn(cfg.vocab, d, device=dev, generator=g).to(torch.bfloat16)
+        self.layers = []
+        E = self.e_hi - self.e_lo
+        for li in range(cfg.n_layers):
+            qkv_a = lin(d, 2176, 1.0 / math.sqrt(d), cfg.bits_b, g)
+            qkv_a.svh[2112:] = 0
+            su_qb = sg(1536, g).to(torch.float16)
+            L = dict(attn_norm=nrm(d), qkv_a=qkv_a, q_norm=nrm(1536), kv_norm=nrm(512), q_b=lin(1536, Hl * 192, 1.0 / math.sqrt(1536), cfg.bits_a, gl, su_qb),
+                     w_uk=(torch.randn(Hl, 128, 512, device=dev, generator=gl) / math.sqrt(128)).to(torch.bfloat16),
+                     w_uv=(torch.randn(Hl, 512, 128, device=dev, generator=gl) / math.sqrt(512)).to(torch.bfloat16),
+                     o=lin(Hl * 128, d, 0.5 / math.sqrt(cfg.n_heads * 128), cfg.bits_a, gl), ffn_norm=nrm(d), router=None)
+            F = cfg.dense_ffn if li < cfg.n_dense else cfg.shared_ffn
+            L["gate_up"] = lin(d, 2 * F, 1.0 / math.sqrt(d), cfg.bits_a, g)
+            L["down"] = lin(F, d, 0.5 / math.sqrt(F), cfg.bits_b, g)
+            if li >= cfg.n_dense:
+                L["router"] = (torch.randn(cfg.n_experts, d, device=dev, generator=g) / math.sqrt(d)).to(torch.bfloat16)
+                L["router_bias"] = 0.1 * torch.randn(cfg.n_experts, device=dev, generator=g)
+                L["gu_w"], L["gu_s"] = mx(E, 2 * cfg.expert_ffn, d, 1.0 / math.sqrt(d))
+                L["dn_w"], L["dn_s"] = mx(E, d, cfg.expert_ffn, 0.5 / math.sqrt(cfg.expert_ffn))
+            self.layers.append(L)
+        self.final_norm = nrm(d)
+        self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d), cfg.bits_b, g)
+        if cfg.vocab_padded != cfg.vocab:
+            self.lm_head.svh[cfg.vocab:] = 0
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * 2 + self.lm_head.nbytes
+        for L in self.layers:
+            n += sum(L[k].nbytes for k in ("qkv_a", "q_b", "o", "gate_up", "down")) + (L["w_uk"].numel() + L["w_uv"].numel()) * 2
+            if L["router"] is not None:
+                n += sum(L[k].numel() for k in ("gu_w", "gu_s", "dn_w", "dn_s")) + L["router"].numel() * 2
+        return n
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc(self, R):
+        cfg, dev = self.cfg, self.device
+        d, Hl, k = cfg.d_model, self.Hl, cfg.top_k
+        Rw = min(R, 256)
+        self.splits = {}
+        part = 0
+        Fmax = max(cfg.dense_ffn, cfg.shared_ffn)
+        shapes = dict(qkv_a=(d, 2176), q_b=(1536, Hl * 192), o=(Hl * 128, d), gu_dense=(d, 2 * cfg.dense_ffn), dn_dense=(cfg.dense_ffn, d),
+                      gu_sh=(d, 2 * cfg.shared_ffn), dn_sh=(cfg.shared_ffn, d), lm_head=(d, cfg.vocab_padded))
+        for cls, rows in (("decode", Rw), ("prefill", R)):
+            for name, (kk, nn) in shapes.items():
+                s = K.plan_splits(kk, nn, cls == "decode")
+                self.splits[(cls, name)] = s
+                part = max(part, s * (rows if name != "lm_head" else Rw) * nn)
+        self.pairs_cap = {"decode": Rw * k, "prefill": R * k}
+        self.mx_splits = {"decode": (2, 2), "prefill": (1, 1)}
+        for cls in ("decode", "prefill"):
+            sg_, sd_ = self.mx_splits[cls]
+            part = max(part, sg_ * self.pairs_cap[cls] * 2 * cfg.expert_ffn, sd_ * self.pairs_cap[cls] * d)
+        self.part = torch.empty(part, dtype=torch.float32, device=dev)
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
+        hf = lambda *s: torch.empty(*s, dtype=torch.float16, device=dev)  # noqa: E731
+        i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)  # noqa: E731
+        self.h, self.xn = bf(R, d), bf(R, d)
+        self.xr_d = hf(R, d)
+        self.a_out = bf(R, 2176)
+        self.xr_q = hf(R, 1536)
+        self.q_full = bf(R, Hl * 192)
+        self.q = bf(R, Hl, 576)
+        self.o_lat = bf(R, Hl, 512)
+        self.o_heads = bf(R, Hl * 128)
+        self.xr_o = hf(R, Hl * 128)
+        self.xr_f = hf(R, Fmax)
+        self.shared = torch.zeros(R, d, dtype=torch.float32, device=dev)
+        self.logits = torch.empty(Rw, cfg.vocab_padded, dtype=torch.float32, device=dev)
+        self.attn_scratch = torch.empty(_lib.load().rx_mla_scratch_floats(R, Hl, self.max_ctx_alloc), dtype=torch.float32, device=dev)
+        self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
+        E = cfg.n_experts
+        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
+        self.max_tiles = {"decode": E + (Rw * k + 31) // 32, "prefill": E + (R * k + 127) // 128}
+        self.tile_tab = i32(3 * max(self.max_tiles.values()))
+        self.xs = torch.zeros(R * k, d, dtype=torch.float16, device=dev)
+        self.xs2 = torch.zeros(R * k, cfg.expert_ffn, dtype=torch.float16, device=dev)
+        self.topk_scratch = K.topk_scratch(Rw, cfg.vocab_padded, 64, dev)
+        self.cand_ids = torch.empty(Rw, 64, dtype=torch.int32, device=dev)
+        self.cand_vals = torch.empty(Rw, 64, dtype=torch.float32, device=dev)
+
+    def _lin(self, xr, w, cls, name):
+        s = self.splits[(cls, name)]
+        K.exl3_gemm(xr, w, self.part, s, self.status)
+        return s
+
+    def _allsum(self, tgt, M, h, norm_w, suh_next, xr_out, xn_out=None):
+        dst, ar, flags, ranks, rows_cap, epoch, use = tgt
+        _lib.check(_lib.load().rx_tp_allsum_add_norm_rot(ar, flags, ranks, rows_cap, epoch, use, M, self.cfg.d_model, h.data_ptr(), norm_w.data_ptr(),
+                                                         self.cfg.eps, _lib.ptr(suh_next), _lib.ptr(xr_out), self.status.data_ptr(), _lib.stream_ptr(),
+                                                         _lib.ptr(xn_out)), "rx_tp_allsum_add_norm_rot")
+        _lib.count()
+
+    # ------------------------------------------------------------------ forward
+    def forward_rows(self, *a, **kw):
+        g = self.forward_phases(*a, **kw)
+        try:
+            while True:
+                next(g)
+        except StopIteration as e:
+            return e.value
+
+    def forward_phases(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True,
+                       n_layers=None):
+        cfg = self.cfg
+        Lib = _lib.load()
+        st = _lib.stream_ptr
+        M = ids.shape[0]
+        cls = "decode" if (prefill is None and M <= 256) else "prefill"
+        d, Hl, k, E = cfg.d_model, self.Hl, cfg.top_k, cfg.n_experts
+        multi = not isinstance(self.comm, _Local)
+        h, xn, xr_d = self.h[:M], self.xn[:M], self.xr_d[:M]
+        a_out, xr_q, q_full, q, o_lat, o_heads, xr_o = self.a_out[:M], self.xr_q[:M], self.q_full[:M], self.q[:M], self.o_lat[:M], self.o_heads[:M], self.xr_o[:M]
+        ctx_cap = max_ctx or self.max_ctx_alloc
+        self.comm.begin()
+        K.embed(ids, self.embed, h)
+        K.norm_rot_in(h, self.layers[0]["attn_norm"], cfg.eps, self.layers[0]["qkv_a"].suh, xr_d)
+        nl = n_layers or len(self.layers)
+        for li in range(nl):
+            L = self.layers[li]
+            s = self._lin(xr_d, L["qkv_a"], cls, "qkv_a")
+            K.finish_store(self.part, s, M, L["qkv_a"], a_out)
+            _lib.check(Lib.rx_mla_row(a_out.data_ptr(), L["q_norm"].data_ptr(), L["kv_norm"].data_ptr(), cfg.eps, L["q_b"].suh.data_ptr(), positions.data_ptr(),
+                                      self.inv_freq.data_ptr(), slots.data_ptr(), xr_q.data_ptr(), self.cache[li].data_ptr(), M, st()), "rx_mla_row")
+            s = self._lin(xr_q, L["q_b"], cls, "q_b")
+            K.finish_store(self.part, s, M, L["q_b"], q_full)
+            _lib.check(Lib.rx_mla_q_rope(q_full.data_ptr(), positions.data_ptr(), self.inv_freq.data_ptr(), Hl, q.data_ptr(), M, st()), "rx_mla_q_rope")
+            _lib.check(Lib.rx_head_gemm(q_full.data_ptr(), Hl * 192, 192, L["w_uk"].data_ptr(), Hl, 128, 512, q.data_ptr(), Hl * 576, 576, M, st()), "absorb")
+            _lib.check(Lib.rx_mla_attn(self.tc[li].ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
+                                       self.attn_scratch.data_ptr(), M, Hl, ctx_cap, 1.0 / math.sqrt(192), o_lat.data_ptr(), self.status.data_ptr(), st()),
+                       "rx_mla_attn")
+            _lib.check(Lib.rx_head_gemm(o_lat.data_ptr(), Hl * 512, 512, L["w_uv"].data_ptr(), Hl, 512, 128, o_heads.data_ptr(), Hl * 128, 128, M, st()), "expand")
+            _lib.count(6)
+            K.norm_rot_in(o_heads, None, cfg.eps, L["o"].suh, xr_o)
+            s = self._lin(xr_o, L["o"], cls, "o")
+            # o_proj partial rows -> every rank's slot, then residual + ffn norm (+ the rotation of the dense / shared FFN input)
+            tgt = self.comm.target(2 * li + 1, M)
+            _lib.check(Lib.rx_tp_finish_bcast(self.part.data_ptr(), s, M, d, L["o"].svh.data_ptr(), None, ctypes.byref(tgt[0]), st()), "rx_tp_finish_bcast") \
+                if multi else self._finish_local(s, M, L["o"], tgt)
+            if multi:
+                yield
+            routed = L["router"] is not None
+            self._allsum(tgt, M, h, L["ffn_norm"], L["gate_up"].suh, xr_d, xn if routed else None)
+            # dense FFN or shared expert
+            F = L["gate_up"].N // 2
+            run_shared = (not routed) or (not multi) or self.rank == 0
+            gname, dname = ("gu_sh", "dn_sh") if routed else ("gu_dense", "dn_dense")
+            xr_f = self.xr_f.view(-1)[:M * F].view(M, F)
+            nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv_a"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
+            tgt2 = self.comm.target(2 * li + 2, M) if routed else None
+            if run_shared:
+                s = self._lin(xr_d, L["gate_up"], cls, gname)
+                K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
+                s = self._lin(xr_f, L["down"], cls, dname)
+            if not routed:
+                # a dense layer: every rank computes the same FFN on the replicated stream, so the sum stays local
+                K.finish_store(self.part, s, M, L["down"], self.local.slot[:M])
+                self._allsum(self.local.target(0, M), M, h, nn_, ns_, xr_d)
+                continue
+            if run_shared:
+                K.finish_store(self.part, s, M, L["down"], self.shared[:M])
+            pairs, cap = M * k, self.pairs_cap[cls]
+            tile_rows = (16 if M <= 16 else 32) if cls == "decode" else 128
+            mt = self.max_tiles[cls]
+            _lib.check(Lib.rx_moe_router(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
+                                         self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st()), "rx_moe_router")
+            _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, mt, self.offs.data_ptr(), self.pos_of_pair.data_ptr(),
+                                       self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(), self.total.data_ptr(), st()),
+                       "rx_moe_plan")
+            _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), self.pick_ids.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, None, self.xs.data_ptr(), st()),
+                       "rx_moe_gather_rot")
+            sg_, sd_ = self.mx_splits[cls]
+            Fe = cfg.expert_ffn
+            self._mx(self.xs, L["gu_w"], L["gu_s"], d, 2 * Fe, sg_, cap, mt, tile_rows)
+            _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), sg_, cap, Fe, self.expert_of_pos.data_ptr(), self.total.data_ptr(), None, None,
+                                             self.xs2.data_ptr(), st()), "rx_moe_swiglu_rot")
+            self._mx(self.xs2, L["dn_w"], L["dn_s"], Fe, d, sd_, cap, mt, tile_rows)
+            _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), sd_, cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(), self.pos_of_pair.data_ptr(),
+                                          None, self.shared.data_ptr() if run_shared else None, ctypes.byref(tgt2[0]), st()), "rx_moe_combine")
+            _lib.count(7)
+            if multi:
+                yield
+            self._allsum(tgt2, M, h, nn_, ns_, xr_d)
+        if not want_logits:
+            return None
+        xl = xr_d if logit_rows is None else xr_d.index_select(0, logit_rows).contiguous()
+        Rr = xl.shape[0]
+        s = self._lin(xl, self.lm_head, "decode", "lm_head")
+        logits = self.logits[:Rr]
+        K.finish_store(self.part, s, Rr, self.lm_head, logits)
+        return logits
+
+    def _mx(self, xs, wq, sc, Kd, N, splits, cap, max_tiles, tile_rows):
+        if splits * cap * N > self.part.numel():
+            raise _lib.KernelError("grouped MXFP4 partials exceed the scratch buffer")
+        El = self.e_hi - self.e_lo
+        wbase = wq.data_ptr() - self.e_lo * N * (Kd // 2)
+        sbase = sc.data_ptr() - self.e_lo * N * (Kd // 32)
+        _lib.check(_lib.load().rx_mxfp4_gemm_grouped(xs.data_ptr(), cap, Kd, ctypes.c_void_p(wbase), ctypes.c_void_p(sbase), self.e_lo + El, N,
+                                                     self.part.data_ptr(), splits, self.tile_tab.data_ptr(), max_tiles, tile_rows, self.status.data_ptr(),
+                                                     _lib.stream_ptr()), "rx_mxfp4_gemm_grouped")
+
+    def _finish_local(self, s, M, w, tgt):
+        """One rank: the finished rows go straight to the local slot (f32), no flags."""
+        K.finish_store(self.part, s, M, w, self.local.slot[:M])
+
+    def candidates(self, logits, count):
+        R = logits.shape[0]
+        if self.cfg.vocab_padded != self.cfg.vocab:
+            logits[:, self.cfg.vocab:] = float("-inf")
+        ids, vals = self.cand_ids.view(-1)[:R * count].view(R, count), self.cand_vals.view(-1)[:R * count].view(R, count)
+        K.topk(logits, count, self.topk_scratch, ids, vals)
+        return ids, vals
+
+    def _ids_view(self, R, count):
+        return self.cand_ids.view(-1)[:R * count].view(R, count)
+
+    def _vals_view(self, R, count):
+        return self.cand_vals.view(-1)[:R * count].view(R, count)
+
+    def check(self, what="forward"):
+        K.check_status(self.status, what)

@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const uint16_t* __restr
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
+    if (bi < 0 || bi >= E) bi = j;   // a row of NaN scores selects nothing: keep the indices in range
     const float p = prob[bi];
     picked_sum += p;
     if (lane == 0) {
@@ -171,10 +172,12 @@ __global__ void moe_gather_rot_kernel(const uint16_t* __restrict__ x, const int*
     const int n0 = b * 128 + lane * 4;
     const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * d + n0);
     float v[4] = {__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u)};
-    const uint2 su = *reinterpret_cast<const uint2*>(suh + (size_t)e * d + n0);
-    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
-    v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
-    fwht128_warp(v);
+    if (suh != nullptr) {          // EXL3 experts: the expert's own input rotation; plain formats (MXFP4) take the row as it is
+      const uint2 su = *reinterpret_cast<const uint2*>(suh + (size_t)e * d + n0);
+      const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+      v[0] *= s01.x; v[1] *= s01.y; v[2] *= s23.x; v[3] *= s23.y;
+      fwht128_warp(v);
+    }
     const __half2 a = __floats2half2_rn(v[0], v[1]), bb = __floats2half2_rn(v[2], v[3]);
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
@@ -198,6 +201,7 @@ __device__ __forceinline__ void moe_finish_block(const float* __restrict__ part,
       }
   }
   y[0] = acc.x; y[1] = acc.y; y[2] = acc.z; y[3] = acc.w;
+  if (svh_n0 == nullptr) return;   // plain formats: no output rotation, no column scale
   fwht128_warp(y);
   const uint2 su = *reinterpret_cast<const uint2*>(svh_n0);
   const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
@@ -219,17 +223,20 @@ __global__ void moe_swiglu_rot_kernel(const float* __restrict__ part, int S, int
   for (int b = blockIdx.y * nw + warp; b < F / 128; b += gridDim.y * nw) {
     const int n0 = b * 128 + lane * 4;
     float g[4], u[4];
-    moe_finish_block(part, S, plane, (size_t)pos * N + n0, svh_gu + (size_t)e * N + n0, g);
-    moe_finish_block(part, S, plane, (size_t)pos * N + F + n0, svh_gu + (size_t)e * N + F + n0, u);
-    const uint2 su = *reinterpret_cast<const uint2*>(suh_down + (size_t)e * F + n0);
-    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
-    const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+    moe_finish_block(part, S, plane, (size_t)pos * N + n0, svh_gu == nullptr ? nullptr : svh_gu + (size_t)e * N + n0, g);
+    moe_finish_block(part, S, plane, (size_t)pos * N + F + n0, svh_gu == nullptr ? nullptr : svh_gu + (size_t)e * N + F + n0, u);
+    float s[4] = {1.f, 1.f, 1.f, 1.f};
+    if (suh_down != nullptr) {
+      const uint2 su = *reinterpret_cast<const uint2*>(suh_down + (size_t)e * F + n0);
+      const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+      s[0] = s01.x; s[1] = s01.y; s[2] = s23.x; s[3] = s23.y;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float a = g[i] / (1.f + __expf(-g[i])) * u[i];
       g[i] = m_bf16_to_f(m_f_to_bf16(a)) * s[i];
     }
-    fwht128_warp(g);
+    if (suh_down != nullptr) fwht128_warp(g);
     const __half2 a = __floats2half2_rn(g[0], g[1]), bb = __floats2half2_rn(g[2], g[3]);
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
@@ -266,7 +273,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ part, int S, int pa
       if (pos < 0) continue;     // warp-uniform
       const int e = ids[pair];
       float y[4];
-      moe_finish_block(part, S, plane, (size_t)pos * d + n0, svh_down + (size_t)e * d + n0, y);
+      moe_finish_block(part, S, plane, (size_t)pos * d + n0, svh_down == nullptr ? nullptr : svh_down + (size_t)e * d + n0, y);
       const float wj = w[pair];
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[i] = fmaf(wj, y[i], acc[i]);

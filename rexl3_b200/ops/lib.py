@@ -62,6 +62,12 @@ def _declare(lib):
         "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_combine_desc_size": (c_int, []),
+        "rx_mla_scratch_floats": (c_ll, [c_int, c_int, c_int]),
+        "rx_mla_attn": (c_int, [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_f, c_void, c_void, c_void]),
+        "rx_head_gemm": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_int, c_void, c_int, c_int, c_int, c_void]),
+        "rx_mla_row": (c_int, [c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void]),
+        "rx_mla_q_rope": (c_int, [c_void, c_void, c_void, c_int, c_void, c_int, c_void]),
+        "rx_mxfp4_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_void, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),
         "rx_moe_combine": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_tp_cand_push": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void]),
         "rx_tp_cand_merge": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, ctypes.c_uint, c_void, c_void, c_void, c_void]),

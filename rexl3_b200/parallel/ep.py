@@ -79,6 +79,20 @@ class EpComm:
         return t, ar, flags, self.R, self.L.rows_cap, self.me + self.L.epoch, li + 1
 
 
+    def target(self, use: int, M: int):
+        """Slot set of the `use`-th collective of a forward (parity alternates with `use`)."""
+        if M > self.L.rows_cap:
+            raise ValueError(f"{M} rows exceed the {self.L.rows_cap}-row all-reduce slots")
+        parity = use & 1
+        t = self._dst[parity]
+        t.use_index = use
+        ar = self.me + self.L.ar + 4 * parity * self.R * self.L.rows_cap * self.L.d
+        return t, ar, self.me + self.L.ar_flag + 4 * parity * self.R, self.R, self.L.rows_cap, self.me + self.L.epoch, use
+
+    def local_slot(self):
+        return None
+
+
 def make_ipc(cfg, rank: int, ranks: int, rows_cap: int, device, ctrl_group) -> EpComm:
     return EpComm(IpcGroup(EpLayout(ranks, rows_cap, cfg.d_model), rank, device, group=ctrl_group), rank)
 

@@ -175,3 +175,47 @@ def test_expert_parallel_loopback_matches_single(ranks):
     o2 = run(a2, max_ctx=256)
     w2 = single.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
     assert torch.equal(o2[0], o2[-1]) and (o2[0] - w2).abs().max().item() < 0.02 * scale
+
+
+@pytest.mark.parametrize("rows,tile_rows", [(5, 16), (70, 32)])
+def test_mxfp4_grouped_gemm_matches_dequantized_reference(rows, tile_rows):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.format import mxfp4
+    from rexl3_b200.ops import kernels as K
+    from rexl3_b200.ops import lib as L
+    lib = L.load()
+    rng = np.random.default_rng(1)
+    E, N, Kd, topk = 6, 256, 384, 2
+    wq, sc, wf = [], [], []
+    for e in range(E):
+        w = rng.normal(0, 0.05 * (1 + e), size=(N, Kd)).astype(np.float32)
+        q, s = mxfp4.quantize(w)
+        wq.append(q.view(np.uint8)); sc.append(s); wf.append(mxfp4.dequant(q, s))
+    d_w = torch.from_numpy(np.stack(wq)).cuda()
+    d_s = torch.from_numpy(np.stack(sc)).cuda()
+    ids = torch.from_numpy(rng.integers(0, E, size=(rows, topk)).astype(np.int32)).cuda()
+    pairs = rows * topk
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")  # noqa: E731
+    offs, pos_of_pair, pair_of_pos, expert_of_pos, total = i32(E + 1), i32(pairs), i32(pairs), i32(pairs), i32(1)
+    max_tiles = E + (pairs + tile_rows - 1) // tile_rows
+    tile_tab = i32(3 * max_tiles)
+    L.check(lib.rx_moe_plan(ids.data_ptr(), pairs, E, 0, E, tile_rows, max_tiles, offs.data_ptr(), pos_of_pair.data_ptr(), pair_of_pos.data_ptr(),
+                            expert_of_pos.data_ptr(), tile_tab.data_ptr(), total.data_ptr(), L.stream_ptr()), "plan")
+    x = torch.from_numpy(rng.normal(0, 1, size=(rows, Kd)).astype(np.float32)).cuda().to(torch.bfloat16)
+    xs = torch.zeros(pairs, Kd, dtype=torch.float16, device="cuda")
+    L.check(lib.rx_moe_gather_rot(x.data_ptr(), ids.data_ptr(), pos_of_pair.data_ptr(), pairs, topk, Kd, None, xs.data_ptr(), L.stream_ptr()), "gather")
+    splits = 2
+    part = torch.zeros(splits, pairs, N, dtype=torch.float32, device="cuda")
+    status = K.new_status()
+    L.check(lib.rx_mxfp4_gemm_grouped(xs.data_ptr(), pairs, Kd, d_w.data_ptr(), d_s.data_ptr(), E, N, part.data_ptr(), splits, tile_tab.data_ptr(),
+                                      max_tiles, tile_rows, status.data_ptr(), L.stream_ptr()), "mxfp4")
+    torch.cuda.synchronize()
+    K.check_status(status, "mxfp4")
+    got = part.sum(0).cpu().numpy()
+    pos = pos_of_pair.cpu().numpy()
+    xh = xs.float().cpu().numpy()
+    idn = ids.cpu().numpy().reshape(-1)
+    for p in range(pairs):
+        want = xh[pos[p]] @ wf[idn[p]].T
+        np.testing.assert_allclose(got[pos[p]], want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
