@@ -419,6 +419,7 @@ class MlaMoEGPU:
         K.embed(ids, self.embed, h)
         K.norm_rot_in(h, self.layers[0]["attn_norm"], cfg.eps, self.layers[0]["qkv_a"].suh, xr_d)
         nl = n_layers or len(self.layers)
+        use = 0        # collectives are numbered in launch order: consecutive ones alternate between the two slot sets
         for li in range(nl):
             L = self.layers[li]
             s = self._lin(xr_d, L["qkv_a"], cls, "qkv_a")
@@ -437,7 +438,8 @@ class MlaMoEGPU:
             K.norm_rot_in(o_heads, None, cfg.eps, L["o"].suh, xr_o)
             s = self._lin(xr_o, L["o"], cls, "o")
             # o_proj partial rows -> every rank's slot, then residual + ffn norm (+ the rotation of the dense / shared FFN input)
-            tgt = self.comm.target(2 * li + 1, M)
+            use += 1
+            tgt = self.comm.target(use, M)
             _lib.check(Lib.rx_tp_finish_bcast(self.part.data_ptr(), s, M, d, L["o"].svh.data_ptr(), None, ctypes.byref(tgt[0]), st()), "rx_tp_finish_bcast") \
                 if multi else self._finish_local(s, M, L["o"], tgt)
             if multi:
@@ -450,7 +452,9 @@ class MlaMoEGPU:
             gname, dname = ("gu_sh", "dn_sh") if routed else ("gu_dense", "dn_dense")
             xr_f = self.xr_f.view(-1)[:M * F].view(M, F)
             nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv_a"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
-            tgt2 = self.comm.target(2 * li + 2, M) if routed else None
+            if routed:
+                use += 1
+            tgt2 = self.comm.target(use, M) if routed else None
             if run_shared:
                 s = self._lin(xr_d, L["gate_up"], cls, gname)
                 K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
