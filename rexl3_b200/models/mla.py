@@ -374,7 +374,9 @@ class MlaMoEGPU:
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
         E = cfg.n_experts
         self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
-        self.max_tiles = {"decode": E + (Rw * k + 31) // 32, "prefill": E + (R * k + 127) // 128}
+        El = self.e_hi - self.e_lo      # the tile table only ever names owned experts
+        self.max_tiles = {"decode": El + (Rw * k + 31) // 32, "prefill": El + (R * k + 127) // 128}
+        self.router_logits = torch.empty(R, E, dtype=torch.float32, device=dev)
         self.tile_tab = i32(3 * max(self.max_tiles.values()))
         self.xs = torch.zeros(R * k, d, dtype=torch.float16, device=dev)
         self.xs2 = torch.zeros(R * k, cfg.expert_ffn, dtype=torch.float16, device=dev)
@@ -469,8 +471,8 @@ class MlaMoEGPU:
             pairs, cap = M * k, self.pairs_cap[cls]
             tile_rows = (16 if M <= 16 else 32) if cls == "decode" else 128
             mt = self.max_tiles[cls]
-            _lib.check(Lib.rx_moe_router(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
-                                         self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st()), "rx_moe_router")
+            _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
+                                          self.router_logits.data_ptr(), self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st()), "rx_moe_router2")
             _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, mt, self.offs.data_ptr(), self.pos_of_pair.data_ptr(),
                                        self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(), self.total.data_ptr(), st()),
                        "rx_moe_plan")
@@ -484,7 +486,7 @@ class MlaMoEGPU:
             self._mx(self.xs2, L["dn_w"], L["dn_s"], Fe, d, sd_, cap, mt, tile_rows)
             _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), sd_, cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(), self.pos_of_pair.data_ptr(),
                                           None, self.shared.data_ptr() if run_shared else None, ctypes.byref(tgt2[0]), st()), "rx_moe_combine")
-            _lib.count(7)
+            _lib.count(8)
             if multi:
                 yield
             self._allsum(tgt2, M, h, nn_, ns_, xr_d)

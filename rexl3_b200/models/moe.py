@@ -242,8 +242,10 @@ class MoEGPU(DenseGPU):
         self.xn = torch.empty(R, d, dtype=torch.bfloat16, device=dev)
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
         self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
-        self.max_tiles_decode = E + (min(R, 256) * k + 31) // 32      # windows use 16- or 32-row tiles: small tiles keep two CTAs per SM
-        self.max_tiles_prefill = E + (R * k + 127) // 128
+        El = self.e_hi - self.e_lo                                       # the tile table only ever names owned experts
+        self.max_tiles_decode = El + (min(R, 256) * k + 31) // 32     # windows use 16- or 32-row tiles: small tiles keep two CTAs per SM
+        self.max_tiles_prefill = El + (R * k + 127) // 128
+        self.router_logits = torch.empty(R, E, dtype=torch.float32, device=dev)
         self.tile_tab = i32(3 * max(self.max_tiles_decode, self.max_tiles_prefill))
         self.xs = torch.zeros(R * k, d, dtype=torch.float16, device=dev)
         self.xs2 = torch.zeros(R * k, F, dtype=torch.float16, device=dev)
@@ -270,9 +272,9 @@ class MoEGPU(DenseGPU):
         cap = self.pairs_cap[cls]
         xn = self.xn[:M]
         K.finish_add_norm_rot(self.part, s_o, M, L["o"], h, L["ffn_norm"], cfg.eps, None, None, xn_out=xn)
-        _lib.check(Lib.rx_moe_router(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
-                                     0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st),
-                   "rx_moe_router")
+        _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
+                                      0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, self.router_logits.data_ptr(),
+                                      self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st), "rx_moe_router2")
         if cls == "decode":
             tile_rows, max_tiles = (16 if M <= 16 else 32), self.max_tiles_decode
         else:
@@ -299,7 +301,7 @@ class MoEGPU(DenseGPU):
             yield          # every rank's combine must be in flight before any rank's sum may wait for it
         _lib.check(Lib.rx_tp_allsum_add_norm_rot(ar, flags, ranks, rows_cap, epoch, use, M, d, h.data_ptr(), next_norm.data_ptr(), cfg.eps,
                                                  next_suh.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(), st, None), "rx_tp_allsum_add_norm_rot")
-        _lib.count(7)
+        _lib.count(8)
 
     def _grouped_shifted(self, xs, st: _ExpertStack, splits, max_tiles, tile_rows, cap):
         """The tile table names GLOBAL expert ids; the stack starts at expert e_lo."""

@@ -24,17 +24,65 @@ __device__ __forceinline__ uint16_t m_f_to_bf16(float f) {
   return *reinterpret_cast<uint16_t*>(&b);
 }
 
+// Gate logits as a small tiled product: CTA = (2 experts, 16 rows); warp w takes rows 2w and 2w + 1 against both experts, so the
+// work of a 64-row window spreads over hundreds of CTAs instead of one CTA per row.  logits: f32 [M, E].
+__global__ void __launch_bounds__(256) moe_router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, int M, int d, int E,
+                                                                float* __restrict__ logits) {
+  pdl_launch();
+  pdl_wait();
+  const int e0 = blockIdx.x * 2, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = blockIdx.y * 16 + warp * 2;
+  if (r0 >= M) return;
+  const bool two = r0 + 1 < M;
+  const uint16_t* xa = x + (size_t)r0 * d;
+  const uint16_t* xb = x + (size_t)(two ? r0 + 1 : r0) * d;
+  const uint16_t* ga = gate + (size_t)e0 * d;
+  const uint16_t* gb = gate + (size_t)(e0 + 1 < E ? e0 + 1 : e0) * d;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};     // (row a, expert a), (a, b), (b, a), (b, b); each lane walks k in a fixed order
+  for (int k = lane * 8; k < d; k += 256) {
+    const uint4 va = *reinterpret_cast<const uint4*>(xa + k), vb = *reinterpret_cast<const uint4*>(xb + k);
+    const uint4 wa = __ldg(reinterpret_cast<const uint4*>(ga + k)), wb = __ldg(reinterpret_cast<const uint4*>(gb + k));
+    const uint32_t xs0[4] = {va.x, va.y, va.z, va.w}, xs1[4] = {vb.x, vb.y, vb.z, vb.w};
+    const uint32_t gs0[4] = {wa.x, wa.y, wa.z, wa.w}, gs1[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a0 = __uint_as_float(xs0[i] << 16), a1 = __uint_as_float(xs0[i] & 0xFFFF0000u);
+      const float b0 = __uint_as_float(xs1[i] << 16), b1 = __uint_as_float(xs1[i] & 0xFFFF0000u);
+      const float g0 = __uint_as_float(gs0[i] << 16), g1 = __uint_as_float(gs0[i] & 0xFFFF0000u);
+      const float h0 = __uint_as_float(gs1[i] << 16), h1 = __uint_as_float(gs1[i] & 0xFFFF0000u);
+      acc[0] = fmaf(a0, g0, acc[0]); acc[0] = fmaf(a1, g1, acc[0]);
+      acc[1] = fmaf(a0, h0, acc[1]); acc[1] = fmaf(a1, h1, acc[1]);
+      acc[2] = fmaf(b0, g0, acc[2]); acc[2] = fmaf(b1, g1, acc[2]);
+      acc[3] = fmaf(b0, h0, acc[3]); acc[3] = fmaf(b1, h1, acc[3]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = warp_sum(acc[i]);
+  if (lane == 0) {
+    logits[(size_t)r0 * E + e0] = acc[0];
+    if (e0 + 1 < E) logits[(size_t)r0 * E + e0 + 1] = acc[1];
+    if (two) {
+      logits[(size_t)(r0 + 1) * E + e0] = acc[2];
+      if (e0 + 1 < E) logits[(size_t)(r0 + 1) * E + e0 + 1] = acc[3];
+    }
+  }
+}
+
 // x: bf16 [M, d] (normalised hidden rows).  gate: bf16 [E, d].  bias: f32 [E] or nullptr (mode 1).
+// `logits_in` (f32 [M, E]) given: the dot products were done by moe_router_logits_kernel and this kernel only scores and picks.
 // out_ids: int32 [M, topk], out_w: f32 [M, topk].  One CTA per row; warp w scores experts w, w + nw, ...
 __global__ void __launch_bounds__(256) moe_router_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const float* __restrict__ bias,
                                                          int M, int d, int E, int topk, int mode, float scale, int* __restrict__ out_ids,
-                                                         float* __restrict__ out_w) {
+                                                         float* __restrict__ out_w, const float* __restrict__ logits_in) {
   pdl_launch();
   pdl_wait();
   __shared__ float score[512];     // selection key
   __shared__ float prob[512];      // weight source
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const uint16_t* xr = x + (size_t)row * d;
+  if (logits_in != nullptr) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) prob[e] = logits_in[(size_t)row * E + e];
+  } else
   for (int e = warp; e < E; e += nw) {
     const uint16_t* g = gate + (size_t)e * d;
     float acc = 0.f;
@@ -108,16 +156,21 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const uint16_t* __restr
 // Single CTA.  ids: int32 [pairs].  Outputs: offs int32 [E + 1] (positions of expert e are offs[e] .. offs[e+1]; experts outside
 // [e_lo, e_hi) get empty ranges), pos_of_pair int32 [pairs] (-1: not owned), pair_of_pos / expert_of_pos int32 [pairs],
 // tile_tab int32 [max_tiles][3], total int32 [1].
-__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles,
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles,
                                                         int* __restrict__ offs, int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos,
                                                         int* __restrict__ expert_of_pos, int* __restrict__ tile_tab, int* __restrict__ total) {
   pdl_launch();
   pdl_wait();
   __shared__ int cnt[513];
   __shared__ int start[513];
+  __shared__ int ids_sh[4096];       // windows: the pair list fits and every scan below reads it as a broadcast
   const int t = threadIdx.x;
   for (int e = t; e <= E; e += blockDim.x) cnt[e] = 0;
+  const bool staged = pairs <= 4096;
+  if (staged)
+    for (int p = t; p < pairs; p += blockDim.x) ids_sh[p] = ids[p];
   __syncthreads();
+  if (staged) ids = ids_sh;
   // thread e counts its pairs in pair order (every thread reads the same id at the same time: broadcast)
   if (t < E && t >= e_lo && t < e_hi) {
     int c = 0;
@@ -300,7 +353,19 @@ RX_API int rx_moe_router(const void* x, const void* gate, const void* bias, int 
                          void* out_w, void* stream) {
   if (M < 1 || d % 256 != 0 || E < 1 || E > 512 || topk < 1 || topk > 32 || topk > E || (mode != 0 && mode != 1)) return (int)cudaErrorInvalidValue;
   return (int)rx::launch(moe_router_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x, (const uint16_t*)gate, (const float*)bias, M,
-                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w);
+                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)nullptr);
+}
+
+// Two-kernel form for windows of many rows: tiled logits, then scoring + top-k per row.  logits: f32 scratch [M, E].
+RX_API int rx_moe_router2(const void* x, const void* gate, const void* bias, int M, int d, int E, int topk, int mode, float scale, void* logits,
+                          void* out_ids, void* out_w, void* stream) {
+  if (M < 1 || d % 256 != 0 || E < 1 || E > 512 || topk < 1 || topk > 32 || topk > E || (mode != 0 && mode != 1) || logits == nullptr)
+    return (int)cudaErrorInvalidValue;
+  int e = (int)rx::launch(moe_router_logits_kernel, dim3((E + 1) / 2, (M + 15) / 16), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x,
+                          (const uint16_t*)gate, M, d, E, (float*)logits);
+  if (e != 0) return e;
+  return (int)rx::launch(moe_router_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x, (const uint16_t*)gate, (const float*)bias, M,
+                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)logits);
 }
 
 RX_API int rx_moe_plan(const void* ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles, void* offs, void* pos_of_pair,

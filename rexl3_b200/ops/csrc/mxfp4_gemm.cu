@@ -11,6 +11,7 @@
 // scalar LUT FMA loop; the tensor-core schedule here is new).  Scales outside the fp16 range saturate (to 0 below 2^-24, to inf
 // above 2^15); 0xFF is NaN.
 #include <cuda.h>
+#include <cuda_fp4.h>
 #include "common.cuh"
 
 namespace rx {
@@ -20,21 +21,23 @@ constexpr int MX_STRIP = 128;
 constexpr int MX_GROUPS = 2;
 constexpr int MX_DEC_WARPS = 8;
 constexpr int MX_THREADS = 64 + MX_DEC_WARPS * 32;
-constexpr int MX_RAW_STAGES = 8;
+constexpr int MX_RAW_STAGES = 4;
+constexpr int MX_SC_ROW = 256;                          // scale bytes per weight row a CTA may need: K range <= 8192
 constexpr int MX_OP_STAGES = 3;
 static_assert(MX_OP_STAGES >= MX_GROUPS, "operand ring shallower than the number of decode groups");
 constexpr int MX_A_STAGE = MX_STRIP * MX_KCH * 2;       // 16 KB of fp16
 constexpr int MX_RAW_STAGE = MX_STRIP * (MX_KCH / 2);   // 4 KB of nibbles
 
 struct MxLayout {
-  int a_off, b_off, raw_off, lut_off, bar_off, total;
+  int a_off, b_off, raw_off, sc_off, lut_off, bar_off, total;
 };
 __host__ __device__ inline MxLayout mx_layout(int brows) {
   MxLayout L;
   L.a_off = 0;
   L.b_off = L.a_off + MX_OP_STAGES * MX_A_STAGE;
   L.raw_off = L.b_off + MX_OP_STAGES * brows * MX_KCH * 2;
-  L.lut_off = L.raw_off + MX_RAW_STAGES * MX_RAW_STAGE;
+  L.sc_off = L.raw_off + MX_RAW_STAGES * MX_RAW_STAGE;
+  L.lut_off = L.sc_off + MX_STRIP * MX_SC_ROW;
   L.bar_off = L.lut_off + 1024;
   L.total = L.bar_off + 256;
   return L;
@@ -89,6 +92,15 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     const uint32_t b = threadIdx.x, lo = b & 15u, hi = b >> 4;
     lut[b] = (mag[lo & 7] | ((lo & 8u) << 12)) | ((mag[hi & 7] | ((hi & 8u) << 12)) << 16);
   }
+  const int w_row0 = e * N + strip * MX_STRIP;      // row of the stacked weight matrix [E * N, K / 2]
+  if (warp >= 2) {
+    // the block scales of this CTA's K range, two bytes per 64-wide chunk: all loads are independent, so their latencies overlap
+    const int dt = threadIdx.x - 64;
+    const int srow_i = dt & 127, half = dt >> 7;
+    const uint8_t* srow = scales + (size_t)(w_row0 + srow_i) * (K / 32) + (size_t)c_begin * 2;
+    uint16_t* dsts = (uint16_t*)(smem + L.sc_off + srow_i * MX_SC_ROW);
+    for (int c = half; c < nchunks; c += 2) dsts[c] = *reinterpret_cast<const uint16_t*>(srow + 2 * c);
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < MX_OP_STAGES; ++i) { mbar_init(&op_full[i], MX_DEC_WARPS / MX_GROUPS + 1); mbar_init(&op_empty[i], 1); }
     for (int i = 0; i < MX_RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], MX_DEC_WARPS / MX_GROUPS); }
@@ -106,7 +118,6 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int w_row0 = e * N + strip * MX_STRIP;      // row of the stacked weight matrix [E * N, K / 2]
 
   if (warp == 0) {
     if (lane == 0) {
@@ -151,14 +162,11 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     const int dw = warp - 2;
     const int grp = dw / (MX_DEC_WARPS / MX_GROUPS);
     const int t = (dw % (MX_DEC_WARPS / MX_GROUPS)) * 32 + lane;     // row of the strip this thread expands
-    const uint8_t* srow = scales + (size_t)(w_row0 + t) * (K / 32);
+    const uint16_t* srow = (const uint16_t*)(smem + L.sc_off + t * MX_SC_ROW);
     bool ok = true;
-    uint32_t sc_next = 0;
-    if (grp < nchunks) sc_next = *reinterpret_cast<const uint16_t*>(srow + (size_t)(c_begin + grp) * 2);
     for (int c = grp; c < nchunks && ok; c += MX_GROUPS) {
       const int rs = c % MX_RAW_STAGES, os = c % MX_OP_STAGES;
-      const uint32_t sc = sc_next;
-      if (c + MX_GROUPS < nchunks) sc_next = *reinterpret_cast<const uint16_t*>(srow + (size_t)(c_begin + c + MX_GROUPS) * 2);
+      const uint32_t sc = srow[c];
       ok = mbar_wait(&raw_full[rs], (c / MX_RAW_STAGES) & 1, abort_flag, status, 63);
       if (!ok) break;
       const uint4* raw = reinterpret_cast<const uint4*>(smem + L.raw_off + rs * MX_RAW_STAGE + t * 32);
@@ -178,8 +186,9 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         uint32_t o[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint32_t v = lut[(w >> (8 * q)) & 0xFFu];
-          const __half2 p = __hmul2(*reinterpret_cast<const __half2*>(&v), s2);
+          // one hardware conversion per byte (two E2M1 values -> half2); the table in shared memory costs bank conflicts instead
+          const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w >> (8 * q)) & 0xFFu), __NV_E2M1);
+          const __half2 p = __hmul2(*reinterpret_cast<const __half2*>(&hr), s2);
           o[q] = *reinterpret_cast<const uint32_t*>(&p);
         }
         *reinterpret_cast<uint4*>(a_row + ((j ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -249,6 +258,7 @@ RX_API int rx_mxfp4_gemm_grouped(const void* xs, int pairs_cap, int K, const voi
                                  int splits, const void* tile_tab, int max_tiles, int tile_rows, int* status, void* stream) {
   if (pairs_cap <= 0 || K % 128 != 0 || N % 128 != 0 || splits < 1 || splits > K / MX_KCH || max_tiles < 1 || max_tiles > 65535 || experts < 1)
     return (int)cudaErrorInvalidValue;
+  if (((K / MX_KCH + splits - 1) / splits + 1) * 2 > MX_SC_ROW) return (int)cudaErrorInvalidValue;   // a split's scale bytes must fit its shared-memory row
   int b = 16;
   while (b < tile_rows && b < 256) b <<= 1;
   if (b != tile_rows) return (int)cudaErrorInvalidValue;

@@ -58,6 +58,7 @@ def _declare(lib):
                                               c_void, c_void, c_void]),
         "rx_exl3_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_ll, c_int, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),
         "rx_moe_router": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f, c_void, c_void, c_void]),
+        "rx_moe_router2": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f, c_void, c_void, c_void, c_void]),
         "rx_moe_plan": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
