@@ -85,7 +85,25 @@ def build(args):
         kv_tokens = args.kv_tokens or args.slots * args.max_model_len
         info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None}
 
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+
+        def make_tp():
+            """Rank 0 of a tensor-parallel group (the other ranks run `follow_rank`): the engine over the lockstep TP backend."""
+            from ..engine.tp_backend import DenseTpBackend
+            from ..parallel import runtime as tprt
+            ctx = tprt.init(timeout_s=600)
+            blocks = -(-args.max_model_len // dense.PAGE) + 1
+            pages = -(-kv_tokens // dense.PAGE) + args.slots
+            shard, _group = tprt.build_dense_tp(ctx, cfg, num_pages=pages, max_rows=max(256, args.prefill_chunk), max_slots=args.slots,
+                                                max_blocks_per_seq=blocks, weights=weights)
+            be = DenseTpBackend(shard, args.slots, ctx.ctrl, use_graphs=not args.no_graphs)
+            prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
+            return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode())
+
         def make():
+            if args.backend == "cuda" and world > 1:
+                return make_tp()
             if args.backend == "cpu":
                 from ..engine.cpu_backend import CpuDenseBackend
                 be = CpuDenseBackend(weights if weights is not None else dense.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
@@ -113,6 +131,29 @@ def build(args):
     return make, tok, fmt, name, info
 
 
+def follow_rank(args) -> int:
+    """Ranks 1.. of a tensor-parallel group: no HTTP, no scheduler - repeat the leader's launches until it stops.
+    Exit status 0 on a clean stop, 70 when the group is lost or the device reports an error (the supervisor restarts the group)."""
+    from ..engine.tp_backend import follow
+    from ..models import dense
+    from ..parallel import runtime as tprt
+    try:
+        if args.random_init:
+            cfg, weights = dense.CONFIGS[args.random_init], None
+        else:
+            from ..quant import quantize
+            cfg, weights = quantize.config_from_pack(args.model), quantize.load_pack(args.model)
+        kv_tokens = args.kv_tokens or args.slots * args.max_model_len
+        ctx = tprt.init(timeout_s=600)
+        shard, group = tprt.build_dense_tp(ctx, cfg, num_pages=-(-kv_tokens // dense.PAGE) + args.slots, max_rows=max(256, args.prefill_chunk),
+                                           max_slots=args.slots, max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, weights=weights)
+        follow(shard, args.slots, ctx.ctrl, use_graphs=not args.no_graphs)
+        return 0
+    except Exception as e:  # a lost leader surfaces as a transport error or a device status
+        print(f"rexl3 level=error event=follower_lost rank={os.environ.get('RANK')} error={e!r}", file=sys.stderr, flush=True)
+        return 70
+
+
 def make_app(args, metrics: Metrics | None = None):
     make, tok, fmt, name, info = build(args)
     rc = RuntimeConfig(queue_depth=args.queue_depth, queue_timeout_s=args.queue_timeout, request_timeout_s=args.request_timeout,
@@ -132,6 +173,8 @@ def main(argv=None) -> int:
         from .. import __version__
         print(f"rexl3-serve (rexl3_b200) {__version__}")
         return 0
+    if args.backend == "cuda" and int(os.environ.get("WORLD_SIZE", "1")) > 1 and int(os.environ.get("RANK", "0")) != 0:
+        return follow_rank(args)
     import uvicorn
     print(f"rexl3 event=start backend={args.backend} host={args.host} port={args.port}", file=sys.stderr, flush=True)
     app, handle = make_app(args)
@@ -156,6 +199,12 @@ def main(argv=None) -> int:
     signal.signal(signal.SIGINT, on_signal)
     server.run()
     handle.stop()
+    be = getattr(getattr(handle, "engine", None), "backend", None)
+    if hasattr(be, "stop"):          # a tensor-parallel leader releases its followers (they exit 0 on the stop message)
+        try:
+            be.stop()
+        except Exception:
+            pass
     return 0
 
 
