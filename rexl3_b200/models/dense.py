@@ -251,7 +251,7 @@ class DenseGPU:
     """
 
     def __init__(self, w: "HostWeights | DenseConfig", num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256,
-                 device="cuda", max_prefill_rows: int = 8192, seed: int = 0):
+                 device="cuda", max_prefill_rows: int = 8192, seed: int = 0, kv_dtype: str = "bf16"):
         """`w` is either host weights (uploaded as stored) or a bare config (random-init EXL3 weights are then generated on the
         device: any random bit ring is a valid trellis, which is how benchmark models of tens of GB are made in seconds)."""
         from ..ops import kernels as K
@@ -266,9 +266,16 @@ class DenseGPU:
         self.num_pages, self.max_seqs, self.max_blocks = num_pages, max_seqs, max_blocks_per_seq
         self.max_rows = max(max_rows, max_prefill_rows)
         self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
-        # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16, plus their TMA descriptors
-        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16 (or E4M3 bytes with one scale per layer, K/V and head),
+        # plus their TMA descriptors
+        if kv_dtype not in ("bf16", "fp8"):
+            raise ValueError(f"kv_dtype {kv_dtype!r}: bf16 or fp8")
+        self.kv_fp8 = kv_dtype == "fp8"
+        cdt = torch.uint8 if self.kv_fp8 else torch.bfloat16
+        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) for _ in range(cfg.n_layers)]
+        self.kv_scale = torch.ones(cfg.n_layers, 2, cfg.n_kv, dtype=torch.float32, device=device) if self.kv_fp8 else None
+        self.kv_amax = None        # set while calibrating
         self.tk = [K.KvTensorMap(c) for c in self.k_cache]
         self.tv = [K.KvTensorMap(c) for c in self.v_cache]
         self.status = K.new_status(device)
@@ -353,6 +360,29 @@ class DenseGPU:
             n += sum(L[k].nbytes for k in ("qkv", "o", "gate_up", "down"))
         return n
 
+    def calibrate_kv(self, tokens, passes: int = 2, headroom: float = 1.25) -> None:
+        """FP8 cache: set the per-(layer, K/V, head) scales from the largest |K| and |V| seen while prefilling `tokens` (a list of token ids,
+        at most one page table row long) into page 0..: scale = amax * headroom / 448.  Two passes, because the first one stores with
+        scale 1.  A pack that ships calibrated scales sets `kv_scale` directly instead.  The pages used are scratch: call before serving."""
+        if not self.kv_fp8:
+            return
+        T = len(tokens)
+        dev = self.device
+        nb = (T + PAGE - 1) // PAGE
+        assert nb <= min(self.max_blocks, self.num_pages) and T <= self.max_rows
+        bt = torch.zeros(self.max_seqs, self.max_blocks, dtype=torch.int32, device=dev)
+        bt[0, :nb] = torch.arange(nb, dtype=torch.int32, device=dev)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)  # noqa: E731
+        pos = list(range(T))
+        pf = dict(seq_ids=i32([0]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+        args = (i32(list(tokens)), i32(pos), i32(pos), i32([0] * T), i32([p + 1 for p in pos]), bt)
+        for _ in range(passes):
+            self.kv_amax = torch.zeros_like(self.kv_scale)
+            self.forward_rows(*args, prefill=pf, want_logits=False)
+            torch.cuda.synchronize()
+            self.kv_scale.copy_(torch.clamp(self.kv_amax, min=1e-4) * (headroom / 448.0))
+        self.kv_amax = None
+
     # ------------------------------------------------------------------ forward
     def _linear(self, xr, w, rows, cls, name):
         s = self.splits[(cls, name)]
@@ -415,15 +445,16 @@ class DenseGPU:
         for li in range(nl):
             L = self.layers[li]
             s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
+            ksc = self.kv_scale[li] if self.kv_fp8 else None
             K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
-                              self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li])
+                              self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li])
             if prefill is None:
                 K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
-                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status)
+                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc)
             else:
                 ao = self.attn_out[:M]
                 K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
-                               ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status)
+                               ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc)
                 K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
             s = self._linear(xr_a, L["o"], M, cls, "o")
             nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)

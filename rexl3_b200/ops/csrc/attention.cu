@@ -13,6 +13,7 @@
 // each take 16 keys of every page and are merged in warp order.
 // Prefill: one CTA per (64 query rows, q head, sequence); warps own 16 query rows each and walk the pages causally.
 #include <cuda.h>
+#include <cuda_fp8.h>
 #include "common.cuh"
 
 namespace rx {
@@ -32,6 +33,19 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// a bf16 pair (as loaded from the query buffer) as an fp16 pair
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t u) {
+  return pack_f16(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -58,9 +72,43 @@ __device__ __forceinline__ void load_kv_page(uint8_t* kdst, uint8_t* vdst, const
   }
 }
 
+// FP8 (E4M3) cache: a page of one KV head is 64 x HD bytes, loaded unswizzled, then expanded by the whole CTA to an fp16 tile in the
+// swizzled layout the fragment loads expect.  E4M3 -> fp16 is exact; the per-head scale is applied to the scores / the output.
+template <int HD>
+__device__ __forceinline__ void load_kv_page8(uint8_t* kdst, uint8_t* vdst, const CUtensorMap* tk, const CUtensorMap* tv, int page, int kvh,
+                                              int n_kv, uint64_t* bar) {
+  constexpr int BYTES = PAGE * HD;
+  mbar_arrive_expect_tx(bar, 2 * BYTES);
+  const int y = (page * n_kv + kvh) * PAGE;
+  tma_load_2d(kdst, tk, 0, y, bar);
+  tma_load_2d(vdst, tv, 0, y, bar);
+}
+
+template <int HD>
+__device__ __forceinline__ void expand_page8(const uint8_t* src, uint8_t* dst) {
+  constexpr int CHUNKS = PAGE * HD / 16;          // 16 fp8 values each
+  const uint32_t dbase = smem_u32(dst);
+  for (int c = threadIdx.x; c < CHUNKS; c += ATT_THREADS) {
+    const int key = c / (HD / 16), j = c % (HD / 16);
+    const uint4 r = *reinterpret_cast<const uint4*>(src + (size_t)c * 16);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    uint32_t h[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xFFFFu), __NV_E4M3);
+      const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
+      h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+      h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+    const uint32_t a0 = kv_chunk_addr<HD>(dbase, key, 2 * j), a1 = kv_chunk_addr<HD>(dbase, key, 2 * j + 1);
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+  }
+}
+
 // One 16-row x NK-key step of flash attention for a warp.  qa: Q fragments [HD/16][4]; keys [key0, key0 + NK) of the
 // page tile at (ksm, vsm).  valid = number of unmasked keys counted from key0 for rows (r_lo) and (r_hi) (causal/ctx).
-template <int HD, int NK>
+template <int HD, int NK, bool F16 = false>
 __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint32_t ksm, uint32_t vsm, int key0, int valid_lo, int valid_hi,
                                           float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HD / 8][4]) {
   const int lane = threadIdx.x & 31;
@@ -76,8 +124,8 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
       const int mi = lane >> 3;
       const int key = key0 + jp * 16 + (mi >> 1) * 8 + (lane & 7);
       ldsm_x4(kv_chunk_addr<HD>(ksm, key, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-      mma_bf16(s[2 * jp], qa[ks], b0, b1);
-      mma_bf16(s[2 * jp + 1], qa[ks], b2, b3);
+      if constexpr (F16) { mma_f16(s[2 * jp], qa[ks], b0, b1); mma_f16(s[2 * jp + 1], qa[ks], b2, b3); }
+      else { mma_bf16(s[2 * jp], qa[ks], b0, b1); mma_bf16(s[2 * jp + 1], qa[ks], b2, b3); }
     }
   }
   // mask + row max
@@ -113,8 +161,8 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
       p[e] = (mm == -INFINITY) ? 0.f : exp2f(s[j][e] - mm);
       rs[e >> 1] += p[e];
     }
-    pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
-    pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+    pa[j >> 1][(j & 1) * 2 + 0] = F16 ? pack_f16(p[0], p[1]) : pack_bf16(p[0], p[1]);
+    pa[j >> 1][(j & 1) * 2 + 1] = F16 ? pack_f16(p[2], p[3]) : pack_bf16(p[2], p[3]);
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) l[r] = l[r] * corr[r] + rs[r];
@@ -130,8 +178,8 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
       const int mi = lane >> 3;
       const int key = key0 + kp * 16 + (mi & 1) * 8 + (lane & 7);
       ldsm_x4_t(kv_chunk_addr<HD>(vsm, key, dp * 2 + (mi >> 1)), b0, b1, b2, b3);
-      mma_bf16(o[2 * dp], pa[kp], b0, b1);
-      mma_bf16(o[2 * dp + 1], pa[kp], b2, b3);
+      if constexpr (F16) { mma_f16(o[2 * dp], pa[kp], b0, b1); mma_f16(o[2 * dp + 1], pa[kp], b2, b3); }
+      else { mma_bf16(o[2 * dp], pa[kp], b0, b1); mma_bf16(o[2 * dp + 1], pa[kp], b2, b3); }
     }
   }
 }
@@ -139,21 +187,26 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
 // ------------------------------------------------------------------------------------------------ decode (split-KV)
 // part_o  : f32 [rows][n_q][max_chunks][HD]   unnormalised partial outputs
 // part_ml : f32 [rows][n_q][max_chunks][2]    (running max in log2 units, sum)
-template <int HD>
+template <int HD, bool FP8>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2, int* status) {
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2_in, int* status,
+                   const float* __restrict__ kv_scale) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int TILE = PAGE * HD * 2;
-  uint64_t* bars = (uint64_t*)(smem + 2 * KV_STAGES * TILE);
+  constexpr int T16 = PAGE * HD * 2;
+  constexpr int TILE = FP8 ? PAGE * HD : T16;       // bytes of one stage of K (or V)
+  uint8_t* conv = smem + 2 * KV_STAGES * TILE;       // FP8: the expanded fp16 K and V tiles of the page being processed
+  uint64_t* bars = (uint64_t*)(conv + (FP8 ? 2 * T16 : 0));
   volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
   const int row = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = n_q / n_kv;
+  const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
+  const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
   const int ctx = ctx_len[row];
   const int k_begin = chunk * DEC_CHUNK;
   if (k_begin >= ctx) return;  // uniform for the CTA; the merge kernel only reads chunks below ctx
@@ -168,8 +221,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p)
-      load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
+    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
+      if constexpr (FP8) load_kv_page8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
+      else load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
+    }
   }
   // Q fragments straight from global: rows of the MMA tile are the G query heads of this KV head
   uint32_t qa[HD / 16][4];
@@ -183,6 +238,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       qa[ks][1] = h1 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h1 * HD + c) : 0u;
       qa[ks][2] = h0 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h0 * HD + c + 8) : 0u;
       qa[ks][3] = h1 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h1 * HD + c + 8) : 0u;
+      if constexpr (FP8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qa[ks][i] = bf16x2_to_f16x2(qa[ks][i]);
+      }
     }
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -195,14 +254,22 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
     const int s = p % KV_STAGES;
     if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
       const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;  // stage sn was consumed in iteration p-1 (barrier below)
-      load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+      if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+      else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
     }
     ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 50);
     if (!ok) break;
     const int key0 = warp * 16;
     const int valid = k_end - (k_begin + p * PAGE + key0);
-    if (valid > 0)
-      attn_step<HD, 16>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid, valid, scale_log2, m, l, o);
+    if constexpr (FP8) {
+      expand_page8<HD>(smem + s * TILE, conv);
+      expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
+      __syncthreads();
+      if (valid > 0) attn_step<HD, 16, true>(qa, smem_u32(conv), smem_u32(conv + T16), key0, valid, valid, scale_log2, m, l, o);
+    } else {
+      if (valid > 0)
+        attn_step<HD, 16>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid, valid, scale_log2, m, l, o);
+    }
     __syncthreads();
   }
   if (!ok || *abort_flag != 0) return;
@@ -244,7 +311,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       lsum += f * sm_ml[(w * 16 + hq) * 2 + 1];
     }
     const size_t pidx = ((size_t)row * n_q + (size_t)kvh * G + hq) * max_chunks + chunk;
-    part_o[pidx * HD + d] = acc;
+    part_o[pidx * HD + d] = acc * v_scale;
     if (d == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = lsum; }
   }
 }
@@ -326,18 +393,20 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 // ------------------------------------------------------------------------------------------------ prefill (causal flash)
 // Queries: rows [q_start[s], q_start[s] + q_len[s]) of `q` belong to sequence s at positions pos0[s].. ; keys are the
 // sequence's cached tokens [0, pos0 + local row] (the chunk's own K/V are already in the cache).  out: bf16 [rows][n_q*HD].
-template <int HD>
+template <int HD, bool FP8>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_ids, const int* __restrict__ q_start,
-                    const int* __restrict__ q_len, const int* __restrict__ pos0, uint16_t* __restrict__ out, int n_q, int n_kv, float scale_log2,
-                    int* status) {
+                    const int* __restrict__ q_len, const int* __restrict__ pos0, uint16_t* __restrict__ out, int n_q, int n_kv, float scale_log2_in,
+                    int* status, const float* __restrict__ kv_scale) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int TILE = PAGE * HD * 2;
-  uint64_t* bars = (uint64_t*)(smem + 2 * KV_STAGES * TILE);
+  constexpr int T16 = PAGE * HD * 2;
+  constexpr int TILE = FP8 ? PAGE * HD : T16;
+  uint8_t* conv = smem + 2 * KV_STAGES * TILE;
+  uint64_t* bars = (uint64_t*)(conv + (FP8 ? 2 * T16 : 0));
   volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
   const int s_idx = blockIdx.z, hq = blockIdx.y;
   const int qlen = q_len[s_idx];
@@ -347,6 +416,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   if (qt < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = n_q / n_kv, kvh = hq / G;
+  const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;
+  const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
   const int p0 = pos0[s_idx], r_base = q_start[s_idx];
   const int* bt = block_table + (size_t)seq_ids[s_idx] * max_blocks;
   const int q_lo = qt * 64;
@@ -360,8 +431,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p)
-      load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
+    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
+      if constexpr (FP8) load_kv_page8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
+      else load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
+    }
   }
   uint32_t qa[HD / 16][4];
   const int lr0 = q_lo + warp * 16 + (lane >> 2), lr1 = lr0 + 8;  // local query rows of this lane
@@ -375,6 +448,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
       qa[ks][1] = lr1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
       qa[ks][2] = lr0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
       qa[ks][3] = lr1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+      if constexpr (FP8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qa[ks][i] = bf16x2_to_f16x2(qa[ks][i]);
+      }
     }
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -388,14 +465,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     const int s = p % KV_STAGES;
     if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
       const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;
-      load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
+      if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
+      else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
     }
     ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 60);
     if (!ok) break;
     const int kbase = p * PAGE;
-    if (kbase <= warp_last_key && q_lo + warp * 16 < qlen) {
-      const int v0 = lr0 < qlen ? (p0 + lr0 + 1 - kbase) : 0, v1 = lr1 < qlen ? (p0 + lr1 + 1 - kbase) : 0;
-      attn_step<HD, 64>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), 0, v0, v1, scale_log2, m, l, o);
+    const bool mine = kbase <= warp_last_key && q_lo + warp * 16 < qlen;
+    const int v0 = lr0 < qlen ? (p0 + lr0 + 1 - kbase) : 0, v1 = lr1 < qlen ? (p0 + lr1 + 1 - kbase) : 0;
+    if constexpr (FP8) {
+      expand_page8<HD>(smem + s * TILE, conv);
+      expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
+      __syncthreads();
+      if (mine) attn_step<HD, 64, true>(qa, smem_u32(conv), smem_u32(conv + T16), 0, v0, v1, scale_log2, m, l, o);
+    } else {
+      if (mine) attn_step<HD, 64>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), 0, v0, v1, scale_log2, m, l, o);
     }
     __syncthreads();
   }
@@ -405,7 +489,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  const float i0 = l[0] > 0.f ? 1.f / l[0] : 0.f, i1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  const float i0 = l[0] > 0.f ? v_scale / l[0] : 0.f, i1 = l[1] > 0.f ? v_scale / l[1] : 0.f;
 #pragma unroll
   for (int d = 0; d < HD / 8; ++d) {
     const int c = d * 8 + 2 * (lane & 3);
@@ -429,7 +513,9 @@ static EncodeTiledFn att_encode_tiled() {
   return fn;
 }
 
-static int att_smem_bytes(int hd) { return 2 * KV_STAGES * PAGE * hd * 2 + 64 + 1024; }
+static int att_smem_bytes(int hd, bool fp8 = false) {
+  return (fp8 ? 2 * KV_STAGES * PAGE * hd + 2 * PAGE * hd * 2 : 2 * KV_STAGES * PAGE * hd * 2) + 64 + 1024;
+}
 
 }  // namespace rx
 
@@ -449,6 +535,20 @@ RX_API int rx_make_kv_tmap(void* out128, const void* base, long long total_rows,
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Tensor map of an FP8 (E4M3) cache [num_pages][n_kv][64][hd] viewed as bytes [num_pages*n_kv*64, hd]; one page of one head is one box.
+RX_API int rx_make_kv_tmap8(void* out128, const void* base, long long total_rows, int hd) {
+  EncodeTiledFn enc = att_encode_tiled();
+  if (enc == nullptr) return (int)cudaErrorNotSupported;
+  if (hd % 64 != 0 || hd > 256 || (((uintptr_t)base) & 127) != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)total_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)hd};
+  cuuint32_t box[2] = {(cuuint32_t)hd, PAGE};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc((CUtensorMap*)out128, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 RX_API int rx_attn_decode_chunk() { return DEC_CHUNK; }
 
 // scratch sizes (floats) for `rows` rows and contexts up to max_ctx
@@ -457,23 +557,23 @@ RX_API long long rx_attn_decode_scratch_floats(int rows, int n_q, int hd, int ma
   return (long long)rows * n_q * mc * (hd + 2);
 }
 
-template <int HD>
+template <int HD, bool FP8>
 static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                          const int* ctx_len, float* scratch, int rows, int n_q, int n_kv, int max_ctx, float scale, const void* suh, void* xr,
-                         void* out_bf16, int* status, cudaStream_t st) {
+                         void* out_bf16, int* status, cudaStream_t st, const float* kv_scale) {
   const int mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)rows * n_q * mc * HD;
-  const int smem = att_smem_bytes(HD);
+  const int smem = att_smem_bytes(HD, FP8);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(rows, n_kv, mc);
-  rx::launch(attn_decode_kernel<HD>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, n_q,
-                                                         n_kv, mc, scale * 1.4426950408889634f, status);
+  rx::launch(attn_decode_kernel<HD, FP8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, n_q,
+                                                         n_kv, mc, scale * 1.4426950408889634f, status, kv_scale);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   const int blocks128 = n_q * HD / 128;
@@ -487,45 +587,44 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
 // q: bf16 [rows][n_q*hd] (already rotated by RoPE).  Either/both outputs: xr = fp16(H(out*suh)) [rows][n_q*hd], out_bf16.
 RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* row_seq,
                           const void* ctx_len, void* scratch, int rows, int n_q, int n_kv, int hd, int max_ctx, float scale, const void* suh,
-                          void* xr, void* out_bf16, int* status, void* stream) {
+                          void* xr, void* out_bf16, int* status, void* stream, const void* kv_scale) {
   if (n_q % n_kv != 0 || n_q / n_kv > 16 || (n_q * hd) % 128 != 0 || rows <= 0 || max_ctx <= 0) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
-  if (hd == 128)
-    return launch_decode<128>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)row_seq,
-                              (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st);
-  if (hd == 64)
-    return launch_decode<64>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)row_seq,
-                             (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st);
+  // kv_scale != nullptr: the maps describe an FP8 cache and kv_scale is f32 [2][n_kv] (K scales, then V scales) of this layer
+#define RX_DEC(HDV, F8) launch_decode<HDV, F8>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
+    (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, (const float*)kv_scale)
+  if (hd == 128) return kv_scale ? RX_DEC(128, true) : RX_DEC(128, false);
+  if (hd == 64) return kv_scale ? RX_DEC(64, true) : RX_DEC(64, false);
+#undef RX_DEC
   return (int)cudaErrorInvalidValue;
 }
 
-template <int HD>
+template <int HD, bool FP8>
 static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* seq_ids,
                           const int* q_start, const int* q_len, const int* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, float scale,
-                          int* status, cudaStream_t st) {
-  const int smem = att_smem_bytes(HD);
+                          int* status, cudaStream_t st, const float* kv_scale) {
+  const int smem = att_smem_bytes(HD, FP8);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid((max_qlen + 63) / 64, n_q, nseq);
-  rx::launch(attn_prefill_kernel<HD>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
-                                                          (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status);
+  rx::launch(attn_prefill_kernel<HD, FP8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
+                                                          (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status, kv_scale);
   return (int)cudaGetLastError();
 }
 
 RX_API int rx_attn_prefill(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
                            const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
-                           float scale, int* status, void* stream) {
+                           float scale, int* status, void* stream, const void* kv_scale) {
   if (n_q % n_kv != 0 || nseq <= 0 || max_qlen <= 0) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
-  if (hd == 128)
-    return launch_prefill<128>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)seq_ids,
-                               (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st);
-  if (hd == 64)
-    return launch_prefill<64>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)seq_ids,
-                              (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st);
+#define RX_PF(HDV, F8) launch_prefill<HDV, F8>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
+    (const int*)seq_ids, (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st, (const float*)kv_scale)
+  if (hd == 128) return kv_scale ? RX_PF(128, true) : RX_PF(128, false);
+  if (hd == 64) return kv_scale ? RX_PF(64, true) : RX_PF(64, false);
+#undef RX_PF
   return (int)cudaErrorInvalidValue;
 }

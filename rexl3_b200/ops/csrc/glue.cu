@@ -3,6 +3,7 @@
 // Semantics matched: reference crates/cuda/csrc/glue.cu:182 (attn_prep: q/k norm + RoPE), attention.cu:234 (kv_write),
 // glue.cu:667-709 (two-stage exact top-k with 64-bit keys, value desc / id asc).  KV layout is this engine's own:
 // bf16 [num_pages][n_kv][64][head_dim].
+#include <cuda_fp8.h>
 #include "exl3_decode.cuh"
 
 namespace rx {
@@ -21,7 +22,9 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
                                        const float* __restrict__ bias, const uint16_t* __restrict__ q_norm, const uint16_t* __restrict__ k_norm,
                                        float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                        const int* __restrict__ slot, uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
-                                       uint16_t* __restrict__ v_cache) {
+                                       uint16_t* __restrict__ v_cache, const float* __restrict__ kv_scale, float* __restrict__ kv_amax) {
+  // kv_scale != nullptr: the caches are FP8 (E4M3) bytes and K / V are stored as value / scale[head] (f32 [2][n_kv]: K scales, V scales),
+  // saturating.  kv_amax != nullptr: the largest |K| and |V| per head are tracked there (f32 [2][n_kv]; used to calibrate the scales).
   pdl_launch();
   pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -90,7 +93,20 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
     } else if (sl >= 0) {
       const int kvh = is_k ? head - n_q : head - n_q - n_kv;
       const size_t addr = (((size_t)(sl / 64) * n_kv + kvh) * 64 + (sl % 64)) * HD + d0;
-      *reinterpret_cast<uint2*>((is_k ? k_cache : v_cache) + addr) = u;
+      if (kv_amax != nullptr) {
+        float am = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
+#pragma unroll
+        for (int o = 1; o < GL; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        if ((lane % GL) == 0) atomicMax(reinterpret_cast<unsigned*>(kv_amax) + (is_k ? 0 : n_kv) + kvh, __float_as_uint(am));   // non-negative floats order like their bits
+      }
+      if (kv_scale != nullptr) {
+        const float inv = 1.f / kv_scale[(is_k ? 0 : n_kv) + kvh];
+        const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(make_float2(y[0] * inv, y[1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t b2 = __nv_cvt_float2_to_fp8x2(make_float2(y[2] * inv, y[3] * inv), __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(is_k ? k_cache : v_cache) + addr) = (uint32_t)a | ((uint32_t)b2 << 16);
+      } else {
+        *reinterpret_cast<uint2*>((is_k ? k_cache : v_cache) + addr) = u;
+      }
     }
   }
 }
@@ -181,14 +197,15 @@ using namespace rx;
 
 RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv, int hd, const void* svh, const void* bias, const void* q_norm,
                               const void* k_norm, float eps, const void* positions, const void* inv_freq, const void* slot, void* q_out,
-                              void* k_cache, void* v_cache, void* stream) {
+                              void* k_cache, void* v_cache, void* stream, const void* kv_scale, void* kv_amax) {
   const int N = (n_q + 2 * n_kv) * hd;
   if (N % 128) return (int)cudaErrorInvalidValue;
   const int per_row = (N / 128 + 7) / 8;   // one warp per 128-block
   dim3 grid(M, per_row < 1 ? 1 : per_row);
   cudaStream_t st = (cudaStream_t)stream;
 #define RX_ARGS (const float*)part, S, M, n_q, n_kv, (const __half*)svh, (const float*)bias, (const uint16_t*)q_norm, (const uint16_t*)k_norm, eps, \
-                (const int*)positions, (const float*)inv_freq, (const int*)slot, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache
+                (const int*)positions, (const float*)inv_freq, (const int*)slot, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache, \
+                (const float*)kv_scale, (float*)kv_amax
   if (hd == 128) rx::launch(finish_qkv_rope_kernel<128>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else if (hd == 64) rx::launch(finish_qkv_rope_kernel<64>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else return (int)cudaErrorInvalidValue;

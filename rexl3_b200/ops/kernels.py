@@ -127,11 +127,14 @@ def finish_swiglu_rot(part, S, M, w: Exl3Weight, suh_down: torch.Tensor, xr: tor
     _lib.count()
 
 
-def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, eps, positions, inv_freq, slot, q_out, k_cache, v_cache) -> None:
+def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, eps, positions, inv_freq, slot, q_out, k_cache, v_cache,
+                    kv_scale=None, kv_amax=None) -> None:
+    """kv_scale (f32 [2, n_kv]) given: the caches are FP8 (E4M3) and K, V are stored divided by their head's scale.  kv_amax (f32 [2, n_kv])
+    given: the largest |K| and |V| per head are recorded there."""
     L = _lib.load()
     _lib.check(L.rx_finish_qkv_rope(part.data_ptr(), S, M, n_q, n_kv, hd, w.svh.data_ptr(), _lib.ptr(w.bias), _lib.ptr(q_norm), _lib.ptr(k_norm),
                                     eps, positions.data_ptr(), inv_freq.data_ptr(), slot.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
-                                    v_cache.data_ptr(), _lib.stream_ptr()), "rx_finish_qkv_rope")
+                                    v_cache.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kv_amax)), "rx_finish_qkv_rope")
     _lib.count()
 
 
@@ -153,11 +156,15 @@ class KvTensorMap:
 
     def __init__(self, cache: torch.Tensor):
         pages, n_kv, page, hd = cache.shape
-        assert page == 64 and cache.dtype == torch.bfloat16 and cache.is_contiguous()
+        assert page == 64 and cache.dtype in (torch.bfloat16, torch.uint8) and cache.is_contiguous()
         self.buf = np.zeros(128, dtype=np.uint8)
         self._keep = cache
+        self.fp8 = cache.dtype == torch.uint8          # E4M3 bytes
         L = _lib.load()
-        _lib.check(L.rx_make_kv_tmap(self.buf.ctypes.data, cache.data_ptr(), pages * n_kv * page, hd), "rx_make_kv_tmap")
+        if self.fp8:
+            _lib.check(L.rx_make_kv_tmap8(self.buf.ctypes.data, cache.data_ptr(), pages * n_kv * page, hd), "rx_make_kv_tmap8")
+        else:
+            _lib.check(L.rx_make_kv_tmap(self.buf.ctypes.data, cache.data_ptr(), pages * n_kv * page, hd), "rx_make_kv_tmap")
 
     @property
     def ptr(self) -> int:
@@ -170,19 +177,21 @@ def attn_decode_scratch(rows: int, n_q: int, hd: int, max_ctx: int, device="cuda
 
 
 def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_len, scratch, n_q, n_kv, hd, max_ctx, scale, suh, xr, out,
-                status) -> None:
+                status, kv_scale=None) -> None:
+    assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
     rows = q.shape[0]
     L = _lib.load()
     _lib.check(L.rx_attn_decode(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
                                 scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out),
-                                status.data_ptr(), _lib.stream_ptr()), "rx_attn_decode")
+                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale)), "rx_attn_decode")
     _lib.count(2)
 
 
 def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,
-                 status) -> None:
+                 status, kv_scale=None) -> None:
+    assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
     L = _lib.load()
     _lib.check(L.rx_attn_prefill(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], seq_ids.data_ptr(), q_start.data_ptr(),
                                  q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
-                                 _lib.stream_ptr()), "rx_attn_prefill")
+                                 _lib.stream_ptr(), _lib.ptr(kv_scale)), "rx_attn_prefill")
     _lib.count()

@@ -82,16 +82,17 @@ def _declare(lib):
         "rx_finish_add_norm_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void]),
         "rx_finish_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_finish_qkv_rope": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void,
-                                       c_void, c_void, c_void, c_void, c_void]),
+                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_topk_scratch_bytes": (c_ll, [c_int, c_int, c_int]),
         "rx_topk": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
         "rx_make_kv_tmap": (c_int, [c_void, c_void, c_ll, c_int]),
+        "rx_make_kv_tmap8": (c_int, [c_void, c_void, c_ll, c_int]),
         "rx_attn_decode_chunk": (c_int, []),
         "rx_attn_decode_scratch_floats": (c_ll, [c_int, c_int, c_int, c_int]),
         "rx_attn_decode": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
-                                   c_void, c_void, c_void, c_void, c_void]),
+                                   c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_attn_prefill": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
-                                    c_int, c_f, c_void, c_void]),
+                                    c_int, c_f, c_void, c_void, c_void]),
     }
     for name, (res, args) in sig.items():
         try:

@@ -53,3 +53,39 @@ def test_prefill_and_decode_logits_match_reference(name):
     ids_c, vals_c = m.candidates(logits, 8)
     v, i = torch.sort(logits[:, :cfg.vocab], dim=1, descending=True, stable=True)
     assert torch.equal(ids_c.long(), i[:, :8]) and torch.equal(vals_c, v[:, :8])
+
+
+def test_fp8_kv_cache_close_to_bf16_cache():
+    """E4M3 KV with calibrated per-head scales: prefill + decode logits stay close to the bf16-cache executor."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+    from rexl3_b200.models import dense
+    for name in ("test-hd128", "tiny-llama"):
+        cfg = dense.CONFIGS[name]
+        w = dense.random_weights(cfg, seed=3)
+        a = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+        b = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256, kv_dtype="fp8")
+        rng = np.random.default_rng(0)
+        b.calibrate_kv(rng.integers(0, cfg.vocab, size=128).tolist())
+        assert float(b.kv_scale.min()) > 0 and not torch.equal(b.kv_scale, torch.ones_like(b.kv_scale))
+        prompt = rng.integers(0, cfg.vocab, size=150).tolist()
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+        bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+        bt[1, :3] = i32([5, 9, 2])
+        T = len(prompt)
+        pos = list(range(T))
+        slots = [int(bt[1, p // 64]) * 64 + p % 64 for p in pos]
+        pf = dict(seq_ids=i32([1]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+        args = (i32(prompt), i32(pos), i32(slots), i32([1] * T), i32([p + 1 for p in pos]), bt)
+        la = a.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+        lb = b.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+        a.check(); b.check()
+        scale = la.abs().max().item()
+        assert (la - lb).abs().max().item() < 0.06 * scale
+        p = T
+        a2 = (i32([7]), i32([p]), i32([int(bt[1, p // 64]) * 64 + p % 64]), i32([1]), i32([p + 1]), bt)
+        da = a.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+        db = b.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+        a.check(); b.check()
+        assert (da - db).abs().max().item() < 0.06 * scale
