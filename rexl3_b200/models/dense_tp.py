@@ -69,7 +69,7 @@ class DenseTPShard:
     """One rank of the tensor-parallel model."""
 
     def __init__(self, cfg: DenseConfig, group: _GroupBase, rank: int, num_pages: int, max_rows: int, max_seqs: int, max_blocks_per_seq: int,
-                 weights: dict | None = None, device="cuda", seed: int = 0):
+                 weights: dict | None = None, device="cuda", seed: int = 0, kv_dtype: str = "bf16"):
         check_abi()
         self.cfg, self.g, self.rank, self.R, self.device = cfg, group, rank, group.ranks, device
         R = self.R
@@ -83,8 +83,12 @@ class DenseTPShard:
             self._random(seed)
         self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
         hd = cfg.head_dim
-        self.k_cache = [torch.zeros(num_pages, self.nkv, PAGE, hd, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(num_pages, self.nkv, PAGE, hd, dtype=torch.bfloat16, device=device) for _ in range(cfg.n_layers)]
+        self.kv_fp8 = kv_dtype == "fp8"
+        cdt = torch.uint8 if self.kv_fp8 else torch.bfloat16
+        self.k_cache = [torch.zeros(num_pages, self.nkv, PAGE, hd, dtype=cdt, device=device) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(num_pages, self.nkv, PAGE, hd, dtype=cdt, device=device) for _ in range(cfg.n_layers)]
+        self.kv_scale = torch.ones(cfg.n_layers, 2, self.nkv, dtype=torch.float32, device=device) if self.kv_fp8 else None
+        self.kv_amax = None
         self.tk = [K.KvTensorMap(c) for c in self.k_cache]
         self.tv = [K.KvTensorMap(c) for c in self.v_cache]
         self.status = K.new_status(device)
@@ -245,10 +249,11 @@ class DenseTPShard:
                 x_in = xr0 if li == 0 else xr_d
                 s = sp[("decode", "qkv")]
                 K.exl3_gemm(x_in, L["qkv"], self.part, s, self.status)
+                ksc = self.kv_scale[li] if self.kv_fp8 else None
                 K.finish_qkv_rope(self.part, s, M, self.nq, self.nkv, hd, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions, self.inv_freq,
-                                  slots, q, self.k_cache[li], self.v_cache[li])
+                                  slots, q, self.k_cache[li], self.v_cache[li], ksc)
                 K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, self.nq, self.nkv, hd,
-                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status)
+                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc)
                 K.exl3_gemm(xr_a, L["o"], self.part, sp[("decode", "o")], self.status)
             yield p_attn
             a, b = chain(self.part, sp[("decode", "o")], L["o"], 0, u_o, L["ffn_norm"], L["gate_up"].suh)
@@ -285,11 +290,12 @@ class DenseTPShard:
                     desc.in_flag = None
                 s = sp[(cls, "qkv")]
                 self._gemm(x_in, L["qkv"], self.part.data_ptr(), s, desc)
+                ksc = self.kv_scale[li] if self.kv_fp8 else None
                 K.finish_qkv_rope(self.part, s, M, self.nq, self.nkv, hd, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions, self.inv_freq,
-                                  slots, q, self.k_cache[li], self.v_cache[li])
+                                  slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li])
                 ao = self.attn_out[:M]
                 K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"],
-                               prefill["pos0"], ao, prefill["nseq"], prefill["max_qlen"], self.nq, self.nkv, hd, scale, self.status)
+                               prefill["pos0"], ao, prefill["nseq"], prefill["max_qlen"], self.nq, self.nkv, hd, scale, self.status, ksc)
                 K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
                 so = sp[(cls, "o")]
                 self._gemm(xr_a, L["o"], g.part_ptr(r, 0), so, g.gemm_rs(r, 0, u_o, so, M))
@@ -389,6 +395,26 @@ class DenseTPShard:
                 _lib.count()
                 return self.cand_ids[:Rw * cand_count].view(Rw, cand_count), self.cand_vals[:Rw * cand_count].view(Rw, cand_count)
             yield p_cand_merge
+
+    def calibrate_kv(self, tokens, passes: int = 2, headroom: float = 1.25) -> None:
+        """FP8 cache: per-head scales from a calibration prefill (see DenseGPU.calibrate_kv).  Every rank of the group calls this with the same
+        tokens at the same time (the forward contains the group's collectives)."""
+        if not self.kv_fp8:
+            return
+        T = len(tokens)
+        dev = self.device
+        nb = (T + PAGE - 1) // PAGE
+        bt = torch.zeros(8, max(nb, 1), dtype=torch.int32, device=dev)
+        bt[0, :nb] = torch.arange(nb, dtype=torch.int32, device=dev)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)  # noqa: E731
+        pos = list(range(T))
+        pf = dict(seq_ids=i32([0]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+        for _ in range(passes):
+            self.kv_amax = torch.zeros_like(self.kv_scale)
+            self.forward(i32(list(tokens)), i32(pos), i32(pos), i32([0] * T), i32([p + 1 for p in pos]), bt, prefill=pf, want_logits=False)
+            torch.cuda.synchronize()
+            self.kv_scale.copy_(torch.clamp(self.kv_amax, min=1e-4) * (headroom / 448.0))
+        self.kv_amax = None
 
     def forward(self, *a, **kw):
         out = None

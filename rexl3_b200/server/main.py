@@ -36,7 +36,7 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--kv-tokens", type=int, default=0, help="tokens of KV cache to reserve (0: slots * max-model-len)")
     p.add_argument("--prefill-chunk", type=int, default=4096)
     p.add_argument("--window-rows", type=int, default=64)
-    p.add_argument("--kv-dtype", choices=["bf16"], default="bf16")
+    p.add_argument("--kv-dtype", choices=["bf16", "fp8"], default="bf16", help="fp8: E4M3 cache with per-head scales (calibrated at boot)")
     p.add_argument("--spec", choices=["auto", "mtp", "copy", "self", "none"], default="auto")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
@@ -113,15 +113,19 @@ def build(args):
                 from ..engine.gpu_backend import DenseGpuBackend
                 pages = -(-kv_tokens // dense.PAGE) + args.slots
                 free, _ = torch.cuda.mem_get_info()
-                mm = ModelMemory(int(cfg.weight_params() * cfg.bits / 8), cfg.kv_bytes_per_token(), activation_reserve=2 << 30)
+                kvb = cfg.kv_bytes_per_token(1 if args.kv_dtype == "fp8" else 2)
+                mm = ModelMemory(int(cfg.weight_params() * cfg.bits / 8), kvb, activation_reserve=2 << 30)
                 adm = Admission(free, 1 << 30, mm, args.slots).with_max_context(args.max_model_len).with_kv_tokens(kv_tokens)
                 adm.check(min(args.max_model_len, 1))     # fail closed: a plan that can never hold one token is refused at boot
-                if pages * cfg.kv_bytes_per_token() * dense.PAGE > adm.capacity:
-                    raise RuntimeError(f"memory plan refused: {kv_tokens} KV tokens need {pages * cfg.kv_bytes_per_token() * dense.PAGE >> 20} MiB, "
+                if pages * kvb * dense.PAGE > adm.capacity:
+                    raise RuntimeError(f"memory plan refused: {kv_tokens} KV tokens need {pages * kvb * dense.PAGE >> 20} MiB, "
                                        f"{adm.capacity >> 20} MiB are available after weights and reserve")
                 model = dense.DenseGPU(weights if weights is not None else cfg, num_pages=pages, max_rows=min(256, args.window_rows),
                                        max_seqs=args.slots, max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1,
-                                       max_prefill_rows=args.prefill_chunk)
+                                       max_prefill_rows=args.prefill_chunk, kv_dtype=args.kv_dtype)
+                if args.kv_dtype == "fp8":
+                    import numpy as np
+                    model.calibrate_kv(np.random.default_rng(0).integers(0, cfg.vocab, size=min(256, args.prefill_chunk)).tolist())
                 be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
