@@ -115,7 +115,7 @@ class ByteTokenizer(Tok):
                 if not skip_special:
                     out += self.special_rev[i].encode()
             else:
-                out += b"?" if not skip_special else b""   # ids beyond the byte range have no text in this vocabulary
+                out += b"?"    # ids beyond the byte range have no text in this vocabulary; they are not specials, so they stay visible
         return bytes(out)
 
     def special_id(self, text):
