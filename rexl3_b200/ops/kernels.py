@@ -195,3 +195,38 @@ def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_st
                                  q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
                                  _lib.stream_ptr(), _lib.ptr(kv_scale)), "rx_attn_prefill")
     _lib.count()
+
+
+# ------------------------------------------------------------------------------------------------ device-side verify / accept
+SEQ_SAMPLING = np.dtype([("seed", "<u8"), ("temperature", "<f8"), ("top_p", "<f8"), ("min_p", "<f8"), ("top_k", "<i4"), ("first_row", "<i4"),
+                         ("n_rows", "<i4"), ("position", "<i4")], align=True)
+
+
+def verify_accept(ids: torch.Tensor, vals: torch.Tensor, windows, device="cuda"):
+    """Keyed samples and accepted-draft counts of one window, on the device.
+
+    ids / vals: the window's candidates [rows, count] (value desc, id asc).  windows: per sequence (sampling, position of the first
+    sample, fed tokens [last, d1 .. dk]).  Returns (samples int32 [rows], accepted int32 [n_seqs], error flag int32 [1]) device tensors.
+    """
+    L = _lib.load()
+    if SEQ_SAMPLING.itemsize != L.rx_verify_desc_size():
+        raise _lib.KernelError("sampling descriptor layout mismatch")
+    rows, count = ids.shape
+    desc = np.zeros(len(windows), dtype=SEQ_SAMPLING)
+    row_seq, fed, r = [], [], 0
+    for i, (s, position, tokens) in enumerate(windows):
+        desc[i] = (s.seed, s.temperature, s.top_p, s.min_p, s.top_k, r, len(tokens), position)
+        row_seq += [i] * len(tokens)
+        fed += [int(t) for t in tokens]
+        r += len(tokens)
+    assert r == rows
+    d_desc = torch.from_numpy(desc.view(np.uint8)).to(device)
+    d_seq = torch.tensor(row_seq, dtype=torch.int32, device=device)
+    d_fed = torch.tensor(fed, dtype=torch.int32, device=device)
+    samples = torch.empty(rows, dtype=torch.int32, device=device)
+    accepted = torch.empty(len(windows), dtype=torch.int32, device=device)
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    _lib.check(L.rx_verify_accept(ids.data_ptr(), vals.data_ptr(), rows, count, d_desc.data_ptr(), len(windows), d_seq.data_ptr(), d_fed.data_ptr(),
+                                  samples.data_ptr(), accepted.data_ptr(), err.data_ptr(), _lib.stream_ptr()), "rx_verify_accept")
+    _lib.count()
+    return samples, accepted, err

@@ -63,6 +63,10 @@ def _declare(lib):
         "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_combine_desc_size": (c_int, []),
+        "rx_verify_desc_size": (c_int, []),
+        "rx_trellis_encode_scratch_bytes": (c_ll, [c_int]),
+        "rx_trellis_encode_cuda": (c_int, [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_void]),
+        "rx_verify_accept": (c_int, [c_void, c_void, c_int, c_int, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_mla_scratch_floats": (c_ll, [c_int, c_int, c_int]),
         "rx_mla_attn": (c_int, [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_f, c_void, c_void, c_void]),
         "rx_head_gemm": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_int, c_void, c_int, c_int, c_int, c_void]),

@@ -33,3 +33,22 @@ def encode_tiles(tiles: np.ndarray, bits: exl3.Bits, codebook: str, threads: int
     if rc != 0:
         raise ValueError("trellis encoder refused its arguments")
     return out, err
+
+
+def encode_tiles_cuda(tiles, bits: exl3.Bits, codebook: str, ctas: int = 148, device="cuda"):
+    """The same search on the GPU (one CTA per tile, bit-identical to `encode_tiles`).  tiles: float32 [T, 256] (array or device tensor)
+    in stream order -> (int16 device tensor [T, 16*bits], squared error per tile)."""
+    import torch
+    from ..ops import lib as _oplib
+    L = _oplib.load()
+    t = torch.as_tensor(tiles, dtype=torch.float32).to(device).contiguous()
+    T = t.shape[0]
+    table = torch.from_numpy(np.ascontiguousarray(exl3.codebook_f32(codebook), dtype=np.float32)).to(device)
+    out = torch.zeros(T, bits.tile_words, dtype=torch.int16, device=device)
+    err = torch.zeros(T, dtype=torch.float32, device=device)
+    ctas = max(1, min(ctas, T))
+    scratch = torch.empty(L.rx_trellis_encode_scratch_bytes(ctas), dtype=torch.uint8, device=device)
+    _oplib.check(L.rx_trellis_encode_cuda(t.data_ptr(), T, bits.twice, table.data_ptr(), out.data_ptr(), err.data_ptr(), scratch.data_ptr(), ctas,
+                                          _oplib.stream_ptr()), "rx_trellis_encode_cuda")
+    _oplib.count()
+    return out, err
