@@ -80,6 +80,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--ttft-samples", type=int, default=5)
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: fused peer-memory kernels (default) or NCCL all-reduce in decode windows (the comparison baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -114,7 +116,8 @@ def main():
         from rexl3_b200.engine.tp_backend import DenseTpBackend, follow
         from rexl3_b200.parallel import runtime as tprt
         ctx = tprt.init(timeout_s=600)
-        shard, group = tprt.build_dense_tp(ctx, cfg, num_pages=pages, max_rows=P, max_slots=B + 1, max_blocks_per_seq=blocks_per_seq, seed=0)
+        shard, group = tprt.build_dense_tp(ctx, cfg, num_pages=pages, max_rows=P, max_slots=B + 1, max_blocks_per_seq=blocks_per_seq, seed=0,
+                                            collective=args.collective)
         if rank != 0:
             ex = follow(shard, B + 1, ctx.ctrl)
             m = ex.marks
@@ -232,7 +235,9 @@ def main():
             "config": {"model": f"{cfg.name}: {cfg.n_layers}L d{cfg.d_model} {cfg.n_q}q/{cfg.n_kv}kv x{cfg.head_dim} ffn{cfg.ffn} vocab{cfg.vocab}, "
                                 f"EXL3 {cfg.bits} bpw random-init, paged bf16 KV (64-token pages)",
                        "global_batch": B, "seq_len": P, "decode_tokens_timed": K,
-                       "parallelism": f"tp{world}" + ("" if world == 1 else " (GEMM epilogue reduce-scatter and all-gather-fed GEMM over NVLink peer memory, no NCCL on the step)"),
+                       "parallelism": f"tp{world}" + ("" if world == 1 else (" (GEMM epilogue reduce-scatter and all-gather-fed GEMM for prefill, one-shot all-reduce for decode windows, "
+                                                                              "all over NVLink peer memory, no NCCL on the step)" if args.collective == "fused" else
+                                                                              " (COMPARISON RUN: NCCL all-reduce in decode windows)")),
                        "l2": "inputs larger than L2 every step (11 GB of weights + the batch's KV are streamed)"},
             "decode_tok_s_bs1": round(tok_s_bs1, 2), "ms_per_step_bs1": round(bs1_ms / K, 4),
             "ttft_p50_ms_8k": round(ttft_p50, 2), "ttft_samples": len(ttfts),

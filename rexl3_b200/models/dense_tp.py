@@ -69,8 +69,14 @@ class DenseTPShard:
     """One rank of the tensor-parallel model."""
 
     def __init__(self, cfg: DenseConfig, group: _GroupBase, rank: int, num_pages: int, max_rows: int, max_seqs: int, max_blocks_per_seq: int,
-                 weights: dict | None = None, device="cuda", seed: int = 0, kv_dtype: str = "bf16"):
+                 weights: dict | None = None, device="cuda", seed: int = 0, kv_dtype: str = "bf16", collective: str = "fused"):
+        """`collective`: "fused" (peer-memory kernels, the product) or "nccl" (the baseline for comparison: decode windows finish their partial
+        rows locally and call NCCL all-reduce on the f32 rows; prefill slices are unchanged)."""
         check_abi()
+        if collective not in ("fused", "nccl"):
+            raise ValueError(collective)
+        self.collective = collective
+        self.ar_local = None
         self.cfg, self.g, self.rank, self.R, self.device = cfg, group, rank, group.ranks, device
         R = self.R
         self.nq, self.nkv = cfg.n_q // R, cfg.n_kv // R
@@ -228,8 +234,31 @@ class DenseTPShard:
         xr_d = self.xr_d[:M * d].view(M, d)
         none = ctypes.c_void_p(0)
 
+        def chain_nccl(x_part, s, w, norm_w, suh_next):
+            """Comparison path: finish locally, NCCL all-reduce of the f32 rows, then the same residual / norm / rotate kernel on one slot."""
+            import torch.distributed as dist
+            if self.ar_local is None:
+                self.ar_local = torch.zeros(AR_ROWS, d, dtype=torch.float32, device=self.device)
+
+            def p_push():
+                buf = self.ar_local[:M]
+                K.finish_store(x_part, s, M, w, buf)
+                if R > 1 and w.bias is not None and r != 0:
+                    buf.sub_(w.bias)                   # the bias counts once
+                dist.all_reduce(buf)
+
+            def p_sum():
+                _lib.check(Lib.rx_tp_allsum_add_norm_rot(self.ar_local.data_ptr(), None, 1, AR_ROWS, None, 0, M, d, h.data_ptr(), norm_w.data_ptr(),
+                                                         cfg.eps, suh_next.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(), _lib.stream_ptr(), None),
+                           "rx_tp_allsum_add_norm_rot")
+                _lib.count()
+            return p_push, p_sum
+
         def chain(x_part, s, w, parity, use, norm_w, suh_next):
             """Two phases: push this rank's finished partial rows to every rank; sum all ranks' rows into the residual, norm, rotate."""
+            if self.collective == "nccl":
+                return chain_nccl(x_part, s, w, norm_w, suh_next)
+
             def p_push():
                 _lib.check(Lib.rx_tp_finish_bcast(x_part.data_ptr(), s, M, d, w.svh.data_ptr(), None if (w.bias is None or r != 0) else w.bias.data_ptr(),
                                                   ctypes.byref(g.bcast(r, parity, use)), _lib.stream_ptr()), "rx_tp_finish_bcast")

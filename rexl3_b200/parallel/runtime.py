@@ -37,14 +37,15 @@ def init(timeout_s: float = 300.0) -> TpContext:
 
 
 def build_dense_tp(ctx: TpContext, cfg, *, num_pages: int, max_rows: int, max_slots: int, max_blocks_per_seq: int, weights=None, seed: int = 0,
-                   kv_dtype: str = "bf16"):
+                   kv_dtype: str = "bf16", collective: str = "fused"):
     """-> (shard, group).  `weights` is a full HostWeights (sliced here for this rank) or None for a random-init shard."""
     from ..models.dense_tp import DenseTPShard, shard_weights
     from .symm import IpcGroup
     layout = DenseTPShard.layout(cfg, ctx.world, max_rows)
     group = IpcGroup(layout, ctx.rank, ctx.device, group=ctx.ctrl)
     w = shard_weights(weights, ctx.rank, ctx.world) if weights is not None else None
-    shard = DenseTPShard(cfg, group, ctx.rank, num_pages, max_rows, max_slots, max_blocks_per_seq, weights=w, device=ctx.device, seed=seed, kv_dtype=kv_dtype)
+    shard = DenseTPShard(cfg, group, ctx.rank, num_pages, max_rows, max_slots, max_blocks_per_seq, weights=w, device=ctx.device, seed=seed, kv_dtype=kv_dtype,
+                         collective=collective)
     shard.max_seqs = max_slots
     torch.cuda.synchronize()
     dist.barrier(group=ctx.ctrl)
