@@ -95,6 +95,18 @@ class Backend:
         """Full-vocabulary logits of every fed row (prompt scoring / logprobs).  Optional."""
         raise NotImplementedError
 
+    def score_last(self, slot: int, tokens: list, chunk: int) -> np.ndarray:
+        """Full-vocabulary float32 logits of the position after `tokens` (prefilled into the empty `slot` in chunks).  Default: built on
+        `score_rows`.  The caller releases the slot."""
+        row = None
+        for a in range(0, len(tokens), chunk):
+            row = self.score_rows(slot, a, tokens[a:a + chunk])[-1]
+            self.commit_scored(slot, a + len(tokens[a:a + chunk]))
+        return np.asarray(row, dtype=np.float32)
+
+    def commit_scored(self, slot: int, length: int) -> None:
+        """Hook for `score_last`'s default: make the scored chunk part of the slot's context (backends whose `score_rows` rolls back)."""
+
     # prefix cache (optional): handles are opaque to the engine
     def prefix_block_tokens(self) -> int:
         return 0                   # 0 = no prefix cache support

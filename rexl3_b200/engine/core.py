@@ -10,6 +10,8 @@ FinishReason), :724-803 (BudgetPolicy, PrefillPolicy).
 """
 from __future__ import annotations
 
+import numpy as np  # noqa: F401  (type of score rows)
+
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -139,6 +141,28 @@ class Engine:
     def take_events(self) -> list:
         ev, self.events = self.events, []
         return ev
+
+    # ------------------------------------------------------------------ prompt scoring (decisions, prompt log-probabilities)
+    def score_prompt(self, tokens) -> "np.ndarray":
+        """Full-vocabulary logits (float32) of the position after `tokens`, computed on a free slot between steps.  Nothing is
+        generated and nothing stays in the KV cache.  Raises AdmitError("NoSlot") when every slot is busy."""
+        tokens = [int(t) for t in tokens]
+        if not tokens:
+            raise ValueError("empty prompt")
+        if self.admission is not None:
+            slot = self.admission.admit(len(tokens) + 1)
+        else:
+            if not self.free_slots:
+                raise AdmitError("NoSlot", reason="every slot is busy")
+            slot = self.free_slots.pop()
+        try:
+            return self.backend.score_last(slot, tokens, self.prefill_chunk)
+        finally:
+            self.backend.release(slot)
+            if self.admission is not None:
+                self.admission.release(slot)
+            else:
+                self.free_slots.append(slot)
 
     # ------------------------------------------------------------------ admission
     def _admit(self) -> None:

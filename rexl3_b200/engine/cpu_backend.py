@@ -64,3 +64,9 @@ class CpuDenseBackend(Backend):
         logits = self.model.forward_seq(slot, tokens, start)
         self.model.truncate(slot, start)
         return logits.numpy()
+
+    def score_last(self, slot, tokens, chunk):
+        row = None
+        for a in range(0, len(tokens), chunk):
+            row = self.model.forward_seq(slot, tokens[a:a + chunk], a)[-1]
+        return row.numpy().astype("float32")

@@ -261,6 +261,35 @@ class DenseGpuBackend(Backend):
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
 
+    # ------------------------------------------------------------------ prompt scoring
+    def score_last(self, slot, tokens, chunk):
+        """Prefill `tokens` into the empty slot in chunks; the last chunk returns the full logits row of the final position."""
+        m = self.m
+        if self.len[slot] != 0:
+            raise BackendError(f"score on slot {slot}, which holds {self.len[slot]} tokens", fatal=False)
+        chunk = min(chunk, m.max_rows)
+        row = None
+        for a in range(0, len(tokens), chunk):
+            part = tokens[a:a + chunk]
+            self._ensure(slot, a + len(part))
+            M = self._fill_rows([(slot, a, part)])
+            hp = self.h_pf.numpy()
+            hp[0, 0], hp[1, 0], hp[2, 0], hp[3, 0] = slot, 0, M, a
+            self._upload_rows(M)
+            self._sync_bt()
+            self.d_pf[:, :1].copy_(self.h_pf[:, :1], non_blocking=True)
+            d = self.d_rows
+            pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=1, max_qlen=M)
+            last = a + len(part) >= len(tokens)
+            lr = torch.tensor([M - 1], dtype=torch.long, device=m.device) if last else None
+            logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr, want_logits=last)
+            self.len[slot] = a + len(part)
+            if last:
+                row = logits[0, :self.vocab_size].float().cpu().numpy()
+        self.h_status.copy_(m.status)
+        self._check()
+        return row
+
     # ------------------------------------------------------------------ self-speculative drafter
     def supports_native_draft(self) -> bool:
         return self.self_draft

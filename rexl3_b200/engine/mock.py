@@ -70,6 +70,13 @@ class MockBackend(Backend):
         self.error = None
         self.generated = {}
 
+    def score_last(self, slot, tokens, chunk):
+        """A full row consistent with `_row`: the candidates' values at their ids, a low floor elsewhere."""
+        r = self._row(list(tokens), 64)
+        row = np.full(self.o.vocab, -30.0, dtype=np.float32)
+        row[r.ids.astype(np.int64)] = r.values
+        return row
+
     # ---------------------------------------------------------------- the "model"
     def _row(self, context, count: int, salt: int = 0) -> RowOutput:
         o = self.o

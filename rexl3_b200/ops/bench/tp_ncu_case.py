@@ -13,10 +13,12 @@ from rexl3_b200.models import dense, dense_tp  # noqa: E402
 from rexl3_b200.ops import kernels as K  # noqa: E402
 from rexl3_b200.parallel.symm import LoopbackGroup  # noqa: E402
 
-R, ROWS = 2, 2048
+R = int(os.environ.get("RX_TP_CASE_RANKS", "2"))     # shards stepped on this one GPU
+ROWS = 2048
+DECODE_ONLY = "--decode-profile" in sys.argv            # launch-list mode: profiler range around two 64-row windows at 8192-token contexts
 cfg = dataclasses.replace(dense.CONFIGS["dense-27b"], n_layers=1, vocab=8192, name="dense-27b-1L")
 g = LoopbackGroup(dense_tp.DenseTPShard.layout(cfg, R, ROWS))
-shards = [dense_tp.DenseTPShard(cfg, g, r, 64, ROWS, 4, 40, None, seed=1) for r in range(R)]
+shards = [dense_tp.DenseTPShard(cfg, g, r, 64, ROWS, 64 if DECODE_ONLY else 4, 130 if DECODE_ONLY else 40, None, seed=1) for r in range(R)]
 i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
 bt = torch.zeros(4, 40, dtype=torch.int32, device="cuda")
 bt[0, :33] = torch.arange(33, dtype=torch.int32, device="cuda")
@@ -38,6 +40,17 @@ def run(a, **kw):
 for _ in range(2):
     run(args, prefill=pf, want_logits=False)
 d = 64
+if DECODE_ONLY:
+    bt2 = torch.zeros(64, 130, dtype=torch.int32, device="cuda")
+    bt2[:] = torch.arange(130, dtype=torch.int32, device="cuda") % 64     # pages are shared: only the traffic pattern matters here
+    a2 = (i32(list(range(d))), i32([8191] * d), i32([63] * d), i32(list(range(d))), i32([8192] * d), bt2)
+    run(a2, max_ctx=8192, want_logits=False)
+    torch.cuda.profiler.start()
+    for _ in range(2):
+        run(a2, max_ctx=8192, want_logits=False)
+    torch.cuda.profiler.stop()
+    print("ok")
+    sys.exit(0)
 a2 = (i32(list(range(d))), i32([ROWS] * d), i32([ROWS + 0] * d), i32([0] * d), i32([ROWS + 1] * d), bt)
 for _ in range(2):
     run(a2, max_ctx=4096, want_logits=False)

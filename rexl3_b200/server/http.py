@@ -172,6 +172,33 @@ def build_app(st: AppState) -> Starlette:
         except api.ApiError as e:
             return _err(e)
 
+    async def decisions(request):
+        from . import decisions as dec
+        from ..sched import AdmitError
+        try:
+            body = await _json_body(request, st)
+            if isinstance(body, dict) and body.get("model") not in (None, st.model_name) and body.get("model") not in st.aliases:
+                raise api.ApiError(404, f"model {body.get('model')!r} is not served", code="model_not_found", param="model")
+            _ready_or_503(st)
+            try:
+                prepared, temp, echo = dec.prepare(body, st.tok, st.fmt, st.max_model_len)
+            except TemplateRefused as e:
+                raise api.bad(str(e), "input", "template_error")
+            loop = asyncio.get_running_loop()
+            rows = []
+            for p_ in prepared:
+                try:
+                    rows.append(await st.handle.score(p_.prompt, loop))
+                except AdmitError as e:
+                    if e.kind == "NoSlot":
+                        raise api.ApiError(503, "every sequence slot is busy; retry", "server_error", "overloaded", retry_after=1)
+                    raise api.ApiError(400, str(e), code="context_length_exceeded")
+                except RuntimeError as e:
+                    raise api.ApiError(503, f"engine unavailable: {e}", "server_error", "engine_unavailable")
+            return JSONResponse(dec.build_response(st.model_name, prepared, rows, [0] * len(rows), temp, echo))
+        except api.ApiError as e:
+            return _err(e)
+
     def render_chat(body, p):
         msgs = api.parse_messages(body)
         try:
@@ -283,7 +310,7 @@ def build_app(st: AppState) -> Starlette:
     routes = [Route("/health/live", live), Route("/health", health), Route("/health/ready", health), Route("/v1/health", health),
               Route("/v1/models", models), Route("/metrics", metrics), Route("/tokenize", tokenize, methods=["POST"]),
               Route("/v1/chat/completions", chat, methods=["POST"]), Route("/v1/completions", completions, methods=["POST"]),
-              Route("/v1/chat/completions/render", render, methods=["POST"])]
+              Route("/v1/chat/completions/render", render, methods=["POST"]), Route("/v1/decisions", decisions, methods=["POST"])]
     app = Starlette(routes=routes)
     app.state.rexl3 = st
     return app

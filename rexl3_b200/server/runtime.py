@@ -131,6 +131,15 @@ class EngineHandle:
         self.cmd.put(("submit", req, t))
         return t
 
+    def score(self, tokens: list, loop: asyncio.AbstractEventLoop) -> "asyncio.Future":
+        """Full-vocabulary logits after `tokens`, computed by the engine thread between steps.  The future resolves to a float32 array or
+        raises (AdmitError when every slot is busy, a backend error)."""
+        if self.state not in ("ready", "degraded"):
+            raise RuntimeError(self.state)
+        fut = loop.create_future()
+        self.cmd.put(("score", tokens, (loop, fut)))
+        return fut
+
     def cancel(self, rid: str) -> None:
         self.cmd.put(("cancel", rid, None))
 
@@ -176,6 +185,15 @@ class EngineHandle:
                             code = "context_length_exceeded" if isinstance(e, AdmitError) and e.kind in ("ContextTooLong", "NeverFits") else "invalid"
                             b.post(("refused", code, str(e)))
                             self.pending -= 1
+                    elif kind == "score":
+                        loop, fut = b
+                        try:
+                            row = eng.score_prompt(a)
+                            loop.call_soon_threadsafe(lambda f=fut, r=row: f.done() or f.set_result(r))
+                            m.inc("decisions_total", status="completed")
+                        except Exception as e:   # the caller's problem (no slot, too long), never the loop's
+                            loop.call_soon_threadsafe(lambda f=fut, e=e: f.done() or f.set_exception(e))
+                            m.inc("decisions_total", status="refused")
                     elif kind == "cancel":
                         eng.cancel(a)
                     elif kind == "drain":
