@@ -99,6 +99,53 @@ def resolve(root: str, family: str, model: str, site: dict, version: str | None 
                     int(prof.get("readiness_timeout_s", 600)), str(fields.get("http_host", "127.0.0.1")), int(fields.get("http_port", 8000)))
 
 
+def seal(vdir: str) -> dict:
+    """Write `source.manifest.json` of a recipe version directory: the sha256 and size of every file in it (the manifest itself excluded)."""
+    import hashlib
+    files = {}
+    for base, _dirs, names in os.walk(vdir):
+        for n in sorted(names):
+            path = os.path.join(base, n)
+            rel = os.path.relpath(path, vdir)
+            if rel == "source.manifest.json":
+                continue
+            with open(path, "rb") as f:
+                data = f.read()
+            files[rel] = {"sha256": hashlib.sha256(data).hexdigest(), "bytes": len(data)}
+    doc = {"schema": "rexl3.source-manifest.v1", "files": files}
+    with open(os.path.join(vdir, "source.manifest.json"), "w") as f:
+        json.dump(doc, f, indent=1, sort_keys=True)
+        f.write("\n")
+    return doc
+
+
+def verify_tree(vdir: str) -> list:
+    """Problems of a sealed recipe version directory against its manifest: missing, changed and unlisted files.  Empty list: intact.
+    (What the reference's tools/verify_runtime_tree.py checks for its sealed trees.)"""
+    import hashlib
+    doc = _read_json(os.path.join(vdir, "source.manifest.json"))
+    if doc.get("schema") != "rexl3.source-manifest.v1" or not isinstance(doc.get("files"), dict):
+        raise RecipeError(f"{vdir}/source.manifest.json: not a source manifest")
+    problems = []
+    seen = set()
+    for rel, want in sorted(doc["files"].items()):
+        path = os.path.join(vdir, rel)
+        seen.add(rel)
+        if not os.path.isfile(path):
+            problems.append(f"missing: {rel}")
+            continue
+        with open(path, "rb") as f:
+            data = f.read()
+        if hashlib.sha256(data).hexdigest() != want.get("sha256") or len(data) != want.get("bytes"):
+            problems.append(f"changed: {rel}")
+    for base, _dirs, names in os.walk(vdir):
+        for n in names:
+            rel = os.path.relpath(os.path.join(base, n), vdir)
+            if rel != "source.manifest.json" and rel not in seen:
+                problems.append(f"unlisted: {rel}")
+    return problems
+
+
 def main(argv=None) -> int:
     import argparse
     import shlex
@@ -111,7 +158,18 @@ def main(argv=None) -> int:
     p.add_argument("--version")
     p.add_argument("--profile")
     p.add_argument("--exec", action="store_true", help="exec the serving binary instead of printing the command")
+    p.add_argument("--verify", action="store_true", help="check the version directory against its source manifest first; refuse a changed tree")
     a = p.parse_args(argv)
+    if a.verify:
+        try:
+            version = a.version or open(os.path.join(a.root, a.family, a.model, "LATEST")).read().strip()
+            problems = verify_tree(os.path.join(a.root, a.family, a.model, version))
+        except (RecipeError, OSError) as e:
+            print(f"rexl3-recipe: {e}", file=sys.stderr)
+            return 2
+        if problems:
+            print("rexl3-recipe: the sealed tree does not match its manifest:\n  " + "\n  ".join(problems), file=sys.stderr)
+            return 2
     try:
         r = resolve(a.root, a.family, a.model, _read_json(a.site), a.version, a.profile)
     except RecipeError as e:

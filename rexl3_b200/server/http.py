@@ -155,7 +155,7 @@ def build_app(st: AppState) -> Starlette:
     async def models(request):
         m = {"id": st.model_name, "object": "model", "owned_by": "rexl3-b200", "max_model_len": st.max_model_len,
              "configured_max_model_len": st.max_model_len, "aliases": sorted(st.aliases)}
-        m.update(st.info)
+        m.update({k: (v() if callable(v) else v) for k, v in st.info.items()})
         return JSONResponse({"object": "list", "data": [m]})
 
     async def metrics(request):

@@ -58,6 +58,8 @@ def parser() -> argparse.ArgumentParser:
 
 def build(args):
     """-> (make_engine callable for the engine thread, tokenizer, chat format, model name, info dict).  No CUDA call happens here."""
+    from ..engine.boot import BootPhases
+    boot = BootPhases()
     folder = args.model if args.model and os.path.isdir(args.model) else None
     if args.backend == "mock":
         opts = MockOptions.parse(args.mock)
@@ -79,11 +81,13 @@ def build(args):
             if folder is None:
                 raise SystemExit("rexl3-serve: --model DIR (or --random-init CONFIG) is required")
             from ..quant import quantize
-            cfg = quantize.config_from_pack(folder)
-            weights = quantize.load_pack(folder)          # header scan + refusals by name happen before CUDA starts
+            with boot.phase("scan_pack", folder=folder):
+                cfg = quantize.config_from_pack(folder)
+            with boot.phase("load_pack_host"):
+                weights = quantize.load_pack(folder)          # header scan + refusals by name happen before CUDA starts
         vocab, name = cfg.vocab, args.served_model_name or cfg.name
         kv_tokens = args.kv_tokens or args.slots * args.max_model_len
-        info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None}
+        info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None, "boot": boot.report}
 
         world = int(os.environ.get("WORLD_SIZE", "1"))
 
@@ -102,6 +106,10 @@ def build(args):
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode())
 
         def make():
+            with boot.phase("engine", backend=args.backend, ranks=world):
+                return make_inner()
+
+        def make_inner():
             if args.backend == "cuda" and world > 1:
                 return make_tp()
             if args.backend == "cpu":

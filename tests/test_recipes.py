@@ -41,3 +41,18 @@ def test_refusals(tmp_path):
         resolve(str(dst), "dense", "dense-27b", SITE)
     with pytest.raises(RecipeError):
         resolve(str(dst), "dense", "nope", SITE)
+
+
+def test_sealed_tree_verification(tmp_path):
+    from rexl3_b200.recipes import seal, verify_tree
+    assert verify_tree(os.path.join(ROOT, "dense", "dense-27b", "v1")) == []          # the shipped tree is sealed and intact
+    dst = tmp_path / "v1"
+    shutil.copytree(os.path.join(ROOT, "dense", "dense-27b", "v1"), dst)
+    (dst / "launch.sh").write_text("#!/bin/sh\necho changed\n")
+    (dst / "extra.txt").write_text("x")
+    os.remove(dst / "profile.json")
+    probs = verify_tree(str(dst))
+    assert "changed: launch.sh" in probs and "unlisted: extra.txt" in probs and "missing: profile.json" in probs
+    (dst / "profile.json").write_text("{}")
+    seal(str(dst))
+    assert verify_tree(str(dst)) == []
