@@ -196,6 +196,7 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
   pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const size_t plane = (size_t)M * N;
+  const unsigned ticket = tp_ticket(tp.epoch, tp.use_index);
   for (int b = blockIdx.y * nw + warp; b < N / 128; b += gridDim.y * nw) {
     const int n0 = b * 128 + lane * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -220,13 +221,14 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
       const float4 bb = *reinterpret_cast<const float4*>(bias + n0);
       y[0] += bb.x; y[1] += bb.y; y[2] += bb.z; y[3] += bb.w;
     }
-    const float4 o = make_float4(y[0], y[1], y[2], y[3]);
-    const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * N + n0;
-    for (int r = 0; r < tp.ranks; ++r) *reinterpret_cast<float4*>(tp.dst[r] + at) = o;
+    // two self-validating packets per lane (8 bytes per value in the slot): no fence, no flag, the consumer polls its own data
+    const size_t at = (((size_t)tp.rank * tp.rows_cap + row) * N + n0) / 2;
+    for (int r = 0; r < tp.ranks; ++r) {
+      uint4* d = reinterpret_cast<uint4*>(tp.dst[r]) + at;
+      ll_store(d, y[0], y[1], ticket);
+      ll_store(d + 1, y[2], y[3], ticket);
+    }
   }
-  __syncthreads();
-  if (threadIdx.x == 0)
-    tp_publish_last(tp.local_count, gridDim.x * gridDim.y, tp.dst_flag, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
 }
 
 // ar: local f32 [ranks][rows_cap][N] filled by every rank's finish_bcast_kernel.  h[row] += sum_r ar[r][row] (rank order), then
@@ -242,23 +244,30 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
   __shared__ float blk_ss[512];
   __shared__ int ok_sh;
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  if (threadIdx.x == 0) {
-    int ok = 1;
-    if (flags != nullptr) {          // nullptr: the slots were filled by an earlier kernel of this stream (one rank)
-      const unsigned ticket = tp_ticket(epoch, use_index);
-      for (int r = 0; r < ranks && ok; ++r) ok = tp_wait_flag(flags + r, ticket, status, 200) ? 1 : 0;
-    }
-    ok_sh = ok;
-  }
-  __syncthreads();
-  if (!ok_sh) return;
+  // flags == nullptr: plain f32 slots filled by an earlier kernel of this stream (one rank).  Otherwise the slots hold self-validating
+  // packets (value, ticket pairs) pushed by every rank, and each thread polls exactly the packets it needs.
+  const bool ll = flags != nullptr;
+  const unsigned ticket = ll ? tp_ticket(epoch, use_index) : 0u;
+  (void)ok_sh;
   const size_t plane = (size_t)rows_cap * N;
   for (int b = warp; b < N / 128; b += nw) {
     const int n0 = b * 128 + lane * 4;
     float4 p[TP_MAX];
 #pragma unroll
     for (int r = 0; r < TP_MAX; ++r)
-      if (r < ranks) p[r] = __ldcg(reinterpret_cast<const float4*>(ar + (size_t)r * plane + (size_t)row * N + n0));
+      if (r < ranks) {
+        if (ll) {
+          // both packets of a rank are requested together; ranks one after another (holding all ranks' packets at once costs more
+          // registers than a 1024-thread CTA has, and the spills cost more than the overlap gains - measured)
+          const uint4* src = reinterpret_cast<const uint4*>(ar) + ((size_t)r * plane + (size_t)row * N + n0) / 2;
+          uint4 a = ll_load(src), c = ll_load(src + 1);
+          if (a.y != ticket || a.w != ticket) a = ll_wait(src, ticket, status, 200);
+          if (c.y != ticket || c.w != ticket) c = ll_wait(src + 1, ticket, status, 201);
+          p[r] = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(c.x), __uint_as_float(c.z));
+        } else {
+          p[r] = __ldcg(reinterpret_cast<const float4*>(ar + (size_t)r * plane + (size_t)row * N + n0));
+        }
+      }
     float4 acc = p[0];
 #pragma unroll
     for (int r = 1; r < TP_MAX; ++r)
@@ -433,10 +442,12 @@ RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void*
   if (desc == nullptr || N % 128 || M < 1 || S < 1) return (int)cudaErrorInvalidValue;
   const BcastTp tp = *(const BcastTp*)desc;
   if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
-  // one warp per 128-block; few rows -> spread the blocks of a row over several CTAs
+  // one warp per 128-block.  The kernel is a chain of dependent loads and R remote stores per block, so it wants many small CTAs in
+  // flight rather than few big ones: split each row's blocks over enough CTAs to fill the machine about four times.
   const int blocks = N / 128;
-  int gy = 1;
-  if (M < 64) { gy = (blocks + 3) / 4; if (gy > 32) gy = 32; }
+  int gy = (592 + M - 1) / M;
+  if (gy > blocks) gy = blocks;
+  if (gy < 1) gy = 1;
   int warps = (blocks + gy - 1) / gy;
   if (warps > 8) warps = 8;
   return (int)rx::launch(finish_bcast_kernel, dim3(M, gy), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh,

@@ -56,6 +56,34 @@ __device__ __forceinline__ bool tp_wait_flag(const unsigned* flag, unsigned tick
   }
 }
 
+// ---- self-validating 16-byte packets for latency-bound exchanges (two (value, ticket) pairs each; the 8-byte halves are written
+// atomically, so a reader that sees the ticket in both halves has the data: no fence, no separate flag, no kernel-level wait).
+// The same idea as NCCL's LL protocol; tickets are unique per collective (epoch and use index), so stale slots never match.
+__device__ __forceinline__ void ll_store(uint4* dst, float a, float b, unsigned ticket) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(ticket), "r"(__float_as_uint(b)), "r"(ticket)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ll_load(const uint4* src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+// Bounded wait for one packet.  On a timeout the status words are set and whatever is there is returned (the caller's result is then
+// garbage, and the host turns the status into a fatal error); nothing hangs.
+__device__ __forceinline__ uint4 ll_wait(const uint4* src, unsigned ticket, int* status, int site) {
+  uint4 v = ll_load(src);
+  if (v.y == ticket && v.w == ticket) return v;
+  const uint64_t t0 = globaltimer_ns();
+  for (unsigned it = 0;; ++it) {
+    v = ll_load(src);
+    if (v.y == ticket && v.w == ticket) return v;
+    if ((it & 63u) == 63u && globaltimer_ns() - t0 > RX_WAIT_LIMIT_NS) {
+      set_status(status, ST_PEER_TIMEOUT, site, (int)ticket);
+      return v;
+    }
+  }
+}
+
 // Called by ONE thread of every CTA after the CTA's peer stores are complete and fenced: the last CTA of the grid resets the
 // counter and publishes the ticket to flag[src = rank] on every destination rank.
 __device__ __forceinline__ void tp_publish_last(unsigned* local_count, unsigned total_ctas, unsigned* const* flags, int ranks, int rank,

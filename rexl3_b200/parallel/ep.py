@@ -32,7 +32,7 @@ class EpLayout:
         self.epoch = take(4)
         self.count = take(4 * 16)
         self.ar_flag = take(4 * 2 * R)
-        self.ar = take(4 * 2 * R * self.rows_cap * self.d)
+        self.ar = take(8 * 2 * R * self.rows_cap * self.d)      # (value, ticket) pairs
         self.total = off
 
 
@@ -57,7 +57,7 @@ class EpComm:
             t.ranks, t.rank, t.rows_cap = self.R, rank, self.L.rows_cap
             for r in range(self.R):
                 b = group.base(rank, r)
-                t.dst[r] = b + self.L.ar + 4 * parity * self.R * self.L.rows_cap * self.L.d
+                t.dst[r] = b + self.L.ar + 8 * parity * self.R * self.L.rows_cap * self.L.d
                 t.dst_flag[r] = b + self.L.ar_flag + 4 * parity * self.R
             t.local_count = me + self.L.count + 4 * parity
             t.epoch = me + self.L.epoch
@@ -74,7 +74,7 @@ class EpComm:
         parity = li & 1
         t = self._dst[parity]
         t.use_index = li + 1
-        ar = self.me + self.L.ar + 4 * parity * self.R * self.L.rows_cap * self.L.d
+        ar = self.me + self.L.ar + 8 * parity * self.R * self.L.rows_cap * self.L.d
         flags = self.me + self.L.ar_flag + 4 * parity * self.R
         return t, ar, flags, self.R, self.L.rows_cap, self.me + self.L.epoch, li + 1
 
@@ -86,7 +86,7 @@ class EpComm:
         parity = use & 1
         t = self._dst[parity]
         t.use_index = use
-        ar = self.me + self.L.ar + 4 * parity * self.R * self.L.rows_cap * self.L.d
+        ar = self.me + self.L.ar + 8 * parity * self.R * self.L.rows_cap * self.L.d
         return t, ar, self.me + self.L.ar_flag + 4 * parity * self.R, self.R, self.L.rows_cap, self.me + self.L.epoch, use
 
     def local_slot(self):

@@ -96,7 +96,7 @@ class ArenaLayout:
         self.part = take(4 * 2 * R * self.plane_elems)  # [site][src][plane]
         self.xr = take(2 * 2 * self.rows_cap * self.d)  # [parity][row][d] fp16
         self.ar_flag = take(4 * 2 * R)                 # [parity][src]
-        self.ar = take(4 * 2 * R * AR_ROWS * self.d)   # [parity][src][row][d] f32: one-shot all-reduce slots
+        self.ar = take(8 * 2 * R * AR_ROWS * self.d)   # [parity][src][row][d] (value, ticket) pairs: one-shot all-reduce slots
         self.cand_flag = take(4 * R)                   # [src]                      (read on the leader only)
         self.cand_ids = take(4 * R * CAND_ROWS * 64)   # [src][row * count + j] u32
         self.cand_vals = take(4 * R * CAND_ROWS * 64)
@@ -176,7 +176,7 @@ class _GroupBase:
         t.ranks, t.rank, t.rows_cap = R, rank, AR_ROWS
         for r in range(R):
             b = self.base(rank, r)
-            t.dst[r] = b + L.ar + 4 * parity * R * AR_ROWS * L.d
+            t.dst[r] = b + L.ar + 8 * parity * R * AR_ROWS * L.d
             t.dst_flag[r] = b + L.ar_flag + 4 * parity * R
         me = self.base(rank, rank)
         t.local_count = me + L.count + 4 * (6 + parity)
@@ -184,7 +184,7 @@ class _GroupBase:
         return t
 
     def ar_ptr(self, rank: int, parity: int) -> int:
-        return self.base(rank, rank) + self.layout.ar + 4 * parity * self.ranks * AR_ROWS * self.layout.d
+        return self.base(rank, rank) + self.layout.ar + 8 * parity * self.ranks * AR_ROWS * self.layout.d
 
     def ar_flag_ptr(self, rank: int, parity: int) -> int:
         return self.base(rank, rank) + self.layout.ar_flag + 4 * parity * self.ranks
