@@ -197,6 +197,7 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const size_t plane = (size_t)M * N;
   const unsigned ticket = tp_ticket(tp.epoch, tp.use_index);
+  const bool ll = M <= LL_MAX_ROWS;
   for (int b = blockIdx.y * nw + warp; b < N / 128; b += gridDim.y * nw) {
     const int n0 = b * 128 + lane * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -221,14 +222,23 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
       const float4 bb = *reinterpret_cast<const float4*>(bias + n0);
       y[0] += bb.x; y[1] += bb.y; y[2] += bb.z; y[3] += bb.w;
     }
-    // two self-validating packets per lane (8 bytes per value in the slot): no fence, no flag, the consumer polls its own data
-    const size_t at = (((size_t)tp.rank * tp.rows_cap + row) * N + n0) / 2;
-    for (int r = 0; r < tp.ranks; ++r) {
-      uint4* d = reinterpret_cast<uint4*>(tp.dst[r]) + at;
-      ll_store(d, y[0], y[1], ticket);
-      ll_store(d + 1, y[2], y[3], ticket);
+    if (ll) {
+      // two self-validating packets per lane (8 bytes per value in the slot): no fence, no flag, the consumer polls its own data
+      const size_t at = (((size_t)tp.rank * tp.rows_cap + row) * N + n0) / 2;
+      for (int r = 0; r < tp.ranks; ++r) {
+        uint4* d = reinterpret_cast<uint4*>(tp.dst[r]) + at;
+        ll_store(d, y[0], y[1], ticket);
+        ll_store(d + 1, y[2], y[3], ticket);
+      }
+    } else {
+      const float4 o = make_float4(y[0], y[1], y[2], y[3]);
+      const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * N + n0;
+      for (int r = 0; r < tp.ranks; ++r) *reinterpret_cast<float4*>(tp.dst[r] + at) = o;
     }
   }
+  if (ll) return;
+  __syncthreads();
+  if (threadIdx.x == 0) tp_publish_last(tp.local_count, gridDim.x * gridDim.y, tp.dst_flag, tp.ranks, tp.rank, ticket);
 }
 
 // ar: local f32 [ranks][rows_cap][N] filled by every rank's finish_bcast_kernel.  h[row] += sum_r ar[r][row] (rank order), then
@@ -244,11 +254,19 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
   __shared__ float blk_ss[512];
   __shared__ int ok_sh;
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  // flags == nullptr: plain f32 slots filled by an earlier kernel of this stream (one rank).  Otherwise the slots hold self-validating
-  // packets (value, ticket pairs) pushed by every rank, and each thread polls exactly the packets it needs.
-  const bool ll = flags != nullptr;
-  const unsigned ticket = ll ? tp_ticket(epoch, use_index) : 0u;
-  (void)ok_sh;
+  // flags == nullptr: plain f32 slots filled by an earlier kernel of this stream (one rank).  Otherwise every rank pushed its rows: small
+  // windows as self-validating packets that each thread polls itself, larger ones as f32 rows behind one flag per source rank.
+  const bool ll = flags != nullptr && M <= LL_MAX_ROWS;
+  const unsigned ticket = flags != nullptr ? tp_ticket(epoch, use_index) : 0u;
+  if (flags != nullptr && !ll) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      for (int r = 0; r < ranks && ok; ++r) ok = tp_wait_flag(flags + r, ticket, status, 202) ? 1 : 0;
+      ok_sh = ok;
+    }
+    __syncthreads();
+    if (!ok_sh) return;
+  }
   const size_t plane = (size_t)rows_cap * N;
   for (int b = warp; b < N / 128; b += nw) {
     const int n0 = b * 128 + lane * 4;
@@ -442,11 +460,17 @@ RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void*
   if (desc == nullptr || N % 128 || M < 1 || S < 1) return (int)cudaErrorInvalidValue;
   const BcastTp tp = *(const BcastTp*)desc;
   if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
-  // one warp per 128-block.  The kernel is a chain of dependent loads and R remote stores per block, so it wants many small CTAs in
-  // flight rather than few big ones: split each row's blocks over enough CTAs to fill the machine about four times.
+  // one warp per 128-block.  Small windows (packet mode): a chain of dependent loads and R remote stores per block wants many small CTAs
+  // in flight.  Larger windows end with one system-scope fence per CTA, so they keep few, fat CTAs.
   const int blocks = N / 128;
-  int gy = (592 + M - 1) / M;
-  if (gy > blocks) gy = blocks;
+  int gy;
+  if (M <= LL_MAX_ROWS) {
+    gy = (592 + M - 1) / M;
+    if (gy > blocks) gy = blocks;
+  } else {
+    gy = 1;
+    if (M < 64) { gy = (blocks + 3) / 4; if (gy > 32) gy = 32; }
+  }
   if (gy < 1) gy = 1;
   int warps = (blocks + gy - 1) / gy;
   if (warps > 8) warps = 8;

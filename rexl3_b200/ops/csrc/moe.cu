@@ -337,7 +337,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ part, int S, int pa
     }
     if (tp.dst_flag[0] == nullptr) {       // one rank: a plain f32 slot read by the next kernel of this stream
       *reinterpret_cast<float4*>(tp.dst[0] + ((size_t)tp.rank * tp.rows_cap + row) * d + n0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    } else {                               // several ranks: self-validating packets into every rank's slot (see tp.cuh)
+    } else if (M <= LL_MAX_ROWS) {         // several ranks, small window: self-validating packets into every rank's slot (see tp.cuh)
       const unsigned ticket = tp_ticket(tp.epoch, tp.use_index);
       const size_t at = (((size_t)tp.rank * tp.rows_cap + row) * d + n0) / 2;
       for (int r = 0; r < tp.ranks; ++r) {
@@ -345,8 +345,16 @@ __global__ void moe_combine_kernel(const float* __restrict__ part, int S, int pa
         ll_store(dd, acc[0], acc[1], ticket);
         ll_store(dd + 1, acc[2], acc[3], ticket);
       }
+    } else {                               // several ranks, larger window: f32 rows, then one flag per source rank
+      const float4 o = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * d + n0;
+      for (int r = 0; r < tp.ranks; ++r) *reinterpret_cast<float4*>(tp.dst[r] + at) = o;
     }
   }
+  if (tp.dst_flag[0] == nullptr || M <= LL_MAX_ROWS) return;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    tp_publish_last(tp.local_count, gridDim.x * gridDim.y, tp.dst_flag, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
 }
 
 }  // namespace rx
@@ -406,8 +414,14 @@ RX_API int rx_moe_combine(const void* part, int S, int pairs_cap, int M, int d, 
   const CombineDst tp = *(const CombineDst*)desc;
   if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
   const int blocks = d / 128;
-  int gy = (592 + M - 1) / M;        // many small CTAs: a chain of dependent loads and R remote stores per block
-  if (gy > blocks) gy = blocks;
+  int gy;
+  if (M <= LL_MAX_ROWS) {              // packet mode: many small CTAs (a chain of dependent loads and R remote stores per block)
+    gy = (592 + M - 1) / M;
+    if (gy > blocks) gy = blocks;
+  } else {                             // one system-scope fence per CTA: few, fat CTAs
+    gy = 1;
+    if (M < 64) { gy = (blocks + 3) / 4; if (gy > 16) gy = 16; }
+  }
   if (gy < 1) gy = 1;
   int warps = (blocks + gy - 1) / gy;
   if (warps > 8) warps = 8;

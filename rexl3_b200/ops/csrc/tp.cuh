@@ -59,6 +59,12 @@ __device__ __forceinline__ bool tp_wait_flag(const unsigned* flag, unsigned tick
 // ---- self-validating 16-byte packets for latency-bound exchanges (two (value, ticket) pairs each; the 8-byte halves are written
 // atomically, so a reader that sees the ticket in both halves has the data: no fence, no separate flag, no kernel-level wait).
 // The same idea as NCCL's LL protocol; tickets are unique per collective (epoch and use index), so stale slots never match.
+// Windows of at most LL_MAX_ROWS rows use the packets (latency-bound: one NVLink hop, no fence); larger windows use plain f32 rows plus one
+// flag per source rank (half the bytes; the system-scope fence is then amortised over more data).  Measured on 8 GPUs: packets take a
+// batch-1 step from 7.6 to 5.9 ms, but a 64-row step from 15.0 to 19.4 ms, hence the split.  Producer and consumer derive the mode from the
+// row count of the window, which both know.
+constexpr int LL_MAX_ROWS = 16;
+
 __device__ __forceinline__ void ll_store(uint4* dst, float a, float b, unsigned ticket) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(ticket), "r"(__float_as_uint(b)), "r"(ticket)
                : "memory");
