@@ -134,12 +134,17 @@ class _TpExec:
         return head, big.numpy()
 
 
-def follow(shard: DenseTPShard, max_slots: int, ctrl_group, use_graphs: bool = True) -> _TpExec:
+def follow(shard: DenseTPShard, max_slots: int, ctrl_group, use_graphs: bool = True, leave_after: int = 0) -> _TpExec:
     """Body of every rank but 0: repeat the leader's launches until it says stop.  Returns the executor (its `marks` hold
-    the timing events the leader asked for)."""
+    the timing events the leader asked for).  `leave_after` (failure tests): return after that many messages, between two steps and with
+    this rank's stream drained, as a rank that goes away would."""
     ex = _TpExec(shard, max_slots, use_graphs, ctrl_group)
+    seen = 0
     while True:
+        if leave_after and seen >= leave_after:
+            break
         head, payload = ex.recv()
+        seen += 1
         if not ex.apply(head, payload):
             break
         st = None

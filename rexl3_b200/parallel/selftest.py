@@ -17,7 +17,58 @@ import numpy as np
 import torch
 
 
+def failure_main(leave_after: int) -> int:
+    """Failure detection without a GPU fault: the last rank leaves between two steps (its stream drained, nothing in flight).  The leader
+    must notice within seconds - either its next control broadcast fails on the host, or the kernels of its next step give up their
+    bounded peer waits and report through the status words - and must NOT hang.  Prints TP_FAILURE_DETECTED on the leader."""
+    import os
+    import time
+    from ..engine import BackendError, Engine, Request, StepError
+    from ..engine.tp_backend import DenseTpBackend, follow
+    from ..models import dense
+    from ..sampling import GREEDY
+    from . import runtime
+    ctx = runtime.init(timeout_s=15)
+    cfg = dataclasses.replace(dense.CONFIGS["test-hd128"], n_kv=4, name="tp-selftest")
+    w = dense.random_weights(cfg, seed=11)
+    shard, group = runtime.build_dense_tp(ctx, cfg, num_pages=32, max_rows=256, max_slots=4, max_blocks_per_seq=6, weights=w)
+    if ctx.rank == ctx.world - 1 and ctx.rank != 0:
+        follow(shard, 4, ctx.ctrl, leave_after=leave_after)
+        torch.cuda.synchronize()
+        os._exit(0)                      # gone: no goodbye message, no collective in flight
+    if ctx.rank != 0:
+        try:
+            follow(shard, 4, ctx.ctrl)
+        except Exception:
+            pass
+        os._exit(0)
+    be = DenseTpBackend(shard, 4, ctx.ctrl)
+    eng = Engine(be, None, window_rows=64, prefill_chunk=256, spec="none")
+    eng.submit(Request("r", np.random.default_rng(3).integers(0, cfg.vocab, size=40).tolist(), 200, GREEDY))
+    t0 = time.time()
+    detected = ""
+    try:
+        for _ in range(400):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                if ev.kind == "error":
+                    detected = f"engine error event: {ev.message}"
+            if detected:
+                break
+    except (StepError, BackendError, RuntimeError) as e:
+        detected = f"{e.__class__.__name__}: {e}"
+    dt = time.time() - t0
+    if detected and dt < 60:
+        print(f"TP_FAILURE_DETECTED after {dt:.1f} s: {detected[:200]}", flush=True)
+        os._exit(0)
+    print(f"the leader did not notice the lost rank ({dt:.1f} s, {detected!r})", file=sys.stderr, flush=True)
+    os._exit(1)
+
+
 def main() -> int:
+    if "--leave-after" in sys.argv:
+        return failure_main(int(sys.argv[sys.argv.index("--leave-after") + 1]))
     from ..engine.tp_backend import DenseTpBackend, follow
     from ..models import dense
     from . import runtime

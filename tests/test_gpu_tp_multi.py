@@ -20,3 +20,16 @@ def test_tp_selftest_over_gpus(ranks):
            "--master-port", str(29540 + ranks), "-m", "rexl3_b200.parallel.selftest"]
     r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
     assert r.returncode == 0 and f"TP_SELFTEST_OK ranks={ranks}" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_lost_rank_is_detected_without_a_hang():
+    """A follower leaves between two steps (stream drained, nothing in flight); the leader notices on the host or through the bounded
+    peer waits of its next step, within seconds.  NVLS off, plain peer stores only."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29549",
+           "-m", "rexl3_b200.parallel.selftest", "--leave-after", "12"]
+    r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=240)
+    assert "TP_FAILURE_DETECTED" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
