@@ -300,7 +300,13 @@ class Engine:
         for s, p, out in zip(active, proposals, rows):
             base = len(s.tokens)
             try:
-                samples = [choose(o.values, o.ids, base + j, s.req.sampling) for j, o in enumerate(out)]
+                if s.req.sampling.temperature == 0.0 and all(len(o.ids) and o.values[0] == o.values[0] and
+                                                              (len(o.ids) == 1 or o.values[0] > o.values[1] or
+                                                               (o.values[0] == o.values[1] and o.ids[0] < o.ids[1])) for o in out):
+                    # greedy over candidates that arrive ordered (value desc, id asc): the first one is the keyed sampler's choice
+                    samples = [int(o.ids[0]) for o in out]
+                else:
+                    samples = [choose(o.values, o.ids, base + j, s.req.sampling) for j, o in enumerate(out)]
             except SamplingError as e:
                 self._finish(s, "error", message=f"sampling failed: {e}")  # a NaN row fails only its sequence
                 continue

@@ -93,6 +93,17 @@ class DenseGpuBackend(Backend):
         """specs: list of (slot, first_position, tokens).  Fills the pinned staging rows; returns M."""
         h = self.h_rows.numpy()
         r = 0
+        if all(len(t) == 1 for _, _, t in specs):
+            # plain decode (one row per sequence): no per-sequence numpy calls, one bulk assignment per array
+            n = len(specs)
+            pages = self.pages
+            h[0, :n] = [t[0] for _, _, t in specs]
+            pos = [p0 for _, p0, _ in specs]
+            h[1, :n] = pos
+            h[2, :n] = [pages[slot][p0 // PAGE] * PAGE + p0 % PAGE for slot, p0, _ in specs]
+            h[3, :n] = [slot for slot, _, _ in specs]
+            h[4, :n] = [p + 1 for p in pos]
+            return n
         for slot, p0, toks in specs:
             n = len(toks)
             pos = np.arange(p0, p0 + n, dtype=np.int64)
