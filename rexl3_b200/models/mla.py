@@ -326,6 +326,15 @@ class MlaMoEGPU:
         if cfg.vocab_padded != cfg.vocab:
             self.lm_head.svh[cfg.vocab:] = 0
 
+    @staticmethod
+    def weight_bytes_estimate(cfg: MlaConfig) -> float:
+        """Bytes of the whole model (all heads, all experts) for the memory plan."""
+        d, H = cfg.d_model, cfg.n_heads
+        attn = (d * 2176 * cfg.bits_b + 1536 * H * 192 * cfg.bits_a + H * 128 * d * cfg.bits_a) / 8 + 2 * H * 128 * 512 * 2
+        dense_ffn = 3 * d * cfg.dense_ffn * (2 * cfg.bits_a + cfg.bits_b) / 3 / 8
+        routed = cfg.n_experts * 3 * d * cfg.expert_ffn * (0.5 + 1 / 32) + 3 * d * cfg.shared_ffn * (2 * cfg.bits_a + cfg.bits_b) / 3 / 8
+        return cfg.n_layers * attn + cfg.n_dense * dense_ffn + (cfg.n_layers - cfg.n_dense) * routed + (cfg.vocab_padded * d * cfg.bits_b) / 8 + cfg.vocab * d * 2
+
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes
         for L in self.layers:

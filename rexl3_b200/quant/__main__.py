@@ -19,6 +19,7 @@ def main(argv=None) -> int:
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--threads", type=int, default=0)
     p.add_argument("--layers", type=int, default=0, help="quantize only the first N layers (smoke runs)")
+    p.add_argument("--device", default="cpu", help="cpu (host Viterbi, all cores) or cuda (one CTA per tile; same bits)")
     a = p.parse_args(argv)
     cfg = dense.CONFIGS[a.arch]
     if a.bits:
@@ -26,7 +27,7 @@ def main(argv=None) -> int:
     if a.layers:
         cfg = dataclasses.replace(cfg, n_layers=a.layers)
     t0 = time.time()
-    w = quantize.quantize_dense(cfg, quantize.random_fp_weights(cfg, a.seed), seed=a.seed, threads=a.threads)
+    w = quantize.quantize_dense(cfg, quantize.random_fp_weights(cfg, a.seed), seed=a.seed, threads=a.threads, device=a.device)
     quantize.write_pack(a.out, w)
     print(f"rexl3-quant: wrote {a.out} ({cfg.name}, {cfg.bits:g} bpw, {cfg.n_layers} layers) in {time.time() - t0:.1f} s")
     return 0

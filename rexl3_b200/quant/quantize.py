@@ -34,8 +34,9 @@ def to_stream_tiles(w: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(t[:, :, r, c]).reshape(-1, 256)
 
 
-def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: int = 0, bias=None, threads: int = 0) -> HostLinear:
-    """w: float [K, N] with y = x @ w.  K and N must be multiples of 128 (pad first)."""
+def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: int = 0, bias=None, threads: int = 0, device: str = "cpu") -> HostLinear:
+    """w: float [K, N] with y = x @ w.  K and N must be multiples of 128 (pad first).  `device="cuda"` runs the trellis search on the GPU
+    (the CUDA encoder emits the same bits as the host one)."""
     w = np.asarray(w, dtype=np.float64)
     k, n = w.shape
     if k % 128 or n % 128:
@@ -50,7 +51,12 @@ def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: i
     std = float(rot.std())
     scale = std / _cb_std(codebook) if std > 0 else 1.0
     tiles = to_stream_tiles(rot / scale)
-    packed, err = encode_tiles(tiles, b, codebook, threads)
+    if device == "cpu":
+        packed, err = encode_tiles(tiles, b, codebook, threads)
+    else:
+        from .trellis import encode_tiles_cuda
+        out, _err = encode_tiles_cuda(tiles, b, codebook, device=device)
+        packed = out.cpu().numpy()
     trellis = packed.reshape(k // 16, n // 16, b.tile_words)
     suh = su.astype(np.float16)
     svh = (sv * scale).astype(np.float16)
@@ -63,7 +69,7 @@ def pad_to(w: np.ndarray, k: int, n: int) -> np.ndarray:
     return out
 
 
-def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0) -> HostWeights:
+def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0, device: str = "cpu") -> HostWeights:
     """fp: float weights of a dense GQA decoder, [in, out] matrices: embed [V, d], final_norm [d], lm_head [d, V] and per layer
     attn_norm, q, k, v, o, ffn_norm, gate, up, down (optionally q_norm, k_norm)."""
     d, F, V = cfg.d_model, cfg.ffn_padded, cfg.vocab_padded
@@ -71,14 +77,14 @@ def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0) 
     for i, L in enumerate(fp["layers"]):
         qkv = np.concatenate([L["q"], L["k"], L["v"]], axis=1)
         gu = np.concatenate([pad_to(L["gate"], d, F), pad_to(L["up"], d, F)], axis=1)
-        lay = HostLayer(np.asarray(L["attn_norm"], np.float32), quantize_linear(qkv, cfg.bits, cfg.codebook, seed + 10 * i + 1, threads=threads),
-                        quantize_linear(L["o"], cfg.bits, cfg.codebook, seed + 10 * i + 2, threads=threads), np.asarray(L["ffn_norm"], np.float32),
-                        quantize_linear(gu, cfg.bits, cfg.codebook, seed + 10 * i + 3, threads=threads),
-                        quantize_linear(pad_to(L["down"], F, d), cfg.bits, cfg.codebook, seed + 10 * i + 4, threads=threads),
+        lay = HostLayer(np.asarray(L["attn_norm"], np.float32), quantize_linear(qkv, cfg.bits, cfg.codebook, seed + 10 * i + 1, threads=threads, device=device),
+                        quantize_linear(L["o"], cfg.bits, cfg.codebook, seed + 10 * i + 2, threads=threads, device=device), np.asarray(L["ffn_norm"], np.float32),
+                        quantize_linear(gu, cfg.bits, cfg.codebook, seed + 10 * i + 3, threads=threads, device=device),
+                        quantize_linear(pad_to(L["down"], F, d), cfg.bits, cfg.codebook, seed + 10 * i + 4, threads=threads, device=device),
                         None if "q_norm" not in L else np.asarray(L["q_norm"], np.float32), None if "k_norm" not in L else np.asarray(L["k_norm"], np.float32))
         w.layers.append(lay)
     w.final_norm = np.asarray(fp["final_norm"], np.float32)
-    w.lm_head = quantize_linear(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, cfg.codebook, seed + 7777, threads=threads)
+    w.lm_head = quantize_linear(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, cfg.codebook, seed + 7777, threads=threads, device=device)
     return w
 
 

@@ -75,7 +75,15 @@ def build(args):
     else:
         from ..models import dense
         if args.random_init:
-            cfg = dense.CONFIGS[args.random_init]
+            from ..models import mla as mla_models
+            from ..models import moe as _moe_models  # noqa: F401  (registers the MoE configs)
+            if args.random_init in mla_models.CONFIGS:
+                cfg = mla_models.CONFIGS[args.random_init]
+            elif args.random_init in dense.CONFIGS:
+                cfg = dense.CONFIGS[args.random_init]
+            else:
+                raise SystemExit(f"rexl3-serve: unknown built-in config {args.random_init!r}; known: "
+                                 f"{sorted(list(dense.CONFIGS) + list(mla_models.CONFIGS))}")
             weights = None
         else:
             if folder is None:
@@ -121,20 +129,34 @@ def build(args):
                 from ..engine.gpu_backend import DenseGpuBackend
                 pages = -(-kv_tokens // dense.PAGE) + args.slots
                 free, _ = torch.cuda.mem_get_info()
-                kvb = cfg.kv_bytes_per_token(1 if args.kv_dtype == "fp8" else 2)
-                mm = ModelMemory(int(cfg.weight_params() * cfg.bits / 8), kvb, activation_reserve=2 << 30)
+                from ..models import mla as mla_models
+                from ..models import moe as moe_models
+                is_mla = isinstance(cfg, mla_models.MlaConfig)
+                is_moe = isinstance(cfg, moe_models.MoEConfig)
+                if (is_mla or is_moe) and args.kv_dtype == "fp8":
+                    raise RuntimeError("--kv-dtype fp8 is available for the dense GQA family")
+                kvb = cfg.kv_bytes_per_token() if is_mla else cfg.kv_bytes_per_token(1 if args.kv_dtype == "fp8" else 2)
+                wbytes = int(mla_models.MlaMoEGPU.weight_bytes_estimate(cfg)) if is_mla else int(cfg.weight_params() * cfg.bits / 8)
+                mm = ModelMemory(wbytes, kvb, activation_reserve=2 << 30)
                 adm = Admission(free, 1 << 30, mm, args.slots).with_max_context(args.max_model_len).with_kv_tokens(kv_tokens)
                 adm.check(min(args.max_model_len, 1))     # fail closed: a plan that can never hold one token is refused at boot
                 if pages * kvb * dense.PAGE > adm.capacity:
                     raise RuntimeError(f"memory plan refused: {kv_tokens} KV tokens need {pages * kvb * dense.PAGE >> 20} MiB, "
                                        f"{adm.capacity >> 20} MiB are available after weights and reserve")
-                model = dense.DenseGPU(weights if weights is not None else cfg, num_pages=pages, max_rows=min(256, args.window_rows),
-                                       max_seqs=args.slots, max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1,
-                                       max_prefill_rows=args.prefill_chunk, kv_dtype=args.kv_dtype)
+                common = dict(num_pages=pages, max_rows=min(256, args.window_rows), max_seqs=args.slots,
+                              max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, max_prefill_rows=args.prefill_chunk)
+                if is_mla:
+                    model = mla_models.MlaMoEGPU(cfg, **common)
+                elif is_moe:
+                    model = moe_models.MoEGPU(cfg, **common)
+                else:
+                    model = dense.DenseGPU(weights if weights is not None else cfg, kv_dtype=args.kv_dtype, **common)
                 if args.kv_dtype == "fp8":
                     import numpy as np
                     model.calibrate_kv(np.random.default_rng(0).integers(0, cfg.vocab, size=min(256, args.prefill_chunk)).tolist())
-                be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs)
+                # the self-speculative drafter (first layers + shared head) is offered by families that define a draft depth
+                be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs,
+                                     self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode())

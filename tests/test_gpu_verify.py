@@ -58,3 +58,14 @@ def test_cuda_trellis_encoder_matches_host_encoder(bits):
     print(f"cuda encoder: {6 / (time.time() - t0):.1f} tiles/s at {bits} bpw")
     np.testing.assert_array_equal(got.cpu().numpy(), want)
     np.testing.assert_allclose(gerr.cpu().numpy(), werr, rtol=1e-6)
+
+
+def test_quantize_linear_on_the_gpu_equals_the_host_quantizer():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.quant import quantize
+    w = np.random.default_rng(4).normal(0, 0.02, size=(128, 256)).astype(np.float32)
+    a = quantize.quantize_linear(w, 4.0, seed=3)
+    b = quantize.quantize_linear(w, 4.0, seed=3, device="cuda")
+    np.testing.assert_array_equal(a.trellis, b.trellis)
+    np.testing.assert_array_equal(a.svh, b.svh)
