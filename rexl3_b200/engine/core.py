@@ -75,7 +75,7 @@ class StepError(Exception):
 class Engine:
     def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
                  spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
-                 prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b""):
+                 prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b"", device_sampler: bool = False):
         self.backend = backend
         self.admission = admission
         self.window_rows = min(window_rows, backend.max_rows)
@@ -85,6 +85,8 @@ class Engine:
         self.cost = cost
         self.prefix = prefix if (prefix is not None and backend.prefix_block_tokens() > 0) else None
         self.prefill_policy = prefill_policy
+        # sample and accept on the device (the keyed sampler's device twin) when the backend offers it: only token ids come back
+        self.device_sampler = bool(device_sampler and getattr(backend, "supports_device_sampler", lambda: False)())
         self.burst_tokens = burst_tokens
         self.cache_namespace = cache_namespace
         self.waiting: deque = deque()
@@ -289,7 +291,12 @@ class Engine:
         cand = max(s.req.sampling.candidate_count(self.backend.vocab_size) for s in active)
         cand = min(cand, 64)
         greedy = [s.req.sampling.temperature == 0.0 for s in active]
-        rows = self.backend.step_verified(reqs, cand, greedy)
+        sampled = None
+        if self.device_sampler:
+            sampled = self.backend.step_sampled(reqs, cand, [(s.req.sampling, len(s.tokens)) for s in active])
+            rows = [[None] * len(q.tokens) for q in reqs]
+        else:
+            rows = self.backend.step_verified(reqs, cand, greedy)
         self._check_backend()
         t2 = time.perf_counter_ns()
         if len(rows) != len(reqs) or any(len(r) != len(q.tokens) for r, q in zip(rows, reqs)):
@@ -297,10 +304,14 @@ class Engine:
         self.counters["rounds"] += 1
         self.counters["rows"] += sum(len(q.tokens) for q in reqs)
         # 5. sample every row at its own position, accept the matching prefix, commit or finish
-        for s, p, out in zip(active, proposals, rows):
+        for si, (s, p, out) in enumerate(zip(active, proposals, rows)):
             base = len(s.tokens)
             try:
-                if s.req.sampling.temperature == 0.0 and all(len(o.ids) and o.values[0] == o.values[0] and
+                if sampled is not None:
+                    samples = sampled[si][0]
+                    if samples is None:
+                        raise SamplingError("NaN logit")
+                elif s.req.sampling.temperature == 0.0 and all(len(o.ids) and o.values[0] == o.values[0] and
                                                               (len(o.ids) == 1 or o.values[0] > o.values[1] or
                                                                (o.values[0] == o.values[1] and o.ids[0] < o.ids[1])) for o in out):
                     # greedy over candidates that arrive ordered (value desc, id asc): the first one is the keyed sampler's choice

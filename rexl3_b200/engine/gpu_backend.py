@@ -208,6 +208,56 @@ class DenseGpuBackend(Backend):
             k += len(r.tokens)
         return out
 
+    # ------------------------------------------------------------------ window with device-side sampling and acceptance
+    def supports_device_sampler(self) -> bool:
+        return True
+
+    def step_sampled(self, reqs, candidates, samplings):
+        """Like `step`, but the keyed samples and the accepted-draft counts are computed on the device (verify kernel) and only token ids
+        come back.  samplings: per request (Sampling, absolute position of the first sample).  Returns per request (samples, accepted);
+        samples is None for a sequence whose rows held a NaN logit."""
+        m = self.m
+        specs = []
+        for r in reqs:
+            if r.first_position != self.len[r.slot]:
+                raise BackendError(f"window at {r.first_position} but slot {r.slot} holds {self.len[r.slot]} tokens", fatal=False)
+            self._ensure(r.slot, r.first_position + len(r.tokens))
+            self.pending[r.slot] = len(r.tokens)
+            specs.append((r.slot, r.first_position, r.tokens))
+        M = self._fill_rows(specs)
+        if M > self.max_rows:
+            raise BackendError(f"window of {M} rows exceeds {self.max_rows}", fatal=False)
+        max_ctx = max(r.first_position + len(r.tokens) for r in reqs)
+        bucket = min(m.max_ctx_alloc, (max_ctx + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
+        count = max(1, min(64, candidates))
+        self._announce_window(M, count, bucket)
+        self._upload_rows(M)
+        self._sync_bt()
+        if self.use_graphs:
+            key = (M, count, bucket)
+            g = self.graphs.get(key)
+            if g is None:
+                g = self._capture(M, count, bucket)
+                self.graphs[key] = g
+            g.replay()
+            self.graph_replays += 1
+            self.replayed_kernels += self.graph_kernels[key]
+        else:
+            self._window(M, count, bucket)
+        windows = [(s, pos, r.tokens) for r, (s, pos) in zip(reqs, samplings)]
+        samples, accepted, err = m.K.verify_accept(m._ids_view(M, count), m._vals_view(M, count), windows, device=m.device)
+        hs, ha = samples.cpu().tolist(), accepted.cpu().tolist()      # the stream-ordered copies also fence the step
+        self.h_status.copy_(m.status)
+        self.d2h_bytes += M * 4 + len(reqs) * 4 + 16
+        self._check()
+        bad = int(err.item()) != 0
+        out, k = [], 0
+        for r, a in zip(reqs, ha):
+            n = len(r.tokens)
+            out.append((None if bad else hs[k:k + n], a))
+            k += n
+        return out
+
     def _announce_window(self, M: int, count: int, bucket: int) -> None:
         """Hook for multi-rank backends: tell the other ranks what is about to run (before the block-table dirty set is cleared)."""
 

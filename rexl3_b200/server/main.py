@@ -52,6 +52,7 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--heartbeat-stale-secs", type=float, default=60)
     p.add_argument("--max-body-mib", type=int, default=64)
     p.add_argument("--no-graphs", action="store_true")
+    p.add_argument("--device-sampler", action="store_true", help="sample and accept drafts on the GPU (verify kernel); only token ids come back")
     p.add_argument("--version", action="store_true")
     return p
 
@@ -159,7 +160,7 @@ def build(args):
                                      self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode())
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode(), device_sampler=args.device_sampler)
     tok = load_tokenizer(folder, vocab)
     fmt = ChatFormat.from_dir(folder)
     return make, tok, fmt, name, info

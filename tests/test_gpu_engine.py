@@ -36,3 +36,37 @@ def test_smoke_entry():
         pytest.skip("needs a CUDA device")
     import __graft_entry__ as g
     g.smoke()
+
+
+def test_device_sampler_equals_host_sampler():
+    """The verify kernel (keyed sampler + accept rule on the device) gives the engine the same tokens as the host sampler."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    from rexl3_b200.models import dense
+    from rexl3_b200.sampling import GREEDY, Sampling
+    cfg = dense.CONFIGS["test-hd128"]
+    w = dense.random_weights(cfg, seed=2)
+    rng = np.random.default_rng(5)
+    base = rng.integers(0, cfg.vocab, size=24).tolist()
+    prompts = [base * 3, rng.integers(0, cfg.vocab, size=40).tolist()]          # a repetitive prompt gives the copy drafter something to offer
+    samplings = [GREEDY, Sampling(seed=11, temperature=0.8, top_k=20, top_p=0.9)]
+    outs = {}
+    for dev in (False, True):
+        m = dense.DenseGPU(w, num_pages=32, max_rows=64, max_seqs=4, max_blocks_per_seq=6, max_prefill_rows=256)
+        eng = Engine(DenseGpuBackend(m, max_slots=4), None, window_rows=32, prefill_chunk=256, spec="copy", device_sampler=dev)
+        assert eng.device_sampler == dev
+        for i, (p, s) in enumerate(zip(prompts, samplings)):
+            eng.submit(Request(f"r{i}", p, 14, s))
+        got = {f"r{i}": [] for i in range(len(prompts))}
+        for _ in range(200):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                if ev.kind == "tokens":
+                    got[ev.id].extend(ev.tokens)
+                assert ev.kind != "error", ev.message
+        outs[dev] = got
+    assert outs[False] == outs[True]
