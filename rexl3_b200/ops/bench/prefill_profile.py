@@ -18,7 +18,12 @@ def one(i):
     while eng.seqs.get(f's{i}') is None or eng.seqs[f's{i}'].generated==0: eng.step()
     torch.cuda.synchronize()
 one(0)
+e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 torch.cuda.profiler.start()
+e0.record()
 one(1)
+e1.record()
 torch.cuda.profiler.stop()
+torch.cuda.synchronize()
+print(f'2-layer 8192-token prefill: {e0.elapsed_time(e1):.2f} ms')
 print('ok')
