@@ -244,8 +244,9 @@ __global__ void __launch_bounds__(128) head_gemm_kernel(const uint16_t* __restri
                                                         uint16_t* __restrict__ out, int out_ld, int out_hs, int M) {
   pdl_launch();
   pdl_wait();
-  __shared__ __align__(16) uint8_t ws[16 * (128 * 2 + 16)];
   constexpr int WSTRIDE = 128 * 2 + 16;
+  constexpr int KS = 64;                         // k rows staged per step (one barrier pair per 64 k instead of per 16)
+  __shared__ __align__(16) uint8_t ws[KS * WSTRIDE];
   const int h = blockIdx.x, m0 = blockIdx.y * 64, n0 = blockIdx.z * 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, mi = lane >> 3;
   const int r_lo = m0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
@@ -256,25 +257,28 @@ __global__ void __launch_bounds__(128) head_gemm_kernel(const uint16_t* __restri
   float acc[16][4];
 #pragma unroll
   for (int d = 0; d < 16; ++d) { acc[d][0] = acc[d][1] = acc[d][2] = acc[d][3] = 0.f; }
-  for (int k0 = 0; k0 < K; k0 += 16) {
+  for (int k0 = 0; k0 < K; k0 += KS) {
+    const int kn = min(KS, K - k0);              // K is a multiple of 16
     __syncthreads();
-    for (int i = threadIdx.x; i < 16 * 16; i += 128) {      // 16 k rows x 16 chunks of 8 columns
+    for (int i = threadIdx.x; i < kn * 16; i += 128) {      // kn k rows x 16 chunks of 8 columns
       const int kr = i >> 4, c = i & 15;
       *reinterpret_cast<uint4*>(ws + kr * WSTRIDE + c * 16) = __ldg(reinterpret_cast<const uint4*>(Wh + (size_t)(k0 + kr) * N + c * 8));
     }
     __syncthreads();
-    uint32_t a[4];
-    const int kc = k0 + 2 * (lane & 3);
-    a[0] = r_lo < M ? *reinterpret_cast<const uint32_t*>(a_lo + kc) : 0u;
-    a[1] = r_hi < M ? *reinterpret_cast<const uint32_t*>(a_hi + kc) : 0u;
-    a[2] = r_lo < M ? *reinterpret_cast<const uint32_t*>(a_lo + kc + 8) : 0u;
-    a[3] = r_hi < M ? *reinterpret_cast<const uint32_t*>(a_hi + kc + 8) : 0u;
+    for (int kk = 0; kk < kn; kk += 16) {
+      uint32_t a[4];
+      const int kc = k0 + kk + 2 * (lane & 3);
+      a[0] = r_lo < M ? *reinterpret_cast<const uint32_t*>(a_lo + kc) : 0u;
+      a[1] = r_hi < M ? *reinterpret_cast<const uint32_t*>(a_hi + kc) : 0u;
+      a[2] = r_lo < M ? *reinterpret_cast<const uint32_t*>(a_lo + kc + 8) : 0u;
+      a[3] = r_hi < M ? *reinterpret_cast<const uint32_t*>(a_hi + kc + 8) : 0u;
 #pragma unroll
-    for (int dp = 0; dp < 8; ++dp) {
-      uint32_t b0, b1, b2, b3;
-      ml_ldsm_x4_t(ws_u + ((mi & 1) * 8 + (lane & 7)) * WSTRIDE + (dp * 16 + (mi >> 1) * 8) * 2, b0, b1, b2, b3);
-      ml_mma(acc[2 * dp], a, b0, b1);
-      ml_mma(acc[2 * dp + 1], a, b2, b3);
+      for (int dp = 0; dp < 8; ++dp) {
+        uint32_t b0, b1, b2, b3;
+        ml_ldsm_x4_t(ws_u + (kk + (mi & 1) * 8 + (lane & 7)) * WSTRIDE + (dp * 16 + (mi >> 1) * 8) * 2, b0, b1, b2, b3);
+        ml_mma(acc[2 * dp], a, b0, b1);
+        ml_mma(acc[2 * dp + 1], a, b2, b3);
+      }
     }
   }
   uint16_t* o_lo = out + (size_t)r_lo * out_ld + (size_t)h * out_hs + n0;

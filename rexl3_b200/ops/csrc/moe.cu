@@ -171,11 +171,16 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, int pair
     for (int p = t; p < pairs; p += blockDim.x) ids_sh[p] = ids[p];
   __syncthreads();
   if (staged) ids = ids_sh;
-  // thread e counts its pairs in pair order (every thread reads the same id at the same time: broadcast)
-  if (t < E && t >= e_lo && t < e_hi) {
+  // One warp per expert (warps take experts round robin): the pair list is walked 32 pairs at a time and a ballot says which of them chose
+  // the expert, so a pass costs pairs / 32 steps per expert instead of `pairs`.  Ranks inside a ballot follow the lane order = pair order.
+  const int lane = t & 31, warp = t >> 5, nw = blockDim.x >> 5;
+  for (int e = e_lo + warp; e < e_hi; e += nw) {
     int c = 0;
-    for (int p = 0; p < pairs; ++p) c += (ids[p] == t) ? 1 : 0;
-    cnt[t] = c;
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+      const int p = p0 + lane;
+      c += __popc(__ballot_sync(0xffffffffu, p < pairs && ids[p] == e));
+    }
+    if (lane == 0) cnt[e] = c;
   }
   __syncthreads();
   if (t == 0) {
@@ -195,15 +200,20 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, int pair
     for (; tile < max_tiles; ++tile) { tile_tab[3 * tile] = 0; tile_tab[3 * tile + 1] = 0; tile_tab[3 * tile + 2] = 0; }
   }
   __syncthreads();
-  if (t < E && t >= e_lo && t < e_hi) {
-    int at = start[t];
-    for (int p = 0; p < pairs; ++p)
-      if (ids[p] == t) {
-        pos_of_pair[p] = at;
-        pair_of_pos[at] = p;
-        expert_of_pos[at] = t;
-        ++at;
+  for (int e = e_lo + warp; e < e_hi; e += nw) {
+    int at = start[e];
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+      const int p = p0 + lane;
+      const bool hit = p < pairs && ids[p] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int pos = at + __popc(mask & ((1u << lane) - 1u));
+        pos_of_pair[p] = pos;
+        pair_of_pos[pos] = p;
+        expert_of_pos[pos] = e;
       }
+      at += __popc(mask);
+    }
   }
   for (int p = t; p < pairs; p += blockDim.x) {
     const int e = ids[p];
@@ -383,8 +393,7 @@ RX_API int rx_moe_router2(const void* x, const void* gate, const void* bias, int
 RX_API int rx_moe_plan(const void* ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles, void* offs, void* pos_of_pair,
                        void* pair_of_pos, void* expert_of_pos, void* tile_tab, void* total, void* stream) {
   if (pairs < 1 || E < 1 || E > 512 || e_lo < 0 || e_hi > E || e_lo >= e_hi || tile_rows < 16 || max_tiles < 1) return (int)cudaErrorInvalidValue;
-  int threads = 32 * ((E + 31) / 32);
-  if (threads < 256) threads = 256;
+  const int threads = 1024;        // 32 warps share the owned experts
   return (int)rx::launch(moe_plan_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream, (const int*)ids, pairs, E, e_lo, e_hi, tile_rows, max_tiles,
                          (int*)offs, (int*)pos_of_pair, (int*)pair_of_pos, (int*)expert_of_pos, (int*)tile_tab, (int*)total);
 }
