@@ -34,6 +34,11 @@ class Request:
     draft: bool = True
     prefix_cache: bool = True
     deadline: float | None = None       # absolute time.monotonic() after which the request is cancelled
+    # reasoning budget: at most `reasoning_budget` tokens inside the thinking block, then the closing tag's tokens are forced, one per round
+    reasoning_budget: int | None = None
+    think_close_ids: tuple = ()
+    reasoning_open: bool = False        # the prompt ends inside the thinking block (the template opened it)
+    think_open_ids: tuple = ()          # a generated opening tag also starts the block
 
 
 @dataclass
@@ -64,6 +69,7 @@ class _Seq:
     t_first: float | None = None
     committed_blocks: int = 0
     hashes: list = None
+    reasoning: dict = None     # reasoning-budget state (see Engine._reasoning_budget)
 
 
 class StepError(Exception):
@@ -334,6 +340,9 @@ class Engine:
             new = samples[:a + 1]
             emitted, reason = [], None
             for t in new:
+                forced = False
+                if s.req.reasoning_budget is not None and s.req.think_close_ids:
+                    t, forced = self._reasoning_budget(s, t)
                 emitted.append(t)
                 s.tokens.append(t)
                 s.generated += 1
@@ -343,6 +352,8 @@ class Engine:
                 if s.generated >= s.req.max_new_tokens:
                     reason = "length"
                     break
+                if forced:
+                    break      # the samples after a forced token were made for another continuation: their rows are not kept
             self.counters["decode_tokens"] += len(emitted)
             self.events.append(Event("tokens", s.req.id, tokens=emitted))
             if reason is not None:
@@ -352,6 +363,34 @@ class Engine:
         self.phase_ns["draft"] += t1 - t0
         self.phase_ns["verify"] += t2 - t1
         self.phase_ns["commit"] += time.perf_counter_ns() - t2
+
+    def _reasoning_budget(self, s, t: int):
+        """Reasoning budget (reference crates/engine/src/lib.rs:572-577): counts tokens inside the thinking block; when the budget is
+        used up the closing tag's tokens replace the sampled ones, one per round.  -> (token to emit, whether it was forced)."""
+        st = s.reasoning
+        if st is None:
+            st = s.reasoning = dict(open=s.req.reasoning_open, used=0, force=None, close_match=0, open_match=0)
+        close, opn = s.req.think_close_ids, s.req.think_open_ids
+        if not st["open"]:
+            if opn:
+                st["open_match"] = st["open_match"] + 1 if t == opn[st["open_match"]] else (1 if t == opn[0] else 0)
+                if st["open_match"] == len(opn):
+                    st.update(open=True, open_match=0, used=0, close_match=0)
+            return t, False
+        if st["force"] is not None:
+            t = close[st["force"]]
+            st["force"] += 1
+            if st["force"] == len(close):
+                st.update(open=False, force=None)
+            return t, True
+        st["close_match"] = st["close_match"] + 1 if t == close[st["close_match"]] else (1 if t == close[0] else 0)
+        if st["close_match"] == len(close):
+            st.update(open=False, close_match=0)
+            return t, False
+        st["used"] += 1
+        if st["used"] >= s.req.reasoning_budget and st["close_match"] == 0:
+            st["force"] = 0
+        return t, False
 
     # ------------------------------------------------------------------ prefill
     def _prefill(self) -> None:

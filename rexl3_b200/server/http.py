@@ -60,7 +60,7 @@ def _ready_or_503(st: AppState) -> None:
         raise api.ApiError(503, f"engine is {s}", "service_unavailable", s, retry_after=5)
 
 
-def _make_request(st: AppState, ids: list, p: api.Params, rid: str) -> Request:
+def _make_request(st: AppState, ids: list, p: api.Params, rid: str, prompt_text: str = "") -> Request:
     if not ids:
         raise api.bad("the prompt is empty")
     limit = st.max_model_len
@@ -72,7 +72,14 @@ def _make_request(st: AppState, ids: list, p: api.Params, rid: str) -> Request:
     if p.seed is None and samp.temperature > 0:
         samp = samp.with_seed(seed_for(ids, 0))
     stop_ids = tuple(st.tok.eos_ids)
-    return Request(rid, ids, max_new, samp, stop_ids, draft=p.draft, prefix_cache=p.prefix_cache)
+    req = Request(rid, ids, max_new, samp, stop_ids, draft=p.draft, prefix_cache=p.prefix_cache)
+    if getattr(p, "max_reasoning_tokens", None) is not None and st.fmt.think_close:
+        # reasoning budget: the engine forces the closing tag once that many tokens were spent inside the thinking block
+        req.reasoning_budget = int(p.max_reasoning_tokens)
+        req.think_close_ids = tuple(st.tok.encode(st.fmt.think_close))
+        req.think_open_ids = tuple(st.tok.encode(st.fmt.think_open)) if st.fmt.think_open else ()
+        req.reasoning_open = bool(st.fmt.think_open) and prompt_text.rstrip().endswith(st.fmt.think_open)
+    return req
 
 
 class _Reply:
@@ -233,7 +240,7 @@ def build_app(st: AppState) -> Starlette:
                 else:
                     raise api.bad("'prompt' must be a string or a list of token ids", "prompt")
             rid = api.new_id("chatcmpl" if chat else "cmpl")
-            req = _make_request(st, ids, p, rid)
+            req = _make_request(st, ids, p, rid, prompt_text if chat else "")
             try:
                 ticket = st.handle.submit(req, asyncio.get_running_loop())
             except OverflowError:

@@ -121,3 +121,35 @@ def test_prefix_cache_hits_share_blocks_and_evict():
     assert MockOptions.parse("vocab=100,native_draft=true,fault=rollback_leak").native_draft
     with pytest.raises(ValueError):
         MockOptions.parse("nope=1")
+
+
+def test_reasoning_budget_forces_the_closing_tag():
+    """After `reasoning_budget` tokens inside the thinking block the closing tag's tokens replace the samples, one per round; drafts
+    accepted beyond a forced token are not kept; without a budget nothing changes."""
+    close = (7001, 7002)
+    opts = MockOptions(slots=2, vocab=8000)
+    base = generate(Engine(MockBackend(opts), None, spec="copy"), [list(range(10, 40))], 24, GREEDY)[0]
+    assert not any(t in close for t in base)
+    eng = Engine(MockBackend(opts), None, spec="copy")
+    req = Request("r", list(range(10, 40)), 24, GREEDY, reasoning_budget=5, think_close_ids=close, reasoning_open=True)
+    eng.submit(req)
+    out = []
+    while eng.has_work():
+        for ev in eng.step():
+            if ev.kind == "tokens":
+                out.extend(ev.tokens)
+    assert len(out) == 24
+    i = out.index(close[0])
+    assert 5 <= i <= 6 and out[i + 1] == close[1]          # the first generated token comes from the prefill and is not counted
+    assert out[:i] == base[:i]                               # identical up to the forced close
+    assert out.count(close[0]) == 1
+    # a closing tag produced by the model itself ends the block: no forcing afterwards
+    eng2 = Engine(MockBackend(opts), None, spec="none")
+    nat = (base[2], base[3])
+    eng2.submit(Request("n", list(range(10, 40)), 24, GREEDY, reasoning_budget=8, think_close_ids=nat, reasoning_open=True))
+    out2 = []
+    while eng2.has_work():
+        for ev in eng2.step():
+            if ev.kind == "tokens":
+                out2.extend(ev.tokens)
+    assert out2 == base
