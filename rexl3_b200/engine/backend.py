@@ -87,6 +87,10 @@ class Backend:
     def supports_native_draft(self) -> bool:
         return False
 
+    def supports_rollback(self) -> bool:
+        """False: rows fed to `step` cannot be rejected afterwards (recurrent state), so the engine plans no draft rows."""
+        return True
+
     def take_error(self):
         """A BackendError raised asynchronously by the last call (device status words), or None."""
         return None

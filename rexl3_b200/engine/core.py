@@ -88,6 +88,7 @@ class Engine:
         self.prefill_chunk = prefill_chunk
         self.spec = spec if isinstance(spec, SpecMode) else SpecMode(spec)
         self.max_drafts = max_drafts
+        self.can_rollback = getattr(backend, "supports_rollback", lambda: True)()
         self.cost = cost
         self.prefix = prefix if (prefix is not None and backend.prefix_block_tokens() > 0) else None
         self.prefill_policy = prefill_policy
@@ -265,7 +266,7 @@ class Engine:
         maxes = []
         for s in active:
             room = s.req.max_new_tokens - s.generated
-            m = min(self.max_drafts, max(0, room - 1)) if (self.spec.enabled and s.req.draft) else 0
+            m = min(self.max_drafts, max(0, room - 1)) if (self.spec.enabled and s.req.draft and self.can_rollback) else 0
             maxes.append(m)
         # 2. proposals: native drafter first, copy drafter otherwise
         proposals = [[] for _ in active]

@@ -443,3 +443,38 @@ class DenseGpuBackend(Backend):
     def stats(self):
         return dict(graph_replays=self.graph_replays, graph_captures=self.graph_captures, replayed_kernels=self.replayed_kernels, h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes,
                     free_pages=self.pool.free_blocks())
+
+
+class _SkipFirstReplay:
+    """A captured window whose first replay is skipped: the eager run that preceded the capture already did that step's work."""
+
+    def __init__(self, graph):
+        self.graph, self.first = graph, True
+
+    def replay(self):
+        if self.first:
+            self.first = False
+            return
+        self.graph.replay()
+
+
+class HybridGpuBackend(DenseGpuBackend):
+    """Backend over a hybrid (Mamba2 + attention) executor.  The recurrent state advances with every row it is fed, so: no draft rows
+    (`supports_rollback` is False), no prefix cache (a cached block would need a state snapshot), and a window is never run twice for
+    one step (the eager run before a graph capture stands in for that graph's first replay)."""
+    name = "cuda-hybrid"
+
+    def __init__(self, model, max_slots=None, use_graphs: bool = True):
+        super().__init__(model, max_slots=max_slots, use_graphs=use_graphs, self_draft=False)
+
+    def supports_rollback(self) -> bool:
+        return False
+
+    def supports_device_sampler(self) -> bool:
+        return False
+
+    def prefix_block_tokens(self):
+        return 0
+
+    def _capture(self, M, count, bucket):
+        return _SkipFirstReplay(super()._capture(M, count, bucket))

@@ -207,6 +207,30 @@ class ReferenceDense:
         F = cfg.ffn_padded
         return h + (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
 
+    def _mix(self, li, L, h, pos, seq, start):
+        """Token mixer of one layer on the residual stream `h` [T, d]: returns what is added to it (here: GQA attention + o_proj)."""
+        cfg = self.cfg
+        T = h.shape[0]
+        x = self._rms(h, L["attn_norm"], cfg.eps)
+        qkv = x @ L["qkv"]
+        q = qkv[:, :cfg.n_q * cfg.head_dim].view(T, cfg.n_q, cfg.head_dim)
+        k = qkv[:, cfg.n_q * cfg.head_dim:(cfg.n_q + cfg.n_kv) * cfg.head_dim].view(T, cfg.n_kv, cfg.head_dim)
+        v = qkv[:, (cfg.n_q + cfg.n_kv) * cfg.head_dim:].view(T, cfg.n_kv, cfg.head_dim)
+        if L["q_norm"] is not None:
+            q, k = self._rms(q, L["q_norm"], cfg.eps), self._rms(k, L["k_norm"], cfg.eps)
+        q, k = self._rope(q, pos), self._rope(k, pos)
+        pk, pv = self.kv[seq][li]
+        kk, vv = torch.cat([pk[:start], k]), torch.cat([pv[:start], v])
+        self.kv[seq][li] = (kk, vv)
+        g = cfg.n_q // cfg.n_kv
+        kq, vq = kk.repeat_interleave(g, dim=1), vv.repeat_interleave(g, dim=1)
+        s = torch.einsum("thd,shd->hts", q, kq) / math.sqrt(cfg.head_dim)
+        kpos = torch.arange(kk.shape[0], device=self.device)
+        mask = kpos[None, :] > pos[:, None]
+        s = s.masked_fill(mask[None], float("-inf"))
+        a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), vq).reshape(T, -1)
+        return a @ L["o"]
+
     @torch.no_grad()
     def forward_seq(self, seq, tokens, start: int, n_layers: int | None = None) -> torch.Tensor:
         """Append `tokens` to sequence `seq` at positions start.. ; returns logits [T, vocab] (fp32).  `n_layers` runs only the
@@ -219,25 +243,7 @@ class ReferenceDense:
         if seq not in self.kv:
             self.kv[seq] = [(torch.zeros(0, cfg.n_kv, cfg.head_dim, device=self.device, dtype=self.dtype),) * 2 for _ in self.layers]
         for li, L in enumerate(self.layers[:n_layers or len(self.layers)]):
-            x = self._rms(h, L["attn_norm"], cfg.eps)
-            qkv = x @ L["qkv"]
-            q = qkv[:, :cfg.n_q * cfg.head_dim].view(T, cfg.n_q, cfg.head_dim)
-            k = qkv[:, cfg.n_q * cfg.head_dim:(cfg.n_q + cfg.n_kv) * cfg.head_dim].view(T, cfg.n_kv, cfg.head_dim)
-            v = qkv[:, (cfg.n_q + cfg.n_kv) * cfg.head_dim:].view(T, cfg.n_kv, cfg.head_dim)
-            if L["q_norm"] is not None:
-                q, k = self._rms(q, L["q_norm"], cfg.eps), self._rms(k, L["k_norm"], cfg.eps)
-            q, k = self._rope(q, pos), self._rope(k, pos)
-            pk, pv = self.kv[seq][li]
-            kk, vv = torch.cat([pk[:start], k]), torch.cat([pv[:start], v])
-            self.kv[seq][li] = (kk, vv)
-            g = cfg.n_q // cfg.n_kv
-            kq, vq = kk.repeat_interleave(g, dim=1), vv.repeat_interleave(g, dim=1)
-            s = torch.einsum("thd,shd->hts", q, kq) / math.sqrt(cfg.head_dim)
-            kpos = torch.arange(kk.shape[0], device=self.device)
-            mask = kpos[None, :] > pos[:, None]
-            s = s.masked_fill(mask[None], float("-inf"))
-            a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), vq).reshape(T, -1)
-            h = self._ffn(li, L, h + a @ L["o"])
+            h = self._ffn(li, L, h + self._mix(li, L, h, pos, seq, start))
         return (self._rms(h, self.final_norm, cfg.eps) @ self.lm_head).float()
 
 
@@ -272,12 +278,13 @@ class DenseGPU:
             raise ValueError(f"kv_dtype {kv_dtype!r}: bf16 or fp8")
         self.kv_fp8 = kv_dtype == "fp8"
         cdt = torch.uint8 if self.kv_fp8 else torch.bfloat16
-        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) for _ in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) for _ in range(cfg.n_layers)]
+        kvl = set(self._kv_layers())
+        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(cfg.n_layers)]
         self.kv_scale = torch.ones(cfg.n_layers, 2, cfg.n_kv, dtype=torch.float32, device=device) if self.kv_fp8 else None
         self.kv_amax = None        # set while calibrating
-        self.tk = [K.KvTensorMap(c) for c in self.k_cache]
-        self.tv = [K.KvTensorMap(c) for c in self.v_cache]
+        self.tk = [None if c is None else K.KvTensorMap(c) for c in self.k_cache]
+        self.tv = [None if c is None else K.KvTensorMap(c) for c in self.v_cache]
         self.status = K.new_status(device)
         self._alloc_scratch(self.max_rows)
 
@@ -328,19 +335,17 @@ class DenseGPU:
     # ------------------------------------------------------------------ buffers
     def _alloc_scratch(self, R: int):
         cfg, K, dev = self.cfg, self.K, self.device
-        widths = [cfg.qkv_width, cfg.d_model, 2 * cfg.ffn_padded]
         self.splits = {}
         part_elems = 0
+        shapes = self._gemm_shapes()
         for cls, rows in (("decode", min(R, 256)), ("prefill", R)):
-            for name, (k, n) in dict(qkv=(cfg.d_model, cfg.qkv_width), o=(cfg.n_q * cfg.head_dim, cfg.d_model),
-                                     gate_up=(cfg.d_model, 2 * cfg.ffn_padded), down=(cfg.ffn_padded, cfg.d_model),
-                                     lm_head=(cfg.d_model, cfg.vocab_padded)).items():
+            for name, (k, n) in shapes.items():
                 s = K.plan_splits(k, n, cls == "decode")
                 self.splits[(cls, name)] = s
                 r = rows if name != "lm_head" else min(rows, 256)
                 part_elems = max(part_elems, s * r * n)
         self.part = torch.empty(part_elems, dtype=torch.float32, device=dev)
-        kmax = max(cfg.d_model, cfg.n_q * cfg.head_dim, cfg.ffn_padded)
+        kmax = max(k for k, _ in shapes.values())
         self.xr = torch.empty(R * kmax, dtype=torch.float16, device=dev)
         self.xr2 = torch.empty(R * cfg.ffn_padded, dtype=torch.float16, device=dev)
         self.h = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
@@ -352,7 +357,16 @@ class DenseGPU:
         self.topk_scratch = K.topk_scratch(min(R, 256), cfg.vocab_padded, 64, dev)
         self.cand_ids = torch.empty(min(R, 256), 64, dtype=torch.int32, device=dev)
         self.cand_vals = torch.empty(min(R, 256), 64, dtype=torch.float32, device=dev)
-        del widths
+
+    def _gemm_shapes(self) -> dict:
+        """name -> (K, N) of every EXL3 GEMM this executor launches through `_linear` (sizes the split plans and the scratch)."""
+        cfg = self.cfg
+        return dict(qkv=(cfg.d_model, cfg.qkv_width), o=(cfg.n_q * cfg.head_dim, cfg.d_model), gate_up=(cfg.d_model, 2 * cfg.ffn_padded),
+                    down=(cfg.ffn_padded, cfg.d_model), lm_head=(cfg.d_model, cfg.vocab_padded))
+
+    def _kv_layers(self):
+        """Indices of the layers that own a paged KV cache (all of them here; a hybrid has layers without one)."""
+        return range(self.cfg.n_layers)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes
@@ -387,6 +401,25 @@ class DenseGPU:
     def _linear(self, xr, w, rows, cls, name):
         s = self.splits[(cls, name)]
         self.K.exl3_gemm(xr, w, self.part, s, self.status)
+        return s
+
+    def _mixer(self, li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale):
+        """The token mixer of layer `li` up to and including its output projection GEMM: leaves that GEMM's K-split partials in self.part
+        and returns the split count.  Here: paged GQA attention."""
+        cfg, K = self.cfg, self.K
+        s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
+        ksc = self.kv_scale[li] if self.kv_fp8 else None
+        K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
+                          self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li])
+        if prefill is None:
+            K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
+                          max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc)
+        else:
+            ao = self.attn_out[:M]
+            K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
+                           ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc)
+            K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
+        s = self._linear(xr_a, L["o"], M, cls, "o")
         return s
 
     def _begin_forward(self) -> None:
@@ -444,19 +477,7 @@ class DenseGPU:
         nl = n_layers or len(self.layers)      # n_layers < all: the self-speculative draft (first layers + shared final norm and head)
         for li in range(nl):
             L = self.layers[li]
-            s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
-            ksc = self.kv_scale[li] if self.kv_fp8 else None
-            K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
-                              self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li])
-            if prefill is None:
-                K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
-                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc)
-            else:
-                ao = self.attn_out[:M]
-                K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
-                               ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc)
-                K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
-            s = self._linear(xr_a, L["o"], M, cls, "o")
+            s = self._mixer(li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale)
             nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
             yield from self._ffn_phases(li, L, M, cls, s, h, xr_d, xr_f, nn_, ns_)
         if not want_logits:

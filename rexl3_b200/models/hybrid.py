@@ -1,0 +1,303 @@
+"""Hybrid decoder family: every layer is a token mixer followed by the dense SwiGLU FFN, and the mixer is either a Mamba2
+(SSD) block with a constant-size recurrent state or (NoPE) GQA attention over the paged KV cache.
+
+What it mirrors: the reference's `nemotron_h_omni` text backbone (Mamba2 + NoPE GQA blocks; crates/model/src/families/
+nemotron_h_omni/mod.rs:58-251, oracle ssm_ref.rs, kernels crates/cuda/csrc/nemotron_ssm.cu:1-45) with this engine's
+own executor: the Mamba2 layer is in_proj (EXL3 GEMM) -> finish to f32 rows -> conv + recurrence + gated norm
+(`ops/csrc/ssm.cu`, three launches) -> rotation -> out_proj (EXL3 GEMM), whose partials feed the same fused
+add + norm + rotate finish as an attention layer's o_proj.
+
+Recurrent state lives in two pools per Mamba2 layer, indexed by the engine's sequence slot.  A row at position 0 restarts
+the state, so slots are reused without a reset call.  Rows are always committed: an engine backend over this executor
+offers no drafts and no prefix cache (a cached prefix would need a state snapshot per block).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..format import exl3
+from .dense import (DenseConfig, DenseGPU, HostLinear, HostWeights, ReferenceDense, _bf16_round, random_linear, rope_inv_freq)
+
+
+@dataclass
+class HybridConfig(DenseConfig):
+    pattern: str = ""            # one letter per layer: 'M' = Mamba2 mixer, 'A' = attention mixer
+    ssm_heads: int = 0
+    ssm_head_dim: int = 64
+    ssm_groups: int = 1
+    ssm_state: int = 128
+    conv_k: int = 4
+    nope: bool = True            # attention layers without rotary embedding
+
+    @property
+    def d_inner(self) -> int:
+        return self.ssm_heads * self.ssm_head_dim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.d_inner + 2 * self.ssm_groups * self.ssm_state
+
+    @property
+    def in_proj_width(self) -> int:
+        """z | x | B | C | dt, padded up to a multiple of 128 columns (the padding columns are exactly zero)."""
+        return (2 * self.d_inner + 2 * self.ssm_groups * self.ssm_state + self.ssm_heads + 127) // 128 * 128
+
+    def mamba_layers(self):
+        return [i for i, c in enumerate(self.pattern) if c == "M"]
+
+    def attn_layers(self):
+        return [i for i, c in enumerate(self.pattern) if c == "A"]
+
+    def validate(self) -> None:
+        if len(self.pattern) != self.n_layers or set(self.pattern) - {"M", "A"}:
+            raise ValueError("pattern needs one of 'M' / 'A' per layer")
+        if self.ssm_head_dim != 64 or self.ssm_state != 128 or self.conv_k != 4:
+            raise ValueError("the Mamba2 kernels are built for head_dim 64, state 128, conv width 4")
+        if self.ssm_heads % self.ssm_groups or self.d_inner % 128:
+            raise ValueError("ssm_heads must be a multiple of ssm_groups and even")
+
+    def state_bytes_per_slot(self) -> int:
+        return len(self.mamba_layers()) * 4 * (self.ssm_heads * self.ssm_head_dim * self.ssm_state + 3 * self.conv_channels)
+
+    def kv_bytes_per_token(self, elem_bytes: int = 2) -> int:
+        return 2 * self.n_kv * self.head_dim * elem_bytes * len(self.attn_layers())
+
+
+CONFIGS = {
+    # the reference family's block geometry (128 heads x 64, state 128, 8 groups; GQA 32q / 2kv x 128) as a dense-FFN hybrid
+    "hybrid-h-56l": HybridConfig(n_layers=56, d_model=4096, n_q=32, n_kv=2, head_dim=128, ffn=14336, vocab=131072, bits=4.0, name="hybrid-h-56l",
+                                 pattern="MMMMMMA" * 8, ssm_heads=128, ssm_groups=8),
+    "test-hybrid": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid",
+                                pattern="MAMM", ssm_heads=16, ssm_groups=2),
+}
+
+
+@dataclass
+class HostMambaLayer:
+    attn_norm: np.ndarray
+    in_proj: HostLinear
+    out_proj: HostLinear
+    conv_w: np.ndarray           # [C, 4], tap 3 multiplies the current row
+    conv_b: np.ndarray           # [C]
+    dt_bias: np.ndarray          # [H]
+    a_log: np.ndarray            # [H]; A = -exp(a_log)
+    d_skip: np.ndarray           # [H]
+    norm_w: np.ndarray           # [d_inner]
+    ffn_norm: np.ndarray
+    gate_up: HostLinear
+    down: HostLinear
+
+
+def random_weights(cfg: HybridConfig, seed: int = 0) -> HostWeights:
+    """Random-init hybrid weights (valid random EXL3 tensors; SSM parameters in their usual ranges)."""
+    from .dense import HostLayer
+    cfg.validate()
+    rng = np.random.default_rng(seed)
+    d, F, DI, H, C = cfg.d_model, cfg.ffn_padded, cfg.d_inner, cfg.ssm_heads, cfg.conv_channels
+    s_in = 1.0 / math.sqrt(d)
+    w = HostWeights(cfg, _bf16_round(rng.normal(0, 1.0, size=(cfg.vocab, d)).astype(np.float32)))
+    nrm = lambda n: _bf16_round(1.0 + 0.1 * rng.normal(size=n))  # noqa: E731
+    for kind in cfg.pattern:
+        gu = random_linear(d, 2 * F, cfg.bits, rng, cfg.codebook, s_in)
+        if F != cfg.ffn:
+            gu.svh[cfg.ffn:F] = 0
+            gu.svh[F + cfg.ffn:] = 0
+        down = random_linear(F, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(F), zero_rows_from=cfg.ffn if F != cfg.ffn else None)
+        if kind == "A":
+            qkv = random_linear(d, cfg.qkv_width, cfg.bits, rng, cfg.codebook, s_in)
+            o = random_linear(cfg.n_q * cfg.head_dim, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(cfg.n_q * cfg.head_dim))
+            w.layers.append(HostLayer(nrm(d), qkv, o, nrm(d), gu, down))
+            continue
+        real = 2 * DI + 2 * cfg.ssm_groups * cfg.ssm_state + H
+        ip = random_linear(d, cfg.in_proj_width, cfg.bits, rng, cfg.codebook, s_in, zero_cols_from=real if real != cfg.in_proj_width else None)
+        op = random_linear(DI, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(DI))
+        w.layers.append(HostMambaLayer(
+            nrm(d), ip, op, _bf16_round(rng.normal(0, 0.5, size=(C, 4))), _bf16_round(rng.normal(0, 0.1, size=C)),
+            rng.uniform(-3.0, -1.0, size=H).astype(np.float32), np.log(rng.uniform(1.0, 16.0, size=H)).astype(np.float32),
+            rng.normal(1.0, 0.1, size=H).astype(np.float32), nrm(DI), nrm(d), gu, down))
+    w.final_norm = nrm(d)
+    w.lm_head = random_linear(d, cfg.vocab_padded, cfg.head_bits or cfg.bits, rng, cfg.codebook, s_in,
+                              zero_cols_from=cfg.vocab if cfg.vocab_padded != cfg.vocab else None)
+    return w
+
+
+# ====================================================================================================== reference
+class ReferenceHybrid(ReferenceDense):
+    """fp32 oracle: the dense reference with a per-layer mixer switch and a token-by-token Mamba2 recurrence."""
+
+    def __init__(self, w: HostWeights, device="cpu", dtype=torch.float32):
+        self.cfg = cfg = w.cfg
+        self.device, self.dtype = device, dtype
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dtype)  # noqa: E731
+        self.embed = t(w.embed)
+        self.layers = []
+        for lay in w.layers:
+            L = dict(attn_norm=t(lay.attn_norm), ffn_norm=t(lay.ffn_norm), gate_up=t(lay.gate_up.dense()), down=t(lay.down.dense()), q_norm=None, k_norm=None)
+            if isinstance(lay, HostMambaLayer):
+                L.update(kind="M", in_proj=t(lay.in_proj.dense()), o=t(lay.out_proj.dense()), conv_w=t(lay.conv_w), conv_b=t(lay.conv_b),
+                         dt_bias=t(lay.dt_bias), a_neg=-torch.exp(t(lay.a_log)), d_skip=t(lay.d_skip), norm_w=t(lay.norm_w))
+            else:
+                L.update(kind="A", qkv=t(lay.qkv.dense()), o=t(lay.o.dense()))
+            self.layers.append(L)
+        self.final_norm = t(w.final_norm)
+        self.lm_head = t(w.lm_head.dense())[:, :cfg.vocab]
+        self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
+        if cfg.nope:
+            self.inv_freq.zero_()
+        self.kv = {}
+        self.ssm = {}          # (seq, layer) -> (conv history [3, C], state [H, P, N])
+
+    def reset(self, seq=None):
+        super().reset(seq)
+        for k in [k for k in self.ssm if seq is None or k[0] == seq]:
+            del self.ssm[k]
+
+    def truncate(self, seq, length: int):
+        raise NotImplementedError("a recurrent state cannot be rolled back")
+
+    def _mix(self, li, L, h, pos, seq, start):
+        if L["kind"] == "A":
+            return super()._mix(li, L, h, pos, seq, start)
+        cfg = self.cfg
+        T, H, P, G, N, DI, C = h.shape[0], cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, cfg.d_inner, cfg.conv_channels
+        proj = self._rms(h, L["attn_norm"], cfg.eps) @ L["in_proj"]
+        z, xbc, dt = proj[:, :DI], proj[:, DI:DI + C], proj[:, DI + C:DI + C + H]
+        if start == 0 or (seq, li) not in self.ssm:
+            hist, S = torch.zeros(3, C, device=h.device, dtype=h.dtype), torch.zeros(H, P, N, device=h.device, dtype=h.dtype)
+        else:
+            hist, S = self.ssm[(seq, li)]
+        full = torch.cat([hist, xbc])
+        conv = L["conv_b"][None, :] + sum(L["conv_w"][:, j][None, :] * full[j:j + T] for j in range(4))
+        act = torch.nn.functional.silu(conv)
+        xs = act[:, :DI].view(T, H, P)
+        Bm = act[:, DI:DI + G * N].view(T, G, N).repeat_interleave(H // G, dim=1)
+        Cm = act[:, DI + G * N:].view(T, G, N).repeat_interleave(H // G, dim=1)
+        dt = torch.nn.functional.softplus(dt + L["dt_bias"][None, :])
+        dA = torch.exp(dt * L["a_neg"][None, :])
+        y = torch.empty(T, H, P, device=h.device, dtype=h.dtype)
+        for t_ in range(T):
+            S = S * dA[t_][:, None, None] + (xs[t_] * dt[t_][:, None])[:, :, None] * Bm[t_][:, None, :]
+            y[t_] = (S * Cm[t_][:, None, :]).sum(-1) + L["d_skip"][:, None] * xs[t_]
+        self.ssm[(seq, li)] = (full[-3:].clone(), S)
+        g = (y.reshape(T, DI) * torch.nn.functional.silu(z)).view(T, G, DI // G)
+        g = g * torch.rsqrt(g.pow(2).mean(-1, keepdim=True) + cfg.eps)
+        return (g.reshape(T, DI) * L["norm_w"]) @ L["o"]
+
+
+# ====================================================================================================== sm_100a executor
+class HybridGPU(DenseGPU):
+    """One B200.  Attention layers run the dense executor's mixer; Mamba2 layers run `_mamba`.  A Mamba2 layer's in_proj / out_proj sit
+    under the keys "qkv" / "o" of its layer dict as well, so the shared layer loop finds each layer's input rotation and output scales."""
+
+    def __init__(self, w: "HostWeights | HybridConfig", num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256,
+                 device="cuda", max_prefill_rows: int = 8192, seed: int = 0, kv_dtype: str = "bf16"):
+        cfg = w if isinstance(w, HybridConfig) else w.cfg
+        cfg.validate()
+        super().__init__(w, num_pages, max_rows, max_seqs, max_blocks_per_seq, device, max_prefill_rows, seed, kv_dtype)
+        if cfg.nope:
+            self.inv_freq.zero_()
+        H, P, N, C = cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_state, cfg.conv_channels
+        self.conv_pool = {li: torch.zeros(max_seqs, 3, C, dtype=torch.float32, device=device) for li in cfg.mamba_layers()}
+        self.ssm_pool = {li: torch.zeros(max_seqs, H, P, N, dtype=torch.float32, device=device) for li in cfg.mamba_layers()}
+
+    def _kv_layers(self):
+        return self.cfg.attn_layers()
+
+    def _gemm_shapes(self) -> dict:
+        cfg = self.cfg
+        s = super()._gemm_shapes()
+        s.update(in_proj=(cfg.d_model, cfg.in_proj_width), out_proj=(cfg.d_inner, cfg.d_model))
+        return s
+
+    def _alloc_scratch(self, R: int):
+        super()._alloc_scratch(R)
+        cfg, dev = self.cfg, self.device
+        self.ssm_proj = torch.empty(R, cfg.in_proj_width, dtype=torch.float32, device=dev)
+        self.ssm_xbc = torch.empty(R, cfg.conv_channels, dtype=torch.float32, device=dev)
+        self.ssm_y = torch.empty(R, cfg.d_inner, dtype=torch.float32, device=dev)
+        self.ssm_out = torch.empty(R, cfg.d_inner, dtype=torch.bfloat16, device=dev)
+
+    # ------------------------------------------------------------------ weights
+    def _mamba_dict(self, attn_norm, ip, op, conv_w, conv_b, dt_bias, a_neg, d_skip, norm_w, ffn_norm, gu, dn):
+        return dict(kind="M", attn_norm=attn_norm, qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=conv_w, conv_b=conv_b, dt_bias=dt_bias, a_neg=a_neg,
+                    d_skip=d_skip, norm_w=norm_w, ffn_norm=ffn_norm, gate_up=gu, down=dn, q_norm=None, k_norm=None)
+
+    def _load_host(self, w: HostWeights) -> None:
+        K, device = self.K, self.device
+        dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
+        up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731
+        bf, f32 = torch.bfloat16, torch.float32
+        self.embed = dev(w.embed, bf)
+        self.layers = []
+        for lay in w.layers:
+            if isinstance(lay, HostMambaLayer):
+                self.layers.append(self._mamba_dict(dev(lay.attn_norm, bf), up(lay.in_proj), up(lay.out_proj), dev(lay.conv_w, bf), dev(lay.conv_b, bf),
+                                                    dev(lay.dt_bias, f32), -torch.exp(dev(lay.a_log, f32)), dev(lay.d_skip, f32), dev(lay.norm_w, bf),
+                                                    dev(lay.ffn_norm, bf), up(lay.gate_up), up(lay.down)))
+            else:
+                self.layers.append(dict(kind="A", attn_norm=dev(lay.attn_norm, bf), qkv=up(lay.qkv), o=up(lay.o), ffn_norm=dev(lay.ffn_norm, bf),
+                                        gate_up=up(lay.gate_up), down=up(lay.down), q_norm=None, k_norm=None))
+        self.final_norm = dev(w.final_norm, bf)
+        self.lm_head = up(w.lm_head)
+
+    def _load_random(self, seed: int) -> None:
+        cfg, K, device = self.cfg, self.K, self.device
+        g = torch.Generator(device=device).manual_seed(seed)
+        tw = exl3.Bits.of(cfg.bits).tile_words
+        cb = cfg.codebook if exl3.Bits.of(cfg.bits).is_integer else "mul1"
+
+        def lin(k, n, scale, words=tw, real_n=None):
+            tr = torch.randint(-32768, 32768, (k // 16, n // 16, words), dtype=torch.int16, device=device, generator=g)
+            sg = lambda m: (torch.randint(0, 2, (m,), device=device, generator=g) * 2 - 1)  # noqa: E731
+            wt = K.Exl3Weight(tr, sg(k).to(torch.float16), (sg(n) * scale).to(torch.float16), None, cb)
+            if real_n is not None and real_n != n:
+                wt.svh[real_n:] = 0
+            return wt
+
+        rn = lambda *s: torch.randn(*s, device=device, generator=g)  # noqa: E731
+        ru = lambda n, lo, hi: lo + (hi - lo) * torch.rand(n, device=device, generator=g)  # noqa: E731
+        norm = lambda n=cfg.d_model: (1.0 + 0.1 * rn(n)).to(torch.bfloat16)  # noqa: E731
+        d, F, HQ, DI, H, C = cfg.d_model, cfg.ffn_padded, cfg.n_q * cfg.head_dim, cfg.d_inner, cfg.ssm_heads, cfg.conv_channels
+        self.embed = rn(cfg.vocab, d).to(torch.bfloat16)
+        self.layers = []
+        for kind in cfg.pattern:
+            gu = lin(d, 2 * F, 1.0 / math.sqrt(d))
+            dn = lin(F, d, 0.5 / math.sqrt(F))
+            if F != cfg.ffn:
+                gu.svh[cfg.ffn:F] = 0
+                gu.svh[F + cfg.ffn:] = 0
+                dn.suh[cfg.ffn:] = 0
+            if kind == "A":
+                self.layers.append(dict(kind="A", attn_norm=norm(), qkv=lin(d, cfg.qkv_width, 1.0 / math.sqrt(d)), o=lin(HQ, d, 0.5 / math.sqrt(HQ)),
+                                        ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
+                continue
+            ip = lin(d, cfg.in_proj_width, 1.0 / math.sqrt(d), real_n=2 * DI + 2 * cfg.ssm_groups * cfg.ssm_state + H)
+            op = lin(DI, d, 0.5 / math.sqrt(DI))
+            self.layers.append(self._mamba_dict(norm(), ip, op, (0.5 * rn(C, 4)).to(torch.bfloat16), (0.1 * rn(C)).to(torch.bfloat16), ru(H, -3.0, -1.0),
+                                                -ru(H, 1.0, 16.0), 1.0 + 0.1 * rn(H), norm(DI), norm(), gu, dn))
+        self.final_norm = norm()
+        hw = exl3.Bits.of(cfg.head_bits or cfg.bits).tile_words
+        self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d), hw, real_n=cfg.vocab)
+
+    def state_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in self.conv_pool.values()) + sum(t.numel() * 4 for t in self.ssm_pool.values())
+
+    # ------------------------------------------------------------------ forward
+    def _mixer(self, li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale):
+        if L["kind"] == "A":
+            return super()._mixer(li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale)
+        cfg, K = self.cfg, self.K
+        s = self._linear(xr_d, L["in_proj"], M, cls, "in_proj")
+        proj = self.ssm_proj[:M]
+        K.finish_store(self.part, s, M, L["in_proj"], proj)
+        seg_s, seg_l, nseg = (prefill["q_start"], prefill["q_len"], prefill["nseq"]) if prefill is not None else (None, None, 0)
+        out = self.ssm_out[:M]
+        K.ssm_mixer(proj, M, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"],
+                    L["dt_bias"], L["a_neg"], L["d_skip"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, self.ssm_y, out)
+        xr_m = self.xr[:M * cfg.d_inner].view(M, cfg.d_inner)
+        K.norm_rot_in(out, None, cfg.eps, L["out_proj"].suh, xr_m)
+        return self._linear(xr_m, L["out_proj"], M, cls, "out_proj")

@@ -1,0 +1,172 @@
+// Mamba2 (SSD) token mixer for hybrid decoders: causal depthwise conv over x | B | C, discretization, fp32 state recurrence,
+// grouped gated RMSNorm.  Semantics matched: reference crates/cuda/csrc/nemotron_ssm.cu:1-45 (conv k=4 with a 3-row history,
+// dt = softplus(dt + bias), decay exp(dt * A), y = C . S + D * x, gated norm over d_inner / groups channels) and
+// crates/model/src/families/nemotron_h_omni/ssm_ref.rs.
+//
+// This engine's own layout and schedule:
+//   proj      f32 [M][ldp]: the in_proj output row, columns z (d_inner) | x (d_inner) | B (G*N) | C (G*N) | dt (H) | padding
+//   conv pool f32 [slots][3][C]      C = d_inner + 2 G N; the last three pre-conv x|B|C rows of the sequence, oldest first
+//   ssm pool  f32 [slots][H][P][N]   P = 64 (head dim), N = 128 (state); n contiguous
+// Rows of one sequence are consecutive and in position order (a "segment"); a sequence appears in at most one segment of a
+// launch.  A row at position 0 starts from a zero state whatever the pools hold, so a slot needs no reset when it is reused.
+// Every row given to these kernels is committed: a backend that runs this mixer offers no drafts to reject.
+//
+// The conv is parallel over rows (each row reads its three predecessors from the launch's own rows or from the pool); the
+// recurrence is sequential over the rows of a segment with the state of one head in the registers of a 256-thread CTA
+// (thread = one p, 32 of the 128 n), so a decode step moves each state once: 2 x 32 KB per (sequence, head).
+#include "common.cuh"
+
+namespace rx {
+
+constexpr int SSM_P = 64, SSM_N = 128, SSM_HIST = 3;
+
+__device__ __forceinline__ float ssm_silu(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ float ssm_bf(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+
+// the pre-conv value of channel c at `back` positions before row r (back 1..3), or of row r itself (back 0)
+__device__ __forceinline__ float ssm_conv_in(const float* __restrict__ proj, int ldp, int xoff, const float* pool, int C,
+                                             const int* __restrict__ row_seq, const int* __restrict__ positions, int r, int back, int c) {
+  const int pos = positions[r];
+  if (pos - back < 0) return 0.f;
+  const int seq = row_seq[r];
+  if (r - back >= 0 && row_seq[r - back] == seq) return proj[(size_t)(r - back) * ldp + xoff + c];
+  // not in this launch: the pool holds positions (first - 3, first - 2, first - 1) of the segment's first row
+  int o = 0;                                   // rows of the segment before r (only 0..2 can get here)
+  while (o < back && r - o - 1 >= 0 && row_seq[r - o - 1] == seq) ++o;
+  return pool[((size_t)seq * SSM_HIST + (SSM_HIST - back + o)) * C + c];
+}
+
+// xbc[r][c] = silu(b[c] + sum_j w[c][j] * in(pos - 3 + j)), grid (M, ceil(C / 256))
+__global__ void __launch_bounds__(256) ssm_conv_kernel(const float* __restrict__ proj, int ldp, int xoff, int C, const int* __restrict__ row_seq,
+                                                      const int* __restrict__ positions, const uint16_t* __restrict__ conv_w,
+                                                      const uint16_t* __restrict__ conv_b, const float* __restrict__ pool, float* __restrict__ xbc) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= C) return;
+  float acc = ssm_bf(conv_b[c]);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc += ssm_bf(conv_w[c * 4 + j]) * ssm_conv_in(proj, ldp, xoff, pool, C, row_seq, positions, r, 3 - j, c);
+  xbc[(size_t)r * C + c] = ssm_silu(acc);
+}
+
+// Recurrence.  grid (segments or rows, H).  With a segment table (seg_start != nullptr) block x is segment x; without one block x is
+// row x and returns unless that row opens a segment.  Block (x, 0) also writes the segment's last three pre-conv rows to the conv pool.
+__global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int xoff,
+                                                      int dtoff, int M, int H, int G, const int* __restrict__ row_seq,
+                                                      const int* __restrict__ positions, const int* __restrict__ seg_start,
+                                                      const int* __restrict__ seg_len, const float* __restrict__ dt_bias,
+                                                      const float* __restrict__ a_neg, const float* __restrict__ d_skip,
+                                                      float* __restrict__ ssm_pool, float* conv_pool, float* __restrict__ y) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sB[SSM_N], sC[SSM_N], sx[SSM_P];
+  int r0, len;
+  if (seg_start != nullptr) {
+    r0 = seg_start[blockIdx.x];
+    len = seg_len[blockIdx.x];
+  } else {
+    r0 = blockIdx.x;
+    if (r0 > 0 && row_seq[r0 - 1] == row_seq[r0]) return;
+    len = 1;
+    while (r0 + len < M && row_seq[r0 + len] == row_seq[r0]) ++len;
+  }
+  if (len <= 0) return;
+  const int h = blockIdx.y, tid = threadIdx.x, p = tid >> 2, nq = tid & 3;
+  const int seq = row_seq[r0], g = h / (H / G), DI = H * SSM_P;
+  float st[32];
+  float* sp = ssm_pool + (((size_t)seq * H + h) * SSM_P + p) * SSM_N + nq * 32;
+  if (positions[r0] == 0) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) st[i] = 0.f;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(sp + i);
+      st[i] = v.x, st[i + 1] = v.y, st[i + 2] = v.z, st[i + 3] = v.w;
+    }
+  }
+  const float A = a_neg[h], Dh = d_skip[h], dtb = dt_bias[h];
+  for (int t = 0; t < len; ++t) {
+    const int r = r0 + t;
+    const float* xr = xbc + (size_t)r * C;
+    __syncthreads();
+    if (tid < SSM_N) sB[tid] = xr[DI + g * SSM_N + tid];
+    else sC[tid - SSM_N] = xr[DI + G * SSM_N + g * SSM_N + (tid - SSM_N)];
+    if (tid < SSM_P) sx[tid] = xr[h * SSM_P + tid];
+    __syncthreads();
+    float dt = proj[(size_t)r * ldp + dtoff + h] + dtb;
+    dt = dt > 20.f ? dt : log1pf(__expf(dt));            // softplus
+    const float dA = __expf(dt * A), xdt = sx[p] * dt;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      st[i] = st[i] * dA + xdt * sB[nq * 32 + i];
+      acc += st[i] * sC[nq * 32 + i];
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (nq == 0) y[(size_t)r * DI + h * SSM_P + p] = acc + Dh * sx[p];
+  }
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
+  if (h == 0) {
+    const int last = r0 + len - 1;
+    for (int c = tid; c < C; c += 256) {
+      float v[SSM_HIST];
+#pragma unroll
+      for (int k = 0; k < SSM_HIST; ++k) v[k] = ssm_conv_in(proj, ldp, xoff, conv_pool, C, row_seq, positions, last, SSM_HIST - 1 - k, c);
+#pragma unroll
+      for (int k = 0; k < SSM_HIST; ++k) conv_pool[((size_t)seq * SSM_HIST + k) * C + c] = v[k];
+    }
+  }
+}
+
+// out[r][c] = bf16( rmsnorm_group( y * silu(z) )[c] * w[c] ), grid (M, G); the group is d_inner / G channels wide
+__global__ void __launch_bounds__(256) ssm_gate_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int ldp, int DI, int G,
+                                                           const uint16_t* __restrict__ norm_w, float eps, uint16_t* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float red[8];
+  const int r = blockIdx.x, g = blockIdx.y, W = DI / G, c0 = g * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += 256) {
+    const float v = y[(size_t)r * DI + c0 + c] * ssm_silu(proj[(size_t)r * ldp + c0 + c]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rinv = rsqrtf(tot / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += 256) {
+    const float v = y[(size_t)r * DI + c0 + c] * ssm_silu(proj[(size_t)r * ldp + c0 + c]);
+    __nv_bfloat16 b = __float2bfloat16_rn(v * rinv * ssm_bf(norm_w[c0 + c]));
+    out[(size_t)r * DI + c0 + c] = *reinterpret_cast<uint16_t*>(&b);
+  }
+}
+
+}  // namespace rx
+
+// One Mamba2 mixer between its two projections: conv, recurrence (pools updated), gated norm.  seg_start / seg_len (device, nseg
+// entries) describe the segments when the host knows them (prefill); pass nullptr and nseg = 0 to have the kernel find them.
+RX_API int rx_ssm_mixer(const void* proj, int ldp, int M, int H, int P, int G, int N, const void* row_seq, const void* positions,
+                        const void* seg_start, const void* seg_len, int nseg, const void* conv_w, const void* conv_b, const void* dt_bias,
+                        const void* a_neg, const void* d_skip, const void* norm_w, float eps, void* conv_pool, void* ssm_pool, void* xbc,
+                        void* y, void* out_bf16, void* stream) {
+  using namespace rx;
+  if (P != SSM_P || N != SSM_N || G <= 0 || H % G || M <= 0) return (int)cudaErrorInvalidValue;
+  const int DI = H * P, C = DI + 2 * G * N, xoff = DI, dtoff = DI + C;
+  if (ldp < dtoff + H) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
+         (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
+  launch(ssm_scan_kernel, dim3(seg_start ? nseg : M, H), dim3(256), 0, st, (const float*)xbc, C, (const float*)proj, ldp, xoff, dtoff, M, H, G,
+         (const int*)row_seq, (const int*)positions, (const int*)seg_start, (const int*)seg_len, (const float*)dt_bias, (const float*)a_neg,
+         (const float*)d_skip, (float*)ssm_pool, (float*)conv_pool, (float*)y);
+  launch(ssm_gate_norm_kernel, dim3(M, G), dim3(256), 0, st, (const float*)y, (const float*)proj, ldp, DI, G, (const uint16_t*)norm_w, eps,
+         (uint16_t*)out_bf16);
+  return (int)cudaGetLastError();
+}

@@ -104,6 +104,20 @@ def norm_rot_in(x: torch.Tensor, norm_w, eps: float, suh: torch.Tensor, xr: torc
     _lib.count()
 
 
+def ssm_mixer(proj: torch.Tensor, M: int, H: int, P: int, G: int, N: int, row_seq, positions, seg_start, seg_len, nseg: int, conv_w, conv_b, dt_bias,
+              a_neg, d_skip, norm_w, eps: float, conv_pool, ssm_pool, xbc, y, out) -> None:
+    """Mamba2 mixer between in_proj and out_proj: `proj` f32 [M, ldp] (z | x | B | C | dt | pad) -> `out` bf16 [M, H*P] (gated, normed);
+    the conv and state pools of the rows' sequences advance.  seg_start / seg_len: device int32 segment table or None (found on the device).
+    Three launches (conv, recurrence, gated norm)."""
+    L = _lib.load()
+    assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and out.dtype == torch.bfloat16
+    _lib.check(L.rx_ssm_mixer(proj.data_ptr(), proj.stride(0), M, H, P, G, N, row_seq.data_ptr(), positions.data_ptr(), _lib.ptr(seg_start),
+                              _lib.ptr(seg_len), nseg, conv_w.data_ptr(), conv_b.data_ptr(), dt_bias.data_ptr(), a_neg.data_ptr(), d_skip.data_ptr(),
+                              norm_w.data_ptr(), eps, conv_pool.data_ptr(), ssm_pool.data_ptr(), xbc.data_ptr(), y.data_ptr(), out.data_ptr(),
+                              _lib.stream_ptr()), "rx_ssm_mixer")
+    _lib.count(3)
+
+
 def finish_store(part, S, M, w: Exl3Weight, out: torch.Tensor) -> None:
     L = _lib.load()
     f32 = 1 if out.dtype == torch.float32 else 0

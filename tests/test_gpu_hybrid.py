@@ -1,0 +1,116 @@
+"""Hybrid (Mamba2 + attention) executor on the sm_100a kernels vs the fp32 reference, and through the engine."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _i32(x):
+    return torch.tensor(x, dtype=torch.int32, device="cuda")
+
+
+def _setup(seed=1):
+    from rexl3_b200.models import hybrid
+    cfg = hybrid.CONFIGS["test-hybrid"]
+    w = hybrid.random_weights(cfg, seed=seed)
+    return cfg, w, hybrid
+
+
+def test_chunked_prefill_and_mixed_decode_match_reference():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    cfg, w, hybrid = _setup()
+    ref = hybrid.ReferenceHybrid(w, device="cuda")
+    m = hybrid.HybridGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    assert m.k_cache[0] is None and m.k_cache[1] is not None
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, size=100).tolist()
+    other = rng.integers(0, cfg.vocab, size=2).tolist()
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[2, :2] = _i32([5, 9])
+    bt[1, :1] = _i32([2])
+    slot = lambda s, p: int(bt[s, p // 64]) * 64 + p % 64  # noqa: E731
+    want = ref.forward_seq(2, prompt, 0)
+    scale = want.abs().max().item()
+    # chunk 1: sequence 2 rows 0..69 together with sequence 1's two-token prompt (two segments in one launch)
+    c1 = 70
+    ids = prompt[:c1] + other
+    pos = list(range(c1)) + [0, 1]
+    seqs = [2] * c1 + [1] * 2
+    pf = dict(seq_ids=_i32([2, 1]), q_start=_i32([0, c1]), q_len=_i32([c1, 2]), pos0=_i32([0, 0]), nseq=2, max_qlen=c1)
+    lg = m.forward_rows(_i32(ids), _i32(pos), _i32([slot(s, p) for s, p in zip(seqs, pos)]), _i32(seqs), _i32([p + 1 for p in pos]), bt, prefill=pf,
+                        logit_rows=torch.tensor([c1 - 1, c1 + 1], device="cuda"))
+    torch.cuda.synchronize()
+    m.check()
+    w_other = ref.forward_seq(1, other, 0)
+    assert (lg[0, :cfg.vocab] - want[c1 - 1]).abs().max().item() < 0.05 * scale
+    assert (lg[1, :cfg.vocab] - w_other[1]).abs().max().item() < 0.05 * scale
+    # chunk 2: the rest of sequence 2 continues from the pools (conv history and state cross the chunk boundary)
+    T = len(prompt)
+    pos = list(range(c1, T))
+    pf = dict(seq_ids=_i32([2]), q_start=_i32([0]), q_len=_i32([T - c1]), pos0=_i32([c1]), nseq=1, max_qlen=T - c1)
+    lg = m.forward_rows(_i32(prompt[c1:]), _i32(pos), _i32([slot(2, p) for p in pos]), _i32([2] * len(pos)), _i32([p + 1 for p in pos]), bt, prefill=pf,
+                        logit_rows=torch.tensor([len(pos) - 1, 0], device="cuda"))
+    torch.cuda.synchronize()
+    m.check()
+    assert (lg[0, :cfg.vocab] - want[T - 1]).abs().max().item() < 0.05 * scale
+    assert (lg[1, :cfg.vocab] - want[c1]).abs().max().item() < 0.05 * scale
+    # decode window: sequence 1 feeds two rows (positions 2, 3), sequence 2 one row, sequence 0 starts at position 0
+    t2 = int(want[T - 1].argmax())
+    ids, pos, seqs = [11, 12, t2, 7], [2, 3, T, 0], [1, 1, 2, 0]
+    bt[0, :1] = _i32([3])
+    lg = m.forward_rows(_i32(ids), _i32(pos), _i32([slot(s, p) for s, p in zip(seqs, pos)]), _i32(seqs), _i32([p + 1 for p in pos]), bt, max_ctx=256)
+    torch.cuda.synchronize()
+    m.check()
+    w1 = ref.forward_seq(1, [11, 12], 2)
+    w2 = ref.forward_seq(2, [t2], T)
+    w0 = ref.forward_seq(0, [7], 0)
+    for row, wv in ((0, w1[0]), (1, w1[1]), (2, w2[0]), (3, w0[0])):
+        assert (lg[row, :cfg.vocab] - wv).abs().max().item() < 0.05 * scale, row
+    # the state pools hold what the reference holds
+    conv_ref, s_ref = ref.ssm[(2, 0)]
+    assert (m.ssm_pool[0][2] - s_ref).abs().max().item() < 0.03 * s_ref.abs().max().item()
+    assert (m.conv_pool[0][2] - conv_ref).abs().max().item() < 0.03 * conv_ref.abs().max().item()
+
+
+def test_engine_greedy_stream_matches_reference_with_graphs():
+    """Engine over the hybrid backend (graph replay, chunked prefill, two streams): greedy tokens follow the fp32 reference while its
+    top-2 margin is clear."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.gpu_backend import HybridGpuBackend
+    from rexl3_b200.sampling import GREEDY
+    cfg, w, hybrid = _setup(seed=4)
+    ref = hybrid.ReferenceHybrid(w, device="cuda")
+    m = hybrid.HybridGPU(w, num_pages=32, max_rows=64, max_seqs=4, max_blocks_per_seq=6, max_prefill_rows=256)
+    be = HybridGpuBackend(m, max_slots=4)
+    eng = Engine(be, None, window_rows=16, prefill_chunk=48, spec="copy")
+    assert not eng.can_rollback and eng.prefix is None
+    rng = np.random.default_rng(3)
+    prompts = {"a": rng.integers(0, cfg.vocab, size=100).tolist(), "b": rng.integers(0, cfg.vocab, size=5).tolist()}
+    n_new = 12
+    for k, p in prompts.items():
+        eng.submit(Request(k, p, n_new, GREEDY))
+    got = {k: [] for k in prompts}
+    for _ in range(300):
+        if not eng.has_work():
+            break
+        for ev in eng.step():
+            assert ev.kind != "error", ev.message
+            if ev.kind == "tokens":
+                got[ev.id].extend(ev.tokens)
+    assert be.graph_replays > 0
+    for si, (k, p) in enumerate(prompts.items()):
+        assert len(got[k]) == n_new
+        lg = ref.forward_seq(si, p, 0)[-1]
+        pos = len(p)
+        for t in got[k]:
+            top = lg.topk(2)
+            if (top.values[0] - top.values[1]).item() < 0.03 * lg.abs().max().item():
+                break                      # a near tie: either token is right, and the streams may part here
+            assert t == int(top.indices[0]), (k, pos)
+            lg = ref.forward_seq(si, [t], pos)[0]
+            pos += 1
+        assert pos - len(p) >= 3, "the comparison ended on a tie too early to mean anything"
