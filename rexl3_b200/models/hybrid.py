@@ -60,6 +60,12 @@ class HybridConfig(DenseConfig):
         if self.ssm_heads % self.ssm_groups or self.d_inner % 128:
             raise ValueError("ssm_heads must be a multiple of ssm_groups and even")
 
+    def weight_params(self) -> int:
+        ffn = 3 * self.d_model * self.ffn_padded
+        attn = self.d_model * self.qkv_width + self.n_q * self.head_dim * self.d_model
+        ssm = self.d_model * self.in_proj_width + self.d_inner * self.d_model
+        return len(self.attn_layers()) * (attn + ffn) + len(self.mamba_layers()) * (ssm + ffn) + self.vocab_padded * self.d_model
+
     def state_bytes_per_slot(self) -> int:
         return len(self.mamba_layers()) * 4 * (self.ssm_heads * self.ssm_head_dim * self.ssm_state + 3 * self.conv_channels)
 

@@ -76,15 +76,18 @@ def build(args):
     else:
         from ..models import dense
         if args.random_init:
+            from ..models import hybrid as hybrid_models
             from ..models import mla as mla_models
             from ..models import moe as _moe_models  # noqa: F401  (registers the MoE configs)
             if args.random_init in mla_models.CONFIGS:
                 cfg = mla_models.CONFIGS[args.random_init]
             elif args.random_init in dense.CONFIGS:
                 cfg = dense.CONFIGS[args.random_init]
+            elif args.random_init in hybrid_models.CONFIGS:
+                cfg = hybrid_models.CONFIGS[args.random_init]
             else:
                 raise SystemExit(f"rexl3-serve: unknown built-in config {args.random_init!r}; known: "
-                                 f"{sorted(list(dense.CONFIGS) + list(mla_models.CONFIGS))}")
+                                 f"{sorted(list(dense.CONFIGS) + list(mla_models.CONFIGS) + list(hybrid_models.CONFIGS))}")
             weights = None
         else:
             if folder is None:
@@ -134,10 +137,14 @@ def build(args):
                 from ..models import moe as moe_models
                 is_mla = isinstance(cfg, mla_models.MlaConfig)
                 is_moe = isinstance(cfg, moe_models.MoEConfig)
-                if (is_mla or is_moe) and args.kv_dtype == "fp8":
+                from ..models import hybrid as hybrid_models
+                is_hybrid = isinstance(cfg, hybrid_models.HybridConfig)
+                if (is_mla or is_moe or is_hybrid) and args.kv_dtype == "fp8":
                     raise RuntimeError("--kv-dtype fp8 is available for the dense GQA family")
                 kvb = cfg.kv_bytes_per_token() if is_mla else cfg.kv_bytes_per_token(1 if args.kv_dtype == "fp8" else 2)
                 wbytes = int(mla_models.MlaMoEGPU.weight_bytes_estimate(cfg)) if is_mla else int(cfg.weight_params() * cfg.bits / 8)
+                if is_hybrid:
+                    wbytes += cfg.state_bytes_per_slot() * args.slots      # the recurrent-state pools are resident like weights
                 mm = ModelMemory(wbytes, kvb, activation_reserve=2 << 30)
                 adm = Admission(free, 1 << 30, mm, args.slots).with_max_context(args.max_model_len).with_kv_tokens(kv_tokens)
                 adm.check(min(args.max_model_len, 1))     # fail closed: a plan that can never hold one token is refused at boot
@@ -150,14 +157,20 @@ def build(args):
                     model = mla_models.MlaMoEGPU(cfg, **common)
                 elif is_moe:
                     model = moe_models.MoEGPU(cfg, **common)
+                elif is_hybrid:
+                    model = hybrid_models.HybridGPU(cfg, **common)
                 else:
                     model = dense.DenseGPU(weights if weights is not None else cfg, kv_dtype=args.kv_dtype, **common)
                 if args.kv_dtype == "fp8":
                     import numpy as np
                     model.calibrate_kv(np.random.default_rng(0).integers(0, cfg.vocab, size=min(256, args.prefill_chunk)).tolist())
                 # the self-speculative drafter (first layers + shared head) is offered by families that define a draft depth
-                be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs,
-                                     self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
+                if is_hybrid:
+                    from ..engine.gpu_backend import HybridGpuBackend
+                    be = HybridGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs)
+                else:
+                    be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs,
+                                         self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode(), device_sampler=args.device_sampler)

@@ -75,8 +75,8 @@ def test_chunked_prefill_and_mixed_decode_match_reference():
 
 
 def test_engine_greedy_stream_matches_reference_with_graphs():
-    """Engine over the hybrid backend (graph replay, chunked prefill, two streams): greedy tokens follow the fp32 reference while its
-    top-2 margin is clear."""
+    """Engine over the hybrid backend (graph replay, chunked prefill, two streams): every greedy token is the fp32 reference's best token
+    (within the kernels' tolerance) when the reference is fed the engine's own stream."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from rexl3_b200.engine import Engine, Request
@@ -90,7 +90,7 @@ def test_engine_greedy_stream_matches_reference_with_graphs():
     assert not eng.can_rollback and eng.prefix is None
     rng = np.random.default_rng(3)
     prompts = {"a": rng.integers(0, cfg.vocab, size=100).tolist(), "b": rng.integers(0, cfg.vocab, size=5).tolist()}
-    n_new = 12
+    n_new, exact = 12, 0
     for k, p in prompts.items():
         eng.submit(Request(k, p, n_new, GREEDY))
     got = {k: [] for k in prompts}
@@ -107,10 +107,9 @@ def test_engine_greedy_stream_matches_reference_with_graphs():
         lg = ref.forward_seq(si, p, 0)[-1]
         pos = len(p)
         for t in got[k]:
-            top = lg.topk(2)
-            if (top.values[0] - top.values[1]).item() < 0.03 * lg.abs().max().item():
-                break                      # a near tie: either token is right, and the streams may part here
-            assert t == int(top.indices[0]), (k, pos)
+            # teacher-forced on the engine's own token: it must be the reference's best token up to the kernels' numeric tolerance
+            assert lg[t].item() >= lg.max().item() - 0.05 * lg.abs().max().item(), (k, pos, t, int(lg.argmax()))
+            exact += int(t == int(lg.argmax()))
             lg = ref.forward_seq(si, [t], pos)[0]
             pos += 1
-        assert pos - len(p) >= 3, "the comparison ended on a tie too early to mean anything"
+    assert exact >= n_new, "most steps have a clear winner and must agree exactly"
