@@ -25,13 +25,15 @@ from .dense import (DenseConfig, DenseGPU, HostLinear, HostWeights, ReferenceDen
 
 @dataclass
 class HybridConfig(DenseConfig):
-    pattern: str = ""            # one letter per layer: 'M' = Mamba2 mixer, 'A' = attention mixer
+    pattern: str = ""            # one letter per layer: 'M' = Mamba2 mixer, 'G' = gated delta net mixer, 'A' = attention mixer
     ssm_heads: int = 0
     ssm_head_dim: int = 64
     ssm_groups: int = 1
     ssm_state: int = 128
     conv_k: int = 4
     nope: bool = True            # attention layers without rotary embedding
+    gdn_k_heads: int = 0         # gated delta net: key heads x 128 (value head h reads key head h // (v_heads / k_heads))
+    gdn_v_heads: int = 0         # value heads x 128
 
     @property
     def d_inner(self) -> int:
@@ -46,6 +48,22 @@ class HybridConfig(DenseConfig):
         """z | x | B | C | dt, padded up to a multiple of 128 columns (the padding columns are exactly zero)."""
         return (2 * self.d_inner + 2 * self.ssm_groups * self.ssm_state + self.ssm_heads + 127) // 128 * 128
 
+    @property
+    def gdn_inner(self) -> int:
+        return self.gdn_v_heads * 128
+
+    @property
+    def gdn_conv_channels(self) -> int:
+        return (2 * self.gdn_k_heads + self.gdn_v_heads) * 128
+
+    @property
+    def gdn_proj_width(self) -> int:
+        """z | q | k | v | b | a, padded up to a multiple of 128 columns."""
+        return (self.gdn_inner + self.gdn_conv_channels + 2 * self.gdn_v_heads + 127) // 128 * 128
+
+    def gdn_layers(self):
+        return [i for i, c in enumerate(self.pattern) if c == "G"]
+
     def mamba_layers(self):
         return [i for i, c in enumerate(self.pattern) if c == "M"]
 
@@ -53,21 +71,29 @@ class HybridConfig(DenseConfig):
         return [i for i, c in enumerate(self.pattern) if c == "A"]
 
     def validate(self) -> None:
-        if len(self.pattern) != self.n_layers or set(self.pattern) - {"M", "A"}:
-            raise ValueError("pattern needs one of 'M' / 'A' per layer")
-        if self.ssm_head_dim != 64 or self.ssm_state != 128 or self.conv_k != 4:
-            raise ValueError("the Mamba2 kernels are built for head_dim 64, state 128, conv width 4")
-        if self.ssm_heads % self.ssm_groups or self.d_inner % 128:
-            raise ValueError("ssm_heads must be a multiple of ssm_groups and even")
+        if len(self.pattern) != self.n_layers or set(self.pattern) - {"M", "A", "G"}:
+            raise ValueError("pattern needs one of 'M' / 'G' / 'A' per layer")
+        if self.conv_k != 4:
+            raise ValueError("the conv kernel is built for width 4")
+        if "M" in self.pattern:
+            if self.ssm_head_dim != 64 or self.ssm_state != 128:
+                raise ValueError("the Mamba2 kernels are built for head_dim 64, state 128")
+            if self.ssm_heads <= 0 or self.ssm_heads % self.ssm_groups or self.d_inner % 128:
+                raise ValueError("ssm_heads must be a multiple of ssm_groups and even")
+        if "G" in self.pattern and (self.gdn_k_heads <= 0 or self.gdn_v_heads % self.gdn_k_heads):
+            raise ValueError("gdn_v_heads must be a positive multiple of gdn_k_heads")
 
     def weight_params(self) -> int:
         ffn = 3 * self.d_model * self.ffn_padded
         attn = self.d_model * self.qkv_width + self.n_q * self.head_dim * self.d_model
         ssm = self.d_model * self.in_proj_width + self.d_inner * self.d_model
-        return len(self.attn_layers()) * (attn + ffn) + len(self.mamba_layers()) * (ssm + ffn) + self.vocab_padded * self.d_model
+        gdn = self.d_model * self.gdn_proj_width + self.gdn_inner * self.d_model
+        return (len(self.attn_layers()) * (attn + ffn) + len(self.mamba_layers()) * (ssm + ffn) + len(self.gdn_layers()) * (gdn + ffn)
+                + self.vocab_padded * self.d_model)
 
     def state_bytes_per_slot(self) -> int:
-        return len(self.mamba_layers()) * 4 * (self.ssm_heads * self.ssm_head_dim * self.ssm_state + 3 * self.conv_channels)
+        return (len(self.mamba_layers()) * 4 * (self.ssm_heads * self.ssm_head_dim * self.ssm_state + 3 * self.conv_channels)
+                + len(self.gdn_layers()) * 4 * (self.gdn_v_heads * 128 * 128 + 3 * self.gdn_conv_channels))
 
     def kv_bytes_per_token(self, elem_bytes: int = 2) -> int:
         return 2 * self.n_kv * self.head_dim * elem_bytes * len(self.attn_layers())
@@ -77,6 +103,12 @@ CONFIGS = {
     # the reference family's block geometry (128 heads x 64, state 128, 8 groups; GQA 32q / 2kv x 128) as a dense-FFN hybrid
     "hybrid-h-56l": HybridConfig(n_layers=56, d_model=4096, n_q=32, n_kv=2, head_dim=128, ffn=14336, vocab=131072, bits=4.0, name="hybrid-h-56l",
                                  pattern="MMMMMMA" * 8, ssm_heads=128, ssm_groups=8),
+    # the reference's flagship layout (three gated-delta-net layers, then one attention layer, x16; 16 key / 48 value heads x 128) on
+    # the 27B-class dense geometry
+    "gdn-hybrid-27b": HybridConfig(n_layers=64, d_model=5120, n_q=40, n_kv=8, head_dim=128, ffn=17408, vocab=151936, rope_theta=1e6, bits=4.0,
+                                   name="gdn-hybrid-27b", pattern="GGGA" * 16, nope=False, gdn_k_heads=16, gdn_v_heads=48),
+    "test-hybrid-gdn": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid-gdn",
+                                    pattern="GAMG", nope=False, ssm_heads=16, ssm_groups=2, gdn_k_heads=2, gdn_v_heads=4),
     "test-hybrid": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid",
                                 pattern="MAMM", ssm_heads=16, ssm_groups=2),
 }
@@ -93,6 +125,21 @@ class HostMambaLayer:
     a_log: np.ndarray            # [H]; A = -exp(a_log)
     d_skip: np.ndarray           # [H]
     norm_w: np.ndarray           # [d_inner]
+    ffn_norm: np.ndarray
+    gate_up: HostLinear
+    down: HostLinear
+
+
+@dataclass
+class HostGdnLayer:
+    attn_norm: np.ndarray
+    in_proj: HostLinear          # z | q | k | v | b | a
+    out_proj: HostLinear
+    conv_w: np.ndarray           # [C, 4]
+    conv_b: np.ndarray           # [C]
+    dt_bias: np.ndarray          # [Hv]
+    a_log: np.ndarray            # [Hv]; A = -exp(a_log)
+    norm_w: np.ndarray           # [128], shared by the heads
     ffn_norm: np.ndarray
     gate_up: HostLinear
     down: HostLinear
@@ -117,6 +164,15 @@ def random_weights(cfg: HybridConfig, seed: int = 0) -> HostWeights:
             qkv = random_linear(d, cfg.qkv_width, cfg.bits, rng, cfg.codebook, s_in)
             o = random_linear(cfg.n_q * cfg.head_dim, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(cfg.n_q * cfg.head_dim))
             w.layers.append(HostLayer(nrm(d), qkv, o, nrm(d), gu, down))
+            continue
+        if kind == "G":
+            GI, GC, Hv = cfg.gdn_inner, cfg.gdn_conv_channels, cfg.gdn_v_heads
+            real = GI + GC + 2 * Hv
+            ip = random_linear(d, cfg.gdn_proj_width, cfg.bits, rng, cfg.codebook, s_in, zero_cols_from=real if real != cfg.gdn_proj_width else None)
+            op = random_linear(GI, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(GI))
+            w.layers.append(HostGdnLayer(
+                nrm(d), ip, op, _bf16_round(rng.normal(0, 0.5, size=(GC, 4))), _bf16_round(rng.normal(0, 0.1, size=GC)),
+                rng.uniform(-2.0, 0.0, size=Hv).astype(np.float32), np.log(rng.uniform(0.5, 4.0, size=Hv)).astype(np.float32), nrm(128), nrm(d), gu, down))
             continue
         real = 2 * DI + 2 * cfg.ssm_groups * cfg.ssm_state + H
         ip = random_linear(d, cfg.in_proj_width, cfg.bits, rng, cfg.codebook, s_in, zero_cols_from=real if real != cfg.in_proj_width else None)
@@ -146,6 +202,9 @@ class ReferenceHybrid(ReferenceDense):
             if isinstance(lay, HostMambaLayer):
                 L.update(kind="M", in_proj=t(lay.in_proj.dense()), o=t(lay.out_proj.dense()), conv_w=t(lay.conv_w), conv_b=t(lay.conv_b),
                          dt_bias=t(lay.dt_bias), a_neg=-torch.exp(t(lay.a_log)), d_skip=t(lay.d_skip), norm_w=t(lay.norm_w))
+            elif isinstance(lay, HostGdnLayer):
+                L.update(kind="G", in_proj=t(lay.in_proj.dense()), o=t(lay.out_proj.dense()), conv_w=t(lay.conv_w), conv_b=t(lay.conv_b),
+                         dt_bias=t(lay.dt_bias), a_neg=-torch.exp(t(lay.a_log)), norm_w=t(lay.norm_w))
             else:
                 L.update(kind="A", qkv=t(lay.qkv.dense()), o=t(lay.o.dense()))
             self.layers.append(L)
@@ -168,6 +227,8 @@ class ReferenceHybrid(ReferenceDense):
     def _mix(self, li, L, h, pos, seq, start):
         if L["kind"] == "A":
             return super()._mix(li, L, h, pos, seq, start)
+        if L["kind"] == "G":
+            return self._gdn(li, L, h, seq, start)
         cfg = self.cfg
         T, H, P, G, N, DI, C = h.shape[0], cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, cfg.d_inner, cfg.conv_channels
         proj = self._rms(h, L["attn_norm"], cfg.eps) @ L["in_proj"]
@@ -194,6 +255,35 @@ class ReferenceHybrid(ReferenceDense):
         return (g.reshape(T, DI) * L["norm_w"]) @ L["o"]
 
 
+    def _gdn(self, li, L, h, seq, start):
+        """Gated delta net, token by token (the public recurrent form: decay, delta-rule write, read, per-head gated RMSNorm)."""
+        cfg, F = self.cfg, torch.nn.functional
+        T, Hk, Hv, D, DI, C = h.shape[0], cfg.gdn_k_heads, cfg.gdn_v_heads, 128, cfg.gdn_inner, cfg.gdn_conv_channels
+        proj = self._rms(h, L["attn_norm"], cfg.eps) @ L["in_proj"]
+        z, qkv, b, a = proj[:, :DI], proj[:, DI:DI + C], proj[:, DI + C:DI + C + Hv], proj[:, DI + C + Hv:DI + C + 2 * Hv]
+        if start == 0 or (seq, li) not in self.ssm:
+            hist, S = torch.zeros(3, C, device=h.device, dtype=h.dtype), torch.zeros(Hv, D, D, device=h.device, dtype=h.dtype)
+        else:
+            hist, S = self.ssm[(seq, li)]
+        full = torch.cat([hist, qkv])
+        act = F.silu(L["conv_b"][None, :] + sum(L["conv_w"][:, j][None, :] * full[j:j + T] for j in range(4)))
+        l2 = lambda x: x * torch.rsqrt(x.pow(2).sum(-1, keepdim=True) + 1e-6)  # noqa: E731
+        q = (l2(act[:, :Hk * D].view(T, Hk, D)) / math.sqrt(D)).repeat_interleave(Hv // Hk, dim=1)
+        k = l2(act[:, Hk * D:2 * Hk * D].view(T, Hk, D)).repeat_interleave(Hv // Hk, dim=1)
+        v = act[:, 2 * Hk * D:].view(T, Hv, D)
+        decay = torch.exp(L["a_neg"][None, :] * F.softplus(a + L["dt_bias"][None, :]))
+        beta = torch.sigmoid(b)
+        o = torch.empty(T, Hv, D, device=h.device, dtype=h.dtype)
+        for t_ in range(T):                                   # S[h, j (value), i (key)]
+            S = S * decay[t_][:, None, None]
+            kv = (S * k[t_][:, None, :]).sum(-1)
+            S = S + ((v[t_] - kv) * beta[t_][:, None])[:, :, None] * k[t_][:, None, :]
+            o[t_] = (S * q[t_][:, None, :]).sum(-1)
+        self.ssm[(seq, li)] = (full[-3:].clone(), S)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.eps) * L["norm_w"][None, None, :]
+        return (o.reshape(T, DI) * F.silu(z)) @ L["o"]
+
+
 # ====================================================================================================== sm_100a executor
 class HybridGPU(DenseGPU):
     """One B200.  Attention layers run the dense executor's mixer; Mamba2 layers run `_mamba`.  A Mamba2 layer's in_proj / out_proj sit
@@ -209,6 +299,9 @@ class HybridGPU(DenseGPU):
         H, P, N, C = cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_state, cfg.conv_channels
         self.conv_pool = {li: torch.zeros(max_seqs, 3, C, dtype=torch.float32, device=device) for li in cfg.mamba_layers()}
         self.ssm_pool = {li: torch.zeros(max_seqs, H, P, N, dtype=torch.float32, device=device) for li in cfg.mamba_layers()}
+        for li in cfg.gdn_layers():
+            self.conv_pool[li] = torch.zeros(max_seqs, 3, cfg.gdn_conv_channels, dtype=torch.float32, device=device)
+            self.ssm_pool[li] = torch.zeros(max_seqs, cfg.gdn_v_heads, 128, 128, dtype=torch.float32, device=device)
 
     def _kv_layers(self):
         return self.cfg.attn_layers()
@@ -216,16 +309,23 @@ class HybridGPU(DenseGPU):
     def _gemm_shapes(self) -> dict:
         cfg = self.cfg
         s = super()._gemm_shapes()
-        s.update(in_proj=(cfg.d_model, cfg.in_proj_width), out_proj=(cfg.d_inner, cfg.d_model))
+        if "M" in cfg.pattern:
+            s.update(in_proj=(cfg.d_model, cfg.in_proj_width), out_proj=(cfg.d_inner, cfg.d_model))
+        if "G" in cfg.pattern:
+            s.update(gdn_in=(cfg.d_model, cfg.gdn_proj_width), gdn_out=(cfg.gdn_inner, cfg.d_model))
         return s
 
     def _alloc_scratch(self, R: int):
         super()._alloc_scratch(R)
         cfg, dev = self.cfg, self.device
-        self.ssm_proj = torch.empty(R, cfg.in_proj_width, dtype=torch.float32, device=dev)
-        self.ssm_xbc = torch.empty(R, cfg.conv_channels, dtype=torch.float32, device=dev)
-        self.ssm_y = torch.empty(R, cfg.d_inner, dtype=torch.float32, device=dev)
-        self.ssm_out = torch.empty(R, cfg.d_inner, dtype=torch.bfloat16, device=dev)
+        m, g = "M" in cfg.pattern, "G" in cfg.pattern
+        wp = max(cfg.in_proj_width if m else 0, cfg.gdn_proj_width if g else 0)
+        wc = max(cfg.conv_channels if m else 0, cfg.gdn_conv_channels if g else 0)
+        wi = max(cfg.d_inner if m else 0, cfg.gdn_inner if g else 0)
+        self.ssm_proj = torch.empty(R * wp, dtype=torch.float32, device=dev)       # flat: each layer kind views its own row width
+        self.ssm_xbc = torch.empty(R * wc, dtype=torch.float32, device=dev)
+        self.ssm_y = torch.empty(R * max(cfg.d_inner, 1), dtype=torch.float32, device=dev)
+        self.ssm_out = torch.empty(R * wi, dtype=torch.bfloat16, device=dev)
 
     # ------------------------------------------------------------------ weights
     def _mamba_dict(self, attn_norm, ip, op, conv_w, conv_b, dt_bias, a_neg, d_skip, norm_w, ffn_norm, gu, dn):
@@ -240,7 +340,13 @@ class HybridGPU(DenseGPU):
         self.embed = dev(w.embed, bf)
         self.layers = []
         for lay in w.layers:
-            if isinstance(lay, HostMambaLayer):
+            if isinstance(lay, HostGdnLayer):
+                ip, op = up(lay.in_proj), up(lay.out_proj)
+                self.layers.append(dict(kind="G", attn_norm=dev(lay.attn_norm, bf), qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=dev(lay.conv_w, bf),
+                                        conv_b=dev(lay.conv_b, bf), dt_bias=dev(lay.dt_bias, f32), a_neg=-torch.exp(dev(lay.a_log, f32)),
+                                        norm_w=dev(lay.norm_w, bf), ffn_norm=dev(lay.ffn_norm, bf), gate_up=up(lay.gate_up), down=up(lay.down),
+                                        q_norm=None, k_norm=None))
+            elif isinstance(lay, HostMambaLayer):
                 self.layers.append(self._mamba_dict(dev(lay.attn_norm, bf), up(lay.in_proj), up(lay.out_proj), dev(lay.conv_w, bf), dev(lay.conv_b, bf),
                                                     dev(lay.dt_bias, f32), -torch.exp(dev(lay.a_log, f32)), dev(lay.d_skip, f32), dev(lay.norm_w, bf),
                                                     dev(lay.ffn_norm, bf), up(lay.gate_up), up(lay.down)))
@@ -281,6 +387,14 @@ class HybridGPU(DenseGPU):
                 self.layers.append(dict(kind="A", attn_norm=norm(), qkv=lin(d, cfg.qkv_width, 1.0 / math.sqrt(d)), o=lin(HQ, d, 0.5 / math.sqrt(HQ)),
                                         ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
                 continue
+            if kind == "G":
+                GI, GC, Hv = cfg.gdn_inner, cfg.gdn_conv_channels, cfg.gdn_v_heads
+                ip = lin(d, cfg.gdn_proj_width, 1.0 / math.sqrt(d), real_n=GI + GC + 2 * Hv)
+                op = lin(GI, d, 0.5 / math.sqrt(GI))
+                self.layers.append(dict(kind="G", attn_norm=norm(), qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=(0.5 * rn(GC, 4)).to(torch.bfloat16),
+                                        conv_b=(0.1 * rn(GC)).to(torch.bfloat16), dt_bias=ru(Hv, -2.0, 0.0), a_neg=-ru(Hv, 0.5, 4.0), norm_w=norm(128),
+                                        ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
+                continue
             ip = lin(d, cfg.in_proj_width, 1.0 / math.sqrt(d), real_n=2 * DI + 2 * cfg.ssm_groups * cfg.ssm_state + H)
             op = lin(DI, d, 0.5 / math.sqrt(DI))
             self.layers.append(self._mamba_dict(norm(), ip, op, (0.5 * rn(C, 4)).to(torch.bfloat16), (0.1 * rn(C)).to(torch.bfloat16), ru(H, -3.0, -1.0),
@@ -297,11 +411,21 @@ class HybridGPU(DenseGPU):
         if L["kind"] == "A":
             return super()._mixer(li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale)
         cfg, K = self.cfg, self.K
-        s = self._linear(xr_d, L["in_proj"], M, cls, "in_proj")
-        proj = self.ssm_proj[:M]
-        K.finish_store(self.part, s, M, L["in_proj"], proj)
         seg_s, seg_l, nseg = (prefill["q_start"], prefill["q_len"], prefill["nseq"]) if prefill is not None else (None, None, 0)
-        out = self.ssm_out[:M]
+        if L["kind"] == "G":
+            s = self._linear(xr_d, L["in_proj"], M, cls, "gdn_in")
+            proj = self.ssm_proj[:M * cfg.gdn_proj_width].view(M, cfg.gdn_proj_width)
+            K.finish_store(self.part, s, M, L["in_proj"], proj)
+            out = self.ssm_out[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
+            K.gdn_mixer(proj, M, cfg.gdn_k_heads, cfg.gdn_v_heads, 128, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"], L["dt_bias"],
+                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, out)
+            xr_g = self.xr[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
+            K.norm_rot_in(out, None, cfg.eps, L["out_proj"].suh, xr_g)
+            return self._linear(xr_g, L["out_proj"], M, cls, "gdn_out")
+        s = self._linear(xr_d, L["in_proj"], M, cls, "in_proj")
+        proj = self.ssm_proj[:M * cfg.in_proj_width].view(M, cfg.in_proj_width)
+        K.finish_store(self.part, s, M, L["in_proj"], proj)
+        out = self.ssm_out[:M * cfg.d_inner].view(M, cfg.d_inner)
         K.ssm_mixer(proj, M, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"],
                     L["dt_bias"], L["a_neg"], L["d_skip"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, self.ssm_y, out)
         xr_m = self.xr[:M * cfg.d_inner].view(M, cfg.d_inner)

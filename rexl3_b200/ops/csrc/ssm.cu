@@ -36,6 +36,18 @@ __device__ __forceinline__ float ssm_conv_in(const float* __restrict__ proj, int
   return pool[((size_t)seq * SSM_HIST + (SSM_HIST - back + o)) * C + c];
 }
 
+// the segment's last three pre-conv rows become the sequence's conv history (called by one CTA per segment, after its recurrence)
+__device__ __forceinline__ void ssm_conv_commit(const float* __restrict__ proj, int ldp, int xoff, float* conv_pool, int C,
+                                                const int* __restrict__ row_seq, const int* __restrict__ positions, int last, int seq) {
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float v[SSM_HIST];
+#pragma unroll
+    for (int k = 0; k < SSM_HIST; ++k) v[k] = ssm_conv_in(proj, ldp, xoff, conv_pool, C, row_seq, positions, last, SSM_HIST - 1 - k, c);
+#pragma unroll
+    for (int k = 0; k < SSM_HIST; ++k) conv_pool[((size_t)seq * SSM_HIST + k) * C + c] = v[k];
+  }
+}
+
 // xbc[r][c] = silu(b[c] + sum_j w[c][j] * in(pos - 3 + j)), grid (M, ceil(C / 256))
 __global__ void __launch_bounds__(256) ssm_conv_kernel(const float* __restrict__ proj, int ldp, int xoff, int C, const int* __restrict__ row_seq,
                                                       const int* __restrict__ positions, const uint16_t* __restrict__ conv_w,
@@ -110,16 +122,7 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
   }
 #pragma unroll
   for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
-  if (h == 0) {
-    const int last = r0 + len - 1;
-    for (int c = tid; c < C; c += 256) {
-      float v[SSM_HIST];
-#pragma unroll
-      for (int k = 0; k < SSM_HIST; ++k) v[k] = ssm_conv_in(proj, ldp, xoff, conv_pool, C, row_seq, positions, last, SSM_HIST - 1 - k, c);
-#pragma unroll
-      for (int k = 0; k < SSM_HIST; ++k) conv_pool[((size_t)seq * SSM_HIST + k) * C + c] = v[k];
-    }
-  }
+  if (h == 0) ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq);
 }
 
 // out[r][c] = bf16( rmsnorm_group( y * silu(z) )[c] * w[c] ), grid (M, G); the group is d_inner / G channels wide
@@ -148,6 +151,101 @@ __global__ void __launch_bounds__(256) ssm_gate_norm_kernel(const float* __restr
   }
 }
 
+// ------------------------------------------------------------------------------------------------ gated delta net
+// Gated DeltaNet linear attention (reference crates/cuda/csrc/gdn.cu:1-25: 16 key heads x 128, 32/48/64 value heads x 128, conv
+// width 4 over q | k | v, l2-normalised q and k, q scaled by 1/sqrt(128), decay exp(g) with g = A * softplus(a + dt_bias), A < 0,
+// beta = sigmoid(b); delta rule S = S e^g; S += k (x) (beta (v - S^T k)); o = S^T q; per-head RMSNorm(o) * w * silu(z)).
+//   proj     f32 [M][ldp]: z (Hv*128) | q (Hk*128) | k (Hk*128) | v (Hv*128) | b (Hv) | a (Hv) | padding
+//   S pool   f32 [slots][Hv][128 value j][128 key i], i contiguous; conv pool as above with C = (2 Hk + Hv) * 128
+// One CTA per (segment, value head), 256 threads: thread = value column j and one half of the 128 keys (64 state values in registers);
+// the two halves meet in one shuffle.  The gated norm runs in the same kernel (the CTA holds the head's whole output row).
+constexpr int GDN_D = 128;
+
+__global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int xoff,
+                                                      int goff, int M, int Hk, int Hv, const int* __restrict__ row_seq,
+                                                      const int* __restrict__ positions, const int* __restrict__ seg_start,
+                                                      const int* __restrict__ seg_len, const float* __restrict__ dt_bias,
+                                                      const float* __restrict__ a_neg, const uint16_t* __restrict__ norm_w, float eps,
+                                                      float* __restrict__ s_pool, float* conv_pool, uint16_t* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sqk[2 * GDN_D], red[8], red2[8];
+  int r0, len;
+  if (seg_start != nullptr) {
+    r0 = seg_start[blockIdx.x];
+    len = seg_len[blockIdx.x];
+  } else {
+    r0 = blockIdx.x;
+    if (r0 > 0 && row_seq[r0 - 1] == row_seq[r0]) return;
+    len = 1;
+    while (r0 + len < M && row_seq[r0 + len] == row_seq[r0]) ++len;
+  }
+  if (len <= 0) return;
+  const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, j = tid >> 1, half = tid & 1;
+  const int seq = row_seq[r0], hk = h / (Hv / Hk), DI = Hv * GDN_D;
+  float st[64];
+  float* sp = s_pool + (((size_t)seq * Hv + h) * GDN_D + j) * GDN_D + half * 64;
+  if (positions[r0] == 0) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) st[i] = 0.f;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(sp + i);
+      st[i] = v.x, st[i + 1] = v.y, st[i + 2] = v.z, st[i + 3] = v.w;
+    }
+  }
+  const float A = a_neg[h], dtb = dt_bias[h], wj = ssm_bf(norm_w[j]);
+  const float* sq = sqk + half * 64;
+  const float* sk = sqk + GDN_D + half * 64;
+  for (int t = 0; t < len; ++t) {
+    const int r = r0 + t;
+    const float* xr = xbc + (size_t)r * C;
+    __syncthreads();
+    const float val = tid < GDN_D ? xr[hk * GDN_D + tid] : xr[(Hk + hk) * GDN_D + (tid - GDN_D)];
+    sqk[tid] = val;
+    const float ss = warp_sum(val * val);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    const float qinv = rsqrtf(red[0] + red[1] + red[2] + red[3] + 1e-6f) * 0.08838834764831845f;
+    const float kinv = rsqrtf(red[4] + red[5] + red[6] + red[7] + 1e-6f);
+    const float v = xr[2 * Hk * GDN_D + h * GDN_D + j];
+    float a = proj[(size_t)r * ldp + goff + Hv + h] + dtb;
+    a = a > 20.f ? a : log1pf(__expf(a));
+    const float decay = __expf(A * a);
+    const float beta = 1.f / (1.f + __expf(-proj[(size_t)r * ldp + goff + h]));
+    float kv = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      st[i] *= decay;
+      kv += st[i] * sk[i];
+    }
+    kv = (kv + __shfl_xor_sync(0xffffffffu, kv, 1)) * kinv;
+    const float delta = (v - kv) * beta * kinv;          // k enters the update normalised as well
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      st[i] += sk[i] * delta;
+      o += st[i] * sq[i];
+    }
+    o = (o + __shfl_xor_sync(0xffffffffu, o, 1)) * qinv;
+    const float ss2 = warp_sum(half == 0 ? o * o : 0.f);
+    if (lane == 0) red2[warp] = ss2;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red2[i];
+    if (half == 0) {
+      const float z = proj[(size_t)r * ldp + h * GDN_D + j];
+      __nv_bfloat16 b = __float2bfloat16_rn(o * rsqrtf(tot / (float)GDN_D + eps) * wj * ssm_silu(z));
+      out[(size_t)r * DI + h * GDN_D + j] = *reinterpret_cast<uint16_t*>(&b);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
+  if (h == 0) ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq);
+}
+
 }  // namespace rx
 
 // One Mamba2 mixer between its two projections: conv, recurrence (pools updated), gated norm.  seg_start / seg_len (device, nseg
@@ -168,5 +266,22 @@ RX_API int rx_ssm_mixer(const void* proj, int ldp, int M, int H, int P, int G, i
          (const float*)d_skip, (float*)ssm_pool, (float*)conv_pool, (float*)y);
   launch(ssm_gate_norm_kernel, dim3(M, G), dim3(256), 0, st, (const float*)y, (const float*)proj, ldp, DI, G, (const uint16_t*)norm_w, eps,
          (uint16_t*)out_bf16);
+  return (int)cudaGetLastError();
+}
+
+// One gated-delta-net mixer between its two projections: conv, then recurrence + gated norm (pools updated).  Two launches.
+RX_API int rx_gdn_mixer(const void* proj, int ldp, int M, int Hk, int Hv, int D, const void* row_seq, const void* positions, const void* seg_start,
+                        const void* seg_len, int nseg, const void* conv_w, const void* conv_b, const void* dt_bias, const void* a_neg,
+                        const void* norm_w, float eps, void* conv_pool, void* s_pool, void* xbc, void* out_bf16, void* stream) {
+  using namespace rx;
+  if (D != GDN_D || Hk <= 0 || Hv % Hk || M <= 0) return (int)cudaErrorInvalidValue;
+  const int DI = Hv * D, C = (2 * Hk + Hv) * D, xoff = DI, goff = DI + C;
+  if (ldp < goff + 2 * Hv) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
+         (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
+  launch(gdn_scan_kernel, dim3(seg_start ? nseg : M, Hv), dim3(256), 0, st, (const float*)xbc, C, (const float*)proj, ldp, xoff, goff, M, Hk, Hv,
+         (const int*)row_seq, (const int*)positions, (const int*)seg_start, (const int*)seg_len, (const float*)dt_bias, (const float*)a_neg,
+         (const uint16_t*)norm_w, eps, (float*)s_pool, (float*)conv_pool, (uint16_t*)out_bf16);
   return (int)cudaGetLastError();
 }

@@ -10,17 +10,18 @@ def _i32(x):
     return torch.tensor(x, dtype=torch.int32, device="cuda")
 
 
-def _setup(seed=1):
+def _setup(seed=1, name="test-hybrid"):
     from rexl3_b200.models import hybrid
-    cfg = hybrid.CONFIGS["test-hybrid"]
+    cfg = hybrid.CONFIGS[name]
     w = hybrid.random_weights(cfg, seed=seed)
     return cfg, w, hybrid
 
 
-def test_chunked_prefill_and_mixed_decode_match_reference():
+@pytest.mark.parametrize("name", ["test-hybrid", "test-hybrid-gdn"])
+def test_chunked_prefill_and_mixed_decode_match_reference(name):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
-    cfg, w, hybrid = _setup()
+    cfg, w, hybrid = _setup(name=name)
     ref = hybrid.ReferenceHybrid(w, device="cuda")
     m = hybrid.HybridGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
     assert m.k_cache[0] is None and m.k_cache[1] is not None
@@ -74,7 +75,8 @@ def test_chunked_prefill_and_mixed_decode_match_reference():
     assert (m.conv_pool[0][2] - conv_ref).abs().max().item() < 0.03 * conv_ref.abs().max().item()
 
 
-def test_engine_greedy_stream_matches_reference_with_graphs():
+@pytest.mark.parametrize("name", ["test-hybrid", "test-hybrid-gdn"])
+def test_engine_greedy_stream_matches_reference_with_graphs(name):
     """Engine over the hybrid backend (graph replay, chunked prefill, two streams): every greedy token is the fp32 reference's best token
     (within the kernels' tolerance) when the reference is fed the engine's own stream."""
     if not torch.cuda.is_available():
@@ -82,7 +84,7 @@ def test_engine_greedy_stream_matches_reference_with_graphs():
     from rexl3_b200.engine import Engine, Request
     from rexl3_b200.engine.gpu_backend import HybridGpuBackend
     from rexl3_b200.sampling import GREEDY
-    cfg, w, hybrid = _setup(seed=4)
+    cfg, w, hybrid = _setup(seed=4, name=name)
     ref = hybrid.ReferenceHybrid(w, device="cuda")
     m = hybrid.HybridGPU(w, num_pages=32, max_rows=64, max_seqs=4, max_blocks_per_seq=6, max_prefill_rows=256)
     be = HybridGpuBackend(m, max_slots=4)

@@ -2,12 +2,16 @@
 import dataclasses
 
 import numpy as np
+import pytest
 import torch
 
 from rexl3_b200.models import hybrid
 
 SMALL = dataclasses.replace(hybrid.CONFIGS["test-hybrid"], n_layers=3, pattern="MAM", d_model=256, n_q=2, n_kv=1, ffn=256, vocab=512, ssm_heads=4,
                             ssm_groups=2, name="cpu-hybrid")
+
+
+GDN = dataclasses.replace(SMALL, pattern="GAG", nope=False, gdn_k_heads=1, gdn_v_heads=2, name="cpu-gdn")
 
 
 def test_config_geometry():
@@ -19,7 +23,16 @@ def test_config_geometry():
     assert cfg.kv_bytes_per_token() == 2 * 2 * 128 * 2 * 8
 
 
-def test_chunked_equals_whole_and_position_zero_restarts():
+def test_gdn_config_geometry():
+    cfg = hybrid.CONFIGS["gdn-hybrid-27b"]
+    cfg.validate()
+    assert cfg.gdn_conv_channels == 10240 and cfg.gdn_inner == 6144 and len(cfg.gdn_layers()) == 48 and len(cfg.attn_layers()) == 16
+    assert cfg.gdn_proj_width % 128 == 0 and cfg.gdn_proj_width >= 6144 + 10240 + 96
+
+
+@pytest.mark.parametrize("cfg", [SMALL, GDN], ids=["mamba2", "gdn"])
+def test_chunked_equals_whole_and_position_zero_restarts(cfg):
+    SMALL = cfg  # noqa: N806
     w = hybrid.random_weights(SMALL, seed=2)
     ref = hybrid.ReferenceHybrid(w)
     rng = np.random.default_rng(0)
