@@ -1,6 +1,7 @@
 """``python -m rexl3_b200.quant`` - make an EXL3 pack: random-init weights of a built-in architecture (N(0, 0.02) from a seed), rotated
 and trellis-quantized with the native Viterbi encoder, written as `config.json` + `model.safetensors`.  Counterpart of the
-reference's `rexl3-quant` for the benchmark models (no calibration data is used: nearest trellis path per tile)."""
+reference's `rexl3-quant` for the benchmark models.  Default: no calibration data (nearest trellis path per tile); `--calibrate ROWS` runs the fp32 teacher
+over synthetic token sequences, accumulates every layer's input Hessian and codes with LDLQ error feedback."""
 from __future__ import annotations
 
 import argparse
@@ -19,6 +20,10 @@ def main(argv=None) -> int:
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--threads", type=int, default=0)
     p.add_argument("--layers", type=int, default=0, help="quantize only the first N layers (smoke runs)")
+    p.add_argument("--calibrate", type=int, default=0, metavar="ROWS",
+                   help="calibration rows: run the fp32 teacher over ROWS synthetic tokens (sequences of --calibrate-cols) and code with LDLQ")
+    p.add_argument("--calibrate-cols", type=int, default=256)
+    p.add_argument("--damp", type=float, default=0.01)
     p.add_argument("--device", default="cpu", help="cpu (host Viterbi, all cores) or cuda (one CTA per tile; same bits)")
     a = p.parse_args(argv)
     cfg = dense.CONFIGS[a.arch]
@@ -27,8 +32,18 @@ def main(argv=None) -> int:
     if a.layers:
         cfg = dataclasses.replace(cfg, n_layers=a.layers)
     t0 = time.time()
-    w = quantize.quantize_dense(cfg, quantize.random_fp_weights(cfg, a.seed), seed=a.seed, threads=a.threads, device=a.device)
-    quantize.write_pack(a.out, w)
+    fp = quantize.random_fp_weights(cfg, a.seed)
+    hessians, extra = None, None
+    if a.calibrate:
+        import numpy as np
+        from . import teacher
+        rng = np.random.default_rng(a.seed + 1)
+        cols = max(1, min(a.calibrate_cols, a.calibrate))
+        seqs = [rng.integers(0, cfg.vocab, size=cols).tolist() for _ in range(max(1, a.calibrate // cols))]
+        hessians = teacher.capture_hessians(cfg, fp, seqs, device="cuda" if a.device != "cpu" else "cpu")
+        extra = {"calibration": {"rows": len(seqs), "cols": cols, "data": "synthetic uniform tokens", "damp": a.damp}}
+    w = quantize.quantize_dense(cfg, fp, seed=a.seed, threads=a.threads, device=a.device, hessians=hessians, damp=a.damp)
+    quantize.write_pack(a.out, w, extra)
     print(f"rexl3-quant: wrote {a.out} ({cfg.name}, {cfg.bits:g} bpw, {cfg.n_layers} layers) in {time.time() - t0:.1f} s")
     return 0
 

@@ -1,10 +1,10 @@
 """EXL3 quantizer: sign flips + 128-block Hadamard rotation on both sides, global scale, trellis (Viterbi) coding, and
 the pack writer / loader.
 
-Stages (behaviour parity with the reference's quantizer outline, crates/quant/src/lib.rs:1-30, without the Hessian /
-LDLQ error feedback, which random-init benchmark weights do not need): W~ = H_K (su * W * sv) H_N / scale is coded tile by
-tile to the nearest trellis path, so that suh * (H W_q H) * svh reproduces W.  A pure "nearest trellis path" quantizer
-writes valid EXL3.
+Stages (behaviour parity with the reference's quantizer outline, crates/quant/src/lib.rs:1-30): W~ = H_K (su * W * sv) H_N / scale
+is coded tile by tile to the nearest trellis path, so that suh * (H W_q H) * svh reproduces W.  Without calibration data that is all
+(a pure "nearest trellis path" quantizer writes valid EXL3, and random-init benchmark weights need no more); with a Hessian per layer
+(`teacher.capture_hessians`) the 16-row tile blocks are coded with LDL error feedback and the scale is refit (`ldlq.py`).
 """
 from __future__ import annotations
 
@@ -34,9 +34,14 @@ def to_stream_tiles(w: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(t[:, :, r, c]).reshape(-1, 256)
 
 
-def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: int = 0, bias=None, threads: int = 0, device: str = "cpu") -> HostLinear:
+def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: int = 0, bias=None, threads: int = 0, device: str = "cpu",
+                    hessian: np.ndarray | None = None, damp: float = 0.01, refit: bool | None = None) -> HostLinear:
     """w: float [K, N] with y = x @ w.  K and N must be multiples of 128 (pad first).  `device="cuda"` runs the trellis search on the GPU
-    (the CUDA encoder emits the same bits as the host one)."""
+    (the CUDA encoder emits the same bits as the host one).
+
+    `hessian` [K, K] (second moment of the layer's inputs, e.g. from `teacher.capture_hessians`): the 16-row tile blocks are coded last to
+    first with LDL error feedback (LDLQ) instead of independently, and the output scale is refit against the Hessian-weighted error
+    (`refit`, default: on with a Hessian, off without)."""
     w = np.asarray(w, dtype=np.float64)
     k, n = w.shape
     if k % 128 or n % 128:
@@ -50,14 +55,31 @@ def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: i
     rot = exl3.rotate(exl3.rotate((w * su[:, None] * sv[None, :]).T.copy()).T.copy())     # H_K (.) H_N, H symmetric and orthonormal
     std = float(rot.std())
     scale = std / _cb_std(codebook) if std > 0 else 1.0
-    tiles = to_stream_tiles(rot / scale)
-    if device == "cpu":
-        packed, err = encode_tiles(tiles, b, codebook, threads)
-    else:
+
+    def encode(tiles):
+        if device == "cpu":
+            return encode_tiles(tiles, b, codebook, threads)[0]
         from .trellis import encode_tiles_cuda
-        out, _err = encode_tiles_cuda(tiles, b, codebook, device=device)
-        packed = out.cpu().numpy()
-    trellis = packed.reshape(k // 16, n // 16, b.tile_words)
+        return encode_tiles_cuda(tiles, b, codebook, device=device)[0].cpu().numpy()
+
+    if hessian is None:
+        trellis = encode(to_stream_tiles(rot / scale)).reshape(k // 16, n // 16, b.tile_words)
+        hr = None
+    else:
+        from . import ldlq
+        if hessian.shape != (k, k):
+            raise ValueError(f"hessian is {hessian.shape}, the layer has {k} inputs")
+        hr = ldlq.rotate_hessian(ldlq.finalize_hessian(hessian, damp), su)
+        trellis = np.zeros((k // 16, n // 16, b.tile_words), dtype=np.int16)
+
+        def code_block(bi, target):
+            trellis[bi] = encode(to_stream_tiles(target)).reshape(n // 16, b.tile_words)
+            return exl3.unpack(trellis[bi:bi + 1], codebook).view(np.float16).astype(np.float64)
+
+        ldlq.ldlq(rot / scale, hr, code_block)
+    if refit if refit is not None else hessian is not None:
+        from . import ldlq
+        scale *= ldlq.refit_scale(rot / scale, exl3.unpack(trellis, codebook).view(np.float16).astype(np.float64), hr)
     suh = su.astype(np.float16)
     svh = (sv * scale).astype(np.float16)
     return HostLinear(trellis, suh, svh, None if bias is None else np.asarray(bias, dtype=np.float32), codebook)
@@ -69,22 +91,25 @@ def pad_to(w: np.ndarray, k: int, n: int) -> np.ndarray:
     return out
 
 
-def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0, device: str = "cpu") -> HostWeights:
+def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0, device: str = "cpu", hessians: dict | None = None,
+                   damp: float = 0.01) -> HostWeights:
     """fp: float weights of a dense GQA decoder, [in, out] matrices: embed [V, d], final_norm [d], lm_head [d, V] and per layer
-    attn_norm, q, k, v, o, ffn_norm, gate, up, down (optionally q_norm, k_norm)."""
+    attn_norm, q, k, v, o, ffn_norm, gate, up, down (optionally q_norm, k_norm).  `hessians` (from `teacher.capture_hessians`): layers
+    found there are coded with LDLQ error feedback, the others tile by tile."""
     d, F, V = cfg.d_model, cfg.ffn_padded, cfg.vocab_padded
+    hs = hessians or {}
+    ql = lambda m, bits, sd, key: quantize_linear(m, bits, cfg.codebook, sd, threads=threads, device=device, hessian=hs.get(key), damp=damp)  # noqa: E731
     w = HostWeights(cfg, np.asarray(fp["embed"], dtype=np.float32))
     for i, L in enumerate(fp["layers"]):
         qkv = np.concatenate([L["q"], L["k"], L["v"]], axis=1)
         gu = np.concatenate([pad_to(L["gate"], d, F), pad_to(L["up"], d, F)], axis=1)
-        lay = HostLayer(np.asarray(L["attn_norm"], np.float32), quantize_linear(qkv, cfg.bits, cfg.codebook, seed + 10 * i + 1, threads=threads, device=device),
-                        quantize_linear(L["o"], cfg.bits, cfg.codebook, seed + 10 * i + 2, threads=threads, device=device), np.asarray(L["ffn_norm"], np.float32),
-                        quantize_linear(gu, cfg.bits, cfg.codebook, seed + 10 * i + 3, threads=threads, device=device),
-                        quantize_linear(pad_to(L["down"], F, d), cfg.bits, cfg.codebook, seed + 10 * i + 4, threads=threads, device=device),
+        lay = HostLayer(np.asarray(L["attn_norm"], np.float32), ql(qkv, cfg.bits, seed + 10 * i + 1, (i, "qkv")),
+                        ql(L["o"], cfg.bits, seed + 10 * i + 2, (i, "o")), np.asarray(L["ffn_norm"], np.float32),
+                        ql(gu, cfg.bits, seed + 10 * i + 3, (i, "gate_up")), ql(pad_to(L["down"], F, d), cfg.bits, seed + 10 * i + 4, (i, "down")),
                         None if "q_norm" not in L else np.asarray(L["q_norm"], np.float32), None if "k_norm" not in L else np.asarray(L["k_norm"], np.float32))
         w.layers.append(lay)
     w.final_norm = np.asarray(fp["final_norm"], np.float32)
-    w.lm_head = quantize_linear(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, cfg.codebook, seed + 7777, threads=threads, device=device)
+    w.lm_head = ql(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, seed + 7777, ("lm_head",))
     return w
 
 
@@ -147,7 +172,10 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
             "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps, "rope_theta": cfg.rope_theta, "qk_norm": cfg.qk_norm, "name": cfg.name,
             "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": cfg.bits, "head_bits": cfg.head_bits or cfg.bits,
                                     "codebook": cfg.codebook, "fused_projections": True}}
-    conf.update(extra_config or {})
+    extra = dict(extra_config or {})
+    if "calibration" in extra:                    # what the pack was calibrated on belongs to the quantization record
+        conf["quantization_config"]["calibration"] = extra.pop("calibration")
+    conf.update(extra)
     json.dump(conf, open(os.path.join(folder, "config.json"), "w"), indent=1)
     json.dump({"eos_token_id": conf.get("eos_token_id", cfg.vocab - 1)}, open(os.path.join(folder, "generation_config.json"), "w"))
 

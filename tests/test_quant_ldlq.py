@@ -1,0 +1,113 @@
+"""Hessian-aware rounding: block LDL, the LDLQ feedback loop and its effect on the layer's output error."""
+import numpy as np
+
+from rexl3_b200.format import exl3
+from rexl3_b200.quant import ldlq, quantize
+
+
+def _correlated_inputs(rng, rows, k, rank=24):
+    base = rng.normal(size=(rows, rank)) @ rng.normal(size=(rank, k))
+    return base + 0.3 * rng.normal(size=(rows, k))
+
+
+def test_block_ldl_reconstructs_and_has_identity_blocks():
+    rng = np.random.default_rng(0)
+    x = _correlated_inputs(rng, 400, 128)
+    h = ldlq.finalize_hessian(x.T @ x / 400)
+    L, d = ldlq.block_ldl(h)
+    assert np.allclose(L @ d @ L.T, h, rtol=1e-9, atol=1e-9 * np.abs(h).max())
+    for b in range(0, 128, 16):
+        assert np.allclose(L[b:b + 16, b:b + 16], np.eye(16), atol=1e-9)
+        assert np.allclose(L[b:b + 16, b + 16:], 0) and np.allclose(d[b:b + 16, b + 16:], 0)
+
+
+def test_finalize_handles_dead_inputs_and_rotation_matches_moment_of_rotated_inputs():
+    rng = np.random.default_rng(1)
+    x = _correlated_inputs(rng, 300, 128)
+    x[:, 5] = 0
+    h = ldlq.finalize_hessian(x.T @ x / 300, damp=0.0)
+    assert h[5, 5] == 1.0 and np.all(h[5, :5] == 0)
+    su = np.where(rng.random(128) < 0.5, -1.0, 1.0)
+    xr = exl3.rotate(x * su)
+    want = xr.T @ xr / 300
+    got = ldlq.rotate_hessian(x.T @ x / 300, su)
+    assert np.allclose(got, want, rtol=1e-9, atol=1e-9 * np.abs(want).max())
+
+
+def test_ldlq_lowers_the_output_error_on_correlated_inputs():
+    rng = np.random.default_rng(2)
+    k, n = 256, 128
+    w = rng.normal(0, 0.02, size=(k, n))
+    x = _correlated_inputs(rng, 2048, k)
+    h = x.T @ x / x.shape[0]
+    plain = quantize.quantize_linear(w, 2.0, seed=3)
+    aware = quantize.quantize_linear(w, 2.0, seed=3, hessian=h)
+    assert plain.trellis.shape == aware.trellis.shape and not np.array_equal(plain.trellis, aware.trellis)
+    y = x @ w
+    e_plain = np.linalg.norm(x @ plain.dense() - y) / np.linalg.norm(y)
+    e_aware = np.linalg.norm(x @ aware.dense() - y) / np.linalg.norm(y)
+    assert e_aware < 0.8 * e_plain, (e_plain, e_aware)
+    # the proxy the loop minimises says the same
+    hf = ldlq.finalize_hessian(h, 0.0)
+    assert ldlq.proxy_error(w, aware.dense(), hf) < ldlq.proxy_error(w, plain.dense(), hf)
+
+
+def test_scale_refit_never_hurts_the_plain_quantizer():
+    rng = np.random.default_rng(4)
+    w = rng.normal(0, 0.02, size=(128, 128))
+    a = quantize.quantize_linear(w, 2.0, seed=1)
+    b = quantize.quantize_linear(w, 2.0, seed=1, refit=True)
+    assert np.array_equal(a.trellis, b.trellis)
+    assert np.linalg.norm(b.dense() - w) <= np.linalg.norm(a.dense() - w) * (1 + 1e-3)
+
+
+def test_teacher_capture_and_calibrated_model_is_closer_to_the_teacher(tmp_path):
+    import dataclasses
+    import json
+
+    import torch
+
+    from rexl3_b200.models import dense
+    from rexl3_b200.quant import teacher
+    cfg = dataclasses.replace(dense.CONFIGS["tiny-llama"], n_layers=1, bits=2.0, vocab=512, ffn=256)
+    fp = quantize.random_fp_weights(cfg, seed=5, std=0.05)
+    rng = np.random.default_rng(6)
+    # a skewed token distribution makes the layer inputs correlated, as real text does
+    probs = rng.dirichlet(np.full(cfg.vocab, 0.05))
+    seqs = [rng.choice(cfg.vocab, size=96, p=probs).tolist() for _ in range(6)]
+    hs = teacher.capture_hessians(cfg, fp, seqs)
+    assert set(hs) == {(0, "qkv"), (0, "o"), (0, "gate_up"), (0, "down"), ("lm_head",)}
+    assert hs[(0, "down")].shape == (cfg.ffn_padded, cfg.ffn_padded) and np.allclose(hs[(0, "qkv")], hs[(0, "qkv")].T)
+    plain = quantize.quantize_dense(cfg, fp, seed=1)
+    aware = quantize.quantize_dense(cfg, fp, seed=1, hessians=hs)
+    # the teacher's logits on held-out sequences of the same distribution
+    test_seqs = [rng.choice(cfg.vocab, size=64, p=probs).tolist() for _ in range(3)]
+
+    def fp_logits(seq):
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))  # noqa: E731
+        hw = dense.HostWeights(cfg, fp["embed"])
+        ref = dense.ReferenceDense.__new__(dense.ReferenceDense)
+        ref.cfg, ref.device, ref.dtype, ref.kv = cfg, "cpu", torch.float32, {}
+        ref.embed = t(fp["embed"])
+        F = cfg.ffn_padded
+        ref.layers = [dict(attn_norm=t(L["attn_norm"]), qkv=t(np.concatenate([L["q"], L["k"], L["v"]], axis=1)), o=t(L["o"]), ffn_norm=t(L["ffn_norm"]),
+                           gate_up=t(np.concatenate([quantize.pad_to(L["gate"], cfg.d_model, F), quantize.pad_to(L["up"], cfg.d_model, F)], axis=1)),
+                           down=t(quantize.pad_to(L["down"], F, cfg.d_model)), q_norm=None, k_norm=None) for L in fp["layers"]]
+        ref.final_norm, ref.lm_head = t(fp["final_norm"]), t(fp["lm_head"])
+        ref.inv_freq = torch.from_numpy(dense.rope_inv_freq(cfg))
+        del hw
+        return ref.forward_seq(0, seq, 0)
+
+    def err(w):
+        ref = dense.ReferenceDense(w)
+        tot = 0.0
+        for i, s in enumerate(test_seqs):
+            want = fp_logits(s)
+            tot += float((ref.forward_seq(i, s, 0) - want).pow(2).sum() / want.pow(2).sum())
+        return tot / len(test_seqs)
+
+    e_plain, e_aware = err(plain), err(aware)
+    assert e_aware < e_plain, (e_plain, e_aware)
+    quantize.write_pack(str(tmp_path / "p"), aware, {"calibration": {"rows": 6, "cols": 96}})
+    conf = json.load(open(tmp_path / "p" / "config.json"))
+    assert conf["quantization_config"]["calibration"] == {"rows": 6, "cols": 96}
