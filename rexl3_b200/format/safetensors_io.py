@@ -129,8 +129,47 @@ def read_header(path: str) -> HeaderScan:
     return out
 
 
+_PREFETCHED = {}   # (absolute file path, file offset, nbytes) -> uint8 view of a staging buffer filled by `prefetch`
+
+
+def prefetch(folder: str, entries, threads: int = 8, direct: bool = False, pinned: bool = False) -> int:
+    """Read all `entries` (of any number of files) with the native parallel range reader into one staging buffer per file; later
+    `read_tensor` calls for them are served from it (each once).  `pinned`: page-locked staging (host->device copies from the returned
+    arrays can then be asynchronous).  Returns the bytes read."""
+    from ..native import host
+    by_file = {}
+    for e in entries:
+        by_file.setdefault(e.file, []).append(e)
+    total = 0
+    for fname, es in by_file.items():
+        path = os.path.abspath(os.path.join(folder, fname))
+        sizes = [e.nbytes for e in es]
+        offs = [e.file_offset for e in es]
+        starts, pos = [], 0
+        for n in sizes:
+            starts.append(pos)
+            pos += (n + 63) // 64 * 64          # every tensor starts 64-byte aligned in the staging buffer
+        if pinned:
+            import torch
+            stage = torch.empty(max(pos, 1), dtype=torch.uint8).pin_memory().numpy()
+        else:
+            stage = np.empty(max(pos, 1), dtype=np.uint8)
+        host.read_ranges(path, offs, sizes, stage, starts, threads=threads, direct=direct)
+        for e, st, n in zip(es, starts, sizes):
+            _PREFETCHED[(path, e.file_offset, n)] = stage[st:st + n]
+        total += sum(sizes)
+    return total
+
+
+def drop_prefetched() -> None:
+    _PREFETCHED.clear()
+
+
 def read_tensor(folder: str, e: Entry) -> np.ndarray:
     """Read one tensor's bytes as numpy (BF16 / F8 come back as raw uint16 / uint8)."""
+    hit = _PREFETCHED.pop((os.path.abspath(os.path.join(folder, e.file)), e.file_offset, e.nbytes), None)
+    if hit is not None:
+        return hit.view(_NP[e.dtype]).reshape(e.shape)
     with open(os.path.join(folder, e.file), "rb") as f:
         f.seek(e.file_offset)
         raw = f.read(e.nbytes)

@@ -80,8 +80,9 @@ class HostLinear:
     codebook: str = "3inst"
 
     def dense(self) -> np.ndarray:
-        """Effective [K, N] float32 weight."""
-        return exl3.decode_weight(self.trellis, self.codebook, self.suh.astype(np.float64), self.svh.astype(np.float64)).astype(np.float32)
+        """Effective [K, N] float32 weight (native multi-threaded decoder; `exl3.decode_weight` is its numpy oracle)."""
+        from ..native import host
+        return host.decode_weight(self.trellis, self.codebook, self.suh.astype(np.float64), self.svh.astype(np.float64)).astype(np.float32)
 
 
 @dataclass

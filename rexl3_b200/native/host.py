@@ -1,0 +1,89 @@
+"""ctypes bindings of the host-side native library (``librexl3_host.so``): the EXL3 codec twin of `rexl3_b200.format.exl3`
+(states / unpack / effective weight, multi-threaded) and the parallel file-range reader used when a pack is loaded."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+from ..format import exl3
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        from . import build as nb
+        path = nb.build()                 # rebuilds only when a source is newer than the library
+        L = ctypes.CDLL(path)
+        c_int, c_void = ctypes.c_int, ctypes.c_void_p
+        L.rx_exl3_states_host.restype = c_int
+        L.rx_exl3_states_host.argtypes = [c_void, c_int, c_int, c_int, c_void, c_int]
+        L.rx_exl3_unpack_host.restype = c_int
+        L.rx_exl3_unpack_host.argtypes = [c_void, c_int, c_int, c_int, c_void, c_void, c_int]
+        L.rx_exl3_decode_weight_host.restype = c_int
+        L.rx_exl3_decode_weight_host.argtypes = [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int]
+        L.rx_read_ranges.restype = c_int
+        L.rx_read_ranges.argtypes = [ctypes.c_char_p, c_int, c_void, c_void, c_void, c_int, c_int, ctypes.POINTER(c_int)]
+        _lib = L
+    return _lib
+
+
+def _trellis(trellis):
+    t = np.ascontiguousarray(trellis, dtype=np.int16)
+    if t.ndim != 3:
+        raise ValueError("trellis is int16 [K/16, N/16, 16*bits]")
+    return t, exl3.Bits.from_trellis_last(t.shape[2])
+
+
+def states(trellis, threads: int = 0) -> np.ndarray:
+    t, b = _trellis(trellis)
+    out = np.empty(t.shape[:2] + (256,), dtype=np.uint16)
+    if lib().rx_exl3_states_host(t.ctypes.data, t.shape[0], t.shape[1], b.twice, out.ctypes.data, threads) != 0:
+        raise ValueError("native codec refused its arguments")
+    return out
+
+
+def unpack(trellis, codebook: str = "3inst", threads: int = 0) -> np.ndarray:
+    """W_q as fp16 bit patterns, uint16 [K, N] (the twin of `exl3.unpack`)."""
+    t, b = _trellis(trellis)
+    table = np.ascontiguousarray(exl3.codebook(codebook))
+    out = np.empty((t.shape[0] * 16, t.shape[1] * 16), dtype=np.uint16)
+    if lib().rx_exl3_unpack_host(t.ctypes.data, t.shape[0], t.shape[1], b.twice, table.ctypes.data, out.ctypes.data, threads) != 0:
+        raise ValueError("native codec refused its arguments")
+    return out
+
+
+def decode_weight(trellis, codebook: str = "3inst", suh=None, svh=None, threads: int = 0) -> np.ndarray:
+    """Effective dense float64 weight [K, N] (the twin of `exl3.decode_weight`; equal to rounding, butterflies instead of matrix products)."""
+    t, b = _trellis(trellis)
+    table = np.ascontiguousarray(exl3.codebook(codebook))
+    su = None if suh is None else np.ascontiguousarray(suh, dtype=np.float64)
+    sv = None if svh is None else np.ascontiguousarray(svh, dtype=np.float64)
+    out = np.empty((t.shape[0] * 16, t.shape[1] * 16), dtype=np.float64)
+    rc = lib().rx_exl3_decode_weight_host(t.ctypes.data, t.shape[0], t.shape[1], b.twice, table.ctypes.data, None if su is None else su.ctypes.data,
+                                          None if sv is None else sv.ctypes.data, out.ctypes.data, threads)
+    if rc != 0:
+        raise ValueError("native codec refused its arguments (K and N must be multiples of 128)")
+    return out
+
+
+def read_ranges(path: str, offsets, sizes, dst: np.ndarray, dst_offsets, threads: int = 8, direct: bool = False) -> bool:
+    """Fill `dst` (a writable uint8 array, e.g. over pinned memory) at `dst_offsets` with the file ranges.  Returns whether O_DIRECT was used
+    (a file system that refuses it falls back to buffered reads).  Raises OSError on any failure."""
+    n = len(offsets)
+    offs = np.ascontiguousarray(offsets, dtype=np.int64)
+    szs = np.ascontiguousarray(sizes, dtype=np.int64)
+    dofs = np.ascontiguousarray(dst_offsets, dtype=np.int64)
+    if dst.dtype != np.uint8 or not dst.flags.c_contiguous or not dst.flags.writeable:
+        raise ValueError("dst is a writable contiguous uint8 array")
+    if n and int((dofs + szs).max()) > dst.nbytes:
+        raise ValueError("a range does not fit the destination")
+    ptrs = (dst.ctypes.data + dofs).astype(np.uint64)
+    used = ctypes.c_int(0)
+    rc = lib().rx_read_ranges(os.fsencode(path), n, offs.ctypes.data, szs.ctypes.data, ptrs.ctypes.data, threads, 1 if direct else 0, ctypes.byref(used))
+    if rc != 0:
+        raise OSError(rc, f"{os.strerror(rc)}: {path}")
+    return bool(used.value)

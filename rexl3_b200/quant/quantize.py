@@ -191,8 +191,9 @@ def config_from_pack(folder: str) -> DenseConfig:
                        bits=float(q.get("bits", 4.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "dense"))
 
 
-def load_pack(folder: str) -> HostWeights:
-    """Scan (headers only), refuse bad groups by name, then read the tensors."""
+def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeights:
+    """Scan (headers only), refuse bad groups by name, then read the tensors: all of them in one pass of the native parallel range
+    reader (`threads` readers, optionally O_DIRECT), from which the per-tensor reads below are served."""
     cfg = config_from_pack(folder)
     ck = checkpoint.scan(folder)
     if ck.bad:
@@ -200,6 +201,8 @@ def load_pack(folder: str) -> HostWeights:
         raise ValueError(f"pack refused: {name}: {why}")
     if ck.issues:
         raise ValueError(f"pack refused: {ck.issues[0]}")
+    if threads > 0:
+        safetensors_io.prefetch(folder, [e for g in ck.groups.values() for e in g.parts.values()] + list(ck.plain.values()), threads=threads, direct=direct)
 
     def lin(prefix):
         g = ck.groups.get(prefix)
@@ -234,4 +237,5 @@ def load_pack(folder: str) -> HostWeights:
         w.layers.append(lay)
     w.final_norm = plain("model.norm.weight")
     w.lm_head = lin("lm_head")
+    safetensors_io.drop_prefetched()          # tensors the model did not ask for
     return w
