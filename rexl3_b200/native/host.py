@@ -27,6 +27,12 @@ def lib():
         L.rx_exl3_decode_weight_host.argtypes = [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int]
         L.rx_read_ranges.restype = c_int
         L.rx_read_ranges.argtypes = [ctypes.c_char_p, c_int, c_void, c_void, c_void, c_int, c_int, ctypes.POINTER(c_int)]
+        L.rx_bpe_new.restype = c_void
+        L.rx_bpe_new.argtypes = [c_void, c_void, c_int]
+        L.rx_bpe_free.restype = None
+        L.rx_bpe_free.argtypes = [c_void]
+        L.rx_bpe_encode.restype = ctypes.c_int64
+        L.rx_bpe_encode.argtypes = [c_void, c_void, c_void, c_int, c_void, ctypes.c_int64]
         _lib = L
     return _lib
 
@@ -87,3 +93,35 @@ def read_ranges(path: str, offsets, sizes, dst: np.ndarray, dst_offsets, threads
     if rc != 0:
         raise OSError(rc, f"{os.strerror(rc)}: {path}")
     return bool(used.value)
+
+
+class BpeCore:
+    """Ranked byte-level BPE merges on token ids (`native/csrc/bpe.cpp`).  byte_ids: the token id of each of the 256 bytes (-1: none);
+    merges: (left id, right id, merged id) triples in rank order."""
+
+    def __init__(self, byte_ids, merges):
+        self._b = np.ascontiguousarray(byte_ids, dtype=np.int32)
+        m = np.ascontiguousarray(merges, dtype=np.int32).reshape(-1, 3)
+        if self._b.shape != (256,):
+            raise ValueError("byte_ids has 256 entries")
+        self._h = lib().rx_bpe_new(self._b.ctypes.data, m.ctypes.data, m.shape[0])
+        self._free = lib().rx_bpe_free
+
+    def encode_pieces(self, pieces) -> list:
+        """pieces: iterable of bytes objects (the pre-tokenizer's output) -> token ids of their concatenation."""
+        pieces = list(pieces)
+        if not pieces:
+            return []
+        offs = np.zeros(len(pieces) + 1, dtype=np.int64)
+        np.cumsum([len(p) for p in pieces], out=offs[1:])
+        buf = np.frombuffer(b"".join(pieces), dtype=np.uint8)
+        out = np.empty(max(int(offs[-1]), 1), dtype=np.int32)       # a piece never yields more tokens than it has bytes
+        n = lib().rx_bpe_encode(self._h, buf.ctypes.data if buf.size else None, offs.ctypes.data, len(pieces), out.ctypes.data, out.size)
+        if n < 0 or n > out.size:
+            raise ValueError("native BPE refused its arguments")
+        return out[:n].tolist()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._free(h)

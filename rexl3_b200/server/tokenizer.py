@@ -150,6 +150,22 @@ class BpeTokenizer(Tok):
         self.u2b = {c: b for b, c in self.b2u.items()}
         self.eos_ids, self.bos_id = tuple(eos_ids), bos_id
         self._cache = {}
+        self._native = self._make_native()
+
+    def _make_native(self):
+        """The merge loop in the host library, when every merge maps onto token ids (else the Python loop below runs)."""
+        try:
+            from ..native import host
+            byte_ids = [self.vocab.get(self.b2u[b], -1) for b in range(256)]
+            triples = []
+            for (a, b), _r in sorted(self.ranks.items(), key=lambda kv: kv[1]):
+                ia, ib, im = self.vocab.get(a), self.vocab.get(b), self.vocab.get(a + b)
+                if ia is None or ib is None or im is None:
+                    return None          # a merge whose pieces are not all tokens: the string-level loop handles such a file
+                triples.append((ia, ib, im))
+            return host.BpeCore(byte_ids, triples)
+        except (OSError, RuntimeError):
+            return None
 
     @staticmethod
     def _split_pattern(pre):
@@ -199,6 +215,8 @@ class BpeTokenizer(Tok):
         return ids
 
     def _encode_plain(self, text: str) -> list:
+        if self._native is not None:
+            return self._native.encode_pieces(m.group(0).encode("utf-8") for m in self.pattern.finditer(text))
         out = []
         for m in self.pattern.finditer(text):
             out.extend(self._bpe("".join(self.b2u[b] for b in m.group(0).encode("utf-8"))))

@@ -75,3 +75,27 @@ def test_pack_loads_through_the_prefetcher(tmp_path):
         assert np.array_equal(la.attn_norm, lb.attn_norm)
     assert np.array_equal(a.embed, b.embed) and np.array_equal(a.lm_head.trellis, b.lm_head.trellis)
     assert os.path.exists(os.path.join(folder, "model.safetensors"))
+
+
+def test_native_bpe_equals_the_python_merge_loop():
+    from rexl3_b200.server import tokenizer
+    b2u = tokenizer.bytes_to_unicode()
+    vocab = {b2u[b]: b for b in range(256)}
+    merges = []
+    def add(a, b):
+        merges.append(f"{a} {b}")
+        vocab.setdefault(a + b, len(vocab))
+    sp = b2u[ord(" ")]
+    for a, b in [("t", "h"), ("th", "e"), (sp, "the"), ("a", "a"), ("aa", "a"), ("aa", "aa"), ("i", "n"), ("in", "g"), (sp, "a"), ("e", "r"), ("1", "2")]:
+        add(a, b)
+    spec = {"model": {"type": "BPE", "vocab": vocab, "merges": merges}, "added_tokens": [{"content": "<|x|>", "id": len(vocab), "special": True}]}
+    tk = tokenizer.BpeTokenizer(spec)
+    assert tk._native is not None
+    py = tokenizer.BpeTokenizer(spec)
+    py._native = None
+    rng = np.random.default_rng(0)
+    texts = ["the theme of the thing", "aaaaaaa aaaa aaaaa", "", " ", "bathing in the aaa<|x|>12 1212", "héllo ✓ 你好 the"]
+    texts += ["".join(rng.choice(list("the aing12r\n"), size=int(rng.integers(1, 60)))) for _ in range(50)]
+    for t in texts:
+        assert tk.encode(t) == py.encode(t), t
+        assert tk.decode(tk.encode(t), skip_special=False) == t
