@@ -126,6 +126,14 @@ class Backend:
     def prefix_release(self, handles: list) -> None:
         pass
 
+    def prefix_export(self, handle) -> bytes | None:
+        """The block's cached state as bytes (for a spill tier), or None when this backend cannot export."""
+        return None
+
+    def prefix_import(self, payload: bytes):
+        """A new handle holding an exported block again (the caller owns one reference), or None (no room, or not supported)."""
+        return None
+
     def prefix_bytes_per_block(self) -> int:
         return 0
 

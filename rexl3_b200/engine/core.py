@@ -81,7 +81,8 @@ class StepError(Exception):
 class Engine:
     def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
                  spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
-                 prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b"", device_sampler: bool = False):
+                 prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b"", device_sampler: bool = False,
+                 spill=None):
         self.backend = backend
         self.admission = admission
         self.window_rows = min(window_rows, backend.max_rows)
@@ -91,6 +92,10 @@ class Engine:
         self.can_rollback = getattr(backend, "supports_rollback", lambda: True)()
         self.cost = cost
         self.prefix = prefix if (prefix is not None and backend.prefix_block_tokens() > 0) else None
+        # second tier (sched.spill.SpillStore): blocks leaving the index are exported to it, and a lookup that ends early continues there
+        self.spill = spill if self.prefix is not None else None
+        if self.spill is not None:
+            self.prefix.on_evict = self._spill_out
         self.prefill_policy = prefill_policy
         # sample and accept on the device (the keyed sampler's device twin) when the backend offers it: only token ids come back
         self.device_sampler = bool(device_sampler and getattr(backend, "supports_device_sampler", lambda: False)())
@@ -208,11 +213,43 @@ class Engine:
         bt = self.backend.prefix_block_tokens()
         s.hashes = chain_hashes(s.tokens[:s.prompt_len], bt, self.cache_namespace)
         chain = self.prefix.lookup(s.hashes, s.prompt_len)
+        if self.spill is not None:
+            chain = self._spill_in(s, chain)
         if chain:
             n = self.backend.prefix_restore(s.slot, [e.handle for e in chain])
             s.prefilled = s.cached = n
             s.committed_blocks = n // bt
             self.counters["cached_tokens"] += n
+
+    def _spill_out(self, entry) -> None:
+        if entry.key in self.spill:
+            return
+        payload = self.backend.prefix_export(entry.handle)
+        if payload is not None and self.spill.put(entry.key, payload):
+            self.counters["spilled_blocks"] = self.counters.get("spilled_blocks", 0) + 1
+
+    def _spill_in(self, s: _Seq, chain: list) -> list:
+        """Continue a device-cache chain with blocks held by the spill tier: import each into the backend and the index, in order."""
+        max_blocks = (s.prompt_len - 1) // self.backend.prefix_block_tokens()
+        k = len(chain)
+        protect = set(s.hashes[:k])
+        while k < max_blocks and s.hashes[k] in self.spill:
+            payload = self.spill.get(s.hashes[k])
+            handle = self.backend.prefix_import(payload) if payload is not None else None
+            if handle is None:
+                break
+            protect.add(s.hashes[k])
+            dup, evicted = self.prefix.insert(s.hashes[:k + 1], [None] * k + [handle], self.backend.prefix_bytes_per_block())
+            gone = [h for h in list(dup) + list(evicted) if h is not None]
+            if gone:
+                self.backend.prefix_release(gone)
+            e = self.prefix.entries.get(s.hashes[k])
+            if e is None or e.handle is not handle:       # the budget could not keep it: stop here
+                break
+            chain = chain + [e]
+            k += 1
+            self.counters["unspilled_blocks"] = self.counters.get("unspilled_blocks", 0) + 1
+        return chain
 
     # ------------------------------------------------------------------ the step
     def step(self) -> list:

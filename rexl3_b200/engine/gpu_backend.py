@@ -437,6 +437,34 @@ class DenseGpuBackend(Backend):
     def prefix_release(self, handles):
         self.pool.release([p for _, p in handles])
 
+    def prefix_export(self, handle):
+        """One page of every layer's K and V cache as bytes ([2 * layers with a cache, n_kv, 64, head_dim] in the cache's own dtype)."""
+        m = self.m
+        if getattr(m, "k_cache", None) is None:
+            return None
+        p = handle[1]
+        parts = [c[p] for c in m.k_cache if c is not None] + [c[p] for c in m.v_cache if c is not None]
+        out = torch.stack(parts).contiguous().view(torch.uint8).cpu()
+        self.d2h_bytes += out.numel()
+        return out.numpy().tobytes()
+
+    def prefix_import(self, payload):
+        m = self.m
+        if getattr(m, "k_cache", None) is None:
+            return None
+        caches = [c for c in m.k_cache if c is not None] + [c for c in m.v_cache if c is not None]
+        page_bytes = caches[0][0].numel() * caches[0].element_size()
+        if len(payload) != page_bytes * len(caches):
+            return None                     # written by a different model or cache format
+        got = self.pool.alloc(1)
+        if got is None:
+            return None
+        src = torch.frombuffer(bytearray(payload), dtype=torch.uint8).to(m.device, non_blocking=False).view(len(caches), page_bytes)
+        for i, c in enumerate(caches):
+            c[got[0]].view(torch.uint8).view(-1).copy_(src[i])
+        self.h2d_bytes += len(payload)
+        return ("page", got[0])
+
     def quiesce(self):
         torch.cuda.synchronize()
 

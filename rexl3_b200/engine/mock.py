@@ -219,3 +219,14 @@ class MockBackend(Backend):
     def prefix_release(self, handles):
         for _, b, _ in handles:
             self.pool.release([b])
+
+    def prefix_export(self, handle):
+        import struct
+        return struct.pack(f"<{len(handle[2])}i", *handle[2])
+
+    def prefix_import(self, payload):
+        import struct
+        got = self.pool.alloc(1)
+        if got is None:
+            return None
+        return ("blk", got[0], struct.unpack(f"<{len(payload) // 4}i", payload))

@@ -235,6 +235,13 @@ class DenseTpBackend(DenseGpuBackend):
         self.ex.run_prefill(M, n, max_qlen, last_rows, count)
         return self._download(len(last_rows), count) if last_rows else None
 
+    # a block's cache is spread over the ranks' shards: no single-rank export (the spill tier stays empty under tensor parallelism)
+    def prefix_export(self, handle):
+        return None
+
+    def prefix_import(self, payload):
+        return None
+
     # ---- bench / lifecycle helpers
     def mark(self):
         self._send(OP_MARK)

@@ -25,7 +25,7 @@ from .dense import (DenseConfig, DenseGPU, HostLinear, HostWeights, ReferenceDen
 
 @dataclass
 class HybridConfig(DenseConfig):
-    pattern: str = ""            # one letter per layer: 'M' = Mamba2 mixer, 'G' = gated delta net mixer, 'A' = attention mixer
+    pattern: str = ""            # one letter per layer: 'M' Mamba2, 'G' gated delta net, 'K' Kimi delta attention, 'A' attention
     ssm_heads: int = 0
     ssm_head_dim: int = 64
     ssm_groups: int = 1
@@ -61,8 +61,17 @@ class HybridConfig(DenseConfig):
         """z | q | k | v | b | a, padded up to a multiple of 128 columns."""
         return (self.gdn_inner + self.gdn_conv_channels + 2 * self.gdn_v_heads + 127) // 128 * 128
 
+    @property
+    def kda_proj_width(self) -> int:
+        """z | q | k | v | b | a (one decay input per key channel), padded up to a multiple of 128 columns."""
+        return (self.gdn_inner + self.gdn_conv_channels + self.gdn_v_heads + self.gdn_inner + 127) // 128 * 128
+
+    def delta_proj_width(self, kind: str) -> int:
+        return self.kda_proj_width if kind == "K" else self.gdn_proj_width
+
     def gdn_layers(self):
-        return [i for i, c in enumerate(self.pattern) if c == "G"]
+        """Layers with a delta-rule mixer ('G' or 'K'): they share head geometry, pools and kernels."""
+        return [i for i, c in enumerate(self.pattern) if c in "GK"]
 
     def mamba_layers(self):
         return [i for i, c in enumerate(self.pattern) if c == "M"]
@@ -71,8 +80,8 @@ class HybridConfig(DenseConfig):
         return [i for i, c in enumerate(self.pattern) if c == "A"]
 
     def validate(self) -> None:
-        if len(self.pattern) != self.n_layers or set(self.pattern) - {"M", "A", "G"}:
-            raise ValueError("pattern needs one of 'M' / 'G' / 'A' per layer")
+        if len(self.pattern) != self.n_layers or set(self.pattern) - {"M", "A", "G", "K"}:
+            raise ValueError("pattern needs one of 'M' / 'G' / 'K' / 'A' per layer")
         if self.conv_k != 4:
             raise ValueError("the conv kernel is built for width 4")
         if "M" in self.pattern:
@@ -80,16 +89,15 @@ class HybridConfig(DenseConfig):
                 raise ValueError("the Mamba2 kernels are built for head_dim 64, state 128")
             if self.ssm_heads <= 0 or self.ssm_heads % self.ssm_groups or self.d_inner % 128:
                 raise ValueError("ssm_heads must be a multiple of ssm_groups and even")
-        if "G" in self.pattern and (self.gdn_k_heads <= 0 or self.gdn_v_heads % self.gdn_k_heads):
+        if ("G" in self.pattern or "K" in self.pattern) and (self.gdn_k_heads <= 0 or self.gdn_v_heads % self.gdn_k_heads):
             raise ValueError("gdn_v_heads must be a positive multiple of gdn_k_heads")
 
     def weight_params(self) -> int:
         ffn = 3 * self.d_model * self.ffn_padded
         attn = self.d_model * self.qkv_width + self.n_q * self.head_dim * self.d_model
         ssm = self.d_model * self.in_proj_width + self.d_inner * self.d_model
-        gdn = self.d_model * self.gdn_proj_width + self.gdn_inner * self.d_model
-        return (len(self.attn_layers()) * (attn + ffn) + len(self.mamba_layers()) * (ssm + ffn) + len(self.gdn_layers()) * (gdn + ffn)
-                + self.vocab_padded * self.d_model)
+        delta = sum(self.d_model * self.delta_proj_width(self.pattern[i]) + self.gdn_inner * self.d_model + ffn for i in self.gdn_layers())
+        return len(self.attn_layers()) * (attn + ffn) + len(self.mamba_layers()) * (ssm + ffn) + delta + self.vocab_padded * self.d_model
 
     def state_bytes_per_slot(self) -> int:
         return (len(self.mamba_layers()) * 4 * (self.ssm_heads * self.ssm_head_dim * self.ssm_state + 3 * self.conv_channels)
@@ -109,6 +117,8 @@ CONFIGS = {
                                    name="gdn-hybrid-27b", pattern="GGGA" * 16, nope=False, gdn_k_heads=16, gdn_v_heads=48),
     "test-hybrid-gdn": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid-gdn",
                                     pattern="GAMG", nope=False, ssm_heads=16, ssm_groups=2, gdn_k_heads=2, gdn_v_heads=4),
+    "test-hybrid-kda": HybridConfig(n_layers=3, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid-kda",
+                                    pattern="KAK", nope=True, gdn_k_heads=4, gdn_v_heads=4),
     "test-hybrid": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid",
                                 pattern="MAMM", ssm_heads=16, ssm_groups=2),
 }
@@ -137,12 +147,13 @@ class HostGdnLayer:
     out_proj: HostLinear
     conv_w: np.ndarray           # [C, 4]
     conv_b: np.ndarray           # [C]
-    dt_bias: np.ndarray          # [Hv]
+    dt_bias: np.ndarray          # [Hv]; Kimi delta attention: [Hv * 128], one per key channel
     a_log: np.ndarray            # [Hv]; A = -exp(a_log)
     norm_w: np.ndarray           # [128], shared by the heads
     ffn_norm: np.ndarray
     gate_up: HostLinear
     down: HostLinear
+    kda: bool = False            # per-key-channel decay and a sigmoid output gate
 
 
 def random_weights(cfg: HybridConfig, seed: int = 0) -> HostWeights:
@@ -165,14 +176,15 @@ def random_weights(cfg: HybridConfig, seed: int = 0) -> HostWeights:
             o = random_linear(cfg.n_q * cfg.head_dim, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(cfg.n_q * cfg.head_dim))
             w.layers.append(HostLayer(nrm(d), qkv, o, nrm(d), gu, down))
             continue
-        if kind == "G":
-            GI, GC, Hv = cfg.gdn_inner, cfg.gdn_conv_channels, cfg.gdn_v_heads
-            real = GI + GC + 2 * Hv
-            ip = random_linear(d, cfg.gdn_proj_width, cfg.bits, rng, cfg.codebook, s_in, zero_cols_from=real if real != cfg.gdn_proj_width else None)
+        if kind in "GK":
+            GI, GC, Hv, kda = cfg.gdn_inner, cfg.gdn_conv_channels, cfg.gdn_v_heads, kind == "K"
+            real, wp = GI + GC + Hv + (GI if kda else Hv), cfg.delta_proj_width(kind)
+            ip = random_linear(d, wp, cfg.bits, rng, cfg.codebook, s_in, zero_cols_from=real if real != wp else None)
             op = random_linear(GI, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(GI))
             w.layers.append(HostGdnLayer(
                 nrm(d), ip, op, _bf16_round(rng.normal(0, 0.5, size=(GC, 4))), _bf16_round(rng.normal(0, 0.1, size=GC)),
-                rng.uniform(-2.0, 0.0, size=Hv).astype(np.float32), np.log(rng.uniform(0.5, 4.0, size=Hv)).astype(np.float32), nrm(128), nrm(d), gu, down))
+                rng.uniform(-2.0, 0.0, size=GI if kda else Hv).astype(np.float32), np.log(rng.uniform(0.5, 4.0, size=Hv)).astype(np.float32), nrm(128),
+                nrm(d), gu, down, kda))
             continue
         real = 2 * DI + 2 * cfg.ssm_groups * cfg.ssm_state + H
         ip = random_linear(d, cfg.in_proj_width, cfg.bits, rng, cfg.codebook, s_in, zero_cols_from=real if real != cfg.in_proj_width else None)
@@ -203,7 +215,7 @@ class ReferenceHybrid(ReferenceDense):
                 L.update(kind="M", in_proj=t(lay.in_proj.dense()), o=t(lay.out_proj.dense()), conv_w=t(lay.conv_w), conv_b=t(lay.conv_b),
                          dt_bias=t(lay.dt_bias), a_neg=-torch.exp(t(lay.a_log)), d_skip=t(lay.d_skip), norm_w=t(lay.norm_w))
             elif isinstance(lay, HostGdnLayer):
-                L.update(kind="G", in_proj=t(lay.in_proj.dense()), o=t(lay.out_proj.dense()), conv_w=t(lay.conv_w), conv_b=t(lay.conv_b),
+                L.update(kind="K" if lay.kda else "G", in_proj=t(lay.in_proj.dense()), o=t(lay.out_proj.dense()), conv_w=t(lay.conv_w), conv_b=t(lay.conv_b),
                          dt_bias=t(lay.dt_bias), a_neg=-torch.exp(t(lay.a_log)), norm_w=t(lay.norm_w))
             else:
                 L.update(kind="A", qkv=t(lay.qkv.dense()), o=t(lay.o.dense()))
@@ -227,8 +239,8 @@ class ReferenceHybrid(ReferenceDense):
     def _mix(self, li, L, h, pos, seq, start):
         if L["kind"] == "A":
             return super()._mix(li, L, h, pos, seq, start)
-        if L["kind"] == "G":
-            return self._gdn(li, L, h, seq, start)
+        if L["kind"] in "GK":
+            return self._gdn(li, L, h, seq, start, L["kind"] == "K")
         cfg = self.cfg
         T, H, P, G, N, DI, C = h.shape[0], cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, cfg.d_inner, cfg.conv_channels
         proj = self._rms(h, L["attn_norm"], cfg.eps) @ L["in_proj"]
@@ -255,12 +267,13 @@ class ReferenceHybrid(ReferenceDense):
         return (g.reshape(T, DI) * L["norm_w"]) @ L["o"]
 
 
-    def _gdn(self, li, L, h, seq, start):
-        """Gated delta net, token by token (the public recurrent form: decay, delta-rule write, read, per-head gated RMSNorm)."""
+    def _gdn(self, li, L, h, seq, start, kda=False):
+        """Gated delta net, token by token (the public recurrent form: decay, delta-rule write, read, per-head gated RMSNorm).  `kda`: the decay
+        is a vector over the key channels and the output gate a sigmoid (Kimi delta attention)."""
         cfg, F = self.cfg, torch.nn.functional
         T, Hk, Hv, D, DI, C = h.shape[0], cfg.gdn_k_heads, cfg.gdn_v_heads, 128, cfg.gdn_inner, cfg.gdn_conv_channels
         proj = self._rms(h, L["attn_norm"], cfg.eps) @ L["in_proj"]
-        z, qkv, b, a = proj[:, :DI], proj[:, DI:DI + C], proj[:, DI + C:DI + C + Hv], proj[:, DI + C + Hv:DI + C + 2 * Hv]
+        z, qkv, b, a = proj[:, :DI], proj[:, DI:DI + C], proj[:, DI + C:DI + C + Hv], proj[:, DI + C + Hv:DI + C + Hv + (DI if kda else Hv)]
         if start == 0 or (seq, li) not in self.ssm:
             hist, S = torch.zeros(3, C, device=h.device, dtype=h.dtype), torch.zeros(Hv, D, D, device=h.device, dtype=h.dtype)
         else:
@@ -271,17 +284,20 @@ class ReferenceHybrid(ReferenceDense):
         q = (l2(act[:, :Hk * D].view(T, Hk, D)) / math.sqrt(D)).repeat_interleave(Hv // Hk, dim=1)
         k = l2(act[:, Hk * D:2 * Hk * D].view(T, Hk, D)).repeat_interleave(Hv // Hk, dim=1)
         v = act[:, 2 * Hk * D:].view(T, Hv, D)
-        decay = torch.exp(L["a_neg"][None, :] * F.softplus(a + L["dt_bias"][None, :]))
+        if kda:        # [T, Hv, 1, D]: one factor per key channel i
+            decay = torch.exp(L["a_neg"][None, :, None] * F.softplus(a + L["dt_bias"][None, :]).view(T, Hv, D))[:, :, None, :]
+        else:
+            decay = torch.exp(L["a_neg"][None, :] * F.softplus(a + L["dt_bias"][None, :]))[:, :, None, None]
         beta = torch.sigmoid(b)
         o = torch.empty(T, Hv, D, device=h.device, dtype=h.dtype)
         for t_ in range(T):                                   # S[h, j (value), i (key)]
-            S = S * decay[t_][:, None, None]
+            S = S * decay[t_]
             kv = (S * k[t_][:, None, :]).sum(-1)
             S = S + ((v[t_] - kv) * beta[t_][:, None])[:, :, None] * k[t_][:, None, :]
             o[t_] = (S * q[t_][:, None, :]).sum(-1)
         self.ssm[(seq, li)] = (full[-3:].clone(), S)
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.eps) * L["norm_w"][None, None, :]
-        return (o.reshape(T, DI) * F.silu(z)) @ L["o"]
+        return (o.reshape(T, DI) * (torch.sigmoid(z) if kda else F.silu(z))) @ L["o"]
 
 
 # ====================================================================================================== sm_100a executor
@@ -313,13 +329,15 @@ class HybridGPU(DenseGPU):
             s.update(in_proj=(cfg.d_model, cfg.in_proj_width), out_proj=(cfg.d_inner, cfg.d_model))
         if "G" in cfg.pattern:
             s.update(gdn_in=(cfg.d_model, cfg.gdn_proj_width), gdn_out=(cfg.gdn_inner, cfg.d_model))
+        if "K" in cfg.pattern:
+            s.update(kda_in=(cfg.d_model, cfg.kda_proj_width), gdn_out=(cfg.gdn_inner, cfg.d_model))
         return s
 
     def _alloc_scratch(self, R: int):
         super()._alloc_scratch(R)
         cfg, dev = self.cfg, self.device
-        m, g = "M" in cfg.pattern, "G" in cfg.pattern
-        wp = max(cfg.in_proj_width if m else 0, cfg.gdn_proj_width if g else 0)
+        m, g = "M" in cfg.pattern, bool(cfg.gdn_layers())
+        wp = max(cfg.in_proj_width if m else 0, cfg.gdn_proj_width if "G" in cfg.pattern else 0, cfg.kda_proj_width if "K" in cfg.pattern else 0)
         wc = max(cfg.conv_channels if m else 0, cfg.gdn_conv_channels if g else 0)
         wi = max(cfg.d_inner if m else 0, cfg.gdn_inner if g else 0)
         self.ssm_proj = torch.empty(R * wp, dtype=torch.float32, device=dev)       # flat: each layer kind views its own row width
@@ -342,7 +360,7 @@ class HybridGPU(DenseGPU):
         for lay in w.layers:
             if isinstance(lay, HostGdnLayer):
                 ip, op = up(lay.in_proj), up(lay.out_proj)
-                self.layers.append(dict(kind="G", attn_norm=dev(lay.attn_norm, bf), qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=dev(lay.conv_w, bf),
+                self.layers.append(dict(kind="K" if lay.kda else "G", attn_norm=dev(lay.attn_norm, bf), qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=dev(lay.conv_w, bf),
                                         conv_b=dev(lay.conv_b, bf), dt_bias=dev(lay.dt_bias, f32), a_neg=-torch.exp(dev(lay.a_log, f32)),
                                         norm_w=dev(lay.norm_w, bf), ffn_norm=dev(lay.ffn_norm, bf), gate_up=up(lay.gate_up), down=up(lay.down),
                                         q_norm=None, k_norm=None))
@@ -387,12 +405,13 @@ class HybridGPU(DenseGPU):
                 self.layers.append(dict(kind="A", attn_norm=norm(), qkv=lin(d, cfg.qkv_width, 1.0 / math.sqrt(d)), o=lin(HQ, d, 0.5 / math.sqrt(HQ)),
                                         ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
                 continue
-            if kind == "G":
-                GI, GC, Hv = cfg.gdn_inner, cfg.gdn_conv_channels, cfg.gdn_v_heads
-                ip = lin(d, cfg.gdn_proj_width, 1.0 / math.sqrt(d), real_n=GI + GC + 2 * Hv)
+            if kind in "GK":
+                GI, GC, Hv, kda = cfg.gdn_inner, cfg.gdn_conv_channels, cfg.gdn_v_heads, kind == "K"
+                ip = lin(d, cfg.delta_proj_width(kind), 1.0 / math.sqrt(d), real_n=GI + GC + Hv + (GI if kda else Hv))
                 op = lin(GI, d, 0.5 / math.sqrt(GI))
-                self.layers.append(dict(kind="G", attn_norm=norm(), qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=(0.5 * rn(GC, 4)).to(torch.bfloat16),
-                                        conv_b=(0.1 * rn(GC)).to(torch.bfloat16), dt_bias=ru(Hv, -2.0, 0.0), a_neg=-ru(Hv, 0.5, 4.0), norm_w=norm(128),
+                self.layers.append(dict(kind=kind, attn_norm=norm(), qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=(0.5 * rn(GC, 4)).to(torch.bfloat16),
+                                        conv_b=(0.1 * rn(GC)).to(torch.bfloat16), dt_bias=ru(GI if kda else Hv, -2.0, 0.0), a_neg=-ru(Hv, 0.5, 4.0),
+                                        norm_w=norm(128),
                                         ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
                 continue
             ip = lin(d, cfg.in_proj_width, 1.0 / math.sqrt(d), real_n=2 * DI + 2 * cfg.ssm_groups * cfg.ssm_state + H)
@@ -412,13 +431,15 @@ class HybridGPU(DenseGPU):
             return super()._mixer(li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale)
         cfg, K = self.cfg, self.K
         seg_s, seg_l, nseg = (prefill["q_start"], prefill["q_len"], prefill["nseq"]) if prefill is not None else (None, None, 0)
-        if L["kind"] == "G":
-            s = self._linear(xr_d, L["in_proj"], M, cls, "gdn_in")
-            proj = self.ssm_proj[:M * cfg.gdn_proj_width].view(M, cfg.gdn_proj_width)
+        if L["kind"] in "GK":
+            kda = L["kind"] == "K"
+            wp = cfg.delta_proj_width(L["kind"])
+            s = self._linear(xr_d, L["in_proj"], M, cls, "kda_in" if kda else "gdn_in")
+            proj = self.ssm_proj[:M * wp].view(M, wp)
             K.finish_store(self.part, s, M, L["in_proj"], proj)
             out = self.ssm_out[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
             K.gdn_mixer(proj, M, cfg.gdn_k_heads, cfg.gdn_v_heads, 128, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"], L["dt_bias"],
-                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, out)
+                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, out, kda=kda)
             xr_g = self.xr[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
             K.norm_rot_in(out, None, cfg.eps, L["out_proj"].suh, xr_g)
             return self._linear(xr_g, L["out_proj"], M, cls, "gdn_out")

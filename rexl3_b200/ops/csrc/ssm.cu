@@ -159,8 +159,13 @@ __global__ void __launch_bounds__(256) ssm_gate_norm_kernel(const float* __restr
 //   S pool   f32 [slots][Hv][128 value j][128 key i], i contiguous; conv pool as above with C = (2 Hk + Hv) * 128
 // One CTA per (segment, value head), 256 threads: thread = value column j and one half of the 128 keys (64 state values in registers);
 // the two halves meet in one shuffle.  The gated norm runs in the same kernel (the CTA holds the head's whole output row).
+//
+// KDA = true: Kimi delta attention (reference crates/cuda/csrc/kda.cu: per-key-channel decay).  The decay is a vector over the key
+// channels, exp(A * softplus(a_i + dt_bias_i)) with a_i taken from 128 columns per head (proj: ... | b (Hv) | a (Hv*128)), and the
+// output gate is a sigmoid instead of SiLU.  Everything else is the same code.
 constexpr int GDN_D = 128;
 
+template <bool KDA>
 __global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int xoff,
                                                       int goff, int M, int Hk, int Hv, const int* __restrict__ row_seq,
                                                       const int* __restrict__ positions, const int* __restrict__ seg_start,
@@ -169,7 +174,7 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__
                                                       float* __restrict__ s_pool, float* conv_pool, uint16_t* __restrict__ out) {
   pdl_launch();
   pdl_wait();
-  __shared__ float sqk[2 * GDN_D], red[8], red2[8];
+  __shared__ float sqk[2 * GDN_D], red[8], red2[8], sdec[KDA ? GDN_D : 1];
   int r0, len;
   if (seg_start != nullptr) {
     r0 = seg_start[blockIdx.x];
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__
       st[i] = v.x, st[i + 1] = v.y, st[i + 2] = v.z, st[i + 3] = v.w;
     }
   }
-  const float A = a_neg[h], dtb = dt_bias[h], wj = ssm_bf(norm_w[j]);
+  const float A = a_neg[h], dtb = KDA ? 0.f : dt_bias[h], wj = ssm_bf(norm_w[j]);
   const float* sq = sqk + half * 64;
   const float* sk = sqk + GDN_D + half * 64;
   for (int t = 0; t < len; ++t) {
@@ -206,18 +211,26 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__
     sqk[tid] = val;
     const float ss = warp_sum(val * val);
     if (lane == 0) red[warp] = ss;
+    if (KDA && tid < GDN_D) {
+      float ai = proj[(size_t)r * ldp + goff + Hv + h * GDN_D + tid] + dt_bias[h * GDN_D + tid];
+      ai = ai > 20.f ? ai : log1pf(__expf(ai));
+      sdec[tid] = __expf(A * ai);
+    }
     __syncthreads();
     const float qinv = rsqrtf(red[0] + red[1] + red[2] + red[3] + 1e-6f) * 0.08838834764831845f;
     const float kinv = rsqrtf(red[4] + red[5] + red[6] + red[7] + 1e-6f);
     const float v = xr[2 * Hk * GDN_D + h * GDN_D + j];
-    float a = proj[(size_t)r * ldp + goff + Hv + h] + dtb;
-    a = a > 20.f ? a : log1pf(__expf(a));
-    const float decay = __expf(A * a);
+    float decay = 1.f;
+    if (!KDA) {
+      float a = proj[(size_t)r * ldp + goff + Hv + h] + dtb;
+      a = a > 20.f ? a : log1pf(__expf(a));
+      decay = __expf(A * a);
+    }
     const float beta = 1.f / (1.f + __expf(-proj[(size_t)r * ldp + goff + h]));
     float kv = 0.f;
 #pragma unroll
     for (int i = 0; i < 64; ++i) {
-      st[i] *= decay;
+      st[i] *= KDA ? sdec[half * 64 + i] : decay;
       kv += st[i] * sk[i];
     }
     kv = (kv + __shfl_xor_sync(0xffffffffu, kv, 1)) * kinv;
@@ -237,7 +250,8 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__
     for (int i = 0; i < 8; ++i) tot += red2[i];
     if (half == 0) {
       const float z = proj[(size_t)r * ldp + h * GDN_D + j];
-      __nv_bfloat16 b = __float2bfloat16_rn(o * rsqrtf(tot / (float)GDN_D + eps) * wj * ssm_silu(z));
+      const float gate = KDA ? 1.f / (1.f + __expf(-z)) : ssm_silu(z);
+      __nv_bfloat16 b = __float2bfloat16_rn(o * rsqrtf(tot / (float)GDN_D + eps) * wj * gate);
       out[(size_t)r * DI + h * GDN_D + j] = *reinterpret_cast<uint16_t*>(&b);
     }
   }
@@ -269,18 +283,19 @@ RX_API int rx_ssm_mixer(const void* proj, int ldp, int M, int H, int P, int G, i
   return (int)cudaGetLastError();
 }
 
-// One gated-delta-net mixer between its two projections: conv, then recurrence + gated norm (pools updated).  Two launches.
+// One gated-delta-net (kda = 0) or Kimi-delta-attention (kda = 1; dt_bias then has Hv*128 entries) mixer between its two projections:
+// conv, then recurrence + gated norm (pools updated).  Two launches.
 RX_API int rx_gdn_mixer(const void* proj, int ldp, int M, int Hk, int Hv, int D, const void* row_seq, const void* positions, const void* seg_start,
                         const void* seg_len, int nseg, const void* conv_w, const void* conv_b, const void* dt_bias, const void* a_neg,
-                        const void* norm_w, float eps, void* conv_pool, void* s_pool, void* xbc, void* out_bf16, void* stream) {
+                        const void* norm_w, float eps, void* conv_pool, void* s_pool, void* xbc, void* out_bf16, void* stream, int kda) {
   using namespace rx;
   if (D != GDN_D || Hk <= 0 || Hv % Hk || M <= 0) return (int)cudaErrorInvalidValue;
   const int DI = Hv * D, C = (2 * Hk + Hv) * D, xoff = DI, goff = DI + C;
-  if (ldp < goff + 2 * Hv) return (int)cudaErrorInvalidValue;
+  if (ldp < goff + Hv + (kda ? Hv * D : Hv)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
   launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
          (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
-  launch(gdn_scan_kernel, dim3(seg_start ? nseg : M, Hv), dim3(256), 0, st, (const float*)xbc, C, (const float*)proj, ldp, xoff, goff, M, Hk, Hv,
+  launch(kda ? gdn_scan_kernel<true> : gdn_scan_kernel<false>, dim3(seg_start ? nseg : M, Hv), dim3(256), 0, st, (const float*)xbc, C, (const float*)proj, ldp, xoff, goff, M, Hk, Hv,
          (const int*)row_seq, (const int*)positions, (const int*)seg_start, (const int*)seg_len, (const float*)dt_bias, (const float*)a_neg,
          (const uint16_t*)norm_w, eps, (float*)s_pool, (float*)conv_pool, (uint16_t*)out_bf16);
   return (int)cudaGetLastError();

@@ -62,6 +62,7 @@ class PrefixIndex:
         self.ghost_capacity = ghost_capacity
         self.clock = 0.0      # GreedyDual inflation value
         self.stats = dict(lookups=0, hits=0, hit_blocks=0, inserts=0, evictions=0, ghost_hits=0)
+        self.on_evict = None  # called with the Entry just before it leaves the index (a spill tier saves the block here)
 
     def __len__(self):
         return len(self.entries)
@@ -130,6 +131,8 @@ class PrefixIndex:
         v = self._victim(protect)
         if v is None:
             return None
+        if self.on_evict is not None:
+            self.on_evict(v)
         del self.entries[v.key]
         self.bytes -= v.nbytes
         if v.parent is not None and v.parent in self.entries:

@@ -42,6 +42,8 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--max-drafts", type=int, default=4)
     p.add_argument("--prefix-cache", choices=["on", "off"], default="on")
     p.add_argument("--prefix-cache-mib", type=int, default=4096)
+    p.add_argument("--prefix-spill-dir", default="", help="directory (e.g. on NVMe) where prefix blocks evicted from the device cache are kept and reused")
+    p.add_argument("--prefix-spill-mib", type=int, default=65536)
     p.add_argument("--default-max-tokens", type=int, default=512)
     p.add_argument("--queue-depth", type=int, default=64)
     p.add_argument("--queue-timeout", type=float, default=300)
@@ -71,7 +73,7 @@ def build(args):
             be = MockBackend(opts)
             prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=be.prefix_block_tokens()) if args.prefix_cache == "on" else None
             return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix)
+                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix))
         info = {"backend": "mock"}
     else:
         from ..models import dense
@@ -173,10 +175,18 @@ def build(args):
                                          self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode(), device_sampler=args.device_sampler)
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode(), device_sampler=args.device_sampler,
+                          spill=_spill_store(args, prefix))
     tok = load_tokenizer(folder, vocab)
     fmt = ChatFormat.from_dir(folder)
     return make, tok, fmt, name, info
+
+
+def _spill_store(args, prefix):
+    if prefix is None or not args.prefix_spill_dir:
+        return None
+    from ..sched.spill import SpillStore
+    return SpillStore(args.prefix_spill_dir, args.prefix_spill_mib << 20)
 
 
 def follow_rank(args) -> int:

@@ -70,3 +70,46 @@ def test_device_sampler_equals_host_sampler():
                 assert ev.kind != "error", ev.message
         outs[dev] = got
     assert outs[False] == outs[True]
+
+
+def test_prefix_spill_tier_restores_pages_bit_for_bit(tmp_path):
+    """Blocks evicted from a two-block device prefix cache go to the spill directory; the same prompt later gets them back (page bytes
+    imported into fresh pages) and decodes exactly what the cold run decoded."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    from rexl3_b200.models import dense
+    from rexl3_b200.sampling import GREEDY
+    from rexl3_b200.sched.prefix import CacheBudget, PrefixIndex
+    from rexl3_b200.sched.spill import SpillStore
+    cfg = dense.CONFIGS["test-hd128"]
+    m = dense.DenseGPU(dense.random_weights(cfg, seed=6), num_pages=48, max_rows=64, max_seqs=4, max_blocks_per_seq=8, max_prefill_rows=512)
+    be = DenseGpuBackend(m, max_slots=4)
+    prefix = PrefixIndex(CacheBudget(max_bytes=2 * be.prefix_bytes_per_block()), block_tokens=64)
+    spill = SpillStore(str(tmp_path / "spill"), max_bytes=1 << 30)
+    eng = Engine(be, None, window_rows=16, prefill_chunk=256, spec="none", prefix=prefix, spill=spill)
+    rng = np.random.default_rng(9)
+    a, b = rng.integers(0, cfg.vocab, size=4 * 64 + 9).tolist(), rng.integers(0, cfg.vocab, size=4 * 64 + 9).tolist()
+
+    def run(rid, prompt):
+        eng.submit(Request(rid, prompt, 10, GREEDY))
+        out = []
+        for _ in range(200):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                assert ev.kind != "error", ev.message
+                if ev.kind == "tokens":
+                    out.extend(ev.tokens)
+        return out
+
+    cold = run("a1", a)
+    run("b1", b)
+    assert len(spill) >= 2 and eng.counters.get("spilled_blocks", 0) >= 2
+    before = eng.counters["cached_tokens"]
+    warm = run("a2", a)
+    assert warm == cold
+    assert eng.counters.get("unspilled_blocks", 0) >= 1 and eng.counters["cached_tokens"] > before
+    assert be.pool.total_blocks() - be.pool.free_blocks() == len(prefix.entries)

@@ -17,7 +17,7 @@ def _setup(seed=1, name="test-hybrid"):
     return cfg, w, hybrid
 
 
-@pytest.mark.parametrize("name", ["test-hybrid", "test-hybrid-gdn"])
+@pytest.mark.parametrize("name", ["test-hybrid", "test-hybrid-gdn", "test-hybrid-kda"])
 def test_chunked_prefill_and_mixed_decode_match_reference(name):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
@@ -75,7 +75,7 @@ def test_chunked_prefill_and_mixed_decode_match_reference(name):
     assert (m.conv_pool[0][2] - conv_ref).abs().max().item() < 0.03 * conv_ref.abs().max().item()
 
 
-@pytest.mark.parametrize("name", ["test-hybrid", "test-hybrid-gdn"])
+@pytest.mark.parametrize("name", ["test-hybrid", "test-hybrid-gdn", "test-hybrid-kda"])
 def test_engine_greedy_stream_matches_reference_with_graphs(name):
     """Engine over the hybrid backend (graph replay, chunked prefill, two streams): every greedy token is the fp32 reference's best token
     (within the kernels' tolerance) when the reference is fed the engine's own stream."""

@@ -12,6 +12,7 @@ SMALL = dataclasses.replace(hybrid.CONFIGS["test-hybrid"], n_layers=3, pattern="
 
 
 GDN = dataclasses.replace(SMALL, pattern="GAG", nope=False, gdn_k_heads=1, gdn_v_heads=2, name="cpu-gdn")
+KDA = dataclasses.replace(SMALL, pattern="KAK", gdn_k_heads=2, gdn_v_heads=2, name="cpu-kda")
 
 
 def test_config_geometry():
@@ -30,7 +31,7 @@ def test_gdn_config_geometry():
     assert cfg.gdn_proj_width % 128 == 0 and cfg.gdn_proj_width >= 6144 + 10240 + 96
 
 
-@pytest.mark.parametrize("cfg", [SMALL, GDN], ids=["mamba2", "gdn"])
+@pytest.mark.parametrize("cfg", [SMALL, GDN, KDA], ids=["mamba2", "gdn", "kda"])
 def test_chunked_equals_whole_and_position_zero_restarts(cfg):
     SMALL = cfg  # noqa: N806
     w = hybrid.random_weights(SMALL, seed=2)
