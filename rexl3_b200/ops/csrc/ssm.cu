@@ -36,10 +36,13 @@ __device__ __forceinline__ float ssm_conv_in(const float* __restrict__ proj, int
   return pool[((size_t)seq * SSM_HIST + (SSM_HIST - back + o)) * C + c];
 }
 
-// the segment's last three pre-conv rows become the sequence's conv history (called by one CTA per segment, after its recurrence)
+// the segment's last three pre-conv rows become the sequence's conv history.  Every CTA of the segment (one per head) commits its own
+// share of the channels after its recurrence: left to one CTA, this loop of dependent loads was most of a decode step's kernel time.
 __device__ __forceinline__ void ssm_conv_commit(const float* __restrict__ proj, int ldp, int xoff, float* conv_pool, int C,
-                                                const int* __restrict__ row_seq, const int* __restrict__ positions, int last, int seq) {
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+                                                const int* __restrict__ row_seq, const int* __restrict__ positions, int last, int seq, int part,
+                                                int nparts) {
+  const int chunk = (C + nparts - 1) / nparts, c0 = part * chunk, c1 = min(C, c0 + chunk);
+  for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     float v[SSM_HIST];
 #pragma unroll
     for (int k = 0; k < SSM_HIST; ++k) v[k] = ssm_conv_in(proj, ldp, xoff, conv_pool, C, row_seq, positions, last, SSM_HIST - 1 - k, c);
@@ -63,7 +66,7 @@ __global__ void __launch_bounds__(256) ssm_conv_kernel(const float* __restrict__
 }
 
 // Recurrence.  grid (segments or rows, H).  With a segment table (seg_start != nullptr) block x is segment x; without one block x is
-// row x and returns unless that row opens a segment.  Block (x, 0) also writes the segment's last three pre-conv rows to the conv pool.
+// row x and returns unless that row opens a segment.  Each block also writes its share of the segment's last three pre-conv rows to the conv pool.
 __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int xoff,
                                                       int dtoff, int M, int H, int G, const int* __restrict__ row_seq,
                                                       const int* __restrict__ positions, const int* __restrict__ seg_start,
@@ -122,7 +125,7 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
   }
 #pragma unroll
   for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
-  if (h == 0) ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq);
+  ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq, h, (int)gridDim.y);
 }
 
 // out[r][c] = bf16( rmsnorm_group( y * silu(z) )[c] * w[c] ), grid (M, G); the group is d_inner / G channels wide
@@ -165,8 +168,10 @@ __global__ void __launch_bounds__(256) ssm_gate_norm_kernel(const float* __restr
 // output gate is a sigmoid instead of SiLU.  Everything else is the same code.
 constexpr int GDN_D = 128;
 
+// Two CTAs per SM (128 registers, a few dozen bytes of spill): a decode step is a chain of dependent loads per CTA, and a second resident
+// CTA hides it; measured 54 us -> see the profile note for 16 streams x 48 heads.
 template <bool KDA>
-__global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int xoff,
+__global__ void __launch_bounds__(256, 2) gdn_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int xoff,
                                                       int goff, int M, int Hk, int Hv, const int* __restrict__ row_seq,
                                                       const int* __restrict__ positions, const int* __restrict__ seg_start,
                                                       const int* __restrict__ seg_len, const float* __restrict__ dt_bias,
@@ -257,7 +262,7 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(const float* __restrict__
   }
 #pragma unroll
   for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
-  if (h == 0) ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq);
+  ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq, h, (int)gridDim.y);
 }
 
 }  // namespace rx
