@@ -19,6 +19,7 @@ from dataclasses import dataclass, field
 from ..sampling import Sampling, SamplingError, choose, seed_for
 from ..sched import AdmitError, Admission, CostModel, Demand, PrefixIndex, chain_hashes, choose_budget
 from ..spec import AcceptStats, CopyDrafter, SpecMode, accept
+from ..utils import trace
 from .backend import Backend, BackendError, DraftAsk, RowRequest
 
 PREFILL_STEP_ROWS = 4096
@@ -257,8 +258,10 @@ class Engine:
         self._expire()
         self._admit()
         try:
-            self._decode_round()
-            self._prefill()
+            with trace.nvtx_range("decode_round"):
+                self._decode_round()
+            with trace.nvtx_range("prefill"):
+                self._prefill()
         except BackendError as e:
             self.counters["errors"] += 1
             if e.fatal:

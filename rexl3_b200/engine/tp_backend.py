@@ -16,6 +16,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.dense_tp import DenseTPShard
+from ..utils import trace
 from .backend import BackendError, RowOutput
 from .gpu_backend import DenseGpuBackend
 
@@ -143,10 +144,13 @@ def follow(shard: DenseTPShard, max_slots: int, ctrl_group, use_graphs: bool = T
     while True:
         if leave_after and seen >= leave_after:
             break
+        trace.tp_event("F", shard.rank, "wait", seen)
         head, payload = ex.recv()
         seen += 1
+        trace.tp_event("F", shard.rank, f"recv_op{int(head[0])}", int(head[1]))
         if not ex.apply(head, payload):
             break
+        trace.tp_event("F", shard.rank, f"launched_op{int(head[0])}", int(head[1]))
         st = None
         if int(head[0]) == OP_SYNC:
             st = shard.status.tolist()
@@ -194,6 +198,7 @@ class DenseTpBackend(DenseGpuBackend):
         fits = HEAD + payload.size <= SMALL
         if fits:
             msg[HEAD:HEAD + payload.size] = payload
+        trace.tp_event("L", 0, f"send_op{op}", M)
         dist.broadcast(self.ex.msg, src=0, group=self.ex.ctrl)
         if not fits:
             dist.broadcast(torch.from_numpy(np.ascontiguousarray(payload)), src=0, group=self.ex.ctrl)

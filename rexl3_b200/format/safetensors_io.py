@@ -154,7 +154,9 @@ def prefetch(folder: str, entries, threads: int = 8, direct: bool = False, pinne
             stage = torch.empty(max(pos, 1), dtype=torch.uint8).pin_memory().numpy()
         else:
             stage = np.empty(max(pos, 1), dtype=np.uint8)
-        host.read_ranges(path, offs, sizes, stage, starts, threads=threads, direct=direct)
+        from ..utils import loadstats
+        with loadstats.stage("pack", "read", sum(sizes)):
+            host.read_ranges(path, offs, sizes, stage, starts, threads=threads, direct=direct)
         for e, st, n in zip(es, starts, sizes):
             _PREFETCHED[(path, e.file_offset, n)] = stage[st:st + n]
         total += sum(sizes)

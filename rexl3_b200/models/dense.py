@@ -290,6 +290,13 @@ class DenseGPU:
         self._alloc_scratch(self.max_rows)
 
     def _load_host(self, w: HostWeights) -> None:
+        from ..utils import loadstats
+        with loadstats.stage("model", "upload"):
+            self._upload_host(w)
+            torch.cuda.synchronize()
+        loadstats.add("model", "upload", 0.0, self.weight_bytes())
+
+    def _upload_host(self, w: HostWeights) -> None:
         K, device = self.K, self.device
         dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
         up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731

@@ -350,7 +350,7 @@ class HybridGPU(DenseGPU):
         return dict(kind="M", attn_norm=attn_norm, qkv=ip, o=op, in_proj=ip, out_proj=op, conv_w=conv_w, conv_b=conv_b, dt_bias=dt_bias, a_neg=a_neg,
                     d_skip=d_skip, norm_w=norm_w, ffn_norm=ffn_norm, gate_up=gu, down=dn, q_norm=None, k_norm=None)
 
-    def _load_host(self, w: HostWeights) -> None:
+    def _upload_host(self, w: HostWeights) -> None:
         K, device = self.K, self.device
         dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
         up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731

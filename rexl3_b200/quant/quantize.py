@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import json
 import os
+import time
 
 import numpy as np
 
@@ -201,6 +202,8 @@ def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeight
         raise ValueError(f"pack refused: {name}: {why}")
     if ck.issues:
         raise ValueError(f"pack refused: {ck.issues[0]}")
+    from ..utils import loadstats
+    t_assemble = time.perf_counter()
     if threads > 0:
         safetensors_io.prefetch(folder, [e for g in ck.groups.values() for e in g.parts.values()] + list(ck.plain.values()), threads=threads, direct=direct)
 
@@ -238,4 +241,6 @@ def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeight
     w.final_norm = plain("model.norm.weight")
     w.lm_head = lin("lm_head")
     safetensors_io.drop_prefetched()          # tensors the model did not ask for
+    read_s = loadstats.snapshot().get(("pack", "read"), (0.0, 0, 0))[0] if threads > 0 else 0.0
+    loadstats.add("pack", "assemble", max(0.0, time.perf_counter() - t_assemble - read_s), ck.total_bytes())
     return w

@@ -166,7 +166,8 @@ def build_app(st: AppState) -> Starlette:
         return JSONResponse({"object": "list", "data": [m]})
 
     async def metrics(request):
-        return PlainTextResponse(st.handle.metrics.render(), media_type="text/plain; version=0.0.4")
+        from ..utils import loadstats
+        return PlainTextResponse(st.handle.metrics.render() + loadstats.render(), media_type="text/plain; version=0.0.4")
 
     async def tokenize(request):
         try:

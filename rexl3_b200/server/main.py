@@ -42,6 +42,8 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--max-drafts", type=int, default=4)
     p.add_argument("--prefix-cache", choices=["on", "off"], default="on")
     p.add_argument("--prefix-cache-mib", type=int, default=4096)
+    p.add_argument("--verify-pack", choices=["off", "sizes", "crc", "lock"], default="off",
+                   help="check the pack before loading: file sizes against model.lock.json, per-tensor crc32.txt, or the lock's sha256 of every file")
     p.add_argument("--prefix-spill-dir", default="", help="directory (e.g. on NVMe) where prefix blocks evicted from the device cache are kept and reused")
     p.add_argument("--prefix-spill-mib", type=int, default=65536)
     p.add_argument("--default-max-tokens", type=int, default=512)
@@ -97,11 +99,22 @@ def build(args):
             from ..quant import quantize
             with boot.phase("scan_pack", folder=folder):
                 cfg = quantize.config_from_pack(folder)
+            if args.verify_pack != "off":
+                from ..format import verify as pack_verify
+                with boot.phase("verify_pack", mode=args.verify_pack):
+                    issues = (pack_verify.verify_crc(folder) if args.verify_pack == "crc"
+                              else pack_verify.verify_lock(folder, sizes_only=args.verify_pack == "sizes"))
+                    if issues:
+                        raise SystemExit(f"rexl3-serve: pack refused by --verify-pack {args.verify_pack}: {issues[0]}"
+                                         + (f" (+{len(issues) - 1} more)" if len(issues) > 1 else ""))
             with boot.phase("load_pack_host"):
                 weights = quantize.load_pack(folder)          # header scan + refusals by name happen before CUDA starts
         vocab, name = cfg.vocab, args.served_model_name or cfg.name
         kv_tokens = args.kv_tokens or args.slots * args.max_model_len
         info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None, "boot": boot.report}
+        if weights is not None:
+            from ..format import verify as pack_verify
+            info["pack_fingerprint"] = pack_verify.fingerprint(folder)
 
         world = int(os.environ.get("WORLD_SIZE", "1"))
 
