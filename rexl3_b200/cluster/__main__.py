@@ -1,21 +1,35 @@
-"""python -m rexl3_b200.cluster COMMAND --cluster FILE [--group NAME] [--dry-run]      (validate | plan | up | supervise)"""
+"""python -m rexl3_b200.cluster COMMAND --cluster FILE [--group NAME]
+   validate | plan | check | up | supervise | status | down | logs          (--dry-run prints the plan instead of starting anything)"""
 import argparse
 import json
+import os
 import shlex
 import sys
 import urllib.request
 
+from . import ops
 from .schema import ClusterError, load_cluster, rank_commands
 from .supervise import LocalRunner, Policy, supervise
 
 
+def _ready(port: int) -> bool:
+    try:
+        return urllib.request.urlopen(f"http://127.0.0.1:{port}/health/ready", timeout=1).status == 200
+    except Exception:  # noqa: BLE001
+        return False
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="rexl3-cluster", allow_abbrev=False)
-    p.add_argument("command", choices=["validate", "plan", "up", "supervise"])
+    p.add_argument("command", choices=["validate", "plan", "check", "up", "supervise", "status", "down", "logs"])
     p.add_argument("--cluster", required=True)
     p.add_argument("--group", default="")
     p.add_argument("--dry-run", action="store_true")
     p.add_argument("--log-dir", default="")
+    p.add_argument("--state-dir", default=".rexl3-cluster", help="state files and GPU locks of the groups started from here")
+    p.add_argument("--need-mib", type=int, default=0, help="check: free memory every GPU of the group must have")
+    p.add_argument("--no-gpu-probe", action="store_true", help="check: skip the NVML facts (memory, idle)")
+    p.add_argument("--lines", type=int, default=40)
     p.add_argument("--max-runtime", type=float, default=0.0)
     a = p.parse_args(argv)
     try:
@@ -30,24 +44,55 @@ def main(argv=None) -> int:
     if group not in c.groups:
         print("rexl3-cluster: --group NAME is required (the file has several groups)", file=sys.stderr)
         return 2
+    g = c.groups[group]
+    gpus = [c.nodes[n].get("gpu", i) for i, n in enumerate(g.ranks)]
+    locks = ops.GpuLocks(os.path.join(a.state_dir, "locks"))
+    if a.command == "status":
+        print(json.dumps(ops.status(a.state_dir, group, _ready)))
+        return 0
+    if a.command == "down":
+        hit = ops.down(a.state_dir, group, locks, gpus)
+        print(json.dumps({"group": group, "signalled": hit}))
+        return 0
+    if a.command == "logs":
+        st = ops.read_state(a.state_dir, group) or {}
+        log_dir = a.log_dir or st.get("log_dir", "")
+        if not log_dir:
+            print("rexl3-cluster: no log directory is known for this group (--log-dir)", file=sys.stderr)
+            return 2
+        for r, lines in ops.tail_logs(log_dir, len(g.ranks), a.lines).items():
+            print(f"==> rank {r} <==")
+            print("\n".join(lines) if lines is not None else "(no log)")
+        return 0
+    if a.command == "check":
+        checks = ops.preflight(c, group, need_mib=a.need_mib, gpu_probe=None if a.no_gpu_probe else ops.nvml_probe, locks=locks)
+        for ch in checks:
+            print(f"{'ok  ' if ch.ok else 'FAIL'} {ch.name}: {ch.detail}")
+        return 0 if all(ch.ok for ch in checks) else 1
     cmds = rank_commands(c, group, sys.executable)
     if a.command == "plan" or a.dry_run:
         for r, (env, argv_) in enumerate(cmds):
             print(f"rank {r}: " + " ".join(f"{k}={shlex.quote(v)}" for k, v in env.items()) + " " + " ".join(shlex.quote(x) for x in argv_))
         return 0
-    port = c.groups[group].http_port
-
-    def ready():
+    if not locks.acquire(gpus, group):
+        print(f"rexl3-cluster: a GPU of group {group} is locked by another group (see {locks.dir})", file=sys.stderr)
+        return 75
+    if a.log_dir:
+        os.makedirs(a.log_dir, exist_ok=True)
+    runner = LocalRunner(cmds, lambda: _ready(g.http_port), a.log_dir, a.max_runtime,
+                         on_start=lambda pids: ops.write_state(a.state_dir, group, os.getpid(), pids, g.http_port, a.log_dir))
+    try:
+        if a.command == "up":
+            att = runner()
+            return 0 if all(c_ == 0 for c_ in att.codes if c_ is not None) else 1
+        sup = c.supervisor
+        return supervise(runner, Policy(sup.get("backoff_s", Policy().backoff_s), sup.get("window_s", 600.0), sup.get("max_failures", 5)))
+    finally:
+        locks.release(gpus, group)
         try:
-            return urllib.request.urlopen(f"http://127.0.0.1:{port}/health/ready", timeout=1).status == 200
-        except Exception:
-            return False
-    runner = LocalRunner(cmds, ready, a.log_dir, a.max_runtime)
-    if a.command == "up":
-        att = runner()
-        return 0 if all(c_ == 0 for c_ in att.codes if c_ is not None) else 1
-    sup = c.supervisor
-    return supervise(runner, Policy(sup.get("backoff_s", Policy().backoff_s), sup.get("window_s", 600.0), sup.get("max_failures", 5)))
+            os.remove(ops.state_path(a.state_dir, group))
+        except OSError:
+            pass
 
 
 if __name__ == "__main__":

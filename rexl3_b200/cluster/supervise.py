@@ -72,8 +72,10 @@ def supervise(run_attempt, policy: Policy | None = None, sleep=time.sleep, clock
 class LocalRunner:
     """Runs the ranks of a group as child processes of this host (one NVLink box).  The first exit tears the others down by pid."""
 
-    def __init__(self, commands, ready_probe=None, log_dir: str = "", max_runtime_s: float = 0.0):
+    def __init__(self, commands, ready_probe=None, log_dir: str = "", max_runtime_s: float = 0.0, on_start=None):
+        """`on_start(pids)`: called with the ranks' pids once they are started (the CLI records them in the group's state file)."""
         self.commands, self.ready_probe, self.log_dir, self.max_runtime_s = commands, ready_probe, log_dir, max_runtime_s
+        self.on_start = on_start
 
     def __call__(self) -> Attempt:
         import os
@@ -84,6 +86,8 @@ class LocalRunner:
         for r, (env, argv) in enumerate(self.commands):
             out = open(os.path.join(self.log_dir, f"rank{r}.log"), "ab") if self.log_dir else None
             procs.append(subprocess.Popen(argv, env={**os.environ, **env}, stdout=out, stderr=subprocess.STDOUT if out else None, start_new_session=True))
+        if self.on_start is not None:
+            self.on_start([p.pid for p in procs])
         ready = False
         try:
             while True:
