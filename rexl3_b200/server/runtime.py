@@ -101,6 +101,8 @@ class EngineHandle:
     def __init__(self, make_engine, cfg: RuntimeConfig | None = None, metrics: Metrics | None = None):
         self.cfg = cfg or RuntimeConfig()
         self.metrics = metrics or Metrics()
+        for kind in ("Backend", "Fatal", "BackendShape"):        # error counters exist from the start: a dashboard sees 0, not "no data"
+            self.metrics.inc("step_errors_total", 0.0, kind=kind)
         self.cmd: "queue.Queue" = queue.Queue()
         self.state = "loading"
         self.error = ""
