@@ -123,6 +123,7 @@ def build(args):
             from ..engine.tp_backend import DenseTpBackend
             from ..parallel import runtime as tprt
             ctx = tprt.init(timeout_s=600)
+            _tp_boot_gate(args, cfg, ctx)
             blocks = -(-args.max_model_len // dense.PAGE) + 1
             pages = -(-kv_tokens // dense.PAGE) + args.slots
             shard, _group = tprt.build_dense_tp(ctx, cfg, num_pages=pages, max_rows=max(256, args.prefill_chunk), max_slots=args.slots,
@@ -195,6 +196,14 @@ def build(args):
     return make, tok, fmt, name, info
 
 
+def _tp_boot_gate(args, cfg, ctx) -> None:
+    """Every rank of the group must be about to run the same thing (raises BootGateError on all ranks otherwise)."""
+    from ..parallel import bootgate
+    flags = dict(slots=args.slots, max_model_len=args.max_model_len, prefill_chunk=args.prefill_chunk, kv_tokens=args.kv_tokens,
+                 graphs=not args.no_graphs, random_init=args.random_init or "")
+    bootgate.gate(bootgate.collect_facts(cfg, world=ctx.world, pack=args.model or None, flags=flags), ctx.ctrl)
+
+
 def _spill_store(args, prefix):
     if prefix is None or not args.prefix_spill_dir:
         return None
@@ -216,6 +225,11 @@ def follow_rank(args) -> int:
             cfg, weights = quantize.config_from_pack(args.model), quantize.load_pack(args.model)
         kv_tokens = args.kv_tokens or args.slots * args.max_model_len
         ctx = tprt.init(timeout_s=600)
+        try:
+            _tp_boot_gate(args, cfg, ctx)
+        except Exception as e:  # a group that disagrees is refused (exit status 2: the supervisor does not restart a refusal blindly)
+            print(f"rexl3 level=error event=boot_refused rank={os.environ.get('RANK')} error={e}", file=sys.stderr, flush=True)
+            return 2
         shard, group = tprt.build_dense_tp(ctx, cfg, num_pages=-(-kv_tokens // dense.PAGE) + args.slots, max_rows=max(256, args.prefill_chunk),
                                            max_slots=args.slots, max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, weights=weights)
         follow(shard, args.slots, ctx.ctrl, use_graphs=not args.no_graphs)
