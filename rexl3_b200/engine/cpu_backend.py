@@ -70,3 +70,32 @@ class CpuDenseBackend(Backend):
         for a in range(0, len(tokens), chunk):
             row = self.model.forward_seq(slot, tokens[a:a + chunk], a)[-1]
         return row.numpy().astype("float32")
+
+
+class CpuHybridBackend(CpuDenseBackend):
+    """The fp32 hybrid (Mamba2 / delta-net + attention) oracle behind the Backend contract.  Rows cannot be rejected once fed
+    (`supports_rollback` is False, the engine plans no drafts); prompt scoring undoes its rows through a state snapshot."""
+    name = "cpu-hybrid-reference"
+
+    def __init__(self, weights: HostWeights, max_slots: int = 8, max_rows: int = 64, dtype=torch.float32):
+        from ..models.hybrid import ReferenceHybrid
+        self.model = ReferenceHybrid(weights, device="cpu", dtype=dtype)
+        self.cfg = weights.cfg
+        self.vocab_size = weights.cfg.vocab
+        self.max_slots, self.max_rows = max_slots, max_rows
+        self.len, self.pending, self.last_logits = {}, {}, None
+
+    def supports_rollback(self) -> bool:
+        return False
+
+    def commit(self, slot, keep):
+        fed = self.pending.pop(slot, 0)
+        if keep < fed:
+            raise BackendError(f"slot {slot}: {fed - keep} rows rejected, but this backend cannot roll back", fatal=False)
+        self.len[slot] = self.len.get(slot, 0) + fed
+
+    def score_rows(self, slot, start, tokens):
+        snap = self.model.snapshot(slot)
+        logits = self.model.forward_seq(slot, tokens, start)
+        self.model.restore(slot, snap)
+        return logits.numpy()

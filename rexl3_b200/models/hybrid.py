@@ -227,14 +227,41 @@ class ReferenceHybrid(ReferenceDense):
             self.inv_freq.zero_()
         self.kv = {}
         self.ssm = {}          # (seq, layer) -> (conv history [3, C], state [H, P, N])
+        self.seq_len = {}
 
     def reset(self, seq=None):
         super().reset(seq)
         for k in [k for k in self.ssm if seq is None or k[0] == seq]:
             del self.ssm[k]
+        if seq is None:
+            self.seq_len.clear()
+        else:
+            self.seq_len.pop(seq, None)
+
+    @torch.no_grad()
+    def forward_seq(self, seq, tokens, start: int, n_layers: int | None = None):
+        out = super().forward_seq(seq, tokens, start, n_layers)
+        self.seq_len[seq] = start + len(tokens)
+        return out
 
     def truncate(self, seq, length: int):
-        raise NotImplementedError("a recurrent state cannot be rolled back")
+        """Only the no-op is possible: a recurrent state cannot be rolled back (callers that must undo rows use snapshot / restore)."""
+        if length != self.seq_len.get(seq, 0):
+            raise NotImplementedError("a recurrent state cannot be rolled back")
+
+    def snapshot(self, seq):
+        """Everything `seq` has accumulated (attention KV, conv histories, recurrent states, length), for `restore`."""
+        return (self.seq_len.get(seq, 0), None if seq not in self.kv else [(k.clone(), v.clone()) for k, v in self.kv[seq]],
+                {k: (c.clone(), s.clone()) for k, (c, s) in self.ssm.items() if k[0] == seq})
+
+    def restore(self, seq, snap) -> None:
+        n, kv, ssm = snap
+        self.reset(seq)
+        self.seq_len[seq] = n
+        if kv is not None:
+            self.kv[seq] = [(k.clone(), v.clone()) for k, v in kv]
+        for k, (c, s) in ssm.items():
+            self.ssm[k] = (c.clone(), s.clone())
 
     def _mix(self, li, L, h, pos, seq, start):
         if L["kind"] == "A":

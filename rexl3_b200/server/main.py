@@ -142,7 +142,12 @@ def build(args):
                 return make_tp()
             if args.backend == "cpu":
                 from ..engine.cpu_backend import CpuDenseBackend
-                be = CpuDenseBackend(weights if weights is not None else dense.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
+                from ..models import hybrid as hybrid_models
+                if isinstance(cfg, hybrid_models.HybridConfig):
+                    from ..engine.cpu_backend import CpuHybridBackend
+                    be = CpuHybridBackend(hybrid_models.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
+                else:
+                    be = CpuDenseBackend(weights if weights is not None else dense.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
                 adm, prefix = None, None
             else:
                 import torch

@@ -78,3 +78,34 @@ def test_engine_plans_no_drafts_without_rollback():
             if ev.kind == "tokens":
                 n += len(ev.tokens)
     assert n == 12
+
+
+@pytest.mark.parametrize("cfg", [SMALL, GDN], ids=["mamba2", "gdn"])
+def test_engine_exactness_checks_on_the_cpu_hybrid_backend(cfg):
+    """The engine's exactness harness over the fp32 hybrid oracle: a stream's tokens do not depend on its window mates, on batching or on
+    how the prompt was chunked; a request with drafts enabled decodes the same tokens (the engine plans none for this backend)."""
+    from rexl3_b200.engine import harness
+    from rexl3_b200.engine.cpu_backend import CpuHybridBackend
+    w = hybrid.random_weights(cfg, seed=5)
+
+    def make():
+        return CpuHybridBackend(w, max_slots=4, max_rows=16)
+    for check in ("row_invariance", "serial_batched_equals_solo", "chunked_prefill_equals_whole", "drafted_equals_serial"):
+        assert getattr(harness, check)(make, cfg.vocab, n=6) is None, check
+
+
+def test_cpu_hybrid_backend_scoring_leaves_the_state_untouched():
+    from rexl3_b200.engine.backend import RowRequest
+    from rexl3_b200.engine.cpu_backend import CpuHybridBackend
+    be = CpuHybridBackend(hybrid.random_weights(SMALL, seed=5), max_slots=2)
+    toks = [5, 9, 200, 31, 7, 7, 100]
+    be.prefill_slice(0, 0, toks[:4], 8, True)
+    a = be.score_rows(0, 4, toks[4:])
+    b = be.score_rows(0, 4, toks[4:])                 # scoring twice gives the same rows: the first call did not advance the state
+    assert np.array_equal(a, b)
+    out = be.step([RowRequest(0, [toks[4]], 4)], 8)
+    assert int(out[0][0].ids[0]) == int(np.argmax(a[0]))
+    be.commit(0, 1)
+    with pytest.raises(Exception):
+        be.step([RowRequest(0, [1, 2], 5)], 8)
+        be.commit(0, 1)                               # rejecting a fed row is refused
