@@ -151,15 +151,30 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
         if l.bias is not None:
             tensors[prefix + ".bias"] = l.bias.astype(np.float32)
 
+    def put_f32(name, a):
+        tensors[name] = np.ascontiguousarray(a, dtype=np.float32)
+
     put_plain("model.embed_tokens.weight", w.embed)
     for i, L in enumerate(w.layers):
         p = f"model.layers.{i}."
         put_plain(p + "input_layernorm.weight", L.attn_norm)
         put_plain(p + "post_attention_layernorm.weight", L.ffn_norm)
-        put_lin(p + "self_attn.qkv_proj", L.qkv)
-        put_lin(p + "self_attn.o_proj", L.o)
         put_lin(p + "mlp.gate_up_proj", L.gate_up)
         put_lin(p + "mlp.down_proj", L.down)
+        if not isinstance(L, HostLayer):              # a recurrent mixer of the hybrid family (Mamba2: "mixer", delta-net: "linear_attn")
+            m = p + ("mixer." if hasattr(L, "d_skip") else "linear_attn.")
+            put_lin(m + "in_proj", L.in_proj)
+            put_lin(m + "out_proj", L.out_proj)
+            put_plain(m + "conv1d.weight", L.conv_w)
+            put_plain(m + "conv1d.bias", L.conv_b)
+            put_plain(m + "norm.weight", L.norm_w)
+            put_f32(m + "dt_bias", L.dt_bias)
+            put_f32(m + "A_log", L.a_log)
+            if hasattr(L, "d_skip"):
+                put_f32(m + "D", L.d_skip)
+            continue
+        put_lin(p + "self_attn.qkv_proj", L.qkv)
+        put_lin(p + "self_attn.o_proj", L.o)
         if L.q_norm is not None:
             put_plain(p + "self_attn.q_norm.weight", L.q_norm)
             put_plain(p + "self_attn.k_norm.weight", L.k_norm)
@@ -173,6 +188,11 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
             "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps, "rope_theta": cfg.rope_theta, "qk_norm": cfg.qk_norm, "name": cfg.name,
             "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": cfg.bits, "head_bits": cfg.head_bits or cfg.bits,
                                     "codebook": cfg.codebook, "fused_projections": True}}
+    if hasattr(cfg, "pattern"):
+        conf.update({"architectures": ["Rexl3HybridForCausalLM"], "model_type": "rexl3_hybrid",
+                     "hybrid": {"pattern": cfg.pattern, "ssm_heads": cfg.ssm_heads, "ssm_head_dim": cfg.ssm_head_dim, "ssm_groups": cfg.ssm_groups,
+                                "ssm_state": cfg.ssm_state, "conv_k": cfg.conv_k, "nope": cfg.nope, "gdn_k_heads": cfg.gdn_k_heads,
+                                "gdn_v_heads": cfg.gdn_v_heads}})
     extra = dict(extra_config or {})
     if "calibration" in extra:                    # what the pack was calibrated on belongs to the quantization record
         conf["quantization_config"]["calibration"] = extra.pop("calibration")
@@ -186,10 +206,16 @@ def config_from_pack(folder: str) -> DenseConfig:
     q = c.get("quantization_config") or (c.get("text_config") or {}).get("quantization_config")
     if not q or q.get("quant_method") != "exl3":
         raise ValueError("config.json has no quantization_config with quant_method exl3")
-    return DenseConfig(n_layers=c["num_hidden_layers"], d_model=c["hidden_size"], n_q=c["num_attention_heads"], n_kv=c["num_key_value_heads"],
-                       head_dim=c.get("head_dim", c["hidden_size"] // c["num_attention_heads"]), ffn=c["intermediate_size"], vocab=c["vocab_size"],
-                       eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), qk_norm=bool(c.get("qk_norm", False)),
-                       bits=float(q.get("bits", 4.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "dense"))
+    common = dict(n_layers=c["num_hidden_layers"], d_model=c["hidden_size"], n_q=c["num_attention_heads"], n_kv=c["num_key_value_heads"],
+                  head_dim=c.get("head_dim", c["hidden_size"] // c["num_attention_heads"]), ffn=c["intermediate_size"], vocab=c["vocab_size"],
+                  eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), qk_norm=bool(c.get("qk_norm", False)),
+                  bits=float(q.get("bits", 4.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "dense"))
+    if c.get("model_type") == "rexl3_hybrid":
+        from ..models.hybrid import HybridConfig
+        cfg = HybridConfig(**common, **(c.get("hybrid") or {}))
+        cfg.validate()
+        return cfg
+    return DenseConfig(**common)
 
 
 def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeights:
@@ -230,9 +256,27 @@ def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeight
             raise ValueError(f"pack refused: no tensor {name}")
         return checkpoint.load_plain(folder, e).astype(np.float32)
 
+    def f32(name):
+        e = ck.plain.get(name)
+        if e is None:
+            raise ValueError(f"pack refused: no tensor {name}")
+        return checkpoint.load_plain(folder, e).astype(np.float32)
+
     w = HostWeights(cfg, plain("model.embed_tokens.weight"))
     for i in range(cfg.n_layers):
         p = f"model.layers.{i}."
+        kind = getattr(cfg, "pattern", "A" * cfg.n_layers)[i]
+        if kind != "A":
+            from ..models.hybrid import HostGdnLayer, HostMambaLayer
+            m = p + ("mixer." if kind == "M" else "linear_attn.")
+            shared = (plain(p + "input_layernorm.weight"), lin(m + "in_proj"), lin(m + "out_proj"), plain(m + "conv1d.weight"), plain(m + "conv1d.bias"),
+                      f32(m + "dt_bias"), f32(m + "A_log"))
+            tail = (plain(p + "post_attention_layernorm.weight"), fused(p + "mlp.", "gate_up_proj", ["gate_proj", "up_proj"]), lin(p + "mlp.down_proj"))
+            if kind == "M":
+                w.layers.append(HostMambaLayer(*shared, f32(m + "D"), plain(m + "norm.weight"), *tail))
+            else:
+                w.layers.append(HostGdnLayer(*shared, plain(m + "norm.weight"), *tail, kind == "K"))
+            continue
         lay = HostLayer(plain(p + "input_layernorm.weight"), fused(p + "self_attn.", "qkv_proj", ["q_proj", "k_proj", "v_proj"]), lin(p + "self_attn.o_proj"),
                         plain(p + "post_attention_layernorm.weight"), fused(p + "mlp.", "gate_up_proj", ["gate_proj", "up_proj"]), lin(p + "mlp.down_proj"))
         if cfg.qk_norm:

@@ -145,7 +145,7 @@ def build(args):
                 from ..models import hybrid as hybrid_models
                 if isinstance(cfg, hybrid_models.HybridConfig):
                     from ..engine.cpu_backend import CpuHybridBackend
-                    be = CpuHybridBackend(hybrid_models.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
+                    be = CpuHybridBackend(weights if weights is not None else hybrid_models.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
                 else:
                     be = CpuDenseBackend(weights if weights is not None else dense.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
                 adm, prefix = None, None
@@ -179,7 +179,7 @@ def build(args):
                 elif is_moe:
                     model = moe_models.MoEGPU(cfg, **common)
                 elif is_hybrid:
-                    model = hybrid_models.HybridGPU(cfg, **common)
+                    model = hybrid_models.HybridGPU(weights if weights is not None else cfg, **common)
                 else:
                     model = dense.DenseGPU(weights if weights is not None else cfg, kv_dtype=args.kv_dtype, **common)
                 if args.kv_dtype == "fp8":

@@ -109,3 +109,25 @@ def test_cpu_hybrid_backend_scoring_leaves_the_state_untouched():
     with pytest.raises(Exception):
         be.step([RowRequest(0, [1, 2], 5)], 8)
         be.commit(0, 1)                               # rejecting a fed row is refused
+
+
+def test_hybrid_pack_roundtrip(tmp_path):
+    """A hybrid model written as a pack and loaded back is the same model: config, every tensor, and the oracle's logits."""
+    from rexl3_b200.format import verify
+    from rexl3_b200.quant import quantize
+    cfg = dataclasses.replace(SMALL, pattern="MKG", gdn_k_heads=1, gdn_v_heads=2, n_layers=3, name="cpu-pack")
+    w = hybrid.random_weights(cfg, seed=8)
+    folder = str(tmp_path / "pack")
+    quantize.write_pack(folder, w)
+    cfg2 = quantize.config_from_pack(folder)
+    assert isinstance(cfg2, hybrid.HybridConfig)
+    assert dataclasses.asdict(cfg2) == dataclasses.asdict(dataclasses.replace(cfg, head_bits=cfg.bits))      # the pack records the head width explicitly
+    w2 = quantize.load_pack(folder)
+    for a, b in zip(w.layers, w2.layers):
+        assert type(a) is type(b)
+        assert np.array_equal(a.in_proj.trellis, b.in_proj.trellis) and np.array_equal(a.out_proj.svh, b.out_proj.svh)
+        assert np.array_equal(a.dt_bias, b.dt_bias) and np.array_equal(a.a_log, b.a_log) and np.array_equal(a.conv_w, b.conv_w)
+        assert getattr(a, "kda", None) == getattr(b, "kda", None)
+    toks = [3, 99, 250, 17, 400, 8]
+    assert torch.equal(hybrid.ReferenceHybrid(w).forward_seq(0, toks, 0), hybrid.ReferenceHybrid(w2).forward_seq(0, toks, 0))
+    assert len(verify.fingerprint(folder)) == 64
