@@ -119,6 +119,9 @@ CONFIGS = {
                                     pattern="GAMG", nope=False, ssm_heads=16, ssm_groups=2, gdn_k_heads=2, gdn_v_heads=4),
     "test-hybrid-kda": HybridConfig(n_layers=3, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid-kda",
                                     pattern="KAK", nope=True, gdn_k_heads=4, gdn_v_heads=4),
+    # CPU plumbing model of the family (one layer of each recurrent kind and one attention layer; quantizes in seconds on the host)
+    "tiny-hybrid": HybridConfig(n_layers=3, d_model=128, n_q=2, n_kv=1, head_dim=64, ffn=128, vocab=256, bits=4.0, name="tiny-hybrid", pattern="MGA",
+                                ssm_heads=2, ssm_groups=1, gdn_k_heads=1, gdn_v_heads=1),
     "test-hybrid": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid",
                                 pattern="MAMM", ssm_heads=16, ssm_groups=2),
 }

@@ -11,10 +11,10 @@ import time
 
 
 def main(argv=None) -> int:
-    from ..models import dense
+    from ..models import dense, hybrid
     from . import quantize
     p = argparse.ArgumentParser(prog="rexl3-quant", allow_abbrev=False)
-    p.add_argument("--arch", required=True, choices=sorted(k for k, v in dense.CONFIGS.items() if type(v) is dense.DenseConfig))
+    p.add_argument("--arch", required=True, choices=sorted([k for k, v in dense.CONFIGS.items() if type(v) is dense.DenseConfig] + list(hybrid.CONFIGS)))
     p.add_argument("--out", required=True)
     p.add_argument("--bits", type=float, default=0.0, help="override the architecture's bits per weight (1, 1.5, ... 8)")
     p.add_argument("--seed", type=int, default=0)
@@ -26,12 +26,20 @@ def main(argv=None) -> int:
     p.add_argument("--damp", type=float, default=0.01)
     p.add_argument("--device", default="cpu", help="cpu (host Viterbi, all cores) or cuda (one CTA per tile; same bits)")
     a = p.parse_args(argv)
-    cfg = dense.CONFIGS[a.arch]
+    is_hybrid = a.arch in hybrid.CONFIGS
+    cfg = hybrid.CONFIGS[a.arch] if is_hybrid else dense.CONFIGS[a.arch]
     if a.bits:
         cfg = dataclasses.replace(cfg, bits=a.bits)
     if a.layers:
-        cfg = dataclasses.replace(cfg, n_layers=a.layers)
+        cfg = dataclasses.replace(cfg, n_layers=a.layers, **({"pattern": cfg.pattern[:a.layers]} if is_hybrid else {}))
     t0 = time.time()
+    if is_hybrid:
+        if a.calibrate:
+            p.error("--calibrate is available for the dense family")
+        w = quantize.quantize_hybrid(cfg, quantize.random_fp_weights_hybrid(cfg, a.seed), seed=a.seed, threads=a.threads, device=a.device)
+        quantize.write_pack(a.out, w)
+        print(f"rexl3-quant: wrote {a.out} ({cfg.name}, {cfg.bits:g} bpw, {cfg.n_layers} layers, pattern {cfg.pattern}) in {time.time() - t0:.1f} s")
+        return 0
     fp = quantize.random_fp_weights(cfg, a.seed)
     hessians, extra = None, None
     if a.calibrate:

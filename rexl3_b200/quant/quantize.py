@@ -114,6 +114,62 @@ def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0, 
     return w
 
 
+def quantize_hybrid(cfg, fp: dict, seed: int = 0, threads: int = 0, device: str = "cpu") -> HostWeights:
+    """fp: float weights of a hybrid decoder (`random_fp_weights_hybrid` shows the keys): attention layers as in `quantize_dense`; recurrent
+    layers carry in_proj [d, real width] (padded here to the stored width with zero columns), out_proj [inner, d] and their small tensors."""
+    from ..models.hybrid import HostGdnLayer, HostMambaLayer
+    cfg.validate()
+    d, F, V = cfg.d_model, cfg.ffn_padded, cfg.vocab_padded
+    ql = lambda m, bits, sd: quantize_linear(m, bits, cfg.codebook, sd, threads=threads, device=device)  # noqa: E731
+    f32 = lambda a: np.asarray(a, np.float32)  # noqa: E731
+    bf = lambda a: _bf16_bits_to_f32(_f32_to_bf16_bits(f32(a)))  # noqa: E731  (stored as bf16: round now so the pack round trip is exact)
+    w = HostWeights(cfg, bf(fp["embed"]))
+    for i, (kind, L) in enumerate(zip(cfg.pattern, fp["layers"])):
+        gu = ql(np.concatenate([pad_to(L["gate"], d, F), pad_to(L["up"], d, F)], axis=1), cfg.bits, seed + 10 * i + 3)
+        down = ql(pad_to(L["down"], F, d), cfg.bits, seed + 10 * i + 4)
+        if kind == "A":
+            w.layers.append(HostLayer(bf(L["attn_norm"]), ql(np.concatenate([L["q"], L["k"], L["v"]], axis=1), cfg.bits, seed + 10 * i + 1),
+                                      ql(L["o"], cfg.bits, seed + 10 * i + 2), bf(L["ffn_norm"]), gu, down))
+            continue
+        width = cfg.in_proj_width if kind == "M" else cfg.delta_proj_width(kind)
+        ip = ql(pad_to(L["in_proj"], d, width), cfg.bits, seed + 10 * i + 1)
+        op = ql(L["out_proj"], cfg.bits, seed + 10 * i + 2)
+        if kind == "M":
+            w.layers.append(HostMambaLayer(bf(L["attn_norm"]), ip, op, bf(L["conv_w"]), bf(L["conv_b"]), f32(L["dt_bias"]), f32(L["a_log"]), f32(L["d_skip"]),
+                                           bf(L["norm_w"]), bf(L["ffn_norm"]), gu, down))
+        else:
+            w.layers.append(HostGdnLayer(bf(L["attn_norm"]), ip, op, bf(L["conv_w"]), bf(L["conv_b"]), f32(L["dt_bias"]), f32(L["a_log"]), bf(L["norm_w"]),
+                                         bf(L["ffn_norm"]), gu, down, kind == "K"))
+    w.final_norm = bf(fp["final_norm"])
+    w.lm_head = ql(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, seed + 7777)
+    return w
+
+
+def random_fp_weights_hybrid(cfg, seed: int = 0, std: float = 0.02) -> dict:
+    """N(0, std) matrices and usual-range SSM parameters for every layer kind of a hybrid config."""
+    rng = np.random.default_rng(seed)
+    d, hd = cfg.d_model, cfg.head_dim
+    g = lambda *s: rng.normal(0, std, size=s).astype(np.float32)  # noqa: E731
+    ones = lambda n: np.ones(n, np.float32)  # noqa: E731
+    layers = []
+    for kind in cfg.pattern:
+        L = dict(attn_norm=ones(d), ffn_norm=ones(d), gate=g(d, cfg.ffn), up=g(d, cfg.ffn), down=g(cfg.ffn, d))
+        if kind == "A":
+            L.update(q=g(d, cfg.n_q * hd), k=g(d, cfg.n_kv * hd), v=g(d, cfg.n_kv * hd), o=g(cfg.n_q * hd, d))
+        elif kind == "M":
+            H, DI, C = cfg.ssm_heads, cfg.d_inner, cfg.conv_channels
+            L.update(in_proj=g(d, DI + C + H), out_proj=g(DI, d), conv_w=rng.normal(0, 0.5, size=(C, 4)).astype(np.float32), conv_b=np.zeros(C, np.float32),
+                     dt_bias=rng.uniform(-3, -1, size=H).astype(np.float32), a_log=np.log(rng.uniform(1, 16, size=H)).astype(np.float32),
+                     d_skip=ones(H), norm_w=ones(DI))
+        else:
+            Hv, GI, C = cfg.gdn_v_heads, cfg.gdn_inner, cfg.gdn_conv_channels
+            L.update(in_proj=g(d, GI + C + Hv + (GI if kind == "K" else Hv)), out_proj=g(GI, d), conv_w=rng.normal(0, 0.5, size=(C, 4)).astype(np.float32),
+                     conv_b=np.zeros(C, np.float32), dt_bias=rng.uniform(-2, 0, size=GI if kind == "K" else Hv).astype(np.float32),
+                     a_log=np.log(rng.uniform(0.5, 4, size=Hv)).astype(np.float32), norm_w=ones(128))
+        layers.append(L)
+    return dict(embed=g(cfg.vocab, d), layers=layers, final_norm=ones(d), lm_head=g(d, cfg.vocab))
+
+
 def random_fp_weights(cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> dict:
     """N(0, std) matrices from a seed (norm weights 1), the shape BASELINE config 1 names."""
     rng = np.random.default_rng(seed)
@@ -125,6 +181,10 @@ def random_fp_weights(cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> dic
 
 
 # ----------------------------------------------------------------------------------------------------- pack I/O
+def _bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
 def _f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
     return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)

@@ -131,3 +131,27 @@ def test_hybrid_pack_roundtrip(tmp_path):
     toks = [3, 99, 250, 17, 400, 8]
     assert torch.equal(hybrid.ReferenceHybrid(w).forward_seq(0, toks, 0), hybrid.ReferenceHybrid(w2).forward_seq(0, toks, 0))
     assert len(verify.fingerprint(folder)) == 64
+
+
+def test_quantize_hybrid_cli_writes_a_loadable_pack_close_to_the_float_model(tmp_path):
+    from rexl3_b200.quant import quantize
+    from rexl3_b200.quant.__main__ import main as quant_main
+    cfg = dataclasses.replace(hybrid.CONFIGS["tiny-hybrid"], n_layers=2, pattern="MG", bits=6.0, name="cpu-q")
+    fp = quantize.random_fp_weights_hybrid(cfg, seed=2)
+    w = quantize.quantize_hybrid(cfg, fp, seed=2)
+    # each quantized projection reproduces its float matrix (zero-padded to the stored width) to 6-bit accuracy
+    for L, F in zip(w.layers, fp["layers"]):
+        proj, ref = (L.qkv, np.concatenate([F["q"], F["k"], F["v"]], axis=1)) if hasattr(L, "qkv") else (L.in_proj, F["in_proj"])
+        got = proj.dense()[:, :ref.shape[1]]
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < 0.05
+        pad = proj.dense()[:, ref.shape[1]:]             # columns nothing reads: only quantization noise of their shared 128-block
+        assert pad.size == 0 or np.abs(pad).max() < 0.1 * np.abs(ref).max()
+    folder = str(tmp_path / "q")
+    quantize.write_pack(folder, w)
+    w2 = quantize.load_pack(folder)
+    toks = [3, 99, 250, 17]
+    assert torch.equal(hybrid.ReferenceHybrid(w).forward_seq(0, toks, 0), hybrid.ReferenceHybrid(w2).forward_seq(0, toks, 0))
+    # the command-line entry point on a built-in hybrid config (two layers of it)
+    assert quant_main(["--arch", "tiny-hybrid", "--out", str(tmp_path / "cli"), "--layers", "1"]) == 0
+    c2 = quantize.config_from_pack(str(tmp_path / "cli"))
+    assert c2.pattern == "M" and c2.n_layers == 1 and len(quantize.load_pack(str(tmp_path / "cli")).layers) == 1
