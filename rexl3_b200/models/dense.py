@@ -60,10 +60,10 @@ class DenseConfig:
 
 
 CONFIGS = {
-    # BASELINE config 1: CPU plumbing model
+    # benchmark configuration 1: CPU plumbing model
     "tiny-llama": DenseConfig(n_layers=2, d_model=256, n_q=4, n_kv=2, head_dim=64, ffn=688, vocab=2048, eps=1e-6, rope_theta=1e4,
                               bits=4.0, name="tiny-llama"),
-    # BASELINE config 2: 27B-class dense GQA decoder
+    # benchmark configuration 2: 27B-class dense GQA decoder
     "dense-27b": DenseConfig(n_layers=64, d_model=5120, n_q=40, n_kv=8, head_dim=128, ffn=17408, vocab=151936, eps=1e-6, rope_theta=1e6,
                              bits=4.0, name="dense-27b"),
     # small GPU test model with the production head geometry

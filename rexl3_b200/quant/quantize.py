@@ -171,7 +171,7 @@ def random_fp_weights_hybrid(cfg, seed: int = 0, std: float = 0.02) -> dict:
 
 
 def random_fp_weights(cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> dict:
-    """N(0, std) matrices from a seed (norm weights 1), the shape BASELINE config 1 names."""
+    """N(0, std) matrices from a seed (norm weights 1), the shape of the CPU plumbing benchmark configuration."""
     rng = np.random.default_rng(seed)
     d, hd = cfg.d_model, cfg.head_dim
     g = lambda *s: rng.normal(0, std, size=s).astype(np.float32)  # noqa: E731
