@@ -108,7 +108,7 @@ class Engine:
         self.free_slots = list(range(backend.max_slots - 1, -1, -1)) if admission is None else None
         self.events: list = []
         self.counters = dict(rounds=0, rows=0, prefill_tokens=0, decode_tokens=0, drafted=0, accepted=0, cached_tokens=0, requests=0,
-                             finished=0, errors=0)
+                             finished=0, errors=0, spilled_blocks=0, unspilled_blocks=0)
         self.phase_ns = dict(draft=0, verify=0, commit=0, prefill=0)
         self.pause_decode = False      # hold decode rounds (used while a benchmark fills the batch with prompts)
 
@@ -227,7 +227,7 @@ class Engine:
             return
         payload = self.backend.prefix_export(entry.handle)
         if payload is not None and self.spill.put(entry.key, payload):
-            self.counters["spilled_blocks"] = self.counters.get("spilled_blocks", 0) + 1
+            self.counters["spilled_blocks"] += 1
 
     def _spill_in(self, s: _Seq, chain: list) -> list:
         """Continue a device-cache chain with blocks held by the spill tier: import each into the backend and the index, in order."""
@@ -249,7 +249,7 @@ class Engine:
                 break
             chain = chain + [e]
             k += 1
-            self.counters["unspilled_blocks"] = self.counters.get("unspilled_blocks", 0) + 1
+            self.counters["unspilled_blocks"] += 1
         return chain
 
     # ------------------------------------------------------------------ the step

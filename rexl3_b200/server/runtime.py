@@ -243,8 +243,17 @@ class EngineHandle:
             c = eng.counters
             m.set("active_sequences", eng.active_count())
             m.set("queued_requests", len(eng.waiting))
-            for k in ("decode_tokens", "prefill_tokens", "drafted", "accepted", "rounds", "cached_tokens"):
-                m.set(f"engine_{k}_total", c[k])
+            for k in ("decode_tokens", "prefill_tokens", "drafted", "accepted", "rounds", "cached_tokens", "spilled_blocks", "unspilled_blocks"):
+                m.set(f"engine_{k}_total", c.get(k, 0))
+            if eng.prefix is not None:
+                m.set("prefix_cache_bytes", eng.prefix.bytes)
+                m.set("prefix_cache_entries", len(eng.prefix))
+                m.set("prefix_cache_reach_tokens", eng.prefix.reach_tokens())
+                for k in ("lookups", "hits", "hit_blocks", "inserts", "evictions", "ghost_hits"):
+                    m.set(f"prefix_cache_{k}_total", eng.prefix.stats[k])
+            if getattr(eng, "spill", None) is not None:
+                m.set("prefix_spill_bytes", eng.spill.bytes)
+                m.set("prefix_spill_entries", len(eng.spill))
 
     def _route(self, events) -> None:
         for ev in events:
