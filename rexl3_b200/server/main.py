@@ -124,6 +124,12 @@ def build(args):
             from ..parallel import runtime as tprt
             ctx = tprt.init(timeout_s=600)
             _tp_boot_gate(args, cfg, ctx)
+            if _is_expert_family(cfg):
+                # expert parallel: every rank runs the whole step on replicated activations; rank 0's backend calls are replayed by the others
+                from ..engine.lockstep import LockstepLeader
+                be = LockstepLeader(_build_ep_backend(args, cfg, ctx, kv_tokens), ctx.ctrl)
+                return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
+                              max_drafts=args.max_drafts, prefix=None, cache_namespace=name.encode())
             blocks = -(-args.max_model_len // dense.PAGE) + 1
             pages = -(-kv_tokens // dense.PAGE) + args.slots
             shard, _group = tprt.build_dense_tp(ctx, cfg, num_pages=pages, max_rows=max(256, args.prefill_chunk), max_slots=args.slots,
@@ -209,6 +215,35 @@ def _tp_boot_gate(args, cfg, ctx) -> None:
     bootgate.gate(bootgate.collect_facts(cfg, world=ctx.world, pack=args.model or None, flags=flags), ctx.ctrl)
 
 
+def _build_ep_backend(args, cfg, ctx, kv_tokens):
+    """This rank's share of an expert-parallel group for the MoE and MLA + MoE families (experts owned by rank, MLA heads split by rank,
+    activations replicated; the combine is the fused all-reduce over the symmetric arena) behind the single-GPU backend class.  The same
+    construction the family benchmarks use (`bench/spec_moe.py`, `bench/mla_moe.py`)."""
+    from ..engine.gpu_backend import DenseGpuBackend
+    from ..models import dense
+    from ..models import mla as mla_models
+    from ..models import moe as moe_models
+    from ..parallel import ep as eplib
+    comm = eplib.make_ipc(cfg, ctx.rank, ctx.world, args.prefill_chunk, ctx.device, ctx.ctrl)
+    experts = eplib.expert_range(cfg.n_experts, ctx.rank, ctx.world)
+    common = dict(num_pages=-(-kv_tokens // dense.PAGE) + args.slots, max_rows=min(256, args.window_rows), max_seqs=args.slots,
+                  max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, max_prefill_rows=args.prefill_chunk, seed=0)
+    if isinstance(cfg, mla_models.MlaConfig):
+        if cfg.n_heads % ctx.world:
+            raise RuntimeError(f"{cfg.n_heads} MLA heads do not split over {ctx.world} ranks")
+        hp = cfg.n_heads // ctx.world
+        model = mla_models.MlaMoEGPU(cfg, heads=(ctx.rank * hp, (ctx.rank + 1) * hp), experts=experts, comm=comm, rank=ctx.rank, **common)
+    else:
+        model = moe_models.MoEGPU(cfg, experts=experts, ep=comm, **common)
+    return DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs)
+
+
+def _is_expert_family(cfg) -> bool:
+    from ..models import mla as mla_models
+    from ..models import moe as moe_models
+    return isinstance(cfg, (mla_models.MlaConfig, moe_models.MoEConfig))
+
+
 def _spill_store(args, prefix):
     if prefix is None or not args.prefix_spill_dir:
         return None
@@ -224,7 +259,10 @@ def follow_rank(args) -> int:
     from ..parallel import runtime as tprt
     try:
         if args.random_init:
-            cfg, weights = dense.CONFIGS[args.random_init], None
+            from ..models import mla as mla_models
+            from ..models import moe as _moe_models  # noqa: F401  (registers the MoE configs)
+            cfg = mla_models.CONFIGS[args.random_init] if args.random_init in mla_models.CONFIGS else dense.CONFIGS[args.random_init]
+            weights = None
         else:
             from ..quant import quantize
             cfg, weights = quantize.config_from_pack(args.model), quantize.load_pack(args.model)
@@ -235,6 +273,12 @@ def follow_rank(args) -> int:
         except Exception as e:  # a group that disagrees is refused (exit status 2: the supervisor does not restart a refusal blindly)
             print(f"rexl3 level=error event=boot_refused rank={os.environ.get('RANK')} error={e}", file=sys.stderr, flush=True)
             return 2
+        if _is_expert_family(cfg):
+            import torch
+            from ..engine import lockstep
+            lockstep.follow(_build_ep_backend(args, cfg, ctx, kv_tokens), ctx.ctrl)
+            torch.cuda.synchronize()
+            return 0
         shard, group = tprt.build_dense_tp(ctx, cfg, num_pages=-(-kv_tokens // dense.PAGE) + args.slots, max_rows=max(256, args.prefill_chunk),
                                            max_slots=args.slots, max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, weights=weights)
         follow(shard, args.slots, ctx.ctrl, use_graphs=not args.no_graphs)
