@@ -209,6 +209,9 @@ def build(args):
 
 def _tp_boot_gate(args, cfg, ctx) -> None:
     """Every rank of the group must be about to run the same thing (raises BootGateError on all ranks otherwise)."""
+    from ..models import hybrid as hybrid_models
+    if isinstance(cfg, hybrid_models.HybridConfig):
+        raise RuntimeError("the hybrid (Mamba2 / delta-net) family runs on one GPU per replica: start one process per GPU behind the router instead")
     from ..parallel import bootgate
     flags = dict(slots=args.slots, max_model_len=args.max_model_len, prefill_chunk=args.prefill_chunk, kv_tokens=args.kv_tokens,
                  graphs=not args.no_graphs, random_init=args.random_init or "")
@@ -261,7 +264,8 @@ def follow_rank(args) -> int:
         if args.random_init:
             from ..models import mla as mla_models
             from ..models import moe as _moe_models  # noqa: F401  (registers the MoE configs)
-            cfg = mla_models.CONFIGS[args.random_init] if args.random_init in mla_models.CONFIGS else dense.CONFIGS[args.random_init]
+            from ..models import hybrid as hybrid_models
+            cfg = (mla_models.CONFIGS.get(args.random_init) or hybrid_models.CONFIGS.get(args.random_init) or dense.CONFIGS[args.random_init])
             weights = None
         else:
             from ..quant import quantize
