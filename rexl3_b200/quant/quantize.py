@@ -280,7 +280,14 @@ def config_from_pack(folder: str) -> DenseConfig:
 
 def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeights:
     """Scan (headers only), refuse bad groups by name, then read the tensors: all of them in one pass of the native parallel range
-    reader (`threads` readers, optionally O_DIRECT), from which the per-tensor reads below are served."""
+    reader (`threads` readers, optionally O_DIRECT), from which the per-tensor reads are served."""
+    try:
+        return _load_pack(folder, threads, direct)
+    finally:
+        safetensors_io.drop_prefetched()          # staged tensors nobody asked for, also when a refusal ends the load early
+
+
+def _load_pack(folder: str, threads: int, direct: bool) -> HostWeights:
     cfg = config_from_pack(folder)
     ck = checkpoint.scan(folder)
     if ck.bad:
@@ -344,7 +351,6 @@ def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeight
         w.layers.append(lay)
     w.final_norm = plain("model.norm.weight")
     w.lm_head = lin("lm_head")
-    safetensors_io.drop_prefetched()          # tensors the model did not ask for
     read_s = loadstats.snapshot().get(("pack", "read"), (0.0, 0, 0))[0] if threads > 0 else 0.0
     loadstats.add("pack", "assemble", max(0.0, time.perf_counter() - t_assemble - read_s), ck.total_bytes())
     return w
