@@ -255,8 +255,75 @@ class BpeTokenizer(Tok):
         return self.added.get(text)
 
 
+class _HfStream:
+    """Incremental detokenizer over a tokenizer that only decodes whole id lists to text: decode the ids since the last rebase, emit what
+    is new, hold back while the text ends in an unfinished character (the replacement mark)."""
+    CONTEXT = 6          # ids kept as left context when the window is rebased (decoders may join a token to its predecessor)
+    REBASE = 96          # ids after which the window is rebased, so a long stream does not re-decode its whole history every token
+
+    def __init__(self, tok: "HfTokenizer", skip_special: bool):
+        self.tok, self.skip = tok, skip_special
+        self.ids, self.emitted = [], 0
+
+    def push(self, ids) -> str:
+        self.ids.extend(int(i) for i in ids)
+        text = self.tok.decode(self.ids, self.skip)
+        if text.endswith("\ufffd"):
+            return ""
+        out, self.emitted = text[self.emitted:], len(text)
+        if len(self.ids) > self.REBASE:
+            self.ids = self.ids[-self.CONTEXT:]
+            self.emitted = len(self.tok.decode(self.ids, self.skip))
+        return out
+
+    def flush(self) -> str:
+        text = self.tok.decode(self.ids, self.skip)
+        out, self.ids, self.emitted = text[self.emitted:], [], 0
+        return out
+
+
+class HfTokenizer(Tok):
+    """Any `tokenizer.json` the `tokenizers` library can load (Unigram / SentencePiece-style, WordPiece, BPE variants this module's own
+    byte-level BPE does not cover).  The fallback path of `load_tokenizer`."""
+
+    def __init__(self, path: str, eos_ids=(), bos_id=None):
+        import tokenizers
+        self.tk = tokenizers.Tokenizer.from_file(path)
+        self.vocab_size = self.tk.get_vocab_size(with_added_tokens=True)
+        self.eos_ids, self.bos_id = tuple(eos_ids), bos_id
+
+    def encode(self, text, allow_special=True):
+        return list(self.tk.encode(text, add_special_tokens=False).ids)
+
+    def decode(self, ids, skip_special=True):
+        return self.tk.decode([int(i) for i in ids], skip_special_tokens=skip_special)
+
+    def decode_bytes(self, ids, skip_special=True):
+        return self.decode(ids, skip_special).encode("utf-8")
+
+    def stream(self, skip_special=True):
+        return _HfStream(self, skip_special)
+
+    def special_id(self, text):
+        return self.tk.token_to_id(text)
+
+
 def load_tokenizer(folder: str | None, vocab_size: int) -> Tok:
-    """The pack's tokenizer.json when there is one, else the byte tokenizer over the model's vocabulary."""
+    """The pack's tokenizer.json when there is one (this module's byte-level BPE, else whatever the `tokenizers` library can load), else
+    the byte tokenizer over the model's vocabulary."""
     if folder and os.path.exists(os.path.join(folder, "tokenizer.json")):
-        return BpeTokenizer.from_dir(folder)
+        try:
+            return BpeTokenizer.from_dir(folder)
+        except (ValueError, KeyError) as own:
+            eos, bos = [], None
+            gp = os.path.join(folder, "generation_config.json")
+            if os.path.exists(gp):
+                g = json.load(open(gp))
+                e = g.get("eos_token_id")
+                eos = [e] if isinstance(e, int) else list(e or [])
+                bos = g.get("bos_token_id")
+            try:
+                return HfTokenizer(os.path.join(folder, "tokenizer.json"), eos, bos)
+            except Exception as hf:  # noqa: BLE001  (neither path can read the file: say both reasons)
+                raise ValueError(f"tokenizer.json: not byte-level BPE ({own}) and the tokenizers library refused it ({hf})") from hf
     return ByteTokenizer(max(vocab_size, 264))

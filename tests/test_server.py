@@ -136,3 +136,24 @@ def test_bpe_tokenizer_matches_the_hf_oracle(tmp_path):
     dec = mine.stream()
     ids = mine.encode("ünï ✓ 你")
     assert "".join(dec.push([i]) for i in ids) + dec.flush() == "ünï ✓ 你"
+
+
+def test_non_bpe_tokenizer_falls_back_to_the_hf_library_with_streaming(tmp_path):
+    pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tk = Tokenizer(models.Unigram())
+    tk.pre_tokenizer = pre_tokenizers.Metaspace()
+    tk.decoder = decoders.Metaspace()
+    corpus = ["the quick brown fox jumps over the lazy dog", "héllo wörld ünïcode 你好 世界", "streaming text one token at a time"] * 30
+    tk.train_from_iterator(corpus, trainers.UnigramTrainer(vocab_size=200, special_tokens=["<unk>", "<s>", "</s>"], unk_token="<unk>"))
+    tk.save(str(tmp_path / "tokenizer.json"))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 2, "bos_token_id": 1}))
+    tok = tokenizer.load_tokenizer(str(tmp_path), 200)
+    assert isinstance(tok, tokenizer.HfTokenizer) and tok.eos_ids == (2,) and tok.bos_id == 1 and tok.special_id("</s>") == 2
+    for s in ["the lazy fox", "héllo 你好 wörld", "one token at a time " * 12]:
+        ids = tok.encode(s)
+        assert ids == tk.encode(s, add_special_tokens=False).ids
+        whole = tok.decode(ids)
+        dec = tok.stream()
+        streamed = "".join(dec.push([i]) for i in ids) + dec.flush()
+        assert streamed == whole and "\ufffd" not in streamed
