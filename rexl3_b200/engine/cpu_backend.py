@@ -5,7 +5,6 @@ backend.  Each sequence is computed on its own, so row invariance holds by const
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from ..models.dense import HostWeights, ReferenceDense

@@ -19,7 +19,7 @@ import torch
 
 from ..format import exl3
 from ..ops import lib as _lib
-from .dense import CONFIGS, DenseConfig, DenseGPU, HostLayer, HostLinear, HostWeights, ReferenceDense, _bf16_round, random_linear
+from .dense import CONFIGS, DenseConfig, DenseGPU, HostLayer, HostWeights, ReferenceDense, _bf16_round, random_linear
 
 TP_MAX = 8
 

@@ -1,9 +1,8 @@
 """CUDA-event timings of the EXL3 GEMM at the 27B config's five matrix shapes (median of 12, weights rotated over several copies)."""
 import os, sys
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))))
-import sys, time, json, numpy as np, torch
+import json, torch
 from rexl3_b200.ops import kernels as K
-from rexl3_b200.format import exl3
 torch.manual_seed(0)
 dev='cuda'
 def mk(k,n,bits=4,copies=4):

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import bisect
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 TREE_MAX_ROWS = 64
 ATTN_ROW_BLOCK = 8

@@ -11,7 +11,7 @@ from __future__ import annotations
 import hashlib
 import struct
 from collections import OrderedDict
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 BLOCK_TOKENS = 64
 
