@@ -19,6 +19,30 @@ def _ready(port: int) -> bool:
         return False
 
 
+def _planned_mib(c, g) -> int:
+    """Memory each GPU of the group needs according to the memory plan of the cluster file's model and serve flags (0: unknown model)."""
+    from .. import plan
+    flags = list(c.flags) + list(g.flags)
+
+    def opt(name, default):
+        return int(flags[flags.index(name) + 1]) if name in flags and flags.index(name) + 1 < len(flags) else default
+    try:
+        if c.random_init:
+            cfg = plan.find_config(c.random_init)
+        else:
+            from ..quant import quantize
+            cfg = quantize.config_from_pack(c.pack)
+    except (KeyError, OSError, ValueError):
+        return 0
+    d = plan.plan(cfg, gpus=len(g.ranks), slots=opt("--slots", 16), max_model_len=opt("--max-model-len", 8192),
+                  kv_dtype="fp8" if "fp8" in flags else "bf16")
+    per = d["per_gpu"]
+    kv = per["kv_for_all_slots"]
+    if "--kv-tokens" in flags:
+        kv = opt("--kv-tokens", 0) * max(1, d["kv_bytes_per_token"] // len(g.ranks))
+    return int((per["weights"] + per["recurrent_state"] + per["reserve"] + kv) >> 20)
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="rexl3-cluster", allow_abbrev=False)
     p.add_argument("command", choices=["validate", "plan", "check", "up", "supervise", "status", "down", "logs"])
@@ -65,7 +89,8 @@ def main(argv=None) -> int:
             print("\n".join(lines) if lines is not None else "(no log)")
         return 0
     if a.command == "check":
-        checks = ops.preflight(c, group, need_mib=a.need_mib, gpu_probe=None if a.no_gpu_probe else ops.nvml_probe, locks=locks)
+        need = a.need_mib or _planned_mib(c, g)
+        checks = ops.preflight(c, group, need_mib=need, gpu_probe=None if a.no_gpu_probe else ops.nvml_probe, locks=locks)
         for ch in checks:
             print(f"{'ok  ' if ch.ok else 'FAIL'} {ch.name}: {ch.detail}")
         return 0 if all(ch.ok for ch in checks) else 1

@@ -85,3 +85,13 @@ def test_cli_check_and_status(tmp_path, capsys):
     assert main(["status", "--cluster", str(f), "--state-dir", str(tmp_path / "s")]) == 0
     assert json.loads(capsys.readouterr().out)["state"] == "down"
     assert main(["logs", "--cluster", str(f), "--state-dir", str(tmp_path / "s")]) == 2
+
+
+def test_check_derives_the_memory_need_from_the_plan():
+    from rexl3_b200.cluster.__main__ import _planned_mib
+    doc = dict(DOC, random_init="dense-27b", serve={"flags": ["--slots", "64", "--max-model-len", "8704"]})
+    c = validate(doc)
+    need = _planned_mib(c, c.groups["tp2"])
+    # half of the weights (about 6 GB) + half of 64 x 8704 tokens of KV (about 68 GB) + the reserve
+    assert 70_000 < need < 85_000
+    assert _planned_mib(validate(dict(DOC, random_init="unknown-model")), c.groups["tp2"]) == 0
