@@ -120,7 +120,7 @@ CONFIGS = {
     "test-hybrid-kda": HybridConfig(n_layers=3, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid-kda",
                                     pattern="KAK", nope=True, gdn_k_heads=4, gdn_v_heads=4),
     # CPU plumbing model of the family (one layer of each recurrent kind and one attention layer; quantizes in seconds on the host)
-    "tiny-hybrid": HybridConfig(n_layers=3, d_model=128, n_q=2, n_kv=1, head_dim=64, ffn=128, vocab=256, bits=4.0, name="tiny-hybrid", pattern="MGA",
+    "tiny-hybrid": HybridConfig(n_layers=3, d_model=128, n_q=2, n_kv=1, head_dim=64, ffn=128, vocab=512, bits=4.0, name="tiny-hybrid", pattern="MGA",
                                 ssm_heads=2, ssm_groups=1, gdn_k_heads=1, gdn_v_heads=1),
     "test-hybrid": HybridConfig(n_layers=4, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hybrid",
                                 pattern="MAMM", ssm_heads=16, ssm_groups=2),
@@ -330,6 +330,13 @@ class ReferenceHybrid(ReferenceDense):
         return (o.reshape(T, DI) * (torch.sigmoid(z) if kda else F.silu(z))) @ L["o"]
 
 
+def delta_state_canonical(pool: torch.Tensor) -> torch.Tensor:
+    """A delta-net state pool [slots, Hv, 128, 128] as stored (the kernel's access order: [warp = j / 16][step s][lane = 2 (j % 16) + half][e],
+    holding S[value j][key i] with i = 64 half + 4 s + e) -> canonical [slots, Hv, value j, key i]."""
+    S, Hv = pool.shape[0], pool.shape[1]
+    return pool.reshape(S, Hv, 8, 16, 16, 2, 4).permute(0, 1, 2, 4, 5, 3, 6).reshape(S, Hv, 128, 128)
+
+
 # ====================================================================================================== sm_100a executor
 class HybridGPU(DenseGPU):
     """One B200.  Attention layers run the dense executor's mixer; Mamba2 layers run `_mamba`.  A Mamba2 layer's in_proj / out_proj sit
@@ -451,6 +458,12 @@ class HybridGPU(DenseGPU):
         self.final_norm = norm()
         hw = exl3.Bits.of(cfg.head_bits or cfg.bits).tile_words
         self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d), hw, real_n=cfg.vocab)
+
+    def state_view(self, li: int) -> torch.Tensor:
+        """The recurrent state pool of layer `li` in canonical order: Mamba2 [slots, H, P, N]; delta-net [slots, Hv, value j, key i] (the
+        delta-net pool is stored in the kernel's access order: [warp = j / 16][step][lane = 2 (j % 16) + half][4], i = 64 half + 4 step + e)."""
+        pool = self.ssm_pool[li]
+        return pool if self.layers[li]["kind"] == "M" else delta_state_canonical(pool)
 
     def state_bytes(self) -> int:
         return sum(t.numel() * 4 for t in self.conv_pool.values()) + sum(t.numel() * 4 for t in self.ssm_pool.values())

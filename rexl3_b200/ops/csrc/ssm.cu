@@ -159,7 +159,11 @@ __global__ void __launch_bounds__(256) ssm_gate_norm_kernel(const float* __restr
 // width 4 over q | k | v, l2-normalised q and k, q scaled by 1/sqrt(128), decay exp(g) with g = A * softplus(a + dt_bias), A < 0,
 // beta = sigmoid(b); delta rule S = S e^g; S += k (x) (beta (v - S^T k)); o = S^T q; per-head RMSNorm(o) * w * silu(z)).
 //   proj     f32 [M][ldp]: z (Hv*128) | q (Hk*128) | k (Hk*128) | v (Hv*128) | b (Hv) | a (Hv) | padding
-//   S pool   f32 [slots][Hv][128 value j][128 key i], i contiguous; conv pool as above with C = (2 Hk + Hv) * 128
+//   S pool   f32 [slots][Hv][64 KB], one head's state S[value j][key i] stored in the order the kernel reads it: thread (j, half) owns
+//            i = 64 half + 4 s + e (s = 0..15 load steps, e = 0..3), and the float4 of step s sits at ((warp * 16 + s) * 32 + lane) * 4 with
+//            warp = j / 16, lane = 2 (j % 16) + half: every load and store instruction of a warp covers one contiguous 512-byte run
+//            (the obvious [j][i] layout made each instruction touch 32 different 128-byte lines; measured in the profile note).
+//            conv pool as above with C = (2 Hk + Hv) * 128
 // One CTA per (segment, value head), 256 threads: thread = value column j and one half of the 128 keys (64 state values in registers);
 // the two halves meet in one shuffle.  The gated norm runs in the same kernel (the CTA holds the head's whole output row).
 //
@@ -194,14 +198,14 @@ __global__ void __launch_bounds__(256, 2) gdn_scan_kernel(const float* __restric
   const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, j = tid >> 1, half = tid & 1;
   const int seq = row_seq[r0], hk = h / (Hv / Hk), DI = Hv * GDN_D;
   float st[64];
-  float* sp = s_pool + (((size_t)seq * Hv + h) * GDN_D + j) * GDN_D + half * 64;
+  float* sp = s_pool + ((size_t)seq * Hv + h) * (GDN_D * GDN_D) + (size_t)warp * (16 * 128) + lane * 4;   // step s adds 128 floats
   if (positions[r0] == 0) {
 #pragma unroll
     for (int i = 0; i < 64; ++i) st[i] = 0.f;
   } else {
 #pragma unroll
     for (int i = 0; i < 64; i += 4) {
-      const float4 v = *reinterpret_cast<const float4*>(sp + i);
+      const float4 v = *reinterpret_cast<const float4*>(sp + (i >> 2) * 128);
       st[i] = v.x, st[i + 1] = v.y, st[i + 2] = v.z, st[i + 3] = v.w;
     }
   }
@@ -261,7 +265,7 @@ __global__ void __launch_bounds__(256, 2) gdn_scan_kernel(const float* __restric
     }
   }
 #pragma unroll
-  for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
+  for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(sp + (i >> 2) * 128) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
   ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq, h, (int)gridDim.y);
 }
 

@@ -71,7 +71,7 @@ def test_chunked_prefill_and_mixed_decode_match_reference(name):
         assert (lg[row, :cfg.vocab] - wv).abs().max().item() < 0.05 * scale, row
     # the state pools hold what the reference holds
     conv_ref, s_ref = ref.ssm[(2, 0)]
-    assert (m.ssm_pool[0][2] - s_ref).abs().max().item() < 0.03 * s_ref.abs().max().item()
+    assert (m.state_view(0)[2] - s_ref).abs().max().item() < 0.03 * s_ref.abs().max().item()
     assert (m.conv_pool[0][2] - conv_ref).abs().max().item() < 0.03 * conv_ref.abs().max().item()
 
 

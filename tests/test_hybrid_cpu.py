@@ -155,3 +155,41 @@ def test_quantize_hybrid_cli_writes_a_loadable_pack_close_to_the_float_model(tmp
     assert quant_main(["--arch", "tiny-hybrid", "--out", str(tmp_path / "cli"), "--layers", "1"]) == 0
     c2 = quantize.config_from_pack(str(tmp_path / "cli"))
     assert c2.pattern == "M" and c2.n_layers == 1 and len(quantize.load_pack(str(tmp_path / "cli")).layers) == 1
+
+
+def test_delta_state_pool_order_matches_the_kernel_address_formula():
+    """The delta-net state is stored in the order its kernel reads it; the canonical view undoes exactly that permutation.  The address
+    below is the kernel's: thread (j, half) of warp j / 16, lane 2 (j % 16) + half, load step s, element e."""
+    pool = torch.zeros(1, 1, 128, 128)
+    flat = pool.view(-1)
+    for j in range(128):
+        for half in range(2):
+            warp, lane = j // 16, 2 * (j % 16) + half
+            for s in range(16):
+                for e in range(4):
+                    flat[warp * (16 * 128) + s * 128 + lane * 4 + e] = j * 1000 + (64 * half + 4 * s + e)
+    want = (torch.arange(128)[:, None] * 1000 + torch.arange(128)[None, :]).float()
+    assert torch.equal(hybrid.delta_state_canonical(pool)[0, 0], want)
+    # every warp-wide load step covers one contiguous 512-byte run
+    for warp in range(8):
+        for s in range(16):
+            addrs = sorted(warp * 2048 + s * 128 + lane * 4 + e for lane in range(32) for e in range(4))
+            assert addrs == list(range(addrs[0], addrs[0] + 128))
+
+
+def test_server_serves_a_hybrid_model_on_the_cpu_backend():
+    from starlette.testclient import TestClient
+
+    from rexl3_b200.server import main
+    args = main.parser().parse_args(["--backend", "cpu", "--random-init", "tiny-hybrid", "--slots", "2", "--max-model-len", "256"])
+    app, handle = main.make_app(args)
+    try:
+        assert handle.wait_ready(60)
+        with TestClient(app) as c:
+            body = {"prompt": "hello hybrid", "max_tokens": 6, "temperature": 0}
+            a, b = c.post("/v1/completions", json=body).json(), c.post("/v1/completions", json=body).json()
+            assert a["model"] == "tiny-hybrid" and a["usage"]["completion_tokens"] >= 1
+            assert a["choices"][0]["text"] == b["choices"][0]["text"]            # a reused slot restarts its recurrent state at position 0
+            assert a["usage"]["spec"]["drafted"] == 0                           # no draft rows for a backend that cannot roll back
+    finally:
+        handle.stop()
