@@ -126,6 +126,12 @@ class Backend:
     def prefix_release(self, handles: list) -> None:
         pass
 
+    def prefix_needs_cuts(self) -> bool:
+        """True for backends with recurrent state: a block can be cached only if a prefill slice ENDED at its last token (that is when the
+        state can be snapshotted), so the engine ends a slice at the prompt's last full-block boundary.  `prefix_restore` of such a backend
+        may restore fewer blocks than it is given (down to the deepest one that carries a snapshot) and returns what it restored."""
+        return False
+
     def prefix_export(self, handle) -> bytes | None:
         """The block's cached state as bytes (for a spill tier), or None when this backend cannot export."""
         return None

@@ -94,6 +94,7 @@ class Engine:
         self.cost = cost
         self.prefix = prefix if (prefix is not None and backend.prefix_block_tokens() > 0) else None
         # second tier (sched.spill.SpillStore): blocks leaving the index are exported to it, and a lookup that ends early continues there
+        self.prefix_cuts = bool(self.prefix is not None and getattr(backend, "prefix_needs_cuts", lambda: False)())
         self.spill = spill if self.prefix is not None else None
         if self.spill is not None:
             self.prefix.on_evict = self._spill_out
@@ -439,7 +440,7 @@ class Engine:
         if not pending:
             return
         t0 = time.perf_counter_ns()
-        if self.prefill_policy == "burst":
+        if self.prefill_policy == "burst" and not self.prefix_cuts:
             # short prompts that fit one slice each are batched into one backend call
             short = [s for s in pending if s.prompt_len - s.prefilled <= self.burst_tokens]
             batch, used = [], 0
@@ -462,6 +463,12 @@ class Engine:
                 return
         s = pending[0]
         n = min(self.prefill_chunk, s.prompt_len - s.prefilled)
+        if self.prefix_cuts and s.req.prefix_cache:
+            # a recurrent backend snapshots its state where a slice ends: end one at the last block boundary a later prompt could reuse
+            bt = self.backend.prefix_block_tokens()
+            cut = (s.prompt_len - 1) // bt * bt
+            if s.prefilled < cut < s.prefilled + n:
+                n = cut - s.prefilled
         last = s.prefilled + n >= s.prompt_len
         cand = min(64, s.req.sampling.candidate_count(self.backend.vocab_size))
         out = self.backend.prefill_slice(s.slot, s.prefilled, s.tokens[s.prefilled:s.prefilled + n], cand, last)

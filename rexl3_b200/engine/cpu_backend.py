@@ -98,3 +98,30 @@ class CpuHybridBackend(CpuDenseBackend):
         logits = self.model.forward_seq(slot, tokens, start)
         self.model.restore(slot, snap)
         return logits.numpy()
+
+    # ---- prefix cache: a block is restorable only where a slice ended (the handle of that block carries a full snapshot)
+    BLOCK = 64
+
+    def prefix_block_tokens(self):
+        return self.BLOCK
+
+    def prefix_needs_cuts(self) -> bool:
+        return True
+
+    def prefix_bytes_per_block(self):
+        return self.cfg.state_bytes_per_slot() + self.cfg.kv_bytes_per_token(4) * self.BLOCK
+
+    def prefix_commit(self, slot, blocks):
+        snap = self.model.snapshot(slot) if self.len.get(slot, 0) == blocks * self.BLOCK else None
+        return [("hyb", i, snap if i == blocks - 1 else None) for i in range(blocks)]
+
+    def prefix_restore(self, slot, handles):
+        best = max((i for i, h in enumerate(handles) if h[2] is not None), default=-1)
+        if best < 0:
+            return 0
+        self.model.restore(slot, handles[best][2])
+        self.len[slot] = (best + 1) * self.BLOCK
+        return self.len[slot]
+
+    def prefix_release(self, handles):
+        pass

@@ -193,3 +193,17 @@ def test_server_serves_a_hybrid_model_on_the_cpu_backend():
             assert a["usage"]["spec"]["drafted"] == 0                           # no draft rows for a backend that cannot roll back
     finally:
         handle.stop()
+
+
+@pytest.mark.parametrize("cfg", [SMALL, GDN], ids=["mamba2", "gdn"])
+def test_prefix_cache_for_recurrent_state_through_slice_cuts(cfg):
+    """A backend with recurrent state caches a block only where a prefill slice ended; the engine cuts a slice at the prompt's last
+    block boundary, the second prompt restores the snapshot taken there, and decodes what a cold run decodes."""
+    from rexl3_b200.engine import harness
+    from rexl3_b200.engine.cpu_backend import CpuHybridBackend
+    w = hybrid.random_weights(cfg, seed=5)
+
+    def make():
+        return CpuHybridBackend(w, max_slots=4, max_rows=16)
+    assert make().prefix_needs_cuts()
+    assert harness.cached_equals_cold(make, cfg.vocab, n=6) is None
