@@ -72,8 +72,9 @@ class CpuDenseBackend(Backend):
 
 
 class CpuHybridBackend(CpuDenseBackend):
-    """The fp32 hybrid (Mamba2 / delta-net + attention) oracle behind the Backend contract.  Rows cannot be rejected once fed
-    (`supports_rollback` is False, the engine plans no drafts); prompt scoring undoes its rows through a state snapshot."""
+    """The fp32 hybrid (Mamba2 / delta-net + attention) oracle behind the Backend contract.  A recurrent state cannot be truncated, so a
+    window is undone the way the reference's record / commit scheme does it: the state before the window is kept (a snapshot), and a
+    commit that keeps fewer rows than were fed restores it and replays the kept rows.  Prompt scoring undoes its rows the same way."""
     name = "cpu-hybrid-reference"
 
     def __init__(self, weights: HostWeights, max_slots: int = 8, max_rows: int = 64, dtype=torch.float32):
@@ -83,15 +84,33 @@ class CpuHybridBackend(CpuDenseBackend):
         self.vocab_size = weights.cfg.vocab
         self.max_slots, self.max_rows = max_slots, max_rows
         self.len, self.pending, self.last_logits = {}, {}, None
+        self._before = {}          # slot -> (snapshot before the window in flight, its tokens, its first position)
 
-    def supports_rollback(self) -> bool:
-        return False
+    def step(self, reqs, candidates):
+        out = []
+        for r in reqs:
+            if r.first_position != self.len.get(r.slot, 0):
+                raise BackendError(f"window at {r.first_position} but slot {r.slot} holds {self.len.get(r.slot, 0)} tokens")
+            self._before[r.slot] = (self.model.snapshot(r.slot), list(r.tokens), r.first_position)
+            logits = self.model.forward_seq(r.slot, r.tokens, r.first_position)
+            self.pending[r.slot] = len(r.tokens)
+            out.append(self._rows(logits, candidates))
+        return out
 
     def commit(self, slot, keep):
         fed = self.pending.pop(slot, 0)
+        before = self._before.pop(slot, None)
+        keep = min(keep, fed)
         if keep < fed:
-            raise BackendError(f"slot {slot}: {fed - keep} rows rejected, but this backend cannot roll back", fatal=False)
-        self.len[slot] = self.len.get(slot, 0) + fed
+            snap, tokens, pos = before
+            self.model.restore(slot, snap)
+            if keep:
+                self.model.forward_seq(slot, tokens[:keep], pos)         # replay of the accepted prefix
+        self.len[slot] = self.len.get(slot, 0) + keep
+
+    def release(self, slot):
+        self._before.pop(slot, None)
+        super().release(slot)
 
     def score_rows(self, slot, start, tokens):
         snap = self.model.snapshot(slot)
