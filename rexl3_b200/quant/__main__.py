@@ -24,6 +24,7 @@ def main(argv=None) -> int:
                    help="calibration rows: run the fp32 teacher over ROWS synthetic tokens (sequences of --calibrate-cols) and code with LDLQ")
     p.add_argument("--calibrate-cols", type=int, default=256)
     p.add_argument("--damp", type=float, default=0.01)
+    p.add_argument("--scale-search", action="store_true", help="try a few output scales per tensor on a sample of tiles and keep the best")
     p.add_argument("--device", default="cpu", help="cpu (host Viterbi, all cores) or cuda (one CTA per tile; same bits)")
     a = p.parse_args(argv)
     is_hybrid = a.arch in hybrid.CONFIGS
@@ -50,7 +51,7 @@ def main(argv=None) -> int:
         seqs = [rng.integers(0, cfg.vocab, size=cols).tolist() for _ in range(max(1, a.calibrate // cols))]
         hessians = teacher.capture_hessians(cfg, fp, seqs, device="cuda" if a.device != "cpu" else "cpu")
         extra = {"calibration": {"rows": len(seqs), "cols": cols, "data": "synthetic uniform tokens", "damp": a.damp}}
-    w = quantize.quantize_dense(cfg, fp, seed=a.seed, threads=a.threads, device=a.device, hessians=hessians, damp=a.damp)
+    w = quantize.quantize_dense(cfg, fp, seed=a.seed, threads=a.threads, device=a.device, hessians=hessians, damp=a.damp, scale_search=a.scale_search)
     quantize.write_pack(a.out, w, extra)
     print(f"rexl3-quant: wrote {a.out} ({cfg.name}, {cfg.bits:g} bpw, {cfg.n_layers} layers) in {time.time() - t0:.1f} s")
     return 0

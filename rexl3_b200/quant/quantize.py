@@ -19,6 +19,7 @@ from ..models.dense import DenseConfig, HostLayer, HostLinear, HostWeights
 from .trellis import encode_tiles
 
 CODEBOOK_STD = {}
+SCALE_GRID = (0.85, 0.92, 1.0, 1.08, 1.17, 1.27)
 
 
 def _cb_std(cb: str) -> float:
@@ -36,13 +37,15 @@ def to_stream_tiles(w: np.ndarray) -> np.ndarray:
 
 
 def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: int = 0, bias=None, threads: int = 0, device: str = "cpu",
-                    hessian: np.ndarray | None = None, damp: float = 0.01, refit: bool | None = None) -> HostLinear:
+                    hessian: np.ndarray | None = None, damp: float = 0.01, refit: bool | None = None, scale_search: bool = False,
+                    scale_search_tiles: int = 96) -> HostLinear:
     """w: float [K, N] with y = x @ w.  K and N must be multiples of 128 (pad first).  `device="cuda"` runs the trellis search on the GPU
     (the CUDA encoder emits the same bits as the host one).
 
     `hessian` [K, K] (second moment of the layer's inputs, e.g. from `teacher.capture_hessians`): the 16-row tile blocks are coded last to
     first with LDL error feedback (LDLQ) instead of independently, and the output scale is refit against the Hessian-weighted error
-    (`refit`, default: on with a Hessian, off without)."""
+    (`refit`, default: on with a Hessian, off without).  `scale_search`: instead of matching the codebook's spread exactly, try the scales of
+    `SCALE_GRID` around it on a sample of tiles and keep the best (after the rotation the optimum is flat near 1: a small gain, cheap to take)."""
     w = np.asarray(w, dtype=np.float64)
     k, n = w.shape
     if k % 128 or n % 128:
@@ -56,6 +59,26 @@ def quantize_linear(w: np.ndarray, bits: float, codebook: str = "3inst", seed: i
     rot = exl3.rotate(exl3.rotate((w * su[:, None] * sv[None, :]).T.copy()).T.copy())     # H_K (.) H_N, H symmetric and orthonormal
     std = float(rot.std())
     scale = std / _cb_std(codebook) if std > 0 else 1.0
+
+    def encode_err(tiles):
+        if device == "cpu":
+            return encode_tiles(tiles, b, codebook, threads)
+        from .trellis import encode_tiles_cuda
+        out, err = encode_tiles_cuda(tiles, b, codebook, device=device)
+        return out.cpu().numpy(), err.cpu().numpy()
+
+    if scale_search and std > 0:
+        # global scale search: code a sample of tiles at a few scales around the spread-matched one and keep the scale with the smallest
+        # error in weight units (err is in coded units, so it is multiplied back by scale^2)
+        all_tiles = to_stream_tiles(rot)
+        pick = np.random.default_rng(seed + 99).choice(all_tiles.shape[0], size=min(scale_search_tiles, all_tiles.shape[0]), replace=False)
+        sample = all_tiles[np.sort(pick)]
+        best = None
+        for f in SCALE_GRID:
+            err = float(encode_err(sample / (scale * f))[1].astype(np.float64).sum()) * (scale * f) ** 2
+            if best is None or err < best[0]:
+                best = (err, f)
+        scale *= best[1]
 
     def encode(tiles):
         if device == "cpu":
@@ -93,13 +116,14 @@ def pad_to(w: np.ndarray, k: int, n: int) -> np.ndarray:
 
 
 def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0, device: str = "cpu", hessians: dict | None = None,
-                   damp: float = 0.01) -> HostWeights:
+                   damp: float = 0.01, scale_search: bool = False) -> HostWeights:
     """fp: float weights of a dense GQA decoder, [in, out] matrices: embed [V, d], final_norm [d], lm_head [d, V] and per layer
     attn_norm, q, k, v, o, ffn_norm, gate, up, down (optionally q_norm, k_norm).  `hessians` (from `teacher.capture_hessians`): layers
     found there are coded with LDLQ error feedback, the others tile by tile."""
     d, F, V = cfg.d_model, cfg.ffn_padded, cfg.vocab_padded
     hs = hessians or {}
-    ql = lambda m, bits, sd, key: quantize_linear(m, bits, cfg.codebook, sd, threads=threads, device=device, hessian=hs.get(key), damp=damp)  # noqa: E731
+    ql = lambda m, bits, sd, key: quantize_linear(m, bits, cfg.codebook, sd, threads=threads, device=device, hessian=hs.get(key), damp=damp,  # noqa: E731
+                                                  scale_search=scale_search)
     w = HostWeights(cfg, np.asarray(fp["embed"], dtype=np.float32))
     for i, L in enumerate(fp["layers"]):
         qkv = np.concatenate([L["q"], L["k"], L["v"]], axis=1)
