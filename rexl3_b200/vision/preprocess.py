@@ -140,3 +140,19 @@ def preprocess_image(img: np.ndarray, patch: int = 14, merge: int = 2, temporal:
     x = (x - np.asarray(mean, dtype=np.float32)) / np.asarray(std, dtype=np.float32)
     rows, grid = patchify(x.transpose(2, 0, 1)[None], patch, merge, temporal)
     return ImageInputs(rows.astype(np.float32), grid, patch_position_ids(grid, merge), rows.shape[0] // (merge * merge))
+
+
+def preprocess_video(frames, patch: int = 14, merge: int = 2, temporal: int = 2, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 320,
+                     mean=CLIP_MEAN, std=CLIP_STD) -> ImageInputs:
+    """A clip as a sequence of HxWx3 uint8 frames of one size -> one ImageInputs whose grid_t counts temporal patches (frame pairs).  Every
+    frame is resized to the same (H, W) chosen from the first frame; the pixel budget is per frame."""
+    frames = list(frames)
+    if not frames:
+        raise ValueError("empty clip")
+    if any(f.shape != frames[0].shape for f in frames):
+        raise ValueError("the frames of a clip must share one size")
+    h, w = smart_resize(frames[0].shape[0], frames[0].shape[1], patch * merge, min_pixels, max_pixels)
+    m, sd = np.asarray(mean, dtype=np.float32), np.asarray(std, dtype=np.float32)
+    stack = np.stack([((bicubic_resize_u8(f[:, :, :3], h, w).astype(np.float32) * np.float32(1.0 / 255.0)) - m) / sd for f in frames])
+    rows, grid = patchify(np.ascontiguousarray(stack.transpose(0, 3, 1, 2)), patch, merge, temporal)
+    return ImageInputs(rows.astype(np.float32), grid, patch_position_ids(grid, merge), rows.shape[0] // (merge * merge))

@@ -42,3 +42,24 @@ def test_crc_and_lock_catch_a_flipped_byte(tmp_path):
     os.remove(os.path.join(folder, "crc32.txt"))
     assert verify.verify_crc(folder) == ["crc32.txt is missing"]
     assert any("crc32.txt: missing" in b for b in verify.verify_lock(folder))
+
+
+def test_server_refuses_a_pack_that_fails_verification(tmp_path):
+    import pytest
+
+    from rexl3_b200.server import main
+    folder = _pack(tmp_path)
+    verify.write_crc(folder)
+    verify.write_lock(folder)
+    base = ["--backend", "cpu", "--model", folder, "--slots", "2", "--max-model-len", "128"]
+    for mode in ("sizes", "crc", "lock"):
+        make, _tok, _fmt, name, info = main.build(main.parser().parse_args(base + ["--verify-pack", mode]))
+        assert len(info["pack_fingerprint"]) == 64
+    path = os.path.join(folder, "model.safetensors")
+    raw = bytearray(open(path, "rb").read())
+    raw[-5] ^= 0x01
+    open(path, "wb").write(raw)
+    main.build(main.parser().parse_args(base + ["--verify-pack", "sizes"]))          # same size: passes the cheap check
+    for mode in ("crc", "lock"):
+        with pytest.raises(SystemExit, match="pack refused"):
+            main.build(main.parser().parse_args(base + ["--verify-pack", mode]))

@@ -53,3 +53,20 @@ def test_preprocess_image_end_to_end():
     assert out.pixel_values.dtype == np.float32 and np.isfinite(out.pixel_values).all()
     lo, hi = (0 - 0.48145466) / 0.26862954, (1 - 0.40821073) / 0.27577711
     assert out.pixel_values.min() >= lo - 1e-4 and out.pixel_values.max() <= hi + 1e-4
+
+
+def test_preprocess_video_pairs_frames():
+    rng = np.random.default_rng(4)
+    frames = [rng.integers(0, 256, size=(60, 90, 3), dtype=np.uint8) for _ in range(5)]
+    out = vision.preprocess_video(frames)
+    gt, gh, gw = out.grid_thw
+    assert gt == 3 and out.pixel_values.shape == (3 * gh * gw, 3 * 2 * 14 * 14)          # five frames -> three pairs (the last frame repeated)
+    one = vision.preprocess_image(frames[0], max_pixels=14 * 14 * 4 * 320)
+    assert one.grid_thw[1:] == (gh, gw)
+    # the first temporal patch holds frames 0 and 1: its first half equals the single-image rows' first half
+    a = out.pixel_values[0].reshape(3, 2, 14, 14)
+    b = one.pixel_values[0].reshape(3, 2, 14, 14)
+    assert np.array_equal(a[:, 0], b[:, 0]) and not np.array_equal(a[:, 1], b[:, 1])
+    assert out.position_ids.shape == (3 * gh * gw, 2) and np.array_equal(out.position_ids[:gh * gw], out.position_ids[gh * gw:2 * gh * gw])
+    with pytest.raises(ValueError):
+        vision.preprocess_video([frames[0], frames[1][:30]])
