@@ -113,6 +113,10 @@ def rank_commands(c: Cluster, group: str, python: str = "python") -> list:
         n = c.nodes[node]
         env = {"RANK": str(r), "WORLD_SIZE": str(R), "LOCAL_RANK": str(n.get("gpu", r)), "MASTER_ADDR": c.nodes[g.ranks[0]].get("address", "127.0.0.1"),
                "MASTER_PORT": str(g.tp_port), "NCCL_NVLS_ENABLE": "0"}
+        if R == 1:
+            # a replica of its own: the process sees only its GPU (the serving binary uses the current device when it is not part of a group)
+            env["CUDA_VISIBLE_DEVICES"] = str(n.get("gpu", 0))
+            env["LOCAL_RANK"] = "0"
         argv = [python, "-m", "rexl3_b200.server", "--backend", "cuda", "--port", str(g.http_port)]
         argv += ["--model", c.pack] if c.pack else ["--random-init", c.random_init]
         argv += c.flags + g.flags

@@ -69,3 +69,19 @@ def test_local_runner_restarts_the_whole_group():
         return a
     assert supervise(attempt, Policy([0.0], 600, 5), log=lambda s: None) == 0
     assert runs[0][1] == 70 and runs[0][0] != 0 and runs[1] == [0, 0]
+
+
+def test_single_rank_groups_pin_their_gpu_through_visibility():
+    import json
+    import os
+
+    from rexl3_b200.cluster.schema import load_cluster, rank_commands
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    c = load_cluster(os.path.join(here, "docs", "examples", "cluster.b200-hybrid-dp8.json"))
+    env, argv = rank_commands(c, "r5")[0]
+    assert env["CUDA_VISIBLE_DEVICES"] == "5" and env["LOCAL_RANK"] == "0" and env["WORLD_SIZE"] == "1"
+    assert argv[argv.index("--port") + 1] == "8085" and "gdn-hybrid-27b" in argv
+    c8 = load_cluster(os.path.join(here, "docs", "examples", "cluster.b200-tp8.json"))
+    envs = [e for e, _ in rank_commands(c8, "tp8")]
+    assert all("CUDA_VISIBLE_DEVICES" not in e for e in envs) and [e["LOCAL_RANK"] for e in envs] == [str(i) for i in range(8)]
+    assert json.dumps(envs[0])
