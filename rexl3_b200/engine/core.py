@@ -18,7 +18,7 @@ from dataclasses import dataclass, field
 
 from ..sampling import Sampling, SamplingError, choose, seed_for
 from ..sched import AdmitError, Admission, CostModel, Demand, PrefixIndex, chain_hashes, choose_budget
-from ..spec import AcceptStats, CopyDrafter, SpecMode, accept
+from ..spec import AcceptStats, CopyDrafter, NgramDrafter, SpecMode, accept
 from ..utils import trace
 from .backend import Backend, BackendError, DraftAsk, RowRequest
 
@@ -62,6 +62,7 @@ class _Seq:
     cached: int = 0
     generated: int = 0
     drafter: CopyDrafter = None
+    ngram: NgramDrafter = None     # created on first use
     stats: AcceptStats = None
     drafted: int = 0
     accepted: int = 0
@@ -323,6 +324,12 @@ class Engine:
                 for i, s in enumerate(active):
                     if not proposals[i] and maxes[i] > 0:
                         proposals[i] = s.drafter.propose(s.tokens, maxes[i])
+            if self.spec.ngram:
+                for i, s in enumerate(active):
+                    if not proposals[i] and maxes[i] > 0:
+                        if s.ngram is None:
+                            s.ngram = NgramDrafter()
+                        proposals[i] = s.ngram.propose(s.tokens, maxes[i])
         # 3. budget: share the window's rows by expected value
         budget = self.window_rows
         demands = [Demand.geometric(s.stats.accept_rate(), len(p)) for s, p in zip(active, proposals)]

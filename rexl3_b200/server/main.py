@@ -37,7 +37,7 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--prefill-chunk", type=int, default=4096)
     p.add_argument("--window-rows", type=int, default=64)
     p.add_argument("--kv-dtype", choices=["bf16", "fp8"], default="bf16", help="fp8: E4M3 cache with per-head scales (calibrated at boot)")
-    p.add_argument("--spec", choices=["auto", "mtp", "copy", "self", "none"], default="auto")
+    p.add_argument("--spec", choices=["auto", "mtp", "copy", "ngram", "self", "none"], default="auto")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
     p.add_argument("--prefix-cache", choices=["on", "off"], default="on")

@@ -130,7 +130,59 @@ class CopyDrafter:
         return m, [at(i) for i in range(end, min(length, end + max_tokens))]
 
 
-SPEC_MODES = ("auto", "mtp", "copy", "self", "none")
+class NgramDrafter:
+    """Statistical n-gram drafter over the sequence's own text (prompt and output so far): for the longest context order that has been
+    seen (down from `order` - 1 tokens to 1), propose the continuation that followed it most often (ties: the most recent), token by token.
+    Complements the copy drafter: it needs no long exact match, so it fires on short repeated patterns (lists, code idioms, formats).
+    Indexed incrementally like the copy drafter; only committed tokens are ever indexed."""
+
+    def __init__(self, order: int = 4, max_draft: int = 7, min_count: int = 2):
+        if order < 2:
+            raise ValueError("order must be at least 2")
+        self.order, self.max_draft, self.min_count = order, max_draft, min_count
+        self.tables = [dict() for _ in range(order)]      # tables[k]: k-token context -> {next token: [count, last position]}
+        self.indexed = 0
+
+    def extend(self, tokens) -> None:
+        if len(tokens) < self.indexed:                     # the sequence got shorter: reused for another one
+            self.tables = [dict() for _ in range(self.order)]
+            self.indexed = 0
+        for pos in range(max(self.indexed, 1), len(tokens)):
+            nxt = tokens[pos]
+            for k in range(1, self.order):
+                if pos - k < 0:
+                    break
+                ent = self.tables[k].setdefault(tuple(tokens[pos - k:pos]), {}).setdefault(nxt, [0, 0])
+                ent[0] += 1
+                ent[1] = pos
+        self.indexed = len(tokens)
+
+    def _next(self, ctx):
+        for k in range(min(self.order - 1, len(ctx)), 0, -1):
+            cand = self.tables[k].get(tuple(ctx[-k:]))
+            if not cand:
+                continue
+            tok, (count, _last) = max(cand.items(), key=lambda kv: (kv[1][0], kv[1][1]))
+            if count >= self.min_count:
+                return tok
+        return None
+
+    def propose(self, tokens, max_tokens: int):
+        mx = min(max_tokens, self.max_draft)
+        if mx <= 0 or len(tokens) < 2:
+            return []
+        self.extend(tokens)
+        ctx, out = list(tokens[-(self.order - 1):]), []
+        for _ in range(mx):
+            t = self._next(ctx)
+            if t is None:
+                break
+            out.append(t)
+            ctx = (ctx + [t])[-(self.order - 1):]
+        return out
+
+
+SPEC_MODES = ("auto", "mtp", "copy", "ngram", "self", "none")
 
 
 @dataclass(frozen=True)
@@ -148,6 +200,11 @@ class SpecMode:
     @property
     def copy(self) -> bool:
         return self.name in ("auto", "copy")
+
+    @property
+    def ngram(self) -> bool:
+        """The n-gram drafter takes over where the copy drafter offers nothing ("auto"), or is the only host drafter ("ngram")."""
+        return self.name in ("auto", "ngram")
 
     @property
     def enabled(self) -> bool:

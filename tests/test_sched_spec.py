@@ -205,3 +205,46 @@ def test_draft_tree_best_first_and_accept():
     assert path == [] and committed == [999]
     g = spec.with_copy(t, [10, 55], 8)
     assert 55 in g.tokens and g.parents[g.tokens.index(55)] == 0
+
+
+def test_ngram_drafter_learns_short_patterns_and_stays_silent_without_evidence():
+    from rexl3_b200.spec import NgramDrafter
+    d = NgramDrafter(order=3, max_draft=5, min_count=2)
+    seq = [1, 2, 3, 9, 1, 2, 3, 8, 1, 2]
+    assert d.propose(seq, 4)[:1] == [3]                    # "1 2" was followed by 3 twice
+    assert d.propose(seq, 4) == [3]                        # ... and after "2 3" came 9 once and 8 once: no evidence, the chain stops
+    assert d.propose(seq + [3], 4) == []
+    assert NgramDrafter().propose([5, 6, 7, 8], 4) == []   # nothing repeated: nothing offered
+    # incremental indexing gives the same tables as indexing at once, and a shorter sequence resets them
+    a, b = NgramDrafter(order=3), NgramDrafter(order=3)
+    for n in range(2, len(seq) + 1):
+        a.propose(seq[:n], 3)
+    b.propose(seq, 3)
+    assert a.tables == b.tables
+    a.propose([4, 4], 3)
+    assert a.indexed == 2 and all(len(t) <= 1 for t in a.tables)
+    assert d.propose(seq, 0) == []
+
+
+def test_engine_uses_the_ngram_drafter_and_stays_exact():
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.mock import MockBackend, MockOptions
+    from rexl3_b200.sampling import GREEDY
+    prompt = [3, 4, 5, 6] * 6
+
+    def run(spec):
+        # order=2: the mock's next token depends on the last two tokens only, so its text falls into a cycle an n-gram table can learn
+        eng = Engine(MockBackend(MockOptions(order=2, vocab=16)), None, window_rows=16, spec=spec)
+        eng.submit(Request("a", prompt, 96, GREEDY))
+        out = []
+        for _ in range(600):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                assert ev.kind != "error", ev.message
+                if ev.kind == "tokens":
+                    out.extend(ev.tokens)
+        return out, eng.counters
+    plain, _ = run("none")
+    drafted, c = run("ngram")
+    assert drafted == plain and c["drafted"] > 0 and c["accepted"] > 0
