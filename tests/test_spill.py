@@ -64,3 +64,27 @@ def test_engine_refills_an_evicted_prefix_from_the_spill_tier(tmp_path):
     assert eng.counters["cached_tokens"] - before >= bt          # part of the prompt came back without being recomputed
     # no page leaks: everything the index still holds is accounted for
     assert be.pool.total_blocks() - be.pool.free_blocks() == len(prefix.entries)
+
+
+def test_server_flag_wires_the_spill_tier(tmp_path):
+    from starlette.testclient import TestClient
+
+    from rexl3_b200.server import main
+    d = str(tmp_path / "spill")
+    args = main.parser().parse_args(["--backend", "mock", "--mock", "vocab=512", "--slots", "2", "--max-model-len", "2048", "--prefix-cache-mib", "1",
+                                     "--prefix-spill-dir", d, "--prefix-spill-mib", "64"])
+    app, handle = main.make_app(args)
+    try:
+        assert handle.wait_ready(10)
+        with TestClient(app) as c:
+            a, b = "a" * 1500, "b" * 1500                         # 23 blocks each against a 16-block device cache
+            for p in (a, b, a):
+                r = c.post("/v1/completions", json={"prompt": p, "max_tokens": 4, "temperature": 0})
+                assert r.status_code == 200
+            t = c.get("/metrics").text
+        vals = {ln.split(" ")[0]: float(ln.split(" ")[1]) for ln in t.splitlines() if ln.startswith("rexl3_") and "{" not in ln}
+        assert vals["rexl3_engine_spilled_blocks_total"] > 0 and vals["rexl3_engine_unspilled_blocks_total"] > 0
+        assert vals["rexl3_prefix_spill_entries"] > 0 and vals["rexl3_prefix_cache_entries"] > 0
+        assert any(n.endswith(".blk") for n in os.listdir(d))
+    finally:
+        handle.stop()
