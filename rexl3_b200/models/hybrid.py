@@ -1,15 +1,21 @@
-"""Hybrid decoder family: every layer is a token mixer followed by the dense SwiGLU FFN, and the mixer is either a Mamba2
-(SSD) block with a constant-size recurrent state or (NoPE) GQA attention over the paged KV cache.
+"""Hybrid decoder family: every layer is a token mixer followed by the dense SwiGLU FFN, and the mixer is one of
+  'M'  a Mamba2 (SSD) block,
+  'G'  a gated delta net block (delta rule with a scalar decay per head),
+  'K'  a Kimi delta attention block (the same rule with a decay per key channel and a sigmoid output gate),
+  'A'  GQA attention over the paged KV cache (with or without rotary embedding),
+chosen per layer by `HybridConfig.pattern`.  The recurrent kinds keep a constant-size state per sequence.
 
-What it mirrors: the reference's `nemotron_h_omni` text backbone (Mamba2 + NoPE GQA blocks; crates/model/src/families/
-nemotron_h_omni/mod.rs:58-251, oracle ssm_ref.rs, kernels crates/cuda/csrc/nemotron_ssm.cu:1-45) with this engine's
-own executor: the Mamba2 layer is in_proj (EXL3 GEMM) -> finish to f32 rows -> conv + recurrence + gated norm
-(`ops/csrc/ssm.cu`, three launches) -> rotation -> out_proj (EXL3 GEMM), whose partials feed the same fused
-add + norm + rotate finish as an attention layer's o_proj.
+What it mirrors: the text backbones of the reference's `qwen` family (GQA + GDN, crates/model/src/families/qwen.rs, kernels
+crates/cuda/csrc/gdn.cu:1-25), its KDA layers (crates/cuda/csrc/kda.cu) and its `nemotron_h_omni` family (Mamba2 + NoPE GQA,
+crates/model/src/families/nemotron_h_omni/mod.rs:58-251, oracle ssm_ref.rs, kernels crates/cuda/csrc/nemotron_ssm.cu:1-45), with
+this engine's own executor: a recurrent layer is in_proj (EXL3 GEMM) -> finish to f32 rows -> conv + recurrence + gated norm
+(`ops/csrc/ssm.cu`) -> rotation -> out_proj (EXL3 GEMM), whose partials feed the same fused add + norm + rotate finish as an
+attention layer's o_proj.
 
-Recurrent state lives in two pools per Mamba2 layer, indexed by the engine's sequence slot.  A row at position 0 restarts
-the state, so slots are reused without a reset call.  Rows are always committed: an engine backend over this executor
-offers no drafts and no prefix cache (a cached prefix would need a state snapshot per block).
+Recurrent state lives in two pools per recurrent layer, indexed by the engine's sequence slot.  A row at position 0 restarts the
+state, so slots are reused without a reset call.  On the GPU every row fed is committed: the CUDA backend over this executor offers
+no drafts and no prefix cache.  The fp32 oracle (`ReferenceHybrid`, behind `engine.cpu_backend.CpuHybridBackend`) can snapshot and
+restore a sequence, which is how drafts, prompt scoring and the prefix cache work over recurrent layers there.
 """
 from __future__ import annotations
 
@@ -339,8 +345,11 @@ def delta_state_canonical(pool: torch.Tensor) -> torch.Tensor:
 
 # ====================================================================================================== sm_100a executor
 class HybridGPU(DenseGPU):
-    """One B200.  Attention layers run the dense executor's mixer; Mamba2 layers run `_mamba`.  A Mamba2 layer's in_proj / out_proj sit
-    under the keys "qkv" / "o" of its layer dict as well, so the shared layer loop finds each layer's input rotation and output scales."""
+    """One B200.  Attention layers run the dense executor's mixer; Mamba2, gated-delta-net and Kimi-delta-attention layers run the recurrent
+    branch of `_mixer` (in_proj GEMM -> f32 rows -> conv + recurrence + gated norm kernels -> rotation -> out_proj GEMM).  A recurrent layer's
+    in_proj / out_proj sit under the keys "qkv" / "o" of its layer dict as well, so the shared layer loop finds each layer's input rotation
+    and output scales.  State pools (`conv_pool`, `ssm_pool`) are indexed by the engine's sequence slot; `state_view` gives them in canonical
+    order."""
 
     def __init__(self, w: "HostWeights | HybridConfig", num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256,
                  device="cuda", max_prefill_rows: int = 8192, seed: int = 0, kv_dtype: str = "bf16"):
