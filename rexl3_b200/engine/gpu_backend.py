@@ -486,14 +486,27 @@ class _SkipFirstReplay:
         self.graph.replay()
 
 
+def deepest_snapshot(handles) -> int:
+    """Index of the last handle of a chain that carries a state snapshot (-1: none): a recurrent backend can restore up to there."""
+    return max((i for i, h in enumerate(handles) if h[2] is not None), default=-1)
+
+
 class HybridGpuBackend(DenseGpuBackend):
-    """Backend over a hybrid (Mamba2 + attention) executor.  The recurrent state advances with every row it is fed, so: no draft rows
-    (`supports_rollback` is False), no prefix cache (a cached block would need a state snapshot), and a window is never run twice for
-    one step (the eager run before a graph capture stands in for that graph's first replay)."""
+    """Backend over a hybrid (Mamba2 / delta-net + attention) executor.  The recurrent state advances with every row it is fed, so: no draft
+    rows (`supports_rollback` is False), and a window is never run twice for one step (the eager run before a graph capture stands in for
+    that graph's first replay).
+
+    Prefix cache: off unless `state_snapshots=True`.  With it, a block's handle is (page, snapshot or None): the KV pages of the attention
+    layers are shared by refcount as in the dense backend, and the handle of the block where a prefill slice ended also holds clones of the
+    slot's conv and state pool rows (the engine cuts a slice at the prompt's last block boundary for backends with `prefix_needs_cuts`).  A
+    restore goes as deep as the last handle with a snapshot.  A snapshot costs the model's whole per-stream state (hundreds of MiB for the
+    large configs), which `prefix_bytes_per_block` charges to every block.  This option has not run on a GPU yet; the same protocol is
+    exercised by the CPU hybrid backend."""
     name = "cuda-hybrid"
 
-    def __init__(self, model, max_slots=None, use_graphs: bool = True):
+    def __init__(self, model, max_slots=None, use_graphs: bool = True, state_snapshots: bool = False):
         super().__init__(model, max_slots=max_slots, use_graphs=use_graphs, self_draft=False)
+        self.state_snapshots = bool(state_snapshots)
 
     def supports_rollback(self) -> bool:
         return False
@@ -502,7 +515,50 @@ class HybridGpuBackend(DenseGpuBackend):
         return False
 
     def prefix_block_tokens(self):
-        return 0
+        return PAGE if self.state_snapshots else 0
+
+    def prefix_needs_cuts(self) -> bool:
+        return self.state_snapshots
+
+    def prefix_bytes_per_block(self):
+        return self.cfg.kv_bytes_per_token() * PAGE + self.cfg.state_bytes_per_slot()
+
+    def _snapshot(self, slot):
+        m = self.m
+        return {li: (m.conv_pool[li][slot].clone(), m.ssm_pool[li][slot].clone()) for li in m.ssm_pool}
+
+    def prefix_commit(self, slot, blocks):
+        ids = self.pages[slot][:blocks]
+        self.pool.retain(ids)
+        snap = self._snapshot(slot) if self.len[slot] == blocks * PAGE else None
+        return [("hpage", p, snap if i == len(ids) - 1 else None) for i, p in enumerate(ids)]
+
+    def prefix_restore(self, slot, handles):
+        assert self.len[slot] == 0 and not self.pages[slot]
+        best = deepest_snapshot(handles)
+        if best < 0:
+            return 0
+        ids = [h[1] for h in handles[:best + 1]]
+        self.pool.retain(ids)
+        self.pages[slot] = list(ids)
+        self.h_bt[slot, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        self.bt_dirty = True
+        self.bt_dirty_slots.add(slot)
+        m = self.m
+        for li, (conv, state) in handles[best][2].items():
+            m.conv_pool[li][slot].copy_(conv)
+            m.ssm_pool[li][slot].copy_(state)
+        self.len[slot] = len(ids) * PAGE
+        return self.len[slot]
+
+    def prefix_release(self, handles):
+        self.pool.release([h[1] for h in handles])
+
+    def prefix_export(self, handle):
+        return None
+
+    def prefix_import(self, payload):
+        return None
 
     def _capture(self, M, count, bucket):
         return _SkipFirstReplay(super()._capture(M, count, bucket))

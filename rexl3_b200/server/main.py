@@ -44,6 +44,8 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--prefix-cache-mib", type=int, default=4096)
     p.add_argument("--verify-pack", choices=["off", "sizes", "crc", "lock"], default="off",
                    help="check the pack before loading: file sizes against model.lock.json, per-tensor crc32.txt, or the lock's sha256 of every file")
+    p.add_argument("--state-snapshots", action="store_true",
+                   help="hybrid families on CUDA: snapshot the recurrent state where a prefill slice ends so the prefix cache can serve them")
     p.add_argument("--prefix-spill-dir", default="", help="directory (e.g. on NVMe) where prefix blocks evicted from the device cache are kept and reused")
     p.add_argument("--prefix-spill-mib", type=int, default=65536)
     p.add_argument("--default-max-tokens", type=int, default=512)
@@ -194,7 +196,7 @@ def build(args):
                 # the self-speculative drafter (first layers + shared head) is offered by families that define a draft depth
                 if is_hybrid:
                     from ..engine.gpu_backend import HybridGpuBackend
-                    be = HybridGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs)
+                    be = HybridGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs, state_snapshots=args.state_snapshots)
                 else:
                     be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs,
                                          self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)

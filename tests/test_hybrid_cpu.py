@@ -209,3 +209,9 @@ def test_prefix_cache_for_recurrent_state_through_slice_cuts(cfg):
         return CpuHybridBackend(w, max_slots=4, max_rows=16)
     assert make().prefix_needs_cuts()
     assert harness.cached_equals_cold(make, cfg.vocab, n=6) is None
+
+
+def test_deepest_snapshot_selection():
+    from rexl3_b200.engine.gpu_backend import deepest_snapshot
+    assert deepest_snapshot([("hpage", 1, None), ("hpage", 2, {0: None}), ("hpage", 3, None)]) == 1
+    assert deepest_snapshot([("hpage", 1, None)]) == -1 and deepest_snapshot([]) == -1
