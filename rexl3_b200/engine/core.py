@@ -235,13 +235,11 @@ class Engine:
         """Continue a device-cache chain with blocks held by the spill tier: import each into the backend and the index, in order."""
         max_blocks = (s.prompt_len - 1) // self.backend.prefix_block_tokens()
         k = len(chain)
-        protect = set(s.hashes[:k])
         while k < max_blocks and s.hashes[k] in self.spill:
             payload = self.spill.get(s.hashes[k])
             handle = self.backend.prefix_import(payload) if payload is not None else None
             if handle is None:
                 break
-            protect.add(s.hashes[k])
             dup, evicted = self.prefix.insert(s.hashes[:k + 1], [None] * k + [handle], self.backend.prefix_bytes_per_block())
             gone = [h for h in list(dup) + list(evicted) if h is not None]
             if gone:
