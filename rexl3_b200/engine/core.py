@@ -84,7 +84,7 @@ class Engine:
     def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
                  spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
                  prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b"", device_sampler: bool = False,
-                 spill=None):
+                 spill=None, arbiter=None):
         self.backend = backend
         self.admission = admission
         self.window_rows = min(window_rows, backend.max_rows)
@@ -95,6 +95,9 @@ class Engine:
         self.cost = cost
         self.prefix = prefix if (prefix is not None and backend.prefix_block_tokens() > 0) else None
         # second tier (sched.spill.SpillStore): blocks leaving the index are exported to it, and a lookup that ends early continues there
+        # optional spec.Arbiter: per round and stream it picks how many of the offered drafts to verify (or none) by expected committed tokens
+        # per model-millisecond, learns each source's acceptance by depth from the outcomes, and probes idle sources now and then
+        self.arbiter = arbiter
         self.prefix_cuts = bool(self.prefix is not None and getattr(backend, "prefix_needs_cuts", lambda: False)())
         self.spill = spill if self.prefix is not None else None
         if self.spill is not None:
@@ -310,6 +313,7 @@ class Engine:
             maxes.append(m)
         # 2. proposals: native drafter first, copy drafter otherwise
         proposals = [[] for _ in active]
+        sources = ["none"] * len(active)        # which drafter each proposal came from: "native" (backend drafter) or "copy" (host drafters)
         if any(maxes):
             if self.spec.native and self.backend.supports_native_draft():
                 asks = [DraftAsk(s.slot, s.tokens, m, s.req.sampling) for s, m in zip(active, maxes) if m > 0]
@@ -318,16 +322,28 @@ class Engine:
                     off = offers.get(s.slot)
                     if off is not None and maxes[i] > 0:
                         proposals[i] = list(off.tokens[:maxes[i]])
+                        sources[i] = "native" if proposals[i] else "none"
             if self.spec.copy:
                 for i, s in enumerate(active):
                     if not proposals[i] and maxes[i] > 0:
                         proposals[i] = s.drafter.propose(s.tokens, maxes[i])
+                        sources[i] = "copy" if proposals[i] else "none"
             if self.spec.ngram:
                 for i, s in enumerate(active):
                     if not proposals[i] and maxes[i] > 0:
                         if s.ngram is None:
                             s.ngram = NgramDrafter()
                         proposals[i] = s.ngram.propose(s.tokens, maxes[i])
+                        sources[i] = "copy" if proposals[i] else "none"
+        choices = None
+        if self.arbiter is not None:
+            offers = {s.req.id: ({sources[i]: len(proposals[i])} if proposals[i] else {}) for i, s in enumerate(active)}
+            picks = self.arbiter.choose(offers, self.window_rows)
+            choices = []
+            for i, s in enumerate(active):
+                c = picks[s.req.id]
+                proposals[i] = proposals[i][:c.drafts()] if c.kind == sources[i] else []
+                choices.append(c if proposals[i] else None)
         # 3. budget: share the window's rows by expected value
         budget = self.window_rows
         demands = [Demand.geometric(s.stats.accept_rate(), len(p)) for s, p in zip(active, proposals)]
@@ -376,6 +392,9 @@ class Engine:
                 continue
             a = accept(p, samples)
             s.rounds += 1
+            if choices is not None:
+                from ..spec.arbiter import NONE, Choice
+                self.arbiter.observe(s.req.id, Choice(choices[si].kind, len(p)) if (choices[si] is not None and p) else NONE, a)
             if p:
                 s.stats.update(len(p), a)
                 s.drafted += len(p)
@@ -533,6 +552,8 @@ class Engine:
 
     def _finish(self, s: _Seq, reason: str, message: str = "") -> None:
         self.backend.release(s.slot)
+        if self.arbiter is not None:
+            self.arbiter.forget(s.req.id)
         if self.admission is not None:
             self.admission.release(s.slot)
         else:

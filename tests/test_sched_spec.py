@@ -248,3 +248,33 @@ def test_engine_uses_the_ngram_drafter_and_stays_exact():
     plain, _ = run("none")
     drafted, c = run("ngram")
     assert drafted == plain and c["drafted"] > 0 and c["accepted"] > 0
+
+
+def test_engine_with_the_arbiter_stays_exact_and_learns_to_draft():
+    """The arbiter decides per round how many offered drafts are worth verifying; whatever it decides, the tokens equal plain decoding.  On a
+    model whose text cycles the copy / n-gram drafts are almost always right, so after its probes the arbiter keeps drafting."""
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.mock import MockBackend, MockOptions
+    from rexl3_b200.sampling import GREEDY
+    from rexl3_b200.spec import Arbiter
+    prompts = [[3, 4, 5, 6] * 6, [7, 8, 9] * 9]
+
+    def run(arbiter):
+        eng = Engine(MockBackend(MockOptions(order=2, vocab=16)), None, window_rows=16, spec="auto" if arbiter else "none", arbiter=arbiter)
+        for i, p in enumerate(prompts):
+            eng.submit(Request(f"r{i}", p, 120, GREEDY))
+        out = {f"r{i}": [] for i in range(len(prompts))}
+        for _ in range(800):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                assert ev.kind != "error", ev.message
+                if ev.kind == "tokens":
+                    out[ev.id].extend(ev.tokens)
+        return out, eng.counters
+    plain, c0 = run(None)
+    arb = Arbiter(verify_ms=lambda streams, rows: 10.0 + 0.05 * rows, probe_every=4)
+    got, c1 = run(arb)
+    assert got == plain
+    assert c1["drafted"] > 0 and c1["accepted"] > 0.8 * c1["drafted"] and c1["rounds"] < c0["rounds"]
+    assert arb.streams == {}                                  # forgotten when the requests finished
