@@ -44,6 +44,8 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--prefix-cache-mib", type=int, default=4096)
     p.add_argument("--verify-pack", choices=["off", "sizes", "crc", "lock"], default="off",
                    help="check the pack before loading: file sizes against model.lock.json, per-tensor crc32.txt, or the lock's sha256 of every file")
+    p.add_argument("--arbiter", action="store_true",
+                   help="let the speculation arbiter decide per round how many offered drafts to verify (default: share rows by acceptance statistics)")
     p.add_argument("--state-snapshots", action="store_true",
                    help="hybrid families on CUDA: snapshot the recurrent state where a prefill slice ends so the prefix cache can serve them")
     p.add_argument("--prefix-spill-dir", default="", help="directory (e.g. on NVMe) where prefix blocks evicted from the device cache are kept and reused")
@@ -77,7 +79,7 @@ def build(args):
             be = MockBackend(opts)
             prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=be.prefix_block_tokens()) if args.prefix_cache == "on" else None
             return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix))
+                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix), arbiter=_arbiter(args))
         info = {"backend": "mock"}
     else:
         from ..models import dense
@@ -203,7 +205,7 @@ def build(args):
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode(), device_sampler=args.device_sampler,
-                          spill=_spill_store(args, prefix))
+                          spill=_spill_store(args, prefix), arbiter=_arbiter(args))
     tok = load_tokenizer(folder, vocab)
     fmt = ChatFormat.from_dir(folder)
     return make, tok, fmt, name, info
@@ -247,6 +249,14 @@ def _is_expert_family(cfg) -> bool:
     from ..models import mla as mla_models
     from ..models import moe as moe_models
     return isinstance(cfg, (mla_models.MlaConfig, moe_models.MoEConfig))
+
+
+def _arbiter(args):
+    if not args.arbiter or args.no_drafts or args.spec == "none":
+        return None
+    from ..spec import Arbiter
+    # a window's time grows slowly with its rows (weights are read once per window): a flat cost plus a small slope per row
+    return Arbiter(verify_ms=lambda streams, rows: 10.0 + 0.05 * rows)
 
 
 def _spill_store(args, prefix):
