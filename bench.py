@@ -19,6 +19,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -180,8 +181,7 @@ def main():
             engine.step()
 
     run_steps(W)
-    clk_path = os.path.join(HERE, "gpurun_out", f"bench_clocks_rank{rank}.csv")
-    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    clk_path = os.path.join(tempfile.mkdtemp(prefix="rexl3_bench_"), f"clocks_rank{rank}.csv")
     mon, mon_f = clocks_monitor(clk_path, local)
     time.sleep(0.3)
     barrier()

@@ -115,6 +115,7 @@ class Engine:
         self.counters = dict(rounds=0, rows=0, prefill_tokens=0, decode_tokens=0, drafted=0, accepted=0, cached_tokens=0, requests=0,
                              finished=0, errors=0, spilled_blocks=0, unspilled_blocks=0)
         self.phase_ns = dict(draft=0, verify=0, commit=0, prefill=0)
+        self._window_start = 0         # rotation of the decode window over the active streams when they outnumber its rows
         self.pause_decode = False      # hold decode rounds (used while a benchmark fills the batch with prompts)
 
     # ------------------------------------------------------------------ submit / cancel
@@ -303,7 +304,12 @@ class Engine:
         active = [self.seqs[i] for i in self.order if self.seqs[i].prefilled >= self.seqs[i].prompt_len and self.seqs[i].generated > 0]
         if not active:
             return
-        active = active[:self.window_rows]
+        if len(active) > self.window_rows:
+            # more decodable streams than window rows: the window's start rotates, so every stream gets its turn (first come is not
+            # first served forever) and none waits for an earlier one to finish
+            start = self._window_start % len(active)
+            active = (active[start:] + active[:start])[:self.window_rows]
+            self._window_start = start + self.window_rows
         t0 = time.perf_counter_ns()
         # 1. how many drafts each stream may use
         maxes = []
@@ -431,8 +437,12 @@ class Engine:
         self.phase_ns["commit"] += time.perf_counter_ns() - t2
 
     def _reasoning_budget(self, s, t: int):
-        """Reasoning budget (reference crates/engine/src/lib.rs:572-577): counts tokens inside the thinking block; when the budget is
-        used up the closing tag's tokens replace the sampled ones, one per round.  -> (token to emit, whether it was forced)."""
+        """Reasoning budget (reference crates/engine/src/lib.rs:560-603): every generated token, the one sampled at the end of prefill
+        included, passes through here before it is committed.  `used` counts the tokens committed inside the thinking block; the token
+        that would be committed when `used == reasoning_budget` while the block is still open is replaced by the closing tag (index 0 for
+        a budget of 0), whose remaining tokens follow one per call.  A closing tag the model commits itself ends the block and spends the
+        budget.  The rule reads committed tokens only, so the serial and every drafted path commit the same token at every index.
+        -> (token to commit, whether it replaced the sample)."""
         st = s.reasoning
         if st is None:
             st = s.reasoning = dict(open=s.req.reasoning_open, used=0, force=None, close_match=0, open_match=0)
@@ -443,19 +453,19 @@ class Engine:
                 if st["open_match"] == len(opn):
                     st.update(open=True, open_match=0, used=0, close_match=0)
             return t, False
+        if st["force"] is None and st["used"] >= s.req.reasoning_budget and not (st["close_match"] > 0 and t == close[st["close_match"]]):
+            st.update(force=0, close_match=0)     # out of budget and the model is not in the middle of closing the block itself
         if st["force"] is not None:
-            t = close[st["force"]]
+            forced = close[st["force"]]
             st["force"] += 1
             if st["force"] == len(close):
                 st.update(open=False, force=None)
-            return t, True
+            return forced, forced != t
         st["close_match"] = st["close_match"] + 1 if t == close[st["close_match"]] else (1 if t == close[0] else 0)
         if st["close_match"] == len(close):
             st.update(open=False, close_match=0)
             return t, False
         st["used"] += 1
-        if st["used"] >= s.req.reasoning_budget and st["close_match"] == 0:
-            st["force"] = 0
         return t, False
 
     # ------------------------------------------------------------------ prefill
@@ -529,6 +539,8 @@ class Engine:
         except SamplingError as e:
             self._finish(s, "error", message=f"sampling failed: {e}")
             return
+        if s.req.reasoning_budget is not None and s.req.think_close_ids:
+            t, _ = self._reasoning_budget(s, t)     # index 0 of the reply obeys the budget like every later token
         s.tokens.append(t)
         s.generated = 1
         s.t_first = time.monotonic()

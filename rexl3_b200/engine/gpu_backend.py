@@ -65,6 +65,22 @@ class DenseGpuBackend(Backend):
         self.graph_kernels = {}     # graph key -> kernels launched per replay
         self.replayed_kernels = 0
         self._err = None
+        # The pinned staging arrays are read by asynchronous copies queued behind earlier kernels.  An event recorded after the last
+        # such copy is waited for before the host writes any of them again (a prefill slice that returns no candidates ends without
+        # a stream synchronisation, so the next slice's fill could otherwise overwrite rows the copy engine has not fetched yet).
+        self._staged = torch.cuda.Event()
+        self._staged_pending = False
+
+    # ------------------------------------------------------------------ staging
+    def _host_writable(self) -> None:
+        """Blocks until the device has taken every upload issued so far from the pinned staging arrays."""
+        if self._staged_pending:
+            self._staged.synchronize()
+            self._staged_pending = False
+
+    def _uploaded(self) -> None:
+        self._staged.record()
+        self._staged_pending = True
 
     # ------------------------------------------------------------------ pages
     def _ensure(self, slot: int, tokens: int) -> None:
@@ -78,6 +94,7 @@ class DenseGpuBackend(Backend):
             raise BackendError("KV page pool exhausted", fatal=False)
         base = len(self.pages[slot])
         self.pages[slot].extend(got)
+        self._host_writable()
         self.h_bt[slot, base:base + need] = torch.tensor(got, dtype=torch.int32)
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
@@ -85,12 +102,14 @@ class DenseGpuBackend(Backend):
     def _sync_bt(self) -> None:
         if self.bt_dirty:
             self.d_bt.copy_(self.h_bt, non_blocking=True)
+            self._uploaded()
             self.h2d_bytes += self.h_bt.numel() * 4
             self.bt_dirty = False
             self.bt_dirty_slots.clear()
 
     def _fill_rows(self, specs) -> int:
         """specs: list of (slot, first_position, tokens).  Fills the pinned staging rows; returns M."""
+        self._host_writable()
         h = self.h_rows.numpy()
         r = 0
         if all(len(t) == 1 for _, _, t in specs):
@@ -118,6 +137,7 @@ class DenseGpuBackend(Backend):
 
     def _upload_rows(self, M: int) -> None:
         self.d_rows[:, :M].copy_(self.h_rows[:, :M], non_blocking=True)
+        self._uploaded()
         self.h2d_bytes += 5 * M * 4
 
     # ------------------------------------------------------------------ prefill
@@ -162,6 +182,7 @@ class DenseGpuBackend(Backend):
         self._upload_rows(M)
         self._sync_bt()
         self.d_pf[:, :n].copy_(self.h_pf[:, :n], non_blocking=True)
+        self._uploaded()
         self.h2d_bytes += 4 * n * 4
         d = self.d_rows
         pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=n, max_qlen=max_qlen)
@@ -318,6 +339,7 @@ class DenseGpuBackend(Backend):
         self.pages[slot] = []
         self.len[slot] = 0
         self.pending[slot] = 0
+        self._host_writable()
         self.h_bt[slot].zero_()
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
@@ -339,6 +361,7 @@ class DenseGpuBackend(Backend):
             self._upload_rows(M)
             self._sync_bt()
             self.d_pf[:, :1].copy_(self.h_pf[:, :1], non_blocking=True)
+            self._uploaded()
             d = self.d_rows
             pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=1, max_qlen=M)
             last = a + len(part) >= len(tokens)
@@ -374,6 +397,7 @@ class DenseGpuBackend(Backend):
         k = min(self.DK, max(a.max_drafts for a in asks))
         if k <= 0:
             return {}
+        self._host_writable()
         h = self.h_draft.numpy()
         top = 0
         for i, a in enumerate(asks):
@@ -389,6 +413,7 @@ class DenseGpuBackend(Backend):
             top = max(top, p0 + k)
         bucket = min(self.m.max_ctx_alloc, (top + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
         self.d_draft[:k, :, :n].copy_(self.h_draft[:k, :, :n], non_blocking=True)
+        self._uploaded()
         self.h2d_bytes += k * 5 * n * 4
         self._sync_bt()
         if self.use_graphs:
@@ -428,6 +453,7 @@ class DenseGpuBackend(Backend):
         ids = [p for _, p in handles]
         self.pool.retain(ids)
         self.pages[slot] = list(ids)
+        self._host_writable()
         self.h_bt[slot, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
@@ -541,6 +567,7 @@ class HybridGpuBackend(DenseGpuBackend):
         ids = [h[1] for h in handles[:best + 1]]
         self.pool.retain(ids)
         self.pages[slot] = list(ids)
+        self._host_writable()
         self.h_bt[slot, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)

@@ -43,6 +43,8 @@ class _TpExec:
         self.tp_graphs = {}
         self.tp_graph_kernels = {}
         self.marks = []
+        self._staged = torch.cuda.Event()       # recorded after the last upload from the pinned arrays; waited for before the next host write
+        self._staged_pending = False
 
     # ---- launches
     def run_window_eager(self, M, count, bucket):
@@ -102,6 +104,9 @@ class _TpExec:
             dist.barrier(group=self.ctrl)
             return True
         k = 0
+        if self._staged_pending:
+            self._staged.synchronize()          # the previous message's copies may still be queued behind its kernels
+            self._staged_pending = False
         self.x_rows_h.numpy()[:, :M] = payload[k:k + 5 * M].reshape(5, M)
         k += 5 * M
         if nseq:
@@ -117,10 +122,13 @@ class _TpExec:
         self.x_rows[:, :M].copy_(self.x_rows_h[:, :M], non_blocking=True)
         if n_dirty:
             self.x_bt.copy_(self.x_bt_h, non_blocking=True)
+        if op != OP_WINDOW:
+            self.x_pf[:, :nseq].copy_(self.x_pf_h[:, :nseq], non_blocking=True)
+        self._staged.record()
+        self._staged_pending = True
         if op == OP_WINDOW:
             self.run_window(M, count, bucket)
         else:
-            self.x_pf[:, :nseq].copy_(self.x_pf_h[:, :nseq], non_blocking=True)
             self.run_prefill(M, nseq, max_qlen, last_rows, count)
         return True
 
@@ -236,6 +244,7 @@ class DenseTpBackend(DenseGpuBackend):
         self._upload_rows(M)
         self._sync_bt()
         self.d_pf[:, :n].copy_(self.h_pf[:, :n], non_blocking=True)
+        self._uploaded()
         self.h2d_bytes += 4 * n * 4
         self.ex.run_prefill(M, n, max_qlen, last_rows, count)
         return self._download(len(last_rows), count) if last_rows else None

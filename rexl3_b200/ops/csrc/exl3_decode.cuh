@@ -35,6 +35,26 @@ __device__ __forceinline__ uint32_t state_of(const uint32_t (&w)[NW + 1]) {
   }
 }
 
+// Pipe balance of the decode (measured on B200 with register-only loops, lane-operations per clock per SM): the integer ALU pipe
+// (LOP3, SHF, PRMT) issues 64, the multiply pipe (IMAD, HADD2 / HFMA2, DP2A / DP4A: they share ONE pipe) issues 64, and the two run
+// side by side.  The decode is bound by whichever pipe gets more operations per weight, so the work is split evenly between them:
+//  * (x & mask) ^ flip is ONE three-input LOP3.  Written with two literals the compiler emits an AND and an XOR (a LOP3 takes a single
+//    immediate); with the constants read from constant memory, which it cannot fold, it keeps the one instruction.
+//  * half of the "low 16 bits" extractions are DP2A(x, 1) on the multiply pipe instead of an AND on the ALU pipe.
+static __constant__ uint32_t rx_dec_consts[4] = {0x8FFF8FFFu, 0x3B603B60u, 1u, 0u};
+
+__device__ __forceinline__ uint32_t mask_flip(uint32_t x) {
+  uint32_t y;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(y) : "r"(x), "r"(rx_dec_consts[0]), "r"(rx_dec_consts[1]));   // (x & mask) ^ flip
+  return y;
+}
+// x & 0xFFFF computed on the multiply pipe: x.h0 * 1 + x.h1 * 0 + 0
+__device__ __forceinline__ uint32_t low16_mul(uint32_t x) {
+  uint32_t s;
+  asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(s) : "r"(x), "r"(rx_dec_consts[2]), "r"(rx_dec_consts[3]));
+  return s;
+}
+
 template <int CB>
 __device__ __forceinline__ uint32_t pair_to_half2(uint32_t sa, uint32_t sb) {
   if constexpr (CB == CB_MUL1) {
@@ -53,23 +73,29 @@ __device__ __forceinline__ uint32_t pair_to_half2(uint32_t sa, uint32_t sb) {
     } else {
       xa = sa * 89226354u + 64248484u; xb = sb * 89226354u + 64248484u;
     }
-    xa = (xa & 0x8FFF8FFFu) ^ 0x3B603B60u;
-    xb = (xb & 0x8FFF8FFFu) ^ 0x3B603B60u;
-    // lo + hi of each word as a half2 add with swizzled operands (fp16 pipe), then ONE byte permute packs the pair:
-    // the integer ALU pipe issues at half rate and is the bottleneck of the decode, so work is moved off it
+    xa = mask_flip(xa);
+    xb = mask_flip(xb);
+    // lo + hi of each word as a half2 add with swizzled operands (multiply pipe), then ONE byte permute packs the pair
     const __half2 a = *reinterpret_cast<const __half2*>(&xa), b = *reinterpret_cast<const __half2*>(&xb);
     const __half2 ra = __hadd2(__low2half2(a), __high2half2(a)), rb = __hadd2(__low2half2(b), __high2half2(b));
     return __byte_perm(*reinterpret_cast<const uint32_t*>(&ra), *reinterpret_cast<const uint32_t*>(&rb), 0x7610);
   }
 }
 
-// 4 sixteen-bit fields of X at MSB-first bit offsets 4, 8, 12, 16 in 5 integer operations
+// 4 sixteen-bit fields of X at MSB-first bit offsets 4, 8, 12, 16: a shift and two byte permutes on the ALU pipe; the two
+// "low 16 bits" go to the multiply pipe when the codebook leaves it room (MUL_LOW), else they are two ANDs
+template <bool MUL_LOW = false>
 __device__ __forceinline__ void extract4(uint32_t X, uint32_t& s0, uint32_t& s1, uint32_t& s2, uint32_t& s3) {
   const uint32_t X4 = X >> 4;
   s0 = __byte_perm(X4, 0, 0x4421);
   s1 = __byte_perm(X, 0, 0x4421);
-  s2 = X4 & 0xFFFFu;
-  s3 = X & 0xFFFFu;
+  if constexpr (MUL_LOW) {
+    s2 = low16_mul(X4);
+    s3 = low16_mul(X);
+  } else {
+    s2 = X4 & 0xFFFFu;
+    s3 = X & 0xFFFFu;
+  }
 }
 
 // 4.0 bpw fast path: 32 consecutive values from their 4 words (w[1..4]) and the word before them (w[0]).
@@ -81,8 +107,8 @@ __device__ __forceinline__ void decode32_b4(const uint32_t (&w)[5], uint32_t (&h
   for (int i = 0; i < 4; ++i) {
     const uint32_t A = __funnelshift_l(w[i + 1], w[i], 16), B = w[i + 1];
     uint32_t s0, s1, s2, s3, s4, s5, s6, s7;
-    extract4(A, s0, s1, s2, s3);
-    extract4(B, s4, s5, s6, s7);
+    extract4<CB != CB_MUL1>(A, s0, s1, s2, s3);
+    extract4<CB != CB_MUL1>(B, s4, s5, s6, s7);
     h2[4 * i + 0] = pair_to_half2<CB>(s0, s1);
     h2[4 * i + 1] = pair_to_half2<CB>(s2, s3);
     h2[4 * i + 2] = pair_to_half2<CB>(s4, s5);

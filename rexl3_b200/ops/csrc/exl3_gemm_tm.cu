@@ -188,7 +188,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           for (int m = 0; m < 4; ++m) {
             const uint32_t X = __funnelshift_lc(w[m + 1], w[m], sh);
             uint32_t s0, s1, s2, s3;
-            extract4(X, s0, s1, s2, s3);
+            extract4<CB != CB_MUL1>(X, s0, s1, s2, s3);
             regs[8 * kk + m] = pair_to_half2<CB>(s0, s1);       // k = 16 kt + 2m, 2m+1
             regs[8 * kk + 4 + m] = pair_to_half2<CB>(s2, s3);   // k = 16 kt + 8 + 2m, +1
           }

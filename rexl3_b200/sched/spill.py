@@ -4,8 +4,10 @@ read back when a later prompt walks the same chain, instead of being recomputed.
 
 One file per block, named by the block's chain hash: `RXSP` magic, payload length, CRC32, payload.  Writes go to a temporary name and
 are renamed, so a crash leaves whole files or none.  The store keeps an LRU over what it holds within a byte budget, drops files that
-fail their checksum, and can adopt the files already in its directory (a restart keeps its warm prefixes: the chain hash covers the
-cache namespace, i.e. the model, so a foreign file never matches).
+fail their checksum, and can adopt the files already in its directory (a restart keeps its warm prefixes).  A file is found again
+only through its chain hash, which starts from the engine's cache namespace; the server derives that namespace from the pack
+fingerprint, the KV dtype and the FP8 scale tensor (`server.main.cache_namespace`), so pages written by a different pack, a
+re-quantised pack of the same name or a differently calibrated cache are never matched.
 """
 from __future__ import annotations
 

@@ -133,7 +133,7 @@ def build(args):
                 from ..engine.lockstep import LockstepLeader
                 be = LockstepLeader(_build_ep_backend(args, cfg, ctx, kv_tokens), ctx.ctrl)
                 return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                              max_drafts=args.max_drafts, prefix=None, cache_namespace=name.encode())
+                              max_drafts=args.max_drafts, prefix=None, cache_namespace=cache_namespace(name, cfg, info, args))
             blocks = -(-args.max_model_len // dense.PAGE) + 1
             pages = -(-kv_tokens // dense.PAGE) + args.slots
             shard, _group = tprt.build_dense_tp(ctx, cfg, num_pages=pages, max_rows=max(256, args.prefill_chunk), max_slots=args.slots,
@@ -141,7 +141,7 @@ def build(args):
             be = DenseTpBackend(shard, args.slots, ctx.ctrl, use_graphs=not args.no_graphs)
             prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode())
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args))
 
         def make():
             with boot.phase("engine", backend=args.backend, ranks=world):
@@ -158,7 +158,7 @@ def build(args):
                     be = CpuHybridBackend(weights if weights is not None else hybrid_models.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
                 else:
                     be = CpuDenseBackend(weights if weights is not None else dense.random_weights(cfg), max_slots=args.slots, max_rows=args.window_rows)
-                adm, prefix = None, None
+                adm, prefix, model = None, None, None
             else:
                 import torch
                 from ..engine.gpu_backend import DenseGpuBackend
@@ -204,11 +204,33 @@ def build(args):
                                          self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=name.encode(), device_sampler=args.device_sampler,
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args, model), device_sampler=args.device_sampler,
                           spill=_spill_store(args, prefix), arbiter=_arbiter(args))
     tok = load_tokenizer(folder, vocab)
     fmt = ChatFormat.from_dir(folder)
     return make, tok, fmt, name, info
+
+
+def cache_namespace(name: str, cfg, info: dict, args, model=None) -> bytes:
+    """Namespace of the prefix cache and of the spill directory: everything that decides what a KV page of some token chain holds.
+    The served name alone is not enough (a re-quantised or fine-tuned pack under the same name, or an FP8 cache with newly calibrated
+    per-head scales, would hash to the same chains and stale pages would be adopted at start): the pack fingerprint (for random-init
+    weights the configuration and its seed), the KV dtype and a digest of the FP8 scale tensor are folded in."""
+    import dataclasses
+    import hashlib
+    h = hashlib.sha256()
+    h.update(name.encode())
+    fp = info.get("pack_fingerprint")
+    if fp:
+        h.update(b"pack:" + str(fp).encode())
+    else:
+        desc = dataclasses.asdict(cfg) if dataclasses.is_dataclass(cfg) else {"name": getattr(cfg, "name", "")}
+        h.update(b"random-init:" + repr(sorted(desc.items())).encode() + b":seed0")
+    h.update(b"kv:" + str(getattr(args, "kv_dtype", "bf16")).encode())
+    scale = getattr(model, "kv_scale", None) if model is not None else None
+    if scale is not None:
+        h.update(b"kv_scale:" + scale.detach().float().cpu().numpy().tobytes())
+    return h.hexdigest()[:32].encode()
 
 
 def _tp_boot_gate(args, cfg, ctx) -> None:

@@ -107,7 +107,8 @@ class EngineHandle:
         self.state = "loading"
         self.error = ""
         self.tickets = {}
-        self.pending = 0                 # queued + running requests
+        self.pending = 0                 # queued + running requests; written by HTTP threads and by the engine thread, always under _plock
+        self._plock = threading.Lock()
         self.heartbeat = time.monotonic()
         self.engine: Engine | None = None
         self.consecutive_errors = 0
@@ -124,12 +125,13 @@ class EngineHandle:
     def submit(self, req: Request, loop: asyncio.AbstractEventLoop) -> Ticket:
         if self.state not in ("ready", "degraded"):
             raise RuntimeError(self.state)
-        if self.pending >= self.cfg.queue_depth:
-            raise OverflowError("queue full")
+        with self._plock:
+            if self.pending >= self.cfg.queue_depth:
+                raise OverflowError("queue full")
+            self.pending += 1
         t = Ticket(req.id, loop, asyncio.Queue())
         if req.deadline is None:
             req.deadline = time.monotonic() + self.cfg.request_timeout_s
-        self.pending += 1
         self.cmd.put(("submit", req, t))
         return t
 
@@ -153,11 +155,16 @@ class EngineHandle:
         return self.state in ("ready", "degraded") and self.pending > 0 and time.monotonic() - self.heartbeat > stale_s
 
     # ------------------------------------------------------------------ the engine thread
+    def _done_one(self) -> None:
+        with self._plock:
+            self.pending = max(0, self.pending - 1)
+
     def _fail_all(self, message: str) -> None:
         for t in list(self.tickets.values()):
             t.post(("error", message))
         self.tickets.clear()
-        self.pending = 0
+        with self._plock:
+            self.pending = 0
 
     def _run(self) -> None:
         try:
@@ -177,7 +184,7 @@ class EngineHandle:
                     if kind == "submit":
                         if draining:
                             b.post(("error", "draining"))
-                            self.pending -= 1
+                            self._done_one()
                             continue
                         try:
                             eng.submit(a)
@@ -186,7 +193,7 @@ class EngineHandle:
                         except (ValueError, AdmitError) as e:
                             code = "context_length_exceeded" if isinstance(e, AdmitError) and e.kind in ("ContextTooLong", "NeverFits") else "invalid"
                             b.post(("refused", code, str(e)))
-                            self.pending -= 1
+                            self._done_one()
                     elif kind == "score":
                         loop, fut = b
                         try:
@@ -275,7 +282,7 @@ class EngineHandle:
                     t.post(("error", ev.message or ev.reason))
                     self.metrics.inc("finished_total", reason="error")
                 self.tickets.pop(ev.id, None)
-                self.pending = max(0, self.pending - 1)
+                self._done_one()
 
     def stop(self) -> None:
         self.cmd.put(("stop", None, None))

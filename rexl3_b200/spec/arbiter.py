@@ -1,9 +1,16 @@
-"""The speculation arbiter: per round and per stream, which drafter's proposal to verify (native head, copy drafter or
-none), chosen by expected committed tokens per model-millisecond, with periodic probing so no estimate goes stale.
+"""Draft-source selection for speculative rounds.
 
-Pure functions of the costs handed in and the outcomes reported, so it is tested on the CPU.  Behaviour parity:
-reference crates/spec/src/arbiter.rs:27-130 (Choice, DepthCurve with chain prior and fade), :255-394 (choose by
-coordinate ascent from "nobody drafts", observe, probing with a gap that doubles after a failed probe).
+Each decode round, every stream can have its window filled from one of three sources: the backend's own draft head
+("native"), the n-gram copy drafter ("copy"), or nothing.  This module picks the source and the draft count that
+maximise committed tokens per millisecond of model time, from two inputs only: the cost figures the caller supplies
+(what a draft step and a verify row cost) and the acceptance outcomes it reports back.  Acceptance is tracked per
+draft depth as an exponentially decayed accept/offer ratio seeded with a prior, so a drafter that stops working
+loses its slot within a few rounds; a source that is currently not chosen is still tried every so often (the probe
+interval doubles each time a probe loses) so that a recovered drafter is noticed.  No GPU, no clock: everything
+here is a pure function of its arguments and runs in the CPU tests.
+
+Same role as the reference's crates/spec/src/arbiter.rs:27-130 (choice type, per-depth curve) and :255-394
+(selection, feedback, probing).
 """
 from __future__ import annotations
 

@@ -140,7 +140,7 @@ def test_reasoning_budget_forces_the_closing_tag():
                 out.extend(ev.tokens)
     assert len(out) == 24
     i = out.index(close[0])
-    assert 5 <= i <= 6 and out[i + 1] == close[1]          # the first generated token comes from the prefill and is not counted
+    assert i == 5 and out[i + 1] == close[1]               # the reply's token at index `budget` is the forced close (index 0 is counted)
     assert out[:i] == base[:i]                               # identical up to the forced close
     assert out.count(close[0]) == 1
     # a closing tag produced by the model itself ends the block: no forcing afterwards
@@ -153,3 +153,31 @@ def test_reasoning_budget_forces_the_closing_tag():
             if ev.kind == "tokens":
                 out2.extend(ev.tokens)
     assert out2 == base
+
+
+def _run_budget(budget, close, spec="copy", prompt=None, n=12):
+    eng = Engine(MockBackend(MockOptions(slots=2, vocab=8000)), None, spec=spec)
+    eng.submit(Request("r", prompt or list(range(10, 40)), n, GREEDY, reasoning_budget=budget, think_close_ids=close, reasoning_open=True))
+    out = []
+    while eng.has_work():
+        for ev in eng.step():
+            if ev.kind == "tokens":
+                out.extend(ev.tokens)
+    return out
+
+
+def test_reasoning_budget_zero_one_and_a_close_sampled_first():
+    """The close is forced at the reply's index `budget` (0 -> the very first token, which is sampled at the end of prefill); a close the
+    model commits itself, even as its first token, spends the budget and is never forced again.  Serial and drafted paths agree."""
+    base = generate(Engine(MockBackend(MockOptions(slots=2, vocab=8000)), None, spec="none"), [list(range(10, 40))], 12, GREEDY)[0]
+    for spec in ("none", "copy"):
+        out0 = _run_budget(0, (7001,), spec)
+        assert out0[0] == 7001 and out0.count(7001) == 1
+        out1 = _run_budget(1, (7001,), spec)
+        assert out1[0] == base[0] and out1[1] == 7001 and out1.count(7001) == 1
+        # the model's own first token is the close tag: the block ends there and nothing is forced later
+        first = _run_budget(4, (base[0],), spec)
+        assert first == base
+        # a two-token close with budget 0 occupies indices 0 and 1
+        two = _run_budget(0, (7001, 7002), spec)
+        assert two[:2] == [7001, 7002] and two.count(7001) == 1

@@ -88,3 +88,22 @@ def test_server_flag_wires_the_spill_tier(tmp_path):
         assert any(n.endswith(".blk") for n in os.listdir(d))
     finally:
         handle.stop()
+
+
+def test_cache_namespace_separates_packs_kv_dtypes_and_scales():
+    """The prefix-cache / spill namespace changes with the pack fingerprint, the KV dtype and the FP8 scale tensor, not only the name."""
+    import types
+    import torch
+    from rexl3_b200.models import dense
+    from rexl3_b200.server.main import cache_namespace
+    cfg = dense.CONFIGS["test-hd128"]
+    a16 = types.SimpleNamespace(kv_dtype="bf16")
+    a8 = types.SimpleNamespace(kv_dtype="fp8")
+    base = cache_namespace("m", cfg, {"pack_fingerprint": "aa"}, a16)
+    assert base == cache_namespace("m", cfg, {"pack_fingerprint": "aa"}, a16)
+    assert base != cache_namespace("m", cfg, {"pack_fingerprint": "bb"}, a16)       # re-quantised pack, same served name
+    assert base != cache_namespace("m", cfg, {}, a16)                               # random-init is its own namespace
+    assert base != cache_namespace("m", cfg, {"pack_fingerprint": "aa"}, a8)
+    m1 = types.SimpleNamespace(kv_scale=torch.ones(2, 2, 2))
+    m2 = types.SimpleNamespace(kv_scale=torch.ones(2, 2, 2) * 1.5)
+    assert cache_namespace("m", cfg, {"pack_fingerprint": "aa"}, a8, m1) != cache_namespace("m", cfg, {"pack_fingerprint": "aa"}, a8, m2)
