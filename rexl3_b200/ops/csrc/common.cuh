@@ -71,13 +71,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` is a CTA-shared word every role polls, so one role's timeout unwinds all.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int site) {
+// `sleep_ns` > 0: the waiter sleeps that long between polls.  A role that waits most of the time (a producer for its consumers, the
+// MMA issuer for the decode warps) then costs a few hundred instructions per kernel instead of a poll loop that competes with the
+// working warps for issue slots (measured: polling was one instruction in five of the decode GEMM).  0: poll back to back, for waits
+// on the critical path.  The abort word and the clock are read every 16th failed poll.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int site, uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
+  uint32_t polls = 0;
   while (true) {
+    if (sleep_ns != 0) __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
+    if ((++polls & 15u) == 0) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > RX_WAIT_LIMIT_NS) {
         *abort_flag = 1;
@@ -101,6 +106,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst_smem, const void* tmap, in
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst_smem)),
       "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// 16-byte shared-memory load by shared-window address (a plain pointer dereference compiles to a generic load here)
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+  return v;
 }
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
@@ -148,6 +159,15 @@ __device__ __forceinline__ void tc_st_32x32b_x32(uint32_t taddr, const uint32_t 
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
       "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
       "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// 32 lanes x 32 bit, 16 consecutive columns: thread t of the warp writes TMEM lane (base lane + t)
+__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+      "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 

@@ -24,7 +24,7 @@ namespace rx {
 constexpr int TM_KCH = 128;                       // k per pipeline chunk: 8 k-tiles, two 128-byte swizzle rows of fp16
 constexpr int TM_STRIP = 128;
 constexpr int TM_RAW_STAGES_MAX = 6;
-__host__ __device__ constexpr int tm_raw_stages(int ng) { return ng == 4 ? 4 : 6; }   // the 256-row variant needs the room for B
+__host__ __device__ constexpr int tm_raw_stages(int ng) { return ng == 4 ? 4 : 6; }   // ring of compressed chunks (8 KB each); the 256-row variant needs the room for B
 constexpr int TM_OP_STAGES = 3;                   // activation (B) ring depth
 // A-stage ring depth.  A decode group waits for "the MMA that last read this stage"; that wait is only sound while the group
 // cannot run two phases ahead of the barrier, which needs at least as many A stages as decode groups.
@@ -34,10 +34,12 @@ constexpr int TM_A_COLS = TM_KCH / 2;             // TMEM columns of one A stage
 
 __host__ __device__ inline int tm_smem_bytes(int brows, int ng) { return TM_OP_STAGES * brows * 256 + tm_raw_stages(ng) * TM_RAW_STAGE_BYTES + 256; }
 
-// Warps: 0 = weight producer, 1 = MMA issuer (+TMEM owner), 2 = activation producer, 3 = idle spare (keeps the decode
-// groups aligned to 4 warps), then NG decode groups of 4 warps.
+// Warps: 0 = weight producer, 1 = MMA issuer (+TMEM owner), 2 = activation producer, then NG decode groups of 4 consecutive warps.
+// A warp may touch the TMEM lane quarter (warp index mod 4); any 4 consecutive warps cover the four quarters, so the groups need
+// no alignment and no spare warp (fewer threads per CTA leave more registers per decode thread at two CTAs per SM).
+constexpr int TM_ROLE_WARPS = 3;
 template <int CB, int NG>
-__global__ void __launch_bounds__(128 + NG * 128, (NG == 2 ? 2 : 1))
+__global__ void __launch_bounds__(TM_ROLE_WARPS * 32 + NG * 128, (NG <= 3 ? 2 : 1))
 exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, float* __restrict__ part, int rows,
                     int K, int N, int splits, int brows, int* status, const __grid_constant__ GemmTp tp) {
   constexpr int TM_RAW_STAGES = tm_raw_stages(NG);
@@ -103,7 +105,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int x = strip * 256;
       for (int c = TM_RAW_STAGES; c < nchunks; ++c, y += 8) {   // the first ring's worth was issued in the prologue
         const int s = c % TM_RAW_STAGES;
-        if (!mbar_wait(&raw_empty[s], ((c / TM_RAW_STAGES) - 1) & 1, abort_flag, status, 110)) break;
+        if (!mbar_wait(&raw_empty[s], ((c / TM_RAW_STAGES) - 1) & 1, abort_flag, status, 110, 1000)) break;
         mbar_arrive_expect_tx(&raw_full[s], TM_RAW_STAGE_BYTES);
         tma_load_2d(raw_base + s * TM_RAW_STAGE_BYTES, &tmap_w, x, y, &raw_full[s]);
       }
@@ -125,7 +127,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             waited_src = src;
           }
         }
-        if (c >= TM_OP_STAGES && !mbar_wait(&b_empty[s], ((c / TM_OP_STAGES) - 1) & 1, abort_flag, status, 111)) break;
+        if (c >= TM_OP_STAGES && !mbar_wait(&b_empty[s], ((c / TM_OP_STAGES) - 1) & 1, abort_flag, status, 111, NG <= 3 ? 500 : 0)) break;
         mbar_arrive_expect_tx(&b_full[s], (uint32_t)b_stage);
         tma_load_2d(b_base + s * b_stage, &tmap_x, x, y, &b_full[s]);
         tma_load_2d(b_base + s * b_stage + b_half, &tmap_x, x + 64, y, &b_full[s]);
@@ -140,7 +142,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % TM_OP_STAGES, sa = c % SA;
         if (!mbar_wait(&b_full[s], (c / TM_OP_STAGES) & 1, abort_flag, status, 120)) break;
-        if (!mbar_wait(&a_full[sa], (c / SA) & 1, abort_flag, status, 121)) break;
+        if (!mbar_wait(&a_full[sa], (c / SA) & 1, abort_flag, status, 121, NG <= 3 ? 250 : 0)) break;   // decode class: the decode warps set the pace
         tc_fence_after();
         const uint64_t bd = desc0 + (uint64_t)(s * stage_units);
         const uint32_t at = a_tmem0 + sa * TM_A_COLS;
@@ -152,8 +154,8 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       }
       tc_commit(acc_full);
     }
-  } else if (warp >= 4) {
-    const int dw = warp - 4;
+  } else if (warp >= TM_ROLE_WARPS) {
+    const int dw = warp - TM_ROLE_WARPS;
     const int grp = dw >> 2;
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const int n = q * 32 + lane;                  // output column of the strip owned by this thread
@@ -165,25 +167,28 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     bool ok = true;
     for (int c = grp; c < nchunks && ok; c += NG) {
       const int rs = c % TM_RAW_STAGES, os = c % SA;
-      ok = mbar_wait(&raw_full[rs], (c / TM_RAW_STAGES) & 1, abort_flag, status, 130);
+      ok = mbar_wait(&raw_full[rs], (c / TM_RAW_STAGES) & 1, abort_flag, status, 130, 200);
       if (!ok) break;
-      const uint4* raw4 = reinterpret_cast<const uint4*>(raw_base + rs * TM_RAW_STAGE_BYTES) + tile_off;
-      uint4 cur[8];
-#pragma unroll
-      for (int kt = 0; kt < 8; ++kt) cur[kt] = raw4[kt * 64];
-      uint32_t prev[8];
-#pragma unroll
-      for (int kt = 0; kt < 8; ++kt) prev[kt] = __shfl_sync(0xffffffffu, cur[kt].w, prev_lane);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+      const uint32_t raw4 = smem_u32(raw_base + rs * TM_RAW_STAGE_BYTES) + (uint32_t)tile_off * 16u;
       bool waited = false;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t regs[32];
+      for (int qt = 0; qt < 4; ++qt) {
+        // two k-tiles at a time: the thread's eighth of each (4 words) and, from the lane before it, the word those follow.
+        // Small steps keep the live registers low (more resident decode warps) and the unrolled body short.
+        uint4 cur[2];
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const int kt = half * 4 + kk;
-          const uint32_t w[5] = {prev[kt], cur[kt].x, cur[kt].y, cur[kt].z, cur[kt].w};
+        for (int kk = 0; kk < 2; ++kk) cur[kk] = lds128(raw4 + (uint32_t)((qt * 2 + kk) * 1024));
+        uint32_t prev[2];
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) prev[kk] = __shfl_sync(0xffffffffu, cur[kk].w, prev_lane);
+        if (qt == 3) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[rs]);   // the stage's last read has landed in registers
+        }
+        uint32_t regs[16];
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint32_t w[5] = {prev[kk], cur[kk].x, cur[kk].y, cur[kk].z, cur[kk].w};
 #pragma unroll
           for (int m = 0; m < 4; ++m) {
             const uint32_t X = __funnelshift_lc(w[m + 1], w[m], sh);
@@ -194,12 +199,12 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           }
         }
         if (!waited) {
-          if (c >= SA) ok = mbar_wait(&a_empty[os], ((c / SA) - 1) & 1, abort_flag, status, 131);
+          if (c >= SA) ok = mbar_wait(&a_empty[os], ((c / SA) - 1) & 1, abort_flag, status, 131, NG == 4 ? 64 : 0);   // prefill class: the tensor core sets the pace
           waited = true;
           if (!ok) break;
           tc_fence_after();
         }
-        tc_st_32x32b_x32(st_addr + os * TM_A_COLS + half * 32, regs);
+        tc_st_32x32b_x16(st_addr + os * TM_A_COLS + qt * 16, regs);
       }
       if (!ok) break;
       tc_wait_st();
@@ -208,7 +213,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (lane == 0) mbar_arrive(&a_full[os]);
     }
     if (dw < 4) {
-      const bool done = mbar_wait(acc_full, 0, abort_flag, status, 140);
+      const bool done = mbar_wait(acc_full, 0, abort_flag, status, 140, 100);
       tc_fence_after();
       if (done && *abort_flag == 0) {
         float* out;
@@ -260,7 +265,7 @@ template <int CB, int NG>
 static int launch_tm(const CUtensorMap& tm, const CUtensorMap& tw, float* part, int rows, int K, int N, int splits, int brows, int row_tiles,
                      int* status, cudaStream_t st, const GemmTp& tp) {
   int smem = tm_smem_bytes(brows, NG) + 1024;
-  if (NG == 2 && smem < 80 * 1024) smem = 80 * 1024;   // at most two CTAs per SM: each allocates 256 TMEM columns
+  if (NG <= 3 && smem < 80 * 1024) smem = 80 * 1024;   // at most two CTAs per SM: each allocates 256 TMEM columns
   if (smem > 232448) return (int)cudaErrorInvalidValue;
   auto kern = exl3_gemm_tm_kernel<CB, NG>;
   static bool configured = false;
@@ -270,7 +275,7 @@ static int launch_tm(const CUtensorMap& tm, const CUtensorMap& tw, float* part, 
     configured = true;
   }
   dim3 grid(N / TM_STRIP, splits, row_tiles);
-  rx::launch(kern, dim3(grid), dim3(128 + NG * 128), smem, st, tm, tw, part, rows, K, N, splits, brows, status, tp);
+  rx::launch(kern, dim3(grid), dim3(TM_ROLE_WARPS * 32 + NG * 128), smem, st, tm, tw, part, rows, K, N, splits, brows, status, tp);
   return (int)cudaGetLastError();
 }
 
@@ -294,9 +299,9 @@ static int gemm_b4(const void* xr, int rows, int K, const void* trellis, int N, 
   if (e != 0) return e;
   cudaStream_t st = (cudaStream_t)stream;
   float* p = (float*)part;
-  const bool big = brows > 64;   // one CTA per SM with 16 decode warps, else two CTAs per SM with 8 each
+  const bool big = brows > 64;   // one CTA per SM with 16 decode warps, else two CTAs per SM with 12 each
 #define RX_TM(CBV) (big ? launch_tm<CBV, 4>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st, tp) \
-                        : launch_tm<CBV, 2>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st, tp))
+                        : launch_tm<CBV, 3>(tm, tw, p, rows, K, N, splits, brows, row_tiles, status, st, tp))
   switch (codebook) {
     case CB_3INST: return RX_TM(CB_3INST);
     case CB_MCG: return RX_TM(CB_MCG);
