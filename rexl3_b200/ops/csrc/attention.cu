@@ -11,7 +11,8 @@
 // order, so a row's bits never depend on the batch (same idea as the reference's 512-key chunks,
 // crates/cuda/csrc/attention.cu:16-21; geometry, page size, KV layout and schedule are new).  The 4 warps of a CTA
 // each take 16 keys of every page and are merged in warp order.
-// Prefill: one CTA per (64 query rows, q head, sequence); warps own 16 query rows each and walk the pages causally.
+// Prefill (this file: FP8 caches and 64-wide heads): one CTA per (64 query rows, q head, sequence); warps own 16 query rows each and
+// walk the pages causally.  bf16 caches with 128-wide heads run the tcgen05 / tensor-memory kernel of attention_tc.cu instead.
 #include <cuda.h>
 #include <cuda_fp8.h>
 #include "common.cuh"
@@ -184,94 +185,6 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
   }
 }
 
-
-// Two 16-row tiles per warp (32 query rows) against NK keys: every K and V fragment that is loaded from shared memory feeds two MMAs, which
-// halves the shared-memory traffic per FLOP (the prefill kernel's bound).  State per tile t: m[t], l[t], o[t].
-template <int HD, int NK, bool F16 = false>
-__device__ __forceinline__ void attn_step2(const uint32_t (&qa)[2][HD / 16][4], uint32_t ksm, uint32_t vsm, int key0, const int (&valid)[2][2],
-                                           float scale_log2, float (&m)[2][2], float (&l)[2][2], float (&o)[2][HD / 8][4]) {
-  const int lane = threadIdx.x & 31;
-  constexpr int NT = NK / 8;
-  float s[2][NT][4];
-#pragma unroll
-  for (int t = 0; t < 2; ++t)
-#pragma unroll
-    for (int j = 0; j < NT; ++j) { s[t][j][0] = s[t][j][1] = s[t][j][2] = s[t][j][3] = 0.f; }
-#pragma unroll
-  for (int ks = 0; ks < HD / 16; ++ks) {
-#pragma unroll
-    for (int jp = 0; jp < NT / 2; ++jp) {
-      uint32_t b0, b1, b2, b3;
-      const int mi = lane >> 3;
-      const int key = key0 + jp * 16 + (mi >> 1) * 8 + (lane & 7);
-      ldsm_x4(kv_chunk_addr<HD>(ksm, key, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if constexpr (F16) { mma_f16(s[t][2 * jp], qa[t][ks], b0, b1); mma_f16(s[t][2 * jp + 1], qa[t][ks], b2, b3); }
-        else { mma_bf16(s[t][2 * jp], qa[t][ks], b0, b1); mma_bf16(s[t][2 * jp + 1], qa[t][ks], b2, b3); }
-      }
-    }
-  }
-  uint32_t pa[2][NT / 2][4];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int kk = j * 8 + 2 * (lane & 3) + (e & 1);
-        const int lim = valid[t][e >> 1];
-        const float v = (kk < lim) ? s[t][j][e] * scale_log2 : -INFINITY;
-        s[t][j][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-      }
-    }
-    float corr[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float mn = fmaxf(m[t][r], mx[r]);
-      corr[r] = (mn == -INFINITY) ? 1.f : exp2f(m[t][r] - mn);
-      m[t][r] = mn;
-    }
-    float rs[2] = {0.f, 0.f};
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      float p[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float mm = m[t][e >> 1];
-        p[e] = (mm == -INFINITY) ? 0.f : exp2f(s[t][j][e] - mm);
-        rs[e >> 1] += p[e];
-      }
-      pa[t][j >> 1][(j & 1) * 2 + 0] = F16 ? pack_f16(p[0], p[1]) : pack_bf16(p[0], p[1]);
-      pa[t][j >> 1][(j & 1) * 2 + 1] = F16 ? pack_f16(p[2], p[3]) : pack_bf16(p[2], p[3]);
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) l[t][r] = l[t][r] * corr[r] + rs[r];
-#pragma unroll
-    for (int d = 0; d < HD / 8; ++d) {
-      o[t][d][0] *= corr[0]; o[t][d][1] *= corr[0]; o[t][d][2] *= corr[1]; o[t][d][3] *= corr[1];
-    }
-  }
-#pragma unroll
-  for (int kp = 0; kp < NT / 2; ++kp) {
-#pragma unroll
-    for (int dp = 0; dp < HD / 16; ++dp) {
-      uint32_t b0, b1, b2, b3;
-      const int mi = lane >> 3;
-      const int key = key0 + kp * 16 + (mi & 1) * 8 + (lane & 7);
-      ldsm_x4_t(kv_chunk_addr<HD>(vsm, key, dp * 2 + (mi >> 1)), b0, b1, b2, b3);
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if constexpr (F16) { mma_f16(o[t][2 * dp], pa[t][kp], b0, b1); mma_f16(o[t][2 * dp + 1], pa[t][kp], b2, b3); }
-        else { mma_bf16(o[t][2 * dp], pa[t][kp], b0, b1); mma_bf16(o[t][2 * dp + 1], pa[t][kp], b2, b3); }
-      }
-    }
-  }
-}
 
 // ------------------------------------------------------------------------------------------------ decode (split-KV)
 // part_o  : f32 [rows][n_q][max_chunks][HD]   unnormalised partial outputs
@@ -588,137 +501,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
 }
 
 
-// ------------------------------------------------------------------------------------------------ prefill, 128 query rows per CTA
-// One CTA per (128 query rows, q head, sequence): each of the 4 warps owns 32 query rows (two MMA row tiles), so every K / V fragment
-// read from shared memory feeds two MMAs.  Q lives in shared memory (two 64-row tiles in the K tile's swizzled layout) and its fragments
-// are re-read per k-step; K / V pages come through a 2-stage TMA ring; 32 keys per softmax step keep the accumulators in registers.
-constexpr int PF2_STAGES = 2;
-
-template <int HD, bool FP8>
-__global__ void __launch_bounds__(ATT_THREADS, 2)
-attn_prefill2_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
-                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_ids, const int* __restrict__ q_start,
-                     const int* __restrict__ q_len, const int* __restrict__ pos0, uint16_t* __restrict__ out, int n_q, int n_kv, float scale_log2_in,
-                     int* status, const float* __restrict__ kv_scale) {
-  pdl_launch();
-  pdl_wait();
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int T16 = PAGE * HD * 2;
-  constexpr int TILE = FP8 ? PAGE * HD : T16;
-  uint8_t* qs = smem + 2 * PF2_STAGES * TILE;                     // two 64-row Q tiles (bf16, or f16 for an FP8 cache)
-  uint8_t* conv = qs + 2 * T16;                                  // FP8: expanded K and V of the current page
-  uint64_t* bars = (uint64_t*)(conv + (FP8 ? 2 * T16 : 0));
-  volatile int* abort_flag = (volatile int*)(bars + PF2_STAGES);
-  const int s_idx = blockIdx.z, hq = blockIdx.y;
-  const int qlen = q_len[s_idx];
-  const int ntiles = (qlen + 127) / 128;
-  const int qt = ntiles - 1 - (int)blockIdx.x;                   // heaviest (latest) query tiles first
-  if (qt < 0) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int G = n_q / n_kv, kvh = hq / G;
-  const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;
-  const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
-  const int p0 = pos0[s_idx], r_base = q_start[s_idx];
-  const int* bt = block_table + (size_t)seq_ids[s_idx] * max_blocks;
-  const int q_lo = qt * 128;
-  const int last_q = min(qlen, q_lo + 128) - 1;
-  const int npages = (p0 + last_q) / PAGE + 1;
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < PF2_STAGES; ++i) mbar_init(&bars[i], 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-  }
-  // Q rows of this CTA -> shared memory (rows past the sequence end are zero)
-  for (int c = threadIdx.x; c < 128 * (HD / 8); c += ATT_THREADS) {
-    const int row = c / (HD / 8), ch = c % (HD / 8);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (q_lo + row < qlen) v = *reinterpret_cast<const uint4*>(q + ((size_t)(r_base + q_lo + row) * n_q + hq) * HD + ch * 8);
-    if constexpr (FP8) { v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y); v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w); }
-    const uint32_t a = kv_chunk_addr<HD>(smem_u32(qs + (row >> 6) * T16), row & 63, ch);
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-  }
-  __syncthreads();
-  auto load = [&](int p) {
-    const int st = p % PF2_STAGES;
-    if constexpr (FP8) load_kv_page8<HD>(smem + st * TILE, smem + (PF2_STAGES + st) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[st]);
-    else load_kv_page<HD>(smem + st * TILE, smem + (PF2_STAGES + st) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[st]);
-  };
-  if (threadIdx.x == 0) {
-    load(0);
-    if (npages > 1) load(1);
-  }
-  // Q fragments of this warp's two row tiles, straight from shared memory (kept in registers: 2 x HD/16 x 4)
-  uint32_t qa[2][HD / 16][4];
-  const int wrow = warp * 32;                                    // this warp's first row inside the CTA's 128
-#pragma unroll
-  for (int t = 0; t < 2; ++t)
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-      const int row = wrow + t * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      ldsm_x4(kv_chunk_addr<HD>(smem_u32(qs + (row >> 6) * T16), row & 63, ks * 2 + (lane >> 4)), qa[t][ks][0], qa[t][ks][1], qa[t][ks][2], qa[t][ks][3]);
-    }
-  float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  float o[2][HD / 8][4];
-#pragma unroll
-  for (int t = 0; t < 2; ++t)
-#pragma unroll
-    for (int d = 0; d < HD / 8; ++d) { o[t][d][0] = o[t][d][1] = o[t][d][2] = o[t][d][3] = 0.f; }
-  // local query rows of this lane: tile t, rows (lane >> 2) and (lane >> 2) + 8
-  int lr[2][2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) { lr[t][0] = q_lo + wrow + t * 16 + (lane >> 2); lr[t][1] = lr[t][0] + 8; }
-  const int warp_last_key = p0 + min(qlen - 1, q_lo + wrow + 31);
-
-  bool ok = true;
-  for (int p = 0; p < npages; ++p) {
-    const int st = p % PF2_STAGES;
-    ok = mbar_wait(&bars[st], (p / PF2_STAGES) & 1, abort_flag, status, 61);
-    if (!ok) break;
-    const int kbase = p * PAGE;
-    const bool mine = kbase <= warp_last_key && q_lo + wrow < qlen;
-    uint32_t ksm, vsm;
-    if constexpr (FP8) {
-      expand_page8<HD>(smem + st * TILE, conv);
-      expand_page8<HD>(smem + (PF2_STAGES + st) * TILE, conv + T16);
-      __syncthreads();
-      ksm = smem_u32(conv); vsm = smem_u32(conv + T16);
-    } else {
-      ksm = smem_u32(smem + st * TILE); vsm = smem_u32(smem + (PF2_STAGES + st) * TILE);
-    }
-    if (mine) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        int valid[2][2];
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-          for (int r = 0; r < 2; ++r) valid[t][r] = lr[t][r] < qlen ? (p0 + lr[t][r] + 1 - kbase - half * 32) : 0;
-        if (kbase + half * 32 <= warp_last_key) attn_step2<HD, 32, FP8>(qa, ksm, vsm, half * 32, valid, scale_log2, m, l, o);
-      }
-    }
-    __syncthreads();                                             // the stage (and the expanded tiles) are free again
-    if (threadIdx.x == 0 && p + PF2_STAGES < npages) load(p + PF2_STAGES);
-  }
-  if (!ok || *abort_flag != 0) return;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l[t][r] += __shfl_xor_sync(0xffffffffu, l[t][r], 1);
-      l[t][r] += __shfl_xor_sync(0xffffffffu, l[t][r], 2);
-    }
-    const float i0 = l[t][0] > 0.f ? v_scale / l[t][0] : 0.f, i1 = l[t][1] > 0.f ? v_scale / l[t][1] : 0.f;
-#pragma unroll
-    for (int d = 0; d < HD / 8; ++d) {
-      const int c = d * 8 + 2 * (lane & 3);
-      if (lr[t][0] < qlen) *reinterpret_cast<uint32_t*>(out + ((size_t)(r_base + lr[t][0]) * n_q + hq) * HD + c) = pack_bf16(o[t][d][0] * i0, o[t][d][1] * i0);
-      if (lr[t][1] < qlen) *reinterpret_cast<uint32_t*>(out + ((size_t)(r_base + lr[t][1]) * n_q + hq) * HD + c) = pack_bf16(o[t][d][2] * i1, o[t][d][3] * i1);
-    }
-  }
-}
-
 // ------------------------------------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -824,24 +606,6 @@ template <int HD, bool FP8>
 static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* seq_ids,
                           const int* q_start, const int* q_len, const int* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, float scale,
                           int* status, cudaStream_t st, const float* kv_scale) {
-  // The 128-row form halves the shared-memory traffic per FLOP, but as written it needs 255 registers with ~150 bytes of spills and a
-  // 2-stage ring, and measured 3 % slower end to end than the 64-row kernel on an 8192-token prefill (21.8 vs 20.7 ms for two layers), so
-  // it is opt-in (RX_PREFILL_128ROWS=1) until its register budget is fixed.
-  static const bool use_v2 = getenv("RX_PREFILL_128ROWS") != nullptr;
-  if (HD == 128 && use_v2) {
-    constexpr int T16 = PAGE * HD * 2;
-    const int smem2 = 2 * PF2_STAGES * (FP8 ? PAGE * HD : T16) + 2 * T16 + (FP8 ? 2 * T16 : 0) + 64 + 1024;
-    static bool configured2 = false;
-    if (!configured2) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill2_kernel<HD, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
-      if (e != cudaSuccess) return (int)e;
-      configured2 = true;
-    }
-    dim3 grid2((max_qlen + 127) / 128, n_q, nseq);
-    rx::launch(attn_prefill2_kernel<HD, FP8>, dim3(grid2), dim3(ATT_THREADS), smem2, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len,
-               pos0, (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status, kv_scale);
-    return (int)cudaGetLastError();
-  }
   const int smem = att_smem_bytes(HD, FP8);
   static bool configured = false;
   if (!configured) {
@@ -855,10 +619,18 @@ static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const vo
   return (int)cudaGetLastError();
 }
 
+extern "C" int rx_attn_prefill_tc(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
+                                  const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
+                                  float scale, int* status, void* stream, int reserved);
+
 RX_API int rx_attn_prefill(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
                            const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
                            float scale, int* status, void* stream, const void* kv_scale) {
   if (n_q % n_kv != 0 || nseq <= 0 || max_qlen <= 0) return (int)cudaErrorInvalidValue;
+  // bf16 caches with 128-wide heads: the tcgen05 / tensor-memory kernel (attention_tc.cu); FP8 caches and 64-wide heads: mma.sync below
+  if (hd == 128 && kv_scale == nullptr)
+    return rx_attn_prefill_tc(tmap_k, tmap_v, q, block_table, max_blocks, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,
+                              status, stream, 0);
   cudaStream_t st = (cudaStream_t)stream;
 #define RX_PF(HDV, F8) launch_prefill<HDV, F8>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
     (const int*)seq_ids, (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st, (const float*)kv_scale)

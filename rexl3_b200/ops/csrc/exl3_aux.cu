@@ -279,17 +279,21 @@ RX_API int rx_embed(const void* ids, const void* table, void* h, int rows, int d
 
 RX_API int rx_norm_rot_in(const void* x_bf16, const void* norm_w_bf16, float eps, const void* suh, void* xr, int rows, int K, void* stream) {
   if (K % 128 || K / 128 > 512) return (int)cudaErrorInvalidValue;
-  rx::launch(norm_rot_in_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, (const uint16_t*)x_bf16, (const uint16_t*)norm_w_bf16, eps, (const __half*)suh,
+  rx::launch(norm_rot_in_kernel, dim3(rows), dim3(rows >= 512 ? 256 : 1024), 0, (cudaStream_t)stream, (const uint16_t*)x_bf16, (const uint16_t*)norm_w_bf16, eps, (const __half*)suh,
                                                             (__half*)xr, K);
   return (int)cudaGetLastError();
 }
 
 static int blocks_y(int rows, int nblocks128) {
   // one warp per 128-block (8 warps per CTA): the kernels without a row-wide reduction get their memory-level parallelism
-  // from many resident warps with one or two loads each, for one row as for thousands
-  (void)rows;
-  const int per_row = (nblocks128 + 7) / 8;
-  return per_row < 1 ? 1 : per_row;
+  // from many resident warps with one or two loads each.  For a few rows that means one CTA per 8 blocks; for a prefill
+  // chunk of thousands of rows the CTAs take several blocks each instead (a grid of 10^5 very short CTAs is bound by the
+  // rate at which CTAs can be launched, not by memory).
+  int per_row = (nblocks128 + 7) / 8;
+  if (per_row < 1) per_row = 1;
+  int cap = 16384 / (rows < 1 ? 1 : rows);
+  if (cap < 1) cap = 1;
+  return per_row < cap ? per_row : cap;
 }
 
 RX_API int rx_finish_store(const void* part, int S, int M, int N, const void* svh, const void* bias, void* out, int f32_out, void* stream) {
@@ -308,7 +312,9 @@ RX_API int rx_finish_add_norm_rot(const void* part, int S, int M, int N, const v
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  rx::launch(finish_add_norm_rot_kernel, dim3(M), dim3(1024), (size_t)N * 4, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh, (const float*)bias,
+  // a window of a few rows wants every row finished fast (1024 threads per row); a prefill chunk wants many rows in flight per SM
+  const int threads = M >= 512 ? 256 : 1024;
+  rx::launch(finish_add_norm_rot_kernel, dim3(M), dim3(threads), (size_t)N * 4, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh, (const float*)bias,
                                                                      (uint16_t*)h_bf16, (const uint16_t*)norm_w, eps, (const __half*)suh_next,
                                                                      (__half*)xr, (uint16_t*)xn_out);
   return (int)cudaGetLastError();

@@ -225,6 +225,17 @@ def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_st
     _lib.count()
 
 
+def attn_prefill_tc(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,
+                    status, v_desc_variant: int = 0) -> None:
+    """The tcgen05 / TMEM prefill attention (bf16 caches, head_dim 128)."""
+    assert not tk.fp8 and hd == 128
+    L = _lib.load()
+    _lib.check(L.rx_attn_prefill_tc(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], seq_ids.data_ptr(), q_start.data_ptr(),
+                                    q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
+                                    _lib.stream_ptr(), v_desc_variant), "rx_attn_prefill_tc")
+    _lib.count()
+
+
 # ------------------------------------------------------------------------------------------------ device-side verify / accept
 SEQ_SAMPLING = np.dtype([("seed", "<u8"), ("temperature", "<f8"), ("top_p", "<f8"), ("min_p", "<f8"), ("top_k", "<i4"), ("first_row", "<i4"),
                          ("n_rows", "<i4"), ("position", "<i4")], align=True)

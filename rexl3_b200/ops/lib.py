@@ -99,6 +99,8 @@ def _declare(lib):
         "rx_attn_decode_scratch_floats": (c_ll, [c_int, c_int, c_int, c_int]),
         "rx_attn_decode": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
                                    c_void, c_void, c_void, c_void, c_void, c_void]),
+        "rx_attn_prefill_tc": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                                       c_int, c_f, c_void, c_void, c_int]),
         "rx_attn_prefill": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                     c_int, c_f, c_void, c_void, c_void]),
     }
