@@ -127,6 +127,7 @@ def main():
             tprt.shutdown(ctx, group)
             return 0
         backend = DenseTpBackend(shard, B + 1, ctx.ctrl)
+        nvls = bool(getattr(group, "mm_mc_base", 0))
     else:
         model = dense.DenseGPU(cfg, num_pages=pages, max_rows=256, max_seqs=B + 1, max_blocks_per_seq=blocks_per_seq, max_prefill_rows=P, seed=rank)
         backend = DenseGpuBackend(model, max_slots=B + 1)
@@ -236,7 +237,7 @@ def main():
                                 f"EXL3 {cfg.bits} bpw random-init, paged bf16 KV (64-token pages)",
                        "global_batch": B, "seq_len": P, "decode_tokens_timed": K,
                        "parallelism": f"tp{world}" + ("" if world == 1 else (" (GEMM epilogue reduce-scatter and all-gather-fed GEMM for prefill, one-shot all-reduce for decode windows, "
-                                                                              "all over NVLink peer memory, no NCCL on the step)" if args.collective == "fused" else
+                                                                              "all over NVLink peer memory" + (", 64-row windows summed in the switch (multimem.ld_reduce)" if nvls else "") + ", no NCCL on the step)" if args.collective == "fused" else
                                                                               " (COMPARISON RUN: NCCL all-reduce in decode windows)")),
                        "l2": "inputs larger than L2 every step (11 GB of weights + the batch's KV are streamed)"},
             "decode_tok_s_bs1": round(tok_s_bs1, 2), "ms_per_step_bs1": round(bs1_ms / K, 4),

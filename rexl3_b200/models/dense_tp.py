@@ -265,9 +265,11 @@ class DenseTPShard:
                 _lib.count()
 
             def p_sum():
-                _lib.check(Lib.rx_tp_allsum_add_norm_rot(g.ar_ptr(r, parity), g.ar_flag_ptr(r, parity), R, AR_ROWS, g.epoch_ptr(r), use, M, d, h.data_ptr(),
-                                                         norm_w.data_ptr(), cfg.eps, suh_next.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(),
-                                                         _lib.stream_ptr(), None), "rx_tp_allsum_add_norm_rot")
+                # with an NVLS buffer bound (g.mm_mc): windows above the packet size read the sum over ranks from the switch
+                _lib.check(Lib.rx_tp_allsum_add_norm_rot_mm(g.ar_ptr(r, parity), g.ar_flag_ptr(r, parity), R, AR_ROWS, g.epoch_ptr(r), use, M, d,
+                                                            h.data_ptr(), norm_w.data_ptr(), cfg.eps, suh_next.data_ptr(), xr_d.data_ptr(),
+                                                            self.status.data_ptr(), _lib.stream_ptr(), None, g.mm_mc(parity) or None),
+                           "rx_tp_allsum_add_norm_rot_mm")
                 _lib.count()
             return p_push, p_sum
 

@@ -188,7 +188,21 @@ struct BcastTp {
   const unsigned* epoch;
   unsigned use_index;
   int rows_cap;
+  // NVLS form (windows above the packet size): when set, the f32 rows go ONLY to this rank's own copy of a buffer that is bound to an
+  // NVLink multicast object ([rows_cap][N], no source dimension); the consumers read the sum over ranks with multimem.ld_reduce, so
+  // the R - 1 peer copies of every row never cross NVLink.  The flags still travel as plain peer stores.
+  float* mm_local;
 };
+
+// 16 bytes of the element-wise f32 sum, over all GPUs of the multicast object, of the values at this offset (reduced in the switch)
+__device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
 
 __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
                                     const float* __restrict__ bias, const __grid_constant__ BcastTp tp) {
@@ -230,6 +244,8 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
         ll_store(d, y[0], y[1], ticket);
         ll_store(d + 1, y[2], y[3], ticket);
       }
+    } else if (tp.mm_local != nullptr) {
+      *reinterpret_cast<float4*>(tp.mm_local + (size_t)row * N + n0) = make_float4(y[0], y[1], y[2], y[3]);
     } else {
       const float4 o = make_float4(y[0], y[1], y[2], y[3]);
       const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * N + n0;
@@ -247,7 +263,7 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
                                                                    int rows_cap, const unsigned* epoch, unsigned use_index, int M, int N,
                                                                    uint16_t* __restrict__ h, const uint16_t* __restrict__ norm_w, float eps,
                                                                    const __half* __restrict__ suh_next, __half* __restrict__ xr, int* status,
-                                                                   uint16_t* __restrict__ xn_out) {
+                                                                   uint16_t* __restrict__ xn_out, const float* __restrict__ mc) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float rowbuf[];
@@ -268,12 +284,14 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
     if (!ok_sh) return;
   }
   const size_t plane = (size_t)rows_cap * N;
+  const bool nvls = mc != nullptr && flags != nullptr && !ll;      // every rank wrote its rows to its own copy; the switch adds them
   for (int b = warp; b < N / 128; b += nw) {
     const int n0 = b * 128 + lane * 4;
     float4 p[TP_MAX];
+    if (nvls) p[0] = multimem_sum_f32x4(mc + (size_t)row * N + n0);
 #pragma unroll
     for (int r = 0; r < TP_MAX; ++r)
-      if (r < ranks) {
+      if (r < ranks && !nvls) {
         if (ll) {
           // both packets of a rank are requested together; ranks one after another (holding all ranks' packets at once costs more
           // registers than a 1024-thread CTA has, and the spills cost more than the overlap gains - measured)
@@ -289,7 +307,7 @@ __global__ void __launch_bounds__(1024) allsum_add_norm_rot_kernel(const float* 
     float4 acc = p[0];
 #pragma unroll
     for (int r = 1; r < TP_MAX; ++r)
-      if (r < ranks) { acc.x += p[r].x; acc.y += p[r].y; acc.z += p[r].z; acc.w += p[r].w; }
+      if (r < ranks && !nvls) { acc.x += p[r].x; acc.y += p[r].y; acc.z += p[r].z; acc.w += p[r].w; }
     const float y[4] = {acc.x, acc.y, acc.z, acc.w};
     uint16_t* hp = h + (size_t)row * N + n0;
     const uint2 hu = *reinterpret_cast<const uint2*>(hp);
@@ -478,8 +496,8 @@ RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void*
                          (const float*)bias, tp);
 }
 
-RX_API int rx_tp_allsum_add_norm_rot(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,
-                                     void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream, void* xn_out) {
+static int allsum_launch(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,
+                         void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream, void* xn_out, const void* mc) {
   if (N % 128 || N / 128 > 512 || M < 1 || M > rows_cap || ranks < 1 || ranks > TP_MAX) return (int)cudaErrorInvalidValue;
   int threads = 32 * (N / 128);
   if (threads > 1024) threads = 1024;
@@ -492,7 +510,20 @@ RX_API int rx_tp_allsum_add_norm_rot(const void* ar, const void* flags, int rank
   }
   return (int)rx::launch(allsum_add_norm_rot_kernel, dim3(M), dim3(threads), smem, (cudaStream_t)stream, (const float*)ar, (const unsigned*)flags, ranks,
                          rows_cap, (const unsigned*)epoch, use_index, M, N, (uint16_t*)h, (const uint16_t*)norm_w, eps, (const __half*)suh_next,
-                         (__half*)xr, status, (uint16_t*)xn_out);
+                         (__half*)xr, status, (uint16_t*)xn_out, (const float*)mc);
+}
+
+RX_API int rx_tp_allsum_add_norm_rot(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,
+                                     void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream, void* xn_out) {
+  return allsum_launch(ar, flags, ranks, rows_cap, epoch, use_index, M, N, h, norm_w, eps, suh_next, xr, status, stream, xn_out, nullptr);
+}
+
+// The same with `mc`: the NVLink-multicast address of the buffer every rank's finish kernel wrote its rows to (BcastTp::mm_local is that
+// rank's own address of it).  Windows above the packet size then take the sum from multimem.ld_reduce instead of R local slots.
+RX_API int rx_tp_allsum_add_norm_rot_mm(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,
+                                        void* h, const void* norm_w, float eps, const void* suh_next, void* xr, int* status, void* stream, void* xn_out,
+                                        const void* mc) {
+  return allsum_launch(ar, flags, ranks, rows_cap, epoch, use_index, M, N, h, norm_w, eps, suh_next, xr, status, stream, xn_out, mc);
 }
 
 RX_API int rx_tp_cand_desc_size() { return (int)sizeof(CandTp); }

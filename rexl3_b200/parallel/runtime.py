@@ -43,6 +43,8 @@ def build_dense_tp(ctx: TpContext, cfg, *, num_pages: int, max_rows: int, max_sl
     from .symm import IpcGroup
     layout = DenseTPShard.layout(cfg, ctx.world, max_rows)
     group = IpcGroup(layout, ctx.rank, ctx.device, group=ctx.ctrl)
+    if collective == "fused":
+        group.enable_nvls()       # in-switch reduction for windows above the packet size, where the fabric and the settings allow it
     w = shard_weights(weights, ctx.rank, ctx.world) if weights is not None else None
     shard = DenseTPShard(cfg, group, ctx.rank, num_pages, max_rows, max_slots, max_blocks_per_seq, weights=w, device=ctx.device, seed=seed, kv_dtype=kv_dtype,
                          collective=collective)

@@ -78,15 +78,20 @@ def main() -> int:
         print(f"selftest model does not split over {ctx.world} ranks", file=sys.stderr)
         return 2
     w = dense.random_weights(cfg, seed=11)
-    slots, max_blocks = 4, 6
-    shard, group = runtime.build_dense_tp(ctx, cfg, num_pages=32, max_rows=256, max_slots=slots, max_blocks_per_seq=max_blocks, weights=w)
+    # --streams N: N concurrent sequences, so the decode windows have N rows (above 16 rows they leave the packet format for f32 rows
+    # with flags, or for the in-switch reduction where an NVLS buffer is bound)
+    streams = int(sys.argv[sys.argv.index("--streams") + 1]) if "--streams" in sys.argv else 3
+    slots, max_blocks = max(4, streams), 6
+    shard, group = runtime.build_dense_tp(ctx, cfg, num_pages=8 * slots, max_rows=256, max_slots=slots, max_blocks_per_seq=max_blocks, weights=w)
+    if ctx.rank == 0:
+        print(f"tp selftest: {streams} streams, NVLS buffer {'bound' if group.mm_mc_base else 'not bound'}", flush=True)
     rc = 0
     if ctx.rank != 0:
         follow(shard, slots, ctx.ctrl)
     else:
         be = DenseTpBackend(shard, slots, ctx.ctrl)
         try:
-            rc = _lead(be, cfg, w, ctx)
+            rc = _lead(be, cfg, w, ctx, streams)
         finally:
             be.stop()
     runtime.shutdown(ctx, group)
@@ -95,14 +100,14 @@ def main() -> int:
     return rc
 
 
-def _lead(be, cfg, w, ctx) -> int:
+def _lead(be, cfg, w, ctx, streams: int = 3) -> int:
     from ..engine import Engine, Request
     from ..models import dense
     from ..sampling import GREEDY
     rc = 0
     eng = Engine(be, None, window_rows=64, prefill_chunk=256, spec="none")
     rng = np.random.default_rng(3)
-    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (70, 33, 129)]
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in ([70, 33, 129] + [20 + 7 * i for i in range(max(0, streams - 3))])[:max(1, streams)]]
     new = 12
     for i, p in enumerate(prompts):
         eng.submit(Request(f"r{i}", p, new, GREEDY))

@@ -49,7 +49,8 @@ class CandTp(ctypes.Structure):
 
 class BcastTp(ctypes.Structure):
     _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("dst", ctypes.c_void_p * TP_MAX), ("dst_flag", ctypes.c_void_p * TP_MAX),
-                ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
+                ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int),
+                ("mm_local", ctypes.c_void_p)]
 
 
 AR_ROWS = 256        # rows of a decode / verify window (the one-shot all-reduce path)
@@ -106,6 +107,14 @@ class ArenaLayout:
 class _GroupBase:
     ranks: int
     layout: ArenaLayout
+    mm_local_base = 0      # this rank's address of the NVLink-multicast all-reduce buffer ([2 parities][AR_ROWS][d] f32), 0 = none
+    mm_mc_base = 0         # the multicast address of the same buffer
+
+    def mm_local(self, parity: int) -> int:
+        return self.mm_local_base + 4 * parity * AR_ROWS * self.layout.d if self.mm_local_base else 0
+
+    def mm_mc(self, parity: int) -> int:
+        return self.mm_mc_base + 4 * parity * AR_ROWS * self.layout.d if self.mm_mc_base else 0
 
     def base(self, viewer: int, owner: int) -> int:
         """Device address of `owner`'s arena as seen from rank `viewer`."""
@@ -181,6 +190,7 @@ class _GroupBase:
         me = self.base(rank, rank)
         t.local_count = me + L.count + 4 * (6 + parity)
         t.epoch, t.use_index = me + L.epoch, use_index
+        t.mm_local = self.mm_local(parity) or None
         return t
 
     def ar_ptr(self, rank: int, parity: int) -> int:
@@ -238,6 +248,7 @@ class IpcGroup(_GroupBase):
     def __init__(self, layout: ArenaLayout, rank: int, device, group=None):
         import torch.distributed as dist
         self.layout, self.ranks, self.rank = layout, layout.ranks, rank
+        self._ctrl = group
         L = _lib.load()
         with torch.cuda.device(device):
             p = ctypes.c_void_p()
@@ -260,6 +271,33 @@ class IpcGroup(_GroupBase):
             _lib.check(L.rx_ipc_open(buf, ctypes.byref(out)), "rx_ipc_open")
             self.bases.append(out.value)
         dist.barrier(group=group)
+        self._mm = None
+
+    def enable_nvls(self) -> bool:
+        """Binds a [2][AR_ROWS][d] f32 buffer to an NVLink multicast object (torch's symmetric-memory allocator does the driver work:
+        cuMemCreate, handle exchange over the process group's store, cuMulticastCreate / BindMem) so that decode windows above the packet
+        size can take their all-reduce from the switch (`multimem.ld_reduce`).  Collective: every rank calls it.  Returns False, and
+        changes nothing, where the fabric has no multicast or NVLS is switched off (NCCL_NVLS_ENABLE=0 or RX_TP_NVLS=0: the setting of
+        every failure test, since a rank that dies while bound to a multicast object can raise NVLink faults on its peers)."""
+        import os
+        import torch.distributed as dist
+        if self.ranks < 2 or os.environ.get("NCCL_NVLS_ENABLE", "1") == "0" or os.environ.get("RX_TP_NVLS", "1") == "0":
+            return False
+        try:
+            import torch.distributed._symmetric_memory as sm
+            t = sm.empty(2 * AR_ROWS * self.layout.d, dtype=torch.float32, device=self.arena.device)
+            hdl = sm.rendezvous(t, dist.group.WORLD)
+            mc = int(hdl.multicast_ptr or 0)
+        except Exception:        # no fabric support in this build / on this machine: keep the peer-store path
+            return False
+        ok = torch.tensor([1 if mc else 0], dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self._ctrl)      # all ranks or none
+        if int(ok[0]) == 0:
+            return False
+        t.zero_()
+        torch.cuda.synchronize()
+        self._mm, self.mm_local_base, self.mm_mc_base = (t, hdl), t.data_ptr(), mc
+        return True
 
     def base(self, viewer, owner):
         assert viewer == self.rank

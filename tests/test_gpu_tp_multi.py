@@ -33,3 +33,17 @@ def test_lost_rank_is_detected_without_a_hang():
            "-m", "rexl3_b200.parallel.selftest", "--leave-after", "12"]
     r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=240)
     assert "TP_FAILURE_DETECTED" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_tp_windows_above_the_packet_size_with_the_in_switch_sum():
+    """24 concurrent streams: the decode windows are wider than the packet format, so the ranks exchange f32 rows; where the fabric
+    offers NVLink multicast the sum comes from `multimem.ld_reduce` (the self test prints which form ran).  Every rank stays alive to
+    the end, so NVLS may be on here (the failure test above keeps it off)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29551",
+           "-m", "rexl3_b200.parallel.selftest", "--streams", "24"]
+    r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
+    assert r.returncode == 0 and "TP_SELFTEST_OK ranks=2" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
