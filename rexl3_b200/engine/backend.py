@@ -29,9 +29,13 @@ class RowOutput:
 
 
 class BackendError(Exception):
-    def __init__(self, message: str, fatal: bool = False):
+    """`group_lost`: the error means a rank of a multi-rank group stopped answering (a peer wait ran out or was aborted); the server
+    then reports the state `group_lost` (reference crates/model/src/lockstep.rs:29-38, StateLost)."""
+
+    def __init__(self, message: str, fatal: bool = False, group_lost: bool = False):
         super().__init__(message)
         self.fatal = fatal
+        self.group_lost = group_lost
 
 
 @dataclass

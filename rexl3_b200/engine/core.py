@@ -75,9 +75,9 @@ class _Seq:
 
 
 class StepError(Exception):
-    def __init__(self, kind: str, message: str, fatal: bool):
+    def __init__(self, kind: str, message: str, fatal: bool, group_lost: bool = False):
         super().__init__(f"{kind}: {message}")
-        self.kind, self.fatal = kind, fatal
+        self.kind, self.fatal, self.group_lost = kind, fatal, group_lost
 
 
 class Engine:
@@ -269,7 +269,7 @@ class Engine:
         except BackendError as e:
             self.counters["errors"] += 1
             if e.fatal:
-                raise StepError("Fatal", str(e), True)
+                raise StepError("Fatal", str(e), True, getattr(e, "group_lost", False))
             for rid in list(self.seqs):
                 self._finish(self.seqs[rid], "error", message=str(e))
             raise StepError("Backend", str(e), False)

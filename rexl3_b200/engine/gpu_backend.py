@@ -47,7 +47,7 @@ class DenseGpuBackend(Backend):
         self.d_pf = torch.zeros(4, self.max_slots, dtype=torch.int32, device=dev)
         self.h_cand_ids = torch.zeros(256, 64, dtype=torch.int32).pin_memory()
         self.h_cand_vals = torch.zeros(256, 64, dtype=torch.float32).pin_memory()
-        self.h_status = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.h_status = torch.zeros(8, dtype=torch.int32).pin_memory()
         self.graphs = {}
         self.draft_graphs = {}
         self.draft_steps = 0
@@ -320,9 +320,11 @@ class DenseGpuBackend(Backend):
     def _check(self) -> None:
         s = self.h_status.tolist()
         if s[0] != 0:
-            self.m.status.zero_()
-            self.h_status.zero_()
-            self._err = BackendError(f"device status code {s[0]} at site {s[1]} (block {s[2]})", fatal=True)
+            self.m.status[:4].zero_()
+            self.h_status[:4].zero_()
+            from ..ops.kernels import ST_ABORTED, ST_PEER_TIMEOUT, STATUS_NAMES
+            self._err = BackendError(f"device status code {s[0]} ({STATUS_NAMES.get(s[0], '?')}) at site {s[1]} (block {s[2]})", fatal=True,
+                                     group_lost=s[0] in (ST_PEER_TIMEOUT, ST_ABORTED))
 
     def take_error(self):
         e, self._err = self._err, None

@@ -30,6 +30,7 @@ class MockOptions:
     draft_error: float = 0.25      # probability a native draft token is wrong
     panic_at_step: int = -1
     fatal_at_step: int = -1
+    group_lost_at_step: int = -1   # a fatal error that names a lost rank of a multi-rank group (what a peer wait that ran out reports)
     retryable_from_step: int = -1
     nan_at_step: int = -1
     eos: int = -1                  # token the model emits after `eos_after` generated tokens (-1: never)
@@ -107,6 +108,8 @@ class MockBackend(Backend):
             raise RuntimeError("mock panic")
         if self.steps == o.fatal_at_step:
             raise BackendError("mock fatal device error", fatal=True)
+        if self.steps == o.group_lost_at_step:
+            raise BackendError("mock: device status code 3 (peer timed out)", fatal=True, group_lost=True)
         if o.retryable_from_step >= 0 and self.steps >= o.retryable_from_step:
             self.error = BackendError("mock retryable error", fatal=False)
 

@@ -103,7 +103,9 @@ def parse_group(prefix: str, parts: dict) -> Group:
                  sorted({p.file for p in parts.values()}), sum(p.nbytes for p in parts.values()), dict(parts))
 
 
-def scan(folder: str) -> Checkpoint:
+def scan(folder: str, verify_markers: bool = False) -> Checkpoint:
+    """Header-only scan.  `verify_markers` also reads the 4 bytes of every codebook marker tensor: a marker that does not hold its
+    codebook's multiplier refuses the group (reference crates/exl3/src/checkpoint.rs:203-220; its scan has the same switch)."""
     ck = Checkpoint(folder)
     files = sorted(f for f in os.listdir(folder) if f.endswith(".safetensors"))
     placement = None
@@ -150,7 +152,15 @@ def scan(folder: str) -> Checkpoint:
         ck.plain[name] = e
     for pre in sorted(trellis_prefixes):
         try:
-            ck.groups[pre] = parse_group(pre, by_prefix[pre])
+            g = parse_group(pre, by_prefix[pre])
+            if verify_markers:
+                for part, want in (("mcg", exl3.MARKER_MCG), ("mul1", exl3.MARKER_MUL1)):
+                    e = by_prefix[pre].get(part)
+                    if e is not None:
+                        got = int(np.frombuffer(read_tensor(folder, e).tobytes()[:4], dtype="<u4")[0])
+                        if got != want:
+                            raise ValueError(f".{part} marker holds 0x{got:08X}, not 0x{want:08X}")
+            ck.groups[pre] = g
         except ValueError as err:
             ck.bad[pre] = str(err)
     return ck

@@ -86,6 +86,57 @@ class HostLinear:
 
 
 @dataclass
+class HostSplitLinear:
+    """Projections that share their input but not their input rotation (a pack quantised one linear at a time: q / k / v, or gate / up,
+    each with its own `suh`).  Served as separate GEMMs whose partial sums land side by side, so everything downstream sees one
+    fused projection; packs written with one shared rotation take the fused single-GEMM path instead."""
+    parts: list                  # HostLinear, in output-column order
+
+    @property
+    def svh(self) -> np.ndarray:
+        return np.concatenate([p.svh for p in self.parts])
+
+    @property
+    def bias(self):
+        return None if self.parts[0].bias is None else np.concatenate([p.bias for p in self.parts])
+
+    @property
+    def codebook(self) -> str:
+        return self.parts[0].codebook
+
+    def dense(self) -> np.ndarray:
+        return np.concatenate([p.dense() for p in self.parts], axis=1)
+
+
+class SplitWeight:
+    """Device form of `HostSplitLinear`: the parts plus what the finish kernels read of a fused projection (svh, bias, N).  `suh` is None:
+    producers that would fuse the next rotation into their epilogue only update the residual, and `DenseGPU._linear` rotates per part."""
+    suh = None
+
+    def __init__(self, parts, norm):
+        self.parts, self.norm = parts, norm
+        self.svh = torch.cat([p.svh for p in parts])
+        self.bias = None if parts[0].bias is None else torch.cat([p.bias for p in parts])
+        self.codebook = parts[0].codebook
+
+    @property
+    def K(self) -> int:
+        return self.parts[0].K
+
+    @property
+    def N(self) -> int:
+        return sum(p.N for p in self.parts)
+
+    @property
+    def twice(self) -> int:
+        return self.parts[0].twice
+
+    @property
+    def nbytes(self) -> int:
+        return sum(p.nbytes for p in self.parts)
+
+
+@dataclass
 class HostLayer:
     attn_norm: np.ndarray
     qkv: HostLinear
@@ -126,8 +177,9 @@ def random_linear(K: int, N: int, bits: float, rng: np.random.Generator, codeboo
     return HostLinear(trellis, suh, svh, None, codebook)
 
 
-def random_weights(cfg: DenseConfig, seed: int = 0) -> HostWeights:
-    """Random-init weights of the architecture with valid random EXL3 tensors (benchmarks and kernel tests)."""
+def random_weights(cfg: DenseConfig, seed: int = 0, per_linear: bool = False) -> HostWeights:
+    """Random-init weights of the architecture with valid random EXL3 tensors (benchmarks and kernel tests).  `per_linear`: q / k / v and
+    gate / up keep their own input rotations (`HostSplitLinear`), the form of a pack that was quantised one linear at a time."""
     rng = np.random.default_rng(seed)
     d, F = cfg.d_model, cfg.ffn_padded
     s_in = 1.0 / math.sqrt(d)
@@ -140,6 +192,16 @@ def random_weights(cfg: DenseConfig, seed: int = 0) -> HostWeights:
             gu.svh[cfg.ffn:F] = 0
             gu.svh[F + cfg.ffn:] = 0
         down = random_linear(F, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(F), zero_rows_from=cfg.ffn if F != cfg.ffn else None)
+        if per_linear:
+            def split(l, widths):
+                parts, c0 = [], 0
+                for wd in widths:
+                    suh = np.where(rng.random(l.trellis.shape[0] * 16) < 0.5, -1.0, 1.0).astype(np.float16)
+                    parts.append(HostLinear(np.ascontiguousarray(l.trellis[:, c0 // 16:(c0 + wd) // 16]), suh, l.svh[c0:c0 + wd].copy(), None, l.codebook))
+                    c0 += wd
+                return HostSplitLinear(parts)
+            qkv = split(qkv, [cfg.n_q * cfg.head_dim, cfg.n_kv * cfg.head_dim, cfg.n_kv * cfg.head_dim])
+            gu = split(gu, [F, F])
         lay = HostLayer(_bf16_round(1.0 + 0.1 * rng.normal(size=d)), qkv, o, _bf16_round(1.0 + 0.1 * rng.normal(size=d)), gu, down)
         if cfg.qk_norm:
             lay.q_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=cfg.head_dim))
@@ -299,12 +361,16 @@ class DenseGPU:
     def _upload_host(self, w: HostWeights) -> None:
         K, device = self.K, self.device
         dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=device, dtype=dt)  # noqa: E731
-        up = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731
+        up1 = lambda l: K.Exl3Weight.from_numpy(l.trellis, l.suh, l.svh, l.bias, l.codebook, device)  # noqa: E731
+
+        def up(l, norm=None):
+            return SplitWeight([up1(p) for p in l.parts], norm) if isinstance(l, HostSplitLinear) else up1(l)
         self.embed = dev(w.embed, torch.bfloat16)
         self.layers = []
         for lay in w.layers:
-            self.layers.append(dict(attn_norm=dev(lay.attn_norm, torch.bfloat16), qkv=up(lay.qkv), o=up(lay.o), ffn_norm=dev(lay.ffn_norm, torch.bfloat16),
-                                    gate_up=up(lay.gate_up), down=up(lay.down),
+            an, fn = dev(lay.attn_norm, torch.bfloat16), dev(lay.ffn_norm, torch.bfloat16)
+            self.layers.append(dict(attn_norm=an, qkv=up(lay.qkv, an), o=up(lay.o), ffn_norm=fn,
+                                    gate_up=up(lay.gate_up, fn), down=up(lay.down),
                                     q_norm=None if lay.q_norm is None else dev(lay.q_norm, torch.bfloat16),
                                     k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16)))
         self.final_norm = dev(w.final_norm, torch.bfloat16)
@@ -353,6 +419,9 @@ class DenseGPU:
                 r = rows if name != "lm_head" else min(rows, 256)
                 part_elems = max(part_elems, s * r * n)
         self.part = torch.empty(part_elems, dtype=torch.float32, device=dev)
+        # split projections (per-linear input rotations) run one GEMM per part into this second buffer before the partials are placed
+        split = any(isinstance(v, SplitWeight) for L in self.layers for v in L.values())
+        self._part_split = torch.empty(part_elems, dtype=torch.float32, device=dev) if split else None
         kmax = max(k for k, _ in shapes.values())
         self.xr = torch.empty(R * kmax, dtype=torch.float16, device=dev)
         self.xr2 = torch.empty(R * cfg.ffn_padded, dtype=torch.float16, device=dev)
@@ -408,6 +477,18 @@ class DenseGPU:
     # ------------------------------------------------------------------ forward
     def _linear(self, xr, w, rows, cls, name):
         s = self.splits[(cls, name)]
+        if isinstance(w, SplitWeight):
+            # per-part input rotation of the normed residual rows, one GEMM per part, partial sums placed side by side
+            K, N = self.K, w.N
+            dst = self.part[:s * rows * N].view(s, rows, N)
+            xr_p = self.xr2[:rows * w.K].view(rows, w.K)
+            off = 0
+            for p in w.parts:
+                K.norm_rot_in(self.h[:rows], w.norm, self.cfg.eps, p.suh, xr_p)
+                K.exl3_gemm(xr_p, p, self._part_split, s, self.status)
+                dst[:, :, off:off + p.N].copy_(self._part_split[:s * rows * p.N].view(s, rows, p.N))
+                off += p.N
+            return s
         self.K.exl3_gemm(xr, w, self.part, s, self.status)
         return s
 
@@ -481,7 +562,8 @@ class DenseGPU:
         self._begin_forward()
         K.embed(ids, self.embed, h)
         L0 = self.layers[0]
-        K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)
+        if L0["qkv"].suh is not None:          # (split projections rotate per part inside _linear)
+            K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)
         nl = n_layers or len(self.layers)      # n_layers < all: the self-speculative draft (first layers + shared final norm and head)
         for li in range(nl):
             L = self.layers[li]

@@ -60,6 +60,24 @@ class MlaConfig:
         return 9 * 64 * 2 * self.n_layers
 
 
+def config_from_dict(c: dict) -> MlaConfig:
+    """MLA + MoE configuration from a config.json dictionary (this repository's `rexl3_mla_moe` packs; DeepSeek-V3 key names)."""
+    q = c.get("quantization_config") or {}
+    if q.get("quant_method") != "exl3":
+        raise ValueError("config.json has no quantization_config with quant_method exl3")
+    cfg = MlaConfig(n_layers=c["num_hidden_layers"], n_dense=int(c.get("first_k_dense_replace", 0)), d_model=c["hidden_size"], n_heads=c["num_attention_heads"],
+                    q_lora=int(c.get("q_lora_rank", 1536)), kv_lora=int(c.get("kv_lora_rank", 512)), rope_dim=int(c.get("qk_rope_head_dim", 64)),
+                    nope_dim=int(c.get("qk_nope_head_dim", 128)), v_dim=int(c.get("v_head_dim", 128)), dense_ffn=int(c.get("intermediate_size", 18432)),
+                    n_experts=int(c.get("n_routed_experts", 256)), top_k=int(c.get("num_experts_per_tok", 8)), expert_ffn=int(c.get("moe_intermediate_size", 2048)),
+                    shared_ffn=int(c.get("moe_intermediate_size", 2048)) * int(c.get("n_shared_experts", 1)), routed_scale=float(c.get("routed_scaling_factor", 2.5)),
+                    vocab=c["vocab_size"], eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), bits_a=float(q.get("bits_a", 2.0)),
+                    bits_b=float(q.get("bits_b", 2.5)), name=c.get("name", "mla-moe"))
+    if (cfg.q_lora, cfg.kv_lora, cfg.rope_dim, cfg.nope_dim, cfg.v_dim) != (1536, 512, 64, 128, 128):
+        raise ValueError(f"MLA geometry q_lora {cfg.q_lora} / kv_lora {cfg.kv_lora} / rope {cfg.rope_dim} / nope {cfg.nope_dim} / v {cfg.v_dim} "
+                         f"is not the 1536 / 512 / 64 / 128 / 128 the latent attention kernels are written for")
+    return cfg
+
+
 CONFIGS = {
     "mla-moe-671b": MlaConfig(),
     "test-mla": MlaConfig(n_layers=3, n_dense=1, d_model=256, n_heads=16, dense_ffn=256, n_experts=8, top_k=2, expert_ffn=128, shared_ffn=128,

@@ -45,6 +45,23 @@ CONFIGS["test-moe"] = MoEConfig(n_layers=3, d_model=256, n_q=4, n_kv=2, head_dim
                                 n_experts=8, top_k=2, expert_ffn=128, draft_layers=1)
 
 
+def config_from_dict(c: dict) -> MoEConfig:
+    """MoE configuration from a config.json dictionary (this repository's `rexl3_moe` packs and Qwen3-MoE shaped Hugging Face keys)."""
+    q = c.get("quantization_config") or {}
+    if q.get("quant_method") != "exl3":
+        raise ValueError("config.json has no quantization_config with quant_method exl3")
+    n_exp = c.get("num_experts", c.get("n_routed_experts"))
+    if not n_exp:
+        raise ValueError("config.json names no experts (num_experts)")
+    return MoEConfig(n_layers=c["num_hidden_layers"], d_model=c["hidden_size"], n_q=c["num_attention_heads"], n_kv=c["num_key_value_heads"],
+                     head_dim=c.get("head_dim", c["hidden_size"] // c["num_attention_heads"]), ffn=c.get("intermediate_size", 128), vocab=c["vocab_size"],
+                     eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e6), qk_norm=bool(c.get("qk_norm", False)),
+                     bits=float(q.get("bits", 3.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "moe"),
+                     n_experts=int(n_exp), top_k=int(c.get("num_experts_per_tok", 2)), expert_ffn=int(c.get("moe_intermediate_size", 128)),
+                     router_mode=c.get("router_mode", "sigmoid_bias" if c.get("scoring_func") == "sigmoid" else "softmax"),
+                     routed_scale=float(c.get("routed_scaling_factor", 1.0)), draft_layers=int(c.get("draft_layers", 4)))
+
+
 @dataclass
 class HostMoELayer(HostLayer):
     router: np.ndarray = None            # f32 [E, d] (bf16-rounded)

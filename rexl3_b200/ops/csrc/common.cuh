@@ -18,7 +18,10 @@
 namespace rx {
 
 // ---------------------------------------------------------------- status words
-// status[0] = first error code (0 = ok), status[1] = site, status[2] = blockIdx.x, status[3] = aux
+// status[0] = first error code (0 = ok), status[1] = site, status[2] = blockIdx.x, status[3] = aux;
+// status[4] = wait limit in microseconds set by the host (0 = the 2 s default), status[5] = abort word: the host (or a watchdog) sets it
+// non-zero and every bounded wait that polls it gives up with ST_ABORTED (the role of the reference's abort word,
+// crates/cuda/csrc/roce_dev.cuh:173-205).  The buffer has 8 words.
 enum : int { ST_OK = 0, ST_TIMEOUT = 1, ST_BAD_ARG = 2, ST_PEER_TIMEOUT = 3, ST_ABORTED = 4 };
 
 __device__ __forceinline__ void set_status(int* status, int code, int site, int aux = 0) {
@@ -38,6 +41,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 #ifndef RX_WAIT_LIMIT_NS
 #define RX_WAIT_LIMIT_NS 2000000000ull  // 2 s: far above any legitimate wait inside one kernel
 #endif
+// the limit of a wait that reports to `status`: the host's override in status[4] (microseconds), else the default
+__device__ __forceinline__ uint64_t wait_limit_ns(const int* status) {
+  if (status != nullptr) {
+    const int us = *reinterpret_cast<const volatile int*>(status + 4);
+    if (us > 0) return (uint64_t)us * 1000ull;
+  }
+  return RX_WAIT_LIMIT_NS;
+}
+__device__ __forceinline__ bool host_abort(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status + 5) != 0;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -78,13 +92,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int site, uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = wait_limit_ns(status);
   uint32_t polls = 0;
   while (true) {
     if (sleep_ns != 0) __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 15u) == 0) {
       if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > RX_WAIT_LIMIT_NS) {
+      if (host_abort(status)) {
+        *abort_flag = 1;
+        set_status(status, ST_ABORTED, site, (int)parity);
+        return false;
+      }
+      if (globaltimer_ns() - t0 > limit) {
         *abort_flag = 1;
         set_status(status, ST_TIMEOUT, site, (int)parity);
         return false;

@@ -46,9 +46,14 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 __device__ __forceinline__ bool tp_wait_flag(const unsigned* flag, unsigned ticket, int* status, int site) {
   if ((int)(ld_acquire_sys(flag) - ticket) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = wait_limit_ns(status);
   while (true) {
     if ((int)(ld_acquire_sys(flag) - ticket) >= 0) return true;
-    if (globaltimer_ns() - t0 > RX_WAIT_LIMIT_NS) {
+    if (host_abort(status)) {
+      set_status(status, ST_ABORTED, site, (int)ticket);
+      return false;
+    }
+    if (globaltimer_ns() - t0 > limit) {
       set_status(status, ST_PEER_TIMEOUT, site, (int)ticket);
       return false;
     }
@@ -80,12 +85,19 @@ __device__ __forceinline__ uint4 ll_wait(const uint4* src, unsigned ticket, int*
   uint4 v = ll_load(src);
   if (v.y == ticket && v.w == ticket) return v;
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = wait_limit_ns(status);
   for (unsigned it = 0;; ++it) {
     v = ll_load(src);
     if (v.y == ticket && v.w == ticket) return v;
-    if ((it & 63u) == 63u && globaltimer_ns() - t0 > RX_WAIT_LIMIT_NS) {
-      set_status(status, ST_PEER_TIMEOUT, site, (int)ticket);
-      return v;
+    if ((it & 63u) == 63u) {
+      if (host_abort(status)) {
+        set_status(status, ST_ABORTED, site, (int)ticket);
+        return v;
+      }
+      if (globaltimer_ns() - t0 > limit) {
+        set_status(status, ST_PEER_TIMEOUT, site, (int)ticket);
+        return v;
+      }
     }
   }
 }

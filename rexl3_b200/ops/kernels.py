@@ -46,15 +46,29 @@ class Exl3Weight:
                           None if bias is None else torch.from_numpy(np.ascontiguousarray(bias, dtype=np.float32)).to(device), codebook)
 
 
+STATUS_WORDS = 8
+ST_TIMEOUT, ST_BAD_ARG, ST_PEER_TIMEOUT, ST_ABORTED = 1, 2, 3, 4
+STATUS_NAMES = {ST_TIMEOUT: "wait timed out", ST_BAD_ARG: "bad argument", ST_PEER_TIMEOUT: "peer timed out", ST_ABORTED: "aborted by the host"}
+
+
 def new_status(device="cuda") -> torch.Tensor:
-    """Four int32 status words kernels write on a bounded-wait timeout: [code, site, block, aux]."""
-    return torch.zeros(4, dtype=torch.int32, device=device)
+    """Eight int32 status words.  Kernels write [code, site, block, aux] into the first four when a bounded wait runs out; the host may set
+    word 4 (wait limit in microseconds, 0 = the 2 s default) and word 5 (abort: every polling wait gives up) before a launch."""
+    return torch.zeros(STATUS_WORDS, dtype=torch.int32, device=device)
+
+
+def set_wait_limit(status: torch.Tensor, microseconds: int) -> None:
+    status[4] = int(microseconds)
+
+
+def set_abort(status: torch.Tensor, on: bool = True) -> None:
+    status[5] = 1 if on else 0
 
 
 def check_status(status: torch.Tensor, what: str = "kernel") -> None:
     s = status.tolist()
     if s[0] != 0:
-        raise _lib.KernelError(f"{what}: device status code {s[0]} at site {s[1]} (block {s[2]}, aux {s[3]})")
+        raise _lib.KernelError(f"{what}: device status code {s[0]} ({STATUS_NAMES.get(s[0], '?')}) at site {s[1]} (block {s[2]}, aux {s[3]})")
 
 
 def plan_splits(K: int, N: int, decode_class: bool) -> int:

@@ -235,6 +235,16 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
         if l.bias is not None:
             tensors[prefix + ".bias"] = l.bias.astype(np.float32)
 
+    def put_group(prefix, fused_name, part_names, l):
+        """A fused projection under its fused name, or - when its parts keep their own input rotations - one group per part under the
+        per-linear names other EXL3 packs use (q_proj / k_proj / v_proj, gate_proj / up_proj)."""
+        from ..models.dense import HostSplitLinear
+        if isinstance(l, HostSplitLinear):
+            for name, part in zip(part_names, l.parts):
+                put_lin(prefix + name, part)
+        else:
+            put_lin(prefix + fused_name, l)
+
     def put_f32(name, a):
         tensors[name] = np.ascontiguousarray(a, dtype=np.float32)
 
@@ -243,7 +253,7 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
         p = f"model.layers.{i}."
         put_plain(p + "input_layernorm.weight", L.attn_norm)
         put_plain(p + "post_attention_layernorm.weight", L.ffn_norm)
-        put_lin(p + "mlp.gate_up_proj", L.gate_up)
+        put_group(p + "mlp.", "gate_up_proj", ["gate_proj", "up_proj"], L.gate_up)
         put_lin(p + "mlp.down_proj", L.down)
         if not isinstance(L, HostLayer):              # a recurrent mixer of the hybrid family (Mamba2: "mixer", delta-net: "linear_attn")
             m = p + ("mixer." if hasattr(L, "d_skip") else "linear_attn.")
@@ -257,7 +267,7 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
             if hasattr(L, "d_skip"):
                 put_f32(m + "D", L.d_skip)
             continue
-        put_lin(p + "self_attn.qkv_proj", L.qkv)
+        put_group(p + "self_attn.", "qkv_proj", ["q_proj", "k_proj", "v_proj"], L.qkv)
         put_lin(p + "self_attn.o_proj", L.o)
         if L.q_norm is not None:
             put_plain(p + "self_attn.q_norm.weight", L.q_norm)
@@ -285,14 +295,28 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
     json.dump({"eos_token_id": conf.get("eos_token_id", cfg.vocab - 1)}, open(os.path.join(folder, "generation_config.json"), "w"))
 
 
-def config_from_pack(folder: str) -> DenseConfig:
+def config_from_pack(folder: str):
+    """The configuration object of the pack's family (dense, hybrid, MoE or MLA + MoE), from config.json."""
     c = json.load(open(os.path.join(folder, "config.json")))
+    mt = c.get("model_type")
+    if mt == "rexl3_moe":
+        from ..models import moe
+        return moe.config_from_dict(c)
+    if mt == "rexl3_mla_moe":
+        from ..models import mla
+        return mla.config_from_dict(c)
+    return config_from_dict(c)
+
+
+def config_from_dict(c: dict) -> DenseConfig:
+    """Dense / hybrid configuration from a config.json dictionary.  Reads the Hugging Face keys, so Llama / Qwen3 / Mistral shaped
+    configurations map directly; `qk_norm` defaults to true for the qwen3 model type (per-head q / k RMSNorm)."""
     q = c.get("quantization_config") or (c.get("text_config") or {}).get("quantization_config")
     if not q or q.get("quant_method") != "exl3":
         raise ValueError("config.json has no quantization_config with quant_method exl3")
     common = dict(n_layers=c["num_hidden_layers"], d_model=c["hidden_size"], n_q=c["num_attention_heads"], n_kv=c["num_key_value_heads"],
                   head_dim=c.get("head_dim", c["hidden_size"] // c["num_attention_heads"]), ffn=c["intermediate_size"], vocab=c["vocab_size"],
-                  eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), qk_norm=bool(c.get("qk_norm", False)),
+                  eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), qk_norm=bool(c.get("qk_norm", c.get("model_type") in ("qwen3", "qwen3_moe"))),
                   bits=float(q.get("bits", 4.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "dense"))
     if c.get("model_type") == "rexl3_hybrid":
         from ..models.hybrid import HybridConfig
@@ -313,7 +337,7 @@ def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeight
 
 def _load_pack(folder: str, threads: int, direct: bool) -> HostWeights:
     cfg = config_from_pack(folder)
-    ck = checkpoint.scan(folder)
+    ck = checkpoint.scan(folder, verify_markers=True)
     if ck.bad:
         name, why = sorted(ck.bad.items())[0]
         raise ValueError(f"pack refused: {name}: {why}")
@@ -335,9 +359,12 @@ def _load_pack(folder: str, threads: int, direct: bool) -> HostWeights:
         if prefix + fused_name in ck.groups:
             return lin(prefix + fused_name)
         ls = [lin(prefix + p) for p in parts]
-        if any(not np.array_equal(l.suh, ls[0].suh) or l.codebook != ls[0].codebook or l.trellis.shape[2] != ls[0].trellis.shape[2] for l in ls[1:]):
-            raise ValueError(f"pack refused: {prefix}{'/'.join(parts)} have different input scales or widths; the fused projection kernels "
-                             f"need one shared input rotation")
+        if any(l.codebook != ls[0].codebook or l.trellis.shape[2] != ls[0].trellis.shape[2] for l in ls[1:]):
+            raise ValueError(f"pack refused: {prefix}{'/'.join(parts)} differ in codebook or bit width; projections of one group must share both")
+        if any(not np.array_equal(l.suh, ls[0].suh) for l in ls[1:]):
+            # quantised one linear at a time (each projection has its own input rotation): served as one GEMM per part
+            from ..models.dense import HostSplitLinear
+            return HostSplitLinear(ls)
         bias = None if ls[0].bias is None else np.concatenate([l.bias for l in ls])
         return HostLinear(np.concatenate([l.trellis for l in ls], axis=1), ls[0].suh, np.concatenate([l.svh for l in ls]), bias, ls[0].codebook)
 

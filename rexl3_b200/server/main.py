@@ -100,9 +100,14 @@ def build(args):
         else:
             if folder is None:
                 raise SystemExit("rexl3-serve: --model DIR (or --random-init CONFIG) is required")
-            from ..quant import quantize
+            from ..models import registry
+            from ..quant import packs
             with boot.phase("scan_pack", folder=folder):
-                cfg = quantize.config_from_pack(folder)
+                try:
+                    family, fplan = registry.probe(folder)     # architecture -> family, refusals by name, before anything is read
+                except registry.FamilyError as e:
+                    raise SystemExit(f"rexl3-serve: pack refused ({e.kind}): {e}")
+                cfg = fplan.config
             if args.verify_pack != "off":
                 from ..format import verify as pack_verify
                 with boot.phase("verify_pack", mode=args.verify_pack):
@@ -112,7 +117,7 @@ def build(args):
                         raise SystemExit(f"rexl3-serve: pack refused by --verify-pack {args.verify_pack}: {issues[0]}"
                                          + (f" (+{len(issues) - 1} more)" if len(issues) > 1 else ""))
             with boot.phase("load_pack_host"):
-                weights = quantize.load_pack(folder)          # header scan + refusals by name happen before CUDA starts
+                weights = packs.load_any(folder)              # header scan + refusals by name happen before CUDA starts
         vocab, name = cfg.vocab, args.served_model_name or cfg.name
         kv_tokens = args.kv_tokens or args.slots * args.max_model_len
         info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None, "boot": boot.report}
@@ -185,9 +190,9 @@ def build(args):
                 common = dict(num_pages=pages, max_rows=min(256, args.window_rows), max_seqs=args.slots,
                               max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, max_prefill_rows=args.prefill_chunk)
                 if is_mla:
-                    model = mla_models.MlaMoEGPU(cfg, **common)
+                    model = mla_models.MlaMoEGPU(weights if weights is not None else cfg, **common)
                 elif is_moe:
-                    model = moe_models.MoEGPU(cfg, **common)
+                    model = moe_models.MoEGPU(weights if weights is not None else cfg, **common)
                 elif is_hybrid:
                     model = hybrid_models.HybridGPU(weights if weights is not None else cfg, **common)
                 else:

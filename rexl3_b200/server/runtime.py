@@ -237,7 +237,8 @@ class EngineHandle:
                 if e.fatal or self.consecutive_errors >= self.cfg.exit_after:
                     self._route(events)
                     self._fail_all(str(e))
-                    self.state, self.error = "failed", str(e)
+                    # a lost rank takes the whole group down (fail-stop): health answers 503 `group_lost` until a supervisor restarts all ranks
+                    self.state, self.error = ("group_lost" if getattr(e, "group_lost", False) else "failed"), str(e)
                     return
                 if self.consecutive_errors >= self.cfg.unready_after:
                     self.state = "degraded"

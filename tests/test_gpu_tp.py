@@ -70,3 +70,50 @@ def test_tp_loopback_matches_single_gpu_and_reference(ranks):
         w0 = ref.forward_seq(0, [t0], p)[0]
         assert (got[0] - w0).abs().max().item() < 0.05 * scale
         t0 = int(w0.argmax())
+
+
+def test_a_peer_wait_that_runs_out_returns_a_status_and_the_context_stays_usable():
+    """The wait for a flag nobody publishes, with a 5 ms limit set by the host: the kernel returns by itself, the status words name the
+    site and say ST_PEER_TIMEOUT, the next kernel on the same context runs normally, and the backend turns the words into a fatal
+    `group_lost` error.  Then the same with the abort word instead of a short limit.  Nothing traps, nothing hangs, no rank dies."""
+    import ctypes
+    import time
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.ops import kernels as K
+    from rexl3_b200.ops import lib as _lib
+    L = _lib.load()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")          # the peers' flag words: never written
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    status = K.new_status()
+    K.set_wait_limit(status, 5000)
+    t0 = time.time()
+    _lib.check(L.rx_tp_wait_flags(flags.data_ptr(), 2, epoch.data_ptr(), 1, status.data_ptr(), st), "rx_tp_wait_flags")
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.5
+    s = status.tolist()
+    assert s[0] == K.ST_PEER_TIMEOUT and s[1] == 190
+    with pytest.raises(_lib.KernelError, match="peer timed out"):
+        K.check_status(status)
+    assert int((torch.arange(10, device="cuda") * 2).sum()) == 90       # the context is alive
+    # abort word: a wait with the default (2 s) limit gives up at once
+    status = K.new_status()
+    K.set_abort(status)
+    t0 = time.time()
+    _lib.check(L.rx_tp_wait_flags(flags.data_ptr(), 2, epoch.data_ptr(), 1, status.data_ptr(), st), "rx_tp_wait_flags")
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0 and status.tolist()[0] == K.ST_ABORTED
+    # the backend's view of the same words
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+
+    class _M:          # the two attributes _check touches
+        pass
+    be = DenseGpuBackend.__new__(DenseGpuBackend)
+    be.m = _M()
+    be.m.status = K.new_status()
+    be.h_status = torch.tensor([K.ST_PEER_TIMEOUT, 190, 0, 1, 0, 0, 0, 0], dtype=torch.int32)
+    be._err = None
+    be._check()
+    err = be.take_error()
+    assert err is not None and err.fatal and err.group_lost

@@ -157,3 +157,23 @@ def test_non_bpe_tokenizer_falls_back_to_the_hf_library_with_streaming(tmp_path)
         dec = tok.stream()
         streamed = "".join(dec.push([i]) for i in ids) + dec.flush()
         assert streamed == whole and "\ufffd" not in streamed
+
+
+def test_a_lost_rank_turns_the_server_to_group_lost():
+    """A fatal backend error that names a lost rank (what a peer wait that ran out reports through the status words) fails the running
+    requests and leaves the server answering 503 `group_lost` on its health routes, never a zombie that accepts work."""
+    import time
+    args = main.parser().parse_args(["--backend", "mock", "--mock", "vocab=512,group_lost_at_step=3", "--slots", "2", "--max-model-len", "256"])
+    app, handle = main.make_app(args)
+    assert handle.wait_ready(10)
+    with TestClient(app) as c:
+        r = chat(c, max_tokens=32)
+        assert r.status_code in (500, 503)
+        for _ in range(50):
+            if handle.state == "group_lost":
+                break
+            time.sleep(0.05)
+        h = c.get("/health")
+        assert h.status_code == 503 and h.json()["status"] == "group_lost" and "peer timed out" in h.json()["error"]
+        assert chat(c).status_code == 503
+    handle.stop()
