@@ -260,8 +260,9 @@ class DenseTPShard:
                 return chain_nccl(x_part, s, w, norm_w, suh_next)
 
             def p_push():
-                _lib.check(Lib.rx_tp_finish_bcast(x_part.data_ptr(), s, M, d, w.svh.data_ptr(), None if (w.bias is None or r != 0) else w.bias.data_ptr(),
-                                                  ctypes.byref(g.bcast(r, parity, use)), _lib.stream_ptr()), "rx_tp_finish_bcast")
+                _lib.check(Lib.rx_tp_finish_bcast_mm(x_part.data_ptr(), s, M, d, w.svh.data_ptr(), None if (w.bias is None or r != 0) else w.bias.data_ptr(),
+                                                     ctypes.byref(g.bcast(r, parity, use)), _lib.stream_ptr(), g.mm_local(parity) or None),
+                           "rx_tp_finish_bcast_mm")
                 _lib.count()
 
             def p_sum():

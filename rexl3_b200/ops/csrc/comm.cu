@@ -188,10 +188,6 @@ struct BcastTp {
   const unsigned* epoch;
   unsigned use_index;
   int rows_cap;
-  // NVLS form (windows above the packet size): when set, the f32 rows go ONLY to this rank's own copy of a buffer that is bound to an
-  // NVLink multicast object ([rows_cap][N], no source dimension); the consumers read the sum over ranks with multimem.ld_reduce, so
-  // the R - 1 peer copies of every row never cross NVLink.  The flags still travel as plain peer stores.
-  float* mm_local;
 };
 
 // 16 bytes of the element-wise f32 sum, over all GPUs of the multicast object, of the values at this offset (reduced in the switch)
@@ -204,8 +200,11 @@ __device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
   return v;
 }
 
+// `mm_local` (NVLS form, windows above the packet size): when set, the f32 rows go ONLY to this rank's own copy of a buffer that is bound
+// to an NVLink multicast object ([rows_cap][N], no source dimension); the consumers read the sum over ranks with multimem.ld_reduce, so
+// the R - 1 peer copies of every row never cross NVLink.  The flags still travel as plain peer stores.
 __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M, int N, const __half* __restrict__ svh,
-                                    const float* __restrict__ bias, const __grid_constant__ BcastTp tp) {
+                                    const float* __restrict__ bias, const __grid_constant__ BcastTp tp, float* __restrict__ mm_local) {
   pdl_launch();
   pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -244,8 +243,8 @@ __global__ void finish_bcast_kernel(const float* __restrict__ part, int S, int M
         ll_store(d, y[0], y[1], ticket);
         ll_store(d + 1, y[2], y[3], ticket);
       }
-    } else if (tp.mm_local != nullptr) {
-      *reinterpret_cast<float4*>(tp.mm_local + (size_t)row * N + n0) = make_float4(y[0], y[1], y[2], y[3]);
+    } else if (mm_local != nullptr) {
+      *reinterpret_cast<float4*>(mm_local + (size_t)row * N + n0) = make_float4(y[0], y[1], y[2], y[3]);
     } else {
       const float4 o = make_float4(y[0], y[1], y[2], y[3]);
       const size_t at = ((size_t)tp.rank * tp.rows_cap + row) * N + n0;
@@ -474,7 +473,19 @@ RX_API int rx_tp_norm_rot_push(const void* h, int M, int n_own, int d, int col0,
 
 RX_API int rx_tp_bcast_desc_size() { return (int)sizeof(BcastTp); }
 
+static int finish_bcast_launch(const void* part, int S, int M, int N, const void* svh, const void* bias, const void* desc, void* stream, void* mm_local);
+
 RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void* svh, const void* bias, const void* desc, void* stream) {
+  return finish_bcast_launch(part, S, M, N, svh, bias, desc, stream, nullptr);
+}
+
+// The same with the NVLS destination (this rank's own address of the multicast-bound buffer of this parity; nullptr = peer stores).
+RX_API int rx_tp_finish_bcast_mm(const void* part, int S, int M, int N, const void* svh, const void* bias, const void* desc, void* stream,
+                                 void* mm_local) {
+  return finish_bcast_launch(part, S, M, N, svh, bias, desc, stream, mm_local);
+}
+
+static int finish_bcast_launch(const void* part, int S, int M, int N, const void* svh, const void* bias, const void* desc, void* stream, void* mm_local) {
   if (desc == nullptr || N % 128 || M < 1 || S < 1) return (int)cudaErrorInvalidValue;
   const BcastTp tp = *(const BcastTp*)desc;
   if (tp.ranks < 1 || tp.ranks > TP_MAX || M > tp.rows_cap) return (int)cudaErrorInvalidValue;
@@ -493,7 +504,7 @@ RX_API int rx_tp_finish_bcast(const void* part, int S, int M, int N, const void*
   int warps = (blocks + gy - 1) / gy;
   if (warps > 8) warps = 8;
   return (int)rx::launch(finish_bcast_kernel, dim3(M, gy), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, M, N, (const __half*)svh,
-                         (const float*)bias, tp);
+                         (const float*)bias, tp, (float*)mm_local);
 }
 
 static int allsum_launch(const void* ar, const void* flags, int ranks, int rows_cap, const void* epoch, unsigned use_index, int M, int N,

@@ -56,6 +56,7 @@ def _declare(lib):
         "rx_tp_finish_bcast": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
         "rx_tp_allsum_add_norm_rot": (c_int, [c_void, c_void, c_int, c_int, c_void, ctypes.c_uint, c_int, c_int, c_void, c_void, c_f, c_void, c_void,
                                               c_void, c_void, c_void]),
+        "rx_tp_finish_bcast_mm": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_tp_allsum_add_norm_rot_mm": (c_int, [c_void, c_void, c_int, c_int, c_void, ctypes.c_uint, c_int, c_int, c_void, c_void, c_f, c_void, c_void,
                                                  c_void, c_void, c_void, c_void]),
         "rx_exl3_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_ll, c_int, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),

@@ -48,6 +48,10 @@ class EpComm:
 
     def __init__(self, group, rank: int):
         from ..models.moe import CombineDst
+        # the same descriptor is handed to the combine kernel and to the finish-and-broadcast kernel: both layouts must be this one
+        L_ = _lib.load()
+        if not (ctypes.sizeof(CombineDst) == L_.rx_moe_combine_desc_size() == L_.rx_tp_bcast_desc_size()):
+            raise _lib.KernelError("combine / broadcast descriptor layouts differ from the library's")
         self.g, self.rank, self.R = group, rank, group.ranks
         self.L = group.layout
         self._dst = []

@@ -49,8 +49,7 @@ class CandTp(ctypes.Structure):
 
 class BcastTp(ctypes.Structure):
     _fields_ = [("ranks", ctypes.c_int), ("rank", ctypes.c_int), ("dst", ctypes.c_void_p * TP_MAX), ("dst_flag", ctypes.c_void_p * TP_MAX),
-                ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int),
-                ("mm_local", ctypes.c_void_p)]
+                ("local_count", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("use_index", ctypes.c_uint), ("rows_cap", ctypes.c_int)]
 
 
 AR_ROWS = 256        # rows of a decode / verify window (the one-shot all-reduce path)
@@ -190,7 +189,6 @@ class _GroupBase:
         me = self.base(rank, rank)
         t.local_count = me + L.count + 4 * (6 + parity)
         t.epoch, t.use_index = me + L.epoch, use_index
-        t.mm_local = self.mm_local(parity) or None
         return t
 
     def ar_ptr(self, rank: int, parity: int) -> int:

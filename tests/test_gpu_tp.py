@@ -93,7 +93,7 @@ def test_a_peer_wait_that_runs_out_returns_a_status_and_the_context_stays_usable
     torch.cuda.synchronize()
     assert time.time() - t0 < 1.5
     s = status.tolist()
-    assert s[0] == K.ST_PEER_TIMEOUT and s[1] == 190
+    assert s[0] == K.ST_PEER_TIMEOUT and s[1] == 180
     with pytest.raises(_lib.KernelError, match="peer timed out"):
         K.check_status(status)
     assert int((torch.arange(10, device="cuda") * 2).sum()) == 90       # the context is alive
@@ -112,7 +112,7 @@ def test_a_peer_wait_that_runs_out_returns_a_status_and_the_context_stays_usable
     be = DenseGpuBackend.__new__(DenseGpuBackend)
     be.m = _M()
     be.m.status = K.new_status()
-    be.h_status = torch.tensor([K.ST_PEER_TIMEOUT, 190, 0, 1, 0, 0, 0, 0], dtype=torch.int32)
+    be.h_status = torch.tensor([K.ST_PEER_TIMEOUT, 180, 0, 1, 0, 0, 0, 0], dtype=torch.int32)
     be._err = None
     be._check()
     err = be.take_error()
