@@ -23,6 +23,7 @@ from ..utils import trace
 from .backend import Backend, BackendError, DraftAsk, RowRequest
 
 PREFILL_STEP_ROWS = 4096
+PREFILL_PASS_GUARD = 8       # steps after which a prompt that keeps being passed over for shorter ones is served first
 
 
 @dataclass
@@ -72,6 +73,7 @@ class _Seq:
     committed_blocks: int = 0
     hashes: list = None
     reasoning: dict = None     # reasoning-budget state (see Engine._reasoning_budget)
+    passed: int = 0            # prefill steps in which shorter prompts were served instead of this one
 
 
 class StepError(Exception):
@@ -83,7 +85,7 @@ class StepError(Exception):
 class Engine:
     def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
                  spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
-                 prefill_policy: str = "burst", burst_tokens: int = 2048, cache_namespace: bytes = b"", device_sampler: bool = False,
+                 prefill_policy: str = "burst", burst_div: int = 2, burst_cap: int = 16, cache_namespace: bytes = b"", device_sampler: bool = False,
                  spill=None, arbiter=None):
         self.backend = backend
         self.admission = admission
@@ -105,7 +107,7 @@ class Engine:
         self.prefill_policy = prefill_policy
         # sample and accept on the device (the keyed sampler's device twin) when the backend offers it: only token ids come back
         self.device_sampler = bool(device_sampler and getattr(backend, "supports_device_sampler", lambda: False)())
-        self.burst_tokens = burst_tokens
+        self.burst_div, self.burst_cap = max(1, burst_div), max(1, burst_cap)
         self.cache_namespace = cache_namespace
         self.waiting: deque = deque()
         self.seqs: dict = {}           # id -> _Seq (admitted)
@@ -470,31 +472,44 @@ class Engine:
 
     # ------------------------------------------------------------------ prefill
     def _prefill(self) -> None:
+        """The prompt rows of one step.  Policy "serial": one slice, the waiting prompts in arrival order.  Policy "burst" (the default):
+        while prompts queue up, up to ceil(waiting / burst_div) slices (at most burst_cap; one while one prompt waits) share ONE backend call
+        of at most `prefill_chunk` rows; each slice goes to the prompt with the fewest rows left, oldest among equals, and a prompt that was
+        passed over PREFILL_PASS_GUARD steps goes first, so a long prompt among short ones is slowed, never starved (the reference's
+        `PrefillPolicy::Burst`, crates/engine/src/lib.rs:766-803).  Every prefill kernel is row-invariant, so the policy moves first tokens in
+        time and changes no bit of any reply."""
         pending = [self.seqs[i] for i in self.order if i in self.seqs and (self.seqs[i].prefilled < self.seqs[i].prompt_len or self.seqs[i].generated == 0)]
         if not pending:
             return
         t0 = time.perf_counter_ns()
-        if self.prefill_policy == "burst" and not self.prefix_cuts:
-            # short prompts that fit one slice each are batched into one backend call
-            short = [s for s in pending if s.prompt_len - s.prefilled <= self.burst_tokens]
-            batch, used = [], 0
-            for s in short:
-                n = s.prompt_len - s.prefilled
-                if batch and used + n > self.prefill_chunk:
+        if self.prefill_policy == "burst" and not self.prefix_cuts and len(pending) > 1:
+            guarded = [s for s in pending if s.passed >= PREFILL_PASS_GUARD]
+            rest = [s for s in pending if s.passed < PREFILL_PASS_GUARD]
+            rest.sort(key=lambda s: s.prompt_len - s.prefilled)        # stable: oldest among equals
+            max_slices = min(self.burst_cap, -(-len(pending) // self.burst_div))
+            chosen, rows_left = [], self.prefill_chunk
+            for s in guarded + rest:
+                if len(chosen) >= max_slices or rows_left <= 0:
                     break
-                batch.append(s)
-                used += n
-            if len(batch) > 1:
-                items = [(s.slot, s.prefilled, s.tokens[s.prefilled:s.prompt_len], True) for s in batch]
-                cand = min(64, max(s.req.sampling.candidate_count(self.backend.vocab_size) for s in batch))
-                outs = self.backend.prefill_slices(items, cand)
-                self._check_backend()
-                for s, o in zip(batch, outs):
-                    self.counters["prefill_tokens"] += s.prompt_len - s.prefilled
-                    s.prefilled = s.prompt_len
+                n = min(rows_left, s.prompt_len - s.prefilled)
+                chosen.append((s, n))
+                rows_left -= n
+            took = {id(s) for s, _ in chosen}
+            for s in pending:
+                s.passed = 0 if id(s) in took else s.passed + 1
+            items = [(s.slot, s.prefilled, s.tokens[s.prefilled:s.prefilled + n], s.prefilled + n >= s.prompt_len) for s, n in chosen]
+            cand = min(64, max(s.req.sampling.candidate_count(self.backend.vocab_size) for s, _ in chosen))
+            outs = self.backend.prefill_slices(items, cand)
+            self._check_backend()
+            for (s, n), o in zip(chosen, outs):
+                s.prefilled += n
+                self.counters["prefill_tokens"] += n
+                if s.prefilled >= s.prompt_len:
                     self._complete_prefill(s, o)
-                self.phase_ns["prefill"] += time.perf_counter_ns() - t0
-                return
+                else:
+                    self._commit_prefix(s)
+            self.phase_ns["prefill"] += time.perf_counter_ns() - t0
+            return
         s = pending[0]
         n = min(self.prefill_chunk, s.prompt_len - s.prefilled)
         if self.prefix_cuts and s.req.prefix_cache:

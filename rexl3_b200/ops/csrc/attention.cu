@@ -209,12 +209,31 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
   const int G = n_q / n_kv;
   const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
   const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
-  const int ctx = ctx_len[row];
+  // Row blocking: the 16 rows of the MMA tile hold RB = 16 / G consecutive window rows of ONE sequence (a verify window feeds
+  // [last, d1 .. dk] of a sequence as adjacent rows) times the G query heads of this KV head, so the sequence's K / V chunk is read
+  // once per RB rows instead of once per row (the reference packs RBLK * GRP = 48 (row, head) pairs the same way,
+  // crates/cuda/csrc/attention.cu:42-50).  The CTA of a row that is not the first of its block exits; which rows share a block is
+  // found here from row_seq (position of the row inside its run of equal sequence ids), so the host passes nothing new.  A tile row
+  // only ever meets its own accumulators and its own key mask, so a row's bits do not depend on its block mates.
+  const int RB = 16 / G > 0 ? 16 / G : 1;
+  const int seq = row_seq[row];
+  int pos_in_run = 0;
+  while (pos_in_run < row && pos_in_run < 64 && row_seq[row - pos_in_run - 1] == seq) ++pos_in_run;
+  if (pos_in_run % RB != 0) return;               // uniform for the CTA: a block mate computes this row
+  int nblk = 1;
+  while (nblk < RB && row + nblk < (int)gridDim.x && row_seq[row + nblk] == seq) ++nblk;
+  int ctx_max = 0;
+  for (int i = 0; i < nblk; ++i) ctx_max = max(ctx_max, ctx_len[row + i]);
   const int k_begin = chunk * DEC_CHUNK;
-  if (k_begin >= ctx) return;  // uniform for the CTA; the merge kernel only reads chunks below ctx
-  const int k_end = min(ctx, k_begin + DEC_CHUNK);
-  const int npages = (k_end - k_begin + PAGE - 1) / PAGE;
-  const int* bt = block_table + (size_t)row_seq[row] * max_blocks;
+  if (k_begin >= ctx_max) return;  // uniform for the CTA; the merge kernel only reads a row's chunks below its own ctx
+  const int k_end_max = min(ctx_max, k_begin + DEC_CHUNK);
+  const int npages = (k_end_max - k_begin + PAGE - 1) / PAGE;
+  const int* bt = block_table + (size_t)seq * max_blocks;
+  // the two tile rows of this lane: (block row, head) and the last key + 1 that row may see inside this chunk
+  const int t0 = lane >> 2, t1 = t0 + 8;
+  const int rb0 = t0 / G, rb1 = t1 / G, hh0 = t0 % G, hh1 = t1 % G;
+  const bool live0 = rb0 < nblk, live1 = rb1 < nblk;
+  const int kend0 = live0 ? min(ctx_len[row + rb0], k_begin + DEC_CHUNK) : 0, kend1 = live1 ? min(ctx_len[row + rb1], k_begin + DEC_CHUNK) : 0;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < KV_STAGES; ++i) mbar_init(&bars[i], 1);
@@ -228,18 +247,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       else load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
     }
   }
-  // Q fragments straight from global: rows of the MMA tile are the G query heads of this KV head
+  // Q fragments straight from global: tile row t = (block row t / G, query head t % G of this KV head)
   uint32_t qa[HD / 16][4];
   {
-    const int h0 = lane >> 2, h1 = h0 + 8;
-    const uint16_t* qrow = q + ((size_t)row * n_q + (size_t)kvh * G) * HD;
+    const uint16_t* q0 = q + ((size_t)(row + (live0 ? rb0 : 0)) * n_q + (size_t)kvh * G + hh0) * HD;
+    const uint16_t* q1 = q + ((size_t)(row + (live1 ? rb1 : 0)) * n_q + (size_t)kvh * G + hh1) * HD;
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
       const int c = ks * 16 + 2 * (lane & 3);
-      qa[ks][0] = h0 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h0 * HD + c) : 0u;
-      qa[ks][1] = h1 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h1 * HD + c) : 0u;
-      qa[ks][2] = h0 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h0 * HD + c + 8) : 0u;
-      qa[ks][3] = h1 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)h1 * HD + c + 8) : 0u;
+      qa[ks][0] = live0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+      qa[ks][1] = live1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+      qa[ks][2] = live0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+      qa[ks][3] = live1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
       if constexpr (FP8) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) qa[ks][i] = bf16x2_to_f16x2(qa[ks][i]);
@@ -262,15 +281,17 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
     ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 50);
     if (!ok) break;
     const int key0 = warp * 16;
-    const int valid = k_end - (k_begin + p * PAGE + key0);
+    const int kpos = k_begin + p * PAGE + key0;
+    const int valid0 = kend0 - kpos, valid1 = kend1 - kpos;      // per tile row: keys of this 16-key slice the row may see
+    const bool any = k_end_max - kpos > 0;                        // uniform for the warp
     if constexpr (FP8) {
       expand_page8<HD>(smem + s * TILE, conv);
       expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
       __syncthreads();
-      if (valid > 0) attn_step<HD, 16, true>(qa, smem_u32(conv), smem_u32(conv + T16), key0, valid, valid, scale_log2, m, l, o);
+      if (any) attn_step<HD, 16, true>(qa, smem_u32(conv), smem_u32(conv + T16), key0, valid0, valid1, scale_log2, m, l, o);
     } else {
-      if (valid > 0)
-        attn_step<HD, 16>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid, valid, scale_log2, m, l, o);
+      if (any)
+        attn_step<HD, 16>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid0, valid1, scale_log2, m, l, o);
     }
     __syncthreads();
   }
@@ -299,20 +320,22 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * HD; idx += ATT_THREADS) {
-    const int hq = idx / HD, d = idx % HD;
+  for (int idx = threadIdx.x; idx < nblk * G * HD; idx += ATT_THREADS) {
+    const int t = idx / HD, d = idx % HD;          // tile row = (block row, head)
+    const int rb = t / G, hq = t % G;
+    if (ctx_len[row + rb] <= k_begin) continue;    // this chunk lies beyond that row's context: nothing of it is ever read
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + hq) * 2]);
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + t) * 2]);
     float acc = 0.f, lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float mw = sm_ml[(w * 16 + hq) * 2];
+      const float mw = sm_ml[(w * 16 + t) * 2];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-      acc += f * sm_o[((size_t)w * 16 + hq) * HD + d];
-      lsum += f * sm_ml[(w * 16 + hq) * 2 + 1];
+      acc += f * sm_o[((size_t)w * 16 + t) * HD + d];
+      lsum += f * sm_ml[(w * 16 + t) * 2 + 1];
     }
-    const size_t pidx = ((size_t)row * n_q + (size_t)kvh * G + hq) * max_chunks + chunk;
+    const size_t pidx = ((size_t)(row + rb) * n_q + (size_t)kvh * G + hq) * max_chunks + chunk;
     part_o[pidx * HD + d] = acc * v_scale;
     if (d == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = lsum; }
   }

@@ -181,3 +181,42 @@ def test_reasoning_budget_zero_one_and_a_close_sampled_first():
         # a two-token close with budget 0 occupies indices 0 and 1
         two = _run_budget(0, (7001, 7002), spec)
         assert two[:2] == [7001, 7002] and two.count(7001) == 1
+
+
+def test_burst_prefill_serves_short_prompts_first_and_never_starves_a_long_one():
+    rng = np.random.default_rng(5)
+    lens = [3000, 40, 700, 41, 2500, 90, 39, 1200, 64, 8]
+    prompts = [rng.integers(0, 512, size=n).tolist() for n in lens]
+
+    def run(policy, **kw):
+        eng = Engine(MockBackend(MockOptions(slots=16, max_rows=512)), spec="none", prefill_policy=policy, prefill_chunk=256, **kw)
+        for i, p in enumerate(prompts):
+            eng.submit(Request(str(i), p, 6, GREEDY))
+        first, out, step = {}, {str(i): [] for i in range(len(prompts))}, 0
+        while eng.has_work():
+            step += 1
+            for ev in eng.step():
+                if ev.kind == "tokens":
+                    first.setdefault(ev.id, step)
+                    out[ev.id].extend(ev.tokens)
+        return first, out, step
+
+    f_serial, o_serial, n_serial = run("serial")
+    f_burst, o_burst, n_burst = run("burst")
+    assert o_serial == o_burst                                     # the policy changes no token
+    # serial: arrival order, so the 8-token prompt waits for all the long ones; burst: the short ones share the first steps
+    short = [str(i) for i, n in enumerate(lens) if n <= 90]
+    assert max(f_burst[i] for i in short) <= 2 and f_serial["9"] > 30
+    assert sorted(f_burst.values())[len(lens) // 2] < sorted(f_serial.values())[len(lens) // 2]
+    # a stream of new short prompts cannot starve the long one: it is served at least every PREFILL_PASS_GUARD + 1 steps
+    eng = Engine(MockBackend(MockOptions(slots=64, max_rows=512)), spec="none", prefill_chunk=256, burst_cap=1)
+    eng.submit(Request("long", prompts[0], 2, GREEDY))
+    k, done_at = 0, None
+    for step in range(1, 400):
+        eng.submit(Request(f"s{k}", prompts[9], 1, GREEDY))
+        eng.submit(Request(f"t{k}", prompts[9], 1, GREEDY))
+        k += 1
+        if any(ev.id == "long" and ev.kind == "tokens" for ev in eng.step()):
+            done_at = step
+            break
+    assert done_at is not None and done_at <= (3000 // 256 + 1) * 10

@@ -210,6 +210,29 @@ def test_paged_attention_decode_and_prefill(K, hd, n_q, n_kv):
         ref = _ref_attn(q[r].view(n_q, hd), seq_k[s], seq_v[s], int(ctx[r]), n_q, n_kv, hd)
         assert (out[r].float() - ref).abs().max() < 2e-2, r
         assert (xr[r].float() - _hadamard(out[r].float() * suh.float())).abs().max() < 2e-2
+    # verify window: rows that share a sequence are blocked into one CTA's MMA tile; every row's bits must equal the bits it gets alone
+    wseq = [0, 0, 0, 0, 0, 1, 1, 0, 2]
+    wctx = [252, 253, 254, 255, 256 + 1, 64, 65, 700, 1]
+    W = len(wseq)
+    qw = torch.randn(W, n_q * hd).to(torch.bfloat16).cuda()
+    scr_w = K.attn_decode_scratch(W, n_q, hd, max_blocks * 64)
+    out_w = torch.empty(W, n_q * hd, dtype=torch.bfloat16, device="cuda")
+    xr_w = torch.empty(W, n_q * hd, dtype=torch.float16, device="cuda")
+    K.attn_decode(tk, tv, qw, bt, torch.tensor(wseq, dtype=torch.int32, device="cuda"), torch.tensor(wctx, dtype=torch.int32, device="cuda"),
+                  scr_w, n_q, n_kv, hd, max_blocks * 64, 1 / math.sqrt(hd), suh, xr_w, out_w, status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    scr_1 = K.attn_decode_scratch(1, n_q, hd, max_blocks * 64)
+    for r in range(W):
+        out_1 = torch.empty(1, n_q * hd, dtype=torch.bfloat16, device="cuda")
+        xr_1 = torch.empty(1, n_q * hd, dtype=torch.float16, device="cuda")
+        K.attn_decode(tk, tv, qw[r:r + 1].contiguous(), bt, torch.tensor(wseq[r:r + 1], dtype=torch.int32, device="cuda"),
+                      torch.tensor(wctx[r:r + 1], dtype=torch.int32, device="cuda"), scr_1, n_q, n_kv, hd, max_blocks * 64, 1 / math.sqrt(hd),
+                      suh, xr_1, out_1, status)
+        torch.cuda.synchronize()
+        assert torch.equal(out_w[r], out_1[0]) and torch.equal(xr_w[r], xr_1[0]), r
+        ref = _ref_attn(qw[r].view(n_q, hd), seq_k[wseq[r]], seq_v[wseq[r]], wctx[r], n_q, n_kv, hd)
+        assert (out_w[r].float() - ref).abs().max() < 2e-2, r
     # prefill: sequence 0 rows 500..699 (chunk of 200) and sequence 1 whole (65 rows)
     q_start = torch.tensor([0, 200], dtype=torch.int32, device="cuda")
     q_len = torch.tensor([200, 65], dtype=torch.int32, device="cuda")
