@@ -204,23 +204,14 @@ class DenseGpuBackend(Backend):
         M = self._fill_rows(specs)
         if M > self.max_rows:
             raise BackendError(f"window of {M} rows exceeds {self.max_rows}", fatal=False)
+        self.m.window_seq_rows = max(len(r.tokens) for r in reqs)
         max_ctx = max(r.first_position + len(r.tokens) for r in reqs)
         bucket = min(m.max_ctx_alloc, (max_ctx + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
         count = max(1, min(64, candidates))
         self._announce_window(M, count, bucket)
         self._upload_rows(M)
         self._sync_bt()
-        if self.use_graphs:
-            key = (M, count, bucket)
-            g = self.graphs.get(key)
-            if g is None:
-                g = self._capture(M, count, bucket)
-                self.graphs[key] = g
-            g.replay()
-            self.graph_replays += 1
-            self.replayed_kernels += self.graph_kernels[key]
-        else:
-            self._window(M, count, bucket)
+        self._run_window(M, count, bucket)
         rows = self._download(M, count)
         self._check()
         out, k = [], 0
@@ -248,23 +239,14 @@ class DenseGpuBackend(Backend):
         M = self._fill_rows(specs)
         if M > self.max_rows:
             raise BackendError(f"window of {M} rows exceeds {self.max_rows}", fatal=False)
+        self.m.window_seq_rows = max(len(r.tokens) for r in reqs)
         max_ctx = max(r.first_position + len(r.tokens) for r in reqs)
         bucket = min(m.max_ctx_alloc, (max_ctx + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
         count = max(1, min(64, candidates))
         self._announce_window(M, count, bucket)
         self._upload_rows(M)
         self._sync_bt()
-        if self.use_graphs:
-            key = (M, count, bucket)
-            g = self.graphs.get(key)
-            if g is None:
-                g = self._capture(M, count, bucket)
-                self.graphs[key] = g
-            g.replay()
-            self.graph_replays += 1
-            self.replayed_kernels += self.graph_kernels[key]
-        else:
-            self._window(M, count, bucket)
+        self._run_window(M, count, bucket)
         windows = [(s, pos, r.tokens) for r, (s, pos) in zip(reqs, samplings)]
         samples, accepted, err = m.K.verify_accept(m._ids_view(M, count), m._vals_view(M, count), windows, device=m.device)
         hs, ha = samples.cpu().tolist(), accepted.cpu().tolist()      # the stream-ordered copies also fence the step
@@ -278,6 +260,22 @@ class DenseGpuBackend(Backend):
             out.append((None if bad else hs[k:k + n], a))
             k += n
         return out
+
+    def _graph_key(self, M: int, count: int, bucket: int) -> tuple:
+        return (M, count, bucket, getattr(self.m, "window_seq_rows", 1))
+
+    def _run_window(self, M: int, count: int, bucket: int) -> None:
+        if not self.use_graphs:
+            self._window(M, count, bucket)
+            return
+        key = self._graph_key(M, count, bucket)
+        g = self.graphs.get(key)
+        if g is None:
+            g = self._capture(M, count, bucket)
+            self.graphs[key] = g
+        g.replay()
+        self.graph_replays += 1
+        self.replayed_kernels += self.graph_kernels[key]
 
     def _announce_window(self, M: int, count: int, bucket: int) -> None:
         """Hook for multi-rank backends: tell the other ranks what is about to run (before the block-table dirty set is cleared)."""
@@ -296,7 +294,7 @@ class DenseGpuBackend(Backend):
         n0 = _oplib.launch_count
         with torch.cuda.graph(g):
             self._window(M, count, bucket)
-        self.graph_kernels[(M, count, bucket)] = _oplib.launch_count - n0
+        self.graph_kernels[self._graph_key(M, count, bucket)] = _oplib.launch_count - n0
         self.graph_captures += 1
         return g
 
@@ -399,6 +397,7 @@ class DenseGpuBackend(Backend):
         k = min(self.DK, max(a.max_drafts for a in asks))
         if k <= 0:
             return {}
+        self.m.window_seq_rows = 1          # draft steps feed one row per sequence
         self._host_writable()
         h = self.h_draft.numpy()
         top = 0
@@ -520,27 +519,105 @@ def deepest_snapshot(handles) -> int:
 
 
 class HybridGpuBackend(DenseGpuBackend):
-    """Backend over a hybrid (Mamba2 / delta-net + attention) executor.  The recurrent state advances with every row it is fed, so: no draft
-    rows (`supports_rollback` is False), and a window is never run twice for one step (the eager run before a graph capture stands in for
-    that graph's first replay).
+    """Backend over a hybrid (Mamba2 / delta-net + attention) executor.
+
+    Rollback: a window that carries draft rows runs the recurrent layers in record mode (the pools are only read; every layer keeps the
+    window's in_proj and post-conv rows), and `commit` queues (first row, rows kept) per sequence; before the next backend call that reads
+    or writes the pools, ONE replay launch per recurrent layer walks the kept rows again and stores state and conv history (the reference's
+    record / commit split, crates/cuda/csrc/gdn.cu:253-322).  The replay is the window's own arithmetic on the recorded inputs, so the
+    pools equal what a serial decode leaves, bit for bit.  A window without drafts stores its state directly; such a window must not run
+    twice for one step, so the eager run before its graph capture stands in for that graph's first replay.  `rollback=False` turns the
+    record path off (no draft rows are planned, no record buffers are allocated).
 
     Prefix cache: off unless `state_snapshots=True`.  With it, a block's handle is (page, snapshot or None): the KV pages of the attention
     layers are shared by refcount as in the dense backend, and the handle of the block where a prefill slice ended also holds clones of the
     slot's conv and state pool rows (the engine cuts a slice at the prompt's last block boundary for backends with `prefix_needs_cuts`).  A
     restore goes as deep as the last handle with a snapshot.  A snapshot costs the model's whole per-stream state (hundreds of MiB for the
-    large configs), which `prefix_bytes_per_block` charges to every block.  This option has not run on a GPU yet; the same protocol is
-    exercised by the CPU hybrid backend."""
+    large configs), which `prefix_bytes_per_block` charges to every block."""
     name = "cuda-hybrid"
 
-    def __init__(self, model, max_slots=None, use_graphs: bool = True, state_snapshots: bool = False):
+    def __init__(self, model, max_slots=None, use_graphs: bool = True, state_snapshots: bool = False, rollback: bool = True):
         super().__init__(model, max_slots=max_slots, use_graphs=use_graphs, self_draft=False)
         self.state_snapshots = bool(state_snapshots)
+        self.rollback = bool(rollback)
+        self._rec_rows = None        # slot -> first row of the last recorded window (None: the last window stored its state itself)
+        self._rec_M = 0
+        self._commits = []           # (first row, rows kept) of the sequences committed since that window
+        self.commit_replays = 0
+        if self.rollback:
+            model.enable_record(self.max_rows)
+            self.h_seg = torch.zeros(2, self.max_rows, dtype=torch.int32).pin_memory()
+            self.d_seg = torch.zeros(2, self.max_rows, dtype=torch.int32, device=model.device)
 
     def supports_rollback(self) -> bool:
-        return False
+        return self.rollback
 
     def supports_device_sampler(self) -> bool:
         return False
+
+    # ------------------------------------------------------------------ record / commit
+    def _graph_key(self, M, count, bucket):
+        return super()._graph_key(M, count, bucket) + (self.m.ssm_mode,)
+
+    def _flush_commits(self) -> None:
+        """Replay the kept rows of the last recorded window into the pools (one launch per recurrent layer)."""
+        segs = [(r0, k) for r0, k in self._commits if k > 0]
+        self._commits = []
+        M, self._rec_rows = self._rec_M, None
+        if not segs:
+            return
+        self._host_writable()
+        h = self.h_seg.numpy()
+        n = len(segs)
+        h[0, :n] = [r0 for r0, _ in segs]
+        h[1, :n] = [k for _, k in segs]
+        self.d_seg[:, :n].copy_(self.h_seg[:, :n], non_blocking=True)
+        self._uploaded()
+        self.h2d_bytes += 8 * n
+        d = self.d_rows
+        self.m.commit_rows(M, d[3, :M], d[1, :M], self.d_seg[0], self.d_seg[1], n)
+        self.commit_replays += 1
+
+    def step(self, reqs, candidates):
+        self._flush_commits()
+        K = self.m.K
+        record = self.rollback and any(len(r.tokens) > 1 for r in reqs)
+        self.m.ssm_mode = K.SCAN_RECORD if record else K.SCAN_FINAL
+        try:
+            out = super().step(reqs, candidates)
+        finally:
+            self.m.ssm_mode = K.SCAN_FINAL
+        if record:
+            self._rec_rows, r0 = {}, 0
+            for r in reqs:
+                self._rec_rows[r.slot] = r0
+                r0 += len(r.tokens)
+            self._rec_M = r0
+        return out
+
+    def commit(self, slot, keep):
+        keep = min(keep, self.pending[slot])
+        if self._rec_rows is not None and slot in self._rec_rows:
+            self._commits.append((self._rec_rows.pop(slot), keep))
+        super().commit(slot, keep)
+
+    def release(self, slot):
+        if self._rec_rows is not None:
+            self._rec_rows.pop(slot, None)        # rows of a window that is dropped with its sequence
+        super().release(slot)
+
+    def prefill_slices(self, items, candidates):
+        self._flush_commits()
+        return super().prefill_slices(items, candidates)
+
+    def score_last(self, slot, tokens, chunk):
+        self._flush_commits()
+        return super().score_last(slot, tokens, chunk)
+
+    def _capture(self, M, count, bucket):
+        g = super()._capture(M, count, bucket)
+        # a recorded window stores nothing, so running it twice is harmless; one that stores its state must not be replayed for the same step
+        return g if self.m.ssm_mode == self.m.K.SCAN_RECORD else _SkipFirstReplay(g)
 
     def prefix_block_tokens(self):
         return PAGE if self.state_snapshots else 0
@@ -552,6 +629,7 @@ class HybridGpuBackend(DenseGpuBackend):
         return self.cfg.kv_bytes_per_token() * PAGE + self.cfg.state_bytes_per_slot()
 
     def _snapshot(self, slot):
+        self._flush_commits()
         m = self.m
         return {li: (m.conv_pool[li][slot].clone(), m.ssm_pool[li][slot].clone()) for li in m.ssm_pool}
 
@@ -563,6 +641,7 @@ class HybridGpuBackend(DenseGpuBackend):
 
     def prefix_restore(self, slot, handles):
         assert self.len[slot] == 0 and not self.pages[slot]
+        self._flush_commits()
         best = deepest_snapshot(handles)
         if best < 0:
             return 0
@@ -589,5 +668,3 @@ class HybridGpuBackend(DenseGpuBackend):
     def prefix_import(self, payload):
         return None
 
-    def _capture(self, M, count, bucket):
-        return _SkipFirstReplay(super()._capture(M, count, bucket))

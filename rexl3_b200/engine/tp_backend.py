@@ -61,7 +61,7 @@ class _TpExec:
             n0 = _oplib.launch_count
             self.run_window_eager(M, count, bucket)
             return _oplib.launch_count - n0
-        key = (M, count, bucket)
+        key = (M, count, bucket, getattr(self.sh, "window_seq_rows", 1))
         g = self.tp_graphs.get(key)
         if g is None:
             self.run_window_eager(M, count, bucket)       # every rank runs this in the same step, so peers are there
@@ -127,6 +127,7 @@ class _TpExec:
         self._staged.record()
         self._staged_pending = True
         if op == OP_WINDOW:
+            self.sh.window_seq_rows = max(1, max_qlen)     # a window's message carries its longest run of rows per sequence in this field
             self.run_window(M, count, bucket)
         else:
             self.run_prefill(M, nseq, max_qlen, last_rows, count)
@@ -213,7 +214,7 @@ class DenseTpBackend(DenseGpuBackend):
         self.ctrl_bytes += 4 * (HEAD + payload.size)
 
     def _announce_window(self, M, count, bucket):
-        self._send(OP_WINDOW, M, count, bucket)
+        self._send(OP_WINDOW, M, count, bucket, 0, getattr(self.m, "window_seq_rows", 1))
 
     def step(self, reqs, candidates):
         return super().step(reqs, candidates)

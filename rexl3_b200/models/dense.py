@@ -325,6 +325,8 @@ class DenseGPU:
         device: any random bit ring is a valid trellis, which is how benchmark models of tens of GB are made in seconds)."""
         from ..ops import kernels as K
         self.K = K
+        self.window_seq_rows = 1       # the most adjacent rows one sequence has in the next decode / verify window (set by the backend)
+        self.attn_plan = None          # device plan of the current window for the attention kernel (allocated with the scratch)
         self.device = device
         if isinstance(w, DenseConfig):
             self.cfg = cfg = w
@@ -431,6 +433,7 @@ class DenseGPU:
         self.logits = torch.empty(min(R, 256), cfg.vocab_padded, dtype=torch.float32, device=dev)
         self.max_ctx_alloc = self.max_blocks * PAGE
         self.attn_scratch = K.attn_decode_scratch(min(R, 256), cfg.n_q, cfg.head_dim, self.max_ctx_alloc, dev)
+        self.attn_plan = K.attn_plan_buffer(dev)
         self.topk_scratch = K.topk_scratch(min(R, 256), cfg.vocab_padded, 64, dev)
         self.cand_ids = torch.empty(min(R, 256), 64, dtype=torch.int32, device=dev)
         self.cand_vals = torch.empty(min(R, 256), 64, dtype=torch.float32, device=dev)
@@ -444,6 +447,17 @@ class DenseGPU:
     def _kv_layers(self):
         """Indices of the layers that own a paged KV cache (all of them here; a hybrid has layers without one)."""
         return range(self.cfg.n_layers)
+
+    def scale_tail(self, first_layer: int, eps: float) -> None:
+        """Multiply the output scales of the residual writers (`o` and `down`, expert stacks included) of layers >= first_layer by eps.
+        A synthetic-weight recipe for speculation benchmarks: with a small eps the layers above the draft depth barely move the residual
+        stream, so a draft made of the first layers plus the shared head agrees with the target often; eps sets how often.  Random-init
+        weights only have this knob: their acceptance is otherwise zero."""
+        for L in self.layers[first_layer:]:
+            for k in ("o", "down"):
+                w = L.get(k)
+                if w is not None and getattr(w, "svh", None) is not None:
+                    w.svh.mul_(eps)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes
@@ -502,7 +516,8 @@ class DenseGPU:
                           self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li])
         if prefill is None:
             K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
-                          max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc)
+                          max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc, max_seq_rows=self.window_seq_rows,
+                          plan=self.attn_plan)
         else:
             ao = self.attn_out[:M]
             K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
@@ -560,6 +575,9 @@ class DenseGPU:
         q = self.q[:M]
         scale = 1.0 / math.sqrt(cfg.head_dim)
         self._begin_forward()
+        if prefill is None and self.attn_plan is not None:
+            # one plan of the window (row blocks and work items of the persistent attention kernel) serves every layer
+            K.attn_plan(row_seq, ctx_len, cfg.n_q, cfg.n_kv, self.window_seq_rows, self.attn_plan)
         K.embed(ids, self.embed, h)
         L0 = self.layers[0]
         if L0["qkv"].suh is not None:          # (split projections rotate per part inside _linear)

@@ -123,6 +123,7 @@ class DenseTPShard:
         self.cand_ids = torch.empty(256 * 64, dtype=torch.int32, device=device)      # merged result (leader)
         self.cand_vals = torch.empty(256 * 64, dtype=torch.float32, device=device)
         self.attn_scratch = K.attn_decode_scratch(min(max_rows, 256), self.nq, hd, max_blocks_per_seq * PAGE, device)
+        self.attn_plan = K.attn_plan_buffer(device)
         self.max_ctx_alloc = max_blocks_per_seq * PAGE
 
     @staticmethod
@@ -210,6 +211,8 @@ class DenseTPShard:
 
         def p_start():
             _lib.check(Lib.rx_tp_bump_epoch(g.epoch_ptr(r), _lib.stream_ptr()), "rx_tp_bump_epoch")
+            if prefill is None:
+                K.attn_plan(row_seq, ctx_len, self.nq, self.nkv, getattr(self, "window_seq_rows", 1), self.attn_plan)
             K.embed(ids, self.embed, h)
             K.norm_rot_in(h, self.layers[0]["attn_norm"], cfg.eps, self.layers[0]["qkv"].suh, xr0)
         yield p_start
@@ -285,7 +288,8 @@ class DenseTPShard:
                 K.finish_qkv_rope(self.part, s, M, self.nq, self.nkv, hd, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions, self.inv_freq,
                                   slots, q, self.k_cache[li], self.v_cache[li], ksc)
                 K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, self.nq, self.nkv, hd,
-                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc)
+                              max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc,
+                              max_seq_rows=getattr(self, "window_seq_rows", 1), plan=self.attn_plan)
                 K.exl3_gemm(xr_a, L["o"], self.part, sp[("decode", "o")], self.status)
             yield p_attn
             a, b = chain(self.part, sp[("decode", "o")], L["o"], 0, u_o, L["ffn_norm"], L["gate_up"].suh)

@@ -364,6 +364,46 @@ class HybridGPU(DenseGPU):
         for li in cfg.gdn_layers():
             self.conv_pool[li] = torch.zeros(max_seqs, 3, cfg.gdn_conv_channels, dtype=torch.float32, device=device)
             self.ssm_pool[li] = torch.zeros(max_seqs, cfg.gdn_v_heads, 128, 128, dtype=torch.float32, device=device)
+        self.ssm_mode = self.K.SCAN_FINAL       # how the recurrent layers treat the rows of the next forward (see `enable_record`)
+        self.rec_proj, self.rec_xbc, self.rec_rows = {}, {}, 0
+
+    # ------------------------------------------------------------------ record / commit split of the recurrent layers
+    def enable_record(self, rows: int) -> None:
+        """Buffers that let a window of up to `rows` rows be fed without touching the pools (`ssm_mode = SCAN_RECORD`): every recurrent layer
+        keeps that window's in_proj rows and post-conv rows, and `commit_rows` later replays the accepted prefix of each sequence from them
+        (the reference's record / commit split, crates/cuda/csrc/gdn.cu:253-322).  Costs (proj width + conv channels) * 4 bytes per row
+        and layer."""
+        cfg, dev = self.cfg, self.device
+        if rows <= self.rec_rows:
+            return
+        for li, L in enumerate(self.layers):
+            if L["kind"] == "A":
+                continue
+            wp = cfg.in_proj_width if L["kind"] == "M" else cfg.delta_proj_width(L["kind"])
+            wc = cfg.conv_channels if L["kind"] == "M" else cfg.gdn_conv_channels
+            self.rec_proj[li] = torch.empty(rows, wp, dtype=torch.float32, device=dev)
+            self.rec_xbc[li] = torch.empty(rows * wc, dtype=torch.float32, device=dev)
+        self.rec_rows = rows
+
+    def record_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in self.rec_proj.values()) + sum(t.numel() * 4 for t in self.rec_xbc.values())
+
+    def commit_rows(self, M: int, row_seq, positions, seg_start, seg_len, nseg: int) -> None:
+        """Advance the pools over the first seg_len[i] rows of segment i of the last recorded window (rows, row_seq and positions as they were
+        fed).  One launch per recurrent layer; the arithmetic is the window's own, so the pools end up as a serial decode leaves them."""
+        cfg, K = self.cfg, self.K
+        for li, L in enumerate(self.layers):
+            if L["kind"] == "A":
+                continue
+            proj = self.rec_proj[li][:M]
+            if L["kind"] in "GK":
+                K.gdn_mixer(proj, M, cfg.gdn_k_heads, cfg.gdn_v_heads, 128, row_seq, positions, seg_start, seg_len, nseg, L["conv_w"], L["conv_b"],
+                            L["dt_bias"], L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.rec_xbc[li], self.ssm_out,
+                            kda=L["kind"] == "K", mode=K.SCAN_COMMIT)
+            else:
+                K.ssm_mixer(proj, M, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, row_seq, positions, seg_start, seg_len, nseg,
+                            L["conv_w"], L["conv_b"], L["dt_bias"], L["a_neg"], L["d_skip"], L["norm_w"], cfg.eps, self.conv_pool[li],
+                            self.ssm_pool[li], self.rec_xbc[li], self.ssm_y, self.ssm_out, mode=K.SCAN_COMMIT)
 
     def _kv_layers(self):
         return self.cfg.attn_layers()
@@ -483,24 +523,29 @@ class HybridGPU(DenseGPU):
             return super()._mixer(li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale)
         cfg, K = self.cfg, self.K
         seg_s, seg_l, nseg = (prefill["q_start"], prefill["q_len"], prefill["nseq"]) if prefill is not None else (None, None, 0)
+        mode = self.ssm_mode if prefill is None else K.SCAN_FINAL
+        rec = mode == K.SCAN_RECORD
+        if rec and M > self.rec_rows:
+            raise ValueError(f"a recorded window of {M} rows exceeds the {self.rec_rows} rows the record buffers hold")
+        xbc = self.rec_xbc[li] if rec else self.ssm_xbc
         if L["kind"] in "GK":
             kda = L["kind"] == "K"
             wp = cfg.delta_proj_width(L["kind"])
             s = self._linear(xr_d, L["in_proj"], M, cls, "kda_in" if kda else "gdn_in")
-            proj = self.ssm_proj[:M * wp].view(M, wp)
+            proj = self.rec_proj[li][:M] if rec else self.ssm_proj[:M * wp].view(M, wp)
             K.finish_store(self.part, s, M, L["in_proj"], proj)
             out = self.ssm_out[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
             K.gdn_mixer(proj, M, cfg.gdn_k_heads, cfg.gdn_v_heads, 128, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"], L["dt_bias"],
-                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, out, kda=kda)
+                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], xbc, out, kda=kda, mode=mode)
             xr_g = self.xr[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
             K.norm_rot_in(out, None, cfg.eps, L["out_proj"].suh, xr_g)
             return self._linear(xr_g, L["out_proj"], M, cls, "gdn_out")
         s = self._linear(xr_d, L["in_proj"], M, cls, "in_proj")
-        proj = self.ssm_proj[:M * cfg.in_proj_width].view(M, cfg.in_proj_width)
+        proj = self.rec_proj[li][:M] if rec else self.ssm_proj[:M * cfg.in_proj_width].view(M, cfg.in_proj_width)
         K.finish_store(self.part, s, M, L["in_proj"], proj)
         out = self.ssm_out[:M * cfg.d_inner].view(M, cfg.d_inner)
         K.ssm_mixer(proj, M, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"],
-                    L["dt_bias"], L["a_neg"], L["d_skip"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.ssm_xbc, self.ssm_y, out)
+                    L["dt_bias"], L["a_neg"], L["d_skip"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], xbc, self.ssm_y, out, mode=mode)
         xr_m = self.xr[:M * cfg.d_inner].view(M, cfg.d_inner)
         K.norm_rot_in(out, None, cfg.eps, L["out_proj"].suh, xr_m)
         return self._linear(xr_m, L["out_proj"], M, cls, "out_proj")

@@ -33,7 +33,8 @@ def case(w):
     scratch = K.attn_decode_scratch(rows, n_q, hd, blocks * 64)
     out = torch.empty(rows, n_q * hd, dtype=torch.bfloat16, device="cuda")
     xr = torch.empty(rows, n_q * hd, dtype=torch.float16, device="cuda")
-    run = lambda: K.attn_decode(tk, tv, q, bt, row_seq, ctx, scratch, n_q, n_kv, hd, blocks * 64, 1 / math.sqrt(hd), suh, xr, out, status)  # noqa: E731
+    run = lambda: K.attn_decode(tk, tv, q, bt, row_seq, ctx, scratch, n_q, n_kv, hd, blocks * 64, 1 / math.sqrt(hd), suh, xr, out, status,
+                                max_seq_rows=w)  # noqa: E731
     for _ in range(3):
         run()
     torch.cuda.synchronize()

@@ -89,7 +89,7 @@ template <int HD>
 __device__ __forceinline__ void expand_page8(const uint8_t* src, uint8_t* dst) {
   constexpr int CHUNKS = PAGE * HD / 16;          // 16 fp8 values each
   const uint32_t dbase = smem_u32(dst);
-  for (int c = threadIdx.x; c < CHUNKS; c += ATT_THREADS) {
+  for (int c = threadIdx.x; c < CHUNKS; c += blockDim.x) {
     const int key = c / (HD / 16), j = c % (HD / 16);
     const uint4 r = *reinterpret_cast<const uint4*>(src + (size_t)c * 16);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
@@ -187,14 +187,73 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
 
 
 // ------------------------------------------------------------------------------------------------ decode (split-KV)
+// Bytes of the decode kernel's main shared region: the K / V stages (and the FP8 expansion tiles) while pages stream, the per-warp partial
+// outputs [4 MT][16][HD] f32 once they are done.  The barriers and the per-warp (max, sum) pairs sit behind it.
+__host__ __device__ constexpr int dec_region_bytes(int hd, bool fp8, int mt) {
+  const int stages = fp8 ? 2 * KV_STAGES * PAGE * hd + 2 * PAGE * hd * 2 : 2 * KV_STAGES * PAGE * hd * 2;
+  const int merge = mt * 4 * 16 * (hd + 8) * 4;   // rows padded by 8 floats
+  return stages > merge ? stages : merge;
+}
+__host__ __device__ constexpr int dec_smem_bytes(int hd, bool fp8, int mt) { return dec_region_bytes(hd, fp8, mt) + 64 + mt * 4 * 16 * 2 * 4 + 128 + 1024; }
+// ---- the window plan: which rows share a CTA's MMA tiles, and the flat list of work items
+// Row blocking: the 16 * MT rows of a CTA's MMA tiles hold RB = 16 MT / G consecutive window rows of ONE sequence (a verify window feeds
+// [last, d1 .. dk] of a sequence as adjacent rows) times the G query heads of one KV head, so the sequence's K / V chunk is read once per RB
+// rows instead of once per row (the reference packs RBLK * GRP = 48 (row, head) pairs the same way, crates/cuda/csrc/attention.cu:42-50).
+// The plan is a function of row_seq and ctx_len only, so one plan serves every layer of a forward.  Layout (int32):
+//   [0] work items in total   [1] blocks   [2] RB   [3] n_kv   then, from PLAN_HEAD on, four arrays of PLAN_MAX_ROWS (+1) entries:
+//   first row of block b | rows in block b | chunks of block b (from the largest context among its rows) | items before block b (prefix)
+// A work item is (block, chunk, kv head): item = prefix[b] + chunk * n_kv + kvh.
+constexpr int PLAN_MAX_ROWS = 1024, PLAN_HEAD = 8;
+constexpr int PLAN_INTS = PLAN_HEAD + 4 * PLAN_MAX_ROWS + 8;
+
+__global__ void __launch_bounds__(256) attn_plan_kernel(const int* __restrict__ row_seq, const int* __restrict__ ctx_len, int rows, int RB, int n_kv,
+                                                       int* __restrict__ plan) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int s_seq[PLAN_MAX_ROWS], s_ctx[PLAN_MAX_ROWS];
+  __shared__ unsigned char s_lead[PLAN_MAX_ROWS];
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) { s_seq[r] = row_seq[r]; s_ctx[r] = ctx_len[r]; }
+  __syncthreads();
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    int pos = 0;                                   // position of the row inside its run of equal sequence ids
+    while (pos < r && s_seq[r - pos - 1] == s_seq[r]) ++pos;
+    s_lead[r] = (pos % RB) == 0;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  int* blk_row = plan + PLAN_HEAD;
+  int* blk_n = blk_row + PLAN_MAX_ROWS;
+  int* blk_nch = blk_n + PLAN_MAX_ROWS;
+  int* prefix = blk_nch + PLAN_MAX_ROWS;
+  int nb = 0, items = 0;
+  for (int r = 0; r < rows; ++r) {
+    if (!s_lead[r]) continue;
+    int n = 1, cmax = s_ctx[r];
+    while (n < RB && r + n < rows && s_seq[r + n] == s_seq[r]) { cmax = max(cmax, s_ctx[r + n]); ++n; }
+    const int nch = (cmax + DEC_CHUNK - 1) / DEC_CHUNK;
+    blk_row[nb] = r; blk_n[nb] = n; blk_nch[nb] = nch; prefix[nb] = items;
+    items += nch * n_kv;
+    ++nb;
+  }
+  prefix[nb] = items;
+  plan[0] = items; plan[1] = nb; plan[2] = RB; plan[3] = n_kv;
+}
+
 // part_o  : f32 [rows][n_q][max_chunks][HD]   unnormalised partial outputs
 // part_ml : f32 [rows][n_q][max_chunks][2]    (running max in log2 units, sum)
-template <int HD, bool FP8>
+// Persistent kernel: two CTAs per SM walk the plan's work items (item = blockIdx.x, + gridDim.x, ...), so no CTA is launched for a row that a
+// block mate computes, barriers are set up once, and the page counter runs on across items (stage = page % KV_STAGES).
+// MT = m16 tiles per CTA.  Each of the four warps owns a 16-key slice of every page and carries MT tiles of accumulators over it; a tile is
+// computed exactly as the one-tile kernel computes it, and a tile row only ever meets its own accumulators and its own key mask, so a row's
+// bits depend neither on MT nor on its block mates; more tiles only let more (row, head) pairs of one sequence share one pass over the
+// K / V chunk.  (Giving each tile its own four warps halved the CTAs per SM and was slower than two one-tile CTAs; launching one CTA per
+// row and letting the non-leaders exit cost more than the K / V reads it saved.)
+template <int HD, bool FP8, int MT>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2_in, int* status,
-                   const float* __restrict__ kv_scale) {
+                   const float* __restrict__ kv_scale, const int* __restrict__ plan) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -202,142 +261,192 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
   constexpr int T16 = PAGE * HD * 2;
   constexpr int TILE = FP8 ? PAGE * HD : T16;       // bytes of one stage of K (or V)
   uint8_t* conv = smem + 2 * KV_STAGES * TILE;       // FP8: the expanded fp16 K and V tiles of the page being processed
-  uint64_t* bars = (uint64_t*)(conv + (FP8 ? 2 * T16 : 0));
+  uint64_t* bars = (uint64_t*)(smem + dec_region_bytes(HD, FP8, MT));
   volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
-  const int row = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kw = warp;                               // this warp's 16-key slice of every page
   const int G = n_q / n_kv;
-  const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
-  const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
-  // Row blocking: the 16 rows of the MMA tile hold RB = 16 / G consecutive window rows of ONE sequence (a verify window feeds
-  // [last, d1 .. dk] of a sequence as adjacent rows) times the G query heads of this KV head, so the sequence's K / V chunk is read
-  // once per RB rows instead of once per row (the reference packs RBLK * GRP = 48 (row, head) pairs the same way,
-  // crates/cuda/csrc/attention.cu:42-50).  The CTA of a row that is not the first of its block exits; which rows share a block is
-  // found here from row_seq (position of the row inside its run of equal sequence ids), so the host passes nothing new.  A tile row
-  // only ever meets its own accumulators and its own key mask, so a row's bits do not depend on its block mates.
-  const int RB = 16 / G > 0 ? 16 / G : 1;
-  const int seq = row_seq[row];
-  int pos_in_run = 0;
-  while (pos_in_run < row && pos_in_run < 64 && row_seq[row - pos_in_run - 1] == seq) ++pos_in_run;
-  if (pos_in_run % RB != 0) return;               // uniform for the CTA: a block mate computes this row
-  int nblk = 1;
-  while (nblk < RB && row + nblk < (int)gridDim.x && row_seq[row + nblk] == seq) ++nblk;
-  int ctx_max = 0;
-  for (int i = 0; i < nblk; ++i) ctx_max = max(ctx_max, ctx_len[row + i]);
-  const int k_begin = chunk * DEC_CHUNK;
-  if (k_begin >= ctx_max) return;  // uniform for the CTA; the merge kernel only reads a row's chunks below its own ctx
-  const int k_end_max = min(ctx_max, k_begin + DEC_CHUNK);
-  const int npages = (k_end_max - k_begin + PAGE - 1) / PAGE;
-  const int* bt = block_table + (size_t)seq * max_blocks;
-  // the two tile rows of this lane: (block row, head) and the last key + 1 that row may see inside this chunk
-  const int t0 = lane >> 2, t1 = t0 + 8;
-  const int rb0 = t0 / G, rb1 = t1 / G, hh0 = t0 % G, hh1 = t1 % G;
-  const bool live0 = rb0 < nblk, live1 = rb1 < nblk;
-  const int kend0 = live0 ? min(ctx_len[row + rb0], k_begin + DEC_CHUNK) : 0, kend1 = live1 ? min(ctx_len[row + rb1], k_begin + DEC_CHUNK) : 0;
-
+  const int total = plan[0], nb = plan[1];
+  const int* blk_row = plan + PLAN_HEAD;
+  const int* blk_n = blk_row + PLAN_MAX_ROWS;
+  const int* prefix = blk_n + 2 * PLAN_MAX_ROWS;
+  if ((int)blockIdx.x >= total) return;
   if (threadIdx.x == 0) {
     for (int i = 0; i < KV_STAGES; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
-      if constexpr (FP8) load_kv_page8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
-      else load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[p]);
+  int gp = 0;                                        // pages this CTA has consumed so far: stage and barrier phase follow it
+  for (int item = blockIdx.x; item < total; item += gridDim.x) {
+    int lo = 0, hi = nb - 1;                         // the block whose item range holds `item`
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (prefix[mid] <= item) lo = mid; else hi = mid - 1;
     }
-  }
-  // Q fragments straight from global: tile row t = (block row t / G, query head t % G of this KV head)
-  uint32_t qa[HD / 16][4];
-  {
-    const uint16_t* q0 = q + ((size_t)(row + (live0 ? rb0 : 0)) * n_q + (size_t)kvh * G + hh0) * HD;
-    const uint16_t* q1 = q + ((size_t)(row + (live1 ? rb1 : 0)) * n_q + (size_t)kvh * G + hh1) * HD;
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-      const int c = ks * 16 + 2 * (lane & 3);
-      qa[ks][0] = live0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
-      qa[ks][1] = live1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
-      qa[ks][2] = live0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
-      qa[ks][3] = live1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
-      if constexpr (FP8) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) qa[ks][i] = bf16x2_to_f16x2(qa[ks][i]);
+    const int local = item - prefix[lo];
+    const int row = blk_row[lo], nblk = blk_n[lo], kvh = local % n_kv, chunk = local / n_kv;
+    const int seq = row_seq[row];
+    const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
+    const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
+    int ctx_max = 0;
+    for (int i = 0; i < nblk; ++i) ctx_max = max(ctx_max, ctx_len[row + i]);
+    const int k_begin = chunk * DEC_CHUNK;
+    const int k_end_max = min(ctx_max, k_begin + DEC_CHUNK);
+    const int npages = (k_end_max - k_begin + PAGE - 1) / PAGE;
+    const int* bt = block_table + (size_t)seq * max_blocks;
+    if (threadIdx.x == 0) {
+      fence_proxy_async();                           // the previous item's merge wrote this memory with plain stores
+      for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
+        const int sg = (gp + p) % KV_STAGES;
+        if constexpr (FP8) load_kv_page8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
+        else load_kv_page<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
       }
     }
-  }
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[HD / 8][4];
+    // the two rows of this lane in every tile: (block row, head) and the last key + 1 that row may see inside this chunk
+    int kend[MT][2];
+    // Q fragments straight from global: tile row t = (block row t / G, query head t % G of this KV head)
+    uint32_t qa[MT][HD / 16][4];
+    float m[MT][2], l[MT][2];
+    float o[MT][HD / 8][4];
 #pragma unroll
-  for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
-
-  bool ok = true;
-  for (int p = 0; p < npages; ++p) {
-    const int s = p % KV_STAGES;
-    if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
-      const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;  // stage sn was consumed in iteration p-1 (barrier below)
-      if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
-      else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+    for (int mt = 0; mt < MT; ++mt) {
+      bool live[2];
+      const uint16_t* qrow[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int t = mt * 16 + (lane >> 2) + 8 * r, rb = t / G, hh = t % G;
+        live[r] = rb < nblk;
+        kend[mt][r] = live[r] ? min(ctx_len[row + rb], k_begin + DEC_CHUNK) : 0;
+        qrow[r] = q + ((size_t)(row + (live[r] ? rb : 0)) * n_q + (size_t)kvh * G + hh) * HD;
+      }
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const int c = ks * 16 + 2 * (lane & 3);
+        qa[mt][ks][0] = live[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + c) : 0u;
+        qa[mt][ks][1] = live[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + c) : 0u;
+        qa[mt][ks][2] = live[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + c + 8) : 0u;
+        qa[mt][ks][3] = live[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + c + 8) : 0u;
+        if constexpr (FP8) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) qa[mt][ks][i] = bf16x2_to_f16x2(qa[mt][ks][i]);
+        }
+      }
+      m[mt][0] = m[mt][1] = -INFINITY;
+      l[mt][0] = l[mt][1] = 0.f;
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d) { o[mt][d][0] = o[mt][d][1] = o[mt][d][2] = o[mt][d][3] = 0.f; }
     }
-    ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 50);
-    if (!ok) break;
-    const int key0 = warp * 16;
-    const int kpos = k_begin + p * PAGE + key0;
-    const int valid0 = kend0 - kpos, valid1 = kend1 - kpos;      // per tile row: keys of this 16-key slice the row may see
-    const bool any = k_end_max - kpos > 0;                        // uniform for the warp
-    if constexpr (FP8) {
-      expand_page8<HD>(smem + s * TILE, conv);
-      expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
+
+    bool ok = true;
+    for (int p = 0; p < npages; ++p) {
+      const int s = (gp + p) % KV_STAGES;
+      if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
+        const int pn = p + KV_STAGES - 1, sn = (gp + pn) % KV_STAGES;  // stage sn was consumed in iteration p-1 (barrier below)
+        if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+        else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+      }
+      ok = mbar_wait(&bars[s], ((gp + p) / KV_STAGES) & 1, abort_flag, status, 50);
+      if (!ok) break;
+      const int key0 = kw * 16;
+      const int kpos = k_begin + p * PAGE + key0;
+      const bool any = k_end_max - kpos > 0;                        // uniform for the warp
+      if constexpr (FP8) {
+        expand_page8<HD>(smem + s * TILE, conv);
+        expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
+        __syncthreads();
+      }
+      if (any) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          if (mt * 16 >= nblk * G) break;                           // uniform: no live row in this tile
+          // per tile row: keys of this 16-key slice the row may see
+          if constexpr (FP8)
+            attn_step<HD, 16, true>(qa[mt], smem_u32(conv), smem_u32(conv + T16), key0, kend[mt][0] - kpos, kend[mt][1] - kpos, scale_log2, m[mt], l[mt], o[mt]);
+          else
+            attn_step<HD, 16>(qa[mt], smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, kend[mt][0] - kpos, kend[mt][1] - kpos,
+                              scale_log2, m[mt], l[mt], o[mt]);
+        }
+      }
       __syncthreads();
-      if (any) attn_step<HD, 16, true>(qa, smem_u32(conv), smem_u32(conv + T16), key0, valid0, valid1, scale_log2, m, l, o);
-    } else {
-      if (any)
-        attn_step<HD, 16>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid0, valid1, scale_log2, m, l, o);
+    }
+    if (!ok || *abort_flag != 0) return;
+    gp += npages;
+    // merge the 4 warps (key slices) through shared memory; the stages are free now: the last iteration ended with a barrier
+    constexpr int HDP = HD + 8;                       // padded row: the float2 stores of a warp then spread over all banks
+    float* sm_o = (float*)smem;                       // [tile][key slice][16][HDP]
+    float* sm_ml = (float*)(bars + 8);                // [tile][key slice][16][2], behind the barriers
+    int* s_ctx = (int*)(sm_ml + MT * 4 * 16 * 2);     // context length of each row of the block
+    const int r0 = lane >> 2, c0 = 2 * (lane & 3);
+    if ((int)threadIdx.x < nblk) s_ctx[threadIdx.x] = ctx_len[row + threadIdx.x];
+    // 1. every warp publishes its rows' running maxima and keeps the quad-reduced sums
+    float ls[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int wslot = mt * 4 + warp;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        ls[mt][r] = l[mt][r];
+        ls[mt][r] += __shfl_xor_sync(0xffffffffu, ls[mt][r], 1);
+        ls[mt][r] += __shfl_xor_sync(0xffffffffu, ls[mt][r], 2);
+      }
+      if ((lane & 3) == 0) {
+        sm_ml[(wslot * 16 + r0) * 2] = m[mt][0];
+        sm_ml[(wslot * 16 + r0 + 8) * 2] = m[mt][1];
+      }
     }
     __syncthreads();
-  }
-  if (!ok || *abort_flag != 0) return;
-  // merge the 4 warps in warp order through shared memory (stages are free now: last iteration ended with a barrier)
-  float* sm_o = (float*)smem;                       // [4][16][HD]
-  float* sm_ml = sm_o + 4 * 16 * HD;                // [4][16][2]
-  {
-    const int r0 = lane >> 2, c0 = 2 * (lane & 3);
+    // 2. rescale the own partial to the row's maximum over the four slices, then publish it
 #pragma unroll
-    for (int d = 0; d < HD / 8; ++d) {
-      float* base = sm_o + ((size_t)warp * 16) * HD + d * 8 + c0;
-      base[(size_t)r0 * HD] = o[d][0]; base[(size_t)r0 * HD + 1] = o[d][1];
-      base[(size_t)(r0 + 8) * HD] = o[d][2]; base[(size_t)(r0 + 8) * HD + 1] = o[d][3];
-    }
-    // row sums: quad-reduce so every lane of a quad holds the full sum of its rows
-    float ls[2] = {l[0], l[1]};
+    for (int mt = 0; mt < MT; ++mt) {
+      const int wslot = mt * 4 + warp;
+      float f[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      ls[r] += __shfl_xor_sync(0xffffffffu, ls[r], 1);
-      ls[r] += __shfl_xor_sync(0xffffffffu, ls[r], 2);
-    }
-    if ((lane & 3) == 0) {
-      sm_ml[(warp * 16 + r0) * 2] = m[0]; sm_ml[(warp * 16 + r0) * 2 + 1] = ls[0];
-      sm_ml[(warp * 16 + r0 + 8) * 2] = m[1]; sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = ls[1];
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < nblk * G * HD; idx += ATT_THREADS) {
-    const int t = idx / HD, d = idx % HD;          // tile row = (block row, head)
-    const int rb = t / G, hq = t % G;
-    if (ctx_len[row + rb] <= k_begin) continue;    // this chunk lies beyond that row's context: nothing of it is ever read
-    float mm = -INFINITY;
+      for (int r = 0; r < 2; ++r) {
+        const int tr = r0 + 8 * r;
+        float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + t) * 2]);
-    float acc = 0.f, lsum = 0.f;
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[((mt * 4 + w) * 16 + tr) * 2]);
+        f[r] = (m[mt][r] == -INFINITY) ? 0.f : exp2f(m[mt][r] - mm);
+      }
+      float* base = sm_o + ((size_t)wslot * 16) * HDP + c0;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = sm_ml[(w * 16 + t) * 2];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-      acc += f * sm_o[((size_t)w * 16 + t) * HD + d];
-      lsum += f * sm_ml[(w * 16 + t) * 2 + 1];
+      for (int d = 0; d < HD / 8; ++d) {
+        *reinterpret_cast<float2*>(base + (size_t)r0 * HDP + d * 8) = make_float2(o[mt][d][0] * f[0], o[mt][d][1] * f[0]);
+        *reinterpret_cast<float2*>(base + (size_t)(r0 + 8) * HDP + d * 8) = make_float2(o[mt][d][2] * f[1], o[mt][d][3] * f[1]);
+      }
+      if ((lane & 3) == 0) {
+        sm_ml[(wslot * 16 + r0) * 2 + 1] = ls[mt][0] * f[0];
+        sm_ml[(wslot * 16 + r0 + 8) * 2 + 1] = ls[mt][1] * f[1];
+      }
     }
-    const size_t pidx = ((size_t)(row + rb) * n_q + (size_t)kvh * G + hq) * max_chunks + chunk;
-    part_o[pidx * HD + d] = acc * v_scale;
-    if (d == 0) { part_ml[pidx * 2] = mm; part_ml[pidx * 2 + 1] = lsum; }
+    __syncthreads();
+    // 3. sum the four slices in slice order, four outputs per thread
+    for (int idx = threadIdx.x; idx < nblk * G * (HD / 4); idx += blockDim.x) {
+      const int t = idx / (HD / 4), d4 = (idx % (HD / 4)) * 4;          // tile row = (block row, head)
+      const int rb = t / G, hq = t % G;
+      if (s_ctx[rb] <= k_begin) continue;            // this chunk lies beyond that row's context: nothing of it is ever read
+      const int wb = (t >> 4) * 4, tr = t & 15;      // the four key-slice warps of the row's tile
+      float4 acc = *reinterpret_cast<const float4*>(sm_o + ((size_t)wb * 16 + tr) * HDP + d4);
+#pragma unroll
+      for (int w = 1; w < 4; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(sm_o + ((size_t)(wb + w) * 16 + tr) * HDP + d4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      const size_t pidx = ((size_t)(row + rb) * n_q + (size_t)kvh * G + hq) * max_chunks + chunk;
+      *reinterpret_cast<float4*>(part_o + pidx * HD + d4) = make_float4(acc.x * v_scale, acc.y * v_scale, acc.z * v_scale, acc.w * v_scale);
+      if (d4 == 0) {
+        float mm = -INFINITY, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          mm = fmaxf(mm, sm_ml[((wb + w) * 16 + tr) * 2]);
+          lsum += sm_ml[((wb + w) * 16 + tr) * 2 + 1];
+        }
+        part_ml[pidx * 2] = mm;
+        part_ml[pidx * 2 + 1] = lsum;
+      }
+    }
+    __syncthreads();                                  // the next item's loads overwrite the merge scratch
   }
 }
 
@@ -577,31 +686,78 @@ RX_API int rx_make_kv_tmap8(void* out128, const void* base, long long total_rows
 
 RX_API int rx_attn_decode_chunk() { return DEC_CHUNK; }
 
+// tiles per CTA for the longest run of rows one sequence has in a window (all of its (row, head) pairs in one pass over K / V where two
+// tiles hold them), and the rows of one sequence a CTA then takes
+static int dec_tiles(int max_seq_rows, int G) { return (max_seq_rows > 1 ? max_seq_rows * G + 15 : 16) / 16 > 1 ? 2 : 1; }
+static int dec_rows_per_block(int tiles, int G) { return 16 * tiles / G > 0 ? 16 * tiles / G : 1; }
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
 // scratch sizes (floats) for `rows` rows and contexts up to max_ctx
 RX_API long long rx_attn_decode_scratch_floats(int rows, int n_q, int hd, int max_ctx) {
   const long long mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
-  return (long long)rows * n_q * mc * (hd + 2);
+  return PLAN_INTS + (long long)rows * n_q * mc * (hd + 2);
+}
+RX_API int rx_attn_plan_ints() { return PLAN_INTS; }
+
+// The window plan of a decode / verify step (see attn_plan_kernel): computed once per forward from row_seq and ctx_len and handed to every
+// layer's rx_attn_decode call of that forward (same rows, n_q, n_kv and max_seq_rows).
+RX_API int rx_attn_plan(const void* row_seq, const void* ctx_len, int rows, int n_q, int n_kv, int max_seq_rows, void* plan, void* stream) {
+  if (rows <= 0 || rows > PLAN_MAX_ROWS || n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > 16) return (int)cudaErrorInvalidValue;
+  const int G = n_q / n_kv;
+  rx::launch(attn_plan_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, (const int*)row_seq, (const int*)ctx_len, rows,
+             dec_rows_per_block(dec_tiles(max_seq_rows, G), G), n_kv, (int*)plan);
+  return (int)cudaGetLastError();
+}
+
+template <int HD, bool FP8, int MT>
+static int launch_decode_kernel(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
+                                const int* ctx_len, float* part_o, float* part_ml, int rows, int n_q, int n_kv, int mc, float scale, int* status,
+                                cudaStream_t st, const float* kv_scale, const int* plan) {
+  constexpr int smem = dec_smem_bytes(HD, FP8, MT);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, FP8, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  // persistent: two CTAs per SM at most, never more than the items the window can have
+  const long long bound = (long long)rows * n_kv * mc;
+  const int grid = (int)(bound < 2 * sm_count() ? bound : 2 * sm_count());
+  rx::launch(attn_decode_kernel<HD, FP8, MT>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq,
+             ctx_len, part_o, part_ml, n_q, n_kv, mc, scale * 1.4426950408889634f, status, kv_scale, plan);
+  return (int)cudaGetLastError();
 }
 
 template <int HD, bool FP8>
 static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                          const int* ctx_len, float* scratch, int rows, int n_q, int n_kv, int max_ctx, float scale, const void* suh, void* xr,
-                         void* out_bf16, int* status, cudaStream_t st, const float* kv_scale) {
+                         void* out_bf16, int* status, cudaStream_t st, const float* kv_scale, int max_seq_rows, const int* plan) {
   const int mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
-  float* part_o = scratch;
-  float* part_ml = scratch + (size_t)rows * n_q * mc * HD;
-  const int smem = att_smem_bytes(HD, FP8);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
+  int* own_plan = (int*)scratch;                    // the head of the scratch holds a plan for callers that bring none
+  float* part_o = scratch + PLAN_INTS;
+  float* part_ml = part_o + (size_t)rows * n_q * mc * HD;
+  // tiles per CTA: enough for the longest run of rows one sequence has in this window (all of its (row, head) pairs in one pass over K / V)
+  const int G = n_q / n_kv;
+  const int tiles = dec_tiles(max_seq_rows, G);
+  if (plan == nullptr) {
+    rx::launch(attn_plan_kernel, dim3(1), dim3(256), 0, st, row_seq, ctx_len, rows, dec_rows_per_block(tiles, G), n_kv, own_plan);
+    plan = own_plan;
   }
-  dim3 grid(rows, n_kv, mc);
-  rx::launch(attn_decode_kernel<HD, FP8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, n_q,
-                                                         n_kv, mc, scale * 1.4426950408889634f, status, kv_scale);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
+  int e;
+#define RX_DEC_T(MT) launch_decode_kernel<HD, FP8, MT>(tk, tv, q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, rows, n_q, n_kv, mc, scale, status, st, kv_scale, plan)
+  if (tiles <= 1) e = RX_DEC_T(1);
+  else e = RX_DEC_T(2);
+#undef RX_DEC_T
+  if (e != 0) return e;
   const int blocks128 = n_q * HD / 128;
   int gy = (296 + rows - 1) / rows;
   if (gy > (blocks128 + 3) / 4) gy = (blocks128 + 3) / 4;
@@ -611,14 +767,18 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
 }
 
 // q: bf16 [rows][n_q*hd] (already rotated by RoPE).  Either/both outputs: xr = fp16(H(out*suh)) [rows][n_q*hd], out_bf16.
+// max_seq_rows: the most adjacent rows any one sequence has in this launch (1 = plain decode; a verify window's 1 + drafts); it only
+// picks how many MMA tiles a CTA carries, results do not depend on it.  plan: rx_attn_plan's output for this window (same max_seq_rows), or
+// nullptr to have it computed here into the head of the scratch.
 RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* row_seq,
                           const void* ctx_len, void* scratch, int rows, int n_q, int n_kv, int hd, int max_ctx, float scale, const void* suh,
-                          void* xr, void* out_bf16, int* status, void* stream, const void* kv_scale) {
-  if (n_q % n_kv != 0 || n_q / n_kv > 16 || (n_q * hd) % 128 != 0 || rows <= 0 || max_ctx <= 0) return (int)cudaErrorInvalidValue;
+                          void* xr, void* out_bf16, int* status, void* stream, const void* kv_scale, int max_seq_rows, const void* plan) {
+  if (n_q % n_kv != 0 || n_q / n_kv > 16 || (n_q * hd) % 128 != 0 || rows <= 0 || rows > PLAN_MAX_ROWS || max_ctx <= 0) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
   // kv_scale != nullptr: the maps describe an FP8 cache and kv_scale is f32 [2][n_kv] (K scales, then V scales) of this layer
 #define RX_DEC(HDV, F8) launch_decode<HDV, F8>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
-    (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, (const float*)kv_scale)
+    (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, (const float*)kv_scale, \
+    max_seq_rows, (const int*)plan)
   if (hd == 128) return kv_scale ? RX_DEC(128, true) : RX_DEC(128, false);
   if (hd == 64) return kv_scale ? RX_DEC(64, true) : RX_DEC(64, false);
 #undef RX_DEC

@@ -9,7 +9,12 @@
 //   ssm pool  f32 [slots][H][P][N]   P = 64 (head dim), N = 128 (state); n contiguous
 // Rows of one sequence are consecutive and in position order (a "segment"); a sequence appears in at most one segment of a
 // launch.  A row at position 0 starts from a zero state whatever the pools hold, so a slot needs no reset when it is reused.
-// Every row given to these kernels is committed: a backend that runs this mixer offers no drafts to reject.
+// Record / commit split (reference crates/cuda/csrc/gdn.cu:253-322: a verify window reads the pools, a later commit replays the accepted
+// prefix): the recurrence kernels take a mode.  SCAN_OUT alone = a window whose rows may still be rejected: the pools are read, outputs are
+// written, nothing is stored back; the caller keeps that launch's `proj` and `xbc` rows (per layer) as the record.  SCAN_STATE alone = the
+// commit: the same kernel walks the first `keep` recorded rows of each sequence again (the same arithmetic on the same inputs, so the state
+// equals what a serial decode of those rows leaves, bit for bit) and stores the state and the conv history; outputs are not written.
+// SCAN_OUT | SCAN_STATE = rows that are final when fed (prefill, windows without drafts).
 //
 // The conv is parallel over rows (each row reads its three predecessors from the launch's own rows or from the pool); the
 // recurrence is sequential over the rows of a segment with the state of one head in the registers of a 256-thread CTA
@@ -19,6 +24,7 @@
 namespace rx {
 
 constexpr int SSM_P = 64, SSM_N = 128, SSM_HIST = 3;
+constexpr int SCAN_OUT = 1, SCAN_STATE = 2;
 
 __device__ __forceinline__ float ssm_silu(float v) { return v / (1.f + __expf(-v)); }
 __device__ __forceinline__ float ssm_bf(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
@@ -72,7 +78,7 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
                                                       const int* __restrict__ positions, const int* __restrict__ seg_start,
                                                       const int* __restrict__ seg_len, const float* __restrict__ dt_bias,
                                                       const float* __restrict__ a_neg, const float* __restrict__ d_skip,
-                                                      float* __restrict__ ssm_pool, float* conv_pool, float* __restrict__ y) {
+                                                      float* __restrict__ ssm_pool, float* conv_pool, float* __restrict__ y, int mode) {
   pdl_launch();
   pdl_wait();
   __shared__ float sB[SSM_N], sC[SSM_N], sx[SSM_P];
@@ -121,8 +127,9 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    if (nq == 0) y[(size_t)r * DI + h * SSM_P + p] = acc + Dh * sx[p];
+    if (nq == 0 && (mode & SCAN_OUT)) y[(size_t)r * DI + h * SSM_P + p] = acc + Dh * sx[p];
   }
+  if (!(mode & SCAN_STATE)) return;
 #pragma unroll
   for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
   ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq, h, (int)gridDim.y);
@@ -180,7 +187,7 @@ __global__ void __launch_bounds__(256, 2) gdn_scan_kernel(const float* __restric
                                                       const int* __restrict__ positions, const int* __restrict__ seg_start,
                                                       const int* __restrict__ seg_len, const float* __restrict__ dt_bias,
                                                       const float* __restrict__ a_neg, const uint16_t* __restrict__ norm_w, float eps,
-                                                      float* __restrict__ s_pool, float* conv_pool, uint16_t* __restrict__ out) {
+                                                      float* __restrict__ s_pool, float* conv_pool, uint16_t* __restrict__ out, int mode) {
   pdl_launch();
   pdl_wait();
   __shared__ float sqk[2 * GDN_D], red[8], red2[8], sdec[KDA ? GDN_D : 1];
@@ -257,13 +264,14 @@ __global__ void __launch_bounds__(256, 2) gdn_scan_kernel(const float* __restric
     float tot = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += red2[i];
-    if (half == 0) {
+    if (half == 0 && (mode & SCAN_OUT)) {
       const float z = proj[(size_t)r * ldp + h * GDN_D + j];
       const float gate = KDA ? 1.f / (1.f + __expf(-z)) : ssm_silu(z);
       __nv_bfloat16 b = __float2bfloat16_rn(o * rsqrtf(tot / (float)GDN_D + eps) * wj * gate);
       out[(size_t)r * DI + h * GDN_D + j] = *reinterpret_cast<uint16_t*>(&b);
     }
   }
+  if (!(mode & SCAN_STATE)) return;
 #pragma unroll
   for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(sp + (i >> 2) * 128) = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
   ssm_conv_commit(proj, ldp, xoff, conv_pool, C, row_seq, positions, r0 + len - 1, seq, h, (int)gridDim.y);
@@ -272,22 +280,27 @@ __global__ void __launch_bounds__(256, 2) gdn_scan_kernel(const float* __restric
 }  // namespace rx
 
 // One Mamba2 mixer between its two projections: conv, recurrence (pools updated), gated norm.  seg_start / seg_len (device, nseg
-// entries) describe the segments when the host knows them (prefill); pass nullptr and nseg = 0 to have the kernel find them.
+// entries) describe the segments when the host knows them (prefill, commit); pass nullptr and nseg = 0 to have the kernel find them.
+// mode: 3 = rows are final (outputs and pools written), 1 = window record (outputs only; keep proj and xbc for the commit),
+// 2 = commit (the recurrence over the recorded proj / xbc rows of the given segments, pools written; conv and norm are not launched).
 RX_API int rx_ssm_mixer(const void* proj, int ldp, int M, int H, int P, int G, int N, const void* row_seq, const void* positions,
                         const void* seg_start, const void* seg_len, int nseg, const void* conv_w, const void* conv_b, const void* dt_bias,
                         const void* a_neg, const void* d_skip, const void* norm_w, float eps, void* conv_pool, void* ssm_pool, void* xbc,
-                        void* y, void* out_bf16, void* stream) {
+                        void* y, void* out_bf16, void* stream, int mode) {
   using namespace rx;
+  if (mode < 1 || mode > 3) return (int)cudaErrorInvalidValue;
   if (P != SSM_P || N != SSM_N || G <= 0 || H % G || M <= 0) return (int)cudaErrorInvalidValue;
   const int DI = H * P, C = DI + 2 * G * N, xoff = DI, dtoff = DI + C;
   if (ldp < dtoff + H) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
-  launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
-         (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
+  if (mode & SCAN_OUT)
+    launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
+           (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
   launch(ssm_scan_kernel, dim3(seg_start ? nseg : M, H), dim3(256), 0, st, (const float*)xbc, C, (const float*)proj, ldp, xoff, dtoff, M, H, G,
          (const int*)row_seq, (const int*)positions, (const int*)seg_start, (const int*)seg_len, (const float*)dt_bias, (const float*)a_neg,
-         (const float*)d_skip, (float*)ssm_pool, (float*)conv_pool, (float*)y);
-  launch(ssm_gate_norm_kernel, dim3(M, G), dim3(256), 0, st, (const float*)y, (const float*)proj, ldp, DI, G, (const uint16_t*)norm_w, eps,
+         (const float*)d_skip, (float*)ssm_pool, (float*)conv_pool, (float*)y, mode);
+  if (mode & SCAN_OUT)
+    launch(ssm_gate_norm_kernel, dim3(M, G), dim3(256), 0, st, (const float*)y, (const float*)proj, ldp, DI, G, (const uint16_t*)norm_w, eps,
          (uint16_t*)out_bf16);
   return (int)cudaGetLastError();
 }
@@ -296,16 +309,18 @@ RX_API int rx_ssm_mixer(const void* proj, int ldp, int M, int H, int P, int G, i
 // conv, then recurrence + gated norm (pools updated).  Two launches.
 RX_API int rx_gdn_mixer(const void* proj, int ldp, int M, int Hk, int Hv, int D, const void* row_seq, const void* positions, const void* seg_start,
                         const void* seg_len, int nseg, const void* conv_w, const void* conv_b, const void* dt_bias, const void* a_neg,
-                        const void* norm_w, float eps, void* conv_pool, void* s_pool, void* xbc, void* out_bf16, void* stream, int kda) {
+                        const void* norm_w, float eps, void* conv_pool, void* s_pool, void* xbc, void* out_bf16, void* stream, int kda, int mode) {
   using namespace rx;
+  if (mode < 1 || mode > 3) return (int)cudaErrorInvalidValue;
   if (D != GDN_D || Hk <= 0 || Hv % Hk || M <= 0) return (int)cudaErrorInvalidValue;
   const int DI = Hv * D, C = (2 * Hk + Hv) * D, xoff = DI, goff = DI + C;
   if (ldp < goff + Hv + (kda ? Hv * D : Hv)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
-  launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
-         (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
+  if (mode & SCAN_OUT)
+    launch(ssm_conv_kernel, dim3(M, (C + 255) / 256), dim3(256), 0, st, (const float*)proj, ldp, xoff, C, (const int*)row_seq, (const int*)positions,
+           (const uint16_t*)conv_w, (const uint16_t*)conv_b, (const float*)conv_pool, (float*)xbc);
   launch(kda ? gdn_scan_kernel<true> : gdn_scan_kernel<false>, dim3(seg_start ? nseg : M, Hv), dim3(256), 0, st, (const float*)xbc, C, (const float*)proj, ldp, xoff, goff, M, Hk, Hv,
          (const int*)row_seq, (const int*)positions, (const int*)seg_start, (const int*)seg_len, (const float*)dt_bias, (const float*)a_neg,
-         (const uint16_t*)norm_w, eps, (float*)s_pool, (float*)conv_pool, (uint16_t*)out_bf16);
+         (const uint16_t*)norm_w, eps, (float*)s_pool, (float*)conv_pool, (uint16_t*)out_bf16, mode);
   return (int)cudaGetLastError();
 }

@@ -118,32 +118,38 @@ def norm_rot_in(x: torch.Tensor, norm_w, eps: float, suh: torch.Tensor, xr: torc
     _lib.count()
 
 
+# modes of the recurrent mixers (bit 0: write outputs, bit 1: write the pools)
+SCAN_RECORD, SCAN_COMMIT, SCAN_FINAL = 1, 2, 3
+
+
 def ssm_mixer(proj: torch.Tensor, M: int, H: int, P: int, G: int, N: int, row_seq, positions, seg_start, seg_len, nseg: int, conv_w, conv_b, dt_bias,
-              a_neg, d_skip, norm_w, eps: float, conv_pool, ssm_pool, xbc, y, out) -> None:
+              a_neg, d_skip, norm_w, eps: float, conv_pool, ssm_pool, xbc, y, out, mode: int = SCAN_FINAL) -> None:
     """Mamba2 mixer between in_proj and out_proj: `proj` f32 [M, ldp] (z | x | B | C | dt | pad) -> `out` bf16 [M, H*P] (gated, normed);
     the conv and state pools of the rows' sequences advance.  seg_start / seg_len: device int32 segment table or None (found on the device).
-    Three launches (conv, recurrence, gated norm)."""
+    Three launches (conv, recurrence, gated norm).  mode: SCAN_FINAL = rows are final (outputs and pools written); SCAN_RECORD = a window
+    whose rows may be rejected (pools only read; the caller keeps `proj` and `xbc` as the record); SCAN_COMMIT = the recurrence again over
+    the recorded rows of the segments given (seg_len = rows kept), pools written, one launch."""
     L = _lib.load()
     assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and out.dtype == torch.bfloat16
     _lib.check(L.rx_ssm_mixer(proj.data_ptr(), proj.stride(0), M, H, P, G, N, row_seq.data_ptr(), positions.data_ptr(), _lib.ptr(seg_start),
                               _lib.ptr(seg_len), nseg, conv_w.data_ptr(), conv_b.data_ptr(), dt_bias.data_ptr(), a_neg.data_ptr(), d_skip.data_ptr(),
                               norm_w.data_ptr(), eps, conv_pool.data_ptr(), ssm_pool.data_ptr(), xbc.data_ptr(), y.data_ptr(), out.data_ptr(),
-                              _lib.stream_ptr()), "rx_ssm_mixer")
-    _lib.count(3)
+                              _lib.stream_ptr(), mode), "rx_ssm_mixer")
+    _lib.count(1 if mode == SCAN_COMMIT else 3)
 
 
 def gdn_mixer(proj: torch.Tensor, M: int, Hk: int, Hv: int, D: int, row_seq, positions, seg_start, seg_len, nseg: int, conv_w, conv_b, dt_bias, a_neg,
-              norm_w, eps: float, conv_pool, s_pool, xbc, out, kda: bool = False) -> None:
+              norm_w, eps: float, conv_pool, s_pool, xbc, out, kda: bool = False, mode: int = SCAN_FINAL) -> None:
     """Gated delta net mixer between in_proj and out_proj: `proj` f32 [M, ldp] (z | q | k | v | b | a | pad) -> `out` bf16 [M, Hv*D]
     (per-head normed and gated); the conv and state pools of the rows' sequences advance.  Two launches (conv; recurrence + norm).
-    `kda`: per-key-channel decay (a and dt_bias have Hv*D entries) and a sigmoid output gate."""
+    `kda`: per-key-channel decay (a and dt_bias have Hv*D entries) and a sigmoid output gate.  `mode` as in `ssm_mixer`."""
     L = _lib.load()
     assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and out.dtype == torch.bfloat16
     _lib.check(L.rx_gdn_mixer(proj.data_ptr(), proj.stride(0), M, Hk, Hv, D, row_seq.data_ptr(), positions.data_ptr(), _lib.ptr(seg_start),
                               _lib.ptr(seg_len), nseg, conv_w.data_ptr(), conv_b.data_ptr(), dt_bias.data_ptr(), a_neg.data_ptr(), norm_w.data_ptr(),
-                              eps, conv_pool.data_ptr(), s_pool.data_ptr(), xbc.data_ptr(), out.data_ptr(), _lib.stream_ptr(), 1 if kda else 0),
-               "rx_gdn_mixer")
-    _lib.count(2)
+                              eps, conv_pool.data_ptr(), s_pool.data_ptr(), xbc.data_ptr(), out.data_ptr(), _lib.stream_ptr(), 1 if kda else 0,
+                              mode), "rx_gdn_mixer")
+    _lib.count(1 if mode == SCAN_COMMIT else 2)
 
 
 def finish_store(part, S, M, w: Exl3Weight, out: torch.Tensor) -> None:
@@ -219,14 +225,31 @@ def attn_decode_scratch(rows: int, n_q: int, hd: int, max_ctx: int, device="cuda
 
 
 def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_len, scratch, n_q, n_kv, hd, max_ctx, scale, suh, xr, out,
-                status, kv_scale=None) -> None:
+                status, kv_scale=None, max_seq_rows: int = 1, plan=None) -> None:
+    """Split-KV decode / verify-window attention.  `max_seq_rows`: the most adjacent rows one sequence has in this window (1 + drafts); it
+    picks how many MMA tiles a CTA carries so that a sequence's rows share one pass over its K / V (results do not depend on it).
+    `plan`: the window plan from `attn_plan` for these rows and this `max_seq_rows` (one plan serves every layer of a forward); None has
+    the call compute it itself."""
     assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
     rows = q.shape[0]
     L = _lib.load()
     _lib.check(L.rx_attn_decode(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
                                 scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out),
-                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale)), "rx_attn_decode")
-    _lib.count(2)
+                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), int(max_seq_rows), _lib.ptr(plan)), "rx_attn_decode")
+    _lib.count(2 if plan is not None else 3)
+
+
+def attn_plan_buffer(device) -> torch.Tensor:
+    return torch.zeros(_lib.load().rx_attn_plan_ints(), dtype=torch.int32, device=device)
+
+
+def attn_plan(row_seq, ctx_len, n_q: int, n_kv: int, max_seq_rows: int, plan: torch.Tensor) -> None:
+    """The work plan of a decode / verify window: which adjacent rows of a sequence share a CTA, and the flat (block, chunk, kv head) item
+    list the persistent attention kernel walks.  A function of row_seq and ctx_len only: compute once per forward."""
+    L = _lib.load()
+    _lib.check(L.rx_attn_plan(row_seq.data_ptr(), ctx_len.data_ptr(), row_seq.shape[0], n_q, n_kv, int(max_seq_rows), plan.data_ptr(), _lib.stream_ptr()),
+               "rx_attn_plan")
+    _lib.count()
 
 
 def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,

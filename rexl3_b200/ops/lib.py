@@ -80,9 +80,9 @@ def _declare(lib):
         "rx_tp_cand_push": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void]),
         "rx_tp_cand_merge": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, ctypes.c_uint, c_void, c_void, c_void, c_void]),
         "rx_ssm_mixer": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void,
-                                 c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_void, c_void]),
+                                 c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_void, c_void, c_int]),
         "rx_gdn_mixer": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void,
-                                 c_f, c_void, c_void, c_void, c_void, c_void, c_int]),
+                                 c_f, c_void, c_void, c_void, c_void, c_void, c_int, c_int]),
         "rx_dev_alloc": (c_int, [c_ll, ctypes.POINTER(ctypes.c_void_p)]),
         "rx_dev_free": (c_int, [c_void]),
         "rx_exl3_unpack": (c_int, [c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
@@ -101,7 +101,9 @@ def _declare(lib):
         "rx_attn_decode_chunk": (c_int, []),
         "rx_attn_decode_scratch_floats": (c_ll, [c_int, c_int, c_int, c_int]),
         "rx_attn_decode": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
-                                   c_void, c_void, c_void, c_void, c_void, c_void]),
+                                   c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void]),
+        "rx_attn_plan_ints": (c_int, []),
+        "rx_attn_plan": (c_int, [c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
         "rx_attn_prefill_tc": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                        c_int, c_f, c_void, c_void, c_int]),
         "rx_attn_prefill": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,

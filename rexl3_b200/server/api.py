@@ -22,8 +22,8 @@ IGNORED_FIELDS = {"user", "metadata", "store", "service_tier", "stream_options",
                   "repetition_penalty", "n", "response_format", "tool_choice", "parallel_tool_calls", "logprobs", "top_logprobs"}
 CHAT_FIELDS = {"messages", "model", "temperature", "top_p", "top_k", "min_p", "seed", "max_tokens", "max_completion_tokens", "stop", "stream",
                "stream_options", "skip_special_tokens", "return_token_ids", "draft", "prefix_cache", "prompt_logprobs", "tools",
-               "chat_template_kwargs", "max_reasoning_tokens"} | IGNORED_FIELDS
-COMPLETION_FIELDS = (CHAT_FIELDS - {"messages", "tools", "chat_template_kwargs", "max_reasoning_tokens"}) | {"prompt", "echo"}
+               "chat_template_kwargs", "max_reasoning_tokens", "reasoning_effort", "thinking"} | IGNORED_FIELDS
+COMPLETION_FIELDS = (CHAT_FIELDS - {"messages", "tools", "chat_template_kwargs", "max_reasoning_tokens", "reasoning_effort", "thinking"}) | {"prompt", "echo"}
 
 
 class ApiError(Exception):
@@ -71,6 +71,9 @@ class Params:
     tools: list | None = None
     template_kwargs: dict = field(default_factory=dict)
     max_reasoning_tokens: int | None = None
+    reasoning_effort: str | None = None
+    thinking: bool | None = None
+    tool_choice: object = None
     model: str | None = None
 
 
@@ -156,7 +159,22 @@ def parse_params(body: dict, allowed: set, defaults: GenDefaults) -> Params:
                   seed=seed, return_token_ids=bool(body.get("return_token_ids", False)), draft=body.get("draft", True) is not False,
                   prefix_cache=body.get("prefix_cache", True) is not False, prompt_logprobs=pl, tools=tools, template_kwargs=tk,
                   max_reasoning_tokens=_num(body, "max_reasoning_tokens", 0, 1 << 31, integer=True),
+                  reasoning_effort=_effort(body), thinking=_thinking(body), tool_choice=body.get("tool_choice"),
                   model=body.get("model") if isinstance(body.get("model"), str) else None)
+
+
+def _effort(body: dict):
+    v = body.get("reasoning_effort")
+    if v is not None and not isinstance(v, str):
+        raise bad("'reasoning_effort' must be a string", "reasoning_effort")
+    return v
+
+
+def _thinking(body: dict):
+    v = body.get("thinking")
+    if v is not None and not isinstance(v, bool):
+        raise bad("'thinking' must be a boolean", "thinking")
+    return v
 
 
 def parse_messages(body: dict) -> list:

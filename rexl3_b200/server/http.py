@@ -19,19 +19,30 @@ from ..engine import Request
 from ..sampling import seed_for
 from . import api
 from .runtime import EngineHandle
+from . import budget, formats
 from .text import ChatFormat, ReasoningSplitter, StopMatcher, TemplateRefused, extract_tool_calls
 from .tokenizer import Tok
 
 
 class AppState:
     def __init__(self, handle: EngineHandle, tok: Tok, fmt: ChatFormat, model_name: str, max_model_len: int, aliases=(), defaults=None,
-                 default_max_tokens: int = 512, fingerprint: str = "rexl3-b200", max_body_bytes: int = 64 << 20, info: dict | None = None):
+                 default_max_tokens: int = 512, fingerprint: str = "rexl3-b200", max_body_bytes: int = 64 << 20, info: dict | None = None,
+                 limits=None, default_thinking: str = "template", default_effort: str | None = None):
         self.handle, self.tok, self.fmt = handle, tok, fmt
         self.model_name, self.aliases = model_name, set(aliases)
         self.max_model_len, self.default_max_tokens = max_model_len, default_max_tokens
         self.defaults = defaults or api.GenDefaults()
         self.fingerprint, self.max_body_bytes = fingerprint, max_body_bytes
         self.info = info or {}
+        # request budgets (body, JSON nodes / depth, rendered prompt, preparation slots, priced tokenizer memory)
+        self.limits = limits or budget.Limits.for_window(max_model_len)
+        self.max_body_bytes = min(self.max_body_bytes, self.limits.body_bytes)
+        self.prep_gate = budget.PreparationGate(self.limits.preparation_concurrency, self.limits.preparation_queue)
+        self.tok_gate = budget.TokenizerGate(self.limits.processing_reserve_bytes, self.limits.tokenizer_wait_s)
+        # what a chat request that names neither the thinking switch nor an effort level gets ("off" | "template"), and an optional default level
+        self.default_thinking, self.default_effort = default_thinking, default_effort
+        self.family = isinstance(fmt, formats.FamilyFormat)
+        self.role_stops = tuple(fmt.reply_role_stops(tok)) if self.family else ()
 
 
 def _err(e: api.ApiError) -> JSONResponse:
@@ -44,9 +55,28 @@ async def _json_body(request: HttpRequest, st: AppState) -> dict:
     if len(raw) > st.max_body_bytes:
         raise api.ApiError(413, "request body too large", code="body_too_large")
     try:
-        return json.loads(raw)
+        body = json.loads(raw)
     except (json.JSONDecodeError, UnicodeDecodeError, RecursionError):
         raise api.bad("the request body is not valid JSON")
+    try:
+        budget.check_json(body, st.limits)
+    except budget.BudgetRefused as e:
+        raise _budget_error(e)
+    return body
+
+
+def _budget_error(e: "budget.BudgetRefused") -> api.ApiError:
+    return api.ApiError(e.status, str(e), "invalid_request_error" if e.status == 413 else "rate_limit_error", e.code, retry_after=e.retry_after)
+
+
+def _encode(st: AppState, text: str) -> list:
+    """Tokenize under the request budgets: the rendered-size cap, then the priced tokenizer memory."""
+    try:
+        n = budget.check_rendered(text, st.limits)
+        with st.tok_gate.charge(n):
+            return st.tok.encode(text)
+    except budget.BudgetRefused as e:
+        raise _budget_error(e)
 
 
 def _check_model(st: AppState, p: api.Params) -> None:
@@ -71,15 +101,21 @@ def _make_request(st: AppState, ids: list, p: api.Params, rid: str, prompt_text:
     samp = p.sampling
     if p.seed is None and samp.temperature > 0:
         samp = samp.with_seed(seed_for(ids, 0))
-    stop_ids = tuple(st.tok.eos_ids)
+    stop_ids = tuple(st.tok.eos_ids) + tuple(t for t in st.role_stops if t not in st.tok.eos_ids)     # a generated role token opens a new turn
     req = Request(rid, ids, max_new, samp, stop_ids, draft=p.draft, prefix_cache=p.prefix_cache)
     if getattr(p, "max_reasoning_tokens", None) is not None and st.fmt.think_close:
         # reasoning budget: the engine forces the closing tag once that many tokens were spent inside the thinking block
         req.reasoning_budget = int(p.max_reasoning_tokens)
         req.think_close_ids = tuple(st.tok.encode(st.fmt.think_close))
         req.think_open_ids = tuple(st.tok.encode(st.fmt.think_open)) if st.fmt.think_open else ()
-        req.reasoning_open = bool(st.fmt.think_open) and prompt_text.rstrip().endswith(st.fmt.think_open)
+        req.reasoning_open = _starts_in_reasoning(st, prompt_text)
     return req
+
+
+def _starts_in_reasoning(st: AppState, prompt_text: str) -> bool:
+    if st.family:
+        return st.fmt.starts_in_reasoning(prompt_text)
+    return bool(st.fmt.think_open) and prompt_text.rstrip().endswith(st.fmt.think_open)
 
 
 class _Reply:
@@ -88,10 +124,10 @@ class _Reply:
     def __init__(self, st: AppState, p: api.Params, chat: bool, prompt_text: str = ""):
         self.dec = st.tok.stream(p.skip_special)
         self.stop = StopMatcher(p.stop)
-        self.reason = ReasoningSplitter(st.fmt.think_open, st.fmt.think_close, started_inside=prompt_text.rstrip().endswith(st.fmt.think_open)) if chat else None
+        self.reason = ReasoningSplitter(st.fmt.think_open, st.fmt.think_close, started_inside=_starts_in_reasoning(st, prompt_text)) if chat else None
         self.ids, self.text, self.reasoning = [], "", ""
         self.stopped = False
-        self.eos = set(st.tok.eos_ids)
+        self.eos = set(st.tok.eos_ids) | set(st.role_stops)
 
     def push(self, ids):
         """-> (content delta, reasoning delta)"""
@@ -208,19 +244,40 @@ def build_app(st: AppState) -> Starlette:
             return _err(e)
 
     def render_chat(body, p):
+        """-> (prompt text, token ids, note for the client or None)"""
         msgs = api.parse_messages(body)
+        kwargs, note = p.template_kwargs, None
+        if st.family:
+            refusal = st.fmt.check_media(msgs)
+            if refusal:
+                raise api.bad(refusal, "messages", "unsupported_media")
+            try:
+                kwargs, note = formats.apply_reasoning_controls(st.fmt.caps, p.template_kwargs, effort=p.reasoning_effort, thinking=p.thinking,
+                                                                default_thinking=st.default_thinking, default_effort=st.default_effort)
+            except formats.ControlRefused as e:
+                raise api.bad(str(e), e.param, "reasoning_control")
+        elif p.reasoning_effort is not None or p.thinking is not None:
+            raise api.bad("this server's chat format declares no reasoning controls", "reasoning_effort", "reasoning_control")
         try:
-            text = st.fmt.render(msgs, tools=p.tools, add_generation_prompt=True, **p.template_kwargs)
+            text = st.fmt.render(msgs, tools=p.tools, add_generation_prompt=True, **kwargs)
         except TemplateRefused as e:
             raise api.bad(str(e), "messages", "template_error")
-        return text, st.tok.encode(text)
+        return text, _encode(st, text), note
+
+    def split_tools(text, p):
+        if not p.tools:
+            return text, []
+        if st.family:
+            return st.fmt.split_tools(text, p.tools, p.tool_choice)
+        return extract_tool_calls(text, st.fmt.tool_open, st.fmt.tool_close)
 
     async def render(request):
         try:
             body = await _json_body(request, st)
             p = api.parse_params(body, api.CHAT_FIELDS, st.defaults)
-            text, ids = render_chat(body, p)
-            return JSONResponse({"prompt": text, "token_ids": ids, "count": len(ids)})
+            with st.prep_gate:
+                text, ids, note = render_chat(body, p)
+            return JSONResponse({"prompt": text, "token_ids": ids, "count": len(ids)}, headers={"X-Rexl3-Note": note} if note else None)
         except api.ApiError as e:
             return _err(e)
 
@@ -230,16 +287,22 @@ def build_app(st: AppState) -> Starlette:
             p = api.parse_params(body, api.CHAT_FIELDS if chat else api.COMPLETION_FIELDS, st.defaults)
             _check_model(st, p)
             _ready_or_503(st)
-            if chat:
-                prompt_text, ids = render_chat(body, p)
-            else:
-                pr = body.get("prompt")
-                if isinstance(pr, list) and pr and all(isinstance(t, int) and not isinstance(t, bool) for t in pr):
-                    prompt_text, ids = "", list(pr)
-                elif isinstance(pr, str):
-                    prompt_text, ids = pr, st.tok.encode(pr)
-                else:
-                    raise api.bad("'prompt' must be a string or a list of token ids", "prompt")
+            note = None
+            try:
+                with st.prep_gate:
+                    if chat:
+                        prompt_text, ids, note = render_chat(body, p)
+                    else:
+                        pr = body.get("prompt")
+                        if isinstance(pr, list) and pr and all(isinstance(t, int) and not isinstance(t, bool) for t in pr):
+                            prompt_text, ids = "", list(pr)
+                        elif isinstance(pr, str):
+                            prompt_text, ids = pr, _encode(st, pr)
+                        else:
+                            raise api.bad("'prompt' must be a string or a list of token ids", "prompt")
+            except budget.BudgetRefused as e:
+                raise _budget_error(e)
+            note_headers = {"X-Rexl3-Note": note} if note else None
             rid = api.new_id("chatcmpl" if chat else "cmpl")
             req = _make_request(st, ids, p, rid, prompt_text if chat else "")
             try:
@@ -254,9 +317,9 @@ def build_app(st: AppState) -> Starlette:
                 reason, usage = await _collect(st, ticket, reply)
                 u = api.usage_object(usage, len(st.tok.encode(reply.reasoning)) if reply.reasoning else 0)
                 if chat:
-                    text, calls = extract_tool_calls(reply.text, st.fmt.tool_open, st.fmt.tool_close) if p.tools else (reply.text, [])
+                    text, calls = split_tools(reply.text, p)
                     return JSONResponse(api.chat_completion(rid, model, text, reply.reasoning, calls, reason, u, st.fingerprint,
-                                                            reply.ids if p.return_token_ids else None))
+                                                            reply.ids if p.return_token_ids else None), headers=note_headers)
                 return JSONResponse(api.text_completion(rid, model, reply.text, reason, u, st.fingerprint))
 
             async def gen():
@@ -305,7 +368,7 @@ def build_app(st: AppState) -> Starlette:
                     ticket.closed = True
                     st.handle.cancel(ticket.id)    # client gone (or done): free the slot
 
-            return StreamingResponse(gen(), media_type="text/event-stream", headers={"Cache-Control": "no-cache", "X-Accel-Buffering": "no"})
+            return StreamingResponse(gen(), media_type="text/event-stream", headers={"Cache-Control": "no-cache", "X-Accel-Buffering": "no", **(note_headers or {})})
         except api.ApiError as e:
             return _err(e)
 

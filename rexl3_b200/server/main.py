@@ -59,6 +59,17 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--exit-after", type=int, default=10)
     p.add_argument("--heartbeat-stale-secs", type=float, default=60)
     p.add_argument("--max-body-mib", type=int, default=64)
+    p.add_argument("--chat-format", default=None, help="chat format id (default: from the model's config.json; see rexl3_b200.server.formats)")
+    p.add_argument("--default-thinking", choices=("off", "template"), default="off",
+                   help="what a chat request that names neither the thinking switch nor an effort level gets: 'off' inserts the switch set to "
+                        "false where the family's switch closes the reasoning block, 'template' leaves it to the template's default")
+    p.add_argument("--default-reasoning-effort", default=None, help="effort level a chat request that names none gets")
+    p.add_argument("--max-rendered-prompt-mib", type=float, default=None, help="cap on a rendered prompt (default: 16 bytes per token of the window, at least 1)")
+    p.add_argument("--max-json-nodes", type=int, default=300_000)
+    p.add_argument("--max-json-depth", type=int, default=128)
+    p.add_argument("--preparation-concurrency", type=int, default=2)
+    p.add_argument("--preparation-queue", type=int, default=64)
+    p.add_argument("--processing-reserve-mib", type=int, default=None, help="memory the tokenizer stage may price at once (default: derived)")
     p.add_argument("--no-graphs", action="store_true")
     p.add_argument("--device-sampler", action="store_true", help="sample and accept drafts on the GPU (verify kernel); only token ids come back")
     p.add_argument("--version", action="store_true")
@@ -212,7 +223,13 @@ def build(args):
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args, model), device_sampler=args.device_sampler,
                           spill=_spill_store(args, prefix), arbiter=_arbiter(args))
     tok = load_tokenizer(folder, vocab)
-    fmt = ChatFormat.from_dir(folder)
+    from . import formats
+    try:
+        fmt = formats.open_format(folder, getattr(args, "chat_format", None))
+    except formats.FormatRefused as e:
+        raise SystemExit(f"rexl3-serve: {e}")
+    info["chat_format"] = fmt.id
+    info["reasoning"] = fmt.caps.describe()
     return make, tok, fmt, name, info
 
 
@@ -339,8 +356,31 @@ def make_app(args, metrics: Metrics | None = None):
     defaults = api.GenDefaults()
     if args.model and os.path.exists(os.path.join(args.model, "generation_config.json")):
         defaults = api.GenDefaults.from_dict(json.load(open(os.path.join(args.model, "generation_config.json"))))
+    from . import budget, formats
+    limits = budget.Limits.for_window(args.max_model_len)
+    limits.body_bytes = args.max_body_mib << 20
+    limits.json_nodes, limits.json_depth = args.max_json_nodes, args.max_json_depth
+    limits.preparation_concurrency, limits.preparation_queue = args.preparation_concurrency, args.preparation_queue
+    if args.max_rendered_prompt_mib is not None:
+        limits.rendered_bytes = int(args.max_rendered_prompt_mib * (1 << 20))
+    limits.processing_reserve_bytes = (args.processing_reserve_mib << 20) if args.processing_reserve_mib is not None else limits.derived_reserve()
+    if args.processing_reserve_mib is None:
+        raw = max(min(limits.body_bytes, limits.total_bytes) * 16, limits.json_nodes * 128) * limits.preparation_concurrency
+        limits.processing_reserve_bytes = max(limits.processing_reserve_bytes, raw)
+    try:
+        limits.validate()
+    except ValueError as e:
+        raise SystemExit(f"rexl3-serve: {e}")
+    if args.default_reasoning_effort is not None:
+        caps = fmt.caps
+        ok = caps.reasons and (caps.level(args.default_reasoning_effort) is not None
+                               or (caps.effort_var and args.default_reasoning_effort in (caps.extra_vars.get(caps.effort_var) or [])))
+        if not ok:
+            raise SystemExit(f"rexl3-serve: --default-reasoning-effort {args.default_reasoning_effort}: this model takes "
+                             f"{', '.join(caps.level_names()) or 'no effort levels'}")
     st = AppState(handle, tok, fmt, name, args.max_model_len, args.model_alias, defaults, args.default_max_tokens,
-                  fingerprint=f"rexl3-b200-{name}", max_body_bytes=args.max_body_mib << 20, info=info)
+                  fingerprint=f"rexl3-b200-{name}", max_body_bytes=args.max_body_mib << 20, info=info, limits=limits,
+                  default_thinking=args.default_thinking, default_effort=args.default_reasoning_effort)
     return build_app(st), handle
 
 

@@ -89,7 +89,7 @@ def test_engine_greedy_stream_matches_reference_with_graphs(name):
     m = hybrid.HybridGPU(w, num_pages=32, max_rows=64, max_seqs=4, max_blocks_per_seq=6, max_prefill_rows=256)
     be = HybridGpuBackend(m, max_slots=4)
     eng = Engine(be, None, window_rows=16, prefill_chunk=48, spec="copy")
-    assert not eng.can_rollback and eng.prefix is None
+    assert eng.can_rollback and eng.prefix is None
     rng = np.random.default_rng(3)
     prompts = {"a": rng.integers(0, cfg.vocab, size=100).tolist(), "b": rng.integers(0, cfg.vocab, size=5).tolist()}
     n_new, exact = 12, 0
@@ -115,3 +115,72 @@ def test_engine_greedy_stream_matches_reference_with_graphs(name):
             lg = ref.forward_seq(si, [t], pos)[0]
             pos += 1
     assert exact >= n_new, "most steps have a clear winner and must agree exactly"
+
+
+@pytest.fixture(scope="module", params=["test-hybrid", "test-hybrid-gdn", "test-hybrid-kda"])
+def make_hybrid_backend(request):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.engine.gpu_backend import HybridGpuBackend
+    cfg, w, hybrid = _setup(seed=6, name=request.param)
+    model = hybrid.HybridGPU(w, num_pages=96, max_rows=64, max_seqs=8, max_blocks_per_seq=8, max_prefill_rows=512)
+
+    def make():
+        # one model, fresh bookkeeping: KV pages are overwritten and a row at position 0 starts from a zero state whatever the pools hold
+        return HybridGpuBackend(model, max_slots=8, state_snapshots=True)
+    make.vocab = cfg.vocab
+    return make
+
+
+@pytest.mark.parametrize("check", ["row_invariance", "serial_batched_equals_solo", "drafted_equals_serial", "chunked_prefill_equals_whole",
+                                   "rollback_equals_replay", "cached_equals_cold"])
+def test_exactness_on_device_with_record_and_commit(make_hybrid_backend, check):
+    """The five exactness checks and cached == cold over the recurrent families: draft rows run in record mode, rejected rows leave no trace
+    in the pools, and a prefix hit restores the state snapshot taken where a prefill slice ended."""
+    from rexl3_b200.engine import harness
+    assert getattr(harness, check)(make_hybrid_backend, make_hybrid_backend.vocab) is None
+
+
+def test_record_then_commit_leaves_the_pools_as_a_direct_run_does():
+    """Model level: a 2-sequence window of 4 rows each in record mode writes nothing; committing (2, 4) rows gives the pools, bit for bit,
+    that feeding exactly those rows as final rows gives."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    for name in ("test-hybrid", "test-hybrid-gdn", "test-hybrid-kda"):
+        cfg, w, hybrid = _setup(seed=9, name=name)
+        m = hybrid.HybridGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+        K = m.K
+        m.enable_record(16)
+        rng = np.random.default_rng(1)
+        bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+        bt[0, 0], bt[1, 0] = 3, 7
+        # positions 0..4 of both sequences as final rows, so the pools hold a real state
+        def rows(seq_pos):     # noqa: E306
+            return (_i32(rng.integers(0, cfg.vocab, size=len(seq_pos)).tolist()), _i32([p for _, p in seq_pos]),
+                    _i32([int(bt[s, 0]) * 64 + p for s, p in seq_pos]), _i32([s for s, _ in seq_pos]), _i32([p + 1 for _, p in seq_pos]))
+        warm = [(0, p) for p in range(5)] + [(1, p) for p in range(5)]
+        m.forward_rows(*rows(warm), bt, want_logits=False)
+        before = {li: (m.conv_pool[li].clone(), m.ssm_pool[li].clone()) for li in m.ssm_pool}
+        win = [(0, p) for p in range(5, 9)] + [(1, p) for p in range(5, 9)]
+        a = rows(win)
+        m.ssm_mode = K.SCAN_RECORD
+        lg_rec = m.forward_rows(*a, bt).clone()
+        m.ssm_mode = K.SCAN_FINAL
+        for li in m.ssm_pool:
+            assert torch.equal(m.conv_pool[li], before[li][0]) and torch.equal(m.ssm_pool[li], before[li][1]), (name, li)
+        m.commit_rows(8, a[3], a[1], _i32([0, 4]), _i32([2, 4]), 2)
+        torch.cuda.synchronize()
+        m.check()
+        got = {li: (m.conv_pool[li].clone(), m.ssm_pool[li].clone()) for li in m.ssm_pool}
+        # the same kept rows as final rows from the same starting pools
+        for li in m.ssm_pool:
+            m.conv_pool[li].copy_(before[li][0])
+            m.ssm_pool[li].copy_(before[li][1])
+        keep = [0, 1, 4, 5, 6, 7]
+        idx = torch.tensor(keep, device="cuda")
+        lg_dir = m.forward_rows(*[t[idx].contiguous() for t in a], bt)
+        torch.cuda.synchronize()
+        m.check()
+        assert torch.equal(lg_dir, lg_rec[idx]), name
+        for li in m.ssm_pool:
+            assert torch.equal(m.conv_pool[li][:2], got[li][0][:2]) and torch.equal(m.ssm_pool[li][:2], got[li][1][:2]), (name, li)

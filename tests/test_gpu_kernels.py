@@ -218,10 +218,14 @@ def test_paged_attention_decode_and_prefill(K, hd, n_q, n_kv):
     scr_w = K.attn_decode_scratch(W, n_q, hd, max_blocks * 64)
     out_w = torch.empty(W, n_q * hd, dtype=torch.bfloat16, device="cuda")
     xr_w = torch.empty(W, n_q * hd, dtype=torch.float16, device="cuda")
-    K.attn_decode(tk, tv, qw, bt, torch.tensor(wseq, dtype=torch.int32, device="cuda"), torch.tensor(wctx, dtype=torch.int32, device="cuda"),
-                  scr_w, n_q, n_kv, hd, max_blocks * 64, 1 / math.sqrt(hd), suh, xr_w, out_w, status)
-    torch.cuda.synchronize()
-    K.check_status(status)
+    outs = []
+    for msr in (1, 5, 9):        # one, two and three MMA tiles per CTA: the same bits
+        K.attn_decode(tk, tv, qw, bt, torch.tensor(wseq, dtype=torch.int32, device="cuda"), torch.tensor(wctx, dtype=torch.int32, device="cuda"),
+                      scr_w, n_q, n_kv, hd, max_blocks * 64, 1 / math.sqrt(hd), suh, xr_w, out_w, status, max_seq_rows=msr)
+        torch.cuda.synchronize()
+        K.check_status(status)
+        outs.append((out_w.clone(), xr_w.clone()))
+    assert all(torch.equal(o, outs[0][0]) and torch.equal(x, outs[0][1]) for o, x in outs[1:])
     scr_1 = K.attn_decode_scratch(1, n_q, hd, max_blocks * 64)
     for r in range(W):
         out_1 = torch.empty(1, n_q * hd, dtype=torch.bfloat16, device="cuda")
