@@ -117,6 +117,9 @@ class Engine:
         self.counters = dict(rounds=0, rows=0, prefill_tokens=0, decode_tokens=0, drafted=0, accepted=0, cached_tokens=0, requests=0,
                              finished=0, errors=0, spilled_blocks=0, unspilled_blocks=0)
         self.phase_ns = dict(draft=0, verify=0, commit=0, prefill=0)
+        # speculation by draft position (0 = the first draft after the anchor): drafts offered to a window, drafts whose row was reached
+        # (every earlier draft accepted), drafts accepted; the per-position acceptance curve is accepted / reached
+        self.spec_pos = dict(offered=[0] * max(1, max_drafts), reached=[0] * max(1, max_drafts), accepted=[0] * max(1, max_drafts))
         self._window_start = 0         # rotation of the decode window over the active streams when they outnumber its rows
         self.pause_decode = False      # hold decode rounds (used while a benchmark fills the batch with prompts)
 
@@ -380,6 +383,8 @@ class Engine:
             raise BackendError("backend returned a window of the wrong shape", fatal=False)
         self.counters["rounds"] += 1
         self.counters["rows"] += sum(len(q.tokens) for q in reqs)
+        self.counters["round_streams"] = self.counters.get("round_streams", 0) + len(reqs)
+        self.counters["round_draft_streams"] = self.counters.get("round_draft_streams", 0) + sum(1 for p in proposals if p)
         # 5. sample every row at its own position, accept the matching prefix, commit or finish
         for si, (s, p, out) in enumerate(zip(active, proposals, rows)):
             base = len(s.tokens)
@@ -404,6 +409,11 @@ class Engine:
                 from ..spec.arbiter import NONE, Choice
                 self.arbiter.observe(s.req.id, Choice(choices[si].kind, len(p)) if (choices[si] is not None and p) else NONE, a)
             if p:
+                sp = self.spec_pos
+                for j in range(min(len(p), len(sp["offered"]))):
+                    sp["offered"][j] += 1
+                    sp["reached"][j] += 1 if j <= a else 0
+                    sp["accepted"][j] += 1 if j < a else 0
                 s.stats.update(len(p), a)
                 s.drafted += len(p)
                 s.accepted += a

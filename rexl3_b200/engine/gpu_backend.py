@@ -614,6 +614,11 @@ class HybridGpuBackend(DenseGpuBackend):
         self._flush_commits()
         return super().score_last(slot, tokens, chunk)
 
+    def stats(self):
+        st = super().stats()
+        st["commit_replays"] = self.commit_replays
+        return st
+
     def _capture(self, M, count, bucket):
         g = super()._capture(M, count, bucket)
         # a recorded window stores nothing, so running it twice is harmless; one that stores its state must not be replayed for the same step

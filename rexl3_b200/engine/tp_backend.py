@@ -184,6 +184,7 @@ class DenseTpBackend(DenseGpuBackend):
         self.ex.x_bt_h, self.ex.x_bt = self.h_bt, self.d_bt
         self.ex.x_pf_h, self.ex.x_pf = self.h_pf, self.d_pf
         self.ctrl_bytes = 0
+        self.commands = 0
 
     # ---- control plane
     def _send(self, op, M=0, count=0, bucket=0, nseq=0, max_qlen=0, last_rows=()):
@@ -212,6 +213,12 @@ class DenseTpBackend(DenseGpuBackend):
         if not fits:
             dist.broadcast(torch.from_numpy(np.ascontiguousarray(payload)), src=0, group=self.ex.ctrl)
         self.ctrl_bytes += 4 * (HEAD + payload.size)
+        self.commands += 1
+
+    def stats(self):
+        st = super().stats()
+        st.update(tp_ranks=dist.get_world_size(group=self.ex.ctrl), ctrl_bytes=self.ctrl_bytes, tp_commands=self.commands)
+        return st
 
     def _announce_window(self, M, count, bucket):
         self._send(OP_WINDOW, M, count, bucket, 0, getattr(self.m, "window_seq_rows", 1))

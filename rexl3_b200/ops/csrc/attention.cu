@@ -186,6 +186,107 @@ __device__ __forceinline__ void attn_step(const uint32_t (&qa)[HD / 16][4], uint
 }
 
 
+// The decode kernel's step: like attn_step for MT tiles at once over the same 16 keys.  Each K / V fragment is fetched from shared memory once
+// and feeds every tile's MMA; a row's running maximum is only moved when the new scores exceed it by more than 2^8 (the accumulators are then
+// rescaled; otherwise the stale maximum stays and P holds values up to 256, well inside bf16 / fp16 range), so the 64 multiplies of the
+// rescale are skipped for most pages.  `ntiles` (uniform) = tiles that hold a live row.
+template <int HD, int MT, bool F16>
+__device__ __forceinline__ void attn_step_mt(const uint32_t (&qa)[MT][HD / 16][4], uint32_t ksm, uint32_t vsm, int key0, const int (&valid)[MT][2],
+                                             int ntiles, float scale_log2, float (&m)[MT][2], float (&l)[MT][2], float (&o)[MT][HD / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  float s[MT][2][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) { s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f; }
+  {
+    const int mi = lane >> 3;
+    const int key = key0 + (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(kv_chunk_addr<HD>(ksm, key, ks * 2 + (mi & 1)), b0, b1, b2, b3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if (mt < ntiles) {
+          if constexpr (F16) { mma_f16(s[mt][0], qa[mt][ks], b0, b1); mma_f16(s[mt][1], qa[mt][ks], b2, b3); }
+          else { mma_bf16(s[mt][0], qa[mt][ks], b0, b1); mma_bf16(s[mt][1], qa[mt][ks], b2, b3); }
+        }
+      }
+    }
+  }
+  uint32_t pa[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    if (mt < ntiles) {
+      // mask + row max
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int kk = j * 8 + 2 * (lane & 3) + (e & 1);
+          const float v = (kk < valid[mt][e >> 1]) ? s[mt][j][e] * scale_log2 : -INFINITY;
+          s[mt][j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float corr[2];
+      bool moved = false;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        corr[r] = 1.f;
+        if (mx[r] > m[mt][r] + 8.f) {              // also the first valid keys of a row (m = -inf)
+          corr[r] = (m[mt][r] == -INFINITY) ? 1.f : exp2f(m[mt][r] - mx[r]);
+          m[mt][r] = mx[r];
+          moved = moved || corr[r] != 1.f;
+        }
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float p[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float mm = m[mt][e >> 1];
+          p[e] = (mm == -INFINITY) ? 0.f : exp2f(s[mt][j][e] - mm);
+          rs[e >> 1] += p[e];
+        }
+        pa[mt][j * 2 + 0] = F16 ? pack_f16(p[0], p[1]) : pack_bf16(p[0], p[1]);
+        pa[mt][j * 2 + 1] = F16 ? pack_f16(p[2], p[3]) : pack_bf16(p[2], p[3]);
+      }
+      if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) l[mt][r] *= corr[r];
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d) {
+          o[mt][d][0] *= corr[0]; o[mt][d][1] *= corr[0]; o[mt][d][2] *= corr[1]; o[mt][d][3] *= corr[1];
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) l[mt][r] += rs[r];
+    }
+  }
+  {
+    const int mi = lane >> 3;
+    const int key = key0 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(kv_chunk_addr<HD>(vsm, key, dp * 2 + (mi >> 1)), b0, b1, b2, b3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if (mt < ntiles) {
+          if constexpr (F16) { mma_f16(o[mt][2 * dp], pa[mt], b0, b1); mma_f16(o[mt][2 * dp + 1], pa[mt], b2, b3); }
+          else { mma_bf16(o[mt][2 * dp], pa[mt], b0, b1); mma_bf16(o[mt][2 * dp + 1], pa[mt], b2, b3); }
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ decode (split-KV)
 // Bytes of the decode kernel's main shared region: the K / V stages (and the FP8 expansion tiles) while pages stream, the per-warp partial
 // outputs [4 MT][16][HD] f32 once they are done.  The barriers and the per-warp (max, sum) pairs sit behind it.
@@ -294,6 +395,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
     const int k_begin = chunk * DEC_CHUNK;
     const int k_end_max = min(ctx_max, k_begin + DEC_CHUNK);
     const int npages = (k_end_max - k_begin + PAGE - 1) / PAGE;
+    const int ntiles = (nblk * G + 15) >> 4;            // tiles that hold a live row
     const int* bt = block_table + (size_t)seq * max_blocks;
     if (threadIdx.x == 0) {
       fence_proxy_async();                           // the previous item's merge wrote this memory with plain stores
@@ -357,16 +459,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
         __syncthreads();
       }
       if (any) {
+        int valid[MT][2];                                           // per tile row: keys of this 16-key slice the row may see
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          if (mt * 16 >= nblk * G) break;                           // uniform: no live row in this tile
-          // per tile row: keys of this 16-key slice the row may see
-          if constexpr (FP8)
-            attn_step<HD, 16, true>(qa[mt], smem_u32(conv), smem_u32(conv + T16), key0, kend[mt][0] - kpos, kend[mt][1] - kpos, scale_log2, m[mt], l[mt], o[mt]);
-          else
-            attn_step<HD, 16>(qa[mt], smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, kend[mt][0] - kpos, kend[mt][1] - kpos,
-                              scale_log2, m[mt], l[mt], o[mt]);
-        }
+        for (int mt = 0; mt < MT; ++mt) { valid[mt][0] = kend[mt][0] - kpos; valid[mt][1] = kend[mt][1] - kpos; }
+        if constexpr (FP8) attn_step_mt<HD, MT, true>(qa, smem_u32(conv), smem_u32(conv + T16), key0, valid, ntiles, scale_log2, m, l, o);
+        else attn_step_mt<HD, MT, false>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid, ntiles, scale_log2, m, l, o);
       }
       __syncthreads();
     }

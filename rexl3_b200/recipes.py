@@ -33,6 +33,10 @@ class Resolved:
     readiness_timeout_s: int = 600
     http_host: str = "127.0.0.1"
     http_port: int = 8000
+    kind: str = "single"            # "single" | "tp" (one process per GPU under torch.distributed.run)
+    ranks: int = 1
+    rendezvous_port: int = 29540
+    model_dir: str | None = None
 
 
 def _read_json(path):
@@ -96,7 +100,8 @@ def resolve(root: str, family: str, model: str, site: dict, version: str | None 
         if unknown:
             raise RecipeError(f"flags this serving binary does not know: {unknown}")
     return Resolved(doc["runtime_id"], version, name, argv, dict(prof.get("env", {})), dict(prof.get("capabilities", {})), prof.get("smoke_request"),
-                    int(prof.get("readiness_timeout_s", 600)), str(fields.get("http_host", "127.0.0.1")), int(fields.get("http_port", 8000)))
+                    int(prof.get("readiness_timeout_s", 600)), str(fields.get("http_host", "127.0.0.1")), int(fields.get("http_port", 8000)),
+                    str(prof.get("kind", "single")), int(prof.get("ranks", 1)), int(prof.get("rendezvous_port", 29540)), fields.get("model_dir"))
 
 
 def seal(vdir: str) -> dict:

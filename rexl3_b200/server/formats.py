@@ -396,7 +396,8 @@ def apply_reasoning_controls(caps: ReasoningCapabilities, kwargs: dict, *, effor
 class FamilyFormat(ChatFormat):
     """A family's conventions bound to a template.  Defaults: ChatML framing, `<think>` blocks, JSON tool calls, text only."""
     id = "chatml"
-    names: tuple = ("rexl3_dense", "rexl3_hybrid", "rexl3_moe", "rexl3_mla_moe", "LlamaForCausalLM", "llama", "Qwen3ForCausalLM", "qwen3", "Qwen3MoeForCausalLM",
+    names: tuple = ("rexl3_dense", "rexl3_hybrid", "rexl3_moe", "rexl3_mla_moe", "Rexl3DenseForCausalLM", "Rexl3HybridForCausalLM", "Rexl3MoEForCausalLM",
+                    "Rexl3MlaMoEForCausalLM", "LlamaForCausalLM", "llama", "Qwen3ForCausalLM", "qwen3", "Qwen3MoeForCausalLM",
                     "qwen3_moe")
     tool = JSON_TOOL_SYNTAX
     role_stop_tokens: tuple = ()          # texts that, generated as ONE token, open a new turn and so end the reply

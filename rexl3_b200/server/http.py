@@ -203,7 +203,13 @@ def build_app(st: AppState) -> Starlette:
 
     async def metrics(request):
         from ..utils import loadstats
-        return PlainTextResponse(st.handle.metrics.render() + loadstats.render(), media_type="text/plain; version=0.0.4")
+        m = st.handle.metrics
+        m.set("tokenizer_gate_bytes_in_use", st.tok_gate.in_use())
+        m.set("tokenizer_gate_bytes_capacity", st.tok_gate.capacity)
+        m.set("tokenizer_gate_waited_total", st.tok_gate.waited)
+        m.set("tokenizer_gate_refused_total", st.tok_gate.refused)
+        m.set("preparation_refused_total", st.prep_gate.refused)
+        return PlainTextResponse(m.render() + loadstats.render(), media_type="text/plain; version=0.0.4")
 
     async def tokenize(request):
         try:
@@ -282,6 +288,8 @@ def build_app(st: AppState) -> Starlette:
             return _err(e)
 
     async def run(request, chat: bool):
+        import time as _time
+        t_in = _time.perf_counter()
         try:
             body = await _json_body(request, st)
             p = api.parse_params(body, api.CHAT_FIELDS if chat else api.COMPLETION_FIELDS, st.defaults)
@@ -305,6 +313,7 @@ def build_app(st: AppState) -> Starlette:
             note_headers = {"X-Rexl3-Note": note} if note else None
             rid = api.new_id("chatcmpl" if chat else "cmpl")
             req = _make_request(st, ids, p, rid, prompt_text if chat else "")
+            st.handle.metrics.observe("request_preprocessing_seconds", _time.perf_counter() - t_in)
             try:
                 ticket = st.handle.submit(req, asyncio.get_running_loop())
             except OverflowError:
@@ -346,6 +355,7 @@ def build_app(st: AppState) -> Starlette:
                         elif msg[0] == "done":
                             c, r = reply.finish()
                             reason = "stop" if reply.stopped else msg[1]
+                            st.handle.metrics.inc("sse_terminal_total", kind=str(reason))
                             if chat:
                                 if r:
                                     yield _sse(api.chat_chunk(rid, model, {"reasoning_content": r}, None, st.fingerprint))
@@ -384,4 +394,31 @@ def build_app(st: AppState) -> Starlette:
               Route("/v1/chat/completions/render", render, methods=["POST"]), Route("/v1/decisions", decisions, methods=["POST"])]
     app = Starlette(routes=routes)
     app.state.rexl3 = st
-    return app
+    return _HttpMetrics(app, st.handle.metrics, {r.path for r in routes})
+
+
+class _HttpMetrics:
+    """ASGI wrapper: requests by route, responses by status code, and the time to the response headers.  Unknown paths count under one
+    label so that a scanner cannot grow the label set."""
+
+    def __init__(self, app, metrics, known_routes):
+        self.app, self.metrics, self.known = app, metrics, known_routes
+        self.state = app.state
+
+    async def __call__(self, scope, receive, send):
+        if scope["type"] != "http":
+            await self.app(scope, receive, send)
+            return
+        import time as _time
+        route = scope.get("path", "") if scope.get("path", "") in self.known else "other"
+        t0 = _time.perf_counter()
+        self.metrics.inc("http_requests_total", route=route)
+
+        async def send_wrapped(message):
+            if message["type"] == "http.response.start":
+                code = str(message.get("status", 0))
+                self.metrics.inc("http_responses_total", code=code)
+                self.metrics.inc("http_route_responses_total", route=route, code=code)
+                self.metrics.observe("http_headers_seconds", _time.perf_counter() - t0)
+            await send(message)
+        await self.app(scope, receive, send_wrapped)

@@ -239,6 +239,9 @@ class EngineHandle:
                     self._fail_all(str(e))
                     # a lost rank takes the whole group down (fail-stop): health answers 503 `group_lost` until a supervisor restarts all ranks
                     self.state, self.error = ("group_lost" if getattr(e, "group_lost", False) else "failed"), str(e)
+                    if self.state == "group_lost":
+                        m.inc("tp_group_lost_total")
+                        m.set("tp_group_up", 0)
                     return
                 if self.consecutive_errors >= self.cfg.unready_after:
                     self.state = "degraded"
@@ -253,6 +256,18 @@ class EngineHandle:
             m.set("queued_requests", len(eng.waiting))
             for k in ("decode_tokens", "prefill_tokens", "drafted", "accepted", "rounds", "cached_tokens", "spilled_blocks", "unspilled_blocks"):
                 m.set(f"engine_{k}_total", c.get(k, 0))
+            m.set("round_streams_total", c.get("round_streams", 0))
+            m.set("round_draft_streams_total", c.get("round_draft_streams", 0))
+            m.set("round_verify_rows_total", c.get("rows", 0))
+            for phase, ns in eng.phase_ns.items():
+                m.set("round_phase_seconds_total", ns / 1e9, phase=phase)
+            for j in range(len(eng.spec_pos["offered"])):
+                for k in ("offered", "reached", "accepted"):
+                    m.set(f"spec_position_{k}_total", eng.spec_pos[k][j], position=str(j + 1))
+            self._backend_metrics(eng.backend)
+            if eng.admission is not None:
+                m.set("admission_bytes_capacity", getattr(eng.admission, "capacity", 0))
+                m.set("admission_bytes_used", getattr(eng.admission, "used", 0))
             if eng.prefix is not None:
                 m.set("prefix_cache_bytes", eng.prefix.bytes)
                 m.set("prefix_cache_entries", len(eng.prefix))
@@ -263,15 +278,45 @@ class EngineHandle:
                 m.set("prefix_spill_bytes", eng.spill.bytes)
                 m.set("prefix_spill_entries", len(eng.spill))
 
+    def _backend_metrics(self, backend) -> None:
+        """Gauges a backend offers through `stats()`: CUDA-graph cache, KV pool, control-plane traffic of a tensor-parallel group."""
+        m = self.metrics
+        m.set("slots_total", getattr(backend, "max_slots", 0))
+        try:
+            st = backend.stats() if hasattr(backend, "stats") else {}
+        except Exception:
+            st = {}
+        m.set("graph_cache_replays_total", st.get("graph_replays", 0))
+        m.set("graph_cache_captures_total", st.get("graph_captures", 0))
+        m.set("graph_cache_replayed_kernels_total", st.get("replayed_kernels", 0))
+        m.set("backend_h2d_bytes_total", st.get("h2d_bytes", 0))
+        m.set("backend_d2h_bytes_total", st.get("d2h_bytes", 0))
+        pool = getattr(backend, "pool", None)
+        if pool is not None and hasattr(pool, "free_blocks"):
+            total = pool.total_blocks() if hasattr(pool, "total_blocks") else 0
+            bt = getattr(pool, "block_tokens", 64)
+            m.set("kv_pool_tokens", total * bt)
+            m.set("kv_pool_tokens_used", max(0, total - pool.free_blocks()) * bt)
+        m.set("tp_ranks", st.get("tp_ranks", 1))
+        m.set("tp_group_up", 0 if self.state == "group_lost" else 1)
+        m.set("tp_commands_sent_total", st.get("tp_commands", 0))
+        m.set("tp_sent_bytes_total", st.get("ctrl_bytes", 0))
+        m.set("commit_replays_total", st.get("commit_replays", 0))
+
     def _route(self, events) -> None:
         for ev in events:
             t = self.tickets.get(ev.id)
             if t is None:
                 continue
             if ev.kind == "tokens":
+                now = time.monotonic()
                 if t.t_first is None:
-                    t.t_first = time.monotonic()
+                    t.t_first = now
                     self.metrics.observe("ttft_seconds", t.t_first - t.t_submit)
+                else:
+                    self.metrics.observe("token_batch_itl_seconds", now - getattr(t, "t_last", now))
+                t.t_last = now
+                self.metrics.inc("token_batches_total")
                 self.metrics.inc("generated_tokens_total", len(ev.tokens))
                 t.post(("tokens", ev.tokens))
             else:
