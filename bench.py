@@ -71,6 +71,22 @@ def reference_arm():
     return 0
 
 
+def _leave(tprt, ctx, group, collective: str) -> None:
+    """End of a multi-rank run.  The product path tears the group down in order.  The NCCL comparison arm created an NCCL communicator,
+    whose teardown inside destroy_process_group did not return on 8 GPUs: it leaves through a last barrier on the control group and a hard
+    exit instead (nothing is in flight: the device is synchronised first)."""
+    if collective == "fused":
+        tprt.shutdown(ctx, group)
+        return
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    dist.barrier(group=ctx.ctrl)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -124,7 +140,7 @@ def main():
             m = ex.marks
             t = torch.tensor([m[0].elapsed_time(m[1]), m[2].elapsed_time(m[3])], dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ctx.ctrl)
-            tprt.shutdown(ctx, group)
+            _leave(tprt, ctx, group, args.collective)
             return 0
         backend = DenseTpBackend(shard, B + 1, ctx.ctrl)
         nvls = bool(getattr(group, "mm_mc_base", 0))
@@ -247,9 +263,9 @@ def main():
                     "api": "rexl3_b200.engine.Engine.step (pinned-host row arrays up, candidate ids/values down, keyed sampler on the host)"},
             "gpu_launches": int(launches), "clocks": clocks, "build_s": round(build_s, 1),
         }
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        tprt.shutdown(ctx, group)
+        _leave(tprt, ctx, group, args.collective)
     return 0
 
 

@@ -536,9 +536,12 @@ class HybridGpuBackend(DenseGpuBackend):
     large configs), which `prefix_bytes_per_block` charges to every block."""
     name = "cuda-hybrid"
 
-    def __init__(self, model, max_slots=None, use_graphs: bool = True, state_snapshots: bool = False, rollback: bool = True):
+    def __init__(self, model, max_slots=None, use_graphs: bool = True, state_snapshots: bool = False, rollback: bool = True,
+                 verify_snapshots: bool = False):
         super().__init__(model, max_slots=max_slots, use_graphs=use_graphs, self_draft=False)
         self.state_snapshots = bool(state_snapshots)
+        # digest every snapshot when it is taken and check the pools against it after a restore (one device-to-host read per restore)
+        self.verify_snapshots = bool(verify_snapshots)
         self.rollback = bool(rollback)
         self._rec_rows = None        # slot -> first row of the last recorded window (None: the last window stored its state itself)
         self._rec_M = 0
@@ -636,7 +639,10 @@ class HybridGpuBackend(DenseGpuBackend):
     def _snapshot(self, slot):
         self._flush_commits()
         m = self.m
-        return {li: (m.conv_pool[li][slot].clone(), m.ssm_pool[li][slot].clone()) for li in m.ssm_pool}
+        snap = {li: (m.conv_pool[li][slot].clone(), m.ssm_pool[li][slot].clone()) for li in m.ssm_pool}
+        if self.verify_snapshots:
+            snap["digest"] = m.K.state_digest([t for li in sorted(m.ssm_pool) for t in snap[li]])
+        return snap
 
     def prefix_commit(self, slot, blocks):
         ids = self.pages[slot][:blocks]
@@ -658,9 +664,15 @@ class HybridGpuBackend(DenseGpuBackend):
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
         m = self.m
-        for li, (conv, state) in handles[best][2].items():
+        snap = handles[best][2]
+        for li in m.ssm_pool:
+            conv, state = snap[li]
             m.conv_pool[li][slot].copy_(conv)
             m.ssm_pool[li][slot].copy_(state)
+        if "digest" in snap:
+            got = m.K.state_digest([t[slot] for li in sorted(m.ssm_pool) for t in (m.conv_pool[li], m.ssm_pool[li])])
+            if not torch.equal(got, snap["digest"]):
+                raise BackendError(f"the state restored into slot {slot} does not have the digest recorded with its snapshot", fatal=True)
         self.len[slot] = len(ids) * PAGE
         return self.len[slot]
 

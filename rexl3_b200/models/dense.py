@@ -35,6 +35,7 @@ class DenseConfig:
     head_bits: float | None = None
     codebook: str = "3inst"
     name: str = "dense-gqa"
+    mrope_sections: tuple | None = None   # (t, h, w) frequency-pair counts of interleaved M-RoPE (sum = head_dim / 2); None = plain RoPE
 
     @property
     def ffn_padded(self) -> int:
@@ -327,6 +328,9 @@ class DenseGPU:
         self.K = K
         self.window_seq_rows = 1       # the most adjacent rows one sequence has in the next decode / verify window (set by the backend)
         self.attn_plan = None          # device plan of the current window for the attention kernel (allocated with the scratch)
+        # int32 [rows, 3] (T, H, W positions) for the next forward of a model whose config has `mrope_sections`; None = text rows, where
+        # the three axes equal `positions` and plain RoPE gives the same bits
+        self.pos3 = None
         self.device = device
         if isinstance(w, DenseConfig):
             self.cfg = cfg = w
@@ -513,7 +517,8 @@ class DenseGPU:
         s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
         ksc = self.kv_scale[li] if self.kv_fp8 else None
         K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
-                          self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li])
+                          self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li],
+                          pos3=self.pos3, mrope_sections=getattr(cfg, "mrope_sections", None))
         if prefill is None:
             K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
                           max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc, max_seq_rows=self.window_seq_rows,
@@ -554,8 +559,11 @@ class DenseGPU:
             return e.value
 
     def forward_phases(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True,
-                       n_layers=None):
+                       n_layers=None, embed_rows=None, pos3=None):
         """Run all layers over M rows.
+
+        embed_rows: (int64 index tensor [n], bf16 [n, d_model]) - rows whose token embedding is replaced (image tokens encoded by a vision
+        tower).  pos3: int32 [M, 3] (T, H, W positions) for a config with `mrope_sections`; None = text rows (all axes = positions).
 
         ids, positions, slots, row_seq, ctx_len: int32 device tensors [M] (slot = physical KV slot page*64+offset of the row's
         own token; ctx_len = number of keys the row attends to = position + 1).  block_table int32 [max_seqs, max_blocks].
@@ -579,6 +587,9 @@ class DenseGPU:
             # one plan of the window (row blocks and work items of the persistent attention kernel) serves every layer
             K.attn_plan(row_seq, ctx_len, cfg.n_q, cfg.n_kv, self.window_seq_rows, self.attn_plan)
         K.embed(ids, self.embed, h)
+        if embed_rows is not None:
+            h.index_copy_(0, embed_rows[0], embed_rows[1].to(h.dtype))
+        self.pos3 = pos3
         L0 = self.layers[0]
         if L0["qkv"].suh is not None:          # (split projections rotate per part inside _linear)
             K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)

@@ -22,7 +22,11 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
                                        const float* __restrict__ bias, const uint16_t* __restrict__ q_norm, const uint16_t* __restrict__ k_norm,
                                        float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                        const int* __restrict__ slot, uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
-                                       uint16_t* __restrict__ v_cache, const float* __restrict__ kv_scale, float* __restrict__ kv_amax) {
+                                       uint16_t* __restrict__ v_cache, const float* __restrict__ kv_scale, float* __restrict__ kv_amax,
+                                       const int* __restrict__ pos3, int lim_h, int lim_w) {
+  // pos3 != nullptr: interleaved M-RoPE (reference crates/cuda/csrc/glue.cu:178-180): int32 [rows][3] = the T, H and W position of each row;
+  // frequency pair i rotates by the position of axis i % 3, the H axis only below pair lim_h = 3 * section_h and the W axis only below
+  // lim_w = 3 * section_w (T elsewhere).  With T = H = W this is plain RoPE, bit for bit.
   // kv_scale != nullptr: the caches are FP8 (E4M3) bytes and K / V are stored as value / scale[head] (f32 [2][n_kv]: K scales, V scales),
   // saturating.  kv_amax != nullptr: the largest |K| and |V| per head are tracked there (f32 [2][n_kv]; used to calibrate the scales).
   pdl_launch();
@@ -80,8 +84,13 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
       for (int i = 0; i < 4; ++i) {
         const float other = __shfl_xor_sync(0xffffffffu, y[i], GL / 2);
         const int fi = (d0 + i) % (HD / 2);
+        float p = pos;
+        if (pos3 != nullptr) {
+          const int axis = (fi % 3 == 1 && fi < lim_h) ? 1 : ((fi % 3 == 2 && fi < lim_w) ? 2 : 0);
+          p = (float)pos3[row * 3 + axis];
+        }
         float sn, cs;
-        sincosf(pos * inv_freq[fi], &sn, &cs);
+        sincosf(p * inv_freq[fi], &sn, &cs);
         y[i] = first ? (y[i] * cs - other * sn) : (y[i] * cs + other * sn);
       }
     }
@@ -197,7 +206,8 @@ using namespace rx;
 
 RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv, int hd, const void* svh, const void* bias, const void* q_norm,
                               const void* k_norm, float eps, const void* positions, const void* inv_freq, const void* slot, void* q_out,
-                              void* k_cache, void* v_cache, void* stream, const void* kv_scale, void* kv_amax) {
+                              void* k_cache, void* v_cache, void* stream, const void* kv_scale, void* kv_amax, const void* pos3, int section_h,
+                              int section_w) {
   const int N = (n_q + 2 * n_kv) * hd;
   if (N % 128) return (int)cudaErrorInvalidValue;
   const int per_row = (N / 128 + 7) / 8;   // one warp per 128-block
@@ -205,7 +215,7 @@ RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv,
   cudaStream_t st = (cudaStream_t)stream;
 #define RX_ARGS (const float*)part, S, M, n_q, n_kv, (const __half*)svh, (const float*)bias, (const uint16_t*)q_norm, (const uint16_t*)k_norm, eps, \
                 (const int*)positions, (const float*)inv_freq, (const int*)slot, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache, \
-                (const float*)kv_scale, (float*)kv_amax
+                (const float*)kv_scale, (float*)kv_amax, (const int*)pos3, 3 * section_h, 3 * section_w
   if (hd == 128) rx::launch(finish_qkv_rope_kernel<128>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else if (hd == 64) rx::launch(finish_qkv_rope_kernel<64>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else return (int)cudaErrorInvalidValue;
@@ -227,6 +237,48 @@ RX_API int rx_topk(const void* logits, int rows, int vocab, int count, void* scr
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   rx::launch(topk_stage2_kernel, dim3(rows), dim3(TOPK_THREADS), 0, st, (const uint64_t*)scratch, nchunks * count, count, (int*)ids, (float*)vals);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ content digest of device memory
+// digest = sum over 8-byte words w_i of mix(w_i xor (i + 1) * 0x9E3779B97F4A7C15) modulo 2^64, mix = the splitmix64 finaliser: keyed by the
+// word's position, and a sum, so any grid computes the same value.  A tail of fewer than 8 bytes is zero-extended.  Role: checking that a
+// snapshot of recurrent state or of KV pages restored from a cache holds what was stored (reference crates/cuda/csrc/state_digest.cu).
+namespace rx {
+__device__ __forceinline__ unsigned long long digest_mix(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__global__ void __launch_bounds__(256) state_digest_kernel(const uint8_t* __restrict__ p, long long bytes, unsigned long long* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const long long words = bytes >> 3;
+  unsigned long long acc = 0;
+  const unsigned long long* w = reinterpret_cast<const unsigned long long*>(p);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (long long)gridDim.x * blockDim.x)
+    acc += digest_mix(w[i] ^ ((unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull));
+  if (blockIdx.x == 0 && threadIdx.x == 0 && (bytes & 7)) {
+    unsigned long long t = 0;
+    for (int k = 0; k < (int)(bytes & 7); ++k) t |= (unsigned long long)p[(words << 3) + k] << (8 * k);
+    acc += digest_mix(t ^ ((unsigned long long)(words + 1) * 0x9E3779B97F4A7C15ull));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0 && acc != 0) atomicAdd(out, acc);
+}
+}  // namespace rx
+
+// *out (a device uint64 the caller zeroed) += digest of `bytes` bytes at `p` (8-byte aligned).  Several calls into the same word digest a
+// scattered object; the order of the calls does not matter only if each part is keyed by the caller (here: it is not - digest parts in a fixed order
+// into separate words when the order must count).
+RX_API int rx_state_digest(const void* p, long long bytes, void* out, void* stream) {
+  if (p == nullptr || out == nullptr || bytes < 0 || ((uintptr_t)p & 7)) return (int)cudaErrorInvalidValue;
+  if (bytes == 0) return 0;
+  long long blocks = (bytes / 8 + 256 * 8 - 1) / (256 * 8);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 1024) blocks = 1024;
+  rx::launch(state_digest_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const uint8_t*)p, bytes, (unsigned long long*)out);
   return (int)cudaGetLastError();
 }
 

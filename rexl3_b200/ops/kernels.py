@@ -176,14 +176,56 @@ def finish_swiglu_rot(part, S, M, w: Exl3Weight, suh_down: torch.Tensor, xr: tor
 
 
 def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, eps, positions, inv_freq, slot, q_out, k_cache, v_cache,
-                    kv_scale=None, kv_amax=None) -> None:
+                    kv_scale=None, kv_amax=None, pos3=None, mrope_sections=None) -> None:
     """kv_scale (f32 [2, n_kv]) given: the caches are FP8 (E4M3) and K, V are stored divided by their head's scale.  kv_amax (f32 [2, n_kv])
-    given: the largest |K| and |V| per head are recorded there."""
+    given: the largest |K| and |V| per head are recorded there.  pos3 (int32 [rows, 3]: T, H, W position of every row) with
+    mrope_sections = (t, h, w) frequency-pair counts: interleaved M-RoPE instead of `positions` (pair i uses axis i % 3 inside its section)."""
+    sec = mrope_sections or (0, 0, 0)
+    assert pos3 is None or (pos3.dtype == torch.int32 and pos3.is_contiguous() and pos3.shape[1] == 3 and sum(sec) == hd // 2)
     L = _lib.load()
     _lib.check(L.rx_finish_qkv_rope(part.data_ptr(), S, M, n_q, n_kv, hd, w.svh.data_ptr(), _lib.ptr(w.bias), _lib.ptr(q_norm), _lib.ptr(k_norm),
                                     eps, positions.data_ptr(), inv_freq.data_ptr(), slot.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
-                                    v_cache.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kv_amax)), "rx_finish_qkv_rope")
+                                    v_cache.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kv_amax), _lib.ptr(pos3), int(sec[1]), int(sec[2])),
+               "rx_finish_qkv_rope")
     _lib.count()
+
+
+def state_digest(tensors, out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """Position-keyed 64-bit content digest of one tensor or of a list of tensors (each part into its own word, the words then folded on the
+    host by `fold_digest`).  Returns the int64 device tensor of per-part digests; nothing synchronises here."""
+    parts = tensors if isinstance(tensors, (list, tuple)) else [tensors]
+    L = _lib.load()
+    if out is None:
+        out = torch.zeros(len(parts), dtype=torch.int64, device=parts[0].device)
+    else:
+        out.zero_()
+    for i, t in enumerate(parts):
+        assert t.is_contiguous()
+        _lib.check(L.rx_state_digest(t.data_ptr(), t.numel() * t.element_size(), out[i:].data_ptr(), _lib.stream_ptr()), "rx_state_digest")
+        _lib.count()
+    return out
+
+
+def state_digest_host(data: bytes) -> int:
+    """The same digest of a byte string on the host (numpy, wrap-around uint64 arithmetic): the oracle of `state_digest`."""
+    import numpy as np
+    n = len(data)
+    buf = np.frombuffer(data + b"\0" * ((-n) % 8), dtype="<u8")
+    with np.errstate(over="ignore"):
+        i = np.arange(1, len(buf) + 1, dtype=np.uint64)
+        z = buf ^ (i * np.uint64(0x9E3779B97F4A7C15))
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+        return int(z.sum(dtype=np.uint64))
+
+
+def fold_digest(words) -> int:
+    """Per-part digests -> one 64-bit value that depends on the order of the parts."""
+    acc = 0
+    for w in words:
+        acc = ((acc * 0x100000001B3) ^ (int(w) & 0xFFFFFFFFFFFFFFFF)) & 0xFFFFFFFFFFFFFFFF
+    return acc
 
 
 def topk_scratch(rows: int, vocab: int, count: int, device="cuda") -> torch.Tensor:

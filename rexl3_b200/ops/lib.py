@@ -93,7 +93,8 @@ def _declare(lib):
         "rx_finish_add_norm_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void]),
         "rx_finish_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_finish_qkv_rope": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void,
-                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
+                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int]),
+        "rx_state_digest": (c_int, [c_void, c_ll, c_void, c_void]),
         "rx_topk_scratch_bytes": (c_ll, [c_int, c_int, c_int]),
         "rx_topk": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
         "rx_make_kv_tmap": (c_int, [c_void, c_void, c_ll, c_int]),

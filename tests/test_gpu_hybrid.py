@@ -127,7 +127,7 @@ def make_hybrid_backend(request):
 
     def make():
         # one model, fresh bookkeeping: KV pages are overwritten and a row at position 0 starts from a zero state whatever the pools hold
-        return HybridGpuBackend(model, max_slots=8, state_snapshots=True)
+        return HybridGpuBackend(model, max_slots=8, state_snapshots=True, verify_snapshots=True)
     make.vocab = cfg.vocab
     return make
 

@@ -281,3 +281,55 @@ def test_qkv_finish_rope_and_cache_write(K):
     assert (kc[1, :, 17].float() - kr[1]).abs().max() < 3e-2 * kr.abs().max()
     assert (vc[1, :, 17].float() - v[1]).abs().max() < 3e-2 * v.abs().max()
     assert kc[0].abs().max() == 0 and kc[2].abs().max() == 0 and kc[4].abs().max() == 0
+
+
+def test_interleaved_mrope_matches_reference_and_reduces_to_rope(K):
+    """Frequency pair i rotates by the T, H or W position (axis i % 3 inside its section); equal axes give plain RoPE bit for bit."""
+    torch.manual_seed(7)
+    M, n_q, n_kv, hd = 6, 4, 2, 128
+    N = (n_q + 2 * n_kv) * hd
+    w, _, _, _ = _mk(K, 128, N, 4, out_scale=1.0)
+    part = torch.randn(1, M, N, device="cuda")
+    y = _hadamard(part.sum(0)) * w.svh.float()
+    inv = torch.from_numpy((1.0 / (1e4 ** (np.arange(0, hd, 2, dtype=np.float32) / hd))).astype(np.float32)).cuda()
+    sec = (24, 20, 20)
+    pos3 = torch.tensor([[0, 0, 0], [5, 5, 5], [9, 2, 7], [9, 3, 1], [100, 40, 41], [4099, 0, 63]], dtype=torch.int32, device="cuda")
+    slot = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    kc = torch.zeros(2, n_kv, 64, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+
+    def run(p3, positions):
+        qo = torch.empty(M, n_q * hd, dtype=torch.bfloat16, device="cuda")
+        K.finish_qkv_rope(part, 1, M, n_q, n_kv, hd, w, None, None, 1e-6, positions, inv, slot, qo, kc, vc, pos3=p3, mrope_sections=sec if p3 is not None else None)
+        return qo
+    t_only = pos3[:, 0].contiguous()
+    same = t_only[:, None].repeat(1, 3).contiguous()
+    assert torch.equal(run(same, t_only), run(None, t_only))
+    got = run(pos3, t_only).float().view(M, n_q, hd)
+    i = torch.arange(hd // 2, device="cuda")
+    axis = torch.where((i % 3 == 1) & (i < 3 * sec[1]), 1, torch.where((i % 3 == 2) & (i < 3 * sec[2]), 2, 0))
+    p = pos3.float()[:, axis]                                    # [M, hd/2]
+    ang = p * inv[None]
+    c, s_ = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+    x = y[:, :n_q * hd].view(M, n_q, hd)
+    x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+    ref = torch.cat([x1 * c - x2 * s_, x2 * c + x1 * s_], -1)
+    assert (got - ref).abs().max() < 3e-2 * ref.abs().max()
+    assert (got[2] - run(None, t_only).float().view(M, n_q, hd)[2]).abs().max() > 0.1        # the H / W axes really rotate differently
+
+
+def test_state_digest_equals_the_host_digest_and_sees_every_byte(K):
+    torch.manual_seed(3)
+    for n in (8, 24, 4096, 1_000_003):
+        t = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
+        d = K.state_digest(t)
+        want = K.state_digest_host(bytes(t.cpu().numpy()))
+        assert (int(d[0].item()) & 0xFFFFFFFFFFFFFFFF) == want, n
+    a = torch.randn(3, 1000, device="cuda")
+    b = a.clone()
+    b[2, 999] += 1e-3
+    swapped = a.flip(0).contiguous()
+    da, db, ds = (int(K.state_digest(x)[0].item()) for x in (a, b, swapped))
+    assert da != db and da != ds                                   # one changed value, and the same rows in another order
+    parts = K.state_digest([a, b]).cpu().tolist()
+    assert K.fold_digest(parts) != K.fold_digest(parts[::-1])
