@@ -399,7 +399,7 @@ class HybridGPU(DenseGPU):
             if L["kind"] in "GK":
                 K.gdn_mixer(proj, M, cfg.gdn_k_heads, cfg.gdn_v_heads, 128, row_seq, positions, seg_start, seg_len, nseg, L["conv_w"], L["conv_b"],
                             L["dt_bias"], L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], self.rec_xbc[li], self.ssm_out,
-                            kda=L["kind"] == "K", mode=K.SCAN_COMMIT)
+                            kda=L["kind"] == "K", mode=K.SCAN_COMMIT, y32=self.ssm_y)
             else:
                 K.ssm_mixer(proj, M, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state, row_seq, positions, seg_start, seg_len, nseg,
                             L["conv_w"], L["conv_b"], L["dt_bias"], L["a_neg"], L["d_skip"], L["norm_w"], cfg.eps, self.conv_pool[li],
@@ -428,7 +428,7 @@ class HybridGPU(DenseGPU):
         wi = max(cfg.d_inner if m else 0, cfg.gdn_inner if g else 0)
         self.ssm_proj = torch.empty(R * wp, dtype=torch.float32, device=dev)       # flat: each layer kind views its own row width
         self.ssm_xbc = torch.empty(R * wc, dtype=torch.float32, device=dev)
-        self.ssm_y = torch.empty(R * max(cfg.d_inner, 1), dtype=torch.float32, device=dev)
+        self.ssm_y = torch.empty(R * max(cfg.d_inner if m else 1, cfg.gdn_inner if g else 1), dtype=torch.float32, device=dev)
         self.ssm_out = torch.empty(R * wi, dtype=torch.bfloat16, device=dev)
 
     # ------------------------------------------------------------------ weights
@@ -536,7 +536,7 @@ class HybridGPU(DenseGPU):
             K.finish_store(self.part, s, M, L["in_proj"], proj)
             out = self.ssm_out[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
             K.gdn_mixer(proj, M, cfg.gdn_k_heads, cfg.gdn_v_heads, 128, row_seq, positions, seg_s, seg_l, nseg, L["conv_w"], L["conv_b"], L["dt_bias"],
-                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], xbc, out, kda=kda, mode=mode)
+                        L["a_neg"], L["norm_w"], cfg.eps, self.conv_pool[li], self.ssm_pool[li], xbc, out, kda=kda, mode=mode, y32=self.ssm_y)
             xr_g = self.xr[:M * cfg.gdn_inner].view(M, cfg.gdn_inner)
             K.norm_rot_in(out, None, cfg.eps, L["out_proj"].suh, xr_g)
             return self._linear(xr_g, L["out_proj"], M, cls, "gdn_out")

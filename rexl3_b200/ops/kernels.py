@@ -139,17 +139,19 @@ def ssm_mixer(proj: torch.Tensor, M: int, H: int, P: int, G: int, N: int, row_se
 
 
 def gdn_mixer(proj: torch.Tensor, M: int, Hk: int, Hv: int, D: int, row_seq, positions, seg_start, seg_len, nseg: int, conv_w, conv_b, dt_bias, a_neg,
-              norm_w, eps: float, conv_pool, s_pool, xbc, out, kda: bool = False, mode: int = SCAN_FINAL) -> None:
+              norm_w, eps: float, conv_pool, s_pool, xbc, out, kda: bool = False, mode: int = SCAN_FINAL, y32=None) -> None:
     """Gated delta net mixer between in_proj and out_proj: `proj` f32 [M, ldp] (z | q | k | v | b | a | pad) -> `out` bf16 [M, Hv*D]
     (per-head normed and gated); the conv and state pools of the rows' sequences advance.  Two launches (conv; recurrence + norm).
-    `kda`: per-key-channel decay (a and dt_bias have Hv*D entries) and a sigmoid output gate.  `mode` as in `ssm_mixer`."""
+    `kda`: per-key-channel decay (a and dt_bias have Hv*D entries) and a sigmoid output gate.  `mode` as in `ssm_mixer`.  `y32` (f32 scratch
+    of M * Hv * D values) with a segment table: the recurrence runs split over a head's value columns and the norm as its own launch (same bits)."""
     L = _lib.load()
     assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and out.dtype == torch.bfloat16
     _lib.check(L.rx_gdn_mixer(proj.data_ptr(), proj.stride(0), M, Hk, Hv, D, row_seq.data_ptr(), positions.data_ptr(), _lib.ptr(seg_start),
                               _lib.ptr(seg_len), nseg, conv_w.data_ptr(), conv_b.data_ptr(), dt_bias.data_ptr(), a_neg.data_ptr(), norm_w.data_ptr(),
                               eps, conv_pool.data_ptr(), s_pool.data_ptr(), xbc.data_ptr(), out.data_ptr(), _lib.stream_ptr(), 1 if kda else 0,
-                              mode), "rx_gdn_mixer")
-    _lib.count(1 if mode == SCAN_COMMIT else 2)
+                              mode, _lib.ptr(y32)), "rx_gdn_mixer")
+    split = seg_start is not None and y32 is not None
+    _lib.count(1 if mode == SCAN_COMMIT else (3 if split else 2))
 
 
 def finish_store(part, S, M, w: Exl3Weight, out: torch.Tensor) -> None:

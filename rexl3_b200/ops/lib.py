@@ -82,7 +82,7 @@ def _declare(lib):
         "rx_ssm_mixer": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void,
                                  c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_void, c_void, c_int]),
         "rx_gdn_mixer": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void,
-                                 c_f, c_void, c_void, c_void, c_void, c_void, c_int, c_int]),
+                                 c_f, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void]),
         "rx_dev_alloc": (c_int, [c_ll, ctypes.POINTER(ctypes.c_void_p)]),
         "rx_dev_free": (c_int, [c_void]),
         "rx_exl3_unpack": (c_int, [c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
