@@ -55,6 +55,8 @@ def main(argv=None) -> int:
     p.add_argument("--no-gpu-probe", action="store_true", help="check: skip the NVML facts (memory, idle)")
     p.add_argument("--lines", type=int, default=40)
     p.add_argument("--max-runtime", type=float, default=0.0)
+    p.add_argument("--ssh", default="", help="ssh client for ranks on other hosts (default: $REXL3_SSH or ssh)")
+    p.add_argument("--remote-workdir", default="", help="path of this repository on the other hosts (default: the same path as here)")
     a = p.parse_args(argv)
     try:
         c = load_cluster(a.cluster)
@@ -91,10 +93,11 @@ def main(argv=None) -> int:
     if a.command == "check":
         need = a.need_mib or _planned_mib(c, g)
         checks = ops.preflight(c, group, need_mib=need, gpu_probe=None if a.no_gpu_probe else ops.nvml_probe, locks=locks)
+        checks += ops.preflight_remote(c, group, need_mib=need, ssh=a.ssh, workdir=a.remote_workdir or os.getcwd(), probe_gpus=not a.no_gpu_probe)
         for ch in checks:
             print(f"{'ok  ' if ch.ok else 'FAIL'} {ch.name}: {ch.detail}")
         return 0 if all(ch.ok for ch in checks) else 1
-    cmds = rank_commands(c, group, sys.executable)
+    cmds = rank_commands(c, group, sys.executable, a.ssh, a.remote_workdir)
     if a.command == "plan" or a.dry_run:
         for r, (env, argv_) in enumerate(cmds):
             print(f"rank {r}: " + " ".join(f"{k}={shlex.quote(v)}" for k, v in env.items()) + " " + " ".join(shlex.quote(x) for x in argv_))

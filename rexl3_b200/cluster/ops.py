@@ -1,6 +1,6 @@
 """Group operations around the supervisor: pre-flight checks, GPU lock files, the state file of a running group, status, down, logs.
 Parity: the reference's `rexl3-cluster` check / up / down / status / logs (crates/cluster/src/check.rs, ops.rs), for the GPUs of one
-NVLink box (ranks are local child processes; remote nodes are planned, not driven).
+NVLink box, or several hosts (ranks on this host are child processes; ranks on other hosts are ssh client children, `cluster.remote`).
 
 Pre-flight facts per group: the kernel and host libraries exist and every rank would load the same bytes (sha256), the pack is present
 and has one identity (structure fingerprint), the group's ports are free, each GPU has the memory the plan needs and runs no other
@@ -97,6 +97,47 @@ def preflight(c: Cluster, group: str, *, need_mib: int = 0, gpu_probe=None, port
         out.append(Check(f"gpu{idx}:idle", idle, "no compute process" if idle else f"busy: pids {f['compute_pids']}"))
         if need_mib:
             out.append(Check(f"gpu{idx}:memory", f["free_mib"] >= need_mib, f"{f['free_mib']} MiB free, {need_mib} needed"))
+    return out
+
+
+def preflight_remote(c: Cluster, group: str, *, need_mib: int = 0, ssh: str = "", workdir: str = "", probe_gpus: bool = True, python: str = "python3",
+                     prober=None) -> list:
+    """The same facts for the ranks of the group that live on other hosts, read through one ssh command per host (`cluster.remote.probe`):
+    the kernel library there must have the hash of the one here (ranks of one group must run one build), the group's ports must be free on
+    the first rank's host, every GPU idle with `need_mib` free.  `prober`: stand-in for `remote.probe` in tests."""
+    from . import remote
+    g = c.groups[group]
+    out, by_host = [], {}
+    for i, node in enumerate(g.ranks):
+        n = c.nodes[node]
+        if not remote.is_local(n.get("address")):
+            by_host.setdefault(n["address"], []).append((i, n.get("gpu", i)))
+    if not by_host:
+        return out
+    from ..ops import lib as oplib
+    here = _sha256(oplib.LIB_PATH)[:16] if os.path.exists(oplib.LIB_PATH) else None
+    rel = os.path.relpath(oplib.LIB_PATH, os.getcwd()) if os.path.exists(oplib.LIB_PATH) else "rexl3_b200/ops/librexl3_kernels.so"
+    first_host = c.nodes[g.ranks[0]].get("address")
+    for host, ranks in sorted(by_host.items()):
+        ports = [g.tp_port, g.http_port] if host == first_host else []
+        try:
+            facts = (prober or remote.probe)(host, workdir, python, ports, [gpu for _, gpu in ranks] if probe_gpus else [], [rel], ssh)
+        except Exception as e:  # noqa: BLE001
+            out.append(Check(f"{host}:reachable", False, str(e)))
+            continue
+        out.append(Check(f"{host}:reachable", True, "answered the probe"))
+        there = next(iter(facts.get("libs", {}).values()), None)
+        out.append(Check(f"{host}:binary", there is not None and there == here, f"{there} there, {here} here"))
+        for port, free in facts.get("ports", {}).items():
+            out.append(Check(f"{host}:port{port}", bool(free), "free" if free else "in use"))
+        for gpu, f in facts.get("gpus", {}).items():
+            if "error" in f:
+                out.append(Check(f"{host}:gpu{gpu}", False, f"probe failed: {f['error']}"))
+                continue
+            idle = not f.get("compute_pids")
+            out.append(Check(f"{host}:gpu{gpu}:idle", idle, "no compute process" if idle else f"busy: pids {f['compute_pids']}"))
+            if need_mib:
+                out.append(Check(f"{host}:gpu{gpu}:memory", f["free_mib"] >= need_mib, f"{f['free_mib']} MiB free, {need_mib} needed"))
     return out
 
 

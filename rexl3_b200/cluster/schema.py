@@ -4,7 +4,7 @@ strict (unknown keys, ranks naming unknown nodes, a node in two groups, port cla
 
 {
   "schema_version": 1, "name": "b200-box",
-  "nodes": [{"name": "g0", "gpu": 0}, ...],                     # "address" for remote hosts (dry-run plans only)
+  "nodes": [{"name": "g0", "gpu": 0}, ...],                     # "address": the rank runs on that host through an ssh client
   "pack": "/models/x", "serve": {"flags": ["--slots", "64"]},
   "groups": [{"name": "tp8", "ranks": ["g0", ..., "g7"], "tp_port": 29600, "http_port": 8080}],
   "supervisor": {"backoff_s": [1, 2, 5, 15], "window_s": 600, "max_failures": 5}
@@ -104,8 +104,10 @@ def load_cluster(path: str) -> Cluster:
             raise ClusterError(f"{path}: {e}") from e
 
 
-def rank_commands(c: Cluster, group: str, python: str = "python") -> list:
-    """One (env, argv) per rank: the serving binary under the lockstep environment of the group."""
+def rank_commands(c: Cluster, group: str, python: str = "python", ssh: str = "", workdir: str = "") -> list:
+    """One (env, argv) per rank: the serving binary under the lockstep environment of the group.  A rank whose node has an `address` that is
+    not this host is wrapped into an ssh client command (`cluster.remote.wrap`; `workdir` = the repository's path on that host, default: the
+    same path as here)."""
     g = c.groups[group]
     out = []
     R = len(g.ranks)
@@ -120,5 +122,10 @@ def rank_commands(c: Cluster, group: str, python: str = "python") -> list:
         argv = [python, "-m", "rexl3_b200.server", "--backend", "cuda", "--port", str(g.http_port)]
         argv += ["--model", c.pack] if c.pack else ["--random-init", c.random_init]
         argv += c.flags + g.flags
+        from . import remote
+        if not remote.is_local(n.get("address")):
+            import os
+            rpy = python if python != os.sys.executable else "python3"      # this host's interpreter path means nothing over there
+            env, argv = remote.wrap(env, [rpy] + argv[1:], n["address"], workdir or os.getcwd(), ssh)
         out.append((env, argv))
     return out
