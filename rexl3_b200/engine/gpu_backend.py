@@ -473,7 +473,12 @@ class DenseGpuBackend(Backend):
         parts = [c[p] for c in m.k_cache if c is not None] + [c[p] for c in m.v_cache if c is not None]
         out = torch.stack(parts).contiguous().view(torch.uint8).cpu()
         self.d2h_bytes += out.numel()
-        return out.numpy().tobytes()
+        blob = out.numpy().tobytes()
+        if getattr(m, "kv_i8", False):              # an int8 page is its bytes plus the per-token scales of every layer
+            sc = torch.stack([t[p] for t in m.k_tscale if t is not None] + [t[p] for t in m.v_tscale if t is not None]).contiguous().cpu()
+            self.d2h_bytes += sc.numel() * 4
+            blob += sc.numpy().tobytes()
+        return blob
 
     def prefix_import(self, payload):
         m = self.m
@@ -481,14 +486,21 @@ class DenseGpuBackend(Backend):
             return None
         caches = [c for c in m.k_cache if c is not None] + [c for c in m.v_cache if c is not None]
         page_bytes = caches[0][0].numel() * caches[0].element_size()
-        if len(payload) != page_bytes * len(caches):
+        scales = ([t for t in m.k_tscale if t is not None] + [t for t in m.v_tscale if t is not None]) if getattr(m, "kv_i8", False) else []
+        scale_bytes = scales[0][0].numel() * 4 if scales else 0
+        if len(payload) != page_bytes * len(caches) + scale_bytes * len(scales):
             return None                     # written by a different model or cache format
         got = self.pool.alloc(1)
         if got is None:
             return None
-        src = torch.frombuffer(bytearray(payload), dtype=torch.uint8).to(m.device, non_blocking=False).view(len(caches), page_bytes)
+        raw = torch.frombuffer(bytearray(payload), dtype=torch.uint8).to(m.device, non_blocking=False)
+        src = raw[:page_bytes * len(caches)].view(len(caches), page_bytes)
         for i, c in enumerate(caches):
             c[got[0]].view(torch.uint8).view(-1).copy_(src[i])
+        if scales:
+            ssrc = raw[page_bytes * len(caches):].view(len(scales), scale_bytes)
+            for i, t in enumerate(scales):
+                t[got[0]].view(torch.uint8).view(-1).copy_(ssrc[i])
         self.h2d_bytes += len(payload)
         return ("page", got[0])
 

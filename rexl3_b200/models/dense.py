@@ -343,15 +343,20 @@ class DenseGPU:
         self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
         # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16 (or E4M3 bytes with one scale per layer, K/V and head),
         # plus their TMA descriptors
-        if kv_dtype not in ("bf16", "fp8"):
-            raise ValueError(f"kv_dtype {kv_dtype!r}: bf16 or fp8")
+        # (or int8 with one power-of-two scale per token and KV head, kept in k_tscale / v_tscale [pages, n_kv, 64] f32 beside each layer's cache)
+        if kv_dtype not in ("bf16", "fp8", "int8"):
+            raise ValueError(f"kv_dtype {kv_dtype!r}: bf16, fp8 or int8")
         self.kv_fp8 = kv_dtype == "fp8"
-        cdt = torch.uint8 if self.kv_fp8 else torch.bfloat16
+        self.kv_i8 = kv_dtype == "int8"
+        cdt = torch.uint8 if self.kv_fp8 else (torch.int8 if self.kv_i8 else torch.bfloat16)
         kvl = set(self._kv_layers())
         self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(cfg.n_layers)]
         self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(cfg.n_layers)]
         self.kv_scale = torch.ones(cfg.n_layers, 2, cfg.n_kv, dtype=torch.float32, device=device) if self.kv_fp8 else None
         self.kv_amax = None        # set while calibrating
+        mk_ts = lambda: torch.ones(num_pages, cfg.n_kv, PAGE, dtype=torch.float32, device=device)  # noqa: E731
+        self.k_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(cfg.n_layers)]
+        self.v_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(cfg.n_layers)]
         self.tk = [None if c is None else K.KvTensorMap(c) for c in self.k_cache]
         self.tv = [None if c is None else K.KvTensorMap(c) for c in self.v_cache]
         self.status = K.new_status(device)
@@ -516,17 +521,18 @@ class DenseGPU:
         cfg, K = self.cfg, self.K
         s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
         ksc = self.kv_scale[li] if self.kv_fp8 else None
+        kts = (self.k_tscale[li], self.v_tscale[li]) if self.kv_i8 else None
         K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
                           self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li],
-                          pos3=self.pos3, mrope_sections=getattr(cfg, "mrope_sections", None))
+                          pos3=self.pos3, mrope_sections=getattr(cfg, "mrope_sections", None), kv_tscale=kts)
         if prefill is None:
             K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
                           max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc, max_seq_rows=self.window_seq_rows,
-                          plan=self.attn_plan)
+                          plan=self.attn_plan, kv_tscale=kts)
         else:
             ao = self.attn_out[:M]
             K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
-                           ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc)
+                           ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc, kv_tscale=kts)
             K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
         s = self._linear(xr_a, L["o"], M, cls, "o")
         return s

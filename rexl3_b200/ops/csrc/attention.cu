@@ -85,21 +85,56 @@ __device__ __forceinline__ void load_kv_page8(uint8_t* kdst, uint8_t* vdst, cons
   tma_load_2d(vdst, tv, 0, y, bar);
 }
 
+// KV cache element formats of the attention kernels
+constexpr int KVQ_BF16 = 0, KVQ_FP8 = 1, KVQ_I8 = 2;
+
+// int8 cache with one power-of-two scale per (token, KV head) (the reference's format, crates/cuda/csrc/nemotron_kv8.cuh:1-14): a page of one KV
+// head is 64 x HD bytes plus 64 f32 scales for K and 64 for V ([pages][n_kv][64] each); the scales ride on the page's barrier as two 256-byte
+// bulk copies.  The expansion multiplies them in: int8 x 2^e is exact in fp16, so the tile holds the dequantised values and the attention
+// step is the fp16 one with no further scale.
 template <int HD>
-__device__ __forceinline__ void expand_page8(const uint8_t* src, uint8_t* dst) {
-  constexpr int CHUNKS = PAGE * HD / 16;          // 16 fp8 values each
+__device__ __forceinline__ void load_kv_page_i8(uint8_t* kdst, uint8_t* vdst, float* sc, const CUtensorMap* tk, const CUtensorMap* tv,
+                                                const float* __restrict__ k_ts, const float* __restrict__ v_ts, int page, int kvh, int n_kv,
+                                                uint64_t* bar) {
+  constexpr int BYTES = PAGE * HD;
+  mbar_arrive_expect_tx(bar, 2 * BYTES + 2 * PAGE * 4);
+  const int y = (page * n_kv + kvh) * PAGE;
+  tma_load_2d(kdst, tk, 0, y, bar);
+  tma_load_2d(vdst, tv, 0, y, bar);
+  bulk_g2s(sc, k_ts + (size_t)y, PAGE * 4, bar);
+  bulk_g2s(sc + PAGE, v_ts + (size_t)y, PAGE * 4, bar);
+}
+
+// sc != nullptr: the bytes are int8 and sc[key] is the key's scale (else: E4M3 bytes)
+template <int HD>
+__device__ __forceinline__ void expand_page8(const uint8_t* src, uint8_t* dst, const float* sc = nullptr) {
+  constexpr int CHUNKS = PAGE * HD / 16;          // 16 values each
   const uint32_t dbase = smem_u32(dst);
   for (int c = threadIdx.x; c < CHUNKS; c += blockDim.x) {
     const int key = c / (HD / 16), j = c % (HD / 16);
     const uint4 r = *reinterpret_cast<const uint4*>(src + (size_t)c * 16);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
     uint32_t h[8];
+    if (sc != nullptr) {
+      // (b ^ 0x80) under the exponent byte 0x64 is the fp16 number 1024 + 128 + b; one fused multiply-add takes it to b * scale, exactly
+      const __half2 s2 = __float2half2_rn(sc[key]);
+      const __half2 off = __hmul2(__float2half2_rn(-1152.f), s2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t u = w[i] ^ 0x80808080u;
+        const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140), hi = __byte_perm(u, 0x64646464u, 0x4342);
+        const __half2 a = __hfma2(*reinterpret_cast<const __half2*>(&lo), s2, off), b = __hfma2(*reinterpret_cast<const __half2*>(&hi), s2, off);
+        h[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+        h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+    } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xFFFFu), __NV_E4M3);
       const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
       h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
       h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
     }
     const uint32_t a0 = kv_chunk_addr<HD>(dbase, key, 2 * j), a1 = kv_chunk_addr<HD>(dbase, key, 2 * j + 1);
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
@@ -295,7 +330,7 @@ __host__ __device__ constexpr int dec_region_bytes(int hd, bool fp8, int mt) {
   const int merge = mt * 4 * 16 * (hd + 8) * 4;   // rows padded by 8 floats
   return stages > merge ? stages : merge;
 }
-__host__ __device__ constexpr int dec_smem_bytes(int hd, bool fp8, int mt) { return dec_region_bytes(hd, fp8, mt) + 64 + mt * 4 * 16 * 2 * 4 + 128 + 1024; }
+__host__ __device__ constexpr int dec_smem_bytes(int hd, bool fp8, int mt) { return dec_region_bytes(hd, fp8, mt) + 64 + mt * 4 * 16 * 2 * 4 + 128 + KV_STAGES * 2 * PAGE * 4 + 1024; }
 // ---- the window plan: which rows share a CTA's MMA tiles, and the flat list of work items
 // Row blocking: the 16 * MT rows of a CTA's MMA tiles hold RB = 16 MT / G consecutive window rows of ONE sequence (a verify window feeds
 // [last, d1 .. dk] of a sequence as adjacent rows) times the G query heads of one KV head, so the sequence's K / V chunk is read once per RB
@@ -349,12 +384,13 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const int* __restrict__ 
 // bits depend neither on MT nor on its block mates; more tiles only let more (row, head) pairs of one sequence share one pass over the
 // K / V chunk.  (Giving each tile its own four warps halved the CTAs per SM and was slower than two one-tile CTAs; launching one CTA per
 // row and letting the non-leaders exit cost more than the K / V reads it saved.)
-template <int HD, bool FP8, int MT>
+template <int HD, bool FP8, int MT, bool I8 = false>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2_in, int* status,
-                   const float* __restrict__ kv_scale, const int* __restrict__ plan) {
+                   const float* __restrict__ kv_scale, const int* __restrict__ plan, const float* __restrict__ k_ts, const float* __restrict__ v_ts) {
+  static_assert(!I8 || FP8, "the int8 cache uses the byte-page path");
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -364,6 +400,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
   uint8_t* conv = smem + 2 * KV_STAGES * TILE;       // FP8: the expanded fp16 K and V tiles of the page being processed
   uint64_t* bars = (uint64_t*)(smem + dec_region_bytes(HD, FP8, MT));
   volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
+  float* tsc = (float*)(bars + 8) + MT * 4 * 16 * 2 + 32;    // int8 cache: per stage 64 K scales then 64 V scales (behind the merge bookkeeping)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kw = warp;                               // this warp's 16-key slice of every page
   const int G = n_q / n_kv;
@@ -388,8 +425,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
     const int local = item - prefix[lo];
     const int row = blk_row[lo], nblk = blk_n[lo], kvh = local % n_kv, chunk = local / n_kv;
     const int seq = row_seq[row];
-    const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
-    const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
+    const float scale_log2 = (FP8 && !I8) ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
+    const float v_scale = (FP8 && !I8) ? kv_scale[n_kv + kvh] : 1.f;
     int ctx_max = 0;
     for (int i = 0; i < nblk; ++i) ctx_max = max(ctx_max, ctx_len[row + i]);
     const int k_begin = chunk * DEC_CHUNK;
@@ -401,7 +438,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       fence_proxy_async();                           // the previous item's merge wrote this memory with plain stores
       for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
         const int sg = (gp + p) % KV_STAGES;
-        if constexpr (FP8) load_kv_page8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
+        if constexpr (I8) load_kv_page_i8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, tsc + sg * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
+        else if constexpr (FP8) load_kv_page8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
         else load_kv_page<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
       }
     }
@@ -445,7 +483,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       const int s = (gp + p) % KV_STAGES;
       if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
         const int pn = p + KV_STAGES - 1, sn = (gp + pn) % KV_STAGES;  // stage sn was consumed in iteration p-1 (barrier below)
-        if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+        if constexpr (I8) load_kv_page_i8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, tsc + sn * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+        else if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
         else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
       }
       ok = mbar_wait(&bars[s], ((gp + p) / KV_STAGES) & 1, abort_flag, status, 50);
@@ -454,8 +493,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       const int kpos = k_begin + p * PAGE + key0;
       const bool any = k_end_max - kpos > 0;                        // uniform for the warp
       if constexpr (FP8) {
-        expand_page8<HD>(smem + s * TILE, conv);
-        expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
+        expand_page8<HD>(smem + s * TILE, conv, I8 ? tsc + s * 2 * PAGE : nullptr);
+        expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, I8 ? tsc + s * 2 * PAGE + PAGE : nullptr);
         __syncthreads();
       }
       if (any) {
@@ -624,12 +663,12 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 // ------------------------------------------------------------------------------------------------ prefill (causal flash)
 // Queries: rows [q_start[s], q_start[s] + q_len[s]) of `q` belong to sequence s at positions pos0[s].. ; keys are the
 // sequence's cached tokens [0, pos0 + local row] (the chunk's own K/V are already in the cache).  out: bf16 [rows][n_q*HD].
-template <int HD, bool FP8>
+template <int HD, bool FP8, bool I8 = false>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_ids, const int* __restrict__ q_start,
                     const int* __restrict__ q_len, const int* __restrict__ pos0, uint16_t* __restrict__ out, int n_q, int n_kv, float scale_log2_in,
-                    int* status, const float* __restrict__ kv_scale) {
+                    int* status, const float* __restrict__ kv_scale, const float* __restrict__ k_ts, const float* __restrict__ v_ts) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -639,6 +678,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   uint8_t* conv = smem + 2 * KV_STAGES * TILE;
   uint64_t* bars = (uint64_t*)(conv + (FP8 ? 2 * T16 : 0));
   volatile int* abort_flag = (volatile int*)(bars + KV_STAGES);
+  float* tsc = (float*)(bars + 8);                   // int8 cache: per stage 64 K scales then 64 V scales
   const int s_idx = blockIdx.z, hq = blockIdx.y;
   const int qlen = q_len[s_idx];
   // heaviest (latest) query tiles first
@@ -647,8 +687,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   if (qt < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = n_q / n_kv, kvh = hq / G;
-  const float scale_log2 = FP8 ? scale_log2_in * kv_scale[kvh] : scale_log2_in;
-  const float v_scale = FP8 ? kv_scale[n_kv + kvh] : 1.f;
+  const float scale_log2 = (FP8 && !I8) ? scale_log2_in * kv_scale[kvh] : scale_log2_in;
+  const float v_scale = (FP8 && !I8) ? kv_scale[n_kv + kvh] : 1.f;
   const int p0 = pos0[s_idx], r_base = q_start[s_idx];
   const int* bt = block_table + (size_t)seq_ids[s_idx] * max_blocks;
   const int q_lo = qt * 64;
@@ -663,7 +703,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
-      if constexpr (FP8) load_kv_page8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
+      if constexpr (I8) load_kv_page_i8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, tsc + p * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[p], kvh, n_kv, &bars[p]);
+      else if constexpr (FP8) load_kv_page8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
       else load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
     }
   }
@@ -696,7 +737,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     const int s = p % KV_STAGES;
     if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
       const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;
-      if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
+      if constexpr (I8) load_kv_page_i8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, tsc + sn * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[pn], kvh, n_kv, &bars[sn]);
+      else if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
       else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
     }
     ok = mbar_wait(&bars[s], (p / KV_STAGES) & 1, abort_flag, status, 60);
@@ -705,8 +747,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     const bool mine = kbase <= warp_last_key && q_lo + warp * 16 < qlen;
     const int v0 = lr0 < qlen ? (p0 + lr0 + 1 - kbase) : 0, v1 = lr1 < qlen ? (p0 + lr1 + 1 - kbase) : 0;
     if constexpr (FP8) {
-      expand_page8<HD>(smem + s * TILE, conv);
-      expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16);
+      expand_page8<HD>(smem + s * TILE, conv, I8 ? tsc + s * 2 * PAGE : nullptr);
+      expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, I8 ? tsc + s * 2 * PAGE + PAGE : nullptr);
       __syncthreads();
       if (mine) attn_step<HD, 64, true>(qa, smem_u32(conv), smem_u32(conv + T16), 0, v0, v1, scale_log2, m, l, o);
     } else {
@@ -746,7 +788,7 @@ static EncodeTiledFn att_encode_tiled() {
 }
 
 static int att_smem_bytes(int hd, bool fp8 = false) {
-  return (fp8 ? 2 * KV_STAGES * PAGE * hd + 2 * PAGE * hd * 2 : 2 * KV_STAGES * PAGE * hd * 2) + 64 + 1024;
+  return (fp8 ? 2 * KV_STAGES * PAGE * hd + 2 * PAGE * hd * 2 : 2 * KV_STAGES * PAGE * hd * 2) + 64 + KV_STAGES * 2 * PAGE * 4 + 1024;
 }
 
 }  // namespace rx
@@ -815,29 +857,30 @@ RX_API int rx_attn_plan(const void* row_seq, const void* ctx_len, int rows, int 
   return (int)cudaGetLastError();
 }
 
-template <int HD, bool FP8, int MT>
+template <int HD, bool FP8, int MT, bool I8>
 static int launch_decode_kernel(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                                 const int* ctx_len, float* part_o, float* part_ml, int rows, int n_q, int n_kv, int mc, float scale, int* status,
-                                cudaStream_t st, const float* kv_scale, const int* plan) {
+                                cudaStream_t st, const float* kv_scale, const int* plan, const float* k_ts, const float* v_ts) {
   constexpr int smem = dec_smem_bytes(HD, FP8, MT);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, FP8, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, FP8, MT, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   // persistent: two CTAs per SM at most, never more than the items the window can have
   const long long bound = (long long)rows * n_kv * mc;
   const int grid = (int)(bound < 2 * sm_count() ? bound : 2 * sm_count());
-  rx::launch(attn_decode_kernel<HD, FP8, MT>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq,
-             ctx_len, part_o, part_ml, n_q, n_kv, mc, scale * 1.4426950408889634f, status, kv_scale, plan);
+  rx::launch(attn_decode_kernel<HD, FP8, MT, I8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq,
+             ctx_len, part_o, part_ml, n_q, n_kv, mc, scale * 1.4426950408889634f, status, kv_scale, plan, k_ts, v_ts);
   return (int)cudaGetLastError();
 }
 
-template <int HD, bool FP8>
+template <int HD, bool FP8, bool I8 = false>
 static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                          const int* ctx_len, float* scratch, int rows, int n_q, int n_kv, int max_ctx, float scale, const void* suh, void* xr,
-                         void* out_bf16, int* status, cudaStream_t st, const float* kv_scale, int max_seq_rows, const int* plan) {
+                         void* out_bf16, int* status, cudaStream_t st, const float* kv_scale, int max_seq_rows, const int* plan,
+                         const float* k_ts = nullptr, const float* v_ts = nullptr) {
   const int mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
   int* own_plan = (int*)scratch;                    // the head of the scratch holds a plan for callers that bring none
   float* part_o = scratch + PLAN_INTS;
@@ -850,7 +893,7 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
     plan = own_plan;
   }
   int e;
-#define RX_DEC_T(MT) launch_decode_kernel<HD, FP8, MT>(tk, tv, q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, rows, n_q, n_kv, mc, scale, status, st, kv_scale, plan)
+#define RX_DEC_T(MT) launch_decode_kernel<HD, FP8, MT, I8>(tk, tv, q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, rows, n_q, n_kv, mc, scale, status, st, kv_scale, plan, k_ts, v_ts)
   if (tiles <= 1) e = RX_DEC_T(1);
   else e = RX_DEC_T(2);
 #undef RX_DEC_T
@@ -869,9 +912,21 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
 // nullptr to have it computed here into the head of the scratch.
 RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* row_seq,
                           const void* ctx_len, void* scratch, int rows, int n_q, int n_kv, int hd, int max_ctx, float scale, const void* suh,
-                          void* xr, void* out_bf16, int* status, void* stream, const void* kv_scale, int max_seq_rows, const void* plan) {
+                          void* xr, void* out_bf16, int* status, void* stream, const void* kv_scale, int max_seq_rows, const void* plan,
+                          const void* k_tscale, const void* v_tscale) {
   if (n_q % n_kv != 0 || n_q / n_kv > 16 || (n_q * hd) % 128 != 0 || rows <= 0 || rows > PLAN_MAX_ROWS || max_ctx <= 0) return (int)cudaErrorInvalidValue;
+  if ((k_tscale == nullptr) != (v_tscale == nullptr) || (k_tscale != nullptr && kv_scale != nullptr)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
+  if (k_tscale != nullptr) {
+    // int8 cache: the maps describe byte pages, k_tscale / v_tscale are f32 [pages][n_kv][64] (one power-of-two scale per token and KV head)
+#define RX_DEC8(HDV) launch_decode<HDV, true, true>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
+    (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, nullptr, max_seq_rows, \
+    (const int*)plan, (const float*)k_tscale, (const float*)v_tscale)
+    if (hd == 128) return RX_DEC8(128);
+    if (hd == 64) return RX_DEC8(64);
+#undef RX_DEC8
+    return (int)cudaErrorInvalidValue;
+  }
   // kv_scale != nullptr: the maps describe an FP8 cache and kv_scale is f32 [2][n_kv] (K scales, then V scales) of this layer
 #define RX_DEC(HDV, F8) launch_decode<HDV, F8>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
     (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, (const float*)kv_scale, \
@@ -882,20 +937,20 @@ RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q,
   return (int)cudaErrorInvalidValue;
 }
 
-template <int HD, bool FP8>
+template <int HD, bool FP8, bool I8 = false>
 static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* seq_ids,
                           const int* q_start, const int* q_len, const int* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, float scale,
-                          int* status, cudaStream_t st, const float* kv_scale) {
+                          int* status, cudaStream_t st, const float* kv_scale, const float* k_ts = nullptr, const float* v_ts = nullptr) {
   const int smem = att_smem_bytes(HD, FP8);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, FP8, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid((max_qlen + 63) / 64, n_q, nseq);
-  rx::launch(attn_prefill_kernel<HD, FP8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
-                                                          (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status, kv_scale);
+  rx::launch(attn_prefill_kernel<HD, FP8, I8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, seq_ids, q_start, q_len, pos0,
+                                                          (uint16_t*)out, n_q, n_kv, scale * 1.4426950408889634f, status, kv_scale, k_ts, v_ts);
   return (int)cudaGetLastError();
 }
 
@@ -905,8 +960,20 @@ extern "C" int rx_attn_prefill_tc(const void* tmap_k, const void* tmap_v, const 
 
 RX_API int rx_attn_prefill(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
                            const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
-                           float scale, int* status, void* stream, const void* kv_scale) {
+                           float scale, int* status, void* stream, const void* kv_scale, const void* k_tscale, const void* v_tscale) {
   if (n_q % n_kv != 0 || nseq <= 0 || max_qlen <= 0) return (int)cudaErrorInvalidValue;
+  if ((k_tscale == nullptr) != (v_tscale == nullptr) || (k_tscale != nullptr && kv_scale != nullptr)) return (int)cudaErrorInvalidValue;
+  if (k_tscale != nullptr) {
+    // int8 cache with per-token scales: the mma.sync kernel over byte pages
+    cudaStream_t st8 = (cudaStream_t)stream;
+#define RX_PF8(HDV) launch_prefill<HDV, true, true>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
+    (const int*)seq_ids, (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st8, nullptr, \
+    (const float*)k_tscale, (const float*)v_tscale)
+    if (hd == 128) return RX_PF8(128);
+    if (hd == 64) return RX_PF8(64);
+#undef RX_PF8
+    return (int)cudaErrorInvalidValue;
+  }
   // bf16 caches with 128-wide heads: the tcgen05 / tensor-memory kernel (attention_tc.cu); FP8 caches and 64-wide heads: mma.sync below
   if (hd == 128 && kv_scale == nullptr)
     return rx_attn_prefill_tc(tmap_k, tmap_v, q, block_table, max_blocks, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,

@@ -23,7 +23,9 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
                                        float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                        const int* __restrict__ slot, uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
                                        uint16_t* __restrict__ v_cache, const float* __restrict__ kv_scale, float* __restrict__ kv_amax,
-                                       const int* __restrict__ pos3, int lim_h, int lim_w) {
+                                       const int* __restrict__ pos3, int lim_h, int lim_w, float* __restrict__ k_ts, float* __restrict__ v_ts) {
+  // k_ts != nullptr: the caches are int8 with one power-of-two scale per (token, KV head), written to k_ts / v_ts (f32 [pages][n_kv][64]):
+  // scale = 2^ceil(log2(amax / 127)), value = round(x / scale) (the reference's format, crates/cuda/csrc/nemotron_kv8.cuh:1-14).
   // pos3 != nullptr: interleaved M-RoPE (reference crates/cuda/csrc/glue.cu:178-180): int32 [rows][3] = the T, H and W position of each row;
   // frequency pair i rotates by the position of axis i % 3, the H axis only below pair lim_h = 3 * section_h and the W axis only below
   // lim_w = 3 * section_w (T elsewhere).  With T = H = W this is plain RoPE, bit for bit.
@@ -108,7 +110,21 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
         for (int o = 1; o < GL; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
         if ((lane % GL) == 0) atomicMax(reinterpret_cast<unsigned*>(kv_amax) + (is_k ? 0 : n_kv) + kvh, __float_as_uint(am));   // non-negative floats order like their bits
       }
-      if (kv_scale != nullptr) {
+      if (k_ts != nullptr) {
+        float am = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
+#pragma unroll
+        for (int o = 1; o < GL; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        // smallest power of two with amax / scale <= 127, kept inside what fp16 can carry when the attention kernels multiply it back in
+        int e = am > 0.f ? (int)ceilf(log2f(am * (1.f / 127.f))) : -14;
+        e = max(-14, min(8, e));
+        const float sc = exp2f((float)e), inv = exp2f((float)-e);
+        int qv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = max(-127, min(127, __float2int_rn(y[i] * inv)));
+        const uint32_t packed = (uint32_t)(qv[0] & 0xFF) | ((uint32_t)(qv[1] & 0xFF) << 8) | ((uint32_t)(qv[2] & 0xFF) << 16) | ((uint32_t)(qv[3] & 0xFF) << 24);
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(is_k ? k_cache : v_cache) + addr) = packed;
+        if ((lane % GL) == 0) (is_k ? k_ts : v_ts)[((size_t)(sl / 64) * n_kv + kvh) * 64 + (sl % 64)] = sc;
+      } else if (kv_scale != nullptr) {
         const float inv = 1.f / kv_scale[(is_k ? 0 : n_kv) + kvh];
         const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(make_float2(y[0] * inv, y[1] * inv), __NV_SATFINITE, __NV_E4M3);
         const __nv_fp8x2_storage_t b2 = __nv_cvt_float2_to_fp8x2(make_float2(y[2] * inv, y[3] * inv), __NV_SATFINITE, __NV_E4M3);
@@ -207,7 +223,7 @@ using namespace rx;
 RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv, int hd, const void* svh, const void* bias, const void* q_norm,
                               const void* k_norm, float eps, const void* positions, const void* inv_freq, const void* slot, void* q_out,
                               void* k_cache, void* v_cache, void* stream, const void* kv_scale, void* kv_amax, const void* pos3, int section_h,
-                              int section_w) {
+                              int section_w, void* k_tscale, void* v_tscale) {
   const int N = (n_q + 2 * n_kv) * hd;
   if (N % 128) return (int)cudaErrorInvalidValue;
   const int per_row = (N / 128 + 7) / 8;   // one warp per 128-block
@@ -215,7 +231,7 @@ RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv,
   cudaStream_t st = (cudaStream_t)stream;
 #define RX_ARGS (const float*)part, S, M, n_q, n_kv, (const __half*)svh, (const float*)bias, (const uint16_t*)q_norm, (const uint16_t*)k_norm, eps, \
                 (const int*)positions, (const float*)inv_freq, (const int*)slot, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache, \
-                (const float*)kv_scale, (float*)kv_amax, (const int*)pos3, 3 * section_h, 3 * section_w
+                (const float*)kv_scale, (float*)kv_amax, (const int*)pos3, 3 * section_h, 3 * section_w, (float*)k_tscale, (float*)v_tscale
   if (hd == 128) rx::launch(finish_qkv_rope_kernel<128>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else if (hd == 64) rx::launch(finish_qkv_rope_kernel<64>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else return (int)cudaErrorInvalidValue;

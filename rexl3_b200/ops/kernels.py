@@ -178,17 +178,18 @@ def finish_swiglu_rot(part, S, M, w: Exl3Weight, suh_down: torch.Tensor, xr: tor
 
 
 def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, eps, positions, inv_freq, slot, q_out, k_cache, v_cache,
-                    kv_scale=None, kv_amax=None, pos3=None, mrope_sections=None) -> None:
+                    kv_scale=None, kv_amax=None, pos3=None, mrope_sections=None, kv_tscale=None) -> None:
     """kv_scale (f32 [2, n_kv]) given: the caches are FP8 (E4M3) and K, V are stored divided by their head's scale.  kv_amax (f32 [2, n_kv])
     given: the largest |K| and |V| per head are recorded there.  pos3 (int32 [rows, 3]: T, H, W position of every row) with
     mrope_sections = (t, h, w) frequency-pair counts: interleaved M-RoPE instead of `positions` (pair i uses axis i % 3 inside its section)."""
+    kts, vts = kv_tscale if kv_tscale is not None else (None, None)     # int8 caches: per-token scales are written there
     sec = mrope_sections or (0, 0, 0)
     assert pos3 is None or (pos3.dtype == torch.int32 and pos3.is_contiguous() and pos3.shape[1] == 3 and sum(sec) == hd // 2)
     L = _lib.load()
     _lib.check(L.rx_finish_qkv_rope(part.data_ptr(), S, M, n_q, n_kv, hd, w.svh.data_ptr(), _lib.ptr(w.bias), _lib.ptr(q_norm), _lib.ptr(k_norm),
                                     eps, positions.data_ptr(), inv_freq.data_ptr(), slot.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
-                                    v_cache.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kv_amax), _lib.ptr(pos3), int(sec[1]), int(sec[2])),
-               "rx_finish_qkv_rope")
+                                    v_cache.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kv_amax), _lib.ptr(pos3), int(sec[1]), int(sec[2]),
+                                    _lib.ptr(kts), _lib.ptr(vts)), "rx_finish_qkv_rope")
     _lib.count()
 
 
@@ -248,12 +249,13 @@ class KvTensorMap:
 
     def __init__(self, cache: torch.Tensor):
         pages, n_kv, page, hd = cache.shape
-        assert page == 64 and cache.dtype in (torch.bfloat16, torch.uint8) and cache.is_contiguous()
+        assert page == 64 and cache.dtype in (torch.bfloat16, torch.uint8, torch.int8) and cache.is_contiguous()
         self.buf = np.zeros(128, dtype=np.uint8)
         self._keep = cache
         self.fp8 = cache.dtype == torch.uint8          # E4M3 bytes
+        self.i8 = cache.dtype == torch.int8            # int8 with one scale per (token, KV head), kept beside the cache
         L = _lib.load()
-        if self.fp8:
+        if self.fp8 or self.i8:
             _lib.check(L.rx_make_kv_tmap8(self.buf.ctypes.data, cache.data_ptr(), pages * n_kv * page, hd), "rx_make_kv_tmap8")
         else:
             _lib.check(L.rx_make_kv_tmap(self.buf.ctypes.data, cache.data_ptr(), pages * n_kv * page, hd), "rx_make_kv_tmap")
@@ -269,17 +271,19 @@ def attn_decode_scratch(rows: int, n_q: int, hd: int, max_ctx: int, device="cuda
 
 
 def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_len, scratch, n_q, n_kv, hd, max_ctx, scale, suh, xr, out,
-                status, kv_scale=None, max_seq_rows: int = 1, plan=None) -> None:
+                status, kv_scale=None, max_seq_rows: int = 1, plan=None, kv_tscale=None) -> None:
     """Split-KV decode / verify-window attention.  `max_seq_rows`: the most adjacent rows one sequence has in this window (1 + drafts); it
     picks how many MMA tiles a CTA carries so that a sequence's rows share one pass over its K / V (results do not depend on it).
     `plan`: the window plan from `attn_plan` for these rows and this `max_seq_rows` (one plan serves every layer of a forward); None has
-    the call compute it itself."""
+    the call compute it itself.  `kv_tscale`: (K scales, V scales), f32 [pages, n_kv, 64] each, of an int8 cache."""
     assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
+    assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
+    kts, vts = kv_tscale if kv_tscale is not None else (None, None)
     rows = q.shape[0]
     L = _lib.load()
     _lib.check(L.rx_attn_decode(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
                                 scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out),
-                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), int(max_seq_rows), _lib.ptr(plan)), "rx_attn_decode")
+                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), int(max_seq_rows), _lib.ptr(plan), _lib.ptr(kts), _lib.ptr(vts)), "rx_attn_decode")
     _lib.count(2 if plan is not None else 3)
 
 
@@ -297,12 +301,14 @@ def attn_plan(row_seq, ctx_len, n_q: int, n_kv: int, max_seq_rows: int, plan: to
 
 
 def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,
-                 status, kv_scale=None) -> None:
+                 status, kv_scale=None, kv_tscale=None) -> None:
     assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
+    assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
+    kts, vts = kv_tscale if kv_tscale is not None else (None, None)
     L = _lib.load()
     _lib.check(L.rx_attn_prefill(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], seq_ids.data_ptr(), q_start.data_ptr(),
                                  q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
-                                 _lib.stream_ptr(), _lib.ptr(kv_scale)), "rx_attn_prefill")
+                                 _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kts), _lib.ptr(vts)), "rx_attn_prefill")
     _lib.count()
 
 

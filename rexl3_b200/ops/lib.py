@@ -93,7 +93,7 @@ def _declare(lib):
         "rx_finish_add_norm_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void]),
         "rx_finish_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_finish_qkv_rope": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void,
-                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int]),
+                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void]),
         "rx_state_digest": (c_int, [c_void, c_ll, c_void, c_void]),
         "rx_topk_scratch_bytes": (c_ll, [c_int, c_int, c_int]),
         "rx_topk": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
@@ -102,13 +102,13 @@ def _declare(lib):
         "rx_attn_decode_chunk": (c_int, []),
         "rx_attn_decode_scratch_floats": (c_ll, [c_int, c_int, c_int, c_int]),
         "rx_attn_decode": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
-                                   c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void]),
+                                   c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void]),
         "rx_attn_plan_ints": (c_int, []),
         "rx_attn_plan": (c_int, [c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
         "rx_attn_prefill_tc": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                        c_int, c_f, c_void, c_void, c_int]),
         "rx_attn_prefill": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
-                                    c_int, c_f, c_void, c_void, c_void]),
+                                    c_int, c_f, c_void, c_void, c_void, c_void, c_void]),
     }
     for name, (res, args) in sig.items():
         try:

@@ -26,14 +26,14 @@ def describe(cfg, kv_dtype: str = "bf16") -> dict:
                    state_bytes_per_slot=0, shards="experts by rank, heads by rank")
     elif isinstance(cfg, hy.HybridConfig):
         out.update(family="hybrid", weight_bytes=int(cfg.weight_params() * cfg.bits / 8) + cfg.vocab * cfg.d_model * 2,
-                   kv_bytes_per_token=int(cfg.kv_bytes_per_token(1 if kv_dtype == "fp8" else 2)), state_bytes_per_slot=int(cfg.state_bytes_per_slot()),
+                   kv_bytes_per_token=int(cfg.kv_bytes_per_token(2 if kv_dtype == "bf16" else 1)), state_bytes_per_slot=int(cfg.state_bytes_per_slot()),
                    pattern=cfg.pattern, shards="one GPU per replica")
     elif isinstance(cfg, mo.MoEConfig):
         out.update(family="moe_gqa", weight_bytes=int(cfg.weight_params() * cfg.bits / 8) + cfg.vocab * cfg.d_model * 2,
                    kv_bytes_per_token=int(cfg.kv_bytes_per_token(2)), state_bytes_per_slot=0, shards="experts by rank")
     else:
         out.update(family="dense_gqa", weight_bytes=int(cfg.weight_params() * cfg.bits / 8) + cfg.vocab * cfg.d_model * 2,
-                   kv_bytes_per_token=int(cfg.kv_bytes_per_token(1 if kv_dtype == "fp8" else 2)), state_bytes_per_slot=0,
+                   kv_bytes_per_token=int(cfg.kv_bytes_per_token(2 if kv_dtype == "bf16" else 1)), state_bytes_per_slot=0,
                    shards="columns / rows and KV heads by rank")
     return out
 
@@ -74,7 +74,7 @@ def main(argv=None) -> int:
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--slots", type=int, default=16)
     p.add_argument("--max-model-len", type=int, default=8192)
-    p.add_argument("--kv-dtype", choices=["bf16", "fp8"], default="bf16")
+    p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8"], default="bf16")
     a = p.parse_args(argv)
     try:
         if a.config:

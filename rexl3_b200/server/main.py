@@ -36,7 +36,8 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--kv-tokens", type=int, default=0, help="tokens of KV cache to reserve (0: slots * max-model-len)")
     p.add_argument("--prefill-chunk", type=int, default=4096)
     p.add_argument("--window-rows", type=int, default=64)
-    p.add_argument("--kv-dtype", choices=["bf16", "fp8"], default="bf16", help="fp8: E4M3 cache with per-head scales (calibrated at boot)")
+    p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8"], default="bf16",
+                   help="fp8: E4M3 cache with per-head scales (calibrated at boot); int8: one power-of-two scale per token and KV head (no calibration)")
     p.add_argument("--spec", choices=["auto", "mtp", "copy", "ngram", "self", "none"], default="auto")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
@@ -186,9 +187,11 @@ def build(args):
                 is_moe = isinstance(cfg, moe_models.MoEConfig)
                 from ..models import hybrid as hybrid_models
                 is_hybrid = isinstance(cfg, hybrid_models.HybridConfig)
-                if (is_mla or is_moe or is_hybrid) and args.kv_dtype == "fp8":
-                    raise RuntimeError("--kv-dtype fp8 is available for the dense GQA family")
-                kvb = cfg.kv_bytes_per_token() if is_mla else cfg.kv_bytes_per_token(1 if args.kv_dtype == "fp8" else 2)
+                if (is_mla or is_moe or is_hybrid) and args.kv_dtype != "bf16":
+                    raise RuntimeError(f"--kv-dtype {args.kv_dtype} is available for the dense GQA family")
+                kvb = cfg.kv_bytes_per_token() if is_mla else cfg.kv_bytes_per_token(2 if args.kv_dtype == "bf16" else 1)
+                if args.kv_dtype == "int8":
+                    kvb += cfg.n_layers * cfg.n_kv * 8          # one f32 scale per token, KV head and tensor
                 wbytes = int(mla_models.MlaMoEGPU.weight_bytes_estimate(cfg)) if is_mla else int(cfg.weight_params() * cfg.bits / 8)
                 if is_hybrid:
                     wbytes += cfg.state_bytes_per_slot() * args.slots      # the recurrent-state pools are resident like weights

@@ -91,6 +91,65 @@ def test_fp8_kv_cache_close_to_bf16_cache():
         assert (da - db).abs().max().item() < 0.06 * scale
 
 
+def test_int8_kv_cache_with_token_scales_close_to_bf16_cache_and_through_the_engine():
+    """int8 KV with one power-of-two scale per (token, KV head): the stored bytes and scales reproduce the bf16 cache within the quantisation step,
+    prefill (mma.sync byte-page kernel) and decode windows stay close to the bf16-cache executor, and the engine's exactness checks that touch the
+    cache (drafted == serial, cached == cold with the spill payload) hold on it."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+    from rexl3_b200.engine import harness
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    from rexl3_b200.models import dense
+    for name in ("test-hd128", "tiny-llama"):
+        cfg = dense.CONFIGS[name]
+        w = dense.random_weights(cfg, seed=3)
+        a = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+        b = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256, kv_dtype="int8")
+        rng = np.random.default_rng(0)
+        prompt = rng.integers(0, cfg.vocab, size=150).tolist()
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+        bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+        bt[1, :3] = i32([5, 9, 2])
+        T = len(prompt)
+        pos = list(range(T))
+        slots = [int(bt[1, p // 64]) * 64 + p % 64 for p in pos]
+        pf = dict(seq_ids=i32([1]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+        args = (i32(prompt), i32(pos), i32(slots), i32([1] * T), i32([p + 1 for p in pos]), bt)
+        la = a.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+        lb = b.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+        a.check(); b.check()
+        # layer 0 sees the same inputs in both executors: its int8 page times its scales is the bf16 page up to half a step
+        k16 = a.k_cache[0][5].float()
+        k8 = b.k_cache[0][5].float() * b.k_tscale[0][5][..., None]
+        step = b.k_tscale[0][5][..., None]
+        assert ((k16 - k8).abs() <= 0.5 * step + 0.01 * k16.abs() + 1e-6).all()
+        sc = b.k_tscale[0][5]
+        assert torch.equal(sc, torch.exp2(torch.round(torch.log2(sc)))) and float(b.k_cache[0][5].abs().max()) <= 127
+        scale = la.abs().max().item()
+        assert (la - lb).abs().max().item() < 0.05 * scale
+        p = T
+        a2 = (i32([7]), i32([p]), i32([int(bt[1, p // 64]) * 64 + p % 64]), i32([1]), i32([p + 1]), bt)
+        da = a.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+        db = b.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+        a.check(); b.check()
+        assert (da - db).abs().max().item() < 0.05 * scale
+    cfg = dense.CONFIGS["test-hd128"]
+    model = dense.DenseGPU(dense.random_weights(cfg, seed=3), num_pages=96, max_rows=64, max_seqs=8, max_blocks_per_seq=8, max_prefill_rows=512, kv_dtype="int8")
+    make = lambda: DenseGpuBackend(model, max_slots=8)  # noqa: E731
+    for check in ("drafted_equals_serial", "rollback_equals_replay", "cached_equals_cold", "row_invariance"):
+        assert getattr(harness, check)(make, cfg.vocab) is None, check
+    be = make()
+    from rexl3_b200.engine import Engine, generate
+    from rexl3_b200.sampling import GREEDY
+    generate(Engine(be, spec="none"), [list(range(1, 130))], 2, GREEDY)
+    handle = ("page", 3)
+    blob = be.prefix_export(handle)
+    assert len(blob) == 2 * cfg.n_layers * (cfg.n_kv * 64 * cfg.head_dim + cfg.n_kv * 64 * 4)
+    got = be.prefix_import(blob)
+    assert got is not None
+
+
 def test_per_linear_rotations_serve_and_match_the_reference(tmp_path):
     """A pack quantised one linear at a time (q / k / v and gate / up each with its own input rotation) is written, loaded and served
     through one GEMM per part; prefill and decode logits match the fp32 reference of the same weights, and the engine generates."""
