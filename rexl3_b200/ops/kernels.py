@@ -193,6 +193,28 @@ def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, ep
     _lib.count()
 
 
+def hc_mix(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scales, norm_w: torch.Tensor, coef: torch.Tensor, out: torch.Tensor, *,
+           rms_eps: float = 1e-6, hc_eps: float = 1e-6, norm_eps: float = 1e-6, iters: int = 20) -> None:
+    """Hyper-connection mix of one site: x f32 [rows, 4, D] -> coef f32 [rows, 24] (pre 4 | post 4 | comb 4x4 after Sinkhorn) and
+    out bf16 [rows, D] = RMSNorm(sum_h pre[h] x[h]) * norm_w, the sublayer's input.  fn f32 [24, 4 * D], base f32 [24], scales (s0, s1, s2)."""
+    rows, ns, D = x.shape
+    assert ns == 4 and x.dtype == torch.float32 and x.is_contiguous() and fn.shape == (24, 4 * D) and fn.dtype == torch.float32 and fn.is_contiguous()
+    assert coef.shape == (rows, 24) and coef.dtype == torch.float32 and out.shape == (rows, D) and out.dtype == torch.bfloat16 and norm_w.dtype == torch.bfloat16
+    L = _lib.load()
+    _lib.check(L.rx_hc_mix(x.data_ptr(), fn.data_ptr(), base.data_ptr(), float(scales[0]), float(scales[1]), float(scales[2]), norm_w.data_ptr(),
+                           rms_eps, hc_eps, norm_eps, iters, rows, D, coef.data_ptr(), out.data_ptr(), _lib.stream_ptr()), "rx_hc_mix")
+    _lib.count()
+
+
+def hc_apply(x: torch.Tensor, y: torch.Tensor, coef: torch.Tensor) -> None:
+    """x[h] <- post[h] y + sum_g comb[g][h] x[g], in place: x f32 [rows, 4, D], y f32 [rows, D] (the sublayer's output), coef from `hc_mix`."""
+    rows, ns, D = x.shape
+    assert ns == 4 and x.dtype == torch.float32 and x.is_contiguous() and y.shape == (rows, D) and y.dtype == torch.float32 and y.is_contiguous()
+    L = _lib.load()
+    _lib.check(L.rx_hc_apply(x.data_ptr(), y.data_ptr(), coef.data_ptr(), rows, D, _lib.stream_ptr()), "rx_hc_apply")
+    _lib.count()
+
+
 def state_digest(tensors, out: "torch.Tensor | None" = None) -> torch.Tensor:
     """Position-keyed 64-bit content digest of one tensor or of a list of tensors (each part into its own word, the words then folded on the
     host by `fold_digest`).  Returns the int64 device tensor of per-part digests; nothing synchronises here."""

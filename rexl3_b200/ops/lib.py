@@ -95,6 +95,8 @@ def _declare(lib):
         "rx_finish_qkv_rope": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void,
                                        c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void]),
         "rx_state_digest": (c_int, [c_void, c_ll, c_void, c_void]),
+        "rx_hc_mix": (c_int, [c_void, c_void, c_void, c_f, c_f, c_f, c_void, c_f, c_f, c_f, c_int, c_int, c_int, c_void, c_void, c_void]),
+        "rx_hc_apply": (c_int, [c_void, c_void, c_void, c_int, c_int, c_void]),
         "rx_topk_scratch_bytes": (c_ll, [c_int, c_int, c_int]),
         "rx_topk": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void]),
         "rx_make_kv_tmap": (c_int, [c_void, c_void, c_ll, c_int]),

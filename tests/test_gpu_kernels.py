@@ -333,3 +333,51 @@ def test_state_digest_equals_the_host_digest_and_sees_every_byte(K):
     assert da != db and da != ds                                   # one changed value, and the same rows in another order
     parts = K.state_digest([a, b]).cpu().tolist()
     assert K.fold_digest(parts) != K.fold_digest(parts[::-1])
+
+
+def _hc_reference(x, fn, base, scales, norm_w, y, rms_eps, hc_eps, norm_eps, iters):
+    """Plain float64 form of one hyper-connection site: (coef [rows, 24], sublayer input [rows, D], streams after the apply)."""
+    x, fn, base, norm_w, y = (t.double() for t in (x, fn, base, norm_w, y))
+    rows, ns, D = x.shape
+    flat = x.reshape(rows, ns * D)
+    S = flat @ fn.T
+    rmr = 1.0 / torch.sqrt((flat * flat).sum(1, keepdim=True) / (ns * D) + rms_eps)
+    pre = torch.sigmoid(S[:, :4] * rmr * scales[0] + base[:4]) + hc_eps
+    post = 2 * torch.sigmoid(S[:, 4:8] * rmr * scales[1] + base[4:8])
+    c = torch.softmax((S[:, 8:] * rmr * scales[2] + base[8:]).view(rows, 4, 4), dim=2) + hc_eps
+    c = c / (c.sum(1, keepdim=True) + hc_eps)
+    for _ in range(iters - 1):
+        c = c / (c.sum(2, keepdim=True) + hc_eps)
+        c = c / (c.sum(1, keepdim=True) + hc_eps)
+    col = (pre[:, :, None] * x).sum(1)
+    hn = col / torch.sqrt((col * col).mean(1, keepdim=True) + norm_eps) * norm_w
+    new = post[:, :, None] * y[:, None, :] + torch.einsum("rgh,rgd->rhd", c, x)
+    return torch.cat([pre, post, c.reshape(rows, 16)], 1), hn, new
+
+
+def test_hyper_connection_mix_and_apply_match_the_reference_and_are_row_invariant(K):
+    torch.manual_seed(11)
+    for D in (512, 5120):
+        rows = 7
+        x = torch.randn(rows, 4, D, device="cuda")
+        fn = torch.randn(24, 4 * D, device="cuda") / math.sqrt(4 * D)
+        base = torch.randn(24, device="cuda") * 0.5
+        scales = (0.7, 1.3, 2.0)
+        nw = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+        y = torch.randn(rows, D, device="cuda")
+        coef = torch.empty(rows, 24, device="cuda")
+        hn = torch.empty(rows, D, dtype=torch.bfloat16, device="cuda")
+        K.hc_mix(x, fn, base, scales, nw, coef, hn, iters=20)
+        want_c, want_h, want_x = _hc_reference(x, fn, base, scales, nw.float(), y, 1e-6, 1e-6, 1e-6, 20)
+        assert (coef.double() - want_c).abs().max() < 1e-4
+        comb = coef[:, 8:].view(rows, 4, 4)
+        assert (comb.sum(1) - 1).abs().max() < 1e-3 and (comb.sum(2) - 1).abs().max() < 1e-2          # Sinkhorn: (almost) doubly stochastic
+        assert (hn.double() - want_h).abs().max() < 2e-2 * want_h.abs().max()
+        x2 = x.clone()
+        K.hc_apply(x2, y, coef)
+        assert (x2.double() - want_x).abs().max() < 1e-4 * want_x.abs().max() + 1e-4
+        # a row's bits do not depend on the other rows of the launch
+        c1 = torch.empty(1, 24, device="cuda")
+        h1 = torch.empty(1, D, dtype=torch.bfloat16, device="cuda")
+        K.hc_mix(x[3:4].contiguous(), fn, base, scales, nw, c1, h1, iters=20)
+        assert torch.equal(c1[0], coef[3]) and torch.equal(h1[0], hn[3])
