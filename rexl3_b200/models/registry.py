@@ -62,6 +62,8 @@ class FamilyPlan:
     prefix_cache: bool = True
     vision: bool = False
     notes: list = field(default_factory=list)
+    servable: bool = True        # False: the family is known well enough to inventory and size it (probe / plan), no executor serves it
+    memory: dict = field(default_factory=dict)
 
 
 class Family:
@@ -164,7 +166,39 @@ class MlaMoEFamily(Family):
         return FamilyPlan(self.id, cfg, ["exl3_linear", "mla_attention", "moe_sigmoid_bias_topk", "mxfp4_experts", "shared_expert"], tp_max=8, ep=True)
 
 
-FAMILIES = (DenseFamily(), HybridFamily(), MoEFamily(), MlaMoEFamily())
+class MimoFamily(Family):
+    """MiMo-V2: probe and plan only (config, tensor inventory by count, memory), as in the reference (crates/model/src/families/mimo): the pack is
+    recognised, sized and refused by name instead of being mistaken for another family."""
+    id = "mimo"
+    architectures = ("MiMoV2ForCausalLM",)
+    model_types = ("mimo_v2",)
+
+    def plan(self, root, folder):
+        t = root.get("text_config") if isinstance(root.get("text_config"), dict) else root
+
+        def need(key, kind=int):
+            v = t.get(key)
+            if not isinstance(v, kind) or isinstance(v, bool) or v <= 0:
+                raise FamilyError("config", f"config.json: `{key}` must be a positive {kind.__name__}")
+            return v
+        d, L, nq, vocab = need("hidden_size"), need("num_hidden_layers"), need("num_attention_heads"), need("vocab_size")
+        nkv = t.get("num_key_value_heads", nq)
+        hd = t.get("head_dim", d // nq)
+        ffn = need("intermediate_size")
+        E, k, eff = t.get("n_routed_experts", t.get("num_experts", 0)) or 0, t.get("num_experts_per_tok", 0) or 0, t.get("moe_intermediate_size", 0) or 0
+        bits = float((_q(root) or {}).get("bits", 4.0))
+        attn = d * (nq + 2 * nkv) * hd + nq * hd * d
+        ffn_params = 3 * d * eff * E + d * E if E else 3 * d * ffn
+        params = L * (attn + ffn_params) + 2 * vocab * d
+        mem = dict(parameters=int(params), weight_bytes=int(params * bits / 8), kv_bytes_per_token=int(2 * L * nkv * hd * 2),
+                   active_parameters_per_token=int(L * (attn + (3 * d * eff * k if E else 3 * d * ffn)) + vocab * d))
+        comps = ["exl3_linear", "gqa_attention", "rope"] + (["moe_softmax_topk"] if E else ["swiglu_ffn"])
+        return FamilyPlan(self.id, dict(d_model=d, n_layers=L, n_q=nq, n_kv=nkv, head_dim=hd, ffn=ffn, n_experts=E, top_k=k, expert_ffn=eff, vocab=vocab,
+                                        bits=bits), comps, servable=False, memory=mem,
+                          notes=["probe / plan only: this family's executor (hybrid sliding-window attention, MTP layers, audio and vision towers) is not built"])
+
+
+FAMILIES = (DenseFamily(), HybridFamily(), MoEFamily(), MlaMoEFamily(), MimoFamily())
 
 
 def infer_components(root: dict) -> list:

@@ -13,6 +13,7 @@ import json
 import sys
 
 GPU_BYTES = 183_359 * (1 << 20)         # what a B200 reports (MiB)
+RESERVE_BYTES = 3 << 30                 # activations, scratch and allocator slack kept free on every GPU
 
 
 def describe(cfg, kv_dtype: str = "bf16") -> dict:
@@ -80,7 +81,22 @@ def main(argv=None) -> int:
         if a.config:
             cfg = find_config(a.config)
         else:
+            from .models import registry
             from .quant import quantize
+            try:
+                fam, fplan = registry.probe(a.pack)
+            except registry.FamilyError as e:
+                print(f"rexl3-plan: pack refused ({e.kind}): {e}", file=sys.stderr)
+                return 2
+            if not fplan.servable:
+                # a family this build only probes: its own memory model, sized against the GPUs asked for
+                m = dict(fplan.memory)
+                kv = m["kv_bytes_per_token"] // (2 if a.kv_dtype != "bf16" else 1) * a.max_model_len * a.slots
+                per = (m["weight_bytes"] + kv) // a.gpus + RESERVE_BYTES
+                doc = dict(family=fam.id, servable=False, notes=fplan.notes, config=fplan.config, memory=m, gpus=a.gpus, slots=a.slots,
+                           max_model_len=a.max_model_len, per_gpu_bytes=int(per), fits=bool(per <= GPU_BYTES))
+                print(json.dumps(doc, indent=1))
+                return 0 if doc["fits"] else 1
             cfg = quantize.config_from_pack(a.pack)
     except (KeyError, OSError, ValueError) as e:
         print(f"rexl3-plan: {e}", file=sys.stderr)

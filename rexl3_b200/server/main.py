@@ -119,6 +119,9 @@ def build(args):
                     family, fplan = registry.probe(folder)     # architecture -> family, refusals by name, before anything is read
                 except registry.FamilyError as e:
                     raise SystemExit(f"rexl3-serve: pack refused ({e.kind}): {e}")
+                if not fplan.servable:
+                    raise SystemExit(f"rexl3-serve: pack refused (plan_only): family `{family.id}` is known to this build for probing and memory "
+                                     f"planning only ({'; '.join(fplan.notes)}); `python -m rexl3_b200.plan --pack {folder}` sizes it")
                 cfg = fplan.config
             if args.verify_pack != "off":
                 from ..format import verify as pack_verify

@@ -136,3 +136,30 @@ def test_hostile_headers_are_refusals_by_name_never_allocations(tmp_path):
     assert "g" not in ck.groups and "marker" in ck.bad["g"]
     with pytest.raises(ValueError, match="pack refused: g: .*marker"):
         quantize.load_pack(str(d))
+
+
+def test_probe_only_family_is_sized_and_refused_by_name(tmp_path, capsys):
+    """A MiMo-V2 config is recognised, inventoried and sized (`plan`), and the server refuses it as plan-only instead of guessing a family."""
+    import json
+    from rexl3_b200 import plan as plan_cli
+    from rexl3_b200.models import registry
+    folder = tmp_path / "mimo"
+    folder.mkdir()
+    cfg = {"architectures": ["MiMoV2ForCausalLM"], "model_type": "mimo_v2", "hidden_size": 4096, "num_hidden_layers": 48, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 11008, "vocab_size": 151680, "n_routed_experts": 0,
+           "quantization_config": {"quant_method": "exl3", "bits": 4.0}}
+    (folder / "config.json").write_text(json.dumps(cfg))
+    fam, p = registry.probe(str(folder))
+    assert fam.id == "mimo" and not p.servable and p.memory["parameters"] > 7e9 and p.memory["kv_bytes_per_token"] == 2 * 48 * 8 * 128 * 2
+    assert plan_cli.main(["--pack", str(folder), "--gpus", "1", "--slots", "4", "--max-model-len", "8192"]) == 0
+    doc = json.loads(capsys.readouterr().out)
+    assert doc["family"] == "mimo" and doc["servable"] is False and doc["fits"] and "probe / plan only" in doc["notes"][0]
+    from rexl3_b200.server import main as srv
+    args = srv.parser().parse_args(["--model", str(folder), "--backend", "cpu"])
+    import pytest as _pt
+    with _pt.raises(SystemExit) as e:
+        srv.build(args)
+    assert "plan_only" in str(e.value) and "mimo" in str(e.value)
+    (folder / "config.json").write_text(json.dumps({**cfg, "hidden_size": "big"}))
+    with _pt.raises(registry.FamilyError):
+        registry.probe(str(folder))
