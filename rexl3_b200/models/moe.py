@@ -171,10 +171,15 @@ class MoEGPU(DenseGPU):
     that supplies the all-reduce slots (see parallel/ep.py); with all experts local the combine writes a local slot."""
 
     def __init__(self, w, num_pages, max_rows=256, max_seqs=64, max_blocks_per_seq=256, device="cuda", max_prefill_rows=4096, seed=0,
-                 experts=None, ep=None):
+                 experts=None, ep=None, a2a=None):
+        """`a2a` (parallel.ep.A2aComm): expert parallelism with DATA-PARALLEL rows - every rank feeds its own sequences, a (row, slot) pair
+        travels to the rank that owns its expert and its result travels back (token all-to-all); `experts` is then this rank's range."""
         cfg = w if isinstance(w, DenseConfig) else w.cfg
         self.e_lo, self.e_hi = experts or (0, cfg.n_experts)
         self.ep = ep
+        self.a2a = a2a
+        if a2a is not None and ep is not None:
+            raise ValueError("replicated-row expert parallelism (ep) and the token all-to-all (a2a) are two different layouts: pick one")
         if ctypes.sizeof(CombineDst) != _lib.load().rx_moe_combine_desc_size():
             raise _lib.KernelError("MoE combine descriptor layout mismatch")
         super().__init__(w, num_pages, max_rows, max_seqs, max_blocks_per_seq, device, max_prefill_rows, seed)
@@ -242,10 +247,15 @@ class MoEGPU(DenseGPU):
         cfg, K, dev = self.cfg, self.K, self.device
         super()._alloc_scratch(R)       # the dense scratch sizes its (unused) FFN buffers from cfg.ffn; the expert buffers follow
         k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
-        self.pairs_cap = {"decode": min(R, 256) * k, "prefill": R * k}   # rows of the sorted-pair buffers a launch of the class addresses
+        # token all-to-all: the expert side of a rank may receive every rank's pairs, so its buffers are sized for ranks x rows
+        # (whatever class this rank's own window has: a peer may be prefilling while this rank decodes)
+        a2a = getattr(self, "a2a", None) is not None
+        mult = self.a2a.R if a2a else 1
+        Rd = R if a2a else min(R, 256)
+        self.pairs_cap = {"decode": Rd * k * mult, "prefill": R * k * mult}   # rows of the sorted-pair buffers a launch of the class addresses
         self.moe_splits = {}
         part = 0
-        for cls, rows in (("decode", min(R, 256)), ("prefill", R)):
+        for cls, rows in (("decode", Rd * mult), ("prefill", R * mult)):
             decode = cls == "decode"
             # the grouped launch already spreads over experts: K splits only where a window has few pairs
             s_gu = K.plan_splits(d, 2 * F, decode) if decode else 1
@@ -258,14 +268,16 @@ class MoEGPU(DenseGPU):
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)  # noqa: E731
         self.xn = torch.empty(R, d, dtype=torch.bfloat16, device=dev)
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
-        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
+        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k * mult), i32(R * k * mult), i32(R * k * mult), i32(1)
+        self.recv_ids = i32(R * k * mult) if a2a else None
         El = self.e_hi - self.e_lo                                       # the tile table only ever names owned experts
-        self.max_tiles_decode = El + (min(R, 256) * k + 31) // 32     # windows use 16- or 32-row tiles: small tiles keep two CTAs per SM
-        self.max_tiles_prefill = El + (R * k + 127) // 128
+        # windows use 16- or 32-row tiles (small tiles keep two CTAs per SM); with the all-to-all a 16-row-tile window may receive a peer's slice
+        self.max_tiles_decode = El + ((R * k * mult + 15) // 16 if a2a else (min(R, 256) * k + 31) // 32)
+        self.max_tiles_prefill = El + (R * k * mult + 127) // 128
         self.router_logits = torch.empty(R, E, dtype=torch.float32, device=dev)
         self.tile_tab = i32(3 * max(self.max_tiles_decode, self.max_tiles_prefill))
-        self.xs = torch.zeros(R * k, d, dtype=torch.float16, device=dev)
-        self.xs2 = torch.zeros(R * k, F, dtype=torch.float16, device=dev)
+        self.xs = torch.zeros(R * k * mult, d, dtype=torch.float16, device=dev)
+        self.xs2 = torch.zeros(R * k * mult, F, dtype=torch.float16, device=dev)
         self.slot = torch.zeros(R, d, dtype=torch.float32, device=dev)        # one-rank all-reduce slot
         self._dst = CombineDst()
         self._dst.ranks, self._dst.rank, self._dst.rows_cap = 1, 0, R
@@ -274,6 +286,8 @@ class MoEGPU(DenseGPU):
     def _begin_forward(self) -> None:
         if self.ep is not None:
             self.ep.begin()
+        if self.a2a is not None:
+            self.a2a.begin()
 
     # ------------------------------------------------------------------ the routed FFN
     def _ffn(self, *a):
@@ -296,6 +310,9 @@ class MoEGPU(DenseGPU):
             tile_rows, max_tiles = (16 if M <= 16 else 32), self.max_tiles_decode
         else:
             tile_rows, max_tiles = 128, self.max_tiles_prefill
+        if self.a2a is not None:
+            yield from self._ffn_a2a(li, L, M, cls, xn, tile_rows, max_tiles, h, xr_d, next_norm, next_suh)
+            return
         _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, max_tiles, self.offs.data_ptr(),
                                    self.pos_of_pair.data_ptr(), self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(),
                                    self.total.data_ptr(), st), "rx_moe_plan")
@@ -319,6 +336,45 @@ class MoEGPU(DenseGPU):
         _lib.check(Lib.rx_tp_allsum_add_norm_rot(ar, flags, ranks, rows_cap, epoch, use, M, d, h.data_ptr(), next_norm.data_ptr(), cfg.eps,
                                                  next_suh.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(), st, None), "rx_tp_allsum_add_norm_rot")
         _lib.count(8)
+
+    def _ffn_a2a(self, li, L, M, cls, xn, tile_rows, max_tiles, h, xr_d, next_norm, next_suh):
+        """The routed FFN with a token all-to-all (the picks of this rank's rows are already in pick_ids / pick_w): dispatch -> (every rank has
+        dispatched) -> list what arrived, plan, gather + rotate, gate|up, SwiGLU, down, return -> (every rank has returned) -> weighted sum in
+        slot order, residual, norm, rotation."""
+        cfg, a = self.cfg, self.a2a
+        Lib = _lib.load()
+        st = _lib.stream_ptr()
+        k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
+        cap = self.pairs_cap[cls]
+        desc = a.desc(li)
+        if M * k > desc.cap:
+            raise ValueError(f"{M} rows x {k} picks exceed the {desc.cap}-pair all-to-all regions")
+        _lib.check(Lib.rx_moe_a2a_dispatch(xn.data_ptr(), self.pick_ids.data_ptr(), M * k, k, self.status.data_ptr(), ctypes.byref(desc), st), "rx_moe_a2a_dispatch")
+        yield          # every rank's rows must be on their way before any rank waits for them
+        recv_pairs = a.R * desc.cap
+        if recv_pairs > cap:
+            raise ValueError(f"the expert buffers hold {cap} pairs, the all-to-all may deliver {recv_pairs}")
+        _lib.check(Lib.rx_moe_a2a_recv_ids(self.recv_ids.data_ptr(), self.status.data_ptr(), ctypes.byref(desc), st), "rx_moe_a2a_recv_ids")
+        _lib.check(Lib.rx_moe_plan(self.recv_ids.data_ptr(), recv_pairs, E, self.e_lo, self.e_hi, tile_rows, max_tiles, self.offs.data_ptr(),
+                                   self.pos_of_pair.data_ptr(), self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(),
+                                   self.total.data_ptr(), st), "rx_moe_plan")
+        gu, dn = L["gu"], L["down"]
+        # a received row is a "pair" of its own (one slot per row): the flat receive index addresses the row
+        _lib.check(Lib.rx_moe_gather_rot(ctypes.c_void_p(a.rx_rows_ptr(li)), self.recv_ids.data_ptr(), self.pos_of_pair.data_ptr(), recv_pairs, 1, d,
+                                         ctypes.c_void_p(gu.suh.data_ptr() - 2 * self.e_lo * gu.K), self.xs.data_ptr(), st), "rx_moe_gather_rot")
+        s_gu, s_dn = self.moe_splits[cls]
+        self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows, cap)
+        _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), s_gu, cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
+                                         ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
+                                         self.xs2.data_ptr(), st), "rx_moe_swiglu_rot")
+        self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows, cap)
+        _lib.check(Lib.rx_moe_a2a_return(self.part.data_ptr(), s_dn, cap, self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.total.data_ptr(),
+                                         ctypes.c_void_p(dn.svh.data_ptr() - 2 * self.e_lo * dn.N), ctypes.byref(desc), st), "rx_moe_a2a_return")
+        yield          # every rank's results must be on their way home before any rank sums them
+        _lib.check(Lib.rx_moe_a2a_home(self.pick_w.data_ptr(), M, k, None, self.slot.data_ptr(), self.status.data_ptr(), ctypes.byref(desc), st), "rx_moe_a2a_home")
+        _lib.check(Lib.rx_tp_allsum_add_norm_rot(self.slot.data_ptr(), None, 1, self._dst.rows_cap, None, 0, M, d, h.data_ptr(), next_norm.data_ptr(), cfg.eps,
+                                                 next_suh.data_ptr(), xr_d.data_ptr(), self.status.data_ptr(), st, None), "rx_tp_allsum_add_norm_rot")
+        _lib.count(10)
 
     def _grouped_shifted(self, xs, st: _ExpertStack, splits, max_tiles, tile_rows, cap):
         """The tile table names GLOBAL expert ids; the stack starts at expert e_lo."""

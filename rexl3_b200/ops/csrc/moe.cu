@@ -367,6 +367,158 @@ __global__ void moe_combine_kernel(const float* __restrict__ part, int S, int pa
     tp_publish_last(tp.local_count, gridDim.x * gridDim.y, tp.dst_flag, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
 }
 
+// ------------------------------------------------------------------------------------------------ token all-to-all (data-parallel rows)
+// Expert parallelism when every rank holds DIFFERENT rows (attention ran data-parallel): a (row, slot) pair travels to the rank that owns its
+// expert and its result travels back (the reference's dispatch / combine all-to-all over NCCL, BASELINE named path 3).  Over NVLink peer memory:
+//   dispatch   every local pair's normalised row (bf16 [d]) is stored into the OWNER's receive region of this source rank at a position taken from
+//              a local counter, with (expert, source pair) beside it; the grid's last CTA publishes the per-destination counts and a ticket.
+//   recv_ids   the owner waits (bounded) for every source's ticket and lists the expert of every received row (-1 past a source's count); the
+//              existing plan / gather-rotate / grouped GEMM / SwiGLU kernels then run over that list as pairs with one slot per "row".
+//   return     finish of the down GEMM per received row (split sum, Hadamard, svh) stored as f32 into the HOME rank's return buffer at the
+//              source pair's index; last CTA publishes a ticket to every home rank.
+//   home       waits (bounded) for every owner's ticket, y[row] = sum_slot w * ret[row * topk + slot] as an fma chain in slot order - the
+//              arithmetic of moe_combine_kernel, so the result equals the one-GPU executor's bit for bit - into the f32 slot the residual /
+//              norm / rotation kernel reads.
+// Positions inside a receive region depend on the order the source's CTAs ran; nothing downstream depends on them (the grouped GEMM is
+// row-invariant and the sum is ordered by slot).  Every transfer is a plain peer store, every wait reads a LOCAL flag.
+struct A2aDesc {
+  int ranks, rank;
+  int cap;                        // rows one source may send to one destination
+  int d;
+  int e_lo[TP_MAX + 1];           // rank r owns experts [e_lo[r], e_lo[r + 1])
+  uint16_t* rx_rows[TP_MAX];      // per destination: bf16 [ranks][cap][d]
+  int* rx_meta[TP_MAX];           // per destination: int32 [ranks][cap][2] = (expert, source pair)
+  int* rx_count[TP_MAX];          // per destination: int32 [ranks]
+  unsigned* rx_flag[TP_MAX];      // per destination: [ranks]
+  float* ret[TP_MAX];             // per home rank: f32 [pairs_cap][d]
+  unsigned* ret_flag[TP_MAX];     // per home rank: [ranks]
+  int* send_count;                // local: int32 [ranks], zero between uses
+  unsigned* local_count;          // local CTA counters: [0] dispatch, [1] return
+  const unsigned* epoch;
+  unsigned use_index;
+};
+
+// grid = pairs (one CTA per local pair), 128 threads
+__global__ void __launch_bounds__(128) moe_a2a_dispatch_kernel(const uint16_t* __restrict__ xn, const int* __restrict__ ids, int pairs, int topk,
+                                                              int* status, const __grid_constant__ A2aDesc a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int s_pos, s_owner;
+  const int pair = blockIdx.x;
+  const int e = ids[pair];
+  if (threadIdx.x == 0) {
+    int o = 0;
+    while (o + 1 < a.ranks && e >= a.e_lo[o + 1]) ++o;
+    const int pos = atomicAdd(a.send_count + o, 1);
+    if (pos >= a.cap) set_status(status, ST_BAD_ARG, 170, pair);     // cannot happen: cap = the most pairs a source has
+    s_owner = o;
+    s_pos = pos < a.cap ? pos : -1;
+  }
+  __syncthreads();
+  const int o = s_owner, pos = s_pos;
+  if (pos >= 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(xn + (size_t)(pair / topk) * a.d);
+    uint4* dst = reinterpret_cast<uint4*>(a.rx_rows[o] + ((size_t)a.rank * a.cap + pos) * a.d);
+    for (int c = threadIdx.x; c < a.d / 8; c += blockDim.x) dst[c] = src[c];
+    if (threadIdx.x == 0) {
+      int* meta = a.rx_meta[o] + ((size_t)a.rank * a.cap + pos) * 2;
+      meta[0] = e;
+      meta[1] = pair;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned old = atomicAdd(a.local_count, 1u);
+    if (old == gridDim.x - 1) {
+      atomicExch(a.local_count, 0u);
+      __threadfence_system();
+      const unsigned ticket = tp_ticket(a.epoch, a.use_index);
+      for (int r = 0; r < a.ranks; ++r) {
+        const int n = atomicExch(a.send_count + r, 0);
+        a.rx_count[r][a.rank] = n < a.cap ? n : a.cap;
+      }
+      __threadfence_system();
+      for (int r = 0; r < a.ranks; ++r) st_release_sys(a.rx_flag[r] + a.rank, ticket);
+    }
+  }
+}
+
+// grid = ranks, 256 threads: recv_ids[s * cap + i] = expert of the i-th row received from source s, -1 past its count
+__global__ void __launch_bounds__(256) moe_a2a_recv_ids_kernel(int* __restrict__ recv_ids, int* status, const __grid_constant__ A2aDesc a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int s_n;
+  const int s = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const bool ok = tp_wait_flag(a.rx_flag[a.rank] + s, tp_ticket(a.epoch, a.use_index), status, 171);
+    s_n = ok ? (int)ld_acquire_sys(reinterpret_cast<const unsigned*>(a.rx_count[a.rank] + s)) : 0;
+  }
+  __syncthreads();
+  const int n = s_n;
+  const int* meta = a.rx_meta[a.rank] + (size_t)s * a.cap * 2;
+  for (int i = threadIdx.x; i < a.cap; i += blockDim.x) recv_ids[(size_t)s * a.cap + i] = i < n ? meta[2 * i] : -1;
+}
+
+// grid = (positions capacity, gy).  part: f32 [S][pairs_cap][d] (down GEMM over the received rows); pair_of_pos maps a position to the flat receive
+// index q = source * cap + i.
+__global__ void moe_a2a_return_kernel(const float* __restrict__ part, int S, int pairs_cap, const int* __restrict__ pair_of_pos,
+                                      const int* __restrict__ expert_of_pos, const int* __restrict__ total, const __half* __restrict__ svh_down,
+                                      const __grid_constant__ A2aDesc a) {
+  pdl_launch();
+  pdl_wait();
+  const int pos = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (pos < *total) {
+    const int q = pair_of_pos[pos], e = expert_of_pos[pos];
+    const int src = q / a.cap;
+    const int src_pair = a.rx_meta[a.rank][(size_t)q * 2 + 1];
+    const size_t plane = (size_t)pairs_cap * a.d;
+    for (int b = blockIdx.y * nw + warp; b < a.d / 128; b += gridDim.y * nw) {
+      const int n0 = b * 128 + lane * 4;
+      float y[4];
+      moe_finish_block(part, S, plane, (size_t)pos * a.d + n0, svh_down == nullptr ? nullptr : svh_down + (size_t)e * a.d + n0, y);
+      *reinterpret_cast<float4*>(a.ret[src] + (size_t)src_pair * a.d + n0) = make_float4(y[0], y[1], y[2], y[3]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tp_publish_last(a.local_count + 1, gridDim.x * gridDim.y, a.ret_flag, a.ranks, a.rank, tp_ticket(a.epoch, a.use_index));
+}
+
+// grid = (M, gy): out f32 [M][d] = sum over slots (in slot order) of w * returned row (+ shared[row])
+__global__ void moe_a2a_home_kernel(const float* __restrict__ w, int M, int topk, const float* __restrict__ shared, float* __restrict__ out, int* status,
+                                    const __grid_constant__ A2aDesc a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    const unsigned ticket = tp_ticket(a.epoch, a.use_index);
+    for (int r = 0; r < a.ranks && ok; ++r) ok = tp_wait_flag(a.ret_flag[a.rank] + r, ticket, status, 172);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* ret = a.ret[a.rank];
+  for (int b = blockIdx.y * nw + warp; b < a.d / 128; b += gridDim.y * nw) {
+    const int n0 = b * 128 + lane * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+      const int pair = row * topk + j;
+      // written by a peer: read around the non-coherent cache
+      float4 y;
+      asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(y.x), "=f"(y.y), "=f"(y.z), "=f"(y.w) : "l"(ret + (size_t)pair * a.d + n0));
+      const float wj = w[pair];
+      acc[0] = fmaf(wj, y.x, acc[0]); acc[1] = fmaf(wj, y.y, acc[1]); acc[2] = fmaf(wj, y.z, acc[2]); acc[3] = fmaf(wj, y.w, acc[3]);
+    }
+    if (shared != nullptr) {
+      const float4 sh = *reinterpret_cast<const float4*>(shared + (size_t)row * a.d + n0);
+      acc[0] += sh.x; acc[1] += sh.y; acc[2] += sh.z; acc[3] += sh.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)row * a.d + n0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  }
+}
+
 }  // namespace rx
 
 using namespace rx;
@@ -436,4 +588,39 @@ RX_API int rx_moe_combine(const void* part, int S, int pairs_cap, int M, int d, 
   if (warps > 8) warps = 8;
   return (int)rx::launch(moe_combine_kernel, dim3(M, gy), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, pairs_cap, M, d, topk,
                          (const int*)ids, (const float*)w, (const int*)pos_of_pair, (const __half*)svh_down, (const float*)shared, tp);
+}
+
+// ---- token all-to-all launchers (desc: host copy of A2aDesc)
+RX_API int rx_moe_a2a_desc_size() { return (int)sizeof(A2aDesc); }
+
+RX_API int rx_moe_a2a_dispatch(const void* xn, const void* ids, int pairs, int topk, int* status, const void* desc, void* stream) {
+  if (desc == nullptr || pairs < 1 || topk < 1) return (int)cudaErrorInvalidValue;
+  const A2aDesc a = *(const A2aDesc*)desc;
+  if (a.ranks < 1 || a.ranks > TP_MAX || a.d % 128 != 0 || pairs > a.cap) return (int)cudaErrorInvalidValue;
+  return (int)rx::launch(moe_a2a_dispatch_kernel, dim3(pairs), dim3(128), 0, (cudaStream_t)stream, (const uint16_t*)xn, (const int*)ids, pairs, topk, status, a);
+}
+
+RX_API int rx_moe_a2a_recv_ids(void* recv_ids, int* status, const void* desc, void* stream) {
+  if (desc == nullptr) return (int)cudaErrorInvalidValue;
+  const A2aDesc a = *(const A2aDesc*)desc;
+  return (int)rx::launch(moe_a2a_recv_ids_kernel, dim3(a.ranks), dim3(256), 0, (cudaStream_t)stream, (int*)recv_ids, status, a);
+}
+
+RX_API int rx_moe_a2a_return(const void* part, int S, int pairs_cap, const void* pair_of_pos, const void* expert_of_pos, const void* total,
+                             const void* svh_down, const void* desc, void* stream) {
+  if (desc == nullptr || S < 1 || pairs_cap < 1) return (int)cudaErrorInvalidValue;
+  const A2aDesc a = *(const A2aDesc*)desc;
+  const int blocks = a.d / 128;
+  int warps = blocks < 8 ? blocks : 8;
+  return (int)rx::launch(moe_a2a_return_kernel, dim3(pairs_cap, 1), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, pairs_cap,
+                         (const int*)pair_of_pos, (const int*)expert_of_pos, (const int*)total, (const __half*)svh_down, a);
+}
+
+RX_API int rx_moe_a2a_home(const void* w, int M, int topk, const void* shared, void* out, int* status, const void* desc, void* stream) {
+  if (desc == nullptr || M < 1) return (int)cudaErrorInvalidValue;
+  const A2aDesc a = *(const A2aDesc*)desc;
+  const int blocks = a.d / 128;
+  int warps = blocks < 8 ? blocks : 8;
+  return (int)rx::launch(moe_a2a_home_kernel, dim3(M, 1), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)w, M, topk, (const float*)shared, (float*)out,
+                         status, a);
 }

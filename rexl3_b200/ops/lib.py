@@ -66,6 +66,11 @@ def _declare(lib):
         "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_combine_desc_size": (c_int, []),
+        "rx_moe_a2a_desc_size": (c_int, []),
+        "rx_moe_a2a_dispatch": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void, c_void]),
+        "rx_moe_a2a_recv_ids": (c_int, [c_void, c_void, c_void, c_void]),
+        "rx_moe_a2a_return": (c_int, [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
+        "rx_moe_a2a_home": (c_int, [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_verify_desc_size": (c_int, []),
         "rx_trellis_encode_scratch_bytes": (c_ll, [c_int]),
         "rx_trellis_encode_cuda": (c_int, [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_void]),

@@ -177,6 +177,57 @@ def test_expert_parallel_loopback_matches_single(ranks):
     assert torch.equal(o2[0], o2[-1]) and (o2[0] - w2).abs().max().item() < 0.02 * scale
 
 
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_token_all_to_all_expert_parallel_equals_single_gpu(ranks):
+    """Data-parallel rows with a token all-to-all: every rank feeds its OWN sequence, (row, slot) pairs travel to the rank that owns their expert
+    and the results travel home; stepped phase by phase on one GPU.  Each rank's logits equal the one-GPU executor's on that sequence bit for
+    bit (same finish, same slot-ordered fma chain), in prefill and in a decode step."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.parallel import ep
+    cfg, w, moe = _setup(seed=4)
+    single = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    comms = ep.make_a2a_loopback(cfg, ranks, 256)
+    shards = [moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256,
+                         experts=ep.expert_range(cfg.n_experts, r, ranks), a2a=comms[r]) for r in range(ranks)]
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (70, 45, 9, 130)[:ranks]]
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[0, :3] = _i32([3, 7, 5])
+
+    def rows_of(tokens, p0):
+        pos = list(range(p0, p0 + len(tokens)))
+        return (_i32(tokens), _i32(pos), _i32([int(bt[0, p // 64]) * 64 + p % 64 for p in pos]), _i32([0] * len(pos)), _i32([p + 1 for p in pos]), bt)
+
+    def run(per_rank):
+        gens = [s.forward_phases(*a, **kw) for s, (a, kw) in zip(shards, per_rank)]
+        outs, live = [None] * ranks, ranks
+        while live:
+            for r, g in enumerate(gens):
+                if outs[r] is not None:
+                    continue
+                try:
+                    next(g)
+                except StopIteration as e:
+                    outs[r] = e.value[:, :cfg.vocab].clone()
+                    live -= 1
+        torch.cuda.synchronize()
+        for s in shards:
+            s.check()
+        return outs
+
+    pf = lambda n: dict(seq_ids=_i32([0]), q_start=_i32([0]), q_len=_i32([n]), pos0=_i32([0]), nseq=1, max_qlen=n)  # noqa: E731
+    outs = run([(rows_of(p, 0), dict(prefill=pf(len(p)))) for p in prompts])
+    for r, p in enumerate(prompts):
+        want = single.forward_rows(*rows_of(p, 0), prefill=pf(len(p)))[:, :cfg.vocab].clone()
+        assert torch.equal(outs[r], want), r
+    outs = run([(rows_of([5 + r], len(p)), dict(max_ctx=256)) for r, p in enumerate(prompts)])
+    for r, p in enumerate(prompts):
+        single.forward_rows(*rows_of(p, 0), prefill=pf(len(p)))
+        want = single.forward_rows(*rows_of([5 + r], len(p)), max_ctx=256)[:, :cfg.vocab].clone()
+        assert torch.equal(outs[r], want), r
+
+
 @pytest.mark.parametrize("rows,tile_rows", [(5, 16), (70, 32)])
 def test_mxfp4_grouped_gemm_matches_dequantized_reference(rows, tile_rows):
     if not torch.cuda.is_available():
