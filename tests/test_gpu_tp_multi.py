@@ -47,3 +47,17 @@ def test_tp_windows_above_the_packet_size_with_the_in_switch_sum():
            "-m", "rexl3_b200.parallel.selftest", "--streams", "24"]
     r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
     assert r.returncode == 0 and "TP_SELFTEST_OK ranks=2" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_token_all_to_all_over_gpus_equals_one_gpu(ranks):
+    """Data-parallel rows + token all-to-all over NVLink peer memory, one process per GPU: every rank's logits on its own sequence equal
+    the one-GPU executor's bit for bit (prefill and decode steps)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29560 + ranks), "-m", "rexl3_b200.parallel.a2a_selftest", "--skip-timing"]
+    r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
+    assert r.returncode == 0 and '"bitwise_equal_to_one_gpu": true' in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
