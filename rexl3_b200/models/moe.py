@@ -5,6 +5,7 @@ FFN of a layer: router (f16/bf16 gate, fp32 scores, exact top-k) -> on-device pl
 rotation -> grouped EXL3 GEMM gate|up -> SwiGLU + rotation -> grouped EXL3 GEMM down -> top-k weighted sum in slot order ->
 residual / norm / next rotation.  Under expert parallelism every rank holds the experts [e_lo, e_hi); activations are replicated,
 so dispatch moves no bytes and the combine is a one-shot all-reduce of each rank's weighted partial rows (summed in rank order).
+With data-parallel rows (`a2a=`) the pairs travel to the expert's owner and back over peer memory (token all-to-all, `_ffn_a2a`).
 Semantics: reference crates/cuda/csrc/fmoe.cu:11-13 (softmax top-k, renormalised), moe_router.cu:3-13 (sigmoid + bias),
 moe_experts.cu:379 (combine), crates/cuda/src/moe_owned.rs:1-30 (expert ownership).
 """
