@@ -27,6 +27,10 @@ from ..ops import lib as _lib
 from .dense import PAGE, HostLinear, _bf16_round, random_linear
 from .moe import CombineDst, route_reference
 
+DSA_H, DSA_D, DSA_P = 32, 128, 4            # index heads, index head dim, tokens per pool (the kernels' geometry)
+DSA_GROUP = 128                             # sparse rows selected / gathered / attended per launch group
+DSA_COL_K, DSA_COL_G, DSA_COL_W = 2176, 2304, 2432
+
 
 @dataclass
 class MlaConfig:
@@ -51,6 +55,21 @@ class MlaConfig:
     bits_a: float = 2.0        # 2.25 bpw overall: the big projections at 2.0 ...
     bits_b: float = 2.5        # ... and the small / sensitive ones at 2.5 (half widths use the mul1 codebook)
     name: str = "mla-moe-671b"
+    # sparse attention (DeepSeek sparse attention with pooled index keys, reference crates/cuda/csrc/dsa.cuh:1-16): 32 index heads x 128, 4-token
+    # pools; a row with more than `dsa_dense_below` tokens of context attends to its `dsa_sel_pools` best pools (+ the incomplete last pool) only
+    dsa: bool = False
+    dsa_sel_pools: int = 512
+    dsa_dense_below: int = 2048
+
+    @property
+    def a_width(self):
+        """Columns of the fused q_a | kv_a projection: 1536 | 512 | 64 | pad 64, then with the indexer: key 128 | gate 128 | head weights 32 | pad 96."""
+        return 2176 + (384 if self.dsa else 0)
+
+    @property
+    def qb_extra(self):
+        """Index-query columns appended to q_b (32 heads x 128), replicated on every head-parallel rank."""
+        return DSA_H * DSA_D if self.dsa else 0
 
     @property
     def vocab_padded(self):
@@ -71,7 +90,10 @@ def config_from_dict(c: dict) -> MlaConfig:
                     n_experts=int(c.get("n_routed_experts", 256)), top_k=int(c.get("num_experts_per_tok", 8)), expert_ffn=int(c.get("moe_intermediate_size", 2048)),
                     shared_ffn=int(c.get("moe_intermediate_size", 2048)) * int(c.get("n_shared_experts", 1)), routed_scale=float(c.get("routed_scaling_factor", 2.5)),
                     vocab=c["vocab_size"], eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), bits_a=float(q.get("bits_a", 2.0)),
-                    bits_b=float(q.get("bits_b", 2.5)), name=c.get("name", "mla-moe"))
+                    bits_b=float(q.get("bits_b", 2.5)), name=c.get("name", "mla-moe"), dsa=bool(c.get("index_topk")) and bool(c.get("index_kpool", 4)),
+                    dsa_sel_pools=int(c.get("index_topk", 2048)) // DSA_P, dsa_dense_below=int(c.get("index_dense_below", c.get("index_topk", 2048))))
+    if cfg.dsa and (int(c.get("index_n_heads", DSA_H)), int(c.get("index_head_dim", DSA_D)), int(c.get("index_kpool", DSA_P))) != (DSA_H, DSA_D, DSA_P):
+        raise ValueError("the sparse-attention indexer kernels are written for 32 index heads x 128 with 4-token pools")
     if (cfg.q_lora, cfg.kv_lora, cfg.rope_dim, cfg.nope_dim, cfg.v_dim) != (1536, 512, 64, 128, 128):
         raise ValueError(f"MLA geometry q_lora {cfg.q_lora} / kv_lora {cfg.kv_lora} / rope {cfg.rope_dim} / nope {cfg.nope_dim} / v {cfg.v_dim} "
                          f"is not the 1536 / 512 / 64 / 128 / 128 the latent attention kernels are written for")
@@ -103,6 +125,9 @@ class HostMlaLayer:
     router_bias: np.ndarray = None
     ex_gu: list = field(default_factory=list)     # per expert (packed uint8 [2F, d/2], scales uint8 [2F, d/32])
     ex_down: list = field(default_factory=list)   # per expert (packed uint8 [d, F/2], scales uint8 [d, F/32])
+    idx_ln_w: np.ndarray = None  # sparse indexer: LayerNorm weight / bias of the index key (f32 [128]) ...
+    idx_ln_b: np.ndarray = None
+    idx_ape: np.ndarray = None   # ... and the pool-member bias of the gate softmax (f32 [4, 128])
 
 
 @dataclass
@@ -120,11 +145,15 @@ def random_mla_weights(cfg: MlaConfig, seed: int = 0) -> HostMla:
     nrm = lambda n: _bf16_round(1.0 + 0.1 * rng.normal(size=n))  # noqa: E731
     layers = []
     for li in range(cfg.n_layers):
-        qkv_a = random_linear(d, 2176, cfg.bits_b, rng, "mul1", 1.0 / math.sqrt(d), zero_cols_from=2112)
-        q_b = random_linear(1536, H * 192, cfg.bits_a, rng, "3inst", 1.0 / math.sqrt(1536))
+        qkv_a = random_linear(d, cfg.a_width, cfg.bits_b, rng, "mul1", 1.0 / math.sqrt(d), zero_cols_from=None if cfg.dsa else 2112)
+        q_b = random_linear(1536, H * 192 + cfg.qb_extra, cfg.bits_a, rng, "3inst", 1.0 / math.sqrt(1536))
         o = random_linear(H * 128, d, cfg.bits_a, rng, "3inst", 0.5 / math.sqrt(H * 128))
         lay = HostMlaLayer(nrm(d), qkv_a, nrm(1536), nrm(512), q_b, _bf16_round(rng.normal(0, 1 / math.sqrt(128), size=(H, 128, 512))),
                            _bf16_round(rng.normal(0, 1 / math.sqrt(512), size=(H, 512, 128))), o, nrm(d))
+        if cfg.dsa:
+            lay.idx_ln_w = (1.0 + 0.1 * rng.normal(size=DSA_D)).astype(np.float32)
+            lay.idx_ln_b = (0.1 * rng.normal(size=DSA_D)).astype(np.float32)
+            lay.idx_ape = (0.5 * rng.normal(size=(DSA_P, DSA_D))).astype(np.float32)
         if li < cfg.n_dense:
             F = cfg.dense_ffn
             lay.gate_up = random_linear(d, 2 * F, cfg.bits_a, rng, "3inst", 1.0 / math.sqrt(d))
@@ -160,6 +189,8 @@ class ReferenceMla:
             L = dict(attn_norm=t(lay.attn_norm), qkv_a=t(lay.qkv_a.dense()), q_norm=t(lay.q_norm), kv_norm=t(lay.kv_norm), q_b=t(lay.q_b.dense()),
                      w_uk=t(lay.w_uk), w_uv=t(lay.w_uv), o=t(lay.o.dense()), ffn_norm=t(lay.ffn_norm), gate_up=t(lay.gate_up.dense()),
                      down=t(lay.down.dense()), router=None)
+            if w.cfg.dsa:
+                L.update(idx_ln_w=t(lay.idx_ln_w), idx_ln_b=t(lay.idx_ln_b), idx_ape=t(lay.idx_ape))
             if lay.router is not None:
                 L.update(router=t(lay.router), router_bias=t(lay.router_bias), gu=[t(mxfp4.dequant(*e)) for e in lay.ex_gu],
                          dn=[t(mxfp4.dequant(*e)) for e in lay.ex_down])
@@ -168,6 +199,42 @@ class ReferenceMla:
         self.lm_head = t(w.lm_head.dense())[:, :w.cfg.vocab]
         self.inv_freq = torch.from_numpy(mla_inv_freq(w.cfg)).to(device)
         self.kv = {}
+        self.idx = {}          # sparse indexer: per sequence and layer the (key, gate) rows of every token
+        self.last_selection = {}
+
+    def _dsa_allowed(self, seq, li, L, a, q_idx, pos, start):
+        """-> bool [T, keys]: which keys each row of the sparse regime may attend to (None: every row is dense).  Planes and scores are rounded to
+        the storage types of the device path (bf16 planes, fp16 scores) so that ties fall the same way."""
+        cfg = self.cfg
+        bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+        k_n = bf(torch.nn.functional.layer_norm(bf(a[:, DSA_COL_K:DSA_COL_K + DSA_D]), (DSA_D,), L["idx_ln_w"], L["idx_ln_b"], 1e-6))
+        gate = bf(a[:, DSA_COL_G:DSA_COL_G + DSA_D])
+        wh = bf(a[:, DSA_COL_W:DSA_COL_W + DSA_H])
+        pk, pg = self.idx.setdefault(seq, {}).get(li, (k_n[:0], gate[:0]))
+        kk, gg = torch.cat([pk[:start], k_n]), torch.cat([pg[:start], gate])
+        self.idx[seq][li] = (kk, gg)
+        if int(pos[-1]) + 1 <= cfg.dsa_dense_below:
+            return None
+        n_pools = kk.shape[0] // DSA_P
+        km, gm = kk[:n_pools * DSA_P].view(n_pools, DSA_P, DSA_D), gg[:n_pools * DSA_P].view(n_pools, DSA_P, DSA_D)
+        pooled = bf((torch.softmax(gm + L["idx_ape"][None], dim=1) * km).sum(1))                          # [pools, 128]
+        T, n_keys = a.shape[0], kk.shape[0]
+        allowed = torch.ones(T, n_keys, dtype=torch.bool, device=a.device)
+        for t in range(T):
+            p = int(pos[t])
+            if p + 1 <= cfg.dsa_dense_below:
+                continue
+            vis = (p + 1) // DSA_P
+            dots = torch.relu(bf(q_idx[t]) @ pooled[:vis].T)                                               # [32, vis]
+            sc = ((dots * wh[t][:, None]).sum(0) / math.sqrt(DSA_H * DSA_D)).to(torch.float16)
+            order = torch.sort(sc.float(), descending=True, stable=True).indices[:cfg.dsa_sel_pools]      # ties: lowest pool index first
+            pools = torch.sort(order).values
+            toks = (pools[:, None] * DSA_P + torch.arange(DSA_P, device=a.device)[None]).reshape(-1)
+            toks = torch.cat([toks, torch.arange(vis * DSA_P, p + 1, device=a.device)])
+            allowed[t] = False
+            allowed[t, toks] = True
+            self.last_selection[(seq, li, p)] = toks.tolist()
+        return allowed
 
     @staticmethod
     def _rms(x, w, eps):
@@ -193,7 +260,9 @@ class ReferenceMla:
         for li, L in enumerate(self.layers):
             x = self._rms(h, L["attn_norm"], cfg.eps)
             a = x @ L["qkv_a"]
-            q = (self._rms(a[:, :1536], L["q_norm"], cfg.eps) @ L["q_b"]).view(T, H, 192)
+            qb_out = self._rms(a[:, :1536], L["q_norm"], cfg.eps) @ L["q_b"]
+            q = qb_out[:, :H * 192].view(T, H, 192)
+            allowed = self._dsa_allowed(seq, li, L, a, qb_out[:, H * 192:].view(T, DSA_H, DSA_D), pos, start) if cfg.dsa else None
             c = self._rms(a[:, 1536:2048], L["kv_norm"], cfg.eps)
             kr = self._rope(a[:, 2048:2112], pos)
             pc, pr = self.kv[seq][li]
@@ -204,6 +273,8 @@ class ReferenceMla:
             s = (torch.einsum("thc,sc->hts", q_lat, cc) + torch.einsum("thr,sr->hts", q_rope, rr)) / math.sqrt(192)
             kpos = torch.arange(cc.shape[0], device=self.device)
             s = s.masked_fill((kpos[None, :] > pos[:, None])[None], float("-inf"))
+            if allowed is not None:
+                s = s.masked_fill(~allowed[None], float("-inf"))
             o_lat = torch.einsum("hts,sc->thc", torch.softmax(s, dim=-1), cc)
             o = torch.einsum("thc,hcv->thv", o_lat, L["w_uv"]).reshape(T, H * 128)
             h = h + o @ L["o"]
@@ -283,12 +354,16 @@ class MlaMoEGPU:
         self.layers = []
         for lay in w.layers:
             qb = lay.q_b
-            qb_l = HostLinear(np.ascontiguousarray(qb.trellis[:, hl * 12:hh * 12]), qb.suh, np.ascontiguousarray(qb.svh[hl * 192:hh * 192]), None, qb.codebook)
+            H = self.cfg.n_heads      # this rank's heads, then (sparse attention) the index-query columns every rank keeps
+            qb_l = HostLinear(np.ascontiguousarray(np.concatenate([qb.trellis[:, hl * 12:hh * 12], qb.trellis[:, H * 12:]], axis=1)), qb.suh,
+                              np.ascontiguousarray(np.concatenate([qb.svh[hl * 192:hh * 192], qb.svh[H * 192:]])), None, qb.codebook)
             o = lay.o
             o_l = HostLinear(np.ascontiguousarray(o.trellis[hl * 8:hh * 8]), np.ascontiguousarray(o.suh[hl * 128:hh * 128]), o.svh, None, o.codebook)
             L = dict(attn_norm=t(lay.attn_norm, torch.bfloat16), qkv_a=up(lay.qkv_a), q_norm=t(lay.q_norm, torch.bfloat16), kv_norm=t(lay.kv_norm, torch.bfloat16),
                      q_b=up(qb_l), w_uk=t(lay.w_uk[hl:hh], torch.bfloat16), w_uv=t(lay.w_uv[hl:hh], torch.bfloat16), o=up(o_l),
                      ffn_norm=t(lay.ffn_norm, torch.bfloat16), gate_up=up(lay.gate_up), down=up(lay.down), router=None)
+            if self.cfg.dsa:
+                L.update(idx_ln_w=t(lay.idx_ln_w, torch.float32), idx_ln_b=t(lay.idx_ln_b, torch.float32), idx_ape=t(lay.idx_ape, torch.float32))
             if lay.router is not None:
                 L.update(router=t(lay.router, torch.bfloat16), router_bias=t(lay.router_bias, torch.float32),
                          gu_w=torch.from_numpy(np.stack([e[0].view(np.uint8) for e in lay.ex_gu[el:eh]])).to(dev),
@@ -323,13 +398,17 @@ class MlaMoEGPU:
         self.layers = []
         E = self.e_hi - self.e_lo
         for li in range(cfg.n_layers):
-            qkv_a = lin(d, 2176, 1.0 / math.sqrt(d), cfg.bits_b, g)
-            qkv_a.svh[2112:] = 0
+            qkv_a = lin(d, cfg.a_width, 1.0 / math.sqrt(d), cfg.bits_b, g)
+            qkv_a.svh[2112:2176] = 0
             su_qb = sg(1536, g).to(torch.float16)
-            L = dict(attn_norm=nrm(d), qkv_a=qkv_a, q_norm=nrm(1536), kv_norm=nrm(512), q_b=lin(1536, Hl * 192, 1.0 / math.sqrt(1536), cfg.bits_a, gl, su_qb),
+            L = dict(attn_norm=nrm(d), qkv_a=qkv_a, q_norm=nrm(1536), kv_norm=nrm(512),
+                     q_b=lin(1536, Hl * 192 + cfg.qb_extra, 1.0 / math.sqrt(1536), cfg.bits_a, gl, su_qb),
                      w_uk=(torch.randn(Hl, 128, 512, device=dev, generator=gl) / math.sqrt(128)).to(torch.bfloat16),
                      w_uv=(torch.randn(Hl, 512, 128, device=dev, generator=gl) / math.sqrt(512)).to(torch.bfloat16),
                      o=lin(Hl * 128, d, 0.5 / math.sqrt(cfg.n_heads * 128), cfg.bits_a, gl), ffn_norm=nrm(d), router=None)
+            if cfg.dsa:
+                L.update(idx_ln_w=1.0 + 0.1 * torch.randn(DSA_D, device=dev, generator=g), idx_ln_b=0.1 * torch.randn(DSA_D, device=dev, generator=g),
+                         idx_ape=0.5 * torch.randn(DSA_P, DSA_D, device=dev, generator=g))
             F = cfg.dense_ffn if li < cfg.n_dense else cfg.shared_ffn
             L["gate_up"] = lin(d, 2 * F, 1.0 / math.sqrt(d), cfg.bits_a, g)
             L["down"] = lin(F, d, 0.5 / math.sqrt(F), cfg.bits_b, g)
@@ -369,7 +448,7 @@ class MlaMoEGPU:
         self.splits = {}
         part = 0
         Fmax = max(cfg.dense_ffn, cfg.shared_ffn)
-        shapes = dict(qkv_a=(d, 2176), q_b=(1536, Hl * 192), o=(Hl * 128, d), gu_dense=(d, 2 * cfg.dense_ffn), dn_dense=(cfg.dense_ffn, d),
+        shapes = dict(qkv_a=(d, cfg.a_width), q_b=(1536, Hl * 192 + cfg.qb_extra), o=(Hl * 128, d), gu_dense=(d, 2 * cfg.dense_ffn), dn_dense=(cfg.dense_ffn, d),
                       gu_sh=(d, 2 * cfg.shared_ffn), dn_sh=(cfg.shared_ffn, d), lm_head=(d, cfg.vocab_padded))
         for cls, rows in (("decode", Rw), ("prefill", R)):
             for name, (kk, nn) in shapes.items():
@@ -387,9 +466,11 @@ class MlaMoEGPU:
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)  # noqa: E731
         self.h, self.xn = bf(R, d), bf(R, d)
         self.xr_d = hf(R, d)
-        self.a_out = bf(R, 2176)
+        self.a_out = bf(R, cfg.a_width)
         self.xr_q = hf(R, 1536)
-        self.q_full = bf(R, Hl * 192)
+        self.q_full = bf(R, Hl * 192 + cfg.qb_extra)
+        if cfg.dsa:
+            self._alloc_dsa(R)
         self.q = bf(R, Hl, 576)
         self.o_lat = bf(R, Hl, 512)
         self.o_heads = bf(R, Hl * 128)
@@ -397,7 +478,10 @@ class MlaMoEGPU:
         self.xr_f = hf(R, Fmax)
         self.shared = torch.zeros(R, d, dtype=torch.float32, device=dev)
         self.logits = torch.empty(Rw, cfg.vocab_padded, dtype=torch.float32, device=dev)
-        self.attn_scratch = torch.empty(_lib.load().rx_mla_scratch_floats(R, Hl, self.max_ctx_alloc), dtype=torch.float32, device=dev)
+        n_scratch = _lib.load().rx_mla_scratch_floats(R, Hl, self.max_ctx_alloc)
+        if cfg.dsa:        # a group of sparse rows attends over its scratch pages: fewer rows, but up to 3 splits each
+            n_scratch = max(n_scratch, _lib.load().rx_mla_scratch_floats(min(R, DSA_GROUP), Hl, self.dsa_pages * PAGE))
+        self.attn_scratch = torch.empty(n_scratch, dtype=torch.float32, device=dev)
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
         E = cfg.n_experts
         self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
@@ -410,6 +494,53 @@ class MlaMoEGPU:
         self.topk_scratch = K.topk_scratch(Rw, cfg.vocab_padded, 64, dev)
         self.cand_ids = torch.empty(Rw, 64, dtype=torch.int32, device=dev)
         self.cand_vals = torch.empty(Rw, 64, dtype=torch.float32, device=dev)
+
+    def _alloc_dsa(self, R):
+        """Planes and scratch of the sparse-attention indexer.  Per layer: the ring of each sequence's last tokens (key | gate rows) and the pooled
+        keys (one 4 KB slab per latent-cache page: + 5.5 %).  Shared by the layers: this call's staging rows, the score / selection buffers of one
+        row group and the scratch pages the selected latent rows are gathered into (33 pages per row at 512 pools)."""
+        cfg, dev = self.cfg, self.device
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)  # noqa: E731
+        if cfg.dsa_sel_pools < 1 or cfg.dsa_sel_pools > 8192:
+            raise ValueError("dsa_sel_pools must be in 1..8192")
+        self.dsa_ring_len = (min(R, 256) + DSA_P + DSA_P - 1) // DSA_P * DSA_P
+        self.dsa_ring = [torch.zeros(self.max_seqs, self.dsa_ring_len, 2 * DSA_D, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+        self.dsa_pool = [torch.zeros(self.num_pages, PAGE // DSA_P, DSA_D, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+        self.dsa_stage = torch.zeros(R, 2 * DSA_D, dtype=torch.bfloat16, device=dev)
+        self.dsa_s_stride = (self.max_ctx_alloc // DSA_P + 7) // 8 * 8
+        self.dsa_k_stride = (cfg.dsa_sel_pools * DSA_P + DSA_P - 1 + 3) // 4 * 4
+        self.dsa_pages = (self.dsa_k_stride + PAGE - 1) // PAGE
+        G = min(R, DSA_GROUP)
+        self.dsa_scores = torch.zeros(G, self.dsa_s_stride, dtype=torch.float16, device=dev)
+        self.dsa_sel = i32(G, self.dsa_k_stride)
+        self.dsa_flag, self.dsa_ctx = i32(R), i32(R)
+        self.dsa_scratch = torch.zeros(G * self.dsa_pages, 9, PAGE, 64, dtype=torch.bfloat16, device=dev)
+        self.dsa_tc = K.KvTensorMap(self.dsa_scratch)
+        self.dsa_vbt = torch.arange(G * self.dsa_pages, dtype=torch.int32, device=dev).view(G, self.dsa_pages).contiguous()
+        self.dsa_rowid = torch.arange(G, dtype=torch.int32, device=dev)
+
+    def _dsa_sparse_rows(self, li, L, M, q_ld, block_table, row_seq, positions, ctx_cap):
+        """Rows of the sparse regime: scores over the pooled keys, exact top-`sel_pools` selection, gather of the selected latent rows into the
+        scratch pages, attention over those through the virtual block table; DSA_GROUP rows per launch group."""
+        cfg, Lib, st, Hl = self.cfg, _lib.load(), _lib.stream_ptr, self.Hl
+        max_pools = min(ctx_cap // DSA_P, self.dsa_s_stride)
+        for g0 in range(0, M, DSA_GROUP):
+            n = min(DSA_GROUP, M - g0)
+            qi = self.q_full.data_ptr() + 2 * (g0 * q_ld + Hl * 192)
+            _lib.check(Lib.rx_dsa_select(ctypes.c_void_p(qi), q_ld, ctypes.c_void_p(self.a_out.data_ptr() + 2 * g0 * cfg.a_width), cfg.a_width, DSA_COL_W,
+                                         self.dsa_pool[li].data_ptr(), block_table.data_ptr(), block_table.shape[1], ctypes.c_void_p(row_seq.data_ptr() + 4 * g0),
+                                         ctypes.c_void_p(positions.data_ptr() + 4 * g0), cfg.dsa_dense_below, 1.0 / math.sqrt(DSA_H * DSA_D), cfg.dsa_sel_pools,
+                                         max_pools, self.dsa_scores.data_ptr(), self.dsa_s_stride, self.dsa_sel.data_ptr(), self.dsa_k_stride,
+                                         ctypes.c_void_p(self.dsa_flag.data_ptr() + 4 * g0), ctypes.c_void_p(self.dsa_ctx.data_ptr() + 4 * g0), n, st()),
+                       "rx_dsa_select")
+            _lib.check(Lib.rx_dsa_gather(self.cache[li].data_ptr(), block_table.data_ptr(), block_table.shape[1], ctypes.c_void_p(row_seq.data_ptr() + 4 * g0),
+                                         self.dsa_sel.data_ptr(), self.dsa_k_stride, ctypes.c_void_p(self.dsa_flag.data_ptr() + 4 * g0),
+                                         ctypes.c_void_p(self.dsa_ctx.data_ptr() + 4 * g0), self.dsa_scratch.data_ptr(), self.dsa_pages, n, st()), "rx_dsa_gather")
+            _lib.check(Lib.rx_mla_attn_sel(self.dsa_tc.ptr, ctypes.c_void_p(self.q.data_ptr() + 2 * g0 * Hl * 576), self.dsa_vbt.data_ptr(), self.dsa_pages,
+                                           self.dsa_rowid.data_ptr(), ctypes.c_void_p(self.dsa_ctx.data_ptr() + 4 * g0), self.attn_scratch.data_ptr(), n, Hl,
+                                           self.dsa_pages * PAGE, 1.0 / math.sqrt(192), ctypes.c_void_p(self.o_lat.data_ptr() + 2 * g0 * Hl * 512),
+                                           self.status.data_ptr(), ctypes.c_void_p(self.dsa_flag.data_ptr() + 4 * g0), 1, st()), "rx_mla_attn_sel")
+            _lib.count(5)
 
     def _lin(self, xr, w, cls, name):
         s = self.splits[(cls, name)]
@@ -449,19 +580,30 @@ class MlaMoEGPU:
         K.norm_rot_in(h, self.layers[0]["attn_norm"], cfg.eps, self.layers[0]["qkv_a"].suh, xr_d)
         nl = n_layers or len(self.layers)
         use = 0        # collectives are numbered in launch order: consecutive ones alternate between the two slot sets
+        q_ld = Hl * 192 + cfg.qb_extra
+        sparse = cfg.dsa and ctx_cap > cfg.dsa_dense_below      # no row of this call can be in the sparse regime otherwise
         for li in range(nl):
             L = self.layers[li]
             s = self._lin(xr_d, L["qkv_a"], cls, "qkv_a")
             K.finish_store(self.part, s, M, L["qkv_a"], a_out)
-            _lib.check(Lib.rx_mla_row(a_out.data_ptr(), L["q_norm"].data_ptr(), L["kv_norm"].data_ptr(), cfg.eps, L["q_b"].suh.data_ptr(), positions.data_ptr(),
-                                      self.inv_freq.data_ptr(), slots.data_ptr(), xr_q.data_ptr(), self.cache[li].data_ptr(), M, st()), "rx_mla_row")
+            _lib.check(Lib.rx_mla_row_ld(a_out.data_ptr(), cfg.a_width, L["q_norm"].data_ptr(), L["kv_norm"].data_ptr(), cfg.eps, L["q_b"].suh.data_ptr(),
+                                         positions.data_ptr(), self.inv_freq.data_ptr(), slots.data_ptr(), xr_q.data_ptr(), self.cache[li].data_ptr(), M, st()),
+                       "rx_mla_row")
+            if cfg.dsa:
+                _lib.check(Lib.rx_dsa_append(a_out.data_ptr(), cfg.a_width, DSA_COL_K, DSA_COL_G, L["idx_ln_w"].data_ptr(), L["idx_ln_b"].data_ptr(), 1e-6,
+                                             L["idx_ape"].data_ptr(), row_seq.data_ptr(), positions.data_ptr(), block_table.data_ptr(),
+                                             block_table.shape[1], self.dsa_stage.data_ptr(), self.dsa_ring[li].data_ptr(), self.dsa_ring_len,
+                                             self.dsa_pool[li].data_ptr(), M, st()), "rx_dsa_append")
+                _lib.count(3)
             s = self._lin(xr_q, L["q_b"], cls, "q_b")
             K.finish_store(self.part, s, M, L["q_b"], q_full)
-            _lib.check(Lib.rx_mla_q_rope(q_full.data_ptr(), positions.data_ptr(), self.inv_freq.data_ptr(), Hl, q.data_ptr(), M, st()), "rx_mla_q_rope")
-            _lib.check(Lib.rx_head_gemm(q_full.data_ptr(), Hl * 192, 192, L["w_uk"].data_ptr(), Hl, 128, 512, q.data_ptr(), Hl * 576, 576, M, st()), "absorb")
-            _lib.check(Lib.rx_mla_attn(self.tc[li].ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
-                                       self.attn_scratch.data_ptr(), M, Hl, ctx_cap, 1.0 / math.sqrt(192), o_lat.data_ptr(), self.status.data_ptr(), st()),
-                       "rx_mla_attn")
+            _lib.check(Lib.rx_mla_q_rope_ld(q_full.data_ptr(), q_ld, positions.data_ptr(), self.inv_freq.data_ptr(), Hl, q.data_ptr(), M, st()), "rx_mla_q_rope")
+            _lib.check(Lib.rx_head_gemm(q_full.data_ptr(), q_ld, 192, L["w_uk"].data_ptr(), Hl, 128, 512, q.data_ptr(), Hl * 576, 576, M, st()), "absorb")
+            if sparse:
+                self._dsa_sparse_rows(li, L, M, q_ld, block_table, row_seq, positions, ctx_cap)
+            _lib.check(Lib.rx_mla_attn_sel(self.tc[li].ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
+                                           self.attn_scratch.data_ptr(), M, Hl, ctx_cap, 1.0 / math.sqrt(192), o_lat.data_ptr(), self.status.data_ptr(),
+                                           self.dsa_flag.data_ptr() if sparse else None, 0, st()), "rx_mla_attn")
             _lib.check(Lib.rx_head_gemm(o_lat.data_ptr(), Hl * 512, 512, L["w_uv"].data_ptr(), Hl, 512, 128, o_heads.data_ptr(), Hl * 128, 128, M, st()), "expand")
             _lib.count(6)
             K.norm_rot_in(o_heads, None, cfg.eps, L["o"].suh, xr_o)

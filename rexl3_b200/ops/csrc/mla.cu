@@ -54,7 +54,7 @@ __device__ __forceinline__ uint32_t ml_chunk_addr(uint32_t base, int key, int dc
 __global__ void __launch_bounds__(128, 1)
 mla_attn_kernel(const __grid_constant__ CUtensorMap tc, const uint16_t* __restrict__ q, const int* __restrict__ block_table, int max_blocks,
                 const int* __restrict__ row_seq, const int* __restrict__ ctx_len, float* __restrict__ part_o, float* __restrict__ part_ml, int H,
-                int max_splits, float scale_log2, int* status) {
+                int max_splits, float scale_log2, int* status, const int* __restrict__ row_sel, int want) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -67,6 +67,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tc, const uint16_t* __restri
   volatile int* abort_flag = (volatile int*)(bars + 2);
   const int row = blockIdx.x, hg = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (row_sel != nullptr && row_sel[row] != want) return;      // rows of the other regime belong to the other call
   const int ctx = ctx_len[row];
   const int k_begin = split * ML_SPLIT_PAGES * ML_PAGE;
   if (k_begin >= ctx) return;
@@ -213,10 +214,11 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tc, const uint16_t* __restri
 
 // grid (rows, H), 128 threads: out_lat bf16 [rows][H][512] = merged splits (split order).
 __global__ void mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ ctx_len, int H,
-                                 int max_splits, uint16_t* __restrict__ out) {
+                                 int max_splits, uint16_t* __restrict__ out, const int* __restrict__ row_sel, int want) {
   pdl_launch();
   pdl_wait();
   const int row = blockIdx.x, h = blockIdx.y;
+  if (row_sel != nullptr && row_sel[row] != want) return;
   const int ctx = ctx_len[row];
   const int ns = (ctx + ML_SPLIT_PAGES * ML_PAGE - 1) / (ML_SPLIT_PAGES * ML_PAGE);
   const float* ml = part_ml + ((size_t)row * H + h) * max_splits * 2;
@@ -298,13 +300,13 @@ __global__ void __launch_bounds__(128) head_gemm_kernel(const uint16_t* __restri
 __global__ void __launch_bounds__(544) mla_row_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ q_norm, const uint16_t* __restrict__ kv_norm,
                                                       float eps, const __half* __restrict__ suh_qb, const int* __restrict__ positions,
                                                       const float* __restrict__ inv_freq, const int* __restrict__ slot, __half* __restrict__ xr_q,
-                                                      uint16_t* __restrict__ cache) {
+                                                      uint16_t* __restrict__ cache, int a_ld) {
   pdl_launch();
   pdl_wait();
   __shared__ float ss[17];
   const int row = blockIdx.x, lane = threadIdx.x & 31, b = threadIdx.x >> 5;
   const int n0 = b * 128 + lane * 4;
-  const uint2 u = *reinterpret_cast<const uint2*>(a + (size_t)row * 2176 + n0);
+  const uint2 u = *reinterpret_cast<const uint2*>(a + (size_t)row * a_ld + n0);
   float v[4] = {__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u)};
   float s2 = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
   s2 = warp_sum(s2);
@@ -368,14 +370,14 @@ __global__ void __launch_bounds__(544) mla_row_kernel(const uint16_t* __restrict
 
 // q_full: bf16 [M][H][192] (nope 128 | rope 64) -> q[row][h][512..575] = RoPE(rope part).  grid (M), H * 16 threads.
 __global__ void mla_q_rope_kernel(const uint16_t* __restrict__ q_full, const int* __restrict__ positions, const float* __restrict__ inv_freq, int H,
-                                  uint16_t* __restrict__ q) {
+                                  uint16_t* __restrict__ q, int q_ld) {
   pdl_launch();
   pdl_wait();
   const int row = blockIdx.x;
   const float pos = (float)positions[row];
   for (int i = threadIdx.x; i < H * 32; i += blockDim.x) {
     const int h = i >> 5, f = i & 31;
-    const uint16_t* src = q_full + ((size_t)row * H + h) * 192 + 128;
+    const uint16_t* src = q_full + (size_t)row * q_ld + (size_t)h * 192 + 128;
     const float x1 = ml_bf(src[f]), x2 = ml_bf(src[f + 32]);
     float sn, cs;
     sincosf(pos * inv_freq[f], &sn, &cs);
@@ -395,8 +397,10 @@ RX_API long long rx_mla_scratch_floats(int rows, int H, int max_ctx) {
 }
 
 // tmap: a tensor map made by rx_make_kv_tmap over the cache viewed as [pages * 9 * 64 rows][64].
-RX_API int rx_mla_attn(const void* tmap, const void* q, const void* block_table, int max_blocks, const void* row_seq, const void* ctx_len, void* scratch,
-                       int rows, int H, int max_ctx, float scale, void* out_lat, int* status, void* stream) {
+// row_sel / want: only rows with row_sel[row] == want are computed and written (nullptr: every row).  The sparse-attention path calls this twice
+// per layer: rows of the dense regime over the layer's cache, rows of the sparse regime over the gathered scratch pages.
+RX_API int rx_mla_attn_sel(const void* tmap, const void* q, const void* block_table, int max_blocks, const void* row_seq, const void* ctx_len, void* scratch,
+                           int rows, int H, int max_ctx, float scale, void* out_lat, int* status, const void* row_sel, int want, void* stream) {
   if (rows < 1 || H % ML_HG != 0 || max_ctx < 1) return (int)cudaErrorInvalidValue;
   const int splits = (max_ctx + ML_SPLIT_PAGES * ML_PAGE - 1) / (ML_SPLIT_PAGES * ML_PAGE);
   float* part_o = (float*)scratch;
@@ -412,10 +416,15 @@ RX_API int rx_mla_attn(const void* tmap, const void* q, const void* block_table,
   memcpy(&tm, tmap, sizeof(tm));
   cudaStream_t st = (cudaStream_t)stream;
   int e = (int)rx::launch(mla_attn_kernel, dim3(rows, H / ML_HG, splits), dim3(128), (size_t)smem, st, tm, (const uint16_t*)q, (const int*)block_table,
-                          max_blocks, (const int*)row_seq, (const int*)ctx_len, part_o, part_ml, H, splits, scale * 1.4426950408889634f, status);
+                          max_blocks, (const int*)row_seq, (const int*)ctx_len, part_o, part_ml, H, splits, scale * 1.4426950408889634f, status,
+                          (const int*)row_sel, want);
   if (e != 0) return e;
   return (int)rx::launch(mla_merge_kernel, dim3(rows, H), dim3(128), 0, st, (const float*)part_o, (const float*)part_ml, (const int*)ctx_len, H, splits,
-                         (uint16_t*)out_lat);
+                         (uint16_t*)out_lat, (const int*)row_sel, want);
+}
+RX_API int rx_mla_attn(const void* tmap, const void* q, const void* block_table, int max_blocks, const void* row_seq, const void* ctx_len, void* scratch,
+                       int rows, int H, int max_ctx, float scale, void* out_lat, int* status, void* stream) {
+  return rx_mla_attn_sel(tmap, q, block_table, max_blocks, row_seq, ctx_len, scratch, rows, H, max_ctx, scale, out_lat, status, nullptr, 0, stream);
 }
 
 RX_API int rx_head_gemm(const void* in, int in_ld, int in_hs, const void* W, int H, int K, int N, void* out, int out_ld, int out_hs, int M, void* stream) {
@@ -424,17 +433,25 @@ RX_API int rx_head_gemm(const void* in, int in_ld, int in_hs, const void* W, int
                          (const uint16_t*)W, K, N, (uint16_t*)out, out_ld, out_hs, M);
 }
 
+// a_ld: elements between rows of `a` (2176, or wider when the projection carries the sparse indexer's columns after the pad)
+RX_API int rx_mla_row_ld(const void* a, int a_ld, const void* q_norm, const void* kv_norm, float eps, const void* suh_qb, const void* positions,
+                         const void* inv_freq, const void* slot, void* xr_q, void* cache, int M, void* stream) {
+  if (M < 1 || a_ld < 2176 || a_ld % 4 != 0) return (int)cudaErrorInvalidValue;
+  return (int)rx::launch(mla_row_kernel, dim3(M), dim3(544), 0, (cudaStream_t)stream, (const uint16_t*)a, (const uint16_t*)q_norm, (const uint16_t*)kv_norm,
+                         eps, (const __half*)suh_qb, (const int*)positions, (const float*)inv_freq, (const int*)slot, (__half*)xr_q, (uint16_t*)cache, a_ld);
+}
 RX_API int rx_mla_row(const void* a, const void* q_norm, const void* kv_norm, float eps, const void* suh_qb, const void* positions, const void* inv_freq,
                       const void* slot, void* xr_q, void* cache, int M, void* stream) {
-  if (M < 1) return (int)cudaErrorInvalidValue;
-  return (int)rx::launch(mla_row_kernel, dim3(M), dim3(544), 0, (cudaStream_t)stream, (const uint16_t*)a, (const uint16_t*)q_norm, (const uint16_t*)kv_norm,
-                         eps, (const __half*)suh_qb, (const int*)positions, (const float*)inv_freq, (const int*)slot, (__half*)xr_q, (uint16_t*)cache);
+  return rx_mla_row_ld(a, 2176, q_norm, kv_norm, eps, suh_qb, positions, inv_freq, slot, xr_q, cache, M, stream);
 }
 
-RX_API int rx_mla_q_rope(const void* q_full, const void* positions, const void* inv_freq, int H, void* q, int M, void* stream) {
-  if (M < 1 || H < 1) return (int)cudaErrorInvalidValue;
+RX_API int rx_mla_q_rope_ld(const void* q_full, int q_ld, const void* positions, const void* inv_freq, int H, void* q, int M, void* stream) {
+  if (M < 1 || H < 1 || q_ld < H * 192) return (int)cudaErrorInvalidValue;
   int threads = H * 32;
   if (threads > 1024) threads = 1024;
   return (int)rx::launch(mla_q_rope_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)stream, (const uint16_t*)q_full, (const int*)positions,
-                         (const float*)inv_freq, H, (uint16_t*)q);
+                         (const float*)inv_freq, H, (uint16_t*)q, q_ld);
+}
+RX_API int rx_mla_q_rope(const void* q_full, const void* positions, const void* inv_freq, int H, void* q, int M, void* stream) {
+  return rx_mla_q_rope_ld(q_full, H * 192, positions, inv_freq, H, q, M, stream);
 }

@@ -80,6 +80,14 @@ def _declare(lib):
         "rx_head_gemm": (c_int, [c_void, c_int, c_int, c_void, c_int, c_int, c_int, c_void, c_int, c_int, c_int, c_void]),
         "rx_mla_row": (c_int, [c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void]),
         "rx_mla_q_rope": (c_int, [c_void, c_void, c_void, c_int, c_void, c_int, c_void]),
+        "rx_mla_attn_sel": (c_int, [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_f, c_void, c_void, c_void, c_int, c_void]),
+        "rx_mla_row_ld": (c_int, [c_void, c_int, c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void]),
+        "rx_mla_q_rope_ld": (c_int, [c_void, c_int, c_void, c_void, c_int, c_void, c_int, c_void]),
+        "rx_dsa_append": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_f, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_int,
+                                  c_void, c_int, c_void]),
+        "rx_dsa_select": (c_int, [c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_void, c_int, c_f, c_int, c_int, c_void, c_int,
+                                  c_void, c_int, c_void, c_void, c_int, c_void]),
+        "rx_dsa_gather": (c_int, [c_void, c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_void]),
         "rx_mxfp4_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_void, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),
         "rx_moe_combine": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_tp_cand_push": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void]),
