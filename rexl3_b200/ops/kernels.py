@@ -215,6 +215,65 @@ def hc_apply(x: torch.Tensor, y: torch.Tensor, coef: torch.Tensor) -> None:
     _lib.count()
 
 
+class Fp8Weight:
+    """An FP8 block-scaled linear on the device: `w` E4M3 bytes uint8 [N, K], `scales` E8M0 bytes uint8 [N / 32, K / 32] (one power of two per
+    32 x 32 tile), optional f32 bias [N] (reference crates/cuda/csrc/fp8_linear.cu:1)."""
+
+    def __init__(self, w: torch.Tensor, scales: torch.Tensor, bias: "torch.Tensor | None" = None):
+        N, Kd = w.shape
+        if w.dtype != torch.uint8 or scales.dtype != torch.uint8 or N % 128 or Kd % 64 or tuple(scales.shape) != (N // 32, Kd // 32):
+            raise ValueError("fp8 weight: uint8 [N, K] with N % 128 == 0, K % 64 == 0 and uint8 scales [N / 32, K / 32]")
+        self.w, self.scales, self.bias, self.N, self.K = w.contiguous(), scales.contiguous(), bias, N, Kd
+        self._part = None
+
+    @staticmethod
+    def quantize(dense: torch.Tensor, bias=None) -> "Fp8Weight":
+        """dense f32 [N, K] -> the smallest power-of-two scale per 32 x 32 tile that brings the tile into the E4M3 range, values rounded to E4M3."""
+        N, Kd = dense.shape
+        t = dense.float().view(N // 32, 32, Kd // 32, 32)
+        amax = t.abs().amax(dim=(1, 3)).clamp_min(2.0 ** -120)
+        e = torch.ceil(torch.log2(amax / 448.0)).clamp(-126, 127)
+        q = (t / torch.exp2(e)[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+        return Fp8Weight(q.view(torch.uint8).view(N, Kd), (e + 127).to(torch.uint8), bias)
+
+    def dense(self) -> torch.Tensor:
+        """The f32 matrix the bytes stand for (oracle side)."""
+        N, Kd = self.w.shape
+        v = self.w.view(torch.float8_e4m3fn).float().view(N // 32, 32, Kd // 32, 32)
+        return (v * torch.exp2(self.scales.float() - 127.0)[:, None, :, None]).view(N, Kd)
+
+
+def fp8_linear(x: torch.Tensor, w: Fp8Weight, status: torch.Tensor, out: "torch.Tensor | None" = None, out_dtype=torch.bfloat16, splits: int = 0) -> torch.Tensor:
+    """y = x @ W^T (+ bias) for an FP8 block-scaled weight on the tcgen05 kernel: x bf16 [rows, K] -> y [rows, N] (bf16, fp16 or fp32).  The
+    block scales are powers of two, so the weights are exact in the bf16 operand tiles; accumulation is fp32 in a fixed order."""
+    rows, Kd = x.shape
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and Kd == w.K
+    if splits < 1:      # few rows: split K until the grid covers the SMs (weight streaming); many rows: one pass
+        ctas = (w.N // 128) * ((rows + 255) // 256)
+        splits = max(1, min(Kd // 64, 8, 296 // max(1, ctas))) if rows <= 256 else 1
+    tr = 16
+    while tr < rows and tr < 256:
+        tr *= 2
+    L = _lib.load()
+    need = L.rx_fp8_linear_scratch_floats(rows, w.N, splits)
+    if w._part is None or w._part.numel() < need:
+        w._part = torch.empty(need, dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(rows, w.N, dtype=out_dtype, device=x.device)
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out.dtype]
+    _lib.check(L.rx_fp8_linear(x.data_ptr(), rows, Kd, w.w.data_ptr(), w.scales.data_ptr(), w.N, w._part.data_ptr(), splits, tr, _lib.ptr(w.bias),
+                               out.data_ptr(), code, status.data_ptr(), _lib.stream_ptr()), "rx_fp8_linear")
+    _lib.count(2)
+    return out
+
+
+def bf16_linear(x: torch.Tensor, weight: torch.Tensor, bias: "torch.Tensor | None" = None) -> torch.Tensor:
+    """Plain bf16 linear y = x @ W^T (+ bias), fp32 accumulate: a LIBRARY GEMM (cuBLASLt through torch), for the tensors a pack keeps unquantised
+    (vision towers, routers, small projections; reference crates/cuda/csrc/dsv4_bf16.cu).  Reduced-precision accumulation is switched off."""
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    return torch.nn.functional.linear(x, weight, bias)
+
+
 def state_digest(tensors, out: "torch.Tensor | None" = None) -> torch.Tensor:
     """Position-keyed 64-bit content digest of one tensor or of a list of tensors (each part into its own word, the words then folded on the
     host by `fold_digest`).  Returns the int64 device tensor of per-part digests; nothing synchronises here."""

@@ -87,6 +87,8 @@ def _declare(lib):
                                   c_void, c_int, c_void]),
         "rx_dsa_select": (c_int, [c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_void, c_int, c_f, c_int, c_int, c_void, c_int,
                                   c_void, c_int, c_void, c_void, c_int, c_void]),
+        "rx_fp8_linear_scratch_floats": (c_ll, [c_int, c_int, c_int]),
+        "rx_fp8_linear": (c_int, [c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_void]),
         "rx_dsa_gather": (c_int, [c_void, c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_void]),
         "rx_mxfp4_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_void, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),
         "rx_moe_combine": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),

@@ -381,3 +381,35 @@ def test_hyper_connection_mix_and_apply_match_the_reference_and_are_row_invarian
         h1 = torch.empty(1, D, dtype=torch.bfloat16, device="cuda")
         K.hc_mix(x[3:4].contiguous(), fn, base, scales, nw, c1, h1, iters=20)
         assert torch.equal(c1[0], coef[3]) and torch.equal(h1[0], hn[3])
+
+
+@pytest.mark.parametrize("rows,K,N", [(1, 512, 256), (5, 1024, 384), (70, 2048, 256), (300, 512, 128)])
+def test_fp8_block_scaled_linear_matches_fp32(rows, K, N):
+    """E4M3 weights with one power-of-two scale per 32 x 32 tile on the tcgen05 kernel against x @ dequant(W)^T in fp32; a row's bits do not
+    depend on the rows it shares the launch with or on its place among them (same K splits, same tile class)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.ops import kernels as K_
+    g = torch.Generator(device="cuda").manual_seed(rows + K)
+    dense = torch.randn(N, K, device="cuda", generator=g) * torch.exp2(torch.randint(-6, 5, (N // 32, 1, K // 32, 1), device="cuda", generator=g).float()
+                                                                      ).expand(N // 32, 32, K // 32, 32).reshape(N, K)
+    bias = torch.randn(N, device="cuda", generator=g)
+    w = K_.Fp8Weight.quantize(dense, bias)
+    x = torch.randn(rows, K, device="cuda", generator=g).to(torch.bfloat16)
+    status = K_.new_status()
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        got = K_.fp8_linear(x, w, status, out_dtype=dt)
+        torch.cuda.synchronize()
+        K_.check_status(status)
+        want = x.float() @ w.dense().T + bias
+        tol = 1e-4 if dt == torch.float32 else 1e-2
+        assert torch.allclose(got.float(), want, rtol=tol, atol=tol * want.abs().max().item()), dt
+    if rows > 1:      # the same rows one position earlier in a launch of the same tile class: bit-identical
+        splits = 2
+        full = K_.fp8_linear(x, w, status, out_dtype=torch.float32, splits=splits).clone()
+        part = K_.fp8_linear(x[1:].contiguous(), w, status, out_dtype=torch.float32, splits=splits)
+        torch.cuda.synchronize()
+        K_.check_status(status)
+        assert torch.equal(full[1:], part)
+    y = K_.bf16_linear(x, dense.to(torch.bfloat16), bias.to(torch.bfloat16))
+    assert torch.allclose(y.float(), x.float() @ dense.to(torch.bfloat16).float().T + bias.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2 * y.abs().max().item())
