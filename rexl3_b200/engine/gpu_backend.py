@@ -21,11 +21,18 @@ CTX_BUCKET = 2048   # decode graphs are captured per (rows, candidate count, con
 class DenseGpuBackend(Backend):
     name = "cuda"
 
-    def __init__(self, model: DenseGPU, max_slots: int | None = None, use_graphs: bool = True, self_draft: bool = False):
+    def __init__(self, model: DenseGPU, max_slots: int | None = None, use_graphs: bool = True, self_draft: bool = False, mtp_draft: bool = False):
         """`self_draft`: offer drafts from the model's first `cfg.draft_layers` layers plus the shared final norm and head (the draft
-        shares the target's KV cache for those layers, so it needs no state of its own)."""
+        shares the target's KV cache for those layers, so it needs no state of its own).
+        `mtp_draft`: offer drafts from the model's multi-token-prediction block (config.mtp).  The block's KV rows lag the trunk by one
+        position: whenever the trunk runs rows whose tokens are known, the block runs the rows one position earlier (hidden of position
+        i, token i + 1), reading the trunk's final residual rows; the last window's rows are kept per slot so that the row before the next
+        window is at hand whatever number of drafts was accepted.  Draft j chains the block on its own output hidden."""
         self.m = model
         self.self_draft = bool(self_draft and getattr(model.cfg, "draft_layers", 0) > 0)
+        self.mtp_draft = bool(mtp_draft and getattr(model, "mtp", None) is not None)
+        if mtp_draft and not self.mtp_draft:
+            raise ValueError("mtp_draft needs a model with a multi-token-prediction block (config.mtp)")
         self.cfg = model.cfg
         self.vocab_size = model.cfg.vocab
         self.max_slots = max_slots or model.max_seqs
@@ -52,7 +59,21 @@ class DenseGpuBackend(Backend):
         self.draft_graphs = {}
         self.draft_steps = 0
         self.DK = 8                                            # most chained drafts one ask may get
-        if self.self_draft:
+        if self.mtp_draft:
+            d_model = model.cfg.d_model
+            self.MTP_W = 16                                    # trunk rows kept per slot (a window has at most 1 + DK rows)
+            NS = self.max_slots * self.MTP_W
+            self.mtp_src = torch.zeros(NS + R, d_model, dtype=torch.bfloat16, device=dev)     # [kept rows of every slot | this call's trunk rows]
+            self.mtp_in = torch.zeros(R, d_model, dtype=torch.bfloat16, device=dev)
+            self.mtp_chain = torch.zeros(self.max_slots, d_model, dtype=torch.bfloat16, device=dev)
+            self.mtp_p0 = [-1] * self.max_slots                # first position of the slot's kept rows (-1: none)
+            self.mtp_n = [0] * self.max_slots
+            self.h_mtp = torch.zeros(6, R, dtype=torch.int32).pin_memory()
+            self.d_mtp = torch.zeros(6, R, dtype=torch.int32, device=dev)
+            self.h_keep = torch.zeros(2, R, dtype=torch.int64).pin_memory()
+            self.d_keep = torch.zeros(2, R, dtype=torch.int64, device=dev)
+            self.mtp_rows = 0
+        if self.self_draft or self.mtp_draft:
             self.h_draft = torch.zeros(self.DK, 5, self.max_slots, dtype=torch.int32).pin_memory()
             self.d_draft = torch.zeros(self.DK, 5, self.max_slots, dtype=torch.int32, device=dev)
             self.d_draft_ids = torch.zeros(self.DK, self.max_slots, dtype=torch.int32, device=dev)
@@ -163,6 +184,8 @@ class DenseGpuBackend(Backend):
             if last:
                 last_rows.append(q0 - 1)
         rows = self._run_prefill(M, n, max(len(t) for _, _, t, _ in items), last_rows, candidates)
+        if self.mtp_draft:
+            self._mtp_after_trunk([(s, st, t) for s, st, t, _ in items], keep_all=False)
         for slot, start, toks, _ in items:
             self.len[slot] = start + len(toks)
             self.pending[slot] = 0
@@ -212,6 +235,8 @@ class DenseGpuBackend(Backend):
         self._upload_rows(M)
         self._sync_bt()
         self._run_window(M, count, bucket)
+        if self.mtp_draft:
+            self._mtp_after_trunk(specs, keep_all=True, bucket=bucket)
         rows = self._download(M, count)
         self._check()
         out, k = [], 0
@@ -219,6 +244,119 @@ class DenseGpuBackend(Backend):
             out.append(rows[k:k + len(r.tokens)])
             k += len(r.tokens)
         return out
+
+    # ------------------------------------------------------------------ multi-token-prediction block: lagged rows and drafts
+    def _mtp_after_trunk(self, specs, keep_all: bool, bucket: int | None = None) -> None:
+        """The trunk has just run `specs` = [(slot, first position, tokens)] (rows in that order; m.h holds their final residual rows).  Runs the
+        block on the rows one position earlier - (hidden of p0 - 1 kept from the slot's last window, token p0), (hidden p0, token p0 + 1), ... -
+        and keeps this call's rows for the next one (`keep_all`: every row of a window, since the accepted count is not known yet; a prefill
+        slice keeps its last row).  Rows past the accepted prefix of a window hold speculative KV that the next call rewrites."""
+        m, W = self.m, self.MTP_W
+        NS = self.max_slots * W
+        self._host_writable()
+        h, hk = self.h_mtp.numpy(), self.h_keep.numpy()
+        n_rows = n_keep = 0
+        r0 = 0
+        seq_rows = 1
+        for slot, p0, toks in specs:
+            n = len(toks)
+            pg = self.pages[slot]
+            have = self.mtp_p0[slot] >= 0 and self.mtp_p0[slot] <= p0 - 1 < self.mtp_p0[slot] + self.mtp_n[slot]
+            first = p0 - 1 if (have and p0 > 0) else p0
+            cnt = p0 + n - 1 - first                     # block rows at positions first .. p0 + n - 2
+            if cnt > 0:
+                pos = np.arange(first, first + cnt, dtype=np.int64)
+                a = n_rows
+                h[0, a:a + cnt] = toks[first + 1 - p0:]                                  # the token AFTER each position
+                h[1, a:a + cnt] = pos
+                h[2, a:a + cnt] = np.asarray(pg, dtype=np.int64)[pos // PAGE] * PAGE + pos % PAGE
+                h[3, a:a + cnt] = slot
+                h[4, a:a + cnt] = pos + 1
+                src = NS + r0 + (pos - p0)                                                # this call's trunk rows ...
+                if first < p0:
+                    src[0] = slot * W + (p0 - 1 - self.mtp_p0[slot])                     # ... and the kept row before them
+                h[5, a:a + cnt] = src
+                n_rows += cnt
+                seq_rows = max(seq_rows, cnt)
+            if keep_all:
+                kn = min(n, W)
+                hk[0, n_keep:n_keep + kn] = r0 + np.arange(kn)
+                hk[1, n_keep:n_keep + kn] = slot * W + np.arange(kn)
+                n_keep += kn
+                self.mtp_p0[slot], self.mtp_n[slot] = p0, kn
+            else:
+                hk[0, n_keep], hk[1, n_keep] = r0 + n - 1, slot * W
+                n_keep += 1
+                self.mtp_p0[slot], self.mtp_n[slot] = p0 + n - 1, 1
+            r0 += n
+        M = r0
+        self.d_mtp[:, :max(1, n_rows)].copy_(self.h_mtp[:, :max(1, n_rows)], non_blocking=True)
+        self.d_keep[:, :n_keep].copy_(self.h_keep[:, :n_keep], non_blocking=True)
+        self._uploaded()
+        self.h2d_bytes += 6 * n_rows * 4 + 2 * n_keep * 8
+        self.mtp_src[NS:NS + M].copy_(m.h[:M])
+        if n_rows:
+            torch.index_select(self.mtp_src, 0, self.d_mtp[5, :n_rows].long(), out=self.mtp_in[:n_rows])
+        # keep this call's rows only after the gather has read the previous ones
+        self.mtp_src.index_copy_(0, self.d_keep[1, :n_keep], m.h.index_select(0, self.d_keep[0, :n_keep]))
+        d = self.d_mtp
+        ctx_cap = bucket or m.max_ctx_alloc
+        saved_rows = m.window_seq_rows
+        for c0 in range(0, n_rows, 256):
+            c1 = min(n_rows, c0 + 256)
+            m.window_seq_rows = min(seq_rows, c1 - c0)
+            m.mtp_forward(d[0, c0:c1], self.mtp_in[c0:c1], d[1, c0:c1], d[2, c0:c1], d[3, c0:c1], d[4, c0:c1], self.d_bt, max_ctx=ctx_cap, want_logits=False)
+        m.window_seq_rows = saved_rows
+        self.mtp_rows += n_rows
+
+    def _mtp_propose(self, asks):
+        from .backend import DraftOffer
+        m, W = self.m, self.MTP_W
+        live = [a for a in asks if self.mtp_p0[a.slot] >= 0 and self.mtp_p0[a.slot] <= self.len[a.slot] - 1 < self.mtp_p0[a.slot] + self.mtp_n[a.slot]
+                and a.max_drafts > 0]
+        if not live:
+            return {}
+        n = len(live)
+        k = min(self.DK, max(a.max_drafts for a in live))
+        self._host_writable()
+        h = self.h_draft.numpy()
+        hk = self.h_keep.numpy()
+        top = 0
+        for i, a in enumerate(live):
+            slot, p0 = a.slot, self.len[a.slot]
+            if p0 != len(a.context) - 1:
+                raise BackendError(f"draft for slot {slot} at {len(a.context) - 1} but the slot holds {p0} tokens", fatal=False)
+            self._ensure(slot, p0 + k + 1)
+            pg = self.pages[slot]
+            for j in range(k):
+                pos = p0 - 1 + j                  # the block's row: hidden of `pos`, token pos + 1 -> predicts token pos + 2
+                h[j, 0, i] = a.context[-1] if j == 0 else 0
+                h[j, 1, i], h[j, 2, i], h[j, 3, i], h[j, 4, i] = pos, pg[pos // PAGE] * PAGE + pos % PAGE, slot, pos + 1
+            hk[0, i] = slot * W + (p0 - 1 - self.mtp_p0[slot])
+            top = max(top, p0 + k)
+        bucket = min(m.max_ctx_alloc, (top + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
+        self.d_draft[:k, :, :n].copy_(self.h_draft[:k, :, :n], non_blocking=True)
+        self.d_keep[0, :n].copy_(self.h_keep[0, :n], non_blocking=True)
+        self._uploaded()
+        self.h2d_bytes += k * 5 * n * 4 + n * 8
+        self._sync_bt()
+        saved_rows, m.window_seq_rows = m.window_seq_rows, 1
+        d = self.d_draft
+        torch.index_select(self.mtp_src, 0, self.d_keep[0, :n], out=self.mtp_chain[:n])
+        for j in range(k):
+            ids = d[0, 0, :n] if j == 0 else self.d_draft_ids[j - 1, :n]
+            logits, hid = m.mtp_forward(ids, self.mtp_chain[:n], d[j, 1, :n], d[j, 2, :n], d[j, 3, :n], d[j, 4, :n], self.d_bt, max_ctx=bucket)
+            if m.cfg.vocab_padded != m.cfg.vocab:
+                logits[:, m.cfg.vocab:] = float("-inf")
+            m.K.topk(logits, 1, m.topk_scratch, self.d_draft_ids[j, :n].view(n, 1), self.d_draft_vals[j, :n].view(n, 1))
+            self.mtp_chain[:n].copy_(hid)
+        m.window_seq_rows = saved_rows
+        self.h_draft_ids[:k, :n].copy_(self.d_draft_ids[:k, :n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += k * n * 4
+        self.draft_steps += k
+        out = self.h_draft_ids.numpy()
+        return {a.slot: DraftOffer([int(out[j, i]) for j in range(min(k, a.max_drafts))]) for i, a in enumerate(live)}
 
     # ------------------------------------------------------------------ window with device-side sampling and acceptance
     def supports_device_sampler(self) -> bool:
@@ -247,6 +385,8 @@ class DenseGpuBackend(Backend):
         self._upload_rows(M)
         self._sync_bt()
         self._run_window(M, count, bucket)
+        if self.mtp_draft:
+            self._mtp_after_trunk(specs, keep_all=True, bucket=bucket)
         windows = [(s, pos, r.tokens) for r, (s, pos) in zip(reqs, samplings)]
         samples, accepted, err = m.K.verify_accept(m._ids_view(M, count), m._vals_view(M, count), windows, device=m.device)
         hs, ha = samples.cpu().tolist(), accepted.cpu().tolist()      # the stream-ordered copies also fence the step
@@ -339,6 +479,8 @@ class DenseGpuBackend(Backend):
         self.pages[slot] = []
         self.len[slot] = 0
         self.pending[slot] = 0
+        if self.mtp_draft:
+            self.mtp_p0[slot], self.mtp_n[slot] = -1, 0
         self._host_writable()
         self.h_bt[slot].zero_()
         self.bt_dirty = True
@@ -376,7 +518,7 @@ class DenseGpuBackend(Backend):
 
     # ------------------------------------------------------------------ self-speculative drafter
     def supports_native_draft(self) -> bool:
-        return self.self_draft
+        return self.self_draft or self.mtp_draft
 
     def _draft_chain(self, n: int, k: int, bucket: int) -> None:
         """k chained greedy draft steps over n sequences, ids handed from step to step on the device."""
@@ -390,6 +532,8 @@ class DenseGpuBackend(Backend):
             m.K.topk(logits, 1, m.topk_scratch, self.d_draft_ids[j, :n].view(n, 1), self.d_draft_vals[j, :n].view(n, 1))
 
     def propose_batch(self, asks):
+        if self.mtp_draft and asks:
+            return self._mtp_propose(asks)
         if not self.self_draft or not asks:
             return {}
         from .backend import DraftOffer
@@ -508,8 +652,11 @@ class DenseGpuBackend(Backend):
         torch.cuda.synchronize()
 
     def stats(self):
-        return dict(graph_replays=self.graph_replays, graph_captures=self.graph_captures, replayed_kernels=self.replayed_kernels, h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes,
-                    free_pages=self.pool.free_blocks())
+        out = dict(graph_replays=self.graph_replays, graph_captures=self.graph_captures, replayed_kernels=self.replayed_kernels, h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes,
+                   free_pages=self.pool.free_blocks())
+        if self.mtp_draft:
+            out.update(mtp_rows=self.mtp_rows, draft_steps=self.draft_steps)
+        return out
 
 
 class _SkipFirstReplay:

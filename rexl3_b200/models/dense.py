@@ -36,6 +36,10 @@ class DenseConfig:
     codebook: str = "3inst"
     name: str = "dense-gqa"
     mrope_sections: tuple | None = None   # (t, h, w) frequency-pair counts of interleaved M-RoPE (sum = head_dim / 2); None = plain RoPE
+    # one multi-token-prediction (NextN) block after the trunk: x = e_proj(norm(embed(next token))) + h_proj(norm(trunk hidden)) - the
+    # `eh_proj` of the concatenation, split along K - then one decoder layer with its own KV cache, its own final norm and the shared head;
+    # row i predicts token i + 2 (reference crates/cuda/csrc/glm_mtp.cu:1-22, mtp.cu:1-6)
+    mtp: bool = False
 
     @property
     def ffn_padded(self) -> int:
@@ -150,12 +154,24 @@ class HostLayer:
 
 
 @dataclass
+class HostMtp:
+    """The multi-token-prediction block of a config with `mtp`."""
+    enorm: np.ndarray
+    hnorm: np.ndarray
+    e_proj: HostLinear           # d -> d: the embedding half of eh_proj
+    h_proj: HostLinear           # d -> d: the hidden half
+    layer: HostLayer
+    final_norm: np.ndarray
+
+
+@dataclass
 class HostWeights:
     cfg: DenseConfig
     embed: np.ndarray            # float32 [vocab, d] (stored bf16 on device)
     layers: list = field(default_factory=list)
     final_norm: np.ndarray = None
     lm_head: HostLinear = None
+    mtp: "HostMtp | None" = None
 
 
 def _bf16_round(a: np.ndarray) -> np.ndarray:
@@ -185,7 +201,7 @@ def random_weights(cfg: DenseConfig, seed: int = 0, per_linear: bool = False) ->
     d, F = cfg.d_model, cfg.ffn_padded
     s_in = 1.0 / math.sqrt(d)
     w = HostWeights(cfg, _bf16_round(rng.normal(0, 1.0, size=(cfg.vocab, d)).astype(np.float32)))
-    for _ in range(cfg.n_layers):
+    for _ in range(cfg.n_layers + (1 if cfg.mtp else 0)):
         qkv = random_linear(d, cfg.qkv_width, cfg.bits, rng, cfg.codebook, s_in)
         o = random_linear(cfg.n_q * cfg.head_dim, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(cfg.n_q * cfg.head_dim))
         gu = random_linear(d, 2 * F, cfg.bits, rng, cfg.codebook, s_in)
@@ -211,6 +227,10 @@ def random_weights(cfg: DenseConfig, seed: int = 0, per_linear: bool = False) ->
     w.final_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=d))
     hb = cfg.head_bits or cfg.bits
     w.lm_head = random_linear(d, cfg.vocab_padded, hb, rng, cfg.codebook, s_in, zero_cols_from=cfg.vocab if cfg.vocab_padded != cfg.vocab else None)
+    if cfg.mtp:
+        nrm = lambda: _bf16_round(1.0 + 0.1 * rng.normal(size=d))  # noqa: E731
+        w.mtp = HostMtp(nrm(), nrm(), random_linear(d, d, cfg.bits, rng, cfg.codebook, 0.7 * s_in), random_linear(d, d, cfg.bits, rng, cfg.codebook, 0.7 * s_in),
+                        w.layers.pop(), nrm())
     return w
 
 
@@ -240,6 +260,14 @@ class ReferenceDense:
         self.lm_head = t(w.lm_head.dense())[:, :cfg.vocab]
         self.inv_freq = torch.from_numpy(rope_inv_freq(cfg)).to(device)
         self.kv = {}  # seq -> list over layers of (k [T, n_kv, hd], v)
+        self.mtp = None
+        if w.mtp is not None:
+            lay = w.mtp.layer
+            self.mtp = dict(enorm=t(w.mtp.enorm), hnorm=t(w.mtp.hnorm), e_proj=t(w.mtp.e_proj.dense()), h_proj=t(w.mtp.h_proj.dense()), final_norm=t(w.mtp.final_norm),
+                            layer=dict(attn_norm=t(lay.attn_norm), qkv=t(lay.qkv.dense()), o=t(lay.o.dense()), ffn_norm=t(lay.ffn_norm),
+                                       gate_up=t(lay.gate_up.dense()), down=t(lay.down.dense()),
+                                       q_norm=None if lay.q_norm is None else t(lay.q_norm), k_norm=None if lay.k_norm is None else t(lay.k_norm)))
+        self.last_hidden = None     # the trunk's final residual rows of the last forward_seq (what an MTP block reads)
 
     def reset(self, seq=None):
         if seq is None:
@@ -305,10 +333,24 @@ class ReferenceDense:
         pos = torch.arange(start, start + T, device=self.device)
         h = self.embed[ids]
         if seq not in self.kv:
-            self.kv[seq] = [(torch.zeros(0, cfg.n_kv, cfg.head_dim, device=self.device, dtype=self.dtype),) * 2 for _ in self.layers]
+            self.kv[seq] = [(torch.zeros(0, cfg.n_kv, cfg.head_dim, device=self.device, dtype=self.dtype),) * 2 for _ in range(len(self.layers) + 1)]
         for li, L in enumerate(self.layers[:n_layers or len(self.layers)]):
             h = self._ffn(li, L, h + self._mix(li, L, h, pos, seq, start))
+        self.last_hidden = h
         return (self._rms(h, self.final_norm, cfg.eps) @ self.lm_head).float()
+
+    @torch.no_grad()
+    def mtp_seq(self, seq, next_tokens, hidden, start: int):
+        """The MTP block on rows at positions start..: row i reads the trunk (or previous MTP) hidden of position i and the token at i + 1.
+        -> (logits [T, vocab] predicting the tokens at i + 2, the block's output hidden rows)."""
+        cfg, m = self.cfg, self.mtp
+        ids = torch.as_tensor(next_tokens, dtype=torch.long, device=self.device)
+        T = ids.shape[0]
+        pos = torch.arange(start, start + T, device=self.device)
+        h = self._rms(self.embed[ids], m["enorm"], cfg.eps) @ m["e_proj"] + self._rms(hidden, m["hnorm"], cfg.eps) @ m["h_proj"]
+        li = len(self.layers)
+        h = self._ffn(li, m["layer"], h + self._mix(li, m["layer"], h, pos, seq, start))
+        return (self._rms(h, m["final_norm"], cfg.eps) @ self.lm_head).float(), h
 
 
 # ====================================================================================================== sm_100a executor
@@ -332,6 +374,7 @@ class DenseGPU:
         # the three axes equal `positions` and plain RoPE gives the same bits
         self.pos3 = None
         self.device = device
+        self.mtp = None                # the multi-token-prediction block's tensors (config.mtp), set by the loaders of the dense family
         if isinstance(w, DenseConfig):
             self.cfg = cfg = w
             self._load_random(seed)
@@ -350,13 +393,20 @@ class DenseGPU:
         self.kv_i8 = kv_dtype == "int8"
         cdt = torch.uint8 if self.kv_fp8 else (torch.int8 if self.kv_i8 else torch.bfloat16)
         kvl = set(self._kv_layers())
-        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(cfg.n_layers)]
-        self.kv_scale = torch.ones(cfg.n_layers, 2, cfg.n_kv, dtype=torch.float32, device=device) if self.kv_fp8 else None
+        nkv = cfg.n_layers + (1 if getattr(cfg, "mtp", False) else 0)      # the MTP block's attention owns cache index n_layers
+        if nkv > cfg.n_layers:
+            if self.mtp is None:
+                raise ValueError(f"{type(self).__name__} has no multi-token-prediction block (config.mtp is a dense-family feature)")
+            if kv_dtype != "bf16":
+                raise ValueError("the multi-token-prediction block runs on a bf16 KV cache")
+            kvl.add(cfg.n_layers)
+        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(nkv)]
+        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(nkv)]
+        self.kv_scale = torch.ones(nkv, 2, cfg.n_kv, dtype=torch.float32, device=device) if self.kv_fp8 else None
         self.kv_amax = None        # set while calibrating
         mk_ts = lambda: torch.ones(num_pages, cfg.n_kv, PAGE, dtype=torch.float32, device=device)  # noqa: E731
-        self.k_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(cfg.n_layers)]
-        self.v_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(cfg.n_layers)]
+        self.k_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(nkv)]
+        self.v_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(nkv)]
         self.tk = [None if c is None else K.KvTensorMap(c) for c in self.k_cache]
         self.tv = [None if c is None else K.KvTensorMap(c) for c in self.v_cache]
         self.status = K.new_status(device)
@@ -386,6 +436,14 @@ class DenseGPU:
                                     k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16)))
         self.final_norm = dev(w.final_norm, torch.bfloat16)
         self.lm_head = up(w.lm_head)
+        if w.mtp is not None and type(self)._upload_host is DenseGPU._upload_host:
+            lay = w.mtp.layer
+            an, fn = dev(lay.attn_norm, torch.bfloat16), dev(lay.ffn_norm, torch.bfloat16)
+            self.mtp = dict(enorm=dev(w.mtp.enorm, torch.bfloat16), hnorm=dev(w.mtp.hnorm, torch.bfloat16), e_proj=up1(w.mtp.e_proj), h_proj=up1(w.mtp.h_proj),
+                            final_norm=dev(w.mtp.final_norm, torch.bfloat16),
+                            layer=dict(attn_norm=an, qkv=up(lay.qkv, an), o=up(lay.o), ffn_norm=fn, gate_up=up(lay.gate_up, fn), down=up(lay.down),
+                                       q_norm=None if lay.q_norm is None else dev(lay.q_norm, torch.bfloat16),
+                                       k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16)))
 
     def _load_random(self, seed: int) -> None:
         cfg, K, device = self.cfg, self.K, self.device
@@ -402,7 +460,7 @@ class DenseGPU:
         d, F, HQ = cfg.d_model, cfg.ffn_padded, cfg.n_q * cfg.head_dim
         self.embed = torch.randn(cfg.vocab, d, device=device, generator=g).to(torch.bfloat16)
         self.layers = []
-        for _ in range(cfg.n_layers):
+        for _ in range(cfg.n_layers + (1 if getattr(cfg, "mtp", False) else 0)):
             gu = lin(d, 2 * F, 1.0 / math.sqrt(d))
             dn = lin(F, d, 0.5 / math.sqrt(F))
             if F != cfg.ffn:
@@ -411,6 +469,9 @@ class DenseGPU:
                 dn.suh[cfg.ffn:] = 0
             self.layers.append(dict(attn_norm=norm(), qkv=lin(d, cfg.qkv_width, 1.0 / math.sqrt(d)), o=lin(HQ, d, 0.5 / math.sqrt(HQ)),
                                     ffn_norm=norm(), gate_up=gu, down=dn, q_norm=None, k_norm=None))
+        if getattr(cfg, "mtp", False):
+            self.mtp = dict(enorm=norm(), hnorm=norm(), e_proj=lin(d, d, 0.7 / math.sqrt(d)), h_proj=lin(d, d, 0.7 / math.sqrt(d)), final_norm=norm(),
+                            layer=self.layers.pop())
         self.final_norm = norm()
         hw = exl3.Bits.of(cfg.head_bits or cfg.bits).tile_words
         self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d), hw)
@@ -437,6 +498,9 @@ class DenseGPU:
         self.xr = torch.empty(R * kmax, dtype=torch.float16, device=dev)
         self.xr2 = torch.empty(R * cfg.ffn_padded, dtype=torch.float16, device=dev)
         self.h = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
+        if self.mtp is not None:        # the block's own residual stream and the embedding rows of the next tokens
+            self.h_mtp = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
+            self.e_mtp = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
         self.q = torch.empty(R, cfg.n_q * cfg.head_dim, dtype=torch.bfloat16, device=dev)
         self.attn_out = torch.empty(R, cfg.n_q * cfg.head_dim, dtype=torch.bfloat16, device=dev)
         self.logits = torch.empty(min(R, 256), cfg.vocab_padded, dtype=torch.float32, device=dev)
@@ -451,7 +515,7 @@ class DenseGPU:
         """name -> (K, N) of every EXL3 GEMM this executor launches through `_linear` (sizes the split plans and the scratch)."""
         cfg = self.cfg
         return dict(qkv=(cfg.d_model, cfg.qkv_width), o=(cfg.n_q * cfg.head_dim, cfg.d_model), gate_up=(cfg.d_model, 2 * cfg.ffn_padded),
-                    down=(cfg.ffn_padded, cfg.d_model), lm_head=(cfg.d_model, cfg.vocab_padded))
+                    down=(cfg.ffn_padded, cfg.d_model), lm_head=(cfg.d_model, cfg.vocab_padded), eh_proj=(cfg.d_model, cfg.d_model))
 
     def _kv_layers(self):
         """Indices of the layers that own a paged KV cache (all of them here; a hybrid has layers without one)."""
@@ -617,6 +681,47 @@ class DenseGPU:
         logits = self.logits[:R]
         K.finish_store(self.part, s, R, self.lm_head, logits)
         return logits
+
+    def mtp_forward(self, ids_next, hidden, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, max_ctx=None, want_logits=True,
+                    logit_rows=None):
+        """The multi-token-prediction block over M rows: row r reads `hidden[r]` (bf16 [M, d]: the trunk's final residual of a position, or this
+        block's own output when drafts are chained) and `ids_next[r]`, the token AFTER that position; positions / slots / ctx_len are the
+        position's own (the block's KV cache is indexed like the trunk's).  Returns (logits of the shared head or None, the block's output
+        residual rows: a view of a reused buffer).  Same kernels and the same row rules as a trunk layer."""
+        if self.mtp is None:
+            raise ValueError("this model has no multi-token-prediction block")
+        cfg, K, m = self.cfg, self.K, self.mtp
+        M = ids_next.shape[0]
+        cls = "decode" if prefill is None else "prefill"
+        assert M <= self.max_rows and (prefill is not None or M <= 256) and hidden.shape == (M, cfg.d_model) and hidden.dtype == torch.bfloat16
+        d, F, HQ = cfg.d_model, cfg.ffn_padded, cfg.n_q * cfg.head_dim
+        h, e = self.h_mtp[:M], self.e_mtp[:M]
+        xr_d = self.xr[:M * d].view(M, d)
+        xr_a = self.xr[:M * HQ].view(M, HQ)
+        xr_f = self.xr2[:M * F].view(M, F)
+        q = self.q[:M]
+        Lm = m["layer"]
+        if prefill is None and self.attn_plan is not None:
+            K.attn_plan(row_seq, ctx_len, cfg.n_q, cfg.n_kv, self.window_seq_rows, self.attn_plan)
+        self.pos3 = None
+        K.embed(ids_next, self.embed, e)
+        K.norm_rot_in(e, m["enorm"], cfg.eps, m["e_proj"].suh, xr_d)
+        s = self._linear(xr_d, m["e_proj"], M, cls, "eh_proj")
+        K.finish_store(self.part, s, M, m["e_proj"], h)
+        K.norm_rot_in(hidden, m["hnorm"], cfg.eps, m["h_proj"].suh, xr_d)
+        s = self._linear(xr_d, m["h_proj"], M, cls, "eh_proj")
+        K.finish_add_norm_rot(self.part, s, M, m["h_proj"], h, Lm["attn_norm"], cfg.eps, Lm["qkv"].suh, xr_d)
+        s = self._mixer(cfg.n_layers, Lm, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, 1.0 / math.sqrt(cfg.head_dim))
+        self._ffn(cfg.n_layers, Lm, M, cls, s, h, xr_d, xr_f, m["final_norm"], self.lm_head.suh)
+        if not want_logits:
+            return None, h
+        xl = xr_d if logit_rows is None else xr_d.index_select(0, logit_rows).contiguous()
+        R = xl.shape[0]
+        assert R <= self.logits.shape[0]
+        s = self._linear(xl, self.lm_head, R, "decode", "lm_head")
+        logits = self.logits[:R]
+        K.finish_store(self.part, s, R, self.lm_head, logits)
+        return logits, h
 
     def candidates(self, logits: torch.Tensor, count: int):
         """Top `count` (value desc, id asc) of each row, padded vocabulary columns excluded by construction (their logit is 0 * svh = 0

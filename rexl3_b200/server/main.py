@@ -222,8 +222,10 @@ def build(args):
                     from ..engine.gpu_backend import HybridGpuBackend
                     be = HybridGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs, state_snapshots=args.state_snapshots)
                 else:
-                    be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs,
-                                         self_draft=args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
+                    # a model with a multi-token-prediction block drafts from it; else the self-speculative drafter where a draft depth is defined
+                    mtp = args.spec in ("auto", "mtp") and not args.no_drafts and getattr(model, "mtp", None) is not None
+                    be = DenseGpuBackend(model, max_slots=args.slots, use_graphs=not args.no_graphs, mtp_draft=mtp,
+                                         self_draft=not mtp and args.spec in ("auto", "self") and not args.no_drafts and getattr(cfg, "draft_layers", 0) > 0)
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args, model), device_sampler=args.device_sampler,

@@ -220,3 +220,85 @@ def test_moe_and_mla_models_load_from_their_packs(tmp_path):
             torch.cuda.synchronize()
             outs.append(lg[0, :cfg.vocab].clone())
         assert torch.equal(outs[0], outs[1]), kind
+
+
+def _mtp_setup(seed=5):
+    import dataclasses
+    from rexl3_b200.models import dense
+    cfg = dataclasses.replace(dense.CONFIGS["test-hd128"], mtp=True, name="test-hd128-mtp")
+    return cfg, dense.random_weights(cfg, seed=seed), dense
+
+
+def test_mtp_block_matches_reference():
+    """The multi-token-prediction block (hidden of position i + token i + 1 -> logits of token i + 2) against the fp32 oracle: a prefill slice
+    of lagged rows, then chained draft rows on the block's own output."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    cfg, w, dense = _mtp_setup()
+    ref = dense.ReferenceDense(w, device="cuda")
+    m = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, cfg.vocab, size=90).tolist()
+    T = len(prompt)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[0, :3] = i32([3, 7, 5])
+    pos = list(range(T))
+    slots = [int(bt[0, p // 64]) * 64 + p % 64 for p in pos]
+    pf = dict(seq_ids=i32([0]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+    m.forward_rows(i32(prompt), i32(pos), i32(slots), i32([0] * T), i32([p + 1 for p in pos]), bt, prefill=pf)
+    hid = m.h[:T].clone()
+    ref.forward_seq(0, prompt, 0)
+    assert (hid.float() - ref.last_hidden).abs().max().item() < 0.05 * ref.last_hidden.abs().max().item()
+    # lagged rows 0 .. T-2 (token i + 1 known), as a prefill slice of the block
+    n = T - 1
+    pf2 = dict(seq_ids=i32([0]), q_start=i32([0]), q_len=i32([n]), pos0=i32([0]), nseq=1, max_qlen=n)
+    logits, hm = m.mtp_forward(i32(prompt[1:]), hid[:n].contiguous(), i32(pos[:n]), i32(slots[:n]), i32([0] * n), i32([p + 1 for p in pos[:n]]), bt, prefill=pf2,
+                               logit_rows=torch.tensor([n - 1], device="cuda"))
+    got, hm = logits[0, :cfg.vocab].clone(), hm.clone()
+    m.check()
+    want, want_h = ref.mtp_seq(0, prompt[1:], ref.last_hidden[:n], 0)
+    scale = want.abs().max().item()
+    assert (got - want[-1]).abs().max().item() < 0.05 * scale
+    assert (hm.float() - want_h).abs().max().item() < 0.05 * want_h.abs().max().item()
+    # row T-1 with a sampled token, then two chained rows on the block's own hidden (decode class, one row each)
+    tok, h_in, h_ref = 17, hid[T - 1:T].contiguous(), ref.last_hidden[T - 1:T]
+    for j in range(3):
+        p = T - 1 + j
+        lg, ho = m.mtp_forward(i32([tok]), h_in, i32([p]), i32([int(bt[0, p // 64]) * 64 + p % 64]), i32([0]), i32([p + 1]), bt, max_ctx=256)
+        lg, h_in = lg[0, :cfg.vocab].clone(), ho.clone()
+        m.check()
+        wl, h_ref = ref.mtp_seq(0, [tok], h_ref, p)
+        assert (lg - wl[0]).abs().max().item() < 0.06 * scale, j
+        tok = int(wl[0].argmax())
+
+
+def test_mtp_drafts_change_the_schedule_never_the_tokens():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.engine import Engine, Request
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    from rexl3_b200.sampling import GREEDY
+    cfg, w, dense = _mtp_setup(seed=6)
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (70, 21, 130)]
+    outs = {}
+    for mode in ("none", "mtp"):
+        m = dense.DenseGPU(w, num_pages=32, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=64)
+        be = DenseGpuBackend(m, max_slots=4, mtp_draft=(mode == "mtp"))
+        eng = Engine(be, None, window_rows=32, prefill_chunk=64, spec=mode, max_drafts=3)
+        for i, p in enumerate(prompts):
+            eng.submit(Request(f"r{i}", p, 12, GREEDY))
+        got = {f"r{i}": [] for i in range(len(prompts))}
+        for _ in range(300):
+            if not eng.has_work():
+                break
+            for ev in eng.step():
+                if ev.kind == "tokens":
+                    got[ev.id].extend(ev.tokens)
+                assert ev.kind != "error", ev.message
+        outs[mode] = got
+        if mode == "mtp":
+            st = be.stats()
+            assert eng.counters["drafted"] > 0 and st["draft_steps"] > 0 and st["mtp_rows"] > 0
+    assert outs["none"] == outs["mtp"]
