@@ -31,7 +31,11 @@ def main() -> int:
     ap.add_argument("--tail-scale", type=float, nargs="*", default=[1.0],
                     help="one run per value: the output scales of o_proj / down_proj in the layers above the draft depth are multiplied by it "
                          "(1.0 = plain random init, acceptance ~0; small values make the 4-layer draft agree with the target more often)")
+    ap.add_argument("--mtp", action="store_true",
+                    help="one GPU, a dense config (--model dense-27b): drafts come from a multi-token-prediction block (random init, so nothing is "
+                         "accepted: the run shows what the block's lagged rows and a chain of k drafts cost per round)")
     args = ap.parse_args()
+    import dataclasses
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -43,7 +47,8 @@ def main() -> int:
     from ..sampling import GREEDY
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    cfg = moe.CONFIGS[args.model]
+    cfg = dataclasses.replace(dense.CONFIGS[args.model], mtp=True, name=args.model + "-mtp") if args.mtp else moe.CONFIGS[args.model]
+    drafter = "mtp" if args.mtp else "self"
     B, P, K, W, D = args.batch, args.prompt, args.steps, max(3, args.warmup), args.drafts
     new_tokens = (K + W) * (D + 1) * 2 + 16
     blocks = (P + new_tokens + dense.PAGE - 1) // dense.PAGE + 1
@@ -60,16 +65,19 @@ def main() -> int:
 
     def measure(eps: float) -> dict:
         results = {}
-        for mode in ("none", "self"):
+        for mode in ("none", drafter):
             measure_mode(eps, mode, results)
         return results
 
     def measure_mode(eps: float, mode: str, results: dict) -> None:
-        model = moe.MoEGPU(cfg, num_pages=pages, max_rows=256, max_seqs=B + 1, max_blocks_per_seq=blocks, max_prefill_rows=P, seed=0,
-                           experts=experts, ep=comm)
-        if eps != 1.0:
-            model.scale_tail(cfg.draft_layers, eps)
-        inner = DenseGpuBackend(model, max_slots=B + 1, self_draft=(mode == "self"))
+        if args.mtp:
+            model = dense.DenseGPU(cfg, num_pages=pages, max_rows=256, max_seqs=B + 1, max_blocks_per_seq=blocks, max_prefill_rows=P, seed=0)
+        else:
+            model = moe.MoEGPU(cfg, num_pages=pages, max_rows=256, max_seqs=B + 1, max_blocks_per_seq=blocks, max_prefill_rows=P, seed=0,
+                               experts=experts, ep=comm)
+            if eps != 1.0:
+                model.scale_tail(cfg.draft_layers, eps)
+        inner = DenseGpuBackend(model, max_slots=B + 1, self_draft=(mode == "self"), mtp_draft=(mode == "mtp"))
         if world > 1 and rank != 0:
             follow(inner, ctx.ctrl)
             torch.cuda.synchronize()
@@ -116,10 +124,11 @@ def main() -> int:
         dist.barrier(group=ctx.ctrl)
     if rank == 0:
         print(json.dumps({"bench": "spec_moe", "model": cfg.name, "n_gpus": world, "parallelism": f"ep{world}" if world > 1 else "single",
-                          "batch": B, "prompt": P, "rounds": K, "draft": f"self: first {cfg.draft_layers} layers + shared head, chain k={D}",
-                          "dtype": "bf16 activations, EXL3 3.0 bpw weights", "data": "synthetic (random init; tail_scale multiplies the output scales of o_proj / down_proj above the draft depth)",
-                          "runs": [dict(tail_scale=eps, spec_off=r["none"], spec_on=r["self"],
-                                        speedup=round(r["self"]["tokens_per_s"] / r["none"]["tokens_per_s"], 3)) for eps, r in runs]}))
+                          "batch": B, "prompt": P, "rounds": K,
+                          "draft": f"mtp block, chain k={D}" if args.mtp else f"self: first {cfg.draft_layers} layers + shared head, chain k={D}",
+                          "dtype": f"bf16 activations, EXL3 {cfg.bits} bpw weights", "data": "synthetic (random init; tail_scale multiplies the output scales of o_proj / down_proj above the draft depth)",
+                          "runs": [dict(tail_scale=eps, spec_off=r["none"], spec_on=r[drafter],
+                                        speedup=round(r[drafter]["tokens_per_s"] / r["none"]["tokens_per_s"], 3)) for eps, r in runs]}))
     if world > 1:
         dist.destroy_process_group()
     return 0

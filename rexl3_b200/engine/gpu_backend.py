@@ -456,6 +456,12 @@ class DenseGpuBackend(Backend):
         return self._download(R, count)
 
     def _check(self) -> None:
+        from ..utils import canary
+        if canary.enabled():
+            try:
+                canary.check_all()
+            except canary.CanaryError as e:
+                self._err = BackendError(f"guard band damaged: {e}", fatal=True)
         s = self.h_status.tolist()
         if s[0] != 0:
             self.m.status[:4].zero_()

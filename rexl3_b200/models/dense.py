@@ -490,20 +490,22 @@ class DenseGPU:
                 self.splits[(cls, name)] = s
                 r = rows if name != "lm_head" else min(rows, 256)
                 part_elems = max(part_elems, s * r * n)
-        self.part = torch.empty(part_elems, dtype=torch.float32, device=dev)
+        from ..utils import canary
+        g = lambda name, shape, dt: canary.guarded(f"{type(self).__name__}.{name}", shape, dt, dev)  # noqa: E731  (guard bands with REXL3_CANARY=1)
+        self.part = g("part", part_elems, torch.float32)
         # split projections (per-linear input rotations) run one GEMM per part into this second buffer before the partials are placed
         split = any(isinstance(v, SplitWeight) for L in self.layers for v in L.values())
         self._part_split = torch.empty(part_elems, dtype=torch.float32, device=dev) if split else None
         kmax = max(k for k, _ in shapes.values())
-        self.xr = torch.empty(R * kmax, dtype=torch.float16, device=dev)
-        self.xr2 = torch.empty(R * cfg.ffn_padded, dtype=torch.float16, device=dev)
-        self.h = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
+        self.xr = g("xr", R * kmax, torch.float16)
+        self.xr2 = g("xr2", R * cfg.ffn_padded, torch.float16)
+        self.h = g("h", (R, cfg.d_model), torch.bfloat16)
         if self.mtp is not None:        # the block's own residual stream and the embedding rows of the next tokens
             self.h_mtp = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
             self.e_mtp = torch.empty(R, cfg.d_model, dtype=torch.bfloat16, device=dev)
-        self.q = torch.empty(R, cfg.n_q * cfg.head_dim, dtype=torch.bfloat16, device=dev)
-        self.attn_out = torch.empty(R, cfg.n_q * cfg.head_dim, dtype=torch.bfloat16, device=dev)
-        self.logits = torch.empty(min(R, 256), cfg.vocab_padded, dtype=torch.float32, device=dev)
+        self.q = g("q", (R, cfg.n_q * cfg.head_dim), torch.bfloat16)
+        self.attn_out = g("attn_out", (R, cfg.n_q * cfg.head_dim), torch.bfloat16)
+        self.logits = g("logits", (min(R, 256), cfg.vocab_padded), torch.float32)
         self.max_ctx_alloc = self.max_blocks * PAGE
         self.attn_scratch = K.attn_decode_scratch(min(R, 256), cfg.n_q, cfg.head_dim, self.max_ctx_alloc, dev)
         self.attn_plan = K.attn_plan_buffer(dev)
@@ -740,3 +742,6 @@ class DenseGPU:
 
     def check(self, what="forward"):
         self.K.check_status(self.status, what)
+        from ..utils import canary
+        if canary.enabled():
+            canary.check_all()

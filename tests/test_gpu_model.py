@@ -302,3 +302,29 @@ def test_mtp_drafts_change_the_schedule_never_the_tokens():
             st = be.stats()
             assert eng.counters["drafted"] > 0 and st["draft_steps"] > 0 and st["mtp_rows"] > 0
     assert outs["none"] == outs["mtp"]
+
+
+def test_guard_bands_stay_intact_through_prefill_and_decode(monkeypatch):
+    """REXL3_CANARY=1: every scratch buffer of the executor sits between guard bands; a prefill slice and decode windows leave them untouched."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    monkeypatch.setenv("REXL3_CANARY", "1")
+    from rexl3_b200.models import dense
+    from rexl3_b200.utils import canary
+    canary.forget()
+    cfg = dense.CONFIGS["test-hd128"]
+    m = dense.DenseGPU(dense.random_weights(cfg, seed=1), num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=128)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[0, :3] = i32([3, 7, 5])
+    T = 128
+    pos = list(range(T))
+    slots = [int(bt[0, p // 64]) * 64 + p % 64 for p in pos]
+    pf = dict(seq_ids=i32([0]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+    m.forward_rows(i32([5] * T), i32(pos), i32(slots), i32([0] * T), i32([p + 1 for p in pos]), bt, prefill=pf, logit_rows=torch.tensor([T - 1], device="cuda"))
+    for p in range(T, T + 3):
+        m.forward_rows(i32([9]), i32([p]), i32([int(bt[0, p // 64]) * 64 + p % 64]), i32([0]), i32([p + 1]), bt, max_ctx=256)
+    torch.cuda.synchronize()
+    m.check()
+    assert canary.check_all() >= 7
+    canary.forget()
