@@ -297,7 +297,12 @@ class ReferenceDense:
         x = self._rms(h, L["ffn_norm"], cfg.eps)
         gu = x @ L["gate_up"]
         F = cfg.ffn_padded
-        return h + (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
+        y = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
+        ov = getattr(self, "interventions", {}).get(li)
+        if ov is not None:                      # runtime overlay at the block's output (models/intervention.py)
+            from .intervention import apply_reference
+            y = apply_reference(y, ov)
+        return h + y
 
     def _mix(self, li, L, h, pos, seq, start):
         """Token mixer of one layer on the residual stream `h` [T, d]: returns what is added to it (here: GQA attention + o_proj)."""
@@ -375,6 +380,8 @@ class DenseGPU:
         self.pos3 = None
         self.device = device
         self.mtp = None                # the multi-token-prediction block's tensors (config.mtp), set by the loaders of the dense family
+        self.interventions = {}        # layer -> (alpha, orthonormal basis f32 [r, d]) runtime overlays (set_interventions)
+        self._iv_y = None
         if isinstance(w, DenseConfig):
             self.cfg = cfg = w
             self._load_random(seed)
@@ -613,7 +620,28 @@ class DenseGPU:
         s = self._linear(xr_d, L["gate_up"], M, cls, "gate_up")
         K.finish_swiglu_rot(self.part, s, M, L["gate_up"], L["down"].suh, xr_f)
         s = self._linear(xr_f, L["down"], M, cls, "down")
-        K.finish_add_norm_rot(self.part, s, M, L["down"], h, next_norm, cfg.eps, next_suh, xr_d)
+        ov = self.interventions.get(li) if self.interventions else None
+        if ov is None:
+            K.finish_add_norm_rot(self.part, s, M, L["down"], h, next_norm, cfg.eps, next_suh, xr_d)
+            return
+        # a runtime overlay on this layer's block output: finish the rows to f32, remove the overlay's directions, then residual, norm, rotation
+        y = self._iv_y[:M]
+        K.finish_store(self.part, s, M, L["down"], y)
+        y.addmm_(y @ ov[1].T, ov[1], alpha=-ov[0])
+        h.copy_(h.float() + y)
+        if next_suh is not None:
+            K.norm_rot_in(h, next_norm, cfg.eps, next_suh, xr_d)
+
+    def set_interventions(self, overlays: dict) -> None:
+        """overlays: {layer: models.intervention.LayerOverlay} (or {} to clear).  Applied at the output of the layer's feed-forward block."""
+        if overlays and (type(self)._ffn is not DenseGPU._ffn or type(self)._ffn_phases is not DenseGPU._ffn_phases):
+            raise ValueError(f"{type(self).__name__} replaces the feed-forward block: no overlay hook there (an overlay never applies silently in part)")
+        for li in overlays:
+            if not 0 <= li < self.cfg.n_layers:
+                raise ValueError(f"intervention on layer {li}: the model has layers 0..{self.cfg.n_layers - 1}")
+        self.interventions = {li: (float(o.alpha), torch.from_numpy(o.basis).to(self.device)) for li, o in overlays.items()}
+        if overlays and getattr(self, "_iv_y", None) is None:
+            self._iv_y = torch.empty(self.max_rows, self.cfg.d_model, dtype=torch.float32, device=self.device)
 
     def _ffn_phases(self, *a):
         """Generator form of `_ffn`: yields wherever the ranks of a multi-rank executor must all have launched the previous kernels

@@ -39,6 +39,8 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8"], default="bf16",
                    help="fp8: E4M3 cache with per-head scales (calibrated at boot); int8: one power-of-two scale per token and KV head (no calibration)")
     p.add_argument("--spec", choices=["auto", "mtp", "copy", "ngram", "self", "none"], default="auto")
+    p.add_argument("--intervention", metavar="DIR", default=None,
+                   help="a runtime overlay directory (intervention.json + direction files): checked against the model at boot, any mismatch refuses")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
     p.add_argument("--prefix-cache", choices=["on", "off"], default="on")
@@ -214,6 +216,14 @@ def build(args):
                     model = hybrid_models.HybridGPU(weights if weights is not None else cfg, **common)
                 else:
                     model = dense.DenseGPU(weights if weights is not None else cfg, kv_dtype=args.kv_dtype, **common)
+                if args.intervention:
+                    from ..models import intervention as _iv
+                    if not hasattr(model, "set_interventions"):
+                        raise SystemExit(f"--intervention: the {type(model).__name__} executor has no overlay hook")
+                    try:
+                        model.set_interventions(_iv.load(args.intervention, n_layers=cfg.n_layers, d_model=cfg.d_model, model_name=None))
+                    except (_iv.InterventionError, ValueError) as e:
+                        raise SystemExit(f"--intervention refused: {e}")
                 if args.kv_dtype == "fp8":
                     import numpy as np
                     model.calibrate_kv(np.random.default_rng(0).integers(0, cfg.vocab, size=min(256, args.prefill_chunk)).tolist())
