@@ -19,7 +19,7 @@ from dataclasses import dataclass, field
 BUILT_COMPONENTS = frozenset({
     "exl3_linear", "gqa_attention", "rope", "qk_norm", "swiglu_ffn", "paged_kv_bf16", "paged_kv_fp8", "paged_kv_int8", "mla_attention", "moe_softmax_topk",
     "moe_sigmoid_bias_topk", "mxfp4_experts", "shared_expert", "mamba2_mixer", "gated_delta_net", "kimi_delta_attention", "self_speculative_draft",
-    "copy_draft", "ngram_draft", "prefix_cache", "tensor_parallel", "expert_parallel", "mtp_head", "vision_tower", "mrope",
+    "copy_draft", "ngram_draft", "prefix_cache", "tensor_parallel", "expert_parallel", "mtp_head", "vision_tower", "mrope", "sparse_indexer",
 })
 
 
@@ -198,7 +198,86 @@ class MimoFamily(Family):
                           notes=["probe / plan only: this family's executor (hybrid sliding-window attention, MTP layers, audio and vision towers) is not built"])
 
 
-FAMILIES = (DenseFamily(), HybridFamily(), MoEFamily(), MlaMoEFamily(), MimoFamily())
+def generic_memory(root: dict) -> tuple:
+    """(config summary, memory model) of a decoder described by well-known Hugging Face keys: GQA or latent attention, dense or routed
+    feed-forward blocks (+ shared experts), recurrent layers counted from a layer-type list where the configuration carries one."""
+    t = root.get("text_config") if isinstance(root.get("text_config"), dict) else root
+
+    def need(key):
+        v = t.get(key)
+        if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+            raise FamilyError("config", f"config.json: `{key}` must be a positive int")
+        return v
+    d, L, nq, vocab = need("hidden_size"), need("num_hidden_layers"), need("num_attention_heads"), need("vocab_size")
+    nkv = t.get("num_key_value_heads") or nq
+    hd = t.get("head_dim") or d // nq
+    bits = float((_q(root) or {}).get("bits", 4.0))
+    kv_lora = t.get("kv_lora_rank") or 0
+    if kv_lora:
+        q_lora, rope, nope, vd = t.get("q_lora_rank") or 0, t.get("qk_rope_head_dim") or 64, t.get("qk_nope_head_dim") or 128, t.get("v_head_dim") or 128
+        attn = (d * q_lora + q_lora * nq * (nope + rope) if q_lora else d * nq * (nope + rope)) + d * (kv_lora + rope) + kv_lora * nq * (nope + vd) + nq * vd * d
+        kv_tok = (kv_lora + rope) * 2
+    else:
+        attn = d * (nq + 2 * nkv) * hd + nq * hd * d
+        kv_tok = 2 * nkv * hd * 2
+    kinds = t.get("layer_types") or t.get("layers_block_type") or []
+    n_attn = sum(1 for k in kinds if "attention" in str(k) and "linear" not in str(k)) if kinds else L
+    E = t.get("n_routed_experts") or t.get("num_experts") or t.get("num_local_experts") or 0
+    k = t.get("num_experts_per_tok") or 0
+    eff = t.get("moe_intermediate_size") or 0
+    shared = (t.get("n_shared_experts") or 0) * eff
+    ffn = t.get("intermediate_size") or 0
+    n_dense = t.get("first_k_dense_replace") or 0 if E else L
+    moe_layers = L - n_dense if E else 0
+    params = L * attn + n_dense * 3 * d * ffn + moe_layers * (3 * d * eff * E + d * E + 3 * d * shared) + 2 * vocab * d
+    active = L * attn + n_dense * 3 * d * ffn + moe_layers * (3 * d * eff * k + 3 * d * shared) + vocab * d
+    cfg = dict(d_model=d, n_layers=L, attention_layers=n_attn, n_q=nq, n_kv=nkv, head_dim=hd, kv_lora_rank=kv_lora, ffn=ffn, n_experts=E, top_k=k, expert_ffn=eff,
+               vocab=vocab, bits=bits)
+    mem = dict(parameters=int(params), weight_bytes=int(params * bits / 8), kv_bytes_per_token=int(kv_tok * n_attn), active_parameters_per_token=int(active))
+    return cfg, mem
+
+
+class ProbeOnlyFamily(Family):
+    """A family of the reference that this build recognises, inventories and sizes, but has no executor for: the pack is refused for serving
+    by its own name with the parts that exist and the parts that are missing, instead of being mistaken for a neighbour."""
+
+    def __init__(self, fid: str, architectures: tuple, model_types: tuple, have: list, missing: str):
+        self.id, self.architectures, self.model_types, self.have, self.missing = fid, tuple(architectures), tuple(model_types), list(have), missing
+
+    def plan(self, root, folder):
+        cfg, mem = generic_memory(root)
+        comps = infer_components(root)
+        return FamilyPlan(self.id, cfg, comps, servable=False, memory=mem, vision=bool(root.get("vision_config")),
+                          notes=[f"probe / plan only: parts this build has: {', '.join(self.have)}; not built as a family executor: {self.missing}"])
+
+
+PROBE_ONLY = (
+    ProbeOnlyFamily("qwen_flash_next", ("Qwen4ExpForConditionalGeneration", "Qwen4ExpForCausalLM"), (),
+                    ["gqa_attention", "gated_delta_net", "hyper_connection kernels", "mtp block (dense family)", "vision tower"],
+                    "the QSA indexer, per-layer embedding tables and the composition of hyper-connections with the mixers"),
+    ProbeOnlyFamily("glm", ("Glm5NextForConditionalGeneration",), (),
+                    ["mla_attention", "kimi_delta_attention", "sparse indexer (DSA with pooled keys)", "hyper_connection kernels", "moe_sigmoid_bias_topk", "mtp block"],
+                    "one executor that alternates KDA and sparse MLA layers under hyper-connections, its TP=2 schedule and its vision tower"),
+    ProbeOnlyFamily("minicpmv4_7", ("MiniCPMV4_7ForConditionalGeneration", "MiniCPMV4_6ForConditionalGeneration"), ("minicpmv4_7", "minicpmv4_6"),
+                    ["gated_delta_net", "gqa_attention", "moe_softmax_topk", "vision preprocessing"],
+                    "the GDN + MoE composition, the DSpark drafter and the SigLIP tower with its resampler"),
+    ProbeOnlyFamily("bailing_moe_v3", ("BailingMoeV3ForCausalLM",), (),
+                    ["mla_attention", "kimi_delta_attention", "moe_sigmoid_bias_topk", "prefix spill tier"],
+                    "gated latent attention, the group-limited router and the MTP head of this family"),
+    ProbeOnlyFamily("deepseek_v41", ("DeepseekV41ForCausalLM",), ("deepseek_v41_text", "deepseek_v4_1_vision"),
+                    ["mla_attention (bf16)", "sparse indexer", "mxfp4_experts", "fp8 block-scaled linear", "hyper_connection kernels", "expert page cache"],
+                    "FP8 latent cache and the compressor planes, Engram tables, q4 KV rows and the NextN head on the latent executor"),
+    ProbeOnlyFamily("qwen", ("Qwen3_5ForConditionalGeneration", "Qwen3_5ForCausalLM", "Qwen3_5MoeForConditionalGeneration", "Qwen3_5MoeForCausalLM"),
+                    ("qwen3_5", "qwen3_5_moe"),
+                    ["gated_delta_net + gqa_attention (served from this repository's rexl3_hybrid packs)", "record / commit of recurrent state", "mrope",
+                     "vision tower"],
+                    "the mapping of this family's own tensor names onto the hybrid executor, the DFlash2 drafter and the MoE variant's composition"),
+    ProbeOnlyFamily("nemotron_h_omni", ("NemotronHOmniForConditionalGeneration", "NemotronHForCausalLM"), ("nemotron_h_omni", "nemotron_h"),
+                    ["mamba2_mixer", "gqa_attention (NoPE)", "paged_kv_int8", "vision tower"],
+                    "the latent-MoE feed-forward (relu^2, top-22), its MTP head and the audio / video towers"),
+)
+
+FAMILIES = (DenseFamily(), HybridFamily(), MoEFamily(), MlaMoEFamily(), MimoFamily()) + PROBE_ONLY
 
 
 def infer_components(root: dict) -> list:
@@ -312,7 +391,7 @@ class Registry:
             raise
         except (KeyError, TypeError, ValueError) as e:
             raise FamilyError("config", f"config.json refused by family `{fam.id}`: {e.__class__.__name__}: {e}")
-        missing = [c for c in plan.components if c not in BUILT_COMPONENTS]
+        missing = [c for c in plan.components if c not in BUILT_COMPONENTS] if plan.servable else []     # a probe-only plan lists what it would need
         if missing:
             raise FamilyError("unsupported", f"family `{fam.id}` needs components this build does not have: {', '.join(missing)}")
         return fam, plan

@@ -35,9 +35,9 @@ def test_refusals_name_what_is_wrong():
         R.probe_config(dict(BASE, architectures="LlamaForCausalLM"))
     # an unknown architecture is never rescued by a familiar model type; the report names missing components and the nearest family
     with pytest.raises(registry.FamilyError) as e:
-        R.probe_config(dict(BASE, architectures=["Qwen4ExpForCausalLM"], model_type="llama", index_topk=2048, num_hyper_connections=4))
+        R.probe_config(dict(BASE, architectures=["Qwen9FutureForCausalLM"], model_type="llama", rope_scaling={"type": "yarn"}, num_hyper_connections=4))
     msg = str(e.value)
-    assert "no family serves `Qwen4ExpForCausalLM`" in msg and "sparse_indexer" in msg and "hyper_connections" in msg and "LlamaForCausalLM" in msg
+    assert "no family serves `Qwen9FutureForCausalLM`" in msg and "yarn_rope" in msg and "hyper_connections" in msg and "LlamaForCausalLM" in msg
     assert e.value.report.nearest in ("dense", "moe")
     with pytest.raises(registry.FamilyError, match="tie_word_embeddings"):
         R.probe_config(dict(BASE, architectures=["LlamaForCausalLM"], tie_word_embeddings=True))
@@ -163,3 +163,27 @@ def test_probe_only_family_is_sized_and_refused_by_name(tmp_path, capsys):
     (folder / "config.json").write_text(json.dumps({**cfg, "hidden_size": "big"}))
     with _pt.raises(registry.FamilyError):
         registry.probe(str(folder))
+
+
+@pytest.mark.parametrize("arch,fid", [("Glm5NextForConditionalGeneration", "glm"), ("DeepseekV41ForCausalLM", "deepseek_v41"),
+                                      ("BailingMoeV3ForCausalLM", "bailing_moe_v3"), ("Qwen4ExpForCausalLM", "qwen_flash_next"),
+                                      ("MiniCPMV4_7ForConditionalGeneration", "minicpmv4_7"), ("NemotronHForCausalLM", "nemotron_h_omni"),
+                                      ("Qwen3_5MoeForCausalLM", "qwen")])
+def test_every_reference_family_is_recognised_sized_and_refused_by_its_own_name(tmp_path, arch, fid):
+    import json
+    from rexl3_b200.models import registry
+    cfg = {"architectures": [arch], "hidden_size": 4096, "num_hidden_layers": 40, "num_attention_heads": 32, "num_key_value_heads": 4, "head_dim": 128,
+           "intermediate_size": 12288, "vocab_size": 151936, "n_routed_experts": 128, "num_experts_per_tok": 8, "moe_intermediate_size": 1024,
+           "n_shared_experts": 1, "first_k_dense_replace": 2, "kv_lora_rank": 512 if fid in ("glm", "deepseek_v41", "bailing_moe_v3") else 0,
+           "q_lora_rank": 1536, "index_topk": 2048, "num_nextn_predict_layers": 1, "quantization_config": {"quant_method": "exl3", "bits": 3.0}}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    fam, p = registry.probe(str(tmp_path))
+    assert fam.id == fid and p.servable is False and "probe / plan only" in p.notes[0]
+    m = p.memory
+    assert m["parameters"] > m["active_parameters_per_token"] > 0 and m["weight_bytes"] == int(m["parameters"] * 3.0 / 8)
+    assert m["kv_bytes_per_token"] == (40 * (512 + 64) * 2 if cfg["kv_lora_rank"] else 40 * 2 * 4 * 128 * 2)
+    assert "sparse_indexer" in p.components and "mtp_head" in p.components
+    from rexl3_b200.server import main as srv
+    with pytest.raises(SystemExit) as e:
+        srv.build(srv.parser().parse_args(["--model", str(tmp_path), "--backend", "cpu"]))
+    assert "plan_only" in str(e.value) and fid in str(e.value)
