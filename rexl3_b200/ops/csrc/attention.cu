@@ -504,6 +504,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
         if constexpr (FP8) attn_step_mt<HD, MT, true>(qa, smem_u32(conv), smem_u32(conv + T16), key0, valid, ntiles, scale_log2, m, l, o);
         else attn_step_mt<HD, MT, false>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), key0, valid, ntiles, scale_log2, m, l, o);
       }
+      fence_proxy_async();      // this page was read with ordinary loads; the refill of its stage (next iteration) writes through the async proxy
       __syncthreads();
     }
     if (!ok || *abort_flag != 0) return;
@@ -754,6 +755,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     } else {
       if (mine) attn_step<HD, 64>(qa, smem_u32(smem + s * TILE), smem_u32(smem + (KV_STAGES + s) * TILE), 0, v0, v1, scale_log2, m, l, o);
     }
+    fence_proxy_async();        // ordinary loads of this page before the async-proxy refill of its stage
     __syncthreads();
   }
   if (!ok || *abort_flag != 0) return;

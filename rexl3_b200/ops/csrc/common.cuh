@@ -113,6 +113,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Release of a shared-memory stage that this warp READ with ordinary loads (generic proxy) back to a writer of the async proxy (a bulk / tensor
+// copy): the proxy fence orders the reads before whatever the arrive lets the copy engine write.  Without it the copy may overtake the reads
+// (seen on B200: operand rows that mixed two K chunks).  Every reading lane runs the fence; one lane arrives.
+__device__ __forceinline__ void release_read_stage(uint64_t* empty_bar, int lane) {
+  fence_proxy_async();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(empty_bar);
+}
+
 // ---------------------------------------------------------------- TMA
 // 1-D bulk copy global -> this CTA's shared memory, completion on an mbarrier (no multicast anywhere).
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {

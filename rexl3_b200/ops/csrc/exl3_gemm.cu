@@ -192,8 +192,7 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
         const uint32_t sh_second = __shfl_sync(0xffffffffu, second.w, src), sh_first = __shfl_sync(0xffffffffu, first.w, src);
         const uint32_t w1[5] = {x ? second.w : sh_second, first.x, first.y, first.z, first.w};
         const uint32_t w2[5] = {x ? sh_first : first.w, second.x, second.y, second.z, second.w};
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        release_read_stage(&raw_empty[rs], lane);      // generic-proxy reads, async-proxy refill: proxy fence before the release
         if (c >= OP_STAGES) ok = mbar_wait(&op_empty[os], ((c / OP_STAGES) - 1) & 1, abort_flag, status, 31);
         if (!ok) break;
         uint8_t* a_tile = smem + L.a_off + os * A_STAGE;
@@ -256,9 +255,7 @@ exl3_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint32_t* __r
           *reinterpret_cast<uint4*>(a_tile + (n_local >> 3) * 1024 + (n_local & 7) * 128 + chunk * 16) = quarter_chunk(h2, a, b2, kc);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);
-      fence_proxy_async();
+      release_read_stage(&raw_empty[rs], lane);        // (the fence also covers the operand tile written above)
       __syncwarp();
       if (lane == 0) mbar_arrive(&op_full[os]);
     }

@@ -182,8 +182,7 @@ exl3_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) prev[kk] = __shfl_sync(0xffffffffu, cur[kk].w, prev_lane);
         if (qt == 3) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&raw_empty[rs]);   // the stage's last read has landed in registers
+          release_read_stage(&raw_empty[rs], lane);   // the stage's last read has landed in registers; proxy fence before the refill
         }
         uint32_t regs[16];
 #pragma unroll

@@ -143,10 +143,13 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       const uint32_t sc = *reinterpret_cast<const uint16_t*>(srow + 2 * c);
       ok = mbar_wait(&raw_full[rs], (c / F8_RAW_STAGES) & 1, abort_flag, status, 183);
       if (!ok) break;
-      const uint4* raw = reinterpret_cast<const uint4*>(smem + L.raw_off + rs * F8_RAW_STAGE + t * 64);
-      const uint4 r0 = raw[0], r1 = raw[1], r2 = raw[2], r3 = raw[3];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+      const uint32_t raw = smem_u32(smem + L.raw_off + rs * F8_RAW_STAGE + t * 64);
+      const uint4 r0 = lds128(raw), r1 = lds128(raw + 16), r2 = lds128(raw + 32), r3 = lds128(raw + 48);
+      // Handing the stage back to the bulk-copy engine: the reads above went through the generic proxy, the next chunk's copy writes through
+      // the async proxy, and nothing orders the two but a proxy fence BEFORE the release (measured without it: the copy for chunk c + 4
+      // overtook these reads in half of the launches at 32 chunks per CTA, whole 32-row blocks of an operand tile then mixed two chunks;
+      // with the fence 0 of 120 launches).
+      release_read_stage(&raw_empty[rs], lane);
       if (c >= F8_OP_STAGES) ok = mbar_wait(&op_empty[os], ((c / F8_OP_STAGES) - 1) & 1, abort_flag, status, 184);
       if (!ok) break;
       uint8_t* a_row = smem + L.a_off + os * F8_A_STAGE + (t >> 3) * 1024 + (t & 7) * 128;

@@ -190,6 +190,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tc, const uint16_t* __restri
         ml_mma(o[2 * dp + 1], a, b2, b3);
       }
     }
+    fence_proxy_async(); // the tile was read with ordinary loads; its refill writes through the async proxy
     __syncthreads();     // the tile and the probability buffer are free again
     if (threadIdx.x == 0 && p + 2 < npages) load_page(p + 2);
   }

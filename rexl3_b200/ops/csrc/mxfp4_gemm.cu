@@ -171,8 +171,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       if (!ok) break;
       const uint4* raw = reinterpret_cast<const uint4*>(smem + L.raw_off + rs * MX_RAW_STAGE + t * 32);
       const uint4 r0 = raw[0], r1 = raw[1];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+      release_read_stage(&raw_empty[rs], lane);      // generic-proxy reads, async-proxy refill: proxy fence before the release
       if (c >= MX_OP_STAGES) ok = mbar_wait(&op_empty[os], ((c / MX_OP_STAGES) - 1) & 1, abort_flag, status, 64);
       if (!ok) break;
       uint8_t* a_row = smem + L.a_off + os * MX_A_STAGE + (t >> 3) * 1024 + (t & 7) * 128;

@@ -413,3 +413,42 @@ def test_fp8_block_scaled_linear_matches_fp32(rows, K, N):
         assert torch.equal(full[1:], part)
     y = K_.bf16_linear(x, dense.to(torch.bfloat16), bias.to(torch.bfloat16))
     assert torch.allclose(y.float(), x.float() @ dense.to(torch.bfloat16).float().T + bias.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2 * y.abs().max().item())
+
+
+def test_long_k_pipelines_are_exact_and_repeatable():
+    """32 and 64 K chunks per CTA with 128-row tiles, integer-valued data (every fp32 sum is exact, so any difference is a wrong byte, not a
+    rounding order): the FP8 linear and the MXFP4 expert GEMM give the exact product on every one of many back-to-back launches.  (Each stage of
+    their weight rings is read with ordinary loads and refilled by a bulk tensor copy; the release needs a proxy fence, without which the copy
+    overtook the reads in about half of such launches.)"""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+    from rexl3_b200.format import mxfp4
+    from rexl3_b200.ops import kernels as K_
+    from rexl3_b200.ops import lib as L
+    lib = L.load()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    st = K_.new_status()
+    N, Kd, rows = 256, 2048, 70
+    xi = torch.randint(-2, 3, (rows, Kd), device="cuda", generator=g).to(torch.bfloat16)
+    wi = K_.Fp8Weight.quantize(torch.randint(-3, 4, (N, Kd), device="cuda", generator=g).float())
+    want = xi.float() @ wi.dense().T
+    bad = sum(int(not torch.equal(K_.fp8_linear(xi, wi, st, out_dtype=torch.float32, splits=1), want)) for _ in range(30))
+    K_.check_status(st)
+    assert bad == 0
+    rng = np.random.default_rng(1)
+    Kd = 4096
+    q, s = mxfp4.quantize(rng.normal(0, 0.05, size=(N, Kd)).astype(np.float32))
+    wf = torch.from_numpy(mxfp4.dequant(q, s)).cuda()
+    d_w, d_s = torch.from_numpy(q.view(np.uint8)[None].copy()).cuda(), torch.from_numpy(s[None].copy()).cuda()
+    xs = torch.from_numpy(rng.integers(-2, 3, size=(rows, Kd)).astype(np.float32)).cuda().to(torch.float16)
+    tile_tab = torch.tensor([0, 0, rows], dtype=torch.int32, device="cuda")
+    want = xs.float() @ wf.T
+    bad = 0
+    for _ in range(30):
+        part = torch.zeros(1, rows, N, dtype=torch.float32, device="cuda")
+        L.check(lib.rx_mxfp4_gemm_grouped(xs.data_ptr(), rows, Kd, d_w.data_ptr(), d_s.data_ptr(), 1, N, part.data_ptr(), 1, tile_tab.data_ptr(), 1, 128,
+                                          st.data_ptr(), L.stream_ptr()), "mxfp4")
+        bad += int(not torch.equal(part[0], want))
+    K_.check_status(st)
+    assert bad == 0
