@@ -120,7 +120,13 @@ class DenseFamily(Family):
             raise FamilyError("config", "config.json: sliding-window attention is not served by the dense family")
         if root.get("tie_word_embeddings"):
             raise FamilyError("config", "config.json: tie_word_embeddings: the pack must carry its own quantised lm_head")
-        return FamilyPlan(self.id, cfg, comps, tp_max=self.tp_max, drafters=self.drafters, kv_dtypes=self.kv_dtypes)
+        mtp = bool(getattr(cfg, "mtp", False))
+        if mtp:
+            comps.append("mtp_head")
+        # the multi-token-prediction block is served on one GPU with a bf16 cache (it is not in the tensor-parallel shard)
+        return FamilyPlan(self.id, cfg, comps, tp_max=1 if mtp else self.tp_max, drafters=(("mtp",) if mtp else ()) + self.drafters,
+                          kv_dtypes=("bf16",) if mtp else self.kv_dtypes,
+                          notes=["multi-token-prediction block: single GPU, bf16 KV cache"] if mtp else [])
 
 
 class HybridFamily(Family):

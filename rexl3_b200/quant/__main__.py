@@ -17,6 +17,7 @@ def main(argv=None) -> int:
     p.add_argument("--arch", required=True, choices=sorted([k for k, v in dense.CONFIGS.items() if type(v) is dense.DenseConfig] + list(hybrid.CONFIGS)))
     p.add_argument("--out", required=True)
     p.add_argument("--bits", type=float, default=0.0, help="override the architecture's bits per weight (1, 1.5, ... 8)")
+    p.add_argument("--mtp", action="store_true", help="dense family: add one multi-token-prediction block (eh_proj + one decoder layer + its norm) to the pack")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--threads", type=int, default=0)
     p.add_argument("--layers", type=int, default=0, help="quantize only the first N layers (smoke runs)")
@@ -31,6 +32,10 @@ def main(argv=None) -> int:
     cfg = hybrid.CONFIGS[a.arch] if is_hybrid else dense.CONFIGS[a.arch]
     if a.bits:
         cfg = dataclasses.replace(cfg, bits=a.bits)
+    if a.mtp:
+        if is_hybrid:
+            p.error("--mtp is available for the dense family")
+        cfg = dataclasses.replace(cfg, mtp=True)
     if a.layers:
         cfg = dataclasses.replace(cfg, n_layers=a.layers, **({"pattern": cfg.pattern[:a.layers]} if is_hybrid else {}))
     t0 = time.time()

@@ -135,6 +135,22 @@ def quantize_dense(cfg: DenseConfig, fp: dict, seed: int = 0, threads: int = 0, 
         w.layers.append(lay)
     w.final_norm = np.asarray(fp["final_norm"], np.float32)
     w.lm_head = ql(pad_to(fp["lm_head"], d, V), cfg.head_bits or cfg.bits, seed + 7777, ("lm_head",))
+    if getattr(cfg, "mtp", False):
+        # the multi-token-prediction block: fp["mtp"] = {enorm, hnorm, eh_proj [2d, d] (embedding rows first), final_norm, layer: {...}}
+        from ..models.dense import HostMtp
+        m = fp.get("mtp")
+        if m is None:
+            raise ValueError("config.mtp is set but the float weights carry no `mtp` block")
+        L = m["layer"]
+        i = cfg.n_layers
+        lay = HostLayer(np.asarray(L["attn_norm"], np.float32), ql(np.concatenate([L["q"], L["k"], L["v"]], axis=1), cfg.bits, seed + 10 * i + 1, (i, "qkv")),
+                        ql(L["o"], cfg.bits, seed + 10 * i + 2, (i, "o")), np.asarray(L["ffn_norm"], np.float32),
+                        ql(np.concatenate([pad_to(L["gate"], d, F), pad_to(L["up"], d, F)], axis=1), cfg.bits, seed + 10 * i + 3, (i, "gate_up")),
+                        ql(pad_to(L["down"], F, d), cfg.bits, seed + 10 * i + 4, (i, "down")),
+                        None if "q_norm" not in L else np.asarray(L["q_norm"], np.float32), None if "k_norm" not in L else np.asarray(L["k_norm"], np.float32))
+        eh = np.asarray(m["eh_proj"], np.float32)
+        w.mtp = HostMtp(np.asarray(m["enorm"], np.float32), np.asarray(m["hnorm"], np.float32), ql(eh[:d], cfg.bits, seed + 10 * i + 5, (i, "e_proj")),
+                        ql(eh[d:], cfg.bits, seed + 10 * i + 6, (i, "h_proj")), lay, np.asarray(m["final_norm"], np.float32))
     return w
 
 
@@ -199,9 +215,13 @@ def random_fp_weights(cfg: DenseConfig, seed: int = 0, std: float = 0.02) -> dic
     rng = np.random.default_rng(seed)
     d, hd = cfg.d_model, cfg.head_dim
     g = lambda *s: rng.normal(0, std, size=s).astype(np.float32)  # noqa: E731
-    layers = [dict(attn_norm=np.ones(d, np.float32), q=g(d, cfg.n_q * hd), k=g(d, cfg.n_kv * hd), v=g(d, cfg.n_kv * hd), o=g(cfg.n_q * hd, d),
-                   ffn_norm=np.ones(d, np.float32), gate=g(d, cfg.ffn), up=g(d, cfg.ffn), down=g(cfg.ffn, d)) for _ in range(cfg.n_layers)]
-    return dict(embed=g(cfg.vocab, d), layers=layers, final_norm=np.ones(d, np.float32), lm_head=g(d, cfg.vocab))
+    layer = lambda: dict(attn_norm=np.ones(d, np.float32), q=g(d, cfg.n_q * hd), k=g(d, cfg.n_kv * hd), v=g(d, cfg.n_kv * hd), o=g(cfg.n_q * hd, d),  # noqa: E731
+                         ffn_norm=np.ones(d, np.float32), gate=g(d, cfg.ffn), up=g(d, cfg.ffn), down=g(cfg.ffn, d))
+    layers = [layer() for _ in range(cfg.n_layers)]
+    out = dict(embed=g(cfg.vocab, d), layers=layers, final_norm=np.ones(d, np.float32), lm_head=g(d, cfg.vocab))
+    if getattr(cfg, "mtp", False):
+        out["mtp"] = dict(enorm=np.ones(d, np.float32), hnorm=np.ones(d, np.float32), eh_proj=g(2 * d, d), final_norm=np.ones(d, np.float32), layer=layer())
+    return out
 
 
 # ----------------------------------------------------------------------------------------------------- pack I/O
@@ -274,6 +294,22 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
             put_plain(p + "self_attn.k_norm.weight", L.k_norm)
     put_plain("model.norm.weight", w.final_norm)
     put_lin("lm_head", w.lm_head)
+    if getattr(w, "mtp", None) is not None:           # the multi-token-prediction block: layer index n_layers, DeepSeek-style names
+        m, p = w.mtp, f"model.layers.{cfg.n_layers}."
+        put_plain(p + "enorm.weight", m.enorm)
+        put_plain(p + "hnorm.weight", m.hnorm)
+        put_lin(p + "eh_proj.e", m.e_proj)
+        put_lin(p + "eh_proj.h", m.h_proj)
+        put_plain(p + "shared_head.norm.weight", m.final_norm)
+        put_plain(p + "input_layernorm.weight", m.layer.attn_norm)
+        put_plain(p + "post_attention_layernorm.weight", m.layer.ffn_norm)
+        put_group(p + "mlp.", "gate_up_proj", ["gate_proj", "up_proj"], m.layer.gate_up)
+        put_lin(p + "mlp.down_proj", m.layer.down)
+        put_group(p + "self_attn.", "qkv_proj", ["q_proj", "k_proj", "v_proj"], m.layer.qkv)
+        put_lin(p + "self_attn.o_proj", m.layer.o)
+        if m.layer.q_norm is not None:
+            put_plain(p + "self_attn.q_norm.weight", m.layer.q_norm)
+            put_plain(p + "self_attn.k_norm.weight", m.layer.k_norm)
     safetensors_io.write_file(os.path.join(folder, "model.safetensors"), tensors, {"format": "pt"}, dtypes)
     json.dump({"metadata": {}, "weight_map": {k: "model.safetensors" for k in sorted(tensors)}},
               open(os.path.join(folder, "model.safetensors.index.json"), "w"), indent=1)
@@ -282,6 +318,8 @@ def write_pack(folder: str, w: HostWeights, extra_config: dict | None = None) ->
             "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps, "rope_theta": cfg.rope_theta, "qk_norm": cfg.qk_norm, "name": cfg.name,
             "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": cfg.bits, "head_bits": cfg.head_bits or cfg.bits,
                                     "codebook": cfg.codebook, "fused_projections": True}}
+    if getattr(cfg, "mtp", False):
+        conf["num_nextn_predict_layers"] = 1
     if hasattr(cfg, "pattern"):
         conf.update({"architectures": ["Rexl3HybridForCausalLM"], "model_type": "rexl3_hybrid",
                      "hybrid": {"pattern": cfg.pattern, "ssm_heads": cfg.ssm_heads, "ssm_head_dim": cfg.ssm_head_dim, "ssm_groups": cfg.ssm_groups,
@@ -323,7 +361,10 @@ def config_from_dict(c: dict) -> DenseConfig:
         cfg = HybridConfig(**common, **(c.get("hybrid") or {}))
         cfg.validate()
         return cfg
-    return DenseConfig(**common)
+    n_mtp = int(c.get("num_nextn_predict_layers") or 0)
+    if n_mtp > 1:
+        raise ValueError(f"config.json asks for {n_mtp} multi-token-prediction layers; one is built")
+    return DenseConfig(**common, mtp=n_mtp == 1)
 
 
 def load_pack(folder: str, threads: int = 8, direct: bool = False) -> HostWeights:
@@ -402,6 +443,14 @@ def _load_pack(folder: str, threads: int, direct: bool) -> HostWeights:
         w.layers.append(lay)
     w.final_norm = plain("model.norm.weight")
     w.lm_head = lin("lm_head")
+    if getattr(cfg, "mtp", False):
+        from ..models.dense import HostMtp
+        p = f"model.layers.{cfg.n_layers}."
+        lay = HostLayer(plain(p + "input_layernorm.weight"), fused(p + "self_attn.", "qkv_proj", ["q_proj", "k_proj", "v_proj"]), lin(p + "self_attn.o_proj"),
+                        plain(p + "post_attention_layernorm.weight"), fused(p + "mlp.", "gate_up_proj", ["gate_proj", "up_proj"]), lin(p + "mlp.down_proj"))
+        if cfg.qk_norm:
+            lay.q_norm, lay.k_norm = plain(p + "self_attn.q_norm.weight"), plain(p + "self_attn.k_norm.weight")
+        w.mtp = HostMtp(plain(p + "enorm.weight"), plain(p + "hnorm.weight"), lin(p + "eh_proj.e"), lin(p + "eh_proj.h"), lay, plain(p + "shared_head.norm.weight"))
     read_s = loadstats.snapshot().get(("pack", "read"), (0.0, 0, 0))[0] if threads > 0 else 0.0
     loadstats.add("pack", "assemble", max(0.0, time.perf_counter() - t_assemble - read_s), ck.total_bytes())
     return w

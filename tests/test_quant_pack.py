@@ -94,3 +94,22 @@ def test_cpu_plumbing_prefill_and_greedy_decode_on_a_quantized_model(micro):
     seq = prompt + out
     full = dense.ReferenceDense(w).forward_seq(0, seq[:-1], 0)
     assert [int(full[i].argmax()) for i in range(63, len(seq) - 1)] == out
+
+
+def test_pack_round_trips_the_multi_token_prediction_block(tmp_path):
+    import dataclasses
+    from rexl3_b200.models import dense, registry
+    from rexl3_b200.quant import quantize
+    cfg = dataclasses.replace(dense.CONFIGS["tiny-llama"], mtp=True)
+    w = dense.random_weights(cfg, seed=3)
+    quantize.write_pack(str(tmp_path), w)
+    w2 = quantize.load_pack(str(tmp_path))
+    assert w2.cfg.mtp and np.array_equal(w2.mtp.e_proj.trellis, w.mtp.e_proj.trellis) and np.array_equal(w2.mtp.layer.down.trellis, w.mtp.layer.down.trellis)
+    a, b = dense.ReferenceDense(w), dense.ReferenceDense(w2)
+    a.forward_seq(0, [1, 2, 3, 4], 0)
+    b.forward_seq(0, [1, 2, 3, 4], 0)
+    ma, _ = a.mtp_seq(0, [2, 3, 4], a.last_hidden[:3], 0)
+    mb, _ = b.mtp_seq(0, [2, 3, 4], b.last_hidden[:3], 0)
+    assert float((ma - mb).abs().max()) == 0.0
+    fam, plan = registry.probe(str(tmp_path))
+    assert fam.id == "dense" and "mtp_head" in plan.components and plan.drafters[0] == "mtp" and plan.tp_max == 1
