@@ -92,14 +92,24 @@ def random_moe_weights(cfg: MoEConfig, seed: int = 0) -> HostWeights:
     return w
 
 
-def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | None):
-    """fp32 router: (ids [T, k], weights [T, k]) with ties to the lowest expert id."""
+def route_reference(logits: torch.Tensor, cfg: MoEConfig, bias: torch.Tensor | None, n_group: int = 0, topk_group: int = 0):
+    """fp32 router: (ids [T, k], weights [T, k]) with ties to the lowest expert id.  n_group / topk_group: group-limited routing (a row keeps
+    the experts of its `topk_group` best groups, a group's score being the sum of its two best selection keys)."""
     if cfg.router_mode == "softmax":
         p = torch.softmax(logits.float(), dim=-1)
         key = p
     else:
         p = torch.sigmoid(logits.float())
         key = p + (bias if bias is not None else 0)
+    if n_group > 1 and topk_group < n_group:
+        T, E = key.shape
+        per = E // n_group
+        gk = key.view(T, n_group, per)
+        gs = gk.topk(min(2, per), dim=-1).values.sum(-1)
+        _, gorder = torch.sort(gs, dim=-1, descending=True, stable=True)
+        keep = torch.zeros(T, n_group, dtype=torch.bool, device=key.device)
+        keep.scatter_(1, gorder[:, :topk_group], True)
+        key = torch.where(keep[:, :, None].expand(T, n_group, per).reshape(T, E), key, torch.full_like(key, float("-inf")))
     _, ids = torch.sort(key, dim=-1, descending=True, stable=True)
     ids = ids[:, :cfg.top_k]
     wts = torch.gather(p, 1, ids)

@@ -575,3 +575,91 @@ RX_API int rx_ipc_open(const void* handle64, void** out) {
   return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
 }
 RX_API int rx_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
+
+// ------------------------------------------------------------------------------------------------ generic collectives (TpComm)
+// The family-neutral collective interface (parallel/tpcomm.py) over the symmetric arena: a rank PUSHES its buffer into slot `rank` of every
+// rank's arena with plain peer stores (the last CTA publishes a ticket to every destination), then every rank combines the R slots it holds
+// LOCALLY: a sum in rank order (all-reduce: the same bits on every rank), or a plain copy-out (all-gather).  One hop, every wait bounded and on
+// a local flag.  Semantics: reference crates/model/src/families/nemotron_h_omni/tp.rs:37-130 (allreduce_sum_f32 in place, the one-shot form)
+// and crates/cuda/csrc/tp_oneshot.cu:1-83 (R operands summed in fixed rank order).
+namespace rx {
+
+struct CollTp {
+  int ranks, rank;
+  long long cap;                  // floats per slot
+  float* slots[TP_MAX];           // per destination rank: f32 [ranks][cap] of this parity set
+  unsigned* flags[TP_MAX];        // per destination rank: [ranks]
+  unsigned* local_count;
+  const unsigned* epoch;
+  unsigned use_index;
+};
+
+// grid-stride copy of `count` floats (count % 4 == 0) into slot `rank` of every rank
+__global__ void __launch_bounds__(256) tp_coll_push_kernel(const float* __restrict__ src, long long count, const __grid_constant__ CollTp tp) {
+  pdl_launch();
+  pdl_wait();
+  const long long n4 = count / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    for (int r = 0; r < tp.ranks; ++r) reinterpret_cast<float4*>(tp.slots[r] + (size_t)tp.rank * tp.cap)[i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tp_publish_last(tp.local_count, gridDim.x, tp.flags, tp.ranks, tp.rank, tp_ticket(tp.epoch, tp.use_index));
+}
+
+// mode 0: dst[i] = sum over ranks (rank order) of slot[r][i];  mode 1: dst[r * count + i] = slot[r][i]
+__global__ void __launch_bounds__(256) tp_coll_combine_kernel(float* __restrict__ dst, long long count, int mode, int* status, const __grid_constant__ CollTp tp) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    const unsigned ticket = tp_ticket(tp.epoch, tp.use_index);
+    for (int r = 0; r < tp.ranks && ok; ++r) ok = tp_wait_flag(tp.flags[tp.rank] + r, ticket, status, 190);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const float* mine = tp.slots[tp.rank];
+  const long long n4 = count / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    if (mode == 0) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < tp.ranks; ++r) {
+        float4 v;      // written by a peer: read around the non-coherent cache
+        asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mine + (size_t)r * tp.cap + 4 * i));
+        if (r == 0) acc = v;
+        else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+      }
+      reinterpret_cast<float4*>(dst)[i] = acc;
+    } else {
+      for (int r = 0; r < tp.ranks; ++r) {
+        float4 v;
+        asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mine + (size_t)r * tp.cap + 4 * i));
+        reinterpret_cast<float4*>(dst + (size_t)r * count)[i] = v;
+      }
+    }
+  }
+}
+
+}  // namespace rx
+
+RX_API int rx_tp_coll_desc_size() { return (int)sizeof(rx::CollTp); }
+
+RX_API int rx_tp_coll_push(const void* src, long long count, const void* desc, void* stream) {
+  if (desc == nullptr || count < 4 || count % 4 != 0) return (int)cudaErrorInvalidValue;
+  const rx::CollTp tp = *(const rx::CollTp*)desc;
+  if (tp.ranks < 1 || tp.ranks > rx::TP_MAX || count > tp.cap || (((uintptr_t)src) & 15) != 0) return (int)cudaErrorInvalidValue;
+  long long blocks = (count / 4 + 255) / 256;
+  if (blocks > 592) blocks = 592;
+  return (int)rx::launch(rx::tp_coll_push_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const float*)src, count, tp);
+}
+
+RX_API int rx_tp_coll_combine(void* dst, long long count, int mode, int* status, const void* desc, void* stream) {
+  if (desc == nullptr || count < 4 || count % 4 != 0 || (mode != 0 && mode != 1)) return (int)cudaErrorInvalidValue;
+  const rx::CollTp tp = *(const rx::CollTp*)desc;
+  if (tp.ranks < 1 || tp.ranks > rx::TP_MAX || count > tp.cap || (((uintptr_t)dst) & 15) != 0) return (int)cudaErrorInvalidValue;
+  long long blocks = (count / 4 + 255) / 256;
+  if (blocks > 592) blocks = 592;
+  return (int)rx::launch(rx::tp_coll_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (float*)dst, count, mode, status, tp);
+}

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) moe_router_logits_kernel(const uint16_t* 
 // out_ids: int32 [M, topk], out_w: f32 [M, topk].  One CTA per row; warp w scores experts w, w + nw, ...
 __global__ void __launch_bounds__(256) moe_router_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const float* __restrict__ bias,
                                                          int M, int d, int E, int topk, int mode, float scale, int* __restrict__ out_ids,
-                                                         float* __restrict__ out_w, const float* __restrict__ logits_in) {
+                                                         float* __restrict__ out_w, const float* __restrict__ logits_in, int n_group, int topk_group) {
   pdl_launch();
   pdl_wait();
   __shared__ float score[512];     // selection key
@@ -124,6 +124,37 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const uint16_t* __restr
     }
   }
   __syncwarp();
+  if (n_group > 1 && topk_group < n_group) {
+    // group-limited routing (DeepSeek-V3 / Bailing: reference crates/cuda/csrc/ling_fmoe.cu:694): a group's score is the sum of its two best
+    // selection keys; only the experts of the `topk_group` best groups (ties to the lowest group) stay eligible.  Lane g owns group g.
+    const int per = E / n_group;
+    float gs = -INFINITY;
+    if (lane < n_group) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+      for (int e = lane * per; e < (lane + 1) * per; ++e) {
+        const float v = score[e];
+        if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v;
+      }
+      gs = per > 1 ? b1 + b2 : b1;
+    }
+    unsigned keep = 0u;
+    for (int j = 0; j < topk_group; ++j) {
+      float best = gs;
+      int bi = lane < n_group ? lane : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (bi < 0 || bi >= n_group) bi = j;
+      keep |= 1u << bi;
+      if (lane == bi) gs = -INFINITY;
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!((keep >> (e / per)) & 1u)) score[e] = -INFINITY;
+    __syncwarp();
+  }
   // exact top-k: k rounds of arg-max, ties to the lowest expert id
   float picked_sum = 0.f;
   for (int j = 0; j < topk; ++j) {
@@ -527,7 +558,7 @@ RX_API int rx_moe_router(const void* x, const void* gate, const void* bias, int 
                          void* out_w, void* stream) {
   if (M < 1 || d % 256 != 0 || E < 1 || E > 512 || topk < 1 || topk > 32 || topk > E || (mode != 0 && mode != 1)) return (int)cudaErrorInvalidValue;
   return (int)rx::launch(moe_router_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x, (const uint16_t*)gate, (const float*)bias, M,
-                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)nullptr);
+                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)nullptr, 0, 0);
 }
 
 // Two-kernel form for windows of many rows: tiled logits, then scoring + top-k per row.  logits: f32 scratch [M, E].
@@ -539,7 +570,21 @@ RX_API int rx_moe_router2(const void* x, const void* gate, const void* bias, int
                           (const uint16_t*)gate, M, d, E, (float*)logits);
   if (e != 0) return e;
   return (int)rx::launch(moe_router_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x, (const uint16_t*)gate, (const float*)bias, M,
-                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)logits);
+                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)logits, 0, 0);
+}
+
+// Group-limited form: the experts are `n_group` equal groups; a row picks its `topk_group` best groups (a group's score = its two best selection
+// keys added) and then its top-k among their experts only.  n_group <= 32, E % n_group == 0.  logits: f32 scratch [M, E].
+RX_API int rx_moe_router_grouped(const void* x, const void* gate, const void* bias, int M, int d, int E, int topk, int mode, float scale, int n_group,
+                                 int topk_group, void* logits, void* out_ids, void* out_w, void* stream) {
+  if (M < 1 || d % 256 != 0 || E < 1 || E > 512 || topk < 1 || topk > 32 || (mode != 0 && mode != 1) || logits == nullptr || n_group < 1 || n_group > 32 ||
+      E % n_group != 0 || topk_group < 1 || topk_group > n_group || topk > topk_group * (E / n_group))
+    return (int)cudaErrorInvalidValue;
+  int e = (int)rx::launch(moe_router_logits_kernel, dim3((E + 1) / 2, (M + 15) / 16), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x,
+                          (const uint16_t*)gate, M, d, E, (float*)logits);
+  if (e != 0) return e;
+  return (int)rx::launch(moe_router_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)x, (const uint16_t*)gate, (const float*)bias, M,
+                         d, E, topk, mode, scale, (int*)out_ids, (float*)out_w, (const float*)logits, n_group, topk_group);
 }
 
 RX_API int rx_moe_plan(const void* ids, int pairs, int E, int e_lo, int e_hi, int tile_rows, int max_tiles, void* offs, void* pos_of_pair,

@@ -62,6 +62,7 @@ def _declare(lib):
         "rx_exl3_gemm_grouped": (c_int, [c_void, c_int, c_int, c_void, c_ll, c_int, c_int, c_int, c_void, c_int, c_void, c_int, c_int, c_void, c_void]),
         "rx_moe_router": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f, c_void, c_void, c_void]),
         "rx_moe_router2": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f, c_void, c_void, c_void, c_void]),
+        "rx_moe_router_grouped": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f, c_int, c_int, c_void, c_void, c_void, c_void]),
         "rx_moe_plan": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
@@ -87,6 +88,9 @@ def _declare(lib):
                                   c_void, c_int, c_void]),
         "rx_dsa_select": (c_int, [c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_void, c_int, c_f, c_int, c_int, c_void, c_int,
                                   c_void, c_int, c_void, c_void, c_int, c_void]),
+        "rx_tp_coll_desc_size": (c_int, []),
+        "rx_tp_coll_push": (c_int, [c_void, c_ll, c_void, c_void]),
+        "rx_tp_coll_combine": (c_int, [c_void, c_ll, c_int, c_void, c_void, c_void]),
         "rx_fp8_linear_scratch_floats": (c_ll, [c_int, c_int, c_int]),
         "rx_fp8_linear": (c_int, [c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void, c_void]),
         "rx_dsa_gather": (c_int, [c_void, c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_void]),

@@ -270,3 +270,31 @@ def test_mxfp4_grouped_gemm_matches_dequantized_reference(rows, tile_rows):
     for p in range(pairs):
         want = xh[pos[p]] @ wf[idn[p]].T
         np.testing.assert_allclose(got[pos[p]], want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
+
+
+@pytest.mark.parametrize("n_group,topk_group", [(8, 3), (4, 1), (16, 16)])
+def test_group_limited_router_matches_reference(n_group, topk_group):
+    """Sigmoid + bias scores, the `topk_group` best of `n_group` expert groups (group score = its two best keys), then top-k inside them."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import dataclasses
+    from rexl3_b200.models import moe
+    from rexl3_b200.ops import lib as L
+    lib = L.load()
+    cfg = dataclasses.replace(moe.CONFIGS["test-moe"], n_experts=64, top_k=6, router_mode="sigmoid_bias", routed_scale=2.5)
+    M, d, E, k = 37, cfg.d_model, cfg.n_experts, cfg.top_k
+    g = torch.Generator(device="cuda").manual_seed(n_group)
+    x = torch.randn(M, d, device="cuda", generator=g).to(torch.bfloat16)
+    gate = (torch.randn(E, d, device="cuda", generator=g) / 16).to(torch.bfloat16)
+    bias = 0.1 * torch.randn(E, device="cuda", generator=g)
+    ids = torch.zeros(M, k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(M, k, dtype=torch.float32, device="cuda")
+    logits = torch.empty(M, E, dtype=torch.float32, device="cuda")
+    L.check(lib.rx_moe_router_grouped(x.data_ptr(), gate.data_ptr(), bias.data_ptr(), M, d, E, k, 1, cfg.routed_scale, n_group, topk_group, logits.data_ptr(),
+                                      ids.data_ptr(), wts.data_ptr(), L.stream_ptr()), "router")
+    torch.cuda.synchronize()
+    want_ids, want_w = moe.route_reference(logits, cfg, bias, n_group, topk_group)      # the device's own logits: the selection is then exact
+    assert torch.equal(ids.long(), want_ids)
+    assert torch.allclose(wts, want_w, rtol=1e-4, atol=1e-6)
+    per = E // n_group
+    assert all(len({int(e) // per for e in row}) <= topk_group for row in ids.tolist())

@@ -61,3 +61,16 @@ def test_token_all_to_all_over_gpus_equals_one_gpu(ranks):
            "--master-port", str(29560 + ranks), "-m", "rexl3_b200.parallel.a2a_selftest", "--skip-timing"]
     r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
     assert r.returncode == 0 and '"bitwise_equal_to_one_gpu": true' in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_tpcomm_peer_memory_collectives_over_gpus():
+    """The generic collective interface on two real GPUs: the peer-memory all-reduce equals the serial rank-order sum bit for bit and the
+    all-gather equals NCCL's (the self test also times both)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29571",
+           "-m", "rexl3_b200.parallel.tpcomm_selftest"]
+    r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=420)
+    assert r.returncode == 0 and '"equal_to_rank_order_sum": true' in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
