@@ -624,9 +624,9 @@ class DenseGpuBackend(Backend):
         out = torch.stack(parts).contiguous().view(torch.uint8).cpu()
         self.d2h_bytes += out.numel()
         blob = out.numpy().tobytes()
-        if getattr(m, "kv_i8", False):              # an int8 page is its bytes plus the per-token scales of every layer
-            sc = torch.stack([t[p] for t in m.k_tscale if t is not None] + [t[p] for t in m.v_tscale if t is not None]).contiguous().cpu()
-            self.d2h_bytes += sc.numel() * 4
+        if getattr(m, "kv_i8", False) or getattr(m, "kv_q4", False):     # an int8 / q4 page is its bytes plus the scales of every layer
+            sc = torch.stack([t[p] for t in m.k_tscale if t is not None] + [t[p] for t in m.v_tscale if t is not None]).contiguous().view(torch.uint8).cpu()
+            self.d2h_bytes += sc.numel()
             blob += sc.numpy().tobytes()
         return blob
 
@@ -636,8 +636,9 @@ class DenseGpuBackend(Backend):
             return None
         caches = [c for c in m.k_cache if c is not None] + [c for c in m.v_cache if c is not None]
         page_bytes = caches[0][0].numel() * caches[0].element_size()
-        scales = ([t for t in m.k_tscale if t is not None] + [t for t in m.v_tscale if t is not None]) if getattr(m, "kv_i8", False) else []
-        scale_bytes = scales[0][0].numel() * 4 if scales else 0
+        scaled = getattr(m, "kv_i8", False) or getattr(m, "kv_q4", False)
+        scales = ([t for t in m.k_tscale if t is not None] + [t for t in m.v_tscale if t is not None]) if scaled else []
+        scale_bytes = scales[0][0].numel() * scales[0].element_size() if scales else 0
         if len(payload) != page_bytes * len(caches) + scale_bytes * len(scales):
             return None                     # written by a different model or cache format
         got = self.pool.alloc(1)

@@ -394,11 +394,16 @@ class DenseGPU:
         # paged KV: one K and one V tensor per layer, [pages, n_kv, 64, hd] bf16 (or E4M3 bytes with one scale per layer, K/V and head),
         # plus their TMA descriptors
         # (or int8 with one power-of-two scale per token and KV head, kept in k_tscale / v_tscale [pages, n_kv, 64] f32 beside each layer's cache)
-        if kv_dtype not in ("bf16", "fp8", "int8"):
-            raise ValueError(f"kv_dtype {kv_dtype!r}: bf16, fp8 or int8")
+        if kv_dtype not in ("bf16", "fp8", "int8", "q4"):
+            raise ValueError(f"kv_dtype {kv_dtype!r}: bf16, fp8, int8 or q4")
         self.kv_fp8 = kv_dtype == "fp8"
         self.kv_i8 = kv_dtype == "int8"
-        cdt = torch.uint8 if self.kv_fp8 else (torch.int8 if self.kv_i8 else torch.bfloat16)
+        # q4: E2M1 nibbles with one E8M0 scale per 32 values (the MXFP4 element format on K / V rows), 68 bytes per 128-wide row instead of 256
+        self.kv_q4 = kv_dtype == "q4"
+        if self.kv_q4 and cfg.head_dim != 128:
+            raise ValueError("the q4 KV cache is built for 128-wide heads")
+        cdt = torch.uint8 if (self.kv_fp8 or self.kv_q4) else (torch.int8 if self.kv_i8 else torch.bfloat16)
+        kw = cfg.head_dim // 2 if self.kv_q4 else cfg.head_dim          # stored width of a row
         kvl = set(self._kv_layers())
         nkv = cfg.n_layers + (1 if getattr(cfg, "mtp", False) else 0)      # the MTP block's attention owns cache index n_layers
         if nkv > cfg.n_layers:
@@ -407,13 +412,14 @@ class DenseGPU:
             if kv_dtype != "bf16":
                 raise ValueError("the multi-token-prediction block runs on a bf16 KV cache")
             kvl.add(cfg.n_layers)
-        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(nkv)]
-        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, cfg.head_dim, dtype=cdt, device=device) if i in kvl else None for i in range(nkv)]
+        self.k_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, kw, dtype=cdt, device=device) if i in kvl else None for i in range(nkv)]
+        self.v_cache = [torch.zeros(num_pages, cfg.n_kv, PAGE, kw, dtype=cdt, device=device) if i in kvl else None for i in range(nkv)]
         self.kv_scale = torch.ones(nkv, 2, cfg.n_kv, dtype=torch.float32, device=device) if self.kv_fp8 else None
         self.kv_amax = None        # set while calibrating
-        mk_ts = lambda: torch.ones(num_pages, cfg.n_kv, PAGE, dtype=torch.float32, device=device)  # noqa: E731
-        self.k_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(nkv)]
-        self.v_tscale = [mk_ts() if (self.kv_i8 and i in kvl) else None for i in range(nkv)]
+        mk_ts = (lambda: torch.full((num_pages, cfg.n_kv, PAGE, cfg.head_dim // 32), 127, dtype=torch.uint8, device=device)) if self.kv_q4 else \
+            (lambda: torch.ones(num_pages, cfg.n_kv, PAGE, dtype=torch.float32, device=device))
+        self.k_tscale = [mk_ts() if ((self.kv_i8 or self.kv_q4) and i in kvl) else None for i in range(nkv)]
+        self.v_tscale = [mk_ts() if ((self.kv_i8 or self.kv_q4) and i in kvl) else None for i in range(nkv)]
         self.tk = [None if c is None else K.KvTensorMap(c) for c in self.k_cache]
         self.tv = [None if c is None else K.KvTensorMap(c) for c in self.v_cache]
         self.status = K.new_status(device)
@@ -594,18 +600,19 @@ class DenseGPU:
         cfg, K = self.cfg, self.K
         s = self._linear(xr_d, L["qkv"], M, cls, "qkv")
         ksc = self.kv_scale[li] if self.kv_fp8 else None
-        kts = (self.k_tscale[li], self.v_tscale[li]) if self.kv_i8 else None
+        kts = (self.k_tscale[li], self.v_tscale[li]) if (self.kv_i8 or self.kv_q4) else None
+        q4 = self.kv_q4
         K.finish_qkv_rope(self.part, s, M, cfg.n_q, cfg.n_kv, cfg.head_dim, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions,
                           self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li],
-                          pos3=self.pos3, mrope_sections=getattr(cfg, "mrope_sections", None), kv_tscale=kts)
+                          pos3=self.pos3, mrope_sections=getattr(cfg, "mrope_sections", None), kv_tscale=kts, q4=q4)
         if prefill is None:
             K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
                           max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc, max_seq_rows=self.window_seq_rows,
-                          plan=self.attn_plan, kv_tscale=kts)
+                          plan=self.attn_plan, kv_tscale=kts, q4=q4)
         else:
             ao = self.attn_out[:M]
             K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
-                           ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc, kv_tscale=kts)
+                           ao, prefill["nseq"], prefill["max_qlen"], cfg.n_q, cfg.n_kv, cfg.head_dim, scale, self.status, ksc, kv_tscale=kts, q4=q4)
             K.norm_rot_in(ao, None, cfg.eps, L["o"].suh, xr_a)
         s = self._linear(xr_a, L["o"], M, cls, "o")
         return s

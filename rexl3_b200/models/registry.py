@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 
 # components this build has executors for (a family may serve a configuration only if every component it implies is here)
 BUILT_COMPONENTS = frozenset({
-    "exl3_linear", "gqa_attention", "rope", "qk_norm", "swiglu_ffn", "paged_kv_bf16", "paged_kv_fp8", "paged_kv_int8", "mla_attention", "moe_softmax_topk",
+    "exl3_linear", "gqa_attention", "rope", "qk_norm", "swiglu_ffn", "paged_kv_bf16", "paged_kv_fp8", "paged_kv_int8", "paged_kv_q4", "mla_attention", "moe_softmax_topk",
     "moe_sigmoid_bias_topk", "mxfp4_experts", "shared_expert", "mamba2_mixer", "gated_delta_net", "kimi_delta_attention", "self_speculative_draft",
     "copy_draft", "ngram_draft", "prefix_cache", "tensor_parallel", "expert_parallel", "mtp_head", "vision_tower", "mrope", "sparse_indexer",
 })
@@ -108,7 +108,7 @@ class DenseFamily(Family):
     model_types = ("rexl3_dense", "llama", "qwen3", "qwen2", "mistral")
     tp_max = 8
     drafters = ("self", "copy", "ngram")
-    kv_dtypes = ("bf16", "fp8", "int8")
+    kv_dtypes = ("bf16", "fp8", "int8", "q4")
 
     def plan(self, root, folder):
         from ..quant import quantize

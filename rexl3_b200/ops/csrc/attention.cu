@@ -15,6 +15,7 @@
 // walk the pages causally.  bf16 caches with 128-wide heads run the tcgen05 / tensor-memory kernel of attention_tc.cu instead.
 #include <cuda.h>
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include "common.cuh"
 
 namespace rx {
@@ -87,6 +88,7 @@ __device__ __forceinline__ void load_kv_page8(uint8_t* kdst, uint8_t* vdst, cons
 
 // KV cache element formats of the attention kernels
 constexpr int KVQ_BF16 = 0, KVQ_FP8 = 1, KVQ_I8 = 2;
+// (template parameter I8 of the byte-page kernels: 0 = E4M3 with per-head scales, 1 = int8 with a scale per token and head, 2 = q4)
 
 // int8 cache with one power-of-two scale per (token, KV head) (the reference's format, crates/cuda/csrc/nemotron_kv8.cuh:1-14): a page of one KV
 // head is 64 x HD bytes plus 64 f32 scales for K and 64 for V ([pages][n_kv][64] each); the scales ride on the page's barrier as two 256-byte
@@ -139,6 +141,55 @@ __device__ __forceinline__ void expand_page8(const uint8_t* src, uint8_t* dst, c
     const uint32_t a0 = kv_chunk_addr<HD>(dbase, key, 2 * j), a1 = kv_chunk_addr<HD>(dbase, key, 2 * j + 1);
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+  }
+}
+
+// q4 cache (E2M1 nibbles with one E8M0 scale per 32 values: the MXFP4 element format on K / V rows; reference crates/cuda/csrc/dsv4_kvq4.cu:1-16
+// for the row format): a page of one KV head is 64 x HD/2 bytes plus 64 x HD/32 scale bytes for K and for V ([pages][n_kv][64][HD/32] uint8).
+// The scale bytes ride on the page's barrier as two bulk copies; the expansion multiplies them in (E2M1 x 2^e is exact in fp16 inside the
+// clamped exponent range), so the attention step is the fp16 one.
+template <int HD>
+__device__ __forceinline__ void load_kv_page_q4(uint8_t* kdst, uint8_t* vdst, uint8_t* sc, const CUtensorMap* tk, const CUtensorMap* tv,
+                                                const uint8_t* __restrict__ k_s4, const uint8_t* __restrict__ v_s4, int page, int kvh, int n_kv,
+                                                uint64_t* bar) {
+  constexpr int BYTES = PAGE * HD / 2, SB = PAGE * HD / 32;
+  mbar_arrive_expect_tx(bar, 2 * BYTES + 2 * SB);
+  const int y = (page * n_kv + kvh) * PAGE;
+  tma_load_2d(kdst, tk, 0, y, bar);
+  tma_load_2d(vdst, tv, 0, y, bar);
+  bulk_g2s(sc, k_s4 + (size_t)y * (HD / 32), SB, bar);
+  bulk_g2s(sc + PAGE * 4, v_s4 + (size_t)y * (HD / 32), SB, bar);
+}
+
+__device__ __forceinline__ uint32_t e8m0_half2(uint32_t b) {      // 2^(b - 127) as two fp16 (the writer keeps b - 127 in -14 .. 12)
+  const int e = (int)b - 127;
+  const uint32_t h = e < -14 ? 0u : (e > 15 ? 0x7C00u : (uint32_t)(e + 15) << 10);
+  return h | (h << 16);
+}
+
+template <int HD>
+__device__ __forceinline__ void expand_page4(const uint8_t* src, uint8_t* dst, const uint8_t* sc) {
+  constexpr int G = HD / 32;                      // scale groups per key
+  constexpr int CHUNKS = PAGE * G;                // one 16-byte source chunk = one group of 32 values
+  const uint32_t dbase = smem_u32(dst);
+  for (int c = threadIdx.x; c < CHUNKS; c += blockDim.x) {
+    const int key = c / G, g = c % G;
+    const uint4 r = *reinterpret_cast<const uint4*>(src + (size_t)c * 16);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    const uint32_t s2u = e8m0_half2(sc[key * G + g]);
+    const __half2 s2 = *reinterpret_cast<const __half2*>(&s2u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {               // word i: 8 values = one 16-byte chunk of the fp16 row
+      uint32_t h[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w[i] >> (8 * q)) & 0xFFu), __NV_E2M1);
+        const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&hr), s2);
+        h[q] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+      const uint32_t a = kv_chunk_addr<HD>(dbase, key, 4 * g + i);
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+    }
   }
 }
 
@@ -384,7 +435,7 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const int* __restrict__ 
 // bits depend neither on MT nor on its block mates; more tiles only let more (row, head) pairs of one sequence share one pass over the
 // K / V chunk.  (Giving each tile its own four warps halved the CTAs per SM and was slower than two one-tile CTAs; launching one CTA per
 // row and letting the non-leaders exit cost more than the K / V reads it saved.)
-template <int HD, bool FP8, int MT, bool I8 = false>
+template <int HD, bool FP8, int MT, int I8 = 0>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
@@ -438,7 +489,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       fence_proxy_async();                           // the previous item's merge wrote this memory with plain stores
       for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
         const int sg = (gp + p) % KV_STAGES;
-        if constexpr (I8) load_kv_page_i8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, tsc + sg * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
+        if constexpr (I8 == 2) load_kv_page_q4<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, (uint8_t*)(tsc + sg * 2 * PAGE), &tk, &tv, (const uint8_t*)k_ts, (const uint8_t*)v_ts, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
+        else if constexpr (I8 == 1) load_kv_page_i8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, tsc + sg * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
         else if constexpr (FP8) load_kv_page8<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
         else load_kv_page<HD>(smem + sg * TILE, smem + (KV_STAGES + sg) * TILE, &tk, &tv, bt[k_begin / PAGE + p], kvh, n_kv, &bars[sg]);
       }
@@ -483,7 +535,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       const int s = (gp + p) % KV_STAGES;
       if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
         const int pn = p + KV_STAGES - 1, sn = (gp + pn) % KV_STAGES;  // stage sn was consumed in iteration p-1 (barrier below)
-        if constexpr (I8) load_kv_page_i8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, tsc + sn * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+        if constexpr (I8 == 2) load_kv_page_q4<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, (uint8_t*)(tsc + sn * 2 * PAGE), &tk, &tv, (const uint8_t*)k_ts, (const uint8_t*)v_ts, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
+        else if constexpr (I8 == 1) load_kv_page_i8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, tsc + sn * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
         else if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
         else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[k_begin / PAGE + pn], kvh, n_kv, &bars[sn]);
       }
@@ -493,8 +546,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       const int kpos = k_begin + p * PAGE + key0;
       const bool any = k_end_max - kpos > 0;                        // uniform for the warp
       if constexpr (FP8) {
-        expand_page8<HD>(smem + s * TILE, conv, I8 ? tsc + s * 2 * PAGE : nullptr);
-        expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, I8 ? tsc + s * 2 * PAGE + PAGE : nullptr);
+        if constexpr (I8 == 2) {
+          expand_page4<HD>(smem + s * TILE, conv, (const uint8_t*)(tsc + s * 2 * PAGE));
+          expand_page4<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, (const uint8_t*)(tsc + s * 2 * PAGE + PAGE));
+        } else {
+          expand_page8<HD>(smem + s * TILE, conv, I8 ? tsc + s * 2 * PAGE : nullptr);
+          expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, I8 ? tsc + s * 2 * PAGE + PAGE : nullptr);
+        }
         __syncthreads();
       }
       if (any) {
@@ -664,7 +722,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 // ------------------------------------------------------------------------------------------------ prefill (causal flash)
 // Queries: rows [q_start[s], q_start[s] + q_len[s]) of `q` belong to sequence s at positions pos0[s].. ; keys are the
 // sequence's cached tokens [0, pos0 + local row] (the chunk's own K/V are already in the cache).  out: bf16 [rows][n_q*HD].
-template <int HD, bool FP8, bool I8 = false>
+template <int HD, bool FP8, int I8 = 0>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_ids, const int* __restrict__ q_start,
@@ -704,7 +762,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
-      if constexpr (I8) load_kv_page_i8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, tsc + p * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[p], kvh, n_kv, &bars[p]);
+      if constexpr (I8 == 2) load_kv_page_q4<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, (uint8_t*)(tsc + p * 2 * PAGE), &tk, &tv, (const uint8_t*)k_ts, (const uint8_t*)v_ts, bt[p], kvh, n_kv, &bars[p]);
+        else if constexpr (I8 == 1) load_kv_page_i8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, tsc + p * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[p], kvh, n_kv, &bars[p]);
       else if constexpr (FP8) load_kv_page8<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
       else load_kv_page<HD>(smem + p * TILE, smem + (KV_STAGES + p) * TILE, &tk, &tv, bt[p], kvh, n_kv, &bars[p]);
     }
@@ -738,7 +797,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     const int s = p % KV_STAGES;
     if (threadIdx.x == 0 && p + KV_STAGES - 1 < npages) {
       const int pn = p + KV_STAGES - 1, sn = pn % KV_STAGES;
-      if constexpr (I8) load_kv_page_i8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, tsc + sn * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[pn], kvh, n_kv, &bars[sn]);
+      if constexpr (I8 == 2) load_kv_page_q4<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, (uint8_t*)(tsc + sn * 2 * PAGE), &tk, &tv, (const uint8_t*)k_ts, (const uint8_t*)v_ts, bt[pn], kvh, n_kv, &bars[sn]);
+        else if constexpr (I8 == 1) load_kv_page_i8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, tsc + sn * 2 * PAGE, &tk, &tv, k_ts, v_ts, bt[pn], kvh, n_kv, &bars[sn]);
       else if constexpr (FP8) load_kv_page8<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
       else load_kv_page<HD>(smem + sn * TILE, smem + (KV_STAGES + sn) * TILE, &tk, &tv, bt[pn], kvh, n_kv, &bars[sn]);
     }
@@ -748,8 +808,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     const bool mine = kbase <= warp_last_key && q_lo + warp * 16 < qlen;
     const int v0 = lr0 < qlen ? (p0 + lr0 + 1 - kbase) : 0, v1 = lr1 < qlen ? (p0 + lr1 + 1 - kbase) : 0;
     if constexpr (FP8) {
-      expand_page8<HD>(smem + s * TILE, conv, I8 ? tsc + s * 2 * PAGE : nullptr);
-      expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, I8 ? tsc + s * 2 * PAGE + PAGE : nullptr);
+      if constexpr (I8 == 2) {
+        expand_page4<HD>(smem + s * TILE, conv, (const uint8_t*)(tsc + s * 2 * PAGE));
+        expand_page4<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, (const uint8_t*)(tsc + s * 2 * PAGE + PAGE));
+      } else {
+        expand_page8<HD>(smem + s * TILE, conv, I8 ? tsc + s * 2 * PAGE : nullptr);
+        expand_page8<HD>(smem + (KV_STAGES + s) * TILE, conv + T16, I8 ? tsc + s * 2 * PAGE + PAGE : nullptr);
+      }
       __syncthreads();
       if (mine) attn_step<HD, 64, true>(qa, smem_u32(conv), smem_u32(conv + T16), 0, v0, v1, scale_log2, m, l, o);
     } else {
@@ -859,7 +924,7 @@ RX_API int rx_attn_plan(const void* row_seq, const void* ctx_len, int rows, int 
   return (int)cudaGetLastError();
 }
 
-template <int HD, bool FP8, int MT, bool I8>
+template <int HD, bool FP8, int MT, int I8>
 static int launch_decode_kernel(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                                 const int* ctx_len, float* part_o, float* part_ml, int rows, int n_q, int n_kv, int mc, float scale, int* status,
                                 cudaStream_t st, const float* kv_scale, const int* plan, const float* k_ts, const float* v_ts) {
@@ -878,7 +943,7 @@ static int launch_decode_kernel(const CUtensorMap* tk, const CUtensorMap* tv, co
   return (int)cudaGetLastError();
 }
 
-template <int HD, bool FP8, bool I8 = false>
+template <int HD, bool FP8, int I8 = 0>
 static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                          const int* ctx_len, float* scratch, int rows, int n_q, int n_kv, int max_ctx, float scale, const void* suh, void* xr,
                          void* out_bf16, int* status, cudaStream_t st, const float* kv_scale, int max_seq_rows, const int* plan,
@@ -921,7 +986,7 @@ RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q,
   cudaStream_t st = (cudaStream_t)stream;
   if (k_tscale != nullptr) {
     // int8 cache: the maps describe byte pages, k_tscale / v_tscale are f32 [pages][n_kv][64] (one power-of-two scale per token and KV head)
-#define RX_DEC8(HDV) launch_decode<HDV, true, true>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
+#define RX_DEC8(HDV) launch_decode<HDV, true, 1>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
     (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, nullptr, max_seq_rows, \
     (const int*)plan, (const float*)k_tscale, (const float*)v_tscale)
     if (hd == 128) return RX_DEC8(128);
@@ -939,7 +1004,7 @@ RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q,
   return (int)cudaErrorInvalidValue;
 }
 
-template <int HD, bool FP8, bool I8 = false>
+template <int HD, bool FP8, int I8 = 0>
 static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* seq_ids,
                           const int* q_start, const int* q_len, const int* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, float scale,
                           int* status, cudaStream_t st, const float* kv_scale, const float* k_ts = nullptr, const float* v_ts = nullptr) {
@@ -956,6 +1021,27 @@ static int launch_prefill(const CUtensorMap* tk, const CUtensorMap* tv, const vo
   return (int)cudaGetLastError();
 }
 
+// q4 cache (head dim 128): the maps describe [pages * n_kv * 64][64] byte pages (rx_make_kv_tmap8 with width 64), k_s4 / v_s4 are the E8M0
+// scale bytes uint8 [pages][n_kv][64][4].
+RX_API int rx_attn_decode_q4(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* row_seq,
+                             const void* ctx_len, void* scratch, int rows, int n_q, int n_kv, int hd, int max_ctx, float scale, const void* suh, void* xr,
+                             void* out_bf16, int* status, void* stream, int max_seq_rows, const void* plan, const void* k_s4, const void* v_s4) {
+  if (hd != 128 || n_q % n_kv != 0 || n_q / n_kv > 16 || rows <= 0 || rows > PLAN_MAX_ROWS || max_ctx <= 0 || k_s4 == nullptr || v_s4 == nullptr)
+    return (int)cudaErrorInvalidValue;
+  return launch_decode<128, true, 2>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)row_seq,
+                                     (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, (cudaStream_t)stream,
+                                     nullptr, max_seq_rows, (const int*)plan, (const float*)k_s4, (const float*)v_s4);
+}
+
+RX_API int rx_attn_prefill_q4(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
+                              const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
+                              float scale, int* status, void* stream, const void* k_s4, const void* v_s4) {
+  if (hd != 128 || n_q % n_kv != 0 || nseq <= 0 || max_qlen <= 0 || k_s4 == nullptr || v_s4 == nullptr) return (int)cudaErrorInvalidValue;
+  return launch_prefill<128, true, 2>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, (const int*)seq_ids,
+                                      (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status,
+                                      (cudaStream_t)stream, nullptr, (const float*)k_s4, (const float*)v_s4);
+}
+
 extern "C" int rx_attn_prefill_tc(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* seq_ids,
                                   const void* q_start, const void* q_len, const void* pos0, void* out, int nseq, int max_qlen, int n_q, int n_kv, int hd,
                                   float scale, int* status, void* stream, int reserved);
@@ -968,7 +1054,7 @@ RX_API int rx_attn_prefill(const void* tmap_k, const void* tmap_v, const void* q
   if (k_tscale != nullptr) {
     // int8 cache with per-token scales: the mma.sync kernel over byte pages
     cudaStream_t st8 = (cudaStream_t)stream;
-#define RX_PF8(HDV) launch_prefill<HDV, true, true>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
+#define RX_PF8(HDV) launch_prefill<HDV, true, 1>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
     (const int*)seq_ids, (const int*)q_start, (const int*)q_len, (const int*)pos0, out, nseq, max_qlen, n_q, n_kv, scale, status, st8, nullptr, \
     (const float*)k_tscale, (const float*)v_tscale)
     if (hd == 128) return RX_PF8(128);

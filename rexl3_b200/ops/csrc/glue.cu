@@ -4,6 +4,7 @@
 // glue.cu:667-709 (two-stage exact top-k with 64-bit keys, value desc / id asc).  KV layout is this engine's own:
 // bf16 [num_pages][n_kv][64][head_dim].
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include "exl3_decode.cuh"
 
 namespace rx {
@@ -23,7 +24,9 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
                                        float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                        const int* __restrict__ slot, uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
                                        uint16_t* __restrict__ v_cache, const float* __restrict__ kv_scale, float* __restrict__ kv_amax,
-                                       const int* __restrict__ pos3, int lim_h, int lim_w, float* __restrict__ k_ts, float* __restrict__ v_ts) {
+                                       const int* __restrict__ pos3, int lim_h, int lim_w, float* __restrict__ k_ts, float* __restrict__ v_ts, int q4) {
+  // q4 != 0 (with k_ts / v_ts): the caches are q4 rows - E2M1 nibbles, one E8M0 scale per 32 values in k_ts / v_ts read as uint8
+  // [pages][n_kv][64][HD / 32]; scale = 2^ceil(log2(max(amax, 1e-4) / 6)) kept in 2^-14 .. 2^12, values rounded to nearest by the hardware conversion.
   // k_ts != nullptr: the caches are int8 with one power-of-two scale per (token, KV head), written to k_ts / v_ts (f32 [pages][n_kv][64]):
   // scale = 2^ceil(log2(amax / 127)), value = round(x / scale) (the reference's format, crates/cuda/csrc/nemotron_kv8.cuh:1-14).
   // pos3 != nullptr: interleaved M-RoPE (reference crates/cuda/csrc/glue.cu:178-180): int32 [rows][3] = the T, H and W position of each row;
@@ -110,7 +113,19 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ part, int S, in
         for (int o = 1; o < GL; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
         if ((lane % GL) == 0) atomicMax(reinterpret_cast<unsigned*>(kv_amax) + (is_k ? 0 : n_kv) + kvh, __float_as_uint(am));   // non-negative floats order like their bits
       }
-      if (k_ts != nullptr) {
+      if (k_ts != nullptr && q4) {
+        float am = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));       // 8 lanes x 4 values = one group of 32
+        int e = (int)ceilf(log2f(fmaxf(am, 1e-4f) * (1.f / 6.f)));
+        e = max(-14, min(12, e));
+        const float inv = exp2f((float)-e);
+        const __nv_fp4x2_storage_t a = __nv_cvt_float2_to_fp4x2(make_float2(y[0] * inv, y[1] * inv), __NV_E2M1, cudaRoundNearest);
+        const __nv_fp4x2_storage_t b2 = __nv_cvt_float2_to_fp4x2(make_float2(y[2] * inv, y[3] * inv), __NV_E2M1, cudaRoundNearest);
+        *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(is_k ? k_cache : v_cache) + addr / 2) = (uint16_t)((uint32_t)a | ((uint32_t)b2 << 8));
+        if ((lane & 7) == 0)
+          reinterpret_cast<uint8_t*>(is_k ? k_ts : v_ts)[(((size_t)(sl / 64) * n_kv + kvh) * 64 + (sl % 64)) * (HD / 32) + d0 / 32] = (uint8_t)(e + 127);
+      } else if (k_ts != nullptr) {
         float am = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
 #pragma unroll
         for (int o = 1; o < GL; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
@@ -223,7 +238,7 @@ using namespace rx;
 RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv, int hd, const void* svh, const void* bias, const void* q_norm,
                               const void* k_norm, float eps, const void* positions, const void* inv_freq, const void* slot, void* q_out,
                               void* k_cache, void* v_cache, void* stream, const void* kv_scale, void* kv_amax, const void* pos3, int section_h,
-                              int section_w, void* k_tscale, void* v_tscale) {
+                              int section_w, void* k_tscale, void* v_tscale, int q4) {
   const int N = (n_q + 2 * n_kv) * hd;
   if (N % 128) return (int)cudaErrorInvalidValue;
   const int per_row = (N / 128 + 7) / 8;   // one warp per 128-block
@@ -231,7 +246,7 @@ RX_API int rx_finish_qkv_rope(const void* part, int S, int M, int n_q, int n_kv,
   cudaStream_t st = (cudaStream_t)stream;
 #define RX_ARGS (const float*)part, S, M, n_q, n_kv, (const __half*)svh, (const float*)bias, (const uint16_t*)q_norm, (const uint16_t*)k_norm, eps, \
                 (const int*)positions, (const float*)inv_freq, (const int*)slot, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache, \
-                (const float*)kv_scale, (float*)kv_amax, (const int*)pos3, 3 * section_h, 3 * section_w, (float*)k_tscale, (float*)v_tscale
+                (const float*)kv_scale, (float*)kv_amax, (const int*)pos3, 3 * section_h, 3 * section_w, (float*)k_tscale, (float*)v_tscale, q4
   if (hd == 128) rx::launch(finish_qkv_rope_kernel<128>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else if (hd == 64) rx::launch(finish_qkv_rope_kernel<64>, dim3(grid), dim3(256), 0, st, RX_ARGS);
   else return (int)cudaErrorInvalidValue;

@@ -178,18 +178,20 @@ def finish_swiglu_rot(part, S, M, w: Exl3Weight, suh_down: torch.Tensor, xr: tor
 
 
 def finish_qkv_rope(part, S, M, n_q, n_kv, hd, w: Exl3Weight, q_norm, k_norm, eps, positions, inv_freq, slot, q_out, k_cache, v_cache,
-                    kv_scale=None, kv_amax=None, pos3=None, mrope_sections=None, kv_tscale=None) -> None:
+                    kv_scale=None, kv_amax=None, pos3=None, mrope_sections=None, kv_tscale=None, q4: bool = False) -> None:
     """kv_scale (f32 [2, n_kv]) given: the caches are FP8 (E4M3) and K, V are stored divided by their head's scale.  kv_amax (f32 [2, n_kv])
     given: the largest |K| and |V| per head are recorded there.  pos3 (int32 [rows, 3]: T, H, W position of every row) with
     mrope_sections = (t, h, w) frequency-pair counts: interleaved M-RoPE instead of `positions` (pair i uses axis i % 3 inside its section)."""
     kts, vts = kv_tscale if kv_tscale is not None else (None, None)     # int8 caches: per-token scales are written there
+    # q4: the caches are uint8 [pages, n_kv, 64, hd / 2] nibbles and kv_tscale holds the E8M0 scale bytes uint8 [pages, n_kv, 64, hd / 32]
+    assert not q4 or (kts is not None and kts.dtype == torch.uint8 and k_cache.dtype == torch.uint8 and k_cache.shape[-1] == hd // 2)
     sec = mrope_sections or (0, 0, 0)
     assert pos3 is None or (pos3.dtype == torch.int32 and pos3.is_contiguous() and pos3.shape[1] == 3 and sum(sec) == hd // 2)
     L = _lib.load()
     _lib.check(L.rx_finish_qkv_rope(part.data_ptr(), S, M, n_q, n_kv, hd, w.svh.data_ptr(), _lib.ptr(w.bias), _lib.ptr(q_norm), _lib.ptr(k_norm),
                                     eps, positions.data_ptr(), inv_freq.data_ptr(), slot.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
                                     v_cache.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kv_amax), _lib.ptr(pos3), int(sec[1]), int(sec[2]),
-                                    _lib.ptr(kts), _lib.ptr(vts)), "rx_finish_qkv_rope")
+                                    _lib.ptr(kts), _lib.ptr(vts), 1 if q4 else 0), "rx_finish_qkv_rope")
     _lib.count()
 
 
@@ -352,16 +354,23 @@ def attn_decode_scratch(rows: int, n_q: int, hd: int, max_ctx: int, device="cuda
 
 
 def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_len, scratch, n_q, n_kv, hd, max_ctx, scale, suh, xr, out,
-                status, kv_scale=None, max_seq_rows: int = 1, plan=None, kv_tscale=None) -> None:
+                status, kv_scale=None, max_seq_rows: int = 1, plan=None, kv_tscale=None, q4: bool = False) -> None:
     """Split-KV decode / verify-window attention.  `max_seq_rows`: the most adjacent rows one sequence has in this window (1 + drafts); it
     picks how many MMA tiles a CTA carries so that a sequence's rows share one pass over its K / V (results do not depend on it).
     `plan`: the window plan from `attn_plan` for these rows and this `max_seq_rows` (one plan serves every layer of a forward); None has
     the call compute it itself.  `kv_tscale`: (K scales, V scales), f32 [pages, n_kv, 64] each, of an int8 cache."""
-    assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
-    assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
     kts, vts = kv_tscale if kv_tscale is not None else (None, None)
     rows = q.shape[0]
     L = _lib.load()
+    if q4:      # E2M1 nibble pages (the maps are 64 bytes wide) + E8M0 scale bytes uint8 [pages, n_kv, 64, hd / 32]
+        assert hd == 128 and kts is not None and kts.dtype == torch.uint8
+        _lib.check(L.rx_attn_decode_q4(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
+                                       scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out), status.data_ptr(),
+                                       _lib.stream_ptr(), int(max_seq_rows), _lib.ptr(plan), kts.data_ptr(), vts.data_ptr()), "rx_attn_decode_q4")
+        _lib.count(2 if plan is not None else 3)
+        return
+    assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
+    assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
     _lib.check(L.rx_attn_decode(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
                                 scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out),
                                 status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), int(max_seq_rows), _lib.ptr(plan), _lib.ptr(kts), _lib.ptr(vts)), "rx_attn_decode")
@@ -382,11 +391,18 @@ def attn_plan(row_seq, ctx_len, n_q: int, n_kv: int, max_seq_rows: int, plan: to
 
 
 def attn_prefill(tk: KvTensorMap, tv: KvTensorMap, q, block_table, seq_ids, q_start, q_len, pos0, out, nseq, max_qlen, n_q, n_kv, hd, scale,
-                 status, kv_scale=None, kv_tscale=None) -> None:
-    assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
-    assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
+                 status, kv_scale=None, kv_tscale=None, q4: bool = False) -> None:
     kts, vts = kv_tscale if kv_tscale is not None else (None, None)
     L = _lib.load()
+    if q4:
+        assert hd == 128 and kts is not None and kts.dtype == torch.uint8
+        _lib.check(L.rx_attn_prefill_q4(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], seq_ids.data_ptr(), q_start.data_ptr(),
+                                        q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
+                                        _lib.stream_ptr(), kts.data_ptr(), vts.data_ptr()), "rx_attn_prefill_q4")
+        _lib.count()
+        return
+    assert tk.fp8 == (kv_scale is not None), "an FP8 cache needs its per-head scales (and only an FP8 cache takes them)"
+    assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
     _lib.check(L.rx_attn_prefill(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], seq_ids.data_ptr(), q_start.data_ptr(),
                                  q_len.data_ptr(), pos0.data_ptr(), out.data_ptr(), nseq, max_qlen, n_q, n_kv, hd, scale, status.data_ptr(),
                                  _lib.stream_ptr(), _lib.ptr(kv_scale), _lib.ptr(kts), _lib.ptr(vts)), "rx_attn_prefill")

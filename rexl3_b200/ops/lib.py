@@ -112,7 +112,7 @@ def _declare(lib):
         "rx_finish_add_norm_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void, c_void, c_void]),
         "rx_finish_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void]),
         "rx_finish_qkv_rope": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_f, c_void, c_void,
-                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void]),
+                                       c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void, c_int]),
         "rx_state_digest": (c_int, [c_void, c_ll, c_void, c_void]),
         "rx_hc_mix": (c_int, [c_void, c_void, c_void, c_f, c_f, c_f, c_void, c_f, c_f, c_f, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_hc_apply": (c_int, [c_void, c_void, c_void, c_int, c_int, c_void]),
@@ -124,6 +124,10 @@ def _declare(lib):
         "rx_attn_decode_scratch_floats": (c_ll, [c_int, c_int, c_int, c_int]),
         "rx_attn_decode": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
                                    c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void]),
+        "rx_attn_decode_q4": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
+                                      c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void]),
+        "rx_attn_prefill_q4": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                                       c_int, c_f, c_void, c_void, c_void, c_void]),
         "rx_attn_plan_ints": (c_int, []),
         "rx_attn_plan": (c_int, [c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
         "rx_attn_prefill_tc": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,

@@ -33,8 +33,9 @@ def describe(cfg, kv_dtype: str = "bf16") -> dict:
         out.update(family="moe_gqa", weight_bytes=int(cfg.weight_params() * cfg.bits / 8) + cfg.vocab * cfg.d_model * 2,
                    kv_bytes_per_token=int(cfg.kv_bytes_per_token(2)), state_bytes_per_slot=0, shards="experts by rank")
     else:
+        kvb = cfg.kv_bytes_per_token(1) // 2 + cfg.kv_bytes_per_token(1) // 32 if kv_dtype == "q4" else cfg.kv_bytes_per_token(2 if kv_dtype == "bf16" else 1)
         out.update(family="dense_gqa", weight_bytes=int(cfg.weight_params() * cfg.bits / 8) + cfg.vocab * cfg.d_model * 2,
-                   kv_bytes_per_token=int(cfg.kv_bytes_per_token(2 if kv_dtype == "bf16" else 1)), state_bytes_per_slot=0,
+                   kv_bytes_per_token=int(kvb), state_bytes_per_slot=0,
                    shards="columns / rows and KV heads by rank")
     return out
 
@@ -75,7 +76,7 @@ def main(argv=None) -> int:
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--slots", type=int, default=16)
     p.add_argument("--max-model-len", type=int, default=8192)
-    p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8"], default="bf16")
+    p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8", "q4"], default="bf16")
     a = p.parse_args(argv)
     try:
         if a.config:

@@ -36,8 +36,9 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--kv-tokens", type=int, default=0, help="tokens of KV cache to reserve (0: slots * max-model-len)")
     p.add_argument("--prefill-chunk", type=int, default=4096)
     p.add_argument("--window-rows", type=int, default=64)
-    p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8"], default="bf16",
-                   help="fp8: E4M3 cache with per-head scales (calibrated at boot); int8: one power-of-two scale per token and KV head (no calibration)")
+    p.add_argument("--kv-dtype", choices=["bf16", "fp8", "int8", "q4"], default="bf16",
+                   help="fp8: E4M3 cache with per-head scales (calibrated at boot); int8: one power-of-two scale per token and KV head (no calibration); "
+                        "q4: E2M1 nibbles with one E8M0 scale per 32 values (68 bytes per 128-wide row, lossy; dense family, one GPU)")
     p.add_argument("--spec", choices=["auto", "mtp", "copy", "ngram", "self", "none"], default="auto")
     p.add_argument("--intervention", metavar="DIR", default=None,
                    help="a runtime overlay directory (intervention.json + direction files): checked against the model at boot, any mismatch refuses")
@@ -197,6 +198,8 @@ def build(args):
                 kvb = cfg.kv_bytes_per_token() if is_mla else cfg.kv_bytes_per_token(2 if args.kv_dtype == "bf16" else 1)
                 if args.kv_dtype == "int8":
                     kvb += cfg.n_layers * cfg.n_kv * 8          # one f32 scale per token, KV head and tensor
+                if args.kv_dtype == "q4":                       # half a byte per value + one scale byte per 32 values
+                    kvb = cfg.kv_bytes_per_token(1) // 2 + cfg.kv_bytes_per_token(1) // 32
                 wbytes = int(mla_models.MlaMoEGPU.weight_bytes_estimate(cfg)) if is_mla else int(cfg.weight_params() * cfg.bits / 8)
                 if is_hybrid:
                     wbytes += cfg.state_bytes_per_slot() * args.slots      # the recurrent-state pools are resident like weights

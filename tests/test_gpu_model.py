@@ -328,3 +328,61 @@ def test_guard_bands_stay_intact_through_prefill_and_decode(monkeypatch):
     m.check()
     assert canary.check_all() >= 7
     canary.forget()
+
+
+def test_q4_kv_cache_rows_and_attention():
+    """q4 KV (E2M1 nibbles, one E8M0 scale per 32 values): the stored rows dequantise to the bf16 cache within half a code step, and prefill and
+    decode windows over them stay close to the bf16-cache executor (a 4-bit cache is lossy: the bound is loose, the row check is tight)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+    from rexl3_b200.models import dense
+    cfg = dense.CONFIGS["test-hd128"]
+    w = dense.random_weights(cfg, seed=3)
+    a = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256)
+    b = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256, kv_dtype="q4")
+    assert b.k_cache[0].shape[-1] == 64 and b.k_tscale[0].shape[-1] == 4
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, size=150).tolist()
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    bt = torch.zeros(4, 4, dtype=torch.int32, device="cuda")
+    bt[1, :3] = i32([5, 9, 2])
+    T = len(prompt)
+    pos = list(range(T))
+    slots = [int(bt[1, p // 64]) * 64 + p % 64 for p in pos]
+    pf = dict(seq_ids=i32([1]), q_start=i32([0]), q_len=i32([T]), pos0=i32([0]), nseq=1, max_qlen=T)
+    args = (i32(prompt), i32(pos), i32(slots), i32([1] * T), i32([p + 1 for p in pos]), bt)
+    la = a.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+    lb = b.forward_rows(*args, prefill=pf)[:, :cfg.vocab].clone()
+    a.check()
+    b.check()
+    # layer 0 sees the same inputs in both executors: dequantise its q4 page on the host
+    mags = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], device="cuda")
+    for cache16, cache4, sc4 in ((a.k_cache[0][5], b.k_cache[0][5], b.k_tscale[0][5]), (a.v_cache[0][5], b.v_cache[0][5], b.v_tscale[0][5])):
+        by = cache4.long()                                              # [n_kv, 64, 64] bytes
+        nib = torch.stack([by & 15, by >> 4], dim=-1).reshape(*by.shape[:-1], 128)
+        val = mags[nib & 7] * torch.where((nib & 8) != 0, -1.0, 1.0)
+        scale = torch.exp2(sc4.float() - 127.0).repeat_interleave(32, dim=-1)
+        deq = val * scale
+        x = cache16.float()
+        amax = x.view(*x.shape[:-1], 4, 32).abs().amax(-1)
+        want_scale = torch.exp2(torch.ceil(torch.log2(amax.clamp_min(1e-4) / 6.0)).clamp(-14, 12))
+        got_scale = torch.exp2(sc4.float() - 127.0)          # (the device takes the group maximum before the bf16 rounding of the other executor's cache)
+        assert (got_scale == want_scale).float().mean().item() > 0.97 and ((got_scale / want_scale - 1).abs() <= 1.0).all()
+        # nearest E2M1 code: the error is at most half the local code spacing (2 at the top of the range) times the scale
+        assert ((x - deq).abs() <= 0.5 * scale * torch.where(x.abs() / scale >= 4, 2.0, torch.where(x.abs() / scale >= 2, 1.0, 0.5)) + 0.01 * x.abs() + 1e-6).all()
+    scale_l = la.abs().max().item()
+    assert (la - lb).abs().max().item() < 0.25 * scale_l and (la - lb).abs().mean().item() < 0.05 * scale_l
+    p = T
+    a2 = (i32([7]), i32([p]), i32([int(bt[1, p // 64]) * 64 + p % 64]), i32([1]), i32([p + 1]), bt)
+    da = a.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+    db = b.forward_rows(*a2, max_ctx=256)[:, :cfg.vocab].clone()
+    b.check()
+    assert (da - db).abs().max().item() < 0.25 * scale_l
+    # decode over the q4 cache == prefill over the q4 cache for the same row (both expand the same bytes)
+    c = dense.DenseGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=256, kv_dtype="q4")
+    pf1 = dict(seq_ids=i32([1]), q_start=i32([0]), q_len=i32([T + 1]), pos0=i32([0]), nseq=1, max_qlen=T + 1)
+    pos1 = list(range(T + 1))
+    slots1 = [int(bt[1, q // 64]) * 64 + q % 64 for q in pos1]
+    lc = c.forward_rows(i32(prompt + [7]), i32(pos1), i32(slots1), i32([1] * (T + 1)), i32([q + 1 for q in pos1]), bt, prefill=pf1)[:, :cfg.vocab].clone()
+    assert (lc[-1] - db[0]).abs().max().item() < 0.02 * scale_l
