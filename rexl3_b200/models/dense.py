@@ -73,6 +73,7 @@ CONFIGS = {
                              bits=4.0, name="dense-27b"),
     # small GPU test model with the production head geometry
     "test-hd128": DenseConfig(n_layers=2, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hd128"),
+    "test-hd128-mtp": DenseConfig(n_layers=2, d_model=512, n_q=8, n_kv=2, head_dim=128, ffn=1024, vocab=4096, bits=4.0, name="test-hd128-mtp", mtp=True),
 }
 
 

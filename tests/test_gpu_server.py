@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("config,extra", [("test-hd128", ["--kv-dtype", "fp8"]), ("test-hd128", ["--kv-dtype", "int8"]), ("test-moe", ["--spec", "self"]), ("test-mla", ["--spec", "none"]),
+@pytest.mark.parametrize("config,extra", [("test-hd128", ["--kv-dtype", "fp8"]), ("test-hd128", ["--kv-dtype", "int8"]), ("test-hd128", ["--kv-dtype", "q4"]), ("test-hd128-mtp", ["--spec", "mtp"]), ("test-moe", ["--spec", "self"]), ("test-mla", ["--spec", "none"]),
                                           ("test-hybrid", ["--spec", "copy"]), ("test-hybrid-gdn", ["--spec", "copy", "--state-snapshots", "--prefix-cache", "on"])])
 def test_completion_over_cuda_backend(config, extra):
     if not torch.cuda.is_available():
