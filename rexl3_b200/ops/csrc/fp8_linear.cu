@@ -10,6 +10,7 @@
 // tcgen05.mma kind::f16 with bf16 operands, warps 2..5 read the accumulator back.  K splits write fp32 planes that a finish kernel sums in
 // split order (+ bias) into the output type.  Scales below 2^-126 flush to zero, 0xFF is NaN.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include "common.cuh"
 
@@ -20,22 +21,25 @@ constexpr int F8_STRIP = 128;
 constexpr int F8_GROUPS = 2;
 constexpr int F8_DEC_WARPS = 8;
 constexpr int F8_THREADS = 64 + F8_DEC_WARPS * 32;
-constexpr int F8_RAW_STAGES = 4;
-constexpr int F8_OP_STAGES = 3;
-static_assert(F8_OP_STAGES >= F8_GROUPS, "operand ring shallower than the number of expand groups");
+// Ring depths: 3 operand stages and 4 raw stages keep two CTAs on an SM at window sizes.  Deeper rings were measured and change nothing
+// (4 / 4, 3 / 6: the same 43.8 us at one row; 6 / 8 drops to one CTA per SM and 68 us), so the chain is not what bounds the kernel - see the
+// profile summary for what does (shared-memory traffic of the expansion at many rows, 64-byte row pieces per bulk copy at few rows).
+constexpr int F8_RAW_STAGES_MAX = 4;
+constexpr int F8_OP_STAGES_MAX = 3;
+static_assert(3 >= F8_GROUPS, "operand ring shallower than the number of expand groups");
 constexpr int F8_A_STAGE = F8_STRIP * F8_KCH * 2;       // 16 KB of bf16
 constexpr int F8_RAW_STAGE = F8_STRIP * F8_KCH;         // 8 KB of E4M3 bytes
 
 struct F8Layout {
   int a_off, b_off, raw_off, bar_off, total;
 };
-__host__ __device__ inline F8Layout f8_layout(int brows) {
+__host__ __device__ inline F8Layout f8_layout(int brows, int ops, int raws) {
   F8Layout L;
   L.a_off = 0;
-  L.b_off = L.a_off + F8_OP_STAGES * F8_A_STAGE;
-  L.raw_off = L.b_off + F8_OP_STAGES * brows * F8_KCH * 2;
-  L.bar_off = L.raw_off + F8_RAW_STAGES * F8_RAW_STAGE;
-  L.total = L.bar_off + 256;
+  L.b_off = L.a_off + ops * F8_A_STAGE;
+  L.raw_off = L.b_off + ops * brows * F8_KCH * 2;
+  L.bar_off = L.raw_off + raws * F8_RAW_STAGE;
+  L.total = L.bar_off + 512;
   return L;
 }
 
@@ -43,20 +47,21 @@ __device__ __forceinline__ float f8_e8m0(uint32_t b) {
   return __uint_as_float(b == 0u ? 0u : (b == 0xFFu ? 0x7fc00000u : (b << 23)));
 }
 
+template <int OPS, int RAWS>
 __global__ void __launch_bounds__(F8_THREADS, 2)
 fp8_linear_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const uint8_t* __restrict__ scales,
-                  float* __restrict__ part, int rows, int K, int N, int splits, int brows, int* status) {
+                  float* __restrict__ part, int rows, int K, int N, int splits, int brows, int* status, int AHEAD_B) {
   pdl_launch();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const F8Layout L = f8_layout(brows);
+  const F8Layout L = f8_layout(brows, OPS, RAWS);
   const int b_stage = brows * F8_KCH * 2;
   uint64_t* bars = (uint64_t*)(smem + L.bar_off);
   uint64_t* op_full = bars;
-  uint64_t* op_empty = bars + F8_OP_STAGES;
-  uint64_t* raw_full = bars + 2 * F8_OP_STAGES;
-  uint64_t* raw_empty = raw_full + F8_RAW_STAGES;
-  uint64_t* acc_full = raw_empty + F8_RAW_STAGES;
+  uint64_t* op_empty = bars + F8_OP_STAGES_MAX;
+  uint64_t* raw_full = bars + 2 * F8_OP_STAGES_MAX;
+  uint64_t* raw_empty = raw_full + F8_RAW_STAGES_MAX;
+  uint64_t* acc_full = raw_empty + F8_RAW_STAGES_MAX;
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -72,8 +77,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   while ((int)ncols < brows) ncols <<= 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < F8_OP_STAGES; ++i) { mbar_init(&op_full[i], F8_DEC_WARPS / F8_GROUPS + 1); mbar_init(&op_empty[i], 1); }
-    for (int i = 0; i < F8_RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], F8_DEC_WARPS / F8_GROUPS); }
+    for (int i = 0; i < OPS; ++i) { mbar_init(&op_full[i], F8_DEC_WARPS / F8_GROUPS + 1); mbar_init(&op_empty[i], 1); }
+    for (int i = 0; i < RAWS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], F8_DEC_WARPS / F8_GROUPS); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -92,21 +97,21 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      constexpr int AHEAD = 4;
+      const int AHEAD = AHEAD_B;
       bool ok = true;
       bool waited = false;
       for (int i = 0; i < nchunks + AHEAD && ok; ++i) {
         if (i < nchunks) {            // weights do not depend on the previous kernel: they stream before griddepcontrol.wait
-          const int c = i, s = c % F8_RAW_STAGES;
-          if (c >= F8_RAW_STAGES) ok = mbar_wait(&raw_empty[s], ((c / F8_RAW_STAGES) - 1) & 1, abort_flag, status, 180);
+          const int c = i, s = c % RAWS;
+          if (c >= RAWS) ok = mbar_wait(&raw_empty[s], ((c / RAWS) - 1) & 1, abort_flag, status, 180);
           if (!ok) break;
           mbar_arrive_expect_tx(&raw_full[s], F8_RAW_STAGE);
           tma_load_2d(smem + L.raw_off + s * F8_RAW_STAGE, &tmap_w, (c_begin + c) * F8_KCH, w_row0, &raw_full[s]);
         }
         if (i >= AHEAD) {
           if (!waited) { pdl_wait(); waited = true; }
-          const int c = i - AHEAD, s = c % F8_OP_STAGES;
-          if (c >= F8_OP_STAGES) ok = mbar_wait(&op_empty[s], ((c / F8_OP_STAGES) - 1) & 1, abort_flag, status, 181);
+          const int c = i - AHEAD, s = c % OPS;
+          if (c >= OPS) ok = mbar_wait(&op_empty[s], ((c / OPS) - 1) & 1, abort_flag, status, 181);
           if (!ok) break;
           mbar_arrive_expect_tx(&op_full[s], (uint32_t)b_stage);
           tma_load_2d(smem + L.b_off + s * b_stage, &tmap_x, (c_begin + c) * F8_KCH, g_row0, &op_full[s]);
@@ -118,8 +123,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       const uint32_t idesc = umma_idesc_f16(F8_STRIP, brows, 1, 1);
       bool ok = true;
       for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c % F8_OP_STAGES;
-        ok = mbar_wait(&op_full[s], (c / F8_OP_STAGES) & 1, abort_flag, status, 182);
+        const int s = c % OPS;
+        ok = mbar_wait(&op_full[s], (c / OPS) & 1, abort_flag, status, 182);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + L.a_off + s * F8_A_STAGE);
@@ -134,41 +139,66 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   } else {
     const int dw = warp - 2;
     const int grp = dw / (F8_DEC_WARPS / F8_GROUPS);
-    const int t = (dw % (F8_DEC_WARPS / F8_GROUPS)) * 32 + lane;     // row of the strip this thread expands
-    // this row's scale bytes: one per 32-wide k tile, shared by the 32 rows of a tile (a warp reads one address)
-    const uint8_t* srow = scales + (size_t)((w_row0 + t) >> 5) * (K / 32) + (size_t)c_begin * 2;
+    // A warp expands 32 rows of the strip (one scale tile) in four 8-row slabs: lane = (row of the slab, 16-byte quarter of the 64-byte raw
+    // row), so one load instruction reads 512 contiguous bytes - free of bank conflicts (a thread per row would read at a 64-byte stride,
+    // 16 ways conflicted: measured 2x slower end to end) - and a lane turns its 16 weights into two 16-byte pieces of the bf16 operand row.
+    const int wq = dw % (F8_DEC_WARPS / F8_GROUPS), sub_r = lane >> 2, sub_c = lane & 3;
+    const uint8_t* srow = scales + (size_t)((w_row0 + 32 * wq) >> 5) * (K / 32) + (size_t)c_begin * 2;
     bool ok = true;
     for (int c = grp; c < nchunks && ok; c += F8_GROUPS) {
-      const int rs = c % F8_RAW_STAGES, os = c % F8_OP_STAGES;
+      const int rs = c % RAWS, os = c % OPS;
       const uint32_t sc = *reinterpret_cast<const uint16_t*>(srow + 2 * c);
-      ok = mbar_wait(&raw_full[rs], (c / F8_RAW_STAGES) & 1, abort_flag, status, 183);
+      ok = mbar_wait(&raw_full[rs], (c / RAWS) & 1, abort_flag, status, 183);
       if (!ok) break;
-      const uint32_t raw = smem_u32(smem + L.raw_off + rs * F8_RAW_STAGE + t * 64);
-      const uint4 r0 = lds128(raw), r1 = lds128(raw + 16), r2 = lds128(raw + 32), r3 = lds128(raw + 48);
+      const uint32_t raw = smem_u32(smem + L.raw_off + rs * F8_RAW_STAGE + (32 * wq + sub_r) * 64 + sub_c * 16);
+      uint4 rw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rw[i] = lds128(raw + i * 8 * 64);
       // Handing the stage back to the bulk-copy engine: the reads above went through the generic proxy, the next chunk's copy writes through
       // the async proxy, and nothing orders the two but a proxy fence BEFORE the release (measured without it: the copy for chunk c + 4
       // overtook these reads in half of the launches at 32 chunks per CTA, whole 32-row blocks of an operand tile then mixed two chunks;
       // with the fence 0 of 120 launches).
       release_read_stage(&raw_empty[rs], lane);
-      if (c >= F8_OP_STAGES) ok = mbar_wait(&op_empty[os], ((c / F8_OP_STAGES) - 1) & 1, abort_flag, status, 184);
+      if (c >= OPS) ok = mbar_wait(&op_empty[os], ((c / OPS) - 1) & 1, abort_flag, status, 184);
       if (!ok) break;
-      uint8_t* a_row = smem + L.a_off + os * F8_A_STAGE + (t >> 3) * 1024 + (t & 7) * 128;
-      const uint32_t words[16] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w, r2.x, r2.y, r2.z, r2.w, r3.x, r3.y, r3.z, r3.w};
-      const float s_lo = f8_e8m0(sc & 0xFFu), s_hi = f8_e8m0(sc >> 8);   // k 0..31 and 32..63 of the chunk
+      uint8_t* a_stage = smem + L.a_off + os * F8_A_STAGE;
+      // E4M3 -> bf16 without a conversion instruction: the byte s eeee mmm, moved to the top of a halfword and shifted right by 4 under a mask, IS
+      // the bf16 number (-1)^s 2^(e - 127) (1 + m / 8) (exponent field = e, mantissa = m << 4; e = 0 gives the matching bf16 subnormal), i.e. the
+      // value times 2^-120.  One packed bf16 multiply by 2^(120 + scale exponent) - a power of two, exact, subnormals included - finishes it:
+      // PRMT, SHF, LOP3, HMUL2 per two weights.  (Scales of 2^8 and more would overflow that constant: those chunks take the float path.)
+      const uint32_t scb = sub_c < 2 ? (sc & 0xFFu) : (sc >> 8);           // this lane's 16 weights lie in k 0..31 or 32..63 of the chunk
+      const int se = (int)scb - 127;
+      const bool fast = se <= 7 && se >= -126 && scb != 0xFFu;
+      const uint32_t kbits = (uint32_t)(se + 120 + 127) << 7;              // bf16 bits of 2^(120 + se)
+      const uint32_t mulw = kbits | (kbits << 16);
+      const __nv_bfloat162 mul = *reinterpret_cast<const __nv_bfloat162*>(&mulw);
+      const float sf = f8_e8m0(scb);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // words 2j, 2j + 1 hold k = 8j .. 8j + 7: one 16-byte column of the bf16 operand row
-        const float s = j < 4 ? s_lo : s_hi;
-        uint32_t o[4];
+      for (int i = 0; i < 4; ++i) {
+        const int r = 32 * wq + 8 * i + sub_r;
+        uint8_t* a_row = a_stage + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t words[4] = {rw[i].x, rw[i].y, rw[i].z, rw[i].w};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t w = words[2 * j + (q >> 1)];
-          const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu), __NV_E4M3);
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-          const __nv_bfloat162 p = __floats2bfloat162_rn(f.x * s, f.y * s);
-          o[q] = *reinterpret_cast<const uint32_t*>(&p);
+        for (int hf = 0; hf < 2; ++hf) {              // words 2 hf, 2 hf + 1 = k 8 (2 sub_c + hf) .. + 7 = one 16-byte piece of the bf16 row
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t w = words[2 * hf + (q >> 1)];
+            if (fast) {
+              const uint32_t pair = __byte_perm(w, 0u, (q & 1) ? 0x3424u : 0x1404u);      // (b1 << 24) | (b0 << 8) of this pair of bytes
+              const uint32_t bits = (pair & 0x80008000u) | ((pair >> 4) & 0x07F007F0u);
+              const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&bits), mul);
+              o[q] = *reinterpret_cast<const uint32_t*>(&v);
+            } else {
+              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu), __NV_E4M3);
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+              const __nv_bfloat162 pv = __floats2bfloat162_rn(f.x * sf, f.y * sf);
+              o[q] = *reinterpret_cast<const uint32_t*>(&pv);
+            }
+          }
+          const int j = 2 * sub_c + hf;
+          *reinterpret_cast<uint4*>(a_row + ((j ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        *reinterpret_cast<uint4*>(a_row + ((j ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       fence_proxy_async();
       __syncwarp();
@@ -256,18 +286,18 @@ RX_API int rx_fp8_linear(const void* x, int rows, int K, const void* w, const vo
   if (e != 0) return e;
   e = make_tmap_u8_2d(&tw, w, (uint64_t)N, (uint64_t)K, F8_KCH, F8_STRIP);
   if (e != 0) return e;
-  const F8Layout L = f8_layout(tile_rows);
+  const F8Layout L = f8_layout(tile_rows, 3, 4);
   const int smem = L.total + 1024;
+  if (smem > 232448) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
   static bool configured = false;
   if (!configured) {
-    cudaError_t ce = cudaFuncSetAttribute(fp8_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    cudaError_t ce = cudaFuncSetAttribute(fp8_linear_kernel<3, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
-  if (smem > 232448) return (int)cudaErrorInvalidValue;
-  cudaStream_t st = (cudaStream_t)stream;
-  e = (int)rx::launch(fp8_linear_kernel, dim3(N / F8_STRIP, splits, (rows + tile_rows - 1) / tile_rows), dim3(F8_THREADS), (size_t)smem, st, tx, tw,
-                      (const uint8_t*)scales, (float*)part, rows, K, N, splits, tile_rows, status);
+  e = (int)rx::launch(fp8_linear_kernel<3, 4>, dim3(N / F8_STRIP, splits, (rows + tile_rows - 1) / tile_rows), dim3(F8_THREADS), (size_t)smem, st, tx, tw,
+                      (const uint8_t*)scales, (float*)part, rows, K, N, splits, tile_rows, status, 4);
   if (e != 0) return e;
   return (int)rx::launch(fp8_finish_kernel, dim3(N / 128, rows), dim3(32), 0, st, (const float*)part, splits, rows, N, (const float*)bias, out, out_type);
 }
