@@ -33,6 +33,10 @@ def lib():
         L.rx_bpe_free.argtypes = [c_void]
         L.rx_bpe_encode.restype = ctypes.c_int64
         L.rx_bpe_encode.argtypes = [c_void, c_void, c_void, c_int, c_void, ctypes.c_int64]
+        L.rx_pretok_split.restype = ctypes.c_int64
+        L.rx_pretok_split.argtypes = [c_int, c_void, ctypes.c_int64, c_void, ctypes.c_int64]
+        L.rx_bpe_encode_text.restype = ctypes.c_int64
+        L.rx_bpe_encode_text.argtypes = [c_void, c_int, c_void, ctypes.c_int64, c_void, ctypes.c_int64]
         _lib = L
     return _lib
 
@@ -95,6 +99,31 @@ def read_ranges(path: str, offsets, sizes, dst: np.ndarray, dst_offsets, threads
     return bool(used.value)
 
 
+# The split patterns the native pre-tokenizer implements (native/csrc/pretok.cpp), by the regular expression a tokenizer file spells them with.
+_GPT2 = r"""'(?:[sdmt]|ll|ve|re)| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+_GPT2_B = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+_CL100K = r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"""
+_QWEN2 = r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"""
+PRETOK_KINDS = {_GPT2: 0, _GPT2_B: 0, _CL100K: 1, _QWEN2: 2}
+
+
+def pretok_kind(pattern: str):
+    """-> the native pattern id of a split regular expression, or None when the scanner does not implement it (the caller keeps `regex`)."""
+    return PRETOK_KINDS.get(pattern)
+
+
+def pretok_split(text: str, kind: int) -> list:
+    """The pieces of `text` under native pattern `kind` (tests compare this with the `regex` oracle)."""
+    raw = text.encode("utf-8")
+    buf = np.frombuffer(raw, dtype=np.uint8) if raw else np.zeros(1, dtype=np.uint8)
+    offs = np.empty(len(raw) + 2, dtype=np.int64)
+    n = lib().rx_pretok_split(kind, buf.ctypes.data, len(raw), offs.ctypes.data, offs.size)
+    if n < 1 or n > offs.size:
+        raise ValueError("native pre-tokenizer refused its arguments")
+    o = offs[:n].tolist()
+    return [raw[a:b].decode("utf-8") for a, b in zip(o[:-1], o[1:])]
+
+
 class BpeCore:
     """Ranked byte-level BPE merges on token ids (`native/csrc/bpe.cpp`).  byte_ids: the token id of each of the 256 bytes (-1: none);
     merges: (left id, right id, merged id) triples in rank order."""
@@ -119,6 +148,18 @@ class BpeCore:
         n = lib().rx_bpe_encode(self._h, buf.ctypes.data if buf.size else None, offs.ctypes.data, len(pieces), out.ctypes.data, out.size)
         if n < 0 or n > out.size:
             raise ValueError("native BPE refused its arguments")
+        return out[:n].tolist()
+
+    def encode_text(self, text: str, kind: int) -> list:
+        """Pre-tokenizer split (pattern `kind`, see `pretok_kind`) + merges in one native call."""
+        raw = text.encode("utf-8")
+        if not raw:
+            return []
+        buf = np.frombuffer(raw, dtype=np.uint8)
+        out = np.empty(len(raw), dtype=np.int32)
+        n = lib().rx_bpe_encode_text(self._h, kind, buf.ctypes.data, len(raw), out.ctypes.data, out.size)
+        if n < 0 or n > out.size:
+            raise ValueError("native tokenizer refused its arguments")
         return out[:n].tolist()
 
     def __del__(self):

@@ -144,13 +144,18 @@ class BpeTokenizer(Tok):
         self.id_to_tok = {v: k for k, v in self.vocab.items()}
         self.id_to_tok.update({v: k for k, v in self.added.items()})
         self.vocab_size = max(self.id_to_tok) + 1
-        self.pattern = regex.compile(self._split_pattern(spec.get("pre_tokenizer")) or GPT2_SPLIT)
+        self.pattern_text = self._split_pattern(spec.get("pre_tokenizer")) or GPT2_SPLIT
+        self.pattern = regex.compile(self.pattern_text)
         self._added_split = regex.compile("(" + "|".join(regex.escape(s) for s in sorted(self.added, key=len, reverse=True)) + ")") if self.added else None
         self.b2u = bytes_to_unicode()
         self.u2b = {c: b for b, c in self.b2u.items()}
         self.eos_ids, self.bos_id = tuple(eos_ids), bos_id
         self._cache = {}
         self._native = self._make_native()
+        self._native_kind = None        # the native scanner's id of this file's split pattern (None: `regex` does the split)
+        if self._native is not None:
+            from ..native import host
+            self._native_kind = host.pretok_kind(self.pattern_text)
 
     def _make_native(self):
         """The merge loop in the host library, when every merge maps onto token ids (else the Python loop below runs)."""
@@ -215,6 +220,8 @@ class BpeTokenizer(Tok):
         return ids
 
     def _encode_plain(self, text: str) -> list:
+        if self._native is not None and self._native_kind is not None:
+            return self._native.encode_text(text, self._native_kind)           # split + merges in one native call
         if self._native is not None:
             return self._native.encode_pieces(m.group(0).encode("utf-8") for m in self.pattern.finditer(text))
         out = []
