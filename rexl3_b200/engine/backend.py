@@ -23,6 +23,22 @@ class RowRequest:
 
 
 @dataclass
+class TreeRequest:
+    """One sequence's rows of a tree window: row 0 is the anchor (the last committed token), row i > 0 a draft node whose parent row is
+    `parents[i]` < i (`parents[0]` = -1).  Row i is the token at position first_position + depth(i)."""
+    slot: int
+    tokens: list
+    parents: list
+    first_position: int
+
+    def depths(self) -> list:
+        d = [0] * len(self.tokens)
+        for i in range(1, len(self.tokens)):
+            d[i] = d[self.parents[i]] + 1
+        return d
+
+
+@dataclass
 class RowOutput:
     ids: np.ndarray        # uint32 [count], ordered (value desc, id asc)
     values: np.ndarray     # float32 [count]
@@ -50,6 +66,7 @@ class DraftAsk:
 class DraftOffer:
     tokens: list = field(default_factory=list)
     conf: list = field(default_factory=list)       # optional per-draft confidence (probability it is accepted given the ones before)
+    lattice: object = None                         # optional spec.tree.Lattice: per level the drafter's candidate ids and scores (level 0 = first draft)
 
 
 class Backend:
@@ -90,6 +107,21 @@ class Backend:
 
     def supports_native_draft(self) -> bool:
         return False
+
+    def supports_trees(self) -> bool:
+        """True: `step_tree` / `commit_path` are implemented (reference crates/engine/src/lib.rs:212-432, step_tree / commit_path /
+        supports_trees)."""
+        return False
+
+    def step_tree(self, reqs: list, candidates: int) -> list:
+        """One window of draft trees (reqs: TreeRequest).  Returns, per request, one RowOutput per row; a row's output is what a one-row step
+        returns after the tokens on the row's path from the anchor."""
+        raise NotImplementedError
+
+    def commit_path(self, slot: int, rows: list) -> None:
+        """Keep the anchor and the rows `rows` (a path: each row's parent is the one before, the first row's parent the anchor) of the slot's
+        last tree window; every other row never happened."""
+        raise NotImplementedError
 
     def supports_rollback(self) -> bool:
         """False: rows fed to `step` cannot be rejected afterwards (recurrent state), so the engine plans no draft rows."""

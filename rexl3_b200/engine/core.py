@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import numpy as np  # noqa: F401  (type of score rows)
 
+import math
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -82,11 +83,26 @@ class StepError(Exception):
         self.kind, self.fatal, self.group_lost = kind, fatal, group_lost
 
 
+@dataclass
+class TreeConfig:
+    """Draft-tree rounds (reference crates/engine/src/lib.rs:724-832, TreeConfig): at most `max_nodes` draft nodes per stream and round
+    (the window holds the anchor as well, and a tree window has at most 64 rows), searched with `policy`."""
+    max_nodes: int = 16
+    policy: object = None
+
+    def __post_init__(self):
+        from ..spec.tree import Policy
+        if self.policy is None:
+            self.policy = Policy()
+        if not 1 <= self.max_nodes <= 63:
+            raise ValueError("a tree holds 1..63 draft nodes")
+
+
 class Engine:
     def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
                  spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
                  prefill_policy: str = "burst", burst_div: int = 2, burst_cap: int = 16, cache_namespace: bytes = b"", device_sampler: bool = False,
-                 spill=None, arbiter=None):
+                 spill=None, arbiter=None, trees=None):
         self.backend = backend
         self.admission = admission
         self.window_rows = min(window_rows, backend.max_rows)
@@ -100,6 +116,8 @@ class Engine:
         # optional spec.Arbiter: per round and stream it picks how many of the offered drafts to verify (or none) by expected committed tokens
         # per model-millisecond, learns each source's acceptance by depth from the outcomes, and probes idle sources now and then
         self.arbiter = arbiter
+        # TreeConfig: verify windows are draft trees when the backend supports them (chain windows otherwise)
+        self.trees = trees
         self.prefix_cuts = bool(self.prefix is not None and getattr(backend, "prefix_needs_cuts", lambda: False)())
         self.spill = spill if self.prefix is not None else None
         if self.spill is not None:
@@ -315,6 +333,8 @@ class Engine:
             start = self._window_start % len(active)
             active = (active[start:] + active[:start])[:self.window_rows]
             self._window_start = start + self.window_rows
+        if self.trees is not None and self.can_rollback and getattr(self.backend, "supports_trees", lambda: False)():
+            return self._decode_round_trees(active)
         t0 = time.perf_counter_ns()
         # 1. how many drafts each stream may use
         maxes = []
@@ -421,29 +441,130 @@ class Engine:
                 self.counters["accepted"] += a
             else:
                 s.stats.relax()
-            new = samples[:a + 1]
-            emitted, reason = [], None
-            for t in new:
-                forced = False
-                if s.req.reasoning_budget is not None and s.req.think_close_ids:
-                    t, forced = self._reasoning_budget(s, t)
-                emitted.append(t)
-                s.tokens.append(t)
-                s.generated += 1
-                if t in s.req.stop_ids:
-                    reason = "stop"
-                    break
-                if s.generated >= s.req.max_new_tokens:
-                    reason = "length"
-                    break
-                if forced:
-                    break      # the samples after a forced token were made for another continuation: their rows are not kept
-            self.counters["decode_tokens"] += len(emitted)
-            self.events.append(Event("tokens", s.req.id, tokens=emitted))
+            emitted, reason = self._emit(s, samples[:a + 1])
             if reason is not None:
                 self._finish(s, reason)
             else:
                 self.backend.commit(s.slot, len(emitted))
+        self.phase_ns["draft"] += t1 - t0
+        self.phase_ns["verify"] += t2 - t1
+        self.phase_ns["commit"] += time.perf_counter_ns() - t2
+
+    def _emit(self, s, new) -> tuple:
+        """Commits the round's tokens `new` to the sequence one by one (reasoning budget, stop ids, length) and queues the event.
+        -> (tokens emitted, finish reason or None)."""
+        emitted, reason = [], None
+        for t in new:
+            forced = False
+            if s.req.reasoning_budget is not None and s.req.think_close_ids:
+                t, forced = self._reasoning_budget(s, t)
+            emitted.append(t)
+            s.tokens.append(t)
+            s.generated += 1
+            if t in s.req.stop_ids:
+                reason = "stop"
+                break
+            if s.generated >= s.req.max_new_tokens:
+                reason = "length"
+                break
+            if forced:
+                break      # the samples after a forced token were made for another continuation: their rows are not kept
+        self.counters["decode_tokens"] += len(emitted)
+        self.events.append(Event("tokens", s.req.id, tokens=emitted))
+        return emitted, reason
+
+    def _decode_round_trees(self, active) -> None:
+        """A decode round whose windows are draft trees (reference crates/engine/src/lib.rs:2215, decode_round_trees): every stream's native
+        offer becomes a best-first tree over its candidate lattice (a chain when the drafter gave no lattice), the copy drafter's chain is
+        grafted below the anchor, the window's rows are shared among the streams by the nodes' probabilities of lying on the accepted path,
+        one forward verifies every node, the target's own samples walk down each tree, and the accepted path is committed.  The committed
+        tokens are the target's samples at their positions, so the output equals the serial run's whatever the trees held."""
+        from ..sched import allocate
+        from ..spec.tree import DraftTree, best_first, with_copy, accept_tree
+        from .backend import TreeRequest
+        cfg = self.trees
+        t0 = time.perf_counter_ns()
+        maxes = []
+        for s in active:
+            room = s.req.max_new_tokens - s.generated
+            maxes.append(min(self.max_drafts, max(0, room - 1)) if (self.spec.enabled and s.req.draft) else 0)
+        trees = [DraftTree() for _ in active]
+        if any(maxes) and self.spec.native and self.backend.supports_native_draft():
+            asks = [DraftAsk(s.slot, s.tokens, m, s.req.sampling) for s, m in zip(active, maxes) if m > 0]
+            offers = self.backend.propose_batch(asks)
+            for i, s in enumerate(active):
+                off = offers.get(s.slot)
+                if off is None or maxes[i] <= 0:
+                    continue
+                if off.lattice is not None and len(off.lattice.ids) > 0:
+                    lat = off.lattice
+                    lat = type(lat)(lat.ids[:maxes[i]], lat.unary[:maxes[i]], None if lat.edge is None else lat.edge[:maxes[i]])
+                    trees[i] = best_first(lat, cfg.max_nodes, cfg.policy)
+                else:
+                    toks = list(off.tokens[:maxes[i]])
+                    conf = list(off.conf[:len(toks)]) + [0.7] * (len(toks) - len(off.conf))
+                    lp, logp = 0.0, []
+                    for c in conf:
+                        lp += math.log(min(1.0, max(1e-6, c)))
+                        logp.append(lp)
+                    trees[i] = DraftTree(toks, list(range(-1, len(toks) - 1)), list(range(1, len(toks) + 1)), logp)
+        if self.spec.copy:
+            for i, s in enumerate(active):
+                if maxes[i] > 0:
+                    chain = s.drafter.propose(s.tokens, maxes[i])
+                    if chain:
+                        trees[i] = with_copy(trees[i], chain, cfg.max_nodes)
+        # nodes are in pop order with non-increasing probabilities: a stream's share of the window is a prefix of its tree
+        demands = [Demand(t.probabilities()) for t in trees]
+        alloc = allocate(demands, self.window_rows)
+        trees = [t.prefix(min(n, cfg.max_nodes, 63)) for t, n in zip(trees, alloc)]
+        t1 = time.perf_counter_ns()
+        reqs = [TreeRequest(s.slot, [s.tokens[-1]] + t.tokens, [-1] + [p + 1 for p in t.parents], len(s.tokens) - 1) for s, t in zip(active, trees)]
+        cand = min(64, max(s.req.sampling.candidate_count(self.backend.vocab_size) for s in active))
+        rows = self.backend.step_tree(reqs, cand)
+        self._check_backend()
+        t2 = time.perf_counter_ns()
+        if len(rows) != len(reqs) or any(len(r) != len(q.tokens) for r, q in zip(rows, reqs)):
+            raise BackendError("backend returned a tree window of the wrong shape", fatal=False)
+        self.counters["rounds"] += 1
+        self.counters["tree_rounds"] = self.counters.get("tree_rounds", 0) + 1
+        self.counters["rows"] += sum(len(q.tokens) for q in reqs)
+        self.counters["round_streams"] = self.counters.get("round_streams", 0) + len(reqs)
+        self.counters["round_draft_streams"] = self.counters.get("round_draft_streams", 0) + sum(1 for t in trees if len(t))
+        for s, t, q, out in zip(active, trees, reqs, rows):
+            base = len(s.tokens)
+            depth = q.depths()
+            try:
+                # row r's sample is the token at index base + depth(r): the keyed sampler draws it for that position
+                samples = [choose(o.values, o.ids, base + depth[r], s.req.sampling) for r, o in enumerate(out)]
+            except SamplingError as e:
+                self._finish(s, "error", message=f"sampling failed: {e}")
+                continue
+            path, committed = accept_tree(t, samples)
+            s.rounds += 1
+            a = len(path)
+            if len(t):
+                deepest = max(t.depth)
+                sp = self.spec_pos
+                for j in range(min(deepest, len(sp["offered"]))):
+                    sp["offered"][j] += 1
+                    sp["reached"][j] += 1 if j <= a else 0
+                    sp["accepted"][j] += 1 if j < a else 0
+                s.stats.update(deepest, a)
+                s.drafted += len(t)
+                s.accepted += a
+                self.counters["drafted"] += len(t)
+                self.counters["accepted"] += a
+                self.counters["tree_nodes"] = self.counters.get("tree_nodes", 0) + len(t)
+                self.counters["tree_depth_kept"] = self.counters.get("tree_depth_kept", 0) + a
+            else:
+                s.stats.relax()
+            emitted, reason = self._emit(s, committed)
+            if reason is not None:
+                self._finish(s, reason)
+            else:
+                # the rows kept are the anchor and the accepted nodes whose tokens were emitted (a forced token ends the list early)
+                self.backend.commit_path(s.slot, [n + 1 for n in path[:len(emitted) - 1]])
         self.phase_ns["draft"] += t1 - t0
         self.phase_ns["verify"] += t2 - t1
         self.phase_ns["commit"] += time.perf_counter_ns() - t2

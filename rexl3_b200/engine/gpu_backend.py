@@ -79,6 +79,32 @@ class DenseGpuBackend(Backend):
             self.d_draft_ids = torch.zeros(self.DK, self.max_slots, dtype=torch.int32, device=dev)
             self.d_draft_vals = torch.zeros(self.DK, self.max_slots, dtype=torch.float32, device=dev)
             self.h_draft_ids = torch.zeros(self.DK, self.max_slots, dtype=torch.int32).pin_memory()
+        # tree windows: per row the anchor's position and the private page table; the per-layer row copies; the accepted paths' row copies
+        from ..ops import kernels as _K
+        self.VBT_W = _K.attn_vbt_width()
+        self.h_tree_base = torch.zeros(R, dtype=torch.int32).pin_memory()
+        self.d_tree_base = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.h_vbt = torch.zeros(R, self.VBT_W, dtype=torch.int32).pin_memory()
+        self.d_vbt = torch.zeros(R, self.VBT_W, dtype=torch.int32, device=dev)
+        self.h_spread = torch.zeros(4096, 3, dtype=torch.int32).pin_memory()
+        self.d_spread = torch.zeros(4096, 3, dtype=torch.int32, device=dev)
+        self.h_moves = torch.zeros(256, 3, dtype=torch.int32).pin_memory()
+        self.d_moves = torch.zeros(256, 3, dtype=torch.int32, device=dev)
+        self.moves = []                                        # (source slot, destination slot, rows) not yet applied on the device
+        self.tree_p0 = [0] * self.max_slots
+        self.tree_parents = [None] * self.max_slots
+        self.tree_slots = [None] * self.max_slots              # slot of each row of the slot's last tree window
+        self.tree_priv = [[] for _ in range(self.max_slots)]   # private pages of the slot's last tree window
+        self._tree_n = 0                                       # > 0 while a tree window runs: row copies per layer (padded)
+        self.tree_windows = 0
+        self.tree_moves = 0
+        self.tree_copies = 0
+        self.LAT_K = 4                                         # candidates per level the self-draft chain offers (its lattice)
+        if self.self_draft:
+            self.d_lat_ids = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.int32, device=dev)
+            self.d_lat_vals = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.float32, device=dev)
+            self.h_lat_ids = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.int32).pin_memory()
+            self.h_lat_vals = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.float32).pin_memory()
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.graph_replays = 0
@@ -120,7 +146,21 @@ class DenseGpuBackend(Backend):
         self.bt_dirty = True
         self.bt_dirty_slots.add(slot)
 
+    def _flush_moves(self) -> None:
+        """Applies the row moves that `commit_path` queued (accepted tree nodes to their positions), in order, before anything reads the
+        caches again; more than the staging array holds go in several launches."""
+        while self.moves:
+            part, self.moves = self.moves[:256], self.moves[256:]
+            self._host_writable()
+            self.h_moves[:len(part)] = torch.tensor(part, dtype=torch.int32)
+            self.d_moves[:len(part)].copy_(self.h_moves[:len(part)], non_blocking=True)
+            self._uploaded()
+            self.h2d_bytes += len(part) * 12
+            self.m.move_kv_rows(self.d_moves, len(part))
+            self.tree_moves += len(part)
+
     def _sync_bt(self) -> None:
+        self._flush_moves()
         if self.bt_dirty:
             self.d_bt.copy_(self.h_bt, non_blocking=True)
             self._uploaded()
@@ -244,6 +284,149 @@ class DenseGpuBackend(Backend):
             out.append(rows[k:k + len(r.tokens)])
             k += len(r.tokens)
         return out
+
+    # ------------------------------------------------------------------ tree windows
+    def supports_trees(self) -> bool:
+        """Tree windows run on one rank (the tree arrays are not announced to a group), without the multi-token-prediction block (its
+        lagged rows follow chain positions) and on a model whose caches the row copies handle."""
+        return (type(self)._announce_window is DenseGpuBackend._announce_window and type(self).step is DenseGpuBackend.step and not self.mtp_draft
+                and self.m.supports_trees())
+
+    def _drop_private(self, slot: int) -> None:
+        if self.tree_priv[slot]:
+            self.pool.release(self.tree_priv[slot])
+            self.tree_priv[slot] = []
+
+    def step_tree(self, reqs, candidates):
+        """One verify window of draft trees (reference crates/engine/src/lib.rs:212-432 step_tree; crates/cuda/csrc/attention.cu:443).
+
+        Row i of a request stands at position p0 + depth(i).  The nodes of the tree's first chain (row i at depth i, parent i - 1) use the
+        sequence's own slots, as a chain window's drafts do.  Every other node gets private pages for the page(s) its path lies in: its own
+        K / V rows are written there at its position, and in every layer the committed rows of that page and the node's ancestors are copied
+        beside them, so that the node's view of the cache is what a serial run over its path would hold.  The attention kernel reads the
+        chunks below the tree through the sequence's block table, shared by all of its rows, and the rest through each row's private table.
+        Row outputs therefore equal, bit for bit, those of one-row steps along the row's path."""
+        m = self.m
+        if not self.supports_trees():
+            raise BackendError("this backend runs no tree windows", fatal=False)
+        VW, CH = self.VBT_W, self.VBT_W // 2 * PAGE             # private-table width (pages), keys per attention chunk
+        self._host_writable()
+        h = self.h_rows.numpy()
+        hb, hv, hs = self.h_tree_base.numpy(), self.h_vbt.numpy(), self.h_spread.numpy()
+        r0, ns, deepest = 0, 0, 0
+        for r in reqs:
+            n, p0, slot = len(r.tokens), r.first_position, r.slot
+            if p0 != self.len[slot]:
+                raise BackendError(f"tree window at {p0} but slot {slot} holds {self.len[slot]} tokens", fatal=False)
+            if n > 64 or r.parents[0] != -1 or any(not 0 <= r.parents[i] < i for i in range(1, n)):
+                raise BackendError("a tree window holds at most 64 rows per sequence, parents before children", fatal=False)
+            if r0 + n > self.max_rows:
+                raise BackendError(f"window of more than {self.max_rows} rows", fatal=False)
+            self._drop_private(slot)
+            depth, spine = [0] * n, [True] * n
+            for i in range(1, n):
+                depth[i] = depth[r.parents[i]] + 1
+                spine[i] = r.parents[i] == i - 1 and spine[i - 1]
+            self._ensure(slot, p0 + max(depth) + 1)
+            self._host_writable()
+            pages = self.pages[slot]
+            first_pi = (p0 + 1) // PAGE                            # the page the tree's first draft position lies in
+            c0 = (p0 + 1) // CH * (CH // PAGE)                     # page index that entry 0 of a private table stands for
+            row_slot, priv = [0] * n, [None] * n
+            for i in range(n):
+                P = p0 + depth[i]
+                if spine[i]:
+                    row_slot[i] = pages[P // PAGE] * PAGE + P % PAGE
+                    continue
+                got = self.pool.alloc(P // PAGE - first_pi + 1)
+                if got is None:
+                    self._drop_private(slot)
+                    raise BackendError("KV page pool exhausted (private pages of a tree window)", fatal=False)
+                self.tree_priv[slot].extend(got)
+                priv[i] = {first_pi + j: pg for j, pg in enumerate(got)}
+                row_slot[i] = priv[i][P // PAGE] * PAGE + P % PAGE
+            for i in range(n):
+                k = r0 + i
+                for j in range(VW):
+                    pi = c0 + j
+                    hv[k, j] = priv[i][pi] if (priv[i] is not None and pi in priv[i]) else (pages[pi] if pi < len(pages) else 0)
+                if priv[i] is None:
+                    continue
+                # private pages: the committed rows (and the anchor) of the page the first draft position lies in, then the ancestors
+                if (p0 + 1) % PAGE != 0:
+                    if ns >= hs.shape[0]:
+                        raise BackendError("tree window: too many row copies", fatal=False)
+                    hs[ns] = (pages[first_pi] * PAGE, priv[i][first_pi] * PAGE, p0 % PAGE + 1)
+                    ns += 1
+                a = r.parents[i]
+                while a > 0:
+                    P = p0 + depth[a]
+                    if ns >= hs.shape[0]:
+                        raise BackendError("tree window: too many row copies", fatal=False)
+                    hs[ns] = (row_slot[a], priv[i][P // PAGE] * PAGE + P % PAGE, 1)
+                    ns += 1
+                    a = r.parents[a]
+            h[0, r0:r0 + n] = r.tokens
+            h[1, r0:r0 + n] = p0 + np.asarray(depth, dtype=np.int64)
+            h[2, r0:r0 + n] = row_slot
+            h[3, r0:r0 + n] = slot
+            h[4, r0:r0 + n] = p0 + np.asarray(depth, dtype=np.int64) + 1
+            hb[r0:r0 + n] = p0
+            self.pending[slot] = n
+            self.tree_p0[slot], self.tree_parents[slot], self.tree_slots[slot] = p0, list(r.parents), row_slot
+            deepest = max(deepest, p0 + max(depth) + 1)
+            r0 += n
+        M = r0
+        nsb = 64
+        while nsb < ns:
+            nsb *= 2                                               # the copy launch's size is part of the graph key: few distinct sizes
+        hs[ns:nsb] = 0                                             # (a run of 0 rows copies nothing)
+        m.window_seq_rows = max(len(r.tokens) for r in reqs)
+        bucket = min(m.max_ctx_alloc, (deepest + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
+        count = max(1, min(64, candidates))
+        self._upload_rows(M)
+        self.d_tree_base[:M].copy_(self.h_tree_base[:M], non_blocking=True)
+        self.d_vbt[:M].copy_(self.h_vbt[:M], non_blocking=True)
+        self.d_spread[:nsb].copy_(self.h_spread[:nsb], non_blocking=True)
+        self._uploaded()
+        self.h2d_bytes += M * 4 * (1 + VW) + nsb * 12
+        self._sync_bt()
+        self._tree_n = nsb
+        try:
+            self._run_window(M, count, bucket)
+        finally:
+            self._tree_n = 0
+        self.tree_windows += 1
+        self.tree_copies += ns
+        rows = self._download(M, count)
+        self._check()
+        out, k = [], 0
+        for r in reqs:
+            out.append(rows[k:k + len(r.tokens)])
+            k += len(r.tokens)
+        return out
+
+    def commit_path(self, slot, rows):
+        """Keeps the anchor and the path `rows` of the slot's last tree window: the node at window row rows[d - 1] becomes position p0 + d
+        (its K / V rows are copied to that position's slot in every layer before the next forward reads the caches)."""
+        n, parents, p0, row_slot = self.pending[slot], self.tree_parents[slot], self.tree_p0[slot], self.tree_slots[slot]
+        prev = 0
+        for r in rows:
+            if parents is None or not 0 < r < n or parents[r] != prev:
+                raise BackendError(f"commit_path: row {r} does not follow row {prev} in slot {slot}'s last tree window", fatal=False)
+            prev = r
+        pg = self.pages[slot]
+        for d, r in enumerate(rows, 1):
+            P = p0 + d
+            dst = pg[P // PAGE] * PAGE + P % PAGE
+            if row_slot[r] != dst:
+                self.moves.append((row_slot[r], dst, 1))
+        # the private pages go back to the pool now: the queued copies run before the next forward (see _flush_moves), and whoever gets a
+        # page writes it in kernels queued after them
+        self._drop_private(slot)
+        self.len[slot] += 1 + len(rows)
+        self.pending[slot] = 0
+        self.tree_parents[slot] = self.tree_slots[slot] = None
 
     # ------------------------------------------------------------------ multi-token-prediction block: lagged rows and drafts
     def _mtp_after_trunk(self, specs, keep_all: bool, bucket: int | None = None) -> None:
@@ -402,7 +585,7 @@ class DenseGpuBackend(Backend):
         return out
 
     def _graph_key(self, M: int, count: int, bucket: int) -> tuple:
-        return (M, count, bucket, getattr(self.m, "window_seq_rows", 1))
+        return (M, count, bucket, getattr(self.m, "window_seq_rows", 1), self._tree_n)
 
     def _run_window(self, M: int, count: int, bucket: int) -> None:
         if not self.use_graphs:
@@ -422,7 +605,8 @@ class DenseGpuBackend(Backend):
 
     def _window(self, M: int, count: int, bucket: int) -> None:
         d = self.d_rows
-        logits = self.m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, max_ctx=bucket)
+        tree = (self.d_tree_base[:M], self.d_vbt[:M], self.d_spread, self._tree_n) if self._tree_n else None
+        logits = self.m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, max_ctx=bucket, **({"tree": tree} if tree else {}))
         self.m.candidates(logits, count)
 
     def _capture(self, M: int, count: int, bucket: int):
@@ -485,6 +669,8 @@ class DenseGpuBackend(Backend):
         self.pages[slot] = []
         self.len[slot] = 0
         self.pending[slot] = 0
+        self._drop_private(slot)
+        self.tree_parents[slot] = self.tree_slots[slot] = None
         if self.mtp_draft:
             self.mtp_p0[slot], self.mtp_n[slot] = -1, 0
         self._host_writable()
@@ -535,7 +721,9 @@ class DenseGpuBackend(Backend):
             logits = m.forward_rows(ids, d[j, 1, :n], d[j, 2, :n], d[j, 3, :n], d[j, 4, :n], self.d_bt, max_ctx=bucket, n_layers=D)
             if m.cfg.vocab_padded != m.cfg.vocab:
                 logits[:, m.cfg.vocab:] = float("-inf")
-            m.K.topk(logits, 1, m.topk_scratch, self.d_draft_ids[j, :n].view(n, 1), self.d_draft_vals[j, :n].view(n, 1))
+            # the level's LAT_K best candidates (value desc, id asc): the first feeds the next step, all of them form the offer's lattice
+            m.K.topk(logits, self.LAT_K, m.topk_scratch, self.d_lat_ids[j, :n], self.d_lat_vals[j, :n])
+            self.d_draft_ids[j, :n].copy_(self.d_lat_ids[j, :n, 0])
 
     def propose_batch(self, asks):
         if self.mtp_draft and asks:
@@ -580,12 +768,19 @@ class DenseGpuBackend(Backend):
             g.replay()
         else:
             self._draft_chain(n, k, bucket)
-        self.h_draft_ids[:k, :n].copy_(self.d_draft_ids[:k, :n], non_blocking=True)
+        self.h_lat_ids[:k, :n].copy_(self.d_lat_ids[:k, :n], non_blocking=True)
+        self.h_lat_vals[:k, :n].copy_(self.d_lat_vals[:k, :n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        self.d2h_bytes += k * n * 4
+        self.d2h_bytes += k * n * self.LAT_K * 8
         self.draft_steps += k
-        out = self.h_draft_ids.numpy()
-        return {a.slot: DraftOffer([int(out[j, i]) for j in range(min(k, a.max_drafts))]) for i, a in enumerate(asks)}
+        from ..spec.tree import Lattice
+        ids, vals = self.h_lat_ids.numpy(), self.h_lat_vals.numpy()
+        offers = {}
+        for i, a in enumerate(asks):
+            kk = min(k, a.max_drafts)
+            offers[a.slot] = DraftOffer([int(ids[j, i, 0]) for j in range(kk)], [],
+                                        Lattice([ids[j, i].tolist() for j in range(kk)], [vals[j, i].tolist() for j in range(kk)]))
+        return offers
 
     # ------------------------------------------------------------------ prefix cache: pages are shared by refcount
     def prefix_block_tokens(self):
@@ -615,6 +810,7 @@ class DenseGpuBackend(Backend):
         self.pool.release([p for _, p in handles])
 
     def prefix_export(self, handle):
+        self._flush_moves()
         """One page of every layer's K and V cache as bytes ([2 * layers with a cache, n_kv, 64, head_dim] in the cache's own dtype)."""
         m = self.m
         if getattr(m, "k_cache", None) is None:
@@ -656,6 +852,7 @@ class DenseGpuBackend(Backend):
         return ("page", got[0])
 
     def quiesce(self):
+        self._flush_moves()
         torch.cuda.synchronize()
 
     def stats(self):
@@ -663,6 +860,8 @@ class DenseGpuBackend(Backend):
                    free_pages=self.pool.free_blocks())
         if self.mtp_draft:
             out.update(mtp_rows=self.mtp_rows, draft_steps=self.draft_steps)
+        if self.tree_windows:
+            out.update(tree_windows=self.tree_windows, tree_moves=self.tree_moves, tree_copies=self.tree_copies)
         return out
 
 
@@ -846,6 +1045,7 @@ class HybridGpuBackend(DenseGpuBackend):
         self.pool.release([h[1] for h in handles])
 
     def prefix_export(self, handle):
+        self._flush_moves()
         return None
 
     def prefix_import(self, payload):

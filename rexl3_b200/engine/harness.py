@@ -112,8 +112,23 @@ def cached_equals_cold(make_backend, vocab, n=16):
     return _diff("cached_equals_cold", cold, [first[0], second[0]])
 
 
+def trees_equal_serial(make_backend, vocab, n=48):
+    """Tree windows (best-first trees over the drafter's lattice, the copy chain grafted in) commit the serial run's tokens; a backend
+    without tree support passes trivially (its rounds stay chains)."""
+    from .core import TreeConfig
+    p = default_prompts(vocab)
+    p.append((p[1][:20] * 6)[:110])
+    serial, _ = _run(make_backend, p, n, spec="none")
+    for nodes in (3, 12):
+        treed, eng = _run(make_backend, p, n, spec="auto", max_drafts=4, trees=TreeConfig(max_nodes=nodes))
+        d = _diff(f"trees_equal_serial[{nodes} nodes]", serial, treed)
+        if d is not None:
+            return d
+    return None
+
+
 ALL = (row_invariance, serial_batched_equals_solo, drafted_equals_serial, chunked_prefill_equals_whole, rollback_equals_replay,
-       cached_equals_cold)
+       cached_equals_cold, trees_equal_serial)
 
 
 def run_all(make_backend, vocab) -> dict:

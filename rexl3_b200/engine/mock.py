@@ -14,6 +14,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from ..sched import BlockPool
+from ..spec.tree import Lattice
 from .backend import Backend, BackendError, DraftOffer, RowOutput
 
 
@@ -28,6 +29,8 @@ class MockOptions:
     fault: str = ""                # "" | window_dependent | chunk_dependent | rollback_leak | prefix_stale
     native_draft: bool = False
     draft_error: float = 0.25      # probability a native draft token is wrong
+    trees: bool = False            # step_tree / commit_path are offered
+    lattice: bool = False          # the native drafter offers four candidates per level (a wrong first one keeps the right one second)
     panic_at_step: int = -1
     fatal_at_step: int = -1
     group_lost_at_step: int = -1   # a fatal error that names a lost rank of a multi-rank group (what a peer wait that ran out reports)
@@ -160,6 +163,45 @@ class MockBackend(Backend):
         self.generated[slot] = self.generated.get(slot, 0) + keep
         ctx.extend(kept)
 
+    def supports_trees(self):
+        return self.o.trees
+
+    def step_tree(self, reqs, candidates):
+        self._tick()
+        out = []
+        total_rows = sum(len(r.tokens) for r in reqs)
+        for r in reqs:
+            ctx = self.ctx.setdefault(r.slot, [])
+            if r.first_position != len(ctx):
+                raise BackendError(f"tree window at {r.first_position} but slot {r.slot} holds {len(ctx)} tokens", fatal=False)
+            if r.parents[0] != -1 or any(not 0 <= r.parents[i] < i for i in range(1, len(r.tokens))):
+                raise BackendError("tree rows must follow their parents", fatal=False)
+            self._ensure_blocks(r.slot, len(ctx) + len(r.tokens))
+            self.pending[r.slot] = (list(r.tokens), list(r.parents))
+            paths, rows = [], []
+            for j in range(len(r.tokens)):
+                paths.append((paths[r.parents[j]] if j else []) + [r.tokens[j]])
+                salt = total_rows if self.o.fault == "window_dependent" else 0
+                row = self._row(ctx + paths[j] + self.leak.get(r.slot, []), candidates, salt)
+                if self.o.eos >= 0 and self.generated.get(r.slot, 0) + len(paths[j]) - 1 >= self.o.eos_after:
+                    row.ids[0] = self.o.eos
+                rows.append(row)
+            out.append(rows)
+        return out
+
+    def commit_path(self, slot, rows):
+        toks, parents = self.pending.pop(slot)
+        prev = 0
+        for r in rows:
+            if parents[r] != prev:
+                raise BackendError(f"commit_path: row {r} does not follow row {prev}", fatal=False)
+            prev = r
+        kept = [toks[0]] + [toks[r] for r in rows]
+        if self.o.fault == "rollback_leak" and len(toks) > len(kept):
+            self.leak[slot] = [next(toks[i] for i in range(1, len(toks)) if i not in rows)]
+        self.generated[slot] = self.generated.get(slot, 0) + len(kept)
+        self.ctx[slot].extend(kept)
+
     def release(self, slot):
         self.ctx.pop(slot, None)
         self.pending.pop(slot, None)
@@ -180,14 +222,22 @@ class MockBackend(Backend):
         out = {}
         for a in asks:
             ctx, toks = list(a.context), []
+            lat_ids, lat_val = [], []
             for j in range(a.max_drafts):
                 row = self._row(ctx, 4)
                 t = int(row.ids[0])
                 if (_h(struct.pack("<qq", len(ctx), t)) % 1000) / 1000.0 < self.o.draft_error:
                     t = (t + 1) % self.o.vocab
                 toks.append(t)
-                ctx.append(t)
-            out[a.slot] = DraftOffer(toks, [0.7] * len(toks))
+                if self.o.lattice:
+                    # candidates of this level: the drafter's pick first, then the model's own order; deeper levels follow the model's pick
+                    rest = [int(x) for x in row.ids[:4] if int(x) != t]
+                    lat_ids.append(([t] + rest)[:4])
+                    lat_val.append([float(x) for x in row.values[:4]])
+                    ctx.append(int(row.ids[0]))
+                else:
+                    ctx.append(t)
+            out[a.slot] = DraftOffer(toks, [0.7] * len(toks), Lattice(lat_ids, lat_val) if self.o.lattice else None)
         return out
 
     # prefix cache: blocks are shared by refcount

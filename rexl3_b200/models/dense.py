@@ -379,6 +379,8 @@ class DenseGPU:
         # int32 [rows, 3] (T, H, W positions) for the next forward of a model whose config has `mrope_sections`; None = text rows, where
         # the three axes equal `positions` and plain RoPE gives the same bits
         self.pos3 = None
+        self.tree = None               # (tree_base, vbt, moves, n_moves) while a forward runs a verify window of draft trees
+        self._kv_ptrs = None
         self.device = device
         self.mtp = None                # the multi-token-prediction block's tensors (config.mtp), set by the loaders of the dense family
         self.interventions = {}        # layer -> (alpha, orthonormal basis f32 [r, d]) runtime overlays (set_interventions)
@@ -607,9 +609,15 @@ class DenseGPU:
                           self.inv_freq, slots, q, self.k_cache[li], self.v_cache[li], ksc, None if self.kv_amax is None else self.kv_amax[li],
                           pos3=self.pos3, mrope_sections=getattr(cfg, "mrope_sections", None), kv_tscale=kts, q4=q4)
         if prefill is None:
+            vbt = None
+            if self.tree is not None:
+                # this layer's K / V rows of the window are written: copy what each node's private pages must hold (the committed rows of the
+                # page its path starts in, and its ancestors at their positions)
+                vbt = self.tree[1]
+                K.kv_move_rows(self._kv_ptr_table()[2 * li:2 * li + 2], self._kv_row_bytes(), cfg.n_kv, self.tree[2], self.tree[3])
             K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
                           max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc, max_seq_rows=self.window_seq_rows,
-                          plan=self.attn_plan, kv_tscale=kts, q4=q4)
+                          plan=self.attn_plan, kv_tscale=kts, q4=q4, vbt=vbt)
         else:
             ao = self.attn_out[:M]
             K.attn_prefill(self.tk[li], self.tv[li], q, block_table, prefill["seq_ids"], prefill["q_start"], prefill["q_len"], prefill["pos0"],
@@ -667,8 +675,16 @@ class DenseGPU:
             return e.value
 
     def forward_phases(self, ids, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, logit_rows=None, max_ctx=None, want_logits=True,
-                       n_layers=None, embed_rows=None, pos3=None):
+                       n_layers=None, embed_rows=None, pos3=None, tree=None):
         """Run all layers over M rows.
+
+        tree: (tree_base int32 [M], vbt int32 [M, attn_vbt_width()], moves int32 [n, 3], n) for a verify window of draft trees (decode path,
+        bf16 cache).  A sequence's rows are its tree's nodes (the anchor first); row r stands at `positions[r]` = tree_base + depth, is written
+        to `slots[r]` (its true slot when the node's path is the tree's first chain, else that position's row of a private page), and
+        ctx_len = positions + 1.  vbt[r] lists the pages that hold the row's view of positions from chunk (tree_base + 1) // 256 on: the
+        sequence's pages, with private pages where the row's own path lies; `moves` (see ops.kernels.kv_move_rows) fill those private pages in
+        every layer once the layer's K / V rows are written.  Each row then attends to exactly the keys, at the positions, of a serial run
+        over its path, so its logits are that run's bits.  `move_kv_rows` afterwards brings the accepted path's rows to their true slots.
 
         embed_rows: (int64 index tensor [n], bf16 [n, d_model]) - rows whose token embedding is replaced (image tokens encoded by a vision
         tower).  pos3: int32 [M, 3] (T, H, W positions) for a config with `mrope_sections`; None = text rows (all axes = positions).
@@ -691,13 +707,16 @@ class DenseGPU:
         q = self.q[:M]
         scale = 1.0 / math.sqrt(cfg.head_dim)
         self._begin_forward()
+        if tree is not None and (prefill is not None or not self.supports_trees() or self.attn_plan is None):
+            raise ValueError("a tree window runs on the decode path of a model with a bf16 KV cache and attention in every layer")
         if prefill is None and self.attn_plan is not None:
             # one plan of the window (row blocks and work items of the persistent attention kernel) serves every layer
-            K.attn_plan(row_seq, ctx_len, cfg.n_q, cfg.n_kv, self.window_seq_rows, self.attn_plan)
+            K.attn_plan(row_seq, ctx_len, cfg.n_q, cfg.n_kv, self.window_seq_rows, self.attn_plan, tree_base=None if tree is None else tree[0])
         K.embed(ids, self.embed, h)
         if embed_rows is not None:
             h.index_copy_(0, embed_rows[0], embed_rows[1].to(h.dtype))
         self.pos3 = pos3
+        self.tree = tree
         L0 = self.layers[0]
         if L0["qkv"].suh is not None:          # (split projections rotate per part inside _linear)
             K.norm_rot_in(h, L0["attn_norm"], cfg.eps, L0["qkv"].suh, xr_d)
@@ -707,6 +726,7 @@ class DenseGPU:
             s = self._mixer(li, L, M, cls, xr_d, xr_a, q, positions, slots, row_seq, ctx_len, block_table, prefill, max_ctx, scale)
             nn_, ns_ = (self.layers[li + 1]["attn_norm"], self.layers[li + 1]["qkv"].suh) if li + 1 < nl else (self.final_norm, self.lm_head.suh)
             yield from self._ffn_phases(li, L, M, cls, s, h, xr_d, xr_f, nn_, ns_)
+        self.tree = None
         if not want_logits:
             return None
         if logit_rows is not None:
@@ -719,6 +739,25 @@ class DenseGPU:
         logits = self.logits[:R]
         K.finish_store(self.part, s, R, self.lm_head, logits)
         return logits
+
+    def supports_trees(self) -> bool:
+        """Tree windows need every layer's token mixer to be the paged attention of this class (a recurrent mixer has no per-node state) and a
+        bf16 cache (the tree mask lives in the bf16 decode kernel)."""
+        return (type(self)._mixer is DenseGPU._mixer and not (self.kv_fp8 or self.kv_i8 or self.kv_q4) and all(c is not None for c in self.k_cache))
+
+    def _kv_ptr_table(self):
+        """int64 device tensor [2 * layers]: the K and V cache addresses, layer by layer."""
+        if self._kv_ptrs is None:
+            self._kv_ptrs = torch.tensor([c.data_ptr() for kv in zip(self.k_cache, self.v_cache) for c in kv], dtype=torch.int64, device=self.device)
+        return self._kv_ptrs
+
+    def _kv_row_bytes(self) -> int:
+        return self.k_cache[0].shape[-1] * self.k_cache[0].element_size()
+
+    def move_kv_rows(self, moves, n_moves: int) -> None:
+        """moves: int32 device tensor [>= n_moves, 3] of (source slot, destination slot, rows), applied to the K and V caches of every layer
+        in one launch: the accepted path of a tree window goes from its nodes' slots to its positions."""
+        self.K.kv_move_rows(self._kv_ptr_table(), self._kv_row_bytes(), self.cfg.n_kv, moves, n_moves)
 
     def mtp_forward(self, ids_next, hidden, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, max_ctx=None, want_logits=True,
                     logit_rows=None):

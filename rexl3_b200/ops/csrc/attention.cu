@@ -387,14 +387,25 @@ __host__ __device__ constexpr int dec_smem_bytes(int hd, bool fp8, int mt) { ret
 // [last, d1 .. dk] of a sequence as adjacent rows) times the G query heads of one KV head, so the sequence's K / V chunk is read once per RB
 // rows instead of once per row (the reference packs RBLK * GRP = 48 (row, head) pairs the same way, crates/cuda/csrc/attention.cu:42-50).
 // The plan is a function of row_seq and ctx_len only, so one plan serves every layer of a forward.  Layout (int32):
-//   [0] work items in total   [1] blocks   [2] RB   [3] n_kv   then, from PLAN_HEAD on, four arrays of PLAN_MAX_ROWS (+1) entries:
-//   first row of block b | rows in block b | chunks of block b (from the largest context among its rows) | items before block b (prefix)
-// A work item is (block, chunk, kv head): item = prefix[b] + chunk * n_kv + kvh.
+//   [0] work items in total   [1] blocks   [2] RB   [3] n_kv   then, from PLAN_HEAD on, six arrays of PLAN_MAX_ROWS (+1) entries:
+//   first row of block b | rows in block b | chunks of block b (from the largest context among its rows) | items before block b (prefix) |
+//   sequence of block b (its block-table row; -1 - r = row r of the private table) | first chunk of block b
+// A work item is (block, chunk, kv head): item = prefix[b] + (chunk - first chunk) * n_kv + kvh.
+//
+// Tree windows (tree_base != nullptr).  A sequence's rows are the nodes of a draft tree: row r stands at position ctx_len[r] - 1 =
+// tree_base[r] + depth and must see the committed keys 0 .. tree_base[r] plus ITS OWN ancestors at positions tree_base + 1 .. .  The chunks that
+// end at or before tree_base are the same for every node: they are planned as shared blocks over the sequence's block-table row, as in a
+// chain window.  The chunks from (tree_base + 1) / DEC_CHUNK on are planned once per row over that row's PRIVATE table (vbt: VBT_W page ids,
+// the first one standing for page index first chunk * 4), in which the caller put the pages that hold the row's own path at its true
+// positions.  So every (row, chunk) partial is computed over exactly the keys, at exactly the positions, of the serial run that feeds the
+// path's tokens one by one, and the bits are the serial run's.  (The reference keeps ancestors' K / V in node buffers for the same end,
+// crates/cuda/csrc/attention.cu:443.)
 constexpr int PLAN_MAX_ROWS = 1024, PLAN_HEAD = 8;
-constexpr int PLAN_INTS = PLAN_HEAD + 4 * PLAN_MAX_ROWS + 8;
+constexpr int PLAN_INTS = PLAN_HEAD + 6 * PLAN_MAX_ROWS + 8;
+constexpr int VBT_W = 2 * (DEC_CHUNK / PAGE);     // a tree's nodes span at most 64 positions: two chunks
 
 __global__ void __launch_bounds__(256) attn_plan_kernel(const int* __restrict__ row_seq, const int* __restrict__ ctx_len, int rows, int RB, int n_kv,
-                                                       int* __restrict__ plan) {
+                                                       int* __restrict__ plan, const int* __restrict__ tree_base) {
   pdl_launch();
   pdl_wait();
   __shared__ int s_seq[PLAN_MAX_ROWS], s_ctx[PLAN_MAX_ROWS];
@@ -412,15 +423,28 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const int* __restrict__ 
   int* blk_n = blk_row + PLAN_MAX_ROWS;
   int* blk_nch = blk_n + PLAN_MAX_ROWS;
   int* prefix = blk_nch + PLAN_MAX_ROWS;
+  int* blk_seq = prefix + PLAN_MAX_ROWS + 1;
+  int* blk_c0 = blk_seq + PLAN_MAX_ROWS;
   int nb = 0, items = 0;
   for (int r = 0; r < rows; ++r) {
     if (!s_lead[r]) continue;
     int n = 1, cmax = s_ctx[r];
     while (n < RB && r + n < rows && s_seq[r + n] == s_seq[r]) { cmax = max(cmax, s_ctx[r + n]); ++n; }
-    const int nch = (cmax + DEC_CHUNK - 1) / DEC_CHUNK;
-    blk_row[nb] = r; blk_n[nb] = n; blk_nch[nb] = nch; prefix[nb] = items;
+    // tree window: the shared block covers the chunks below the tree (every row of a sequence has the same tree_base)
+    const int nch = tree_base != nullptr ? (tree_base[r] + 1) / DEC_CHUNK : (cmax + DEC_CHUNK - 1) / DEC_CHUNK;
+    if (nch == 0) continue;
+    blk_row[nb] = r; blk_n[nb] = n; blk_nch[nb] = nch; prefix[nb] = items; blk_seq[nb] = s_seq[r]; blk_c0[nb] = 0;
     items += nch * n_kv;
     ++nb;
+  }
+  if (tree_base != nullptr) {
+    for (int r = 0; r < rows; ++r) {
+      const int c0 = (tree_base[r] + 1) / DEC_CHUNK, nch = (s_ctx[r] + DEC_CHUNK - 1) / DEC_CHUNK - c0;
+      if (nch <= 0) continue;
+      blk_row[nb] = r; blk_n[nb] = 1; blk_nch[nb] = nch; prefix[nb] = items; blk_seq[nb] = -1 - r; blk_c0[nb] = c0;
+      items += nch * n_kv;
+      ++nb;
+    }
   }
   prefix[nb] = items;
   plan[0] = items; plan[1] = nb; plan[2] = RB; plan[3] = n_kv;
@@ -440,7 +464,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, const uint16_t* __restrict__ q,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ ctx_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_q, int n_kv, int max_chunks, float scale_log2_in, int* status,
-                   const float* __restrict__ kv_scale, const int* __restrict__ plan, const float* __restrict__ k_ts, const float* __restrict__ v_ts) {
+                   const float* __restrict__ kv_scale, const int* __restrict__ plan, const float* __restrict__ k_ts, const float* __restrict__ v_ts,
+                   const int* __restrict__ vbt) {
   static_assert(!I8 || FP8, "the int8 cache uses the byte-page path");
   pdl_launch();
   pdl_wait();
@@ -459,6 +484,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
   const int* blk_row = plan + PLAN_HEAD;
   const int* blk_n = blk_row + PLAN_MAX_ROWS;
   const int* prefix = blk_n + 2 * PLAN_MAX_ROWS;
+  const int* blk_seq = prefix + PLAN_MAX_ROWS + 1;
+  const int* blk_c0 = blk_seq + PLAN_MAX_ROWS;
   if ((int)blockIdx.x >= total) return;
   if (threadIdx.x == 0) {
     for (int i = 0; i < KV_STAGES; ++i) mbar_init(&bars[i], 1);
@@ -474,8 +501,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
       if (prefix[mid] <= item) lo = mid; else hi = mid - 1;
     }
     const int local = item - prefix[lo];
-    const int row = blk_row[lo], nblk = blk_n[lo], kvh = local % n_kv, chunk = local / n_kv;
-    const int seq = row_seq[row];
+    const int row = blk_row[lo], nblk = blk_n[lo], kvh = local % n_kv, chunk = blk_c0[lo] + local / n_kv;
+    const int seq = blk_seq[lo];
     const float scale_log2 = (FP8 && !I8) ? scale_log2_in * kv_scale[kvh] : scale_log2_in;     // K was stored as k / k_scale
     const float v_scale = (FP8 && !I8) ? kv_scale[n_kv + kvh] : 1.f;
     int ctx_max = 0;
@@ -484,7 +511,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant
     const int k_end_max = min(ctx_max, k_begin + DEC_CHUNK);
     const int npages = (k_end_max - k_begin + PAGE - 1) / PAGE;
     const int ntiles = (nblk * G + 15) >> 4;            // tiles that hold a live row
-    const int* bt = block_table + (size_t)seq * max_blocks;
+    // a tree row's private table starts at the page index of its block's first chunk
+    const int* bt = seq >= 0 ? block_table + (size_t)seq * max_blocks : vbt + (size_t)(-1 - seq) * VBT_W - blk_c0[lo] * (DEC_CHUNK / PAGE);
     if (threadIdx.x == 0) {
       fence_proxy_async();                           // the previous item's merge wrote this memory with plain stores
       for (int p = 0; p < npages && p < KV_STAGES - 1; ++p) {
@@ -916,18 +944,22 @@ RX_API int rx_attn_plan_ints() { return PLAN_INTS; }
 
 // The window plan of a decode / verify step (see attn_plan_kernel): computed once per forward from row_seq and ctx_len and handed to every
 // layer's rx_attn_decode call of that forward (same rows, n_q, n_kv and max_seq_rows).
-RX_API int rx_attn_plan(const void* row_seq, const void* ctx_len, int rows, int n_q, int n_kv, int max_seq_rows, void* plan, void* stream) {
+// tree_base: nullptr for a chain window; int32 [rows] for a tree window (see attn_plan_kernel), whose plan holds up to two blocks per row.
+RX_API int rx_attn_plan(const void* row_seq, const void* ctx_len, int rows, int n_q, int n_kv, int max_seq_rows, void* plan, void* stream,
+                        const void* tree_base) {
   if (rows <= 0 || rows > PLAN_MAX_ROWS || n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > 16) return (int)cudaErrorInvalidValue;
+  if (tree_base != nullptr && 2 * rows > PLAN_MAX_ROWS) return (int)cudaErrorInvalidValue;
   const int G = n_q / n_kv;
   rx::launch(attn_plan_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, (const int*)row_seq, (const int*)ctx_len, rows,
-             dec_rows_per_block(dec_tiles(max_seq_rows, G), G), n_kv, (int*)plan);
+             dec_rows_per_block(dec_tiles(max_seq_rows, G), G), n_kv, (int*)plan, (const int*)tree_base);
   return (int)cudaGetLastError();
 }
+RX_API int rx_attn_vbt_width() { return VBT_W; }
 
 template <int HD, bool FP8, int MT, int I8>
 static int launch_decode_kernel(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                                 const int* ctx_len, float* part_o, float* part_ml, int rows, int n_q, int n_kv, int mc, float scale, int* status,
-                                cudaStream_t st, const float* kv_scale, const int* plan, const float* k_ts, const float* v_ts) {
+                                cudaStream_t st, const float* kv_scale, const int* plan, const float* k_ts, const float* v_ts, const int* vbt) {
   constexpr int smem = dec_smem_bytes(HD, FP8, MT);
   static bool configured = false;
   if (!configured) {
@@ -939,7 +971,7 @@ static int launch_decode_kernel(const CUtensorMap* tk, const CUtensorMap* tv, co
   const long long bound = (long long)rows * n_kv * mc;
   const int grid = (int)(bound < 2 * sm_count() ? bound : 2 * sm_count());
   rx::launch(attn_decode_kernel<HD, FP8, MT, I8>, dim3(grid), dim3(ATT_THREADS), smem, st, *tk, *tv, (const uint16_t*)q, bt, max_blocks, row_seq,
-             ctx_len, part_o, part_ml, n_q, n_kv, mc, scale * 1.4426950408889634f, status, kv_scale, plan, k_ts, v_ts);
+             ctx_len, part_o, part_ml, n_q, n_kv, mc, scale * 1.4426950408889634f, status, kv_scale, plan, k_ts, v_ts, vbt);
   return (int)cudaGetLastError();
 }
 
@@ -947,7 +979,7 @@ template <int HD, bool FP8, int I8 = 0>
 static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const void* q, const int* bt, int max_blocks, const int* row_seq,
                          const int* ctx_len, float* scratch, int rows, int n_q, int n_kv, int max_ctx, float scale, const void* suh, void* xr,
                          void* out_bf16, int* status, cudaStream_t st, const float* kv_scale, int max_seq_rows, const int* plan,
-                         const float* k_ts = nullptr, const float* v_ts = nullptr) {
+                         const float* k_ts = nullptr, const float* v_ts = nullptr, const int* vbt = nullptr) {
   const int mc = (max_ctx + DEC_CHUNK - 1) / DEC_CHUNK;
   int* own_plan = (int*)scratch;                    // the head of the scratch holds a plan for callers that bring none
   float* part_o = scratch + PLAN_INTS;
@@ -956,11 +988,11 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
   const int G = n_q / n_kv;
   const int tiles = dec_tiles(max_seq_rows, G);
   if (plan == nullptr) {
-    rx::launch(attn_plan_kernel, dim3(1), dim3(256), 0, st, row_seq, ctx_len, rows, dec_rows_per_block(tiles, G), n_kv, own_plan);
+    rx::launch(attn_plan_kernel, dim3(1), dim3(256), 0, st, row_seq, ctx_len, rows, dec_rows_per_block(tiles, G), n_kv, own_plan, (const int*)nullptr);
     plan = own_plan;
   }
   int e;
-#define RX_DEC_T(MT) launch_decode_kernel<HD, FP8, MT, I8>(tk, tv, q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, rows, n_q, n_kv, mc, scale, status, st, kv_scale, plan, k_ts, v_ts)
+#define RX_DEC_T(MT) launch_decode_kernel<HD, FP8, MT, I8>(tk, tv, q, bt, max_blocks, row_seq, ctx_len, part_o, part_ml, rows, n_q, n_kv, mc, scale, status, st, kv_scale, plan, k_ts, v_ts, vbt)
   if (tiles <= 1) e = RX_DEC_T(1);
   else e = RX_DEC_T(2);
 #undef RX_DEC_T
@@ -980,7 +1012,9 @@ static int launch_decode(const CUtensorMap* tk, const CUtensorMap* tv, const voi
 RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q, const void* block_table, int max_blocks, const void* row_seq,
                           const void* ctx_len, void* scratch, int rows, int n_q, int n_kv, int hd, int max_ctx, float scale, const void* suh,
                           void* xr, void* out_bf16, int* status, void* stream, const void* kv_scale, int max_seq_rows, const void* plan,
-                          const void* k_tscale, const void* v_tscale) {
+                          const void* k_tscale, const void* v_tscale, const void* vbt) {
+  // vbt: int32 [rows][rx_attn_vbt_width()], the private page tables of a tree window whose `plan` was made with tree_base; nullptr otherwise
+  if (vbt != nullptr && plan == nullptr) return (int)cudaErrorInvalidValue;
   if (n_q % n_kv != 0 || n_q / n_kv > 16 || (n_q * hd) % 128 != 0 || rows <= 0 || rows > PLAN_MAX_ROWS || max_ctx <= 0) return (int)cudaErrorInvalidValue;
   if ((k_tscale == nullptr) != (v_tscale == nullptr) || (k_tscale != nullptr && kv_scale != nullptr)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
@@ -988,7 +1022,7 @@ RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q,
     // int8 cache: the maps describe byte pages, k_tscale / v_tscale are f32 [pages][n_kv][64] (one power-of-two scale per token and KV head)
 #define RX_DEC8(HDV) launch_decode<HDV, true, 1>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
     (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, nullptr, max_seq_rows, \
-    (const int*)plan, (const float*)k_tscale, (const float*)v_tscale)
+    (const int*)plan, (const float*)k_tscale, (const float*)v_tscale, (const int*)vbt)
     if (hd == 128) return RX_DEC8(128);
     if (hd == 64) return RX_DEC8(64);
 #undef RX_DEC8
@@ -997,11 +1031,36 @@ RX_API int rx_attn_decode(const void* tmap_k, const void* tmap_v, const void* q,
   // kv_scale != nullptr: the maps describe an FP8 cache and kv_scale is f32 [2][n_kv] (K scales, then V scales) of this layer
 #define RX_DEC(HDV, F8) launch_decode<HDV, F8>((const CUtensorMap*)tmap_k, (const CUtensorMap*)tmap_v, q, (const int*)block_table, max_blocks, \
     (const int*)row_seq, (const int*)ctx_len, (float*)scratch, rows, n_q, n_kv, max_ctx, scale, suh, xr, out_bf16, status, st, (const float*)kv_scale, \
-    max_seq_rows, (const int*)plan)
+    max_seq_rows, (const int*)plan, nullptr, nullptr, (const int*)vbt)
   if (hd == 128) return kv_scale ? RX_DEC(128, true) : RX_DEC(128, false);
   if (hd == 64) return kv_scale ? RX_DEC(64, true) : RX_DEC(64, false);
 #undef RX_DEC
   return (int)cudaErrorInvalidValue;
+}
+
+// Copies runs of KV rows inside the paged caches: moves int32 [n_moves][3] = (source slot, destination slot, rows), slot = page * 64 + offset, a
+// run stays inside one page on both sides; tensors = the base addresses of n_tensors caches laid out [pages][n_kv][64][row_bytes].  No
+// destination row of one move may be a source or destination row of another (the moves run in parallel).  Used by tree windows: before a
+// layer's attention the committed rows and the ancestors of each node are copied into the node's private pages, and after the window the
+// accepted path's rows are copied to their positions.
+__global__ void __launch_bounds__(128) kv_move_rows_kernel(const unsigned long long* __restrict__ tensors, int row_bytes, int n_kv, const int* __restrict__ moves) {
+  pdl_launch();
+  pdl_wait();
+  uint8_t* base = (uint8_t*)tensors[blockIdx.z];
+  const int h = blockIdx.y;
+  const int src = moves[3 * blockIdx.x], dst = moves[3 * blockIdx.x + 1], n = moves[3 * blockIdx.x + 2];
+  const uint8_t* sp = base + (((size_t)(src / PAGE) * n_kv + h) * PAGE + src % PAGE) * row_bytes;
+  uint8_t* dp = base + (((size_t)(dst / PAGE) * n_kv + h) * PAGE + dst % PAGE) * row_bytes;
+  for (int c = threadIdx.x * 16; c < n * row_bytes; c += blockDim.x * 16)
+    *reinterpret_cast<uint4*>(dp + c) = *reinterpret_cast<const uint4*>(sp + c);
+}
+
+RX_API int rx_kv_move_rows(const void* tensors, int n_tensors, int row_bytes, int n_kv, const void* moves, int n_moves, void* stream) {
+  if (n_tensors <= 0 || n_tensors > 65535 || n_kv <= 0 || n_kv > 65535 || row_bytes <= 0 || row_bytes % 16 != 0 || n_moves < 0) return (int)cudaErrorInvalidValue;
+  if (n_moves == 0) return 0;
+  rx::launch(kv_move_rows_kernel, dim3(n_moves, n_kv, n_tensors), dim3(128), 0, (cudaStream_t)stream, (const unsigned long long*)tensors, row_bytes, n_kv,
+             (const int*)moves);
+  return (int)cudaGetLastError();
 }
 
 template <int HD, bool FP8, int I8 = 0>

@@ -354,14 +354,16 @@ def attn_decode_scratch(rows: int, n_q: int, hd: int, max_ctx: int, device="cuda
 
 
 def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_len, scratch, n_q, n_kv, hd, max_ctx, scale, suh, xr, out,
-                status, kv_scale=None, max_seq_rows: int = 1, plan=None, kv_tscale=None, q4: bool = False) -> None:
+                status, kv_scale=None, max_seq_rows: int = 1, plan=None, kv_tscale=None, q4: bool = False, vbt=None) -> None:
     """Split-KV decode / verify-window attention.  `max_seq_rows`: the most adjacent rows one sequence has in this window (1 + drafts); it
     picks how many MMA tiles a CTA carries so that a sequence's rows share one pass over its K / V (results do not depend on it).
     `plan`: the window plan from `attn_plan` for these rows and this `max_seq_rows` (one plan serves every layer of a forward); None has
-    the call compute it itself.  `kv_tscale`: (K scales, V scales), f32 [pages, n_kv, 64] each, of an int8 cache."""
+    the call compute it itself.  `kv_tscale`: (K scales, V scales), f32 [pages, n_kv, 64] each, of an int8 cache.
+    `vbt`: the rows' private page tables, int32 [rows, attn_vbt_width()], of a tree window whose plan was made with `tree_base`."""
     kts, vts = kv_tscale if kv_tscale is not None else (None, None)
     rows = q.shape[0]
     L = _lib.load()
+    assert vbt is None or (plan is not None and not q4 and vbt.dtype == torch.int32 and vbt.shape[0] >= rows)
     if q4:      # E2M1 nibble pages (the maps are 64 bytes wide) + E8M0 scale bytes uint8 [pages, n_kv, 64, hd / 32]
         assert hd == 128 and kts is not None and kts.dtype == torch.uint8
         _lib.check(L.rx_attn_decode_q4(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
@@ -373,20 +375,40 @@ def attn_decode(tk: KvTensorMap, tv: KvTensorMap, q, block_table, row_seq, ctx_l
     assert tk.i8 == (kv_tscale is not None), "an int8 cache needs its per-token scales (and only an int8 cache takes them)"
     _lib.check(L.rx_attn_decode(tk.ptr, tv.ptr, q.data_ptr(), block_table.data_ptr(), block_table.shape[1], row_seq.data_ptr(), ctx_len.data_ptr(),
                                 scratch.data_ptr(), rows, n_q, n_kv, hd, max_ctx, scale, _lib.ptr(suh), _lib.ptr(xr), _lib.ptr(out),
-                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), int(max_seq_rows), _lib.ptr(plan), _lib.ptr(kts), _lib.ptr(vts)), "rx_attn_decode")
+                                status.data_ptr(), _lib.stream_ptr(), _lib.ptr(kv_scale), int(max_seq_rows), _lib.ptr(plan), _lib.ptr(kts), _lib.ptr(vts), _lib.ptr(vbt)), "rx_attn_decode")
     _lib.count(2 if plan is not None else 3)
+
+
+def kv_move_rows(tensor_ptrs, row_bytes: int, n_kv: int, moves, n_moves: int) -> None:
+    """Copies runs of cache rows, moves[i] = (source slot, destination slot, rows), in every cache whose base address is in `tensor_ptrs`
+    (int64 device tensor); caches are [pages, n_kv, 64, row_bytes]; a run stays inside one page; no destination row is a source or a
+    destination of another move.  moves: int32 device tensor [>= n_moves, 3]."""
+    if n_moves <= 0:
+        return
+    L = _lib.load()
+    _lib.check(L.rx_kv_move_rows(tensor_ptrs.data_ptr(), tensor_ptrs.numel(), int(row_bytes), int(n_kv), moves.data_ptr(), int(n_moves), _lib.stream_ptr()),
+               "rx_kv_move_rows")
+    _lib.count()
 
 
 def attn_plan_buffer(device) -> torch.Tensor:
     return torch.zeros(_lib.load().rx_attn_plan_ints(), dtype=torch.int32, device=device)
 
 
-def attn_plan(row_seq, ctx_len, n_q: int, n_kv: int, max_seq_rows: int, plan: torch.Tensor) -> None:
+def attn_vbt_width() -> int:
+    return _lib.load().rx_attn_vbt_width()
+
+
+def attn_plan(row_seq, ctx_len, n_q: int, n_kv: int, max_seq_rows: int, plan: torch.Tensor, tree_base=None) -> None:
     """The work plan of a decode / verify window: which adjacent rows of a sequence share a CTA, and the flat (block, chunk, kv head) item
-    list the persistent attention kernel walks.  A function of row_seq and ctx_len only: compute once per forward."""
+    list the persistent attention kernel walks.  A function of row_seq and ctx_len only: compute once per forward.
+    tree_base (int32 [rows]): the window's rows are nodes of draft trees; row r stands at position ctx_len[r] - 1 = tree_base[r] + depth.
+    The chunks that end at or before tree_base are planned over the sequence's block-table row and shared by its rows; the later ones are
+    planned per row over the row's private table (the `vbt` of attn_decode), whose entry 0 stands for page index
+    (tree_base + 1) // chunk * (chunk // 64)."""
     L = _lib.load()
-    _lib.check(L.rx_attn_plan(row_seq.data_ptr(), ctx_len.data_ptr(), row_seq.shape[0], n_q, n_kv, int(max_seq_rows), plan.data_ptr(), _lib.stream_ptr()),
-               "rx_attn_plan")
+    _lib.check(L.rx_attn_plan(row_seq.data_ptr(), ctx_len.data_ptr(), row_seq.shape[0], n_q, n_kv, int(max_seq_rows), plan.data_ptr(), _lib.stream_ptr(),
+                              _lib.ptr(tree_base)), "rx_attn_plan")
     _lib.count()
 
 

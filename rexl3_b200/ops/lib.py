@@ -123,13 +123,15 @@ def _declare(lib):
         "rx_attn_decode_chunk": (c_int, []),
         "rx_attn_decode_scratch_floats": (c_ll, [c_int, c_int, c_int, c_int]),
         "rx_attn_decode": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
-                                   c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void]),
+                                   c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void]),
         "rx_attn_decode_q4": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_f,
                                       c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void]),
+        "rx_attn_vbt_width": (c_int, []),
+        "rx_kv_move_rows": (c_int, [c_void, c_int, c_int, c_int, c_void, c_int, c_void]),
         "rx_attn_prefill_q4": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                        c_int, c_f, c_void, c_void, c_void, c_void]),
         "rx_attn_plan_ints": (c_int, []),
-        "rx_attn_plan": (c_int, [c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_void]),
+        "rx_attn_plan": (c_int, [c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_attn_prefill_tc": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                        c_int, c_f, c_void, c_void, c_int]),
         "rx_attn_prefill": (c_int, [c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,

@@ -44,6 +44,9 @@ def parser() -> argparse.ArgumentParser:
                    help="a runtime overlay directory (intervention.json + direction files): checked against the model at boot, any mismatch refuses")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
+    p.add_argument("--spec-tree", type=int, default=0, metavar="NODES",
+                   help="verify draft trees of up to NODES nodes per stream (best first over the drafter's candidate lattice, the copy chain grafted in) "
+                        "when the backend runs tree windows; 0 = chain windows")
     p.add_argument("--prefix-cache", choices=["on", "off"], default="on")
     p.add_argument("--prefix-cache-mib", type=int, default=4096)
     p.add_argument("--verify-pack", choices=["off", "sizes", "crc", "lock"], default="off",
@@ -94,7 +97,7 @@ def build(args):
             be = MockBackend(opts)
             prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=be.prefix_block_tokens()) if args.prefix_cache == "on" else None
             return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix), arbiter=_arbiter(args))
+                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix), arbiter=_arbiter(args), trees=_trees(args))
         info = {"backend": "mock"}
     else:
         from ..models import dense
@@ -242,7 +245,7 @@ def build(args):
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args, model), device_sampler=args.device_sampler,
-                          spill=_spill_store(args, prefix), arbiter=_arbiter(args))
+                          spill=_spill_store(args, prefix), arbiter=_arbiter(args), trees=_trees(args))
     tok = load_tokenizer(folder, vocab)
     from . import formats
     try:
@@ -314,6 +317,13 @@ def _is_expert_family(cfg) -> bool:
     from ..models import mla as mla_models
     from ..models import moe as moe_models
     return isinstance(cfg, (mla_models.MlaConfig, moe_models.MoEConfig))
+
+
+def _trees(args):
+    if getattr(args, "spec_tree", 0) <= 0 or args.no_drafts:
+        return None
+    from ..engine import TreeConfig
+    return TreeConfig(max_nodes=min(63, args.spec_tree))
 
 
 def _arbiter(args):

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from rexl3_b200 import sched
-from rexl3_b200.engine import BackendError, Engine, MockBackend, MockOptions, Request, StepError, generate, harness
+from rexl3_b200.engine import BackendError, Engine, MockBackend, MockOptions, Request, StepError, TreeConfig, TreeRequest, generate, harness
 from rexl3_b200.sampling import GREEDY, Sampling
 
 
@@ -220,3 +220,53 @@ def test_burst_prefill_serves_short_prompts_first_and_never_starves_a_long_one()
             done_at = step
             break
     assert done_at is not None and done_at <= (3000 // 256 + 1) * 10
+
+
+def test_tree_rounds_commit_the_serial_tokens_and_keep_more_than_chains():
+    """Tree windows on the mock: same tokens as the serial run at every tree size, greedy and sampled; with a drafter whose first candidate
+    is wrong a quarter of the time but whose second is then right, trees keep more drafts per round than chains over the same offers."""
+    p = harness.default_prompts(512)
+    for sampling in (GREEDY, harness.SAMPLING):
+        serial = generate(Engine(MockBackend(MockOptions()), spec="none"), p, 64, sampling)
+        chain = Engine(MockBackend(MockOptions(native_draft=True, lattice=True)), spec="auto", max_drafts=4)
+        assert generate(chain, p, 64, sampling) == serial
+        tree = Engine(MockBackend(MockOptions(native_draft=True, lattice=True, trees=True)), spec="auto", max_drafts=4, trees=TreeConfig(max_nodes=12))
+        assert generate(tree, p, 64, sampling) == serial
+        assert tree.counters["tree_rounds"] == tree.counters["rounds"] > 0
+        assert tree.counters["rounds"] < chain.counters["rounds"], (tree.counters, chain.counters)
+    # the harness check catches a backend whose rejected tree rows leak into the state
+    assert harness.trees_equal_serial(mk(native_draft=True, lattice=True, trees=True), 512) is None
+    assert harness.trees_equal_serial(mk(native_draft=True, lattice=True, trees=True, fault="rollback_leak"), 512) is not None
+
+
+def test_tree_rounds_with_stop_ids_budgets_and_many_streams():
+    """Stop tokens and length limits inside an accepted path end the request at the same token as the serial run; more streams than the
+    window has rows still get their anchors."""
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 512, size=int(n)).tolist() for n in rng.integers(3, 40, size=12)]
+    for kw in (dict(), dict(eos=7, eos_after=9)):
+        serial = generate(Engine(MockBackend(MockOptions(slots=16, **kw)), spec="none"), prompts, 23, GREEDY, stop_ids=(7,))
+        eng = Engine(MockBackend(MockOptions(slots=16, native_draft=True, lattice=True, trees=True, **kw)), spec="auto", max_drafts=4, window_rows=16,
+                     trees=TreeConfig(max_nodes=8))
+        assert generate(eng, prompts, 23, GREEDY, stop_ids=(7,)) == serial
+
+
+def test_mock_tree_window_rows_equal_one_row_steps():
+    """Each row of a tree window returns what a one-row step returns after the tokens on its path; commit_path refuses rows that are no path."""
+    be = MockBackend(MockOptions(trees=True))
+    ctx = [5, 6, 7]
+    be.prefill_slice(0, 0, ctx[:-1], 8, False)
+    q = TreeRequest(0, [7, 11, 12, 13, 14], [-1, 0, 0, 1, 2], 2)
+    assert q.depths() == [0, 1, 1, 2, 2]
+    rows = be.step_tree([q], 8)[0]
+    for r, path in enumerate(([7], [7, 11], [7, 12], [7, 11, 13], [7, 12, 14])):
+        ref = MockBackend(MockOptions())
+        ref.prefill_slice(0, 0, ctx[:-1] + path[:-1], 8, False) if len(ctx[:-1] + path[:-1]) else None
+        from rexl3_b200.engine import RowRequest
+        one = ref.step([RowRequest(0, [path[-1]], len(ctx) - 1 + len(path) - 1)], 8)[0][0]
+        assert (one.ids == rows[r].ids).all() and (one.values == rows[r].values).all()
+    with pytest.raises(BackendError):
+        be.commit_path(0, [1, 4])
+    be.step_tree([q], 8)
+    be.commit_path(0, [2, 4])
+    assert be.ctx[0] == [5, 6, 7, 12, 14]

@@ -25,7 +25,7 @@ def make_backend():
 
 
 @pytest.mark.parametrize("check", ["row_invariance", "serial_batched_equals_solo", "drafted_equals_serial", "chunked_prefill_equals_whole",
-                                   "rollback_equals_replay", "cached_equals_cold"])
+                                   "rollback_equals_replay", "cached_equals_cold", "trees_equal_serial"])
 def test_exactness_on_device(make_backend, check):
     from rexl3_b200.engine import harness
     assert getattr(harness, check)(make_backend, make_backend.vocab) is None
