@@ -23,6 +23,7 @@ def _serial_row(model, ctx, path, count):
     from rexl3_b200.engine import RowRequest
     from rexl3_b200.engine.gpu_backend import DenseGpuBackend
     be = DenseGpuBackend(model, max_slots=8, use_graphs=False)
+    be.pool.alloc(96)          # the backend under test holds the model's first pages: this run keeps to pages 96..
     be.prefill_slice(3, 0, ctx[:-1], count, False)
     out = None
     for j, t in enumerate([ctx[-1]] + path):
