@@ -34,6 +34,9 @@ def main() -> int:
     ap.add_argument("--mtp", action="store_true",
                     help="one GPU, a dense config (--model dense-27b): drafts come from a multi-token-prediction block (random init, so nothing is "
                          "accepted: the run shows what the block's lagged rows and a chain of k drafts cost per round)")
+    ap.add_argument("--tree", type=int, default=0, metavar="NODES",
+                    help="one GPU, self draft: a third run whose verify windows are draft trees of up to NODES nodes per stream, searched best "
+                         "first over the four candidates the draft chain gives per level")
     args = ap.parse_args()
     import dataclasses
     import numpy as np
@@ -52,7 +55,7 @@ def main() -> int:
     B, P, K, W, D = args.batch, args.prompt, args.steps, max(3, args.warmup), args.drafts
     new_tokens = (K + W) * (D + 1) * 2 + 16
     blocks = (P + new_tokens + dense.PAGE - 1) // dense.PAGE + 1
-    pages = (B + 1) * blocks
+    pages = (B + 1) * blocks + 2 * B * args.tree          # a tree node outside the first chain holds up to two private pages for a round
     ctx = comm = None
     if world > 1:
         from ..parallel import runtime as rt
@@ -65,7 +68,7 @@ def main() -> int:
 
     def measure(eps: float) -> dict:
         results = {}
-        for mode in ("none", drafter):
+        for mode in ("none", drafter) + (("tree",) if args.tree > 0 and not args.mtp and world == 1 else ()):
             measure_mode(eps, mode, results)
         return results
 
@@ -77,7 +80,7 @@ def main() -> int:
                                experts=experts, ep=comm)
             if eps != 1.0:
                 model.scale_tail(cfg.draft_layers, eps)
-        inner = DenseGpuBackend(model, max_slots=B + 1, self_draft=(mode == "self"), mtp_draft=(mode == "mtp"))
+        inner = DenseGpuBackend(model, max_slots=B + 1, self_draft=(mode in ("self", "tree")), mtp_draft=(mode == "mtp"))
         if world > 1 and rank != 0:
             follow(inner, ctx.ctrl)
             torch.cuda.synchronize()
@@ -85,7 +88,12 @@ def main() -> int:
             torch.cuda.empty_cache()
             return
         be = LockstepLeader(inner, ctx.ctrl) if world > 1 else inner
-        eng = Engine(be, None, window_rows=B * (D + 1), prefill_chunk=P, spec=mode, max_drafts=D, prefill_policy="serial")
+        if mode == "tree":
+            from ..engine import TreeConfig
+            eng = Engine(be, None, window_rows=min(256, B * (args.tree + 1)), prefill_chunk=P, spec="self", max_drafts=D, prefill_policy="serial",
+                         trees=TreeConfig(max_nodes=args.tree))
+        else:
+            eng = Engine(be, None, window_rows=B * (D + 1), prefill_chunk=P, spec=mode, max_drafts=D, prefill_policy="serial")
         rng = np.random.default_rng(7)
         for i in range(B):
             eng.submit(Request(f"s{i}", rng.integers(0, cfg.vocab, size=P).tolist(), new_tokens, GREEDY))
@@ -113,7 +121,7 @@ def main() -> int:
         results[mode] = dict(tokens_per_s=round(toks / (ms / 1e3), 2), ms_per_round=round(ms / K, 3), tokens=toks,
                              verify_step_ms=round((eng.phase_ns["verify"] - v0) / K / 1e6, 3), drafted=drafted, accepted=accepted,
                              acceptance=round(accepted / drafted, 4) if drafted else None, rows_per_round=(c1["rows"] - c0["rows"]) / K,
-                             prefill_s=round(prefill_s, 2))
+                             prefill_s=round(prefill_s, 2), **({"backend": inner.stats()} if mode == "tree" else {}))
         if world > 1:
             be.stop()
         del eng, be, inner, model
@@ -128,7 +136,10 @@ def main() -> int:
                           "draft": f"mtp block, chain k={D}" if args.mtp else f"self: first {cfg.draft_layers} layers + shared head, chain k={D}",
                           "dtype": f"bf16 activations, EXL3 {cfg.bits} bpw weights", "data": "synthetic (random init; tail_scale multiplies the output scales of o_proj / down_proj above the draft depth)",
                           "runs": [dict(tail_scale=eps, spec_off=r["none"], spec_on=r[drafter],
-                                        speedup=round(r[drafter]["tokens_per_s"] / r["none"]["tokens_per_s"], 3)) for eps, r in runs]}))
+                                        speedup=round(r[drafter]["tokens_per_s"] / r["none"]["tokens_per_s"], 3),
+                                        **({"spec_tree": r["tree"], "tree_nodes": args.tree,
+                                            "tree_speedup": round(r["tree"]["tokens_per_s"] / r["none"]["tokens_per_s"], 3)} if "tree" in r else {}))
+                                   for eps, r in runs]}))
     if world > 1:
         dist.destroy_process_group()
     return 0
