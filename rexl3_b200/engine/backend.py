@@ -39,6 +39,31 @@ class TreeRequest:
 
 
 @dataclass
+class MediaInputs:
+    """What a prompt with images carries beside its tokens (the prompt holds one run of the placeholder token per image).
+    rows: indices of the placeholder tokens in the prompt, ascending; embeds: [len(rows), d_model] rows that replace those tokens'
+    embeddings (a vision tower's output, any float dtype, host or device tensor); pos3: int32 [len(prompt), 3] (T, H, W) positions for a model
+    with M-RoPE sections, or None (plain positions); rope_delta: what decode rows add to their position on every axis (the text after an
+    image continues at 1 + the largest position the image used, which is less than the token count); keys: one content digest per image
+    with (first row index into `rows`, count), from which the prefix cache's block hashes are made."""
+    rows: np.ndarray
+    embeds: object
+    pos3: np.ndarray | None = None
+    rope_delta: int = 0
+    keys: list = field(default_factory=list)      # [(first, count, digest bytes)]
+
+    def hash_tokens(self, prompt: list) -> list:
+        """The prompt with every placeholder replaced by a pseudo-token made from its image's content and the index inside the image: equal
+        block hashes then mean equal text AND equal images (reference crates/sched/src/lib.rs:300-360, image_token / prefix_hashes)."""
+        from ..sched.prefix import image_token
+        out = list(prompt)
+        for first, count, digest in self.keys:
+            for j in range(count):
+                out[int(self.rows[first + j])] = image_token(digest, j)
+        return out
+
+
+@dataclass
 class RowOutput:
     ids: np.ndarray        # uint32 [count], ordered (value desc, id asc)
     values: np.ndarray     # float32 [count]
@@ -121,6 +146,14 @@ class Backend:
     def commit_path(self, slot: int, rows: list) -> None:
         """Keep the anchor and the rows `rows` (a path: each row's parent is the one before, the first row's parent the anchor) of the slot's
         last tree window; every other row never happened."""
+        raise NotImplementedError
+
+    def supports_media(self) -> bool:
+        """True: `set_media` is implemented (prompts whose placeholder rows take a vision tower's embeddings)."""
+        return False
+
+    def set_media(self, slot: int, media) -> None:
+        """The MediaInputs of the prompt that `slot` is about to prefill (None clears); `release` forgets them."""
         raise NotImplementedError
 
     def supports_rollback(self) -> bool:

@@ -42,6 +42,7 @@ class Request:
     think_close_ids: tuple = ()
     reasoning_open: bool = False        # the prompt ends inside the thinking block (the template opened it)
     think_open_ids: tuple = ()          # a generated opening tag also starts the block
+    media: object = None                # backend.MediaInputs: image rows of the prompt (embeddings, positions, content digests)
 
 
 @dataclass
@@ -150,6 +151,13 @@ class Engine:
             raise ValueError("prompt token outside the vocabulary")
         if req.max_new_tokens < 1:
             raise ValueError("max_new_tokens must be at least 1")
+        if req.media is not None:
+            if not getattr(self.backend, "supports_media", lambda: False)():
+                raise ValueError("this backend takes no image inputs")
+            m = req.media
+            if len(m.rows) != len(m.embeds) or (len(m.rows) and (int(m.rows[0]) < 0 or int(m.rows[-1]) >= len(req.prompt))) or \
+                    (m.pos3 is not None and len(m.pos3) != len(req.prompt)):
+                raise ValueError("image rows do not match the prompt")
         (req.sampling or Sampling()).validate()
         if self.admission is not None:
             self.admission.check(len(req.prompt) + req.max_new_tokens)
@@ -235,13 +243,16 @@ class Engine:
             s = _Seq(req, slot, list(req.prompt), len(req.prompt), drafter=CopyDrafter(), stats=AcceptStats(), t_submit=t0)
             self.seqs[req.id] = s
             self.order.append(req.id)
+            if req.media is not None:
+                self.backend.set_media(slot, req.media)
             self._plan_prefix(s)
 
     def _plan_prefix(self, s: _Seq) -> None:
         if self.prefix is None or not s.req.prefix_cache:
             return
         bt = self.backend.prefix_block_tokens()
-        s.hashes = chain_hashes(s.tokens[:s.prompt_len], bt, self.cache_namespace)
+        # image placeholders hash by their image's content, not by the placeholder id
+        s.hashes = chain_hashes(s.tokens[:s.prompt_len] if s.req.media is None else s.req.media.hash_tokens(s.tokens[:s.prompt_len]), bt, self.cache_namespace)
         chain = self.prefix.lookup(s.hashes, s.prompt_len)
         if self.spill is not None:
             chain = self._spill_in(s, chain)

@@ -105,6 +105,10 @@ class DenseGpuBackend(Backend):
             self.d_lat_vals = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.float32, device=dev)
             self.h_lat_ids = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.int32).pin_memory()
             self.h_lat_vals = torch.zeros(self.DK, self.max_slots, self.LAT_K, dtype=torch.float32).pin_memory()
+        # image prompts: per slot the MediaInputs of the prompt in flight (embeddings on the device) and what decode rows add to their position
+        self.media = [None] * self.max_slots
+        self.rope_delta = [0] * self.max_slots
+        self.media_rows = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.graph_replays = 0
@@ -168,11 +172,80 @@ class DenseGpuBackend(Backend):
             self.bt_dirty = False
             self.bt_dirty_slots.clear()
 
+    # ------------------------------------------------------------------ image prompts
+    def supports_media(self) -> bool:
+        """Image rows ride on this class's own prefill path of one rank; the multi-token-prediction block's lagged rows do not carry them."""
+        return (type(self).prefill_slices is DenseGpuBackend.prefill_slices and type(self)._run_prefill is DenseGpuBackend._run_prefill
+                and type(self)._announce_window is DenseGpuBackend._announce_window and not self.mtp_draft)
+
+    def set_media(self, slot, media) -> None:
+        if media is None:
+            self.media[slot], self.rope_delta[slot] = None, 0
+            return
+        if not self.supports_media():
+            raise BackendError("this backend takes no image inputs", fatal=False)
+        emb = torch.as_tensor(media.embeds).to(device=self.m.device, dtype=self.m.embed.dtype)
+        if emb.ndim != 2 or emb.shape[1] != self.cfg.d_model or emb.shape[0] != len(media.rows):
+            raise BackendError(f"image rows of shape {tuple(emb.shape)} do not fit {len(media.rows)} placeholders of width {self.cfg.d_model}", fatal=False)
+        if getattr(self.cfg, "mrope_sections", None) is not None and media.pos3 is None:
+            raise BackendError("this model rotates by (T, H, W) positions: the image prompt must bring them", fatal=False)
+        self.media[slot] = (np.asarray(media.rows, dtype=np.int64), emb, None if media.pos3 is None else np.asarray(media.pos3, dtype=np.int32))
+        self.rope_delta[slot] = int(media.rope_delta) if media.pos3 is not None else 0
+        self.h2d_bytes += emb.numel() * emb.element_size()
+
+    def _prefill_media(self, items, M):
+        """-> (embed_rows, pos3) of a prefill forward over `items`, or (None, None) when none of their slots holds image rows."""
+        if not any(self.media[slot] is not None for slot, _, _, _ in items):
+            return None, None
+        dev = self.m.device
+        need3 = getattr(self.cfg, "mrope_sections", None) is not None
+        p3 = np.empty((M, 3), dtype=np.int32) if need3 else None
+        idx, emb, q0 = [], [], 0
+        for slot, start, toks, _ in items:
+            n, md = len(toks), self.media[slot]
+            if need3:
+                if md is not None and md[2] is not None:
+                    p3[q0:q0 + n] = md[2][start:start + n]
+                else:
+                    p3[q0:q0 + n] = np.arange(start, start + n, dtype=np.int32)[:, None]
+            if md is not None:
+                lo, hi = np.searchsorted(md[0], start), np.searchsorted(md[0], start + n)
+                if hi > lo:
+                    idx.append(q0 + (md[0][lo:hi] - start))
+                    emb.append(md[1][lo:hi])
+            q0 += n
+        er = None
+        if idx:
+            ii = np.concatenate(idx)
+            er = (torch.as_tensor(ii, device=dev), torch.cat(emb, 0))
+            self.media_rows += len(ii)
+            self.h2d_bytes += ii.nbytes
+        t3 = None
+        if need3:
+            t3 = torch.as_tensor(p3, device=dev).contiguous()
+            self.h2d_bytes += p3.nbytes
+        return er, t3
+
     def _fill_rows(self, specs) -> int:
-        """specs: list of (slot, first_position, tokens).  Fills the pinned staging rows; returns M."""
+        """specs: list of (slot, first_position, tokens).  Fills the pinned staging rows; returns M.  Rows after an image prompt rotate at
+        position + the slot's delta (rows of the prompt itself keep their index: their (T, H, W) positions travel apart)."""
         self._host_writable()
         h = self.h_rows.numpy()
         r = 0
+        if any(self.rope_delta[slot] for slot, _, _ in specs):
+            for slot, p0, toks in specs:
+                n = len(toks)
+                pos = np.arange(p0, p0 + n, dtype=np.int64)
+                pg = np.asarray(self.pages[slot], dtype=np.int64)[pos // PAGE]
+                md = self.media[slot]
+                plen = len(md[2]) if (md is not None and md[2] is not None) else 0
+                h[0, r:r + n] = toks
+                h[1, r:r + n] = np.where(pos >= plen, pos + self.rope_delta[slot], pos)
+                h[2, r:r + n] = pg * PAGE + pos % PAGE
+                h[3, r:r + n] = slot
+                h[4, r:r + n] = pos + 1
+                r += n
+            return r
         if all(len(t) == 1 for _, _, t in specs):
             # plain decode (one row per sequence): no per-sequence numpy calls, one bulk assignment per array
             n = len(specs)
@@ -223,7 +296,8 @@ class DenseGpuBackend(Backend):
             q0 += len(toks)
             if last:
                 last_rows.append(q0 - 1)
-        rows = self._run_prefill(M, n, max(len(t) for _, _, t, _ in items), last_rows, candidates)
+        er, p3 = self._prefill_media(items, M)
+        rows = self._run_prefill(M, n, max(len(t) for _, _, t, _ in items), last_rows, candidates, **({"embed_rows": er, "pos3": p3} if (er or p3 is not None) else {}))
         if self.mtp_draft:
             self._mtp_after_trunk([(s, st, t) for s, st, t, _ in items], keep_all=False)
         for slot, start, toks, _ in items:
@@ -239,7 +313,7 @@ class DenseGpuBackend(Backend):
         self._check()
         return outs
 
-    def _run_prefill(self, M, n, max_qlen, last_rows, candidates):
+    def _run_prefill(self, M, n, max_qlen, last_rows, candidates, embed_rows=None, pos3=None):
         """Uploads the staged rows and runs one prefill forward; returns the candidate rows of `last_rows` (or None)."""
         m = self.m
         self._upload_rows(M)
@@ -250,8 +324,13 @@ class DenseGpuBackend(Backend):
         d = self.d_rows
         pf = dict(seq_ids=self.d_pf[0], q_start=self.d_pf[1], q_len=self.d_pf[2], pos0=self.d_pf[3], nseq=n, max_qlen=max_qlen)
         lr = torch.tensor(last_rows, dtype=torch.long, device=m.device) if last_rows else None
+        kw = {}
+        if embed_rows is not None:
+            kw["embed_rows"] = embed_rows
+        if pos3 is not None:
+            kw["pos3"] = pos3
         logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr,
-                                want_logits=bool(last_rows))
+                                want_logits=bool(last_rows), **kw)
         return self._read_candidates(logits, candidates) if last_rows else None
 
     # ------------------------------------------------------------------ decode / verify window
@@ -367,7 +446,7 @@ class DenseGpuBackend(Backend):
                     ns += 1
                     a = r.parents[a]
             h[0, r0:r0 + n] = r.tokens
-            h[1, r0:r0 + n] = p0 + np.asarray(depth, dtype=np.int64)
+            h[1, r0:r0 + n] = p0 + np.asarray(depth, dtype=np.int64) + self.rope_delta[slot]
             h[2, r0:r0 + n] = row_slot
             h[3, r0:r0 + n] = slot
             h[4, r0:r0 + n] = p0 + np.asarray(depth, dtype=np.int64) + 1
@@ -514,7 +593,7 @@ class DenseGpuBackend(Backend):
             for j in range(k):
                 pos = p0 - 1 + j                  # the block's row: hidden of `pos`, token pos + 1 -> predicts token pos + 2
                 h[j, 0, i] = a.context[-1] if j == 0 else 0
-                h[j, 1, i], h[j, 2, i], h[j, 3, i], h[j, 4, i] = pos, pg[pos // PAGE] * PAGE + pos % PAGE, slot, pos + 1
+                h[j, 1, i], h[j, 2, i], h[j, 3, i], h[j, 4, i] = pos + self.rope_delta[slot], pg[pos // PAGE] * PAGE + pos % PAGE, slot, pos + 1
             hk[0, i] = slot * W + (p0 - 1 - self.mtp_p0[slot])
             top = max(top, p0 + k)
         bucket = min(m.max_ctx_alloc, (top + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
@@ -671,6 +750,7 @@ class DenseGpuBackend(Backend):
         self.pending[slot] = 0
         self._drop_private(slot)
         self.tree_parents[slot] = self.tree_slots[slot] = None
+        self.media[slot], self.rope_delta[slot] = None, 0
         if self.mtp_draft:
             self.mtp_p0[slot], self.mtp_n[slot] = -1, 0
         self._host_writable()
@@ -748,7 +828,7 @@ class DenseGpuBackend(Backend):
             for j in range(k):
                 pos = p0 + j
                 h[j, 0, i] = a.context[-1] if j == 0 else 0
-                h[j, 1, i], h[j, 2, i], h[j, 3, i], h[j, 4, i] = pos, pg[pos // PAGE] * PAGE + pos % PAGE, slot, pos + 1
+                h[j, 1, i], h[j, 2, i], h[j, 3, i], h[j, 4, i] = pos + self.rope_delta[slot], pg[pos // PAGE] * PAGE + pos % PAGE, slot, pos + 1
             top = max(top, p0 + k)
         bucket = min(self.m.max_ctx_alloc, (top + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
         self.d_draft[:k, :, :n].copy_(self.h_draft[:k, :, :n], non_blocking=True)
@@ -860,6 +940,8 @@ class DenseGpuBackend(Backend):
                    free_pages=self.pool.free_blocks())
         if self.mtp_draft:
             out.update(mtp_rows=self.mtp_rows, draft_steps=self.draft_steps)
+        if self.media_rows:
+            out.update(media_rows=self.media_rows)
         if self.tree_windows:
             out.update(tree_windows=self.tree_windows, tree_moves=self.tree_moves, tree_copies=self.tree_copies)
         return out

@@ -73,6 +73,7 @@ class MockBackend(Backend):
         self.steps = 0
         self.error = None
         self.generated = {}
+        self.media = {}        # slot -> {prompt position: pseudo-token of the image row there}
 
     def score_last(self, slot, tokens, chunk):
         """A full row consistent with `_row`: the candidates' values at their ids, a low floor elsewhere."""
@@ -122,7 +123,8 @@ class MockBackend(Backend):
         ctx = self.ctx.setdefault(slot, [])
         if start != len(ctx):
             raise BackendError(f"prefill at {start} but slot {slot} holds {len(ctx)} tokens", fatal=False)
-        ctx.extend(tokens)
+        seen = self.media.get(slot)
+        ctx.extend(tokens if not seen else [seen.get(start + j, t) for j, t in enumerate(tokens)])
         self.pending.pop(slot, None)
         self._ensure_blocks(slot, len(ctx))
         if not last:
@@ -166,6 +168,17 @@ class MockBackend(Backend):
     def supports_trees(self):
         return self.o.trees
 
+    def supports_media(self):
+        return True
+
+    def set_media(self, slot, media):
+        """The mock "sees" an image through its rows: every placeholder position reads as a pseudo-token made from that row's embedding."""
+        if media is None:
+            self.media.pop(slot, None)
+            return
+        emb = np.asarray(media.embeds, dtype=np.float32)
+        self.media[slot] = {int(r): _h(emb[i].tobytes()) & 0x7FFFFFFF for i, r in enumerate(media.rows)}
+
     def step_tree(self, reqs, candidates):
         self._tick()
         out = []
@@ -207,6 +220,7 @@ class MockBackend(Backend):
         self.pending.pop(slot, None)
         self.leak.pop(slot, None)
         self.generated.pop(slot, None)
+        self.media.pop(slot, None)
         b = self.blocks.pop(slot, None)
         if b:
             self.pool.release(b)

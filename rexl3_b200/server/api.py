@@ -177,7 +177,9 @@ def _thinking(body: dict):
     return v
 
 
-def parse_messages(body: dict) -> list:
+def parse_messages(body: dict, image_hook=None) -> list:
+    """`image_hook(part) -> str`: called for every image part when the server has a vision tower; what it returns (the chat format's image
+    placeholder) takes the part's place in the message text.  Without a hook an image part is refused by name."""
     msgs = body.get("messages")
     if not isinstance(msgs, list) or not msgs:
         raise bad("'messages' must be a non-empty list", "messages")
@@ -195,7 +197,9 @@ def parse_messages(body: dict) -> list:
                 if ty == "text":
                     parts.append(str(part.get("text", "")))
                 elif ty in ("image_url", "image"):
-                    raise bad("image input is not supported by this model", "messages", "unsupported")
+                    if image_hook is None:
+                        raise bad("image input is not supported by this model", "messages", "unsupported")
+                    parts.append(image_hook(part))
                 else:
                     raise bad(f"content part type '{ty}' is not supported", "messages", "unsupported")
             c = "".join(parts)

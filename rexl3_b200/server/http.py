@@ -27,8 +27,9 @@ from .tokenizer import Tok
 class AppState:
     def __init__(self, handle: EngineHandle, tok: Tok, fmt: ChatFormat, model_name: str, max_model_len: int, aliases=(), defaults=None,
                  default_max_tokens: int = 512, fingerprint: str = "rexl3-b200", max_body_bytes: int = 64 << 20, info: dict | None = None,
-                 limits=None, default_thinking: str = "template", default_effort: str | None = None):
+                 limits=None, default_thinking: str = "template", default_effort: str | None = None, vision=None):
         self.handle, self.tok, self.fmt = handle, tok, fmt
+        self.vision = vision              # server.media.VisionIngress: image parts of chat messages are decoded, encoded and laid into the prompt
         self.model_name, self.aliases = model_name, set(aliases)
         self.max_model_len, self.default_max_tokens = max_model_len, default_max_tokens
         self.defaults = defaults or api.GenDefaults()
@@ -102,7 +103,7 @@ def _make_request(st: AppState, ids: list, p: api.Params, rid: str, prompt_text:
     if p.seed is None and samp.temperature > 0:
         samp = samp.with_seed(seed_for(ids, 0))
     stop_ids = tuple(st.tok.eos_ids) + tuple(t for t in st.role_stops if t not in st.tok.eos_ids)     # a generated role token opens a new turn
-    req = Request(rid, ids, max_new, samp, stop_ids, draft=p.draft, prefix_cache=p.prefix_cache)
+    req = Request(rid, ids, max_new, samp, stop_ids, draft=p.draft, prefix_cache=p.prefix_cache, media=getattr(p, "media", None))
     if getattr(p, "max_reasoning_tokens", None) is not None and st.fmt.think_close:
         # reasoning budget: the engine forces the closing tag once that many tokens were spent inside the thinking block
         req.reasoning_budget = int(p.max_reasoning_tokens)
@@ -251,7 +252,19 @@ def build_app(st: AppState) -> Starlette:
 
     def render_chat(body, p):
         """-> (prompt text, token ids, note for the client or None)"""
-        msgs = api.parse_messages(body)
+        images, hook = [], None
+        if st.vision is not None:
+            from .media import MediaError
+
+            def hook(part):
+                if len(images) >= st.vision.max_images:
+                    raise api.bad(f"more than {st.vision.max_images} images in one request", "messages", "too_many_images")
+                try:
+                    images.append(st.vision.decode(part))
+                except MediaError as e:
+                    raise api.bad(str(e), "messages", e.code)
+                return st.vision.placeholder_text
+        msgs = api.parse_messages(body, hook)
         kwargs, note = p.template_kwargs, None
         if st.family:
             refusal = st.fmt.check_media(msgs)
@@ -268,7 +281,14 @@ def build_app(st: AppState) -> Starlette:
             text = st.fmt.render(msgs, tools=p.tools, add_generation_prompt=True, **kwargs)
         except TemplateRefused as e:
             raise api.bad(str(e), "messages", "template_error")
-        return text, _encode(st, text), note
+        ids = _encode(st, text)
+        p.media = None
+        if images:
+            try:
+                ids, p.media = st.vision.prepare(ids, images)
+            except MediaError as e:
+                raise api.bad(str(e), "messages", e.code)
+        return text, ids, note
 
     def split_tools(text, p):
         if not p.tools:

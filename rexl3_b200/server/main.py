@@ -44,6 +44,12 @@ def parser() -> argparse.ArgumentParser:
                    help="a runtime overlay directory (intervention.json + direction files): checked against the model at boot, any mismatch refuses")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
+    p.add_argument("--vision-tower", default=None, metavar="CONFIG",
+                   help="serve image parts of chat messages through a vision tower of this built-in shape (random init, seed --vision-seed; its output "
+                        "width follows the model); without it image parts are refused by name")
+    p.add_argument("--vision-seed", type=int, default=0)
+    p.add_argument("--vision-max-pixels", type=int, default=14 * 14 * 4 * 1280, help="pixel budget an image is resized into before it is cut into patches")
+    p.add_argument("--vision-max-images", type=int, default=8, help="images one request may carry")
     p.add_argument("--spec-tree", type=int, default=0, metavar="NODES",
                    help="verify draft trees of up to NODES nodes per stream (best first over the drafter's candidate lattice, the copy chain grafted in) "
                         "when the backend runs tree windows; 0 = chain windows")
@@ -140,6 +146,7 @@ def build(args):
             with boot.phase("load_pack_host"):
                 weights = packs.load_any(folder)              # header scan + refusals by name happen before CUDA starts
         vocab, name = cfg.vocab, args.served_model_name or cfg.name
+        args._model_cfg = cfg
         kv_tokens = args.kv_tokens or args.slots * args.max_model_len
         info = {"backend": args.backend, "kv_pool_tokens": kv_tokens, "pack_validated": weights is not None, "boot": boot.report}
         if weights is not None:
@@ -326,6 +333,38 @@ def _trees(args):
     return TreeConfig(max_nodes=min(63, args.spec_tree))
 
 
+def _vision(args, tok, fmt, info):
+    """The image path of the chat route (server.media.VisionIngress), or None.  Refusals come at start-up, by name."""
+    if not getattr(args, "vision_tower", None):
+        return None
+    import dataclasses
+    from ..vision import tower as vt
+    from .media import VisionIngress
+    if args.vision_tower not in vt.CONFIGS:
+        raise SystemExit(f"rexl3-serve: unknown --vision-tower {args.vision_tower!r}; known: {sorted(vt.CONFIGS)}")
+    vcfg = vt.CONFIGS[args.vision_tower]
+    cfg = getattr(args, "_model_cfg", None)
+    if cfg is not None:
+        if not hasattr(cfg, "d_model") or type(cfg).__name__ not in ("DenseConfig", "MoEConfig"):
+            raise SystemExit(f"rexl3-serve: --vision-tower: the `{cfg.name}` executor takes no image rows (dense and MoE GQA decoders do)")
+        if getattr(args, "spec", "") == "mtp" or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            raise SystemExit("rexl3-serve: --vision-tower runs on one rank and without --spec mtp")
+        vcfg = dataclasses.replace(vcfg, out_dim=cfg.d_model)
+    placeholder = getattr(fmt, "image_placeholder", "<|vision_start|><|image_pad|><|vision_end|>")
+    tid = tok.special_id("<|image_pad|>")
+    if tid is None:
+        raise SystemExit("rexl3-serve: --vision-tower: the tokenizer has no <|image_pad|> token")
+    fmt.serves_images = True
+    cuda = args.backend == "cuda"
+
+    def make_tower():
+        import torch
+        return vt.VisionTower(vcfg, seed=args.vision_seed, device="cuda" if cuda else "cpu", dtype=torch.bfloat16 if cuda else torch.float32)
+    info["vision"] = {"tower": vcfg.name, "out_dim": vcfg.out_dim, "patch": vcfg.patch, "merge": vcfg.merge, "weights": f"random init, seed {args.vision_seed}"}
+    return VisionIngress(vcfg, make_tower, tid, placeholder, mrope=getattr(cfg, "mrope_sections", None) is not None, max_pixels=args.vision_max_pixels,
+                         max_images=args.vision_max_images)
+
+
 def _arbiter(args):
     if not args.arbiter or args.no_drafts or args.spec == "none":
         return None
@@ -411,7 +450,7 @@ def make_app(args, metrics: Metrics | None = None):
                              f"{', '.join(caps.level_names()) or 'no effort levels'}")
     st = AppState(handle, tok, fmt, name, args.max_model_len, args.model_alias, defaults, args.default_max_tokens,
                   fingerprint=f"rexl3-b200-{name}", max_body_bytes=args.max_body_mib << 20, info=info, limits=limits,
-                  default_thinking=args.default_thinking, default_effort=args.default_reasoning_effort)
+                  default_thinking=args.default_thinking, default_effort=args.default_reasoning_effort, vision=_vision(args, tok, fmt, info))
     return build_app(st), handle
 
 

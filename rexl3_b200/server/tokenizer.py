@@ -85,11 +85,14 @@ class ByteTokenizer(Tok):
     """ids 0..255 are bytes; specials follow.  For mock / synthetic models whose vocabulary has no text meaning."""
 
     SPECIALS = ("<|bos|>", "<|eos|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>")
+    VISION_SPECIALS = ("<|vision_start|>", "<|image_pad|>", "<|vision_end|>")        # present when the vocabulary has room for them
 
     def __init__(self, vocab_size: int = 512):
         if vocab_size < 256 + len(self.SPECIALS):
             raise ValueError("byte tokenizer needs a vocabulary of at least 264")
         self.vocab_size = vocab_size
+        if vocab_size >= 256 + len(self.SPECIALS) + len(self.VISION_SPECIALS):
+            self.SPECIALS = self.SPECIALS + self.VISION_SPECIALS
         self.special = {s: 256 + i for i, s in enumerate(self.SPECIALS)}
         self.special_rev = {v: k for k, v in self.special.items()}
         self.bos_id, self.eos_ids = self.special["<|bos|>"], (self.special["<|eos|>"], self.special["<|im_end|>"])
