@@ -264,6 +264,8 @@ class EngineHandle:
             for j in range(len(eng.spec_pos["offered"])):
                 for k in ("offered", "reached", "accepted"):
                     m.set(f"spec_position_{k}_total", eng.spec_pos[k][j], position=str(j + 1))
+            for k in ("tree_rounds", "tree_nodes", "tree_depth_kept"):        # draft-tree rounds: windows, nodes verified, accepted path lengths
+                m.set(f"spec_{k}_total", c.get(k, 0))
             self._backend_metrics(eng.backend)
             if eng.admission is not None:
                 m.set("admission_bytes_capacity", getattr(eng.admission, "capacity", 0))
@@ -302,6 +304,9 @@ class EngineHandle:
         m.set("tp_commands_sent_total", st.get("tp_commands", 0))
         m.set("tp_sent_bytes_total", st.get("ctrl_bytes", 0))
         m.set("commit_replays_total", st.get("commit_replays", 0))
+        m.set("backend_tree_windows_total", st.get("tree_windows", 0))
+        m.set("backend_tree_row_copies_total", st.get("tree_copies", 0) + st.get("tree_moves", 0))
+        m.set("backend_image_rows_total", st.get("media_rows", 0))
 
     def _route(self, events) -> None:
         for ev in events:
