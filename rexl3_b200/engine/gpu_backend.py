@@ -37,7 +37,8 @@ class DenseGpuBackend(Backend):
         self.vocab_size = model.cfg.vocab
         self.max_slots = max_slots or model.max_seqs
         self.max_rows = min(256, model.max_rows)
-        self.use_graphs = use_graphs
+        # paged experts read the router's picks on the host in every layer: nothing there can be captured
+        self.use_graphs = use_graphs and getattr(model, "paged", None) is None
         self.pool = BlockPool(model.num_pages, PAGE)
         self.len = [0] * self.max_slots            # committed tokens per slot
         self.pages = [[] for _ in range(self.max_slots)]
@@ -942,6 +943,8 @@ class DenseGpuBackend(Backend):
             out.update(mtp_rows=self.mtp_rows, draft_steps=self.draft_steps)
         if self.media_rows:
             out.update(media_rows=self.media_rows)
+        if getattr(self.m, "paged", None) is not None:
+            out.update({"expert_" + k: v for k, v in self.m.paged.stats().items()})
         if self.tree_windows:
             out.update(tree_windows=self.tree_windows, tree_moves=self.tree_moves, tree_copies=self.tree_copies)
         return out

@@ -182,8 +182,11 @@ class MoEGPU(DenseGPU):
     that supplies the all-reduce slots (see parallel/ep.py); with all experts local the combine writes a local slot."""
 
     def __init__(self, w, num_pages, max_rows=256, max_seqs=64, max_blocks_per_seq=256, device="cuda", max_prefill_rows=4096, seed=0,
-                 experts=None, ep=None, a2a=None):
-        """`a2a` (parallel.ep.A2aComm): expert parallelism with DATA-PARALLEL rows - every rank feeds its own sequences, a (row, slot) pair
+                 experts=None, ep=None, a2a=None, expert_paging=None):
+        """`expert_paging` = dict(path=FILE, budget_bytes=N[, fill_threads, direct]): the routed experts stay in a record file (written there
+        from the host weights when FILE does not exist yet) and are paged into a device slab of N bytes as the router asks for them
+        (models/expert_paging.py); one rank, weights from host tensors.  Every layer's call then costs a device -> host read of its picks.
+        `a2a` (parallel.ep.A2aComm): expert parallelism with DATA-PARALLEL rows - every rank feeds its own sequences, a (row, slot) pair
         travels to the rank that owns its expert and its result travels back (token all-to-all); `experts` is then this rank's range."""
         cfg = w if isinstance(w, DenseConfig) else w.cfg
         self.e_lo, self.e_hi = experts or (0, cfg.n_experts)
@@ -191,6 +194,10 @@ class MoEGPU(DenseGPU):
         self.a2a = a2a
         if a2a is not None and ep is not None:
             raise ValueError("replicated-row expert parallelism (ep) and the token all-to-all (a2a) are two different layouts: pick one")
+        self.paged = None
+        self._paging = expert_paging
+        if expert_paging is not None and (ep is not None or a2a is not None or experts is not None or isinstance(w, DenseConfig)):
+            raise ValueError("expert paging runs on one rank that owns every expert, over host weights")
         if ctypes.sizeof(CombineDst) != _lib.load().rx_moe_combine_desc_size():
             raise _lib.KernelError("MoE combine descriptor layout mismatch")
         super().__init__(w, num_pages, max_rows, max_seqs, max_blocks_per_seq, device, max_prefill_rows, seed)
@@ -203,13 +210,23 @@ class MoEGPU(DenseGPU):
         self.embed = dev(w.embed, torch.bfloat16)
         self.layers = []
         lo, hi = self.e_lo, self.e_hi
+        stacks = None
+        if self._paging is not None:
+            from . import expert_paging as xp
+            pg = dict(self._paging)
+            layout = xp.write_records(w, pg.pop("path"))       # (an existing file of the right size is kept)
+            self.paged = xp.PagedExperts(layout, pg.pop("budget_bytes"), device, **pg)
+            t, cb = self.paged.slab.t, layout.codebook
+            # every layer reads "its experts" from the same slab: a layer's call translates expert ids to slot ids first
+            stacks = (_ExpertStack(t["gu_trellis"], t["gu_suh"], t["gu_svh"], cb), _ExpertStack(t["dn_trellis"], t["dn_suh"], t["dn_svh"], cb))
         for lay in w.layers:
             self.layers.append(dict(attn_norm=dev(lay.attn_norm, torch.bfloat16), qkv=up(lay.qkv), o=up(lay.o), ffn_norm=dev(lay.ffn_norm, torch.bfloat16),
                                     q_norm=None if lay.q_norm is None else dev(lay.q_norm, torch.bfloat16),
                                     k_norm=None if lay.k_norm is None else dev(lay.k_norm, torch.bfloat16),
                                     router=dev(lay.router, torch.bfloat16),
                                     router_bias=None if lay.router_bias is None else dev(lay.router_bias, torch.float32),
-                                    gu=_ExpertStack.from_host(lay.experts_gu[lo:hi], device), down=_ExpertStack.from_host(lay.experts_down[lo:hi], device)))
+                                    gu=stacks[0] if stacks else _ExpertStack.from_host(lay.experts_gu[lo:hi], device),
+                                    down=stacks[1] if stacks else _ExpertStack.from_host(lay.experts_down[lo:hi], device)))
         self.final_norm = dev(w.final_norm, torch.bfloat16)
         self.lm_head = up(w.lm_head)
 
@@ -250,14 +267,15 @@ class MoEGPU(DenseGPU):
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes
         for L in self.layers:
-            n += L["qkv"].nbytes + L["o"].nbytes + L["gu"].nbytes + L["down"].nbytes + L["router"].numel() * 2
-        return n
+            n += L["qkv"].nbytes + L["o"].nbytes + L["router"].numel() * 2 + (0 if self.paged is not None else L["gu"].nbytes + L["down"].nbytes)
+        return n + (self.paged.slab.nbytes() if self.paged is not None else 0)
 
     # ------------------------------------------------------------------ buffers
     def _alloc_scratch(self, R: int):
         cfg, K, dev = self.cfg, self.K, self.device
         super()._alloc_scratch(R)       # the dense scratch sizes its (unused) FFN buffers from cfg.ffn; the expert buffers follow
         k, d, F, E = cfg.top_k, cfg.d_model, cfg.expert_ffn, cfg.n_experts
+        S = self.paged.slots if getattr(self, "paged", None) is not None else 0      # paged experts: the kernels see slot ids, 0 .. S - 1
         # token all-to-all: the expert side of a rank may receive every rank's pairs, so its buffers are sized for ranks x rows
         # (whatever class this rank's own window has: a peer may be prefilling while this rank decodes)
         a2a = getattr(self, "a2a", None) is not None
@@ -279,9 +297,13 @@ class MoEGPU(DenseGPU):
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)  # noqa: E731
         self.xn = torch.empty(R, d, dtype=torch.bfloat16, device=dev)
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
-        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k * mult), i32(R * k * mult), i32(R * k * mult), i32(1)
+        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(max(E, S) + 1), i32(R * k * mult), i32(R * k * mult), i32(R * k * mult), i32(1)
         self.recv_ids = i32(R * k * mult) if a2a else None
-        El = self.e_hi - self.e_lo                                       # the tile table only ever names owned experts
+        El = max(self.e_hi - self.e_lo, S)                               # the tile table only ever names owned experts (or slots)
+        if S:
+            self.pick_slot = i32(R * k)
+            self.slot_table_h = torch.zeros(E, dtype=torch.int32).pin_memory()
+            self.slot_table = i32(E)
         # windows use 16- or 32-row tiles (small tiles keep two CTAs per SM); with the all-to-all a 16-row-tile window may receive a peer's slice
         self.max_tiles_decode = El + ((R * k * mult + 15) // 16 if a2a else (min(R, 256) * k + 31) // 32)
         self.max_tiles_prefill = El + (R * k * mult + 127) // 128
@@ -324,13 +346,23 @@ class MoEGPU(DenseGPU):
         if self.a2a is not None:
             yield from self._ffn_a2a(li, L, M, cls, xn, tile_rows, max_tiles, h, xr_d, next_norm, next_suh)
             return
-        _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, max_tiles, self.offs.data_ptr(),
+        picks, e_lo, e_hi = self.pick_ids, self.e_lo, self.e_hi
+        if self.paged is not None:
+            # the picks come to the host (which also means every kernel queued so far has run: the last call's leases can go), the experts
+            # they name are made resident, and the rest of the layer runs over slot ids
+            ids_h = self.pick_ids[:pairs].cpu().numpy()
+            self.paged.release_held()
+            self.slot_table_h.copy_(torch.from_numpy(self.paged.resolve(li, ids_h)))
+            self.slot_table.copy_(self.slot_table_h, non_blocking=True)
+            torch.index_select(self.slot_table, 0, self.pick_ids[:pairs].long(), out=self.pick_slot[:pairs])
+            picks, E, e_lo, e_hi = self.pick_slot, self.paged.slots, 0, self.paged.slots
+        _lib.check(Lib.rx_moe_plan(picks.data_ptr(), pairs, E, e_lo, e_hi, tile_rows, max_tiles, self.offs.data_ptr(),
                                    self.pos_of_pair.data_ptr(), self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(),
                                    self.total.data_ptr(), st), "rx_moe_plan")
         # local expert index = global - e_lo: the stacks hold only the owned experts, so shift the pointers instead of the ids
         gu, dn = L["gu"], L["down"]
         suh_gu = gu.suh.data_ptr() - 2 * self.e_lo * gu.K
-        _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), self.pick_ids.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, ctypes.c_void_p(suh_gu),
+        _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), picks.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, ctypes.c_void_p(suh_gu),
                                          self.xs.data_ptr(), st), "rx_moe_gather_rot")
         s_gu, s_dn = self.moe_splits[cls]
         self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows, cap)
@@ -339,7 +371,7 @@ class MoEGPU(DenseGPU):
                                          self.xs2.data_ptr(), st), "rx_moe_swiglu_rot")
         self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows, cap)
         dst, ar, flags, ranks, rows_cap, epoch, use = self._combine_target(li, M)
-        _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), s_dn, cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(),
+        _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), s_dn, cap, M, d, k, picks.data_ptr(), self.pick_w.data_ptr(),
                                       self.pos_of_pair.data_ptr(), ctypes.c_void_p(dn.svh.data_ptr() - 2 * self.e_lo * dn.N), None, ctypes.byref(dst), st),
                    "rx_moe_combine")
         if self.ep is not None:

@@ -44,6 +44,11 @@ def parser() -> argparse.ArgumentParser:
                    help="a runtime overlay directory (intervention.json + direction files): checked against the model at boot, any mismatch refuses")
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
+    p.add_argument("--expert-cache-mib", type=int, default=0,
+                   help="MoE packs on one GPU: keep the routed experts in a record file and page them into a device slab of this many MiB as the "
+                        "router asks for them (hits, misses, bytes read and evictions are on /metrics); 0 = every expert resident")
+    p.add_argument("--expert-cache-file", default=None, help="the record file (default: experts.records inside the pack; written at first start)")
+    p.add_argument("--expert-cache-direct", action="store_true", help="read the record file with O_DIRECT")
     p.add_argument("--vision-tower", default=None, metavar="CONFIG",
                    help="serve image parts of chat messages through a vision tower of this built-in shape (random init, seed --vision-seed; its output "
                         "width follows the model); without it image parts are refused by name")
@@ -213,6 +218,9 @@ def build(args):
                 wbytes = int(mla_models.MlaMoEGPU.weight_bytes_estimate(cfg)) if is_mla else int(cfg.weight_params() * cfg.bits / 8)
                 if is_hybrid:
                     wbytes += cfg.state_bytes_per_slot() * args.slots      # the recurrent-state pools are resident like weights
+                if is_moe and not is_mla and args.expert_cache_mib:
+                    # paged experts: the slab stands where the expert stacks would be
+                    wbytes += (args.expert_cache_mib << 20) - int(cfg.n_layers * cfg.n_experts * 3 * cfg.d_model * cfg.expert_ffn * cfg.bits / 8)
                 mm = ModelMemory(wbytes, kvb, activation_reserve=2 << 30)
                 adm = Admission(free, 1 << 30, mm, args.slots).with_max_context(args.max_model_len).with_kv_tokens(kv_tokens)
                 adm.check(min(args.max_model_len, 1))     # fail closed: a plan that can never hold one token is refused at boot
@@ -224,7 +232,13 @@ def build(args):
                 if is_mla:
                     model = mla_models.MlaMoEGPU(weights if weights is not None else cfg, **common)
                 elif is_moe:
-                    model = moe_models.MoEGPU(weights if weights is not None else cfg, **common)
+                    paging = None
+                    if args.expert_cache_mib:
+                        if weights is None:
+                            raise RuntimeError("--expert-cache-mib pages the experts of a pack (--model DIR), not of a random-init config")
+                        paging = dict(path=args.expert_cache_file or os.path.join(folder, "experts.records"), budget_bytes=args.expert_cache_mib << 20,
+                                      direct=args.expert_cache_direct)
+                    model = moe_models.MoEGPU(weights if weights is not None else cfg, expert_paging=paging, **common)
                 elif is_hybrid:
                     model = hybrid_models.HybridGPU(weights if weights is not None else cfg, **common)
                 else:

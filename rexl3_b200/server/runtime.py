@@ -307,6 +307,11 @@ class EngineHandle:
         m.set("backend_tree_windows_total", st.get("tree_windows", 0))
         m.set("backend_tree_row_copies_total", st.get("tree_copies", 0) + st.get("tree_moves", 0))
         m.set("backend_image_rows_total", st.get("media_rows", 0))
+        if "expert_slots" in st:            # routed experts paged from a record file
+            m.set("expert_cache_slots", st["expert_slots"])
+            m.set("expert_cache_resident", st.get("expert_resident", 0))
+            for k in ("hits", "misses", "bytes_read", "evictions", "hint_fills", "hint_drops", "asked", "cold"):
+                m.set(f"expert_cache_{k}_total", st.get("expert_" + k, 0))
 
     def _route(self, events) -> None:
         for ev in events:
