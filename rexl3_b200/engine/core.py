@@ -76,12 +76,16 @@ class _Seq:
     hashes: list = None
     reasoning: dict = None     # reasoning-budget state (see Engine._reasoning_budget)
     passed: int = 0            # prefill steps in which shorter prompts were served instead of this one
+    curve: object = None       # spec.arbiter.DepthCurve: this stream's conditional acceptance by draft position (budget policies past "legacy")
 
 
 class StepError(Exception):
     def __init__(self, kind: str, message: str, fatal: bool, group_lost: bool = False):
         super().__init__(f"{kind}: {message}")
         self.kind, self.fatal, self.group_lost = kind, fatal, group_lost
+
+
+BUDGET_POLICIES = ("legacy", "curve", "plan", "margin", "scored")
 
 
 @dataclass
@@ -103,7 +107,7 @@ class Engine:
     def __init__(self, backend: Backend, admission: Admission | None = None, *, window_rows: int = 64, prefill_chunk: int = PREFILL_STEP_ROWS,
                  spec: SpecMode | str = "auto", max_drafts: int = 4, cost: CostModel | None = None, prefix: PrefixIndex | None = None,
                  prefill_policy: str = "burst", burst_div: int = 2, burst_cap: int = 16, cache_namespace: bytes = b"", device_sampler: bool = False,
-                 spill=None, arbiter=None, trees=None):
+                 spill=None, arbiter=None, trees=None, budget_policy: str = "legacy", round_cost=None):
         self.backend = backend
         self.admission = admission
         self.window_rows = min(window_rows, backend.max_rows)
@@ -117,6 +121,15 @@ class Engine:
         # optional spec.Arbiter: per round and stream it picks how many of the offered drafts to verify (or none) by expected committed tokens
         # per model-millisecond, learns each source's acceptance by depth from the outcomes, and probes idle sources now and then
         self.arbiter = arbiter
+        # how many of a stream's drafts ride in the verify window (reference crates/engine/src/lib.rs:724-746, BudgetPolicy); no policy changes a
+        # committed token.  legacy: one geometric acceptance rate per stream, trimmed after the draft by the verify step's cost.  curve: the
+        # stream's measured conditional acceptance by draft position instead.  plan: curve, decided BEFORE the draft with the draft's cost in
+        # the model (`round_cost`: sched.RoundCost), so a stream not worth drafting is not drafted and the drafter is asked only for the
+        # positions that will be verified.  margin: plan, then trimmed again after the draft by the drafter's own confidence in each pick.
+        # scored: the pre-draft plan only picks WHICH streams draft (they are asked for every pick), the confidences trim afterwards.
+        if budget_policy not in BUDGET_POLICIES:
+            raise ValueError(f"unknown budget policy {budget_policy!r}; one of {', '.join(BUDGET_POLICIES)}")
+        self.budget_policy, self.round_cost = budget_policy, round_cost
         # TreeConfig: verify windows are draft trees when the backend supports them (chain windows otherwise)
         self.trees = trees
         self.prefix_cuts = bool(self.prefix is not None and getattr(backend, "prefix_needs_cuts", lambda: False)())
@@ -353,8 +366,16 @@ class Engine:
             room = s.req.max_new_tokens - s.generated
             m = min(self.max_drafts, max(0, room - 1)) if (self.spec.enabled and s.req.draft and self.can_rollback) else 0
             maxes.append(m)
+        pol = self.budget_policy
+        if pol in ("plan", "margin", "scored") and any(maxes):
+            # decided before the draft, with the draft's own cost: who drafts, and (plan, margin) how deep
+            pre = [Demand.from_conditional(self._curve(s).conditional(m), m).with_kv_tokens(len(s.tokens)) for s, m in zip(active, maxes)]
+            ahead = self._share(pre, self.window_rows, draft_sunk=False)
+            maxes = [(m if a > 0 else 0) if pol == "scored" else min(m, a) for m, a in zip(maxes, ahead)]
+            self.counters["planned_out"] = self.counters.get("planned_out", 0) + sum(1 for m in maxes if m == 0)
         # 2. proposals: native drafter first, copy drafter otherwise
         proposals = [[] for _ in active]
+        confs = [None] * len(active)
         sources = ["none"] * len(active)        # which drafter each proposal came from: "native" (backend drafter) or "copy" (host drafters)
         if any(maxes):
             if self.spec.native and self.backend.supports_native_draft():
@@ -364,6 +385,7 @@ class Engine:
                     off = offers.get(s.slot)
                     if off is not None and maxes[i] > 0:
                         proposals[i] = list(off.tokens[:maxes[i]])
+                        confs[i] = list(off.conf[:len(proposals[i])]) if off.conf else None
                         sources[i] = "native" if proposals[i] else "none"
             if self.spec.copy:
                 for i, s in enumerate(active):
@@ -388,12 +410,14 @@ class Engine:
                 choices.append(c if proposals[i] else None)
         # 3. budget: share the window's rows by expected value
         budget = self.window_rows
-        demands = [Demand.geometric(s.stats.accept_rate(), len(p)) for s, p in zip(active, proposals)]
-        if self.cost is not None:
-            _, alloc = choose_budget(self.cost, demands, budget)
-        else:
-            from ..sched import allocate
-            alloc = allocate(demands, budget)
+        if pol == "legacy":
+            demands = [Demand.geometric(s.stats.accept_rate(), len(p)) for s, p in zip(active, proposals)]
+        elif pol in ("curve", "plan"):
+            demands = [Demand.from_conditional(self._curve(s).conditional(len(p)), len(p)).with_kv_tokens(len(s.tokens)) for s, p in zip(active, proposals)]
+        else:       # margin, scored: the drafter's own confidence in each pick where it gave one
+            demands = [Demand.from_conditional(c if (c and len(c) >= len(p)) else self._curve(s).conditional(len(p)), len(p)).with_kv_tokens(len(s.tokens))
+                       for s, p, c in zip(active, proposals, confs)]
+        alloc = self._share(demands, budget, draft_sunk=True)
         for i in range(len(active)):
             proposals[i] = proposals[i][:alloc[i]]
         t1 = time.perf_counter_ns()
@@ -446,6 +470,7 @@ class Engine:
                     sp["reached"][j] += 1 if j <= a else 0
                     sp["accepted"][j] += 1 if j < a else 0
                 s.stats.update(len(p), a)
+                self._curve(s).observe(len(p), a)
                 s.drafted += len(p)
                 s.accepted += a
                 self.counters["drafted"] += len(p)
@@ -460,6 +485,23 @@ class Engine:
         self.phase_ns["draft"] += t1 - t0
         self.phase_ns["verify"] += t2 - t1
         self.phase_ns["commit"] += time.perf_counter_ns() - t2
+
+    def _curve(self, s):
+        if s.curve is None:
+            from ..spec.arbiter import DepthCurve
+            s.curve = DepthCurve([0.7])
+        return s.curve
+
+    def _share(self, demands, budget: int, draft_sunk: bool) -> list:
+        """Drafts per stream for a window of `budget` rows: by the round cost model where there is one (with the draft's own cost when the
+        draft has not run yet), else by the verify step's cost table, else by marginal value alone."""
+        if self.round_cost is not None:
+            from ..sched import plan_round
+            return plan_round(self.round_cost, demands, budget, draft_sunk).drafts
+        if self.cost is not None:
+            return choose_budget(self.cost, demands, budget)[1]
+        from ..sched import allocate
+        return allocate(demands, budget)
 
     def _emit(self, s, new) -> tuple:
         """Commits the round's tokens `new` to the sequence one by one (reasoning budget, stop ids, length) and queues the event.

@@ -55,6 +55,10 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--vision-seed", type=int, default=0)
     p.add_argument("--vision-max-pixels", type=int, default=14 * 14 * 4 * 1280, help="pixel budget an image is resized into before it is cut into patches")
     p.add_argument("--vision-max-images", type=int, default=8, help="images one request may carry")
+    p.add_argument("--spec-budget-policy", choices=["legacy", "curve", "plan", "margin", "scored"], default="legacy",
+                   help="how many of a stream's drafts ride in the verify window: one acceptance rate per stream (legacy), its measured acceptance by "
+                        "draft position (curve), decided before the draft (plan), trimmed again by the drafter's confidences (margin), or only the "
+                        "choice of streams decided ahead and the confidences sharing the rows (scored); replies are the same under every policy")
     p.add_argument("--spec-tree", type=int, default=0, metavar="NODES",
                    help="verify draft trees of up to NODES nodes per stream (best first over the drafter's candidate lattice, the copy chain grafted in) "
                         "when the backend runs tree windows; 0 = chain windows")
@@ -108,7 +112,7 @@ def build(args):
             be = MockBackend(opts)
             prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=be.prefix_block_tokens()) if args.prefix_cache == "on" else None
             return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix), arbiter=_arbiter(args), trees=_trees(args))
+                          max_drafts=args.max_drafts, prefix=prefix, spill=_spill_store(args, prefix), arbiter=_arbiter(args), trees=_trees(args), budget_policy=args.spec_budget_policy)
         info = {"backend": "mock"}
     else:
         from ..models import dense
@@ -266,7 +270,7 @@ def build(args):
                 prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, adm, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
                           max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args, model), device_sampler=args.device_sampler,
-                          spill=_spill_store(args, prefix), arbiter=_arbiter(args), trees=_trees(args))
+                          spill=_spill_store(args, prefix), arbiter=_arbiter(args), trees=_trees(args), budget_policy=args.spec_budget_policy)
     tok = load_tokenizer(folder, vocab)
     from . import formats
     try:

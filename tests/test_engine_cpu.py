@@ -270,3 +270,66 @@ def test_mock_tree_window_rows_equal_one_row_steps():
     be.step_tree([q], 8)
     be.commit_path(0, [2, 4])
     assert be.ctx[0] == [5, 6, 7, 12, 14]
+
+
+@pytest.mark.parametrize("policy", ["legacy", "curve", "plan", "margin", "scored"])
+def test_budget_policies_never_change_a_token(policy):
+    from rexl3_b200.sched import DraftCost, RoundCost, StepCost
+    p = harness.default_prompts(512) + [harness.default_prompts(512)[1][:20] * 5]
+    serial = generate(Engine(MockBackend(MockOptions()), spec="none"), p, 40, harness.SAMPLING)
+    from rexl3_b200.sched import CostModel
+    rc = RoundCost(StepCost({1: CostModel([(1, 10.0), (64, 14.0)]), 8: CostModel([(8, 11.0), (64, 16.0)])}),
+                   DraftCost(CostModel([(1, 1.0), (8, 2.0)]), CostModel([(1, 0.2), (32, 0.8)]), 0.5))
+    for kw in (dict(), dict(round_cost=rc)):
+        eng = Engine(MockBackend(MockOptions(native_draft=True)), spec="auto", max_drafts=4, window_rows=10, budget_policy=policy, **kw)
+        assert generate(eng, p, 40, harness.SAMPLING) == serial
+        assert eng.counters["accepted"] > 0
+    with pytest.raises(ValueError):
+        Engine(MockBackend(MockOptions()), budget_policy="greedy")
+
+
+def test_scored_policy_gives_scarce_rows_to_the_confident_stream():
+    """Two streams, a window with room for four drafts in all.  The drafter is sure of one stream's picks and unsure of the other's:
+    `scored` (every pick asked for, the confidences share the rows) verifies the sure stream's whole chain, `legacy` (one measured rate per
+    stream) leaves the other stream a real share; `plan` with a costly draft stops drafting a stream whose measured acceptance has collapsed."""
+    from rexl3_b200.engine import DraftOffer
+    from rexl3_b200.sched import CostModel, DraftCost, RoundCost, StepCost
+
+    class Sure(MockBackend):
+        rows_by_slot = None
+
+        def propose_batch(self, asks):
+            out = super().propose_batch(asks)
+            for a in asks:
+                out[a.slot] = DraftOffer(out[a.slot].tokens, [0.95 if a.slot == sure_slot[0] else 0.15] * len(out[a.slot].tokens))
+            return out
+
+        def step(self, reqs, candidates):
+            if len(reqs) == 2:                      # only the rounds in which the two streams compete for the rows
+                for r in reqs:
+                    self.rows_by_slot.setdefault(r.slot, []).append(len(r.tokens) - 1)
+            return super().step(reqs, candidates)
+
+    p = harness.default_prompts(512, (9, 11))
+    got = {}
+    for policy in ("legacy", "scored"):
+        be = Sure(MockOptions(native_draft=True, draft_error=0.0))
+        be.rows_by_slot = {}
+        eng = Engine(be, spec="auto", max_drafts=4, window_rows=6, budget_policy=policy)
+        sure_slot = [None]
+        for i, q in enumerate(p):
+            eng.submit(Request(str(i), q, 40, GREEDY))
+        eng.step()
+        sure_slot[0] = eng.seqs["0"].slot
+        other = eng.seqs["1"].slot
+        while eng.has_work():
+            eng.step()
+        got[policy] = (sum(be.rows_by_slot[sure_slot[0]]), sum(be.rows_by_slot[other]))
+    assert got["scored"][0] > got["scored"][1] * 2        # the confident stream rode with (almost) all the drafts
+    assert got["legacy"][1] * 4 > sum(got["legacy"])        # one measured rate each, both accept everything: the other stream keeps a real share
+    assert got["scored"][1] * 10 < sum(got["scored"])
+    # plan: a drafter that is always wrong drives the stream's curve down until the plan, which counts the draft's cost, stops asking
+    rc = RoundCost(StepCost.rows_only(CostModel([(1, 10.0), (64, 12.0)])), DraftCost(CostModel([(1, 6.0), (8, 8.0)]), CostModel([(1, 0.5), (32, 2.0)]), 1.0))
+    eng = Engine(MockBackend(MockOptions(native_draft=True, draft_error=1.0)), spec="auto", max_drafts=4, budget_policy="plan", round_cost=rc)
+    generate(eng, [p[0]], 40, GREEDY)
+    assert eng.counters.get("planned_out", 0) > 10 and eng.counters["drafted"] < 40
