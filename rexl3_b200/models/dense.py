@@ -381,6 +381,7 @@ class DenseGPU:
         self.pos3 = None
         self.tree = None               # (tree_base, vbt, moves, n_moves) while a forward runs a verify window of draft trees
         self._kv_ptrs = None
+        self._kv_scale_ptrs = None
         self.device = device
         self.mtp = None                # the multi-token-prediction block's tensors (config.mtp), set by the loaders of the dense family
         self.interventions = {}        # layer -> (alpha, orthonormal basis f32 [r, d]) runtime overlays (set_interventions)
@@ -615,6 +616,8 @@ class DenseGPU:
                 # page its path starts in, and its ancestors at their positions)
                 vbt = self.tree[1]
                 K.kv_move_rows(self._kv_ptr_table()[2 * li:2 * li + 2], self._kv_row_bytes(), cfg.n_kv, self.tree[2], self.tree[3])
+                if kts is not None:
+                    K.kv_move_rows(self._kv_scale_ptr_table()[2 * li:2 * li + 2], self._kv_scale_row_bytes(), cfg.n_kv, self.tree[2], self.tree[3])
             K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, cfg.n_q, cfg.n_kv, cfg.head_dim,
                           max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc, max_seq_rows=self.window_seq_rows,
                           plan=self.attn_plan, kv_tscale=kts, q4=q4, vbt=vbt)
@@ -741,9 +744,10 @@ class DenseGPU:
         return logits
 
     def supports_trees(self) -> bool:
-        """Tree windows need every layer's token mixer to be the paged attention of this class (a recurrent mixer has no per-node state) and a
-        bf16 cache (the tree mask lives in the bf16 decode kernel)."""
-        return (type(self)._mixer is DenseGPU._mixer and not (self.kv_fp8 or self.kv_i8 or self.kv_q4) and all(c is not None for c in self.k_cache))
+        """Tree windows need every layer's token mixer to be the paged attention of this class (a recurrent mixer has no per-node state).  bf16,
+        fp8 and int8 caches work (the window's row copies also move the int8 cache's per-token scale planes); the q4 decode entry takes no
+        private tables."""
+        return type(self)._mixer is DenseGPU._mixer and not self.kv_q4 and all(c is not None for c in self.k_cache)
 
     def _kv_ptr_table(self):
         """int64 device tensor [2 * layers]: the K and V cache addresses, layer by layer."""
@@ -754,10 +758,23 @@ class DenseGPU:
     def _kv_row_bytes(self) -> int:
         return self.k_cache[0].shape[-1] * self.k_cache[0].element_size()
 
+    def _kv_scale_ptr_table(self):
+        """int64 device tensor [2 * layers]: the per-token scale planes of an int8 cache, layer by layer."""
+        if self._kv_scale_ptrs is None:
+            self._kv_scale_ptrs = torch.tensor([c.data_ptr() for kv in zip(self.k_tscale, self.v_tscale) for c in kv], dtype=torch.int64, device=self.device)
+        return self._kv_scale_ptrs
+
+    def _kv_scale_row_bytes(self) -> int:
+        t = self.k_tscale[0]
+        return (t.shape[3] if t.ndim == 4 else 1) * t.element_size()
+
     def move_kv_rows(self, moves, n_moves: int) -> None:
         """moves: int32 device tensor [>= n_moves, 3] of (source slot, destination slot, rows), applied to the K and V caches of every layer
-        in one launch: the accepted path of a tree window goes from its nodes' slots to its positions."""
+        in one launch (and to the scale planes of an int8 cache in another): the accepted path of a tree window goes from its nodes' slots
+        to its positions."""
         self.K.kv_move_rows(self._kv_ptr_table(), self._kv_row_bytes(), self.cfg.n_kv, moves, n_moves)
+        if self.kv_i8:
+            self.K.kv_move_rows(self._kv_scale_ptr_table(), self._kv_scale_row_bytes(), self.cfg.n_kv, moves, n_moves)
 
     def mtp_forward(self, ids_next, hidden, positions, slots, row_seq, ctx_len, block_table, *, prefill=None, max_ctx=None, want_logits=True,
                     logit_rows=None):

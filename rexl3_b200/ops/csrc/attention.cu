@@ -1051,12 +1051,17 @@ __global__ void __launch_bounds__(128) kv_move_rows_kernel(const unsigned long l
   const int src = moves[3 * blockIdx.x], dst = moves[3 * blockIdx.x + 1], n = moves[3 * blockIdx.x + 2];
   const uint8_t* sp = base + (((size_t)(src / PAGE) * n_kv + h) * PAGE + src % PAGE) * row_bytes;
   uint8_t* dp = base + (((size_t)(dst / PAGE) * n_kv + h) * PAGE + dst % PAGE) * row_bytes;
-  for (int c = threadIdx.x * 16; c < n * row_bytes; c += blockDim.x * 16)
-    *reinterpret_cast<uint4*>(dp + c) = *reinterpret_cast<const uint4*>(sp + c);
+  if (row_bytes % 16 == 0) {
+    for (int c = threadIdx.x * 16; c < n * row_bytes; c += blockDim.x * 16)
+      *reinterpret_cast<uint4*>(dp + c) = *reinterpret_cast<const uint4*>(sp + c);
+  } else {            // the per-token scale planes of the int8 cache: 4 bytes per row
+    for (int c = threadIdx.x * 4; c < n * row_bytes; c += blockDim.x * 4)
+      *reinterpret_cast<uint32_t*>(dp + c) = *reinterpret_cast<const uint32_t*>(sp + c);
+  }
 }
 
 RX_API int rx_kv_move_rows(const void* tensors, int n_tensors, int row_bytes, int n_kv, const void* moves, int n_moves, void* stream) {
-  if (n_tensors <= 0 || n_tensors > 65535 || n_kv <= 0 || n_kv > 65535 || row_bytes <= 0 || row_bytes % 16 != 0 || n_moves < 0) return (int)cudaErrorInvalidValue;
+  if (n_tensors <= 0 || n_tensors > 65535 || n_kv <= 0 || n_kv > 65535 || row_bytes <= 0 || row_bytes % 4 != 0 || n_moves < 0) return (int)cudaErrorInvalidValue;
   if (n_moves == 0) return 0;
   rx::launch(kv_move_rows_kernel, dim3(n_moves, n_kv, n_tensors), dim3(128), 0, (cudaStream_t)stream, (const unsigned long long*)tensors, row_bytes, n_kv,
              (const int*)moves);

@@ -18,6 +18,16 @@ def model():
     return dense.DenseGPU(dense.random_weights(cfg, seed=3), num_pages=160, max_rows=64, max_seqs=8, max_blocks_per_seq=8, max_prefill_rows=512)
 
 
+@pytest.fixture(scope="module", params=["fp8", "int8"])
+def qmodel(request):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.models import dense
+    cfg = dense.CONFIGS["test-hd128"]
+    return dense.DenseGPU(dense.random_weights(cfg, seed=3), num_pages=160, max_rows=64, max_seqs=8, max_blocks_per_seq=8, max_prefill_rows=512,
+                          kv_dtype=request.param)
+
+
 def _serial_row(model, ctx, path, count):
     """The output of the last one-row step of a serial run: prompt ctx[:-1], then ctx[-1] and the path's tokens one by one."""
     from rexl3_b200.engine import RowRequest
@@ -121,3 +131,33 @@ def test_engine_tree_rounds_emit_the_serial_tokens(model):
         assert eng.counters["tree_rounds"] > 0 and eng.counters["accepted"] > 20 and st["tree_moves"] > 0 and st["tree_copies"] > 0, (eng.counters, st)
         assert eng.counters["rounds"] < n        # fewer rounds than tokens: paths were kept
         assert be.pool.free_blocks() == be.pool.total_blocks()
+
+
+@pytest.mark.parametrize("ctx_len", [65, 257])
+def test_tree_window_over_quantized_caches(qmodel, ctx_len):
+    """The same property over an fp8 cache (static per-head scales) and an int8 cache (one scale per token and head, which moves with its row)."""
+    from rexl3_b200.engine import RowRequest, TreeRequest
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    rng = np.random.default_rng(ctx_len + 1000)
+    V = qmodel.cfg.vocab
+    ctx = rng.integers(0, V, size=ctx_len).tolist()
+    toks = [ctx[-1]] + rng.integers(0, V, size=5).tolist()
+    parents = [-1, 0, 0, 2, 1, 3]
+    be = DenseGpuBackend(qmodel, max_slots=8)
+    assert be.supports_trees()
+    be.prefill_slice(1, 0, ctx[:-1], 8, False)
+    out = be.step_tree([TreeRequest(1, toks, parents, len(ctx) - 1)], 8)[0]
+    assert be.take_error() is None
+    for r in range(len(toks)):
+        path, a = [], r
+        while a > 0:
+            path.append(toks[a])
+            a = parents[a]
+        ref = _serial_row(qmodel, ctx, path[::-1], 8)
+        assert np.array_equal(ref.ids, out[r].ids) and np.array_equal(ref.values, out[r].values), f"row {r}"
+    be.commit_path(1, [2, 3, 5])
+    nxt = be.step([RowRequest(1, [77], len(ctx) + 3)], 8)[0][0]
+    ref = _serial_row(qmodel, ctx, [toks[2], toks[3], toks[5], 77], 8)
+    assert np.array_equal(ref.ids, nxt.ids) and np.array_equal(ref.values, nxt.values)
+    be.release(1)
+    assert be.pool.free_blocks() == be.pool.total_blocks()
