@@ -92,6 +92,7 @@ class DraftOffer:
     tokens: list = field(default_factory=list)
     conf: list = field(default_factory=list)       # optional per-draft confidence (probability it is accepted given the ones before)
     lattice: object = None                         # optional spec.tree.Lattice: per level the drafter's candidate ids and scores (level 0 = first draft)
+    margin: list = field(default_factory=list)     # optional per draft: how far the pick leads the drafter's runner-up, in logits
 
 
 class Backend:

@@ -130,6 +130,9 @@ class Engine:
         if budget_policy not in BUDGET_POLICIES:
             raise ValueError(f"unknown budget policy {budget_policy!r}; one of {', '.join(BUDGET_POLICIES)}")
         self.budget_policy, self.round_cost = budget_policy, round_cost
+        from ..spec.stats import MODES, MarginBins, PositionStats
+        self.position_stats = {m: PositionStats() for m in MODES}     # per draft position: offered / verified / reached / accepted
+        self.margin_bins = MarginBins()                               # acceptance by the drafter's margin (the confidence of margin / scored)
         # TreeConfig: verify windows are draft trees when the backend supports them (chain windows otherwise)
         self.trees = trees
         self.prefix_cuts = bool(self.prefix is not None and getattr(backend, "prefix_needs_cuts", lambda: False)())
@@ -376,6 +379,8 @@ class Engine:
         # 2. proposals: native drafter first, copy drafter otherwise
         proposals = [[] for _ in active]
         confs = [None] * len(active)
+        margins = [None] * len(active)
+        offered = [0] * len(active)
         sources = ["none"] * len(active)        # which drafter each proposal came from: "native" (backend drafter) or "copy" (host drafters)
         if any(maxes):
             if self.spec.native and self.backend.supports_native_draft():
@@ -386,6 +391,10 @@ class Engine:
                     if off is not None and maxes[i] > 0:
                         proposals[i] = list(off.tokens[:maxes[i]])
                         confs[i] = list(off.conf[:len(proposals[i])]) if off.conf else None
+                        margins[i] = list(off.margin[:len(proposals[i])]) if off.margin else None
+                        if confs[i] is None and margins[i] and len(margins[i]) >= len(proposals[i]):
+                            # conditional confidences from the margins: what picks with such a lead have done so far
+                            confs[i] = self.margin_bins.confidences(margins[i])
                         sources[i] = "native" if proposals[i] else "none"
             if self.spec.copy:
                 for i, s in enumerate(active):
@@ -408,6 +417,7 @@ class Engine:
                 c = picks[s.req.id]
                 proposals[i] = proposals[i][:c.drafts()] if c.kind == sources[i] else []
                 choices.append(c if proposals[i] else None)
+        offered = [len(p) for p in proposals]
         # 3. budget: share the window's rows by expected value
         budget = self.window_rows
         if pol == "legacy":
@@ -471,6 +481,10 @@ class Engine:
                     sp["accepted"][j] += 1 if j < a else 0
                 s.stats.update(len(p), a)
                 self._curve(s).observe(len(p), a)
+                from ..spec.stats import mode_of
+                self.position_stats[mode_of(s.req.sampling)].record(max(offered[si], len(p)), len(p), a)
+                if margins[si]:
+                    self.margin_bins.record(margins[si], len(p), a)
                 s.drafted += len(p)
                 s.accepted += a
                 self.counters["drafted"] += len(p)

@@ -860,7 +860,8 @@ class DenseGpuBackend(Backend):
         for i, a in enumerate(asks):
             kk = min(k, a.max_drafts)
             offers[a.slot] = DraftOffer([int(ids[j, i, 0]) for j in range(kk)], [],
-                                        Lattice([ids[j, i].tolist() for j in range(kk)], [vals[j, i].tolist() for j in range(kk)]))
+                                        Lattice([ids[j, i].tolist() for j in range(kk)], [vals[j, i].tolist() for j in range(kk)]),
+                                        [float(vals[j, i, 0] - vals[j, i, 1]) for j in range(kk)])
         return offers
 
     # ------------------------------------------------------------------ prefix cache: pages are shared by refcount

@@ -31,6 +31,7 @@ class MockOptions:
     draft_error: float = 0.25      # probability a native draft token is wrong
     trees: bool = False            # step_tree / commit_path are offered
     lattice: bool = False          # the native drafter offers four candidates per level (a wrong first one keeps the right one second)
+    margins: bool = False          # the native drafter reports each pick's lead over its runner-up instead of a confidence
     panic_at_step: int = -1
     fatal_at_step: int = -1
     group_lost_at_step: int = -1   # a fatal error that names a lost rank of a multi-rank group (what a peer wait that ran out reports)
@@ -236,12 +237,14 @@ class MockBackend(Backend):
         out = {}
         for a in asks:
             ctx, toks = list(a.context), []
-            lat_ids, lat_val = [], []
+            lat_ids, lat_val, margins = [], [], []
             for j in range(a.max_drafts):
                 row = self._row(ctx, 4)
                 t = int(row.ids[0])
                 if (_h(struct.pack("<qq", len(ctx), t)) % 1000) / 1000.0 < self.o.draft_error:
                     t = (t + 1) % self.o.vocab
+                # a wrong pick comes with a small lead, a right one with a large lead (what a margin is good for)
+                margins.append(0.2 if t != int(row.ids[0]) else 6.0)
                 toks.append(t)
                 if self.o.lattice:
                     # candidates of this level: the drafter's pick first, then the model's own order; deeper levels follow the model's pick
@@ -251,7 +254,8 @@ class MockBackend(Backend):
                     ctx.append(int(row.ids[0]))
                 else:
                     ctx.append(t)
-            out[a.slot] = DraftOffer(toks, [0.7] * len(toks), Lattice(lat_ids, lat_val) if self.o.lattice else None)
+            out[a.slot] = DraftOffer(toks, [0.7] * len(toks) if not self.o.margins else [], Lattice(lat_ids, lat_val) if self.o.lattice else None,
+                                     margins if self.o.margins else [])
         return out
 
     # prefix cache: blocks are shared by refcount

@@ -264,6 +264,15 @@ class EngineHandle:
             for j in range(len(eng.spec_pos["offered"])):
                 for k in ("offered", "reached", "accepted"):
                     m.set(f"spec_position_{k}_total", eng.spec_pos[k][j], position=str(j + 1))
+            for mode, ps in getattr(eng, "position_stats", {}).items():
+                m.set("spec_rounds_by_mode_total", ps.rounds, mode=mode)
+                m.set("spec_verify_rows_wasted_total", ps.wasted_rows(), mode=mode)
+            mb = getattr(eng, "margin_bins", None)
+            if mb is not None:
+                for b in range(len(mb.reached)):
+                    if mb.reached[b]:
+                        m.set("spec_margin_reached_total", mb.reached[b], bin=str(b))
+                        m.set("spec_margin_accepted_total", mb.accepted[b], bin=str(b))
             for k in ("tree_rounds", "tree_nodes", "tree_depth_kept"):        # draft-tree rounds: windows, nodes verified, accepted path lengths
                 m.set(f"spec_{k}_total", c.get(k, 0))
             self._backend_metrics(eng.backend)
