@@ -47,6 +47,8 @@ class Checkpoint:
         return sum(g.bytes for g in self.groups.values()) + sum(e.nbytes for e in self.plain.values())
 
 
+SIDECAR_FILES = ("vision.safetensors",)
+
 def parse_group(prefix: str, parts: dict) -> Group:
     """Raises ValueError(reason) for a group that must not load."""
     tr = parts.get("trellis")
@@ -107,7 +109,8 @@ def scan(folder: str, verify_markers: bool = False) -> Checkpoint:
     """Header-only scan.  `verify_markers` also reads the 4 bytes of every codebook marker tensor: a marker that does not hold its
     codebook's multiplier refuses the group (reference crates/exl3/src/checkpoint.rs:203-220; its scan has the same switch)."""
     ck = Checkpoint(folder)
-    files = sorted(f for f in os.listdir(folder) if f.endswith(".safetensors"))
+    # sidecar files hold tensors of another network (the vision tower): they are not shards of the language model's index
+    files = sorted(f for f in os.listdir(folder) if f.endswith(".safetensors") and f not in SIDECAR_FILES)
     placement = None
     idx = os.path.join(folder, "model.safetensors.index.json")
     if os.path.exists(idx):

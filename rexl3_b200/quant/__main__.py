@@ -18,6 +18,9 @@ def main(argv=None) -> int:
     p.add_argument("--out", required=True)
     p.add_argument("--bits", type=float, default=0.0, help="override the architecture's bits per weight (1, 1.5, ... 8)")
     p.add_argument("--mtp", action="store_true", help="dense family: add one multi-token-prediction block (eh_proj + one decoder layer + its norm) to the pack")
+    p.add_argument("--vision", default=None, metavar="CONFIG",
+                   help="dense family: store a vision tower of this built-in shape beside the pack (vision.safetensors + vision_config; random init "
+                        "from --seed, output width = the model's), for `rexl3-serve --vision-tower pack`")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--threads", type=int, default=0)
     p.add_argument("--layers", type=int, default=0, help="quantize only the first N layers (smoke runs)")
@@ -58,7 +61,14 @@ def main(argv=None) -> int:
         extra = {"calibration": {"rows": len(seqs), "cols": cols, "data": "synthetic uniform tokens", "damp": a.damp}}
     w = quantize.quantize_dense(cfg, fp, seed=a.seed, threads=a.threads, device=a.device, hessians=hessians, damp=a.damp, scale_search=a.scale_search)
     quantize.write_pack(a.out, w, extra)
-    print(f"rexl3-quant: wrote {a.out} ({cfg.name}, {cfg.bits:g} bpw, {cfg.n_layers} layers) in {time.time() - t0:.1f} s")
+    if a.vision:
+        import torch
+        from ..vision import tower as vt
+        if a.vision not in vt.CONFIGS:
+            p.error(f"unknown --vision {a.vision!r}; known: {sorted(vt.CONFIGS)}")
+        vt.save_tower(a.out, vt.VisionTower(dataclasses.replace(vt.CONFIGS[a.vision], out_dim=cfg.d_model), seed=a.seed, device="cpu", dtype=torch.bfloat16))
+    print(f"rexl3-quant: wrote {a.out} ({cfg.name}, {cfg.bits:g} bpw, {cfg.n_layers} layers{', vision tower ' + a.vision if a.vision else ''}) "
+          f"in {time.time() - t0:.1f} s")
     return 0
 
 

@@ -50,8 +50,9 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--expert-cache-file", default=None, help="the record file (default: experts.records inside the pack; written at first start)")
     p.add_argument("--expert-cache-direct", action="store_true", help="read the record file with O_DIRECT")
     p.add_argument("--vision-tower", default=None, metavar="CONFIG",
-                   help="serve image parts of chat messages through a vision tower of this built-in shape (random init, seed --vision-seed; its output "
-                        "width follows the model); without it image parts are refused by name")
+                   help="serve image parts of chat messages through a vision tower: `pack` = the tower stored beside the pack (vision.safetensors + "
+                        "vision_config), or a built-in shape with random-init weights (seed --vision-seed; its output width follows the model); "
+                        "without the flag image parts are refused by name")
     p.add_argument("--vision-seed", type=int, default=0)
     p.add_argument("--vision-max-pixels", type=int, default=14 * 14 * 4 * 1280, help="pixel budget an image is resized into before it is cut into patches")
     p.add_argument("--vision-max-images", type=int, default=8, help="images one request may carry")
@@ -358,15 +359,27 @@ def _vision(args, tok, fmt, info):
     import dataclasses
     from ..vision import tower as vt
     from .media import VisionIngress
-    if args.vision_tower not in vt.CONFIGS:
-        raise SystemExit(f"rexl3-serve: unknown --vision-tower {args.vision_tower!r}; known: {sorted(vt.CONFIGS)}")
-    vcfg = vt.CONFIGS[args.vision_tower]
+    from_pack = args.vision_tower == "pack"
+    folder = args.model if args.model and os.path.isdir(args.model) else None
+    if from_pack:
+        try:
+            vcfg = vt.config_from_pack(folder) if folder else None
+        except ValueError as e:
+            raise SystemExit(f"rexl3-serve: --vision-tower pack: {e}")
+        if vcfg is None:
+            raise SystemExit("rexl3-serve: --vision-tower pack: the pack (--model DIR) holds no vision tower (vision.safetensors + vision_config)")
+    elif args.vision_tower not in vt.CONFIGS:
+        raise SystemExit(f"rexl3-serve: unknown --vision-tower {args.vision_tower!r}; known: pack, {', '.join(sorted(vt.CONFIGS))}")
+    else:
+        vcfg = vt.CONFIGS[args.vision_tower]
     cfg = getattr(args, "_model_cfg", None)
     if cfg is not None:
         if not hasattr(cfg, "d_model") or type(cfg).__name__ not in ("DenseConfig", "MoEConfig"):
             raise SystemExit(f"rexl3-serve: --vision-tower: the `{cfg.name}` executor takes no image rows (dense and MoE GQA decoders do)")
         if getattr(args, "spec", "") == "mtp" or int(os.environ.get("WORLD_SIZE", "1")) > 1:
             raise SystemExit("rexl3-serve: --vision-tower runs on one rank and without --spec mtp")
+        if from_pack and vcfg.out_dim != cfg.d_model:
+            raise SystemExit(f"rexl3-serve: --vision-tower pack: the tower writes rows of width {vcfg.out_dim}, the model is {cfg.d_model} wide")
         vcfg = dataclasses.replace(vcfg, out_dim=cfg.d_model)
     placeholder = getattr(fmt, "image_placeholder", "<|vision_start|><|image_pad|><|vision_end|>")
     tid = tok.special_id("<|image_pad|>")
@@ -377,8 +390,10 @@ def _vision(args, tok, fmt, info):
 
     def make_tower():
         import torch
-        return vt.VisionTower(vcfg, seed=args.vision_seed, device="cuda" if cuda else "cpu", dtype=torch.bfloat16 if cuda else torch.float32)
-    info["vision"] = {"tower": vcfg.name, "out_dim": vcfg.out_dim, "patch": vcfg.patch, "merge": vcfg.merge, "weights": f"random init, seed {args.vision_seed}"}
+        dev, dt = ("cuda", torch.bfloat16) if cuda else ("cpu", torch.float32)
+        return vt.load_tower(folder, dev, dt) if from_pack else vt.VisionTower(vcfg, seed=args.vision_seed, device=dev, dtype=dt)
+    info["vision"] = {"tower": vcfg.name, "out_dim": vcfg.out_dim, "patch": vcfg.patch, "merge": vcfg.merge,
+                      "weights": "vision.safetensors of the pack" if from_pack else f"random init, seed {args.vision_seed}"}
     return VisionIngress(vcfg, make_tower, tid, placeholder, mrope=getattr(cfg, "mrope_sections", None) is not None, max_pixels=args.vision_max_pixels,
                          max_images=args.vision_max_images)
 

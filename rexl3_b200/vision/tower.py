@@ -85,10 +85,93 @@ def interpolation_table(grid_h: int, grid_w: int, pos_grid: int):
     return idx, wgt
 
 
+VISION_FILE = "vision.safetensors"
+_BLOCK_KEYS = ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "proj_w", "proj_b", "ln2_w", "ln2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")
+_TOP_KEYS = ("patch_w", "patch_b", "pos_table", "ln_w", "ln_b", "m1_w", "m1_b", "m2_w", "m2_b")
+
+
+def _flat(w: dict) -> dict:
+    out = {f"vision.{k}": w[k] for k in _TOP_KEYS}
+    for i, blk in enumerate(w["blocks"]):
+        out.update({f"vision.blocks.{i}.{k}": blk[k] for k in _BLOCK_KEYS})
+    return out
+
+
+def save_tower(folder: str, tower: "VisionTower") -> None:
+    """Writes the tower beside a pack: `vision.safetensors` (bf16 tensors `vision.*`) and a `vision_config` object in config.json."""
+    import dataclasses
+    import json
+    import os
+    from ..format import safetensors_io as sio
+    tensors, dtypes = {}, {}
+    for name, t in _flat(tower.w).items():
+        tensors[name] = t.detach().to("cpu", torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16)
+        dtypes[name] = "BF16"
+    sio.write_file(os.path.join(folder, VISION_FILE), tensors, {"format": "rexl3-vision-v1"}, dtypes)
+    path = os.path.join(folder, "config.json")
+    doc = json.load(open(path)) if os.path.exists(path) else {}
+    doc["vision_config"] = dataclasses.asdict(tower.cfg)
+    with open(path, "w") as f:
+        json.dump(doc, f, indent=1)
+
+
+def config_from_pack(folder: str) -> "VisionConfig | None":
+    """The pack's `vision_config`, or None when the pack has no tower.  Unknown keys are refused by name."""
+    import json
+    import os
+    path = os.path.join(folder, "config.json")
+    if not os.path.exists(path) or not os.path.exists(os.path.join(folder, VISION_FILE)):
+        return None
+    vc = json.load(open(path)).get("vision_config")
+    if not isinstance(vc, dict):
+        raise ValueError(f"{folder}: {VISION_FILE} is there but config.json has no vision_config")
+    known = {f.name for f in __import__("dataclasses").fields(VisionConfig)}
+    bad = sorted(set(vc) - known)
+    if bad:
+        raise ValueError(f"{folder}: vision_config has unknown keys {bad}")
+    cfg = VisionConfig(**vc)
+    cfg.validate()
+    return cfg
+
+
+def load_tower(folder: str, device="cuda", dtype=torch.bfloat16) -> "VisionTower":
+    """The tower stored beside a pack.  Every tensor the shape needs must be there with the right shape; surplus tensors are refused."""
+    import os
+    from ..format import safetensors_io as sio
+    cfg = config_from_pack(folder)
+    if cfg is None:
+        raise ValueError(f"{folder}: the pack holds no vision tower ({VISION_FILE} + vision_config)")
+    tower = VisionTower(cfg, seed=0, device="cpu", dtype=torch.float32)          # shapes (and a place to put the tensors)
+    want = _flat(tower.w)
+    scan = sio.read_header(os.path.join(folder, VISION_FILE))
+    if scan.issues:
+        raise ValueError(f"{folder}/{VISION_FILE}: {scan.issues[0]}")
+    have = dict(scan.entries)
+    missing, extra = sorted(set(want) - set(have)), sorted(set(have) - set(want))
+    if missing or extra:
+        raise ValueError(f"{folder}/{VISION_FILE}: missing {missing[:3]}{'...' if len(missing) > 3 else ''}, unexpected {extra[:3]}{'...' if len(extra) > 3 else ''}")
+    def put(dst: dict, key: str, name: str):
+        e = have[name]
+        if e.dtype != "BF16" or tuple(e.shape) != tuple(dst[key].shape):
+            raise ValueError(f"{VISION_FILE}: {name} is {e.dtype} {list(e.shape)}, the shape needs BF16 {list(dst[key].shape)}")
+        bits = sio.read_tensor(folder, e)
+        dst[key] = torch.from_numpy(np.array(bits, copy=True).view(np.int16)).view(torch.bfloat16).to(device=device, dtype=dtype)
+    for k in _TOP_KEYS:
+        put(tower.w, k, f"vision.{k}")
+    for i, blk in enumerate(tower.w["blocks"]):
+        for k in _BLOCK_KEYS:
+            put(blk, k, f"vision.blocks.{i}.{k}")
+    tower.device, tower.dtype = torch.device(device), dtype
+    tower.inv_freq = tower.inv_freq.to(tower.device)
+    tower.from_pack = True
+    return tower
+
+
 class VisionTower:
     def __init__(self, cfg: VisionConfig, seed: int = 0, device="cuda", dtype=torch.bfloat16):
         cfg.validate()
         self.cfg, self.device, self.dtype, self.seed = cfg, torch.device(device), dtype, seed
+        self.from_pack = False
         self.w = _weights(cfg, seed, self.device, dtype)
         hd = cfg.head_dim
         self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))).to(self.device)   # hd / 4 frequencies per axis

@@ -118,3 +118,40 @@ def test_chat_route_serves_an_image_on_the_cuda_backend():
             assert c.get("/v1/models").json()["data"][0]["vision"]["tower"] == "test-vit"
     finally:
         handle.stop()
+
+
+def test_chat_route_with_the_packs_own_tower(tmp_path):
+    """A pack with a tower beside it (vision.safetensors + vision_config): `--vision-tower pack` loads it, the reply follows the pixels, and
+    the rows equal what the stored tower gives on the host."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from starlette.testclient import TestClient
+    from rexl3_b200.models import dense
+    from rexl3_b200.quant import quantize
+    from rexl3_b200.server.main import make_app, parser
+    from rexl3_b200.vision import tower
+    cfg = dense.CONFIGS["test-hd128"]
+    folder = str(tmp_path / "pack")
+    quantize.write_pack(folder, dense.random_weights(cfg, seed=3))
+    tower.save_tower(folder, tower.VisionTower(tower.CONFIGS["test-vit"], seed=9, device="cpu", dtype=torch.bfloat16))
+    args = parser().parse_args(["--backend", "cuda", "--model", folder, "--slots", "3", "--max-model-len", "1024", "--prefill-chunk", "256",
+                                "--kv-tokens", "4096", "--window-rows", "16", "--vision-tower", "pack", "--vision-max-pixels", str(28 * 28 * 40)])
+    app, handle = make_app(args)
+    try:
+        assert handle.wait_ready(120), handle.error
+        with TestClient(app) as c:
+            def ask(seed):
+                r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [_part(seed), {"type": "text", "text": " what?"}]}],
+                                                         "max_tokens": 5, "temperature": 0, "return_token_ids": True})
+                assert r.status_code == 200, r.text
+                return r.json()["choices"][0]["token_ids"]
+            assert ask(1) == ask(1) and ask(1) != ask(2)
+            v = c.get("/v1/models").json()["data"][0]["vision"]
+            assert v["weights"].startswith("vision.safetensors") and v["out_dim"] == cfg.d_model
+    finally:
+        handle.stop()
+    # a pack without a tower is refused at start-up, by name
+    bare = str(tmp_path / "bare")
+    quantize.write_pack(bare, dense.random_weights(cfg, seed=3))
+    with pytest.raises(SystemExit, match="holds no vision tower"):
+        make_app(parser().parse_args(["--backend", "cuda", "--model", bare, "--vision-tower", "pack"]))

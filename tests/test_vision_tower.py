@@ -96,3 +96,33 @@ def test_tower_on_the_device_and_image_rows_reach_the_decoder():
     torch.cuda.synchronize()
     m.check()
     assert torch.isfinite(with_image).all() and (with_image - text_only).abs().max() > 1e-3
+
+
+def test_tower_round_trips_through_a_pack_folder(tmp_path):
+    """save_tower / load_tower: same rows bit for bit (both compute in fp32 from the stored bf16 tensors), config in config.json, refusals by name."""
+    import json
+    cfg = tower.CONFIGS["test-vit"]
+    tw = tower.VisionTower(cfg, seed=5, device="cpu", dtype=torch.bfloat16)
+    (tmp_path / "config.json").write_text(json.dumps({"architectures": ["X"], "hidden_size": 512}))
+    tower.save_tower(str(tmp_path), tw)
+    doc = json.loads((tmp_path / "config.json").read_text())
+    assert doc["hidden_size"] == 512 and doc["vision_config"]["hidden"] == cfg.hidden and doc["vision_config"]["out_dim"] == cfg.out_dim
+    assert tower.config_from_pack(str(tmp_path)) == cfg
+    back = tower.load_tower(str(tmp_path), "cpu", torch.float32)
+    assert back.from_pack
+    rng = np.random.default_rng(0)
+    inp = preprocess.preprocess_image(rng.integers(0, 256, size=(50, 70, 3), dtype=np.uint8), min_pixels=28 * 28, max_pixels=28 * 28 * 9)
+    a = tw.reference("cpu").encode(inp.pixel_values, inp.grid_thw, inp.position_ids)
+    b = back.encode(inp.pixel_values, inp.grid_thw, inp.position_ids)
+    assert torch.equal(a, b)
+    # a folder without the file has no tower; a surplus or a missing tensor, or an unknown config key, is refused by name
+    assert tower.config_from_pack(str(tmp_path / "nowhere")) is None
+    doc["vision_config"]["colour"] = 1
+    (tmp_path / "config.json").write_text(json.dumps(doc))
+    with pytest.raises(ValueError, match="unknown keys \\['colour'\\]"):
+        tower.config_from_pack(str(tmp_path))
+    del doc["vision_config"]["colour"]
+    doc["vision_config"]["depth"] = 3
+    (tmp_path / "config.json").write_text(json.dumps(doc))
+    with pytest.raises(ValueError, match="missing \\['vision.blocks.2"):
+        tower.load_tower(str(tmp_path), "cpu", torch.float32)
