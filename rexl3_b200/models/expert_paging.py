@@ -37,39 +37,72 @@ def _parts_of(gu, dn):
             np.ascontiguousarray(dn.trellis), np.ascontiguousarray(dn.suh, dtype=np.float16), np.ascontiguousarray(dn.svh, dtype=np.float16)]
 
 
-def write_records(weights, path: str, overwrite: bool = False) -> Layout:
+def write_records(weights, path: str, overwrite: bool = False, tag: str = "") -> Layout:
     """weights: models.dense.HostWeights of an MoE model (layers with experts_gu / experts_down).  Writes the record file unless one of the
-    expected size is there already (and `overwrite` is off); -> Layout."""
+    expected size and the same `tag` is there already (and `overwrite` is off); -> Layout.  The tag (the pack's fingerprint) sits in
+    `path + ".tag"`: a record file left by another pack of the same shape is rewritten, not trusted."""
+    n_exp = len(weights.layers[0].experts_gu)
+    if any(len(lay.experts_gu) != n_exp for lay in weights.layers):
+        raise ValueError("every layer must hold the same number of experts")
+    return write_records_of(path, list(range(len(weights.layers))), n_exp, PARTS,
+                            lambda li, e: _parts_of(weights.layers[li].experts_gu[e], weights.layers[li].experts_down[e]),
+                            weights.layers[0].experts_gu[0].codebook, overwrite, tag)
+
+
+MX_PARTS = ("gu_w", "gu_s", "dn_w", "dn_s")
+
+
+def write_mx_records(weights, path: str, overwrite: bool = False, tag: str = "") -> Layout:
+    """The MXFP4 experts of a latent-attention MoE model (models.mla.HostMla: routed layers hold ex_gu / ex_down = [(nibbles, scales)]): one
+    record per (routed layer, expert) with the gate|up nibbles and scale bytes and the down nibbles and scale bytes."""
+    routed = [li for li, lay in enumerate(weights.layers) if lay.router is not None]
+    if not routed:
+        raise ValueError("the model has no routed layers")
+    n_exp = len(weights.layers[routed[0]].ex_gu)
+
+    def parts(li, e):
+        lay = weights.layers[li]
+        return [np.ascontiguousarray(lay.ex_gu[e][0]).view(np.uint8), np.ascontiguousarray(lay.ex_gu[e][1]),
+                np.ascontiguousarray(lay.ex_down[e][0]).view(np.uint8), np.ascontiguousarray(lay.ex_down[e][1])]
+    return write_records_of(path, routed, n_exp, MX_PARTS, parts, "mxfp4", overwrite, tag)
+
+
+def write_records_of(path: str, layers: list, n_exp: int, names, get_parts, codebook: str, overwrite: bool = False, tag: str = "") -> Layout:
+    """The general form: `get_parts(layer, expert)` -> the expert's tensors (numpy, in the order of `names`), the same shapes for every expert
+    of every layer in `layers`."""
     import os
-    first = _parts_of(weights.layers[0].experts_gu[0], weights.layers[0].experts_down[0])
+    first = get_parts(layers[0], 0)
     parts, off = [], 0
-    for name, a in zip(PARTS, first):
+    for name, a in zip(names, first):
         parts.append((name, off, a.nbytes, tuple(a.shape), a.dtype.name))
         off = (off + a.nbytes + ec.PART_ALIGN - 1) // ec.PART_ALIGN * ec.PART_ALIGN
     expert_bytes = parts[-1][1] + parts[-1][2]
     record = (expert_bytes + ec.PAGE - 1) // ec.PAGE * ec.PAGE
     index, pos = {}, 0
-    n_exp = len(weights.layers[0].experts_gu)
-    if not overwrite and os.path.exists(path) and os.path.getsize(path) == record * n_exp * len(weights.layers):
-        for li in range(len(weights.layers)):
+    same_tag = os.path.exists(path + ".tag") and open(path + ".tag").read() == tag if tag else not os.path.exists(path + ".tag")
+    if not overwrite and same_tag and os.path.exists(path) and os.path.getsize(path) == record * n_exp * len(layers):
+        for li in layers:
             for e in range(n_exp):
                 index[(li, e)] = (pos, expert_bytes)
                 pos += record
-        return Layout(path, index, parts, expert_bytes, len(weights.layers), n_exp, weights.layers[0].experts_gu[0].codebook)
+        return Layout(path, index, parts, expert_bytes, len(layers), n_exp, codebook)
     with open(path, "wb") as f:
-        for li, lay in enumerate(weights.layers):
-            if len(lay.experts_gu) != len(weights.layers[0].experts_gu):
-                raise ValueError("every layer must hold the same number of experts")
-            for e, (gu, dn) in enumerate(zip(lay.experts_gu, lay.experts_down)):
+        for li in layers:
+            for e in range(n_exp):
                 buf = bytearray(record)
-                for (name, o, n, shape, dt), a in zip(parts, _parts_of(gu, dn)):
+                for (name, o, n, shape, dt), a in zip(parts, get_parts(li, e)):
                     if a.shape != shape or a.dtype.name != dt:
-                        raise ValueError(f"expert ({li}, {e}) part {name} has shape {a.shape}, the first expert has {shape}")
+                        raise ValueError(f"expert ({li}, {e}) part {name} has shape {a.shape} {a.dtype.name}, the first expert has {shape} {dt}")
                     buf[o:o + n] = a.tobytes()
                 f.write(buf)
                 index[(li, e)] = (pos, expert_bytes)
                 pos += record
-    return Layout(path, index, parts, expert_bytes, len(weights.layers), len(weights.layers[0].experts_gu), weights.layers[0].experts_gu[0].codebook)
+    if tag:
+        with open(path + ".tag", "w") as f:
+            f.write(tag)
+    elif os.path.exists(path + ".tag"):
+        os.remove(path + ".tag")
+    return Layout(path, index, parts, expert_bytes, len(layers), n_exp, codebook)
 
 
 class StackSlab(ec.Slab):

@@ -319,8 +319,15 @@ class _Local:
 
 class MlaMoEGPU:
     def __init__(self, w: "HostMla | MlaConfig", num_pages: int, max_rows: int = 256, max_seqs: int = 64, max_blocks_per_seq: int = 256, device="cuda",
-                 max_prefill_rows: int = 4096, seed: int = 0, heads=None, experts=None, comm=None, rank: int = 0):
+                 max_prefill_rows: int = 4096, seed: int = 0, heads=None, experts=None, comm=None, rank: int = 0, expert_paging=None):
+        """`expert_paging` = dict(path=FILE, budget_bytes=N[, fill_threads, direct]): the routed MXFP4 experts stay in a record file (written from
+        the host weights when it is not there yet) and are paged into a device slab of N bytes as the router asks for them
+        (models/expert_paging.py); one rank, weights from host tensors.  Each routed layer then reads its picks on the host."""
         self.K = K
+        self.paged = None
+        self._paging = expert_paging
+        if expert_paging is not None and (isinstance(w, MlaConfig) or heads is not None or experts is not None or comm is not None):
+            raise ValueError("expert paging runs on one rank that owns every head and expert, over host weights")
         self.device = device
         self.cfg = cfg = w if isinstance(w, MlaConfig) else w.cfg
         self.h_lo, self.h_hi = heads or (0, cfg.n_heads)
@@ -352,6 +359,13 @@ class MlaMoEGPU:
         hl, hh, el, eh = self.h_lo, self.h_hi, self.e_lo, self.e_hi
         self.embed = t(w.embed, torch.bfloat16)
         self.layers = []
+        slab = None
+        if self._paging is not None:
+            from . import expert_paging as xp
+            pg = dict(self._paging)
+            layout = xp.write_mx_records(w, pg.pop("path"), tag=pg.pop("tag", ""))
+            self.paged = xp.PagedExperts(layout, pg.pop("budget_bytes"), dev, **pg)
+            slab = self.paged.slab.t          # every routed layer reads "its experts" from the same slab, through slot ids
         for lay in w.layers:
             qb = lay.q_b
             H = self.cfg.n_heads      # this rank's heads, then (sparse attention) the index-query columns every rank keeps
@@ -364,7 +378,10 @@ class MlaMoEGPU:
                      ffn_norm=t(lay.ffn_norm, torch.bfloat16), gate_up=up(lay.gate_up), down=up(lay.down), router=None)
             if self.cfg.dsa:
                 L.update(idx_ln_w=t(lay.idx_ln_w, torch.float32), idx_ln_b=t(lay.idx_ln_b, torch.float32), idx_ape=t(lay.idx_ape, torch.float32))
-            if lay.router is not None:
+            if lay.router is not None and slab is not None:
+                L.update(router=t(lay.router, torch.bfloat16), router_bias=t(lay.router_bias, torch.float32),
+                         gu_w=slab["gu_w"], gu_s=slab["gu_s"], dn_w=slab["dn_w"], dn_s=slab["dn_s"])
+            elif lay.router is not None:
                 L.update(router=t(lay.router, torch.bfloat16), router_bias=t(lay.router_bias, torch.float32),
                          gu_w=torch.from_numpy(np.stack([e[0].view(np.uint8) for e in lay.ex_gu[el:eh]])).to(dev),
                          gu_s=torch.from_numpy(np.stack([e[1] for e in lay.ex_gu[el:eh]])).to(dev),
@@ -437,8 +454,8 @@ class MlaMoEGPU:
         for L in self.layers:
             n += sum(L[k].nbytes for k in ("qkv_a", "q_b", "o", "gate_up", "down")) + (L["w_uk"].numel() + L["w_uv"].numel()) * 2
             if L["router"] is not None:
-                n += sum(L[k].numel() for k in ("gu_w", "gu_s", "dn_w", "dn_s")) + L["router"].numel() * 2
-        return n
+                n += L["router"].numel() * 2 + (0 if self.paged is not None else sum(L[k].numel() for k in ("gu_w", "gu_s", "dn_w", "dn_s")))
+        return n + (self.paged.slab.nbytes() if self.paged is not None else 0)
 
     # ------------------------------------------------------------------ buffers
     def _alloc(self, R):
@@ -484,8 +501,13 @@ class MlaMoEGPU:
         self.attn_scratch = torch.empty(n_scratch, dtype=torch.float32, device=dev)
         self.pick_ids, self.pick_w = i32(R * k), torch.zeros(R * k, dtype=torch.float32, device=dev)
         E = cfg.n_experts
-        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(E + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
-        El = self.e_hi - self.e_lo      # the tile table only ever names owned experts
+        S = self.paged.slots if self.paged is not None else 0            # paged experts: the kernels see slot ids, 0 .. S - 1
+        self.offs, self.pos_of_pair, self.pair_of_pos, self.expert_of_pos, self.total = i32(max(E, S) + 1), i32(R * k), i32(R * k), i32(R * k), i32(1)
+        El = max(self.e_hi - self.e_lo, S)      # the tile table only ever names owned experts (or slots)
+        if S:
+            self.pick_slot = i32(R * k)
+            self.slot_table_h = torch.zeros(E, dtype=torch.int32).pin_memory()
+            self.slot_table = i32(E)
         self.max_tiles = {"decode": El + (Rw * k + 31) // 32, "prefill": El + (R * k + 127) // 128}
         self.router_logits = torch.empty(R, E, dtype=torch.float32, device=dev)
         self.tile_tab = i32(3 * max(self.max_tiles.values()))
@@ -642,10 +664,20 @@ class MlaMoEGPU:
             mt = self.max_tiles[cls]
             _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
                                           self.router_logits.data_ptr(), self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st()), "rx_moe_router2")
-            _lib.check(Lib.rx_moe_plan(self.pick_ids.data_ptr(), pairs, E, self.e_lo, self.e_hi, tile_rows, mt, self.offs.data_ptr(), self.pos_of_pair.data_ptr(),
+            picks, En, e_lo, e_hi = self.pick_ids, E, self.e_lo, self.e_hi
+            if self.paged is not None:
+                # the picks come to the host (every kernel queued so far has then run: the last call's leases can go), the experts they name
+                # are made resident, and the rest of the layer runs over slot ids
+                ids_h = self.pick_ids[:pairs].cpu().numpy()
+                self.paged.release_held()
+                self.slot_table_h.copy_(torch.from_numpy(self.paged.resolve(li, ids_h)))
+                self.slot_table.copy_(self.slot_table_h, non_blocking=True)
+                torch.index_select(self.slot_table, 0, self.pick_ids[:pairs].long(), out=self.pick_slot[:pairs])
+                picks, En, e_lo, e_hi = self.pick_slot, self.paged.slots, 0, self.paged.slots
+            _lib.check(Lib.rx_moe_plan(picks.data_ptr(), pairs, En, e_lo, e_hi, tile_rows, mt, self.offs.data_ptr(), self.pos_of_pair.data_ptr(),
                                        self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.tile_tab.data_ptr(), self.total.data_ptr(), st()),
                        "rx_moe_plan")
-            _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), self.pick_ids.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, None, self.xs.data_ptr(), st()),
+            _lib.check(Lib.rx_moe_gather_rot(xn.data_ptr(), picks.data_ptr(), self.pos_of_pair.data_ptr(), pairs, k, d, None, self.xs.data_ptr(), st()),
                        "rx_moe_gather_rot")
             sg_, sd_ = self.mx_splits[cls]
             Fe = cfg.expert_ffn
@@ -653,7 +685,7 @@ class MlaMoEGPU:
             _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), sg_, cap, Fe, self.expert_of_pos.data_ptr(), self.total.data_ptr(), None, None,
                                              self.xs2.data_ptr(), st()), "rx_moe_swiglu_rot")
             self._mx(self.xs2, L["dn_w"], L["dn_s"], Fe, d, sd_, cap, mt, tile_rows)
-            _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), sd_, cap, M, d, k, self.pick_ids.data_ptr(), self.pick_w.data_ptr(), self.pos_of_pair.data_ptr(),
+            _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), sd_, cap, M, d, k, picks.data_ptr(), self.pick_w.data_ptr(), self.pos_of_pair.data_ptr(),
                                           None, self.shared.data_ptr() if run_shared else None, ctypes.byref(tgt2[0]), st()), "rx_moe_combine")
             _lib.count(8)
             if multi:
@@ -671,7 +703,7 @@ class MlaMoEGPU:
     def _mx(self, xs, wq, sc, Kd, N, splits, cap, max_tiles, tile_rows):
         if splits * cap * N > self.part.numel():
             raise _lib.KernelError("grouped MXFP4 partials exceed the scratch buffer")
-        El = self.e_hi - self.e_lo
+        El = self.paged.slots if self.paged is not None else self.e_hi - self.e_lo      # paged: the stacks are the slab, one row per slot
         wbase = wq.data_ptr() - self.e_lo * N * (Kd // 2)
         sbase = sc.data_ptr() - self.e_lo * N * (Kd // 32)
         _lib.check(_lib.load().rx_mxfp4_gemm_grouped(xs.data_ptr(), cap, Kd, ctypes.c_void_p(wbase), ctypes.c_void_p(sbase), self.e_lo + El, N,

@@ -214,7 +214,7 @@ class MoEGPU(DenseGPU):
         if self._paging is not None:
             from . import expert_paging as xp
             pg = dict(self._paging)
-            layout = xp.write_records(w, pg.pop("path"))       # (an existing file of the right size is kept)
+            layout = xp.write_records(w, pg.pop("path"), tag=pg.pop("tag", ""))       # (an existing file of the right size and tag is kept)
             self.paged = xp.PagedExperts(layout, pg.pop("budget_bytes"), device, **pg)
             t, cb = self.paged.slab.t, layout.codebook
             # every layer reads "its experts" from the same slab: a layer's call translates expert ids to slot ids first

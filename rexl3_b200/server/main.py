@@ -45,7 +45,7 @@ def parser() -> argparse.ArgumentParser:
     p.add_argument("--no-drafts", action="store_true")
     p.add_argument("--max-drafts", type=int, default=4)
     p.add_argument("--expert-cache-mib", type=int, default=0,
-                   help="MoE packs on one GPU: keep the routed experts in a record file and page them into a device slab of this many MiB as the "
+                   help="MoE packs (EXL3 experts, or MXFP4 experts under latent attention) on one GPU: keep the routed experts in a record file and page them into a device slab of this many MiB as the "
                         "router asks for them (hits, misses, bytes read and evictions are on /metrics); 0 = every expert resident")
     p.add_argument("--expert-cache-file", default=None, help="the record file (default: experts.records inside the pack; written at first start)")
     p.add_argument("--expert-cache-direct", action="store_true", help="read the record file with O_DIRECT")
@@ -226,6 +226,8 @@ def build(args):
                 if is_moe and not is_mla and args.expert_cache_mib:
                     # paged experts: the slab stands where the expert stacks would be
                     wbytes += (args.expert_cache_mib << 20) - int(cfg.n_layers * cfg.n_experts * 3 * cfg.d_model * cfg.expert_ffn * cfg.bits / 8)
+                if is_mla and args.expert_cache_mib:
+                    wbytes += (args.expert_cache_mib << 20) - int((cfg.n_layers - cfg.n_dense) * cfg.n_experts * 3 * cfg.d_model * cfg.expert_ffn * (0.5 + 1 / 32))
                 mm = ModelMemory(wbytes, kvb, activation_reserve=2 << 30)
                 adm = Admission(free, 1 << 30, mm, args.slots).with_max_context(args.max_model_len).with_kv_tokens(kv_tokens)
                 adm.check(min(args.max_model_len, 1))     # fail closed: a plan that can never hold one token is refused at boot
@@ -234,15 +236,17 @@ def build(args):
                                        f"{adm.capacity >> 20} MiB are available after weights and reserve")
                 common = dict(num_pages=pages, max_rows=min(256, args.window_rows), max_seqs=args.slots,
                               max_blocks_per_seq=-(-args.max_model_len // dense.PAGE) + 1, max_prefill_rows=args.prefill_chunk)
+                paging = None
+                if args.expert_cache_mib:
+                    if not (is_mla or is_moe):
+                        raise RuntimeError("--expert-cache-mib: this model has no routed experts")
+                    if weights is None:
+                        raise RuntimeError("--expert-cache-mib pages the experts of a pack (--model DIR), not of a random-init config")
+                    paging = dict(path=args.expert_cache_file or os.path.join(folder, "experts.records"), budget_bytes=args.expert_cache_mib << 20,
+                                  direct=args.expert_cache_direct, tag=info.get("pack_fingerprint", ""))
                 if is_mla:
-                    model = mla_models.MlaMoEGPU(weights if weights is not None else cfg, **common)
+                    model = mla_models.MlaMoEGPU(weights if weights is not None else cfg, expert_paging=paging, **common)
                 elif is_moe:
-                    paging = None
-                    if args.expert_cache_mib:
-                        if weights is None:
-                            raise RuntimeError("--expert-cache-mib pages the experts of a pack (--model DIR), not of a random-init config")
-                        paging = dict(path=args.expert_cache_file or os.path.join(folder, "experts.records"), budget_bytes=args.expert_cache_mib << 20,
-                                      direct=args.expert_cache_direct)
                     model = moe_models.MoEGPU(weights if weights is not None else cfg, expert_paging=paging, **common)
                 elif is_hybrid:
                     model = hybrid_models.HybridGPU(weights if weights is not None else cfg, **common)
