@@ -281,6 +281,7 @@ class DenseGpuBackend(Backend):
 
     def prefill_slices(self, items, candidates):
         m = self.m
+        self._flush_moves()
         for slot, start, toks, _ in items:
             if start != self.len[slot]:
                 raise BackendError(f"prefill at {start} but slot {slot} holds {self.len[slot]} tokens", fatal=False)
@@ -337,6 +338,7 @@ class DenseGpuBackend(Backend):
     # ------------------------------------------------------------------ decode / verify window
     def step(self, reqs, candidates):
         m = self.m
+        self._flush_moves()          # (a multi-rank backend tells the other ranks: before this window is announced)
         specs = []
         for r in reqs:
             if r.first_position != self.len[r.slot]:
@@ -389,6 +391,7 @@ class DenseGpuBackend(Backend):
         m = self.m
         if not self.supports_trees():
             raise BackendError("this backend runs no tree windows", fatal=False)
+        self._flush_moves()
         VW, CH = self.VBT_W, self.VBT_W // 2 * PAGE             # private-table width (pages), keys per attention chunk
         self._host_writable()
         h = self.h_rows.numpy()
@@ -464,6 +467,7 @@ class DenseGpuBackend(Backend):
         m.window_seq_rows = max(len(r.tokens) for r in reqs)
         bucket = min(m.max_ctx_alloc, (deepest + CTX_BUCKET - 1) // CTX_BUCKET * CTX_BUCKET)
         count = max(1, min(64, candidates))
+        self._announce_tree_window(M, count, bucket, nsb)
         self._upload_rows(M)
         self.d_tree_base[:M].copy_(self.h_tree_base[:M], non_blocking=True)
         self.d_vbt[:M].copy_(self.h_vbt[:M], non_blocking=True)
@@ -682,6 +686,9 @@ class DenseGpuBackend(Backend):
 
     def _announce_window(self, M: int, count: int, bucket: int) -> None:
         """Hook for multi-rank backends: tell the other ranks what is about to run (before the block-table dirty set is cleared)."""
+
+    def _announce_tree_window(self, M: int, count: int, bucket: int, tree_n: int) -> None:
+        """The same for a window of draft trees (the tree arrays are staged by then)."""
 
     def _window(self, M: int, count: int, bucket: int) -> None:
         d = self.d_rows

@@ -20,7 +20,9 @@ from ..utils import trace
 from .backend import BackendError, RowOutput
 from .gpu_backend import DenseGpuBackend
 
-OP_STOP, OP_WINDOW, OP_PREFILL, OP_MARK, OP_SYNC = 0, 1, 2, 3, 4
+OP_STOP, OP_WINDOW, OP_PREFILL, OP_MARK, OP_SYNC, OP_TREE, OP_MOVES = 0, 1, 2, 3, 4, 5, 6
+# OP_TREE: a window of draft trees.  Payload: the rows, the dirty block-table rows, then tree_base [M], the private tables [M x W] and the
+# row copies [n x 3]; head[9] = n, head[10] = W.  OP_MOVES: head[1] = n row copies [n x 3] to apply to every layer's caches (an accepted path).
 HEAD = 16
 SMALL = 8192       # words of the fixed first broadcast
 
@@ -40,6 +42,8 @@ class _TpExec:
         self.x_pf_h = torch.zeros(4, max_slots, dtype=torch.int32).pin_memory()
         self.x_pf = torch.zeros(4, max_slots, dtype=torch.int32, device=dev)
         self.msg = torch.zeros(SMALL, dtype=torch.int32)
+        self.x_tree = None          # (tree_base, private tables, row copies) staging: (host pinned, device) pairs, made on first use
+        self.x_moves = None
         self.tp_graphs = {}
         self.tp_graph_kernels = {}
         self.marks = []
@@ -47,29 +51,42 @@ class _TpExec:
         self._staged_pending = False
 
     # ---- launches
-    def run_window_eager(self, M, count, bucket):
+    def tree_staging(self):
+        if self.x_tree is None:
+            from ..ops import kernels as _K
+            dev, R, W = self.sh.device, self.sh.max_rows, _K.attn_vbt_width()
+            mk = lambda *shape: (torch.zeros(*shape, dtype=torch.int32).pin_memory(), torch.zeros(*shape, dtype=torch.int32, device=dev))  # noqa: E731
+            self.x_tree = (mk(R), mk(R, W), mk(4096, 3))
+            self.x_moves = mk(256, 3)
+        return self.x_tree
+
+    def run_window_eager(self, M, count, bucket, tree_n=0):
         d = self.x_rows
         out = None
-        for p in self.sh.phases(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.x_bt, max_ctx=bucket, cand_count=count):
+        tree = None
+        if tree_n:
+            (_, tb), (_, vbt), (_, spread) = self.tree_staging()
+            tree = (tb[:M], vbt[:M], spread, tree_n)
+        for p in self.sh.phases(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.x_bt, max_ctx=bucket, cand_count=count, tree=tree):
             out = p()
         return out
 
-    def run_window(self, M, count, bucket) -> int:
+    def run_window(self, M, count, bucket, tree_n=0) -> int:
         """Runs one decode / verify window; returns the number of kernels launched (replayed)."""
         from ..ops import lib as _oplib
         if not self.use_graphs:
             n0 = _oplib.launch_count
-            self.run_window_eager(M, count, bucket)
+            self.run_window_eager(M, count, bucket, tree_n)
             return _oplib.launch_count - n0
-        key = (M, count, bucket, getattr(self.sh, "window_seq_rows", 1))
+        key = (M, count, bucket, getattr(self.sh, "window_seq_rows", 1), tree_n)
         g = self.tp_graphs.get(key)
         if g is None:
-            self.run_window_eager(M, count, bucket)       # every rank runs this in the same step, so peers are there
+            self.run_window_eager(M, count, bucket, tree_n)       # every rank runs this in the same step, so peers are there
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = _oplib.launch_count
             with torch.cuda.graph(g):
-                self.run_window_eager(M, count, bucket)
+                self.run_window_eager(M, count, bucket, tree_n)
             self.tp_graph_kernels[key] = _oplib.launch_count - n0
             self.tp_graphs[key] = g
             dist.barrier(group=self.ctrl)                 # capture time differs per rank: start the replay together
@@ -107,6 +124,15 @@ class _TpExec:
         if self._staged_pending:
             self._staged.synchronize()          # the previous message's copies may still be queued behind its kernels
             self._staged_pending = False
+        if op == OP_MOVES:
+            self.tree_staging()
+            mh, md = self.x_moves
+            mh.numpy()[:M] = payload[:3 * M].reshape(M, 3)
+            md[:M].copy_(mh[:M], non_blocking=True)
+            self._staged.record()
+            self._staged_pending = True
+            self.sh.move_kv_rows(md, M)
+            return True
         self.x_rows_h.numpy()[:, :M] = payload[k:k + 5 * M].reshape(5, M)
         k += 5 * M
         if nseq:
@@ -119,16 +145,31 @@ class _TpExec:
         for _ in range(n_dirty):
             bt[int(payload[k])] = payload[k + 1:k + 1 + nb]
             k += 1 + nb
+        tree_n = 0
+        if op == OP_TREE:
+            tree_n, W = int(head[9]), int(head[10])
+            (tbh, tbd), (vh, vd), (sh_, sd) = self.tree_staging()
+            if W != vh.shape[1]:
+                raise BackendError(f"the leader's private tables are {W} pages wide, this rank's {vh.shape[1]}", fatal=True)
+            tbh.numpy()[:M] = payload[k:k + M]
+            k += M
+            vh.numpy()[:M] = payload[k:k + M * W].reshape(M, W)
+            k += M * W
+            sh_.numpy()[:tree_n] = payload[k:k + 3 * tree_n].reshape(tree_n, 3)
+            k += 3 * tree_n
+            tbd[:M].copy_(tbh[:M], non_blocking=True)
+            vd[:M].copy_(vh[:M], non_blocking=True)
+            sd[:tree_n].copy_(sh_[:tree_n], non_blocking=True)
         self.x_rows[:, :M].copy_(self.x_rows_h[:, :M], non_blocking=True)
         if n_dirty:
             self.x_bt.copy_(self.x_bt_h, non_blocking=True)
-        if op != OP_WINDOW:
+        if op not in (OP_WINDOW, OP_TREE):
             self.x_pf[:, :nseq].copy_(self.x_pf_h[:, :nseq], non_blocking=True)
         self._staged.record()
         self._staged_pending = True
-        if op == OP_WINDOW:
+        if op in (OP_WINDOW, OP_TREE):
             self.sh.window_seq_rows = max(1, max_qlen)     # a window's message carries its longest run of rows per sequence in this field
-            self.run_window(M, count, bucket)
+            self.run_window(M, count, bucket, tree_n)
         else:
             self.run_prefill(M, nseq, max_qlen, last_rows, count)
         return True
@@ -183,13 +224,17 @@ class DenseTpBackend(DenseGpuBackend):
         self.ex.x_rows_h, self.ex.x_rows = self.h_rows, self.d_rows
         self.ex.x_bt_h, self.ex.x_bt = self.h_bt, self.d_bt
         self.ex.x_pf_h, self.ex.x_pf = self.h_pf, self.d_pf
+        self.ex.x_tree = ((self.h_tree_base, self.d_tree_base), (self.h_vbt, self.d_vbt), (self.h_spread, self.d_spread))
+        self.ex.x_moves = (self.h_moves, self.d_moves)
         self.ctrl_bytes = 0
         self.commands = 0
 
     # ---- control plane
-    def _send(self, op, M=0, count=0, bucket=0, nseq=0, max_qlen=0, last_rows=()):
+    def _send(self, op, M=0, count=0, bucket=0, nseq=0, max_qlen=0, last_rows=(), tree_n=0, moves=None):
         parts = []
-        if op in (OP_WINDOW, OP_PREFILL):
+        if op == OP_MOVES:
+            parts.append(np.asarray(moves, dtype=np.int32).reshape(-1))
+        if op in (OP_WINDOW, OP_PREFILL, OP_TREE):
             parts.append(self.h_rows.numpy()[:, :M].reshape(-1))
             if nseq:
                 parts.append(self.h_pf.numpy()[:, :nseq].reshape(-1))
@@ -199,12 +244,15 @@ class DenseTpBackend(DenseGpuBackend):
             for s in dirty:
                 parts.append(np.asarray([s], dtype=np.int32))
                 parts.append(bt[s])
+            if op == OP_TREE:
+                parts += [self.h_tree_base.numpy()[:M], self.h_vbt.numpy()[:M].reshape(-1), self.h_spread.numpy()[:tree_n].reshape(-1)]
         else:
             dirty = []
         payload = np.concatenate(parts).astype(np.int32, copy=False) if parts else np.zeros(0, dtype=np.int32)
         msg = self.ex.msg.numpy()
         msg[:HEAD] = 0
         msg[:9] = [op, M, count, bucket, nseq, max_qlen, len(last_rows), len(dirty), payload.size]
+        msg[9], msg[10] = tree_n, self.VBT_W
         fits = HEAD + payload.size <= SMALL
         if fits:
             msg[HEAD:HEAD + payload.size] = payload
@@ -223,11 +271,29 @@ class DenseTpBackend(DenseGpuBackend):
     def _announce_window(self, M, count, bucket):
         self._send(OP_WINDOW, M, count, bucket, 0, getattr(self.m, "window_seq_rows", 1))
 
+    def _announce_tree_window(self, M, count, bucket, tree_n):
+        self._send(OP_TREE, M, count, bucket, 0, getattr(self.m, "window_seq_rows", 1), tree_n=tree_n)
+
+    def supports_trees(self) -> bool:
+        return True
+
+    def _flush_moves(self) -> None:
+        """An accepted path's row copies go to every rank (each applies them to its own KV heads) before the next launch is announced."""
+        while self.moves:
+            part, self.moves = self.moves[:256], self.moves[256:]
+            self._send(OP_MOVES, len(part), moves=part)
+            self._host_writable()
+            self.h_moves[:len(part)] = torch.tensor(part, dtype=torch.int32)
+            self.d_moves[:len(part)].copy_(self.h_moves[:len(part)], non_blocking=True)
+            self._uploaded()
+            self.m.move_kv_rows(self.d_moves, len(part))
+            self.tree_moves += len(part)
+
     def step(self, reqs, candidates):
         return super().step(reqs, candidates)
 
     def _window(self, M, count, bucket):
-        self.ex.run_window_eager(M, count, bucket)
+        self.ex.run_window_eager(M, count, bucket, self._tree_n)
 
     def _capture(self, M, count, bucket):
         g = super()._capture(M, count, bucket)

@@ -190,7 +190,7 @@ class DenseTPShard:
         _lib.count()
 
     def phases(self, ids, positions, slots, row_seq, ctx_len, block_table, prefill=None, max_ctx=None, want_logits=True, logit_rows=None,
-               cand_count=None, leader=0):
+               cand_count=None, leader=0, tree=None):
         """Generator of closures, one per phase; calling them in order runs this rank's forward.  Between two phases every
         cross-rank dependency points backwards, so a loopback group may interleave the ranks phase by phase."""
         cfg, g, r, R = self.cfg, self.g, self.rank, self.R
@@ -212,19 +212,35 @@ class DenseTPShard:
         def p_start():
             _lib.check(Lib.rx_tp_bump_epoch(g.epoch_ptr(r), _lib.stream_ptr()), "rx_tp_bump_epoch")
             if prefill is None:
-                K.attn_plan(row_seq, ctx_len, self.nq, self.nkv, getattr(self, "window_seq_rows", 1), self.attn_plan)
+                K.attn_plan(row_seq, ctx_len, self.nq, self.nkv, getattr(self, "window_seq_rows", 1), self.attn_plan,
+                            tree_base=None if tree is None else tree[0])
             K.embed(ids, self.embed, h)
             K.norm_rot_in(h, self.layers[0]["attn_norm"], cfg.eps, self.layers[0]["qkv"].suh, xr0)
         yield p_start
 
         if prefill is None:
-            yield from self._window_phases(M, positions, slots, row_seq, ctx_len, block_table, max_ctx, h, q, xr_a, xr_f, xr0)
+            yield from self._window_phases(M, positions, slots, row_seq, ctx_len, block_table, max_ctx, h, q, xr_a, xr_f, xr0, tree)
         else:
             yield from self._prefill_phases(M, positions, slots, block_table, prefill, h, q, xr_a, xr_f, xr0)
         yield from self._head_phases(M, want_logits, logit_rows, cand_count, leader, prefill is None)
 
-    def _window_phases(self, M, positions, slots, row_seq, ctx_len, block_table, max_ctx, h, q, xr_a, xr_f, xr0):
-        """Decode / verify windows (rows <= 256): one-shot all-reduce after o_proj and down_proj, residual stream replicated."""
+    def supports_trees(self) -> bool:
+        return True
+
+    def _kv_ptr_table(self):
+        if getattr(self, "_kv_ptrs", None) is None:
+            self._kv_ptrs = torch.tensor([c.data_ptr() for kv in zip(self.k_cache, self.v_cache) for c in kv], dtype=torch.int64, device=self.device)
+        return self._kv_ptrs
+
+    def move_kv_rows(self, moves, n_moves: int) -> None:
+        """(source slot, destination slot, rows) copies over this rank's K and V caches of every layer (see DenseGPU.move_kv_rows)."""
+        c = self.k_cache[0]
+        K.kv_move_rows(self._kv_ptr_table(), c.shape[-1] * c.element_size(), self.nkv, moves, n_moves)
+
+    def _window_phases(self, M, positions, slots, row_seq, ctx_len, block_table, max_ctx, h, q, xr_a, xr_f, xr0, tree=None):
+        """Decode / verify windows (rows <= 256): one-shot all-reduce after o_proj and down_proj, residual stream replicated.
+        tree = (tree_base, vbt, row copies, count): a window of draft trees (see DenseGPU.forward_phases); the slots, private tables and copies
+        are the same on every rank, each rank applies them to its own KV heads."""
         cfg, g, r, R = self.cfg, self.g, self.rank, self.R
         from ..parallel.symm import AR_ROWS
         hd, d = cfg.head_dim, self.d
@@ -287,9 +303,12 @@ class DenseTPShard:
                 ksc = self.kv_scale[li] if self.kv_fp8 else None
                 K.finish_qkv_rope(self.part, s, M, self.nq, self.nkv, hd, L["qkv"], L["q_norm"], L["k_norm"], cfg.eps, positions, self.inv_freq,
                                   slots, q, self.k_cache[li], self.v_cache[li], ksc)
+                if tree is not None:
+                    c = self.k_cache[li]
+                    K.kv_move_rows(self._kv_ptr_table()[2 * li:2 * li + 2], c.shape[-1] * c.element_size(), self.nkv, tree[2], tree[3])
                 K.attn_decode(self.tk[li], self.tv[li], q, block_table, row_seq, ctx_len, self.attn_scratch, self.nq, self.nkv, hd,
                               max_ctx or self.max_ctx_alloc, scale, L["o"].suh, xr_a, None, self.status, ksc,
-                              max_seq_rows=getattr(self, "window_seq_rows", 1), plan=self.attn_plan)
+                              max_seq_rows=getattr(self, "window_seq_rows", 1), plan=self.attn_plan, vbt=None if tree is None else tree[1])
                 K.exl3_gemm(xr_a, L["o"], self.part, sp[("decode", "o")], self.status)
             yield p_attn
             a, b = chain(self.part, sp[("decode", "o")], L["o"], 0, u_o, L["ffn_norm"], L["gate_up"].suh)

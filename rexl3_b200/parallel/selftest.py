@@ -141,6 +141,65 @@ def _lead(be, cfg, w, ctx, streams: int = 3) -> int:
                 rc = 1
     st = be.stats()
     print(f"tp selftest: worst margin {worst:.5f}, graph replays {st['graph_replays']}, control bytes {be.ctrl_bytes}")
+    if rc == 0 and "--trees" in sys.argv:
+        rc = _lead_trees(be, cfg, prompts, out, new)
+    return rc
+
+
+def _lead_trees(be, cfg, prompts, serial: dict, new: int) -> int:
+    """Tree rounds over the tensor-parallel group: the same prompts again with verify windows of draft trees.  The drafter knows the run
+    above and hides the right token at a hashed rank of each level (or leaves it out), so accepted paths run through second and third
+    candidates - private pages, ancestor copies and path moves on every rank.  The tokens must equal the first run's, bit for bit."""
+    import hashlib
+    from ..engine import DraftOffer, Engine, Request, TreeConfig
+    from ..sampling import GREEDY
+    from ..spec.tree import Lattice
+    want = [serial[f"r{i}"] for i in range(len(prompts))]
+
+    def propose(asks):
+        offers = {}
+        for a in asks:
+            i = next(k for k, p in enumerate(prompts) if a.context[:len(p)] == p and len(a.context) - len(p) <= new)
+            g = len(a.context) - len(prompts[i])
+            ids = []
+            for j in range(a.max_drafts):
+                hsh = int.from_bytes(hashlib.blake2b(f"{i}.{g}.{j}".encode(), digest_size=8).digest(), "little")
+                cand = [(hsh >> (8 * k)) % cfg.vocab for k in range(1, 5)]
+                if g + j < len(want[i]) and hsh % 5 < 4:
+                    cand[hsh % 5] = want[i][g + j]
+                ids.append(cand)
+            offers[a.slot] = DraftOffer([c[0] for c in ids], [], Lattice(ids, [[3.0, 2.0, 1.0, 0.0]] * len(ids)))
+        return offers
+    if not be.supports_trees():
+        print("the tensor-parallel backend offers no tree windows", file=sys.stderr)
+        return 1
+    be.supports_native_draft = lambda: True
+    be.propose_batch = propose
+    eng = Engine(be, None, window_rows=64, prefill_chunk=256, spec="self", max_drafts=4, trees=TreeConfig(max_nodes=10))
+    for i, p in enumerate(prompts):
+        eng.submit(Request(f"t{i}", p, new, GREEDY))
+    got = {f"t{i}": [] for i in range(len(prompts))}
+    rc = 0
+    for _ in range(400):
+        if not eng.has_work():
+            break
+        for ev in eng.step():
+            if ev.kind == "tokens":
+                got[ev.id].extend(ev.tokens)
+            elif ev.kind == "error":
+                print("engine error (trees):", ev.message, file=sys.stderr)
+                rc = 1
+    be.sync_all()
+    for i in range(len(prompts)):
+        if got[f"t{i}"] != want[i]:
+            print(f"trees: sequence {i} gave {got[f't{i}']}, the serial run {want[i]}", file=sys.stderr)
+            rc = 1
+    st = be.stats()
+    if eng.counters.get("tree_rounds", 0) == 0 or eng.counters["accepted"] < 6 or st.get("tree_moves", 0) == 0:
+        print(f"trees: nothing was exercised ({eng.counters}, {st})", file=sys.stderr)
+        rc = 1
+    print(f"tp selftest trees: rounds {eng.counters.get('tree_rounds')}, accepted {eng.counters['accepted']}, path moves {st.get('tree_moves')}, "
+          f"row copies {st.get('tree_copies')}")
     return rc
 
 

@@ -184,7 +184,8 @@ def build(args):
             be = DenseTpBackend(shard, args.slots, ctx.ctrl, use_graphs=not args.no_graphs)
             prefix = PrefixIndex(CacheBudget(args.prefix_cache_mib << 20), block_tokens=dense.PAGE) if args.prefix_cache == "on" else None
             return Engine(be, None, window_rows=args.window_rows, prefill_chunk=args.prefill_chunk, spec="none" if args.no_drafts else args.spec,
-                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args))
+                          max_drafts=args.max_drafts, prefix=prefix, cache_namespace=cache_namespace(name, cfg, info, args), trees=_trees(args),
+                          budget_policy=args.spec_budget_policy)
 
         def make():
             with boot.phase("engine", backend=args.backend, ranks=world):

@@ -49,6 +49,16 @@ def test_tp_windows_above_the_packet_size_with_the_in_switch_sum():
     assert r.returncode == 0 and "TP_SELFTEST_OK ranks=2" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def test_tree_rounds_over_a_tensor_parallel_group():
+    """Verify windows of draft trees on 2 ranks: the tree arrays and the accepted paths' row copies reach every rank, tokens equal the chain-free run's."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 CUDA devices")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29553",
+           "-m", "rexl3_b200.parallel.selftest", "--trees"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_SELFTEST_OK" in r.stdout and "tp selftest trees" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
+
+
 @pytest.mark.parametrize("ranks", [2, 4])
 def test_token_all_to_all_over_gpus_equals_one_gpu(ranks):
     """Data-parallel rows + token all-to-all over NVLink peer memory, one process per GPU: every rank's logits on its own sequence equal
