@@ -331,8 +331,13 @@ class DenseGpuBackend(Backend):
             kw["embed_rows"] = embed_rows
         if pos3 is not None:
             kw["pos3"] = pos3
-        logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr,
-                                want_logits=bool(last_rows), **kw)
+        try:
+            logits = m.forward_rows(d[0, :M], d[1, :M], d[2, :M], d[3, :M], d[4, :M], self.d_bt, prefill=pf, logit_rows=lr,
+                                    want_logits=bool(last_rows), **kw)
+        except RuntimeError as e:
+            if type(e).__name__ != "CacheFull":
+                raise
+            raise BackendError(str(e), fatal=False)
         return self._read_candidates(logits, candidates) if last_rows else None
 
     # ------------------------------------------------------------------ decode / verify window
@@ -673,7 +678,13 @@ class DenseGpuBackend(Backend):
 
     def _run_window(self, M: int, count: int, bucket: int) -> None:
         if not self.use_graphs:
-            self._window(M, count, bucket)
+            try:
+                self._window(M, count, bucket)
+            except RuntimeError as e:
+                if type(e).__name__ != "CacheFull":
+                    raise
+                # paged experts: this window touches more experts of one layer than the slab has slots; the batch fails, the server lives
+                raise BackendError(str(e), fatal=False)
             return
         key = self._graph_key(M, count, bucket)
         g = self.graphs.get(key)
