@@ -158,3 +158,27 @@ def test_a_record_file_of_another_pack_is_rewritten(tmp_path):
     assert len(b) == len(a) and b != a and open(path + ".tag").read() == "pack-b"
     xp.write_records(moe.random_moe_weights(cfg, seed=1), path)                        # untagged caller: does not trust a tagged file
     assert open(path, "rb").read() == a and not __import__("os").path.exists(path + ".tag")
+
+
+@pytest.mark.gpu
+def test_a_window_that_needs_more_experts_than_slots_fails_its_batch_only(tmp_path):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from rexl3_b200.engine import BackendError, RowRequest
+    from rexl3_b200.engine.gpu_backend import DenseGpuBackend
+    cfg = moe.CONFIGS["test-moe"]
+    w = moe.random_moe_weights(cfg, seed=1)
+    lay = xp.write_records(w, str(tmp_path / "e.bin"))
+    rec = (lay.expert_bytes + ec.PAGE - 1) // ec.PAGE * ec.PAGE
+    m = moe.MoEGPU(w, expert_paging=dict(path=lay.path, budget_bytes=3 * rec + 1), num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4,
+                   max_prefill_rows=128)
+    be = DenseGpuBackend(m, max_slots=4)
+    rng = np.random.default_rng(0)
+    with pytest.raises(BackendError) as e:
+        be.prefill_slice(0, 0, rng.integers(0, cfg.vocab, size=100).tolist(), 4, True)        # 200 picks: all 8 experts of a layer, 3 slots
+    assert not e.value.fatal and "the slab holds 3" in str(e.value)
+    be.release(0)
+    out = be.prefill_slice(1, 0, [5], 4, True)             # one row picks 2 experts per layer: fits
+    assert out is not None and np.isfinite(out.values).all()
+    assert be.step([RowRequest(1, [7], 1)], 4)[0][0].ids.shape == (4,)
+    m.paged.close()
