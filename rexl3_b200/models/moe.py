@@ -33,17 +33,32 @@ class MoEConfig(DenseConfig):
     router_mode: str = "softmax"       # "softmax" (renormalised top-k) | "sigmoid_bias" (DeepSeek-V3: rank by score + bias)
     routed_scale: float = 1.0
     draft_layers: int = 4              # self-speculative draft depth
+    expert_act: str = "swiglu"         # "swiglu": down(silu(gate) * up), the stack holds gate | up; "relu2": down(relu(up)^2), no gate (the
+                                       # feed-forward of the Mamba2 hybrids' experts, reference crates/cuda/csrc/nemotron_moe.cu)
+
+    @property
+    def expert_up_width(self) -> int:
+        return self.expert_ffn * (2 if self.expert_act == "swiglu" else 1)
 
     def weight_params(self) -> int:
         attn = self.d_model * self.qkv_width + self.n_q * self.head_dim * self.d_model
-        ffn = self.n_experts * 3 * self.d_model * self.expert_ffn
+        ffn = self.n_experts * (3 if self.expert_act == "swiglu" else 2) * self.d_model * self.expert_ffn
         return (attn + ffn) * self.n_layers + self.vocab_padded * self.d_model
 
 
 CONFIGS["moe-spec-30b"] = MoEConfig(n_layers=48, d_model=2048, n_q=32, n_kv=4, head_dim=128, ffn=128, vocab=151936, eps=1e-6, rope_theta=1e6,
                                     bits=3.0, name="moe-spec-30b", n_experts=128, top_k=8, expert_ffn=768)
+CONFIGS["test-moe-relu2"] = MoEConfig(n_layers=2, d_model=256, n_q=4, n_kv=2, head_dim=128, ffn=128, vocab=1024, bits=3.0, name="test-moe-relu2",
+                                      n_experts=16, top_k=6, expert_ffn=128, draft_layers=1, expert_act="relu2", router_mode="sigmoid_bias")
 CONFIGS["test-moe"] = MoEConfig(n_layers=3, d_model=256, n_q=4, n_kv=2, head_dim=128, ffn=128, vocab=1024, bits=3.0, name="test-moe",
                                 n_experts=8, top_k=2, expert_ffn=128, draft_layers=1)
+
+
+def _expert_act(c: dict) -> str:
+    a = c.get("expert_act", "relu2" if c.get("mlp_hidden_act") == "relu2" else "swiglu")
+    if a not in ("swiglu", "relu2"):
+        raise ValueError(f"expert activation {a!r}: this executor runs swiglu and relu2 experts")
+    return a
 
 
 def config_from_dict(c: dict) -> MoEConfig:
@@ -60,7 +75,8 @@ def config_from_dict(c: dict) -> MoEConfig:
                      bits=float(q.get("bits", 3.0)), head_bits=q.get("head_bits"), codebook=q.get("codebook", "3inst"), name=c.get("name", "moe"),
                      n_experts=int(n_exp), top_k=int(c.get("num_experts_per_tok", 2)), expert_ffn=int(c.get("moe_intermediate_size", 128)),
                      router_mode=c.get("router_mode", "sigmoid_bias" if c.get("scoring_func") == "sigmoid" else "softmax"),
-                     routed_scale=float(c.get("routed_scaling_factor", 1.0)), draft_layers=int(c.get("draft_layers", 4)))
+                     routed_scale=float(c.get("routed_scaling_factor", 1.0)), draft_layers=int(c.get("draft_layers", 4)),
+                     expert_act=_expert_act(c))
 
 
 @dataclass
@@ -83,7 +99,7 @@ def random_moe_weights(cfg: MoEConfig, seed: int = 0) -> HostWeights:
         lay.router = _bf16_round(rng.normal(0, 1.0 / math.sqrt(d), size=(cfg.n_experts, d)))
         if cfg.router_mode == "sigmoid_bias":
             lay.router_bias = rng.normal(0, 0.1, size=cfg.n_experts).astype(np.float32)
-        lay.experts_gu = [random_linear(d, 2 * F, cfg.bits, rng, cfg.codebook, s_in) for _ in range(cfg.n_experts)]
+        lay.experts_gu = [random_linear(d, cfg.expert_up_width, cfg.bits, rng, cfg.codebook, s_in) for _ in range(cfg.n_experts)]
         lay.experts_down = [random_linear(F, d, cfg.bits, rng, cfg.codebook, 0.5 / math.sqrt(F)) for _ in range(cfg.n_experts)]
         w.layers.append(lay)
     w.final_norm = _bf16_round(1.0 + 0.1 * rng.normal(size=d))
@@ -146,7 +162,8 @@ class ReferenceMoE(ReferenceDense):
             for j in range(cfg.top_k):
                 e = int(ids[t, j])
                 gu = x[t] @ L["gu"][e]
-                out[t] += wts[t, j] * ((torch.nn.functional.silu(gu[:F]) * gu[F:]) @ L["down"][e])
+                act = torch.relu(gu) ** 2 if cfg.expert_act == "relu2" else torch.nn.functional.silu(gu[:F]) * gu[F:]
+                out[t] += wts[t, j] * (act @ L["down"][e])
         return h + out
 
 
@@ -258,7 +275,7 @@ class MoEGPU(DenseGPU):
                                     q_norm=None, k_norm=None,
                                     router=(torch.randn(cfg.n_experts, d, device=device, generator=g) / math.sqrt(d)).to(torch.bfloat16),
                                     router_bias=None if cfg.router_mode == "softmax" else 0.1 * torch.randn(cfg.n_experts, device=device, generator=g),
-                                    gu=stack(E, d, 2 * F, 1.0 / math.sqrt(d)), down=stack(E, F, d, 0.5 / math.sqrt(F))))
+                                    gu=stack(E, d, cfg.expert_up_width, 1.0 / math.sqrt(d)), down=stack(E, F, d, 0.5 / math.sqrt(F))))
         self.final_norm = norm()
         self.lm_head = lin(d, cfg.vocab_padded, 1.0 / math.sqrt(d))
         if cfg.vocab_padded != cfg.vocab:
@@ -287,7 +304,7 @@ class MoEGPU(DenseGPU):
         for cls, rows in (("decode", Rd * mult), ("prefill", R * mult)):
             decode = cls == "decode"
             # the grouped launch already spreads over experts: K splits only where a window has few pairs
-            s_gu = K.plan_splits(d, 2 * F, decode) if decode else 1
+            s_gu = K.plan_splits(d, cfg.expert_up_width, decode) if decode else 1
             s_dn = K.plan_splits(F, d, decode) if decode else 1
             s_gu, s_dn = max(1, min(s_gu, 4)), max(1, min(s_dn, 4))
             self.moe_splits[cls] = (s_gu, s_dn)
@@ -366,9 +383,10 @@ class MoEGPU(DenseGPU):
                                          self.xs.data_ptr(), st), "rx_moe_gather_rot")
         s_gu, s_dn = self.moe_splits[cls]
         self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows, cap)
-        _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), s_gu, cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
-                                         ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
-                                         self.xs2.data_ptr(), st), "rx_moe_swiglu_rot")
+        act_rot = Lib.rx_moe_relu2_rot if cfg.expert_act == "relu2" else Lib.rx_moe_swiglu_rot
+        _lib.check(act_rot(self.part.data_ptr(), s_gu, cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
+                           ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
+                           self.xs2.data_ptr(), st), "rx_moe_act_rot")
         self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows, cap)
         dst, ar, flags, ranks, rows_cap, epoch, use = self._combine_target(li, M)
         _lib.check(Lib.rx_moe_combine(self.part.data_ptr(), s_dn, cap, M, d, k, picks.data_ptr(), self.pick_w.data_ptr(),
@@ -407,9 +425,10 @@ class MoEGPU(DenseGPU):
                                          ctypes.c_void_p(gu.suh.data_ptr() - 2 * self.e_lo * gu.K), self.xs.data_ptr(), st), "rx_moe_gather_rot")
         s_gu, s_dn = self.moe_splits[cls]
         self._grouped_shifted(self.xs, gu, s_gu, max_tiles, tile_rows, cap)
-        _lib.check(Lib.rx_moe_swiglu_rot(self.part.data_ptr(), s_gu, cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
-                                         ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
-                                         self.xs2.data_ptr(), st), "rx_moe_swiglu_rot")
+        act_rot = Lib.rx_moe_relu2_rot if cfg.expert_act == "relu2" else Lib.rx_moe_swiglu_rot
+        _lib.check(act_rot(self.part.data_ptr(), s_gu, cap, F, self.expert_of_pos.data_ptr(), self.total.data_ptr(),
+                           ctypes.c_void_p(gu.svh.data_ptr() - 2 * self.e_lo * gu.N), ctypes.c_void_p(dn.suh.data_ptr() - 2 * self.e_lo * dn.K),
+                           self.xs2.data_ptr(), st), "rx_moe_act_rot")
         self._grouped_shifted(self.xs2, dn, s_dn, max_tiles, tile_rows, cap)
         _lib.check(Lib.rx_moe_a2a_return(self.part.data_ptr(), s_dn, cap, self.pair_of_pos.data_ptr(), self.expert_of_pos.data_ptr(), self.total.data_ptr(),
                                          ctypes.c_void_p(dn.svh.data_ptr() - 2 * self.e_lo * dn.N), ctypes.byref(desc), st), "rx_moe_a2a_return")

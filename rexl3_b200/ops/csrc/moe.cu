@@ -338,6 +338,41 @@ __global__ void moe_swiglu_rot_kernel(const float* __restrict__ part, int S, int
   }
 }
 
+// The same finish for experts WITHOUT a gate (the latent-MoE feed-forward of the Mamba2 hybrids: down(relu(up(x))^2), reference
+// crates/cuda/csrc/nemotron_moe.cu): part is f32 [S][pairs_cap][F] (the up projection alone), xs2 = H(relu(up)^2 * suh_down[e]).
+__global__ void moe_relu2_rot_kernel(const float* __restrict__ part, int S, int pairs_cap, int F, const int* __restrict__ expert_of_pos,
+                                     const int* __restrict__ total, const __half* __restrict__ svh_up, const __half* __restrict__ suh_down,
+                                     __half* __restrict__ xs2) {
+  pdl_launch();
+  pdl_wait();
+  const int pos = blockIdx.x;
+  if (pos >= *total) return;
+  const int e = expert_of_pos[pos];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const size_t plane = (size_t)pairs_cap * F;
+  for (int b = blockIdx.y * nw + warp; b < F / 128; b += gridDim.y * nw) {
+    const int n0 = b * 128 + lane * 4;
+    float u[4];
+    moe_finish_block(part, S, plane, (size_t)pos * F + n0, svh_up == nullptr ? nullptr : svh_up + (size_t)e * F + n0, u);
+    float s[4] = {1.f, 1.f, 1.f, 1.f};
+    if (suh_down != nullptr) {
+      const uint2 su = *reinterpret_cast<const uint2*>(suh_down + (size_t)e * F + n0);
+      const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+      s[0] = s01.x; s[1] = s01.y; s[2] = s23.x; s[3] = s23.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float r = fmaxf(u[i], 0.f);
+      u[i] = m_bf16_to_f(m_f_to_bf16(r * r)) * s[i];
+    }
+    if (suh_down != nullptr) fwht128_warp(u);
+    const __half2 a = __floats2half2_rn(u[0], u[1]), bb = __floats2half2_rn(u[2], u[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&bb);
+    *reinterpret_cast<uint2*>(xs2 + (size_t)pos * F + n0) = o;
+  }
+}
+
 struct CombineDst {
   int ranks, rank;
   float* dst[TP_MAX];            // f32 [ranks][rows_cap][d] on every rank (one rank: a local buffer)
@@ -610,6 +645,15 @@ RX_API int rx_moe_swiglu_rot(const void* part, int S, int pairs_cap, int F, cons
   if (warps > 8) warps = 8;
   return (int)rx::launch(moe_swiglu_rot_kernel, dim3(pairs_cap, 1), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, pairs_cap, F,
                          (const int*)expert_of_pos, (const int*)total, (const __half*)svh_gu, (const __half*)suh_down, (__half*)xs2);
+}
+
+RX_API int rx_moe_relu2_rot(const void* part, int S, int pairs_cap, int F, const void* expert_of_pos, const void* total, const void* svh_up,
+                            const void* suh_down, void* xs2, void* stream) {
+  if (pairs_cap < 1 || F % 128 != 0 || S < 1) return (int)cudaErrorInvalidValue;
+  int warps = F / 128;
+  if (warps > 8) warps = 8;
+  return (int)rx::launch(moe_relu2_rot_kernel, dim3(pairs_cap, 1), dim3(32 * warps), 0, (cudaStream_t)stream, (const float*)part, S, pairs_cap, F,
+                         (const int*)expert_of_pos, (const int*)total, (const __half*)svh_up, (const __half*)suh_down, (__half*)xs2);
 }
 
 RX_API int rx_moe_combine_desc_size() { return (int)sizeof(CombineDst); }

@@ -66,6 +66,7 @@ def _declare(lib):
         "rx_moe_plan": (c_int, [c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_gather_rot": (c_int, [c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_void]),
         "rx_moe_swiglu_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
+        "rx_moe_relu2_rot": (c_int, [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void]),
         "rx_moe_combine_desc_size": (c_int, []),
         "rx_moe_a2a_desc_size": (c_int, []),
         "rx_moe_a2a_dispatch": (c_int, [c_void, c_void, c_int, c_int, c_void, c_void, c_void]),

@@ -86,6 +86,7 @@ def write_moe_pack(folder: str, w: HostWeights) -> None:
                       "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps, "rope_theta": cfg.rope_theta, "qk_norm": cfg.qk_norm, "name": cfg.name,
                       "num_experts": cfg.n_experts, "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.expert_ffn,
                       "router_mode": cfg.router_mode, "routed_scaling_factor": cfg.routed_scale, "draft_layers": cfg.draft_layers,
+                      "expert_act": cfg.expert_act,
                       "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": cfg.bits, "head_bits": cfg.head_bits or cfg.bits,
                                               "codebook": cfg.codebook, "fused_projections": True}})
 

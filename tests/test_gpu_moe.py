@@ -42,10 +42,18 @@ def test_router_matches_reference(mode):
     torch.testing.assert_close(wts, rw, rtol=2e-3, atol=1e-5)
 
 
-def test_moe_model_matches_reference_prefill_and_decode():
+@pytest.mark.parametrize("act", ["swiglu", "relu2"])
+def test_moe_model_matches_reference_prefill_and_decode(act):
+    """`relu2`: experts without a gate, down(relu(up)^2), sixteen of them with six picks per token under the sigmoid router."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
-    cfg, w, moe = _setup()
+    if act == "swiglu":
+        cfg, w, moe = _setup()
+    else:
+        from rexl3_b200.models import moe
+        cfg = moe.CONFIGS["test-moe-relu2"]
+        w = moe.random_moe_weights(cfg, seed=3)
+        assert w.layers[0].experts_gu[0].svh.shape[0] == cfg.expert_ffn
     ref = moe.ReferenceMoE(w, device="cuda")
     # prefill scratch larger than the decode class: the two classes address the sorted-pair buffers with different strides
     m = moe.MoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=1024)

@@ -113,3 +113,16 @@ def test_pack_round_trips_the_multi_token_prediction_block(tmp_path):
     assert float((ma - mb).abs().max()) == 0.0
     fam, plan = registry.probe(str(tmp_path))
     assert fam.id == "dense" and "mtp_head" in plan.components and plan.drafters[0] == "mtp" and plan.tp_max == 1
+
+
+def test_moe_pack_keeps_the_expert_activation(tmp_path):
+    from rexl3_b200.models import moe
+    from rexl3_b200.quant import packs
+    cfg = moe.CONFIGS["test-moe-relu2"]
+    w = moe.random_moe_weights(cfg, seed=2)
+    packs.write_moe_pack(str(tmp_path), w)
+    back = packs.load_any(str(tmp_path))
+    assert back.cfg.expert_act == "relu2" and back.cfg.router_mode == "sigmoid_bias" and back.cfg.expert_up_width == cfg.expert_ffn
+    assert back.layers[1].experts_gu[3].trellis.shape == w.layers[1].experts_gu[3].trellis.shape
+    import numpy as np
+    assert np.array_equal(back.layers[1].experts_gu[3].trellis, w.layers[1].experts_gu[3].trellis)
