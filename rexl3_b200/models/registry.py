@@ -20,6 +20,7 @@ BUILT_COMPONENTS = frozenset({
     "exl3_linear", "gqa_attention", "rope", "qk_norm", "swiglu_ffn", "paged_kv_bf16", "paged_kv_fp8", "paged_kv_int8", "paged_kv_q4", "mla_attention", "moe_softmax_topk",
     "moe_sigmoid_bias_topk", "mxfp4_experts", "shared_expert", "mamba2_mixer", "gated_delta_net", "kimi_delta_attention", "self_speculative_draft",
     "copy_draft", "ngram_draft", "prefix_cache", "tensor_parallel", "expert_parallel", "mtp_head", "vision_tower", "mrope", "sparse_indexer",
+    "relu2_experts", "draft_trees", "expert_paging", "image_ingress",
 })
 
 
@@ -279,8 +280,8 @@ PROBE_ONLY = (
                      "vision tower"],
                     "the mapping of this family's own tensor names onto the hybrid executor, the DFlash2 drafter and the MoE variant's composition"),
     ProbeOnlyFamily("nemotron_h_omni", ("NemotronHOmniForConditionalGeneration", "NemotronHForCausalLM"), ("nemotron_h_omni", "nemotron_h"),
-                    ["mamba2_mixer", "gqa_attention (NoPE)", "paged_kv_int8", "vision tower"],
-                    "the latent-MoE feed-forward (relu^2, top-22), its MTP head and the audio / video towers"),
+                    ["mamba2_mixer", "gqa_attention (NoPE)", "paged_kv_int8", "vision tower", "relu2_experts (gate-free experts in the MoE executor)"],
+                    "the latent projections around the latent-MoE feed-forward and its composition with the Mamba2 hybrid, its MTP head and the audio / video towers"),
 )
 
 FAMILIES = (DenseFamily(), HybridFamily(), MoEFamily(), MlaMoEFamily(), MimoFamily()) + PROBE_ONLY
