@@ -49,6 +49,8 @@ class MlaConfig:
     expert_ffn: int = 2048
     shared_ffn: int = 2048
     routed_scale: float = 2.5
+    n_group: int = 0           # group-limited routing (DeepSeek-V3: 8 groups, a token keeps its 4 best); 0 = every expert competes
+    topk_group: int = 0
     vocab: int = 129280
     eps: float = 1e-6
     rope_theta: float = 1e4
@@ -89,6 +91,7 @@ def config_from_dict(c: dict) -> MlaConfig:
                     nope_dim=int(c.get("qk_nope_head_dim", 128)), v_dim=int(c.get("v_head_dim", 128)), dense_ffn=int(c.get("intermediate_size", 18432)),
                     n_experts=int(c.get("n_routed_experts", 256)), top_k=int(c.get("num_experts_per_tok", 8)), expert_ffn=int(c.get("moe_intermediate_size", 2048)),
                     shared_ffn=int(c.get("moe_intermediate_size", 2048)) * int(c.get("n_shared_experts", 1)), routed_scale=float(c.get("routed_scaling_factor", 2.5)),
+                    n_group=int(c.get("n_group", 0) or 0), topk_group=int(c.get("topk_group", 0) or 0),
                     vocab=c["vocab_size"], eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e4), bits_a=float(q.get("bits_a", 2.0)),
                     bits_b=float(q.get("bits_b", 2.5)), name=c.get("name", "mla-moe"), dsa=bool(c.get("index_topk")) and bool(c.get("index_kpool", 4)),
                     dsa_sel_pools=int(c.get("index_topk", 2048)) // DSA_P, dsa_dense_below=int(c.get("index_dense_below", c.get("index_topk", 2048))))
@@ -284,7 +287,7 @@ class ReferenceMla:
             y = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ L["down"]
             if L["router"] is not None:
                 mc = _RouteCfg(cfg)
-                ids_e, wts = route_reference(x @ L["router"].T, mc, L["router_bias"])
+                ids_e, wts = route_reference(x @ L["router"].T, mc, L["router_bias"], cfg.n_group, cfg.topk_group)
                 Fe = cfg.expert_ffn
                 for t in range(T):
                     for j in range(cfg.top_k):
@@ -662,8 +665,13 @@ class MlaMoEGPU:
             pairs, cap = M * k, self.pairs_cap[cls]
             tile_rows = (16 if M <= 16 else 32) if cls == "decode" else 128
             mt = self.max_tiles[cls]
-            _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
-                                          self.router_logits.data_ptr(), self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st()), "rx_moe_router2")
+            if cfg.n_group > 1 and 0 < cfg.topk_group < cfg.n_group:
+                _lib.check(Lib.rx_moe_router_grouped(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
+                                                     cfg.n_group, cfg.topk_group, self.router_logits.data_ptr(), self.pick_ids.data_ptr(),
+                                                     self.pick_w.data_ptr(), st()), "rx_moe_router_grouped")
+            else:
+                _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), L["router_bias"].data_ptr(), M, d, E, k, 1, cfg.routed_scale,
+                                              self.router_logits.data_ptr(), self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st()), "rx_moe_router2")
             picks, En, e_lo, e_hi = self.pick_ids, E, self.e_lo, self.e_hi
             if self.paged is not None:
                 # the picks come to the host (every kernel queued so far has then run: the last call's leases can go), the experts they name

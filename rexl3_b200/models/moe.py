@@ -33,6 +33,8 @@ class MoEConfig(DenseConfig):
     router_mode: str = "softmax"       # "softmax" (renormalised top-k) | "sigmoid_bias" (DeepSeek-V3: rank by score + bias)
     routed_scale: float = 1.0
     draft_layers: int = 4              # self-speculative draft depth
+    n_group: int = 0                   # group-limited routing: experts in `n_group` groups, a row keeps its `topk_group` best groups (0: off)
+    topk_group: int = 0
     expert_act: str = "swiglu"         # "swiglu": down(silu(gate) * up), the stack holds gate | up; "relu2": down(relu(up)^2), no gate (the
                                        # feed-forward of the Mamba2 hybrids' experts, reference crates/cuda/csrc/nemotron_moe.cu)
 
@@ -76,7 +78,7 @@ def config_from_dict(c: dict) -> MoEConfig:
                      n_experts=int(n_exp), top_k=int(c.get("num_experts_per_tok", 2)), expert_ffn=int(c.get("moe_intermediate_size", 128)),
                      router_mode=c.get("router_mode", "sigmoid_bias" if c.get("scoring_func") == "sigmoid" else "softmax"),
                      routed_scale=float(c.get("routed_scaling_factor", 1.0)), draft_layers=int(c.get("draft_layers", 4)),
-                     expert_act=_expert_act(c))
+                     expert_act=_expert_act(c), n_group=int(c.get("n_group", 0) or 0), topk_group=int(c.get("topk_group", 0) or 0))
 
 
 @dataclass
@@ -155,7 +157,7 @@ class ReferenceMoE(ReferenceDense):
     def _ffn(self, li, L, h):
         cfg = self.cfg
         x = self._rms(h, L["ffn_norm"], cfg.eps)
-        ids, wts = route_reference(x @ L["router"].T, cfg, L["router_bias"])
+        ids, wts = route_reference(x @ L["router"].T, cfg, L["router_bias"], cfg.n_group, cfg.topk_group)
         F = cfg.expert_ffn
         out = torch.zeros_like(h)
         for t in range(x.shape[0]):
@@ -353,9 +355,14 @@ class MoEGPU(DenseGPU):
         cap = self.pairs_cap[cls]
         xn = self.xn[:M]
         K.finish_add_norm_rot(self.part, s_o, M, L["o"], h, L["ffn_norm"], cfg.eps, None, None, xn_out=xn)
-        _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
-                                      0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, self.router_logits.data_ptr(),
-                                      self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st), "rx_moe_router2")
+        if cfg.n_group > 1 and 0 < cfg.topk_group < cfg.n_group:
+            _lib.check(Lib.rx_moe_router_grouped(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
+                                                 0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, cfg.n_group, cfg.topk_group,
+                                                 self.router_logits.data_ptr(), self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st), "rx_moe_router_grouped")
+        else:
+            _lib.check(Lib.rx_moe_router2(xn.data_ptr(), L["router"].data_ptr(), _lib.ptr(L["router_bias"]), M, d, E, k,
+                                          0 if cfg.router_mode == "softmax" else 1, cfg.routed_scale, self.router_logits.data_ptr(),
+                                          self.pick_ids.data_ptr(), self.pick_w.data_ptr(), st), "rx_moe_router2")
         if cls == "decode":
             tile_rows, max_tiles = (16 if M <= 16 else 32), self.max_tiles_decode
         else:

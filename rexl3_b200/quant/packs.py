@@ -86,7 +86,7 @@ def write_moe_pack(folder: str, w: HostWeights) -> None:
                       "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps, "rope_theta": cfg.rope_theta, "qk_norm": cfg.qk_norm, "name": cfg.name,
                       "num_experts": cfg.n_experts, "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.expert_ffn,
                       "router_mode": cfg.router_mode, "routed_scaling_factor": cfg.routed_scale, "draft_layers": cfg.draft_layers,
-                      "expert_act": cfg.expert_act,
+                      "expert_act": cfg.expert_act, "n_group": cfg.n_group, "topk_group": cfg.topk_group,
                       "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": cfg.bits, "head_bits": cfg.head_bits or cfg.bits,
                                               "codebook": cfg.codebook, "fused_projections": True}})
 
@@ -124,7 +124,7 @@ def write_mla_pack(folder: str, w) -> None:
                       "kv_lora_rank": cfg.kv_lora, "qk_rope_head_dim": cfg.rope_dim, "qk_nope_head_dim": cfg.nope_dim, "v_head_dim": cfg.v_dim,
                       "intermediate_size": cfg.dense_ffn, "n_routed_experts": cfg.n_experts, "num_experts_per_tok": cfg.top_k,
                       "moe_intermediate_size": cfg.expert_ffn, "n_shared_experts": max(1, cfg.shared_ffn // cfg.expert_ffn), "scoring_func": "sigmoid",
-                      "topk_method": "noaux_tc", "routed_scaling_factor": cfg.routed_scale, "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps,
+                      "topk_method": "noaux_tc", "n_group": cfg.n_group, "topk_group": cfg.topk_group, "routed_scaling_factor": cfg.routed_scale, "vocab_size": cfg.vocab, "rms_norm_eps": cfg.eps,
                       "rope_theta": cfg.rope_theta, "name": cfg.name,
                       "quantization_config": {"quant_method": "exl3", "version": "0.0.1", "bits": 2.25, "bits_a": cfg.bits_a, "bits_b": cfg.bits_b,
                                               "expert_format": "mxfp4"}})

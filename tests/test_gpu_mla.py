@@ -10,11 +10,16 @@ def _i32(x):
     return torch.tensor(x, dtype=torch.int32, device="cuda")
 
 
-def test_mla_moe_model_matches_reference():
+@pytest.mark.parametrize("grouped", [False, True])
+def test_mla_moe_model_matches_reference(grouped):
+    """grouped: group-limited routing (8 experts in 4 groups, a token keeps its 2 best groups), as the DeepSeek-V3 router has it."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
+    import dataclasses
     from rexl3_b200.models import mla
     cfg = mla.CONFIGS["test-mla"]
+    if grouped:
+        cfg = dataclasses.replace(cfg, n_group=4, topk_group=2, name="test-mla-grouped")
     w = mla.random_mla_weights(cfg, seed=2)
     ref = mla.ReferenceMla(w, device="cuda")
     m = mla.MlaMoEGPU(w, num_pages=16, max_rows=64, max_seqs=4, max_blocks_per_seq=4, max_prefill_rows=512)

@@ -42,13 +42,15 @@ def test_router_matches_reference(mode):
     torch.testing.assert_close(wts, rw, rtol=2e-3, atol=1e-5)
 
 
-@pytest.mark.parametrize("act", ["swiglu", "relu2"])
+@pytest.mark.parametrize("act", ["swiglu", "relu2", "grouped"])
 def test_moe_model_matches_reference_prefill_and_decode(act):
     """`relu2`: experts without a gate, down(relu(up)^2), sixteen of them with six picks per token under the sigmoid router."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     if act == "swiglu":
         cfg, w, moe = _setup()
+    elif act == "grouped":          # group-limited routing in the executor: 16 experts in 4 groups, a token keeps its 2 best groups
+        cfg, w, moe = _setup(n_experts=16, top_k=4, router_mode="sigmoid_bias", routed_scale=2.5, n_group=4, topk_group=2)
     else:
         from rexl3_b200.models import moe
         cfg = moe.CONFIGS["test-moe-relu2"]

@@ -126,3 +126,17 @@ def test_moe_pack_keeps_the_expert_activation(tmp_path):
     assert back.layers[1].experts_gu[3].trellis.shape == w.layers[1].experts_gu[3].trellis.shape
     import numpy as np
     assert np.array_equal(back.layers[1].experts_gu[3].trellis, w.layers[1].experts_gu[3].trellis)
+
+
+def test_group_limited_routing_keys_round_trip(tmp_path):
+    import dataclasses
+    from rexl3_b200.models import mla, moe
+    from rexl3_b200.quant import packs
+    cfg = dataclasses.replace(moe.CONFIGS["test-moe"], n_experts=16, top_k=4, router_mode="sigmoid_bias", n_group=4, topk_group=2)
+    packs.write_moe_pack(str(tmp_path / "a"), moe.random_moe_weights(cfg, seed=2))
+    back = packs.load_any(str(tmp_path / "a")).cfg
+    assert (back.n_group, back.topk_group) == (4, 2)
+    mc = dataclasses.replace(mla.CONFIGS["test-mla"], n_group=4, topk_group=2)
+    packs.write_mla_pack(str(tmp_path / "b"), mla.random_mla_weights(mc, seed=2))
+    back = packs.load_any(str(tmp_path / "b")).cfg
+    assert (back.n_group, back.topk_group) == (4, 2)
